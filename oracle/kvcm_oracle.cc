@@ -1,0 +1,465 @@
+// CPU oracle for the KVCM hot path.  TEST INFRASTRUCTURE ONLY.
+//
+// This file restates, on the CPU, the algorithms of alibaba/tair-kvcache that the
+// CUDA library replaces.  It exists to check the CUDA results and to be timed as the
+// CPU baseline; the product never links, loads or calls it.  Every function names the
+// reference file:line it follows.
+//
+// Parity pins:
+//   * hash chain      - checked against the reference's own header compiled as-is
+//                       (oracle/_ref/libkvcm_ref_hash.so, built by oracle/Makefile) and
+//                       against tests/golden/hash_kat.json generated from that build.
+//   * prefix / SW / batch-get match - checked against the known-answer tables of the
+//                       reference's unit tests (tests/golden/match_kat.json).
+//   * gather/scatter  - checked against the index rule of the reference's Triton
+//                       kernels restated as Python loops in its own test file.
+//   * CRC-32          - checked against the three known answers of the reference's test.
+//
+// Build: make -C oracle   (g++ -O2 -shared -fPIC -pthread)
+
+#include <algorithm>
+#include <atomic>
+#include <cstdint>
+#include <cstring>
+#include <functional>
+#include <thread>
+#include <unordered_map>
+#include <vector>
+
+namespace {
+
+// ---------------------------------------------------------------------------------
+// helpers
+// ---------------------------------------------------------------------------------
+template <class F>
+void ParallelFor(int64_t n, int threads, F &&body) {
+    if (threads <= 1 || n <= 1) {
+        for (int64_t i = 0; i < n; ++i) body(i);
+        return;
+    }
+    std::atomic<int64_t> next{0};
+    std::vector<std::thread> pool;
+    pool.reserve(threads);
+    for (int t = 0; t < threads; ++t) {
+        pool.emplace_back([&] {
+            // small dynamic chunks: request lengths are ragged
+            for (;;) {
+                int64_t i = next.fetch_add(1, std::memory_order_relaxed);
+                if (i >= n) break;
+                body(i);
+            }
+        });
+    }
+    for (auto &th : pool) th.join();
+}
+
+// kv_cache_manager/manager/hash_util.h:8-12 (hashInt64Func).  std::hash<int64_t> is the
+// identity in libstdc++, the reference's toolchain.  The signed shifts of the original
+// are written out on unsigned words so that nothing here is undefined behaviour:
+// `hash << 12` keeps the low 64 bits, `hash >> 32` is an arithmetic (sign-extending) shift.
+inline int64_t HashStep(int64_t hash, int64_t value) {
+    const uint64_t h = static_cast<uint64_t>(hash);
+    const uint64_t sra32 = static_cast<uint64_t>(hash >> 32);  // arithmetic on gcc
+    const uint64_t mixed = static_cast<uint64_t>(value) + 0x9e3779b97f4a7c15ULL + (h << 12) + sra32;
+    return static_cast<int64_t>(h ^ mixed);
+}
+
+// One location of a block: kv_cache_manager/manager/cache_location.h:44-50 (status),
+// kv_cache_manager/data_storage/storage_config.h:8-13 (storage type).
+struct Loc {
+    int32_t status;
+    int32_t type;
+};
+
+// kv_cache_manager/meta/meta_local_backend.h:60 keeps an unordered_map keyed by the int64
+// block key; the value's "__uri__" field is the JSON of the location map.  Here the value
+// is the decoded location list; an entry with zero locations models an empty location map.
+struct OracleIndex {
+    std::unordered_map<int64_t, std::vector<Loc>> table;
+};
+
+// kv_cache_manager/manager/select_location_policy.cc:40-48 (StaticWeightSLPolicy::GetWeight):
+// weight = table[type] when type indexes the table, else DEFAULT (1).
+inline uint32_t Weight(int32_t type, const uint32_t *weights, int n_weights) {
+    if (type >= 0 && type < n_weights) return weights[type];
+    return 1u;
+}
+
+// kv_cache_manager/manager/select_location_policy.cc:8-27 (SelectForMatch != nullptr):
+// some location is CLS_SERVING (3) and has weight > 0.
+inline bool Servable(const std::vector<Loc> &locs, const uint32_t *weights, int n_weights) {
+    for (const Loc &l : locs) {
+        if (l.status == 3 && Weight(l.type, weights, n_weights) > 0) return true;
+    }
+    return false;
+}
+
+// kv_cache_manager/manager/select_location_policy.cc:29-38 (ExistsForWrite).
+inline bool ExistsForWrite(const std::vector<Loc> &locs, const uint32_t *weights, int n_weights) {
+    for (const Loc &l : locs) {
+        if (l.status != 0 && Weight(l.type, weights, n_weights) > 0) return true;
+    }
+    return false;
+}
+
+// kv_cache_manager/manager/cache_location.cc:9-21 (IsIndexInMaskRange).
+// mask_kind 0: bool vector (mask_vec, mask_len); 1: offset (mask_off).
+inline bool Masked(int mask_kind, const uint8_t *mask_vec, int64_t mask_len, int64_t mask_off, int64_t i) {
+    if (mask_kind == 0) return i < mask_len ? mask_vec[i] != 0 : false;
+    return i < mask_off;
+}
+
+// The per-key outcome of MetaIndexer::Get as the matchers see it
+// (kv_cache_manager/meta/meta_indexer.cc:695-698,735-738): a missing key and a key whose
+// "__uri__" is empty both read as EC_NOENT.  The oracle stores decoded location lists, so
+// only a missing key is EC_NOENT; an existing key with an empty list is EC_OK with an
+// empty location map (meta_searcher.cc:99-103 then stops the prefix match).
+inline const std::vector<Loc> *Get(const OracleIndex *ix, int64_t key) {
+    auto it = ix->table.find(key);
+    return it == ix->table.end() ? nullptr : &it->second;
+}
+
+// kv_cache_manager/manager/meta_searcher.cc:120-145 + 74-118 (PrefixMatch).
+int64_t PrefixMatchOne(const OracleIndex *ix, const int64_t *keys, int64_t n, int mask_kind,
+                       const uint8_t *mask_vec, int64_t mask_len, int64_t mask_off, const uint32_t *w, int nw) {
+    std::vector<int64_t> query;
+    query.reserve(n);
+    for (int64_t i = 0; i < n; ++i) {
+        if (!Masked(mask_kind, mask_vec, mask_len, mask_off, i)) query.push_back(keys[i]);
+    }
+    int64_t len = 0;
+    for (int64_t k : query) {
+        const std::vector<Loc> *locs = Get(ix, k);
+        if (locs == nullptr) break;           // Get != EC_OK
+        if (locs->empty()) break;             // location_map.empty()
+        if (!Servable(*locs, w, nw)) break;   // SelectForMatch == nullptr
+        ++len;
+    }
+    return len;
+}
+
+// kv_cache_manager/manager/meta_searcher.cc:196-265 (ReverseRollSlideWindowMatch), kept in
+// its two phases: existence over the whole window first, then the servable predicate.
+int64_t SwMatchOne(const OracleIndex *ix, const int64_t *keys, int64_t n, int64_t sw, const uint32_t *w, int nw) {
+    for (int64_t base = n - sw; base >= 0;) {
+        bool is_match = false;
+        for (int64_t off = 0; off < sw; ++off) {
+            if (Get(ix, keys[base + off]) == nullptr) {
+                base -= sw - off;
+                is_match = false;
+                break;
+            }
+            is_match = true;
+        }
+        if (!is_match) continue;
+        for (int64_t off = 0; off < sw; ++off) {
+            const std::vector<Loc> *locs = Get(ix, keys[base + off]);
+            if (locs->empty() || !Servable(*locs, w, nw)) {
+                base -= sw - off;
+                is_match = false;
+                break;
+            }
+        }
+        if (is_match) return base;
+    }
+    return -1;
+}
+
+}  // namespace
+
+extern "C" {
+
+// ---------------------------------------------------------------------------------
+// (2a) chained block hash
+// ---------------------------------------------------------------------------------
+
+int64_t kvcm_oracle_hash_step(int64_t hash, int64_t value) { return HashStep(hash, value); }
+
+// kv_cache_manager/manager/cache_manager.cc:76-87 (GenKeyVector): n = tokens/block_size keys,
+// the state is carried across blocks, the trailing partial block is dropped.
+int64_t kvcm_oracle_gen_key_vector_i64(const int64_t *tokens, int64_t n_tokens, int64_t block_size, int64_t *keys) {
+    if (block_size <= 0) return 0;
+    const int64_t total_blocks = n_tokens / block_size;
+    int64_t hash = 0;
+    for (int64_t b = 0; b < total_blocks; ++b) {
+        const int64_t *p = tokens + b * block_size;
+        for (int64_t t = 0; t < block_size; ++t) hash = HashStep(hash, p[t]);
+        keys[b] = hash;
+    }
+    return total_blocks;
+}
+
+// Same loop over uint32 token ids, zero-extended to the int64 the wire format carries
+// (kv_cache_manager/protocol/protobuf/meta_service.proto:199).
+int64_t kvcm_oracle_gen_key_vector_u32(const uint32_t *tokens, int64_t n_tokens, int64_t block_size, int64_t *keys) {
+    if (block_size <= 0) return 0;
+    const int64_t total_blocks = n_tokens / block_size;
+    int64_t hash = 0;
+    for (int64_t b = 0; b < total_blocks; ++b) {
+        const uint32_t *p = tokens + b * block_size;
+        for (int64_t t = 0; t < block_size; ++t) hash = HashStep(hash, static_cast<int64_t>(p[t]));
+        keys[b] = hash;
+    }
+    return total_blocks;
+}
+
+// kv_cache_manager/optimizer/trace_converter/trace_util.cc:47-56 (ApplyPrefixHash): one key per id.
+void kvcm_oracle_apply_prefix_hash(const int64_t *ids, int64_t n, int64_t *keys) {
+    int64_t hash = 0;
+    for (int64_t i = 0; i < n; ++i) {
+        hash = HashStep(hash, ids[i]);
+        keys[i] = hash;
+    }
+}
+
+// Batch of requests in CSR form: request r owns tokens[tok_off[r], tok_off[r+1]) and writes
+// keys[key_off[r], key_off[r] + len/block_size).  One GenKeyVector per request.
+void kvcm_oracle_hash_blocks_u32(const uint32_t *tokens, const int64_t *tok_off, int64_t n_req, int64_t block_size,
+                                 int64_t *keys, const int64_t *key_off, int threads) {
+    ParallelFor(n_req, threads, [&](int64_t r) {
+        kvcm_oracle_gen_key_vector_u32(tokens + tok_off[r], tok_off[r + 1] - tok_off[r], block_size, keys + key_off[r]);
+    });
+}
+
+void kvcm_oracle_hash_blocks_i64(const int64_t *tokens, const int64_t *tok_off, int64_t n_req, int64_t block_size,
+                                 int64_t *keys, const int64_t *key_off, int threads) {
+    ParallelFor(n_req, threads, [&](int64_t r) {
+        kvcm_oracle_gen_key_vector_i64(tokens + tok_off[r], tok_off[r + 1] - tok_off[r], block_size, keys + key_off[r]);
+    });
+}
+
+// ---------------------------------------------------------------------------------
+// (2b) block index + matchers
+// ---------------------------------------------------------------------------------
+
+void *kvcm_oracle_index_create() { return new OracleIndex(); }
+void kvcm_oracle_index_destroy(void *h) { delete static_cast<OracleIndex *>(h); }
+int64_t kvcm_oracle_index_size(void *h) { return static_cast<int64_t>(static_cast<OracleIndex *>(h)->table.size()); }
+void kvcm_oracle_index_reserve(void *h, int64_t n) { static_cast<OracleIndex *>(h)->table.reserve(n); }
+
+// Replace the location list of each key: key i owns statuses/types[loc_off[i], loc_off[i+1]).
+void kvcm_oracle_index_put(void *h, const int64_t *keys, int64_t n, const int64_t *loc_off, const int32_t *statuses,
+                           const int32_t *types) {
+    auto *ix = static_cast<OracleIndex *>(h);
+    for (int64_t i = 0; i < n; ++i) {
+        std::vector<Loc> locs;
+        for (int64_t j = loc_off[i]; j < loc_off[i + 1]; ++j) locs.push_back({statuses[j], types[j]});
+        ix->table[keys[i]] = std::move(locs);
+    }
+}
+
+// Every key gets one location of the given status and storage type.
+void kvcm_oracle_index_put_uniform(void *h, const int64_t *keys, int64_t n, int32_t status, int32_t type) {
+    auto *ix = static_cast<OracleIndex *>(h);
+    for (int64_t i = 0; i < n; ++i) ix->table[keys[i]] = std::vector<Loc>{{status, type}};
+}
+
+void kvcm_oracle_index_erase(void *h, const int64_t *keys, int64_t n) {
+    auto *ix = static_cast<OracleIndex *>(h);
+    for (int64_t i = 0; i < n; ++i) ix->table.erase(keys[i]);
+}
+
+// Prefix match of one request; returns the matched length in keys (of the unmasked keys).
+int64_t kvcm_oracle_prefix_match(void *h, const int64_t *keys, int64_t n, int mask_kind, const uint8_t *mask_vec,
+                                 int64_t mask_len, int64_t mask_off, const uint32_t *weights, int n_weights) {
+    return PrefixMatchOne(static_cast<OracleIndex *>(h), keys, n, mask_kind, mask_vec, mask_len, mask_off, weights,
+                          n_weights);
+}
+
+// Sliding-window match of one request.  *base_out = start of the rightmost fully servable
+// window of `sw` keys, or -1.  Return value follows the guard of
+// kv_cache_manager/manager/cache_manager.cc:993-997: EC_BADARGS (6) when n < sw or sw < 0.
+// sw == 0 never terminates in the reference (meta_searcher.cc:218-229 makes no progress);
+// the oracle rejects it with EC_BADARGS as the replacement must.
+int32_t kvcm_oracle_sw_match(void *h, const int64_t *keys, int64_t n, int64_t sw, const uint32_t *weights,
+                             int n_weights, int64_t *base_out) {
+    *base_out = -1;
+    if (sw <= 0 || n < sw) return 6;
+    *base_out = SwMatchOne(static_cast<OracleIndex *>(h), keys, n, sw, weights, n_weights);
+    return 0;
+}
+
+// kv_cache_manager/manager/meta_searcher.cc:147-194 (BatchGetBestLocation) and
+// kv_cache_manager/manager/cache_manager.cc:589-635 (what FilterWriteCache reads from
+// BatchGetLocation).  flags[i]: bit0 servable (a location would be returned), bit1 key
+// exists, bit2 location map non-empty, bit3 ExistsForWrite.
+void kvcm_oracle_batch_get(void *h, const int64_t *keys, int64_t n, const uint32_t *weights, int n_weights,
+                           uint8_t *flags) {
+    auto *ix = static_cast<OracleIndex *>(h);
+    for (int64_t i = 0; i < n; ++i) {
+        const std::vector<Loc> *locs = Get(ix, keys[i]);
+        uint8_t f = 0;
+        if (locs != nullptr) {
+            f |= 2;
+            if (!locs->empty()) f |= 4;
+            if (Servable(*locs, weights, n_weights)) f |= 1;
+            if (ExistsForWrite(*locs, weights, n_weights)) f |= 8;
+        }
+        flags[i] = f;
+    }
+}
+
+// kv_cache_manager/manager/cache_manager.cc:589-635 (FilterWriteCache).  Returns 1 when the
+// result is an offset mask (*offset_out = first key without a writable location), 0 when it
+// is a bool vector (mask_out[i] = location map non-empty).  n_new_out = number of keys that
+// still have to be written.
+int32_t kvcm_oracle_filter_write(void *h, const int64_t *keys, int64_t n, const uint32_t *weights, int n_weights,
+                                 int64_t *offset_out, uint8_t *mask_out, int64_t *n_new_out) {
+    auto *ix = static_cast<OracleIndex *>(h);
+    std::vector<uint8_t> exists(n), nonempty(n);
+    for (int64_t i = 0; i < n; ++i) {
+        const std::vector<Loc> *locs = Get(ix, keys[i]);
+        exists[i] = locs != nullptr && ExistsForWrite(*locs, weights, n_weights);
+        nonempty[i] = locs != nullptr && !locs->empty();
+    }
+    int64_t first_empty = 0;
+    while (first_empty < n && exists[first_empty]) ++first_empty;
+    bool only_prefix = true;
+    for (int64_t i = first_empty; i < n; ++i) only_prefix = only_prefix && !exists[i];
+    if (only_prefix) {
+        *offset_out = first_empty;
+        *n_new_out = n - first_empty;
+        return 1;
+    }
+    int64_t n_new = 0;
+    for (int64_t i = 0; i < n; ++i) {
+        mask_out[i] = nonempty[i];
+        if (!nonempty[i]) ++n_new;
+    }
+    *offset_out = -1;
+    *n_new_out = n_new;
+    return 0;
+}
+
+// Batched matchers over CSR keys (request r owns keys[key_off[r], key_off[r+1])).
+// mask_off may be null (nothing masked); otherwise request r masks its first mask_off[r] keys
+// (BlockMaskOffset form, the one the vLLM connector sends).
+void kvcm_oracle_prefix_match_batch(void *h, const int64_t *keys, const int64_t *key_off, int64_t n_req,
+                                    const int64_t *mask_off, const uint32_t *weights, int n_weights, int32_t *len_out,
+                                    int threads) {
+    auto *ix = static_cast<OracleIndex *>(h);
+    ParallelFor(n_req, threads, [&](int64_t r) {
+        len_out[r] = static_cast<int32_t>(PrefixMatchOne(ix, keys + key_off[r], key_off[r + 1] - key_off[r], 1, nullptr,
+                                                         0, mask_off ? mask_off[r] : 0, weights, n_weights));
+    });
+}
+
+// base_out[r] = window start, -1 = no window, -2 = bad arguments for this request.
+void kvcm_oracle_sw_match_batch(void *h, const int64_t *keys, const int64_t *key_off, int64_t n_req, int64_t sw,
+                                const uint32_t *weights, int n_weights, int32_t *base_out, int threads) {
+    auto *ix = static_cast<OracleIndex *>(h);
+    ParallelFor(n_req, threads, [&](int64_t r) {
+        const int64_t n = key_off[r + 1] - key_off[r];
+        if (sw <= 0 || n < sw) {
+            base_out[r] = -2;
+            return;
+        }
+        base_out[r] = static_cast<int32_t>(SwMatchOne(ix, keys + key_off[r], n, sw, weights, n_weights));
+    });
+}
+
+// ---------------------------------------------------------------------------------
+// (1) paged-KV gather / scatter
+// ---------------------------------------------------------------------------------
+
+// kv_cache_manager/py_connector/kernel/batch_gather_scatter_helper.py:46-98 (gather) and
+// :152-205 (scatter), in bytes: a pool is [pool_rows, row_bytes]; block b moves its
+// rows_per_block rows row_idx[b][t] to/from staging slot slot_idx[b], whose layout is
+// [n_pools, rows_per_block, row_bytes].  A row is one token (the reference's form) or one
+// engine page (page-table form); the arithmetic is the same.
+// dir 0 = gather (pool -> staging), 1 = scatter (staging -> pool).
+// Rows outside [0, pool_rows) and slots outside [0, n_slots) are skipped and counted in the
+// return value (the reference's batch kernels do not check; its legacy kernels skip,
+// gather_scatter_helper.py:36-38,87-89).
+int64_t kvcm_oracle_move_rows(uint8_t *const *pools, int32_t n_pools, uint8_t *staging, int64_t n_slots,
+                              const int32_t *row_idx, const int32_t *slot_idx, int64_t n_blocks,
+                              int64_t rows_per_block, int64_t row_bytes, int64_t pool_rows, int dir, int threads) {
+    std::atomic<int64_t> skipped{0};
+    const int64_t slot_bytes = static_cast<int64_t>(n_pools) * rows_per_block * row_bytes;
+    ParallelFor(n_blocks, threads, [&](int64_t b) {
+        const int64_t slot = slot_idx ? slot_idx[b] : b;
+        if (slot < 0 || slot >= n_slots) {
+            skipped.fetch_add(static_cast<int64_t>(n_pools) * rows_per_block);
+            return;
+        }
+        for (int32_t p = 0; p < n_pools; ++p) {
+            uint8_t *stage = staging + slot * slot_bytes + static_cast<int64_t>(p) * rows_per_block * row_bytes;
+            for (int64_t t = 0; t < rows_per_block; ++t) {
+                const int64_t row = row_idx[b * rows_per_block + t];
+                if (row < 0 || row >= pool_rows) {
+                    skipped.fetch_add(1);
+                    continue;
+                }
+                uint8_t *in_pool = pools[p] + row * row_bytes;
+                if (dir == 0) {
+                    std::memcpy(stage + t * row_bytes, in_pool, row_bytes);
+                } else {
+                    std::memcpy(in_pool, stage + t * row_bytes, row_bytes);
+                }
+            }
+        }
+    });
+    return skipped.load();
+}
+
+// kv_cache_manager/py_connector/kernel/gather_scatter_helper.py:10-107 (legacy single-block
+// kernels): layer tensor [2, total_tokens, hidden] per pointer, staging
+// [n_layers, 2, n_tokens, hidden]; a token index >= total_tokens is skipped (:36-38, :87-89).
+void kvcm_oracle_move_legacy(uint8_t *const *layers, int32_t n_layers, int64_t total_tokens, uint8_t *staging,
+                             const int32_t *token_idx, int64_t n_tokens, int64_t hidden_bytes, int dir) {
+    for (int32_t l = 0; l < n_layers; ++l) {
+        for (int64_t t = 0; t < n_tokens; ++t) {
+            const int64_t tok = token_idx[t];
+            if (tok >= total_tokens || tok < 0) continue;
+            for (int kv = 0; kv < 2; ++kv) {
+                uint8_t *stage = staging + ((static_cast<int64_t>(l) * 2 + kv) * n_tokens + t) * hidden_bytes;
+                uint8_t *cache = layers[l] + (kv * total_tokens + tok) * hidden_bytes;
+                if (dir == 0) {
+                    std::memcpy(stage, cache, hidden_bytes);
+                } else {
+                    std::memcpy(cache, stage, hidden_bytes);
+                }
+            }
+        }
+    }
+}
+
+// kv_cache_manager/client/src/internal/sdk/local_file_sdk.cc:223-245 (DoGet) and :326-353
+// (DoPut): the iovs of a block are consumed in order against a contiguous byte string; an
+// iov with `ignore`, a null base or zero size moves nothing but still advances the offset.
+// dir 0 = iov -> block string (Put / save), 1 = block string -> iov (Get / load).
+// Returns the number of bytes the iov list spans.
+int64_t kvcm_oracle_copy_iovs(uint8_t *const *bases, const int64_t *sizes, const uint8_t *ignore, int64_t n_iovs,
+                              uint8_t *block_string, int dir) {
+    int64_t offset = 0;
+    for (int64_t i = 0; i < n_iovs; ++i) {
+        if (!ignore[i] && bases[i] != nullptr && sizes[i] > 0) {
+            if (dir == 0) {
+                std::memcpy(block_string + offset, bases[i], sizes[i]);
+            } else {
+                std::memcpy(bases[i], block_string + offset, sizes[i]);
+            }
+        }
+        offset += sizes[i];
+    }
+    return offset;
+}
+
+// kv_cache_manager/client/src/internal/sdk/sdk_buffer_check_util.cu:10-44: reflected CRC-32
+// (polynomial 0xEDB88320, init ~0, final complement) over the first and the last
+// `cal_bytes` bytes of an iov.
+uint32_t kvcm_oracle_iov_crc(const uint8_t *base, int64_t size, int64_t cal_bytes) {
+    uint32_t crc = 0xFFFFFFFFu;
+    auto feed = [&crc](uint8_t byte) {
+        crc ^= byte;
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t mask = 0u - (crc & 1u);
+            crc = (crc >> 1) ^ (0xEDB88320u & mask);
+        }
+    };
+    for (int64_t i = 0; i < cal_bytes; ++i) feed(base[i]);
+    for (int64_t i = size - cal_bytes; i < size; ++i) feed(base[i]);
+    return ~crc;
+}
+
+}  // extern "C"

@@ -1,0 +1,361 @@
+"""ctypes front end of the CPU oracle.  TEST INFRASTRUCTURE ONLY.
+
+The oracle restates the reference's hot-path algorithms on the CPU (see kvcm_oracle.cc for the
+reference file:line of every function).  Only tests, the smoke check and the bench's CPU-baseline
+leg import this module; the product package never does.
+
+`ref_hash()` additionally loads oracle/_ref/libkvcm_ref_hash.so - the reference's own
+kv_cache_manager/manager/hash_util.h compiled in place by oracle/Makefile - when it has been built.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libkvcm_oracle.so")
+_REF_PATH = os.path.join(_HERE, "_ref", "libkvcm_ref_hash.so")
+
+# kv_cache_manager/manager/select_location_policy.h:42-57: weights indexed by DataStorageType
+# (UNKNOWN, HF3FS, MOONCAKE, TAIR_MEMPOOL, NFS).
+DEFAULT_WEIGHTS = (1, 3, 3, 3, 5)
+
+# kv_cache_manager/manager/cache_location.h:44-50
+CLS_NOT_FOUND, CLS_NEW, CLS_WRITING, CLS_SERVING, CLS_DELETING = range(5)
+
+_c_i64p = ctypes.POINTER(ctypes.c_int64)
+_c_i32p = ctypes.POINTER(ctypes.c_int32)
+_c_u32p = ctypes.POINTER(ctypes.c_uint32)
+_c_u8p = ctypes.POINTER(ctypes.c_uint8)
+
+
+def build(force=False):
+    """Compile the oracle (and the reference header wrapper when the reference tree is present)."""
+    if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(
+            os.path.join(_HERE, "kvcm_oracle.cc")):
+        subprocess.run(["make", "-C", _HERE], check=True, stdout=subprocess.DEVNULL)
+    return _LIB_PATH
+
+
+_lib = None
+_ref = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        L = ctypes.CDLL(_LIB_PATH)
+        L.kvcm_oracle_hash_step.restype = ctypes.c_int64
+        L.kvcm_oracle_hash_step.argtypes = [ctypes.c_int64, ctypes.c_int64]
+        for name in ("kvcm_oracle_gen_key_vector_i64", "kvcm_oracle_gen_key_vector_u32"):
+            getattr(L, name).restype = ctypes.c_int64
+        L.kvcm_oracle_index_create.restype = ctypes.c_void_p
+        L.kvcm_oracle_index_size.restype = ctypes.c_int64
+        L.kvcm_oracle_prefix_match.restype = ctypes.c_int64
+        L.kvcm_oracle_sw_match.restype = ctypes.c_int32
+        L.kvcm_oracle_filter_write.restype = ctypes.c_int32
+        L.kvcm_oracle_move_rows.restype = ctypes.c_int64
+        L.kvcm_oracle_copy_iovs.restype = ctypes.c_int64
+        L.kvcm_oracle_iov_crc.restype = ctypes.c_uint32
+        _lib = L
+    return _lib
+
+
+def ref_hash():
+    """The reference's own hash header behind a C wrapper, or None when it was not built."""
+    global _ref
+    if _ref is None and os.path.exists(_REF_PATH):
+        R = ctypes.CDLL(_REF_PATH)
+        R.kvcm_ref_hash_step.restype = ctypes.c_int64
+        R.kvcm_ref_hash_step.argtypes = [ctypes.c_int64, ctypes.c_int64]
+        R.kvcm_ref_hash_array.restype = ctypes.c_int64
+        R.kvcm_ref_gen_key_vector.restype = ctypes.c_int64
+        _ref = R
+    return _ref
+
+
+def _ptr(a, ctype):
+    return a.ctypes.data_as(ctypes.POINTER(ctype))
+
+
+def _i64(a):
+    return np.ascontiguousarray(a, dtype=np.int64)
+
+
+def _weights(weights):
+    w = np.ascontiguousarray(weights, dtype=np.uint32)
+    return w, _ptr(w, ctypes.c_uint32), ctypes.c_int(len(w))
+
+
+# ------------------------------------------------------------------------------------------
+# hash
+# ------------------------------------------------------------------------------------------
+
+def hash_step(h, v):
+    return int(lib().kvcm_oracle_hash_step(h, v))
+
+
+def hash_step_py(h, v):
+    """Pure-Python closed form of one step (kv_cache_manager/manager/hash_util.h:8-12), for tiny cases."""
+    m = (1 << 64) - 1
+    hu = h & m
+    sra = (h >> 32) & m  # Python's >> on a negative int is arithmetic
+    out = hu ^ (((v & m) + 0x9E3779B97F4A7C15 + ((hu << 12) & m) + sra) & m)
+    return out - (1 << 64) if out >> 63 else out
+
+
+def gen_key_vector(tokens, block_size):
+    """GenKeyVector of one request (kv_cache_manager/manager/cache_manager.cc:76-87)."""
+    tokens = np.asarray(tokens)
+    n = len(tokens) // block_size if block_size > 0 else 0
+    keys = np.empty(n, dtype=np.int64)
+    if tokens.dtype == np.uint32:
+        t = np.ascontiguousarray(tokens)
+        lib().kvcm_oracle_gen_key_vector_u32(_ptr(t, ctypes.c_uint32), ctypes.c_int64(len(t)),
+                                             ctypes.c_int64(block_size), _ptr(keys, ctypes.c_int64))
+    else:
+        t = _i64(tokens)
+        lib().kvcm_oracle_gen_key_vector_i64(_ptr(t, ctypes.c_int64), ctypes.c_int64(len(t)),
+                                             ctypes.c_int64(block_size), _ptr(keys, ctypes.c_int64))
+    return keys
+
+
+def apply_prefix_hash(ids):
+    ids = _i64(ids)
+    keys = np.empty(len(ids), dtype=np.int64)
+    lib().kvcm_oracle_apply_prefix_hash(_ptr(ids, ctypes.c_int64), ctypes.c_int64(len(ids)),
+                                        _ptr(keys, ctypes.c_int64))
+    return keys
+
+
+def key_offsets(tok_off, block_size):
+    """Exclusive prefix sum of floor(len / block_size) per request."""
+    tok_off = _i64(tok_off)
+    counts = (tok_off[1:] - tok_off[:-1]) // block_size
+    out = np.zeros(len(tok_off), dtype=np.int64)
+    np.cumsum(counts, out=out[1:])
+    return out
+
+
+def hash_blocks(tokens, tok_off, block_size, threads=1):
+    """Keys of a CSR batch of requests; returns (keys, key_off)."""
+    tokens = np.ascontiguousarray(tokens)
+    tok_off = _i64(tok_off)
+    key_off = key_offsets(tok_off, block_size)
+    keys = np.empty(int(key_off[-1]), dtype=np.int64)
+    n_req = len(tok_off) - 1
+    if tokens.dtype == np.uint32:
+        fn, ct = lib().kvcm_oracle_hash_blocks_u32, ctypes.c_uint32
+    else:
+        tokens = _i64(tokens)
+        fn, ct = lib().kvcm_oracle_hash_blocks_i64, ctypes.c_int64
+    fn(_ptr(tokens, ct), _ptr(tok_off, ctypes.c_int64), ctypes.c_int64(n_req), ctypes.c_int64(block_size),
+       _ptr(keys, ctypes.c_int64), _ptr(key_off, ctypes.c_int64), ctypes.c_int(threads))
+    return keys, key_off
+
+
+# ------------------------------------------------------------------------------------------
+# index + matchers
+# ------------------------------------------------------------------------------------------
+
+class Index:
+    """Block index as the matchers see it: int64 key -> list of (status, storage type)."""
+
+    def __init__(self):
+        self._h = ctypes.c_void_p(lib().kvcm_oracle_index_create())
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().kvcm_oracle_index_destroy(self._h)
+            self._h = None
+
+    def __len__(self):
+        return int(lib().kvcm_oracle_index_size(self._h))
+
+    def put(self, keys, locations):
+        """locations[i] = list of (status, type) for keys[i]; an empty list is an empty location map."""
+        keys = _i64(keys)
+        loc_off = np.zeros(len(keys) + 1, dtype=np.int64)
+        st, ty = [], []
+        for i, locs in enumerate(locations):
+            for s, t in locs:
+                st.append(s)
+                ty.append(t)
+            loc_off[i + 1] = len(st)
+        st = np.asarray(st, dtype=np.int32)
+        ty = np.asarray(ty, dtype=np.int32)
+        lib().kvcm_oracle_index_put(self._h, _ptr(keys, ctypes.c_int64), ctypes.c_int64(len(keys)),
+                                    _ptr(loc_off, ctypes.c_int64), _ptr(st, ctypes.c_int32), _ptr(ty, ctypes.c_int32))
+
+    def put_uniform(self, keys, status=CLS_SERVING, storage_type=4):
+        keys = _i64(keys)
+        lib().kvcm_oracle_index_reserve(self._h, ctypes.c_int64(len(self) + len(keys)))
+        lib().kvcm_oracle_index_put_uniform(self._h, _ptr(keys, ctypes.c_int64), ctypes.c_int64(len(keys)),
+                                            ctypes.c_int32(status), ctypes.c_int32(storage_type))
+
+    def erase(self, keys):
+        keys = _i64(keys)
+        lib().kvcm_oracle_index_erase(self._h, _ptr(keys, ctypes.c_int64), ctypes.c_int64(len(keys)))
+
+    def prefix_match(self, keys, mask=None, weights=DEFAULT_WEIGHTS):
+        """mask: None, an int offset, or a sequence of bools (kv_cache_manager/manager/cache_location.h:52-57)."""
+        keys = _i64(keys)
+        w, wp, nw = _weights(weights)
+        kind, vec, vec_len, off = 1, None, 0, 0
+        if mask is None:
+            kind = 0
+            vec = np.zeros(0, dtype=np.uint8)
+        elif isinstance(mask, (int, np.integer)):
+            off = int(mask)
+        else:
+            kind = 0
+            vec = np.ascontiguousarray(np.asarray(mask, dtype=bool).astype(np.uint8))
+            vec_len = len(vec)
+        vp = _ptr(vec, ctypes.c_uint8) if vec is not None else None
+        return int(lib().kvcm_oracle_prefix_match(self._h, _ptr(keys, ctypes.c_int64), ctypes.c_int64(len(keys)),
+                                                  ctypes.c_int(kind), vp, ctypes.c_int64(vec_len), ctypes.c_int64(off),
+                                                  wp, nw))
+
+    def sw_match(self, keys, sw, weights=DEFAULT_WEIGHTS):
+        """Returns (error_code, base): base = start of the matched window or -1."""
+        keys = _i64(keys)
+        w, wp, nw = _weights(weights)
+        base = ctypes.c_int64(-1)
+        ec = lib().kvcm_oracle_sw_match(self._h, _ptr(keys, ctypes.c_int64), ctypes.c_int64(len(keys)),
+                                        ctypes.c_int64(sw), wp, nw, ctypes.byref(base))
+        return int(ec), int(base.value)
+
+    def batch_get(self, keys, weights=DEFAULT_WEIGHTS):
+        """flags per key: bit0 servable, bit1 exists, bit2 location map non-empty, bit3 exists-for-write."""
+        keys = _i64(keys)
+        w, wp, nw = _weights(weights)
+        flags = np.zeros(len(keys), dtype=np.uint8)
+        lib().kvcm_oracle_batch_get(self._h, _ptr(keys, ctypes.c_int64), ctypes.c_int64(len(keys)), wp, nw,
+                                    _ptr(flags, ctypes.c_uint8))
+        return flags
+
+    def filter_write(self, keys, weights=DEFAULT_WEIGHTS):
+        """Returns ("offset", first_missing, n_new) or ("vector", bool mask, n_new)."""
+        keys = _i64(keys)
+        w, wp, nw = _weights(weights)
+        off = ctypes.c_int64(0)
+        n_new = ctypes.c_int64(0)
+        mask = np.zeros(max(len(keys), 1), dtype=np.uint8)
+        is_off = lib().kvcm_oracle_filter_write(self._h, _ptr(keys, ctypes.c_int64), ctypes.c_int64(len(keys)), wp, nw,
+                                                ctypes.byref(off), _ptr(mask, ctypes.c_uint8), ctypes.byref(n_new))
+        if is_off:
+            return "offset", int(off.value), int(n_new.value)
+        return "vector", mask[:len(keys)].astype(bool), int(n_new.value)
+
+    def prefix_match_batch(self, keys, key_off, mask_off=None, weights=DEFAULT_WEIGHTS, threads=1):
+        keys = _i64(keys)
+        key_off = _i64(key_off)
+        w, wp, nw = _weights(weights)
+        n_req = len(key_off) - 1
+        out = np.zeros(n_req, dtype=np.int32)
+        mp = None
+        if mask_off is not None:
+            mask_off = _i64(mask_off)
+            mp = _ptr(mask_off, ctypes.c_int64)
+        lib().kvcm_oracle_prefix_match_batch(self._h, _ptr(keys, ctypes.c_int64), _ptr(key_off, ctypes.c_int64),
+                                             ctypes.c_int64(n_req), mp, wp, nw, _ptr(out, ctypes.c_int32),
+                                             ctypes.c_int(threads))
+        return out
+
+    def sw_match_batch(self, keys, key_off, sw, weights=DEFAULT_WEIGHTS, threads=1):
+        keys = _i64(keys)
+        key_off = _i64(key_off)
+        w, wp, nw = _weights(weights)
+        n_req = len(key_off) - 1
+        out = np.zeros(n_req, dtype=np.int32)
+        lib().kvcm_oracle_sw_match_batch(self._h, _ptr(keys, ctypes.c_int64), _ptr(key_off, ctypes.c_int64),
+                                         ctypes.c_int64(n_req), ctypes.c_int64(sw), wp, nw,
+                                         _ptr(out, ctypes.c_int32), ctypes.c_int(threads))
+        return out
+
+
+# ------------------------------------------------------------------------------------------
+# gather / scatter
+# ------------------------------------------------------------------------------------------
+
+def _ptr_table(arrays):
+    tab = (ctypes.c_void_p * len(arrays))()
+    for i, a in enumerate(arrays):
+        tab[i] = a.ctypes.data if a is not None else None
+    return tab
+
+
+def move_rows(pools, staging, row_idx, slot_idx, rows_per_block, row_bytes, direction, threads=1):
+    """Gather (direction 0) or scatter (1) between numpy uint8 pools [pool_rows*row_bytes] and staging.
+
+    Layout rule: kv_cache_manager/py_connector/kernel/batch_gather_scatter_helper.py:46-98,152-205.
+    Returns the number of rows skipped for being out of range.
+    """
+    row_idx = np.ascontiguousarray(row_idx, dtype=np.int32)
+    n_blocks = len(row_idx) // rows_per_block
+    sp = None
+    if slot_idx is not None:
+        slot_idx = np.ascontiguousarray(slot_idx, dtype=np.int32)
+        sp = _ptr(slot_idx, ctypes.c_int32)
+    n_pools = len(pools)
+    slot_bytes = n_pools * rows_per_block * row_bytes
+    n_slots = staging.nbytes // slot_bytes if slot_bytes else 0
+    pool_rows = pools[0].nbytes // row_bytes
+    tab = _ptr_table(pools)
+    return int(lib().kvcm_oracle_move_rows(tab, ctypes.c_int32(n_pools), ctypes.c_void_p(staging.ctypes.data),
+                                           ctypes.c_int64(n_slots), _ptr(row_idx, ctypes.c_int32), sp,
+                                           ctypes.c_int64(n_blocks), ctypes.c_int64(rows_per_block),
+                                           ctypes.c_int64(row_bytes), ctypes.c_int64(pool_rows),
+                                           ctypes.c_int(direction), ctypes.c_int(threads)))
+
+
+def move_rows_py(pools, staging, row_idx, slot_idx, rows_per_block, row_bytes, direction):
+    """The same rule as plain Python loops over numpy views (small cases only)."""
+    n_pools = len(pools)
+    n_blocks = len(row_idx) // rows_per_block
+    st = staging.reshape(-1, n_pools, rows_per_block, row_bytes)
+    for b in range(n_blocks):
+        slot = slot_idx[b] if slot_idx is not None else b
+        for p in range(n_pools):
+            pool = pools[p].reshape(-1, row_bytes)
+            for t in range(rows_per_block):
+                row = row_idx[b * rows_per_block + t]
+                if row < 0 or row >= pool.shape[0]:
+                    continue
+                if direction == 0:
+                    st[slot, p, t] = pool[row]
+                else:
+                    pool[row] = st[slot, p, t]
+
+
+def move_legacy(layers, total_tokens, staging, token_idx, hidden_bytes, direction):
+    """Legacy single-block form (kv_cache_manager/py_connector/kernel/gather_scatter_helper.py:10-107)."""
+    token_idx = np.ascontiguousarray(token_idx, dtype=np.int32)
+    tab = _ptr_table(layers)
+    lib().kvcm_oracle_move_legacy(tab, ctypes.c_int32(len(layers)), ctypes.c_int64(total_tokens),
+                                  ctypes.c_void_p(staging.ctypes.data), _ptr(token_idx, ctypes.c_int32),
+                                  ctypes.c_int64(len(token_idx)), ctypes.c_int64(hidden_bytes),
+                                  ctypes.c_int(direction))
+
+
+def copy_iovs(iovs, block_string, direction):
+    """iovs: list of (numpy uint8 array or None, size, ignore).  direction 0: iovs -> string, 1: string -> iovs."""
+    n = len(iovs)
+    tab = (ctypes.c_void_p * n)()
+    sizes = np.zeros(n, dtype=np.int64)
+    ign = np.zeros(n, dtype=np.uint8)
+    for i, (arr, size, ignore) in enumerate(iovs):
+        tab[i] = arr.ctypes.data if arr is not None else None
+        sizes[i] = size
+        ign[i] = 1 if ignore else 0
+    return int(lib().kvcm_oracle_copy_iovs(tab, _ptr(sizes, ctypes.c_int64), _ptr(ign, ctypes.c_uint8),
+                                           ctypes.c_int64(n), ctypes.c_void_p(block_string.ctypes.data),
+                                           ctypes.c_int(direction)))
+
+
+def iov_crc(buf, cal_bytes):
+    buf = np.ascontiguousarray(np.frombuffer(buf, dtype=np.uint8) if isinstance(buf, (bytes, bytearray)) else buf)
+    return int(lib().kvcm_oracle_iov_crc(ctypes.c_void_p(buf.ctypes.data), ctypes.c_int64(buf.nbytes),
+                                         ctypes.c_int64(cal_bytes)))

@@ -1,0 +1,202 @@
+"""The CPU oracle against the reference's golden vectors (no GPU)."""
+import numpy as np
+import pytest
+
+from oracle import kvcm_oracle as oracle
+
+
+def _index_from(table):
+    ix = oracle.Index()
+    keys = [int(k) for k in table]
+    ix.put(keys, [[tuple(l) for l in table[str(k)]] for k in keys])
+    return ix
+
+
+def test_hash_steps_match_reference_header(hash_kat):
+    for s in hash_kat["steps"]:
+        h, v, out = int(s["h"]), int(s["v"]), int(s["out"])
+        assert oracle.hash_step(h, v) == out
+        assert oracle.hash_step_py(h, v) == out
+
+
+def test_hash_chains_match_reference_header(hash_kat):
+    for c in hash_kat["chains"]:
+        want = np.array([int(k) for k in c["keys"]], dtype=np.int64)
+        got = oracle.gen_key_vector(np.array(c["tokens"], dtype=np.int64), c["block_size"])
+        assert np.array_equal(got, want), c["name"]
+        got32 = oracle.gen_key_vector(np.array(c["tokens"], dtype=np.uint32), c["block_size"])
+        assert np.array_equal(got32, want), c["name"]
+
+
+def test_apply_prefix_hash(hash_kat):
+    p = hash_kat["apply_prefix_hash"]
+    assert oracle.apply_prefix_hash(p["ids"]).tolist() == [int(k) for k in p["keys"]]
+    # ApplyPrefixHash is GenKeyVector with block_size 1
+    assert np.array_equal(oracle.apply_prefix_hash(p["ids"]), oracle.gen_key_vector(np.array(p["ids"]), 1))
+
+
+def test_oracle_equals_compiled_reference_header_on_random_chains():
+    ref = oracle.ref_hash()
+    if ref is None:
+        pytest.skip("oracle/_ref not built (reference tree absent)")
+    import ctypes
+    rng = np.random.default_rng(7)
+    p64 = ctypes.POINTER(ctypes.c_int64)
+    for bs in (1, 16, 64):
+        toks = rng.integers(0, 1 << 32, size=5000).astype(np.int64)
+        want = np.empty(len(toks) // bs, dtype=np.int64)
+        ref.kvcm_ref_gen_key_vector(toks.ctypes.data_as(p64), ctypes.c_int64(len(toks)), ctypes.c_int64(bs),
+                                    want.ctypes.data_as(p64))
+        assert np.array_equal(oracle.gen_key_vector(toks, bs), want)
+
+
+def test_hash_blocks_csr_is_per_request_gen_key_vector():
+    rng = np.random.default_rng(3)
+    lens = [0, 5, 64, 130, 63, 1000]
+    toks = rng.integers(0, 151936, size=sum(lens)).astype(np.uint32)
+    off = np.concatenate([[0], np.cumsum(lens)])
+    for threads in (1, 4):
+        keys, key_off = oracle.hash_blocks(toks, off, 64, threads=threads)
+        assert key_off.tolist() == [0, 0, 0, 1, 3, 3, 18]
+        for r in range(len(lens)):
+            want = oracle.gen_key_vector(toks[off[r]:off[r + 1]], 64)
+            assert np.array_equal(keys[key_off[r]:key_off[r + 1]], want)
+
+
+def test_prefix_match_tables(match_kat):
+    for group in match_kat["prefix"]:
+        ix = _index_from(group["index"])
+        for case in group["cases"]:
+            assert ix.prefix_match(case["keys"], case["mask"]) == case["len"], (group["source"], case)
+
+
+def test_sw_match_tables(match_kat):
+    for group in match_kat["sw"]:
+        ix = _index_from(group["index"])
+        for case in group["cases"]:
+            ec, base = ix.sw_match(case["keys"], case["sw"])
+            assert (ec, base) == (case["ec"], case["base"]), (group["source"], case)
+
+
+def test_sw_zero_is_rejected():
+    ix = oracle.Index()
+    ix.put_uniform([1, 2])
+    assert ix.sw_match([1, 2], 0)[0] == 6
+
+
+def test_batch_get_tables(match_kat):
+    for group in match_kat["batch_get"]:
+        ix = _index_from(group["index"])
+        for case in group["cases"]:
+            flags = ix.batch_get(case["keys"])
+            assert [(int(f) & 1) == 1 for f in flags] == case["servable"], (group["source"], case)
+
+
+def test_sw_match_is_rightmost_full_window_property():
+    rng = np.random.default_rng(11)
+    for _ in range(200):
+        n = int(rng.integers(1, 40))
+        sw = int(rng.integers(1, n + 1))
+        state = rng.integers(0, 3, size=n)  # 0 absent, 1 writing, 2 serving
+        ix = oracle.Index()
+        keys = np.arange(100, 100 + n)
+        ix.put(keys[state == 1], [[(oracle.CLS_WRITING, 4)]] * int((state == 1).sum()))
+        ix.put(keys[state == 2], [[(oracle.CLS_SERVING, 4)]] * int((state == 2).sum()))
+        want = -1
+        for base in range(n - sw, -1, -1):
+            if np.all(state[base:base + sw] == 2):
+                want = base
+                break
+        assert ix.sw_match(keys, sw) == (0, want)
+
+
+def test_policy_weights_gate_servable():
+    ix = oracle.Index()
+    ix.put([1, 2], [[(oracle.CLS_SERVING, 1)], [(oracle.CLS_SERVING, 4)]])
+    assert ix.prefix_match([1, 2]) == 2
+    assert ix.prefix_match([1, 2], weights=(1, 0, 3, 3, 5)) == 0  # HF3FS unavailable
+    assert ix.prefix_match([2, 1], weights=(1, 0, 3, 3, 5)) == 1
+    # storage type beyond the weight table gets the default weight 1
+    ix.put([3], [[(oracle.CLS_SERVING, 5)]])
+    assert ix.prefix_match([3]) == 1
+
+
+def test_filter_write():
+    ix = oracle.Index()
+    ix.put([1, 2, 3], [[(oracle.CLS_SERVING, 4)], [(oracle.CLS_WRITING, 4)], []])
+    assert ix.filter_write([1, 2, 9, 8]) == ("offset", 2, 2)
+    assert ix.filter_write([9, 8]) == ("offset", 0, 2)
+    kind, mask, n_new = ix.filter_write([1, 9, 2, 3])
+    assert kind == "vector" and mask.tolist() == [True, False, True, False] and n_new == 2
+
+
+def test_crc_known_answers(match_kat):
+    for case in match_kat["crc"][0]["cases"]:
+        data = case["text"].encode()
+        cal = min(case["min_cal_bytes"], len(data) // 2)
+        assert oracle.iov_crc(data, cal) == int(case["crc"], 16)
+
+
+def _pools(rng, n_pools, pool_rows, row_bytes):
+    return [rng.integers(0, 256, size=pool_rows * row_bytes, dtype=np.uint8) for _ in range(n_pools)]
+
+
+def test_move_rows_matches_python_loops_and_roundtrips():
+    rng = np.random.default_rng(42)
+    n_pools, pool_rows, row_bytes, rpb, n_blocks, n_slots = 4, 200, 48, 8, 10, 16
+    pools = _pools(rng, n_pools, pool_rows, row_bytes)
+    row_idx = rng.permutation(pool_rows)[:n_blocks * rpb].astype(np.int32)
+    slot_idx = rng.permutation(n_slots)[:n_blocks].astype(np.int32)
+    st_c = np.zeros(n_slots * n_pools * rpb * row_bytes, dtype=np.uint8)
+    st_py = st_c.copy()
+    assert oracle.move_rows(pools, st_c, row_idx, slot_idx, rpb, row_bytes, 0, threads=3) == 0
+    oracle.move_rows_py(pools, st_py, row_idx, slot_idx, rpb, row_bytes, 0)
+    assert np.array_equal(st_c, st_py)
+    # element-wise statement of the rule (batch_gather_scatter_helper.py:57-98)
+    st = st_c.reshape(n_slots, n_pools, rpb, row_bytes)
+    for b in range(n_blocks):
+        for p in range(n_pools):
+            for t in range(rpb):
+                row = row_idx[b * rpb + t]
+                assert np.array_equal(st[slot_idx[b], p, t], pools[p].reshape(-1, row_bytes)[row])
+    fresh = [np.zeros_like(p) for p in pools]
+    oracle.move_rows(fresh, st_c, row_idx, slot_idx, rpb, row_bytes, 1)
+    for p in range(n_pools):
+        a = fresh[p].reshape(-1, row_bytes)
+        assert np.array_equal(a[row_idx], pools[p].reshape(-1, row_bytes)[row_idx])
+        untouched = np.setdiff1d(np.arange(pool_rows), row_idx)
+        assert not a[untouched].any()
+
+
+def test_move_rows_skips_out_of_range():
+    rng = np.random.default_rng(1)
+    pools = _pools(rng, 2, 10, 16)
+    st = np.zeros(2 * 2 * 2 * 16, dtype=np.uint8)
+    skipped = oracle.move_rows(pools, st, np.array([0, 10, -1, 3], dtype=np.int32), None, 2, 16, 0)
+    assert skipped == 2 * 2  # two bad rows x two pools
+    assert not st.reshape(2, 2, 2, 16)[0, :, 1].any()
+
+
+def test_move_legacy_skips_tokens_past_the_cache():
+    rng = np.random.default_rng(5)
+    total, hidden, n_layers = 32, 24, 3
+    layers = [rng.integers(0, 256, size=2 * total * hidden, dtype=np.uint8) for _ in range(n_layers)]
+    tok = np.array([4, 31, 32, 0], dtype=np.int32)
+    st = np.zeros(n_layers * 2 * len(tok) * hidden, dtype=np.uint8)
+    oracle.move_legacy(layers, total, st, tok, hidden, 0)
+    v = st.reshape(n_layers, 2, len(tok), hidden)
+    for l in range(n_layers):
+        cache = layers[l].reshape(2, total, hidden)
+        assert np.array_equal(v[l, :, 0], cache[:, 4]) and np.array_equal(v[l, :, 1], cache[:, 31])
+        assert not v[l, :, 2].any()
+
+
+def test_copy_iovs_ignore_advances_offset():
+    a = np.arange(8, dtype=np.uint8)
+    b = np.arange(100, 104, dtype=np.uint8)
+    s = np.zeros(16, dtype=np.uint8)
+    n = oracle.copy_iovs([(a, 8, False), (None, 4, True), (b, 4, False)], s, 0)
+    assert n == 16 and s.tolist() == list(range(8)) + [0] * 4 + [100, 101, 102, 103]
+    a2, b2 = np.zeros_like(a), np.zeros_like(b)
+    oracle.copy_iovs([(a2, 8, False), (None, 4, True), (b2, 4, False)], s, 1)
+    assert np.array_equal(a, a2) and np.array_equal(b, b2)
