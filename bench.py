@@ -1,0 +1,476 @@
+"""Benchmark of the KVCM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload c2|c3|c1]
+
+Default workload (`c2`): Llama-3-8B-shaped paged-KV transfer on one GPU - 32 layers x (K,V) pools of
+65,536 pages of 16 tokens x 1024 bf16, 2,048 transfer blocks of 4 pages each addressed through a random
+non-contiguous page table, gathered into contiguous device staging and scattered back.  One step = one
+gather plus one scatter of all blocks.  `value` is GB/s of algorithmic bytes (2 x payload per direction:
+every payload byte is read once and written once), inputs resident in HBM.  `e2e` is the same metric
+through the Python operator API with the staging buffers in pinned host memory, i.e. with the
+device<->host traffic of a real save / load inside the timed region.
+
+With N > 1 (torchrun) every rank moves its own tensor-parallel slice of the same shape: no data-path
+collective, weak scaling, time = max over ranks.
+
+`--impl reference` times the CPU restatement of the same step (oracle/, all host threads) on a bounded
+sample of the workload, on rank 0 only.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "kv_block_gather_scatter_bandwidth"
+UNIT = "GB/s"
+
+WORKLOADS = {
+    # name: layers, kv pools per layer, page tokens, bytes per token per pool, pages per pool, blocks, pages per block
+    "c2": dict(desc="llama3-8b paged-KV gather+scatter, 32 layers x (K,V), 8 kv heads x 128 bf16, page 16, "
+                    "2048 blocks x 64 tokens, random page table, device staging",
+               n_pools=64, page_tokens=16, token_bytes=2048, pool_pages=65536, n_blocks=2048, pages_per_block=4),
+    "c3": dict(desc="llama3-70b TP=8 slice per rank, 80 layers x (K,V), 1 kv head x 128 bf16, page 32, "
+                    "8192 blocks x 128 tokens per rank, random page table, device staging",
+               n_pools=160, page_tokens=32, token_bytes=256, pool_pages=65536, n_blocks=8192, pages_per_block=4),
+}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ----------------------------------------------------------------------------------------------
+# clocks
+# ----------------------------------------------------------------------------------------------
+class ClockSampler:
+    """nvidia-smi sampling of SM clocks and throttle reasons while the timed region runs (read-only)."""
+    FIELDS = ("uuid,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, uuid):
+        self.uuid = uuid
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, reasons, sm_max = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 8 or (self.uuid and self.uuid not in parts[0]):
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    sm_max = float(parts[2])
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[4:8]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=sm_max, reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ----------------------------------------------------------------------------------------------
+# workload
+# ----------------------------------------------------------------------------------------------
+def build_transfer_workload(cfg, device, seed):
+    """Pools, page table, staging slot order on `device`.  Pool size shrinks if the GPU cannot hold it
+    (the referenced pages and the bytes moved stay the same)."""
+    import torch
+    n_pools, page_bytes = cfg["n_pools"], cfg["page_tokens"] * cfg["token_bytes"]
+    n_blocks, ppb = cfg["n_blocks"], cfg["pages_per_block"]
+    payload = n_blocks * n_pools * ppb * page_bytes
+    free, _ = torch.cuda.mem_get_info(device)
+    pool_pages = cfg["pool_pages"]
+    while pool_pages > 2 * n_blocks * ppb and n_pools * pool_pages * page_bytes + payload + (6 << 30) > free:
+        pool_pages //= 2
+    gen = torch.Generator(device=device).manual_seed(seed)
+    pools = []
+    for _ in range(n_pools):
+        # random 32-bit patterns = random bf16 bit patterns, NaN and Inf payloads included
+        t = torch.empty(pool_pages * page_bytes // 4, dtype=torch.int32, device=device)
+        t.random_(-(1 << 31), (1 << 31) - 1, generator=gen)
+        pools.append(t)
+    ptrs = torch.tensor([p.data_ptr() for p in pools], dtype=torch.int64, device=device)
+    rng = np.random.default_rng(seed)
+    table = torch.from_numpy(rng.permutation(pool_pages)[:n_blocks * ppb].astype(np.int32)).to(device)
+    slots = torch.from_numpy(rng.permutation(n_blocks).astype(np.int32)).to(device)
+    staging = torch.zeros(payload // 4, dtype=torch.int32, device=device)
+    return dict(pools=pools, ptrs=ptrs, table=table, slots=slots, staging=staging, pool_pages=pool_pages,
+                page_bytes=page_bytes, payload=payload, n_pools=n_pools, n_blocks=n_blocks, ppb=ppb)
+
+
+def verify_staging(w, n_check=64):
+    """Staged bytes equal a torch gather of the pools on a sample of (block, pool) tiles."""
+    import torch
+    rng = np.random.default_rng(1)
+    st = w["staging"].view(w["n_blocks"], w["n_pools"], w["ppb"], -1)
+    table = w["table"].long().view(w["n_blocks"], w["ppb"])
+    slots = w["slots"].long()
+    for _ in range(n_check):
+        b, p = int(rng.integers(0, w["n_blocks"])), int(rng.integers(0, w["n_pools"]))
+        want = w["pools"][p].view(w["pool_pages"], -1)[table[b]]
+        if not torch.equal(st[slots[b], p], want):
+            return False
+    return True
+
+
+def run_cpu_transfer(cfg, threads, steps, warmup, budget_s=20.0):
+    """The CPU restatement of one gather + scatter step on a bounded sample (host memory)."""
+    from oracle import kvcm_oracle as oracle
+    n_pools, page_bytes, ppb = cfg["n_pools"], cfg["page_tokens"] * cfg["token_bytes"], cfg["pages_per_block"]
+    n_blocks = max(1, (1 << 30) // (n_pools * ppb * page_bytes))  # ~1 GiB of payload per step
+    pool_pages = 2 * n_blocks * ppb
+    rng = np.random.default_rng(0xB2000002)
+    pools = [rng.integers(0, 256, size=pool_pages * page_bytes, dtype=np.uint8) for _ in range(n_pools)]
+    table = rng.permutation(pool_pages)[:n_blocks * ppb].astype(np.int32)
+    slots = rng.permutation(n_blocks).astype(np.int32)
+    staging = np.zeros(n_blocks * n_pools * ppb * page_bytes, dtype=np.uint8)
+    payload = staging.nbytes
+
+    def step():
+        oracle.move_rows(pools, staging, table, slots, ppb, page_bytes, 0, threads=threads)
+        oracle.move_rows(pools, staging, table, slots, ppb, page_bytes, 1, threads=threads)
+
+    for _ in range(warmup):
+        step()
+    times = []
+    t_begin = time.perf_counter()
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+        if time.perf_counter() - t_begin > budget_s:
+            break
+    total = sum(times)
+    gbs = 4.0 * payload * len(times) / total / 1e9
+    sample = "%d of %d blocks (%.2f GiB payload per direction), %d pools of %d pages in host memory, %d steps" % (
+        n_blocks, cfg["n_blocks"], payload / 2 ** 30, n_pools, pool_pages, len(times))
+    return gbs, 1e3 * total / len(times), sample, len(times)
+
+
+# ----------------------------------------------------------------------------------------------
+# prefix-match side workload (second half of the metric), small and quick
+# ----------------------------------------------------------------------------------------------
+def build_prefix_workload(seed=0xB2000001, n_req=4096, n_prior_blocks=200000, bs=64):
+    """CPU-runnable prefix-match configuration: uint32 tokens uniform in [0,151936), lengths uniform 512-8192,
+    half of the requests reuse a random-length prefix of an earlier sequence, index pre-filled with the
+    hashes of n_prior_blocks prior blocks."""
+    rng = np.random.default_rng(seed)
+    prior, n = [], 0
+    while n < n_prior_blocks:
+        t = rng.integers(0, 151936, size=int(rng.integers(512, 8193)), dtype=np.int64).astype(np.uint32)
+        prior.append(t)
+        n += len(t) // bs
+    seqs = list(prior)
+    reqs = []
+    for _ in range(n_req):
+        t = rng.integers(0, 151936, size=int(rng.integers(512, 8193)), dtype=np.int64).astype(np.uint32)
+        if rng.random() < 0.5:
+            src = seqs[int(rng.integers(0, len(seqs)))]
+            m = int(rng.integers(1, min(len(t), len(src)) + 1))
+            t[:m] = src[:m]
+        reqs.append(t)
+        seqs.append(t)
+
+    def csr(seq_list):
+        off = np.zeros(len(seq_list) + 1, dtype=np.int64)
+        np.cumsum([len(s) for s in seq_list], out=off[1:])
+        return np.concatenate(seq_list), off
+
+    return csr(prior), csr(reqs), n_prior_blocks, bs
+
+
+def run_prefix_gpu(device, steps, warmup):
+    import torch
+    from tair_kvcache_b200.manager import (BatchMetaSearcher, BlockIndex, GenKeyVectorBatch, encode_locations,
+                                           key_offsets)
+    (ptoks, poff), (toks, off), n_prior, bs = build_prefix_workload()
+    pko = key_offsets(poff, bs)
+    pkeys = GenKeyVectorBatch(torch.from_numpy(ptoks.view(np.int32)).to(device), torch.from_numpy(poff).to(device), bs,
+                              torch.from_numpy(pko).to(device), int(pko[-1]))[:n_prior]
+    index = BlockIndex(n_prior, device)
+    index.upsert(pkeys, None, encode_locations([(3, 4)]))
+    searcher = BatchMetaSearcher(index)
+    ko = key_offsets(off, bs)
+    n_keys = int(ko[-1])
+    h_toks = torch.from_numpy(toks.view(np.int32)).pin_memory()
+    h_off = torch.from_numpy(off).pin_memory()
+    h_ko = torch.from_numpy(ko).pin_memory()
+    d_toks, d_off, d_ko = h_toks.to(device), h_off.to(device), h_ko.to(device)
+    d_keys = torch.empty(n_keys, dtype=torch.int64, device=device)
+    d_len = torch.empty(len(off) - 1, dtype=torch.int32, device=device)
+    h_len = torch.empty(len(off) - 1, dtype=torch.int32).pin_memory()
+
+    def resident():
+        GenKeyVectorBatch(d_toks, d_off, bs, d_ko, n_keys, out=d_keys)
+        searcher.PrefixMatch(d_keys, d_ko, out=d_len)
+
+    def e2e():
+        d_toks.copy_(h_toks, non_blocking=True)
+        d_off.copy_(h_off, non_blocking=True)
+        d_ko.copy_(h_ko, non_blocking=True)
+        resident()
+        h_len.copy_(d_len, non_blocking=True)
+
+    out = {}
+    for name, fn in (("resident", resident), ("e2e", e2e)):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(device)
+        out[name] = n_keys * steps / (e0.elapsed_time(e1) * 1e-3)
+    matched = int(h_len.sum().item())
+    return dict(workload="4096 requests x 512-8192 uint32 tokens, block 64, 50% prefix reuse, index of 200k prior "
+                         "blocks; hash + prefix match",
+                token_blocks=n_keys, matched_blocks=matched, token_blocks_per_s=out["resident"],
+                e2e_token_blocks_per_s=out["e2e"], h2d_bytes_per_step=int(h_toks.numel() * 4 + h_off.numel() * 16),
+                d2h_bytes_per_step=int(h_len.numel() * 4), gpu_launches_per_step=2), (toks, off, ko, bs, ptoks, poff)
+
+
+def run_prefix_cpu(data, threads, budget_s=12.0):
+    from oracle import kvcm_oracle as oracle
+    toks, off, ko, bs, ptoks, poff = data
+    pkeys, _ = oracle.hash_blocks(ptoks, poff, bs, threads=threads)
+    ox = oracle.Index()
+    ox.put_uniform(pkeys[:200000])
+    n, t_total = 0, 0.0
+    while t_total < budget_s and n < 20:
+        t0 = time.perf_counter()
+        keys, ko2 = oracle.hash_blocks(toks, off, bs, threads=threads)
+        ox.prefix_match_batch(keys, ko2, threads=threads)
+        t_total += time.perf_counter() - t0
+        n += 1
+    return int(ko[-1]) * n / t_total, n
+
+
+# ----------------------------------------------------------------------------------------------
+# main arms
+# ----------------------------------------------------------------------------------------------
+def main_reference(args, cfg, rank):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    gbs, ms, sample, n = run_cpu_transfer(cfg, threads, args.steps, min(args.warmup, 1))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": n,
+        "warmup": min(args.warmup, 1), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+        "config": {"workload": cfg["desc"], "note": "the reference has no CPU gather/scatter (Triton only, and its "
+                   "sources cannot travel to the GPU box); this arm times the CPU restatement of the same index "
+                   "rule with all host threads on a bounded sample"},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main_b200(args, cfg, rank, world):
+    import torch
+    import torch.distributed as dist
+
+    import tair_kvcache_b200  # noqa: F401
+    from tair_kvcache_b200.kernel import (batch_gather_kv_caches, batch_gather_kv_pages, batch_scatter_kv_caches,
+                                          batch_scatter_kv_pages)
+
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    w = build_transfer_workload(cfg, device, seed=0xB2000002 + rank)
+    ptrs, table, slots, staging = w["ptrs"], w["table"], w["slots"], w["staging"]
+    ppb, page_bytes, pool_pages, payload = w["ppb"], w["page_bytes"], w["pool_pages"], w["payload"]
+
+    def gather():
+        batch_gather_kv_pages(ptrs, staging, table, slots, ppb, page_bytes, pool_pages)
+
+    def scatter():
+        batch_scatter_kv_pages(ptrs, staging, table, slots, ppb, page_bytes, pool_pages)
+
+    gather()
+    torch.cuda.synchronize(device)
+    parity_ok = verify_staging(w)
+
+    for _ in range(args.warmup):
+        gather()
+        scatter()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    sampler = ClockSampler(str(torch.cuda.get_device_properties(device).uuid)) if rank == 0 else None
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    if sampler:
+        sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for k in range(args.steps):
+        ev[k][0].record()
+        gather()
+        ev[k][1].record()
+        scatter()
+        ev[k][2].record()
+    stop.record()
+    torch.cuda.synchronize(device)
+    if world > 1:
+        dist.barrier()
+    clocks = sampler.stop() if sampler else None
+    elapsed_ms = start.elapsed_time(stop)
+    gather_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    scatter_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    if world > 1:
+        t = torch.tensor([elapsed_ms, gather_ms, scatter_ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms, gather_ms, scatter_ms = t.tolist()
+    alg_bytes_step = 4 * payload  # gather: read + write payload; scatter: the same
+    value = world * alg_bytes_step * args.steps / (elapsed_ms * 1e-3) / 1e9
+
+    # ---- end to end: pinned host staging through the operator API, python index lists included
+    T = ppb * cfg["page_tokens"]
+    task_blocks = min(128, w["n_blocks"])  # blocks per save / load task of the reference connector
+    n_tasks = min(w["n_blocks"] // task_blocks, 8 if cfg is WORKLOADS["c2"] else 4)
+    dim = cfg["token_bytes"] // 2
+    host_staging = torch.empty(task_blocks, w["n_pools"], T, dim, dtype=torch.bfloat16, pin_memory=True)
+    table_np = table.cpu().numpy().reshape(w["n_blocks"], ppb)
+    tok_np = (table_np[:, :, None].astype(np.int64) * cfg["page_tokens"] +
+              np.arange(cfg["page_tokens"])[None, None, :]).reshape(w["n_blocks"], T)
+    task_tok = [tok_np[i * task_blocks:(i + 1) * task_blocks].reshape(-1).tolist() for i in range(n_tasks)]
+    task_slots = list(range(task_blocks))
+
+    def e2e_step():
+        for i in range(n_tasks):
+            batch_gather_kv_caches(ptrs, host_staging, task_tok[i], task_slots, T, dim)
+            batch_scatter_kv_caches(ptrs, host_staging, task_tok[i], task_slots, T, dim)
+
+    e2e_steps = max(1, min(args.steps, 3))
+    e2e_step()
+    torch.cuda.synchronize(device)
+    if world > 1:
+        dist.barrier()
+    s2, p2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_wall = time.perf_counter()
+    s2.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    p2.record()
+    torch.cuda.synchronize(device)
+    e2e_ms = max(s2.elapsed_time(p2), (time.perf_counter() - t_wall) * 1e3)  # host list conversion counts
+    if world > 1:
+        t = torch.tensor([e2e_ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = t.item()
+    task_payload = task_blocks * w["n_pools"] * T * cfg["token_bytes"]
+    e2e_value = world * 4 * task_payload * n_tasks * e2e_steps / (e2e_ms * 1e-3) / 1e9
+    idx_bytes = n_tasks * 2 * (task_blocks * T + task_blocks) * 4
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = peaks()
+    gather_gbs = 2 * payload / (gather_ms * 1e-3) / 1e9
+    scatter_gbs = 2 * payload / (scatter_ms * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "u8", "data": "synthetic",
+        "config": {"workload": cfg["desc"], "pool_pages": pool_pages, "payload_bytes_per_direction": payload,
+                   "l2": "inputs (%.1f GiB staged per direction) far exceed the 126 MB L2; no flush needed"
+                         % (payload / 2 ** 30),
+                   "parity_sample_ok": parity_ok},
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": "MoveRowsKernel<gather>", "achieved": gather_gbs, "peak": peak,
+                     "peak_kind": peak_kind, "unit": "GB/s", "frac": gather_gbs / peak, "traffic": None,
+                     "algorithmic_bytes_per_launch": 2 * payload, "launch_ms": gather_ms,
+                     "scatter": {"kernel": "MoveRowsKernel<scatter>", "achieved": scatter_gbs,
+                                 "frac": scatter_gbs / peak, "launch_ms": scatter_ms}},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": task_payload * n_tasks + idx_bytes,
+                "d2h_bytes_per_step": task_payload * n_tasks,
+                "note": "%d save+load tasks of %d blocks, staging in pinned host memory, token-index lists "
+                        "converted per call" % (n_tasks, task_blocks)},
+        "gpu_launches": 2 * args.steps,
+    }
+    if world == 1:
+        threads = os.cpu_count() or 1
+        cpu_gbs, _, sample, _ = run_cpu_transfer(cfg, threads, 8, 1)
+        line["cpu_baseline"] = {"value": cpu_gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
+        if not args.no_prefix:
+            del w, staging, host_staging
+            torch.cuda.empty_cache()
+            pm, data = run_prefix_gpu(device, 20, 3)
+            cpu_pm, n_rep = run_prefix_cpu(data, threads)
+            pm["cpu_baseline"] = {"value": cpu_pm, "unit": "token-blocks/s", "cores": threads, "kind": "port",
+                                  "sample": "the whole workload, %d repetitions; omits the reference's per-key JSON "
+                                            "parse and string copies, so it over-states the reference" % n_rep}
+            line["prefix_match"] = pm
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-prefix", action="store_true", help="skip the prefix-match side measurement")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    cfg = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        main_reference(args, cfg, rank)
+    else:
+        main_b200(args, cfg, rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,261 @@
+/*
+ * kvcm_b200.h - C ABI of libkvcm_b200.so, the sm_100a implementation of the Tair KVCache
+ * Manager (KVCM) data-parallel hot path:
+ *
+ *   (1) paged-KV block gather / scatter between an engine's per-layer K/V page pools and the
+ *       contiguous staging blocks that storage backends read and write;
+ *   (2) chained 64-bit token-block hashing, a GPU-resident block index, and batched prefix /
+ *       sliding-window / batch-get matching against it.
+ *
+ * Every entry point names the interface of alibaba/tair-kvcache it stands in for (file:line
+ * relative to that project's root).  Conventions:
+ *   - plain pointers and sizes only; pointers prefixed d_ are device addresses (staging buffers
+ *     may also be pinned host memory reachable from the device);
+ *   - every call is asynchronous on `stream` (a cudaStream_t passed as void*, NULL = default
+ *     stream) unless its comment says it synchronises;
+ *   - the int32 return value is 0 (KVCM_OK) or one of the codes below; nothing throws and
+ *     nothing traps on the device.  Problems only the device can see (an index out of range,
+ *     a full table) are skipped and counted in a caller-owned status word.
+ *   - there is no CPU fallback: without a CUDA device every compute entry point returns
+ *     KVCM_ER_NO_DEVICE.
+ */
+#ifndef KVCM_B200_H_
+#define KVCM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define KVCM_API __attribute__((visibility("default")))
+#else
+#define KVCM_API
+#endif
+
+/* ------------------------------------------------------------------------------------------
+ * Return codes.  Transfer-side values are numerically those of ClientErrorCode
+ * (kv_cache_manager/client/include/common.h:11-63); manager-side values (index, match) are
+ * those of ErrorCode (kv_cache_manager/common/error_code.h:6-28) offset by KVCM_EC_BASE so the
+ * two families cannot collide in one int32.
+ * ---------------------------------------------------------------------------------------- */
+#define KVCM_OK 0
+#define KVCM_ER_INVALID_PARAMS 3                    /* ER_INVALID_PARAMS */
+#define KVCM_ER_INVALID_ADDRESS 107                 /* ER_INVALID_ADDRESS */
+#define KVCM_ER_UNSUPPORTED_MEMORY_TYPE 109         /* ER_UNSUPPORTED_MEMORY_TYPE */
+#define KVCM_ER_CUDAMEMCPY_ERROR 112                /* ER_CUDAMEMCPY_ERROR: a launch or copy failed */
+#define KVCM_ER_CUDA_STREAM_SYNCHRONIZE_ERROR 115   /* ER_CUDA_STREAM_SYNCHRONIZE_ERROR */
+#define KVCM_ER_NO_DEVICE 900                       /* no CUDA device / driver: there is no CPU path */
+#define KVCM_EC_BASE 1000
+#define KVCM_EC_ERROR (KVCM_EC_BASE + 1)            /* EC_ERROR */
+#define KVCM_EC_NOENT (KVCM_EC_BASE + 2)            /* EC_NOENT */
+#define KVCM_EC_BADARGS (KVCM_EC_BASE + 6)          /* EC_BADARGS */
+#define KVCM_EC_NOSPC (KVCM_EC_BASE + 9)            /* EC_NOSPC: index full */
+
+typedef void *kvcm_stream_t; /* cudaStream_t */
+
+KVCM_API int32_t kvcm_b200_abi_version(void);
+/* Binds the calling thread to CUDA device `device` for the calls that follow (one process drives
+ * one GPU; a host that already selected its device through the CUDA runtime it shares with this
+ * library need not call it).  Grid sizing uses the properties of the device current at first use. */
+KVCM_API int32_t kvcm_b200_set_device(int32_t device);
+KVCM_API const char *kvcm_b200_error_string(int32_t code);
+/* Number of SMs and L2 bytes of the current device (synchronous, cached). */
+KVCM_API int32_t kvcm_b200_device_info(int32_t *sm_count, int64_t *l2_bytes, int64_t *free_bytes,
+                                       int64_t *total_bytes);
+
+/* ------------------------------------------------------------------------------------------
+ * (1) Gather / scatter of paged KV.
+ *
+ * Replaces the Triton kernels kv_cache_batch_gather_kernel / kv_cache_batch_scatter_kernel and
+ * their wrappers batch_gather_kv_caches / batch_scatter_kv_caches
+ * (kv_cache_manager/py_connector/kernel/batch_gather_scatter_helper.py:33-136, 139-248).
+ *
+ * A pool is one K or V tensor of one layer, row-major [pool_rows, row_bytes].  d_pool_ptrs is
+ * the device array of n_pools pool base addresses (the reference's int64 `kv_caches_ptrs_tensor`,
+ * order layer0.K, layer0.V, layer1.K, ...).  Block b owns rows_per_block rows
+ * d_row_idx[b*rows_per_block + t] of every pool, and staging slot d_slot_idx[b] (NULL = slot b).
+ * A staging slot is [n_pools, rows_per_block, row_bytes] contiguous bytes:
+ *
+ *   gather :  staging[slot][p][t][:] = pool_p[row_idx[b][t]][:]
+ *   scatter:  pool_p[row_idx[b][t]][:] = staging[slot][p][t][:]
+ *
+ * "tokens" form: a row is one token (row_bytes = dim * itemsize) and d_row_idx is the reference's
+ * flat block_token_indices.  "pages" form: a row is one engine page (row_bytes = page_tokens *
+ * dim * itemsize) and d_row_idx is the engine's block table itself, which removes
+ * generate_blocks_idx (kv_cache_manager/py_connector/vllm/v1_connector.py:308-320).  The byte
+ * result is identical when the token indices of a block are whole pages.
+ *
+ * Rows outside [0, pool_rows) and slots outside [0, n_slots) are skipped, never dereferenced;
+ * if d_status is not NULL, d_status[0] is incremented once per skipped (pool,row) pair and
+ * d_status[1] keeps 1 + the largest offending block number.  The caller zeroes d_status.
+ * Scattering the same row twice in one call is a data race, as in the reference.
+ * Fastest when row_bytes and all base addresses are multiples of 16; any alignment is correct.
+ * ---------------------------------------------------------------------------------------- */
+KVCM_API int32_t kvcm_b200_gather_tokens(const void *const *d_pool_ptrs, int32_t n_pools, void *staging,
+                                         int64_t n_slots, const int32_t *d_token_idx, const int32_t *d_slot_idx,
+                                         int32_t n_blocks, int32_t tokens_per_block, int64_t bytes_per_token,
+                                         int64_t pool_tokens, uint32_t *d_status, kvcm_stream_t stream);
+KVCM_API int32_t kvcm_b200_scatter_tokens(const void *const *d_pool_ptrs, int32_t n_pools, const void *staging,
+                                          int64_t n_slots, const int32_t *d_token_idx, const int32_t *d_slot_idx,
+                                          int32_t n_blocks, int32_t tokens_per_block, int64_t bytes_per_token,
+                                          int64_t pool_tokens, uint32_t *d_status, kvcm_stream_t stream);
+KVCM_API int32_t kvcm_b200_gather_pages(const void *const *d_pool_ptrs, int32_t n_pools, void *staging,
+                                        int64_t n_slots, const int32_t *d_page_table, const int32_t *d_slot_idx,
+                                        int32_t n_blocks, int32_t pages_per_block, int64_t page_bytes,
+                                        int64_t pool_pages, uint32_t *d_status, kvcm_stream_t stream);
+KVCM_API int32_t kvcm_b200_scatter_pages(const void *const *d_pool_ptrs, int32_t n_pools, const void *staging,
+                                         int64_t n_slots, const int32_t *d_page_table, const int32_t *d_slot_idx,
+                                         int32_t n_blocks, int32_t pages_per_block, int64_t page_bytes,
+                                         int64_t pool_pages, uint32_t *d_status, kvcm_stream_t stream);
+
+/* Legacy single-block form: kv_cache_gather_kernel / kv_cache_scatter_kernel and gather_kv_caches /
+ * scatter_kv_caches (kv_cache_manager/py_connector/kernel/gather_scatter_helper.py:10-172).
+ * d_layer_ptrs[l] is a layer tensor [2, total_tokens, hidden_bytes]; staging is
+ * [n_layers, 2, n_tokens, hidden_bytes].  A token index >= total_tokens (or < 0) is skipped
+ * silently, as the reference kernels do (:36-38, :87-89). */
+KVCM_API int32_t kvcm_b200_gather_legacy(const void *const *d_layer_ptrs, int32_t n_layers, int64_t total_tokens,
+                                         void *staging, const int32_t *d_token_idx, int32_t n_tokens,
+                                         int64_t hidden_bytes, kvcm_stream_t stream);
+KVCM_API int32_t kvcm_b200_scatter_legacy(const void *const *d_layer_ptrs, int32_t n_layers, int64_t total_tokens,
+                                          const void *staging, const int32_t *d_token_idx, int32_t n_tokens,
+                                          int64_t hidden_bytes, kvcm_stream_t stream);
+
+/* Batched iov copy: replaces the per-Iov cudaMemcpyAsync loops of LocalFileSdk::DoGet / DoPut
+ * (kv_cache_manager/client/src/internal/sdk/local_file_sdk.cc:223-245, 326-353) and
+ * Hf3fsUsrbioClient::CopyIovs (kv_cache_manager/client/src/internal/sdk/hf3fs_usrbio_client.cc:478-505)
+ * with one launch.  Segment i copies d_segs[i].bytes bytes from src to dst; the host helper
+ * kvcm_b200_iovs_to_segments lays the reference's Iov list (kv_cache_manager/client/include/common.h:99-116)
+ * against a contiguous block string, honouring `ignore` (bytes skipped, offset still advanced). */
+typedef struct kvcm_b200_seg {
+    void *dst;
+    const void *src;
+    uint64_t bytes;
+} kvcm_b200_seg_t;
+
+typedef struct kvcm_b200_iov {
+    uint8_t type;   /* MemoryType: 0 CPU, 1 GPU */
+    uint8_t ignore; /* bool */
+    uint8_t pad_[6];
+    void *base;
+    uint64_t size;
+} kvcm_b200_iov_t;
+
+KVCM_API int32_t kvcm_b200_copy_segments(const kvcm_b200_seg_t *d_segs, int32_t n_segs, kvcm_stream_t stream);
+/* Host-only: direction 0 = iovs -> block string (Put), 1 = block string -> iovs (Get).  Writes at
+ * most n_iovs segments to h_segs_out, returns their number in *n_segs_out and the bytes the iov
+ * list spans in *span_bytes_out. */
+KVCM_API int32_t kvcm_b200_iovs_to_segments(const kvcm_b200_iov_t *h_iovs, int32_t n_iovs, void *block_string,
+                                            int32_t direction, kvcm_b200_seg_t *h_segs_out, int32_t *n_segs_out,
+                                            uint64_t *span_bytes_out);
+
+/* Debug check of transferred buffers: replaces the GetIovsCrcDevice kernel
+ * (kv_cache_manager/client/src/internal/sdk/sdk_buffer_check_util.cu:21-44).  d_crc_out[i] = reflected
+ * CRC-32 (poly 0xEDB88320) of the first and last cal_bytes bytes of segment i (src, bytes). */
+KVCM_API int32_t kvcm_b200_iov_crc(const kvcm_b200_seg_t *d_segs, int32_t n_segs, uint64_t cal_bytes,
+                                   uint32_t *d_crc_out, kvcm_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * (2a) Chained token-block hash.
+ *
+ * Replaces GenKeyVector (kv_cache_manager/manager/cache_manager.cc:76-87) over hashInt64Array
+ * (kv_cache_manager/manager/hash_util.h:8-24) for a whole batch of requests, and ApplyPrefixHash
+ * (kv_cache_manager/optimizer/trace_converter/trace_util.cc:47-56) with block_size = 1.
+ * Request r owns tokens[tok_off[r], tok_off[r+1]) and writes floor(len/block_size) keys at
+ * d_keys[key_off[r] ...]; the hash state starts at 0 per request and is carried across blocks;
+ * a trailing partial block is dropped.  u32 tokens are zero-extended (token ids are non-negative).
+ * n_tokens_total is the extent of d_tokens (reads stay inside it).
+ * ---------------------------------------------------------------------------------------- */
+KVCM_API int32_t kvcm_b200_hash_blocks_u32(const uint32_t *d_tokens, int64_t n_tokens_total, const int64_t *d_tok_off,
+                                           int32_t n_req, int32_t block_size, int64_t *d_keys,
+                                           const int64_t *d_key_off, kvcm_stream_t stream);
+KVCM_API int32_t kvcm_b200_hash_blocks_i64(const int64_t *d_tokens, int64_t n_tokens_total, const int64_t *d_tok_off,
+                                           int32_t n_req, int32_t block_size, int64_t *d_keys,
+                                           const int64_t *d_key_off, kvcm_stream_t stream);
+/* Host-only helper: key_off[r] = sum_{q<r} floor((tok_off[q+1]-tok_off[q]) / block_size); n_req+1 entries. */
+KVCM_API int32_t kvcm_b200_key_offsets(const int64_t *h_tok_off, int32_t n_req, int32_t block_size,
+                                       int64_t *h_key_off);
+
+/* ------------------------------------------------------------------------------------------
+ * (2b) Block index: the GPU-resident replica of MetaIndexer's key -> locations map that the
+ * matchers probe (kv_cache_manager/meta/meta_indexer.cc:419-440, 650-752;
+ * kv_cache_manager/meta/meta_local_backend.cc:253-327; kv_cache_manager/common/concurrent_hash_map.h).
+ * Open addressing, 16-byte slots {int64 key, uint64 value}.  Every int64 is a legal key.
+ *
+ * The value word summarises the key's location map for the matchers
+ * (kv_cache_manager/manager/select_location_policy.cc:8-38).  A location has a status
+ * (kv_cache_manager/manager/cache_location.h:44-50) and a storage class c in [0,16) - the
+ * DataStorageType, or a per-storage id under a named policy:
+ *   bit c        (0..15)  some location of class c is CLS_SERVING
+ *   bit 16 + c   (16..31) some location of class c has status != CLS_NOT_FOUND
+ *   bit 32                the location map is non-empty
+ *   bit 63                always set in a stored value (lookups return 0 for an absent key)
+ * `avail_mask` arguments carry bit c set when the active SelectLocationPolicy gives class c a
+ * weight > 0 (all classes with the default static weights).
+ * ---------------------------------------------------------------------------------------- */
+#define KVCM_VAL_SERVING(c) (1ull << (c))
+#define KVCM_VAL_WRITABLE(c) (1ull << (16 + (c)))
+#define KVCM_VAL_NONEMPTY (1ull << 32)
+#define KVCM_VAL_PRESENT (1ull << 63)
+#define KVCM_AVAIL_ALL 0xFFFFu
+
+typedef struct kvcm_b200_index kvcm_b200_index_t;
+
+/* Allocates a table for at least max_keys keys at load factor <= 0.5 on the current device
+ * (synchronous).  Insertions beyond the capacity are refused and counted, never spin. */
+KVCM_API int32_t kvcm_b200_index_create(int64_t max_keys, kvcm_b200_index_t **out);
+KVCM_API int32_t kvcm_b200_index_destroy(kvcm_b200_index_t *index);
+KVCM_API int32_t kvcm_b200_index_clear(kvcm_b200_index_t *index, kvcm_stream_t stream);
+/* Number of slots, and (synchronous on `stream`) the number of live keys. */
+KVCM_API int32_t kvcm_b200_index_stats(kvcm_b200_index_t *index, int64_t *slots, int64_t *live_keys,
+                                       kvcm_stream_t stream);
+/* Insert or overwrite: value[i] (or `uniform_value` when d_values is NULL) is stored with
+ * KVCM_VAL_PRESENT or-ed in.  Mirrors the write side MetaIndexer::Put / Update reduces to for the
+ * matchers.  d_status[0] counts keys refused because the table is full. */
+KVCM_API int32_t kvcm_b200_index_upsert(kvcm_b200_index_t *index, const int64_t *d_keys, const uint64_t *d_values,
+                                        uint64_t uniform_value, int64_t n, uint32_t *d_status, kvcm_stream_t stream);
+KVCM_API int32_t kvcm_b200_index_erase(kvcm_b200_index_t *index, const int64_t *d_keys, int64_t n,
+                                       kvcm_stream_t stream);
+/* d_values_out[i] = stored value of key i, 0 when absent (MetaIndexer::Get -> EC_NOENT). */
+KVCM_API int32_t kvcm_b200_index_lookup(kvcm_b200_index_t *index, const int64_t *d_keys, int64_t n,
+                                        uint64_t *d_values_out, kvcm_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * (2b) Matchers.  Requests are given in CSR form: request r owns d_keys[key_off[r], key_off[r+1]).
+ * ---------------------------------------------------------------------------------------- */
+
+/* MetaSearcher::PrefixMatch (kv_cache_manager/manager/meta_searcher.cc:120-145 over :74-118).
+ * Keys with IsIndexInMaskRange true (kv_cache_manager/manager/cache_location.cc:9-21) are removed
+ * first: d_mask_off[r] masks the first mask_off[r] keys of request r (BlockMaskOffset);
+ * d_mask_bits is a per-key byte array aligned with d_keys (BlockMaskVector, padded with 0);
+ * either or both may be NULL.  d_len_out[r] = number of leading unmasked keys that have a
+ * SERVING location with weight > 0. */
+KVCM_API int32_t kvcm_b200_match_prefix(kvcm_b200_index_t *index, const int64_t *d_keys, const int64_t *d_key_off,
+                                        int32_t n_req, const int64_t *d_mask_off, const uint8_t *d_mask_bits,
+                                        uint32_t avail_mask, int32_t *d_len_out, kvcm_stream_t stream);
+
+/* MetaSearcher::ReverseRollSlideWindowMatch (kv_cache_manager/manager/meta_searcher.cc:196-265)
+ * with the argument guard of kv_cache_manager/manager/cache_manager.cc:993-997.
+ * d_base_out[r] = start of the rightmost window of sw_blocks consecutive servable keys, -1 when
+ * there is none, -2 when the request has fewer than sw_blocks keys (EC_BADARGS for that request).
+ * sw_blocks <= 0 returns KVCM_EC_BADARGS for the call (0 never terminates in the reference). */
+KVCM_API int32_t kvcm_b200_match_sw(kvcm_b200_index_t *index, const int64_t *d_keys, const int64_t *d_key_off,
+                                    int32_t n_req, int32_t sw_blocks, uint32_t avail_mask, int32_t *d_base_out,
+                                    kvcm_stream_t stream);
+
+/* MetaSearcher::BatchGetBestLocation / BatchGetLocation (kv_cache_manager/manager/meta_searcher.cc:147-194,
+ * 267-310): per key, no early stop.  d_flags_out[i]: bit0 a location would be returned (servable),
+ * bit1 key exists, bit2 location map non-empty, bit3 ExistsForWrite (select_location_policy.cc:29-38). */
+#define KVCM_FLAG_SERVABLE 1u
+#define KVCM_FLAG_EXISTS 2u
+#define KVCM_FLAG_NONEMPTY 4u
+#define KVCM_FLAG_WRITABLE 8u
+KVCM_API int32_t kvcm_b200_batch_get(kvcm_b200_index_t *index, const int64_t *d_keys, int64_t n, uint32_t avail_mask,
+                                     uint8_t *d_flags_out, kvcm_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KVCM_B200_H_ */

@@ -1,0 +1,128 @@
+"""ctypes binding of libkvcm_b200.so - the only way this package reaches the GPU.
+
+There is no CPU path: if the library has not been built or cannot be loaded, importing this
+module's `lib()` raises, and every wrapper raises KvcmError on a non-zero return code.
+"""
+import ctypes
+import os
+import threading
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libkvcm_b200.so")
+
+KVCM_OK = 0
+KVCM_ER_INVALID_PARAMS = 3
+KVCM_ER_INVALID_ADDRESS = 107
+KVCM_ER_UNSUPPORTED_MEMORY_TYPE = 109
+KVCM_ER_CUDAMEMCPY_ERROR = 112
+KVCM_ER_CUDA_STREAM_SYNCHRONIZE_ERROR = 115
+KVCM_ER_NO_DEVICE = 900
+KVCM_EC_BASE = 1000
+KVCM_EC_ERROR = KVCM_EC_BASE + 1
+KVCM_EC_NOENT = KVCM_EC_BASE + 2
+KVCM_EC_BADARGS = KVCM_EC_BASE + 6
+KVCM_EC_NOSPC = KVCM_EC_BASE + 9
+
+VAL_NONEMPTY = 1 << 32
+VAL_PRESENT = 1 << 63
+AVAIL_ALL = 0xFFFF
+FLAG_SERVABLE, FLAG_EXISTS, FLAG_NONEMPTY, FLAG_WRITABLE = 1, 2, 4, 8
+
+_vp = ctypes.c_void_p
+_i32 = ctypes.c_int32
+_i64 = ctypes.c_int64
+_u32 = ctypes.c_uint32
+_u64 = ctypes.c_uint64
+
+
+class Seg(ctypes.Structure):
+    _fields_ = [("dst", _vp), ("src", _vp), ("bytes", _u64)]
+
+
+class Iov(ctypes.Structure):
+    _fields_ = [("type", ctypes.c_uint8), ("ignore", ctypes.c_uint8), ("pad_", ctypes.c_uint8 * 6), ("base", _vp),
+                ("size", _u64)]
+
+
+# name -> argtypes, in the order of include/kvcm_b200.h; every function returns int32 unless noted.
+_MOVE = [_vp, _i32, _vp, _i64, _vp, _vp, _i32, _i32, _i64, _i64, _vp, _vp]
+_LEGACY = [_vp, _i32, _i64, _vp, _vp, _i32, _i64, _vp]
+_HASH = [_vp, _i64, _vp, _i32, _i32, _vp, _vp, _vp]
+SIGNATURES = {
+    "kvcm_b200_abi_version": [],
+    "kvcm_b200_set_device": [_i32],
+    "kvcm_b200_error_string": [_i32],
+    "kvcm_b200_device_info": [_vp, _vp, _vp, _vp],
+    "kvcm_b200_gather_tokens": _MOVE,
+    "kvcm_b200_scatter_tokens": _MOVE,
+    "kvcm_b200_gather_pages": _MOVE,
+    "kvcm_b200_scatter_pages": _MOVE,
+    "kvcm_b200_gather_legacy": _LEGACY,
+    "kvcm_b200_scatter_legacy": _LEGACY,
+    "kvcm_b200_copy_segments": [_vp, _i32, _vp],
+    "kvcm_b200_iovs_to_segments": [_vp, _i32, _vp, _i32, _vp, _vp, _vp],
+    "kvcm_b200_iov_crc": [_vp, _i32, _u64, _vp, _vp],
+    "kvcm_b200_hash_blocks_u32": _HASH,
+    "kvcm_b200_hash_blocks_i64": _HASH,
+    "kvcm_b200_key_offsets": [_vp, _i32, _i32, _vp],
+    "kvcm_b200_index_create": [_i64, _vp],
+    "kvcm_b200_index_destroy": [_vp],
+    "kvcm_b200_index_clear": [_vp, _vp],
+    "kvcm_b200_index_stats": [_vp, _vp, _vp, _vp],
+    "kvcm_b200_index_upsert": [_vp, _vp, _vp, _u64, _i64, _vp, _vp],
+    "kvcm_b200_index_erase": [_vp, _vp, _i64, _vp],
+    "kvcm_b200_index_lookup": [_vp, _vp, _i64, _vp, _vp],
+    "kvcm_b200_match_prefix": [_vp, _vp, _vp, _i32, _vp, _vp, _u32, _vp, _vp],
+    "kvcm_b200_match_sw": [_vp, _vp, _vp, _i32, _i32, _u32, _vp, _vp],
+    "kvcm_b200_batch_get": [_vp, _vp, _i64, _u32, _vp, _vp],
+}
+
+
+class KvcmError(RuntimeError):
+    def __init__(self, code, what):
+        self.code = code
+        super().__init__("%s failed with code %d (%s)" % (what, code, error_string(code)))
+
+
+_lib = None
+
+
+def lib():
+    """The loaded library.  Raises if it is missing: this package has no fallback."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError("%s is missing: build it with __graft_entry__.build() "
+                              "(nvcc, sm_100a); there is no CPU fallback" % LIB_PATH)
+        L = ctypes.CDLL(LIB_PATH)
+        for name, argtypes in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.argtypes = argtypes
+            fn.restype = ctypes.c_char_p if name == "kvcm_b200_error_string" else _i32
+        _lib = L
+    return _lib
+
+
+def error_string(code):
+    return lib().kvcm_b200_error_string(code).decode()
+
+
+def check(code, what):
+    if code != KVCM_OK:
+        raise KvcmError(code, what)
+
+
+def call(name, *args):
+    check(getattr(lib(), name)(*args), name)
+
+
+_tls = threading.local()
+
+
+def bind_device(index):
+    """Make CUDA device `index` current for this thread inside the library's own CUDA runtime
+    (it is linked statically, so torch.cuda.set_device does not reach it)."""
+    index = 0 if index is None else int(index)
+    if getattr(_tls, "device", None) != index:
+        call("kvcm_b200_set_device", index)
+        _tls.device = index

@@ -1,0 +1,400 @@
+// GPU-resident block index and the batched matchers that probe it (sm_100a).
+//
+// The index is the device replica of MetaIndexer's key -> location-map table
+// (kv_cache_manager/meta/meta_indexer.cc:419-440,650-752; kv_cache_manager/meta/meta_local_backend.cc:253-327)
+// reduced to what the matchers read: one 64-bit summary word per key (see kvcm_b200.h).
+// The matchers stand in for MetaSearcher::PrefixMatch, ReverseRollSlideWindowMatch,
+// BatchGetBestLocation and BatchGetLocation (kv_cache_manager/manager/meta_searcher.cc:74-310).
+//
+// Layout in HBM: a power-of-two array of 16-byte slots {int64 key, uint64 value}, open
+// addressing with linear probing at load factor <= 0.5, slot = fmix64(key) (chained block
+// hashes are not uniformly mixed in their low bits).  A probe is one aligned 128-bit load; the
+// expected chain is under two slots, so a lookup costs one or two 32-byte sectors.  Two key
+// values are reserved as EMPTY and TOMBSTONE markers; real keys with those values live in two
+// side cells, so every int64 stays a legal key.  All loops are bounded by the slot count.
+#include "kvcm_common.cuh"
+
+struct kvcm_b200_index {
+    ulonglong2 *slots;
+    uint64_t *cells;  // [0],[1]: values of the two reserved keys; [2]: live key count
+    uint64_t n_slots;
+    uint64_t max_live;
+    int device;
+};
+
+namespace kvcm {
+namespace {
+
+constexpr uint64_t kEmptyKey = 0x8000000000000000ull;
+constexpr uint64_t kTombKey = 0x8000000000000001ull;
+constexpr int kMatchWarps = 8;
+
+struct IndexView {
+    ulonglong2 *slots;
+    uint64_t *cells;
+    uint64_t mask;
+    uint64_t max_live;
+};
+
+__host__ __device__ __forceinline__ uint64_t Mix(uint64_t k) {
+    k ^= k >> 33;
+    k *= 0xff51afd7ed558ccdull;
+    k ^= k >> 33;
+    k *= 0xc4ceb9fe1a85ec53ull;
+    k ^= k >> 33;
+    return k;
+}
+
+__device__ __forceinline__ ulonglong2 LoadSlot(const ulonglong2 *p) {
+    ulonglong2 s;
+    asm volatile("ld.global.v2.u64 {%0,%1}, [%2];\n" : "=l"(s.x), "=l"(s.y) : "l"(p));
+    return s;
+}
+
+// Value word of a key, 0 when absent (MetaIndexer::Get -> EC_NOENT).
+__device__ __forceinline__ uint64_t Lookup(const IndexView &ix, uint64_t key) {
+    if (key == kEmptyKey) return ix.cells[0];
+    if (key == kTombKey) return ix.cells[1];
+    uint64_t slot = Mix(key) & ix.mask;
+    for (uint64_t probe = 0; probe <= ix.mask; ++probe) {
+        const ulonglong2 s = LoadSlot(ix.slots + slot);
+        if (s.x == key) return s.y;
+        if (s.x == kEmptyKey) return 0;
+        slot = (slot + 1) & ix.mask;
+    }
+    return 0;
+}
+
+// A key is a hit for the matchers when some location is SERVING in a storage class whose
+// policy weight is > 0 (kv_cache_manager/manager/select_location_policy.cc:8-27).
+__device__ __forceinline__ bool Servable(uint64_t value, uint32_t avail_mask) {
+    return (static_cast<uint32_t>(value) & avail_mask & 0xFFFFu) != 0;
+}
+
+__global__ void ClearKernel(IndexView ix) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i <= ix.mask; i += stride) {
+        ix.slots[i] = make_ulonglong2(kEmptyKey, 0);
+    }
+    if (blockIdx.x == 0 && threadIdx.x < 3) ix.cells[threadIdx.x] = 0;
+}
+
+__global__ void UpsertKernel(IndexView ix, const int64_t *__restrict__ keys, const uint64_t *__restrict__ values,
+                             uint64_t uniform_value, int64_t n, uint32_t *status) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint64_t key = static_cast<uint64_t>(keys[i]);
+    const uint64_t value = (values != nullptr ? values[i] : uniform_value) | KVCM_VAL_PRESENT;
+    if (key == kEmptyKey || key == kTombKey) {
+        const uint64_t old = atomicExch(reinterpret_cast<unsigned long long *>(&ix.cells[key - kEmptyKey]), value);
+        if (old == 0) atomicAdd(reinterpret_cast<unsigned long long *>(&ix.cells[2]), 1ull);
+        return;
+    }
+    unsigned long long *words = reinterpret_cast<unsigned long long *>(ix.slots);
+    uint64_t slot = Mix(key) & ix.mask;
+    bool reserved = false;
+    for (uint64_t probe = 0; probe <= ix.mask; ++probe) {
+        uint64_t seen = LoadSlot(ix.slots + slot).x;
+        if (seen == kEmptyKey) {
+            if (!reserved) {
+                // Take a seat before claiming a slot so the table can never fill up completely.
+                const uint64_t live = atomicAdd(reinterpret_cast<unsigned long long *>(&ix.cells[2]), 1ull);
+                if (live >= ix.max_live) {
+                    atomicAdd(reinterpret_cast<unsigned long long *>(&ix.cells[2]), ~0ull);  // -1
+                    if (status != nullptr) atomicAdd(&status[0], 1u);
+                    return;
+                }
+                reserved = true;
+            }
+            seen = atomicCAS(&words[2 * slot], kEmptyKey, key);
+            if (seen == kEmptyKey) {
+                atomicExch(&words[2 * slot + 1], value);
+                return;
+            }
+        }
+        if (seen == key) {
+            // Present already (or inserted by a duplicate of this key in the same batch).
+            if (reserved) atomicAdd(reinterpret_cast<unsigned long long *>(&ix.cells[2]), ~0ull);
+            atomicExch(&words[2 * slot + 1], value);
+            return;
+        }
+        slot = (slot + 1) & ix.mask;
+    }
+    if (reserved) atomicAdd(reinterpret_cast<unsigned long long *>(&ix.cells[2]), ~0ull);
+    if (status != nullptr) atomicAdd(&status[0], 1u);
+}
+
+__global__ void EraseKernel(IndexView ix, const int64_t *__restrict__ keys, int64_t n) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint64_t key = static_cast<uint64_t>(keys[i]);
+    if (key == kEmptyKey || key == kTombKey) {
+        const uint64_t old = atomicExch(reinterpret_cast<unsigned long long *>(&ix.cells[key - kEmptyKey]), 0ull);
+        if (old != 0) atomicAdd(reinterpret_cast<unsigned long long *>(&ix.cells[2]), ~0ull);
+        return;
+    }
+    unsigned long long *words = reinterpret_cast<unsigned long long *>(ix.slots);
+    uint64_t slot = Mix(key) & ix.mask;
+    for (uint64_t probe = 0; probe <= ix.mask; ++probe) {
+        const uint64_t seen = LoadSlot(ix.slots + slot).x;
+        if (seen == kEmptyKey) return;
+        if (seen == key) {
+            // The slot stays occupied (tombstone) so that probe chains through it stay intact.
+            if (atomicCAS(&words[2 * slot], key, kTombKey) == key) {
+                atomicExch(&words[2 * slot + 1], 0ull);
+                atomicAdd(reinterpret_cast<unsigned long long *>(&ix.cells[2]), ~0ull);
+            }
+            return;
+        }
+        slot = (slot + 1) & ix.mask;
+    }
+}
+
+__global__ void LookupKernel(IndexView ix, const int64_t *__restrict__ keys, int64_t n, uint64_t *__restrict__ out) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = Lookup(ix, static_cast<uint64_t>(keys[i]));
+}
+
+__global__ void BatchGetKernel(IndexView ix, const int64_t *__restrict__ keys, int64_t n, uint32_t avail_mask,
+                               uint8_t *__restrict__ flags) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint64_t v = Lookup(ix, static_cast<uint64_t>(keys[i]));
+    uint32_t f = 0;
+    if (v != 0) {
+        f |= KVCM_FLAG_EXISTS;
+        if (v & KVCM_VAL_NONEMPTY) f |= KVCM_FLAG_NONEMPTY;
+        if (Servable(v, avail_mask)) f |= KVCM_FLAG_SERVABLE;
+        if ((static_cast<uint32_t>(v >> 16) & avail_mask & 0xFFFFu) != 0) f |= KVCM_FLAG_WRITABLE;
+    }
+    flags[i] = static_cast<uint8_t>(f);
+}
+
+// One warp per request; each pass probes 32 consecutive keys, one per lane, and a ballot finds
+// the first unmasked key that is not servable.  The warp leaves at that key: the reference
+// probes every key of the request and then stops counting at the first miss, which yields the
+// same length.
+__global__ void __launch_bounds__(kMatchWarps * 32)
+    PrefixMatchKernel(IndexView ix, const int64_t *__restrict__ keys, const int64_t *__restrict__ key_off,
+                      int32_t n_req, const int64_t *__restrict__ mask_off, const uint8_t *__restrict__ mask_bits,
+                      uint32_t avail_mask, int32_t *__restrict__ len_out) {
+    const int32_t req = blockIdx.x * kMatchWarps + (threadIdx.x >> 5);
+    if (req >= n_req) return;
+    const uint32_t lane = LaneId();
+    const int64_t beg = key_off[req];
+    const int64_t n = key_off[req + 1] - beg;
+    const int64_t skip = mask_off != nullptr ? mask_off[req] : 0;
+    int32_t matched = 0;
+    for (int64_t base = 0; base < n; base += 32) {
+        const int64_t i = base + lane;
+        bool counted = false, stop = false;
+        if (i < n) {
+            const bool masked = i < skip || (mask_bits != nullptr && mask_bits[beg + i] != 0);
+            if (!masked) {
+                const bool hit = Servable(Lookup(ix, static_cast<uint64_t>(keys[beg + i])), avail_mask);
+                counted = hit;
+                stop = !hit;
+            }
+        }
+        const uint32_t stops = __ballot_sync(0xffffffffu, stop);
+        const uint32_t hits = __ballot_sync(0xffffffffu, counted);
+        if (stops != 0) {
+            const uint32_t below = (1u << (__ffs(stops) - 1)) - 1u;
+            matched += __popc(hits & below);
+            break;
+        }
+        matched += __popc(hits);
+    }
+    if (lane == 0) len_out[req] = matched;
+}
+
+// Rightmost window of `sw` consecutive servable keys.  One warp per request scans 32 keys per
+// pass from the right end; `run` is the length of the servable run that ends (exclusively) at
+// `right_end` and reaches down to the scan position.  The first time a run reaches `sw` keys
+// its right-most `sw` keys are the answer: this is where the reference's roll-back loop stops,
+// because every window it skips contains a known miss.
+__global__ void __launch_bounds__(kMatchWarps * 32)
+    SwMatchKernel(IndexView ix, const int64_t *__restrict__ keys, const int64_t *__restrict__ key_off, int32_t n_req,
+                  int32_t sw, uint32_t avail_mask, int32_t *__restrict__ base_out) {
+    const int32_t req = blockIdx.x * kMatchWarps + (threadIdx.x >> 5);
+    if (req >= n_req) return;
+    const uint32_t lane = LaneId();
+    const int64_t beg = key_off[req];
+    const int64_t n = key_off[req + 1] - beg;
+    if (n < sw) {
+        if (lane == 0) base_out[req] = -2;
+        return;
+    }
+    int64_t run = 0, right_end = n, found = -1;
+    for (int64_t hi = n; hi > 0 && found < 0; hi -= 32) {
+        if (hi + run < sw) break;  // not enough keys left for a window
+        const int64_t lo = hi - 32;
+        const int64_t i = lo + lane;
+        const bool hit = i >= 0 && Servable(Lookup(ix, static_cast<uint64_t>(keys[beg + i])), avail_mask);
+        const uint32_t bits = __ballot_sync(0xffffffffu, hit);
+        int cur = 32;  // bits [0, cur) are still to be scanned, from bit cur-1 downwards
+        while (cur > 0) {
+            const uint32_t x = bits << (32 - cur);
+            int ones = __clz(~x);
+            ones = ones < cur ? ones : cur;
+            run += ones;
+            cur -= ones;
+            if (run >= sw) {
+                found = right_end - sw;
+                break;
+            }
+            if (cur > 0) {
+                int zeros = __clz(bits << (32 - cur));
+                zeros = zeros < cur ? zeros : cur;
+                cur -= zeros;
+                run = 0;
+                right_end = lo + cur;
+            }
+        }
+    }
+    if (lane == 0) base_out[req] = static_cast<int32_t>(found);
+}
+
+IndexView View(const kvcm_b200_index *ix) {
+    IndexView v;
+    v.slots = ix->slots;
+    v.cells = ix->cells;
+    v.mask = ix->n_slots - 1;
+    v.max_live = ix->max_live;
+    return v;
+}
+
+unsigned GridFor(int64_t n, int threads) { return static_cast<unsigned>((n + threads - 1) / threads); }
+
+}  // namespace
+}  // namespace kvcm
+
+extern "C" {
+
+int32_t kvcm_b200_index_create(int64_t max_keys, kvcm_b200_index_t **out) {
+    if (out == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    *out = nullptr;
+    if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
+    if (max_keys < 0 || max_keys > (1ll << 36)) return KVCM_EC_BADARGS;
+    uint64_t n_slots = 1024;
+    while (n_slots < 2ull * static_cast<uint64_t>(max_keys)) n_slots <<= 1;
+    auto *ix = new kvcm_b200_index();
+    ix->n_slots = n_slots;
+    ix->max_live = n_slots - n_slots / 8;  // the matchers rely on at least one EMPTY slot per chain
+    cudaGetDevice(&ix->device);
+    if (cudaMalloc(&ix->slots, n_slots * sizeof(ulonglong2)) != cudaSuccess ||
+        cudaMalloc(&ix->cells, 3 * sizeof(uint64_t)) != cudaSuccess) {
+        cudaGetLastError();
+        if (ix->slots) cudaFree(ix->slots);
+        delete ix;
+        return KVCM_EC_NOSPC;
+    }
+    const int32_t rc = kvcm_b200_index_clear(ix, nullptr);
+    if (rc != KVCM_OK || cudaStreamSynchronize(nullptr) != cudaSuccess) {
+        cudaFree(ix->slots);
+        cudaFree(ix->cells);
+        delete ix;
+        return KVCM_ER_CUDA_STREAM_SYNCHRONIZE_ERROR;
+    }
+    *out = ix;
+    return KVCM_OK;
+}
+
+int32_t kvcm_b200_index_destroy(kvcm_b200_index_t *ix) {
+    if (ix == nullptr) return KVCM_OK;
+    cudaFree(ix->slots);
+    cudaFree(ix->cells);
+    delete ix;
+    return KVCM_OK;
+}
+
+int32_t kvcm_b200_index_clear(kvcm_b200_index_t *ix, kvcm_stream_t stream) {
+    if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    const unsigned grid = static_cast<unsigned>(kvcm::GetDeviceInfo().sm_count * 8);
+    kvcm::ClearKernel<<<grid, 256, 0, kvcm::AsStream(stream)>>>(kvcm::View(ix));
+    return kvcm::LaunchStatus();
+}
+
+int32_t kvcm_b200_index_stats(kvcm_b200_index_t *ix, int64_t *slots, int64_t *live_keys, kvcm_stream_t stream) {
+    if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (slots != nullptr) *slots = static_cast<int64_t>(ix->n_slots);
+    if (live_keys != nullptr) {
+        uint64_t live = 0;
+        if (cudaMemcpyAsync(&live, ix->cells + 2, sizeof(live), cudaMemcpyDeviceToHost, kvcm::AsStream(stream)) !=
+                cudaSuccess ||
+            cudaStreamSynchronize(kvcm::AsStream(stream)) != cudaSuccess) {
+            return KVCM_ER_CUDA_STREAM_SYNCHRONIZE_ERROR;
+        }
+        *live_keys = static_cast<int64_t>(live);
+    }
+    return KVCM_OK;
+}
+
+int32_t kvcm_b200_index_upsert(kvcm_b200_index_t *ix, const int64_t *d_keys, const uint64_t *d_values,
+                               uint64_t uniform_value, int64_t n, uint32_t *d_status, kvcm_stream_t stream) {
+    if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (n < 0) return KVCM_EC_BADARGS;
+    if (n == 0) return KVCM_OK;
+    if (d_keys == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    kvcm::UpsertKernel<<<kvcm::GridFor(n, 256), 256, 0, kvcm::AsStream(stream)>>>(kvcm::View(ix), d_keys, d_values,
+                                                                                   uniform_value, n, d_status);
+    return kvcm::LaunchStatus();
+}
+
+int32_t kvcm_b200_index_erase(kvcm_b200_index_t *ix, const int64_t *d_keys, int64_t n, kvcm_stream_t stream) {
+    if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (n < 0) return KVCM_EC_BADARGS;
+    if (n == 0) return KVCM_OK;
+    if (d_keys == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    kvcm::EraseKernel<<<kvcm::GridFor(n, 256), 256, 0, kvcm::AsStream(stream)>>>(kvcm::View(ix), d_keys, n);
+    return kvcm::LaunchStatus();
+}
+
+int32_t kvcm_b200_index_lookup(kvcm_b200_index_t *ix, const int64_t *d_keys, int64_t n, uint64_t *d_values_out,
+                               kvcm_stream_t stream) {
+    if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (n < 0) return KVCM_EC_BADARGS;
+    if (n == 0) return KVCM_OK;
+    if (d_keys == nullptr || d_values_out == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    kvcm::LookupKernel<<<kvcm::GridFor(n, 256), 256, 0, kvcm::AsStream(stream)>>>(kvcm::View(ix), d_keys, n,
+                                                                                   d_values_out);
+    return kvcm::LaunchStatus();
+}
+
+int32_t kvcm_b200_match_prefix(kvcm_b200_index_t *ix, const int64_t *d_keys, const int64_t *d_key_off, int32_t n_req,
+                               const int64_t *d_mask_off, const uint8_t *d_mask_bits, uint32_t avail_mask,
+                               int32_t *d_len_out, kvcm_stream_t stream) {
+    if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (n_req < 0) return KVCM_EC_BADARGS;
+    if (n_req == 0) return KVCM_OK;
+    if (d_key_off == nullptr || d_len_out == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    kvcm::PrefixMatchKernel<<<kvcm::GridFor(n_req, kvcm::kMatchWarps), kvcm::kMatchWarps * 32, 0,
+                              kvcm::AsStream(stream)>>>(kvcm::View(ix), d_keys, d_key_off, n_req, d_mask_off,
+                                                        d_mask_bits, avail_mask, d_len_out);
+    return kvcm::LaunchStatus();
+}
+
+int32_t kvcm_b200_match_sw(kvcm_b200_index_t *ix, const int64_t *d_keys, const int64_t *d_key_off, int32_t n_req,
+                           int32_t sw_blocks, uint32_t avail_mask, int32_t *d_base_out, kvcm_stream_t stream) {
+    if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (n_req < 0 || sw_blocks <= 0) return KVCM_EC_BADARGS;
+    if (n_req == 0) return KVCM_OK;
+    if (d_key_off == nullptr || d_base_out == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    kvcm::SwMatchKernel<<<kvcm::GridFor(n_req, kvcm::kMatchWarps), kvcm::kMatchWarps * 32, 0,
+                          kvcm::AsStream(stream)>>>(kvcm::View(ix), d_keys, d_key_off, n_req, sw_blocks, avail_mask,
+                                                    d_base_out);
+    return kvcm::LaunchStatus();
+}
+
+int32_t kvcm_b200_batch_get(kvcm_b200_index_t *ix, const int64_t *d_keys, int64_t n, uint32_t avail_mask,
+                            uint8_t *d_flags_out, kvcm_stream_t stream) {
+    if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (n < 0) return KVCM_EC_BADARGS;
+    if (n == 0) return KVCM_OK;
+    if (d_keys == nullptr || d_flags_out == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    kvcm::BatchGetKernel<<<kvcm::GridFor(n, 256), 256, 0, kvcm::AsStream(stream)>>>(kvcm::View(ix), d_keys, n,
+                                                                                     avail_mask, d_flags_out);
+    return kvcm::LaunchStatus();
+}
+
+}  // extern "C"

@@ -1,0 +1,44 @@
+// Shared host/device helpers of libkvcm_b200.so (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "kvcm_b200.h"
+
+namespace kvcm {
+
+// Device properties the launchers size their grids from; queried once per device.
+struct DeviceInfo {
+    int sm_count = 0;
+    int64_t l2_bytes = 0;
+    bool ok = false;
+};
+
+const DeviceInfo &GetDeviceInfo();
+
+inline cudaStream_t AsStream(kvcm_stream_t s) { return static_cast<cudaStream_t>(s); }
+
+// Maps the state of the CUDA runtime after a launch to a return code of the C ABI.
+inline int32_t LaunchStatus() {
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? KVCM_OK : KVCM_ER_CUDAMEMCPY_ERROR;
+}
+
+// True when a device is present; every compute entry point checks it first so that a box
+// without a GPU gets KVCM_ER_NO_DEVICE instead of a silent no-op.
+bool HaveDevice();
+
+__device__ __forceinline__ uint32_t LaneId() { return threadIdx.x & 31u; }
+
+// One step of the reference's chained block hash (kv_cache_manager/manager/hash_util.h:8-12):
+//   hash ^= value + 0x9e3779b97f4a7c15 + (hash << 12) + (hash >> 32)
+// on int64 with wrap-around; `>>` is the arithmetic shift of a signed value.  Written on
+// unsigned words so that the device code has no signed overflow.
+__host__ __device__ __forceinline__ uint64_t HashStep(uint64_t h, uint64_t v) {
+    const uint64_t sra32 = static_cast<uint64_t>(static_cast<int64_t>(h) >> 32);
+    return h ^ (v + 0x9e3779b97f4a7c15ull + (h << 12) + sra32);
+}
+
+}  // namespace kvcm

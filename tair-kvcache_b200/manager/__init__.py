@@ -1,0 +1,4 @@
+"""Batched twins of the CacheManager / MetaSearcher operators on the hash + match path."""
+from .block_index import BlockIndex, encode_locations  # noqa: F401
+from .hash_util import ApplyPrefixHashBatch, GenKeyVectorBatch, key_offsets  # noqa: F401
+from .meta_searcher import BatchMetaSearcher, QueryType  # noqa: F401

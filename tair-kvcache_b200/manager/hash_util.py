@@ -1,0 +1,51 @@
+"""Batched chained block hash on the GPU.
+
+GenKeyVectorBatch is GenKeyVector (kv_cache_manager/manager/cache_manager.cc:76-87) for many
+requests in one launch; ApplyPrefixHashBatch is ApplyPrefixHash
+(kv_cache_manager/optimizer/trace_converter/trace_util.cc:47-56), i.e. block size 1.
+"""
+import ctypes
+
+import numpy as np
+import torch
+
+from .. import _cabi
+
+
+def key_offsets(tok_off, block_size: int) -> np.ndarray:
+    """key_off[r] = number of keys of requests before r (floor(len / block_size) each); host side."""
+    tok_off = np.ascontiguousarray(tok_off, dtype=np.int64)
+    out = np.empty(len(tok_off), dtype=np.int64)
+    _cabi.call("kvcm_b200_key_offsets", tok_off.ctypes.data_as(ctypes.c_void_p), len(tok_off) - 1, block_size,
+               out.ctypes.data_as(ctypes.c_void_p))
+    return out
+
+
+def GenKeyVectorBatch(tokens: torch.Tensor, tok_off: torch.Tensor, block_size: int, key_off: torch.Tensor,
+                      n_keys: int, out: torch.Tensor = None) -> torch.Tensor:
+    """Keys of a CSR batch of requests.
+
+    tokens: CUDA tensor of token ids, int32/uint32 (zero-extended) or int64; tok_off / key_off:
+    int64 CUDA tensors of n_req + 1 offsets; n_keys = key_off[-1] known on the host.  Returns the
+    int64 key tensor (CSR by key_off).  Asynchronous on the current stream."""
+    if not tokens.is_cuda:
+        raise ValueError("tokens must be a CUDA tensor: this path has no CPU implementation")
+    n_req = tok_off.numel() - 1
+    if out is None:
+        out = torch.empty(max(n_keys, 1), dtype=torch.int64, device=tokens.device)
+    if tokens.dtype in (torch.int32, torch.uint32):
+        entry = "kvcm_b200_hash_blocks_u32"
+    elif tokens.dtype == torch.int64:
+        entry = "kvcm_b200_hash_blocks_i64"
+    else:
+        raise ValueError("token ids must be 32- or 64-bit integers")
+    _cabi.bind_device(tokens.device.index)
+    with torch.cuda.device(tokens.device):
+        _cabi.call(entry, tokens.data_ptr(), tokens.numel(), tok_off.data_ptr(), n_req, block_size, out.data_ptr(),
+                   key_off.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    return out[:n_keys]
+
+
+def ApplyPrefixHashBatch(hash_ids: torch.Tensor, id_off: torch.Tensor) -> torch.Tensor:
+    """One chained key per id; the key CSR equals the id CSR."""
+    return GenKeyVectorBatch(hash_ids, id_off, 1, id_off, hash_ids.numel())

@@ -1,0 +1,58 @@
+"""Batched matchers over a BlockIndex: many requests per call, results as lengths / window starts.
+
+Each method is the batched twin of one MetaSearcher operator
+(kv_cache_manager/manager/meta_searcher.cc:74-310); the single-request operators of the reference
+are the batch-of-one case.
+"""
+import enum
+from typing import Optional
+
+import torch
+
+from .. import _cabi
+from .block_index import BlockIndex
+
+
+class QueryType(enum.IntEnum):
+    # kv_cache_manager/client/include/common.h:65-70
+    QT_UNSPECIFIED = 0
+    QT_BATCH_GET = 1
+    QT_PREFIX_MATCH = 2
+    QT_REVERSE_ROLL_SW_MATCH = 3
+
+
+class BatchMetaSearcher:
+    def __init__(self, index: BlockIndex, avail_mask: int = _cabi.AVAIL_ALL):
+        self.index = index
+        self.avail_mask = avail_mask
+
+    def PrefixMatch(self, keys: torch.Tensor, key_off: torch.Tensor, mask_off: Optional[torch.Tensor] = None,
+                    mask_bits: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """int32 matched length (in keys) per request.  mask_off: int64 per request (BlockMaskOffset);
+        mask_bits: uint8 per key (BlockMaskVector padded with zeros)."""
+        n_req = key_off.numel() - 1
+        if out is None:
+            out = torch.empty(max(n_req, 1), dtype=torch.int32, device=self.index.device)
+        _cabi.call("kvcm_b200_match_prefix", self.index.handle, keys.data_ptr(), key_off.data_ptr(), n_req,
+                   mask_off.data_ptr() if mask_off is not None else None,
+                   mask_bits.data_ptr() if mask_bits is not None else None, self.avail_mask, out.data_ptr(),
+                   self.index._s())
+        return out[:n_req]
+
+    def ReverseRollSlideWindowMatch(self, keys: torch.Tensor, key_off: torch.Tensor, sw_size: int,
+                                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """int32 per request: start of the matched window, -1 no window, -2 fewer keys than sw_size.
+        Raises KvcmError(KVCM_EC_BADARGS) for sw_size <= 0."""
+        n_req = key_off.numel() - 1
+        if out is None:
+            out = torch.empty(max(n_req, 1), dtype=torch.int32, device=self.index.device)
+        _cabi.call("kvcm_b200_match_sw", self.index.handle, keys.data_ptr(), key_off.data_ptr(), n_req, sw_size,
+                   self.avail_mask, out.data_ptr(), self.index._s())
+        return out[:n_req]
+
+    def BatchGet(self, keys: torch.Tensor) -> torch.Tensor:
+        """uint8 flags per key (FLAG_SERVABLE | FLAG_EXISTS | FLAG_NONEMPTY | FLAG_WRITABLE)."""
+        out = torch.empty(max(keys.numel(), 1), dtype=torch.uint8, device=self.index.device)
+        _cabi.call("kvcm_b200_batch_get", self.index.handle, keys.data_ptr(), keys.numel(), self.avail_mask,
+                   out.data_ptr(), self.index._s())
+        return out[:keys.numel()]

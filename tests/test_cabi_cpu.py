@@ -1,0 +1,97 @@
+"""The C-ABI library on a box without a GPU: it loads, exports every declared symbol, and refuses
+to compute (no CPU fallback)."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+from conftest import ROOT
+
+import tair_kvcache_b200  # noqa: F401
+from tair_kvcache_b200 import _cabi
+
+
+def _declared_symbols():
+    names = []
+    inc = os.path.join(ROOT, "include")
+    for fn in sorted(os.listdir(inc)):
+        if fn.endswith(".h"):
+            text = open(os.path.join(inc, fn)).read()
+            names += re.findall(r"KVCM_API\s+[\w\s\*]+?\b(kvcm_b200_\w+)\s*\(", text)
+    return names
+
+
+def test_library_exports_every_declared_symbol():
+    names = _declared_symbols()
+    assert len(names) >= 25
+    L = ctypes.CDLL(_cabi.LIB_PATH)
+    for name in names:
+        assert hasattr(L, name), name
+    # and the Python binding knows each of them
+    assert set(names) == set(_cabi.SIGNATURES)
+
+
+def test_abi_version_and_error_strings():
+    assert _cabi.lib().kvcm_b200_abi_version() == 1
+    assert "no CPU path" in _cabi.error_string(_cabi.KVCM_ER_NO_DEVICE)
+    assert _cabi.error_string(_cabi.KVCM_EC_BADARGS) == "bad arguments"
+
+
+def test_key_offsets_host_helper():
+    from tair_kvcache_b200.manager import key_offsets
+    assert key_offsets([0, 5, 64, 130, 130], 64).tolist() == [0, 0, 0, 1, 1]
+    with pytest.raises(_cabi.KvcmError):
+        key_offsets([0, 5], 0)
+
+
+def test_iovs_to_segments_honours_ignore():
+    iovs = (_cabi.Iov * 3)()
+    bufs = [np.zeros(8, np.uint8), None, np.zeros(4, np.uint8)]
+    for i, (b, size, ign) in enumerate([(bufs[0], 8, 0), (None, 4, 1), (bufs[2], 4, 0)]):
+        iovs[i].type = 1
+        iovs[i].ignore = ign
+        iovs[i].base = b.ctypes.data if b is not None else None
+        iovs[i].size = size
+    segs = (_cabi.Seg * 3)()
+    n, span = ctypes.c_int32(), ctypes.c_uint64()
+    string = np.zeros(16, np.uint8)
+    _cabi.call("kvcm_b200_iovs_to_segments", ctypes.addressof(iovs), 3, string.ctypes.data, 0,
+               ctypes.addressof(segs), ctypes.addressof(n), ctypes.addressof(span))
+    assert (n.value, span.value) == (2, 16)
+    assert segs[0].dst == string.ctypes.data and segs[0].src == bufs[0].ctypes.data and segs[0].bytes == 8
+    assert segs[1].dst == string.ctypes.data + 12 and segs[1].bytes == 4
+    _cabi.call("kvcm_b200_iovs_to_segments", ctypes.addressof(iovs), 3, string.ctypes.data, 1,
+               ctypes.addressof(segs), ctypes.addressof(n), ctypes.addressof(span))
+    assert segs[1].src == string.ctypes.data + 12 and segs[1].dst == bufs[2].ctypes.data
+
+
+def test_compute_entry_points_refuse_without_a_device():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    L = _cabi.lib()
+    one = ctypes.c_void_p(16)
+    assert L.kvcm_b200_gather_tokens(one, 1, one, 1, one, None, 1, 1, 16, 1, None, None) == _cabi.KVCM_ER_NO_DEVICE
+    assert L.kvcm_b200_hash_blocks_u32(one, 4, one, 1, 1, one, one, None) == _cabi.KVCM_ER_NO_DEVICE
+    h = ctypes.c_void_p()
+    assert L.kvcm_b200_index_create(10, ctypes.byref(h)) == _cabi.KVCM_ER_NO_DEVICE and not h.value
+    assert L.kvcm_b200_copy_segments(one, 1, None) == _cabi.KVCM_ER_NO_DEVICE
+
+
+def test_encode_locations_matches_oracle_predicates():
+    from oracle import kvcm_oracle as oracle
+    from tair_kvcache_b200.manager.block_index import avail_mask_from_weights, encode_locations
+    rng = np.random.default_rng(0)
+    for weights in [(1, 3, 3, 3, 5), (1, 0, 3, 0, 5), (0, 0, 0, 0, 0)]:
+        avail = avail_mask_from_weights(weights)
+        for _ in range(200):
+            locs = [(int(rng.integers(0, 5)), int(rng.integers(0, 6))) for _ in range(int(rng.integers(0, 4)))]
+            ix = oracle.Index()
+            ix.put([7], [locs])
+            f = int(ix.batch_get([7], weights=weights)[0])
+            w = encode_locations(locs)
+            assert bool(f & 1) == bool(w & avail & 0xFFFF)
+            assert bool(f & 4) == bool(w & _cabi.VAL_NONEMPTY)
+            assert bool(f & 8) == bool((w >> 16) & avail & 0xFFFF)

@@ -1,0 +1,276 @@
+"""Byte-exact parity of the CUDA gather / scatter with the CPU oracle, through the C ABI.
+
+Shapes of the first cases follow the reference's own kernel test
+(kv_cache_manager/py_connector/test/kernel/test_batch_gather_scatter.py:9-216,301-494): seed 42,
+4 layers x (K,V), 10240 tokens, 16 tokens per block, hidden 1024 bf16, 128 of 1024 staging blocks,
+staging in pinned host memory and on the device; its edge case is one block of one token (:221-298).
+Values are random 16-bit patterns (NaN payloads included) and every comparison is on raw bytes."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import kvcm_oracle as oracle
+
+import tair_kvcache_b200  # noqa: F401
+from tair_kvcache_b200 import _cabi
+from tair_kvcache_b200.kernel import (CopyBufferAllocator, batch_gather_kv_caches, batch_gather_kv_pages,
+                                      batch_scatter_kv_caches, batch_scatter_kv_pages, gather_kv_caches,
+                                      scatter_kv_caches)
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _rand_bytes(gen, n):
+    return torch.randint(0, 256, (n,), dtype=torch.uint8, generator=gen)
+
+
+def _make(seed, n_pools, pool_rows, row_bytes):
+    gen = torch.Generator().manual_seed(seed)
+    host = [_rand_bytes(gen, pool_rows * row_bytes) for _ in range(n_pools)]
+    dev = [h.to(DEV) for h in host]
+    ptrs = torch.tensor([d.data_ptr() for d in dev], dtype=torch.int64, device=DEV)
+    return host, dev, ptrs
+
+
+def _np(ts):
+    return [t.numpy() for t in ts]
+
+
+@pytest.mark.parametrize("staging_on", ["pinned_host", "device"])
+def test_gather_reference_shapes(staging_on):
+    torch.manual_seed(42)
+    n_layers, total_tokens, T, hidden, n_blocks, n_slots = 4, 10240, 16, 1024, 128, 1024
+    P, row_bytes = n_layers * 2, hidden * 2
+    host, dev, ptrs = _make(42, P, total_tokens, row_bytes)
+    tok = torch.cat([torch.randperm(total_tokens)[:T] for _ in range(n_blocks)]).tolist()
+    slots = torch.randperm(n_slots)[:n_blocks].tolist()
+    if staging_on == "pinned_host":
+        dst = torch.zeros(n_slots, P, T, hidden, dtype=torch.bfloat16, pin_memory=True)
+    else:
+        dst = torch.zeros(n_slots, P, T, hidden, dtype=torch.bfloat16, device=DEV)
+    batch_gather_kv_caches(ptrs, dst, tok, slots, T, hidden)
+    torch.cuda.synchronize()
+    want = np.zeros(n_slots * P * T * row_bytes, dtype=np.uint8)
+    assert oracle.move_rows(_np(host), want, tok, slots, T, row_bytes, 0, threads=4) == 0
+    got = dst.cpu().view(torch.uint8).numpy().reshape(-1)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("staging_on", ["pinned_host", "device"])
+def test_scatter_reference_shapes(staging_on):
+    torch.manual_seed(42)
+    n_layers, total_tokens, T, hidden, n_blocks, n_slots = 4, 10240, 16, 1024, 128, 1024
+    P, row_bytes = n_layers * 2, hidden * 2
+    host, dev, ptrs = _make(43, P, total_tokens, row_bytes)
+    tok = torch.randperm(total_tokens)[:n_blocks * T].tolist()  # unique rows, as the reference test uses
+    slots = torch.randperm(n_slots)[:n_blocks].tolist()
+    gen = torch.Generator().manual_seed(7)
+    src_bytes = _rand_bytes(gen, n_slots * P * T * row_bytes)
+    src = src_bytes.view(torch.bfloat16).view(n_slots, P, T, hidden)
+    src = src.pin_memory() if staging_on == "pinned_host" else src.to(DEV)
+    batch_scatter_kv_caches(ptrs, src, tok, slots, T, hidden)
+    torch.cuda.synchronize()
+    want = [h.numpy().copy() for h in host]
+    oracle.move_rows(want, src_bytes.numpy(), tok, slots, T, row_bytes, 1, threads=4)
+    for p in range(P):
+        assert np.array_equal(dev[p].cpu().numpy(), want[p]), p
+
+
+def test_single_token_single_block_edge_case():
+    host, dev, ptrs = _make(1, 8, 10240, 2048)
+    dst = torch.zeros(4, 8, 1, 1024, dtype=torch.bfloat16, device=DEV)
+    batch_gather_kv_caches(ptrs, dst, [777], [2], 1, 1024)
+    torch.cuda.synchronize()
+    want = np.zeros(4 * 8 * 2048, dtype=np.uint8)
+    oracle.move_rows(_np(host), want, [777], [2], 1, 2048, 0)
+    assert np.array_equal(dst.cpu().view(torch.uint8).numpy().reshape(-1), want)
+
+
+def test_empty_batch_is_a_no_op():
+    host, dev, ptrs = _make(2, 2, 64, 64)
+    dst = torch.zeros(2, 2, 4, 32, dtype=torch.bfloat16, device=DEV)
+    batch_gather_kv_caches(ptrs, dst, [], [], 4, 32)
+    torch.cuda.synchronize()
+    assert not dst.view(torch.uint8).any()
+
+
+@pytest.mark.parametrize("row_bytes,rows_per_block", [(6, 5), (2, 3), (48, 7), (4098, 2), (40000, 3), (16, 1)])
+def test_ragged_row_sizes_any_alignment(row_bytes, rows_per_block):
+    n_pools, pool_rows, n_blocks, n_slots = 3, 101, 9, 12
+    host, dev, ptrs = _make(row_bytes, n_pools, pool_rows, row_bytes)
+    rng = np.random.default_rng(row_bytes)
+    rows = rng.permutation(pool_rows)[:n_blocks * rows_per_block].astype(np.int32)
+    slots = rng.permutation(n_slots)[:n_blocks].astype(np.int32)
+    staging = torch.zeros(n_slots * n_pools * rows_per_block * row_bytes, dtype=torch.uint8, device=DEV)
+    batch_gather_kv_pages(ptrs, staging, torch.from_numpy(rows), torch.from_numpy(slots), rows_per_block, row_bytes,
+                          pool_rows)
+    torch.cuda.synchronize()
+    want = np.zeros(staging.numel(), dtype=np.uint8)
+    oracle.move_rows(_np(host), want, rows, slots, rows_per_block, row_bytes, 0)
+    assert np.array_equal(staging.cpu().numpy(), want)
+    # scatter the staged bytes into zeroed pools: referenced rows come back, the rest stay zero
+    zero = [torch.zeros_like(d) for d in dev]
+    zptrs = torch.tensor([z.data_ptr() for z in zero], dtype=torch.int64, device=DEV)
+    batch_scatter_kv_pages(zptrs, staging, torch.from_numpy(rows), torch.from_numpy(slots), rows_per_block,
+                           row_bytes, pool_rows)
+    torch.cuda.synchronize()
+    wantp = [np.zeros_like(h.numpy()) for h in host]
+    oracle.move_rows(wantp, want, rows, slots, rows_per_block, row_bytes, 1)
+    for p in range(n_pools):
+        assert np.array_equal(zero[p].cpu().numpy(), wantp[p])
+
+
+def test_unaligned_pool_base_addresses():
+    row_bytes, pool_rows, T = 64, 50, 4
+    gen = torch.Generator().manual_seed(5)
+    raw = [_rand_bytes(gen, pool_rows * row_bytes + 16).to(DEV) for _ in range(2)]
+    views = [raw[0][3:3 + pool_rows * row_bytes], raw[1][8:8 + pool_rows * row_bytes]]
+    ptrs = torch.tensor([v.data_ptr() for v in views], dtype=torch.int64, device=DEV)
+    rows = np.arange(12, dtype=np.int32)[::-1].copy()
+    staging = torch.zeros(3 * 2 * T * row_bytes, dtype=torch.uint8, device=DEV)
+    batch_gather_kv_pages(ptrs, staging, torch.from_numpy(rows), None, T, row_bytes, pool_rows)
+    torch.cuda.synchronize()
+    want = np.zeros(staging.numel(), dtype=np.uint8)
+    oracle.move_rows([v.cpu().numpy() for v in views], want, rows, None, T, row_bytes, 0)
+    assert np.array_equal(staging.cpu().numpy(), want)
+
+
+def test_out_of_range_rows_and_slots_are_skipped_and_counted():
+    n_pools, pool_rows, row_bytes, T = 2, 32, 256, 4
+    host, dev, ptrs = _make(9, n_pools, pool_rows, row_bytes)
+    rows = np.array([0, 1, 2, 3, 4, 32, -1, 7, 8, 9, 10, 11], dtype=np.int32)  # block 1 has two bad rows
+    slots = np.array([1, 0, 5], dtype=np.int32)  # block 2 names a slot that does not exist
+    staging = torch.zeros(3 * n_pools * T * row_bytes, dtype=torch.uint8, device=DEV)
+    status = torch.zeros(2, dtype=torch.int32, device=DEV)
+    batch_gather_kv_pages(ptrs, staging, torch.from_numpy(rows), torch.from_numpy(slots), T, row_bytes, pool_rows,
+                          status=status)
+    torch.cuda.synchronize()
+    want = np.zeros(staging.numel(), dtype=np.uint8)
+    skipped = oracle.move_rows(_np(host), want, rows, slots, T, row_bytes, 0)
+    assert np.array_equal(staging.cpu().numpy(), want)
+    assert status[0].item() == skipped == 2 * n_pools + T * n_pools
+    assert status[1].item() == 3  # 1 + largest offending block
+
+
+def test_page_table_form_equals_token_form():
+    # Llama-3-8B geometry, shrunk: page 16 tokens x 2 KiB, block = 4 pages = 64 tokens
+    n_pools, pool_pages, page_tokens, tok_bytes, pages_per_block, n_blocks = 6, 256, 16, 2048, 4, 40
+    host, dev, ptrs = _make(11, n_pools, pool_pages * page_tokens, tok_bytes)
+    rng = np.random.default_rng(11)
+    table = rng.permutation(pool_pages)[:n_blocks * pages_per_block].astype(np.int32)
+    slots = rng.permutation(n_blocks).astype(np.int32)
+    # what generate_blocks_idx (kv_cache_manager/py_connector/vllm/v1_connector.py:308-320) would build
+    tok = (table[:, None] * page_tokens + np.arange(page_tokens, dtype=np.int32)[None, :]).reshape(-1)
+    T = pages_per_block * page_tokens
+    a = torch.zeros(n_blocks * n_pools * T * tok_bytes, dtype=torch.uint8, device=DEV)
+    b = torch.zeros_like(a)
+    batch_gather_kv_pages(ptrs, a, torch.from_numpy(table), torch.from_numpy(slots), pages_per_block,
+                          page_tokens * tok_bytes, pool_pages)
+    batch_gather_kv_caches(ptrs, b.view(torch.bfloat16).view(n_blocks, n_pools, T, tok_bytes // 2), tok.tolist(),
+                           slots.tolist(), T, tok_bytes // 2)
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)
+    want = np.zeros(a.numel(), dtype=np.uint8)
+    oracle.move_rows(_np(host), want, tok, slots, T, tok_bytes, 0, threads=4)
+    assert np.array_equal(a.cpu().numpy(), want)
+
+
+def test_mla_shaped_block_roundtrip():
+    # DeepSeek-style latent cache: one pool per layer, 576 bf16 per token, page = block = 64 tokens
+    n_pools, pool_pages, page_bytes = 5, 40, 64 * 1152
+    host, dev, ptrs = _make(13, n_pools, pool_pages, page_bytes)
+    table = torch.randperm(pool_pages, generator=torch.Generator().manual_seed(1))[:17].to(torch.int32)
+    staging = torch.zeros(17 * n_pools * page_bytes, dtype=torch.uint8, device=DEV)
+    batch_gather_kv_pages(ptrs, staging, table, None, 1, page_bytes, pool_pages)
+    zero = [torch.zeros_like(d) for d in dev]
+    zptrs = torch.tensor([z.data_ptr() for z in zero], dtype=torch.int64, device=DEV)
+    batch_scatter_kv_pages(zptrs, staging, table, None, 1, page_bytes, pool_pages)
+    torch.cuda.synchronize()
+    idx = table.long().to(DEV)
+    for p in range(n_pools):
+        assert torch.equal(zero[p].view(pool_pages, page_bytes)[idx], dev[p].view(pool_pages, page_bytes)[idx])
+        assert int(zero[p].view(pool_pages, page_bytes).any(dim=1).sum()) == 17
+
+
+def test_legacy_single_block_operators():
+    # kv_cache_manager/py_connector/kernel/gather_scatter_helper.py:279-317 self-test shapes
+    torch.manual_seed(42)
+    n_layers, total, n_tok, hidden = 4, 128, 32, 512
+    gen = torch.Generator().manual_seed(42)
+    host = [_rand_bytes(gen, 2 * total * hidden * 4) for _ in range(n_layers)]
+    caches = [h.to(DEV).view(torch.float32).view(2, total, hidden) for h in host]
+    ptrs = torch.tensor([c.data_ptr() for c in caches], device=DEV, dtype=torch.int64)
+    tok = torch.randperm(total)[:n_tok].tolist()
+    tok[5] = total + 3  # past the cache: skipped by the reference kernels
+    dst = torch.zeros(n_layers, 2, n_tok, hidden, dtype=torch.float32, device=DEV)
+    gather_kv_caches(ptrs, total, dst, tok)
+    torch.cuda.synchronize()
+    want = np.zeros(dst.numel() * 4, dtype=np.uint8)
+    oracle.move_legacy(_np(host), total, want, tok, hidden * 4, 0)
+    assert np.array_equal(dst.cpu().view(torch.uint8).numpy().reshape(-1), want)
+
+    src_b = _rand_bytes(gen, dst.numel() * 4)
+    src = src_b.to(DEV).view(torch.float32).view(n_layers, 2, n_tok, hidden)
+    scatter_kv_caches(ptrs, total, src, tok)
+    torch.cuda.synchronize()
+    wantc = [h.numpy().copy() for h in host]
+    oracle.move_legacy(wantc, total, src_b.numpy(), tok, hidden * 4, 1)
+    for l in range(n_layers):
+        assert np.array_equal(caches[l].cpu().view(torch.uint8).numpy().reshape(-1), wantc[l])
+
+
+def test_copy_buffer_allocator_with_gather():
+    alloc = CopyBufferAllocator(torch.device(DEV), torch.bfloat16, [2, 4, 64], 8)
+    idx = alloc.alloc_buffer_idx_blocking(3)
+    assert len(idx) == 3 and alloc._raw_buffer.shape == (8, 2, 4, 64)
+    host, dev, ptrs = _make(3, 2, 64, 128)
+    tok = list(range(12))
+    batch_gather_kv_caches(ptrs, alloc._raw_buffer, tok, idx, 4, 64)
+    torch.cuda.synchronize()
+    bufs = alloc.get_buffer_by_idx(idx)
+    for b in range(3):
+        for p in range(2):
+            want = dev[p].view(64, 128)[b * 4:(b + 1) * 4]
+            assert torch.equal(bufs[b][p].view(torch.uint8).view(4, 128), want)
+    alloc.free_buffer(idx)
+    with pytest.raises(RuntimeError):
+        alloc.free_buffer([0])
+
+
+def test_large_roundtrip_property():
+    """A few GiB, larger than L2: gather -> scatter into zeroed pools restores exactly the referenced pages,
+    and the staged bytes equal a torch index_select of the pools."""
+    n_pools, pool_pages, page_bytes, ppb, n_blocks = 8, 4096, 32768, 4, 512
+    gen = torch.Generator(device=DEV).manual_seed(99)
+    dev = [torch.randint(0, 1 << 31, (pool_pages * page_bytes // 4,), dtype=torch.int32, device=DEV, generator=gen)
+           for _ in range(n_pools)]
+    ptrs = torch.tensor([d.data_ptr() for d in dev], dtype=torch.int64, device=DEV)
+    table = torch.randperm(pool_pages, device=DEV)[:n_blocks * ppb].to(torch.int32)
+    slots = torch.randperm(n_blocks, device=DEV).to(torch.int32)
+    staging = torch.zeros(n_blocks, n_pools, ppb, page_bytes // 4, dtype=torch.int32, device=DEV)
+    batch_gather_kv_pages(ptrs, staging, table, slots, ppb, page_bytes, pool_pages)
+    torch.cuda.synchronize()
+    tl = table.long().view(n_blocks, ppb)
+    for p in range(n_pools):
+        want = dev[p].view(pool_pages, -1)[tl]  # [n_blocks, ppb, page]
+        assert torch.equal(staging[slots.long(), p], want)
+    zero = [torch.zeros_like(d) for d in dev]
+    zptrs = torch.tensor([z.data_ptr() for z in zero], dtype=torch.int64, device=DEV)
+    batch_scatter_kv_pages(zptrs, staging, table, slots, ppb, page_bytes, pool_pages)
+    torch.cuda.synchronize()
+    for p in range(n_pools):
+        z = zero[p].view(pool_pages, -1)
+        assert torch.equal(z[table.long()], dev[p].view(pool_pages, -1)[table.long()])
+        assert int((z != 0).any(dim=1).sum()) == n_blocks * ppb
+
+
+def test_bad_arguments_return_codes():
+    L = _cabi.lib()
+    _cabi.bind_device(0)
+    t = torch.zeros(64, dtype=torch.uint8, device=DEV)
+    p = t.data_ptr()
+    assert L.kvcm_b200_gather_tokens(p, 0, p, 1, p, None, 1, 1, 16, 1, None, None) == _cabi.KVCM_ER_INVALID_PARAMS
+    assert L.kvcm_b200_gather_tokens(p, 1, p, 1, p, None, 1, 1, 0, 1, None, None) == _cabi.KVCM_ER_INVALID_PARAMS
+    assert L.kvcm_b200_gather_tokens(None, 1, p, 1, p, None, 1, 1, 16, 1, None, None) == _cabi.KVCM_ER_INVALID_ADDRESS
+    assert L.kvcm_b200_gather_tokens(p, 1, p, 1, p, None, 1, 2, 1 << 30, 1, None, None) == _cabi.KVCM_ER_INVALID_PARAMS
