@@ -72,7 +72,7 @@ class ClockSampler:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -372,9 +372,10 @@ def main_b200(args, cfg, rank, world):
     # ---- end to end: pinned host staging through the operator API, python index lists included
     T = ppb * cfg["page_tokens"]
     task_blocks = min(128, w["n_blocks"])  # blocks per save / load task of the reference connector
-    n_tasks = min(w["n_blocks"] // task_blocks, 8 if cfg is WORKLOADS["c2"] else 4)
+    n_tasks = min(w["n_blocks"] // task_blocks, 8)
     dim = cfg["token_bytes"] // 2
-    host_staging = torch.empty(task_blocks, w["n_pools"], T, dim, dtype=torch.bfloat16, pin_memory=True)
+    host_staging = torch.empty(1 if args.no_e2e else task_blocks, w["n_pools"], T, dim, dtype=torch.bfloat16,
+                               pin_memory=True)
     table_np = table.cpu().numpy().reshape(w["n_blocks"], ppb)
     tok_np = (table_np[:, :, None].astype(np.int64) * cfg["page_tokens"] +
               np.arange(cfg["page_tokens"])[None, None, :]).reshape(w["n_blocks"], T)
@@ -386,8 +387,9 @@ def main_b200(args, cfg, rank, world):
             batch_gather_kv_caches(ptrs, host_staging, task_tok[i], task_slots, T, dim)
             batch_scatter_kv_caches(ptrs, host_staging, task_tok[i], task_slots, T, dim)
 
-    e2e_steps = max(1, min(args.steps, 3))
-    e2e_step()
+    e2e_steps = 0 if args.no_e2e else max(1, min(args.steps, 3))
+    if e2e_steps:
+        e2e_step()
     torch.cuda.synchronize(device)
     if world > 1:
         dist.barrier()
@@ -404,7 +406,7 @@ def main_b200(args, cfg, rank, world):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = t.item()
     task_payload = task_blocks * w["n_pools"] * T * cfg["token_bytes"]
-    e2e_value = world * 4 * task_payload * n_tasks * e2e_steps / (e2e_ms * 1e-3) / 1e9
+    e2e_value = world * 4 * task_payload * n_tasks * e2e_steps / (e2e_ms * 1e-3) / 1e9 if e2e_steps else None
     idx_bytes = n_tasks * 2 * (task_blocks * T + task_blocks) * 4
 
     if rank != 0:
@@ -435,9 +437,9 @@ def main_b200(args, cfg, rank, world):
                         "converted per call" % (n_tasks, task_blocks)},
         "gpu_launches": 2 * args.steps,
     }
-    if world == 1:
+    if world == 1 and not args.no_cpu:
         threads = os.cpu_count() or 1
-        cpu_gbs, _, sample, _ = run_cpu_transfer(cfg, threads, 8, 1)
+        cpu_gbs, _, sample, _ = run_cpu_transfer(cfg, threads, 40, 1, budget_s=8.0)
         line["cpu_baseline"] = {"value": cpu_gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
         if not args.no_prefix:
             del w, staging, host_staging
@@ -461,11 +463,22 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-prefix", action="store_true", help="skip the prefix-match side measurement")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-staging leg (profiling runs)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    ap.add_argument("--n-blocks", type=int, default=0, help="override the number of transfer blocks (small cases)")
+    ap.add_argument("--pool-pages", type=int, default=0, help="override the pages per pool (small cases)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
-    cfg = WORKLOADS[args.workload]
+    cfg = dict(WORKLOADS[args.workload])
+    cfg["full_size"] = not (args.n_blocks or args.pool_pages)
+    if args.n_blocks:
+        cfg["n_blocks"] = args.n_blocks
+    if args.pool_pages:
+        cfg["pool_pages"] = args.pool_pages
+    if not cfg["full_size"]:
+        cfg["desc"] += " [REDUCED for profiling: %d blocks, %d pages per pool]" % (cfg["n_blocks"], cfg["pool_pages"])
     if args.impl == "reference":
         main_reference(args, cfg, rank)
     else:

@@ -39,6 +39,13 @@ def avail_mask_from_weights(weights: Sequence[int], default_weight: int = 1) -> 
     return mask
 
 
+def _keys(keys: torch.Tensor, device: torch.device) -> torch.Tensor:
+    """The C ABI takes dense int64 device arrays; a strided view is compacted first."""
+    if keys.dtype != torch.int64 or keys.device != device:
+        raise ValueError("keys must be an int64 tensor on %s" % device)
+    return keys.contiguous()
+
+
 class BlockIndex:
     """Handle of one device-resident index (one per instance_id, as MetaIndexerManager keeps them)."""
 
@@ -76,14 +83,19 @@ class BlockIndex:
     def upsert(self, keys: torch.Tensor, values: Optional[torch.Tensor] = None, uniform_value: int = 0,
                status: Optional[torch.Tensor] = None):
         """keys int64 CUDA; values uint64-as-int64 CUDA tensor of value words, or one word for all."""
+        keys = _keys(keys, self.device)
+        if values is not None:
+            values = values.contiguous()
         _cabi.call("kvcm_b200_index_upsert", self._h, keys.data_ptr(),
                    values.data_ptr() if values is not None else None, uniform_value, keys.numel(),
                    status.data_ptr() if status is not None else None, self._s())
 
     def erase(self, keys: torch.Tensor):
+        keys = _keys(keys, self.device)
         _cabi.call("kvcm_b200_index_erase", self._h, keys.data_ptr(), keys.numel(), self._s())
 
     def lookup(self, keys: torch.Tensor) -> torch.Tensor:
+        keys = _keys(keys, self.device)
         out = torch.empty(keys.numel(), dtype=torch.int64, device=self.device)
         _cabi.call("kvcm_b200_index_lookup", self._h, keys.data_ptr(), keys.numel(), out.data_ptr(), self._s())
         return out

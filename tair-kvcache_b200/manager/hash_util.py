@@ -31,6 +31,7 @@ def GenKeyVectorBatch(tokens: torch.Tensor, tok_off: torch.Tensor, block_size: i
     if not tokens.is_cuda:
         raise ValueError("tokens must be a CUDA tensor: this path has no CPU implementation")
     n_req = tok_off.numel() - 1
+    tokens, tok_off, key_off = tokens.contiguous(), tok_off.contiguous(), key_off.contiguous()
     if out is None:
         out = torch.empty(max(n_keys, 1), dtype=torch.int64, device=tokens.device)
     if tokens.dtype in (torch.int32, torch.uint32):

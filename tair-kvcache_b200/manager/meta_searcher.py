@@ -10,7 +10,7 @@ from typing import Optional
 import torch
 
 from .. import _cabi
-from .block_index import BlockIndex
+from .block_index import BlockIndex, _keys
 
 
 class QueryType(enum.IntEnum):
@@ -31,6 +31,7 @@ class BatchMetaSearcher:
         """int32 matched length (in keys) per request.  mask_off: int64 per request (BlockMaskOffset);
         mask_bits: uint8 per key (BlockMaskVector padded with zeros)."""
         n_req = key_off.numel() - 1
+        keys, key_off = _keys(keys, self.index.device), _keys(key_off, self.index.device)
         if out is None:
             out = torch.empty(max(n_req, 1), dtype=torch.int32, device=self.index.device)
         _cabi.call("kvcm_b200_match_prefix", self.index.handle, keys.data_ptr(), key_off.data_ptr(), n_req,
@@ -44,6 +45,7 @@ class BatchMetaSearcher:
         """int32 per request: start of the matched window, -1 no window, -2 fewer keys than sw_size.
         Raises KvcmError(KVCM_EC_BADARGS) for sw_size <= 0."""
         n_req = key_off.numel() - 1
+        keys, key_off = _keys(keys, self.index.device), _keys(key_off, self.index.device)
         if out is None:
             out = torch.empty(max(n_req, 1), dtype=torch.int32, device=self.index.device)
         _cabi.call("kvcm_b200_match_sw", self.index.handle, keys.data_ptr(), key_off.data_ptr(), n_req, sw_size,
@@ -52,6 +54,7 @@ class BatchMetaSearcher:
 
     def BatchGet(self, keys: torch.Tensor) -> torch.Tensor:
         """uint8 flags per key (FLAG_SERVABLE | FLAG_EXISTS | FLAG_NONEMPTY | FLAG_WRITABLE)."""
+        keys = _keys(keys, self.index.device)
         out = torch.empty(max(keys.numel(), 1), dtype=torch.uint8, device=self.index.device)
         _cabi.call("kvcm_b200_batch_get", self.index.handle, keys.data_ptr(), keys.numel(), self.avail_mask,
                    out.data_ptr(), self.index._s())
