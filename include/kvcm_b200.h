@@ -88,9 +88,10 @@ KVCM_API int32_t kvcm_b200_device_info(int32_t *sm_count, int64_t *l2_bytes, int
  * generate_blocks_idx (kv_cache_manager/py_connector/vllm/v1_connector.py:308-320).  The byte
  * result is identical when the token indices of a block are whole pages.
  *
- * Rows outside [0, pool_rows) and slots outside [0, n_slots) are skipped, never dereferenced;
- * if d_status is not NULL, d_status[0] is incremented once per skipped (pool,row) pair and
- * d_status[1] keeps 1 + the largest offending block number.  The caller zeroes d_status.
+ * Rows outside [0, pool_rows) and slots outside [0, n_slots) are skipped, never dereferenced.
+ * d_status, when not NULL, points to four caller-zeroed uint32 words: [0] is incremented once per
+ * skipped (pool,row) pair, [1] keeps 1 + the largest offending block number, [2] becomes 1 if a
+ * bounded wait inside the kernel ran out (the copy is then incomplete), [3] is reserved.
  * Scattering the same row twice in one call is a data race, as in the reference.
  * Fastest when row_bytes and all base addresses are multiples of 16; any alignment is correct.
  * ---------------------------------------------------------------------------------------- */
@@ -110,6 +111,18 @@ KVCM_API int32_t kvcm_b200_scatter_pages(const void *const *d_pool_ptrs, int32_t
                                          int64_t n_slots, const int32_t *d_page_table, const int32_t *d_slot_idx,
                                          int32_t n_blocks, int32_t pages_per_block, int64_t page_bytes,
                                          int64_t pool_pages, uint32_t *d_status, kvcm_stream_t stream);
+
+/* Tuning knob, process-wide: which of the two gather/scatter kernels large aligned rows use.
+ * mover 0 = 16-byte vector loads and stores, 1 = shared-memory ring driven by bulk async copies
+ * (default); cache_hint 0|1|2 = default / streaming / streaming-loads-only policy of the vector
+ * kernel; -1 leaves a setting unchanged.  Results are byte-identical in every setting.  The
+ * environment variables KVCM_B200_MOVER=ldg|bulk and KVCM_B200_MOVER_HINT=0|1|2 set the initial
+ * values.  Not stream-ordered: call it while no gather/scatter call is being issued. */
+KVCM_API int32_t kvcm_b200_set_mover(int32_t mover, int32_t cache_hint);
+/* Geometry of the bulk-copy ring: stages (2..8) of chunk_bytes (multiple of 1024) per CTA and CTAs
+ * per SM; stages * chunk_bytes * ctas_per_sm must fit the SM's 224 KiB of shared memory.
+ * Default 2 x 32 KiB x 3.  Same calling rule as kvcm_b200_set_mover. */
+KVCM_API int32_t kvcm_b200_set_bulk_geometry(int32_t stages, int32_t ctas_per_sm, int32_t chunk_bytes);
 
 /* Legacy single-block form: kv_cache_gather_kernel / kv_cache_scatter_kernel and gather_kv_caches /
  * scatter_kv_caches (kv_cache_manager/py_connector/kernel/gather_scatter_helper.py:10-172).

@@ -57,6 +57,8 @@ SIGNATURES = {
     "kvcm_b200_scatter_tokens": _MOVE,
     "kvcm_b200_gather_pages": _MOVE,
     "kvcm_b200_scatter_pages": _MOVE,
+    "kvcm_b200_set_mover": [_i32, _i32],
+    "kvcm_b200_set_bulk_geometry": [_i32, _i32, _i32],
     "kvcm_b200_gather_legacy": _LEGACY,
     "kvcm_b200_scatter_legacy": _LEGACY,
     "kvcm_b200_copy_segments": [_vp, _i32, _vp],

@@ -16,6 +16,9 @@
 // streaming cache hints because no byte is touched twice.  The row index of a 16-byte vector
 // is one 32-bit division by row_bytes and one cached 4-byte table read - the table is read
 // per vector from L1, never per element from DRAM.
+#include <cstdlib>
+#include <cstring>
+
 #include "kvcm_common.cuh"
 
 namespace kvcm {
@@ -25,6 +28,25 @@ constexpr int kThreads = 256;
 constexpr int kUnroll = 8;
 constexpr uint32_t kVecBytes = 16;
 constexpr uint32_t kChunkBytes = kThreads * kVecBytes * kUnroll;  // 32 KiB
+
+// Cache policy of the 16-byte accesses: 0 default, 1 streaming (evict-first) loads and stores,
+// 2 streaming loads with default stores.
+template <int kHint>
+__device__ __forceinline__ uint4 LoadVec(const void *p) {
+    if constexpr (kHint == 0) {
+        return *reinterpret_cast<const uint4 *>(p);
+    } else {
+        return __ldcs(reinterpret_cast<const uint4 *>(p));
+    }
+}
+template <int kHint>
+__device__ __forceinline__ void StoreVec(void *p, uint4 v) {
+    if constexpr (kHint == 1) {
+        __stcs(reinterpret_cast<uint4 *>(p), v);
+    } else {
+        *reinterpret_cast<uint4 *>(p) = v;
+    }
+}
 
 struct MoveParams {
     const uint64_t *pool_ptrs;  // device array of base addresses
@@ -44,6 +66,8 @@ struct MoveParams {
     int32_t sub_per_ptr;  // 1, or 2 for the legacy [2, total_tokens, hidden] layer tensors
     int32_t rows_per_block;
     int32_t report_skips;  // 0 for the legacy form, which skips silently
+    uint32_t chunk_bytes;  // bytes per work item (fixed kChunkBytes for the vector kernel)
+    int32_t stages;        // ring depth of the bulk kernel
 };
 
 __device__ __forceinline__ void ReportSkip(const MoveParams &p, uint32_t block, uint32_t count) {
@@ -54,7 +78,7 @@ __device__ __forceinline__ void ReportSkip(const MoveParams &p, uint32_t block, 
 }
 
 // kGather: pool -> staging.  !kGather: staging -> pool.
-template <bool kGather>
+template <bool kGather, int kHint>
 __global__ void __launch_bounds__(kThreads) MoveRowsKernel(const MoveParams p) {
     const uint32_t tid = threadIdx.x;
     for (uint32_t chunk = blockIdx.x; chunk < p.total_chunks; chunk += gridDim.x) {
@@ -100,20 +124,20 @@ __global__ void __launch_bounds__(kThreads) MoveRowsKernel(const MoveParams p) {
             if (kGather) {
 #pragma unroll
                 for (int j = 0; j < kUnroll; ++j) {
-                    if (in_pool[j] != nullptr) v[j] = __ldcs(reinterpret_cast<const uint4 *>(in_pool[j]));
+                    if (in_pool[j] != nullptr) v[j] = LoadVec<kHint>(in_pool[j]);
                 }
 #pragma unroll
                 for (int j = 0; j < kUnroll; ++j) {
-                    if (in_pool[j] != nullptr) __stcs(reinterpret_cast<uint4 *>(stage + off[j]), v[j]);
+                    if (in_pool[j] != nullptr) StoreVec<kHint>(stage + off[j], v[j]);
                 }
             } else {
 #pragma unroll
                 for (int j = 0; j < kUnroll; ++j) {
-                    if (in_pool[j] != nullptr) v[j] = __ldcs(reinterpret_cast<const uint4 *>(stage + off[j]));
+                    if (in_pool[j] != nullptr) v[j] = LoadVec<kHint>(stage + off[j]);
                 }
 #pragma unroll
                 for (int j = 0; j < kUnroll; ++j) {
-                    if (in_pool[j] != nullptr) __stcs(reinterpret_cast<uint4 *>(in_pool[j]), v[j]);
+                    if (in_pool[j] != nullptr) StoreVec<kHint>(in_pool[j], v[j]);
                 }
             }
         } else {
@@ -139,17 +163,289 @@ __global__ void __launch_bounds__(kThreads) MoveRowsKernel(const MoveParams p) {
     }
 }
 
-int ResidentCtas(bool gather) {
-    static int cached[2] = {0, 0};
-    int &slot = cached[gather ? 0 : 1];
-    if (slot == 0) {
-        int per_sm = 0;
-        cudaError_t e = gather ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, MoveRowsKernel<true>, kThreads, 0)
-                               : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, MoveRowsKernel<false>, kThreads, 0);
-        if (e != cudaSuccess || per_sm < 1) per_sm = 1;
-        slot = per_sm * GetDeviceInfo().sm_count;
+// ------------------------------------------------------------------------------------------
+// Bulk-copy (TMA) mover.  One warp per CTA; lane 0 drives a ring of kBulkStages shared-memory
+// buffers of kChunkBytes with cp.async.bulk: global -> shared completes on an mbarrier,
+// shared -> global is tracked by bulk groups.  No thread touches the payload, so the SM spends
+// a few hundred instructions per 32 KiB.  Used when rows are large multiples of 16 bytes; a chunk
+// whose pool base turns out to be misaligned is copied by the warp with plain byte accesses.
+// Every wait is bounded: after kSpinLimit failed polls the CTA raises status[2] and leaves.
+// ------------------------------------------------------------------------------------------
+constexpr int kBulkMaxStages = 8;
+constexpr uint32_t kBulkMinRowBytes = 1024;
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t SmemAddr(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void MbarInit(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void MbarArriveExpectTx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool MbarTryWait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void BulkLoad(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                     dst_smem),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void BulkStore(void *dst, uint32_t src_smem, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(dst), "r"(src_smem), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void BulkCommit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void BulkWaitRead() {
+    asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(kPending) : "memory");
+}
+__device__ __forceinline__ void BulkWaitAll() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
+
+struct ChunkDesc {
+    uint8_t *pool_base;
+    uint8_t *stage;  // start of this chunk in staging
+    const int32_t *rows;
+    uint32_t chunk_off;  // offset of the chunk inside its tile
+    uint32_t len;
+    uint32_t block;
+    bool first_in_tile;
+    bool slot_ok;
+    bool aligned;
+};
+
+__device__ __forceinline__ ChunkDesc Describe(const MoveParams &p, uint32_t chunk) {
+    ChunkDesc d;
+    const uint32_t tile = chunk / p.chunks_per_tile;
+    const uint32_t chunk_in_tile = chunk - tile * p.chunks_per_tile;
+    d.block = tile / static_cast<uint32_t>(p.n_pools);
+    const uint32_t pool = tile - d.block * static_cast<uint32_t>(p.n_pools);
+    const int64_t slot = p.slot_idx != nullptr ? static_cast<int64_t>(__ldg(p.slot_idx + d.block))
+                                               : static_cast<int64_t>(d.block);
+    d.slot_ok = slot >= 0 && slot < p.n_slots;
+    d.first_in_tile = chunk_in_tile == 0;
+    d.chunk_off = chunk_in_tile * p.chunk_bytes;
+    d.len = min(p.chunk_bytes, p.tile_bytes - d.chunk_off);
+    const uint32_t ptr_i = pool / static_cast<uint32_t>(p.sub_per_ptr);
+    const uint32_t sub_i = pool - ptr_i * static_cast<uint32_t>(p.sub_per_ptr);
+    d.pool_base = reinterpret_cast<uint8_t *>(__ldg(p.pool_ptrs + ptr_i)) + sub_i * p.sub_stride;
+    d.stage = p.staging + (d.slot_ok ? slot : 0) * p.slot_bytes + static_cast<int64_t>(pool) * p.tile_bytes +
+              d.chunk_off;
+    d.rows = p.row_idx + static_cast<int64_t>(d.block) * p.rows_per_block;
+    d.aligned = (reinterpret_cast<uintptr_t>(d.pool_base) & 15u) == 0;
+    return d;
+}
+
+// Calls fn(offset in chunk, address in pool or nullptr when the row is out of range, length,
+// starts_row) for every run of the chunk that is contiguous in the pool.
+template <typename F>
+__device__ __forceinline__ void ForEachRun(const MoveParams &p, const ChunkDesc &d, F &&fn) {
+    uint32_t off = 0;
+    uint32_t r = d.chunk_off / p.row_bytes;
+    uint32_t within = d.chunk_off - r * p.row_bytes;
+    while (off < d.len) {
+        const uint32_t run = min(p.row_bytes - within, d.len - off);
+        const int64_t row = __ldg(d.rows + r);
+        uint8_t *addr = (row >= 0 && row < p.pool_rows) ? d.pool_base + row * p.row_bytes + within : nullptr;
+        fn(off, addr, run, within == 0);
+        off += run;
+        within = 0;
+        ++r;
     }
-    return slot;
+}
+
+template <bool kGather>
+__global__ void __launch_bounds__(32) MoveRowsBulkKernel(const MoveParams p) {
+    extern __shared__ __align__(128) uint8_t ring[];
+    __shared__ __align__(8) uint64_t bars[kBulkMaxStages];
+    const uint32_t lane = threadIdx.x;
+    const uint32_t n_stages = static_cast<uint32_t>(p.stages);
+    if (lane == 0) {
+        for (uint32_t s = 0; s < n_stages; ++s) MbarInit(SmemAddr(&bars[s]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async;\n" ::: "memory");
+    }
+    __syncwarp();
+    const uint32_t ring_base = SmemAddr(ring);
+    const uint32_t n_my =
+        p.total_chunks > blockIdx.x ? (p.total_chunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    uint32_t direct_mask = 0;  // bit s: the chunk in stage s was handled without the ring
+
+    auto load = [&](uint32_t k) {
+        const uint32_t s = k % n_stages;
+        const uint32_t bar = SmemAddr(&bars[s]);
+        const uint32_t buf = ring_base + s * p.chunk_bytes;
+        const ChunkDesc d = Describe(p, blockIdx.x + k * gridDim.x);
+        direct_mask &= ~(1u << s);
+        if (!d.slot_ok) {
+            if (lane == 0) {
+                if (d.first_in_tile) ReportSkip(p, d.block, static_cast<uint32_t>(p.rows_per_block));
+                MbarArriveExpectTx(bar, 0);
+            }
+            direct_mask |= 1u << s;
+            return;
+        }
+        if (!d.aligned) {
+            // Misaligned pool base: the warp moves the chunk byte by byte, no staging through the ring.
+            ForEachRun(p, d, [&](uint32_t off, uint8_t *addr, uint32_t run, bool starts_row) {
+                if (addr == nullptr) {
+                    if (lane == 0 && starts_row) ReportSkip(p, d.block, 1u);
+                    return;
+                }
+                for (uint32_t i = lane; i < run; i += 32) {
+                    if (kGather) {
+                        d.stage[off + i] = addr[i];
+                    } else {
+                        addr[i] = d.stage[off + i];
+                    }
+                }
+            });
+            if (lane == 0) MbarArriveExpectTx(bar, 0);
+            direct_mask |= 1u << s;
+            return;
+        }
+        if (lane != 0) return;
+        if (kGather) {
+            uint32_t total = 0;
+            ForEachRun(p, d, [&](uint32_t, uint8_t *addr, uint32_t run, bool starts_row) {
+                if (addr != nullptr) {
+                    total += run;
+                } else if (starts_row) {
+                    ReportSkip(p, d.block, 1u);
+                }
+            });
+            MbarArriveExpectTx(bar, total);
+            ForEachRun(p, d, [&](uint32_t off, uint8_t *addr, uint32_t run, bool) {
+                if (addr != nullptr) BulkLoad(buf + off, addr, run, bar);
+            });
+        } else {
+            MbarArriveExpectTx(bar, d.len);
+            BulkLoad(buf, d.stage, d.len, bar);
+        }
+    };
+
+    auto store = [&](uint32_t k) {
+        const uint32_t s = k % n_stages;
+        if (lane != 0) return;
+        if (((direct_mask >> s) & 1u) == 0) {
+            const uint32_t buf = ring_base + s * p.chunk_bytes;
+            const ChunkDesc d = Describe(p, blockIdx.x + k * gridDim.x);
+            ForEachRun(p, d, [&](uint32_t off, uint8_t *addr, uint32_t run, bool starts_row) {
+                if (addr != nullptr) {
+                    BulkStore(kGather ? d.stage + off : addr, buf + off, run);
+                } else if (!kGather && starts_row) {
+                    ReportSkip(p, d.block, 1u);
+                }
+            });
+        }
+        BulkCommit();  // an empty group keeps the group count in step with the chunk count
+    };
+
+    const uint32_t kAhead = n_stages - 1;
+    for (uint32_t k = 0; k < kAhead && k < n_my; ++k) load(k);
+    bool failed = false;
+    for (uint32_t k = 0; k < n_my; ++k) {
+        const uint32_t s = k % n_stages;
+        if (lane == 0) {
+            const uint32_t parity = (k / n_stages) & 1u;
+            uint32_t spins = 0;
+            while (!MbarTryWait(SmemAddr(&bars[s]), parity)) {
+                if (++spins >= kSpinLimit) {
+                    failed = true;
+                    break;
+                }
+            }
+        }
+        failed = __shfl_sync(0xffffffffu, failed ? 1 : 0, 0) != 0;
+        if (failed) break;
+        store(k);
+        if (k + kAhead < n_my) {
+            // The stage about to be refilled was drained by the store of chunk k-1: let every
+            // bulk group but the newest finish reading shared memory first.
+            if (lane == 0) BulkWaitRead<1>();
+            __syncwarp();
+            load(k + kAhead);
+        }
+    }
+    if (lane == 0) {
+        BulkWaitAll();
+        if (failed && p.status != nullptr) atomicExch(&p.status[2], 1u);
+    }
+}
+
+// 0 = plain 16-byte loads/stores, 1 = bulk-copy ring.  KVCM_B200_MOVER=ldg|bulk overrides the default;
+// KVCM_B200_MOVER_HINT=0|1|2 picks the cache policy of the plain mover.
+struct MoverConfig {
+    int mover = 1;
+    int hint = 0;
+    int bulk_stages = 2;
+    int bulk_ctas_per_sm = 3;
+    uint32_t bulk_chunk_bytes = 32768;
+};
+
+MoverConfig &GetMoverConfig() {
+    static MoverConfig cfg = [] {
+        MoverConfig c;
+        if (const char *m = getenv("KVCM_B200_MOVER")) {
+            if (strcmp(m, "ldg") == 0) c.mover = 0;
+            if (strcmp(m, "bulk") == 0) c.mover = 1;
+        }
+        if (const char *h = getenv("KVCM_B200_MOVER_HINT")) {
+            if (h[0] >= '0' && h[0] <= '2') c.hint = h[0] - '0';
+        }
+        return c;
+    }();
+    return cfg;
+}
+
+template <bool kGather, int kHint>
+int ResidentCtas() {
+    static int cached = 0;
+    if (cached == 0) {
+        int per_sm = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, MoveRowsKernel<kGather, kHint>, kThreads, 0) !=
+                cudaSuccess ||
+            per_sm < 1) {
+            cudaGetLastError();
+            per_sm = 1;
+        }
+        cached = per_sm * GetDeviceInfo().sm_count;
+    }
+    return cached;
+}
+
+template <bool kGather, int kHint>
+void LaunchPlain(const MoveParams &p, cudaStream_t stream) {
+    const int64_t resident = ResidentCtas<kGather, kHint>();
+    const unsigned grid = static_cast<unsigned>(p.total_chunks < resident ? p.total_chunks : resident);
+    MoveRowsKernel<kGather, kHint><<<grid, kThreads, 0, stream>>>(p);
+}
+
+constexpr int kBulkMaxSmem = 224 * 1024;
+
+template <bool kGather>
+void LaunchBulk(const MoveParams &p, int ctas_per_sm, cudaStream_t stream) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(MoveRowsBulkKernel<kGather>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkMaxSmem);
+        attr_set = true;
+    }
+    const int smem = p.stages * static_cast<int>(p.chunk_bytes);
+    const int64_t resident = static_cast<int64_t>(GetDeviceInfo().sm_count) * ctas_per_sm;
+    const unsigned grid = static_cast<unsigned>(p.total_chunks < resident ? p.total_chunks : resident);
+    MoveRowsBulkKernel<kGather><<<grid, 32, smem, stream>>>(p);
 }
 
 int32_t LaunchMove(bool gather, const void *const *d_ptrs, int32_t n_ptrs, int32_t sub_per_ptr, int64_t sub_stride,
@@ -165,7 +461,13 @@ int32_t LaunchMove(bool gather, const void *const *d_ptrs, int32_t n_ptrs, int32
     const int64_t tile_bytes = static_cast<int64_t>(rows_per_block) * row_bytes;
     const int64_t n_pools = static_cast<int64_t>(n_ptrs) * sub_per_ptr;
     if (tile_bytes >= (1ll << 31) || n_pools >= (1ll << 31)) return KVCM_ER_INVALID_PARAMS;
-    const int64_t chunks_per_tile = (tile_bytes + kChunkBytes - 1) / kChunkBytes;
+    const MoverConfig &cfg = GetMoverConfig();
+    // The bulk ring needs 16-byte granularity everywhere and rows long enough to amortise one
+    // copy instruction each; the sub-pool stride of the legacy layout must keep that alignment.
+    const bool bulk_ok = cfg.mover == 1 && row_bytes % 16 == 0 && row_bytes >= kBulkMinRowBytes &&
+                         (reinterpret_cast<uintptr_t>(staging) & 15u) == 0 && sub_stride % 16 == 0;
+    const int64_t chunk_bytes = bulk_ok ? cfg.bulk_chunk_bytes : kChunkBytes;
+    const int64_t chunks_per_tile = (tile_bytes + chunk_bytes - 1) / chunk_bytes;
     const int64_t total_chunks = chunks_per_tile * n_pools * n_blocks;
     if (total_chunks >= (1ll << 32) - (1ll << 20)) return KVCM_ER_INVALID_PARAMS;
 
@@ -187,13 +489,22 @@ int32_t LaunchMove(bool gather, const void *const *d_ptrs, int32_t n_ptrs, int32
     p.sub_per_ptr = sub_per_ptr;
     p.rows_per_block = rows_per_block;
     p.report_skips = report_skips ? 1 : 0;
+    p.chunk_bytes = static_cast<uint32_t>(chunk_bytes);
+    p.stages = cfg.bulk_stages;
 
-    const int64_t resident = ResidentCtas(gather);
-    const unsigned grid = static_cast<unsigned>(total_chunks < resident ? total_chunks : resident);
-    if (gather) {
-        MoveRowsKernel<true><<<grid, kThreads, 0, AsStream(stream)>>>(p);
+    cudaStream_t s = AsStream(stream);
+    if (bulk_ok) {
+        if (gather) {
+            LaunchBulk<true>(p, cfg.bulk_ctas_per_sm, s);
+        } else {
+            LaunchBulk<false>(p, cfg.bulk_ctas_per_sm, s);
+        }
+    } else if (cfg.hint == 0) {
+        gather ? LaunchPlain<true, 0>(p, s) : LaunchPlain<false, 0>(p, s);
+    } else if (cfg.hint == 2) {
+        gather ? LaunchPlain<true, 2>(p, s) : LaunchPlain<false, 2>(p, s);
     } else {
-        MoveRowsKernel<false><<<grid, kThreads, 0, AsStream(stream)>>>(p);
+        gather ? LaunchPlain<true, 1>(p, s) : LaunchPlain<false, 1>(p, s);
     }
     return LaunchStatus();
 }
@@ -202,6 +513,27 @@ int32_t LaunchMove(bool gather, const void *const *d_ptrs, int32_t n_ptrs, int32
 }  // namespace kvcm
 
 extern "C" {
+
+int32_t kvcm_b200_set_mover(int32_t mover, int32_t cache_hint) {
+    if (mover > 1 || cache_hint > 2) return KVCM_ER_INVALID_PARAMS;
+    kvcm::MoverConfig &cfg = kvcm::GetMoverConfig();
+    if (mover >= 0) cfg.mover = mover;
+    if (cache_hint >= 0) cfg.hint = cache_hint;
+    return KVCM_OK;
+}
+
+int32_t kvcm_b200_set_bulk_geometry(int32_t stages, int32_t ctas_per_sm, int32_t chunk_bytes) {
+    if (stages < 2 || stages > kvcm::kBulkMaxStages || ctas_per_sm < 1 || ctas_per_sm > 8 || chunk_bytes < 1024 ||
+        chunk_bytes % 1024 != 0 ||
+        static_cast<int64_t>(stages) * chunk_bytes * ctas_per_sm > kvcm::kBulkMaxSmem) {
+        return KVCM_ER_INVALID_PARAMS;
+    }
+    kvcm::MoverConfig &cfg = kvcm::GetMoverConfig();
+    cfg.bulk_stages = stages;
+    cfg.bulk_ctas_per_sm = ctas_per_sm;
+    cfg.bulk_chunk_bytes = static_cast<uint32_t>(chunk_bytes);
+    return KVCM_OK;
+}
 
 int32_t kvcm_b200_gather_tokens(const void *const *d_pool_ptrs, int32_t n_pools, void *staging, int64_t n_slots,
                                 const int32_t *d_token_idx, const int32_t *d_slot_idx, int32_t n_blocks,

@@ -88,7 +88,7 @@ def batch_gather_kv_caches(
 
     `sm_count` is accepted for signature compatibility and ignored: the library sizes its
     persistent grid from the device.  `total_token_in_kvcache` (optional) bounds the token
-    indices; out-of-range rows are skipped and counted in `status` (uint32[2] CUDA tensor)."""
+    indices; out-of-range rows are skipped and counted in `status` (four zeroed 32-bit words on the GPU)."""
     del sm_count
     _move("kvcm_b200_gather_tokens", kv_caches_ptrs_tensor, dst_tensor, block_token_indices, dst_block_indices,
           num_tokens_per_block, dim_size_per_token_per_layer * dst_tensor.element_size(), total_token_in_kvcache,

@@ -21,6 +21,14 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
+@pytest.fixture(autouse=True, params=["bulk", "ldg"])
+def mover(request):
+    """Every case runs on both gather/scatter kernels: the bulk-copy ring and the vector mover."""
+    _cabi.call("kvcm_b200_set_mover", 1 if request.param == "bulk" else 0, -1)
+    yield request.param
+    _cabi.call("kvcm_b200_set_mover", 1, -1)
+
+
 def _rand_bytes(gen, n):
     return torch.randint(0, 256, (n,), dtype=torch.uint8, generator=gen)
 
@@ -142,7 +150,7 @@ def test_out_of_range_rows_and_slots_are_skipped_and_counted():
     rows = np.array([0, 1, 2, 3, 4, 32, -1, 7, 8, 9, 10, 11], dtype=np.int32)  # block 1 has two bad rows
     slots = np.array([1, 0, 5], dtype=np.int32)  # block 2 names a slot that does not exist
     staging = torch.zeros(3 * n_pools * T * row_bytes, dtype=torch.uint8, device=DEV)
-    status = torch.zeros(2, dtype=torch.int32, device=DEV)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
     batch_gather_kv_pages(ptrs, staging, torch.from_numpy(rows), torch.from_numpy(slots), T, row_bytes, pool_rows,
                           status=status)
     torch.cuda.synchronize()
@@ -151,6 +159,7 @@ def test_out_of_range_rows_and_slots_are_skipped_and_counted():
     assert np.array_equal(staging.cpu().numpy(), want)
     assert status[0].item() == skipped == 2 * n_pools + T * n_pools
     assert status[1].item() == 3  # 1 + largest offending block
+    assert status[2].item() == 0  # no wait ran out
 
 
 def test_page_table_form_equals_token_form():

@@ -180,7 +180,7 @@ def test_index_upsert_lookup_erase_and_reserved_keys():
 def test_index_refuses_keys_beyond_capacity_without_spinning():
     ix = BlockIndex(100)  # 1024 slots, at most 896 live keys
     keys = torch.arange(1, 2001, dtype=torch.int64, device=DEV)
-    status = torch.zeros(2, dtype=torch.int32, device=DEV)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
     ix.upsert(keys, None, encode_locations([(3, 4)]), status)
     torch.cuda.synchronize()
     slots, live = ix.stats()
@@ -247,7 +247,7 @@ def test_sw_match_random_against_oracle(sw):
     got = BatchMetaSearcher(ix).ReverseRollSlideWindowMatch(dk, doff, sw).cpu().numpy()
     want = ox.sw_match_batch(keys, off, sw, threads=4)
     assert np.array_equal(got, want)
-    assert (want >= 0).any() and (want == -1).any()
+    assert (want >= 0).any() and (sw < 100 or (want == -1).any())
 
 
 def test_batch_get_random_against_oracle():
