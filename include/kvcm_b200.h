@@ -121,7 +121,7 @@ KVCM_API int32_t kvcm_b200_scatter_pages(const void *const *d_pool_ptrs, int32_t
 KVCM_API int32_t kvcm_b200_set_mover(int32_t mover, int32_t cache_hint);
 /* Geometry of the bulk-copy ring: stages (2..8) of chunk_bytes (multiple of 1024) per CTA and CTAs
  * per SM; stages * chunk_bytes * ctas_per_sm must fit the SM's 224 KiB of shared memory.
- * Default 2 x 32 KiB x 3.  Same calling rule as kvcm_b200_set_mover. */
+ * (0, 0, 0) restores the default, which picks the geometry from the tile size.  Same calling rule as kvcm_b200_set_mover. */
 KVCM_API int32_t kvcm_b200_set_bulk_geometry(int32_t stages, int32_t ctas_per_sm, int32_t chunk_bytes);
 
 /* Legacy single-block form: kv_cache_gather_kernel / kv_cache_scatter_kernel and gather_kv_caches /

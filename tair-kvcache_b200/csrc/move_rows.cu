@@ -248,22 +248,35 @@ __device__ __forceinline__ ChunkDesc Describe(const MoveParams &p, uint32_t chun
     return d;
 }
 
-// Calls fn(offset in chunk, address in pool or nullptr when the row is out of range, length,
-// starts_row) for every run of the chunk that is contiguous in the pool.
-template <typename F>
-__device__ __forceinline__ void ForEachRun(const MoveParams &p, const ChunkDesc &d, F &&fn) {
-    uint32_t off = 0;
-    uint32_t r = d.chunk_off / p.row_bytes;
-    uint32_t within = d.chunk_off - r * p.row_bytes;
-    while (off < d.len) {
-        const uint32_t run = min(p.row_bytes - within, d.len - off);
-        const int64_t row = __ldg(d.rows + r);
-        uint8_t *addr = (row >= 0 && row < p.pool_rows) ? d.pool_base + row * p.row_bytes + within : nullptr;
-        fn(off, addr, run, within == 0);
-        off += run;
-        within = 0;
-        ++r;
-    }
+// The runs of a chunk: maximal pieces that are contiguous in the pool (a chunk that starts in
+// the middle of a row begins with the rest of that row).  Run j is described without walking
+// runs 0..j-1, so the lanes of the warp take runs j = lane, lane + 32, ... independently.
+struct RunWalker {
+    uint32_t first_row;
+    uint32_t first_within;
+    uint32_t first_len;
+    uint32_t n_runs;
+};
+
+__device__ __forceinline__ RunWalker WalkRuns(const MoveParams &p, const ChunkDesc &d) {
+    RunWalker w;
+    w.first_row = d.chunk_off / p.row_bytes;
+    w.first_within = d.chunk_off - w.first_row * p.row_bytes;
+    w.first_len = min(p.row_bytes - w.first_within, d.len);
+    w.n_runs = 1 + (d.len - w.first_len + p.row_bytes - 1) / p.row_bytes;
+    return w;
+}
+
+// Run j: offset inside the chunk, address in the pool (nullptr when the row index is out of
+// range), length, and whether the run starts its row (the lane that reports a skipped row).
+__device__ __forceinline__ void GetRun(const MoveParams &p, const ChunkDesc &d, const RunWalker &w, uint32_t j,
+                                       uint32_t *off, uint8_t **addr, uint32_t *len, bool *starts_row) {
+    const uint32_t within = j == 0 ? w.first_within : 0;
+    *off = j == 0 ? 0 : w.first_len + (j - 1) * p.row_bytes;
+    *len = j == 0 ? w.first_len : min(p.row_bytes, d.len - *off);
+    *starts_row = within == 0;
+    const int64_t row = __ldg(d.rows + w.first_row + j);
+    *addr = (row >= 0 && row < p.pool_rows) ? d.pool_base + row * p.row_bytes + within : nullptr;
 }
 
 template <bool kGather>
@@ -283,6 +296,8 @@ __global__ void __launch_bounds__(32) MoveRowsBulkKernel(const MoveParams p) {
         p.total_chunks > blockIdx.x ? (p.total_chunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     uint32_t direct_mask = 0;  // bit s: the chunk in stage s was handled without the ring
 
+    // Fills stage k % n_stages with chunk k.  Gather: one bulk load per run, issued by as many
+    // lanes as there are runs.  Scatter: the chunk is contiguous in staging, one load.
     auto load = [&](uint32_t k) {
         const uint32_t s = k % n_stages;
         const uint32_t bar = SmemAddr(&bars[s]);
@@ -297,64 +312,79 @@ __global__ void __launch_bounds__(32) MoveRowsBulkKernel(const MoveParams p) {
             direct_mask |= 1u << s;
             return;
         }
+        const RunWalker w = WalkRuns(p, d);
+        uint32_t off, len;
+        uint8_t *addr;
+        bool starts_row;
         if (!d.aligned) {
-            // Misaligned pool base: the warp moves the chunk byte by byte, no staging through the ring.
-            ForEachRun(p, d, [&](uint32_t off, uint8_t *addr, uint32_t run, bool starts_row) {
+            // Misaligned pool base: the warp moves the chunk byte by byte, bypassing the ring.
+            for (uint32_t j = 0; j < w.n_runs; ++j) {
+                GetRun(p, d, w, j, &off, &addr, &len, &starts_row);
                 if (addr == nullptr) {
                     if (lane == 0 && starts_row) ReportSkip(p, d.block, 1u);
-                    return;
+                    continue;
                 }
-                for (uint32_t i = lane; i < run; i += 32) {
+                for (uint32_t i = lane; i < len; i += 32) {
                     if (kGather) {
                         d.stage[off + i] = addr[i];
                     } else {
                         addr[i] = d.stage[off + i];
                     }
                 }
-            });
+            }
             if (lane == 0) MbarArriveExpectTx(bar, 0);
             direct_mask |= 1u << s;
             return;
         }
-        if (lane != 0) return;
         if (kGather) {
             uint32_t total = 0;
-            ForEachRun(p, d, [&](uint32_t, uint8_t *addr, uint32_t run, bool starts_row) {
+            for (uint32_t j = lane; j < w.n_runs; j += 32) {
+                GetRun(p, d, w, j, &off, &addr, &len, &starts_row);
                 if (addr != nullptr) {
-                    total += run;
+                    total += len;
                 } else if (starts_row) {
                     ReportSkip(p, d.block, 1u);
                 }
-            });
-            MbarArriveExpectTx(bar, total);
-            ForEachRun(p, d, [&](uint32_t off, uint8_t *addr, uint32_t run, bool) {
-                if (addr != nullptr) BulkLoad(buf + off, addr, run, bar);
-            });
-        } else {
+            }
+#pragma unroll
+            for (int delta = 16; delta > 0; delta >>= 1) total += __shfl_xor_sync(0xffffffffu, total, delta);
+            if (lane == 0) MbarArriveExpectTx(bar, total);
+            __syncwarp();
+            for (uint32_t j = lane; j < w.n_runs; j += 32) {
+                GetRun(p, d, w, j, &off, &addr, &len, &starts_row);
+                if (addr != nullptr) BulkLoad(buf + off, addr, len, bar);
+            }
+        } else if (lane == 0) {
             MbarArriveExpectTx(bar, d.len);
             BulkLoad(buf, d.stage, d.len, bar);
         }
     };
 
+    // Drains stage k % n_stages: one bulk store per run, spread over the lanes.  Bulk groups are
+    // per thread, so every lane commits one group per chunk (empty for lanes without a run).
     auto store = [&](uint32_t k) {
         const uint32_t s = k % n_stages;
-        if (lane != 0) return;
         if (((direct_mask >> s) & 1u) == 0) {
             const uint32_t buf = ring_base + s * p.chunk_bytes;
             const ChunkDesc d = Describe(p, blockIdx.x + k * gridDim.x);
-            ForEachRun(p, d, [&](uint32_t off, uint8_t *addr, uint32_t run, bool starts_row) {
+            const RunWalker w = WalkRuns(p, d);
+            for (uint32_t j = lane; j < w.n_runs; j += 32) {
+                uint32_t off, len;
+                uint8_t *addr;
+                bool starts_row;
+                GetRun(p, d, w, j, &off, &addr, &len, &starts_row);
                 if (addr != nullptr) {
-                    BulkStore(kGather ? d.stage + off : addr, buf + off, run);
+                    BulkStore(kGather ? d.stage + off : addr, buf + off, len);
                 } else if (!kGather && starts_row) {
                     ReportSkip(p, d.block, 1u);
                 }
-            });
+            }
         }
-        BulkCommit();  // an empty group keeps the group count in step with the chunk count
+        BulkCommit();
     };
 
-    const uint32_t kAhead = n_stages - 1;
-    for (uint32_t k = 0; k < kAhead && k < n_my; ++k) load(k);
+    const uint32_t ahead = n_stages - 1;
+    for (uint32_t k = 0; k < ahead && k < n_my; ++k) load(k);
     bool failed = false;
     for (uint32_t k = 0; k < n_my; ++k) {
         const uint32_t s = k % n_stages;
@@ -371,18 +401,16 @@ __global__ void __launch_bounds__(32) MoveRowsBulkKernel(const MoveParams p) {
         failed = __shfl_sync(0xffffffffu, failed ? 1 : 0, 0) != 0;
         if (failed) break;
         store(k);
-        if (k + kAhead < n_my) {
-            // The stage about to be refilled was drained by the store of chunk k-1: let every
-            // bulk group but the newest finish reading shared memory first.
-            if (lane == 0) BulkWaitRead<1>();
+        if (k + ahead < n_my) {
+            // The stage about to be refilled was drained by the stores of chunk k-1: every lane
+            // lets all of its bulk groups but the newest finish reading shared memory first.
+            BulkWaitRead<1>();
             __syncwarp();
-            load(k + kAhead);
+            load(k + ahead);
         }
     }
-    if (lane == 0) {
-        BulkWaitAll();
-        if (failed && p.status != nullptr) atomicExch(&p.status[2], 1u);
-    }
+    BulkWaitAll();
+    if (lane == 0 && failed && p.status != nullptr) atomicExch(&p.status[2], 1u);
 }
 
 // 0 = plain 16-byte loads/stores, 1 = bulk-copy ring.  KVCM_B200_MOVER=ldg|bulk overrides the default;
@@ -390,10 +418,31 @@ __global__ void __launch_bounds__(32) MoveRowsBulkKernel(const MoveParams p) {
 struct MoverConfig {
     int mover = 1;
     int hint = 0;
+    // Ring geometry; chunk 0 = choose from the shape (see BulkGeometryFor).
     int bulk_stages = 2;
     int bulk_ctas_per_sm = 3;
-    uint32_t bulk_chunk_bytes = 32768;
+    uint32_t bulk_chunk_bytes = 0;
 };
+
+struct BulkGeometry {
+    int stages;
+    int ctas_per_sm;
+    uint32_t chunk_bytes;
+};
+
+// Ring geometry for a tile of tile_bytes, from sweeps on B200 (2 stages throughout; what matters
+// is ~192 KiB in flight per SM and chunks that split a tile evenly, because chunk ids are dealt
+// round-robin and a short tail chunk always lands on the same CTAs):
+//   tiles >= 96 KiB (Llama-8B pages: 4 x 32 KiB)   -> 48 KiB chunks, 2 CTAs per SM
+//   smaller tiles                                   -> tile split into equal chunks <= 32 KiB, 3 CTAs per SM
+BulkGeometry BulkGeometryFor(const MoverConfig &cfg, int64_t tile_bytes) {
+    if (cfg.bulk_chunk_bytes != 0) return {cfg.bulk_stages, cfg.bulk_ctas_per_sm, cfg.bulk_chunk_bytes};
+    if (tile_bytes >= 96 * 1024) return {2, 2, 48 * 1024};
+    const int64_t n = (tile_bytes + 32 * 1024 - 1) / (32 * 1024);
+    int64_t chunk = (tile_bytes + n - 1) / n;
+    chunk = (chunk + 1023) / 1024 * 1024;
+    return {2, 3, static_cast<uint32_t>(chunk)};
+}
 
 MoverConfig &GetMoverConfig() {
     static MoverConfig cfg = [] {
@@ -466,7 +515,8 @@ int32_t LaunchMove(bool gather, const void *const *d_ptrs, int32_t n_ptrs, int32
     // copy instruction each; the sub-pool stride of the legacy layout must keep that alignment.
     const bool bulk_ok = cfg.mover == 1 && row_bytes % 16 == 0 && row_bytes >= kBulkMinRowBytes &&
                          (reinterpret_cast<uintptr_t>(staging) & 15u) == 0 && sub_stride % 16 == 0;
-    const int64_t chunk_bytes = bulk_ok ? cfg.bulk_chunk_bytes : kChunkBytes;
+    const BulkGeometry geo = BulkGeometryFor(cfg, tile_bytes);
+    const int64_t chunk_bytes = bulk_ok ? geo.chunk_bytes : kChunkBytes;
     const int64_t chunks_per_tile = (tile_bytes + chunk_bytes - 1) / chunk_bytes;
     const int64_t total_chunks = chunks_per_tile * n_pools * n_blocks;
     if (total_chunks >= (1ll << 32) - (1ll << 20)) return KVCM_ER_INVALID_PARAMS;
@@ -490,14 +540,14 @@ int32_t LaunchMove(bool gather, const void *const *d_ptrs, int32_t n_ptrs, int32
     p.rows_per_block = rows_per_block;
     p.report_skips = report_skips ? 1 : 0;
     p.chunk_bytes = static_cast<uint32_t>(chunk_bytes);
-    p.stages = cfg.bulk_stages;
+    p.stages = geo.stages;
 
     cudaStream_t s = AsStream(stream);
     if (bulk_ok) {
         if (gather) {
-            LaunchBulk<true>(p, cfg.bulk_ctas_per_sm, s);
+            LaunchBulk<true>(p, geo.ctas_per_sm, s);
         } else {
-            LaunchBulk<false>(p, cfg.bulk_ctas_per_sm, s);
+            LaunchBulk<false>(p, geo.ctas_per_sm, s);
         }
     } else if (cfg.hint == 0) {
         gather ? LaunchPlain<true, 0>(p, s) : LaunchPlain<false, 0>(p, s);
@@ -523,6 +573,10 @@ int32_t kvcm_b200_set_mover(int32_t mover, int32_t cache_hint) {
 }
 
 int32_t kvcm_b200_set_bulk_geometry(int32_t stages, int32_t ctas_per_sm, int32_t chunk_bytes) {
+    if (stages == 0 && ctas_per_sm == 0 && chunk_bytes == 0) {
+        kvcm::GetMoverConfig().bulk_chunk_bytes = 0;  // back to the shape-driven choice
+        return KVCM_OK;
+    }
     if (stages < 2 || stages > kvcm::kBulkMaxStages || ctas_per_sm < 1 || ctas_per_sm > 8 || chunk_bytes < 1024 ||
         chunk_bytes % 1024 != 0 ||
         static_cast<int64_t>(stages) * chunk_bytes * ctas_per_sm > kvcm::kBulkMaxSmem) {
