@@ -33,6 +33,10 @@ if ROOT not in sys.path:
 
 METRIC = "kv_block_gather_scatter_bandwidth"
 UNIT = "GB/s"
+# DRAM bytes read + written per algorithmic byte of MoveRowsBulkKernel, from the ncu capture summarised in
+# profiles/move_rows_bulk_llama8b_reduced_ncu_full.md (4.2505 GB per 4.2950 GB launch); traffic grows in
+# proportion to the blocks moved, so the full-size figure is this ratio times the launch's algorithmic bytes.
+DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = (2.147519 + 2.102969) / 4.294967296
 
 WORKLOADS = {
     # name: layers, kv pools per layer, page tokens, bytes per token per pool, pages per pool, blocks, pages per block
@@ -427,7 +431,9 @@ def main_b200(args, cfg, rank, world):
                    "parity_sample_ok": parity_ok},
         "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "MoveRowsKernel<gather>", "achieved": gather_gbs, "peak": peak,
-                     "peak_kind": peak_kind, "unit": "GB/s", "frac": gather_gbs / peak, "traffic": None,
+                     "peak_kind": peak_kind, "unit": "GB/s", "frac": gather_gbs / peak,
+                     "traffic": int(DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE * 2 * payload),
+                     "traffic_source": "ncu capture on a reduced case scaled by blocks moved",
                      "algorithmic_bytes_per_launch": 2 * payload, "launch_ms": gather_ms,
                      "scatter": {"kernel": "MoveRowsKernel<scatter>", "achieved": scatter_gbs,
                                  "frac": scatter_gbs / peak, "launch_ms": scatter_ms}},

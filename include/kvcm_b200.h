@@ -268,6 +268,30 @@ KVCM_API int32_t kvcm_b200_match_sw(kvcm_b200_index_t *index, const int64_t *d_k
 KVCM_API int32_t kvcm_b200_batch_get(kvcm_b200_index_t *index, const int64_t *d_keys, int64_t n, uint32_t avail_mask,
                                      uint8_t *d_flags_out, kvcm_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------
+ * (2c) Optimizer trace replay, no eviction.
+ *
+ * Replaces the sequential loop OptimizerRunner::RunTraces
+ * (kv_cache_manager/optimizer/manager/optimizer_runner.cc:29-215) over RadixTreeIndex::InsertWithQuery /
+ * PrefixQuery / InsertOnly (kv_cache_manager/optimizer/index/radix_tree_index.cc:198-282, 129-196, 19-87)
+ * for one instance.  Traces are given in replay order (sorted by timestamp) in CSR form; the order
+ * is the trace number.  d_trace_type[t]: 0 DialogTurn (query + insert of total_keys), 1 GetLocation
+ * (query; the first d_mask_off[t] keys are masked, d_mask_off may be NULL), 2 WriteCache (insert).
+ * Outputs per trace, as the ReadRecord / WriteRecord of the reference hold them: external hit
+ * blocks, internal (masked) hit blocks, blocks newly written, and - if d_cache_blocks is not NULL -
+ * the number of cached blocks after the trace.  Exact for prefix-unique chained keys (the output of
+ * the hash entry points); capacity-driven eviction is not modelled.
+ * d_workspace: caller-owned scratch of at least kvcm_b200_replay_workspace_bytes(n_keys_total)
+ * bytes, 256-byte aligned, contents irrelevant before and after.  d_status[0] counts keys that
+ * found no room in the scratch table (cannot happen with the stated size).
+ * ---------------------------------------------------------------------------------------- */
+KVCM_API int64_t kvcm_b200_replay_workspace_bytes(int64_t n_keys_total);
+KVCM_API int32_t kvcm_b200_replay(const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type,
+                                  const int64_t *d_mask_off, int32_t n_traces, int64_t n_keys_total,
+                                  void *d_workspace, int64_t workspace_bytes, int32_t *d_ext_hit,
+                                  int32_t *d_int_hit, int32_t *d_written, int64_t *d_cache_blocks,
+                                  uint32_t *d_status, kvcm_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

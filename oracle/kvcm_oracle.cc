@@ -462,4 +462,97 @@ uint32_t kvcm_oracle_iov_crc(const uint8_t *base, int64_t size, int64_t cal_byte
     return ~crc;
 }
 
+// ---------------------------------------------------------------------------------
+// (2c) Optimizer trace replay
+// ---------------------------------------------------------------------------------
+
+}  // extern "C"
+
+namespace {
+
+// The prefix tree of kv_cache_manager/optimizer/index/radix_tree_index.cc, without eviction
+// (IsBlockEvict is then always false).  The reference compresses chains of blocks into one
+// node and splits nodes on divergence (:89-127); with no eviction that is observationally a
+// plain trie with one block per node, which is what is kept here.
+struct TrieNode {
+    std::unordered_map<int64_t, TrieNode *> children;
+    ~TrieNode() {
+        for (auto &kv : children) delete kv.second;
+    }
+};
+
+struct OracleReplay {
+    TrieNode root;
+    int64_t cached_blocks = 0;
+};
+
+}  // namespace
+
+extern "C" {
+
+void *kvcm_oracle_replay_create() { return new OracleReplay(); }
+void kvcm_oracle_replay_destroy(void *h) { delete static_cast<OracleReplay *>(h); }
+
+// Replays traces in the given order (the caller sorts by timestamp, as
+// kv_cache_manager/optimizer/manager/optimizer_loader.cc:14-20 does).  Trace t owns
+// keys[key_off[t], key_off[t+1]).  type: 0 DialogTurn -> RadixTreeIndex::InsertWithQuery
+// (radix_tree_index.cc:198-282), 1 GetLocation -> PrefixQuery (:129-196) with the first
+// mask_off[t] keys masked, 2 WriteCache -> InsertOnly (:19-87).  Per trace, as
+// OptimizerRunner::HandleDialogTurn / HandleGetLocation / HandleWriteCache record them
+// (kv_cache_manager/optimizer/manager/optimizer_runner.cc:70-215): external hit blocks,
+// internal (masked) hit blocks, newly written blocks, and the cache size after the trace.
+void kvcm_oracle_replay_run(void *h, const int64_t *keys, const int64_t *key_off, const uint8_t *type,
+                            const int64_t *mask_off, int64_t n_traces, int32_t *ext_hit, int32_t *int_hit,
+                            int32_t *written, int64_t *cache_blocks) {
+    auto *st = static_cast<OracleReplay *>(h);
+    for (int64_t t = 0; t < n_traces; ++t) {
+        const int64_t *k = keys + key_off[t];
+        const int64_t n = key_off[t + 1] - key_off[t];
+        int32_t ext = 0, inte = 0, wr = 0;
+        TrieNode *node = &st->root;
+        if (type[t] == 1) {
+            // PrefixQuery classifies by key VALUE: a key counts as external when its value occurs
+            // at some unmasked position, else internal when it occurs at a masked one (:137-146,:165-173).
+            const int64_t mo = mask_off ? mask_off[t] : 0;
+            std::unordered_map<int64_t, int> cls;  // 1 = query key, 2 = mask key only
+            for (int64_t i = 0; i < n; ++i) {
+                if (i < mo) {
+                    cls.emplace(k[i], 2);
+                } else {
+                    cls[k[i]] = 1;
+                }
+            }
+            for (int64_t i = 0; i < n; ++i) {
+                auto it = node->children.find(k[i]);
+                if (it == node->children.end()) break;
+                if (cls[k[i]] == 1) {
+                    ++ext;
+                } else {
+                    ++inte;
+                }
+                node = it->second;
+            }
+        } else {
+            int64_t i = 0;
+            for (; i < n; ++i) {
+                auto it = node->children.find(k[i]);
+                if (it == node->children.end()) break;
+                node = it->second;
+            }
+            if (type[t] == 0) ext = static_cast<int32_t>(i);  // leading blocks already cached are the hits
+            for (; i < n; ++i) {
+                TrieNode *child = new TrieNode();
+                node->children.emplace(k[i], child);
+                node = child;
+                ++wr;
+            }
+            st->cached_blocks += wr;
+        }
+        ext_hit[t] = ext;
+        int_hit[t] = inte;
+        written[t] = wr;
+        cache_blocks[t] = st->cached_blocks;
+    }
+}
+
 }  // extern "C"

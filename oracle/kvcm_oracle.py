@@ -359,3 +359,43 @@ def iov_crc(buf, cal_bytes):
     buf = np.ascontiguousarray(np.frombuffer(buf, dtype=np.uint8) if isinstance(buf, (bytes, bytearray)) else buf)
     return int(lib().kvcm_oracle_iov_crc(ctypes.c_void_p(buf.ctypes.data), ctypes.c_int64(buf.nbytes),
                                          ctypes.c_int64(cal_bytes)))
+
+
+# ------------------------------------------------------------------------------------------
+# optimizer trace replay
+# ------------------------------------------------------------------------------------------
+
+TRACE_DIALOG_TURN, TRACE_GET_LOCATION, TRACE_WRITE_CACHE = 0, 1, 2
+
+
+class Replay:
+    """Sequential replay over the prefix tree, no eviction
+    (kv_cache_manager/optimizer/manager/optimizer_runner.cc:29-215)."""
+
+    def __init__(self):
+        lib().kvcm_oracle_replay_create.restype = ctypes.c_void_p
+        self._h = ctypes.c_void_p(lib().kvcm_oracle_replay_create())
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().kvcm_oracle_replay_destroy(self._h)
+            self._h = None
+
+    def run(self, keys, key_off, trace_type, mask_off=None):
+        """Returns (external hits, internal hits, written blocks, cached blocks after) per trace."""
+        keys, key_off = _i64(keys), _i64(key_off)
+        n = len(key_off) - 1
+        trace_type = np.ascontiguousarray(trace_type, dtype=np.uint8)
+        mp = None
+        if mask_off is not None:
+            mask_off = _i64(mask_off)
+            mp = _ptr(mask_off, ctypes.c_int64)
+        ext = np.zeros(n, dtype=np.int32)
+        inte = np.zeros(n, dtype=np.int32)
+        wr = np.zeros(n, dtype=np.int32)
+        cached = np.zeros(n, dtype=np.int64)
+        lib().kvcm_oracle_replay_run(self._h, _ptr(keys, ctypes.c_int64), _ptr(key_off, ctypes.c_int64),
+                                     _ptr(trace_type, ctypes.c_uint8), mp, ctypes.c_int64(n),
+                                     _ptr(ext, ctypes.c_int32), _ptr(inte, ctypes.c_int32), _ptr(wr, ctypes.c_int32),
+                                     _ptr(cached, ctypes.c_int64))
+        return ext, inte, wr, cached

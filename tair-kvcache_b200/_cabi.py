@@ -77,6 +77,8 @@ SIGNATURES = {
     "kvcm_b200_match_prefix": [_vp, _vp, _vp, _i32, _vp, _vp, _u32, _vp, _vp],
     "kvcm_b200_match_sw": [_vp, _vp, _vp, _i32, _i32, _u32, _vp, _vp],
     "kvcm_b200_batch_get": [_vp, _vp, _i64, _u32, _vp, _vp],
+    "kvcm_b200_replay_workspace_bytes": [_i64],
+    "kvcm_b200_replay": [_vp, _vp, _vp, _vp, _i32, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp],
 }
 
 
@@ -100,7 +102,8 @@ def lib():
         for name, argtypes in SIGNATURES.items():
             fn = getattr(L, name)
             fn.argtypes = argtypes
-            fn.restype = ctypes.c_char_p if name == "kvcm_b200_error_string" else _i32
+            fn.restype = (ctypes.c_char_p if name == "kvcm_b200_error_string" else
+                          _i64 if name == "kvcm_b200_replay_workspace_bytes" else _i32)
         _lib = L
     return _lib
 

@@ -1,0 +1,3 @@
+"""Batched twin of the Optimizer's trace replay loop (kv_cache_manager/optimizer/manager)."""
+from .replay import (TRACE_DIALOG_TURN, TRACE_GET_LOCATION, TRACE_WRITE_CACHE, ReplayResult,  # noqa: F401
+                     RunTraces, replay_workspace_bytes)

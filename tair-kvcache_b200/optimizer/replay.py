@@ -1,0 +1,57 @@
+"""Trace replay on the GPU, no eviction.
+
+RunTraces is the batched twin of OptimizerRunner::RunTraces
+(kv_cache_manager/optimizer/manager/optimizer_runner.cc:29-215): every trace of one instance in one
+call, results as the per-trace numbers the reference keeps in ReadRecord / WriteRecord
+(kv_cache_manager/optimizer/analysis/result_structure.h:6-33).
+"""
+from typing import NamedTuple, Optional
+
+import torch
+
+from .. import _cabi
+
+TRACE_DIALOG_TURN, TRACE_GET_LOCATION, TRACE_WRITE_CACHE = 0, 1, 2
+
+
+class ReplayResult(NamedTuple):
+    external_hit_blocks: torch.Tensor  # int32 per trace
+    internal_hit_blocks: torch.Tensor  # int32 per trace (masked keys that were cached)
+    write_blocks: torch.Tensor         # int32 per trace
+    current_cache_blocks: torch.Tensor  # int64 per trace, after the trace
+
+
+def replay_workspace_bytes(n_keys_total: int) -> int:
+    n = _cabi.lib().kvcm_b200_replay_workspace_bytes(n_keys_total)
+    if n < 0:
+        raise ValueError("too many keys for one replay call")
+    return n
+
+
+def RunTraces(keys: torch.Tensor, key_off: torch.Tensor, trace_type: torch.Tensor,
+              mask_off: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None,
+              status: Optional[torch.Tensor] = None) -> ReplayResult:
+    """keys: int64 CUDA tensor of chained block keys, CSR by key_off (int64, n_traces + 1), traces in replay
+    (timestamp) order; trace_type: uint8 per trace (TRACE_*); mask_off: int64 per trace for GetLocation traces.
+    workspace: optional uint8 CUDA tensor of replay_workspace_bytes(keys.numel()) bytes to reuse across calls."""
+    if not keys.is_cuda:
+        raise ValueError("keys must be a CUDA tensor: this path has no CPU implementation")
+    dev = keys.device
+    keys, key_off, trace_type = keys.contiguous(), key_off.contiguous(), trace_type.contiguous()
+    n_traces = key_off.numel() - 1
+    need = replay_workspace_bytes(keys.numel())
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+    elif workspace.numel() < need or workspace.device != dev:
+        raise ValueError("workspace too small: %d < %d bytes" % (workspace.numel(), need))
+    ext = torch.empty(max(n_traces, 1), dtype=torch.int32, device=dev)
+    inte = torch.empty_like(ext)
+    wr = torch.empty_like(ext)
+    size = torch.empty(max(n_traces, 1), dtype=torch.int64, device=dev)
+    _cabi.bind_device(dev.index)
+    _cabi.call("kvcm_b200_replay", keys.data_ptr(), key_off.data_ptr(), trace_type.data_ptr(),
+               mask_off.contiguous().data_ptr() if mask_off is not None else None, n_traces, keys.numel(),
+               workspace.data_ptr(), workspace.numel(), ext.data_ptr(), inte.data_ptr(), wr.data_ptr(),
+               size.data_ptr(), status.data_ptr() if status is not None else None,
+               torch.cuda.current_stream(dev).cuda_stream)
+    return ReplayResult(ext[:n_traces], inte[:n_traces], wr[:n_traces], size[:n_traces])

@@ -200,3 +200,18 @@ def test_copy_iovs_ignore_advances_offset():
     a2, b2 = np.zeros_like(a), np.zeros_like(b)
     oracle.copy_iovs([(a2, 8, False), (None, 4, True), (b2, 4, False)], s, 1)
     assert np.array_equal(a, a2) and np.array_equal(b, b2)
+
+
+def test_replay_reference_known_answers():
+    # kv_cache_manager/optimizer/test/optimizer_manager_py_test.py:57-84
+    ext, inte, wr, size = oracle.Replay().run([1, 2, 3, 1, 2, 4], [0, 3, 6],
+                                              [oracle.TRACE_WRITE_CACHE, oracle.TRACE_GET_LOCATION])
+    assert ext.tolist() == [0, 2] and wr.tolist() == [3, 0] and size.tolist() == [3, 3]
+    ext, inte, wr, size = oracle.Replay().run([1, 2], [0, 2], [oracle.TRACE_WRITE_CACHE])
+    assert wr.tolist() == [2] and ext.tolist() == [0]
+    # dialog turns read and write in one step; masked keys count as internal hits
+    ext, inte, wr, size = oracle.Replay().run([1, 2, 3, 1, 2, 4, 5, 1, 2, 4], [0, 3, 7, 10],
+                                              [oracle.TRACE_DIALOG_TURN, oracle.TRACE_DIALOG_TURN,
+                                               oracle.TRACE_GET_LOCATION], [0, 0, 1])
+    assert ext.tolist() == [0, 2, 2] and inte.tolist() == [0, 0, 1] and wr.tolist() == [3, 2, 0]
+    assert size.tolist() == [3, 5, 5]
