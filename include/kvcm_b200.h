@@ -53,6 +53,7 @@ extern "C" {
 #define KVCM_EC_NOENT (KVCM_EC_BASE + 2)            /* EC_NOENT */
 #define KVCM_EC_BADARGS (KVCM_EC_BASE + 6)          /* EC_BADARGS */
 #define KVCM_EC_NOSPC (KVCM_EC_BASE + 9)            /* EC_NOSPC: index full */
+#define KVCM_EC_OUT_OF_LIMIT (KVCM_EC_BASE + 14)    /* EC_OUT_OF_LIMIT: size beyond a fixed limit */
 
 typedef void *kvcm_stream_t; /* cudaStream_t */
 
@@ -291,6 +292,34 @@ KVCM_API int32_t kvcm_b200_replay(const int64_t *d_keys, const int64_t *d_key_of
                                   void *d_workspace, int64_t workspace_bytes, int32_t *d_ext_hit,
                                   int32_t *d_int_hit, int32_t *d_written, int64_t *d_cache_blocks,
                                   uint32_t *d_status, kvcm_stream_t stream);
+
+/* Trace replay for callers that cannot allocate device memory.  (No counterpart in the reference: it
+ * exists for how this library gets embedded, not for a reference interface.)
+ *
+ * Who needs it: a connector or optimizer hook that runs inside an inference engine's process after
+ * the engine has claimed nearly all of HBM for weights and KV pools - a cudaMalloc at that point can
+ * fail, and even when it succeeds it synchronises the device and stalls the engine's streams - and
+ * plugin hosts whose rules simply forbid allocator calls on the serving path.  Such a caller owns its
+ * inputs and outputs but has nowhere to get the replay's scratch table from.
+ *
+ * Same arguments, results and kernels as kvcm_b200_replay minus the workspace pair: the scratch table
+ * is a fixed array inside the library's device image, KVCM_B200_REPLAY_NOALLOC_SCRATCH_BYTES (8 MiB +
+ * 256 B) held by every GPU that loads the library until the process exits.  Limits and rules:
+ *   - at most KVCM_B200_REPLAY_NOALLOC_MAX_KEYS keys per call; more returns KVCM_EC_OUT_OF_LIMIT
+ *     ("size beyond the fixed limit of this entry point") before anything is launched;
+ *   - the call performs no cudaMalloc / cudaFree and calls no allocating library routine;
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress with that
+ *     device current); make that first call before any stream capture begins;
+ *   - every call on a device shares the one array.  Each call rebuilds the part of the table it uses
+ *     before reading it, so results never depend on the previous call, but two calls that overlap on
+ *     the GPU (different streams, or threads without ordering) race on it: serialise them. */
+#define KVCM_B200_REPLAY_NOALLOC_MAX_KEYS 262144
+#define KVCM_B200_REPLAY_NOALLOC_SCRATCH_BYTES (524288 * 16 + 256)
+KVCM_API int32_t kvcm_b200_replay_noalloc(const int64_t *d_keys, const int64_t *d_key_off,
+                                          const uint8_t *d_trace_type, const int64_t *d_mask_off, int32_t n_traces,
+                                          int64_t n_keys_total, int32_t *d_ext_hit, int32_t *d_int_hit,
+                                          int32_t *d_written, int64_t *d_cache_blocks, uint32_t *d_status,
+                                          kvcm_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -22,6 +22,8 @@ KVCM_EC_ERROR = KVCM_EC_BASE + 1
 KVCM_EC_NOENT = KVCM_EC_BASE + 2
 KVCM_EC_BADARGS = KVCM_EC_BASE + 6
 KVCM_EC_NOSPC = KVCM_EC_BASE + 9
+KVCM_EC_OUT_OF_LIMIT = KVCM_EC_BASE + 14
+REPLAY_NOALLOC_MAX_KEYS = 262144
 
 VAL_NONEMPTY = 1 << 32
 VAL_PRESENT = 1 << 63
@@ -79,6 +81,7 @@ SIGNATURES = {
     "kvcm_b200_batch_get": [_vp, _vp, _i64, _u32, _vp, _vp],
     "kvcm_b200_replay_workspace_bytes": [_i64],
     "kvcm_b200_replay": [_vp, _vp, _vp, _vp, _i32, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp],
+    "kvcm_b200_replay_noalloc": [_vp, _vp, _vp, _vp, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _vp],
 }
 
 

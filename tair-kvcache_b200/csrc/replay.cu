@@ -14,7 +14,13 @@
 //
 // Scratch: an open-addressing table {int64 key, uint64 first_writer} in caller-provided
 // workspace, 16-byte slots, at least twice as many slots as keys.
+#include <mutex>
+
 #include "kvcm_common.cuh"
+
+// Scratch of kvcm_b200_replay_noalloc: a fixed table that lives in the library's device image.
+// Every GPU that loads the library holds these bytes until the process exits.
+static __device__ __align__(256) unsigned char g_replay_noalloc_scratch[KVCM_B200_REPLAY_NOALLOC_SCRATCH_BYTES];
 
 namespace kvcm {
 namespace {
@@ -190,6 +196,48 @@ int32_t kvcm_b200_replay(const int64_t *d_keys, const int64_t *d_key_off, const 
         kvcm::ReplayRunningSizeKernel<<<1, 1024, 0, s>>>(d_written, n_traces, 0, d_cache_blocks);
     }
     return kvcm::LaunchStatus();
+}
+
+// The replay for callers that must not allocate.  Same contract and same kernels as
+// kvcm_b200_replay; the scratch table is g_replay_noalloc_scratch instead of caller memory.
+//
+// In host code the name of a __device__ array is only a stand-in, not an address a kernel can
+// use, so the device address is asked for once per device - with that device current - through
+// cudaGetSymbolAddress and kept.  The first call on a device performs that query.
+int32_t kvcm_b200_replay_noalloc(const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type,
+                                 const int64_t *d_mask_off, int32_t n_traces, int64_t n_keys_total,
+                                 int32_t *d_ext_hit, int32_t *d_int_hit, int32_t *d_written, int64_t *d_cache_blocks,
+                                 uint32_t *d_status, kvcm_stream_t stream) {
+    if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
+    if (n_keys_total < 0) return KVCM_EC_BADARGS;
+    if (n_keys_total > KVCM_B200_REPLAY_NOALLOC_MAX_KEYS) return KVCM_EC_OUT_OF_LIMIT;
+
+    constexpr int kMaxDevices = 64;
+    static std::mutex mu;
+    static void *scratch_of_device[kMaxDevices] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        cudaGetLastError();
+        return KVCM_ER_NO_DEVICE;
+    }
+    void *scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (scratch_of_device[dev] == nullptr) {
+            void *p = nullptr;
+            if (cudaGetSymbolAddress(&p, g_replay_noalloc_scratch) != cudaSuccess || p == nullptr) {
+                cudaGetLastError();
+                return KVCM_ER_INVALID_ADDRESS;
+            }
+            scratch_of_device[dev] = p;
+        }
+        scratch = scratch_of_device[dev];
+    }
+    // The table is rebuilt from its first slot by every call (the init kernel covers every slot
+    // the call uses), so what an earlier call left behind is never read.
+    return kvcm_b200_replay(d_keys, d_key_off, d_trace_type, d_mask_off, n_traces, n_keys_total, scratch,
+                            KVCM_B200_REPLAY_NOALLOC_SCRATCH_BYTES, d_ext_hit, d_int_hit, d_written, d_cache_blocks,
+                            d_status, stream);
 }
 
 }  // extern "C"

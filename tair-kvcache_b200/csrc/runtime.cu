@@ -50,6 +50,7 @@ const char *kvcm_b200_error_string(int32_t code) {
         case KVCM_EC_NOENT: return "entry does not exist";
         case KVCM_EC_BADARGS: return "bad arguments";
         case KVCM_EC_NOSPC: return "out of space";
+        case KVCM_EC_OUT_OF_LIMIT: return "size beyond the fixed limit of this entry point";
         default: return "unknown code";
     }
 }
