@@ -270,6 +270,31 @@ KVCM_API int32_t kvcm_b200_batch_get(kvcm_b200_index_t *index, const int64_t *d_
                                      uint8_t *d_flags_out, kvcm_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Hash-range-sharded index: one logical index split over shard_count GPUs.  Key k belongs to shard
+ * floor(fmix64(k) * shard_count / 2^64).  Each GPU holds an ordinary index with the keys it owns;
+ * the exchange between GPUs (all-gather of keys, min / max reduction of results) is the caller's,
+ * over NCCL.  The reference has no sharded index (one MetaIndexer per instance,
+ * kv_cache_manager/meta/meta_indexer_manager.cc:9-30); these entry points keep the results of the
+ * matchers above identical when the table is split:
+ *   upsert_sharded        inserts only the keys this shard owns out of the full batch;
+ *   match_prefix_sharded  as match_prefix, but keys of other shards never stop the count, so
+ *                         min over shards of d_len_out = the unsharded prefix length;
+ *   batch_get (above)     on a shard returns 0 for keys it does not own, so a byte-wise max over
+ *                         shards of the flags = the unsharded flags;
+ *   match_sw_from_flags   the sliding-window search of match_sw over such combined flags (bit0).
+ * ---------------------------------------------------------------------------------------- */
+KVCM_API int32_t kvcm_b200_index_upsert_sharded(kvcm_b200_index_t *index, const int64_t *d_keys,
+                                                const uint64_t *d_values, uint64_t uniform_value, int64_t n,
+                                                int32_t shard_count, int32_t shard_rank, uint32_t *d_status,
+                                                kvcm_stream_t stream);
+KVCM_API int32_t kvcm_b200_match_prefix_sharded(kvcm_b200_index_t *index, const int64_t *d_keys,
+                                                const int64_t *d_key_off, int32_t n_req, const int64_t *d_mask_off,
+                                                const uint8_t *d_mask_bits, uint32_t avail_mask, int32_t shard_count,
+                                                int32_t shard_rank, int32_t *d_len_out, kvcm_stream_t stream);
+KVCM_API int32_t kvcm_b200_match_sw_from_flags(const uint8_t *d_flags, const int64_t *d_key_off, int32_t n_req,
+                                               int32_t sw_blocks, int32_t *d_base_out, kvcm_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
  * (2c) Optimizer trace replay, no eviction.
  *
  * Replaces the sequential loop OptimizerRunner::RunTraces

@@ -45,6 +45,16 @@ __host__ __device__ __forceinline__ uint64_t Mix(uint64_t k) {
     return k;
 }
 
+// Hash-range sharding of one logical index over `shards` GPUs: a key belongs to the shard whose
+// range of the mixed 64-bit hash contains it.  shards == 1 owns everything.
+struct Shard {
+    uint32_t count;
+    uint32_t rank;
+};
+__device__ __forceinline__ bool Owns(const Shard &sh, uint64_t key) {
+    return sh.count <= 1 || static_cast<uint32_t>(__umul64hi(Mix(key), sh.count)) == sh.rank;
+}
+
 __device__ __forceinline__ ulonglong2 LoadSlot(const ulonglong2 *p) {
     ulonglong2 s;
     asm volatile("ld.global.v2.u64 {%0,%1}, [%2];\n" : "=l"(s.x), "=l"(s.y) : "l"(p));
@@ -80,10 +90,11 @@ __global__ void ClearKernel(IndexView ix) {
 }
 
 __global__ void UpsertKernel(IndexView ix, const int64_t *__restrict__ keys, const uint64_t *__restrict__ values,
-                             uint64_t uniform_value, int64_t n, uint32_t *status) {
+                             uint64_t uniform_value, int64_t n, Shard shard, uint32_t *status) {
     const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const uint64_t key = static_cast<uint64_t>(keys[i]);
+    if (!Owns(shard, key)) return;
     const uint64_t value = (values != nullptr ? values[i] : uniform_value) | KVCM_VAL_PRESENT;
     if (key == kEmptyKey || key == kTombKey) {
         const uint64_t old = atomicExch(reinterpret_cast<unsigned long long *>(&ix.cells[key - kEmptyKey]), value);
@@ -177,7 +188,7 @@ __global__ void BatchGetKernel(IndexView ix, const int64_t *__restrict__ keys, i
 __global__ void __launch_bounds__(kMatchWarps * 32)
     PrefixMatchKernel(IndexView ix, const int64_t *__restrict__ keys, const int64_t *__restrict__ key_off,
                       int32_t n_req, const int64_t *__restrict__ mask_off, const uint8_t *__restrict__ mask_bits,
-                      uint32_t avail_mask, int32_t *__restrict__ len_out) {
+                      uint32_t avail_mask, Shard shard, int32_t *__restrict__ len_out) {
     const int32_t req = blockIdx.x * kMatchWarps + (threadIdx.x >> 5);
     if (req >= n_req) return;
     const uint32_t lane = LaneId();
@@ -191,7 +202,10 @@ __global__ void __launch_bounds__(kMatchWarps * 32)
         if (i < n) {
             const bool masked = i < skip || (mask_bits != nullptr && mask_bits[beg + i] != 0);
             if (!masked) {
-                const bool hit = Servable(Lookup(ix, static_cast<uint64_t>(keys[beg + i])), avail_mask);
+                // A key of another shard cannot stop this shard's count: its owner decides, and the
+                // caller takes the minimum over shards.
+                const uint64_t key = static_cast<uint64_t>(keys[beg + i]);
+                const bool hit = !Owns(shard, key) || Servable(Lookup(ix, key), avail_mask);
                 counted = hit;
                 stop = !hit;
             }
@@ -233,6 +247,51 @@ __global__ void __launch_bounds__(kMatchWarps * 32)
         const bool hit = i >= 0 && Servable(Lookup(ix, static_cast<uint64_t>(keys[beg + i])), avail_mask);
         const uint32_t bits = __ballot_sync(0xffffffffu, hit);
         int cur = 32;  // bits [0, cur) are still to be scanned, from bit cur-1 downwards
+        while (cur > 0) {
+            const uint32_t x = bits << (32 - cur);
+            int ones = __clz(~x);
+            ones = ones < cur ? ones : cur;
+            run += ones;
+            cur -= ones;
+            if (run >= sw) {
+                found = right_end - sw;
+                break;
+            }
+            if (cur > 0) {
+                int zeros = __clz(bits << (32 - cur));
+                zeros = zeros < cur ? zeros : cur;
+                cur -= zeros;
+                run = 0;
+                right_end = lo + cur;
+            }
+        }
+    }
+    if (lane == 0) base_out[req] = static_cast<int32_t>(found);
+}
+
+// The same right-to-left window search over a per-key servable byte (bit0) instead of index
+// probes: the second half of the sharded sliding-window match, run after the per-key flags of all
+// shards have been combined.
+__global__ void __launch_bounds__(kMatchWarps * 32)
+    SwFromFlagsKernel(const uint8_t *__restrict__ flags, const int64_t *__restrict__ key_off, int32_t n_req, int32_t sw,
+                      int32_t *__restrict__ base_out) {
+    const int32_t req = blockIdx.x * kMatchWarps + (threadIdx.x >> 5);
+    if (req >= n_req) return;
+    const uint32_t lane = LaneId();
+    const int64_t beg = key_off[req];
+    const int64_t n = key_off[req + 1] - beg;
+    if (n < sw) {
+        if (lane == 0) base_out[req] = -2;
+        return;
+    }
+    int64_t run = 0, right_end = n, found = -1;
+    for (int64_t hi = n; hi > 0 && found < 0; hi -= 32) {
+        if (hi + run < sw) break;
+        const int64_t lo = hi - 32;
+        const int64_t i = lo + lane;
+        const bool hit = i >= 0 && (flags[beg + i] & KVCM_FLAG_SERVABLE) != 0;
+        const uint32_t bits = __ballot_sync(0xffffffffu, hit);
+        int cur = 32;
         while (cur > 0) {
             const uint32_t x = bits << (32 - cur);
             int ones = __clz(~x);
@@ -336,8 +395,21 @@ int32_t kvcm_b200_index_upsert(kvcm_b200_index_t *ix, const int64_t *d_keys, con
     if (n < 0) return KVCM_EC_BADARGS;
     if (n == 0) return KVCM_OK;
     if (d_keys == nullptr) return KVCM_ER_INVALID_ADDRESS;
-    kvcm::UpsertKernel<<<kvcm::GridFor(n, 256), 256, 0, kvcm::AsStream(stream)>>>(kvcm::View(ix), d_keys, d_values,
-                                                                                   uniform_value, n, d_status);
+    kvcm::UpsertKernel<<<kvcm::GridFor(n, 256), 256, 0, kvcm::AsStream(stream)>>>(
+        kvcm::View(ix), d_keys, d_values, uniform_value, n, kvcm::Shard{1, 0}, d_status);
+    return kvcm::LaunchStatus();
+}
+
+int32_t kvcm_b200_index_upsert_sharded(kvcm_b200_index_t *ix, const int64_t *d_keys, const uint64_t *d_values,
+                                       uint64_t uniform_value, int64_t n, int32_t shard_count, int32_t shard_rank,
+                                       uint32_t *d_status, kvcm_stream_t stream) {
+    if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (n < 0 || shard_count < 1 || shard_rank < 0 || shard_rank >= shard_count) return KVCM_EC_BADARGS;
+    if (n == 0) return KVCM_OK;
+    if (d_keys == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    kvcm::UpsertKernel<<<kvcm::GridFor(n, 256), 256, 0, kvcm::AsStream(stream)>>>(
+        kvcm::View(ix), d_keys, d_values, uniform_value, n,
+        kvcm::Shard{static_cast<uint32_t>(shard_count), static_cast<uint32_t>(shard_rank)}, d_status);
     return kvcm::LaunchStatus();
 }
 
@@ -370,7 +442,33 @@ int32_t kvcm_b200_match_prefix(kvcm_b200_index_t *ix, const int64_t *d_keys, con
     if (d_key_off == nullptr || d_len_out == nullptr) return KVCM_ER_INVALID_ADDRESS;
     kvcm::PrefixMatchKernel<<<kvcm::GridFor(n_req, kvcm::kMatchWarps), kvcm::kMatchWarps * 32, 0,
                               kvcm::AsStream(stream)>>>(kvcm::View(ix), d_keys, d_key_off, n_req, d_mask_off,
-                                                        d_mask_bits, avail_mask, d_len_out);
+                                                        d_mask_bits, avail_mask, kvcm::Shard{1, 0}, d_len_out);
+    return kvcm::LaunchStatus();
+}
+
+int32_t kvcm_b200_match_prefix_sharded(kvcm_b200_index_t *ix, const int64_t *d_keys, const int64_t *d_key_off,
+                                       int32_t n_req, const int64_t *d_mask_off, const uint8_t *d_mask_bits,
+                                       uint32_t avail_mask, int32_t shard_count, int32_t shard_rank,
+                                       int32_t *d_len_out, kvcm_stream_t stream) {
+    if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (n_req < 0 || shard_count < 1 || shard_rank < 0 || shard_rank >= shard_count) return KVCM_EC_BADARGS;
+    if (n_req == 0) return KVCM_OK;
+    if (d_key_off == nullptr || d_len_out == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    kvcm::PrefixMatchKernel<<<kvcm::GridFor(n_req, kvcm::kMatchWarps), kvcm::kMatchWarps * 32, 0,
+                              kvcm::AsStream(stream)>>>(
+        kvcm::View(ix), d_keys, d_key_off, n_req, d_mask_off, d_mask_bits, avail_mask,
+        kvcm::Shard{static_cast<uint32_t>(shard_count), static_cast<uint32_t>(shard_rank)}, d_len_out);
+    return kvcm::LaunchStatus();
+}
+
+int32_t kvcm_b200_match_sw_from_flags(const uint8_t *d_flags, const int64_t *d_key_off, int32_t n_req,
+                                      int32_t sw_blocks, int32_t *d_base_out, kvcm_stream_t stream) {
+    if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
+    if (n_req < 0 || sw_blocks <= 0) return KVCM_EC_BADARGS;
+    if (n_req == 0) return KVCM_OK;
+    if (d_key_off == nullptr || d_base_out == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    kvcm::SwFromFlagsKernel<<<kvcm::GridFor(n_req, kvcm::kMatchWarps), kvcm::kMatchWarps * 32, 0,
+                              kvcm::AsStream(stream)>>>(d_flags, d_key_off, n_req, sw_blocks, d_base_out);
     return kvcm::LaunchStatus();
 }
 

@@ -2,3 +2,4 @@
 from .block_index import BlockIndex, encode_locations  # noqa: F401
 from .hash_util import ApplyPrefixHashBatch, GenKeyVectorBatch, key_offsets  # noqa: F401
 from .meta_searcher import BatchMetaSearcher, QueryType  # noqa: F401
+from .sharded_searcher import CudaShardBackend, ShardedMetaSearcher, shard_of_keys  # noqa: F401

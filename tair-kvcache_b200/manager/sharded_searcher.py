@@ -1,0 +1,151 @@
+"""Hash-range-sharded matching across GPUs: one process per GPU, one index shard per process.
+
+The index of one instance is split by key-hash range over the ranks of a torch.distributed group; every
+rank hashes and submits its own batch of requests.  One exchange step per query:
+
+  prefix match    all-gather of keys  ->  every shard counts leading keys, skipping keys it does not own
+                  ->  all-reduce(MIN) of the per-request lengths;
+  sliding window  all-gather of keys  ->  every shard writes the servable flag of the keys it owns
+                  ->  all-reduce(MAX) of the flag bytes  ->  local window search over the flags.
+
+Both equal MetaSearcher::PrefixMatch / ReverseRollSlideWindowMatch
+(kv_cache_manager/manager/meta_searcher.cc:120-145, 196-265) on the unsharded index because every key has
+exactly one owner.  The collectives run over the group's backend (NCCL on GPUs); data lands in local
+buffers before any kernel reads it.
+"""
+from typing import Optional, Tuple
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from .. import _cabi
+
+_MASK64 = (1 << 64) - 1
+
+
+def shard_of_keys(keys: np.ndarray, shard_count: int) -> np.ndarray:
+    """Owner shard of each int64 key: floor(fmix64(key) * shard_count / 2**64).  Host twin of the device rule."""
+    out = np.empty(len(keys), dtype=np.int32)
+    for i, k in enumerate(np.asarray(keys, dtype=np.int64).tolist()):
+        k &= _MASK64
+        k ^= k >> 33
+        k = (k * 0xFF51AFD7ED558CCD) & _MASK64
+        k ^= k >> 33
+        k = (k * 0xC4CEB9FE1A85EC53) & _MASK64
+        k ^= k >> 33
+        out[i] = (k * shard_count) >> 64
+    return out
+
+
+class CudaShardBackend:
+    """The shard-local work, on the GPU through the C ABI."""
+
+    def __init__(self, max_keys: int, device: torch.device, avail_mask: int = _cabi.AVAIL_ALL):
+        from .block_index import BlockIndex
+        self.index = BlockIndex(max_keys, device)
+        self.device = self.index.device
+        self.avail_mask = avail_mask
+
+    def upsert_owned(self, keys, value_word, shard_count, shard_rank):
+        _cabi.call("kvcm_b200_index_upsert_sharded", self.index.handle, keys.data_ptr(), None, value_word,
+                   keys.numel(), shard_count, shard_rank, None, self.index._s())
+
+    def prefix_owned(self, keys, key_off, mask_off, shard_count, shard_rank):
+        n_req = key_off.numel() - 1
+        out = torch.empty(n_req, dtype=torch.int32, device=self.device)
+        _cabi.call("kvcm_b200_match_prefix_sharded", self.index.handle, keys.data_ptr(), key_off.data_ptr(), n_req,
+                   mask_off.data_ptr() if mask_off is not None else None, None, self.avail_mask, shard_count,
+                   shard_rank, out.data_ptr(), self.index._s())
+        return out
+
+    def servable_flags(self, keys):
+        out = torch.empty(keys.numel(), dtype=torch.uint8, device=self.device)
+        _cabi.call("kvcm_b200_batch_get", self.index.handle, keys.data_ptr(), keys.numel(), self.avail_mask,
+                   out.data_ptr(), self.index._s())
+        return out
+
+    def sw_from_flags(self, flags, key_off, sw):
+        n_req = key_off.numel() - 1
+        out = torch.empty(n_req, dtype=torch.int32, device=self.device)
+        _cabi.call("kvcm_b200_match_sw_from_flags", flags.data_ptr(), key_off.data_ptr(), n_req, sw, out.data_ptr(),
+                   self.index._s())
+        return out
+
+
+class ShardedMetaSearcher:
+    """Collective front end: every rank of `group` calls each method with its own requests."""
+
+    def __init__(self, backend, group: Optional[dist.ProcessGroup] = None):
+        self.backend = backend
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.device = backend.device
+
+    # ---- exchange -----------------------------------------------------------------------------
+    def _gather_requests(self, keys: torch.Tensor, key_off: torch.Tensor, per_req: Optional[torch.Tensor]
+                         ) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor], int, int]:
+        """All ranks' requests as one CSR batch with fixed per-rank strides.
+
+        Rank r contributes max_req + 1 requests over a segment of max_keys keys: its real requests, then empty
+        ones up to max_req, then one filler request that covers the zero padding of its segment (so the CSR
+        stays contiguous).  Returns (all keys, all offsets, all per-request values, max_req, my first request)."""
+        n_req, n_keys = key_off.numel() - 1, int(keys.numel())
+        sizes = torch.tensor([n_req, n_keys], dtype=torch.int64, device=self.device)
+        all_sizes = torch.empty(self.world * 2, dtype=torch.int64, device=self.device)
+        dist.all_gather_into_tensor(all_sizes, sizes, group=self.group)
+        all_sizes = all_sizes.view(self.world, 2).cpu()
+        max_req, max_keys = int(all_sizes[:, 0].max()), int(all_sizes[:, 1].max())
+        seg_keys = torch.zeros(max(max_keys, 1), dtype=torch.int64, device=self.device)
+        seg_keys[:n_keys] = keys
+        seg_off = torch.full((max_req + 1,), n_keys, dtype=torch.int64, device=self.device)
+        seg_off[:n_req + 1] = key_off
+        all_keys = torch.empty(self.world * seg_keys.numel(), dtype=torch.int64, device=self.device)
+        all_off = torch.empty(self.world * (max_req + 1), dtype=torch.int64, device=self.device)
+        dist.all_gather_into_tensor(all_keys, seg_keys, group=self.group)
+        dist.all_gather_into_tensor(all_off, seg_off, group=self.group)
+        stride = seg_keys.numel()
+        base = torch.arange(self.world, dtype=torch.int64, device=self.device).repeat_interleave(max_req + 1) * stride
+        csr = torch.cat([all_off + base, torch.tensor([self.world * stride], dtype=torch.int64, device=self.device)])
+        all_per_req = None
+        if per_req is not None:
+            seg = torch.zeros(max_req + 1, dtype=per_req.dtype, device=self.device)
+            seg[:n_req] = per_req
+            all_per_req = torch.empty(self.world * (max_req + 1), dtype=per_req.dtype, device=self.device)
+            dist.all_gather_into_tensor(all_per_req, seg, group=self.group)
+        return all_keys, csr, all_per_req, max_req, self.rank * (max_req + 1)
+
+    def _gather_keys(self, keys: torch.Tensor) -> torch.Tensor:
+        n = torch.tensor([keys.numel()], dtype=torch.int64, device=self.device)
+        counts = torch.empty(self.world, dtype=torch.int64, device=self.device)
+        dist.all_gather_into_tensor(counts, n, group=self.group)
+        counts = counts.cpu().tolist()
+        seg = torch.zeros(max(max(counts), 1), dtype=torch.int64, device=self.device)
+        seg[:keys.numel()] = keys
+        out = torch.empty(self.world * seg.numel(), dtype=torch.int64, device=self.device)
+        dist.all_gather_into_tensor(out, seg, group=self.group)
+        return torch.cat([out[r * seg.numel(): r * seg.numel() + c] for r, c in enumerate(counts)])
+
+    # ---- operators ----------------------------------------------------------------------------
+    def upsert(self, keys: torch.Tensor, value_word: int) -> None:
+        """Every rank contributes keys; each key is stored on the shard that owns it."""
+        self.backend.upsert_owned(self._gather_keys(keys.contiguous()), value_word, self.world, self.rank)
+
+    def PrefixMatch(self, keys: torch.Tensor, key_off: torch.Tensor, mask_off: Optional[torch.Tensor] = None
+                    ) -> torch.Tensor:
+        n_req = key_off.numel() - 1
+        all_keys, csr, all_mask, _, first = self._gather_requests(keys.contiguous(), key_off.contiguous(), mask_off)
+        lens = self.backend.prefix_owned(all_keys, csr, all_mask, self.world, self.rank)
+        dist.all_reduce(lens, op=dist.ReduceOp.MIN, group=self.group)
+        return lens[first:first + n_req]
+
+    def ReverseRollSlideWindowMatch(self, keys: torch.Tensor, key_off: torch.Tensor, sw_size: int) -> torch.Tensor:
+        if sw_size <= 0:
+            raise _cabi.KvcmError(_cabi.KVCM_EC_BADARGS, "ReverseRollSlideWindowMatch")
+        n_req = key_off.numel() - 1
+        all_keys, csr, _, _, first = self._gather_requests(keys.contiguous(), key_off.contiguous(), None)
+        flags = self.backend.servable_flags(all_keys)
+        dist.all_reduce(flags, op=dist.ReduceOp.MAX, group=self.group)
+        base = self.backend.sw_from_flags(flags, csr, sw_size)
+        return base[first:first + n_req]

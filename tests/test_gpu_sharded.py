@@ -1,0 +1,121 @@
+"""Hash-range-sharded matching on the GPU.
+
+The shard-local kernels are checked on one GPU by running both shards of a two-way split one after the other and
+combining them with the same min / max the collectives apply.  The full NCCL path runs as two ranks when the box
+has two GPUs."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import kvcm_oracle as oracle
+
+import tair_kvcache_b200  # noqa: F401
+from tair_kvcache_b200 import _cabi
+from tair_kvcache_b200.manager import BlockIndex, CudaShardBackend, ShardedMetaSearcher, encode_locations, shard_of_keys
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _world(seed, n_ranks=2):
+    rng = np.random.default_rng(seed)
+    universe = rng.integers(-(1 << 62), 1 << 62, size=6000, dtype=np.int64)
+    present = universe[rng.random(len(universe)) < 0.7]
+    reqs = []
+    for rank in range(n_ranks):
+        lens = rng.integers(0, 300, size=200 + 50 * rank)
+        keys = [rng.choice(universe, size=n) for n in lens]
+        for k in keys:
+            hit = rng.random(len(k)) < 0.95
+            k[hit] = rng.choice(present, size=int(hit.sum()))
+        off = np.zeros(len(lens) + 1, dtype=np.int64)
+        np.cumsum(lens, out=off[1:])
+        reqs.append((np.concatenate(keys + [np.zeros(0, np.int64)]), off,
+                     rng.integers(0, 6, size=len(lens)).astype(np.int64)))
+    return present, reqs
+
+
+def test_shard_kernels_combine_to_the_unsharded_answer_on_one_gpu():
+    present, reqs = _world(7)
+    keys, off, mask = reqs[0]
+    full = oracle.Index()
+    full.put_uniform(present)
+    word = encode_locations([(3, 4)])
+    dk, doff, dmask = (torch.from_numpy(a).to(DEV) for a in (keys, off, mask))
+    dpresent = torch.from_numpy(present).to(DEV)
+    for count in (2, 3):
+        shards = [CudaShardBackend(len(present), torch.device(DEV)) for _ in range(count)]
+        for r, sh in enumerate(shards):
+            sh.upsert_owned(dpresent, word, count, r)
+        stored = [sh.index.stats()[1] for sh in shards]
+        # the device ownership rule equals the host one
+        assert stored == np.bincount(shard_of_keys(np.unique(present), count), minlength=count).tolist()
+        lens = torch.stack([sh.prefix_owned(dk, doff, None, count, r) for r, sh in enumerate(shards)]).min(0).values
+        assert np.array_equal(lens.cpu().numpy(), full.prefix_match_batch(keys, off))
+        lens = torch.stack([sh.prefix_owned(dk, doff, dmask, count, r) for r, sh in enumerate(shards)]).min(0).values
+        assert np.array_equal(lens.cpu().numpy(), full.prefix_match_batch(keys, off, mask))
+        flags = torch.stack([sh.servable_flags(dk) for sh in shards]).max(0).values
+        assert np.array_equal(flags.cpu().numpy(), full.batch_get(keys))
+        for sw in (1, 4, 40):
+            base = shards[0].sw_from_flags(flags, doff, sw)
+            assert np.array_equal(base.cpu().numpy(), full.sw_match_batch(keys, off, sw))
+
+
+def test_sw_from_flags_equals_match_sw_on_the_same_index():
+    present, reqs = _world(8)
+    keys, off, _ = reqs[1]
+    sh = CudaShardBackend(len(present), torch.device(DEV))
+    sh.upsert_owned(torch.from_numpy(present).to(DEV), encode_locations([(3, 1)]), 1, 0)
+    dk, doff = torch.from_numpy(keys).to(DEV), torch.from_numpy(off).to(DEV)
+    from tair_kvcache_b200.manager import BatchMetaSearcher
+    for sw in (2, 33, 64):
+        a = sh.sw_from_flags(sh.servable_flags(dk), doff, sw)
+        b = BatchMetaSearcher(sh.index).ReverseRollSlideWindowMatch(dk, doff, sw)
+        assert torch.equal(a, b)
+
+
+def _rank_main(rank, port, results):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=2, device_id=dev)
+    try:
+        present, reqs = _world(9)
+        searcher = ShardedMetaSearcher(CudaShardBackend(len(present), dev))
+        searcher.upsert(torch.from_numpy(present[rank::2].copy()).to(dev), encode_locations([(3, 4)]))
+        keys, off, mask = (torch.from_numpy(a).to(dev) for a in reqs[rank])
+        out = {
+            "stored": searcher.backend.index.stats()[1],
+            "prefix": searcher.PrefixMatch(keys, off).cpu().numpy(),
+            "prefix_masked": searcher.PrefixMatch(keys, off, mask).cpu().numpy(),
+            "sw4": searcher.ReverseRollSlideWindowMatch(keys, off, 4).cpu().numpy(),
+        }
+        torch.cuda.synchronize()
+        results[rank] = out
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_nccl_ranks_match_the_unsharded_oracle():
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    with mp.Manager() as m:
+        results = m.dict()
+        mp.spawn(_rank_main, args=(port, results), nprocs=2, join=True)
+        results = dict(results)
+    present, reqs = _world(9)
+    full = oracle.Index()
+    full.put_uniform(present)
+    assert results[0]["stored"] + results[1]["stored"] == len(np.unique(present))
+    for rank in range(2):
+        keys, off, mask = reqs[rank]
+        assert np.array_equal(results[rank]["prefix"], full.prefix_match_batch(keys, off))
+        assert np.array_equal(results[rank]["prefix_masked"], full.prefix_match_batch(keys, off, mask))
+        assert np.array_equal(results[rank]["sw4"], full.sw_match_batch(keys, off, 4))

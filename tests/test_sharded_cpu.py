@@ -1,0 +1,134 @@
+"""The multi-rank logic of the hash-range-sharded matcher on CPU: two gloo ranks, the shard-local work done by
+an oracle-backed stand-in (test only), results compared with the unsharded oracle."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import kvcm_oracle as oracle
+
+import tair_kvcache_b200  # noqa: F401
+from tair_kvcache_b200.manager.sharded_searcher import ShardedMetaSearcher, shard_of_keys
+
+
+class OracleShardBackend:
+    """CPU stand-in for CudaShardBackend, for tests only: same four operations through the oracle."""
+
+    def __init__(self):
+        self.index = oracle.Index()
+        self.device = torch.device("cpu")
+
+    def upsert_owned(self, keys, value_word, shard_count, shard_rank):
+        k = keys.numpy()
+        self.index.put_uniform(k[shard_of_keys(k, shard_count) == shard_rank])
+
+    def prefix_owned(self, keys, key_off, mask_off, shard_count, shard_rank):
+        k, off = keys.numpy(), key_off.numpy()
+        owner = shard_of_keys(k, shard_count)
+        flags = self.index.batch_get(k) & 1
+        ok = (owner != shard_rank) | (flags == 1)
+        out = np.zeros(len(off) - 1, dtype=np.int32)
+        for r in range(len(off) - 1):
+            skip = int(mask_off[r]) if mask_off is not None else 0
+            n = 0
+            for i in range(off[r] + skip, off[r + 1]):
+                if not ok[i]:
+                    break
+                n += 1
+            out[r] = n
+        return torch.from_numpy(out)
+
+    def servable_flags(self, keys):
+        return torch.from_numpy(self.index.batch_get(keys.numpy()))
+
+    def sw_from_flags(self, flags, key_off, sw):
+        f, off = flags.numpy() & 1, key_off.numpy()
+        out = np.full(len(off) - 1, -1, dtype=np.int32)
+        for r in range(len(off) - 1):
+            seg = f[off[r]:off[r + 1]]
+            if len(seg) < sw:
+                out[r] = -2
+                continue
+            for base in range(len(seg) - sw, -1, -1):
+                if seg[base:base + sw].all():
+                    out[r] = base
+                    break
+        return torch.from_numpy(out)
+
+
+def _world(seed):
+    rng = np.random.default_rng(seed)
+    universe = rng.integers(-(1 << 62), 1 << 62, size=600, dtype=np.int64)
+    present = universe[rng.random(600) < 0.7]
+    reqs = {}
+    for rank in range(2):
+        lens = rng.integers(0, 40, size=5 + 3 * rank)
+        keys = [rng.choice(universe, size=n) for n in lens]
+        for k in keys:  # long servable runs so windows exist
+            hit = rng.random(len(k)) < 0.8
+            k[hit] = rng.choice(present, size=int(hit.sum()))
+        off = np.zeros(len(lens) + 1, dtype=np.int64)
+        np.cumsum(lens, out=off[1:])
+        mask = rng.integers(0, 4, size=len(lens)).astype(np.int64)
+        reqs[rank] = (np.concatenate(keys + [np.zeros(0, np.int64)]), off, mask)
+    return present, reqs
+
+
+def _rank_main(rank, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=2)
+    try:
+        present, reqs = _world(123)
+        searcher = ShardedMetaSearcher(OracleShardBackend())
+        # each rank submits half of the index content; ownership decides where a key is stored
+        searcher.upsert(torch.from_numpy(present[rank::2].copy()), 0)
+        keys, off, mask = reqs[rank]
+        tk, to, tm = torch.from_numpy(keys), torch.from_numpy(off), torch.from_numpy(mask)
+        out = {
+            "stored": len(searcher.backend.index),
+            "prefix": searcher.PrefixMatch(tk, to).numpy().copy(),
+            "prefix_masked": searcher.PrefixMatch(tk, to, tm).numpy().copy(),
+            "sw2": searcher.ReverseRollSlideWindowMatch(tk, to, 2).numpy().copy(),
+            "sw5": searcher.ReverseRollSlideWindowMatch(tk, to, 5).numpy().copy(),
+        }
+        results[rank] = out
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_match_the_unsharded_oracle():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    with mp.Manager() as m:
+        results = m.dict()
+        mp.spawn(_rank_main, args=(port, results), nprocs=2, join=True)
+        results = dict(results)
+    present, reqs = _world(123)
+    full = oracle.Index()
+    full.put_uniform(present)
+    assert results[0]["stored"] + results[1]["stored"] == len(np.unique(present))
+    assert results[0]["stored"] > 0 and results[1]["stored"] > 0
+    for rank in range(2):
+        keys, off, mask = reqs[rank]
+        assert np.array_equal(results[rank]["prefix"], full.prefix_match_batch(keys, off))
+        assert np.array_equal(results[rank]["prefix_masked"], full.prefix_match_batch(keys, off, mask))
+        assert np.array_equal(results[rank]["sw2"], full.sw_match_batch(keys, off, 2))
+        assert np.array_equal(results[rank]["sw5"], full.sw_match_batch(keys, off, 5))
+    assert (results[0]["sw2"] >= 0).any() and results[0]["prefix"].max() > 0
+
+
+def test_shard_of_keys_is_a_balanced_partition():
+    rng = np.random.default_rng(0)
+    keys = rng.integers(-(1 << 63), (1 << 63) - 1, size=4000, dtype=np.int64)
+    for count in (1, 2, 8):
+        owner = shard_of_keys(keys, count)
+        assert owner.min() >= 0 and owner.max() < count
+        assert np.bincount(owner, minlength=count).min() > 4000 / count * 0.8
+    # chained block hashes of consecutive blocks spread too
+    chain = oracle.gen_key_vector(np.arange(64 * 800, dtype=np.int64), 64)
+    assert np.bincount(shard_of_keys(chain, 8), minlength=8).min() > 60
