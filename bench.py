@@ -247,11 +247,31 @@ def run_prefix_gpu(device, steps, warmup):
         GenKeyVectorBatch(d_toks, d_off, bs, d_ko, n_keys, out=d_keys)
         searcher.PrefixMatch(d_keys, d_ko, out=d_len)
 
+    # End to end: tokens start in pinned host memory and the lengths end there.  The batch is cut into request
+    # ranges that alternate between two streams, so the token copy of one range overlaps hash + match of the other.
+    n_req = len(off) - 1
+    n_chunks = 8
+    bounds = [int(np.searchsorted(off, off[-1] * c // n_chunks)) for c in range(n_chunks)] + [n_req]
+    bounds = sorted(set(min(max(b, 0), n_req) for b in bounds))
+    streams = [torch.cuda.Stream(device), torch.cuda.Stream(device)]
+
     def e2e():
-        d_toks.copy_(h_toks, non_blocking=True)
+        main = torch.cuda.current_stream(device)
         d_off.copy_(h_off, non_blocking=True)
         d_ko.copy_(h_ko, non_blocking=True)
-        resident()
+        ready = torch.cuda.Event()
+        ready.record(main)
+        for c in range(len(bounds) - 1):
+            r0, r1 = bounds[c], bounds[c + 1]
+            t0, t1 = int(off[r0]), int(off[r1])
+            st = streams[c % 2]
+            st.wait_event(ready)
+            with torch.cuda.stream(st):
+                d_toks[t0:t1].copy_(h_toks[t0:t1], non_blocking=True)
+                GenKeyVectorBatch(d_toks, d_off[r0:r1 + 1], bs, d_ko[r0:r1 + 1], n_keys, out=d_keys)
+                searcher.PrefixMatch(d_keys, d_ko[r0:r1 + 1], out=d_len[r0:r1])
+        for st in streams:
+            main.wait_stream(st)
         h_len.copy_(d_len, non_blocking=True)
 
     out = {}
@@ -373,45 +393,55 @@ def main_b200(args, cfg, rank, world):
     alg_bytes_step = 4 * payload  # gather: read + write payload; scatter: the same
     value = world * alg_bytes_step * args.steps / (elapsed_ms * 1e-3) / 1e9
 
-    # ---- end to end: pinned host staging through the operator API, python index lists included
+    # ---- end to end: pinned host staging through the operator API, python index lists included.
+    # As in the reference connector (kv_cache_manager/py_connector/vllm/data_transfer.py:77-78,138,203) saves run
+    # on one CUDA stream and loads on another, each with its own pool of pinned staging blocks, so the two PCIe
+    # directions work at the same time.  A step = every save task (gather -> host) and every load task
+    # (host -> scatter) once.
     T = ppb * cfg["page_tokens"]
     task_blocks = min(128, w["n_blocks"])  # blocks per save / load task of the reference connector
     n_tasks = min(w["n_blocks"] // task_blocks, 8)
     dim = cfg["token_bytes"] // 2
-    host_staging = torch.empty(1 if args.no_e2e else task_blocks, w["n_pools"], T, dim, dtype=torch.bfloat16,
-                               pin_memory=True)
-    table_np = table.cpu().numpy().reshape(w["n_blocks"], ppb)
-    tok_np = (table_np[:, :, None].astype(np.int64) * cfg["page_tokens"] +
-              np.arange(cfg["page_tokens"])[None, None, :]).reshape(w["n_blocks"], T)
-    task_tok = [tok_np[i * task_blocks:(i + 1) * task_blocks].reshape(-1).tolist() for i in range(n_tasks)]
-    task_slots = list(range(task_blocks))
-
-    def e2e_step():
-        for i in range(n_tasks):
-            batch_gather_kv_caches(ptrs, host_staging, task_tok[i], task_slots, T, dim)
-            batch_scatter_kv_caches(ptrs, host_staging, task_tok[i], task_slots, T, dim)
-
-    e2e_steps = 0 if args.no_e2e else max(1, min(args.steps, 3))
-    if e2e_steps:
-        e2e_step()
-    torch.cuda.synchronize(device)
-    if world > 1:
-        dist.barrier()
-    s2, p2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t_wall = time.perf_counter()
-    s2.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    p2.record()
-    torch.cuda.synchronize(device)
-    e2e_ms = max(s2.elapsed_time(p2), (time.perf_counter() - t_wall) * 1e3)  # host list conversion counts
-    if world > 1:
-        t = torch.tensor([e2e_ms], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = t.item()
     task_payload = task_blocks * w["n_pools"] * T * cfg["token_bytes"]
-    e2e_value = world * 4 * task_payload * n_tasks * e2e_steps / (e2e_ms * 1e-3) / 1e9 if e2e_steps else None
     idx_bytes = n_tasks * 2 * (task_blocks * T + task_blocks) * 4
+    e2e_value, e2e_steps, e2e_parity = None, 0, None
+    if not args.no_e2e:
+        save_pool = torch.empty(task_blocks, w["n_pools"], T, dim, dtype=torch.bfloat16, pin_memory=True)
+        load_pool = torch.empty(n_tasks, task_blocks, w["n_pools"], T, dim, dtype=torch.bfloat16, pin_memory=True)
+        table_np = table.cpu().numpy().reshape(w["n_blocks"], ppb)
+        tok_np = (table_np[:, :, None].astype(np.int64) * cfg["page_tokens"] +
+                  np.arange(cfg["page_tokens"])[None, None, :]).reshape(w["n_blocks"], T)
+        task_tok = [tok_np[i * task_blocks:(i + 1) * task_blocks].reshape(-1).tolist() for i in range(n_tasks)]
+        task_slots = list(range(task_blocks))
+        for i in range(n_tasks):  # what storage would hand back: the blocks as saved
+            batch_gather_kv_caches(ptrs, load_pool[i], task_tok[i], task_slots, T, dim)
+        torch.cuda.synchronize(device)
+        save_stream, load_stream = torch.cuda.Stream(device), torch.cuda.Stream(device)
+
+        def e2e_step():
+            for i in range(n_tasks):
+                with torch.cuda.stream(save_stream):
+                    batch_gather_kv_caches(ptrs, save_pool, task_tok[i], task_slots, T, dim)
+                with torch.cuda.stream(load_stream):
+                    batch_scatter_kv_caches(ptrs, load_pool[i], task_tok[i], task_slots, T, dim)
+
+        e2e_steps = max(1, min(args.steps, 3))
+        e2e_step()
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+        t_wall = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        torch.cuda.synchronize(device)  # both streams drained: every staged byte has crossed PCIe
+        e2e_ms = (time.perf_counter() - t_wall) * 1e3  # wall clock around the calls: host list conversion counts
+        if world > 1:
+            t = torch.tensor([e2e_ms], dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = t.item()
+        e2e_value = world * 4 * task_payload * n_tasks * e2e_steps / (e2e_ms * 1e-3) / 1e9
+        e2e_parity = bool(torch.equal(save_pool, load_pool[n_tasks - 1]))
+        del save_pool, load_pool
 
     if rank != 0:
         if world > 1:
@@ -430,25 +460,25 @@ def main_b200(args, cfg, rank, world):
                          % (payload / 2 ** 30),
                    "parity_sample_ok": parity_ok},
         "clocks": clocks,
-        "roofline": {"bound": "hbm", "kernel": "MoveRowsKernel<gather>", "achieved": gather_gbs, "peak": peak,
+        "roofline": {"bound": "hbm", "kernel": "MoveRowsBulkKernel<gather>", "achieved": gather_gbs, "peak": peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": gather_gbs / peak,
                      "traffic": int(DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE * 2 * payload),
                      "traffic_source": "ncu capture on a reduced case scaled by blocks moved",
                      "algorithmic_bytes_per_launch": 2 * payload, "launch_ms": gather_ms,
-                     "scatter": {"kernel": "MoveRowsKernel<scatter>", "achieved": scatter_gbs,
+                     "scatter": {"kernel": "MoveRowsBulkKernel<scatter>", "achieved": scatter_gbs,
                                  "frac": scatter_gbs / peak, "launch_ms": scatter_ms}},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": task_payload * n_tasks + idx_bytes,
-                "d2h_bytes_per_step": task_payload * n_tasks,
-                "note": "%d save+load tasks of %d blocks, staging in pinned host memory, token-index lists "
-                        "converted per call" % (n_tasks, task_blocks)},
-        "gpu_launches": 2 * args.steps,
+                "d2h_bytes_per_step": task_payload * n_tasks, "parity_ok": e2e_parity,
+                "note": "%d save tasks and %d load tasks of %d blocks per step on two streams, staging in pinned "
+                        "host memory, token-index lists converted per call" % (n_tasks, n_tasks, task_blocks)},
+        "gpu_launches": 2 * args.steps * world,
     }
     if world == 1 and not args.no_cpu:
         threads = os.cpu_count() or 1
         cpu_gbs, _, sample, _ = run_cpu_transfer(cfg, threads, 40, 1, budget_s=8.0)
         line["cpu_baseline"] = {"value": cpu_gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
         if not args.no_prefix:
-            del w, staging, host_staging
+            del w, staging
             torch.cuda.empty_cache()
             pm, data = run_prefix_gpu(device, 20, 3)
             cpu_pm, n_rep = run_prefix_cpu(data, threads)
