@@ -440,7 +440,7 @@ def main_b200(args, cfg, rank, world):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             e2e_ms = t.item()
         e2e_value = world * 4 * task_payload * n_tasks * e2e_steps / (e2e_ms * 1e-3) / 1e9
-        e2e_parity = bool(torch.equal(save_pool, load_pool[n_tasks - 1]))
+        e2e_parity = bool(torch.equal(save_pool.view(torch.int16), load_pool[n_tasks - 1].view(torch.int16)))
         del save_pool, load_pool
 
     if rank != 0:

@@ -93,25 +93,54 @@ KVCM_API int32_t kvcm_b200_device_info(int32_t *sm_count, int64_t *l2_bytes, int
  * d_status, when not NULL, points to four caller-zeroed uint32 words: [0] is incremented once per
  * skipped (pool,row) pair, [1] keeps 1 + the largest offending block number, [2] becomes 1 if a
  * bounded wait inside the kernel ran out (the copy is then incomplete), [3] is reserved.
+ * max_sms bounds the SMs the launch occupies - the role of the reference's `sm_count` argument
+ * (batch_gather_scatter_helper.py:110,115).  0 = the library's choice: every SM when staging is device
+ * memory, 16 when staging is host memory (the PCIe link is then the bound, and the other SMs stay free
+ * for the engine and for a transfer in the opposite direction on another stream).
  * Scattering the same row twice in one call is a data race, as in the reference.
  * Fastest when row_bytes and all base addresses are multiples of 16; any alignment is correct.
  * ---------------------------------------------------------------------------------------- */
 KVCM_API int32_t kvcm_b200_gather_tokens(const void *const *d_pool_ptrs, int32_t n_pools, void *staging,
                                          int64_t n_slots, const int32_t *d_token_idx, const int32_t *d_slot_idx,
                                          int32_t n_blocks, int32_t tokens_per_block, int64_t bytes_per_token,
-                                         int64_t pool_tokens, uint32_t *d_status, kvcm_stream_t stream);
+                                         int64_t pool_tokens, uint32_t *d_status, int32_t max_sms,
+                                         kvcm_stream_t stream);
 KVCM_API int32_t kvcm_b200_scatter_tokens(const void *const *d_pool_ptrs, int32_t n_pools, const void *staging,
                                           int64_t n_slots, const int32_t *d_token_idx, const int32_t *d_slot_idx,
                                           int32_t n_blocks, int32_t tokens_per_block, int64_t bytes_per_token,
-                                          int64_t pool_tokens, uint32_t *d_status, kvcm_stream_t stream);
+                                          int64_t pool_tokens, uint32_t *d_status, int32_t max_sms,
+                                         kvcm_stream_t stream);
 KVCM_API int32_t kvcm_b200_gather_pages(const void *const *d_pool_ptrs, int32_t n_pools, void *staging,
                                         int64_t n_slots, const int32_t *d_page_table, const int32_t *d_slot_idx,
                                         int32_t n_blocks, int32_t pages_per_block, int64_t page_bytes,
-                                        int64_t pool_pages, uint32_t *d_status, kvcm_stream_t stream);
+                                        int64_t pool_pages, uint32_t *d_status, int32_t max_sms,
+                                         kvcm_stream_t stream);
 KVCM_API int32_t kvcm_b200_scatter_pages(const void *const *d_pool_ptrs, int32_t n_pools, const void *staging,
                                          int64_t n_slots, const int32_t *d_page_table, const int32_t *d_slot_idx,
                                          int32_t n_blocks, int32_t pages_per_block, int64_t page_bytes,
-                                         int64_t pool_pages, uint32_t *d_status, kvcm_stream_t stream);
+                                         int64_t pool_pages, uint32_t *d_status, int32_t max_sms,
+                                         kvcm_stream_t stream);
+
+/* Save / load with the staging blocks in HOST memory (pinned), the form the vLLM connector runs in
+ * production (kv_cache_manager/py_connector/vllm/v1_connector.py:431-432,
+ * kv_cache_manager/py_connector/vllm/data_transfer.py:119-150, 205-217).  Same layout rule as gather /
+ * scatter above (a row is a token or a page), but the PCIe leg is done by the copy engines: blocks are
+ * gathered into the caller's device bounce buffer and copied out (save), or copied in and scattered
+ * (load), in groups of floor(bounce_bytes / block_bytes) blocks, all ordered on `stream`.  A save on
+ * one stream and a load on another then use both PCIe directions at full rate, which kernels writing
+ * host memory directly do not.  h_slot_idx is a HOST array of staging slots (NULL = slot b); slots
+ * outside [0, n_slots) return KVCM_ER_INVALID_PARAMS before anything for that group is copied.
+ * d_bounce: device memory, 16-byte aligned, at least one block (n_pools * rows_per_block * row_bytes). */
+KVCM_API int32_t kvcm_b200_save_rows_to_host(const void *const *d_pool_ptrs, int32_t n_pools, void *h_staging,
+                                             int64_t n_slots, const int32_t *d_row_idx, const int32_t *h_slot_idx,
+                                             int32_t n_blocks, int32_t rows_per_block, int64_t row_bytes,
+                                             int64_t pool_rows, void *d_bounce, int64_t bounce_bytes,
+                                             uint32_t *d_status, kvcm_stream_t stream);
+KVCM_API int32_t kvcm_b200_load_rows_from_host(const void *const *d_pool_ptrs, int32_t n_pools,
+                                               const void *h_staging, int64_t n_slots, const int32_t *d_row_idx,
+                                               const int32_t *h_slot_idx, int32_t n_blocks, int32_t rows_per_block,
+                                               int64_t row_bytes, int64_t pool_rows, void *d_bounce,
+                                               int64_t bounce_bytes, uint32_t *d_status, kvcm_stream_t stream);
 
 /* Tuning knob, process-wide: which of the two gather/scatter kernels large aligned rows use.
  * mover 0 = 16-byte vector loads and stores, 1 = shared-memory ring driven by bulk async copies

@@ -47,7 +47,7 @@ class Iov(ctypes.Structure):
 
 
 # name -> argtypes, in the order of include/kvcm_b200.h; every function returns int32 unless noted.
-_MOVE = [_vp, _i32, _vp, _i64, _vp, _vp, _i32, _i32, _i64, _i64, _vp, _vp]
+_MOVE = [_vp, _i32, _vp, _i64, _vp, _vp, _i32, _i32, _i64, _i64, _vp, _i32, _vp]
 _LEGACY = [_vp, _i32, _i64, _vp, _vp, _i32, _i64, _vp]
 _HASH = [_vp, _i64, _vp, _i32, _i32, _vp, _vp, _vp]
 SIGNATURES = {
@@ -59,6 +59,8 @@ SIGNATURES = {
     "kvcm_b200_scatter_tokens": _MOVE,
     "kvcm_b200_gather_pages": _MOVE,
     "kvcm_b200_scatter_pages": _MOVE,
+    "kvcm_b200_save_rows_to_host": [_vp, _i32, _vp, _i64, _vp, _vp, _i32, _i32, _i64, _i64, _vp, _i64, _vp, _vp],
+    "kvcm_b200_load_rows_from_host": [_vp, _i32, _vp, _i64, _vp, _vp, _i32, _i32, _i64, _i64, _vp, _i64, _vp, _vp],
     "kvcm_b200_set_mover": [_i32, _i32],
     "kvcm_b200_set_bulk_geometry": [_i32, _i32, _i32],
     "kvcm_b200_gather_legacy": _LEGACY,

@@ -475,9 +475,26 @@ int ResidentCtas() {
     return cached;
 }
 
+// Number of SMs a launch may occupy.  0 = the library's choice: every SM when staging is device
+// memory (the transfer is HBM-bound), kHostStagingSms when staging is host memory - the transfer
+// is then bound by the PCIe link, a few SMs saturate it, and the rest stay free for the engine's
+// own kernels and for a transfer in the other direction.
+constexpr int kHostStagingSms = 16;
+
+int SmBudget(int32_t max_sms, const void *staging) {
+    const int all = GetDeviceInfo().sm_count;
+    if (max_sms > 0) return max_sms < all ? max_sms : all;
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, staging) == cudaSuccess && attr.type == cudaMemoryTypeHost) {
+        return kHostStagingSms < all ? kHostStagingSms : all;
+    }
+    cudaGetLastError();
+    return all;
+}
+
 template <bool kGather, int kHint>
-void LaunchPlain(const MoveParams &p, cudaStream_t stream) {
-    const int64_t resident = ResidentCtas<kGather, kHint>();
+void LaunchPlain(const MoveParams &p, int sms, cudaStream_t stream) {
+    const int64_t resident = static_cast<int64_t>(ResidentCtas<kGather, kHint>()) / GetDeviceInfo().sm_count * sms;
     const unsigned grid = static_cast<unsigned>(p.total_chunks < resident ? p.total_chunks : resident);
     MoveRowsKernel<kGather, kHint><<<grid, kThreads, 0, stream>>>(p);
 }
@@ -485,14 +502,14 @@ void LaunchPlain(const MoveParams &p, cudaStream_t stream) {
 constexpr int kBulkMaxSmem = 224 * 1024;
 
 template <bool kGather>
-void LaunchBulk(const MoveParams &p, int ctas_per_sm, cudaStream_t stream) {
+void LaunchBulk(const MoveParams &p, int ctas_per_sm, int sms, cudaStream_t stream) {
     static bool attr_set = false;
     if (!attr_set) {
         cudaFuncSetAttribute(MoveRowsBulkKernel<kGather>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkMaxSmem);
         attr_set = true;
     }
     const int smem = p.stages * static_cast<int>(p.chunk_bytes);
-    const int64_t resident = static_cast<int64_t>(GetDeviceInfo().sm_count) * ctas_per_sm;
+    const int64_t resident = static_cast<int64_t>(sms) * ctas_per_sm;
     const unsigned grid = static_cast<unsigned>(p.total_chunks < resident ? p.total_chunks : resident);
     MoveRowsBulkKernel<kGather><<<grid, 32, smem, stream>>>(p);
 }
@@ -500,8 +517,9 @@ void LaunchBulk(const MoveParams &p, int ctas_per_sm, cudaStream_t stream) {
 int32_t LaunchMove(bool gather, const void *const *d_ptrs, int32_t n_ptrs, int32_t sub_per_ptr, int64_t sub_stride,
                    void *staging, int64_t n_slots, const int32_t *d_row_idx, const int32_t *d_slot_idx,
                    int32_t n_blocks, int32_t rows_per_block, int64_t row_bytes, int64_t pool_rows, uint32_t *d_status,
-                   bool report_skips, kvcm_stream_t stream) {
+                   bool report_skips, int32_t max_sms, kvcm_stream_t stream) {
     if (!HaveDevice()) return KVCM_ER_NO_DEVICE;
+    if (max_sms < 0) return KVCM_ER_INVALID_PARAMS;
     if (n_blocks < 0 || n_ptrs <= 0 || rows_per_block <= 0 || row_bytes <= 0 || pool_rows < 0 || n_slots < 0) {
         return KVCM_ER_INVALID_PARAMS;
     }
@@ -543,18 +561,19 @@ int32_t LaunchMove(bool gather, const void *const *d_ptrs, int32_t n_ptrs, int32
     p.stages = geo.stages;
 
     cudaStream_t s = AsStream(stream);
+    const int sms = SmBudget(max_sms, staging);
     if (bulk_ok) {
         if (gather) {
-            LaunchBulk<true>(p, geo.ctas_per_sm, s);
+            LaunchBulk<true>(p, geo.ctas_per_sm, sms, s);
         } else {
-            LaunchBulk<false>(p, geo.ctas_per_sm, s);
+            LaunchBulk<false>(p, geo.ctas_per_sm, sms, s);
         }
     } else if (cfg.hint == 0) {
-        gather ? LaunchPlain<true, 0>(p, s) : LaunchPlain<false, 0>(p, s);
+        gather ? LaunchPlain<true, 0>(p, sms, s) : LaunchPlain<false, 0>(p, sms, s);
     } else if (cfg.hint == 2) {
-        gather ? LaunchPlain<true, 2>(p, s) : LaunchPlain<false, 2>(p, s);
+        gather ? LaunchPlain<true, 2>(p, sms, s) : LaunchPlain<false, 2>(p, sms, s);
     } else {
-        gather ? LaunchPlain<true, 1>(p, s) : LaunchPlain<false, 1>(p, s);
+        gather ? LaunchPlain<true, 1>(p, sms, s) : LaunchPlain<false, 1>(p, sms, s);
     }
     return LaunchStatus();
 }
@@ -592,34 +611,32 @@ int32_t kvcm_b200_set_bulk_geometry(int32_t stages, int32_t ctas_per_sm, int32_t
 int32_t kvcm_b200_gather_tokens(const void *const *d_pool_ptrs, int32_t n_pools, void *staging, int64_t n_slots,
                                 const int32_t *d_token_idx, const int32_t *d_slot_idx, int32_t n_blocks,
                                 int32_t tokens_per_block, int64_t bytes_per_token, int64_t pool_tokens,
-                                uint32_t *d_status, kvcm_stream_t stream) {
+                                uint32_t *d_status, int32_t max_sms, kvcm_stream_t stream) {
     return kvcm::LaunchMove(true, d_pool_ptrs, n_pools, 1, 0, staging, n_slots, d_token_idx, d_slot_idx, n_blocks,
-                            tokens_per_block, bytes_per_token, pool_tokens, d_status, true, stream);
+                            tokens_per_block, bytes_per_token, pool_tokens, d_status, true, max_sms, stream);
 }
 
 int32_t kvcm_b200_scatter_tokens(const void *const *d_pool_ptrs, int32_t n_pools, const void *staging, int64_t n_slots,
                                  const int32_t *d_token_idx, const int32_t *d_slot_idx, int32_t n_blocks,
                                  int32_t tokens_per_block, int64_t bytes_per_token, int64_t pool_tokens,
-                                 uint32_t *d_status, kvcm_stream_t stream) {
+                                 uint32_t *d_status, int32_t max_sms, kvcm_stream_t stream) {
     return kvcm::LaunchMove(false, d_pool_ptrs, n_pools, 1, 0, const_cast<void *>(staging), n_slots, d_token_idx,
                             d_slot_idx, n_blocks, tokens_per_block, bytes_per_token, pool_tokens, d_status, true,
-                            stream);
+                            max_sms, stream);
 }
 
 int32_t kvcm_b200_gather_pages(const void *const *d_pool_ptrs, int32_t n_pools, void *staging, int64_t n_slots,
                                const int32_t *d_page_table, const int32_t *d_slot_idx, int32_t n_blocks,
-                               int32_t pages_per_block, int64_t page_bytes, int64_t pool_pages, uint32_t *d_status,
-                               kvcm_stream_t stream) {
+                               int32_t pages_per_block, int64_t page_bytes, int64_t pool_pages, uint32_t *d_status, int32_t max_sms, kvcm_stream_t stream) {
     return kvcm::LaunchMove(true, d_pool_ptrs, n_pools, 1, 0, staging, n_slots, d_page_table, d_slot_idx, n_blocks,
-                            pages_per_block, page_bytes, pool_pages, d_status, true, stream);
+                            pages_per_block, page_bytes, pool_pages, d_status, true, max_sms, stream);
 }
 
 int32_t kvcm_b200_scatter_pages(const void *const *d_pool_ptrs, int32_t n_pools, const void *staging, int64_t n_slots,
                                 const int32_t *d_page_table, const int32_t *d_slot_idx, int32_t n_blocks,
-                                int32_t pages_per_block, int64_t page_bytes, int64_t pool_pages, uint32_t *d_status,
-                                kvcm_stream_t stream) {
+                                int32_t pages_per_block, int64_t page_bytes, int64_t pool_pages, uint32_t *d_status, int32_t max_sms, kvcm_stream_t stream) {
     return kvcm::LaunchMove(false, d_pool_ptrs, n_pools, 1, 0, const_cast<void *>(staging), n_slots, d_page_table,
-                            d_slot_idx, n_blocks, pages_per_block, page_bytes, pool_pages, d_status, true, stream);
+                            d_slot_idx, n_blocks, pages_per_block, page_bytes, pool_pages, d_status, true, max_sms, stream);
 }
 
 // Legacy form: one block, layer tensors [2, total_tokens, hidden]; the K and V halves of a
@@ -630,7 +647,7 @@ int32_t kvcm_b200_gather_legacy(const void *const *d_layer_ptrs, int32_t n_layer
                                 kvcm_stream_t stream) {
     if (n_tokens == 0) return KVCM_OK;
     return kvcm::LaunchMove(true, d_layer_ptrs, n_layers, 2, total_tokens * hidden_bytes, staging, 1, d_token_idx,
-                            nullptr, 1, n_tokens, hidden_bytes, total_tokens, nullptr, false, stream);
+                            nullptr, 1, n_tokens, hidden_bytes, total_tokens, nullptr, false, 0, stream);
 }
 
 int32_t kvcm_b200_scatter_legacy(const void *const *d_layer_ptrs, int32_t n_layers, int64_t total_tokens,
@@ -639,7 +656,84 @@ int32_t kvcm_b200_scatter_legacy(const void *const *d_layer_ptrs, int32_t n_laye
     if (n_tokens == 0) return KVCM_OK;
     return kvcm::LaunchMove(false, d_layer_ptrs, n_layers, 2, total_tokens * hidden_bytes,
                             const_cast<void *>(staging), 1, d_token_idx, nullptr, 1, n_tokens, hidden_bytes,
-                            total_tokens, nullptr, false, stream);
+                            total_tokens, nullptr, false, 0, stream);
+}
+
+// Save / load with staging in HOST memory, the PCIe leg done by the copy engines.
+//
+// SM-issued loads and stores over PCIe saturate one direction (about 52 GB/s on a Gen5 x16 link)
+// but a save and a load running at once reach only ~35 GB/s each; the DMA engines sustain ~50 GB/s
+// each way at the same time.  So blocks are gathered into a device bounce buffer at HBM speed and
+// leave through cudaMemcpyAsync (save), or arrive through cudaMemcpyAsync and are scattered (load).
+// Blocks are processed in groups that fit the bounce buffer; everything is ordered on `stream`.
+static int32_t MoveRowsThroughBounce(bool save, const void *const *d_pool_ptrs, int32_t n_pools, void *h_staging,
+                                     int64_t n_slots, const int32_t *d_row_idx, const int32_t *h_slot_idx,
+                                     int32_t n_blocks, int32_t rows_per_block, int64_t row_bytes, int64_t pool_rows,
+                                     void *d_bounce, int64_t bounce_bytes, uint32_t *d_status, kvcm_stream_t stream) {
+    if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
+    if (n_blocks < 0 || n_pools <= 0 || rows_per_block <= 0 || row_bytes <= 0 || n_slots < 0) {
+        return KVCM_ER_INVALID_PARAMS;
+    }
+    if (n_blocks == 0) return KVCM_OK;
+    if (h_staging == nullptr || d_bounce == nullptr || d_row_idx == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    const int64_t block_bytes = static_cast<int64_t>(n_pools) * rows_per_block * row_bytes;
+    const int64_t group = bounce_bytes / block_bytes;
+    if (group < 1) return KVCM_ER_INVALID_PARAMS;
+    cudaStream_t s = kvcm::AsStream(stream);
+    uint8_t *host = static_cast<uint8_t *>(h_staging);
+    uint8_t *bounce = static_cast<uint8_t *>(d_bounce);
+    for (int64_t first = 0; first < n_blocks; first += group) {
+        const int32_t n = static_cast<int32_t>(first + group <= n_blocks ? group : n_blocks - first);
+        const int32_t *rows = d_row_idx + first * rows_per_block;
+        if (save) {
+            const int32_t rc = kvcm::LaunchMove(true, d_pool_ptrs, n_pools, 1, 0, bounce, n, rows, nullptr, n,
+                                                rows_per_block, row_bytes, pool_rows, d_status, true, 0, stream);
+            if (rc != KVCM_OK) return rc;
+        }
+        // One copy per run of blocks whose host slots are consecutive.
+        for (int32_t i = 0; i < n;) {
+            const int64_t slot = h_slot_idx != nullptr ? h_slot_idx[first + i] : first + i;
+            if (slot < 0 || slot >= n_slots) return KVCM_ER_INVALID_PARAMS;
+            int32_t j = i + 1;
+            while (j < n && (h_slot_idx != nullptr ? h_slot_idx[first + j] : first + j) == slot + (j - i)) ++j;
+            if (slot + (j - i) > n_slots) return KVCM_ER_INVALID_PARAMS;
+            const size_t bytes = static_cast<size_t>(j - i) * block_bytes;
+            const cudaError_t e =
+                save ? cudaMemcpyAsync(host + slot * block_bytes, bounce + i * block_bytes, bytes,
+                                       cudaMemcpyDeviceToHost, s)
+                     : cudaMemcpyAsync(bounce + i * block_bytes, host + slot * block_bytes, bytes,
+                                       cudaMemcpyHostToDevice, s);
+            if (e != cudaSuccess) {
+                cudaGetLastError();
+                return KVCM_ER_CUDAMEMCPY_ERROR;
+            }
+            i = j;
+        }
+        if (!save) {
+            const int32_t rc = kvcm::LaunchMove(false, d_pool_ptrs, n_pools, 1, 0, bounce, n, rows, nullptr, n,
+                                                rows_per_block, row_bytes, pool_rows, d_status, true, 0, stream);
+            if (rc != KVCM_OK) return rc;
+        }
+    }
+    return KVCM_OK;
+}
+
+int32_t kvcm_b200_save_rows_to_host(const void *const *d_pool_ptrs, int32_t n_pools, void *h_staging, int64_t n_slots,
+                                    const int32_t *d_row_idx, const int32_t *h_slot_idx, int32_t n_blocks,
+                                    int32_t rows_per_block, int64_t row_bytes, int64_t pool_rows, void *d_bounce,
+                                    int64_t bounce_bytes, uint32_t *d_status, kvcm_stream_t stream) {
+    return MoveRowsThroughBounce(true, d_pool_ptrs, n_pools, h_staging, n_slots, d_row_idx, h_slot_idx, n_blocks,
+                                 rows_per_block, row_bytes, pool_rows, d_bounce, bounce_bytes, d_status, stream);
+}
+
+int32_t kvcm_b200_load_rows_from_host(const void *const *d_pool_ptrs, int32_t n_pools, const void *h_staging,
+                                      int64_t n_slots, const int32_t *d_row_idx, const int32_t *h_slot_idx,
+                                      int32_t n_blocks, int32_t rows_per_block, int64_t row_bytes, int64_t pool_rows,
+                                      void *d_bounce, int64_t bounce_bytes, uint32_t *d_status,
+                                      kvcm_stream_t stream) {
+    return MoveRowsThroughBounce(false, d_pool_ptrs, n_pools, const_cast<void *>(h_staging), n_slots, d_row_idx,
+                                 h_slot_idx, n_blocks, rows_per_block, row_bytes, pool_rows, d_bounce, bounce_bytes,
+                                 d_status, stream);
 }
 
 }  // extern "C"

@@ -45,7 +45,7 @@ def _np(ts):
     return [t.numpy() for t in ts]
 
 
-@pytest.mark.parametrize("staging_on", ["pinned_host", "device"])
+@pytest.mark.parametrize("staging_on", ["pinned_host", "pinned_host_zero_copy", "device"])
 def test_gather_reference_shapes(staging_on):
     torch.manual_seed(42)
     n_layers, total_tokens, T, hidden, n_blocks, n_slots = 4, 10240, 16, 1024, 128, 1024
@@ -53,11 +53,13 @@ def test_gather_reference_shapes(staging_on):
     host, dev, ptrs = _make(42, P, total_tokens, row_bytes)
     tok = torch.cat([torch.randperm(total_tokens)[:T] for _ in range(n_blocks)]).tolist()
     slots = torch.randperm(n_slots)[:n_blocks].tolist()
-    if staging_on == "pinned_host":
+    if staging_on.startswith("pinned_host"):
         dst = torch.zeros(n_slots, P, T, hidden, dtype=torch.bfloat16, pin_memory=True)
     else:
         dst = torch.zeros(n_slots, P, T, hidden, dtype=torch.bfloat16, device=DEV)
-    batch_gather_kv_caches(ptrs, dst, tok, slots, T, hidden)
+    # pinned host staging goes through a device bounce buffer and the copy engines unless an SM budget is given,
+    # in which case the kernel writes host memory itself (the reference's mode of operation)
+    batch_gather_kv_caches(ptrs, dst, tok, slots, T, hidden, sm_count=8 if staging_on.endswith("zero_copy") else None)
     torch.cuda.synchronize()
     want = np.zeros(n_slots * P * T * row_bytes, dtype=np.uint8)
     assert oracle.move_rows(_np(host), want, tok, slots, T, row_bytes, 0, threads=4) == 0
@@ -65,7 +67,7 @@ def test_gather_reference_shapes(staging_on):
     assert np.array_equal(got, want)
 
 
-@pytest.mark.parametrize("staging_on", ["pinned_host", "device"])
+@pytest.mark.parametrize("staging_on", ["pinned_host", "pinned_host_zero_copy", "device"])
 def test_scatter_reference_shapes(staging_on):
     torch.manual_seed(42)
     n_layers, total_tokens, T, hidden, n_blocks, n_slots = 4, 10240, 16, 1024, 128, 1024
@@ -76,8 +78,8 @@ def test_scatter_reference_shapes(staging_on):
     gen = torch.Generator().manual_seed(7)
     src_bytes = _rand_bytes(gen, n_slots * P * T * row_bytes)
     src = src_bytes.view(torch.bfloat16).view(n_slots, P, T, hidden)
-    src = src.pin_memory() if staging_on == "pinned_host" else src.to(DEV)
-    batch_scatter_kv_caches(ptrs, src, tok, slots, T, hidden)
+    src = src.pin_memory() if staging_on.startswith("pinned_host") else src.to(DEV)
+    batch_scatter_kv_caches(ptrs, src, tok, slots, T, hidden, sm_count=8 if staging_on.endswith("zero_copy") else None)
     torch.cuda.synchronize()
     want = [h.numpy().copy() for h in host]
     oracle.move_rows(want, src_bytes.numpy(), tok, slots, T, row_bytes, 1, threads=4)
@@ -160,6 +162,35 @@ def test_out_of_range_rows_and_slots_are_skipped_and_counted():
     assert status[0].item() == skipped == 2 * n_pools + T * n_pools
     assert status[1].item() == 3  # 1 + largest offending block
     assert status[2].item() == 0  # no wait ran out
+
+
+def test_host_staging_in_groups_smaller_than_the_batch(monkeypatch):
+    """The bounce buffer holds fewer blocks than the call moves: several gather + copy rounds, ragged last group,
+    consecutive and scattered host slots."""
+    from tair_kvcache_b200.kernel import batch_gather_scatter_helper as helper
+    n_pools, pool_pages, page_bytes, ppb, n_blocks, n_slots = 3, 300, 4096, 2, 37, 64
+    monkeypatch.setattr(helper, "_BOUNCE_BYTES", 5 * n_pools * ppb * page_bytes)
+    host, dev, ptrs = _make(21, n_pools, pool_pages, page_bytes)
+    rng = np.random.default_rng(21)
+    table = rng.permutation(pool_pages)[:n_blocks * ppb].astype(np.int32)
+    slots = np.concatenate([np.arange(10, 30), rng.permutation(np.r_[0:10, 30:64])[:17]]).astype(np.int32)
+    staging = torch.zeros(n_slots * n_pools * ppb * page_bytes, dtype=torch.uint8, pin_memory=True)
+    batch_gather_kv_pages(ptrs, staging, torch.from_numpy(table), slots.tolist(), ppb, page_bytes, pool_pages)
+    torch.cuda.synchronize()
+    want = np.zeros(staging.numel(), dtype=np.uint8)
+    oracle.move_rows(_np(host), want, table, slots, ppb, page_bytes, 0)
+    assert np.array_equal(staging.numpy(), want)
+    zero = [torch.zeros_like(d) for d in dev]
+    zptrs = torch.tensor([z.data_ptr() for z in zero], dtype=torch.int64, device=DEV)
+    batch_scatter_kv_pages(zptrs, staging, torch.from_numpy(table), torch.from_numpy(slots), ppb, page_bytes,
+                           pool_pages)
+    torch.cuda.synchronize()
+    wantp = [np.zeros_like(h.numpy()) for h in host]
+    oracle.move_rows(wantp, want, table, slots, ppb, page_bytes, 1)
+    for p in range(n_pools):
+        assert np.array_equal(zero[p].cpu().numpy(), wantp[p])
+    with pytest.raises(_cabi.KvcmError):  # a slot outside the staging tensor is refused on the host
+        batch_gather_kv_pages(ptrs, staging, torch.from_numpy(table[:ppb]), [n_slots], ppb, page_bytes, pool_pages)
 
 
 def test_page_table_form_equals_token_form():
@@ -279,7 +310,7 @@ def test_bad_arguments_return_codes():
     _cabi.bind_device(0)
     t = torch.zeros(64, dtype=torch.uint8, device=DEV)
     p = t.data_ptr()
-    assert L.kvcm_b200_gather_tokens(p, 0, p, 1, p, None, 1, 1, 16, 1, None, None) == _cabi.KVCM_ER_INVALID_PARAMS
-    assert L.kvcm_b200_gather_tokens(p, 1, p, 1, p, None, 1, 1, 0, 1, None, None) == _cabi.KVCM_ER_INVALID_PARAMS
-    assert L.kvcm_b200_gather_tokens(None, 1, p, 1, p, None, 1, 1, 16, 1, None, None) == _cabi.KVCM_ER_INVALID_ADDRESS
-    assert L.kvcm_b200_gather_tokens(p, 1, p, 1, p, None, 1, 2, 1 << 30, 1, None, None) == _cabi.KVCM_ER_INVALID_PARAMS
+    assert L.kvcm_b200_gather_tokens(p, 0, p, 1, p, None, 1, 1, 16, 1, None, 0, None) == _cabi.KVCM_ER_INVALID_PARAMS
+    assert L.kvcm_b200_gather_tokens(p, 1, p, 1, p, None, 1, 1, 0, 1, None, 0, None) == _cabi.KVCM_ER_INVALID_PARAMS
+    assert L.kvcm_b200_gather_tokens(None, 1, p, 1, p, None, 1, 1, 16, 1, None, 0, None) == _cabi.KVCM_ER_INVALID_ADDRESS
+    assert L.kvcm_b200_gather_tokens(p, 1, p, 1, p, None, 1, 2, 1 << 30, 1, None, 0, None) == _cabi.KVCM_ER_INVALID_PARAMS
