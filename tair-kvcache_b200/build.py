@@ -51,6 +51,23 @@ def build_library(force=False, verbose=False):
     return LIB
 
 
+HOST_TEST_SRC = os.path.join(ROOT, "tests", "cpp", "host_adapter_test.cc")
+HOST_TEST_BIN = os.path.join(ROOT, "tests", "cpp", "host_adapter_test.bin")
+
+
+def build_host_adapter_test():
+    """Compile the C++ test of the host adapters against the built library (host code only; nvcc is used as the
+    compiler driver so that the CUDA runtime headers and library are found)."""
+    cmd = [nvcc(), "-O2", "-std=c++17", "-I", os.path.join(ROOT, "include"), "-I", os.path.join(HERE, "host"),
+           "-o", HOST_TEST_BIN, HOST_TEST_SRC, "-L", HERE, "-lkvcm_b200", "-Xlinker", "-rpath=" + HERE]
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if proc.returncode != 0:
+        print(proc.stdout)
+        raise RuntimeError("building the host adapter test failed (exit %d)" % proc.returncode)
+    return HOST_TEST_BIN
+
+
 if __name__ == "__main__":
     import sys
     print(build_library(force=True, verbose="-v" in sys.argv))
+    print(build_host_adapter_test())

@@ -19,11 +19,13 @@
 namespace kvcm {
 namespace {
 
-constexpr int kStages = 8;
+constexpr int kStages = 8;  // power of two
 constexpr int kStageBytes = 64;                         // per lane
 constexpr int kPieces = kStageBytes / 16;               // cp.async pieces per lane per stage
 constexpr int kWarpRingBytes = kStages * kPieces * 32 * 16;  // 16 KiB
 constexpr int kMaxWarpsPerCta = 4;
+// Batches of up to 16 x SMs x this many requests run with half-filled warps (tuning experiments set it).
+int g_half_warp_sm_multiple = 2;
 
 __device__ __forceinline__ void CpAsync16(uint32_t smem_addr, uint64_t gmem_addr, uint32_t src_bytes) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr), "l"(gmem_addr), "r"(src_bytes)
@@ -35,29 +37,55 @@ __device__ __forceinline__ void CpAsyncWait() {
     asm volatile("cp.async.wait_group %0;\n" ::"n"(kPending) : "memory");
 }
 
-template <typename T>
-__device__ __forceinline__ uint64_t Widen(T v);
-template <>
-__device__ __forceinline__ uint64_t Widen<uint32_t>(uint32_t v) {
-    return static_cast<uint64_t>(v);
-}
-template <>
-__device__ __forceinline__ uint64_t Widen<int64_t>(int64_t v) {
-    return static_cast<uint64_t>(v);
+// What bounds this kernel is the latency of ONE lane's dependent chain (the longest request), and
+// for a lone warp on an SM the integer pipe takes two cycles per warp instruction.  So the loop is
+// shaped to spend as few instructions per token as possible next to the chain itself:
+//  * a stage (64 bytes per lane) is unpacked into registers, as `token + C`, one stage ahead of
+//    the chain (ping-pong register buffers): shared-memory latency never sits on the chain;
+//  * a stage that lies wholly inside the request runs as one unrolled run of steps.  When
+//    block_size is a multiple of the tokens per stage, a block can only end at the positions
+//    {last, 0 .. tokens-per-16-bytes - 2} of a stage (the request's misalignment against the
+//    16-byte copy grid is a per-lane constant), so only those few positions carry a predicated
+//    key store; other block sizes check every position;
+//  * only the first and last stage of a request, and blocks shorter than a stage, take the
+//    per-token checked path; staging copies of inner stages are four unconditional cp.async.
+// With few requests (lanes_per_warp = 16) only half of each warp is used, so that twice as many
+// SMs work on the batch and the longest chains do not share a warp's issue slots more than needed.
+template <typename T, bool kAligned>
+__device__ __forceinline__ void RunFullStage(uint64_t &h, const uint64_t (&vc)[kStageBytes / sizeof(T)], int32_t &left,
+                                             int64_t *&out, int32_t block_size) {
+    constexpr int kPerPiece = 16 / sizeof(T);
+    constexpr int kPerStage = kStageBytes / sizeof(T);
+    uint32_t hl = static_cast<uint32_t>(h), hh = static_cast<uint32_t>(h >> 32);
+#pragma unroll
+    for (int i = 0; i < kPerStage; ++i) {
+        HashStep32(hl, hh, static_cast<uint32_t>(vc[i]), static_cast<uint32_t>(vc[i] >> 32));
+        if (!kAligned || i == kPerStage - 1 || i < kPerPiece - 1) {
+            if (i + 1 == left) *out = static_cast<int64_t>(static_cast<uint64_t>(hl) | (static_cast<uint64_t>(hh) << 32));
+        }
+    }
+    h = static_cast<uint64_t>(hl) | (static_cast<uint64_t>(hh) << 32);
+    if (left <= kPerStage) {
+        ++out;
+        left += block_size;
+    }
+    left -= kPerStage;
 }
 
-template <typename T>
+template <typename T, bool kAligned>
 __global__ void __launch_bounds__(kMaxWarpsPerCta * 32)
     HashBlocksKernel(const T *__restrict__ tokens, int64_t n_tokens_total, const int64_t *__restrict__ tok_off,
                      int32_t n_req, int32_t block_size, int64_t *__restrict__ keys,
-                     const int64_t *__restrict__ key_off) {
+                     const int64_t *__restrict__ key_off, uint32_t lanes_per_warp) {
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr int kPerPiece = 16 / sizeof(T);
+    constexpr int kPerStage = kStageBytes / sizeof(T);
+    constexpr uint64_t kGolden = 0x9e3779b97f4a7c15ull;
     const uint32_t lane = LaneId();
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t warps_per_cta = blockDim.x >> 5;
-    const int64_t req = (static_cast<int64_t>(blockIdx.x) * warps_per_cta + warp) * 32 + lane;
-    const bool active = req < n_req;
+    const int64_t req = (static_cast<int64_t>(blockIdx.x) * warps_per_cta + warp) * lanes_per_warp + lane;
+    const bool active = lane < lanes_per_warp && req < n_req;
 
     int64_t first_tok = 0, n_tok = 0, key_base = 0;
     if (active) {
@@ -72,7 +100,15 @@ __global__ void __launch_bounds__(kMaxWarpsPerCta * 32)
     const uint64_t beg = arr_beg + static_cast<uint64_t>(first_tok) * sizeof(T);
     const uint64_t end = beg + static_cast<uint64_t>(used) * sizeof(T);
     const uint64_t a0 = beg & ~15ull;  // arr_beg is 16-byte aligned, so a0 >= arr_beg
-    const int64_t n_stages = used > 0 ? static_cast<int64_t>((end - a0 + kStageBytes - 1) / kStageBytes) : 0;
+    const uint64_t span = used > 0 ? end - a0 : 0;
+    const int64_t n_stages = static_cast<int64_t>((span + kStageBytes - 1) / kStageBytes);
+    const int64_t n_pieces = static_cast<int64_t>((span + 15) / 16);
+    // The last piece may hang over the end of the token array: copy only what exists.
+    const uint64_t last_piece = a0 + static_cast<uint64_t>(n_pieces > 0 ? n_pieces - 1 : 0) * 16;
+    const uint32_t last_piece_bytes = arr_end - last_piece >= 16 ? 16u : static_cast<uint32_t>(arr_end - last_piece);
+    const int head_skip = static_cast<int>((beg - a0) / sizeof(T));  // tokens of stage 0 before the request
+    const int tail_count =                                           // valid tokens of the last stage
+        static_cast<int>((span - static_cast<uint64_t>(n_stages > 0 ? n_stages - 1 : 0) * kStageBytes) / sizeof(T));
     int64_t max_stages = n_stages;
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) {
@@ -82,62 +118,85 @@ __global__ void __launch_bounds__(kMaxWarpsPerCta * 32)
 
     const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(smem)) + warp * kWarpRingBytes + lane * 16;
     auto issue = [&](int64_t s) {
-        if (s < n_stages) {
-            const uint32_t slot = static_cast<uint32_t>(s % kStages);
+        const uint32_t dst = ring + (static_cast<uint32_t>(s) & (kStages - 1)) * (kPieces * 512);
+        const uint64_t src = a0 + static_cast<uint64_t>(s) * kStageBytes;
+        if (s + 1 < n_stages) {  // an inner stage: four whole pieces
+#pragma unroll
+            for (int c = 0; c < kPieces; ++c) CpAsync16(dst + c * 512, src + c * 16, 16u);
+        } else if (s < n_stages) {  // the last stage: some pieces may be absent, the last one short
+            const int64_t p0 = s * kPieces;
 #pragma unroll
             for (int c = 0; c < kPieces; ++c) {
-                const uint64_t a = a0 + static_cast<uint64_t>(s) * kStageBytes + c * 16;
-                if (a < end) {
-                    const uint64_t left = arr_end - a;
-                    CpAsync16(ring + (slot * kPieces + c) * 512, a, left >= 16 ? 16u : static_cast<uint32_t>(left));
+                if (p0 + c < n_pieces) {
+                    CpAsync16(dst + c * 512, src + c * 16, p0 + c == n_pieces - 1 ? last_piece_bytes : 16u);
                 }
             }
         }
         CpAsyncCommit();
     };
 
+    // Unpacks one stage from the ring into `token + golden` values (garbage beyond the request:
+    // the caller never consumes those).
+    auto unpack = [&](int64_t s, uint64_t (&vc)[kPerStage]) {
+        const uint32_t src = ring + (static_cast<uint32_t>(s) & (kStages - 1)) * (kPieces * 512);
 #pragma unroll
-    for (int s = 0; s < kStages - 1; ++s) issue(s);
+        for (int c = 0; c < kPieces; ++c) {
+            uint4 q;
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                         : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+                         : "r"(src + c * 512));
+            if constexpr (sizeof(T) == 4) {
+                vc[c * kPerPiece + 0] = static_cast<uint64_t>(q.x) + kGolden;
+                vc[c * kPerPiece + 1] = static_cast<uint64_t>(q.y) + kGolden;
+                vc[c * kPerPiece + 2] = static_cast<uint64_t>(q.z) + kGolden;
+                vc[c * kPerPiece + 3] = static_cast<uint64_t>(q.w) + kGolden;
+            } else {
+                vc[c * kPerPiece + 0] = (static_cast<uint64_t>(q.x) | (static_cast<uint64_t>(q.y) << 32)) + kGolden;
+                vc[c * kPerPiece + 1] = (static_cast<uint64_t>(q.z) | (static_cast<uint64_t>(q.w) << 32)) + kGolden;
+            }
+        }
+    };
 
     uint64_t h = 0;
-    int32_t left_in_block = block_size;
+    int32_t left = block_size;  // tokens still to come in the current block, this one included
     int64_t *out = keys + key_base;
-    for (int64_t k = 0; k < max_stages; ++k) {
-        issue(k + kStages - 1);
-        CpAsyncWait<kStages - 1>();  // stage k has landed; a lane only reads what it copied itself
-        if (k < n_stages) {
-            const uint32_t slot = static_cast<uint32_t>(k % kStages);
-            const uint64_t stage_lo = a0 + static_cast<uint64_t>(k) * kStageBytes;
-            const bool full = stage_lo >= beg && stage_lo + kStageBytes <= end;
+    // Runs the chain over stage k, held in `vc`.
+    auto consume = [&](int64_t k, const uint64_t (&vc)[kPerStage]) {
+        if (k >= n_stages) return;
+        const int lo = k == 0 ? head_skip : 0;
+        const int hi = k == n_stages - 1 ? tail_count : kPerStage;
+        if (lo == 0 && hi == kPerStage && block_size >= kPerStage) {
+            RunFullStage<T, kAligned>(h, vc, left, out, block_size);
+        } else {
 #pragma unroll
-            for (int c = 0; c < kPieces; ++c) {
-                uint4 q;
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                             : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
-                             : "r"(ring + (slot * kPieces + c) * 512));
-                T tok[kPerPiece];
-                if constexpr (sizeof(T) == 4) {
-                    tok[0] = static_cast<T>(q.x);
-                    tok[1] = static_cast<T>(q.y);
-                    tok[2] = static_cast<T>(q.z);
-                    tok[3] = static_cast<T>(q.w);
-                } else {
-                    tok[0] = static_cast<T>(static_cast<uint64_t>(q.x) | (static_cast<uint64_t>(q.y) << 32));
-                    tok[1] = static_cast<T>(static_cast<uint64_t>(q.z) | (static_cast<uint64_t>(q.w) << 32));
-                }
-#pragma unroll
-                for (int i = 0; i < kPerPiece; ++i) {
-                    const uint64_t pos = stage_lo + c * 16 + i * sizeof(T);
-                    if (full || (pos >= beg && pos < end)) {
-                        h = HashStep(h, Widen<T>(tok[i]));
-                        if (--left_in_block == 0) {
-                            *out++ = static_cast<int64_t>(h);
-                            left_in_block = block_size;
-                        }
+            for (int i = 0; i < kPerStage; ++i) {
+                if (i >= lo && i < hi) {
+                    h = HashStepPre(h, vc[i]);
+                    if (--left == 0) {
+                        *out++ = static_cast<int64_t>(h);
+                        left = block_size;
                     }
                 }
             }
         }
+    };
+
+#pragma unroll
+    for (int s = 0; s < kStages - 1; ++s) issue(s);
+    CpAsyncWait<kStages - 2>();  // stage 0 has landed
+    uint64_t even[kPerStage], odd[kPerStage];
+    unpack(0, even);
+    // Stage k+1 is fetched from shared memory while the chain runs over stage k, which is already
+    // in registers.  Two stages per trip so that the two register buffers swap roles without copies.
+    for (int64_t k = 0; k < max_stages; k += 2) {
+        issue(k + kStages - 1);
+        CpAsyncWait<kStages - 2>();  // stage k+1 has landed; a lane only reads what it copied itself
+        unpack(k + 1, odd);
+        consume(k, even);
+        issue(k + kStages);
+        CpAsyncWait<kStages - 2>();  // stage k+2
+        unpack(k + 2, even);
+        consume(k + 1, odd);
     }
     CpAsyncWait<0>();
 }
@@ -157,18 +216,29 @@ int32_t LaunchHash(const T *d_tokens, int64_t n_tokens_total, const int64_t *d_t
 
     static bool attr_set = false;
     if (!attr_set) {
-        cudaFuncSetAttribute(HashBlocksKernel<uint32_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kMaxWarpsPerCta * kWarpRingBytes);
-        cudaFuncSetAttribute(HashBlocksKernel<int64_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kMaxWarpsPerCta * kWarpRingBytes);
+        const int bytes = kMaxWarpsPerCta * kWarpRingBytes;
+        cudaFuncSetAttribute(HashBlocksKernel<uint32_t, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        cudaFuncSetAttribute(HashBlocksKernel<uint32_t, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        cudaFuncSetAttribute(HashBlocksKernel<int64_t, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        cudaFuncSetAttribute(HashBlocksKernel<int64_t, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
         attr_set = true;
     }
-    // Few requests: one warp per CTA so the chains spread over as many SMs as possible.
-    const int64_t n_warps = (static_cast<int64_t>(n_req) + 31) / 32;
-    const int warps_per_cta = n_warps <= 2ll * GetDeviceInfo().sm_count ? 1 : kMaxWarpsPerCta;
+    // Few requests: half-filled warps, one per CTA, so the chains spread over as many SMs as possible.
+    const int sms = GetDeviceInfo().sm_count;
+    const uint32_t lanes_per_warp = static_cast<int64_t>(n_req) <= 16ll * sms * g_half_warp_sm_multiple ? 16u : 32u;
+    const int64_t n_warps = (static_cast<int64_t>(n_req) + lanes_per_warp - 1) / lanes_per_warp;
+    const int warps_per_cta = n_warps <= 2ll * sms ? 1 : kMaxWarpsPerCta;
     const unsigned grid = static_cast<unsigned>((n_warps + warps_per_cta - 1) / warps_per_cta);
-    HashBlocksKernel<T><<<grid, warps_per_cta * 32, warps_per_cta * kWarpRingBytes, AsStream(stream)>>>(
-        d_tokens, n_tokens_total, d_tok_off, n_req, block_size, d_keys, d_key_off);
+    const unsigned threads = warps_per_cta * 32;
+    const size_t smem = static_cast<size_t>(warps_per_cta) * kWarpRingBytes;
+    constexpr int kPerStage = kStageBytes / sizeof(T);
+    if (block_size % kPerStage == 0) {
+        HashBlocksKernel<T, true><<<grid, threads, smem, AsStream(stream)>>>(
+            d_tokens, n_tokens_total, d_tok_off, n_req, block_size, d_keys, d_key_off, lanes_per_warp);
+    } else {
+        HashBlocksKernel<T, false><<<grid, threads, smem, AsStream(stream)>>>(
+            d_tokens, n_tokens_total, d_tok_off, n_req, block_size, d_keys, d_key_off, lanes_per_warp);
+    }
     return LaunchStatus();
 }
 

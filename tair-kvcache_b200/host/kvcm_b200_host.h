@@ -1,0 +1,404 @@
+// C++ host adapters over the C ABI of libkvcm_b200.so, with the shapes of the reference's own
+// operators so that C++ callers (CacheManager, MetaSearcher, the Optimizer, TransferClient SDKs)
+// can switch without touching CUDA:
+//
+//   GenKeyVector / GenKeyVectorBatch / ApplyPrefixHash
+//       kv_cache_manager/manager/cache_manager.cc:76-87, kv_cache_manager/optimizer/trace_converter/trace_util.cc:47-56
+//   GpuBlockIndex        the device replica of MetaIndexer's table (kv_cache_manager/meta/meta_indexer.cc:419-440)
+//   GpuMetaSearcher      PrefixMatch / ReverseRollSlideWindowMatch / BatchGet
+//       kv_cache_manager/manager/meta_searcher.cc:74-265, batch-of-one and batched forms
+//   IovCopier            the per-Iov loops of kv_cache_manager/client/src/internal/sdk/local_file_sdk.cc:223-245,326-353
+//
+// Header-only, C++17, needs only <cuda_runtime.h> and kvcm_b200.h.  Every call stages its
+// arguments through pinned host buffers owned by the adapter, runs on the adapter's stream and
+// synchronises before returning (the reference operators are synchronous too).  Return values are
+// the C ABI's codes: 0 = ok, transfer side = ClientErrorCode numbers, manager side = 1000 + ErrorCode.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstring>
+#include <variant>
+#include <vector>
+
+#include "kvcm_b200.h"
+
+namespace kvcm_b200 {
+
+using KeyVector = std::vector<int64_t>;       // kv_cache_manager/manager/cache_manager.h:53-56
+using TokenIdsVector = std::vector<int64_t>;
+using BlockMaskVector = std::vector<bool>;    // kv_cache_manager/manager/cache_location.h:52-57
+using BlockMaskOffset = size_t;
+using BlockMask = std::variant<BlockMaskVector, BlockMaskOffset>;
+
+// kv_cache_manager/manager/cache_location.h:44-50
+enum CacheLocationStatus : int32_t { CLS_NOT_FOUND = 0, CLS_NEW = 1, CLS_WRITING = 2, CLS_SERVING = 3, CLS_DELETING = 4 };
+
+struct LocationSummary {
+    CacheLocationStatus status;
+    int32_t storage_class;  // DataStorageType, or a per-storage id under a named policy; clamped to [0, 15]
+};
+
+// Value word of a key from its location map (the facts SelectForMatch / ExistsForWrite read,
+// kv_cache_manager/manager/select_location_policy.cc:8-38).
+inline uint64_t EncodeLocations(const std::vector<LocationSummary> &locations) {
+    uint64_t word = 0;
+    for (const LocationSummary &l : locations) {
+        const int c = l.storage_class < 0 ? 0 : (l.storage_class > 15 ? 15 : l.storage_class);
+        word |= KVCM_VAL_NONEMPTY;
+        if (l.status == CLS_SERVING) word |= KVCM_VAL_SERVING(c);
+        if (l.status != CLS_NOT_FOUND) word |= KVCM_VAL_WRITABLE(c);
+    }
+    return word;
+}
+
+namespace detail {
+
+// Grow-only pair of a pinned host buffer and a device buffer of the same size.
+class Mirror {
+public:
+    Mirror() = default;
+    Mirror(const Mirror &) = delete;
+    Mirror &operator=(const Mirror &) = delete;
+    ~Mirror() { Release(); }
+    bool Reserve(size_t bytes) {
+        if (bytes <= capacity_) return true;
+        Release();
+        size_t cap = 4096;
+        while (cap < bytes) cap <<= 1;
+        if (cudaMallocHost(&host_, cap) != cudaSuccess || cudaMalloc(&dev_, cap) != cudaSuccess) {
+            cudaGetLastError();
+            Release();
+            return false;
+        }
+        capacity_ = cap;
+        return true;
+    }
+    template <class T>
+    T *host() { return static_cast<T *>(host_); }
+    template <class T>
+    T *dev() { return static_cast<T *>(dev_); }
+    bool ToDevice(size_t bytes, cudaStream_t s) {
+        return bytes == 0 || cudaMemcpyAsync(dev_, host_, bytes, cudaMemcpyHostToDevice, s) == cudaSuccess;
+    }
+    bool ToHost(size_t bytes, cudaStream_t s) {
+        return bytes == 0 || cudaMemcpyAsync(host_, dev_, bytes, cudaMemcpyDeviceToHost, s) == cudaSuccess;
+    }
+
+private:
+    void Release() {
+        if (host_) cudaFreeHost(host_);
+        if (dev_) cudaFree(dev_);
+        host_ = dev_ = nullptr;
+        capacity_ = 0;
+    }
+    void *host_ = nullptr;
+    void *dev_ = nullptr;
+    size_t capacity_ = 0;
+};
+
+inline int32_t Sync(cudaStream_t s) {
+    return cudaStreamSynchronize(s) == cudaSuccess ? KVCM_OK : KVCM_ER_CUDA_STREAM_SYNCHRONIZE_ERROR;
+}
+
+}  // namespace detail
+
+// Batched chained block hash.  One instance per thread (it owns staging buffers).
+class GpuKeyGenerator {
+public:
+    explicit GpuKeyGenerator(cudaStream_t stream = nullptr) : stream_(stream) {}
+
+    // GenKeyVector for many requests: keys[r] = chained hashes of the whole blocks of tokens[r].
+    int32_t GenKeyVectorBatch(const std::vector<TokenIdsVector> &tokens, int64_t block_size,
+                              std::vector<KeyVector> *keys) {
+        keys->assign(tokens.size(), {});
+        if (block_size <= 0) return KVCM_EC_BADARGS;
+        const int32_t n_req = static_cast<int32_t>(tokens.size());
+        if (n_req == 0) return KVCM_OK;
+        int64_t n_tok = 0;
+        for (const auto &t : tokens) n_tok += static_cast<int64_t>(t.size());
+        const size_t off_bytes = sizeof(int64_t) * (n_req + 1);
+        if (!tok_.Reserve(sizeof(int64_t) * (n_tok + 2)) || !tok_off_.Reserve(off_bytes) ||
+            !key_off_.Reserve(off_bytes)) {
+            return KVCM_EC_NOSPC;
+        }
+        int64_t at = 0;
+        for (int32_t r = 0; r < n_req; ++r) {
+            tok_off_.host<int64_t>()[r] = at;
+            if (!tokens[r].empty()) std::memcpy(tok_.host<int64_t>() + at, tokens[r].data(), sizeof(int64_t) * tokens[r].size());
+            at += static_cast<int64_t>(tokens[r].size());
+        }
+        tok_off_.host<int64_t>()[n_req] = at;
+        int32_t rc = kvcm_b200_key_offsets(tok_off_.host<int64_t>(), n_req, static_cast<int32_t>(block_size),
+                                           key_off_.host<int64_t>());
+        if (rc != KVCM_OK) return rc;
+        const int64_t n_keys = key_off_.host<int64_t>()[n_req];
+        if (!keys_.Reserve(sizeof(int64_t) * (n_keys + 1))) return KVCM_EC_NOSPC;
+        if (!tok_.ToDevice(sizeof(int64_t) * n_tok, stream_) || !tok_off_.ToDevice(off_bytes, stream_) ||
+            !key_off_.ToDevice(off_bytes, stream_)) {
+            return KVCM_ER_CUDAMEMCPY_ERROR;
+        }
+        rc = kvcm_b200_hash_blocks_i64(tok_.dev<int64_t>(), n_tok, tok_off_.dev<int64_t>(), n_req,
+                                       static_cast<int32_t>(block_size), keys_.dev<int64_t>(),
+                                       key_off_.dev<int64_t>(), stream_);
+        if (rc != KVCM_OK) return rc;
+        if (!keys_.ToHost(sizeof(int64_t) * n_keys, stream_)) return KVCM_ER_CUDAMEMCPY_ERROR;
+        rc = detail::Sync(stream_);
+        if (rc != KVCM_OK) return rc;
+        for (int32_t r = 0; r < n_req; ++r) {
+            const int64_t b = key_off_.host<int64_t>()[r], e = key_off_.host<int64_t>()[r + 1];
+            (*keys)[r].assign(keys_.host<int64_t>() + b, keys_.host<int64_t>() + e);
+        }
+        return KVCM_OK;
+    }
+
+    // The reference's single-request operator: a batch of one.
+    KeyVector GenKeyVector(const TokenIdsVector &tokens, int64_t block_size) {
+        std::vector<KeyVector> out;
+        GenKeyVectorBatch({tokens}, block_size, &out);
+        return out.empty() ? KeyVector{} : out[0];
+    }
+
+    // One chained key per id (block size 1).
+    KeyVector ApplyPrefixHash(const std::vector<int64_t> &hash_ids) { return GenKeyVector(hash_ids, 1); }
+
+private:
+    cudaStream_t stream_;
+    detail::Mirror tok_, tok_off_, key_off_, keys_;
+};
+
+// Device-resident block index of one instance.
+class GpuBlockIndex {
+public:
+    explicit GpuBlockIndex(int64_t max_keys, cudaStream_t stream = nullptr) : stream_(stream) {
+        kvcm_b200_index_create(max_keys, &index_);
+    }
+    GpuBlockIndex(const GpuBlockIndex &) = delete;
+    GpuBlockIndex &operator=(const GpuBlockIndex &) = delete;
+    ~GpuBlockIndex() { kvcm_b200_index_destroy(index_); }
+    bool ok() const { return index_ != nullptr; }
+    kvcm_b200_index_t *handle() const { return index_; }
+
+    // Mirrors a MetaIndexer::Put / Update batch: key i gets value word values[i] (EncodeLocations).
+    int32_t Put(const KeyVector &keys, const std::vector<uint64_t> &values) {
+        if (keys.size() != values.size()) return KVCM_EC_BADARGS;
+        const size_t n = keys.size();
+        if (n == 0) return KVCM_OK;
+        if (!keys_.Reserve(sizeof(int64_t) * n) || !vals_.Reserve(sizeof(uint64_t) * n)) return KVCM_EC_NOSPC;
+        std::memcpy(keys_.host<int64_t>(), keys.data(), sizeof(int64_t) * n);
+        std::memcpy(vals_.host<uint64_t>(), values.data(), sizeof(uint64_t) * n);
+        if (!keys_.ToDevice(sizeof(int64_t) * n, stream_) || !vals_.ToDevice(sizeof(uint64_t) * n, stream_)) {
+            return KVCM_ER_CUDAMEMCPY_ERROR;
+        }
+        const int32_t rc = kvcm_b200_index_upsert(index_, keys_.dev<int64_t>(), vals_.dev<uint64_t>(), 0,
+                                                  static_cast<int64_t>(n), nullptr, stream_);
+        return rc != KVCM_OK ? rc : detail::Sync(stream_);
+    }
+
+    int32_t Erase(const KeyVector &keys) {
+        const size_t n = keys.size();
+        if (n == 0) return KVCM_OK;
+        if (!keys_.Reserve(sizeof(int64_t) * n)) return KVCM_EC_NOSPC;
+        std::memcpy(keys_.host<int64_t>(), keys.data(), sizeof(int64_t) * n);
+        if (!keys_.ToDevice(sizeof(int64_t) * n, stream_)) return KVCM_ER_CUDAMEMCPY_ERROR;
+        const int32_t rc = kvcm_b200_index_erase(index_, keys_.dev<int64_t>(), static_cast<int64_t>(n), stream_);
+        return rc != KVCM_OK ? rc : detail::Sync(stream_);
+    }
+
+private:
+    cudaStream_t stream_;
+    kvcm_b200_index_t *index_ = nullptr;
+    detail::Mirror keys_, vals_;
+};
+
+// The matchers of MetaSearcher over a GpuBlockIndex.  Results are lengths / window starts / flags;
+// turning matched keys into CacheLocation objects stays with the caller's CPU-side table.
+class GpuMetaSearcher {
+public:
+    GpuMetaSearcher(GpuBlockIndex *index, uint32_t avail_mask = KVCM_AVAIL_ALL, cudaStream_t stream = nullptr)
+        : index_(index), avail_mask_(avail_mask), stream_(stream) {}
+
+    // Batched PrefixMatch: out_len[r] = number of leading unmasked servable keys of request r.
+    int32_t PrefixMatchBatch(const std::vector<KeyVector> &keys, const std::vector<BlockMask> &masks,
+                             std::vector<int32_t> *out_len) {
+        const int32_t n_req = static_cast<int32_t>(keys.size());
+        out_len->assign(n_req, 0);
+        if (!masks.empty() && masks.size() != keys.size()) return KVCM_EC_BADARGS;
+        if (n_req == 0) return KVCM_OK;
+        int32_t rc = Stage(keys);
+        if (rc != KVCM_OK) return rc;
+        const int64_t n_keys = key_off_.host<int64_t>()[n_req];
+        // Offsets and vectors both become a per-key byte mask: index i is masked when
+        // IsIndexInMaskRange says so (kv_cache_manager/manager/cache_location.cc:9-21).
+        const uint8_t *d_bits = nullptr;
+        if (!masks.empty()) {
+            if (!bits_.Reserve(static_cast<size_t>(n_keys) + 1)) return KVCM_EC_NOSPC;
+            uint8_t *bits = bits_.host<uint8_t>();
+            std::memset(bits, 0, static_cast<size_t>(n_keys));
+            for (int32_t r = 0; r < n_req; ++r) {
+                uint8_t *b = bits + key_off_.host<int64_t>()[r];
+                const size_t n = keys[r].size();
+                if (std::holds_alternative<BlockMaskVector>(masks[r])) {
+                    const auto &v = std::get<BlockMaskVector>(masks[r]);
+                    for (size_t i = 0; i < n && i < v.size(); ++i) b[i] = v[i] ? 1 : 0;
+                } else {
+                    const size_t off = std::get<BlockMaskOffset>(masks[r]);
+                    for (size_t i = 0; i < n && i < off; ++i) b[i] = 1;
+                }
+            }
+            if (!bits_.ToDevice(static_cast<size_t>(n_keys), stream_)) return KVCM_ER_CUDAMEMCPY_ERROR;
+            d_bits = bits_.dev<uint8_t>();
+        }
+        if (!out_.Reserve(sizeof(int32_t) * n_req)) return KVCM_EC_NOSPC;
+        rc = kvcm_b200_match_prefix(index_->handle(), keys_.dev<int64_t>(), key_off_.dev<int64_t>(), n_req, nullptr,
+                                    d_bits, avail_mask_, out_.dev<int32_t>(), stream_);
+        if (rc != KVCM_OK) return rc;
+        if (!out_.ToHost(sizeof(int32_t) * n_req, stream_)) return KVCM_ER_CUDAMEMCPY_ERROR;
+        rc = detail::Sync(stream_);
+        if (rc == KVCM_OK) std::memcpy(out_len->data(), out_.host<int32_t>(), sizeof(int32_t) * n_req);
+        return rc;
+    }
+
+    // MetaSearcher::PrefixMatch for one request.
+    int32_t PrefixMatch(const KeyVector &keys, const BlockMask &mask, size_t *out_len) {
+        std::vector<int32_t> len;
+        const int32_t rc = PrefixMatchBatch({keys}, {mask}, &len);
+        *out_len = rc == KVCM_OK ? static_cast<size_t>(len[0]) : 0;
+        return rc;
+    }
+
+    // Batched ReverseRollSlideWindowMatch: out_base[r] = start of the matched window, -1 none,
+    // -2 when request r has fewer than sw_size keys.  sw_size <= 0 -> KVCM_EC_BADARGS.
+    int32_t ReverseRollSlideWindowMatchBatch(const std::vector<KeyVector> &keys, int32_t sw_size,
+                                             std::vector<int32_t> *out_base) {
+        const int32_t n_req = static_cast<int32_t>(keys.size());
+        out_base->assign(n_req, -1);
+        if (sw_size <= 0) return KVCM_EC_BADARGS;
+        if (n_req == 0) return KVCM_OK;
+        int32_t rc = Stage(keys);
+        if (rc != KVCM_OK) return rc;
+        if (!out_.Reserve(sizeof(int32_t) * n_req)) return KVCM_EC_NOSPC;
+        rc = kvcm_b200_match_sw(index_->handle(), keys_.dev<int64_t>(), key_off_.dev<int64_t>(), n_req, sw_size,
+                                avail_mask_, out_.dev<int32_t>(), stream_);
+        if (rc != KVCM_OK) return rc;
+        if (!out_.ToHost(sizeof(int32_t) * n_req, stream_)) return KVCM_ER_CUDAMEMCPY_ERROR;
+        rc = detail::Sync(stream_);
+        if (rc == KVCM_OK) std::memcpy(out_base->data(), out_.host<int32_t>(), sizeof(int32_t) * n_req);
+        return rc;
+    }
+
+    // One request, with the reference's argument guard (kv_cache_manager/manager/cache_manager.cc:993-997).
+    int32_t ReverseRollSlideWindowMatch(const KeyVector &keys, int32_t sw_size, int64_t *out_base) {
+        *out_base = -1;
+        if (sw_size <= 0 || keys.size() < static_cast<size_t>(sw_size)) return KVCM_EC_BADARGS;
+        std::vector<int32_t> base;
+        const int32_t rc = ReverseRollSlideWindowMatchBatch({keys}, sw_size, &base);
+        if (rc == KVCM_OK) *out_base = base[0];
+        return rc;
+    }
+
+    // BatchGetBestLocation / BatchGetLocation: flags per key (KVCM_FLAG_*), no early stop.
+    int32_t BatchGet(const KeyVector &keys, std::vector<uint8_t> *flags) {
+        flags->assign(keys.size(), 0);
+        if (keys.empty()) return KVCM_OK;
+        int32_t rc = Stage({keys});
+        if (rc != KVCM_OK) return rc;
+        if (!out_.Reserve(keys.size())) return KVCM_EC_NOSPC;
+        rc = kvcm_b200_batch_get(index_->handle(), keys_.dev<int64_t>(), static_cast<int64_t>(keys.size()),
+                                 avail_mask_, out_.dev<uint8_t>(), stream_);
+        if (rc != KVCM_OK) return rc;
+        if (!out_.ToHost(keys.size(), stream_)) return KVCM_ER_CUDAMEMCPY_ERROR;
+        rc = detail::Sync(stream_);
+        if (rc == KVCM_OK) std::memcpy(flags->data(), out_.host<uint8_t>(), keys.size());
+        return rc;
+    }
+
+private:
+    // Copies the requests to the device in CSR form.
+    int32_t Stage(const std::vector<KeyVector> &keys) {
+        const size_t n_req = keys.size();
+        size_t n_keys = 0;
+        for (const auto &k : keys) n_keys += k.size();
+        if (!keys_.Reserve(sizeof(int64_t) * (n_keys + 1)) || !key_off_.Reserve(sizeof(int64_t) * (n_req + 1))) {
+            return KVCM_EC_NOSPC;
+        }
+        int64_t at = 0;
+        for (size_t r = 0; r < n_req; ++r) {
+            key_off_.host<int64_t>()[r] = at;
+            if (!keys[r].empty()) std::memcpy(keys_.host<int64_t>() + at, keys[r].data(), sizeof(int64_t) * keys[r].size());
+            at += static_cast<int64_t>(keys[r].size());
+        }
+        key_off_.host<int64_t>()[n_req] = at;
+        if (!keys_.ToDevice(sizeof(int64_t) * n_keys, stream_) ||
+            !key_off_.ToDevice(sizeof(int64_t) * (n_req + 1), stream_)) {
+            return KVCM_ER_CUDAMEMCPY_ERROR;
+        }
+        return KVCM_OK;
+    }
+
+    GpuBlockIndex *index_;
+    uint32_t avail_mask_;
+    cudaStream_t stream_;
+    detail::Mirror keys_, key_off_, bits_, out_;
+};
+
+// kv_cache_manager/client/include/common.h:94-116
+enum class MemoryType : uint8_t { CPU = 0, GPU = 1 };
+struct Iov {
+    MemoryType type{MemoryType::GPU};
+    void *base{nullptr};
+    size_t size{0};
+    bool ignore{false};
+};
+struct BlockBuffer {
+    std::vector<Iov> iovs;
+};
+
+// One launch for all iovs of a request instead of one cudaMemcpyAsync per Iov.
+class IovCopier {
+public:
+    explicit IovCopier(cudaStream_t stream = nullptr) : stream_(stream) {
+        cudaEventCreateWithFlags(&staged_, cudaEventDisableTiming);
+    }
+    IovCopier(const IovCopier &) = delete;
+    IovCopier &operator=(const IovCopier &) = delete;
+    ~IovCopier() { cudaEventDestroy(staged_); }
+
+    // direction 0: iovs -> block_string (Put), 1: block_string -> iovs (Get).  block_string must be
+    // reachable from the device (device memory, or host memory registered with cudaHostRegister as the
+    // reference's LocalFileSdk does for its mmap).  Asynchronous on the adapter's stream; the caller
+    // keeps the reference's single cudaStreamSynchronize.  *span_bytes = bytes the iov list covers.
+    int32_t CopyIovs(const BlockBuffer &buffer, void *block_string, int direction, uint64_t *span_bytes) {
+        const int32_t n = static_cast<int32_t>(buffer.iovs.size());
+        if (n == 0) {
+            if (span_bytes) *span_bytes = 0;
+            return KVCM_OK;
+        }
+        std::vector<kvcm_b200_iov_t> iovs(n);
+        for (int32_t i = 0; i < n; ++i) {
+            iovs[i].type = static_cast<uint8_t>(buffer.iovs[i].type);
+            iovs[i].ignore = buffer.iovs[i].ignore ? 1 : 0;
+            iovs[i].base = buffer.iovs[i].base;
+            iovs[i].size = buffer.iovs[i].size;
+        }
+        // The pinned segment table is reused: wait until the previous call's copy of it has left.
+        if (cudaEventSynchronize(staged_) != cudaSuccess) return KVCM_ER_CUDA_STREAM_SYNCHRONIZE_ERROR;
+        if (!segs_.Reserve(sizeof(kvcm_b200_seg_t) * n)) return KVCM_EC_NOSPC;
+        int32_t n_segs = 0;
+        int32_t rc = kvcm_b200_iovs_to_segments(iovs.data(), n, block_string, direction,
+                                                segs_.host<kvcm_b200_seg_t>(), &n_segs, span_bytes);
+        if (rc != KVCM_OK) return rc;
+        if (!segs_.ToDevice(sizeof(kvcm_b200_seg_t) * n_segs, stream_)) return KVCM_ER_CUDAMEMCPY_ERROR;
+        rc = kvcm_b200_copy_segments(segs_.dev<kvcm_b200_seg_t>(), n_segs, stream_);
+        cudaEventRecord(staged_, stream_);  // also covers the kernel: the device table may be rewritten after it
+        return rc;
+    }
+
+private:
+    cudaStream_t stream_;
+    cudaEvent_t staged_ = nullptr;
+    detail::Mirror segs_;
+};
+
+}  // namespace kvcm_b200

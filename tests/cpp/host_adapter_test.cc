@@ -1,0 +1,172 @@
+// Drives the C++ host adapters (tair-kvcache_b200/host/kvcm_b200_host.h) with the known-answer
+// tables of the reference's own C++ unit tests, the way those tests call MetaSearcher and
+// CacheManager.  Needs a GPU.  Exit code 0 = all checks passed.
+//   kv_cache_manager/manager/test/meta_searcher_test.cc:196-274   prefix match, masks
+//   kv_cache_manager/manager/test/cache_manager_test.cc:474-786   prefix / batch-get / sliding window
+//   hash values: from the reference's hash_util.h compiled as-is (see tests/golden/hash_kat.json)
+#include <cstdio>
+#include <string>
+
+#include "kvcm_b200_host.h"
+
+using namespace kvcm_b200;
+
+static int g_failed = 0;
+#define EXPECT_EQ(a, b)                                                                      \
+    do {                                                                                     \
+        const auto va = (a);                                                                 \
+        const auto vb = (b);                                                                 \
+        if (!(va == vb)) {                                                                   \
+            std::printf("FAIL %s:%d: %s != %s (%lld vs %lld)\n", __FILE__, __LINE__, #a, #b, \
+                        (long long)va, (long long)vb);                                       \
+            ++g_failed;                                                                      \
+        }                                                                                    \
+    } while (0)
+
+static uint64_t Serving(int type) { return EncodeLocations({{CLS_SERVING, type}}); }
+static uint64_t Writing(int type) { return EncodeLocations({{CLS_WRITING, type}}); }
+
+static void TestHash() {
+    GpuKeyGenerator gen;
+    const KeyVector k1 = gen.GenKeyVector({1, 2, 3, 4}, 2);
+    EXPECT_EQ(k1.size(), size_t(2));
+    EXPECT_EQ(k1[0], -8366447769517741626LL);
+    EXPECT_EQ(k1[1], 455111481605203084LL);
+    TokenIdsVector t(130);
+    for (int i = 0; i < 130; ++i) t[i] = i;
+    const KeyVector k2 = gen.GenKeyVector(t, 64);
+    EXPECT_EQ(k2.size(), size_t(2));
+    EXPECT_EQ(k2[0], 2681637840371060507LL);
+    EXPECT_EQ(k2[1], -6990124544746687103LL);
+    const KeyVector k3 = gen.ApplyPrefixHash({100, 200, 300});
+    EXPECT_EQ(k3.size(), size_t(3));
+    EXPECT_EQ(k3[0], -7046029254386353031LL);
+    EXPECT_EQ(k3[2], 8024479186332561338LL);
+    EXPECT_EQ(gen.GenKeyVector({}, 16).size(), size_t(0));
+    EXPECT_EQ(gen.GenKeyVector({1, 2, 3}, 16).size(), size_t(0));
+    std::vector<KeyVector> batch;
+    EXPECT_EQ(gen.GenKeyVectorBatch({{1, 2, 3, 4}, {}, t}, 2, &batch), KVCM_OK);
+    EXPECT_EQ(batch[0][1], 455111481605203084LL);
+    EXPECT_EQ(batch[1].size(), size_t(0));
+    EXPECT_EQ(batch[2].size(), size_t(65));
+}
+
+static void TestPrefixMatch() {
+    GpuBlockIndex index(64);
+    GpuMetaSearcher searcher(&index);
+    size_t len = 99;
+    // locations added but not yet SERVING: nothing matches (meta_searcher_test.cc:196-204)
+    EXPECT_EQ(index.Put({10, 20, 30}, {Writing(4), Writing(1), Writing(2)}), KVCM_OK);
+    EXPECT_EQ(searcher.PrefixMatch({10, 20, 30}, BlockMask{}, &len), KVCM_OK);
+    EXPECT_EQ(len, size_t(0));
+    EXPECT_EQ(index.Put({10, 20, 30}, {Serving(4), Serving(1), Serving(2)}), KVCM_OK);
+    struct Case {
+        KeyVector keys;
+        size_t want;
+    };
+    const std::vector<Case> cases = {{{10, 20, 30}, 3}, {{10, 20, 999}, 2}, {{10, 999, 999}, 1}, {{999, 999, 999}, 0},
+                                     {{}, 0},           {{10}, 1},          {{10, 20}, 2},       {{10, 999, 30}, 1}};
+    for (const Case &c : cases) {
+        EXPECT_EQ(searcher.PrefixMatch(c.keys, BlockMask{}, &len), KVCM_OK);
+        EXPECT_EQ(len, c.want);
+    }
+    // masks: vector {true,false,false} and offset 1 both skip the first key (:254-274)
+    EXPECT_EQ(searcher.PrefixMatch({10, 20, 30}, BlockMask{BlockMaskVector{true, false, false}}, &len), KVCM_OK);
+    EXPECT_EQ(len, size_t(2));
+    EXPECT_EQ(searcher.PrefixMatch({10, 20, 30}, BlockMask{BlockMaskOffset{1}}, &len), KVCM_OK);
+    EXPECT_EQ(len, size_t(2));
+    // batched form, mixed masks
+    std::vector<int32_t> lens;
+    EXPECT_EQ(searcher.PrefixMatchBatch({{10, 20, 30}, {10, 999, 30}, {}, {999, 10}},
+                                        {BlockMask{}, BlockMask{BlockMaskOffset{0}}, BlockMask{},
+                                         BlockMask{BlockMaskVector{true}}},
+                                        &lens),
+              KVCM_OK);
+    EXPECT_EQ(lens[0], 3);
+    EXPECT_EQ(lens[1], 1);
+    EXPECT_EQ(lens[2], 0);
+    EXPECT_EQ(lens[3], 1);
+    // a storage class the policy has switched off is not servable
+    GpuMetaSearcher no_hf3fs(&index, KVCM_AVAIL_ALL & ~(1u << 1));
+    EXPECT_EQ(no_hf3fs.PrefixMatch({10, 20, 30}, BlockMask{}, &len), KVCM_OK);
+    EXPECT_EQ(len, size_t(1));
+    // erase
+    EXPECT_EQ(index.Erase({20}), KVCM_OK);
+    EXPECT_EQ(searcher.PrefixMatch({10, 20, 30}, BlockMask{}, &len), KVCM_OK);
+    EXPECT_EQ(len, size_t(1));
+}
+
+static void TestSlidingWindowAndBatchGet() {
+    // keys 1..6 started, first five finished: 1..5 SERVING, 6 WRITING (cache_manager_test.cc:666-749)
+    GpuBlockIndex index(64);
+    GpuMetaSearcher searcher(&index);
+    EXPECT_EQ(index.Put({1, 2, 3, 4, 5, 6}, {Serving(4), Serving(4), Serving(4), Serving(4), Serving(4), Writing(4)}),
+              KVCM_OK);
+    int64_t base = 0;
+    EXPECT_EQ(searcher.ReverseRollSlideWindowMatch({1, 2, 3, 4, 5, 6, 7}, 2, &base), KVCM_OK);
+    EXPECT_EQ(base, 3);  // non-empty exactly at positions 3,4
+    EXPECT_EQ(searcher.ReverseRollSlideWindowMatch({1, 2, 3, 10, 5, 6, 7}, 2, &base), KVCM_OK);
+    EXPECT_EQ(base, 1);  // non-empty exactly at positions 1,2
+    EXPECT_EQ(searcher.ReverseRollSlideWindowMatch({6, 7, 8}, 2, &base), KVCM_OK);
+    EXPECT_EQ(base, -1);
+    EXPECT_EQ(searcher.ReverseRollSlideWindowMatch({1}, 2, &base), KVCM_EC_BADARGS);   // keys.size() < sw_size
+    EXPECT_EQ(searcher.ReverseRollSlideWindowMatch({1}, -1, &base), KVCM_EC_BADARGS);  // sw_size < 0
+    EXPECT_EQ(searcher.ReverseRollSlideWindowMatch({1}, 0, &base), KVCM_EC_BADARGS);   // never ends in the reference
+    std::vector<uint8_t> flags;
+    EXPECT_EQ(searcher.BatchGet({1, 2, 111, 6}, &flags), KVCM_OK);  // cache_manager_test.cc:547-630
+    EXPECT_EQ(flags[0] & KVCM_FLAG_SERVABLE, 1);
+    EXPECT_EQ(flags[1] & KVCM_FLAG_SERVABLE, 1);
+    EXPECT_EQ(int(flags[2]), 0);
+    EXPECT_EQ(flags[3] & KVCM_FLAG_SERVABLE, 0);
+    EXPECT_EQ(flags[3] & KVCM_FLAG_WRITABLE, int(KVCM_FLAG_WRITABLE));
+}
+
+static void TestIovCopier() {
+    // a block of 3 layers x (K,V) iovs with one ignored iov in the middle
+    const size_t sz = 4096;
+    std::vector<uint8_t> host(6 * sz);
+    for (size_t i = 0; i < host.size(); ++i) host[i] = static_cast<uint8_t>(i * 7 + i / sz);
+    uint8_t *d_src = nullptr, *d_string = nullptr, *d_back = nullptr;
+    cudaMalloc(&d_src, host.size());
+    cudaMalloc(&d_string, host.size());
+    cudaMalloc(&d_back, host.size());
+    cudaMemcpy(d_src, host.data(), host.size(), cudaMemcpyHostToDevice);
+    cudaMemset(d_string, 0, host.size());
+    cudaMemset(d_back, 0, host.size());
+    BlockBuffer put, get;
+    for (int i = 0; i < 6; ++i) {
+        put.iovs.push_back({MemoryType::GPU, d_src + i * sz, sz, i == 2});
+        get.iovs.push_back({MemoryType::GPU, d_back + i * sz, sz, i == 2});
+    }
+    IovCopier copier;
+    uint64_t span = 0;
+    EXPECT_EQ(copier.CopyIovs(put, d_string, 0, &span), KVCM_OK);
+    EXPECT_EQ(span, uint64_t(6 * sz));
+    EXPECT_EQ(copier.CopyIovs(get, d_string, 1, &span), KVCM_OK);
+    cudaDeviceSynchronize();
+    std::vector<uint8_t> back(host.size());
+    cudaMemcpy(back.data(), d_back, back.size(), cudaMemcpyDeviceToHost);
+    for (int i = 0; i < 6; ++i) {
+        bool same = std::memcmp(back.data() + i * sz, host.data() + i * sz, sz) == 0;
+        bool zero = true;
+        for (size_t j = 0; j < sz; ++j) zero = zero && back[i * sz + j] == 0;
+        EXPECT_EQ(i == 2 ? zero : same, true);
+    }
+    cudaFree(d_src);
+    cudaFree(d_string);
+    cudaFree(d_back);
+}
+
+int main() {
+    int32_t sms = 0;
+    if (kvcm_b200_device_info(&sms, nullptr, nullptr, nullptr) != KVCM_OK) {
+        std::printf("no CUDA device: the adapters have no CPU path\n");
+        return 2;
+    }
+    TestHash();
+    TestPrefixMatch();
+    TestSlidingWindowAndBatchGet();
+    TestIovCopier();
+    std::printf(g_failed == 0 ? "host adapter test: all checks passed\n" : "host adapter test: %d checks FAILED\n", g_failed);
+    return g_failed == 0 ? 0 : 1;
+}
