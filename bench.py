@@ -247,10 +247,12 @@ def run_prefix_gpu(device, steps, warmup):
         GenKeyVectorBatch(d_toks, d_off, bs, d_ko, n_keys, out=d_keys)
         searcher.PrefixMatch(d_keys, d_ko, out=d_len)
 
-    # End to end: tokens start in pinned host memory and the lengths end there.  The batch is cut into request
-    # ranges that alternate between two streams, so the token copy of one range overlaps hash + match of the other.
+    # End to end: tokens start in pinned host memory and the lengths end there.  The hash kernel's time is the
+    # latency of the longest chain, not its volume, so cutting the batch into many ranges to overlap copy and
+    # compute would repeat that latency per range: one range is fastest at this size (more only pay off when a
+    # range's copy takes much longer than the longest chain).
     n_req = len(off) - 1
-    n_chunks = 8
+    n_chunks = 1
     bounds = [int(np.searchsorted(off, off[-1] * c // n_chunks)) for c in range(n_chunks)] + [n_req]
     bounds = sorted(set(min(max(b, 0), n_req) for b in bounds))
     streams = [torch.cuda.Stream(device), torch.cuda.Stream(device)]
@@ -491,13 +493,56 @@ def main_b200(args, cfg, rank, world):
         dist.destroy_process_group()
 
 
+def main_prefix(args, rank, world):
+    """--workload c1: the CPU-runnable prefix-match configuration on its own (hash + prefix match of 4,096
+    requests against an index of 200k prior blocks).  Replicas only: every rank runs the same batch."""
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    if args.impl == "reference":
+        data = build_prefix_workload()
+        (ptoks, poff), (toks, off), _, bs = data
+        from oracle import kvcm_oracle as oracle
+        cpu, n_rep = run_prefix_cpu((toks, off, oracle.key_offsets(off, bs), bs, ptoks, poff), threads)
+        print(json.dumps({"impl": "reference", "metric": "prefix_match_token_blocks_per_s", "value": cpu,
+                          "unit": "token-blocks/s", "n_gpus": args.gpus, "steps": n_rep, "warmup": 0,
+                          "higher_is_better": True, "dtype": "int64", "data": "synthetic",
+                          "config": {"workload": "4096 requests, block 64, index of 200k blocks (CPU restatement, "
+                                                 "without the reference's per-key JSON parse)"},
+                          "cpu_baseline": {"value": cpu, "unit": "token-blocks/s", "cores": threads, "kind": "port",
+                                           "sample": "the whole workload, %d repetitions" % n_rep},
+                          "e2e": {"value": cpu, "unit": "token-blocks/s", "h2d_bytes_per_step": 0,
+                                  "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
+        return
+    import torch
+
+    import tair_kvcache_b200  # noqa: F401
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+    torch.cuda.set_device(device)
+    pm, data = run_prefix_gpu(device, args.steps, args.warmup)
+    line = {"metric": "prefix_match_token_blocks_per_s", "value": pm["token_blocks_per_s"], "unit": "token-blocks/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1e3 * pm["token_blocks"] / pm["token_blocks_per_s"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
+            "config": {"workload": pm["workload"]},
+            "e2e": {"value": pm["e2e_token_blocks_per_s"], "unit": "token-blocks/s",
+                    "h2d_bytes_per_step": pm["h2d_bytes_per_step"], "d2h_bytes_per_step": pm["d2h_bytes_per_step"]},
+            "gpu_launches": 2 * args.steps}
+    if not args.no_cpu:
+        cpu, n_rep = run_prefix_cpu(data, threads)
+        line["cpu_baseline"] = {"value": cpu, "unit": "token-blocks/s", "cores": threads, "kind": "port",
+                                "sample": "the whole workload, %d repetitions; omits the reference's per-key JSON "
+                                          "parse and string copies" % n_rep}
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c1"])
     ap.add_argument("--no-prefix", action="store_true", help="skip the prefix-match side measurement")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-staging leg (profiling runs)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
@@ -507,6 +552,9 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
+    if args.workload == "c1":
+        main_prefix(args, rank, world)
+        return
     cfg = dict(WORKLOADS[args.workload])
     cfg["full_size"] = not (args.n_blocks or args.pool_pages)
     if args.n_blocks:
