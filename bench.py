@@ -643,7 +643,8 @@ def main_window(args, rank, world):
     def step():
         keys = GenKeyVectorBatch(w["toks"], d_off, bs, d_ko, n_keys, out=d_keys)
         if world > 1:
-            return searcher.PrefixMatch(keys, d_ko), searcher.ReverseRollSlideWindowMatch(keys, d_ko, sw)
+            g = searcher.Gather(keys, d_ko)  # one exchange of the keys serves both queries
+            return searcher.PrefixMatch(g), searcher.ReverseRollSlideWindowMatch(g, sw_size=sw)
         return local_index.PrefixMatch(keys, d_ko), local_index.ReverseRollSlideWindowMatch(keys, d_ko, sw)
 
     for _ in range(args.warmup):

@@ -308,8 +308,8 @@ KVCM_API int32_t kvcm_b200_batch_get(kvcm_b200_index_t *index, const int64_t *d_
  *   upsert_sharded        inserts only the keys this shard owns out of the full batch;
  *   match_prefix_sharded  as match_prefix, but keys of other shards never stop the count, so
  *                         min over shards of d_len_out = the unsharded prefix length;
- *   batch_get (above)     on a shard returns 0 for keys it does not own, so a byte-wise max over
- *                         shards of the flags = the unsharded flags;
+ *   batch_get_sharded     as batch_get, 0 for keys of other shards without probing, so a byte-wise
+ *                         max over shards of the flags = the unsharded flags;
  *   match_sw_from_flags   the sliding-window search of match_sw over such combined flags (bit0).
  * ---------------------------------------------------------------------------------------- */
 KVCM_API int32_t kvcm_b200_index_upsert_sharded(kvcm_b200_index_t *index, const int64_t *d_keys,
@@ -320,6 +320,9 @@ KVCM_API int32_t kvcm_b200_match_prefix_sharded(kvcm_b200_index_t *index, const 
                                                 const int64_t *d_key_off, int32_t n_req, const int64_t *d_mask_off,
                                                 const uint8_t *d_mask_bits, uint32_t avail_mask, int32_t shard_count,
                                                 int32_t shard_rank, int32_t *d_len_out, kvcm_stream_t stream);
+KVCM_API int32_t kvcm_b200_batch_get_sharded(kvcm_b200_index_t *index, const int64_t *d_keys, int64_t n,
+                                             uint32_t avail_mask, int32_t shard_count, int32_t shard_rank,
+                                             uint8_t *d_flags_out, kvcm_stream_t stream);
 KVCM_API int32_t kvcm_b200_match_sw_from_flags(const uint8_t *d_flags, const int64_t *d_key_off, int32_t n_req,
                                                int32_t sw_blocks, int32_t *d_base_out, kvcm_stream_t stream);
 

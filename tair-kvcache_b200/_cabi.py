@@ -83,6 +83,7 @@ SIGNATURES = {
     "kvcm_b200_batch_get": [_vp, _vp, _i64, _u32, _vp, _vp],
     "kvcm_b200_index_upsert_sharded": [_vp, _vp, _vp, _u64, _i64, _i32, _i32, _vp, _vp],
     "kvcm_b200_match_prefix_sharded": [_vp, _vp, _vp, _i32, _vp, _vp, _u32, _i32, _i32, _vp, _vp],
+    "kvcm_b200_batch_get_sharded": [_vp, _vp, _i64, _u32, _i32, _i32, _vp, _vp],
     "kvcm_b200_match_sw_from_flags": [_vp, _vp, _i32, _i32, _vp, _vp],
     "kvcm_b200_replay_workspace_bytes": [_i64],
     "kvcm_b200_replay": [_vp, _vp, _vp, _vp, _i32, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp],

@@ -167,10 +167,12 @@ __global__ void LookupKernel(IndexView ix, const int64_t *__restrict__ keys, int
 }
 
 __global__ void BatchGetKernel(IndexView ix, const int64_t *__restrict__ keys, int64_t n, uint32_t avail_mask,
-                               uint8_t *__restrict__ flags) {
+                               Shard shard, uint8_t *__restrict__ flags) {
     const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    const uint64_t v = Lookup(ix, static_cast<uint64_t>(keys[i]));
+    const uint64_t key = static_cast<uint64_t>(keys[i]);
+    // A key of another shard is reported absent without touching the table.
+    const uint64_t v = Owns(shard, key) ? Lookup(ix, key) : 0;
     uint32_t f = 0;
     if (v != 0) {
         f |= KVCM_FLAG_EXISTS;
@@ -490,8 +492,21 @@ int32_t kvcm_b200_batch_get(kvcm_b200_index_t *ix, const int64_t *d_keys, int64_
     if (n < 0) return KVCM_EC_BADARGS;
     if (n == 0) return KVCM_OK;
     if (d_keys == nullptr || d_flags_out == nullptr) return KVCM_ER_INVALID_ADDRESS;
-    kvcm::BatchGetKernel<<<kvcm::GridFor(n, 256), 256, 0, kvcm::AsStream(stream)>>>(kvcm::View(ix), d_keys, n,
-                                                                                     avail_mask, d_flags_out);
+    kvcm::BatchGetKernel<<<kvcm::GridFor(n, 256), 256, 0, kvcm::AsStream(stream)>>>(
+        kvcm::View(ix), d_keys, n, avail_mask, kvcm::Shard{1, 0}, d_flags_out);
+    return kvcm::LaunchStatus();
+}
+
+int32_t kvcm_b200_batch_get_sharded(kvcm_b200_index_t *ix, const int64_t *d_keys, int64_t n, uint32_t avail_mask,
+                                    int32_t shard_count, int32_t shard_rank, uint8_t *d_flags_out,
+                                    kvcm_stream_t stream) {
+    if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (n < 0 || shard_count < 1 || shard_rank < 0 || shard_rank >= shard_count) return KVCM_EC_BADARGS;
+    if (n == 0) return KVCM_OK;
+    if (d_keys == nullptr || d_flags_out == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    kvcm::BatchGetKernel<<<kvcm::GridFor(n, 256), 256, 0, kvcm::AsStream(stream)>>>(
+        kvcm::View(ix), d_keys, n, avail_mask,
+        kvcm::Shard{static_cast<uint32_t>(shard_count), static_cast<uint32_t>(shard_rank)}, d_flags_out);
     return kvcm::LaunchStatus();
 }
 

@@ -59,10 +59,10 @@ class CudaShardBackend:
                    shard_rank, out.data_ptr(), self.index._s())
         return out
 
-    def servable_flags(self, keys):
+    def servable_flags(self, keys, shard_count=1, shard_rank=0):
         out = torch.empty(keys.numel(), dtype=torch.uint8, device=self.device)
-        _cabi.call("kvcm_b200_batch_get", self.index.handle, keys.data_ptr(), keys.numel(), self.avail_mask,
-                   out.data_ptr(), self.index._s())
+        _cabi.call("kvcm_b200_batch_get_sharded", self.index.handle, keys.data_ptr(), keys.numel(), self.avail_mask,
+                   shard_count, shard_rank, out.data_ptr(), self.index._s())
         return out
 
     def sw_from_flags(self, flags, key_off, sw):
@@ -71,6 +71,13 @@ class CudaShardBackend:
         _cabi.call("kvcm_b200_match_sw_from_flags", flags.data_ptr(), key_off.data_ptr(), n_req, sw, out.data_ptr(),
                    self.index._s())
         return out
+
+
+class GatheredRequests:
+    """All ranks' requests after the exchange step, reusable for several queries on the same keys."""
+
+    def __init__(self, keys, csr, per_req, first, n_req):
+        self.keys, self.csr, self.per_req, self.first, self.n_req = keys, csr, per_req, first, n_req
 
 
 class ShardedMetaSearcher:
@@ -132,20 +139,26 @@ class ShardedMetaSearcher:
         """Every rank contributes keys; each key is stored on the shard that owns it."""
         self.backend.upsert_owned(self._gather_keys(keys.contiguous()), value_word, self.world, self.rank)
 
-    def PrefixMatch(self, keys: torch.Tensor, key_off: torch.Tensor, mask_off: Optional[torch.Tensor] = None
-                    ) -> torch.Tensor:
-        n_req = key_off.numel() - 1
+    def Gather(self, keys: torch.Tensor, key_off: torch.Tensor, mask_off: Optional[torch.Tensor] = None
+               ) -> GatheredRequests:
+        """The exchange step on its own: all-gather of every rank's keys (and mask offsets).  Pass the result to
+        PrefixMatch / ReverseRollSlideWindowMatch to run several queries on one exchange."""
         all_keys, csr, all_mask, _, first = self._gather_requests(keys.contiguous(), key_off.contiguous(), mask_off)
-        lens = self.backend.prefix_owned(all_keys, csr, all_mask, self.world, self.rank)
-        dist.all_reduce(lens, op=dist.ReduceOp.MIN, group=self.group)
-        return lens[first:first + n_req]
+        return GatheredRequests(all_keys, csr, all_mask, first, key_off.numel() - 1)
 
-    def ReverseRollSlideWindowMatch(self, keys: torch.Tensor, key_off: torch.Tensor, sw_size: int) -> torch.Tensor:
+    def PrefixMatch(self, keys, key_off: Optional[torch.Tensor] = None, mask_off: Optional[torch.Tensor] = None
+                    ) -> torch.Tensor:
+        g = keys if isinstance(keys, GatheredRequests) else self.Gather(keys, key_off, mask_off)
+        lens = self.backend.prefix_owned(g.keys, g.csr, g.per_req, self.world, self.rank)
+        dist.all_reduce(lens, op=dist.ReduceOp.MIN, group=self.group)
+        return lens[g.first:g.first + g.n_req]
+
+    def ReverseRollSlideWindowMatch(self, keys, key_off: Optional[torch.Tensor] = None, sw_size: int = 0
+                                    ) -> torch.Tensor:
         if sw_size <= 0:
             raise _cabi.KvcmError(_cabi.KVCM_EC_BADARGS, "ReverseRollSlideWindowMatch")
-        n_req = key_off.numel() - 1
-        all_keys, csr, _, _, first = self._gather_requests(keys.contiguous(), key_off.contiguous(), None)
-        flags = self.backend.servable_flags(all_keys)
+        g = keys if isinstance(keys, GatheredRequests) else self.Gather(keys, key_off, None)
+        flags = self.backend.servable_flags(g.keys, self.world, self.rank)
         dist.all_reduce(flags, op=dist.ReduceOp.MAX, group=self.group)
-        base = self.backend.sw_from_flags(flags, csr, sw_size)
-        return base[first:first + n_req]
+        base = self.backend.sw_from_flags(flags, g.csr, sw_size)
+        return base[g.first:g.first + g.n_req]

@@ -57,7 +57,7 @@ def test_shard_kernels_combine_to_the_unsharded_answer_on_one_gpu():
         assert np.array_equal(lens.cpu().numpy(), full.prefix_match_batch(keys, off))
         lens = torch.stack([sh.prefix_owned(dk, doff, dmask, count, r) for r, sh in enumerate(shards)]).min(0).values
         assert np.array_equal(lens.cpu().numpy(), full.prefix_match_batch(keys, off, mask))
-        flags = torch.stack([sh.servable_flags(dk) for sh in shards]).max(0).values
+        flags = torch.stack([sh.servable_flags(dk, count, r) for r, sh in enumerate(shards)]).max(0).values
         assert np.array_equal(flags.cpu().numpy(), full.batch_get(keys))
         for sw in (1, 4, 40):
             base = shards[0].sw_from_flags(flags, doff, sw)
@@ -92,7 +92,7 @@ def _rank_main(rank, port, results):
             "stored": searcher.backend.index.stats()[1],
             "prefix": searcher.PrefixMatch(keys, off).cpu().numpy(),
             "prefix_masked": searcher.PrefixMatch(keys, off, mask).cpu().numpy(),
-            "sw4": searcher.ReverseRollSlideWindowMatch(keys, off, 4).cpu().numpy(),
+            "sw4": searcher.ReverseRollSlideWindowMatch(keys, off, sw_size=4).cpu().numpy(),
         }
         torch.cuda.synchronize()
         results[rank] = out

@@ -42,7 +42,7 @@ class OracleShardBackend:
             out[r] = n
         return torch.from_numpy(out)
 
-    def servable_flags(self, keys):
+    def servable_flags(self, keys, shard_count=1, shard_rank=0):
         return torch.from_numpy(self.index.batch_get(keys.numpy()))
 
     def sw_from_flags(self, flags, key_off, sw):
@@ -95,6 +95,9 @@ def _rank_main(rank, port, results):
             "sw2": searcher.ReverseRollSlideWindowMatch(tk, to, 2).numpy().copy(),
             "sw5": searcher.ReverseRollSlideWindowMatch(tk, to, 5).numpy().copy(),
         }
+        g = searcher.Gather(tk, to, tm)  # one exchange, two queries
+        assert np.array_equal(searcher.PrefixMatch(g).numpy(), out["prefix_masked"])
+        assert np.array_equal(searcher.ReverseRollSlideWindowMatch(g, sw_size=5).numpy(), out["sw5"])
         results[rank] = out
     finally:
         dist.destroy_process_group()
