@@ -608,7 +608,7 @@ def main_window(args, rank, world):
 
     # ---- index content: root blocks (this rank hashes a slice of the roots), then request blocks up to the quota
     backend = CudaShardBackend(2 * index_keys // world + 1024, device)
-    searcher = ShardedMetaSearcher(backend) if world > 1 else None
+    searcher = ShardedMetaSearcher(backend, mode=args.shard_mode) if world > 1 else None
     local_index = BatchMetaSearcher(backend.index)
 
     def insert(keys):
@@ -642,6 +642,8 @@ def main_window(args, rank, world):
 
     def step():
         keys = GenKeyVectorBatch(w["toks"], d_off, bs, d_ko, n_keys, out=d_keys)
+        if world > 1 and args.shard_mode == "peer":  # every key is probed at its owner over NVLink: no collective
+            return searcher.PrefixMatch(keys, d_ko), searcher.ReverseRollSlideWindowMatch(keys, d_ko, sw)
         if world > 1:
             g = searcher.Gather(keys, d_ko)  # one exchange of the keys serves both queries
             return searcher.PrefixMatch(g), searcher.ReverseRollSlideWindowMatch(g, sw_size=sw)
@@ -695,14 +697,19 @@ def main_window(args, rank, world):
                 "dtype": "int64", "data": "synthetic",
                 "config": {"workload": "%d requests, lengths log-uniform 256-131072 tokens, block 16, Zipf(1.1) prefix "
                                        "sharing over 1000 roots, window 256 blocks, index of %d keys split by hash "
-                                       "range over %d GPU(s); hash + prefix match + sliding-window match per step"
-                                       % (n_req_total, int(total_stored), world),
+                                       "range over %d GPU(s)%s; hash + prefix match + sliding-window match per step"
+                                       % (n_req_total, int(total_stored), world,
+                                          "" if world == 1 else (", shards probed over NVLink peer loads"
+                                                                 if args.shard_mode == "peer" else
+                                                                 ", all-gather of keys + min/max all-reduce")),
                            "token_blocks": int(total_keys), "longest_request_tokens": longest,
                            "requests_with_prefix_hit": int(n_prefix_hits), "requests_with_window": int(n_windows),
                            "parity_sample_ok": parity},
                 "gpu_launches": (3 if world == 1 else 4) * args.steps * world}
         print(json.dumps(line))
     if world > 1:
+        if args.shard_mode == "peer":
+            searcher.detach_peers()
         dist.destroy_process_group()
 
 
@@ -715,6 +722,8 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c1", "c4"])
     ap.add_argument("--n-requests", type=int, default=0, help="c4: override the number of requests")
     ap.add_argument("--index-keys", type=int, default=0, help="c4: override the number of indexed keys")
+    ap.add_argument("--shard-mode", default="peer", choices=["peer", "exchange"],
+                    help="c4 on several GPUs: probe remote shards over NVLink, or exchange keys and reduce results")
     ap.add_argument("--no-prefix", action="store_true", help="skip the prefix-match side measurement")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-staging leg (profiling runs)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")

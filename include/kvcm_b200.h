@@ -326,6 +326,29 @@ KVCM_API int32_t kvcm_b200_batch_get_sharded(kvcm_b200_index_t *index, const int
 KVCM_API int32_t kvcm_b200_match_sw_from_flags(const uint8_t *d_flags, const int64_t *d_key_off, int32_t n_req,
                                                int32_t sw_blocks, int32_t *d_base_out, kvcm_stream_t stream);
 
+/* Peer-attached shards: the collective-free way to query a sharded index on one NVLink / NVSwitch
+ * box.  Every GPU exports its shard once; each GPU maps the others' shards (CUDA IPC, peer access)
+ * and attaches them to its own handle.  From then on match_prefix, match_sw, batch_get and
+ * index_lookup on that handle resolve every key in the table of the shard that owns it, with plain
+ * 16-byte peer loads over NVLink - a rank matches its own requests against the whole index without
+ * any exchange step.  Writes (upsert_sharded, erase, clear) stay local to the shard; after a batch
+ * of writes the ranks synchronise their streams and meet at a host barrier before anyone queries.
+ * A process must detach (or destroy the index) before a peer frees its shard, and must not leave
+ * while peers may still be probing its memory.  attach_local_peers is the same for shards that live
+ * in one process (several GPUs driven by one process with peer access enabled, or tests). */
+typedef struct kvcm_b200_index_export {
+    uint8_t ipc_handle[64];
+    uint64_t n_slots;
+    int32_t device;
+    int32_t reserved_;
+} kvcm_b200_index_export_t;
+KVCM_API int32_t kvcm_b200_index_export(kvcm_b200_index_t *index, kvcm_b200_index_export_t *out);
+KVCM_API int32_t kvcm_b200_index_attach_peers(kvcm_b200_index_t *index, int32_t shard_count, int32_t shard_rank,
+                                              const kvcm_b200_index_export_t *exports);
+KVCM_API int32_t kvcm_b200_index_attach_local_peers(kvcm_b200_index_t *index, int32_t shard_count,
+                                                    int32_t shard_rank, kvcm_b200_index_t *const *shards);
+KVCM_API int32_t kvcm_b200_index_detach_peers(kvcm_b200_index_t *index);
+
 /* ------------------------------------------------------------------------------------------
  * (2c) Optimizer trace replay, no eviction.
  *

@@ -41,6 +41,10 @@ class Seg(ctypes.Structure):
     _fields_ = [("dst", _vp), ("src", _vp), ("bytes", _u64)]
 
 
+class IndexExport(ctypes.Structure):
+    _fields_ = [("ipc_handle", ctypes.c_uint8 * 64), ("n_slots", _u64), ("device", _i32), ("reserved_", _i32)]
+
+
 class Iov(ctypes.Structure):
     _fields_ = [("type", ctypes.c_uint8), ("ignore", ctypes.c_uint8), ("pad_", ctypes.c_uint8 * 6), ("base", _vp),
                 ("size", _u64)]
@@ -85,6 +89,10 @@ SIGNATURES = {
     "kvcm_b200_match_prefix_sharded": [_vp, _vp, _vp, _i32, _vp, _vp, _u32, _i32, _i32, _vp, _vp],
     "kvcm_b200_batch_get_sharded": [_vp, _vp, _i64, _u32, _i32, _i32, _vp, _vp],
     "kvcm_b200_match_sw_from_flags": [_vp, _vp, _i32, _i32, _vp, _vp],
+    "kvcm_b200_index_export": [_vp, _vp],
+    "kvcm_b200_index_attach_peers": [_vp, _i32, _i32, _vp],
+    "kvcm_b200_index_attach_local_peers": [_vp, _i32, _i32, _vp],
+    "kvcm_b200_index_detach_peers": [_vp],
     "kvcm_b200_replay_workspace_bytes": [_i64],
     "kvcm_b200_replay": [_vp, _vp, _vp, _vp, _i32, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp],
     "kvcm_b200_replay_noalloc": [_vp, _vp, _vp, _vp, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _vp],

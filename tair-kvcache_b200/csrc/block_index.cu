@@ -12,14 +12,23 @@
 // expected chain is under two slots, so a lookup costs one or two 32-byte sectors.  Two key
 // values are reserved as EMPTY and TOMBSTONE markers; real keys with those values live in two
 // side cells, so every int64 stays a legal key.  All loops are bounded by the slot count.
+#include <cstring>
+
 #include "kvcm_common.cuh"
 
 struct kvcm_b200_index {
+    void *base;         // one allocation: 256-byte header (the cells) followed by the slots
     ulonglong2 *slots;
-    uint64_t *cells;  // [0],[1]: values of the two reserved keys; [2]: live key count
+    uint64_t *cells;    // [0],[1]: values of the two reserved keys; [2]: live key count
     uint64_t n_slots;
     uint64_t max_live;
     int device;
+    // Set by attach_peers: device array of the views of all shards of one logical index (this
+    // one included), and the mappings opened from other processes.
+    void *d_peer_views;
+    uint32_t peer_count;
+    void *opened[64];
+    int n_opened;
 };
 
 namespace kvcm {
@@ -28,12 +37,17 @@ namespace {
 constexpr uint64_t kEmptyKey = 0x8000000000000000ull;
 constexpr uint64_t kTombKey = 0x8000000000000001ull;
 constexpr int kMatchWarps = 8;
+constexpr size_t kIndexHeaderBytes = 256;
 
 struct IndexView {
     ulonglong2 *slots;
     uint64_t *cells;
     uint64_t mask;
     uint64_t max_live;
+    // Shards of the logical index this table is part of (peer GPUs' tables mapped into this
+    // address space), indexed by owner; null / 0 when the table stands alone.
+    const IndexView *peers;
+    uint32_t peer_count;
 };
 
 __host__ __device__ __forceinline__ uint64_t Mix(uint64_t k) {
@@ -61,16 +75,34 @@ __device__ __forceinline__ ulonglong2 LoadSlot(const ulonglong2 *p) {
     return s;
 }
 
-// Value word of a key, 0 when absent (MetaIndexer::Get -> EC_NOENT).
+__device__ __forceinline__ uint32_t OwnerOf(uint64_t key, uint32_t shards) {
+    return static_cast<uint32_t>(__umul64hi(Mix(key), shards));
+}
+
+// Value word of a key in one table, 0 when absent (MetaIndexer::Get -> EC_NOENT).
+__device__ __forceinline__ uint64_t LookupIn(const ulonglong2 *slots, const uint64_t *cells, uint64_t mask,
+                                             uint64_t key);
+
+// Value word of a key.  With peers attached the probe goes to the owner shard's table, which may
+// live in another GPU's memory: plain 16-byte peer loads over NVLink, no collective.
 __device__ __forceinline__ uint64_t Lookup(const IndexView &ix, uint64_t key) {
-    if (key == kEmptyKey) return ix.cells[0];
-    if (key == kTombKey) return ix.cells[1];
-    uint64_t slot = Mix(key) & ix.mask;
-    for (uint64_t probe = 0; probe <= ix.mask; ++probe) {
-        const ulonglong2 s = LoadSlot(ix.slots + slot);
+    if (ix.peer_count > 1) {
+        const IndexView &owner = ix.peers[OwnerOf(key, ix.peer_count)];
+        return LookupIn(owner.slots, owner.cells, owner.mask, key);
+    }
+    return LookupIn(ix.slots, ix.cells, ix.mask, key);
+}
+
+__device__ __forceinline__ uint64_t LookupIn(const ulonglong2 *slots, const uint64_t *cells, uint64_t mask,
+                                             uint64_t key) {
+    if (key == kEmptyKey) return cells[0];
+    if (key == kTombKey) return cells[1];
+    uint64_t slot = Mix(key) & mask;
+    for (uint64_t probe = 0; probe <= mask; ++probe) {
+        const ulonglong2 s = LoadSlot(slots + slot);
         if (s.x == key) return s.y;
         if (s.x == kEmptyKey) return 0;
-        slot = (slot + 1) & ix.mask;
+        slot = (slot + 1) & mask;
     }
     return 0;
 }
@@ -316,12 +348,23 @@ __global__ void __launch_bounds__(kMatchWarps * 32)
     if (lane == 0) base_out[req] = static_cast<int32_t>(found);
 }
 
+// View for the matchers: probes follow the attached peers.
 IndexView View(const kvcm_b200_index *ix) {
     IndexView v;
     v.slots = ix->slots;
     v.cells = ix->cells;
     v.mask = ix->n_slots - 1;
     v.max_live = ix->max_live;
+    v.peers = static_cast<const IndexView *>(ix->d_peer_views);
+    v.peer_count = ix->peer_count;
+    return v;
+}
+
+// View of this table alone, for the kernels that write it.
+IndexView LocalView(const kvcm_b200_index *ix) {
+    IndexView v = View(ix);
+    v.peers = nullptr;
+    v.peer_count = 0;
     return v;
 }
 
@@ -343,17 +386,16 @@ int32_t kvcm_b200_index_create(int64_t max_keys, kvcm_b200_index_t **out) {
     ix->n_slots = n_slots;
     ix->max_live = n_slots - n_slots / 8;  // the matchers rely on at least one EMPTY slot per chain
     cudaGetDevice(&ix->device);
-    if (cudaMalloc(&ix->slots, n_slots * sizeof(ulonglong2)) != cudaSuccess ||
-        cudaMalloc(&ix->cells, 3 * sizeof(uint64_t)) != cudaSuccess) {
+    if (cudaMalloc(&ix->base, kvcm::kIndexHeaderBytes + n_slots * sizeof(ulonglong2)) != cudaSuccess) {
         cudaGetLastError();
-        if (ix->slots) cudaFree(ix->slots);
         delete ix;
         return KVCM_EC_NOSPC;
     }
+    ix->cells = static_cast<uint64_t *>(ix->base);
+    ix->slots = reinterpret_cast<ulonglong2 *>(static_cast<uint8_t *>(ix->base) + kvcm::kIndexHeaderBytes);
     const int32_t rc = kvcm_b200_index_clear(ix, nullptr);
     if (rc != KVCM_OK || cudaStreamSynchronize(nullptr) != cudaSuccess) {
-        cudaFree(ix->slots);
-        cudaFree(ix->cells);
+        cudaFree(ix->base);
         delete ix;
         return KVCM_ER_CUDA_STREAM_SYNCHRONIZE_ERROR;
     }
@@ -361,18 +403,102 @@ int32_t kvcm_b200_index_create(int64_t max_keys, kvcm_b200_index_t **out) {
     return KVCM_OK;
 }
 
+int32_t kvcm_b200_index_detach_peers(kvcm_b200_index_t *ix) {
+    if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (ix->d_peer_views != nullptr) cudaFree(ix->d_peer_views);
+    ix->d_peer_views = nullptr;
+    ix->peer_count = 0;
+    for (int i = 0; i < ix->n_opened; ++i) cudaIpcCloseMemHandle(ix->opened[i]);
+    ix->n_opened = 0;
+    cudaGetLastError();
+    return KVCM_OK;
+}
+
 int32_t kvcm_b200_index_destroy(kvcm_b200_index_t *ix) {
     if (ix == nullptr) return KVCM_OK;
-    cudaFree(ix->slots);
-    cudaFree(ix->cells);
+    kvcm_b200_index_detach_peers(ix);
+    cudaFree(ix->base);
     delete ix;
     return KVCM_OK;
+}
+
+int32_t kvcm_b200_index_export(kvcm_b200_index_t *ix, kvcm_b200_index_export_t *out) {
+    if (ix == nullptr || out == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    static_assert(sizeof(cudaIpcMemHandle_t) <= sizeof(out->ipc_handle), "IPC handle does not fit");
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, ix->base) != cudaSuccess) {
+        cudaGetLastError();
+        return KVCM_EC_ERROR;
+    }
+    memset(out, 0, sizeof(*out));
+    memcpy(out->ipc_handle, &h, sizeof(h));
+    out->n_slots = ix->n_slots;
+    out->device = ix->device;
+    return KVCM_OK;
+}
+
+// Uploads the table of shard views; shard_rank's own entry is the local table.
+static int32_t InstallPeerViews(kvcm_b200_index_t *ix, int32_t shard_count, const kvcm::IndexView *views) {
+    void *d = nullptr;
+    if (cudaMalloc(&d, sizeof(kvcm::IndexView) * shard_count) != cudaSuccess ||
+        cudaMemcpy(d, views, sizeof(kvcm::IndexView) * shard_count, cudaMemcpyHostToDevice) != cudaSuccess) {
+        cudaGetLastError();
+        if (d != nullptr) cudaFree(d);
+        return KVCM_EC_NOSPC;
+    }
+    ix->d_peer_views = d;
+    ix->peer_count = static_cast<uint32_t>(shard_count);
+    return KVCM_OK;
+}
+
+int32_t kvcm_b200_index_attach_peers(kvcm_b200_index_t *ix, int32_t shard_count, int32_t shard_rank,
+                                     const kvcm_b200_index_export_t *exports) {
+    if (ix == nullptr || exports == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (shard_count < 1 || shard_count > 64 || shard_rank < 0 || shard_rank >= shard_count) return KVCM_EC_BADARGS;
+    kvcm_b200_index_detach_peers(ix);
+    kvcm::IndexView views[64];
+    for (int32_t r = 0; r < shard_count; ++r) {
+        kvcm::IndexView &v = views[r];
+        v.peers = nullptr;
+        v.peer_count = 0;
+        v.max_live = 0;
+        if (r == shard_rank) {
+            v = kvcm::LocalView(ix);
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, exports[r].ipc_handle, sizeof(h));
+        void *base = nullptr;
+        if (cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            cudaGetLastError();
+            kvcm_b200_index_detach_peers(ix);
+            return KVCM_EC_ERROR;
+        }
+        ix->opened[ix->n_opened++] = base;
+        v.cells = static_cast<uint64_t *>(base);
+        v.slots = reinterpret_cast<ulonglong2 *>(static_cast<uint8_t *>(base) + kvcm::kIndexHeaderBytes);
+        v.mask = exports[r].n_slots - 1;
+    }
+    return InstallPeerViews(ix, shard_count, views);
+}
+
+int32_t kvcm_b200_index_attach_local_peers(kvcm_b200_index_t *ix, int32_t shard_count, int32_t shard_rank,
+                                           kvcm_b200_index_t *const *shards) {
+    if (ix == nullptr || shards == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (shard_count < 1 || shard_count > 64 || shard_rank < 0 || shard_rank >= shard_count) return KVCM_EC_BADARGS;
+    kvcm_b200_index_detach_peers(ix);
+    kvcm::IndexView views[64];
+    for (int32_t r = 0; r < shard_count; ++r) {
+        if (shards[r] == nullptr) return KVCM_ER_INVALID_ADDRESS;
+        views[r] = kvcm::LocalView(shards[r]);
+    }
+    return InstallPeerViews(ix, shard_count, views);
 }
 
 int32_t kvcm_b200_index_clear(kvcm_b200_index_t *ix, kvcm_stream_t stream) {
     if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
     const unsigned grid = static_cast<unsigned>(kvcm::GetDeviceInfo().sm_count * 8);
-    kvcm::ClearKernel<<<grid, 256, 0, kvcm::AsStream(stream)>>>(kvcm::View(ix));
+    kvcm::ClearKernel<<<grid, 256, 0, kvcm::AsStream(stream)>>>(kvcm::LocalView(ix));
     return kvcm::LaunchStatus();
 }
 
@@ -398,7 +524,7 @@ int32_t kvcm_b200_index_upsert(kvcm_b200_index_t *ix, const int64_t *d_keys, con
     if (n == 0) return KVCM_OK;
     if (d_keys == nullptr) return KVCM_ER_INVALID_ADDRESS;
     kvcm::UpsertKernel<<<kvcm::GridFor(n, 256), 256, 0, kvcm::AsStream(stream)>>>(
-        kvcm::View(ix), d_keys, d_values, uniform_value, n, kvcm::Shard{1, 0}, d_status);
+        kvcm::LocalView(ix), d_keys, d_values, uniform_value, n, kvcm::Shard{1, 0}, d_status);
     return kvcm::LaunchStatus();
 }
 
@@ -410,7 +536,7 @@ int32_t kvcm_b200_index_upsert_sharded(kvcm_b200_index_t *ix, const int64_t *d_k
     if (n == 0) return KVCM_OK;
     if (d_keys == nullptr) return KVCM_ER_INVALID_ADDRESS;
     kvcm::UpsertKernel<<<kvcm::GridFor(n, 256), 256, 0, kvcm::AsStream(stream)>>>(
-        kvcm::View(ix), d_keys, d_values, uniform_value, n,
+        kvcm::LocalView(ix), d_keys, d_values, uniform_value, n,
         kvcm::Shard{static_cast<uint32_t>(shard_count), static_cast<uint32_t>(shard_rank)}, d_status);
     return kvcm::LaunchStatus();
 }
@@ -420,7 +546,7 @@ int32_t kvcm_b200_index_erase(kvcm_b200_index_t *ix, const int64_t *d_keys, int6
     if (n < 0) return KVCM_EC_BADARGS;
     if (n == 0) return KVCM_OK;
     if (d_keys == nullptr) return KVCM_ER_INVALID_ADDRESS;
-    kvcm::EraseKernel<<<kvcm::GridFor(n, 256), 256, 0, kvcm::AsStream(stream)>>>(kvcm::View(ix), d_keys, n);
+    kvcm::EraseKernel<<<kvcm::GridFor(n, 256), 256, 0, kvcm::AsStream(stream)>>>(kvcm::LocalView(ix), d_keys, n);
     return kvcm::LaunchStatus();
 }
 

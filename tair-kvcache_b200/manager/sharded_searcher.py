@@ -72,6 +72,13 @@ class CudaShardBackend:
                    self.index._s())
         return out
 
+    def sw_direct(self, keys, key_off, sw):
+        n_req = key_off.numel() - 1
+        out = torch.empty(n_req, dtype=torch.int32, device=self.device)
+        _cabi.call("kvcm_b200_match_sw", self.index.handle, keys.data_ptr(), key_off.data_ptr(), n_req, sw,
+                   self.avail_mask, out.data_ptr(), self.index._s())
+        return out
+
 
 class GatheredRequests:
     """All ranks' requests after the exchange step, reusable for several queries on the same keys."""
@@ -81,14 +88,48 @@ class GatheredRequests:
 
 
 class ShardedMetaSearcher:
-    """Collective front end: every rank of `group` calls each method with its own requests."""
+    """Collective front end: every rank of `group` calls each method with its own requests.
 
-    def __init__(self, backend, group: Optional[dist.ProcessGroup] = None):
+    mode "exchange": one all-gather of keys and one min / max all-reduce per query (works on any backend).
+    mode "peer":     after `attach_peers()` every rank probes the owner shard of each key directly over NVLink
+                     (CUDA IPC mappings, plain peer loads): queries need no collective at all; only writes do."""
+
+    def __init__(self, backend, group: Optional[dist.ProcessGroup] = None, mode: str = "exchange"):
         self.backend = backend
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         self.device = backend.device
+        self.mode = mode
+        if mode == "peer":
+            self.attach_peers()
+
+    def attach_peers(self) -> None:
+        """Exchange the shards' IPC handles and map every shard into this process (one-time set-up)."""
+        import ctypes
+        exp = _cabi.IndexExport()
+        _cabi.call("kvcm_b200_index_export", self.backend.index.handle, ctypes.byref(exp))
+        blobs = [None] * self.world
+        dist.all_gather_object(blobs, bytes(exp), group=self.group)
+        arr = (_cabi.IndexExport * self.world)()
+        for r, blob in enumerate(blobs):
+            ctypes.memmove(ctypes.addressof(arr[r]), blob, ctypes.sizeof(_cabi.IndexExport))
+        _cabi.bind_device(self.device.index)
+        _cabi.call("kvcm_b200_index_attach_peers", self.backend.index.handle, self.world, self.rank, arr)
+        self.mode = "peer"
+
+    def detach_peers(self) -> None:
+        """Unmap the peers' shards; every rank calls it (after a barrier) before any shard is freed."""
+        dist.barrier(group=self.group)
+        _cabi.call("kvcm_b200_index_detach_peers", self.backend.index.handle)
+        dist.barrier(group=self.group)
+        self.mode = "exchange"
+
+    def _publish_writes(self) -> None:
+        """Writes of all shards become visible to every rank's next query."""
+        if self.mode == "peer":
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)
 
     # ---- exchange -----------------------------------------------------------------------------
     def _gather_requests(self, keys: torch.Tensor, key_off: torch.Tensor, per_req: Optional[torch.Tensor]
@@ -138,6 +179,7 @@ class ShardedMetaSearcher:
     def upsert(self, keys: torch.Tensor, value_word: int) -> None:
         """Every rank contributes keys; each key is stored on the shard that owns it."""
         self.backend.upsert_owned(self._gather_keys(keys.contiguous()), value_word, self.world, self.rank)
+        self._publish_writes()
 
     def Gather(self, keys: torch.Tensor, key_off: torch.Tensor, mask_off: Optional[torch.Tensor] = None
                ) -> GatheredRequests:
@@ -148,6 +190,8 @@ class ShardedMetaSearcher:
 
     def PrefixMatch(self, keys, key_off: Optional[torch.Tensor] = None, mask_off: Optional[torch.Tensor] = None
                     ) -> torch.Tensor:
+        if self.mode == "peer":  # the attached handle resolves every key at its owner: a purely local call
+            return self.backend.prefix_owned(keys.contiguous(), key_off.contiguous(), mask_off, 1, 0)
         g = keys if isinstance(keys, GatheredRequests) else self.Gather(keys, key_off, mask_off)
         lens = self.backend.prefix_owned(g.keys, g.csr, g.per_req, self.world, self.rank)
         dist.all_reduce(lens, op=dist.ReduceOp.MIN, group=self.group)
@@ -157,6 +201,8 @@ class ShardedMetaSearcher:
                                     ) -> torch.Tensor:
         if sw_size <= 0:
             raise _cabi.KvcmError(_cabi.KVCM_EC_BADARGS, "ReverseRollSlideWindowMatch")
+        if self.mode == "peer":
+            return self.backend.sw_direct(keys.contiguous(), key_off.contiguous(), sw_size)
         g = keys if isinstance(keys, GatheredRequests) else self.Gather(keys, key_off, None)
         flags = self.backend.servable_flags(g.keys, self.world, self.rank)
         dist.all_reduce(flags, op=dist.ReduceOp.MAX, group=self.group)

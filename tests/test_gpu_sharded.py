@@ -64,6 +64,41 @@ def test_shard_kernels_combine_to_the_unsharded_answer_on_one_gpu():
             assert np.array_equal(base.cpu().numpy(), full.sw_match_batch(keys, off, sw))
 
 
+def test_locally_attached_shards_answer_like_one_index():
+    """Three shards in one process, attached to each other: every handle resolves each key at its owner."""
+    import ctypes
+    from tair_kvcache_b200.manager import BatchMetaSearcher
+    present, reqs = _world(17)
+    keys, off, mask = reqs[0]
+    full = oracle.Index()
+    full.put_uniform(present)
+    dk, doff, dmask = (torch.from_numpy(a).to(DEV) for a in (keys, off, mask))
+    count = 3
+    shards = [CudaShardBackend(len(present), torch.device(DEV)) for _ in range(count)]
+    for r, sh in enumerate(shards):
+        sh.upsert_owned(torch.from_numpy(present).to(DEV), encode_locations([(3, 4)]), count, r)
+    handles = (ctypes.c_void_p * count)(*[sh.index.handle.value for sh in shards])
+    for r, sh in enumerate(shards):
+        _cabi.call("kvcm_b200_index_attach_local_peers", sh.index.handle, count, r, handles)
+    for sh in shards:
+        ms = BatchMetaSearcher(sh.index)
+        assert np.array_equal(ms.PrefixMatch(dk, doff).cpu().numpy(), full.prefix_match_batch(keys, off))
+        assert np.array_equal(ms.PrefixMatch(dk, doff, dmask).cpu().numpy(), full.prefix_match_batch(keys, off, mask))
+        assert np.array_equal(ms.ReverseRollSlideWindowMatch(dk, doff, 4).cpu().numpy(),
+                              full.sw_match_batch(keys, off, 4))
+        assert np.array_equal(ms.BatchGet(dk).cpu().numpy(), full.batch_get(keys))
+    # writes stay local: a key stored through shard 0 is seen by all once it lands in its owner's table
+    new = torch.tensor([123456789], dtype=torch.int64, device=DEV)
+    owner = int(shard_of_keys(new.cpu().numpy(), count)[0])
+    shards[owner].upsert_owned(new, encode_locations([(3, 4)]), count, owner)
+    torch.cuda.synchronize()
+    for sh in shards:
+        assert sh.index.lookup(new).item() != 0
+    for sh in shards:
+        _cabi.call("kvcm_b200_index_detach_peers", sh.index.handle)
+    assert sum(int(sh.index.lookup(new).item() != 0) for sh in shards) == 1
+
+
 def test_sw_from_flags_equals_match_sw_on_the_same_index():
     present, reqs = _world(8)
     keys, off, _ = reqs[1]
@@ -77,7 +112,7 @@ def test_sw_from_flags_equals_match_sw_on_the_same_index():
         assert torch.equal(a, b)
 
 
-def _rank_main(rank, port, results):
+def _rank_main(rank, port, results, mode):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     dev = torch.device("cuda", rank)
@@ -85,7 +120,7 @@ def _rank_main(rank, port, results):
     dist.init_process_group("nccl", rank=rank, world_size=2, device_id=dev)
     try:
         present, reqs = _world(9)
-        searcher = ShardedMetaSearcher(CudaShardBackend(len(present), dev))
+        searcher = ShardedMetaSearcher(CudaShardBackend(len(present), dev), mode=mode)
         searcher.upsert(torch.from_numpy(present[rank::2].copy()).to(dev), encode_locations([(3, 4)]))
         keys, off, mask = (torch.from_numpy(a).to(dev) for a in reqs[rank])
         out = {
@@ -96,19 +131,22 @@ def _rank_main(rank, port, results):
         }
         torch.cuda.synchronize()
         results[rank] = out
+        if mode == "peer":
+            searcher.detach_peers()  # nobody frees a shard while a peer still maps it
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_nccl_ranks_match_the_unsharded_oracle():
+@pytest.mark.parametrize("mode", ["exchange", "peer"])
+def test_two_nccl_ranks_match_the_unsharded_oracle(mode):
     import torch.multiprocessing as mp
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     with mp.Manager() as m:
         results = m.dict()
-        mp.spawn(_rank_main, args=(port, results), nprocs=2, join=True)
+        mp.spawn(_rank_main, args=(port, results, mode), nprocs=2, join=True)
         results = dict(results)
     present, reqs = _world(9)
     full = oracle.Index()
