@@ -586,7 +586,7 @@ def main_window(args, rank, world):
 
     import tair_kvcache_b200  # noqa: F401
     from tair_kvcache_b200.manager import (BatchMetaSearcher, CudaShardBackend, GenKeyVectorBatch,
-                                           ShardedMetaSearcher, encode_locations, key_offsets)
+                                           ShardedMetaSearcher, encode_locations, key_offsets, length_order)
 
     local = int(os.environ.get("LOCAL_RANK", 0))
     device = torch.device("cuda", local)
@@ -603,7 +603,7 @@ def main_window(args, rank, world):
     def hash_csr(tokens, off_np):
         ko = key_offsets(off_np, bs)
         keys = GenKeyVectorBatch(tokens, torch.from_numpy(off_np).to(device), bs, torch.from_numpy(ko).to(device),
-                                 int(ko[-1]))
+                                 int(ko[-1]), order=torch.from_numpy(length_order(off_np)).to(device))
         return keys, ko
 
     # ---- index content: root blocks (this rank hashes a slice of the roots), then request blocks up to the quota
@@ -639,9 +639,10 @@ def main_window(args, rank, world):
     d_ko = torch.from_numpy(req_ko).to(device)
     n_keys = int(req_ko[-1])
     d_keys = torch.empty(max(n_keys, 1), dtype=torch.int64, device=device)
+    d_order = torch.from_numpy(length_order(w["off"])).to(device)  # ragged lengths: longest chains first
 
     def step():
-        keys = GenKeyVectorBatch(w["toks"], d_off, bs, d_ko, n_keys, out=d_keys)
+        keys = GenKeyVectorBatch(w["toks"], d_off, bs, d_ko, n_keys, out=d_keys, order=d_order)
         if world > 1 and args.shard_mode == "peer":  # every key is probed at its owner over NVLink: no collective
             return searcher.PrefixMatch(keys, d_ko), searcher.ReverseRollSlideWindowMatch(keys, d_ko, sw)
         if world > 1:

@@ -209,14 +209,22 @@ KVCM_API int32_t kvcm_b200_iov_crc(const kvcm_b200_seg_t *d_segs, int32_t n_segs
  * Request r owns tokens[tok_off[r], tok_off[r+1]) and writes floor(len/block_size) keys at
  * d_keys[key_off[r] ...]; the hash state starts at 0 per request and is carried across blocks;
  * a trailing partial block is dropped.  u32 tokens are zero-extended (token ids are non-negative).
- * n_tokens_total is the extent of d_tokens (reads stay inside it).
+ * n_tokens_total is the extent of d_tokens (reads stay inside it).  d_tokens must be 16-byte aligned.
+ * d_req_order (optional, NULL = request order) is a permutation of [0, n_req) saying which request
+ * each lane takes; listing requests longest first (kvcm_b200_length_order) groups chains of similar
+ * length into one warp and starts the longest chains first, which matters for ragged batches.  The
+ * keys written do not depend on it.
  * ---------------------------------------------------------------------------------------- */
 KVCM_API int32_t kvcm_b200_hash_blocks_u32(const uint32_t *d_tokens, int64_t n_tokens_total, const int64_t *d_tok_off,
                                            int32_t n_req, int32_t block_size, int64_t *d_keys,
-                                           const int64_t *d_key_off, kvcm_stream_t stream);
+                                           const int64_t *d_key_off, const int32_t *d_req_order,
+                                           kvcm_stream_t stream);
 KVCM_API int32_t kvcm_b200_hash_blocks_i64(const int64_t *d_tokens, int64_t n_tokens_total, const int64_t *d_tok_off,
                                            int32_t n_req, int32_t block_size, int64_t *d_keys,
-                                           const int64_t *d_key_off, kvcm_stream_t stream);
+                                           const int64_t *d_key_off, const int32_t *d_req_order,
+                                           kvcm_stream_t stream);
+/* Host-only helper: h_order_out = requests sorted by token count, longest first (stable). */
+KVCM_API int32_t kvcm_b200_length_order(const int64_t *h_tok_off, int32_t n_req, int32_t *h_order_out);
 /* Host-only helper: key_off[r] = sum_{q<r} floor((tok_off[q+1]-tok_off[q]) / block_size); n_req+1 entries. */
 KVCM_API int32_t kvcm_b200_key_offsets(const int64_t *h_tok_off, int32_t n_req, int32_t block_size,
                                        int64_t *h_key_off);

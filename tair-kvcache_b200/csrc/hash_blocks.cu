@@ -14,6 +14,9 @@
 // the token array's extent, so nothing outside the caller's buffer is read) and consumes a
 // stage with four conflict-free 128-bit shared loads.  The ring keeps kStages-1 stages (about
 // a hundred tokens) in flight per lane, which hides DRAM latency behind the chain itself.
+#include <algorithm>
+#include <vector>
+
 #include "kvcm_common.cuh"
 
 namespace kvcm {
@@ -76,7 +79,8 @@ template <typename T, bool kAligned>
 __global__ void __launch_bounds__(kMaxWarpsPerCta * 32)
     HashBlocksKernel(const T *__restrict__ tokens, int64_t n_tokens_total, const int64_t *__restrict__ tok_off,
                      int32_t n_req, int32_t block_size, int64_t *__restrict__ keys,
-                     const int64_t *__restrict__ key_off, uint32_t lanes_per_warp) {
+                     const int64_t *__restrict__ key_off, const int32_t *__restrict__ order,
+                     uint32_t lanes_per_warp) {
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr int kPerPiece = 16 / sizeof(T);
     constexpr int kPerStage = kStageBytes / sizeof(T);
@@ -84,8 +88,11 @@ __global__ void __launch_bounds__(kMaxWarpsPerCta * 32)
     const uint32_t lane = LaneId();
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t warps_per_cta = blockDim.x >> 5;
-    const int64_t req = (static_cast<int64_t>(blockIdx.x) * warps_per_cta + warp) * lanes_per_warp + lane;
-    const bool active = lane < lanes_per_warp && req < n_req;
+    const int64_t pos = (static_cast<int64_t>(blockIdx.x) * warps_per_cta + warp) * lanes_per_warp + lane;
+    const bool active = lane < lanes_per_warp && pos < n_req;
+    // `order` (optional) lists the requests longest first: lanes of one warp then walk chains of
+    // similar length, and the longest chains start first.
+    const int64_t req = active && order != nullptr ? order[pos] : pos;
 
     int64_t first_tok = 0, n_tok = 0, key_base = 0;
     if (active) {
@@ -203,7 +210,8 @@ __global__ void __launch_bounds__(kMaxWarpsPerCta * 32)
 
 template <typename T>
 int32_t LaunchHash(const T *d_tokens, int64_t n_tokens_total, const int64_t *d_tok_off, int32_t n_req,
-                   int32_t block_size, int64_t *d_keys, const int64_t *d_key_off, kvcm_stream_t stream) {
+                   int32_t block_size, int64_t *d_keys, const int64_t *d_key_off, const int32_t *d_order,
+                   kvcm_stream_t stream) {
     if (!HaveDevice()) return KVCM_ER_NO_DEVICE;
     if (n_req < 0 || block_size <= 0 || n_tokens_total < 0) return KVCM_ER_INVALID_PARAMS;
     if (n_req == 0) return KVCM_OK;
@@ -234,10 +242,10 @@ int32_t LaunchHash(const T *d_tokens, int64_t n_tokens_total, const int64_t *d_t
     constexpr int kPerStage = kStageBytes / sizeof(T);
     if (block_size % kPerStage == 0) {
         HashBlocksKernel<T, true><<<grid, threads, smem, AsStream(stream)>>>(
-            d_tokens, n_tokens_total, d_tok_off, n_req, block_size, d_keys, d_key_off, lanes_per_warp);
+            d_tokens, n_tokens_total, d_tok_off, n_req, block_size, d_keys, d_key_off, d_order, lanes_per_warp);
     } else {
         HashBlocksKernel<T, false><<<grid, threads, smem, AsStream(stream)>>>(
-            d_tokens, n_tokens_total, d_tok_off, n_req, block_size, d_keys, d_key_off, lanes_per_warp);
+            d_tokens, n_tokens_total, d_tok_off, n_req, block_size, d_keys, d_key_off, d_order, lanes_per_warp);
     }
     return LaunchStatus();
 }
@@ -249,16 +257,28 @@ extern "C" {
 
 int32_t kvcm_b200_hash_blocks_u32(const uint32_t *d_tokens, int64_t n_tokens_total, const int64_t *d_tok_off,
                                   int32_t n_req, int32_t block_size, int64_t *d_keys, const int64_t *d_key_off,
-                                  kvcm_stream_t stream) {
+                                  const int32_t *d_req_order, kvcm_stream_t stream) {
     return kvcm::LaunchHash<uint32_t>(d_tokens, n_tokens_total, d_tok_off, n_req, block_size, d_keys, d_key_off,
-                                      stream);
+                                      d_req_order, stream);
 }
 
 int32_t kvcm_b200_hash_blocks_i64(const int64_t *d_tokens, int64_t n_tokens_total, const int64_t *d_tok_off,
                                   int32_t n_req, int32_t block_size, int64_t *d_keys, const int64_t *d_key_off,
-                                  kvcm_stream_t stream) {
+                                  const int32_t *d_req_order, kvcm_stream_t stream) {
     return kvcm::LaunchHash<int64_t>(d_tokens, n_tokens_total, d_tok_off, n_req, block_size, d_keys, d_key_off,
-                                     stream);
+                                     d_req_order, stream);
+}
+
+int32_t kvcm_b200_length_order(const int64_t *h_tok_off, int32_t n_req, int32_t *h_order_out) {
+    if (h_tok_off == nullptr || h_order_out == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (n_req < 0) return KVCM_ER_INVALID_PARAMS;
+    std::vector<int32_t> idx(n_req);
+    for (int32_t r = 0; r < n_req; ++r) idx[r] = r;
+    std::stable_sort(idx.begin(), idx.end(), [&](int32_t a, int32_t b) {
+        return h_tok_off[a + 1] - h_tok_off[a] > h_tok_off[b + 1] - h_tok_off[b];
+    });
+    for (int32_t r = 0; r < n_req; ++r) h_order_out[r] = idx[r];
+    return KVCM_OK;
 }
 
 int32_t kvcm_b200_key_offsets(const int64_t *h_tok_off, int32_t n_req, int32_t block_size, int64_t *h_key_off) {

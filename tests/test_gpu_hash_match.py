@@ -79,13 +79,29 @@ def test_long_chain_and_many_requests():
     assert np.array_equal(got, want)
 
 
+def test_longest_first_order_gives_the_same_keys():
+    from tair_kvcache_b200.manager import length_order
+    rng = np.random.default_rng(12)
+    lens = np.exp(rng.uniform(np.log(16), np.log(20000), size=700)).astype(np.int64)
+    toks = rng.integers(0, 151936, size=int(lens.sum())).astype(np.uint32)
+    off = _csr(lens)
+    order = length_order(off)
+    assert sorted(order.tolist()) == list(range(700)) and (np.diff(lens[order]) <= 0).all()
+    ko = key_offsets(off, 16)
+    keys = GenKeyVectorBatch(torch.from_numpy(toks.view(np.int32)).to(DEV), torch.from_numpy(off).to(DEV), 16,
+                             torch.from_numpy(ko).to(DEV), int(ko[-1]), order=torch.from_numpy(order).to(DEV))
+    torch.cuda.synchronize()
+    want, _ = oracle.hash_blocks(toks, off, 16, threads=4)
+    assert np.array_equal(keys.cpu().numpy(), want)
+
+
 def test_hash_rejects_misaligned_token_buffer():
     t = torch.zeros(64, dtype=torch.int32, device=DEV)
     off = torch.tensor([0, 16], dtype=torch.int64, device=DEV)
     out = torch.zeros(4, dtype=torch.int64, device=DEV)
     _cabi.bind_device(0)
     rc = _cabi.lib().kvcm_b200_hash_blocks_u32(t.data_ptr() + 4, 32, off.data_ptr(), 1, 4, out.data_ptr(),
-                                               off.data_ptr(), None)
+                                               off.data_ptr(), None, None)
     assert rc == _cabi.KVCM_ER_INVALID_ADDRESS
 
 
