@@ -602,8 +602,9 @@ def main_window(args, rank, world):
 
     def hash_csr(tokens, off_np):
         ko = key_offsets(off_np, bs)
+        order, cap = length_order(off_np, with_residency=True)
         keys = GenKeyVectorBatch(tokens, torch.from_numpy(off_np).to(device), bs, torch.from_numpy(ko).to(device),
-                                 int(ko[-1]), order=torch.from_numpy(length_order(off_np)).to(device))
+                                 int(ko[-1]), order=torch.from_numpy(order).to(device), warps_per_sm=cap)
         return keys, ko
 
     # ---- index content: root blocks (this rank hashes a slice of the roots), then request blocks up to the quota
@@ -639,10 +640,11 @@ def main_window(args, rank, world):
     d_ko = torch.from_numpy(req_ko).to(device)
     n_keys = int(req_ko[-1])
     d_keys = torch.empty(max(n_keys, 1), dtype=torch.int64, device=device)
-    d_order = torch.from_numpy(length_order(w["off"])).to(device)  # ragged lengths: longest chains first
+    order_np, residency = length_order(w["off"], with_residency=True)  # ragged lengths: longest chains first
+    d_order = torch.from_numpy(order_np).to(device)
 
     def step():
-        keys = GenKeyVectorBatch(w["toks"], d_off, bs, d_ko, n_keys, out=d_keys, order=d_order)
+        keys = GenKeyVectorBatch(w["toks"], d_off, bs, d_ko, n_keys, out=d_keys, order=d_order, warps_per_sm=residency)
         if world > 1 and args.shard_mode == "peer":  # every key is probed at its owner over NVLink: no collective
             return searcher.PrefixMatch(keys, d_ko), searcher.ReverseRollSlideWindowMatch(keys, d_ko, sw)
         if world > 1:
@@ -664,6 +666,23 @@ def main_window(args, rank, world):
     if world > 1:
         dist.barrier()
     ms = e0.elapsed_time(e1)
+    # where a step goes (one extra untimed step, phases bracketed by events)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    ev[0].record()
+    keys = GenKeyVectorBatch(w["toks"], d_off, bs, d_ko, n_keys, out=d_keys, order=d_order, warps_per_sm=residency)
+    ev[1].record()
+    if world > 1:
+        searcher.PrefixMatch(keys, d_ko)
+        ev[2].record()
+        searcher.ReverseRollSlideWindowMatch(keys, d_ko, sw)
+    else:
+        local_index.PrefixMatch(keys, d_ko)
+        ev[2].record()
+        local_index.ReverseRollSlideWindowMatch(keys, d_ko, sw)
+    ev[3].record()
+    torch.cuda.synchronize(device)
+    phase_ms = {"hash": ev[0].elapsed_time(ev[1]), "prefix_match": ev[1].elapsed_time(ev[2]),
+                "window_match": ev[2].elapsed_time(ev[3])}
     stats = torch.tensor([ms, float(n_keys), float(stored), float((prefix > 0).sum()), float((window >= 0).sum())],
                          dtype=torch.float64, device=device)
     if world > 1:
@@ -705,7 +724,7 @@ def main_window(args, rank, world):
                                                                  ", all-gather of keys + min/max all-reduce")),
                            "token_blocks": int(total_keys), "longest_request_tokens": longest,
                            "requests_with_prefix_hit": int(n_prefix_hits), "requests_with_window": int(n_windows),
-                           "parity_sample_ok": parity},
+                           "parity_sample_ok": parity, "phase_ms_rank0": phase_ms},
                 "gpu_launches": (3 if world == 1 else 4) * args.steps * world}
         print(json.dumps(line))
     if world > 1:

@@ -212,19 +212,23 @@ KVCM_API int32_t kvcm_b200_iov_crc(const kvcm_b200_seg_t *d_segs, int32_t n_segs
  * n_tokens_total is the extent of d_tokens (reads stay inside it).  d_tokens must be 16-byte aligned.
  * d_req_order (optional, NULL = request order) is a permutation of [0, n_req) saying which request
  * each lane takes; listing requests longest first (kvcm_b200_length_order) groups chains of similar
- * length into one warp and starts the longest chains first, which matters for ragged batches.  The
- * keys written do not depend on it.
+ * length into one warp and starts the longest chains first, which matters for ragged batches.
+ * warps_per_sm (0 = fill the SMs) caps the warps resident per SM; 4 gives every warp a scheduler of
+ * its own, which is what a batch ruled by a few very long requests wants (kvcm_b200_length_order
+ * suggests the value).  The keys written depend on neither.
  * ---------------------------------------------------------------------------------------- */
 KVCM_API int32_t kvcm_b200_hash_blocks_u32(const uint32_t *d_tokens, int64_t n_tokens_total, const int64_t *d_tok_off,
                                            int32_t n_req, int32_t block_size, int64_t *d_keys,
                                            const int64_t *d_key_off, const int32_t *d_req_order,
-                                           kvcm_stream_t stream);
+                                           int32_t warps_per_sm, kvcm_stream_t stream);
 KVCM_API int32_t kvcm_b200_hash_blocks_i64(const int64_t *d_tokens, int64_t n_tokens_total, const int64_t *d_tok_off,
                                            int32_t n_req, int32_t block_size, int64_t *d_keys,
                                            const int64_t *d_key_off, const int32_t *d_req_order,
-                                           kvcm_stream_t stream);
-/* Host-only helper: h_order_out = requests sorted by token count, longest first (stable). */
-KVCM_API int32_t kvcm_b200_length_order(const int64_t *h_tok_off, int32_t n_req, int32_t *h_order_out);
+                                           int32_t warps_per_sm, kvcm_stream_t stream);
+/* Host-only helper: h_order_out = requests sorted by token count, longest first (stable);
+ * *warps_per_sm_out (optional) = the residency cap to pass along with that order. */
+KVCM_API int32_t kvcm_b200_length_order(const int64_t *h_tok_off, int32_t n_req, int32_t *h_order_out,
+                                        int32_t *warps_per_sm_out);
 /* Host-only helper: key_off[r] = sum_{q<r} floor((tok_off[q+1]-tok_off[q]) / block_size); n_req+1 entries. */
 KVCM_API int32_t kvcm_b200_key_offsets(const int64_t *h_tok_off, int32_t n_req, int32_t block_size,
                                        int64_t *h_key_off);

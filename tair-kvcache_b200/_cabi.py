@@ -53,7 +53,7 @@ class Iov(ctypes.Structure):
 # name -> argtypes, in the order of include/kvcm_b200.h; every function returns int32 unless noted.
 _MOVE = [_vp, _i32, _vp, _i64, _vp, _vp, _i32, _i32, _i64, _i64, _vp, _i32, _vp]
 _LEGACY = [_vp, _i32, _i64, _vp, _vp, _i32, _i64, _vp]
-_HASH = [_vp, _i64, _vp, _i32, _i32, _vp, _vp, _vp, _vp]
+_HASH = [_vp, _i64, _vp, _i32, _i32, _vp, _vp, _vp, _i32, _vp]
 SIGNATURES = {
     "kvcm_b200_abi_version": [],
     "kvcm_b200_set_device": [_i32],
@@ -75,7 +75,7 @@ SIGNATURES = {
     "kvcm_b200_hash_blocks_u32": _HASH,
     "kvcm_b200_hash_blocks_i64": _HASH,
     "kvcm_b200_key_offsets": [_vp, _i32, _i32, _vp],
-    "kvcm_b200_length_order": [_vp, _i32, _vp],
+    "kvcm_b200_length_order": [_vp, _i32, _vp, _vp],
     "kvcm_b200_index_create": [_i64, _vp],
     "kvcm_b200_index_destroy": [_vp],
     "kvcm_b200_index_clear": [_vp, _vp],

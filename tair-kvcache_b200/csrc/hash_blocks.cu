@@ -27,6 +27,7 @@ constexpr int kStageBytes = 64;                         // per lane
 constexpr int kPieces = kStageBytes / 16;               // cp.async pieces per lane per stage
 constexpr int kWarpRingBytes = kStages * kPieces * 32 * 16;  // 16 KiB
 constexpr int kMaxWarpsPerCta = 4;
+constexpr int kMaxHashSmemPerSm = 224 * 1024;
 // Batches of up to 16 x SMs x this many requests run with half-filled warps (tuning experiments set it).
 int g_half_warp_sm_multiple = 2;
 
@@ -211,9 +212,9 @@ __global__ void __launch_bounds__(kMaxWarpsPerCta * 32)
 template <typename T>
 int32_t LaunchHash(const T *d_tokens, int64_t n_tokens_total, const int64_t *d_tok_off, int32_t n_req,
                    int32_t block_size, int64_t *d_keys, const int64_t *d_key_off, const int32_t *d_order,
-                   kvcm_stream_t stream) {
+                   int32_t warps_per_sm, kvcm_stream_t stream) {
     if (!HaveDevice()) return KVCM_ER_NO_DEVICE;
-    if (n_req < 0 || block_size <= 0 || n_tokens_total < 0) return KVCM_ER_INVALID_PARAMS;
+    if (n_req < 0 || block_size <= 0 || n_tokens_total < 0 || warps_per_sm < 0) return KVCM_ER_INVALID_PARAMS;
     if (n_req == 0) return KVCM_OK;
     if (d_tok_off == nullptr || d_key_off == nullptr || (d_tokens == nullptr && n_tokens_total > 0)) {
         return KVCM_ER_INVALID_ADDRESS;
@@ -224,7 +225,7 @@ int32_t LaunchHash(const T *d_tokens, int64_t n_tokens_total, const int64_t *d_t
 
     static bool attr_set = false;
     if (!attr_set) {
-        const int bytes = kMaxWarpsPerCta * kWarpRingBytes;
+        const int bytes = kMaxHashSmemPerSm;
         cudaFuncSetAttribute(HashBlocksKernel<uint32_t, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
         cudaFuncSetAttribute(HashBlocksKernel<uint32_t, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
         cudaFuncSetAttribute(HashBlocksKernel<int64_t, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
@@ -235,10 +236,22 @@ int32_t LaunchHash(const T *d_tokens, int64_t n_tokens_total, const int64_t *d_t
     const int sms = GetDeviceInfo().sm_count;
     const uint32_t lanes_per_warp = static_cast<int64_t>(n_req) <= 16ll * sms * g_half_warp_sm_multiple ? 16u : 32u;
     const int64_t n_warps = (static_cast<int64_t>(n_req) + lanes_per_warp - 1) / lanes_per_warp;
-    const int warps_per_cta = n_warps <= 2ll * sms ? 1 : kMaxWarpsPerCta;
+    // One warp per CTA while every warp of the batch can be resident at once (16 KiB of shared memory
+    // each, 14 per SM): a warp that finishes frees its slot alone and CTAs land on the SMs round-robin.
+    // A caller that knows the batch is ruled by its longest chains (kvcm_b200_length_order says so) asks
+    // for fewer resident warps per SM: shared memory per CTA is then padded so that only that many
+    // one-warp CTAs fit, the longest chains - launched first - run alone on their scheduler, and the
+    // shorter ones take over the slots as they free up.
+    int warps_per_cta = n_warps <= 14ll * sms ? 1 : kMaxWarpsPerCta;
+    size_t smem_per_warp = kWarpRingBytes;
+    if (warps_per_sm > 0 && warps_per_sm < 14) {
+        warps_per_cta = 1;
+        smem_per_warp = (static_cast<size_t>(kMaxHashSmemPerSm) / warps_per_sm) & ~static_cast<size_t>(1023);
+        if (smem_per_warp < kWarpRingBytes) smem_per_warp = kWarpRingBytes;
+    }
+    const size_t smem = static_cast<size_t>(warps_per_cta) * smem_per_warp;
     const unsigned grid = static_cast<unsigned>((n_warps + warps_per_cta - 1) / warps_per_cta);
     const unsigned threads = warps_per_cta * 32;
-    const size_t smem = static_cast<size_t>(warps_per_cta) * kWarpRingBytes;
     constexpr int kPerStage = kStageBytes / sizeof(T);
     if (block_size % kPerStage == 0) {
         HashBlocksKernel<T, true><<<grid, threads, smem, AsStream(stream)>>>(
@@ -257,27 +270,40 @@ extern "C" {
 
 int32_t kvcm_b200_hash_blocks_u32(const uint32_t *d_tokens, int64_t n_tokens_total, const int64_t *d_tok_off,
                                   int32_t n_req, int32_t block_size, int64_t *d_keys, const int64_t *d_key_off,
-                                  const int32_t *d_req_order, kvcm_stream_t stream) {
+                                  const int32_t *d_req_order, int32_t warps_per_sm, kvcm_stream_t stream) {
     return kvcm::LaunchHash<uint32_t>(d_tokens, n_tokens_total, d_tok_off, n_req, block_size, d_keys, d_key_off,
-                                      d_req_order, stream);
+                                      d_req_order, warps_per_sm, stream);
 }
 
 int32_t kvcm_b200_hash_blocks_i64(const int64_t *d_tokens, int64_t n_tokens_total, const int64_t *d_tok_off,
                                   int32_t n_req, int32_t block_size, int64_t *d_keys, const int64_t *d_key_off,
-                                  const int32_t *d_req_order, kvcm_stream_t stream) {
+                                  const int32_t *d_req_order, int32_t warps_per_sm, kvcm_stream_t stream) {
     return kvcm::LaunchHash<int64_t>(d_tokens, n_tokens_total, d_tok_off, n_req, block_size, d_keys, d_key_off,
-                                     d_req_order, stream);
+                                     d_req_order, warps_per_sm, stream);
 }
 
-int32_t kvcm_b200_length_order(const int64_t *h_tok_off, int32_t n_req, int32_t *h_order_out) {
+int32_t kvcm_b200_length_order(const int64_t *h_tok_off, int32_t n_req, int32_t *h_order_out,
+                               int32_t *warps_per_sm_out) {
     if (h_tok_off == nullptr || h_order_out == nullptr) return KVCM_ER_INVALID_ADDRESS;
     if (n_req < 0) return KVCM_ER_INVALID_PARAMS;
+    if (warps_per_sm_out != nullptr) *warps_per_sm_out = 0;
     std::vector<int32_t> idx(n_req);
     for (int32_t r = 0; r < n_req; ++r) idx[r] = r;
     std::stable_sort(idx.begin(), idx.end(), [&](int32_t a, int32_t b) {
         return h_tok_off[a + 1] - h_tok_off[a] > h_tok_off[b + 1] - h_tok_off[b];
     });
     for (int32_t r = 0; r < n_req; ++r) h_order_out[r] = idx[r];
+    if (warps_per_sm_out != nullptr && n_req > 0) {
+        // A lone warp advances one token per ~47 cycles (dependent chain); a scheduler shared by several
+        // warps issues one token step per ~31 cycles in total.  If the longest chain alone outlasts the
+        // whole batch spread over all schedulers, keep one warp per scheduler (4 per SM) so that chain is
+        // never slowed down; otherwise fill the SMs.
+        const int sms = kvcm::HaveDevice() ? kvcm::GetDeviceInfo().sm_count : 148;
+        const double longest = static_cast<double>(h_tok_off[idx[0] + 1] - h_tok_off[idx[0]]);
+        double warp_steps = 0;
+        for (int32_t r = 0; r < n_req; r += 32) warp_steps += static_cast<double>(h_tok_off[idx[r] + 1] - h_tok_off[idx[r]]);
+        *warps_per_sm_out = longest * 47.0 >= warp_steps * 31.0 / (4.0 * sms) ? 4 : 0;
+    }
     return KVCM_OK;
 }
 

@@ -141,7 +141,7 @@ public:
         }
         rc = kvcm_b200_hash_blocks_i64(tok_.dev<int64_t>(), n_tok, tok_off_.dev<int64_t>(), n_req,
                                        static_cast<int32_t>(block_size), keys_.dev<int64_t>(),
-                                       key_off_.dev<int64_t>(), nullptr, stream_);
+                                       key_off_.dev<int64_t>(), nullptr, 0, stream_);
         if (rc != KVCM_OK) return rc;
         if (!keys_.ToHost(sizeof(int64_t) * n_keys, stream_)) return KVCM_ER_CUDAMEMCPY_ERROR;
         rc = detail::Sync(stream_);

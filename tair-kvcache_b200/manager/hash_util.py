@@ -21,18 +21,21 @@ def key_offsets(tok_off, block_size: int) -> np.ndarray:
     return out
 
 
-def length_order(tok_off) -> np.ndarray:
+def length_order(tok_off, with_residency: bool = False):
     """Requests sorted by token count, longest first (int32 permutation, host side).  Passing it to
-    GenKeyVectorBatch makes ragged batches hash several times faster; the keys are the same."""
+    GenKeyVectorBatch speeds up ragged batches; the keys are the same.  with_residency=True also returns the
+    `warps_per_sm` value to pass along (4 when a few very long requests rule the batch, else 0)."""
     tok_off = np.ascontiguousarray(tok_off, dtype=np.int64)
     out = np.empty(len(tok_off) - 1, dtype=np.int32)
+    residency = ctypes.c_int32(0)
     _cabi.call("kvcm_b200_length_order", tok_off.ctypes.data_as(ctypes.c_void_p), len(tok_off) - 1,
-               out.ctypes.data_as(ctypes.c_void_p))
-    return out
+               out.ctypes.data_as(ctypes.c_void_p), ctypes.byref(residency))
+    return (out, residency.value) if with_residency else out
 
 
 def GenKeyVectorBatch(tokens: torch.Tensor, tok_off: torch.Tensor, block_size: int, key_off: torch.Tensor,
-                      n_keys: int, out: torch.Tensor = None, order: torch.Tensor = None) -> torch.Tensor:
+                      n_keys: int, out: torch.Tensor = None, order: torch.Tensor = None,
+                      warps_per_sm: int = 0) -> torch.Tensor:
     """Keys of a CSR batch of requests.
 
     tokens: CUDA tensor of token ids, int32/uint32 (zero-extended) or int64; tok_off / key_off:
@@ -55,7 +58,7 @@ def GenKeyVectorBatch(tokens: torch.Tensor, tok_off: torch.Tensor, block_size: i
     with torch.cuda.device(tokens.device):
         _cabi.call(entry, tokens.data_ptr(), tokens.numel(), tok_off.data_ptr(), n_req, block_size, out.data_ptr(),
                    key_off.data_ptr(), order.contiguous().data_ptr() if order is not None else None,
-                   torch.cuda.current_stream().cuda_stream)
+                   warps_per_sm, torch.cuda.current_stream().cuda_stream)
     return out[:n_keys]
 
 

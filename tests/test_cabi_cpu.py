@@ -74,7 +74,7 @@ def test_compute_entry_points_refuse_without_a_device():
     L = _cabi.lib()
     one = ctypes.c_void_p(16)
     assert L.kvcm_b200_gather_tokens(one, 1, one, 1, one, None, 1, 1, 16, 1, None, 0, None) == _cabi.KVCM_ER_NO_DEVICE
-    assert L.kvcm_b200_hash_blocks_u32(one, 4, one, 1, 1, one, one, None, None) == _cabi.KVCM_ER_NO_DEVICE
+    assert L.kvcm_b200_hash_blocks_u32(one, 4, one, 1, 1, one, one, None, 0, None) == _cabi.KVCM_ER_NO_DEVICE
     h = ctypes.c_void_p()
     assert L.kvcm_b200_index_create(10, ctypes.byref(h)) == _cabi.KVCM_ER_NO_DEVICE and not h.value
     assert L.kvcm_b200_copy_segments(one, 1, None) == _cabi.KVCM_ER_NO_DEVICE

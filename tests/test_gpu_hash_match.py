@@ -85,14 +85,35 @@ def test_longest_first_order_gives_the_same_keys():
     lens = np.exp(rng.uniform(np.log(16), np.log(20000), size=700)).astype(np.int64)
     toks = rng.integers(0, 151936, size=int(lens.sum())).astype(np.uint32)
     off = _csr(lens)
-    order = length_order(off)
+    order, residency = length_order(off, with_residency=True)
     assert sorted(order.tolist()) == list(range(700)) and (np.diff(lens[order]) <= 0).all()
+    assert residency == 4  # 22 warps on 148 SMs: the longest chain rules
     ko = key_offsets(off, 16)
-    keys = GenKeyVectorBatch(torch.from_numpy(toks.view(np.int32)).to(DEV), torch.from_numpy(off).to(DEV), 16,
-                             torch.from_numpy(ko).to(DEV), int(ko[-1]), order=torch.from_numpy(order).to(DEV))
-    torch.cuda.synchronize()
     want, _ = oracle.hash_blocks(toks, off, 16, threads=4)
-    assert np.array_equal(keys.cpu().numpy(), want)
+    for cap in (0, 1, 4, residency):
+        keys = GenKeyVectorBatch(torch.from_numpy(toks.view(np.int32)).to(DEV), torch.from_numpy(off).to(DEV), 16,
+                                 torch.from_numpy(ko).to(DEV), int(ko[-1]), order=torch.from_numpy(order).to(DEV),
+                                 warps_per_sm=cap)
+        torch.cuda.synchronize()
+        assert np.array_equal(keys.cpu().numpy(), want), cap
+
+
+def test_residency_cap_with_more_warps_than_slots_gives_the_same_keys():
+    """More warps than the capped residency admits at once: CTAs queue up behind the longest chains."""
+    from tair_kvcache_b200.manager import length_order
+    rng = np.random.default_rng(13)
+    lens = np.concatenate([rng.integers(0, 300, size=30000), [40000, 35000, 7]])
+    rng.shuffle(lens)
+    toks = rng.integers(0, 151936, size=int(lens.sum())).astype(np.uint32)
+    off = _csr(lens)
+    order = length_order(off)
+    ko = key_offsets(off, 16)
+    want, _ = oracle.hash_blocks(toks, off, 16, threads=8)
+    d = [torch.from_numpy(a).to(DEV) for a in (toks.view(np.int32), off, ko, order)]
+    for use_order in (True, False):
+        keys = GenKeyVectorBatch(d[0], d[1], 16, d[2], int(ko[-1]), order=d[3] if use_order else None, warps_per_sm=4)
+        torch.cuda.synchronize()
+        assert np.array_equal(keys.cpu().numpy(), want), use_order
 
 
 def test_hash_rejects_misaligned_token_buffer():
@@ -101,7 +122,7 @@ def test_hash_rejects_misaligned_token_buffer():
     out = torch.zeros(4, dtype=torch.int64, device=DEV)
     _cabi.bind_device(0)
     rc = _cabi.lib().kvcm_b200_hash_blocks_u32(t.data_ptr() + 4, 32, off.data_ptr(), 1, 4, out.data_ptr(),
-                                               off.data_ptr(), None, None)
+                                               off.data_ptr(), None, 0, None)
     assert rc == _cabi.KVCM_ER_INVALID_ADDRESS
 
 
