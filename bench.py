@@ -61,53 +61,71 @@ def peaks():
 # clocks
 # ----------------------------------------------------------------------------------------------
 class ClockSampler:
-    """nvidia-smi sampling of SM clocks and throttle reasons while the timed region runs (read-only)."""
-    FIELDS = ("uuid,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    """nvidia-smi sampling of this GPU's SM clock and throttle reasons (read-only).  The sampler is started well
+    before the timed region (nvidia-smi needs a moment to come up) and only the samples whose timestamps fall
+    inside [mark_begin(), mark_end()] are kept."""
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, uuid):
-        self.uuid = uuid
+        self.uuid = uuid if str(uuid).startswith("GPU-") else "GPU-" + str(uuid)
         self.proc = None
         self.path = None
+        self.t0 = self.t1 = None
 
     def start(self):
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "20"],
-                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+                ["nvidia-smi", "-i", self.uuid, "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "10"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+            time.sleep(0.5)
         except OSError:
             self.proc = None
 
+    def mark_begin(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
+
     def stop(self):
+        import datetime
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.proc is None:
             return out
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, reasons, sm_max = [], set(), None
+        inside, everything, reasons, sm_max = [], [], set(), None
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         with open(self.path) as f:
             for line in f:
                 parts = [p.strip() for p in line.split(",")]
-                if len(parts) < 8 or (self.uuid and self.uuid not in parts[0]):
+                if len(parts) < 8:
                     continue
                 try:
-                    sm.append(float(parts[1]))
+                    ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    mhz = float(parts[1])
                     sm_max = float(parts[2])
                 except ValueError:
                     continue
-                for name, val in zip(names, parts[4:8]):
-                    if val.lower().startswith("active"):
-                        reasons.add(name)
+                everything.append(mhz)
+                if self.t0 is None or self.t0 - 0.01 <= ts <= (self.t1 or ts) + 0.01:
+                    inside.append(mhz)
+                    for name, val in zip(names, parts[4:8]):
+                        if val.lower().startswith("active"):
+                            reasons.add(name)
         os.unlink(self.path)
-        if sm:
-            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=sm_max, reasons=sorted(reasons), samples=len(sm))
+        use = inside or everything
+        if use:
+            out.update(sm_mhz=statistics.median(use), sm_max_mhz=sm_max, reasons=sorted(reasons),
+                       samples=len(inside), samples_around=len(everything))
         return out
 
 
@@ -362,16 +380,18 @@ def main_b200(args, cfg, rank, world):
     torch.cuda.synchronize(device)
     parity_ok = verify_staging(w)
 
+    sampler = ClockSampler(str(torch.cuda.get_device_properties(device).uuid)) if rank == 0 else None
+    if sampler:
+        sampler.start()  # before the warm-up, so the GPU does not idle between warm-up and the timed region
     for _ in range(args.warmup):
         gather()
         scatter()
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
-    sampler = ClockSampler(str(torch.cuda.get_device_properties(device).uuid)) if rank == 0 else None
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize(device)
     if sampler:
-        sampler.start()
+        sampler.mark_begin()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for k in range(args.steps):
@@ -382,6 +402,8 @@ def main_b200(args, cfg, rank, world):
         ev[k][2].record()
     stop.record()
     torch.cuda.synchronize(device)
+    if sampler:
+        sampler.mark_end()
     if world > 1:
         dist.barrier()
     clocks = sampler.stop() if sampler else None
