@@ -310,6 +310,17 @@ KVCM_API int32_t kvcm_b200_match_sw(kvcm_b200_index_t *index, const int64_t *d_k
 KVCM_API int32_t kvcm_b200_batch_get(kvcm_b200_index_t *index, const int64_t *d_keys, int64_t n, uint32_t avail_mask,
                                      uint8_t *d_flags_out, kvcm_stream_t stream);
 
+/* CacheManager::FilterWriteCache (kv_cache_manager/manager/cache_manager.cc:589-635) for a batch of
+ * StartWriteCache requests: which keys still have to be written.  A key "exists" when it has a location
+ * with status != CLS_NOT_FOUND and weight > 0 (ExistsForWrite).  If the existing keys of request r form
+ * a prefix, d_offset_out[r] = index of the first missing key (the BlockMaskOffset the reference returns)
+ * and d_n_new_out[r] = keys after it.  Otherwise d_offset_out[r] = -1, the answer is the BlockMaskVector
+ * d_mask_out (per key, aligned with d_keys: 1 = location map non-empty; always written when not NULL)
+ * and d_n_new_out[r] = keys whose map is empty. */
+KVCM_API int32_t kvcm_b200_filter_write(kvcm_b200_index_t *index, const int64_t *d_keys, const int64_t *d_key_off,
+                                        int32_t n_req, uint32_t avail_mask, int32_t *d_offset_out,
+                                        uint8_t *d_mask_out, int32_t *d_n_new_out, kvcm_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------
  * Hash-range-sharded index: one logical index split over shard_count GPUs.  Key k belongs to shard
  * floor(fmix64(k) * shard_count / 2^64).  Each GPU holds an ordinary index with the keys it owns;

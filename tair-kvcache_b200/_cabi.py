@@ -86,6 +86,7 @@ SIGNATURES = {
     "kvcm_b200_match_prefix": [_vp, _vp, _vp, _i32, _vp, _vp, _u32, _vp, _vp],
     "kvcm_b200_match_sw": [_vp, _vp, _vp, _i32, _i32, _u32, _vp, _vp],
     "kvcm_b200_batch_get": [_vp, _vp, _i64, _u32, _vp, _vp],
+    "kvcm_b200_filter_write": [_vp, _vp, _vp, _i32, _u32, _vp, _vp, _vp, _vp],
     "kvcm_b200_index_upsert_sharded": [_vp, _vp, _vp, _u64, _i64, _i32, _i32, _vp, _vp],
     "kvcm_b200_match_prefix_sharded": [_vp, _vp, _vp, _i32, _vp, _vp, _u32, _i32, _i32, _vp, _vp],
     "kvcm_b200_batch_get_sharded": [_vp, _vp, _i64, _u32, _i32, _i32, _vp, _vp],

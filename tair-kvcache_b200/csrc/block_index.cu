@@ -348,6 +348,58 @@ __global__ void __launch_bounds__(kMatchWarps * 32)
     if (lane == 0) base_out[req] = static_cast<int32_t>(found);
 }
 
+// CacheManager::FilterWriteCache (kv_cache_manager/manager/cache_manager.cc:589-635) for a batch of
+// requests, one warp each.  exists(key) = ExistsForWrite: some location with status != NOT_FOUND and
+// weight > 0.  If the keys that exist form a prefix of the request, the answer is the offset of the
+// first missing key (offset_out >= 0, new keys = the suffix); otherwise offset_out = -1 and the answer
+// is the per-key mask "location map non-empty" written to mask_out (new keys = the rest).
+__global__ void __launch_bounds__(kMatchWarps * 32)
+    FilterWriteKernel(IndexView ix, const int64_t *__restrict__ keys, const int64_t *__restrict__ key_off,
+                      int32_t n_req, uint32_t avail_mask, int32_t *__restrict__ offset_out,
+                      uint8_t *__restrict__ mask_out, int32_t *__restrict__ n_new_out) {
+    const int32_t req = blockIdx.x * kMatchWarps + (threadIdx.x >> 5);
+    if (req >= n_req) return;
+    const uint32_t lane = LaneId();
+    const int64_t beg = key_off[req];
+    const int64_t n = key_off[req + 1] - beg;
+    int64_t first_missing = n;   // first key without a writable location
+    bool exists_after = false;   // some key at or after first_missing exists
+    int32_t n_empty = 0;         // keys whose location map is empty
+    for (int64_t base = 0; base < n; base += 32) {
+        const int64_t i = base + lane;
+        bool exists = false, nonempty = false;
+        if (i < n) {
+            const uint64_t v = Lookup(ix, static_cast<uint64_t>(keys[beg + i]));
+            exists = (static_cast<uint32_t>(v >> 16) & avail_mask & 0xFFFFu) != 0;
+            nonempty = (v & KVCM_VAL_NONEMPTY) != 0;
+            if (mask_out != nullptr) mask_out[beg + i] = nonempty ? 1 : 0;
+        }
+        const uint32_t in_range = __ballot_sync(0xffffffffu, i < n);
+        const uint32_t ex = __ballot_sync(0xffffffffu, exists);
+        const uint32_t ne = __ballot_sync(0xffffffffu, nonempty);
+        n_empty += __popc(in_range & ~ne);
+        if (first_missing == n) {
+            const uint32_t missing = in_range & ~ex;
+            if (missing != 0) {
+                const int pos = __ffs(missing) - 1;
+                first_missing = base + pos;
+                if ((ex >> pos) != 0) exists_after = true;  // an existing key later in this pass
+            }
+        } else if (ex != 0) {
+            exists_after = true;
+        }
+    }
+    if (lane == 0) {
+        if (!exists_after) {
+            offset_out[req] = static_cast<int32_t>(first_missing);
+            n_new_out[req] = static_cast<int32_t>(n - first_missing);
+        } else {
+            offset_out[req] = -1;
+            n_new_out[req] = n_empty;
+        }
+    }
+}
+
 // View for the matchers: probes follow the attached peers.
 IndexView View(const kvcm_b200_index *ix) {
     IndexView v;
@@ -609,6 +661,19 @@ int32_t kvcm_b200_match_sw(kvcm_b200_index_t *ix, const int64_t *d_keys, const i
     kvcm::SwMatchKernel<<<kvcm::GridFor(n_req, kvcm::kMatchWarps), kvcm::kMatchWarps * 32, 0,
                           kvcm::AsStream(stream)>>>(kvcm::View(ix), d_keys, d_key_off, n_req, sw_blocks, avail_mask,
                                                     d_base_out);
+    return kvcm::LaunchStatus();
+}
+
+int32_t kvcm_b200_filter_write(kvcm_b200_index_t *ix, const int64_t *d_keys, const int64_t *d_key_off, int32_t n_req,
+                               uint32_t avail_mask, int32_t *d_offset_out, uint8_t *d_mask_out, int32_t *d_n_new_out,
+                               kvcm_stream_t stream) {
+    if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (n_req < 0) return KVCM_EC_BADARGS;
+    if (n_req == 0) return KVCM_OK;
+    if (d_key_off == nullptr || d_offset_out == nullptr || d_n_new_out == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    kvcm::FilterWriteKernel<<<kvcm::GridFor(n_req, kvcm::kMatchWarps), kvcm::kMatchWarps * 32, 0,
+                              kvcm::AsStream(stream)>>>(kvcm::View(ix), d_keys, d_key_off, n_req, avail_mask,
+                                                        d_offset_out, d_mask_out, d_n_new_out);
     return kvcm::LaunchStatus();
 }
 

@@ -59,3 +59,17 @@ class BatchMetaSearcher:
         _cabi.call("kvcm_b200_batch_get", self.index.handle, keys.data_ptr(), keys.numel(), self.avail_mask,
                    out.data_ptr(), self.index._s())
         return out[:keys.numel()]
+
+    def FilterWriteCache(self, keys: torch.Tensor, key_off: torch.Tensor):
+        """Batched CacheManager::FilterWriteCache.  Returns (offset, mask, n_new): int32 offset per request (index
+        of the first key still to be written when the existing keys form a prefix, else -1), uint8 per-key mask
+        (1 = location map non-empty; the BlockMaskVector for requests with offset -1), int32 keys to write."""
+        n_req = key_off.numel() - 1
+        keys, key_off = _keys(keys, self.index.device), _keys(key_off, self.index.device)
+        dev = self.index.device
+        offset = torch.empty(max(n_req, 1), dtype=torch.int32, device=dev)
+        n_new = torch.empty(max(n_req, 1), dtype=torch.int32, device=dev)
+        mask = torch.empty(max(keys.numel(), 1), dtype=torch.uint8, device=dev)
+        _cabi.call("kvcm_b200_filter_write", self.index.handle, keys.data_ptr(), key_off.data_ptr(), n_req,
+                   self.avail_mask, offset.data_ptr(), mask.data_ptr(), n_new.data_ptr(), self.index._s())
+        return offset[:n_req], mask[:keys.numel()], n_new[:n_req]

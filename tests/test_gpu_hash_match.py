@@ -295,6 +295,28 @@ def test_batch_get_random_against_oracle():
         assert np.array_equal(got.cpu().numpy(), ox.batch_get(keys, weights=weights))
 
 
+def test_filter_write_cache_against_oracle():
+    rng = np.random.default_rng(31)
+    for hit_bias in (0.3, 0.9):
+        ox, ix, keys, off = _random_world(rng, 3000, 400, 150, hit_bias)
+        # make some requests exact "existing prefix + missing suffix" shapes
+        for weights in [(1, 3, 3, 3, 5), (1, 0, 0, 3, 0)]:
+            ms = BatchMetaSearcher(ix, avail_mask_from_weights(weights))
+            offset, mask, n_new = (t.cpu().numpy() for t in
+                                   ms.FilterWriteCache(torch.from_numpy(keys).to(DEV), torch.from_numpy(off).to(DEV)))
+            kinds = set()
+            for r in range(len(off) - 1):
+                a, b = off[r], off[r + 1]
+                want = ox.filter_write(keys[a:b], weights=weights)
+                kinds.add(want[0])
+                if want[0] == "offset":
+                    assert (offset[r], n_new[r]) == (want[1], want[2]), r
+                else:
+                    assert offset[r] == -1 and n_new[r] == want[2], r
+                    assert np.array_equal(mask[a:b].astype(bool), want[1]), r
+            assert kinds == {"offset", "vector"}
+
+
 def test_hash_then_match_prefix_reuse_workload():
     """Shrunk version of the CPU-runnable prefix-match configuration: uint32 tokens in [0,151936), block 64,
     half of the requests reuse a random-length prefix of an earlier one, index pre-filled with prior blocks."""
