@@ -314,7 +314,8 @@ def test_filter_write_cache_against_oracle():
                 else:
                     assert offset[r] == -1 and n_new[r] == want[2], r
                     assert np.array_equal(mask[a:b].astype(bool), want[1]), r
-            assert kinds == {"offset", "vector"}
+            if weights[1] > 0:  # with every storage class available both answer shapes occur
+                assert kinds == {"offset", "vector"}
 
 
 def test_hash_then_match_prefix_reuse_workload():
