@@ -153,6 +153,9 @@ KVCM_API int32_t kvcm_b200_set_mover(int32_t mover, int32_t cache_hint);
  * per SM; stages * chunk_bytes * ctas_per_sm must fit the SM's 224 KiB of shared memory.
  * (0, 0, 0) restores the default, which picks the geometry from the tile size.  Same calling rule as kvcm_b200_set_mover. */
 KVCM_API int32_t kvcm_b200_set_bulk_geometry(int32_t stages, int32_t ctas_per_sm, int32_t chunk_bytes);
+/* Rows shorter than this many bytes (multiple of 16, default 512) use the vector kernel even when the
+ * bulk-copy ring is selected.  Same calling rule as kvcm_b200_set_mover. */
+KVCM_API int32_t kvcm_b200_set_bulk_min_row_bytes(int32_t row_bytes);
 
 /* Legacy single-block form: kv_cache_gather_kernel / kv_cache_scatter_kernel and gather_kv_caches /
  * scatter_kv_caches (kv_cache_manager/py_connector/kernel/gather_scatter_helper.py:10-172).

@@ -67,6 +67,7 @@ SIGNATURES = {
     "kvcm_b200_load_rows_from_host": [_vp, _i32, _vp, _i64, _vp, _vp, _i32, _i32, _i64, _i64, _vp, _i64, _vp, _vp],
     "kvcm_b200_set_mover": [_i32, _i32],
     "kvcm_b200_set_bulk_geometry": [_i32, _i32, _i32],
+    "kvcm_b200_set_bulk_min_row_bytes": [_i32],
     "kvcm_b200_gather_legacy": _LEGACY,
     "kvcm_b200_scatter_legacy": _LEGACY,
     "kvcm_b200_copy_segments": [_vp, _i32, _vp],

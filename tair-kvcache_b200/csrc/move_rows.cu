@@ -172,7 +172,7 @@ __global__ void __launch_bounds__(kThreads) MoveRowsKernel(const MoveParams p) {
 // Every wait is bounded: after kSpinLimit failed polls the CTA raises status[2] and leaves.
 // ------------------------------------------------------------------------------------------
 constexpr int kBulkMaxStages = 8;
-constexpr uint32_t kBulkMinRowBytes = 1024;
+constexpr uint32_t kBulkMinRowBytes = 512;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t SmemAddr(const void *p) {
@@ -418,6 +418,7 @@ __global__ void __launch_bounds__(32) MoveRowsBulkKernel(const MoveParams p) {
 struct MoverConfig {
     int mover = 1;
     int hint = 0;
+    uint32_t bulk_min_row_bytes = kBulkMinRowBytes;  // shorter rows use the vector kernel
     // Ring geometry; chunk 0 = choose from the shape (see BulkGeometryFor).
     int bulk_stages = 2;
     int bulk_ctas_per_sm = 3;
@@ -430,14 +431,17 @@ struct BulkGeometry {
     uint32_t chunk_bytes;
 };
 
-// Ring geometry for a tile of tile_bytes, from sweeps on B200 (2 stages throughout; what matters
-// is ~192 KiB in flight per SM and chunks that split a tile evenly, because chunk ids are dealt
-// round-robin and a short tail chunk always lands on the same CTAs):
-//   tiles >= 96 KiB (Llama-8B pages: 4 x 32 KiB)   -> 48 KiB chunks, 2 CTAs per SM
-//   smaller tiles                                   -> tile split into equal chunks <= 32 KiB, 3 CTAs per SM
-BulkGeometry BulkGeometryFor(const MoverConfig &cfg, int64_t tile_bytes) {
+// Ring geometry from the shape, from sweeps on B200 (2 stages throughout; what matters is ~192 KiB
+// in flight per SM, enough CTAs to issue the copies of short rows in parallel, and chunks that split
+// a tile evenly, because chunk ids are dealt round-robin and a short tail chunk always lands on the
+// same CTAs):
+//   rows < 2 KiB (token rows)                       -> 16 KiB chunks, 6 CTAs per SM
+//   rows >= 8 KiB in tiles >= 96 KiB (Llama-8B pages) -> 48 KiB chunks, 2 CTAs per SM
+//   otherwise                                        -> tile split into equal chunks <= 32 KiB, 3 CTAs per SM
+BulkGeometry BulkGeometryFor(const MoverConfig &cfg, int64_t tile_bytes, int64_t row_bytes) {
     if (cfg.bulk_chunk_bytes != 0) return {cfg.bulk_stages, cfg.bulk_ctas_per_sm, cfg.bulk_chunk_bytes};
-    if (tile_bytes >= 96 * 1024) return {2, 2, 48 * 1024};
+    if (row_bytes < 2048) return {2, 6, 16 * 1024};
+    if (row_bytes >= 8192 && tile_bytes >= 96 * 1024) return {2, 2, 48 * 1024};
     const int64_t n = (tile_bytes + 32 * 1024 - 1) / (32 * 1024);
     int64_t chunk = (tile_bytes + n - 1) / n;
     chunk = (chunk + 1023) / 1024 * 1024;
@@ -531,9 +535,9 @@ int32_t LaunchMove(bool gather, const void *const *d_ptrs, int32_t n_ptrs, int32
     const MoverConfig &cfg = GetMoverConfig();
     // The bulk ring needs 16-byte granularity everywhere and rows long enough to amortise one
     // copy instruction each; the sub-pool stride of the legacy layout must keep that alignment.
-    const bool bulk_ok = cfg.mover == 1 && row_bytes % 16 == 0 && row_bytes >= kBulkMinRowBytes &&
+    const bool bulk_ok = cfg.mover == 1 && row_bytes % 16 == 0 && row_bytes >= cfg.bulk_min_row_bytes &&
                          (reinterpret_cast<uintptr_t>(staging) & 15u) == 0 && sub_stride % 16 == 0;
-    const BulkGeometry geo = BulkGeometryFor(cfg, tile_bytes);
+    const BulkGeometry geo = BulkGeometryFor(cfg, tile_bytes, row_bytes);
     const int64_t chunk_bytes = bulk_ok ? geo.chunk_bytes : kChunkBytes;
     const int64_t chunks_per_tile = (tile_bytes + chunk_bytes - 1) / chunk_bytes;
     const int64_t total_chunks = chunks_per_tile * n_pools * n_blocks;
@@ -588,6 +592,12 @@ int32_t kvcm_b200_set_mover(int32_t mover, int32_t cache_hint) {
     kvcm::MoverConfig &cfg = kvcm::GetMoverConfig();
     if (mover >= 0) cfg.mover = mover;
     if (cache_hint >= 0) cfg.hint = cache_hint;
+    return KVCM_OK;
+}
+
+int32_t kvcm_b200_set_bulk_min_row_bytes(int32_t row_bytes) {
+    if (row_bytes < 16 || row_bytes % 16 != 0) return KVCM_ER_INVALID_PARAMS;
+    kvcm::GetMoverConfig().bulk_min_row_bytes = static_cast<uint32_t>(row_bytes);
     return KVCM_OK;
 }
 
