@@ -129,7 +129,7 @@ KVCM_API int32_t kvcm_b200_scatter_pages(const void *const *d_pool_ptrs, int32_t
  * (load), in groups of floor(bounce_bytes / block_bytes) blocks, all ordered on `stream`.  A save on
  * one stream and a load on another then use both PCIe directions at full rate, which kernels writing
  * host memory directly do not.  h_slot_idx is a HOST array of staging slots (NULL = slot b); slots
- * outside [0, n_slots) return KVCM_ER_INVALID_PARAMS before anything for that group is copied.
+ * outside [0, n_slots) return KVCM_ER_INVALID_PARAMS before anything is launched or copied.
  * d_bounce: device memory, 16-byte aligned, at least one block (n_pools * rows_per_block * row_bytes). */
 KVCM_API int32_t kvcm_b200_save_rows_to_host(const void *const *d_pool_ptrs, int32_t n_pools, void *h_staging,
                                              int64_t n_slots, const int32_t *d_row_idx, const int32_t *h_slot_idx,

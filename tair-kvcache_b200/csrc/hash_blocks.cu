@@ -28,8 +28,8 @@ constexpr int kPieces = kStageBytes / 16;               // cp.async pieces per l
 constexpr int kWarpRingBytes = kStages * kPieces * 32 * 16;  // 16 KiB
 constexpr int kMaxWarpsPerCta = 4;
 constexpr int kMaxHashSmemPerSm = 224 * 1024;
-// Batches of up to 16 x SMs x this many requests run with half-filled warps (tuning experiments set it).
-int g_half_warp_sm_multiple = 2;
+// Batches of up to 16 x SMs x this many requests run with half-filled warps.
+constexpr int kHalfWarpSmMultiple = 2;
 
 __device__ __forceinline__ void CpAsync16(uint32_t smem_addr, uint64_t gmem_addr, uint32_t src_bytes) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr), "l"(gmem_addr), "r"(src_bytes)
@@ -234,7 +234,7 @@ int32_t LaunchHash(const T *d_tokens, int64_t n_tokens_total, const int64_t *d_t
     }
     // Few requests: half-filled warps, one per CTA, so the chains spread over as many SMs as possible.
     const int sms = GetDeviceInfo().sm_count;
-    const uint32_t lanes_per_warp = static_cast<int64_t>(n_req) <= 16ll * sms * g_half_warp_sm_multiple ? 16u : 32u;
+    const uint32_t lanes_per_warp = static_cast<int64_t>(n_req) <= 16ll * sms * kHalfWarpSmMultiple ? 16u : 32u;
     const int64_t n_warps = (static_cast<int64_t>(n_req) + lanes_per_warp - 1) / lanes_per_warp;
     // One warp per CTA while every warp of the batch can be resident at once (16 KiB of shared memory
     // each, 14 per SM): a warp that finishes frees its slot alone and CTAs land on the SMs round-robin.

@@ -689,6 +689,13 @@ static int32_t MoveRowsThroughBounce(bool save, const void *const *d_pool_ptrs, 
     const int64_t block_bytes = static_cast<int64_t>(n_pools) * rows_per_block * row_bytes;
     const int64_t group = bounce_bytes / block_bytes;
     if (group < 1) return KVCM_ER_INVALID_PARAMS;
+    if (h_slot_idx != nullptr) {  // refuse a bad slot before anything is launched or copied
+        for (int32_t b = 0; b < n_blocks; ++b) {
+            if (h_slot_idx[b] < 0 || h_slot_idx[b] >= n_slots) return KVCM_ER_INVALID_PARAMS;
+        }
+    } else if (n_blocks > n_slots) {
+        return KVCM_ER_INVALID_PARAMS;
+    }
     cudaStream_t s = kvcm::AsStream(stream);
     uint8_t *host = static_cast<uint8_t *>(h_staging);
     uint8_t *bounce = static_cast<uint8_t *>(d_bounce);

@@ -95,3 +95,32 @@ def test_encode_locations_matches_oracle_predicates():
             assert bool(f & 1) == bool(w & avail & 0xFFFF)
             assert bool(f & 4) == bool(w & _cabi.VAL_NONEMPTY)
             assert bool(f & 8) == bool((w >> 16) & avail & 0xFFFF)
+
+
+def test_block_table_helpers_match_the_connector_loop():
+    from tair_kvcache_b200.kernel.block_table import generate_block_page_table, generate_blocks_idx
+
+    def reference_loop(manager_block_idxes, local_block_ids, M, L):
+        # the double loop of kv_cache_manager/py_connector/vllm/v1_connector.py:308-320, restated
+        out = []
+        for mb in manager_block_idxes:
+            row = []
+            for i in range(M):
+                t = mb * M + i
+                row.append(local_block_ids[t // L] * L + t % L)
+            out.append(row)
+        return out
+
+    rng = np.random.default_rng(4)
+    for M, L in [(64, 16), (16, 16), (32, 64), (48, 16)]:
+        n_local = 40
+        ids = rng.permutation(1000)[:n_local].tolist()
+        n_manager = n_local * L // M
+        mbs = rng.permutation(n_manager)[:min(7, n_manager)].tolist()
+        assert generate_blocks_idx(mbs, ids, M, L) == reference_loop(mbs, ids, M, L)
+        if M % L == 0:
+            table = generate_block_page_table(mbs, ids, M, L)
+            tok = (table[:, :, None].astype(np.int64) * L + np.arange(L)[None, None, :]).reshape(len(mbs), M)
+            assert tok.tolist() == reference_loop(mbs, ids, M, L)
+    with pytest.raises(ValueError):
+        generate_block_page_table([0], [1, 2], 32, 64)
