@@ -151,3 +151,35 @@ def bind_device(index):
     if getattr(_tls, "device", None) != index:
         call("kvcm_b200_set_device", index)
         _tls.device = index
+
+
+_shim = None
+_shim_tried = False
+
+
+def shim():
+    """The pybind11 module over the same C ABI (built next to the library), or None when it is not there.
+    The gather / scatter operators of py_connector go through it; ctypes is the equivalent route without it."""
+    global _shim, _shim_tried
+    if not _shim_tried:
+        _shim_tried = True
+        if os.environ.get("KVCM_B200_NO_PYBIND", "") == "":
+            try:
+                from . import kvcm_b200_py as mod
+                if mod.abi_version() == lib().kvcm_b200_abi_version():
+                    _shim = mod
+            except ImportError:
+                _shim = None
+    return _shim
+
+
+def call_move(name, *args):
+    """A gather / scatter entry point by its C name with integer addresses (None = NULL): through the pybind
+    shim when it is built, else through ctypes.  Raises KvcmError on a non-zero code either way."""
+    mod = shim()
+    if mod is not None:
+        fn = getattr(mod, name[len("kvcm_b200_"):], None)
+        if fn is not None:
+            check(fn(*[0 if a is None else int(a) for a in args]), name)
+            return
+    call(name, *args)

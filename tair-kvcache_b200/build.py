@@ -67,7 +67,31 @@ def build_host_adapter_test():
     return HOST_TEST_BIN
 
 
+def pybind_path():
+    import sysconfig
+    return os.path.join(HERE, "kvcm_b200_py" + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_pybind_shim():
+    """Compile the pybind11 shim for py_connector (plain g++: it only forwards to the C ABI)."""
+    import sysconfig
+
+    import pybind11
+    out = pybind_path()
+    src = os.path.join(HERE, "pybind", "kvcm_b200_py.cc")
+    cxx = shutil.which("g++") or "g++"
+    cmd = [cxx, "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-I", pybind11.get_include(),
+           "-I", sysconfig.get_paths()["include"], "-I", os.path.join(ROOT, "include"), "-o", out, src,
+           "-L", HERE, "-lkvcm_b200", "-Wl,-rpath,$ORIGIN"]
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if proc.returncode != 0:
+        print(proc.stdout)
+        raise RuntimeError("building the pybind shim failed (exit %d)" % proc.returncode)
+    return out
+
+
 if __name__ == "__main__":
     import sys
     print(build_library(force=True, verbose="-v" in sys.argv))
     print(build_host_adapter_test())
+    print(build_pybind_shim())

@@ -9,7 +9,6 @@ current CUDA stream.  torch is used only to own memory and streams.
 Like the reference, the calls return as soon as the kernel is enqueued on the current stream;
 callers record an event and synchronise (kv_cache_manager/py_connector/vllm/data_transfer.py:138-150).
 """
-import ctypes
 import os
 from typing import List, Optional, Sequence, Union
 
@@ -75,10 +74,10 @@ def _move(entry: str, kv_caches_ptrs_tensor: torch.Tensor, staging: torch.Tensor
     n_slots = staging.numel() * staging.element_size() // slot_bytes if slot_bytes else 0
     _cabi.bind_device(device.index)
     with torch.cuda.device(device):
-        _cabi.call(entry, kv_caches_ptrs_tensor.data_ptr(), n_pools, staging.data_ptr(), n_slots, rows.data_ptr(),
-                   slots.data_ptr() if slots is not None else None, n_blocks, rows_per_block, row_bytes,
-                   _NO_BOUND if pool_rows is None else pool_rows,
-                   status.data_ptr() if status is not None else None, int(sm_count or 0), _stream())
+        _cabi.call_move(entry, kv_caches_ptrs_tensor.data_ptr(), n_pools, staging.data_ptr(), n_slots,
+                        rows.data_ptr(), slots.data_ptr() if slots is not None else None, n_blocks, rows_per_block,
+                        row_bytes, _NO_BOUND if pool_rows is None else pool_rows,
+                        status.data_ptr() if status is not None else None, int(sm_count or 0), _stream())
     # keep the index tensors alive until the stream has consumed them
     rows.record_stream(torch.cuda.current_stream())
     if slots is not None:
@@ -108,10 +107,10 @@ def _move_through_bounce(entry, kv_caches_ptrs_tensor, staging, rows, slot_indic
     name = "kvcm_b200_save_rows_to_host" if "gather" in entry else "kvcm_b200_load_rows_from_host"
     _cabi.bind_device(device.index)
     with torch.cuda.device(device):
-        _cabi.call(name, kv_caches_ptrs_tensor.data_ptr(), n_pools, staging.data_ptr(), n_slots, rows.data_ptr(),
-                   slots.ctypes.data_as(ctypes.c_void_p) if slots is not None else None, n_blocks, rows_per_block,
-                   row_bytes, _NO_BOUND if pool_rows is None else pool_rows, bounce.data_ptr(), bounce.numel(),
-                   status.data_ptr() if status is not None else None, _stream())
+        _cabi.call_move(name, kv_caches_ptrs_tensor.data_ptr(), n_pools, staging.data_ptr(), n_slots,
+                        rows.data_ptr(), slots.ctypes.data if slots is not None else None, n_blocks, rows_per_block,
+                        row_bytes, _NO_BOUND if pool_rows is None else pool_rows, bounce.data_ptr(), bounce.numel(),
+                        status.data_ptr() if status is not None else None, _stream())
     rows.record_stream(torch.cuda.current_stream())
     bounce.record_stream(torch.cuda.current_stream())
 

@@ -21,7 +21,7 @@ def _legacy(entry: str, kv_caches_ptrs: torch.Tensor, total_token_in_kvcache: in
     hidden_bytes = tensor.shape[-1] * tensor.element_size()
     _cabi.bind_device(kv_caches_ptrs.device.index)
     with torch.cuda.device(kv_caches_ptrs.device):
-        _cabi.call(entry, kv_caches_ptrs.data_ptr(), kv_caches_ptrs.shape[0], total_token_in_kvcache,
+        _cabi.call_move(entry, kv_caches_ptrs.data_ptr(), kv_caches_ptrs.shape[0], total_token_in_kvcache,
                    tensor.data_ptr(), idx.data_ptr(), idx.numel(), hidden_bytes, _stream())
     idx.record_stream(torch.cuda.current_stream())
 

@@ -193,6 +193,28 @@ def test_host_staging_in_groups_smaller_than_the_batch(monkeypatch):
         batch_gather_kv_pages(ptrs, staging, torch.from_numpy(table[:ppb]), [n_slots], ppb, page_bytes, pool_pages)
 
 
+def test_pybind_shim_and_ctypes_routes_agree(monkeypatch):
+    """The operators reach the C ABI through the pybind shim when it is built; ctypes is the same call."""
+    if _cabi.shim() is None:
+        pytest.skip("pybind shim not built")
+    host, dev, ptrs = _make(77, 4, 512, 4096)
+    table = torch.randperm(512)[:64].to(torch.int32)
+    via_shim = torch.zeros(16 * 4 * 4 * 4096, dtype=torch.uint8, device=DEV)
+    via_ctypes = torch.zeros_like(via_shim)
+    pinned = torch.zeros(16 * 4 * 4 * 4096, dtype=torch.uint8, pin_memory=True)
+    batch_gather_kv_pages(ptrs, via_shim, table, None, 4, 4096, 512)
+    batch_gather_kv_pages(ptrs, pinned, table, list(range(16)), 4, 4096, 512)
+    monkeypatch.setattr(_cabi, "_shim", None)
+    batch_gather_kv_pages(ptrs, via_ctypes, table, None, 4, 4096, 512)
+    torch.cuda.synchronize()
+    assert torch.equal(via_shim, via_ctypes) and via_shim.any()
+    assert torch.equal(pinned, via_shim.cpu())
+    with pytest.raises(_cabi.KvcmError):
+        monkeypatch.undo()
+        _cabi.call_move("kvcm_b200_gather_pages", ptrs.data_ptr(), 0, via_shim.data_ptr(), 1, table.data_ptr(), None,
+                        1, 1, 16, 1, None, 0, None)
+
+
 def test_page_table_form_equals_token_form():
     # Llama-3-8B geometry, shrunk: page 16 tokens x 2 KiB, block = 4 pages = 64 tokens
     n_pools, pool_pages, page_tokens, tok_bytes, pages_per_block, n_blocks = 6, 256, 16, 2048, 4, 40
