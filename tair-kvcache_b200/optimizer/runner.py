@@ -1,0 +1,88 @@
+"""Trace file -> per-instance replay on the GPU -> hit-rate table, the shape of OptimizerRunner::Run followed by
+HitAnalysis::Analyze (kv_cache_manager/optimizer/manager/optimizer_runner.cc:13-68,
+kv_cache_manager/optimizer/analysis/result_analysis.cc:10-113), for configurations without eviction."""
+import os
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+from ..manager.hash_util import ApplyPrefixHashBatch
+from . import trace_reader as tr
+from .replay import RunTraces
+
+CSV_HEADER = ("TimestampUs,CachedBlocksCurrentInstance,CachedBlocksPerInstance,CachedBlocksAllInstance,"
+              "InternalReadBlocks,ExternalReadBlocks,TotalReadBlocks,InternalHitBlocks,"
+              "InternalHitRate,ExternalHitBlocks,ExternalHitRate,HitRate,AccInternalHitRate,AccExternalHitRate,"
+              "AccHitRate\n")
+
+
+def _g(x: float) -> str:
+    """A double as a C++ ostream prints it by default (6 significant digits)."""
+    return "%g" % x
+
+
+def replay_instance(traces: List[tr.Trace], device, rw_separation: bool = False) -> Dict[str, np.ndarray]:
+    """Replays the traces of one instance.  As OptimizerRunner::RunTrace does, only prefix_match queries are
+    replayed, dialog turns are skipped in read/write-separation mode and Get/Write traces are skipped otherwise."""
+    keep = []
+    for t in traces:
+        if t.kind != tr.WRITE_CACHE and t.query_type != "prefix_match":
+            continue
+        if (t.kind == tr.DIALOG_TURN) == rw_separation:
+            continue
+        keep.append(t)
+    keys, off, kind, mask, read = tr.to_csr(keep)
+    d_keys, d_off = torch.from_numpy(keys).to(device), torch.from_numpy(off).to(device)
+    if any(t.needs_prefix_hash for t in keep):  # Qwen-Bailian ids: chain them first
+        d_keys = ApplyPrefixHashBatch(d_keys, d_off)
+    res = RunTraces(d_keys, d_off, torch.from_numpy(kind).to(device), torch.from_numpy(mask).to(device))
+    ext, inte, wr, size = (x.cpu().numpy() for x in res)
+    ts = np.array([t.timestamp_us for t in keep], dtype=np.int64)
+    # GetLocation: masked keys are internal reads; a dialog turn reads its query keys externally and replays total_keys
+    internal_read = np.where(kind == tr.GET_LOCATION, mask, 0)
+    external_read = np.where(kind == tr.WRITE_CACHE, 0, read - internal_read)
+    return dict(timestamp_us=ts, kind=kind, external_read_blocks=external_read, internal_read_blocks=internal_read,
+                external_hit_blocks=ext, internal_hit_blocks=inte, write_blocks=wr, current_cache_blocks=size)
+
+
+def export_hit_rates(path: str, rec: Dict[str, np.ndarray]) -> None:
+    """`<instance>_hit_rates.csv` of HitAnalysis::ExportHitRates (result_analysis.cc:64-113): one line per read
+    record, same columns, separators and number formatting; one instance per file, so the per-instance column holds
+    this instance's cached blocks."""
+    reads = rec["kind"] != tr.WRITE_CACHE
+    acc_total = acc_ext = acc_int = 0
+    with open(path, "w") as f:
+        f.write(CSV_HEADER)
+        for i in np.nonzero(reads)[0]:
+            ir, er = int(rec["internal_read_blocks"][i]), int(rec["external_read_blocks"][i])
+            ih, eh = int(rec["internal_hit_blocks"][i]), int(rec["external_hit_blocks"][i])
+            total = ir + er
+            ext_rate = eh / total if total else 0.0
+            int_rate = ih / total if total else 0.0
+            acc_total, acc_ext, acc_int = acc_total + total, acc_ext + eh, acc_int + ih
+            acc_e = acc_ext / acc_total if acc_total else 0.0
+            acc_i = acc_int / acc_total if acc_total else 0.0
+            cached = int(rec["current_cache_blocks"][i])
+            f.write(", ".join([str(int(rec["timestamp_us"][i])), str(cached), str(cached), str(cached), str(ir),
+                               str(er), str(total), str(ih), _g(int_rate), str(eh), _g(ext_rate),
+                               _g(int_rate + ext_rate), _g(acc_i), _g(acc_e), _g(acc_i + acc_e)]) + "\n")
+
+
+def run_trace_file(trace_path: str, trace_type: str, output_dir: str, device=None,
+                   block_sizes: Optional[Dict[str, int]] = None, rw_separation: bool = False
+                   ) -> Dict[str, Dict[str, np.ndarray]]:
+    """Loads a trace file, replays every instance on the GPU and writes `<instance>_hit_rates.csv` per instance."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    traces = tr.load_traces(trace_path, trace_type, block_sizes)
+    by_instance: Dict[str, List[tr.Trace]] = {}
+    for t in traces:
+        by_instance.setdefault(t.instance_id, []).append(t)
+    os.makedirs(output_dir, exist_ok=True)
+    out = {}
+    for instance_id, ts in sorted(by_instance.items()):
+        rec = replay_instance(ts, device, rw_separation)
+        if (rec["kind"] != tr.WRITE_CACHE).any():
+            export_hit_rates(os.path.join(output_dir, instance_id + "_hit_rates.csv"), rec)
+        out[instance_id] = rec
+    return out

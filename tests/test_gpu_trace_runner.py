@@ -1,0 +1,76 @@
+"""Trace file -> GPU replay -> hit-rate CSV, against the sequential oracle replay of the same traces."""
+import json
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import kvcm_oracle as oracle
+
+import tair_kvcache_b200  # noqa: F401
+from tair_kvcache_b200.optimizer import run_trace_file, trace_reader as tr
+from tair_kvcache_b200.optimizer.runner import CSV_HEADER
+
+pytestmark = pytest.mark.gpu
+
+
+def _write_qwen_trace(path, rng, n):
+    """Dialog turns whose per-block ids share prefixes with earlier turns."""
+    seqs = []
+    with open(path, "w") as f:
+        for i in range(n):
+            ids = rng.integers(1, 1 << 40, size=int(rng.integers(0, 30))).tolist()
+            if seqs and rng.random() < 0.7:
+                src = seqs[int(rng.integers(0, len(seqs)))]
+                m = int(rng.integers(0, min(len(src), len(ids)) + 1))
+                ids[:m] = src[:m]
+            seqs.append(ids)
+            f.write(json.dumps({"timestamp": float(n - i) + 0.5, "hash_ids": ids, "input_length": len(ids) * 16,
+                                "output_length": 1}) + "\n")  # descending timestamps: the loader must sort
+    return seqs
+
+
+def test_qwen_bailian_file_end_to_end(tmp_path):
+    rng = np.random.default_rng(8)
+    path = tmp_path / "trace.jsonl"
+    seqs = _write_qwen_trace(path, rng, 400)
+    out = run_trace_file(str(path), "qwen_bailian", str(tmp_path / "out"), device="cuda:0")
+    rec = out["instance"]
+    # oracle: ApplyPrefixHash per turn, turns in timestamp order (= reversed file order), sequential replay
+    ordered = seqs[::-1]
+    keys = [oracle.apply_prefix_hash(s) for s in ordered]
+    off = np.zeros(len(keys) + 1, dtype=np.int64)
+    np.cumsum([len(k) for k in keys], out=off[1:])
+    want = oracle.Replay().run(np.concatenate(keys), off, np.zeros(len(keys), dtype=np.uint8))
+    assert np.array_equal(rec["external_hit_blocks"], want[0]) and np.array_equal(rec["write_blocks"], want[2])
+    assert np.array_equal(rec["current_cache_blocks"], want[3]) and want[0].sum() > 0
+    lines = (tmp_path / "out" / "instance_hit_rates.csv").read_text().splitlines()
+    assert lines[0] + "\n" == CSV_HEADER and len(lines) == 401
+    # last line: accumulated external hit rate = all hits / all reads, printed like a C++ double
+    acc = want[0].sum() / sum(len(s) for s in seqs)
+    assert lines[-1].split(", ")[-1] == "%g" % acc and lines[-1].split(", ")[0] == "400500000"
+
+
+def test_publisher_log_file_in_both_replay_modes(tmp_path):
+    def ev(kind, ts, **kw):
+        return json.dumps(dict(type=kind, source="i1", trigger_time_us=ts, **kw))
+    path = tmp_path / "pub.log"
+    path.write_text("\n".join([
+        ev("GetCacheLocation", 10, query_type="prefix_match", keys=[1, 2, 3, 4], block_mask=0),
+        ev("StartWriteCache", 20, write_session_id="a", keys=[1, 2, 3, 4, 5]),
+        ev("FinishWriteCache", 30, write_session_id="a"),
+        ev("GetCacheLocation", 40, query_type="prefix_match", keys=[1, 2, 3, 9], block_mask=1),
+        ev("StartWriteCache", 50, write_session_id="b", keys=[1, 2, 3, 9, 10]),
+        ev("FinishWriteCache", 60, write_session_id="b")]))
+    # dialog-turn mode: turn 1 writes 5 blocks, turn 2 hits [1,2,3] and writes [9,10]
+    rec = run_trace_file(str(path), "publisher_log", str(tmp_path / "o1"), "cuda:0", {"i1": 64})["i1"]
+    assert rec["kind"].tolist() == [tr.DIALOG_TURN, tr.DIALOG_TURN]
+    assert rec["external_hit_blocks"].tolist() == [0, 3] and rec["write_blocks"].tolist() == [5, 2]
+    assert rec["external_read_blocks"].tolist() == [4, 4] and rec["current_cache_blocks"].tolist() == [5, 7]
+    # read/write-separation mode: Get(10) misses, Write(30) writes 5, Get(40) masks key 1 (internal) and hits 2,3
+    rec = run_trace_file(str(path), "publisher_log", str(tmp_path / "o2"), "cuda:0", {"i1": 64}, rw_separation=True)["i1"]
+    assert rec["kind"].tolist() == [tr.GET_LOCATION, tr.WRITE_CACHE, tr.GET_LOCATION, tr.WRITE_CACHE]
+    assert rec["external_hit_blocks"].tolist() == [0, 0, 2, 0] and rec["internal_hit_blocks"].tolist() == [0, 0, 1, 0]
+    assert rec["write_blocks"].tolist() == [0, 5, 0, 2] and rec["internal_read_blocks"].tolist() == [0, 0, 1, 0]
+    csv = (tmp_path / "o2" / "i1_hit_rates.csv").read_text().splitlines()
+    assert len(csv) == 3 and csv[2] == "40, 5, 5, 5, 1, 3, 4, 1, 0.25, 2, 0.5, 0.75, 0.125, 0.25, 0.375"

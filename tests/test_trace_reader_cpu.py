@@ -1,0 +1,79 @@
+"""The trace-file readers (host logic) on hand-made lines that exercise the rules of the reference's converters."""
+import json
+
+import numpy as np
+import pytest
+
+import tair_kvcache_b200  # noqa: F401
+from tair_kvcache_b200.optimizer import trace_reader as tr
+
+
+def _lines(*docs):
+    return [json.dumps(d) for d in docs]
+
+
+def test_qwen_bailian_lines_become_dialog_turns_with_raw_ids():
+    t = tr.read_qwen_bailian(_lines({"timestamp": 1.5, "hash_ids": [100, 200, 300], "input_length": 48,
+                                     "output_length": 7}, {"timestamp": 0.25, "hash_ids": []}) + ["not json", ""])
+    assert [x.kind for x in t] == [tr.DIALOG_TURN, tr.DIALOG_TURN]
+    assert t[0].timestamp_us == 1500000 and t[0].keys == [100, 200, 300] and t[0].needs_prefix_hash
+    assert t[0].instance_id == "instance" and t[0].input_len == 48 and t[0].output_len == 7
+    assert t[1].timestamp_us == 250000 and t[1].keys == []
+
+
+def test_optimizer_schema_type_is_inferred_from_the_fields():
+    t = tr.read_optimizer_schema(_lines(
+        {"instance_id": "a", "timestamp_us": 3, "keys": [1, 2], "query_type": "prefix_match", "block_mask": 1,
+         "sw_size": 0, "input_len": 128, "output_len": 64, "total_keys": [1, 2, 3]},
+        {"instance_id": "a", "timestamp_us": 1, "keys": [1, 2], "query_type": "prefix_match",
+         "block_mask": [True, False]},
+        {"instance_id": "b", "timestamp_us": 2, "keys": [9]}))
+    assert [x.kind for x in t] == [tr.DIALOG_TURN, tr.GET_LOCATION, tr.WRITE_CACHE]
+    assert t[0].total_keys == [1, 2, 3] and t[0].block_mask == 1 and t[0].replay_keys() == [1, 2, 3]
+    assert t[1].block_mask == [True, False] and t[2].instance_id == "b"
+
+
+def test_publisher_log_events_are_paired_like_the_reference():
+    lines = _lines(
+        {"type": "GetCacheLocation", "source": "i1", "trigger_time_us": 10, "query_type": "prefix_match",
+         "keys": [1, 2, 3, 99], "block_mask": 1, "sw_size": -1},
+        {"type": "GetCacheLocation", "source": "other", "trigger_time_us": 11, "keys": [5]},       # unknown instance
+        {"type": "StartWriteCache", "source": "i1", "trigger_time_us": 20, "write_session_id": "s1",
+         "keys": [1, 2, 3, 4, 5]},                                                                # opens with [1,2,3]
+        {"type": "FinishWriteCache", "source": "i1", "trigger_time_us": 30, "write_session_id": "s1",
+         "success_block": 5},
+        {"type": "StartWriteCache", "source": "i1", "trigger_time_us": 40, "write_session_id": "s2", "keys": [7, 8]},
+        {"type": "GetCacheLocation", "source": "i1", "trigger_time_us": 50, "query_type": "prefix_match",
+         "keys": [7, 8, 9], "block_mask": [True, False, False]},
+        {"type": "FinishWriteCache", "source": "i1", "trigger_time_us": 60, "write_session_id": "nope"})
+    t = tr.read_publisher_log(lines, {"i1": 64})
+    kinds = [(x.kind, x.timestamp_us) for x in t]
+    # the first Get, its dialog turn (keeps the Get's timestamp), the finished write (finish time), then what was
+    # left pending: the unfinished write (+100 ms) and the unmatched Get as a dialog turn over its own keys
+    assert kinds == [(tr.GET_LOCATION, 10), (tr.DIALOG_TURN, 10), (tr.WRITE_CACHE, 30), (tr.GET_LOCATION, 50),
+                     (tr.WRITE_CACHE, 100040), (tr.DIALOG_TURN, 50)]
+    turn = t[1]
+    assert turn.keys == [1, 2, 3, 99] and turn.total_keys == [1, 2, 3, 4, 5]
+    assert turn.input_len == 4 * 64 and turn.output_len == (5 - 3) * 64 and turn.block_mask == 1
+    assert t[5].total_keys == [7, 8, 9] and t[5].output_len == 0
+
+
+def test_load_traces_sorts_by_timestamp_and_csr_layout(tmp_path):
+    p = tmp_path / "schema.jsonl"
+    p.write_text("\n".join(_lines(
+        {"instance_id": "a", "timestamp_us": 30, "keys": [1, 2, 4], "query_type": "prefix_match", "block_mask": 1},
+        {"instance_id": "a", "timestamp_us": 10, "keys": [1, 2, 3]})))
+    t = tr.load_traces(str(p), "optimizer_schema")
+    assert [x.timestamp_us for x in t] == [10, 30]
+    keys, off, kind, mask, read = tr.to_csr(t)
+    assert keys.tolist() == [1, 2, 3, 1, 2, 4] and off.tolist() == [0, 3, 6]
+    assert kind.tolist() == [tr.WRITE_CACHE, tr.GET_LOCATION] and mask.tolist() == [0, 1] and read.tolist() == [0, 3]
+    with pytest.raises(ValueError):
+        tr.load_traces(str(p), "nonsense")
+
+
+def test_mask_offset_rules():
+    assert tr.mask_offset(None, 5) == 0 and tr.mask_offset(3, 5) == 3 and tr.mask_offset(9, 5) == 5
+    assert tr.mask_offset([True, True, False], 3) == 2 and tr.mask_offset([], 3) == 0
+    with pytest.raises(ValueError):
+        tr.mask_offset([True, False, True], 3)
