@@ -7,6 +7,7 @@
 //   GpuBlockIndex        the device replica of MetaIndexer's table (kv_cache_manager/meta/meta_indexer.cc:419-440)
 //   GpuMetaSearcher      PrefixMatch / ReverseRollSlideWindowMatch / BatchGet
 //       kv_cache_manager/manager/meta_searcher.cc:74-265, batch-of-one and batched forms
+//   GpuTraceReplayer     OptimizerRunner::RunTraces without eviction (kv_cache_manager/optimizer/manager/optimizer_runner.cc:29-215)
 //   IovCopier            the per-Iov loops of kv_cache_manager/client/src/internal/sdk/local_file_sdk.cc:223-245,326-353
 //
 // Header-only, C++17, needs only <cuda_runtime.h> and kvcm_b200.h.  Every call stages its
@@ -62,12 +63,13 @@ public:
     Mirror(const Mirror &) = delete;
     Mirror &operator=(const Mirror &) = delete;
     ~Mirror() { Release(); }
-    bool Reserve(size_t bytes) {
+    // device_only: no pinned twin (scratch that never crosses PCIe).
+    bool Reserve(size_t bytes, bool device_only = false) {
         if (bytes <= capacity_) return true;
         Release();
         size_t cap = 4096;
         while (cap < bytes) cap <<= 1;
-        if (cudaMallocHost(&host_, cap) != cudaSuccess || cudaMalloc(&dev_, cap) != cudaSuccess) {
+        if ((!device_only && cudaMallocHost(&host_, cap) != cudaSuccess) || cudaMalloc(&dev_, cap) != cudaSuccess) {
             cudaGetLastError();
             Release();
             return false;
@@ -341,6 +343,83 @@ private:
     uint32_t avail_mask_;
     cudaStream_t stream_;
     detail::Mirror keys_, key_off_, bits_, out_;
+};
+
+// Trace replay without eviction, the loop of OptimizerRunner::RunTraces
+// (kv_cache_manager/optimizer/manager/optimizer_runner.cc:29-215) for the traces of one instance.
+enum class TraceKind : uint8_t { DialogTurn = 0, GetLocation = 1, WriteCache = 2 };
+
+struct ReplayTrace {
+    TraceKind kind;
+    KeyVector keys;            // DialogTurn: total_keys; GetLocation / WriteCache: keys
+    BlockMaskOffset mask = 0;  // GetLocation: number of leading masked (engine-resident) keys
+};
+
+// What the reference records per trace (ReadRecord / WriteRecord,
+// kv_cache_manager/optimizer/analysis/result_structure.h:15-32).
+struct ReplayRecord {
+    int32_t external_hit_blocks;
+    int32_t internal_hit_blocks;
+    int32_t write_blocks;
+    int64_t current_cache_blocks;
+};
+
+class GpuTraceReplayer {
+public:
+    explicit GpuTraceReplayer(cudaStream_t stream = nullptr) : stream_(stream) {}
+
+    // Traces in replay (timestamp) order; keys must be prefix-unique chained block keys.
+    int32_t RunTraces(const std::vector<ReplayTrace> &traces, std::vector<ReplayRecord> *records) {
+        const int32_t n = static_cast<int32_t>(traces.size());
+        records->assign(n, ReplayRecord{0, 0, 0, 0});
+        if (n == 0) return KVCM_OK;
+        int64_t n_keys = 0;
+        for (const auto &t : traces) n_keys += static_cast<int64_t>(t.keys.size());
+        const int64_t ws_bytes = kvcm_b200_replay_workspace_bytes(n_keys);
+        if (ws_bytes < 0) return KVCM_EC_BADARGS;
+        const size_t off_bytes = sizeof(int64_t) * (n + 1);
+        if (!keys_.Reserve(sizeof(int64_t) * (n_keys + 1)) || !off_.Reserve(off_bytes) || !kind_.Reserve(n) ||
+            !mask_.Reserve(sizeof(int64_t) * n) || !ext_.Reserve(sizeof(int32_t) * n) ||
+            !int_.Reserve(sizeof(int32_t) * n) || !wr_.Reserve(sizeof(int32_t) * n) ||
+            !size_.Reserve(sizeof(int64_t) * n) || !workspace_.Reserve(static_cast<size_t>(ws_bytes), true)) {
+            return KVCM_EC_NOSPC;
+        }
+        int64_t at = 0;
+        for (int32_t i = 0; i < n; ++i) {
+            off_.host<int64_t>()[i] = at;
+            if (!traces[i].keys.empty()) {
+                std::memcpy(keys_.host<int64_t>() + at, traces[i].keys.data(), sizeof(int64_t) * traces[i].keys.size());
+            }
+            at += static_cast<int64_t>(traces[i].keys.size());
+            kind_.host<uint8_t>()[i] = static_cast<uint8_t>(traces[i].kind);
+            mask_.host<int64_t>()[i] = static_cast<int64_t>(traces[i].mask);
+        }
+        off_.host<int64_t>()[n] = at;
+        if (!keys_.ToDevice(sizeof(int64_t) * n_keys, stream_) || !off_.ToDevice(off_bytes, stream_) ||
+            !kind_.ToDevice(n, stream_) || !mask_.ToDevice(sizeof(int64_t) * n, stream_)) {
+            return KVCM_ER_CUDAMEMCPY_ERROR;
+        }
+        int32_t rc = kvcm_b200_replay(keys_.dev<int64_t>(), off_.dev<int64_t>(), kind_.dev<uint8_t>(),
+                                      mask_.dev<int64_t>(), n, n_keys, workspace_.dev<void>(), ws_bytes,
+                                      ext_.dev<int32_t>(), int_.dev<int32_t>(), wr_.dev<int32_t>(),
+                                      size_.dev<int64_t>(), nullptr, stream_);
+        if (rc != KVCM_OK) return rc;
+        if (!ext_.ToHost(sizeof(int32_t) * n, stream_) || !int_.ToHost(sizeof(int32_t) * n, stream_) ||
+            !wr_.ToHost(sizeof(int32_t) * n, stream_) || !size_.ToHost(sizeof(int64_t) * n, stream_)) {
+            return KVCM_ER_CUDAMEMCPY_ERROR;
+        }
+        rc = detail::Sync(stream_);
+        if (rc != KVCM_OK) return rc;
+        for (int32_t i = 0; i < n; ++i) {
+            (*records)[i] = ReplayRecord{ext_.host<int32_t>()[i], int_.host<int32_t>()[i], wr_.host<int32_t>()[i],
+                                         size_.host<int64_t>()[i]};
+        }
+        return KVCM_OK;
+    }
+
+private:
+    cudaStream_t stream_;
+    detail::Mirror keys_, off_, kind_, mask_, ext_, int_, wr_, size_, workspace_;
 };
 
 // kv_cache_manager/client/include/common.h:94-116

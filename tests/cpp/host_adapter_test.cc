@@ -157,6 +157,29 @@ static void TestIovCopier() {
     cudaFree(d_back);
 }
 
+static void TestReplay() {
+    // kv_cache_manager/optimizer/test/optimizer_manager_py_test.py:57-84: write [1,2,3], query [1,2,4] -> hit 2
+    GpuTraceReplayer replayer;
+    std::vector<ReplayRecord> rec;
+    EXPECT_EQ(replayer.RunTraces({{TraceKind::WriteCache, {1, 2, 3}}, {TraceKind::GetLocation, {1, 2, 4}}}, &rec),
+              KVCM_OK);
+    EXPECT_EQ(rec[0].write_blocks, 3);
+    EXPECT_EQ(rec[1].external_hit_blocks, 2);
+    EXPECT_EQ(rec[1].current_cache_blocks, 3);
+    // dialog turns read and write in one step; a masked key that is cached counts as an internal hit
+    EXPECT_EQ(replayer.RunTraces({{TraceKind::DialogTurn, {1, 2, 3}},
+                                  {TraceKind::DialogTurn, {1, 2, 4, 5}},
+                                  {TraceKind::GetLocation, {1, 2, 4}, 1}},
+                                 &rec),
+              KVCM_OK);
+    EXPECT_EQ(rec[1].external_hit_blocks, 2);
+    EXPECT_EQ(rec[1].write_blocks, 2);
+    EXPECT_EQ(rec[2].external_hit_blocks, 2);
+    EXPECT_EQ(rec[2].internal_hit_blocks, 1);
+    EXPECT_EQ(rec[2].current_cache_blocks, 5);
+    EXPECT_EQ(replayer.RunTraces({}, &rec), KVCM_OK);
+}
+
 int main() {
     int32_t sms = 0;
     if (kvcm_b200_device_info(&sms, nullptr, nullptr, nullptr) != KVCM_OK) {
@@ -167,6 +190,7 @@ int main() {
     TestPrefixMatch();
     TestSlidingWindowAndBatchGet();
     TestIovCopier();
+    TestReplay();
     std::printf(g_failed == 0 ? "host adapter test: all checks passed\n" : "host adapter test: %d checks FAILED\n", g_failed);
     return g_failed == 0 ? 0 : 1;
 }
