@@ -883,6 +883,105 @@ def main_replay(args, rank, world):
         dist.destroy_process_group()
 
 
+def main_window_reference(args):
+    """CPU arm of --workload c4 on a bounded sample: the same length / sharing distributions at 1/32 of the requests
+    and of the index, hashed and matched by the oracle with all host threads."""
+    from oracle import kvcm_oracle as oracle
+    threads = os.cpu_count() or 1
+    n_req, n_roots, bs, sw = (args.n_requests or 65536) // 32, 64, 16, 256
+    rng = np.random.default_rng(0xB2000004)
+
+    def loguniform(n):
+        return np.exp(rng.uniform(np.log(256), np.log(131072), size=n)).astype(np.int64)
+
+    root_len, req_len = loguniform(n_roots), loguniform(n_req)
+    zipf = 1.0 / np.arange(1, n_roots + 1) ** 1.1
+    root_of = rng.choice(n_roots, size=n_req, p=zipf / zipf.sum())
+    roots = [rng.integers(0, 151936, size=n, dtype=np.int64).astype(np.uint32) for n in root_len]
+    reqs = []
+    for r in range(n_req):
+        t = rng.integers(0, 151936, size=req_len[r], dtype=np.int64).astype(np.uint32)
+        m = int(rng.random() * (min(req_len[r], root_len[root_of[r]]) + 1))
+        t[:m] = roots[root_of[r]][:m]
+        reqs.append(t)
+    off = np.zeros(n_req + 1, dtype=np.int64)
+    np.cumsum(req_len, out=off[1:])
+    toks = np.concatenate(reqs)
+    ox = oracle.Index()
+    for t in roots:
+        ox.put_uniform(oracle.gen_key_vector(t, bs))
+    keys0, ko0 = oracle.hash_blocks(toks, off, bs, threads=threads)
+    ox.put_uniform(keys0[:int(ko0[n_req // 8])])
+    t_total, n = 0.0, 0
+    while t_total < 10.0 and n < 500:
+        t0 = time.perf_counter()
+        keys, ko = oracle.hash_blocks(toks, off, bs, threads=threads)
+        ox.prefix_match_batch(keys, ko, threads=threads)
+        ox.sw_match_batch(keys, ko, sw, threads=threads)
+        t_total += time.perf_counter() - t0
+        n += 1
+    value = int(ko0[-1]) * n / t_total
+    sample = "%d of %d requests (%d token blocks), index of %d keys, %d repetitions" % (
+        n_req, args.n_requests or 65536, int(ko0[-1]), len(ox), n)
+    print(json.dumps({"impl": "reference", "metric": "prefix_and_window_match_token_blocks_per_s", "value": value,
+                      "unit": "token-blocks/s", "n_gpus": args.gpus, "steps": n, "warmup": 0, "higher_is_better": True,
+                      "dtype": "int64", "data": "synthetic",
+                      "config": {"workload": "CPU restatement (hash + prefix + sliding-window match, without the "
+                                             "reference's per-key JSON parse) on a bounded sample"},
+                      "cpu_baseline": {"value": value, "unit": "token-blocks/s", "cores": threads, "kind": "port",
+                                       "sample": sample},
+                      "e2e": {"value": value, "unit": "token-blocks/s", "h2d_bytes_per_step": 0,
+                              "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
+
+
+def main_replay_reference(args):
+    """CPU arm of --workload c5 on a bounded sample: hash, sequential prefix-tree replay (one core, as the reference
+    replays), and a memcpy gather of the missed blocks from host-resident MLA pools with all host threads."""
+    from oracle import kvcm_oracle as oracle
+    threads = os.cpu_count() or 1
+    n_req, bs, n_prompts, n_layers, page_bytes, pool_pages = 2000, 64, 500, 61, 64 * 1152, 256
+    rng = np.random.default_rng(0xB2000005)
+    prompt_len = rng.integers(256, 2049, size=n_prompts)
+    req_len = rng.integers(256, 2049, size=n_req)
+    zipf = 1.0 / np.arange(1, n_prompts + 1) ** 0.9
+    prompt_of = rng.choice(n_prompts, size=n_req, p=zipf / zipf.sum())
+    prompts = [rng.integers(0, 151936, size=n, dtype=np.int64).astype(np.uint32) for n in prompt_len]
+    reqs = []
+    for r in range(n_req):
+        t = rng.integers(0, 151936, size=req_len[r], dtype=np.int64).astype(np.uint32)
+        m = int(rng.random() * (min(req_len[r], prompt_len[prompt_of[r]]) + 1))
+        t[:m] = prompts[prompt_of[r]][:m]
+        reqs.append(t)
+    off = np.zeros(n_req + 1, dtype=np.int64)
+    np.cumsum(req_len, out=off[1:])
+    toks = np.concatenate(reqs)
+    pools = [rng.integers(0, 256, size=pool_pages * page_bytes, dtype=np.uint8) for _ in range(n_layers)]
+    staging = np.zeros(128 * n_layers * page_bytes, dtype=np.uint8)
+    t_total, n, n_miss = 0.0, 0, 0
+    while t_total < 10.0 and n < 10:
+        t0 = time.perf_counter()
+        keys, ko = oracle.hash_blocks(toks, off, bs, threads=threads)
+        ext, _, wr, _ = oracle.Replay().run(keys, ko, np.zeros(n_req, dtype=np.uint8))
+        miss = np.concatenate([keys[ko[r] + ext[r]:ko[r + 1]] for r in range(n_req)])
+        pages = ((miss & 0x7FFFFFFF) % pool_pages).astype(np.int32)
+        for a in range(0, len(pages), 128):
+            chunk = pages[a:a + 128]
+            oracle.move_rows(pools, staging, chunk, None, 1, page_bytes, 0, threads=threads)
+        t_total += time.perf_counter() - t0
+        n, n_miss = n + 1, len(pages)
+    value = n_req * n / t_total
+    print(json.dumps({"impl": "reference", "metric": "mixed_replay_requests_per_s", "value": value, "unit": "requests/s",
+                      "n_gpus": args.gpus, "steps": n, "warmup": 0, "higher_is_better": True, "dtype": "int64+u8",
+                      "data": "synthetic",
+                      "config": {"workload": "CPU restatement (hash + sequential replay + memcpy gather of misses from "
+                                             "host-resident MLA pools) on a bounded sample"},
+                      "cpu_baseline": {"value": value, "unit": "requests/s", "cores": threads, "kind": "port",
+                                       "sample": "%d requests, %d missed blocks of 4.5 MB per step, %d repetitions"
+                                                 % (n_req, n_miss, n)},
+                      "e2e": {"value": value, "unit": "requests/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                      "gpu_launches": 0}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -909,16 +1008,14 @@ def main():
     if args.workload == "c5":
         if args.impl == "reference":
             if rank == 0:
-                print(json.dumps({"impl": "reference", "unavailable": "the mixed replay configuration is timed on the "
-                                  "GPU only; its sequential CPU restatement checks a sample inside the b200 arm"}))
+                main_replay_reference(args)
             return
         main_replay(args, rank, world)
         return
     if args.workload == "c4":
         if args.impl == "reference":
             if rank == 0:
-                print(json.dumps({"impl": "reference", "unavailable": "the sliding-window configuration is timed "
-                                  "on the GPU only; its CPU restatement checks a sample inside the b200 arm"}))
+                main_window_reference(args)
             return
         main_window(args, rank, world)
         return

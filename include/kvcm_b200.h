@@ -97,6 +97,8 @@ KVCM_API int32_t kvcm_b200_device_info(int32_t *sm_count, int64_t *l2_bytes, int
  * (batch_gather_scatter_helper.py:110,115).  0 = the library's choice: every SM when staging is device
  * memory, 16 when staging is host memory (the PCIe link is then the bound, and the other SMs stay free
  * for the engine and for a transfer in the opposite direction on another stream).
+ * Staging in pageable (unpinned, unregistered) host memory is refused with
+ * KVCM_ER_UNSUPPORTED_MEMORY_TYPE: pin or register it, or use the save / load entry points below.
  * Scattering the same row twice in one call is a data race, as in the reference.
  * Fastest when row_bytes and all base addresses are multiples of 16; any alignment is correct.
  * ---------------------------------------------------------------------------------------- */

@@ -485,14 +485,17 @@ int ResidentCtas() {
 // own kernels and for a transfer in the other direction.
 constexpr int kHostStagingSms = 16;
 
+// Returns 0 when `staging` is plain pageable host memory, which a kernel cannot address.
 int SmBudget(int32_t max_sms, const void *staging) {
     const int all = GetDeviceInfo().sm_count;
-    if (max_sms > 0) return max_sms < all ? max_sms : all;
     cudaPointerAttributes attr;
-    if (cudaPointerGetAttributes(&attr, staging) == cudaSuccess && attr.type == cudaMemoryTypeHost) {
-        return kHostStagingSms < all ? kHostStagingSms : all;
+    if (cudaPointerGetAttributes(&attr, staging) != cudaSuccess) {
+        cudaGetLastError();
+        return max_sms > 0 && max_sms < all ? max_sms : all;
     }
-    cudaGetLastError();
+    if (attr.type == cudaMemoryTypeUnregistered) return 0;
+    if (max_sms > 0) return max_sms < all ? max_sms : all;
+    if (attr.type == cudaMemoryTypeHost) return kHostStagingSms < all ? kHostStagingSms : all;
     return all;
 }
 
@@ -566,6 +569,7 @@ int32_t LaunchMove(bool gather, const void *const *d_ptrs, int32_t n_ptrs, int32
 
     cudaStream_t s = AsStream(stream);
     const int sms = SmBudget(max_sms, staging);
+    if (sms == 0) return KVCM_ER_UNSUPPORTED_MEMORY_TYPE;  // pageable host memory: pin it or use save/load_rows
     if (bulk_ok) {
         if (gather) {
             LaunchBulk<true>(p, geo.ctas_per_sm, sms, s);

@@ -327,6 +327,21 @@ def test_large_roundtrip_property():
         assert int((z != 0).any(dim=1).sum()) == n_blocks * ppb
 
 
+def test_pageable_host_staging_is_refused_not_dereferenced():
+    import ctypes
+    host, dev, ptrs = _make(31, 1, 16, 64)
+    pageable = np.zeros(4096, dtype=np.uint8)
+    rows = torch.arange(4, dtype=torch.int32, device=DEV)
+    _cabi.bind_device(0)
+    rc = _cabi.lib().kvcm_b200_gather_tokens(ptrs.data_ptr(), 1, pageable.ctypes.data, 4, rows.data_ptr(), None, 4, 1,
+                                             64, 16, None, 0, None)
+    assert rc == _cabi.KVCM_ER_UNSUPPORTED_MEMORY_TYPE
+    torch.cuda.synchronize()
+    assert not pageable.any()
+    with pytest.raises(ValueError):  # the Python operator says the same before reaching the library
+        batch_gather_kv_pages(ptrs, torch.from_numpy(pageable), rows, None, 1, 64, 16)
+
+
 def test_bad_arguments_return_codes():
     L = _cabi.lib()
     _cabi.bind_device(0)
