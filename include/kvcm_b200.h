@@ -218,9 +218,12 @@ KVCM_API int32_t kvcm_b200_iov_crc(const kvcm_b200_seg_t *d_segs, int32_t n_segs
  * d_req_order (optional, NULL = request order) is a permutation of [0, n_req) saying which request
  * each lane takes; listing requests longest first (kvcm_b200_length_order) groups chains of similar
  * length into one warp and starts the longest chains first, which matters for ragged batches.
- * warps_per_sm (0 = fill the SMs) caps the warps resident per SM; 4 gives every warp a scheduler of
- * its own, which is what a batch ruled by a few very long requests wants (kvcm_b200_length_order
- * suggests the value).  The keys written depend on neither.
+ * warps_per_sm (0 = fill the SMs) caps the hashing warps resident per SM; 4 gives every such warp a
+ * scheduler of its own, which is what a batch ruled by a few very long requests wants
+ * (kvcm_b200_length_order suggests the value).  The keys written depend on neither.
+ * Tokens reach shared memory by bulk copies that complete on mbarriers; every wait on one is bounded,
+ * and a warp whose wait ran out stops writing keys and counts itself in a per-device counter that
+ * kvcm_b200_hash_wait_timeouts reads (0 in any healthy run).
  * ---------------------------------------------------------------------------------------- */
 KVCM_API int32_t kvcm_b200_hash_blocks_u32(const uint32_t *d_tokens, int64_t n_tokens_total, const int64_t *d_tok_off,
                                            int32_t n_req, int32_t block_size, int64_t *d_keys,
@@ -230,6 +233,10 @@ KVCM_API int32_t kvcm_b200_hash_blocks_i64(const int64_t *d_tokens, int64_t n_to
                                            int32_t n_req, int32_t block_size, int64_t *d_keys,
                                            const int64_t *d_key_off, const int32_t *d_req_order,
                                            int32_t warps_per_sm, kvcm_stream_t stream);
+/* *h_count_out = warps of kvcm_b200_hash_blocks_* launches on the current device that gave up on a
+ * bounded wait since the library was loaded.  Synchronises with the device.  (No counterpart in the
+ * reference, whose hash runs on the CPU.) */
+KVCM_API int32_t kvcm_b200_hash_wait_timeouts(uint32_t *h_count_out);
 /* Host-only helper: h_order_out = requests sorted by token count, longest first (stable);
  * *warps_per_sm_out (optional) = the residency cap to pass along with that order. */
 KVCM_API int32_t kvcm_b200_length_order(const int64_t *h_tok_off, int32_t n_req, int32_t *h_order_out,

@@ -75,6 +75,7 @@ SIGNATURES = {
     "kvcm_b200_iov_crc": [_vp, _i32, _u64, _vp, _vp],
     "kvcm_b200_hash_blocks_u32": _HASH,
     "kvcm_b200_hash_blocks_i64": _HASH,
+    "kvcm_b200_hash_wait_timeouts": [_vp],
     "kvcm_b200_key_offsets": [_vp, _i32, _i32, _vp],
     "kvcm_b200_length_order": [_vp, _i32, _vp, _vp],
     "kvcm_b200_index_create": [_i64, _vp],

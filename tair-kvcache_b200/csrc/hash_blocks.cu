@@ -9,12 +9,12 @@
 // one lane walks one request.  What bounds the kernel is the latency of the chain, not HBM:
 // a request of L tokens takes L dependent steps however many SMs are idle.
 //
-// Token tiles are staged through shared memory.  Each lane owns a ring of kStages x 64 bytes;
-// it fills the ring with 16-byte cp.async copies from its own request (src-size clamped to
-// the token array's extent, so nothing outside the caller's buffer is read) and consumes a
-// stage with four conflict-free 128-bit shared loads.  The ring keeps kStages-1 stages (about
-// a hundred tokens) in flight per lane, which hides DRAM latency behind the chain itself.
+// Tokens are staged through shared memory by a producer warp with bulk copies (TMA); the consumer
+// warp runs the chains out of registers.  The two sections below describe the chain loop and the
+// staging ring.
 #include <algorithm>
+#include <mutex>
+#include <utility>
 #include <vector>
 
 #include "kvcm_common.cuh"
@@ -22,24 +22,18 @@
 namespace kvcm {
 namespace {
 
-constexpr int kStages = 8;  // power of two
-constexpr int kStageBytes = 64;                         // per lane
-constexpr int kPieces = kStageBytes / 16;               // cp.async pieces per lane per stage
-constexpr int kWarpRingBytes = kStages * kPieces * 32 * 16;  // 16 KiB
-constexpr int kMaxWarpsPerCta = 4;
+constexpr int kStageBytes = 64;            // bytes of one lane unpacked into registers at a time
+constexpr int kPieces = kStageBytes / 16;  // 128-bit shared loads per stage
+constexpr int kMinis = 4;                  // 64-byte stages per ring fill: one bulk copy brings 256 bytes of a request
+constexpr int kSlots = 3;                  // ring fills per warp: two in flight ahead of the one being hashed
+constexpr int kLaneStride = kMinis * kStageBytes + 16;  // an odd number of 16-byte words
+constexpr int kWarpRingBytes = kSlots * 32 * kLaneStride;  // 25.5 KiB
+constexpr int kMaxWarpsPerCta = 4;         // consumer warps; a CTA has as many producer warps again
 constexpr int kMaxHashSmemPerSm = 224 * 1024;
+// Consumer warps that fit on an SM (1 KiB of shared memory per CTA goes to the system).
+constexpr int kResidentWarpsPerSm = kMaxHashSmemPerSm / (kWarpRingBytes + 1024);
 // Batches of up to 16 x SMs x this many requests run with half-filled warps.
 constexpr int kHalfWarpSmMultiple = 2;
-
-__device__ __forceinline__ void CpAsync16(uint32_t smem_addr, uint64_t gmem_addr, uint32_t src_bytes) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr), "l"(gmem_addr), "r"(src_bytes)
-                 : "memory");
-}
-__device__ __forceinline__ void CpAsyncCommit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-template <int kPending>
-__device__ __forceinline__ void CpAsyncWait() {
-    asm volatile("cp.async.wait_group %0;\n" ::"n"(kPending) : "memory");
-}
 
 // What bounds this kernel is the latency of ONE lane's dependent chain (the longest request), and
 // for a lone warp on an SM the integer pipe takes two cycles per warp instruction.  So the loop is
@@ -52,7 +46,7 @@ __device__ __forceinline__ void CpAsyncWait() {
 //    16-byte copy grid is a per-lane constant), so only those few positions carry a predicated
 //    key store; other block sizes check every position;
 //  * only the first and last stage of a request, and blocks shorter than a stage, take the
-//    per-token checked path; staging copies of inner stages are four unconditional cp.async.
+//    per-token checked path.
 // With few requests (lanes_per_warp = 16) only half of each warp is used, so that twice as many
 // SMs work on the batch and the longest chains do not share a warp's issue slots more than needed.
 template <typename T, bool kAligned>
@@ -76,30 +70,49 @@ __device__ __forceinline__ void RunFullStage(uint64_t &h, const uint64_t (&vc)[k
     left -= kPerStage;
 }
 
-template <typename T, bool kAligned>
-__global__ void __launch_bounds__(kMaxWarpsPerCta * 32)
-    HashBlocksKernel(const T *__restrict__ tokens, int64_t n_tokens_total, const int64_t *__restrict__ tok_off,
-                     int32_t n_req, int32_t block_size, int64_t *__restrict__ keys,
-                     const int64_t *__restrict__ key_off, const int32_t *__restrict__ order,
-                     uint32_t lanes_per_warp) {
-    extern __shared__ __align__(16) uint8_t smem[];
-    constexpr int kPerPiece = 16 / sizeof(T);
-    constexpr int kPerStage = kStageBytes / sizeof(T);
-    constexpr uint64_t kGolden = 0x9e3779b97f4a7c15ull;
-    const uint32_t lane = LaneId();
-    const uint32_t warp = threadIdx.x >> 5;
-    const uint32_t warps_per_cta = blockDim.x >> 5;
-    const int64_t pos = (static_cast<int64_t>(blockIdx.x) * warps_per_cta + warp) * lanes_per_warp + lane;
-    const bool active = lane < lanes_per_warp && pos < n_req;
-    // `order` (optional) lists the requests longest first: lanes of one warp then walk chains of
-    // similar length, and the longest chains start first.
-    const int64_t req = active && order != nullptr ? order[pos] : pos;
+// ---------------------------------------------------------------------------------------------
+// The staging ring.  One lane = one request, so the 32 lanes of a warp read 32 unrelated places of
+// the token array.  Fetched with per-lane 16-byte copies that is 32 cache lines per warp instruction,
+// and with more than a few warps per SM the L1 tag stage, not the chain, sets the pace (measured:
+// 2.6x slower on 65,536 requests of 21k tokens).  Here a request is fetched kMinis x 64 bytes at a
+// time with ONE bulk copy (cp.async.bulk, global -> shared, completion counted on an mbarrier),
+// which goes through the TMA unit and bypasses L1.  A bulk copy costs its issuing warp some tens of
+// cycles per lane (about 900 cycles per warp-wide fill), so the copies are issued by a second warp: CTA = consumer warps [0, n) that run the chains + producer
+// warps [n, 2n), producer lane j fetching for consumer lane j.  Per consumer warp and ring slot
+// there is a `full` barrier (32 producer arrivals + the bytes in flight) and an `empty` barrier
+// (32 consumer arrivals once the slot has been read into registers).  A lane's bytes of a slot are
+// contiguous; lanes are kMinis*64+16 bytes apart, an odd number of 16-byte words, so the 128-bit
+// reads of a warp stay conflict-free.  Every wait is bounded: after kSpinLimit polls the warp
+// raises g_hash_wait_timeouts, waits once more (bounded) for the copies in flight, and returns.
+// ---------------------------------------------------------------------------------------------
+__device__ uint32_t g_hash_wait_timeouts = 0;
 
-    int64_t first_tok = 0, n_tok = 0, key_base = 0;
+// Where a lane's request lies in the token array, as the staging copies see it.
+template <typename T>
+struct LaneSpan {
+    uint64_t a0;          // 16-byte aligned start of the bytes to fetch
+    uint64_t fetch;       // bytes to fetch, a multiple of 16
+    uint64_t bulk_total;  // of which bulk copies bring this many (the rest is the piece at the array's end)
+    uint32_t over;        // bytes by which the last piece would overrun the token array (0..15)
+    int64_t n_stages;     // 64-byte stages
+    int64_t n_ring;       // ring fills
+    int head_skip;        // tokens of stage 0 that precede the request
+    int tail_count;       // valid tokens of the last stage
+    int64_t key_base;
+};
+
+template <typename T>
+__device__ __forceinline__ LaneSpan<T> DescribeLane(const T *tokens, int64_t n_tokens_total, const int64_t *tok_off,
+                                                    const int64_t *key_off, const int32_t *order, int64_t pos,
+                                                    bool active, int32_t block_size) {
+    LaneSpan<T> s;
+    const int64_t req = active && order != nullptr ? order[pos] : pos;
+    int64_t first_tok = 0, n_tok = 0;
+    s.key_base = 0;
     if (active) {
         first_tok = tok_off[req];
         n_tok = tok_off[req + 1] - first_tok;
-        key_base = key_off[req];
+        s.key_base = key_off[req];
     }
     // Only whole blocks are hashed; the trailing partial block is never read.
     const int64_t used = n_tok > 0 ? (n_tok / block_size) * block_size : 0;
@@ -107,52 +120,129 @@ __global__ void __launch_bounds__(kMaxWarpsPerCta * 32)
     const uint64_t arr_end = arr_beg + static_cast<uint64_t>(n_tokens_total) * sizeof(T);
     const uint64_t beg = arr_beg + static_cast<uint64_t>(first_tok) * sizeof(T);
     const uint64_t end = beg + static_cast<uint64_t>(used) * sizeof(T);
-    const uint64_t a0 = beg & ~15ull;  // arr_beg is 16-byte aligned, so a0 >= arr_beg
-    const uint64_t span = used > 0 ? end - a0 : 0;
-    const int64_t n_stages = static_cast<int64_t>((span + kStageBytes - 1) / kStageBytes);
-    const int64_t n_pieces = static_cast<int64_t>((span + 15) / 16);
-    // The last piece may hang over the end of the token array: copy only what exists.
-    const uint64_t last_piece = a0 + static_cast<uint64_t>(n_pieces > 0 ? n_pieces - 1 : 0) * 16;
-    const uint32_t last_piece_bytes = arr_end - last_piece >= 16 ? 16u : static_cast<uint32_t>(arr_end - last_piece);
-    const int head_skip = static_cast<int>((beg - a0) / sizeof(T));  // tokens of stage 0 before the request
-    const int tail_count =                                           // valid tokens of the last stage
-        static_cast<int>((span - static_cast<uint64_t>(n_stages > 0 ? n_stages - 1 : 0) * kStageBytes) / sizeof(T));
-    int64_t max_stages = n_stages;
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) {
-        const int64_t other = __shfl_xor_sync(0xffffffffu, max_stages, d);
-        max_stages = other > max_stages ? other : max_stages;
-    }
+    s.a0 = beg & ~15ull;  // arr_beg is 16-byte aligned, so a0 >= arr_beg
+    const uint64_t span = used > 0 ? end - s.a0 : 0;
+    s.n_stages = static_cast<int64_t>((span + kStageBytes - 1) / kStageBytes);
+    s.n_ring = (s.n_stages + kMinis - 1) / kMinis;
+    s.fetch = (span + 15) & ~15ull;
+    s.over = s.a0 + s.fetch > arr_end ? static_cast<uint32_t>(s.a0 + s.fetch - arr_end) : 0u;
+    s.bulk_total = s.over > 0 ? s.fetch - 16 : s.fetch;
+    s.head_skip = static_cast<int>((beg - s.a0) / sizeof(T));
+    s.tail_count =
+        static_cast<int>((span - static_cast<uint64_t>(s.n_stages > 0 ? s.n_stages - 1 : 0) * kStageBytes) / sizeof(T));
+    return s;
+}
 
-    const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(smem)) + warp * kWarpRingBytes + lane * 16;
-    auto issue = [&](int64_t s) {
-        const uint32_t dst = ring + (static_cast<uint32_t>(s) & (kStages - 1)) * (kPieces * 512);
-        const uint64_t src = a0 + static_cast<uint64_t>(s) * kStageBytes;
-        if (s + 1 < n_stages) {  // an inner stage: four whole pieces
+__device__ __forceinline__ bool BoundedWait(uint32_t bar, uint32_t parity) {
+    uint32_t spins = 0;
+    while (!MbarTryWait(bar, parity)) {
+        if (++spins >= kSpinLimit) return false;
+    }
+    return true;
+}
+
+template <typename T, bool kAligned>
+__global__ void __launch_bounds__(2 * kMaxWarpsPerCta * 32)
+    HashBlocksKernel(const T *__restrict__ tokens, int64_t n_tokens_total, const int64_t *__restrict__ tok_off,
+                         int32_t n_req, int32_t block_size, int64_t *__restrict__ keys,
+                         const int64_t *__restrict__ key_off, const int32_t *__restrict__ order,
+                         uint32_t lanes_per_warp, uint32_t warp_smem_bytes) {
+    static_assert(kMinis % 2 == 0 && kSlots >= 2 && (kLaneStride / 16) % 2 == 1, "ring geometry");
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ __align__(8) uint64_t full_bars[kMaxWarpsPerCta][kSlots];
+    __shared__ __align__(8) uint64_t empty_bars[kMaxWarpsPerCta][kSlots];
+    constexpr int kPerPiece = 16 / sizeof(T);
+    constexpr int kPerStage = kStageBytes / sizeof(T);
+    constexpr uint64_t kGolden = 0x9e3779b97f4a7c15ull;
+    constexpr uint32_t kFull = kMinis * kStageBytes;   // bytes of one lane in one ring slot
+    constexpr uint32_t kSlotBytes = 32 * kLaneStride;  // one ring slot of a warp
+    const uint32_t lane = LaneId();
+    const uint32_t n_consumers = blockDim.x >> 6;
+    const uint32_t warp_in_cta = threadIdx.x >> 5;
+    const bool producer = warp_in_cta >= n_consumers;
+    const uint32_t warp = producer ? warp_in_cta - n_consumers : warp_in_cta;  // the consumer warp served
+    const int64_t pos = (static_cast<int64_t>(blockIdx.x) * n_consumers + warp) * lanes_per_warp + lane;
+    const bool active = lane < lanes_per_warp && pos < n_req;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t w = 0; w < n_consumers; ++w) {
 #pragma unroll
-            for (int c = 0; c < kPieces; ++c) CpAsync16(dst + c * 512, src + c * 16, 16u);
-        } else if (s < n_stages) {  // the last stage: some pieces may be absent, the last one short
-            const int64_t p0 = s * kPieces;
-#pragma unroll
-            for (int c = 0; c < kPieces; ++c) {
-                if (p0 + c < n_pieces) {
-                    CpAsync16(dst + c * 512, src + c * 16, p0 + c == n_pieces - 1 ? last_piece_bytes : 16u);
-                }
+            for (int s = 0; s < kSlots; ++s) {
+                MbarInit(SmemAddr(&full_bars[w][s]), 32);
+                MbarInit(SmemAddr(&empty_bars[w][s]), 32);
             }
         }
-        CpAsyncCommit();
-    };
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async;\n" ::: "memory");
+    }
+    __syncthreads();
 
-    // Unpacks one stage from the ring into `token + golden` values (garbage beyond the request:
-    // the caller never consumes those).
-    auto unpack = [&](int64_t s, uint64_t (&vc)[kPerStage]) {
-        const uint32_t src = ring + (static_cast<uint32_t>(s) & (kStages - 1)) * (kPieces * 512);
+    const LaneSpan<T> sp =
+        DescribeLane<T>(tokens, n_tokens_total, tok_off, key_off, order, pos, active, block_size);
+    int64_t max_ring = sp.n_ring;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+        const int64_t other = __shfl_xor_sync(0xffffffffu, max_ring, d);
+        max_ring = other > max_ring ? other : max_ring;
+    }
+    const uint32_t full0 = SmemAddr(&full_bars[warp][0]);
+    const uint32_t empty0 = SmemAddr(&empty_bars[warp][0]);
+    const uint32_t ring = SmemAddr(smem) + warp * warp_smem_bytes + lane * kLaneStride;
+
+    if (producer) {
+        // Fill r carries this lane's bytes [r*kFull, (r+1)*kFull) of its request into slot r % kSlots.
+        // Every lane arrives for every fill, with or without bytes: a phase of `full` is one fill of the warp.
+        bool ok = true;
+        uint32_t slot = 0, round = 0;  // r = round * kSlots + slot
+        for (int64_t r = 0; r < max_ring && ok; ++r) {
+            if (round > 0) ok = BoundedWait(empty0 + slot * 8, (round - 1) & 1u);  // fill r - kSlots was drained
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            const uint32_t bar = full0 + slot * 8;
+            const uint64_t at = static_cast<uint64_t>(r) * kFull;
+            if (sp.over > 0 && r == sp.n_ring - 1) {  // the piece at the very end of the token array
+                const uint64_t tail_at = sp.fetch - 16;
+                const T *src = reinterpret_cast<const T *>(sp.a0 + tail_at);
+                const uint32_t dst = ring + slot * kSlotBytes + static_cast<uint32_t>(tail_at - at);
+                const int n_words = static_cast<int>((16 - sp.over) / sizeof(T));
+                for (int w = 0; w < n_words; ++w) {
+                    if constexpr (sizeof(T) == 4) {
+                        asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(dst + w * 4), "r"(static_cast<uint32_t>(src[w]))
+                                     : "memory");
+                    } else {
+                        asm volatile("st.shared.u64 [%0], %1;\n" ::"r"(dst + w * 8), "l"(static_cast<uint64_t>(src[w]))
+                                     : "memory");
+                    }
+                }
+            }
+            if (r < sp.n_ring && at < sp.bulk_total) {
+                const uint32_t bytes =
+                    sp.bulk_total - at >= kFull ? kFull : static_cast<uint32_t>(sp.bulk_total - at);
+                MbarArriveExpectTx(bar, bytes);
+                BulkLoad(ring + slot * kSlotBytes, reinterpret_cast<const void *>(sp.a0 + at), bytes, bar);
+            } else {
+                MbarArrive(bar);  // releases the tail words stored above to the consumer, too
+            }
+            if (++slot == kSlots) {
+                slot = 0;
+                ++round;
+            }
+        }
+        if (!ok && lane == 0) atomicAdd(&g_hash_wait_timeouts, 1u);
+        return;  // copies still in flight land in shared memory that lives until the consumer, which waits for them, is done
+    }
+
+    // ---- consumer ----
+    // Unpacks 64-byte stage m of the fill held in the slot at `slot_base` into `token + golden` values
+    // (garbage beyond the request: the caller never consumes those).
+    auto unpack = [&](uint32_t slot_base, int m, uint64_t (&vc)[kPerStage]) {
+        const uint32_t src = slot_base + m * kStageBytes;
 #pragma unroll
         for (int c = 0; c < kPieces; ++c) {
             uint4 q;
             asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
                          : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
-                         : "r"(src + c * 512));
+                         : "r"(src + c * 16));
             if constexpr (sizeof(T) == 4) {
                 vc[c * kPerPiece + 0] = static_cast<uint64_t>(q.x) + kGolden;
                 vc[c * kPerPiece + 1] = static_cast<uint64_t>(q.y) + kGolden;
@@ -167,12 +257,13 @@ __global__ void __launch_bounds__(kMaxWarpsPerCta * 32)
 
     uint64_t h = 0;
     int32_t left = block_size;  // tokens still to come in the current block, this one included
-    int64_t *out = keys + key_base;
-    // Runs the chain over stage k, held in `vc`.
+    int64_t *out = keys + sp.key_base;
+    const int64_t n_stages = sp.n_stages;
+    // Runs the chain over 64-byte stage k, held in `vc`.
     auto consume = [&](int64_t k, const uint64_t (&vc)[kPerStage]) {
         if (k >= n_stages) return;
-        const int lo = k == 0 ? head_skip : 0;
-        const int hi = k == n_stages - 1 ? tail_count : kPerStage;
+        const int lo = k == 0 ? sp.head_skip : 0;
+        const int hi = k == n_stages - 1 ? sp.tail_count : kPerStage;
         if (lo == 0 && hi == kPerStage && block_size >= kPerStage) {
             RunFullStage<T, kAligned>(h, vc, left, out, block_size);
         } else {
@@ -189,24 +280,52 @@ __global__ void __launch_bounds__(kMaxWarpsPerCta * 32)
         }
     };
 
-#pragma unroll
-    for (int s = 0; s < kStages - 1; ++s) issue(s);
-    CpAsyncWait<kStages - 2>();  // stage 0 has landed
+    bool ok = max_ring == 0 || BoundedWait(full0, 0);
+    ok = __all_sync(0xffffffffu, ok);
     uint64_t even[kPerStage], odd[kPerStage];
-    unpack(0, even);
-    // Stage k+1 is fetched from shared memory while the chain runs over stage k, which is already
-    // in registers.  Two stages per trip so that the two register buffers swap roles without copies.
-    for (int64_t k = 0; k < max_stages; k += 2) {
-        issue(k + kStages - 1);
-        CpAsyncWait<kStages - 2>();  // stage k+1 has landed; a lane only reads what it copied itself
-        unpack(k + 1, odd);
-        consume(k, even);
-        issue(k + kStages);
-        CpAsyncWait<kStages - 2>();  // stage k+2
-        unpack(k + 2, even);
-        consume(k + 1, odd);
+    uint32_t slot = 0, round = 0;  // fill r = round * kSlots + slot
+    int64_t waited = 1;            // fills whose `full` wait has returned
+    if (ok && max_ring > 0) {
+        unpack(ring, 0, even);
+        for (int64_t r = 0; r < max_ring; ++r) {
+            const uint32_t next_slot = slot + 1 == kSlots ? 0 : slot + 1;
+            const uint32_t next_round = slot + 1 == kSlots ? round + 1 : round;
+            const uint32_t cur = ring + slot * kSlotBytes;
+            const uint32_t nxt = ring + next_slot * kSlotBytes;
+            const int64_t k0 = r * kMinis;
+#pragma unroll
+            for (int m = 0; m < kMinis; m += 2) {
+                // Stage m+1 is fetched from shared memory while the chain runs over stage m, which is
+                // already in registers; two stages per step so the register buffers swap without copies.
+                unpack(cur, m + 1, odd);
+                consume(k0 + m, even);
+                if (m + 2 < kMinis) {
+                    unpack(cur, m + 2, even);
+                } else {
+                    MbarArrive(empty0 + slot * 8);  // this fill now lives in registers: the slot may be refilled
+                    if (r + 1 < max_ring) {
+                        ok = BoundedWait(full0 + next_slot * 8, next_round & 1u);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (ok) {
+                            ++waited;
+                            unpack(nxt, 0, even);
+                        }
+                    }
+                }
+                consume(k0 + m + 1, odd);
+            }
+            if (!ok) break;
+            slot = next_slot;
+            round = next_round;
+        }
     }
-    CpAsyncWait<0>();
+    if (!ok) {
+        // Leave no copy in flight behind: one more bounded wait for each fill the producer may have started.
+        for (int64_t r = waited; r < max_ring && r < waited + kSlots; ++r) {
+            BoundedWait(full0 + static_cast<uint32_t>(r % kSlots) * 8, static_cast<uint32_t>(r / kSlots) & 1u);
+        }
+        if (lane == 0) atomicAdd(&g_hash_wait_timeouts, 1u);
+    }
 }
 
 template <typename T>
@@ -223,42 +342,49 @@ int32_t LaunchHash(const T *d_tokens, int64_t n_tokens_total, const int64_t *d_t
     if (d_keys == nullptr) return KVCM_ER_INVALID_ADDRESS;
     if (reinterpret_cast<uintptr_t>(d_tokens) & 15u) return KVCM_ER_INVALID_ADDRESS;  // 16-byte staging copies
 
-    static bool attr_set = false;
-    if (!attr_set) {
-        const int bytes = kMaxHashSmemPerSm;
-        cudaFuncSetAttribute(HashBlocksKernel<uint32_t, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        cudaFuncSetAttribute(HashBlocksKernel<uint32_t, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        cudaFuncSetAttribute(HashBlocksKernel<int64_t, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        cudaFuncSetAttribute(HashBlocksKernel<int64_t, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        attr_set = true;
-    }
-    // Few requests: half-filled warps, one per CTA, so the chains spread over as many SMs as possible.
     const int sms = GetDeviceInfo().sm_count;
+    // Few requests: half-filled warps, one per CTA, so the chains spread over as many SMs as possible.
     const uint32_t lanes_per_warp = static_cast<int64_t>(n_req) <= 16ll * sms * kHalfWarpSmMultiple ? 16u : 32u;
     const int64_t n_warps = (static_cast<int64_t>(n_req) + lanes_per_warp - 1) / lanes_per_warp;
-    // One warp per CTA while every warp of the batch can be resident at once (16 KiB of shared memory
-    // each, 14 per SM): a warp that finishes frees its slot alone and CTAs land on the SMs round-robin.
+    // One consumer warp (+ its producer) per CTA while every warp of the batch can be resident at once:
+    // a warp that finishes frees its slot alone and CTAs land on the SMs round-robin.
     // A caller that knows the batch is ruled by its longest chains (kvcm_b200_length_order says so) asks
     // for fewer resident warps per SM: shared memory per CTA is then padded so that only that many
     // one-warp CTAs fit, the longest chains - launched first - run alone on their scheduler, and the
     // shorter ones take over the slots as they free up.
-    int warps_per_cta = n_warps <= 14ll * sms ? 1 : kMaxWarpsPerCta;
+    int warps_per_cta = n_warps <= static_cast<int64_t>(kResidentWarpsPerSm) * sms ? 1 : kMaxWarpsPerCta;
     size_t smem_per_warp = kWarpRingBytes;
-    if (warps_per_sm > 0 && warps_per_sm < 14) {
+    if (warps_per_sm > 0 && warps_per_sm < kResidentWarpsPerSm) {
         warps_per_cta = 1;
-        smem_per_warp = (static_cast<size_t>(kMaxHashSmemPerSm) / warps_per_sm) & ~static_cast<size_t>(1023);
-        if (smem_per_warp < kWarpRingBytes) smem_per_warp = kWarpRingBytes;
+        smem_per_warp = std::max<size_t>(kWarpRingBytes, (static_cast<size_t>(kMaxHashSmemPerSm) / warps_per_sm - 1024) &
+                                                             ~static_cast<size_t>(1023));
     }
     const size_t smem = static_cast<size_t>(warps_per_cta) * smem_per_warp;
     const unsigned grid = static_cast<unsigned>((n_warps + warps_per_cta - 1) / warps_per_cta);
-    const unsigned threads = warps_per_cta * 32;
+    const unsigned threads = 2 * warps_per_cta * 32;  // consumer warps + their producer warps
     constexpr int kPerStage = kStageBytes / sizeof(T);
+    auto launch = [&](auto kernel) {
+        // The opt-in to large dynamic shared memory is per device and per kernel.
+        static std::mutex mu;
+        static std::vector<std::pair<int, const void *>> done;
+        int device = 0;
+        cudaGetDevice(&device);
+        {
+            const std::pair<int, const void *> key(device, reinterpret_cast<const void *>(kernel));
+            std::lock_guard<std::mutex> lock(mu);
+            if (std::find(done.begin(), done.end(), key) == done.end()) {
+                cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxHashSmemPerSm);
+                done.push_back(key);
+            }
+        }
+        kernel<<<grid, threads, smem, AsStream(stream)>>>(d_tokens, n_tokens_total, d_tok_off, n_req, block_size, d_keys,
+                                                          d_key_off, d_order, lanes_per_warp,
+                                                          static_cast<uint32_t>(smem_per_warp));
+    };
     if (block_size % kPerStage == 0) {
-        HashBlocksKernel<T, true><<<grid, threads, smem, AsStream(stream)>>>(
-            d_tokens, n_tokens_total, d_tok_off, n_req, block_size, d_keys, d_key_off, d_order, lanes_per_warp);
+        launch(HashBlocksKernel<T, true>);
     } else {
-        HashBlocksKernel<T, false><<<grid, threads, smem, AsStream(stream)>>>(
-            d_tokens, n_tokens_total, d_tok_off, n_req, block_size, d_keys, d_key_off, d_order, lanes_per_warp);
+        launch(HashBlocksKernel<T, false>);
     }
     return LaunchStatus();
 }
@@ -280,6 +406,13 @@ int32_t kvcm_b200_hash_blocks_i64(const int64_t *d_tokens, int64_t n_tokens_tota
                                   const int32_t *d_req_order, int32_t warps_per_sm, kvcm_stream_t stream) {
     return kvcm::LaunchHash<int64_t>(d_tokens, n_tokens_total, d_tok_off, n_req, block_size, d_keys, d_key_off,
                                      d_req_order, warps_per_sm, stream);
+}
+
+int32_t kvcm_b200_hash_wait_timeouts(uint32_t *h_count_out) {
+    if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
+    if (h_count_out == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    const cudaError_t e = cudaMemcpyFromSymbol(h_count_out, kvcm::g_hash_wait_timeouts, sizeof(uint32_t));
+    return e == cudaSuccess ? KVCM_OK : KVCM_ER_CUDAMEMCPY_ERROR;
 }
 
 int32_t kvcm_b200_length_order(const int64_t *h_tok_off, int32_t n_req, int32_t *h_order_out,
