@@ -133,10 +133,14 @@ __device__ __forceinline__ LaneSpan<T> DescribeLane(const T *tokens, int64_t n_t
     return s;
 }
 
+// kRelaxed: the waiter is far ahead of what it waits for (the producer), so it sleeps between polls
+// instead of taking issue slots from the chains.
+template <bool kRelaxed = false>
 __device__ __forceinline__ bool BoundedWait(uint32_t bar, uint32_t parity) {
     uint32_t spins = 0;
     while (!MbarTryWait(bar, parity)) {
         if (++spins >= kSpinLimit) return false;
+        if (kRelaxed) __nanosleep(256);
     }
     return true;
 }
@@ -159,12 +163,17 @@ __global__ void __launch_bounds__(2 * kMaxWarpsPerCta * 32)
     const uint32_t lane = LaneId();
     const uint32_t n_consumers = blockDim.x >> 6;
     const uint32_t warp_in_cta = threadIdx.x >> 5;
-    const bool producer = warp_in_cta >= n_consumers;
-    const uint32_t warp = producer ? warp_in_cta - n_consumers : warp_in_cta;  // the consumer warp served
-    const int64_t pos = (static_cast<int64_t>(blockIdx.x) * n_consumers + warp) * lanes_per_warp + lane;
-    const bool active = lane < lanes_per_warp && pos < n_req;
+    __shared__ uint32_t swap_roles;
 
     if (threadIdx.x == 0) {
+        // A two-warp CTA sits in warp slots (2k, 2k+1) of its SM and a warp's scheduler is its slot modulo
+        // 4, so with the consumer always first the chains of all CTAs of an SM would crowd onto
+        // schedulers 0 and 2 (measured: issue-active 57% on two schedulers, 23% on the others).  The first
+        // warp reads its slot and the CTA swaps the roles in every other pair of pairs: consumers then
+        // land on slots 0, 2, 5, 7, ... = schedulers 0, 2, 1, 3.  Only balance depends on this.
+        uint32_t slot_id;
+        asm volatile("mov.u32 %0, %%warpid;\n" : "=r"(slot_id));
+        swap_roles = n_consumers == 1 ? (slot_id >> 2) & 1u : 0u;
         for (uint32_t w = 0; w < n_consumers; ++w) {
 #pragma unroll
             for (int s = 0; s < kSlots; ++s) {
@@ -176,6 +185,10 @@ __global__ void __launch_bounds__(2 * kMaxWarpsPerCta * 32)
         asm volatile("fence.proxy.async;\n" ::: "memory");
     }
     __syncthreads();
+    const bool producer = n_consumers == 1 ? (warp_in_cta ^ swap_roles) == 1 : warp_in_cta >= n_consumers;
+    const uint32_t warp = n_consumers == 1 ? 0 : (producer ? warp_in_cta - n_consumers : warp_in_cta);  // consumer served
+    const int64_t pos = (static_cast<int64_t>(blockIdx.x) * n_consumers + warp) * lanes_per_warp + lane;
+    const bool active = lane < lanes_per_warp && pos < n_req;
 
     const LaneSpan<T> sp =
         DescribeLane<T>(tokens, n_tokens_total, tok_off, key_off, order, pos, active, block_size);
@@ -195,7 +208,7 @@ __global__ void __launch_bounds__(2 * kMaxWarpsPerCta * 32)
         bool ok = true;
         uint32_t slot = 0, round = 0;  // r = round * kSlots + slot
         for (int64_t r = 0; r < max_ring && ok; ++r) {
-            if (round > 0) ok = BoundedWait(empty0 + slot * 8, (round - 1) & 1u);  // fill r - kSlots was drained
+            if (round > 0) ok = BoundedWait<true>(empty0 + slot * 8, (round - 1) & 1u);  // fill r - kSlots was drained
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             const uint32_t bar = full0 + slot * 8;
@@ -427,15 +440,15 @@ int32_t kvcm_b200_length_order(const int64_t *h_tok_off, int32_t n_req, int32_t 
     });
     for (int32_t r = 0; r < n_req; ++r) h_order_out[r] = idx[r];
     if (warps_per_sm_out != nullptr && n_req > 0) {
-        // A lone warp advances one token per ~47 cycles (dependent chain); a scheduler shared by several
-        // warps issues one token step per ~31 cycles in total.  If the longest chain alone outlasts the
-        // whole batch spread over all schedulers, keep one warp per scheduler (4 per SM) so that chain is
-        // never slowed down; otherwise fill the SMs.
+        // A warp alone on its scheduler advances one token per ~40 cycles (the dependent chain); two warps
+        // sharing a scheduler advance one token each per ~78 cycles.  If the longest chain alone outlasts
+        // the whole batch spread over all schedulers, keep one hashing warp per scheduler (4 per SM) so that
+        // chain is never slowed down; otherwise fill the SMs.
         const int sms = kvcm::HaveDevice() ? kvcm::GetDeviceInfo().sm_count : 148;
         const double longest = static_cast<double>(h_tok_off[idx[0] + 1] - h_tok_off[idx[0]]);
         double warp_steps = 0;
         for (int32_t r = 0; r < n_req; r += 32) warp_steps += static_cast<double>(h_tok_off[idx[r] + 1] - h_tok_off[idx[r]]);
-        *warps_per_sm_out = longest * 47.0 >= warp_steps * 31.0 / (4.0 * sms) ? 4 : 0;
+        *warps_per_sm_out = longest * 40.0 >= warp_steps * 39.0 / (4.0 * sms) ? 4 : 0;
     }
     return KVCM_OK;
 }
