@@ -408,6 +408,36 @@ KVCM_API int32_t kvcm_b200_replay(const int64_t *d_keys, const int64_t *d_key_of
                                   int32_t *d_int_hit, int32_t *d_written, int64_t *d_cache_blocks,
                                   uint32_t *d_status, kvcm_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------
+ * (2c') Optimizer trace replay with LRU eviction, for a sweep of quotas in one call.
+ *
+ * Replaces one run of OptimizerRunner::RunTraces per tradeoff-curve point
+ * (kv_cache_manager/optimizer/analysis/script/optimizer_analysis_utils.py:95-144,278-330 start one
+ * optimizer run per (capacity, policy) pair) for the "lru" policy
+ * (kv_cache_manager/optimizer/eviction_policy/lru.cc:6-49) on the shared tier with one instance per
+ * group: after every DialogTurn / WriteCache trace the cached blocks beyond the quota are evicted
+ * from the cold end of the recency list (OptIndexerManager::CheckAndEvict,
+ * kv_cache_manager/optimizer/manager/indexer_manager.cc:55-90).  precise = 0: whole batches of
+ * evict_batch blocks until the excess is covered (EVICTION_MODE_GROUP_ROUGH / INSTANCE_ROUGH,
+ * kv_cache_manager/optimizer/manager/eviction_manager.cc:86-192); precise != 0: exactly the excess
+ * (EVICTION_MODE_INSTANCE_PRECISE, :194-239).  d_quota_blocks[c] is configuration c's
+ * size_t(quota_capacity * used_percentage) (:249-266).
+ * Trace encoding as kvcm_b200_replay.  Outputs are [n_configs][n_traces], configuration-major.
+ * Exact for prefix-unique chained keys without repeats inside one trace.  Configurations are
+ * independent and run in parallel (one warp each); one configuration is replayed in trace order.
+ * d_workspace: kvcm_b200_replay_lru_workspace_bytes(n_keys_total, n_configs) bytes (-1: too large:
+ * n_keys_total < 2^32 - 1, n_configs <= 65535), 256-byte aligned, contents irrelevant before and after.
+ * Not covered: leaf_aware_lru and random_lru (they depend on the tree shape / a random stream),
+ * several instances sharing one group quota, hierarchical tiers.
+ * ---------------------------------------------------------------------------------------- */
+KVCM_API int64_t kvcm_b200_replay_lru_workspace_bytes(int64_t n_keys_total, int32_t n_configs);
+KVCM_API int32_t kvcm_b200_replay_lru(const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type,
+                                      const int64_t *d_mask_off, int32_t n_traces, int64_t n_keys_total,
+                                      const int64_t *d_quota_blocks, int32_t n_configs, int32_t evict_batch,
+                                      int32_t precise, void *d_workspace, int64_t workspace_bytes,
+                                      int32_t *d_ext_hit, int32_t *d_int_hit, int32_t *d_written,
+                                      int64_t *d_cache_blocks, uint32_t *d_status, kvcm_stream_t stream);
+
 /* Trace replay for callers that cannot allocate device memory.  (No counterpart in the reference: it
  * exists for how this library gets embedded, not for a reference interface.)
  *

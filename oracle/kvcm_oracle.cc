@@ -22,8 +22,11 @@
 #include <cstdint>
 #include <cstring>
 #include <functional>
+#include <list>
+#include <memory>
 #include <thread>
 #include <unordered_map>
+#include <unordered_set>
 #include <vector>
 
 namespace {
@@ -552,6 +555,251 @@ void kvcm_oracle_replay_run(void *h, const int64_t *keys, const int64_t *key_off
         int_hit[t] = inte;
         written[t] = wr;
         cache_blocks[t] = st->cached_blocks;
+    }
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------
+// (2c') Optimizer trace replay with LRU eviction
+// ---------------------------------------------------------------------------------
+// Restates, for one instance in a group of its own and the "lru" policy on the shared tier:
+//   RadixTreeIndex InsertNode / SplitNode / PrefixQuery / InsertQuery / CleanEmptyBlocks / WriteToTier
+//     (kv_cache_manager/optimizer/index/radix_tree_index.cc:19-127,129-196,198-282,284-325,327-392),
+//   LruEvictionPolicy (kv_cache_manager/optimizer/eviction_policy/lru.cc:6-49),
+//   OptEvictionManager::EvictByInstanceRough / EvictByInstancePrecise / GetExcessUsageForInstanceInGroup
+//     (kv_cache_manager/optimizer/manager/eviction_manager.cc:148-239,249-266; with one instance per
+//     group EvictByGroupRough (:86-146) does the same as EvictByInstanceRough),
+//   OptIndexerManager::CheckAndEvict (kv_cache_manager/optimizer/manager/indexer_manager.cc:55-90),
+//   and the three handlers of OptimizerRunner (optimizer_runner.cc:70-215).
+// The tree is kept compressed and split exactly as the reference does, so that this oracle does not
+// assume what the GPU replay assumes (that only per-key residency matters).
+
+namespace {
+
+struct LruNode;
+struct LruBlock {
+    int64_t key = 0;
+    bool cached = false;  // location_map non-empty
+    LruNode *owner = nullptr;
+    std::list<LruBlock *>::iterator where;  // position in the recency list while cached
+};
+struct LruNode {
+    LruNode *parent = nullptr;
+    std::vector<std::unique_ptr<LruBlock>> blocks;
+    std::unordered_map<int64_t, std::unique_ptr<LruNode>> children;
+    bool leaf() const { return children.empty(); }
+};
+
+struct OracleLruReplay {
+    std::unique_ptr<LruNode> root{new LruNode()};
+    std::list<LruBlock *> recency;  // front = most recently written or accessed
+    int64_t quota = 0;
+    int32_t batch = 1;
+    bool precise = false;
+
+    void on_written(LruBlock *b) {  // lru.cc:6-11
+        b->cached = true;
+        recency.push_front(b);
+        b->where = recency.begin();
+    }
+    void on_accessed(LruBlock *b) {  // lru.cc:18-26
+        if (!b->cached) return;
+        recency.splice(recency.begin(), recency, b->where);
+        b->where = recency.begin();
+    }
+    // WriteToTier without a callback: new blocks at the end of `node` (radix_tree_index.cc:327-343,377-392)
+    void append_new(LruNode *node, const int64_t *k, int64_t n) {
+        for (int64_t i = 0; i < n; ++i) {
+            std::unique_ptr<LruBlock> b(new LruBlock());
+            b->key = k[i];
+            b->owner = node;
+            LruBlock *raw = b.get();
+            node->blocks.push_back(std::move(b));
+            on_written(raw);
+        }
+    }
+    // WriteToTier with AppendEvictBlocks: evicted blocks of a node get their location back (:355-375)
+    void revive(const std::vector<LruBlock *> &blocks) {
+        for (LruBlock *b : blocks) on_written(b);
+    }
+    void split(LruNode *node, size_t pos, const int64_t *right, int64_t n_right) {  // :89-127
+        if (pos == 0 || node->parent == nullptr) return;
+        LruNode *parent = node->parent;
+        const int64_t edge = node->blocks.front()->key;
+        std::unique_ptr<LruNode> old = std::move(parent->children[edge]);
+        std::unique_ptr<LruNode> mid(new LruNode());
+        LruNode *mid_raw = mid.get();
+        for (size_t i = 0; i < pos; ++i) {
+            mid_raw->blocks.push_back(std::move(old->blocks[i]));
+            mid_raw->blocks.back()->owner = mid_raw;
+        }
+        mid_raw->parent = parent;
+        old->blocks.erase(old->blocks.begin(), old->blocks.begin() + pos);
+        old->parent = mid_raw;
+        const int64_t old_edge = old->blocks.front()->key;
+        mid_raw->children[old_edge] = std::move(old);
+        if (n_right > 0) {
+            std::unique_ptr<LruNode> fresh(new LruNode());
+            fresh->parent = mid_raw;
+            append_new(fresh.get(), right, n_right);
+            mid_raw->children[right[0]] = std::move(fresh);
+        }
+        parent->children[edge] = std::move(mid);
+    }
+    // InsertNode (:30-87) when query == false, InsertQuery (:214-282) when query == true.
+    // Returns the number of keys written; `hits` counts the leading cached blocks of a query.
+    int64_t insert(LruNode *node, const int64_t *k, int64_t n, bool query, bool alive, int64_t *hits) {
+        if (n == 0) return 0;
+        if (node->leaf() && node->parent != nullptr) {
+            append_new(node, k, n);
+            return n;
+        }
+        auto it = node->children.find(k[0]);
+        if (it == node->children.end()) {
+            std::unique_ptr<LruNode> fresh(new LruNode());
+            fresh->parent = node;
+            append_new(fresh.get(), k, n);
+            node->children[k[0]] = std::move(fresh);
+            return n;
+        }
+        LruNode *child = it->second.get();
+        std::vector<LruBlock *> evicted;
+        size_t m = 0;
+        while (m < child->blocks.size() && static_cast<int64_t>(m) < n && child->blocks[m]->key == k[m]) {
+            LruBlock *b = child->blocks[m].get();
+            if (!b->cached) {
+                evicted.push_back(b);
+                alive = false;
+            } else if (query && alive) {
+                ++*hits;
+                on_accessed(b);
+            }
+            ++m;
+        }
+        int64_t wrote = static_cast<int64_t>(evicted.size());
+        revive(evicted);
+        if (m == child->blocks.size()) return wrote + insert(child, k + m, n - m, query, alive, hits);
+        if (static_cast<int64_t>(m) == n) return wrote;
+        split(child, m, k + m, n - m);
+        return wrote + (n - static_cast<int64_t>(m));
+    }
+    void prefix_query(const int64_t *k, int64_t n, int64_t mask_off, int32_t *ext, int32_t *inte) {  // :129-196
+        std::unordered_map<int64_t, int> cls;  // 1 = occurs unmasked, 2 = occurs masked only
+        for (int64_t i = 0; i < n; ++i) {
+            if (i < mask_off) {
+                cls.emplace(k[i], 2);
+            } else {
+                cls[k[i]] = 1;
+            }
+        }
+        LruNode *node = root.get();
+        int64_t at = 0;
+        while (at < n) {
+            auto it = node->children.find(k[at]);
+            if (it == node->children.end()) break;
+            LruNode *child = it->second.get();
+            size_t m = 0;
+            while (m < child->blocks.size() && at + static_cast<int64_t>(m) < n && child->blocks[m]->key == k[at + m]) {
+                LruBlock *b = child->blocks[m].get();
+                if (!b->cached) break;
+                if (cls[k[at + m]] == 1) {
+                    ++*ext;
+                } else {
+                    ++*inte;
+                }
+                on_accessed(b);
+                ++m;
+            }
+            if (m < child->blocks.size() || at + static_cast<int64_t>(m) == n) break;
+            node = child;
+            at += static_cast<int64_t>(m);
+        }
+    }
+    std::vector<LruBlock *> evict_blocks(int64_t count) {  // lru.cc:28-49
+        std::vector<LruBlock *> out;
+        for (int64_t i = 0; i < count && !recency.empty(); ++i) {
+            LruBlock *b = recency.back();
+            recency.pop_back();
+            b->cached = false;
+            out.push_back(b);
+        }
+        return out;
+    }
+    void clean(const std::vector<LruBlock *> &gone) {  // radix_tree_index.cc:284-325
+        std::unordered_set<LruNode *> check;
+        for (LruBlock *b : gone) {
+            if (!b->cached && b->owner != nullptr && b->owner->parent != nullptr) check.insert(b->owner);
+        }
+        bool removed = true;
+        while (removed) {
+            removed = false;
+            for (auto it = check.begin(); it != check.end();) {
+                LruNode *node = *it;
+                bool all_gone = true;
+                for (const auto &b : node->blocks) all_gone = all_gone && !b->cached;
+                if (all_gone && !node->blocks.empty() && node->parent != nullptr && node->leaf()) {
+                    node->parent->children.erase(node->blocks.front()->key);
+                    it = check.erase(it);
+                    removed = true;
+                } else {
+                    ++it;
+                }
+            }
+        }
+    }
+    void check_and_evict() {  // indexer_manager.cc:55-90, eviction_manager.cc:148-266
+        const int64_t used = static_cast<int64_t>(recency.size());
+        const int64_t excess = used > quota ? used - quota : 0;
+        if (excess == 0) return;
+        std::vector<LruBlock *> all;
+        int64_t total = 0;
+        while (total < excess) {
+            const int64_t count = precise ? std::min<int64_t>(batch, excess - total) : batch;
+            std::vector<LruBlock *> round = evict_blocks(count);
+            if (round.empty()) break;
+            total += static_cast<int64_t>(round.size());
+            all.insert(all.end(), round.begin(), round.end());
+        }
+        clean(all);
+    }
+};
+
+}  // namespace
+
+extern "C" {
+
+void *kvcm_oracle_lru_replay_create(int64_t quota_blocks, int32_t evict_batch, int32_t precise) {
+    auto *st = new OracleLruReplay();
+    st->quota = quota_blocks;
+    st->batch = evict_batch;
+    st->precise = precise != 0;
+    return st;
+}
+void kvcm_oracle_lru_replay_destroy(void *h) { delete static_cast<OracleLruReplay *>(h); }
+
+// Same trace encoding and outputs as kvcm_oracle_replay_run; cache_blocks[t] is the number of cached
+// blocks after trace t (EvictionPolicy::size(), after CheckAndEvict for the writing kinds).
+void kvcm_oracle_lru_replay_run(void *h, const int64_t *keys, const int64_t *key_off, const uint8_t *type,
+                                const int64_t *mask_off, int64_t n_traces, int32_t *ext_hit, int32_t *int_hit,
+                                int32_t *written, int64_t *cache_blocks) {
+    auto *st = static_cast<OracleLruReplay *>(h);
+    for (int64_t t = 0; t < n_traces; ++t) {
+        const int64_t *k = keys + key_off[t];
+        const int64_t n = key_off[t + 1] - key_off[t];
+        int32_t ext = 0, inte = 0;
+        int64_t wr = 0, hits = 0;
+        if (type[t] == 1) {
+            if (n > 0) st->prefix_query(k, n, mask_off ? mask_off[t] : 0, &ext, &inte);
+        } else {
+            wr = st->insert(st->root.get(), k, n, type[t] == 0, true, &hits);
+            ext = static_cast<int32_t>(hits);
+            st->check_and_evict();
+        }
+        ext_hit[t] = ext;
+        int_hit[t] = inte;
+        written[t] = static_cast<int32_t>(wr);
+        cache_blocks[t] = static_cast<int64_t>(st->recency.size());
     }
 }
 

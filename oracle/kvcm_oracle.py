@@ -399,3 +399,40 @@ class Replay:
                                      _ptr(ext, ctypes.c_int32), _ptr(inte, ctypes.c_int32), _ptr(wr, ctypes.c_int32),
                                      _ptr(cached, ctypes.c_int64))
         return ext, inte, wr, cached
+
+
+class LruReplay(Replay):
+    """Sequential replay over the compressed prefix tree with the "lru" eviction policy and a block quota
+    (kv_cache_manager/optimizer/index/radix_tree_index.cc, eviction_policy/lru.cc,
+    manager/eviction_manager.cc:148-266).  precise=False evicts whole batches of evict_batch blocks until the
+    excess is covered (EVICTION_MODE_GROUP_ROUGH / INSTANCE_ROUGH with one instance per group), precise=True
+    evicts exactly the excess (INSTANCE_PRECISE)."""
+
+    def __init__(self, quota_blocks, evict_batch=100, precise=False):
+        lib().kvcm_oracle_lru_replay_create.restype = ctypes.c_void_p
+        self._h = ctypes.c_void_p(lib().kvcm_oracle_lru_replay_create(ctypes.c_int64(int(quota_blocks)),
+                                                                      ctypes.c_int32(int(evict_batch)),
+                                                                      ctypes.c_int32(1 if precise else 0)))
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().kvcm_oracle_lru_replay_destroy(self._h)
+            self._h = None
+
+    def run(self, keys, key_off, trace_type, mask_off=None):
+        keys, key_off = _i64(keys), _i64(key_off)
+        n = len(key_off) - 1
+        trace_type = np.ascontiguousarray(trace_type, dtype=np.uint8)
+        mp = None
+        if mask_off is not None:
+            mask_off = _i64(mask_off)
+            mp = _ptr(mask_off, ctypes.c_int64)
+        ext = np.zeros(n, dtype=np.int32)
+        inte = np.zeros(n, dtype=np.int32)
+        wr = np.zeros(n, dtype=np.int32)
+        cached = np.zeros(n, dtype=np.int64)
+        lib().kvcm_oracle_lru_replay_run(self._h, _ptr(keys, ctypes.c_int64), _ptr(key_off, ctypes.c_int64),
+                                         _ptr(trace_type, ctypes.c_uint8), mp, ctypes.c_int64(n),
+                                         _ptr(ext, ctypes.c_int32), _ptr(inte, ctypes.c_int32),
+                                         _ptr(wr, ctypes.c_int32), _ptr(cached, ctypes.c_int64))
+        return ext, inte, wr, cached

@@ -99,6 +99,9 @@ SIGNATURES = {
     "kvcm_b200_index_detach_peers": [_vp],
     "kvcm_b200_replay_workspace_bytes": [_i64],
     "kvcm_b200_replay": [_vp, _vp, _vp, _vp, _i32, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp],
+    "kvcm_b200_replay_lru_workspace_bytes": [_i64, _i32],
+    "kvcm_b200_replay_lru": [_vp, _vp, _vp, _vp, _i32, _i64, _vp, _i32, _i32, _i32, _vp, _i64, _vp, _vp, _vp, _vp, _vp,
+                             _vp],
     "kvcm_b200_replay_noalloc": [_vp, _vp, _vp, _vp, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _vp],
 }
 
@@ -124,7 +127,7 @@ def lib():
             fn = getattr(L, name)
             fn.argtypes = argtypes
             fn.restype = (ctypes.c_char_p if name == "kvcm_b200_error_string" else
-                          _i64 if name == "kvcm_b200_replay_workspace_bytes" else _i32)
+                          _i64 if name.endswith("_workspace_bytes") else _i32)
         _lib = L
     return _lib
 

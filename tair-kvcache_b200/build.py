@@ -8,7 +8,8 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libkvcm_b200.so")
 
-SOURCES = ["runtime.cu", "move_rows.cu", "copy_segments.cu", "hash_blocks.cu", "block_index.cu", "replay.cu"]
+SOURCES = ["runtime.cu", "move_rows.cu", "copy_segments.cu", "hash_blocks.cu", "block_index.cu", "replay.cu",
+           "replay_lru.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -1,0 +1,321 @@
+// Optimizer trace replay with LRU eviction, for a sweep of cache quotas at once (sm_100a).
+//
+// Stands in for OptimizerRunner::RunTraces (kv_cache_manager/optimizer/manager/optimizer_runner.cc:29-215)
+// over RadixTreeIndex (kv_cache_manager/optimizer/index/radix_tree_index.cc:19-392) with the "lru"
+// eviction policy (kv_cache_manager/optimizer/eviction_policy/lru.cc:6-49) and the quota check after
+// every write (OptIndexerManager::CheckAndEvict, kv_cache_manager/optimizer/manager/indexer_manager.cc:55-90;
+// OptEvictionManager::EvictByInstanceRough / EvictByInstancePrecise / GetExcessUsageForInstanceInGroup,
+// kv_cache_manager/optimizer/manager/eviction_manager.cc:148-266), one instance per group.
+//
+// With eviction the replay of ONE configuration is sequential: what trace t hits depends on what
+// the traces before it touched and evicted.  The reference's tradeoff-curve scripts run the same
+// trace once per (quota, policy) point (kv_cache_manager/optimizer/analysis/script/
+// optimizer_analysis_utils.py:95-144,181-207,278-330); those runs are independent, and that is the
+// parallel axis here: one warp per configuration, all walking the same trace.
+//
+// Per configuration the tree collapses to per-key state, because keys are prefix-unique chained
+// hashes and because of how the reference orders its recency updates: within one trace it first
+// moves the leading cached blocks to the front (in order, stopping at the first evicted or absent
+// block) and then writes the missing blocks (in order); blocks that are cached but lie behind the
+// first miss are not touched.  So:
+//   stamp[key]  0 = not cached, else the sequence number of its last write or access;
+//   queue       every write or access appends (key, stamp); an entry is live while it still
+//               carries the key's current stamp.  The recency list of the reference is the
+//               live entries in queue order, its tail is the oldest live entry.
+// A trace is handled 32 keys at a time: ballot for the first miss, ranks from the ballot give
+// the stamps and queue positions.  Eviction pops live entries from the head of the queue.
+// Keys are renamed to dense ids 0..D-1 once, for all configurations, so that per-configuration
+// state is two flat arrays (4 + 8 bytes per key occurrence of the trace).
+#include "kvcm_common.cuh"
+
+namespace kvcm {
+namespace {
+
+constexpr uint64_t kEmptyKey = 0x8000000000000000ull;
+constexpr int kWarps = 8;
+
+struct IdTable {
+    ulonglong2 *slots;         // {key, id}
+    unsigned long long *cells;  // [0] = number of ids handed out, [1] = id of the key equal to kEmptyKey (or ~0)
+    uint64_t mask;
+};
+
+__host__ __device__ __forceinline__ uint64_t Mix(uint64_t k) {
+    k ^= k >> 33;
+    k *= 0xff51afd7ed558ccdull;
+    k ^= k >> 33;
+    k *= 0xc4ceb9fe1a85ec53ull;
+    k ^= k >> 33;
+    return k;
+}
+
+__global__ void LruInitKernel(IdTable t, uint32_t *stamps, uint64_t n_stamps) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    const uint64_t first = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (uint64_t i = first; i <= t.mask; i += stride) t.slots[i] = make_ulonglong2(kEmptyKey, ~0ull);
+    for (uint64_t i = first; i < n_stamps; i += stride) stamps[i] = 0u;
+    if (first == 0) {
+        t.cells[0] = 0ull;
+        t.cells[1] = ~0ull;
+    }
+}
+
+// Pass 1: every key gets a slot; the thread that claims the slot takes the next id.
+__global__ void __launch_bounds__(256)
+    LruClaimIdsKernel(IdTable t, const int64_t *__restrict__ keys, int64_t n_keys, uint32_t *status) {
+    unsigned long long *words = reinterpret_cast<unsigned long long *>(t.slots);
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_keys; i += stride) {
+        const uint64_t key = static_cast<uint64_t>(keys[i]);
+        if (key == kEmptyKey) {
+            if (atomicCAS(&t.cells[1], ~0ull, ~0ull - 1) == ~0ull) t.cells[1] = atomicAdd(&t.cells[0], 1ull);
+            continue;
+        }
+        uint64_t slot = Mix(key) & t.mask;
+        bool placed = false;
+        for (uint64_t probe = 0; probe <= t.mask; ++probe) {
+            unsigned long long seen = *reinterpret_cast<volatile unsigned long long *>(&words[2 * slot]);
+            if (seen == kEmptyKey) {
+                seen = atomicCAS(&words[2 * slot], kEmptyKey, key);
+                if (seen == kEmptyKey) {
+                    words[2 * slot + 1] = atomicAdd(&t.cells[0], 1ull);
+                    placed = true;
+                    break;
+                }
+            }
+            if (seen == key) {
+                placed = true;
+                break;
+            }
+            slot = (slot + 1) & t.mask;
+        }
+        if (!placed && status != nullptr) atomicAdd(&status[0], 1u);
+    }
+}
+
+// Pass 2 (a launch of its own, so every id of pass 1 is visible): key occurrence -> id.
+__global__ void __launch_bounds__(256)
+    LruLookupIdsKernel(IdTable t, const int64_t *__restrict__ keys, int64_t n_keys, uint32_t *__restrict__ ids) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_keys; i += stride) {
+        const uint64_t key = static_cast<uint64_t>(keys[i]);
+        uint32_t id = 0;
+        if (key == kEmptyKey) {
+            id = static_cast<uint32_t>(t.cells[1]);
+        } else {
+            uint64_t slot = Mix(key) & t.mask;
+            for (uint64_t probe = 0; probe <= t.mask; ++probe) {
+                const ulonglong2 s = t.slots[slot];
+                if (s.x == key) {
+                    id = static_cast<uint32_t>(s.y);
+                    break;
+                }
+                if (s.x == kEmptyKey) break;  // not reached for a key that pass 1 placed
+                slot = (slot + 1) & t.mask;
+            }
+        }
+        ids[i] = id;
+    }
+}
+
+struct LruSweep {
+    const uint32_t *ids;
+    const int64_t *key_off;
+    const uint8_t *type;
+    const int64_t *mask_off;
+    const int64_t *quota;
+    uint32_t *stamps;  // [n_configs][n_keys]
+    uint2 *queue;      // [n_configs][n_keys]
+    int32_t *ext_hit, *int_hit, *written;
+    int64_t *cache_blocks;
+    int64_t n_keys;
+    int32_t n_traces;
+    int32_t n_configs;
+    int32_t evict_batch;
+    int32_t precise;
+};
+
+// type: 0 DialogTurn (InsertWithQuery), 1 GetLocation (PrefixQuery), 2 WriteCache (InsertOnly).
+__global__ void __launch_bounds__(32) LruSweepKernel(const LruSweep p) {
+    const int32_t cfg = blockIdx.x;
+    const uint32_t lane = LaneId();
+    const uint32_t lt = (1u << lane) - 1u;
+    uint32_t *stamp = p.stamps + static_cast<int64_t>(cfg) * p.n_keys;
+    uint2 *queue = p.queue + static_cast<int64_t>(cfg) * p.n_keys;
+    const int64_t quota = p.quota[cfg];
+    const int64_t out0 = static_cast<int64_t>(cfg) * p.n_traces;
+    uint32_t counter = 0;  // last stamp handed out
+    int64_t head = 0, tail = 0, resident = 0;
+
+    for (int32_t t = 0; t < p.n_traces; ++t) {
+        const int64_t beg = p.key_off[t];
+        const int64_t n = p.key_off[t + 1] - beg;
+        const uint8_t ty = p.type[t];
+        const int64_t skip = (ty == 1 && p.mask_off != nullptr) ? p.mask_off[t] : 0;
+        int32_t ext = 0, inte = 0, wr = 0;
+        bool alive = ty != 2;  // still inside the leading run of cached blocks
+        for (int64_t base = 0; base < n; base += 32) {
+            const int64_t i = base + lane;
+            const bool have = i < n;
+            const uint32_t id = have ? p.ids[beg + i] : 0u;
+            const uint32_t cur = have ? stamp[id] : 0u;
+            const uint32_t in_range = __ballot_sync(0xffffffffu, have);
+            const uint32_t cached = __ballot_sync(0xffffffffu, have && cur != 0u);
+            const uint32_t miss = in_range & ~cached;
+            uint32_t touch = 0;  // leading cached blocks: hits, moved to the front in order
+            if (alive) {
+                touch = miss != 0 ? cached & ((1u << (__ffs(miss) - 1)) - 1u) : cached;
+                const uint32_t masked = __ballot_sync(0xffffffffu, i < skip);
+                ext += __popc(touch & ~masked);
+                inte += __popc(touch & masked);
+                if (miss != 0) alive = false;
+            }
+            const uint32_t write = ty == 1 ? 0u : miss;  // then the missing blocks are written, in order
+            const uint32_t n_touch = __popc(touch), n_write = __popc(write);
+            if ((touch >> lane) & 1u) {
+                const uint32_t r = __popc(touch & lt);
+                stamp[id] = counter + 1 + r;
+                queue[tail + r] = make_uint2(id, counter + 1 + r);
+            } else if ((write >> lane) & 1u) {
+                const uint32_t r = n_touch + __popc(write & lt);
+                stamp[id] = counter + 1 + r;
+                queue[tail + r] = make_uint2(id, counter + 1 + r);
+            }
+            counter += n_touch + n_write;
+            tail += n_touch + n_write;
+            resident += n_write;
+            wr += static_cast<int32_t>(n_write);
+            __syncwarp();
+            if (ty == 1 && !alive) break;
+        }
+        if (ty != 1 && resident > quota) {
+            // CheckAndEvict: whole batches until the excess is covered, or exactly the excess.
+            const int64_t excess = resident - quota;
+            int64_t need = excess;
+            if (p.precise == 0) {
+                const int64_t batches = (excess + p.evict_batch - 1) / p.evict_batch;
+                need = batches * p.evict_batch;
+                if (need > resident) need = resident;
+            }
+            while (need > 0 && head < tail) {
+                const int64_t j = head + lane;
+                uint2 e = make_uint2(0u, 0u);
+                bool live = false;
+                if (j < tail) {
+                    e = queue[j];
+                    live = stamp[e.x] == e.y;
+                }
+                const uint32_t lives = __ballot_sync(0xffffffffu, live);
+                const uint32_t n_live = __popc(lives);
+                uint32_t take = lives;
+                int64_t advance = tail - head < 32 ? tail - head : 32;
+                if (static_cast<int64_t>(n_live) > need) {
+                    // keep only the first `need` live entries of this window; stop right behind the last one
+                    const bool mine = live && static_cast<int64_t>(__popc(lives & lt)) < need;
+                    take = __ballot_sync(0xffffffffu, mine);
+                    advance = 32 - __clz(take);
+                }
+                if ((take >> lane) & 1u) stamp[e.x] = 0u;
+                const uint32_t n_take = __popc(take);
+                need -= n_take;
+                resident -= n_take;
+                head += advance;
+                __syncwarp();
+            }
+        }
+        if (lane == 0) {
+            p.ext_hit[out0 + t] = ext;
+            p.int_hit[out0 + t] = inte;
+            p.written[out0 + t] = wr;
+            p.cache_blocks[out0 + t] = resident;
+        }
+    }
+}
+
+uint64_t SlotsFor(int64_t n_keys) {
+    uint64_t n = 1024;
+    while (n < 2ull * static_cast<uint64_t>(n_keys)) n <<= 1;
+    return n;
+}
+
+struct LruLayout {
+    uint64_t table_off, ids_off, stamps_off, queue_off, total;
+};
+
+LruLayout LayoutFor(int64_t n_keys, int32_t n_configs) {
+    auto up = [](uint64_t v) { return (v + 255u) & ~static_cast<uint64_t>(255u); };
+    LruLayout l;
+    const uint64_t nk = static_cast<uint64_t>(n_keys > 0 ? n_keys : 1);
+    l.table_off = 256;
+    l.ids_off = up(l.table_off + SlotsFor(n_keys) * sizeof(ulonglong2));
+    l.stamps_off = up(l.ids_off + nk * sizeof(uint32_t));
+    l.queue_off = up(l.stamps_off + nk * sizeof(uint32_t) * static_cast<uint64_t>(n_configs));
+    l.total = up(l.queue_off + nk * sizeof(uint2) * static_cast<uint64_t>(n_configs));
+    return l;
+}
+
+}  // namespace
+}  // namespace kvcm
+
+extern "C" {
+
+int64_t kvcm_b200_replay_lru_workspace_bytes(int64_t n_keys_total, int32_t n_configs) {
+    if (n_keys_total < 0 || n_keys_total >= (1ll << 32) - 1 || n_configs <= 0 || n_configs > 65535) return -1;
+    return static_cast<int64_t>(kvcm::LayoutFor(n_keys_total, n_configs).total);
+}
+
+int32_t kvcm_b200_replay_lru(const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type,
+                             const int64_t *d_mask_off, int32_t n_traces, int64_t n_keys_total,
+                             const int64_t *d_quota_blocks, int32_t n_configs, int32_t evict_batch, int32_t precise,
+                             void *d_workspace, int64_t workspace_bytes, int32_t *d_ext_hit, int32_t *d_int_hit,
+                             int32_t *d_written, int64_t *d_cache_blocks, uint32_t *d_status, kvcm_stream_t stream) {
+    if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
+    if (n_traces < 0 || n_keys_total < 0 || n_configs <= 0 || evict_batch <= 0) return KVCM_EC_BADARGS;
+    const int64_t need = kvcm_b200_replay_lru_workspace_bytes(n_keys_total, n_configs);
+    if (need < 0) return KVCM_EC_OUT_OF_LIMIT;
+    if (n_traces == 0) return KVCM_OK;
+    if (d_key_off == nullptr || d_trace_type == nullptr || d_quota_blocks == nullptr || d_ext_hit == nullptr ||
+        d_int_hit == nullptr || d_written == nullptr || d_cache_blocks == nullptr || d_workspace == nullptr ||
+        (d_keys == nullptr && n_keys_total > 0)) {
+        return KVCM_ER_INVALID_ADDRESS;
+    }
+    if (reinterpret_cast<uintptr_t>(d_workspace) & 255u) return KVCM_ER_INVALID_ADDRESS;
+    if (workspace_bytes < need) return KVCM_EC_NOSPC;
+    const kvcm::LruLayout l = kvcm::LayoutFor(n_keys_total, n_configs);
+    uint8_t *ws = static_cast<uint8_t *>(d_workspace);
+    kvcm::IdTable t;
+    t.cells = reinterpret_cast<unsigned long long *>(ws);
+    t.slots = reinterpret_cast<ulonglong2 *>(ws + l.table_off);
+    t.mask = kvcm::SlotsFor(n_keys_total) - 1;
+    uint32_t *ids = reinterpret_cast<uint32_t *>(ws + l.ids_off);
+    uint32_t *stamps = reinterpret_cast<uint32_t *>(ws + l.stamps_off);
+    cudaStream_t s = kvcm::AsStream(stream);
+    const int sms = kvcm::GetDeviceInfo().sm_count;
+    const uint64_t n_stamps = static_cast<uint64_t>(n_keys_total) * static_cast<uint64_t>(n_configs);
+    kvcm::LruInitKernel<<<sms * 8, 256, 0, s>>>(t, stamps, n_stamps);
+    if (n_keys_total > 0) {
+        kvcm::LruClaimIdsKernel<<<sms * 8, 256, 0, s>>>(t, d_keys, n_keys_total, d_status);
+        kvcm::LruLookupIdsKernel<<<sms * 8, 256, 0, s>>>(t, d_keys, n_keys_total, ids);
+    }
+    kvcm::LruSweep p;
+    p.ids = ids;
+    p.key_off = d_key_off;
+    p.type = d_trace_type;
+    p.mask_off = d_mask_off;
+    p.quota = d_quota_blocks;
+    p.stamps = stamps;
+    p.queue = reinterpret_cast<uint2 *>(ws + l.queue_off);
+    p.ext_hit = d_ext_hit;
+    p.int_hit = d_int_hit;
+    p.written = d_written;
+    p.cache_blocks = d_cache_blocks;
+    p.n_keys = n_keys_total > 0 ? n_keys_total : 1;
+    p.n_traces = n_traces;
+    p.n_configs = n_configs;
+    p.evict_batch = evict_batch;
+    p.precise = precise;
+    kvcm::LruSweepKernel<<<static_cast<unsigned>(n_configs), 32, 0, s>>>(p);
+    return kvcm::LaunchStatus();
+}
+
+}  // extern "C"

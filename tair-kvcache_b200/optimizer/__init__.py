@@ -1,5 +1,5 @@
 """Batched twin of the Optimizer's trace replay loop (kv_cache_manager/optimizer/manager)."""
-from .replay import (TRACE_DIALOG_TURN, TRACE_GET_LOCATION, TRACE_WRITE_CACHE, ReplayResult,  # noqa: F401
-                     RunTraces, replay_workspace_bytes)
+from .replay import (TRACE_DIALOG_TURN, TRACE_GET_LOCATION, TRACE_WRITE_CACHE, LruSweepResult,  # noqa: F401
+                     ReplayResult, RunTraces, RunTracesLru, replay_lru_workspace_bytes, replay_workspace_bytes)
 from . import trace_reader  # noqa: F401
 from .runner import export_hit_rates, replay_instance, run_trace_file  # noqa: F401

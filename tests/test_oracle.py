@@ -215,3 +215,62 @@ def test_replay_reference_known_answers():
                                                oracle.TRACE_GET_LOCATION], [0, 0, 1])
     assert ext.tolist() == [0, 2, 2] and inte.tolist() == [0, 0, 1] and wr.tolist() == [3, 2, 0]
     assert size.tolist() == [3, 5, 5]
+
+
+W, G, D = oracle.TRACE_WRITE_CACHE, oracle.TRACE_GET_LOCATION, oracle.TRACE_DIALOG_TURN
+
+
+def test_lru_replay_follows_the_reference_policy_tests():
+    # kv_cache_manager/optimizer/test/lru_eviction_policy_test.cc:44-65 (OnBlockAccessed): write 1, write 2,
+    # access 1 -> the next eviction of one block takes 2.  As traces: the third write overflows a quota of 2.
+    ext, inte, wr, size = oracle.LruReplay(2, evict_batch=1, precise=True).run(
+        [1, 2, 1, 3, 2, 1, 3], [0, 1, 2, 3, 4, 5, 6, 7], [W, W, G, W, G, G, G])
+    assert wr.tolist() == [1, 1, 0, 1, 0, 0, 0]
+    assert ext.tolist() == [0, 0, 1, 0, 0, 1, 1]  # 2 is gone, 1 and 3 stayed
+    assert size.tolist() == [1, 2, 2, 2, 2, 2, 2]
+    # :67-96 (EvictBlocks): write 1, 2, 3, evict 2 -> 1 and 2 go, in that order
+    ext, inte, wr, size = oracle.LruReplay(1, evict_batch=1, precise=True).run(
+        [1, 2, 3, 1, 2, 3], [0, 1, 2, 3, 4, 5, 6], [W, W, W, G, G, G])
+    assert size.tolist() == [1, 1, 1, 1, 1, 1] and ext.tolist() == [0, 0, 0, 0, 0, 1]
+    # :98-115, 133-146 (evict more than there is): a batch larger than the list empties it
+    ext, inte, wr, size = oracle.LruReplay(1, evict_batch=10, precise=False).run([1, 2, 1], [0, 1, 2, 3], [W, W, G])
+    assert size.tolist() == [1, 0, 0] and ext.tolist() == [0, 0, 0]
+
+
+def test_lru_replay_rough_mode_evicts_whole_batches():
+    # kv_cache_manager/optimizer/manager/eviction_manager.cc:148-192: rounds of evict_batch until the excess is covered
+    keys = list(range(1, 11))
+    run = lambda precise: oracle.LruReplay(7, evict_batch=2, precise=precise).run(  # noqa: E731
+        keys + [11], [0, 10, 11], [W, W])
+    assert run(True)[3].tolist() == [7, 7]     # 10 -> excess 3 -> 7; 8 -> excess 1 -> 7
+    assert run(False)[3].tolist() == [6, 7]    # 10 -> two batches of 2 -> 6; 7 -> no excess
+
+
+def test_lru_replay_with_room_for_everything_is_the_plain_replay():
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(1, 1 << 60, size=int(rng.integers(1, 30))) for _ in range(8)]
+    keys, off, types, mo = [], [0], [], []
+    for t in range(500):
+        p = prompts[int(rng.integers(0, len(prompts)))]
+        k = list(p[:int(rng.integers(0, len(p) + 1))]) + [int(x) for x in rng.integers(1 << 61, 1 << 62, size=3)]
+        ty = int(rng.integers(0, 3))
+        keys += k
+        off.append(len(keys))
+        types.append(ty)
+        mo.append(int(rng.integers(0, len(k))) if ty == G else 0)
+    want = oracle.Replay().run(keys, off, types, mo)
+    got = oracle.LruReplay(1 << 40).run(keys, off, types, mo)
+    for a, b in zip(want, got):
+        assert np.array_equal(a, b)
+    # and a tight quota changes the answers (the test above would be vacuous otherwise)
+    tight = oracle.LruReplay(20, evict_batch=4).run(keys, off, types, mo)
+    assert tight[3].max() <= 20 + 40 and not np.array_equal(tight[0], want[0])
+
+
+def test_lru_replay_revives_evicted_blocks_inside_a_node():
+    # a chain 1-2-3-4 written as one node; a quota of 2 evicts 1 and 2 (the oldest); the dialog turn [1,2,3,4]
+    # then finds no leading hit (1 is gone), rewrites 1 and 2 and leaves 3 and 4 untouched
+    # (kv_cache_manager/optimizer/index/radix_tree_index.cc:246-262), so the next eviction takes 3 and 4.
+    ext, inte, wr, size = oracle.LruReplay(2, evict_batch=1, precise=True).run(
+        [1, 2, 3, 4, 1, 2, 3, 4, 1, 2, 3, 4], [0, 4, 8, 12], [W, D, G])
+    assert wr.tolist() == [4, 2, 0] and ext.tolist() == [0, 0, 2] and size.tolist() == [2, 2, 2]
