@@ -982,17 +982,193 @@ def main_replay_reference(args):
                       "gpu_launches": 0}))
 
 
+def _lru_trace(n_req, seed, n_prompts=10000, bs=64):
+    """Token lengths and prefix sharing of the mixed-replay workload (Zipf(0.9) reuse over a prompt pool), as numpy
+    arrays: request offsets, prompt offsets, the prompt each request shares a prefix with and how many tokens."""
+    rng = np.random.default_rng(seed)
+    prompt_len = rng.integers(256, 2049, size=n_prompts)
+    req_len = rng.integers(256, 2049, size=n_req)
+    zipf = 1.0 / np.arange(1, n_prompts + 1) ** 0.9
+    prompt_of = rng.choice(n_prompts, size=n_req, p=zipf / zipf.sum())
+    share = (rng.random(n_req) * (np.minimum(req_len, prompt_len[prompt_of]) + 1)).astype(np.int64)
+    poff = np.zeros(n_prompts + 1, dtype=np.int64)
+    np.cumsum(prompt_len, out=poff[1:])
+    off = np.zeros(n_req + 1, dtype=np.int64)
+    np.cumsum(req_len, out=off[1:])
+    return off, poff, prompt_of, share
+
+
+def _lru_quotas(n_keys, n_configs):
+    """Quota points of a tradeoff curve: evenly spaced fractions of the blocks the trace writes in total."""
+    return [max(100, int(n_keys * (c + 1) / (2 * n_configs))) for c in range(n_configs)]
+
+
+def main_lru(args, rank, world):
+    """Tradeoff-curve sweep of the Optimizer: the mixed-replay trace (dialog turns, block 64) replayed with the "lru"
+    policy once per quota point, all points of this rank in one launch (one warp each).  Ranks take different
+    quota points of the same curve (no exchange).  One step = hash the trace + the whole sweep."""
+    import torch
+    import torch.distributed as dist
+
+    import tair_kvcache_b200  # noqa: F401
+    from tair_kvcache_b200.manager import GenKeyVectorBatch, key_offsets, length_order
+    from tair_kvcache_b200.optimizer import TRACE_DIALOG_TURN, RunTracesLru, replay_lru_workspace_bytes
+
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    n_req = args.n_requests or 125000
+    n_cfg = args.n_configs or 148
+    bs = 64
+    off, poff, prompt_of, share = _lru_trace(n_req, 0xB2000005)
+    gen = torch.Generator(device=device).manual_seed(0xB2000005)
+    prompts = torch.randint(0, 151936, (int(poff[-1]),), dtype=torch.int32, device=device, generator=gen)
+    toks = torch.randint(0, 151936, (int(off[-1]),), dtype=torch.int32, device=device, generator=gen)
+    d_share = torch.from_numpy(share).to(device)
+    within = torch.arange(int(share.sum()), device=device) - torch.repeat_interleave(
+        torch.cumsum(d_share, 0) - d_share, d_share)
+    toks[torch.repeat_interleave(torch.from_numpy(off[:-1]).to(device), d_share) + within] = prompts[
+        torch.repeat_interleave(torch.from_numpy(poff[prompt_of]).to(device), d_share) + within]
+    del within, prompts
+    ko = key_offsets(off, bs)
+    n_keys = int(ko[-1])
+    d_off, d_ko = torch.from_numpy(off).to(device), torch.from_numpy(ko).to(device)
+    order_np, residency = length_order(off, with_residency=True)
+    d_order = torch.from_numpy(order_np).to(device)
+    d_keys = torch.empty(n_keys, dtype=torch.int64, device=device)
+    d_type = torch.full((n_req,), TRACE_DIALOG_TURN, dtype=torch.uint8, device=device)
+    all_quotas = _lru_quotas(n_keys, n_cfg * world)
+    quotas = all_quotas[rank::world]  # every rank gets points from the whole range
+    workspace = torch.empty(replay_lru_workspace_bytes(n_keys, n_cfg), dtype=torch.uint8, device=device)
+    status = torch.zeros(4, dtype=torch.int32, device=device)
+
+    def step():
+        keys = GenKeyVectorBatch(toks, d_off, bs, d_ko, n_keys, out=d_keys, order=d_order, warps_per_sm=residency)
+        return RunTracesLru(keys, d_ko, d_type, quotas, evict_batch=100, precise=False, workspace=workspace,
+                            status=status)
+
+    sampler = ClockSampler(str(torch.cuda.get_device_properties(device).uuid)) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    for _ in range(max(1, min(args.warmup, 3))):
+        res = step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    steps = max(1, min(args.steps, 5))
+    if sampler:
+        sampler.mark_begin()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        res = step()
+    e1.record()
+    torch.cuda.synchronize(device)
+    if sampler:
+        sampler.mark_end()
+    clocks = sampler.stop() if sampler else None
+    if world > 1:
+        dist.barrier()
+    ms = e0.elapsed_time(e1) / steps
+    # the sweep kernel alone
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    RunTracesLru(d_keys, d_ko, d_type, quotas, evict_batch=100, precise=False, workspace=workspace, status=status)
+    e3.record()
+    torch.cuda.synchronize(device)
+    sweep_ms = e2.elapsed_time(e3)
+    hit_rate = (res.external_hit_blocks.sum(dim=1).double() / max(n_keys, 1)).cpu().numpy()
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+
+    parity = None
+    if rank == 0 and not args.no_cpu:
+        from oracle import kvcm_oracle as oracle
+        m = min(n_req, 20000)  # the sequential CPU replay of the first requests sees the same history
+        k = d_keys[:int(ko[m])].cpu().numpy()
+        c = len(quotas) // 3
+        want = oracle.LruReplay(quotas[c], evict_batch=100, precise=False).run(k, ko[:m + 1], np.zeros(m, np.uint8))
+        parity = bool(np.array_equal(want[0], res.external_hit_blocks[c, :m].cpu().numpy()) and
+                      np.array_equal(want[2], res.write_blocks[c, :m].cpu().numpy()) and
+                      np.array_equal(want[3], res.current_cache_blocks[c, :m].cpu().numpy()))
+    if rank == 0:
+        replays = n_req * n_cfg * world
+        print(json.dumps({
+            "metric": "lru_tradeoff_sweep_request_replays_per_s", "value": replays / (ms / 1e3),
+            "unit": "request-replays/s", "n_gpus": world, "steps": steps, "warmup": max(1, min(args.warmup, 3)),
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int64", "data": "synthetic",
+            "config": {"workload": "%d requests (dialog turns, 256-2048 uint32 tokens, block 64, Zipf(0.9) prefix "
+                                   "reuse over 10000 prompts = %d token blocks) replayed with LRU eviction at %d quota "
+                                   "points per GPU (%d..%d blocks, rough mode, batches of 100); hash + sweep per step"
+                                   % (n_req, n_keys, n_cfg, min(all_quotas), max(all_quotas)),
+                       "sweep_kernel_ms_rank0": sweep_ms, "hit_rate_lowest_quota": float(hit_rate[0]),
+                       "hit_rate_highest_quota": float(hit_rate[-1]), "table_overflows": int(status[0].item()),
+                       "parity_sample_ok": parity},
+            "clocks": clocks, "gpu_launches": 5 * steps}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main_lru_reference(args):
+    """CPU arm of --workload lru on a bounded sample: the first requests of the same trace hashed and replayed with
+    the radix tree + LRU restatement, one quota point per host thread at a time (the reference's tradeoff scripts
+    likewise run one optimizer per point in a thread pool)."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    from oracle import kvcm_oracle as oracle
+    threads = os.cpu_count() or 1
+    n_req_full = args.n_requests or 125000
+    n_req, bs = min(n_req_full, 20000), 64
+    n_cfg = min(args.n_configs or 148, 2 * threads)
+    off, poff, prompt_of, share = _lru_trace(n_req_full, 0xB2000005)
+    off = off[:n_req + 1]
+    rng = np.random.default_rng(0xB2000005)
+    prompts = rng.integers(0, 151936, size=int(poff[-1]), dtype=np.int64).astype(np.uint32)
+    toks = rng.integers(0, 151936, size=int(off[-1]), dtype=np.int64).astype(np.uint32)
+    for r in range(n_req):
+        toks[off[r]:off[r] + share[r]] = prompts[poff[prompt_of[r]]:poff[prompt_of[r]] + share[r]]
+    types = np.zeros(n_req, dtype=np.uint8)
+    t0 = time.perf_counter()
+    keys, ko = oracle.hash_blocks(toks, off, bs, threads=threads)
+    quotas = _lru_quotas(int(ko[-1]), n_cfg)
+
+    def one(q):
+        return int(oracle.LruReplay(q, evict_batch=100, precise=False).run(keys, ko, types)[0].sum())
+
+    with ThreadPoolExecutor(max_workers=threads) as pool:
+        hits = list(pool.map(one, quotas))
+    dt = time.perf_counter() - t0
+    value = n_req * n_cfg / dt
+    sample = "first %d of %d requests (%d token blocks), %d quota points, hit blocks %d..%d" % (
+        n_req, n_req_full, int(ko[-1]), n_cfg, min(hits), max(hits))
+    print(json.dumps({"impl": "reference", "metric": "lru_tradeoff_sweep_request_replays_per_s", "value": value,
+                      "unit": "request-replays/s", "n_gpus": args.gpus, "steps": 1, "warmup": 0,
+                      "higher_is_better": True, "dtype": "int64", "data": "synthetic",
+                      "config": {"workload": "CPU restatement (hash + radix tree with LRU eviction, one quota point "
+                                             "per thread) on a bounded sample"},
+                      "cpu_baseline": {"value": value, "unit": "request-replays/s", "cores": threads, "kind": "port",
+                                       "sample": sample},
+                      "e2e": {"value": value, "unit": "request-replays/s", "h2d_bytes_per_step": 0,
+                              "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c1", "c4", "c5"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c1", "c4", "c5", "lru"])
     ap.add_argument("--n-requests", type=int, default=0, help="c4: override the number of requests")
     ap.add_argument("--index-keys", type=int, default=0, help="c4: override the number of indexed keys")
     ap.add_argument("--shard-mode", default="peer", choices=["peer", "exchange"],
                     help="c4 on several GPUs: probe remote shards over NVLink, or exchange keys and reduce results")
+    ap.add_argument("--n-configs", type=int, default=0, help="lru: quota points per GPU (default 148)")
     ap.add_argument("--no-prefix", action="store_true", help="skip the prefix-match side measurement")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-staging leg (profiling runs)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
@@ -1011,6 +1187,13 @@ def main():
                 main_replay_reference(args)
             return
         main_replay(args, rank, world)
+        return
+    if args.workload == "lru":
+        if args.impl == "reference":
+            if rank == 0:
+                main_lru_reference(args)
+            return
+        main_lru(args, rank, world)
         return
     if args.workload == "c4":
         if args.impl == "reference":

@@ -32,7 +32,7 @@ namespace kvcm {
 namespace {
 
 constexpr uint64_t kEmptyKey = 0x8000000000000000ull;
-constexpr int kWarps = 8;
+constexpr int kEvictWindows = 4;
 
 struct IdTable {
     ulonglong2 *slots;         // {key, id}
@@ -147,17 +147,36 @@ __global__ void __launch_bounds__(32) LruSweepKernel(const LruSweep p) {
     uint32_t counter = 0;  // last stamp handed out
     int64_t head = 0, tail = 0, resident = 0;
 
+    // What a trace reads before it touches any state (its extent, kind and the ids of its first 32
+    // keys) is fetched one trace ahead, its extent two traces ahead, so that the only load a trace
+    // waits for is the one that depends on the traces before it: stamp[id].
+    auto extent = [&](int32_t t, int64_t *beg, int64_t *n, uint8_t *ty, int64_t *skip) {
+        if (t < p.n_traces) {
+            *beg = p.key_off[t];
+            *n = p.key_off[t + 1] - *beg;
+            *ty = p.type[t];
+            *skip = (*ty == 1 && p.mask_off != nullptr) ? p.mask_off[t] : 0;
+        } else {
+            *beg = 0, *n = 0, *ty = 1, *skip = 0;
+        }
+    };
+    int64_t beg, n, skip, beg1, n1, skip1;
+    uint8_t ty, ty1;
+    extent(0, &beg, &n, &ty, &skip);
+    extent(1, &beg1, &n1, &ty1, &skip1);
+    uint32_t first_id = lane < n ? p.ids[beg + lane] : 0u;
+
     for (int32_t t = 0; t < p.n_traces; ++t) {
-        const int64_t beg = p.key_off[t];
-        const int64_t n = p.key_off[t + 1] - beg;
-        const uint8_t ty = p.type[t];
-        const int64_t skip = (ty == 1 && p.mask_off != nullptr) ? p.mask_off[t] : 0;
+        const uint32_t next_first_id = lane < n1 ? p.ids[beg1 + lane] : 0u;
+        int64_t beg2, n2, skip2;
+        uint8_t ty2;
+        extent(t + 2, &beg2, &n2, &ty2, &skip2);
         int32_t ext = 0, inte = 0, wr = 0;
         bool alive = ty != 2;  // still inside the leading run of cached blocks
         for (int64_t base = 0; base < n; base += 32) {
             const int64_t i = base + lane;
             const bool have = i < n;
-            const uint32_t id = have ? p.ids[beg + i] : 0u;
+            const uint32_t id = base == 0 ? first_id : (have ? p.ids[beg + i] : 0u);
             const uint32_t cur = have ? stamp[id] : 0u;
             const uint32_t in_range = __ballot_sync(0xffffffffu, have);
             const uint32_t cached = __ballot_sync(0xffffffffu, have && cur != 0u);
@@ -197,28 +216,42 @@ __global__ void __launch_bounds__(32) LruSweepKernel(const LruSweep p) {
                 need = batches * p.evict_batch;
                 if (need > resident) need = resident;
             }
+            // The queue is read kEvictWindows x 32 entries at a time: the entries, then their stamps, are
+            // independent loads, so a round of ~100 evictions costs two memory round trips, not eight.
             while (need > 0 && head < tail) {
-                const int64_t j = head + lane;
-                uint2 e = make_uint2(0u, 0u);
-                bool live = false;
-                if (j < tail) {
-                    e = queue[j];
-                    live = stamp[e.x] == e.y;
+                uint2 e[kEvictWindows];
+                bool live[kEvictWindows];
+#pragma unroll
+                for (int u = 0; u < kEvictWindows; ++u) {
+                    const int64_t j = head + u * 32 + lane;
+                    e[u] = j < tail ? queue[j] : make_uint2(0u, 0u);
                 }
-                const uint32_t lives = __ballot_sync(0xffffffffu, live);
-                const uint32_t n_live = __popc(lives);
-                uint32_t take = lives;
-                int64_t advance = tail - head < 32 ? tail - head : 32;
-                if (static_cast<int64_t>(n_live) > need) {
-                    // keep only the first `need` live entries of this window; stop right behind the last one
-                    const bool mine = live && static_cast<int64_t>(__popc(lives & lt)) < need;
-                    take = __ballot_sync(0xffffffffu, mine);
-                    advance = 32 - __clz(take);
+#pragma unroll
+                for (int u = 0; u < kEvictWindows; ++u) {
+                    const int64_t j = head + u * 32 + lane;
+                    live[u] = j < tail && stamp[e[u].x] == e[u].y;
                 }
-                if ((take >> lane) & 1u) stamp[e.x] = 0u;
-                const uint32_t n_take = __popc(take);
-                need -= n_take;
-                resident -= n_take;
+                int64_t advance = 0;
+#pragma unroll
+                for (int u = 0; u < kEvictWindows; ++u) {
+                    const int64_t left = tail - (head + u * 32);  // entries from this window on
+                    if (need > 0 && left > 0) {
+                        const uint32_t lives = __ballot_sync(0xffffffffu, live[u]);
+                        uint32_t take = lives;
+                        int64_t step = left < 32 ? left : 32;
+                        if (static_cast<int64_t>(__popc(lives)) > need) {
+                            // keep only the first `need` live entries of this window; stop right behind the last one
+                            const bool mine = live[u] && static_cast<int64_t>(__popc(lives & lt)) < need;
+                            take = __ballot_sync(0xffffffffu, mine);
+                            step = 32 - __clz(take);
+                        }
+                        if ((take >> lane) & 1u) stamp[e[u].x] = 0u;
+                        const uint32_t n_take = __popc(take);
+                        need -= n_take;
+                        resident -= n_take;
+                        advance += step;
+                    }
+                }
                 head += advance;
                 __syncwarp();
             }
@@ -229,6 +262,8 @@ __global__ void __launch_bounds__(32) LruSweepKernel(const LruSweep p) {
             p.written[out0 + t] = wr;
             p.cache_blocks[out0 + t] = resident;
         }
+        beg = beg1, n = n1, ty = ty1, skip = skip1, first_id = next_first_id;
+        beg1 = beg2, n1 = n2, ty1 = ty2, skip1 = skip2;
     }
 }
 
