@@ -7,7 +7,8 @@
 //   GpuBlockIndex        the device replica of MetaIndexer's table (kv_cache_manager/meta/meta_indexer.cc:419-440)
 //   GpuMetaSearcher      PrefixMatch / ReverseRollSlideWindowMatch / BatchGet
 //       kv_cache_manager/manager/meta_searcher.cc:74-265, batch-of-one and batched forms
-//   GpuTraceReplayer     OptimizerRunner::RunTraces without eviction (kv_cache_manager/optimizer/manager/optimizer_runner.cc:29-215)
+//   GpuTraceReplayer     OptimizerRunner::RunTraces (kv_cache_manager/optimizer/manager/optimizer_runner.cc:29-215) without
+//                        eviction, or with the "lru" policy at many quota points at once
 //   IovCopier            the per-Iov loops of kv_cache_manager/client/src/internal/sdk/local_file_sdk.cc:223-245,326-353
 //
 // Header-only, C++17, needs only <cuda_runtime.h> and kvcm_b200.h.  Every call stages its
@@ -374,14 +375,65 @@ public:
         records->assign(n, ReplayRecord{0, 0, 0, 0});
         if (n == 0) return KVCM_OK;
         int64_t n_keys = 0;
-        for (const auto &t : traces) n_keys += static_cast<int64_t>(t.keys.size());
+        int32_t rc = Pack(traces, &n_keys);
+        if (rc != KVCM_OK) return rc;
         const int64_t ws_bytes = kvcm_b200_replay_workspace_bytes(n_keys);
         if (ws_bytes < 0) return KVCM_EC_BADARGS;
+        if (!Outputs(n, 1) || !workspace_.Reserve(static_cast<size_t>(ws_bytes), true)) return KVCM_EC_NOSPC;
+        rc = kvcm_b200_replay(keys_.dev<int64_t>(), off_.dev<int64_t>(), kind_.dev<uint8_t>(), mask_.dev<int64_t>(), n,
+                              n_keys, workspace_.dev<void>(), ws_bytes, ext_.dev<int32_t>(), int_.dev<int32_t>(),
+                              wr_.dev<int32_t>(), size_.dev<int64_t>(), nullptr, stream_);
+        if (rc != KVCM_OK) return rc;
+        rc = Fetch(static_cast<size_t>(n));
+        if (rc != KVCM_OK) return rc;
+        for (int32_t i = 0; i < n; ++i) (*records)[i] = Record(i);
+        return KVCM_OK;
+    }
+
+    // The same traces replayed with the "lru" eviction policy once per entry of quota_blocks (the points of a
+    // tradeoff curve; quota_capacity * used_percentage in blocks), all in one launch.  evict_batch and precise are
+    // eviction_batch_size_per_instance and the eviction mode (false = the rough modes, which evict whole batches;
+    // true = INSTANCE_PRECISE).  (*records)[c][t] belongs to quota c and trace t.
+    int32_t RunTracesLru(const std::vector<ReplayTrace> &traces, const std::vector<int64_t> &quota_blocks,
+                         int32_t evict_batch, bool precise, std::vector<std::vector<ReplayRecord>> *records) {
+        const int32_t n = static_cast<int32_t>(traces.size());
+        const int32_t n_cfg = static_cast<int32_t>(quota_blocks.size());
+        records->assign(n_cfg, std::vector<ReplayRecord>(n, ReplayRecord{0, 0, 0, 0}));
+        if (n_cfg == 0) return KVCM_EC_BADARGS;
+        if (n == 0) return KVCM_OK;
+        int64_t n_keys = 0;
+        int32_t rc = Pack(traces, &n_keys);
+        if (rc != KVCM_OK) return rc;
+        const int64_t ws_bytes = kvcm_b200_replay_lru_workspace_bytes(n_keys, n_cfg);
+        if (ws_bytes < 0) return KVCM_EC_OUT_OF_LIMIT;
+        if (!Outputs(n, n_cfg) || !quota_.Reserve(sizeof(int64_t) * n_cfg) ||
+            !workspace_.Reserve(static_cast<size_t>(ws_bytes), true)) {
+            return KVCM_EC_NOSPC;
+        }
+        std::memcpy(quota_.host<int64_t>(), quota_blocks.data(), sizeof(int64_t) * n_cfg);
+        if (!quota_.ToDevice(sizeof(int64_t) * n_cfg, stream_)) return KVCM_ER_CUDAMEMCPY_ERROR;
+        rc = kvcm_b200_replay_lru(keys_.dev<int64_t>(), off_.dev<int64_t>(), kind_.dev<uint8_t>(),
+                                  mask_.dev<int64_t>(), n, n_keys, quota_.dev<int64_t>(), n_cfg, evict_batch,
+                                  precise ? 1 : 0, workspace_.dev<void>(), ws_bytes, ext_.dev<int32_t>(),
+                                  int_.dev<int32_t>(), wr_.dev<int32_t>(), size_.dev<int64_t>(), nullptr, stream_);
+        if (rc != KVCM_OK) return rc;
+        rc = Fetch(static_cast<size_t>(n) * n_cfg);
+        if (rc != KVCM_OK) return rc;
+        for (int32_t c = 0; c < n_cfg; ++c) {
+            for (int32_t i = 0; i < n; ++i) (*records)[c][i] = Record(static_cast<size_t>(c) * n + i);
+        }
+        return KVCM_OK;
+    }
+
+private:
+    // CSR form of the traces in pinned memory, copied to the device.
+    int32_t Pack(const std::vector<ReplayTrace> &traces, int64_t *n_keys_out) {
+        const int32_t n = static_cast<int32_t>(traces.size());
+        int64_t n_keys = 0;
+        for (const auto &t : traces) n_keys += static_cast<int64_t>(t.keys.size());
         const size_t off_bytes = sizeof(int64_t) * (n + 1);
         if (!keys_.Reserve(sizeof(int64_t) * (n_keys + 1)) || !off_.Reserve(off_bytes) || !kind_.Reserve(n) ||
-            !mask_.Reserve(sizeof(int64_t) * n) || !ext_.Reserve(sizeof(int32_t) * n) ||
-            !int_.Reserve(sizeof(int32_t) * n) || !wr_.Reserve(sizeof(int32_t) * n) ||
-            !size_.Reserve(sizeof(int64_t) * n) || !workspace_.Reserve(static_cast<size_t>(ws_bytes), true)) {
+            !mask_.Reserve(sizeof(int64_t) * n)) {
             return KVCM_EC_NOSPC;
         }
         int64_t at = 0;
@@ -399,27 +451,28 @@ public:
             !kind_.ToDevice(n, stream_) || !mask_.ToDevice(sizeof(int64_t) * n, stream_)) {
             return KVCM_ER_CUDAMEMCPY_ERROR;
         }
-        int32_t rc = kvcm_b200_replay(keys_.dev<int64_t>(), off_.dev<int64_t>(), kind_.dev<uint8_t>(),
-                                      mask_.dev<int64_t>(), n, n_keys, workspace_.dev<void>(), ws_bytes,
-                                      ext_.dev<int32_t>(), int_.dev<int32_t>(), wr_.dev<int32_t>(),
-                                      size_.dev<int64_t>(), nullptr, stream_);
-        if (rc != KVCM_OK) return rc;
-        if (!ext_.ToHost(sizeof(int32_t) * n, stream_) || !int_.ToHost(sizeof(int32_t) * n, stream_) ||
-            !wr_.ToHost(sizeof(int32_t) * n, stream_) || !size_.ToHost(sizeof(int64_t) * n, stream_)) {
-            return KVCM_ER_CUDAMEMCPY_ERROR;
-        }
-        rc = detail::Sync(stream_);
-        if (rc != KVCM_OK) return rc;
-        for (int32_t i = 0; i < n; ++i) {
-            (*records)[i] = ReplayRecord{ext_.host<int32_t>()[i], int_.host<int32_t>()[i], wr_.host<int32_t>()[i],
-                                         size_.host<int64_t>()[i]};
-        }
+        *n_keys_out = n_keys;
         return KVCM_OK;
     }
+    bool Outputs(int32_t n, int32_t n_cfg) {
+        const size_t m = static_cast<size_t>(n) * n_cfg;
+        return ext_.Reserve(sizeof(int32_t) * m) && int_.Reserve(sizeof(int32_t) * m) &&
+               wr_.Reserve(sizeof(int32_t) * m) && size_.Reserve(sizeof(int64_t) * m);
+    }
+    int32_t Fetch(size_t m) {
+        if (!ext_.ToHost(sizeof(int32_t) * m, stream_) || !int_.ToHost(sizeof(int32_t) * m, stream_) ||
+            !wr_.ToHost(sizeof(int32_t) * m, stream_) || !size_.ToHost(sizeof(int64_t) * m, stream_)) {
+            return KVCM_ER_CUDAMEMCPY_ERROR;
+        }
+        return detail::Sync(stream_);
+    }
+    ReplayRecord Record(size_t i) {
+        return ReplayRecord{ext_.host<int32_t>()[i], int_.host<int32_t>()[i], wr_.host<int32_t>()[i],
+                            size_.host<int64_t>()[i]};
+    }
 
-private:
     cudaStream_t stream_;
-    detail::Mirror keys_, off_, kind_, mask_, ext_, int_, wr_, size_, workspace_;
+    detail::Mirror keys_, off_, kind_, mask_, quota_, ext_, int_, wr_, size_, workspace_;
 };
 
 // kv_cache_manager/client/include/common.h:94-116

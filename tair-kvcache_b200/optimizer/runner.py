@@ -1,15 +1,17 @@
 """Trace file -> per-instance replay on the GPU -> hit-rate table, the shape of OptimizerRunner::Run followed by
 HitAnalysis::Analyze (kv_cache_manager/optimizer/manager/optimizer_runner.cc:13-68,
-kv_cache_manager/optimizer/analysis/result_analysis.cc:10-113), for configurations without eviction."""
+kv_cache_manager/optimizer/analysis/result_analysis.cc:10-113): without eviction, or with the "lru" policy at
+one or many quota points (the tradeoff curves of kv_cache_manager/optimizer/analysis/script/
+tradeoff_curve_by_instances.py)."""
 import os
-from typing import Dict, List, Optional
+from typing import Dict, List, Optional, Sequence, Union
 
 import numpy as np
 import torch
 
 from ..manager.hash_util import ApplyPrefixHashBatch
 from . import trace_reader as tr
-from .replay import RunTraces
+from .replay import RunTraces, RunTracesLru
 
 CSV_HEADER = ("TimestampUs,CachedBlocksCurrentInstance,CachedBlocksPerInstance,CachedBlocksAllInstance,"
               "InternalReadBlocks,ExternalReadBlocks,TotalReadBlocks,InternalHitBlocks,"
@@ -22,9 +24,14 @@ def _g(x: float) -> str:
     return "%g" % x
 
 
-def replay_instance(traces: List[tr.Trace], device, rw_separation: bool = False) -> Dict[str, np.ndarray]:
+def replay_instance(traces: List[tr.Trace], device, rw_separation: bool = False,
+                    quota_blocks: Union[None, int, Sequence[int]] = None, evict_batch: int = 100,
+                    precise: bool = False):
     """Replays the traces of one instance.  As OptimizerRunner::RunTrace does, only prefix_match queries are
-    replayed, dialog turns are skipped in read/write-separation mode and Get/Write traces are skipped otherwise."""
+    replayed, dialog turns are skipped in read/write-separation mode and Get/Write traces are skipped otherwise.
+    quota_blocks = None: nothing is ever evicted; an int: "lru" eviction at that quota (quota_capacity *
+    used_percentage, in blocks); a sequence: one record per quota, all replayed in one launch.  evict_batch and
+    precise are eviction_batch_size_per_instance and the eviction mode (False = the rough modes)."""
     keep = []
     for t in traces:
         if t.kind != tr.WRITE_CACHE and t.query_type != "prefix_match":
@@ -36,14 +43,38 @@ def replay_instance(traces: List[tr.Trace], device, rw_separation: bool = False)
     d_keys, d_off = torch.from_numpy(keys).to(device), torch.from_numpy(off).to(device)
     if any(t.needs_prefix_hash for t in keep):  # Qwen-Bailian ids: chain them first
         d_keys = ApplyPrefixHashBatch(d_keys, d_off)
-    res = RunTraces(d_keys, d_off, torch.from_numpy(kind).to(device), torch.from_numpy(mask).to(device))
-    ext, inte, wr, size = (x.cpu().numpy() for x in res)
     ts = np.array([t.timestamp_us for t in keep], dtype=np.int64)
     # GetLocation: masked keys are internal reads; a dialog turn reads its query keys externally and replays total_keys
     internal_read = np.where(kind == tr.GET_LOCATION, mask, 0)
     external_read = np.where(kind == tr.WRITE_CACHE, 0, read - internal_read)
-    return dict(timestamp_us=ts, kind=kind, external_read_blocks=external_read, internal_read_blocks=internal_read,
-                external_hit_blocks=ext, internal_hit_blocks=inte, write_blocks=wr, current_cache_blocks=size)
+
+    def record(ext, inte, wr, size):
+        return dict(timestamp_us=ts, kind=kind, external_read_blocks=external_read,
+                    internal_read_blocks=internal_read, external_hit_blocks=ext, internal_hit_blocks=inte,
+                    write_blocks=wr, current_cache_blocks=size)
+
+    d_kind, d_mask = torch.from_numpy(kind).to(device), torch.from_numpy(mask).to(device)
+    if quota_blocks is None:
+        return record(*(x.cpu().numpy() for x in RunTraces(d_keys, d_off, d_kind, d_mask)))
+    quotas = [int(quota_blocks)] if np.isscalar(quota_blocks) else [int(q) for q in quota_blocks]
+    res = [x.cpu().numpy() for x in RunTracesLru(d_keys, d_off, d_kind, quotas, d_mask, evict_batch, precise)]
+    recs = [record(*(x[c] for x in res)) for c in range(len(quotas))]
+    return recs[0] if np.isscalar(quota_blocks) else recs
+
+
+def tradeoff_curve(recs: Sequence[Dict[str, np.ndarray]]) -> np.ndarray:
+    """Accumulated hit rates at the end of each replay: rows of (internal, external, total), the three numbers the
+    reference's tradeoff scripts read from the last line of every run's CSV
+    (kv_cache_manager/optimizer/analysis/script/optimizer_analysis_utils.py:207-270)."""
+    out = np.zeros((len(recs), 3))
+    for c, rec in enumerate(recs):
+        reads = rec["kind"] != tr.WRITE_CACHE
+        total = int((rec["internal_read_blocks"][reads] + rec["external_read_blocks"][reads]).sum())
+        if total:
+            out[c, 0] = int(rec["internal_hit_blocks"][reads].sum()) / total
+            out[c, 1] = int(rec["external_hit_blocks"][reads].sum()) / total
+        out[c, 2] = out[c, 0] + out[c, 1]
+    return out
 
 
 def export_hit_rates(path: str, rec: Dict[str, np.ndarray]) -> None:
@@ -70,19 +101,26 @@ def export_hit_rates(path: str, rec: Dict[str, np.ndarray]) -> None:
 
 
 def run_trace_file(trace_path: str, trace_type: str, output_dir: str, device=None,
-                   block_sizes: Optional[Dict[str, int]] = None, rw_separation: bool = False
-                   ) -> Dict[str, Dict[str, np.ndarray]]:
-    """Loads a trace file, replays every instance on the GPU and writes `<instance>_hit_rates.csv` per instance."""
+                   block_sizes: Optional[Dict[str, int]] = None, rw_separation: bool = False,
+                   quota_blocks: Union[None, int, Sequence[int]] = None, evict_batch: int = 100,
+                   precise: bool = False):
+    """Loads a trace file, replays every instance on the GPU and writes `<instance>_hit_rates.csv` per instance
+    (`<instance>_quota<q>_hit_rates.csv` per instance and quota when quota_blocks is a sequence).  Every instance is
+    replayed on its own: instances that share one group quota in the reference's configuration are not modelled."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     traces = tr.load_traces(trace_path, trace_type, block_sizes)
     by_instance: Dict[str, List[tr.Trace]] = {}
     for t in traces:
         by_instance.setdefault(t.instance_id, []).append(t)
     os.makedirs(output_dir, exist_ok=True)
+    sweep = quota_blocks is not None and not np.isscalar(quota_blocks)
     out = {}
     for instance_id, ts in sorted(by_instance.items()):
-        rec = replay_instance(ts, device, rw_separation)
-        if (rec["kind"] != tr.WRITE_CACHE).any():
-            export_hit_rates(os.path.join(output_dir, instance_id + "_hit_rates.csv"), rec)
+        rec = replay_instance(ts, device, rw_separation, quota_blocks, evict_batch, precise)
+        for c, r in enumerate(rec if sweep else [rec]):
+            if (r["kind"] != tr.WRITE_CACHE).any():
+                name = "%s_quota%d_hit_rates.csv" % (instance_id, int(quota_blocks[c])) if sweep else \
+                    instance_id + "_hit_rates.csv"
+                export_hit_rates(os.path.join(output_dir, name), r)
         out[instance_id] = rec
     return out

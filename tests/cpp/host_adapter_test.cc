@@ -178,6 +178,21 @@ static void TestReplay() {
     EXPECT_EQ(rec[2].internal_hit_blocks, 1);
     EXPECT_EQ(rec[2].current_cache_blocks, 5);
     EXPECT_EQ(replayer.RunTraces({}, &rec), KVCM_OK);
+    // kv_cache_manager/optimizer/test/lru_eviction_policy_test.cc:44-65 as traces: write 1, write 2, read 1; a third
+    // block then overflows a quota of 2 and the least recently used block, 2, goes.  With room for all, nothing goes.
+    std::vector<std::vector<ReplayRecord>> sweep;
+    const std::vector<ReplayTrace> lru = {{TraceKind::WriteCache, {1}},  {TraceKind::WriteCache, {2}},
+                                          {TraceKind::GetLocation, {1}}, {TraceKind::WriteCache, {3}},
+                                          {TraceKind::GetLocation, {2}}, {TraceKind::GetLocation, {1}}};
+    EXPECT_EQ(replayer.RunTracesLru(lru, {2, 100}, 1, true, &sweep), KVCM_OK);
+    EXPECT_EQ(sweep.size(), 2u);
+    EXPECT_EQ(sweep[0][2].external_hit_blocks, 1);
+    EXPECT_EQ(sweep[0][3].current_cache_blocks, 2);
+    EXPECT_EQ(sweep[0][4].external_hit_blocks, 0);
+    EXPECT_EQ(sweep[0][5].external_hit_blocks, 1);
+    EXPECT_EQ(sweep[1][4].external_hit_blocks, 1);
+    EXPECT_EQ(sweep[1][5].current_cache_blocks, 3);
+    EXPECT_EQ(replayer.RunTracesLru(lru, {}, 1, true, &sweep), KVCM_EC_BADARGS);
 }
 
 int main() {

@@ -74,3 +74,34 @@ def test_publisher_log_file_in_both_replay_modes(tmp_path):
     assert rec["write_blocks"].tolist() == [0, 5, 0, 2] and rec["internal_read_blocks"].tolist() == [0, 0, 1, 0]
     csv = (tmp_path / "o2" / "i1_hit_rates.csv").read_text().splitlines()
     assert len(csv) == 3 and csv[2] == "40, 5, 5, 5, 1, 3, 4, 1, 0.25, 2, 0.5, 0.75, 0.125, 0.25, 0.375"
+
+
+def test_qwen_bailian_file_with_lru_quota_sweep(tmp_path):
+    from tair_kvcache_b200.optimizer import tradeoff_curve
+    rng = np.random.default_rng(9)
+    path = tmp_path / "trace.jsonl"
+    seqs = _write_qwen_trace(path, rng, 600)
+    quotas = [10, 50, 200, 1000, 100000]
+    out = run_trace_file(str(path), "qwen_bailian", str(tmp_path / "out"), device="cuda:0", quota_blocks=quotas,
+                         evict_batch=5)
+    recs = out["instance"]
+    ordered = seqs[::-1]
+    keys = [oracle.apply_prefix_hash(s) for s in ordered]
+    off = np.zeros(len(keys) + 1, dtype=np.int64)
+    np.cumsum([len(k) for k in keys], out=off[1:])
+    flat, kinds = np.concatenate(keys), np.zeros(len(keys), dtype=np.uint8)
+    rates = tradeoff_curve(recs)
+    for c, q in enumerate(quotas):
+        want = oracle.LruReplay(q, evict_batch=5).run(flat, off, kinds)
+        assert np.array_equal(recs[c]["external_hit_blocks"], want[0])
+        assert np.array_equal(recs[c]["write_blocks"], want[2])
+        assert np.array_equal(recs[c]["current_cache_blocks"], want[3])
+        assert rates[c, 1] == want[0].sum() / sum(len(s) for s in seqs) and rates[c, 0] == 0
+        lines = (tmp_path / "out" / ("instance_quota%d_hit_rates.csv" % q)).read_text().splitlines()
+        assert len(lines) == 601 and lines[-1].split(", ")[-1] == "%g" % rates[c, 2]
+    assert rates[0, 2] < rates[2, 2] <= rates[4, 2]  # a larger cache never hurts this trace
+    # a single quota gives one record and the plain file name
+    rec = run_trace_file(str(path), "qwen_bailian", str(tmp_path / "one"), device="cuda:0", quota_blocks=50,
+                         evict_batch=5)["instance"]
+    assert np.array_equal(rec["external_hit_blocks"], recs[1]["external_hit_blocks"])
+    assert (tmp_path / "one" / "instance_hit_rates.csv").exists()
