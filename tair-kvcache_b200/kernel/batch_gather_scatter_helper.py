@@ -46,6 +46,37 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+def _coalesce_token_runs(row_indices, slot_indices, rows_per_block: int, pool_rows: Optional[int], n_slots: int):
+    """Token indices given as a host list (the reference's argument type) almost always come from a block table:
+    runs of page_size consecutive tokens that start at a multiple of page_size
+    (kv_cache_manager/py_connector/vllm/v1_connector.py:308-320).  Such a list is the page form with longer rows, and
+    long rows move faster (one bulk copy per page instead of one vector loop per token).  Returns
+    (row array, rows per block, run length) with run length g > 1 when every block splits into aligned runs of g
+    tokens, else None.  Only lists whose indices and staging slots are all in range are rewritten, so that the
+    counts reported in the status words cannot change."""
+    if isinstance(row_indices, torch.Tensor) or rows_per_block < 2:
+        return None
+    arr = np.asarray(row_indices, dtype=np.int64)
+    if arr.size == 0 or arr.size % rows_per_block != 0 or arr.min() < 0:
+        return None
+    if pool_rows is not None and arr.max() >= pool_rows:
+        return None
+    if slot_indices is not None and not isinstance(slot_indices, torch.Tensor):
+        sl = np.asarray(slot_indices, dtype=np.int64)
+        if sl.size and (sl.min() < 0 or sl.max() >= n_slots):
+            return None
+    elif slot_indices is not None:
+        return None  # device-resident slots cannot be range-checked here without a sync
+    g = rows_per_block
+    while g >= 2:
+        if rows_per_block % g == 0 and (pool_rows is None or pool_rows % g == 0):
+            runs = arr.reshape(-1, g)
+            if not (runs[:, 0] % g).any() and (np.diff(runs, axis=1) == 1).all():
+                return np.ascontiguousarray(runs[:, 0] // g, dtype=np.int32), rows_per_block // g, g
+        g //= 2 if g % 2 == 0 else g  # halve while even; an odd length is tried once
+    return None
+
+
 def _move(entry: str, kv_caches_ptrs_tensor: torch.Tensor, staging: torch.Tensor, row_indices: IndexArg,
           slot_indices: Optional[IndexArg], rows_per_block: int, row_bytes: int, pool_rows: Optional[int],
           status: Optional[torch.Tensor], sm_count: Optional[int] = None) -> None:
@@ -56,6 +87,17 @@ def _move(entry: str, kv_caches_ptrs_tensor: torch.Tensor, staging: torch.Tensor
     if not (staging.is_cuda or staging.is_pinned()):
         raise ValueError("the staging tensor must live on the GPU or in pinned host memory")
     device = kv_caches_ptrs_tensor.device
+    if entry.endswith("_tokens") and rows_per_block > 0 and row_bytes > 0:
+        n_pools_ = kv_caches_ptrs_tensor.numel()
+        slot_bytes_ = n_pools_ * rows_per_block * row_bytes
+        merged = _coalesce_token_runs(row_indices, slot_indices, rows_per_block, pool_rows,
+                                      staging.numel() * staging.element_size() // slot_bytes_ if slot_bytes_ else 0)
+        if merged is not None:
+            row_indices, rows_per_block, g = merged
+            row_indices = torch.from_numpy(row_indices)
+            row_bytes *= g
+            pool_rows = None if pool_rows is None else pool_rows // g
+            entry = entry.replace("_tokens", "_pages")
     rows = _index_tensor(row_indices, device)
     if rows_per_block <= 0 or rows.numel() % rows_per_block != 0:
         raise ValueError("index count %d is not a multiple of %d" % (rows.numel(), rows_per_block))

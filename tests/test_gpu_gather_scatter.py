@@ -351,3 +351,50 @@ def test_bad_arguments_return_codes():
     assert L.kvcm_b200_gather_tokens(p, 1, p, 1, p, None, 1, 1, 0, 1, None, 0, None) == _cabi.KVCM_ER_INVALID_PARAMS
     assert L.kvcm_b200_gather_tokens(None, 1, p, 1, p, None, 1, 1, 16, 1, None, 0, None) == _cabi.KVCM_ER_INVALID_ADDRESS
     assert L.kvcm_b200_gather_tokens(p, 1, p, 1, p, None, 1, 2, 1 << 30, 1, None, 0, None) == _cabi.KVCM_ER_INVALID_PARAMS
+
+
+def test_token_lists_made_of_page_runs_take_the_page_path():
+    """Llama-3-70B / TP8 geometry, shrunk: 256-byte token rows in pages of 32.  Token lists built from a block table
+    are moved as 8 KiB page runs; lists that do not split into aligned runs, or that hold an out-of-range index,
+    keep the per-token path - bytes and status words are the same either way."""
+    from tair_kvcache_b200.kernel.batch_gather_scatter_helper import _coalesce_token_runs
+    n_pools, pool_pages, page_tokens, tok_bytes, pages_per_block, n_blocks = 5, 128, 32, 256, 4, 24
+    T = pages_per_block * page_tokens
+    host, dev, ptrs = _make(21, n_pools, pool_pages * page_tokens, tok_bytes)
+    rng = np.random.default_rng(21)
+    table = rng.permutation(pool_pages)[:n_blocks * pages_per_block].astype(np.int64)
+    slots = rng.permutation(n_blocks).astype(np.int32)
+    tok = (table[:, None] * page_tokens + np.arange(page_tokens)[None, :]).reshape(-1)
+    assert _coalesce_token_runs(tok.tolist(), slots.tolist(), T, pool_pages * page_tokens, n_blocks)[1:] == (4, 32)
+    broken = tok.copy()
+    broken[5], broken[6] = broken[6], broken[5]  # same tokens, one run out of order: runs of 4 at best... not even
+    assert _coalesce_token_runs(broken.tolist(), slots.tolist(), T, None, n_blocks) is None
+    outside = tok.copy()
+    outside[40] = pool_pages * page_tokens + 3
+    assert _coalesce_token_runs(outside.tolist(), slots.tolist(), T, pool_pages * page_tokens, n_blocks) is None
+    for name, idx, skipped in (("runs", tok, 0), ("broken", broken, 0), ("outside", outside, n_pools)):
+        for staging_on in ("device", "pinned_host"):
+            stage = torch.zeros(n_blocks * n_pools * T * tok_bytes, dtype=torch.uint8,
+                                device=DEV if staging_on == "device" else "cpu")
+            if staging_on != "device":
+                stage = stage.pin_memory()
+            status = torch.zeros(4, dtype=torch.int32, device=DEV)
+            batch_gather_kv_caches(ptrs, stage.view(torch.bfloat16).view(n_blocks, n_pools, T, tok_bytes // 2),
+                                   idx.tolist(), slots.tolist(), T, tok_bytes // 2,
+                                   total_token_in_kvcache=pool_pages * page_tokens, status=status)
+            torch.cuda.synchronize()
+            want = np.zeros(stage.numel(), dtype=np.uint8)
+            oracle.move_rows(_np(host), want, idx.astype(np.int32), slots, T, tok_bytes, 0, threads=4)
+            assert np.array_equal(stage.cpu().numpy(), want), (name, staging_on)
+            assert status[0].item() == skipped, (name, staging_on)
+            # and back: scatter into zeroed pools restores exactly the referenced tokens
+            zero = [torch.zeros_like(d) for d in dev]
+            zptrs = torch.tensor([z.data_ptr() for z in zero], dtype=torch.int64, device=DEV)
+            batch_scatter_kv_caches(zptrs, stage.view(torch.bfloat16).view(n_blocks, n_pools, T, tok_bytes // 2),
+                                    idx.tolist(), slots.tolist(), T, tok_bytes // 2,
+                                    total_token_in_kvcache=pool_pages * page_tokens)
+            torch.cuda.synchronize()
+            wantp = [np.zeros_like(h.numpy()) for h in host]
+            oracle.move_rows(wantp, want, idx.astype(np.int32), slots, T, tok_bytes, 1, threads=4)
+            for z, w in zip(zero, wantp):
+                assert np.array_equal(z.cpu().numpy(), w), (name, staging_on)
