@@ -310,6 +310,7 @@ def run_prefix_gpu(device, steps, warmup):
     return dict(workload="4096 requests x 512-8192 uint32 tokens, block 64, 50% prefix reuse, index of 200k prior "
                          "blocks; hash + prefix match",
                 token_blocks=n_keys, matched_blocks=matched, token_blocks_per_s=out["resident"],
+                block_size=bs, longest_request_tokens=int(np.max(off[1:] - off[:-1])),
                 e2e_token_blocks_per_s=out["e2e"], h2d_bytes_per_step=int(h_toks.numel() * 4 + h_off.numel() * 16),
                 d2h_bytes_per_step=int(h_len.numel() * 4), gpu_launches_per_step=2), (toks, off, ko, bs, ptoks, poff)
 
@@ -550,6 +551,15 @@ def main_prefix(args, rank, world):
             "e2e": {"value": pm["e2e_token_blocks_per_s"], "unit": "token-blocks/s",
                     "h2d_bytes_per_step": pm["h2d_bytes_per_step"], "d2h_bytes_per_step": pm["d2h_bytes_per_step"]},
             "gpu_launches": 2 * args.steps}
+    # Roofline of the step (hash + match kernels together): algorithmic bytes per token block = the block's tokens
+    # + the key written + one index slot read.  The binding limit is the dependent chain of the longest request
+    # (~40 cycles per token), stated beside the HBM fraction.
+    peak, peak_kind = peaks()
+    ms_step = 1e3 * pm["token_blocks"] / pm["token_blocks_per_s"]
+    achieved = pm["token_blocks"] * (4 * pm["block_size"] + 8 + 16) / (ms_step * 1e-3) / 1e9
+    line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                        "traffic": None, "peak_kind": peak_kind,
+                        "chain_latency_floor_ms": pm["longest_request_tokens"] * 40 / 1.965e6}
     if not args.no_cpu:
         cpu, n_rep = run_prefix_cpu(data, threads)
         line["cpu_baseline"] = {"value": cpu, "unit": "token-blocks/s", "cores": threads, "kind": "port",
