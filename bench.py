@@ -1167,13 +1167,227 @@ def main_lru_reference(args):
                               "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
 
 
+def main_iov(args, rank, world):
+    """TransferClient side (the per-iov copy loops of LocalFileSdk::DoGet / DoPut and Hf3fsUsrbioClient::CopyIovs):
+    blocks of layer_num x (K, V) iovs <-> contiguous block strings, at the Llama-3-8B shape (64 iovs of 128 KiB per
+    block, 2,048 blocks = 131,072 iovs, 16 GiB).  One step = Put (iovs -> strings) + Get (strings -> iovs), each one
+    kvcm_b200_copy_segments launch.  Beside it, on the same buffers: the reference's own structure, one
+    cudaMemcpyAsync per iov, on a bounded number of blocks."""
+    import ctypes
+
+    import torch
+    import torch.distributed as dist
+
+    import tair_kvcache_b200  # noqa: F401
+    from tair_kvcache_b200 import _cabi
+
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    _cabi.bind_device(local)
+    n_blocks = args.n_blocks or 2048
+    n_iovs, iov_bytes = 64, 64 * 2048  # 32 layers x (K, V); 64 tokens x 2 KiB
+    block_bytes = n_iovs * iov_bytes
+    gen = torch.Generator(device=device).manual_seed(0xB2000002 + rank)
+    # engine side: one buffer per (layer, K/V) holding that iov of every block, blocks at permuted positions
+    bufs = [torch.empty(n_blocks * iov_bytes // 4, dtype=torch.int32, device=device).random_(generator=gen)
+            for _ in range(n_iovs)]
+    strings = torch.zeros(n_blocks * block_bytes // 4, dtype=torch.int32, device=device)
+    perm = np.random.default_rng(0xB2000002 + rank).permutation(n_blocks)
+    base = np.array([b.data_ptr() for b in bufs], dtype=np.uint64)
+    iov_addr = base[None, :] + (perm.astype(np.uint64) * np.uint64(iov_bytes))[:, None]          # [block, iov]
+    str_addr = np.uint64(strings.data_ptr()) + (np.arange(n_blocks, dtype=np.uint64) * np.uint64(block_bytes))[:, None] \
+        + (np.arange(n_iovs, dtype=np.uint64) * np.uint64(iov_bytes))[None, :]
+
+    def seg_table(dst, src):
+        t = np.empty((n_blocks * n_iovs, 3), dtype=np.uint64)
+        t[:, 0], t[:, 1], t[:, 2] = dst.reshape(-1), src.reshape(-1), iov_bytes
+        return torch.from_numpy(t.view(np.uint8).reshape(-1)).to(device)
+
+    put_segs, get_segs = seg_table(str_addr, iov_addr), seg_table(iov_addr, str_addr)
+    n_segs = n_blocks * n_iovs
+    stream = torch.cuda.current_stream(device).cuda_stream
+
+    def put():
+        _cabi.call("kvcm_b200_copy_segments", put_segs.data_ptr(), n_segs, stream)
+
+    def get():
+        _cabi.call("kvcm_b200_copy_segments", get_segs.data_ptr(), n_segs, stream)
+
+    sampler = ClockSampler(str(torch.cuda.get_device_properties(device).uuid)) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    put()
+    torch.cuda.synchronize(device)
+    # parity: a sample of block strings against a torch gather of the iov buffers
+    ok = True
+    for b in np.random.default_rng(1).choice(n_blocks, size=min(16, n_blocks), replace=False):
+        want = torch.stack([buf.view(n_blocks, -1)[int(perm[b])] for buf in bufs]).reshape(-1)
+        ok = ok and bool(torch.equal(strings.view(n_blocks, -1)[int(b)], want))
+    for _ in range(args.warmup):
+        put()
+        get()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    if sampler:
+        sampler.mark_begin()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    for k in range(args.steps):
+        ev[k][0].record()
+        put()
+        ev[k][1].record()
+        get()
+        ev[k][2].record()
+    torch.cuda.synchronize(device)
+    if sampler:
+        sampler.mark_end()
+    clocks = sampler.stop() if sampler else None
+    put_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    get_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    total_ms = ev[0][0].elapsed_time(ev[-1][2])
+    if world > 1:
+        t = torch.tensor([total_ms, put_ms, get_ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, put_ms, get_ms = t.tolist()
+    payload = n_blocks * block_bytes
+    value = world * 4 * payload * args.steps / (total_ms * 1e-3) / 1e9
+
+    # the reference's structure on the same buffers: one cudaMemcpyAsync per iov, then one stream sync
+    # (a compiled loop under oracle/, so that no interpreter overhead is charged to it)
+    loop_gbs = loop_calls = loop_us = None
+    loop_lib = os.path.join(ROOT, "oracle", "libkvcm_ref_memcpy_loop.so")
+    if rank == 0 and os.path.exists(loop_lib):
+        rt = ctypes.CDLL(loop_lib)
+        rt.kvcm_ref_memcpy_loop.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                            ctypes.c_void_p]
+        m = min(n_blocks, 512)
+        dsts = np.ascontiguousarray(str_addr[:m].reshape(-1))
+        srcs = np.ascontiguousarray(iov_addr[:m].reshape(-1))
+        sizes = np.full(len(dsts), iov_bytes, dtype=np.uint64)
+        torch.cuda.synchronize(device)
+        best = None
+        for _ in range(3):
+            t0 = time.perf_counter()
+            rc = rt.kvcm_ref_memcpy_loop(dsts.ctypes.data, srcs.ctypes.data, sizes.ctypes.data, len(dsts), stream)
+            dt = time.perf_counter() - t0
+            best = dt if best is None or dt < best else best
+        loop_calls = len(dsts)
+        if rc == 0:
+            loop_gbs, loop_us = 2 * m * block_bytes / best / 1e9, best / loop_calls * 1e6
+
+    # end to end: block strings in pinned host memory (LocalFileSdk registers its mmap'ed file with the driver).
+    # As the IovCopier adapter does: the strings cross PCIe as one copy-engine transfer into / out of a device
+    # bounce buffer and the kernel runs device to device; Put on one stream, Get on another.
+    e2e = None
+    if not args.no_e2e:
+        m = min(n_blocks, 128)
+        words = m * block_bytes // 4
+        h_str = torch.empty(words, dtype=torch.int32, pin_memory=True)
+        h_back = strings[:words].cpu().pin_memory()
+        d_put_b, d_get_b = torch.empty(words, dtype=torch.int32, device=device), torch.empty(
+            words, dtype=torch.int32, device=device)
+        rel = str_addr[:m] - np.uint64(strings.data_ptr())
+
+        def small(dst, src):
+            t = np.empty((m * n_iovs, 3), dtype=np.uint64)
+            t[:, 0], t[:, 1], t[:, 2] = dst.reshape(-1), src.reshape(-1), iov_bytes
+            return torch.from_numpy(t.view(np.uint8).reshape(-1)).pin_memory()
+
+        h_put = small(np.uint64(d_put_b.data_ptr()) + rel, iov_addr[:m])
+        h_get = small(iov_addr[:m], np.uint64(d_get_b.data_ptr()) + rel)
+        d_put, d_get = torch.empty_like(h_put, device=device), torch.empty_like(h_get, device=device)
+        s1, s2 = torch.cuda.Stream(device), torch.cuda.Stream(device)
+
+        def e2e_step():
+            with torch.cuda.stream(s1):
+                d_put.copy_(h_put, non_blocking=True)  # the segment table crosses PCIe with every request
+                _cabi.call("kvcm_b200_copy_segments", d_put.data_ptr(), m * n_iovs, s1.cuda_stream)
+                h_str.copy_(d_put_b, non_blocking=True)
+            with torch.cuda.stream(s2):
+                d_get.copy_(h_get, non_blocking=True)
+                d_get_b.copy_(h_back, non_blocking=True)
+                _cabi.call("kvcm_b200_copy_segments", d_get.data_ptr(), m * n_iovs, s2.cuda_stream)
+
+        e2e_step()
+        torch.cuda.synchronize(device)
+        reps = max(1, min(args.steps, 3))
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            e2e_step()
+        torch.cuda.synchronize(device)
+        dt = time.perf_counter() - t0
+        e2e = {"value": world * 4 * m * block_bytes * reps / dt / 1e9, "unit": UNIT,
+               "h2d_bytes_per_step": m * block_bytes + 2 * m * n_iovs * 24, "d2h_bytes_per_step": m * block_bytes,
+               "parity_ok": bool(torch.equal(h_str, h_back))}
+    if rank != 0:
+        return
+    peak, peak_kind = peaks()
+    kern = 2 * payload / (min(put_ms, get_ms) * 1e-3) / 1e9
+    line = {"metric": "iov_copy_algorithmic_GBps", "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+            "config": {"workload": "%d blocks x %d iovs x %d KiB (Llama-3-8B block layout), Put + Get per step, block "
+                                   "strings and iov buffers in HBM, inputs larger than L2" % (n_blocks, n_iovs,
+                                                                                             iov_bytes // 1024),
+                       "put_ms": put_ms, "get_ms": get_ms, "parity_sample_ok": ok,
+                       "memcpy_async_per_iov_GBps": loop_gbs, "memcpy_async_calls": loop_calls,
+                       "memcpy_async_us_per_call": loop_us},
+            "roofline": {"bound": "hbm", "achieved": kern, "peak": peak, "unit": UNIT, "frac": kern / peak,
+                         "traffic": None, "peak_kind": peak_kind},
+            "clocks": clocks, "gpu_launches": 2 * args.steps}
+    if e2e:
+        line["e2e"] = e2e
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main_iov_reference(args):
+    """CPU arm of --workload iov: the same per-iov loop with memcpy between host buffers (oracle.copy_iovs), on a
+    bounded number of blocks, all host threads (one block per task)."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    from oracle import kvcm_oracle as oracle
+    threads = os.cpu_count() or 1
+    n_iovs, iov_bytes, m = 64, 64 * 2048, 64
+    rng = np.random.default_rng(0xB2000002)
+    bufs = [[rng.integers(0, 256, size=iov_bytes, dtype=np.uint8) for _ in range(n_iovs)] for _ in range(m)]
+    strings = [np.zeros(n_iovs * iov_bytes, dtype=np.uint8) for _ in range(m)]
+
+    def one(b):
+        oracle.copy_iovs([(v, iov_bytes, False) for v in bufs[b]], strings[b], 0)
+        oracle.copy_iovs([(v, iov_bytes, False) for v in bufs[b]], strings[b], 1)
+
+    with ThreadPoolExecutor(max_workers=threads) as pool:
+        list(pool.map(one, range(m)))
+        t_total, n = 0.0, 0
+        while t_total < 5.0 and n < 50:
+            t0 = time.perf_counter()
+            list(pool.map(one, range(m)))
+            t_total += time.perf_counter() - t0
+            n += 1
+    value = 4 * m * n_iovs * iov_bytes * n / t_total / 1e9
+    print(json.dumps({"impl": "reference", "metric": "iov_copy_algorithmic_GBps", "value": value, "unit": UNIT,
+                      "n_gpus": args.gpus, "steps": n, "warmup": 1, "higher_is_better": True, "dtype": "u8",
+                      "data": "synthetic",
+                      "config": {"workload": "CPU restatement of the per-iov loop (memcpy between host buffers)"},
+                      "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                                       "sample": "%d blocks x %d iovs x %d KiB, Put + Get, %d repetitions" % (
+                                           m, n_iovs, iov_bytes // 1024, n)},
+                      "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                      "gpu_launches": 0}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c1", "c4", "c5", "lru"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c1", "c4", "c5", "lru", "iov"])
     ap.add_argument("--n-requests", type=int, default=0, help="c4: override the number of requests")
     ap.add_argument("--index-keys", type=int, default=0, help="c4: override the number of indexed keys")
     ap.add_argument("--shard-mode", default="peer", choices=["peer", "exchange"],
@@ -1197,6 +1411,13 @@ def main():
                 main_replay_reference(args)
             return
         main_replay(args, rank, world)
+        return
+    if args.workload == "iov":
+        if args.impl == "reference":
+            if rank == 0:
+                main_iov_reference(args)
+            return
+        main_iov(args, rank, world)
         return
     if args.workload == "lru":
         if args.impl == "reference":

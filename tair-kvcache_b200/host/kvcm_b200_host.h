@@ -490,47 +490,94 @@ struct BlockBuffer {
 // One launch for all iovs of a request instead of one cudaMemcpyAsync per Iov.
 class IovCopier {
 public:
-    explicit IovCopier(cudaStream_t stream = nullptr) : stream_(stream) {
+    // through_bounce: a block string in host memory is staged through a device buffer of the same size and crosses
+    // PCIe as one copy-engine transfer (a Put and a Get on two streams then use both PCIe directions at full rate);
+    // false: the kernel reads / writes the host string itself (no extra device memory).
+    explicit IovCopier(cudaStream_t stream = nullptr, bool through_bounce = true)
+        : stream_(stream), through_bounce_(through_bounce) {
         cudaEventCreateWithFlags(&staged_, cudaEventDisableTiming);
     }
     IovCopier(const IovCopier &) = delete;
     IovCopier &operator=(const IovCopier &) = delete;
     ~IovCopier() { cudaEventDestroy(staged_); }
 
-    // direction 0: iovs -> block_string (Put), 1: block_string -> iovs (Get).  block_string must be
-    // reachable from the device (device memory, or host memory registered with cudaHostRegister as the
-    // reference's LocalFileSdk does for its mmap).  Asynchronous on the adapter's stream; the caller
-    // keeps the reference's single cudaStreamSynchronize.  *span_bytes = bytes the iov list covers.
+    // direction 0: iovs -> block_string (Put), 1: block_string -> iovs (Get).  block_string is device memory, or
+    // host memory that is pinned or registered with cudaHostRegister (as the reference's LocalFileSdk does for its
+    // mmap); pageable host memory is refused.  Asynchronous on the adapter's stream; the caller keeps the
+    // reference's single cudaStreamSynchronize.  *span_bytes = bytes the iov list covers.  Bytes of block_string
+    // under ignored, null or empty iovs are never written.
     int32_t CopyIovs(const BlockBuffer &buffer, void *block_string, int direction, uint64_t *span_bytes) {
         const int32_t n = static_cast<int32_t>(buffer.iovs.size());
-        if (n == 0) {
-            if (span_bytes) *span_bytes = 0;
-            return KVCM_OK;
-        }
+        if (span_bytes) *span_bytes = 0;
+        if (n == 0) return KVCM_OK;
+        if (direction != 0 && direction != 1) return KVCM_ER_INVALID_PARAMS;
         std::vector<kvcm_b200_iov_t> iovs(n);
+        uint64_t span = 0;
         for (int32_t i = 0; i < n; ++i) {
             iovs[i].type = static_cast<uint8_t>(buffer.iovs[i].type);
             iovs[i].ignore = buffer.iovs[i].ignore ? 1 : 0;
             iovs[i].base = buffer.iovs[i].base;
             iovs[i].size = buffer.iovs[i].size;
+            span += buffer.iovs[i].size;
         }
-        // The pinned segment table is reused: wait until the previous call's copy of it has left.
+        bool host_string = false;
+        if (block_string != nullptr) {
+            cudaPointerAttributes attr{};
+            if (cudaPointerGetAttributes(&attr, block_string) != cudaSuccess) {
+                cudaGetLastError();
+                return KVCM_ER_INVALID_ADDRESS;
+            }
+            if (attr.type == cudaMemoryTypeUnregistered) return KVCM_ER_UNSUPPORTED_MEMORY_TYPE;
+            host_string = attr.type == cudaMemoryTypeHost;
+        }
+        // The pinned segment table and the bounce buffer are reused: wait until the previous call is through.
         if (cudaEventSynchronize(staged_) != cudaSuccess) return KVCM_ER_CUDA_STREAM_SYNCHRONIZE_ERROR;
         if (!segs_.Reserve(sizeof(kvcm_b200_seg_t) * n)) return KVCM_EC_NOSPC;
+        void *target = block_string;
+        const bool bounce = host_string && through_bounce_ && span > 0;
+        if (bounce) {
+            if (!bounce_.Reserve(span, true)) return KVCM_EC_NOSPC;
+            target = bounce_.dev<void>();
+            if (direction == 1 &&
+                cudaMemcpyAsync(target, block_string, span, cudaMemcpyHostToDevice, stream_) != cudaSuccess) {
+                return KVCM_ER_CUDAMEMCPY_ERROR;
+            }
+        }
         int32_t n_segs = 0;
-        int32_t rc = kvcm_b200_iovs_to_segments(iovs.data(), n, block_string, direction,
-                                                segs_.host<kvcm_b200_seg_t>(), &n_segs, span_bytes);
+        int32_t rc = kvcm_b200_iovs_to_segments(iovs.data(), n, target, direction, segs_.host<kvcm_b200_seg_t>(),
+                                                &n_segs, span_bytes);
         if (rc != KVCM_OK) return rc;
         if (!segs_.ToDevice(sizeof(kvcm_b200_seg_t) * n_segs, stream_)) return KVCM_ER_CUDAMEMCPY_ERROR;
         rc = kvcm_b200_copy_segments(segs_.dev<kvcm_b200_seg_t>(), n_segs, stream_);
+        if (rc == KVCM_OK && bounce && direction == 0) {
+            // Back to the host string: one copy per run of bytes that iovs actually filled.
+            uint64_t run_begin = 0, at = 0;
+            auto flush = [&](uint64_t end) {
+                if (end > run_begin && cudaMemcpyAsync(static_cast<uint8_t *>(block_string) + run_begin,
+                                                       static_cast<uint8_t *>(target) + run_begin, end - run_begin,
+                                                       cudaMemcpyDeviceToHost, stream_) != cudaSuccess) {
+                    rc = KVCM_ER_CUDAMEMCPY_ERROR;
+                }
+            };
+            for (int32_t i = 0; i < n; ++i) {
+                const bool filled = !iovs[i].ignore && iovs[i].base != nullptr && iovs[i].size > 0;
+                if (!filled) {
+                    flush(at);
+                    run_begin = at + iovs[i].size;
+                }
+                at += iovs[i].size;
+            }
+            flush(at);
+        }
         cudaEventRecord(staged_, stream_);  // also covers the kernel: the device table may be rewritten after it
         return rc;
     }
 
 private:
     cudaStream_t stream_;
+    bool through_bounce_;
     cudaEvent_t staged_ = nullptr;
-    detail::Mirror segs_;
+    detail::Mirror segs_, bounce_;
 };
 
 }  // namespace kvcm_b200

@@ -152,6 +152,36 @@ static void TestIovCopier() {
         for (size_t j = 0; j < sz; ++j) zero = zero && back[i * sz + j] == 0;
         EXPECT_EQ(i == 2 ? zero : same, true);
     }
+    // The same block with its string in pinned host memory (what LocalFileSdk's registered mmap is), staged through
+    // the bounce buffer and read / written by the kernel directly: the bytes under the ignored iov stay as they were.
+    uint8_t *h_string = nullptr;
+    cudaMallocHost(&h_string, host.size());
+    for (int mode = 0; mode < 2; ++mode) {
+        IovCopier host_copier(nullptr, mode == 0);
+        std::memset(h_string, 0xEE, host.size());
+        cudaMemset(d_back, 0, host.size());
+        EXPECT_EQ(host_copier.CopyIovs(put, h_string, 0, &span), KVCM_OK);
+        cudaDeviceSynchronize();
+        for (int i = 0; i < 6; ++i) {
+            bool same = std::memcmp(h_string + i * sz, host.data() + i * sz, sz) == 0;
+            bool kept = true;
+            for (size_t j = 0; j < sz; ++j) kept = kept && h_string[i * sz + j] == 0xEE;
+            EXPECT_EQ(i == 2 ? kept : same, true);
+        }
+        EXPECT_EQ(host_copier.CopyIovs(get, h_string, 1, &span), KVCM_OK);
+        cudaDeviceSynchronize();
+        cudaMemcpy(back.data(), d_back, back.size(), cudaMemcpyDeviceToHost);
+        for (int i = 0; i < 6; ++i) {
+            bool same = std::memcmp(back.data() + i * sz, host.data() + i * sz, sz) == 0;
+            bool zero = true;
+            for (size_t j = 0; j < sz; ++j) zero = zero && back[i * sz + j] == 0;
+            EXPECT_EQ(i == 2 ? zero : same, true);
+        }
+    }
+    // pageable host memory is refused, not dereferenced
+    std::vector<uint8_t> pageable(host.size());
+    EXPECT_EQ(copier.CopyIovs(put, pageable.data(), 0, &span), KVCM_ER_UNSUPPORTED_MEMORY_TYPE);
+    cudaFreeHost(h_string);
     cudaFree(d_src);
     cudaFree(d_string);
     cudaFree(d_back);
