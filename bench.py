@@ -715,6 +715,29 @@ def main_window(args, rank, world):
     torch.cuda.synchronize(device)
     phase_ms = {"hash": ev[0].elapsed_time(ev[1]), "prefix_match": ev[1].elapsed_time(ev[2]),
                 "window_match": ev[2].elapsed_time(ev[3])}
+    if world == 1:
+        # the other index operators on the same keys, outside the timed step: BatchGet (one flag byte per key),
+        # FilterWriteCache (what StartWriteCache asks before a write) and the write side (upsert of fresh keys into
+        # a second index of the same size, then their erase)
+        from tair_kvcache_b200.manager import BlockIndex
+        ev2 = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+        fresh = BlockIndex(max(int(stored), 1024), device)
+        some = keys[:min(n_keys, int(stored))]
+        ev2[0].record()
+        local_index.BatchGet(keys)
+        ev2[1].record()
+        local_index.FilterWriteCache(keys, d_ko)
+        ev2[2].record()
+        fresh.upsert(some, None, word)
+        ev2[3].record()
+        fresh.erase(some)
+        ev2[4].record()
+        torch.cuda.synchronize(device)
+        phase_ms.update({"batch_get_all_keys": ev2[0].elapsed_time(ev2[1]),
+                         "filter_write_all_requests": ev2[1].elapsed_time(ev2[2]),
+                         "upsert_%d_keys" % some.numel(): ev2[2].elapsed_time(ev2[3]),
+                         "erase_%d_keys" % some.numel(): ev2[3].elapsed_time(ev2[4])})
+        del fresh
     stats = torch.tensor([ms, float(n_keys), float(stored), float((prefix > 0).sum()), float((window >= 0).sum())],
                          dtype=torch.float64, device=device)
     if world > 1:
