@@ -1234,10 +1234,10 @@ def main_iov(args, rank, world):
     stream = torch.cuda.current_stream(device).cuda_stream
 
     def put():
-        _cabi.call("kvcm_b200_copy_segments", put_segs.data_ptr(), n_segs, stream)
+        _cabi.call("kvcm_b200_copy_segments_sized", put_segs.data_ptr(), n_segs, n_segs * iov_bytes, stream)
 
     def get():
-        _cabi.call("kvcm_b200_copy_segments", get_segs.data_ptr(), n_segs, stream)
+        _cabi.call("kvcm_b200_copy_segments_sized", get_segs.data_ptr(), n_segs, n_segs * iov_bytes, stream)
 
     sampler = ClockSampler(str(torch.cuda.get_device_properties(device).uuid)) if rank == 0 else None
     if sampler:
@@ -1327,12 +1327,12 @@ def main_iov(args, rank, world):
         def e2e_step():
             with torch.cuda.stream(s1):
                 d_put.copy_(h_put, non_blocking=True)  # the segment table crosses PCIe with every request
-                _cabi.call("kvcm_b200_copy_segments", d_put.data_ptr(), m * n_iovs, s1.cuda_stream)
+                _cabi.call("kvcm_b200_copy_segments_sized", d_put.data_ptr(), m * n_iovs, m * block_bytes, s1.cuda_stream)
                 h_str.copy_(d_put_b, non_blocking=True)
             with torch.cuda.stream(s2):
                 d_get.copy_(h_get, non_blocking=True)
                 d_get_b.copy_(h_back, non_blocking=True)
-                _cabi.call("kvcm_b200_copy_segments", d_get.data_ptr(), m * n_iovs, s2.cuda_stream)
+                _cabi.call("kvcm_b200_copy_segments_sized", d_get.data_ptr(), m * n_iovs, m * block_bytes, s2.cuda_stream)
 
         e2e_step()
         torch.cuda.synchronize(device)

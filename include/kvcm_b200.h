@@ -192,6 +192,15 @@ typedef struct kvcm_b200_iov {
 } kvcm_b200_iov_t;
 
 KVCM_API int32_t kvcm_b200_copy_segments(const kvcm_b200_seg_t *d_segs, int32_t n_segs, kvcm_stream_t stream);
+/* The same copy for callers that know how many bytes the segments hold in total (the span that
+ * kvcm_b200_iovs_to_segments returns, minus ignored iovs): with a mean segment of 8 KiB or more the copy runs on
+ * the bulk-copy (TMA) ring at the HBM roofline; segments whose ends are not 16-byte aligned are then moved by
+ * one warp with byte accesses, so callers with large unaligned segments pass total_bytes = 0 (= the call above).
+ * The waits of the ring are bounded; kvcm_b200_copy_wait_timeouts reads the per-device count of CTAs that gave
+ * up (0 in any healthy run; synchronises with the device). */
+KVCM_API int32_t kvcm_b200_copy_segments_sized(const kvcm_b200_seg_t *d_segs, int32_t n_segs, uint64_t total_bytes,
+                                               kvcm_stream_t stream);
+KVCM_API int32_t kvcm_b200_copy_wait_timeouts(uint32_t *h_count_out);
 /* Host-only: direction 0 = iovs -> block string (Put), 1 = block string -> iovs (Get).  Writes at
  * most n_iovs segments to h_segs_out, returns their number in *n_segs_out and the bytes the iov
  * list spans in *span_bytes_out. */

@@ -71,6 +71,8 @@ SIGNATURES = {
     "kvcm_b200_gather_legacy": _LEGACY,
     "kvcm_b200_scatter_legacy": _LEGACY,
     "kvcm_b200_copy_segments": [_vp, _i32, _vp],
+    "kvcm_b200_copy_segments_sized": [_vp, _i32, _u64, _vp],
+    "kvcm_b200_copy_wait_timeouts": [_vp],
     "kvcm_b200_iovs_to_segments": [_vp, _i32, _vp, _i32, _vp, _vp, _vp],
     "kvcm_b200_iov_crc": [_vp, _i32, _u64, _vp, _vp],
     "kvcm_b200_hash_blocks_u32": _HASH,

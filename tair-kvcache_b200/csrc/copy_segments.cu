@@ -5,6 +5,10 @@
 // Hf3fsUsrbioClient::CopyIovs (kv_cache_manager/client/src/internal/sdk/hf3fs_usrbio_client.cc:478-505):
 // one launch moves every segment of a request instead of one runtime call per Iov.
 // iov_crc stands in for GetIovsCrcDevice (kv_cache_manager/client/src/internal/sdk/sdk_buffer_check_util.cu:21-44).
+#include <algorithm>
+#include <mutex>
+#include <vector>
+
 #include "kvcm_common.cuh"
 
 namespace kvcm {
@@ -13,6 +17,110 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kUnroll = 8;
 constexpr uint64_t kChunk = static_cast<uint64_t>(kThreads) * 16 * kUnroll;  // 32 KiB
+
+// ------------------------------------------------------------------------------------------
+// Bulk-copy (TMA) form, used when segments are large: persistent one-warp CTAs, a ring of shared-
+// memory stages, one cp.async.bulk load and one cp.async.bulk store per chunk, no thread touching
+// the payload (the same machinery as the gather / scatter ring).  CTA b walks segments
+// b / parts, b / parts + lanes, ... and of each segment the chunks b % parts, b % parts + parts, ...
+// A chunk whose ends are not 16-byte aligned is moved by the warp with plain accesses, as is the
+// tail of fewer than 16 bytes.  Every wait is bounded; a CTA that gives up counts itself in
+// g_copy_wait_timeouts and returns.
+// ------------------------------------------------------------------------------------------
+constexpr int kBulkStages = 2;
+constexpr uint32_t kBulkChunk = 32 * 1024;  // 48 KiB for segments of 96 KiB and more, see the launcher
+constexpr uint64_t kBulkMinSegment = 8 * 1024;  // below this mean size the vector kernel is used
+
+__device__ uint32_t g_copy_wait_timeouts = 0;
+
+struct ChunkItem {
+    const uint8_t *src;
+    uint8_t *dst;
+    uint32_t len;
+    uint32_t bulk_len;  // leading bytes moved by bulk copies (0: the warp moves the whole chunk)
+};
+
+__global__ void __launch_bounds__(32)
+    CopySegmentsBulkKernel(const kvcm_b200_seg_t *__restrict__ segs, int32_t n, uint32_t parts, uint32_t seg_lanes,
+                           uint32_t chunk_bytes) {
+    extern __shared__ __align__(128) uint8_t ring[];
+    __shared__ __align__(8) uint64_t bars[kBulkStages];
+    const uint32_t lane = threadIdx.x;
+    if (lane == 0) {
+        for (int s = 0; s < kBulkStages; ++s) MbarInit(SmemAddr(&bars[s]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async;\n" ::: "memory");
+    }
+    __syncwarp();
+    const uint32_t my_part = blockIdx.x % parts;
+    int64_t seg = blockIdx.x / parts;
+    if (seg >= seg_lanes) return;
+    uint64_t chunk = my_part;
+    // Next chunk of this CTA's walk (warp-uniform); false when the walk is over.
+    auto next = [&](ChunkItem *it) -> bool {
+        while (seg < n) {
+            const uint8_t *src = static_cast<const uint8_t *>(segs[seg].src);
+            uint8_t *dst = static_cast<uint8_t *>(segs[seg].dst);
+            const uint64_t bytes = (src == nullptr || dst == nullptr) ? 0 : segs[seg].bytes;
+            const uint64_t off = chunk * chunk_bytes;
+            if (off < bytes) {
+                it->src = src + off;
+                it->dst = dst + off;
+                it->len = bytes - off < chunk_bytes ? static_cast<uint32_t>(bytes - off) : chunk_bytes;
+                const bool aligned = ((reinterpret_cast<uintptr_t>(it->src) | reinterpret_cast<uintptr_t>(it->dst)) & 15u) == 0;
+                it->bulk_len = aligned ? (it->len & ~15u) : 0u;
+                chunk += parts;
+                return true;
+            }
+            seg += seg_lanes;
+            chunk = my_part;
+        }
+        return false;
+    };
+    const uint32_t ring_base = SmemAddr(ring);
+    ChunkItem items[kBulkStages];
+    bool live[kBulkStages];
+    auto load = [&](int s) {
+        live[s] = next(&items[s]);
+        if (!live[s]) return;
+        const ChunkItem &it = items[s];
+        if (lane == 0) {
+            MbarArriveExpectTx(SmemAddr(&bars[s]), it.bulk_len);
+            if (it.bulk_len > 0) BulkLoad(ring_base + s * chunk_bytes, it.src, it.bulk_len, SmemAddr(&bars[s]));
+        }
+        for (uint32_t i = it.bulk_len + lane; i < it.len; i += 32) it.dst[i] = it.src[i];  // what bulk copies cannot take
+    };
+#pragma unroll
+    for (int s = 0; s < kBulkStages - 1; ++s) load(s);
+    live[kBulkStages - 1] = false;
+    bool failed = false;
+    uint32_t k = 0;
+    while (true) {
+        const int s = k % kBulkStages;
+        if (!live[s]) break;
+        if (lane == 0) {
+            uint32_t spins = 0;
+            while (!MbarTryWait(SmemAddr(&bars[s]), (k / kBulkStages) & 1u)) {
+                if (++spins >= kSpinLimit) {
+                    failed = true;
+                    break;
+                }
+            }
+        }
+        failed = __shfl_sync(0xffffffffu, failed ? 1 : 0, 0) != 0;
+        if (failed) break;
+        if (lane == 0 && items[s].bulk_len > 0) BulkStore(items[s].dst, ring_base + s * chunk_bytes, items[s].bulk_len);
+        BulkCommit();
+        // The stage refilled next was drained by the store of chunk k-1: let every group but the newest finish
+        // reading shared memory first.
+        BulkWaitRead<1>();
+        __syncwarp();
+        load((k + kBulkStages - 1) % kBulkStages);
+        ++k;
+    }
+    BulkWaitAll();
+    if (failed && lane == 0) atomicAdd(&g_copy_wait_timeouts, 1u);
+}
 
 // grid.x strides over segments, grid.y CTAs share the chunks of one segment.
 __global__ void __launch_bounds__(kThreads) CopySegmentsKernel(const kvcm_b200_seg_t *__restrict__ segs, int32_t n) {
@@ -71,10 +179,54 @@ __global__ void IovCrcKernel(const kvcm_b200_seg_t *__restrict__ segs, int32_t n
 extern "C" {
 
 int32_t kvcm_b200_copy_segments(const kvcm_b200_seg_t *d_segs, int32_t n_segs, kvcm_stream_t stream) {
+    return kvcm_b200_copy_segments_sized(d_segs, n_segs, 0, stream);
+}
+
+int32_t kvcm_b200_copy_wait_timeouts(uint32_t *h_count_out) {
+    if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
+    if (h_count_out == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    const cudaError_t e = cudaMemcpyFromSymbol(h_count_out, kvcm::g_copy_wait_timeouts, sizeof(uint32_t));
+    return e == cudaSuccess ? KVCM_OK : KVCM_ER_CUDAMEMCPY_ERROR;
+}
+
+int32_t kvcm_b200_copy_segments_sized(const kvcm_b200_seg_t *d_segs, int32_t n_segs, uint64_t total_bytes,
+                                      kvcm_stream_t stream) {
     if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
     if (n_segs < 0) return KVCM_ER_INVALID_PARAMS;
     if (n_segs == 0) return KVCM_OK;
     if (d_segs == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (total_bytes / static_cast<uint64_t>(n_segs) >= kvcm::kBulkMinSegment) {
+        // Large segments: the bulk-copy ring.  64 KiB of shared memory per one-warp CTA, three CTAs per SM.
+        static std::mutex mu;
+        static std::vector<int> opted;
+        int device = 0;
+        cudaGetDevice(&device);
+        // Geometry from a sweep on B200 (131,072 segments of 128 KiB): 48 KiB chunks x 2 CTAs per SM reach 0.99 of
+        // the measured copy peak, 32 KiB x 3 reach 0.97, 64 KiB x 1 0.93; 192 KiB are in flight per SM either way.
+        // Short segments would leave most of a 48 KiB stage empty.
+        const bool wide = total_bytes / static_cast<uint64_t>(n_segs) >= 96 * 1024;
+        const uint32_t chunk_bytes = wide ? 48 * 1024 : kvcm::kBulkChunk;
+        const int ctas_per_sm = wide ? 2 : 3;
+        const int smem = kvcm::kBulkStages * static_cast<int>(chunk_bytes);
+        {
+            std::lock_guard<std::mutex> lock(mu);
+            if (std::find(opted.begin(), opted.end(), device) == opted.end()) {
+                cudaFuncSetAttribute(kvcm::CopySegmentsBulkKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     kvcm::kBulkStages * 48 * 1024);
+                opted.push_back(device);
+            }
+        }
+        const uint32_t grid = static_cast<uint32_t>(kvcm::GetDeviceInfo().sm_count) * ctas_per_sm;
+        uint32_t parts = 1, seg_lanes = grid;
+        if (static_cast<uint32_t>(n_segs) < grid) {
+            parts = grid / static_cast<uint32_t>(n_segs);
+            parts = parts > 64 ? 64 : parts;
+            seg_lanes = static_cast<uint32_t>(n_segs);
+        }
+        kvcm::CopySegmentsBulkKernel<<<seg_lanes * parts, 32, smem, kvcm::AsStream(stream)>>>(d_segs, n_segs, parts,
+                                                                                            seg_lanes, chunk_bytes);
+        return kvcm::LaunchStatus();
+    }
     const int resident = kvcm::GetDeviceInfo().sm_count * 8;
     int parts = resident / n_segs;
     parts = parts < 1 ? 1 : (parts > 64 ? 64 : parts);

@@ -174,17 +174,6 @@ __global__ void __launch_bounds__(kThreads) MoveRowsKernel(const MoveParams p) {
 constexpr int kBulkMaxStages = 8;
 constexpr uint32_t kBulkMinRowBytes = 512;
 
-__device__ __forceinline__ void BulkStore(void *dst, uint32_t src_smem, uint32_t bytes) {
-    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(dst), "r"(src_smem), "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ void BulkCommit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
-template <int kPending>
-__device__ __forceinline__ void BulkWaitRead() {
-    asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(kPending) : "memory");
-}
-__device__ __forceinline__ void BulkWaitAll() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
-
 struct ChunkDesc {
     uint8_t *pool_base;
     uint8_t *stage;  // start of this chunk in staging

@@ -548,7 +548,15 @@ public:
                                                 &n_segs, span_bytes);
         if (rc != KVCM_OK) return rc;
         if (!segs_.ToDevice(sizeof(kvcm_b200_seg_t) * n_segs, stream_)) return KVCM_ER_CUDAMEMCPY_ERROR;
-        rc = kvcm_b200_copy_segments(segs_.dev<kvcm_b200_seg_t>(), n_segs, stream_);
+        // Device buffers of an engine are 16-byte aligned; an iov list that is not takes the vector kernel.
+        uint64_t moved = 0;
+        bool aligned = true;
+        for (int32_t i = 0; i < n_segs; ++i) {
+            const kvcm_b200_seg_t &g = segs_.host<kvcm_b200_seg_t>()[i];
+            moved += g.bytes;
+            aligned = aligned && ((reinterpret_cast<uintptr_t>(g.dst) | reinterpret_cast<uintptr_t>(g.src)) & 15u) == 0;
+        }
+        rc = kvcm_b200_copy_segments_sized(segs_.dev<kvcm_b200_seg_t>(), n_segs, aligned ? moved : 0, stream_);
         if (rc == KVCM_OK && bounce && direction == 0) {
             // Back to the host string: one copy per run of bytes that iovs actually filled.
             uint64_t run_begin = 0, at = 0;

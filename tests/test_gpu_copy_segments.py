@@ -50,6 +50,13 @@ def test_block_of_layer_iovs_put_and_get_match_the_reference_loop():
     assert span == total and n_segs == sum(1 for s, g in zip(sizes, ignore) if s > 0 and not g)
     _cabi.call("kvcm_b200_copy_segments", segs.data_ptr(), n_segs, torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
+    # the same list with its size stated takes the bulk-copy ring (mean segment 129 KiB): identical bytes
+    ring_string = torch.zeros_like(string)
+    ring_segs, _, _ = _segments_from_iovs(iovs, ring_string.data_ptr(), 0)
+    _cabi.call("kvcm_b200_copy_segments_sized", ring_segs.data_ptr(), n_segs, total,
+               torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert torch.equal(ring_string, string)
     want = np.zeros(total, dtype=np.uint8)
     oracle.copy_iovs([(hv if s > 0 else None, s, g) for hv, s, g in zip(hviews, sizes, ignore)], want, 0)
     assert np.array_equal(string.cpu().numpy(), want)
@@ -120,3 +127,31 @@ def test_iov_crc_random_against_oracle():
     got = out.cpu().numpy().view(np.uint32)
     want = np.array([oracle.iov_crc(h, 4) for h in host], dtype=np.uint32)
     assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("n_segs,seg_bytes", [(3, 5 << 20), (700, 96 * 1024 + 48), (40, 8192), (1, 1 << 20)])
+def test_bulk_ring_path_of_sized_copies(n_segs, seg_bytes):
+    """Few large segments (chunks of one segment shared by several CTAs), more segments than CTAs, sizes that are
+    not multiples of the 32 KiB chunk or of 16 bytes, and one segment whose ends are not 16-byte aligned."""
+    _cabi.bind_device(0)
+    gen = torch.Generator(device=DEV).manual_seed(n_segs)
+    pad = 64
+    src = torch.randint(0, 256, (n_segs * (seg_bytes + pad),), dtype=torch.uint8, device=DEV, generator=gen)
+    dst = torch.zeros_like(src)
+    sizes = [seg_bytes - (7 if i % 3 == 1 else 0) for i in range(n_segs)]
+    shift = [5 if i == n_segs - 1 and n_segs > 1 else 0 for i in range(n_segs)]  # one unaligned segment
+    segs = (_cabi.Seg * n_segs)()
+    for i in range(n_segs):
+        segs[i].dst = dst.data_ptr() + i * (seg_bytes + pad) + shift[i]
+        segs[i].src = src.data_ptr() + i * (seg_bytes + pad) + shift[i]
+        segs[i].bytes = sizes[i]
+    d = torch.from_numpy(np.frombuffer(bytes(segs), dtype=np.uint8).copy()).to(DEV)
+    _cabi.call("kvcm_b200_copy_segments_sized", d.data_ptr(), n_segs, sum(sizes), None)
+    torch.cuda.synchronize()
+    a, b = dst.view(n_segs, -1).cpu().numpy(), src.view(n_segs, -1).cpu().numpy()
+    for i in range(n_segs):
+        assert np.array_equal(a[i, shift[i]:shift[i] + sizes[i]], b[i, shift[i]:shift[i] + sizes[i]]), i
+        assert not a[i, :shift[i]].any() and not a[i, shift[i] + sizes[i]:].any(), i  # nothing outside a segment
+    count = (ctypes.c_uint32 * 1)()
+    _cabi.call("kvcm_b200_copy_wait_timeouts", ctypes.addressof(count))
+    assert count[0] == 0
