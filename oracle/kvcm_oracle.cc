@@ -574,6 +574,9 @@ void kvcm_oracle_replay_run(void *h, const int64_t *keys, const int64_t *key_off
 //   and the three handlers of OptimizerRunner (optimizer_runner.cc:70-215).
 // The tree is kept compressed and split exactly as the reference does, so that this oracle does not
 // assume what the GPU replay assumes (that only per-key residency matters).
+// Pins: the recency-order cases of kv_cache_manager/optimizer/test/lru_eviction_policy_test.cc:44-146
+// restated as traces, and the eviction-free replay above when the quota is never reached.  The
+// reference records no end-to-end numbers for tree clean-up under eviction: parity unpinned there.
 
 namespace {
 
