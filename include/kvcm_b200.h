@@ -258,7 +258,9 @@ KVCM_API int32_t kvcm_b200_key_offsets(const int64_t *h_tok_off, int32_t n_req, 
  * (2b) Block index: the GPU-resident replica of MetaIndexer's key -> locations map that the
  * matchers probe (kv_cache_manager/meta/meta_indexer.cc:419-440, 650-752;
  * kv_cache_manager/meta/meta_local_backend.cc:253-327; kv_cache_manager/common/concurrent_hash_map.h).
- * Open addressing, 16-byte slots {int64 key, uint64 value}.  Every int64 is a legal key.
+ * Open addressing, 16-byte slots {int64 key, uint64 value} plus one tag byte per slot (0 = never used,
+ * else an 8-bit fingerprint) that lets a miss end in the L2-resident tag array instead of HBM.
+ * Every int64 is a legal key.  17 bytes per slot, two slots per key of capacity.
  *
  * The value word summarises the key's location map for the matchers
  * (kv_cache_manager/manager/select_location_policy.cc:8-38).  A location has a status

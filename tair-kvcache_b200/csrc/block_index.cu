@@ -12,13 +12,20 @@
 // expected chain is under two slots, so a lookup costs one or two 32-byte sectors.  Two key
 // values are reserved as EMPTY and TOMBSTONE markers; real keys with those values live in two
 // side cells, so every int64 stays a legal key.  All loops are bounded by the slot count.
+//
+// Beside the slots lies one TAG byte per slot: 0 = the slot was never used, 1 = tombstone,
+// 2..255 = an 8-bit fingerprint of the key stored there.  Readers walk the tags and touch a slot
+// only where the fingerprint matches.  Most probes of a match are misses that end at a never-used
+// slot; with tags they end in a byte array sixteen times smaller than the table (32 MiB for 10 M
+// keys), which stays in the 126 MB L2, instead of a random 32-byte sector of HBM per probe.
 #include <cstring>
 
 #include "kvcm_common.cuh"
 
 struct kvcm_b200_index {
-    void *base;         // one allocation: 256-byte header (the cells) followed by the slots
+    void *base;         // one allocation: 256-byte header (the cells), the slots, then one tag byte per slot
     ulonglong2 *slots;
+    uint8_t *tags;
     uint64_t *cells;    // [0],[1]: values of the two reserved keys; [2]: live key count
     uint64_t n_slots;
     uint64_t max_live;
@@ -41,6 +48,7 @@ constexpr size_t kIndexHeaderBytes = 256;
 
 struct IndexView {
     ulonglong2 *slots;
+    uint8_t *tags;
     uint64_t *cells;
     uint64_t mask;
     uint64_t max_live;
@@ -57,6 +65,12 @@ __host__ __device__ __forceinline__ uint64_t Mix(uint64_t k) {
     k *= 0xc4ceb9fe1a85ec53ull;
     k ^= k >> 33;
     return k;
+}
+
+constexpr uint8_t kTagEmpty = 0, kTagTomb = 1;
+// Fingerprint 2..255 from the top byte of the mixed hash (the slot comes from its low bits).
+__host__ __device__ __forceinline__ uint8_t TagOf(uint64_t mixed) {
+    return static_cast<uint8_t>(2u + (static_cast<uint32_t>(mixed >> 56) * 254u >> 8));
 }
 
 // Hash-range sharding of one logical index over `shards` GPUs: a key belongs to the shard whose
@@ -80,31 +94,43 @@ __device__ __forceinline__ uint32_t OwnerOf(uint64_t key, uint32_t shards) {
 }
 
 // Value word of a key in one table, 0 when absent (MetaIndexer::Get -> EC_NOENT).
-__device__ __forceinline__ uint64_t LookupIn(const ulonglong2 *slots, const uint64_t *cells, uint64_t mask,
-                                             uint64_t key);
-
-// Value word of a key.  With peers attached the probe goes to the owner shard's table, which may
-// live in another GPU's memory: plain 16-byte peer loads over NVLink, no collective.
-__device__ __forceinline__ uint64_t Lookup(const IndexView &ix, uint64_t key) {
-    if (ix.peer_count > 1) {
-        const IndexView &owner = ix.peers[OwnerOf(key, ix.peer_count)];
-        return LookupIn(owner.slots, owner.cells, owner.mask, key);
+// kExpectHit: the caller mostly asks for keys that are there (the leading keys of a prefix match), so
+// the probes read the slots themselves and not the tags: one memory round trip per probe of a hit
+// instead of two dependent ones, at the price of a sector of HBM when the key is absent.
+template <bool kExpectHit>
+__device__ __forceinline__ uint64_t LookupIn(const IndexView &t, uint64_t key) {
+    if (key == kEmptyKey) return t.cells[0];
+    if (key == kTombKey) return t.cells[1];
+    const uint64_t mixed = Mix(key);
+    const uint8_t tag = TagOf(mixed);
+    uint64_t slot = mixed & t.mask;
+    if (kExpectHit) {
+        for (uint64_t probe = 0; probe <= t.mask; ++probe) {
+            const ulonglong2 s = LoadSlot(t.slots + slot);  // the slot itself says whether it is the key, or empty
+            if (s.x == key) return s.y;
+            if (s.x == kEmptyKey) return 0;
+            slot = (slot + 1) & t.mask;
+        }
+        return 0;
     }
-    return LookupIn(ix.slots, ix.cells, ix.mask, key);
-}
-
-__device__ __forceinline__ uint64_t LookupIn(const ulonglong2 *slots, const uint64_t *cells, uint64_t mask,
-                                             uint64_t key) {
-    if (key == kEmptyKey) return cells[0];
-    if (key == kTombKey) return cells[1];
-    uint64_t slot = Mix(key) & mask;
-    for (uint64_t probe = 0; probe <= mask; ++probe) {
-        const ulonglong2 s = LoadSlot(slots + slot);
-        if (s.x == key) return s.y;
-        if (s.x == kEmptyKey) return 0;
-        slot = (slot + 1) & mask;
+    for (uint64_t probe = 0; probe <= t.mask; ++probe) {
+        const uint8_t seen = t.tags[slot];
+        if (seen == kTagEmpty) return 0;
+        if (seen == tag) {
+            const ulonglong2 s = LoadSlot(t.slots + slot);
+            if (s.x == key) return s.y;
+        }
+        slot = (slot + 1) & t.mask;
     }
     return 0;
+}
+
+// Value word of a key.  With peers attached the probe goes to the owner shard's table, which may
+// live in another GPU's memory: plain peer loads over NVLink, no collective.
+template <bool kExpectHit = false>
+__device__ __forceinline__ uint64_t Lookup(const IndexView &ix, uint64_t key) {
+    if (ix.peer_count > 1) return LookupIn<kExpectHit>(ix.peers[OwnerOf(key, ix.peer_count)], key);
+    return LookupIn<kExpectHit>(ix, key);
 }
 
 // A key is a hit for the matchers when some location is SERVING in a storage class whose
@@ -117,6 +143,7 @@ __global__ void ClearKernel(IndexView ix) {
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i <= ix.mask; i += stride) {
         ix.slots[i] = make_ulonglong2(kEmptyKey, 0);
+        ix.tags[i] = kTagEmpty;
     }
     if (blockIdx.x == 0 && threadIdx.x < 3) ix.cells[threadIdx.x] = 0;
 }
@@ -152,6 +179,7 @@ __global__ void UpsertKernel(IndexView ix, const int64_t *__restrict__ keys, con
             seen = atomicCAS(&words[2 * slot], kEmptyKey, key);
             if (seen == kEmptyKey) {
                 atomicExch(&words[2 * slot + 1], value);
+                ix.tags[slot] = TagOf(Mix(key));  // readers of later launches find the slot through its tag
                 return;
             }
         }
@@ -185,6 +213,7 @@ __global__ void EraseKernel(IndexView ix, const int64_t *__restrict__ keys, int6
             // The slot stays occupied (tombstone) so that probe chains through it stay intact.
             if (atomicCAS(&words[2 * slot], key, kTombKey) == key) {
                 atomicExch(&words[2 * slot + 1], 0ull);
+                ix.tags[slot] = kTagTomb;
                 atomicAdd(reinterpret_cast<unsigned long long *>(&ix.cells[2]), ~0ull);
             }
             return;
@@ -239,7 +268,7 @@ __global__ void __launch_bounds__(kMatchWarps * 32)
                 // A key of another shard cannot stop this shard's count: its owner decides, and the
                 // caller takes the minimum over shards.
                 const uint64_t key = static_cast<uint64_t>(keys[beg + i]);
-                const bool hit = !Owns(shard, key) || Servable(Lookup(ix, key), avail_mask);
+                const bool hit = !Owns(shard, key) || Servable(Lookup<true>(ix, key), avail_mask);
                 counted = hit;
                 stop = !hit;
             }
@@ -404,6 +433,7 @@ __global__ void __launch_bounds__(kMatchWarps * 32)
 IndexView View(const kvcm_b200_index *ix) {
     IndexView v;
     v.slots = ix->slots;
+    v.tags = ix->tags;
     v.cells = ix->cells;
     v.mask = ix->n_slots - 1;
     v.max_live = ix->max_live;
@@ -438,13 +468,14 @@ int32_t kvcm_b200_index_create(int64_t max_keys, kvcm_b200_index_t **out) {
     ix->n_slots = n_slots;
     ix->max_live = n_slots - n_slots / 8;  // the matchers rely on at least one EMPTY slot per chain
     cudaGetDevice(&ix->device);
-    if (cudaMalloc(&ix->base, kvcm::kIndexHeaderBytes + n_slots * sizeof(ulonglong2)) != cudaSuccess) {
+    if (cudaMalloc(&ix->base, kvcm::kIndexHeaderBytes + n_slots * (sizeof(ulonglong2) + 1)) != cudaSuccess) {
         cudaGetLastError();
         delete ix;
         return KVCM_EC_NOSPC;
     }
     ix->cells = static_cast<uint64_t *>(ix->base);
     ix->slots = reinterpret_cast<ulonglong2 *>(static_cast<uint8_t *>(ix->base) + kvcm::kIndexHeaderBytes);
+    ix->tags = reinterpret_cast<uint8_t *>(ix->slots + n_slots);
     const int32_t rc = kvcm_b200_index_clear(ix, nullptr);
     if (rc != KVCM_OK || cudaStreamSynchronize(nullptr) != cudaSuccess) {
         cudaFree(ix->base);
@@ -529,6 +560,7 @@ int32_t kvcm_b200_index_attach_peers(kvcm_b200_index_t *ix, int32_t shard_count,
         ix->opened[ix->n_opened++] = base;
         v.cells = static_cast<uint64_t *>(base);
         v.slots = reinterpret_cast<ulonglong2 *>(static_cast<uint8_t *>(base) + kvcm::kIndexHeaderBytes);
+        v.tags = reinterpret_cast<uint8_t *>(v.slots + exports[r].n_slots);
         v.mask = exports[r].n_slots - 1;
     }
     return InstallPeerViews(ix, shard_count, views);

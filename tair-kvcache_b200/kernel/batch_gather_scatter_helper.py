@@ -67,13 +67,16 @@ def _coalesce_token_runs(row_indices, slot_indices, rows_per_block: int, pool_ro
             return None
     elif slot_indices is not None:
         return None  # device-resident slots cannot be range-checked here without a sync
-    g = rows_per_block
-    while g >= 2:
-        if rows_per_block % g == 0 and (pool_rows is None or pool_rows % g == 0):
-            runs = arr.reshape(-1, g)
-            if not (runs[:, 0] % g).any() and (np.diff(runs, axis=1) == 1).all():
-                return np.ascontiguousarray(runs[:, 0] // g, dtype=np.int32), rows_per_block // g, g
-        g //= 2 if g % 2 == 0 else g  # halve while even; an odd length is tried once
+    # the first place where the list stops counting up bounds the run length; try its divisors that also divide
+    # the block length, longest first
+    breaks = np.flatnonzero(np.diff(arr) != 1)
+    longest = int(breaks[0]) + 1 if breaks.size else arr.size
+    for g in range(min(longest, rows_per_block), 1, -1):
+        if rows_per_block % g or (pool_rows is not None and pool_rows % g):
+            continue
+        runs = arr.reshape(-1, g)
+        if not (runs[:, 0] % g).any() and (np.diff(runs, axis=1) == 1).all():
+            return np.ascontiguousarray(runs[:, 0] // g, dtype=np.int32), rows_per_block // g, g
     return None
 
 
