@@ -35,8 +35,8 @@ constexpr int kResidentWarpsPerSm = kMaxHashSmemPerSm / (kWarpRingBytes + 1024);
 // Batches of up to 16 x SMs x this many requests run with half-filled warps.
 constexpr int kHalfWarpSmMultiple = 2;
 
-// What bounds this kernel is the latency of ONE lane's dependent chain (the longest request), and
-// for a lone warp on an SM the integer pipe takes two cycles per warp instruction.  So the loop is
+// What bounds this kernel is the latency of ONE lane's dependent chain (the longest request, ~40
+// cycles per token), and for a lone warp on an SM the integer pipe takes two cycles per warp instruction.  So the loop is
 // shaped to spend as few instructions per token as possible next to the chain itself:
 //  * a stage (64 bytes per lane) is unpacked into registers, as `token + C`, one stage ahead of
 //    the chain (ping-pong register buffers): shared-memory latency never sits on the chain;
@@ -77,8 +77,10 @@ __device__ __forceinline__ void RunFullStage(uint64_t &h, const uint64_t (&vc)[k
 // 2.6x slower on 65,536 requests of 21k tokens).  Here a request is fetched kMinis x 64 bytes at a
 // time with ONE bulk copy (cp.async.bulk, global -> shared, completion counted on an mbarrier),
 // which goes through the TMA unit and bypasses L1.  A bulk copy costs its issuing warp some tens of
-// cycles per lane (about 900 cycles per warp-wide fill), so the copies are issued by a second warp: CTA = consumer warps [0, n) that run the chains + producer
-// warps [n, 2n), producer lane j fetching for consumer lane j.  Per consumer warp and ring slot
+// cycles per lane (about 900 cycles per warp-wide fill), so the copies are issued by a second warp:
+// CTA = consumer warps [0, n) that run the chains + producer warps [n, 2n), producer lane j
+// fetching for consumer lane j (a one-consumer CTA may swap the two roles, see the kernel).  Per
+// consumer warp and ring slot
 // there is a `full` barrier (32 producer arrivals + the bytes in flight) and an `empty` barrier
 // (32 consumer arrivals once the slot has been read into registers).  A lane's bytes of a slot are
 // contiguous; lanes are kMinis*64+16 bytes apart, an odd number of 16-byte words, so the 128-bit

@@ -3,6 +3,7 @@ HitAnalysis::Analyze (kv_cache_manager/optimizer/manager/optimizer_runner.cc:13-
 kv_cache_manager/optimizer/analysis/result_analysis.cc:10-113): without eviction, or with the "lru" policy at
 one or many quota points (the tradeoff curves of kv_cache_manager/optimizer/analysis/script/
 tradeoff_curve_by_instances.py)."""
+import json
 import os
 from typing import Dict, List, Optional, Sequence, Union
 
@@ -102,8 +103,8 @@ def export_hit_rates(path: str, rec: Dict[str, np.ndarray]) -> None:
 
 def run_trace_file(trace_path: str, trace_type: str, output_dir: str, device=None,
                    block_sizes: Optional[Dict[str, int]] = None, rw_separation: bool = False,
-                   quota_blocks: Union[None, int, Sequence[int]] = None, evict_batch: int = 100,
-                   precise: bool = False):
+                   quota_blocks: Union[None, int, Sequence[int], Dict[str, Union[int, Sequence[int]]]] = None,
+                   evict_batch: int = 100, precise: bool = False):
     """Loads a trace file, replays every instance on the GPU and writes `<instance>_hit_rates.csv` per instance
     (`<instance>_quota<q>_hit_rates.csv` per instance and quota when quota_blocks is a sequence).  Every instance is
     replayed on its own: instances that share one group quota in the reference's configuration are not modelled."""
@@ -113,14 +114,72 @@ def run_trace_file(trace_path: str, trace_type: str, output_dir: str, device=Non
     for t in traces:
         by_instance.setdefault(t.instance_id, []).append(t)
     os.makedirs(output_dir, exist_ok=True)
-    sweep = quota_blocks is not None and not np.isscalar(quota_blocks)
     out = {}
     for instance_id, ts in sorted(by_instance.items()):
-        rec = replay_instance(ts, device, rw_separation, quota_blocks, evict_batch, precise)
+        # a dict gives every instance its own quota (or quotas); instances it does not name are never evicted
+        quota = quota_blocks.get(instance_id) if isinstance(quota_blocks, dict) else quota_blocks
+        sweep = quota is not None and not np.isscalar(quota)
+        rec = replay_instance(ts, device, rw_separation, quota, evict_batch, precise)
         for c, r in enumerate(rec if sweep else [rec]):
             if (r["kind"] != tr.WRITE_CACHE).any():
-                name = "%s_quota%d_hit_rates.csv" % (instance_id, int(quota_blocks[c])) if sweep else \
+                name = "%s_quota%d_hit_rates.csv" % (instance_id, int(quota[c])) if sweep else \
                     instance_id + "_hit_rates.csv"
                 export_hit_rates(os.path.join(output_dir, name), r)
         out[instance_id] = rec
     return out
+
+
+EVICTION_MODE_UNSPECIFIED, EVICTION_MODE_GROUP_ROUGH, EVICTION_MODE_INSTANCE_ROUGH, EVICTION_MODE_INSTANCE_PRECISE = \
+    0, 1, 2, 3  # kv_cache_manager/optimizer/config/types.h
+
+
+def parse_startup_config(config: Union[str, dict]) -> dict:
+    """The Optimizer's startup configuration (kv_cache_manager/optimizer/optimizer_startup_config_load.json, read
+    by kv_cache_manager/optimizer/config/optimizer_config.cc:4-12, instance_group_config.cc:5-12,
+    instance_config.cc:6-22, eviction_config.cc:5-8) reduced to what the GPU replay needs.  Raises
+    NotImplementedError for what it cannot replay exactly: policies other than "lru", hierarchical eviction, and
+    groups whose quota is shared by several instances."""
+    if isinstance(config, str):
+        with open(config) as f:
+            config = json.load(f)
+    ev = config.get("eviction_params", {})
+    mode = int(ev.get("eviction_mode", EVICTION_MODE_UNSPECIFIED))
+    if mode not in (EVICTION_MODE_UNSPECIFIED, EVICTION_MODE_GROUP_ROUGH, EVICTION_MODE_INSTANCE_ROUGH,
+                    EVICTION_MODE_INSTANCE_PRECISE):
+        raise ValueError("unknown eviction_mode %r" % mode)
+    quotas, block_sizes = {}, {}
+    for group in config.get("instance_groups", []):
+        instances = group.get("instances", [])
+        if group.get("hierarchical_eviction_enabled", False):
+            raise NotImplementedError("group %r: hierarchical eviction is not replayed" % group.get("group_name"))
+        if len(instances) > 1 and mode != EVICTION_MODE_UNSPECIFIED:
+            raise NotImplementedError("group %r: %d instances share one quota" % (group.get("group_name"),
+                                                                                   len(instances)))
+        for inst in instances:
+            policy = inst.get("eviction_policy_type", "lru")
+            if policy != "lru" and mode != EVICTION_MODE_UNSPECIFIED:
+                raise NotImplementedError("instance %r: eviction policy %r is not replayed (only \"lru\")"
+                                          % (inst.get("instance_id"), policy))
+            iid = str(inst["instance_id"])
+            block_sizes[iid] = int(inst.get("block_size", 16))
+            # eviction_manager.cc:249-266: quota = size_t(quota_capacity * used_percentage); an unspecified mode
+            # never evicts (:60-63)
+            if mode != EVICTION_MODE_UNSPECIFIED:
+                quotas[iid] = int(group["quota_capacity"] * float(group.get("used_percentage", 1.0)))
+    return dict(trace_file_path=config.get("trace_file_path"), trace_type=config.get("trace_type"),
+                output_result_path=config.get("output_result_path"), quota_blocks=quotas, block_sizes=block_sizes,
+                evict_batch=int(ev.get("eviction_batch_size_per_instance", 100)),
+                precise=mode == EVICTION_MODE_INSTANCE_PRECISE)
+
+
+def run_startup_config(config: Union[str, dict], device=None, rw_separation: Optional[bool] = None):
+    """What `optimizer_main <config>` does (kv_cache_manager/optimizer/main.cc; OptimizerRunner::Run +
+    HitAnalysis), on the GPU: load the trace the configuration names, replay every instance with its group's
+    quota and write `<instance>_hit_rates.csv` under output_result_path.  As the reference's converter factory
+    decides it (kv_cache_manager/optimizer/trace_converter/converter_factory.cc:19-28), publisher logs are
+    replayed with reads and writes separate and the two dialog-turn formats are not."""
+    c = parse_startup_config(config)
+    if rw_separation is None:
+        rw_separation = c["trace_type"] == "publisher_log"
+    return run_trace_file(c["trace_file_path"], c["trace_type"], c["output_result_path"], device, c["block_sizes"],
+                          rw_separation, c["quota_blocks"] or None, c["evict_batch"], c["precise"])

@@ -105,3 +105,40 @@ def test_qwen_bailian_file_with_lru_quota_sweep(tmp_path):
                          evict_batch=5)["instance"]
     assert np.array_equal(rec["external_hit_blocks"], recs[1]["external_hit_blocks"])
     assert (tmp_path / "one" / "instance_hit_rates.csv").exists()
+
+
+def test_startup_config_drives_a_publisher_log_replay_with_eviction(tmp_path):
+    """The reference's `optimizer_main <config>` flow: configuration file -> trace -> per-instance CSV, with a group
+    quota small enough to evict.  Expected numbers are worked out by hand from the LRU rules."""
+    from tair_kvcache_b200.optimizer import run_startup_config
+
+    def ev(kind, ts, **kw):
+        return json.dumps(dict(type=kind, source="i1", trigger_time_us=ts, **kw))
+    path = tmp_path / "pub.log"
+    path.write_text("\n".join([
+        ev("StartWriteCache", 10, write_session_id="a", keys=[1, 2, 3]),
+        ev("FinishWriteCache", 11, write_session_id="a"),                       # cache: 1 2 3
+        ev("GetCacheLocation", 20, query_type="prefix_match", keys=[1, 2, 3], block_mask=0),  # hit 3, all refreshed
+        ev("StartWriteCache", 30, write_session_id="b", keys=[7, 8]),
+        ev("FinishWriteCache", 31, write_session_id="b"),                       # 5 cached > 4: one batch of 2 evicts 1, 2
+        ev("GetCacheLocation", 40, query_type="prefix_match", keys=[1, 2, 3], block_mask=0),  # 1 is gone: no hit
+        ev("GetCacheLocation", 50, query_type="prefix_match", keys=[7, 8, 9], block_mask=1)]))  # 7 masked, 8 hit
+    cfg = {"trace_file_path": str(path), "trace_type": "publisher_log", "output_result_path": str(tmp_path / "out"),
+           "eviction_params": {"eviction_mode": 2, "eviction_batch_size_per_instance": 2},
+           "instance_groups": [{"group_name": "g", "quota_capacity": 8, "used_percentage": 0.5,
+                                "hierarchical_eviction_enabled": False, "storages": [],
+                                "instances": [{"instance_id": "i1", "block_size": 64, "eviction_policy_type": "lru",
+                                               "eviction_policy_params": {"sample_rate": 0.1}}]}]}
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(json.dumps(cfg))
+    rec = run_startup_config(str(cfg_path), device="cuda:0")["i1"]
+    assert rec["kind"].tolist() == [tr.WRITE_CACHE, tr.GET_LOCATION, tr.WRITE_CACHE, tr.GET_LOCATION, tr.GET_LOCATION]
+    assert rec["write_blocks"].tolist() == [3, 0, 2, 0, 0]
+    assert rec["external_hit_blocks"].tolist() == [0, 3, 0, 0, 1]
+    assert rec["internal_hit_blocks"].tolist() == [0, 0, 0, 0, 1]
+    assert rec["current_cache_blocks"].tolist() == [3, 3, 3, 3, 3]
+    # the same through the oracle's radix tree
+    keys, off = [1, 2, 3, 1, 2, 3, 7, 8, 1, 2, 3, 7, 8, 9], [0, 3, 6, 8, 11, 14]
+    want = oracle.LruReplay(4, evict_batch=2).run(keys, off, rec["kind"], [0, 0, 0, 0, 1])
+    assert np.array_equal(want[0], rec["external_hit_blocks"]) and np.array_equal(want[3], rec["current_cache_blocks"])
+    assert len((tmp_path / "out" / "i1_hit_rates.csv").read_text().splitlines()) == 4

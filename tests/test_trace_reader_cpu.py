@@ -77,3 +77,36 @@ def test_mask_offset_rules():
     assert tr.mask_offset([True, True, False], 3) == 2 and tr.mask_offset([], 3) == 0
     with pytest.raises(ValueError):
         tr.mask_offset([True, False, True], 3)
+
+
+def test_startup_config_of_the_reference_is_understood():
+    """The shipped example (kv_cache_manager/optimizer/optimizer_startup_config_load.json), transcribed: one group,
+    quota 12000 x 1.0, rough group eviction in batches of 100, one "lru" instance with block size 16."""
+    import pytest
+    from tair_kvcache_b200.optimizer.runner import parse_startup_config
+    cfg = {"trace_file_path": "/data/event_publisher.log", "trace_type": "publisher_log",
+           "output_result_path": "/data/out",
+           "eviction_params": {"eviction_mode": 1, "eviction_batch_size_per_instance": 100},
+           "instance_groups": [{"group_name": "instance_group_01", "quota_capacity": 12000, "used_percentage": 1.0,
+                                "hierarchical_eviction_enabled": False,
+                                "storages": [{"unique_name": "pace_00", "storage_type": "pace", "capacity": 100000}],
+                                "instances": [{"instance_id": "3780643326877293460", "block_size": 16,
+                                               "eviction_policy_type": "lru",
+                                               "eviction_policy_params": {"sample_rate": 0.1}}]}]}
+    c = parse_startup_config(cfg)
+    assert c["quota_blocks"] == {"3780643326877293460": 12000} and c["block_sizes"] == {"3780643326877293460": 16}
+    assert c["evict_batch"] == 100 and c["precise"] is False and c["trace_type"] == "publisher_log"
+    cfg["instance_groups"][0]["used_percentage"] = 0.75
+    cfg["eviction_params"]["eviction_mode"] = 3
+    c = parse_startup_config(cfg)
+    assert c["quota_blocks"]["3780643326877293460"] == 9000 and c["precise"] is True
+    # what the GPU replay does not reproduce is refused, not approximated
+    cfg["instance_groups"][0]["instances"][0]["eviction_policy_type"] = "leaf_aware_lru"
+    with pytest.raises(NotImplementedError):
+        parse_startup_config(cfg)
+    cfg["instance_groups"][0]["instances"][0]["eviction_policy_type"] = "lru"
+    cfg["instance_groups"][0]["instances"].append({"instance_id": "b", "block_size": 16, "eviction_policy_type": "lru"})
+    with pytest.raises(NotImplementedError):
+        parse_startup_config(cfg)
+    cfg["eviction_params"]["eviction_mode"] = 0  # no eviction is ever performed: any grouping replays
+    assert parse_startup_config(cfg)["quota_blocks"] == {}
