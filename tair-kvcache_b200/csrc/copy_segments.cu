@@ -196,11 +196,7 @@ int32_t kvcm_b200_copy_segments_sized(const kvcm_b200_seg_t *d_segs, int32_t n_s
     if (n_segs == 0) return KVCM_OK;
     if (d_segs == nullptr) return KVCM_ER_INVALID_ADDRESS;
     if (total_bytes / static_cast<uint64_t>(n_segs) >= kvcm::kBulkMinSegment) {
-        // Large segments: the bulk-copy ring.  64 KiB of shared memory per one-warp CTA, three CTAs per SM.
-        static std::mutex mu;
-        static std::vector<int> opted;
-        int device = 0;
-        cudaGetDevice(&device);
+        // Large segments: the bulk-copy ring, two stages of shared memory per one-warp CTA.
         // Geometry from a sweep on B200 (131,072 segments of 128 KiB): 48 KiB chunks x 2 CTAs per SM reach 0.99 of
         // the measured copy peak, 32 KiB x 3 reach 0.97, 64 KiB x 1 0.93; 192 KiB are in flight per SM either way.
         // Short segments would leave most of a 48 KiB stage empty.
@@ -208,14 +204,7 @@ int32_t kvcm_b200_copy_segments_sized(const kvcm_b200_seg_t *d_segs, int32_t n_s
         const uint32_t chunk_bytes = wide ? 48 * 1024 : kvcm::kBulkChunk;
         const int ctas_per_sm = wide ? 2 : 3;
         const int smem = kvcm::kBulkStages * static_cast<int>(chunk_bytes);
-        {
-            std::lock_guard<std::mutex> lock(mu);
-            if (std::find(opted.begin(), opted.end(), device) == opted.end()) {
-                cudaFuncSetAttribute(kvcm::CopySegmentsBulkKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     kvcm::kBulkStages * 48 * 1024);
-                opted.push_back(device);
-            }
-        }
+        kvcm::EnsureDynamicSmem(kvcm::CopySegmentsBulkKernel, kvcm::kBulkStages * 48 * 1024);
         const uint32_t grid = static_cast<uint32_t>(kvcm::GetDeviceInfo().sm_count) * ctas_per_sm;
         uint32_t parts = 1, seg_lanes = grid;
         if (static_cast<uint32_t>(n_segs) < grid) {

@@ -379,19 +379,7 @@ int32_t LaunchHash(const T *d_tokens, int64_t n_tokens_total, const int64_t *d_t
     const unsigned threads = 2 * warps_per_cta * 32;  // consumer warps + their producer warps
     constexpr int kPerStage = kStageBytes / sizeof(T);
     auto launch = [&](auto kernel) {
-        // The opt-in to large dynamic shared memory is per device and per kernel.
-        static std::mutex mu;
-        static std::vector<std::pair<int, const void *>> done;
-        int device = 0;
-        cudaGetDevice(&device);
-        {
-            const std::pair<int, const void *> key(device, reinterpret_cast<const void *>(kernel));
-            std::lock_guard<std::mutex> lock(mu);
-            if (std::find(done.begin(), done.end(), key) == done.end()) {
-                cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxHashSmemPerSm);
-                done.push_back(key);
-            }
-        }
+        EnsureDynamicSmem(kernel, kMaxHashSmemPerSm);
         kernel<<<grid, threads, smem, AsStream(stream)>>>(d_tokens, n_tokens_total, d_tok_off, n_req, block_size, d_keys,
                                                           d_key_off, d_order, lanes_per_warp,
                                                           static_cast<uint32_t>(smem_per_warp));

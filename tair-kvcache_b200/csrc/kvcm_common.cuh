@@ -3,7 +3,11 @@
 
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdint>
+#include <mutex>
+#include <utility>
+#include <vector>
 
 #include "kvcm_b200.h"
 
@@ -29,6 +33,22 @@ inline int32_t LaunchStatus() {
 // True when a device is present; every compute entry point checks it first so that a box
 // without a GPU gets KVCM_ER_NO_DEVICE instead of a silent no-op.
 bool HaveDevice();
+
+// The opt-in to more than 48 KiB of dynamic shared memory is per device and per kernel; this makes it
+// once for each pair, whichever host thread gets there first.
+template <typename Kernel>
+inline void EnsureDynamicSmem(Kernel kernel, int bytes) {
+    static std::mutex mu;
+    static std::vector<std::pair<int, const void *>> done;
+    int device = 0;
+    cudaGetDevice(&device);
+    const std::pair<int, const void *> key(device, reinterpret_cast<const void *>(kernel));
+    std::lock_guard<std::mutex> lock(mu);
+    if (std::find(done.begin(), done.end(), key) == done.end()) {
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        done.push_back(key);
+    }
+}
 
 __device__ __forceinline__ uint32_t LaneId() { return threadIdx.x & 31u; }
 

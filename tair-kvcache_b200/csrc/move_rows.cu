@@ -470,11 +470,7 @@ constexpr int kBulkMaxSmem = 224 * 1024;
 
 template <bool kGather>
 void LaunchBulk(const MoveParams &p, int ctas_per_sm, int sms, cudaStream_t stream) {
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaFuncSetAttribute(MoveRowsBulkKernel<kGather>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkMaxSmem);
-        attr_set = true;
-    }
+    EnsureDynamicSmem(MoveRowsBulkKernel<kGather>, kBulkMaxSmem);
     const int smem = p.stages * static_cast<int>(p.chunk_bytes);
     const int64_t resident = static_cast<int64_t>(sms) * ctas_per_sm;
     const unsigned grid = static_cast<unsigned>(p.total_chunks < resident ? p.total_chunks : resident);
