@@ -67,19 +67,6 @@ __host__ __device__ __forceinline__ uint64_t HashStepPre(uint64_t h, uint64_t va
     return h ^ (value_plus_golden + (h << 12) + sra32);
 }
 
-// The same step on 32-bit halves, written so that the dependent chain is four operations deep:
-// shifts (1) -> three-input low add (2) -> carry into the high word (3) -> xor (4).  `vl`/`vh` are
-// the halves of value + 0x9e3779b97f4a7c15.  (Multiply-add forms of the shifts were measured
-// slower on B200: 58 against 47 cycles per token for a lone warp.)
-__device__ __forceinline__ void HashStep32(uint32_t &hl, uint32_t &hh, uint32_t vl, uint32_t vh) {
-    const uint32_t ah = __funnelshift_l(hl, hh, 12);                            // high word of h << 12
-    const uint32_t bh = static_cast<uint32_t>(static_cast<int32_t>(hh) >> 31);  // high word of h >> 32 (arithmetic)
-    const uint64_t lo = static_cast<uint64_t>(hl << 12) + hh + vl;              // low words, carry (0..2) on top
-    const uint32_t hi = ah + bh + vh;
-    hl ^= static_cast<uint32_t>(lo);
-    hh ^= hi + static_cast<uint32_t>(lo >> 32);
-}
-
 // ---- mbarrier and bulk-copy (TMA) primitives shared by the kernels that stage through shared memory ----
 // Failed polls of a barrier after which a kernel gives up, raises its error word and returns.
 constexpr uint32_t kSpinLimit = 1u << 22;
