@@ -1114,7 +1114,7 @@ def main_lru(args, rank, world):
     e3.record()
     torch.cuda.synchronize(device)
     sweep_ms = e2.elapsed_time(e3)
-    hit_rate = (res.external_hit_blocks.sum(dim=1).double() / max(n_keys, 1)).cpu().numpy()
+    hit_rate = (res.totals[:, 0].double() / max(n_keys, 1)).cpu().numpy()
     t = torch.tensor([ms], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

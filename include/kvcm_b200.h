@@ -433,7 +433,10 @@ KVCM_API int32_t kvcm_b200_replay(const int64_t *d_keys, const int64_t *d_key_of
  * kv_cache_manager/optimizer/manager/eviction_manager.cc:86-192); precise != 0: exactly the excess
  * (EVICTION_MODE_INSTANCE_PRECISE, :194-239).  d_quota_blocks[c] is configuration c's
  * size_t(quota_capacity * used_percentage) (:249-266).
- * Trace encoding as kvcm_b200_replay.  Outputs are [n_configs][n_traces], configuration-major.
+ * Trace encoding as kvcm_b200_replay.  Per-trace outputs are [n_configs][n_traces], configuration-major; pass
+ * all four or none (NULL).  d_totals (optional, [n_configs][4] int64) receives per configuration the sums of
+ * external hits, internal hits and written blocks over the trace and the cached blocks at its end - all a
+ * tradeoff curve needs, so a large sweep can skip the per-trace arrays.
  * Exact for prefix-unique chained keys without repeats inside one trace.  Configurations are
  * independent and run in parallel (one warp each); one configuration is replayed in trace order.
  * d_workspace: kvcm_b200_replay_lru_workspace_bytes(n_keys_total, n_configs) bytes (-1: too large:
@@ -447,7 +450,8 @@ KVCM_API int32_t kvcm_b200_replay_lru(const int64_t *d_keys, const int64_t *d_ke
                                       const int64_t *d_quota_blocks, int32_t n_configs, int32_t evict_batch,
                                       int32_t precise, void *d_workspace, int64_t workspace_bytes,
                                       int32_t *d_ext_hit, int32_t *d_int_hit, int32_t *d_written,
-                                      int64_t *d_cache_blocks, uint32_t *d_status, kvcm_stream_t stream);
+                                      int64_t *d_cache_blocks, int64_t *d_totals, uint32_t *d_status,
+                                      kvcm_stream_t stream);
 
 /* Trace replay for callers that cannot allocate device memory.  (No counterpart in the reference: it
  * exists for how this library gets embedded, not for a reference interface.)

@@ -126,8 +126,9 @@ struct LruSweep {
     const int64_t *quota;
     uint32_t *stamps;  // [n_configs][n_keys]
     uint2 *queue;      // [n_configs][n_keys]
-    int32_t *ext_hit, *int_hit, *written;
+    int32_t *ext_hit, *int_hit, *written;  // per trace; all four may be null when only totals are wanted
     int64_t *cache_blocks;
+    int64_t *totals;  // [n_configs][4]: external hits, internal hits, written blocks, cached blocks at the end
     int64_t n_keys;
     int32_t n_traces;
     int32_t n_configs;
@@ -146,6 +147,7 @@ __global__ void __launch_bounds__(32) LruSweepKernel(const LruSweep p) {
     const int64_t out0 = static_cast<int64_t>(cfg) * p.n_traces;
     uint32_t counter = 0;  // last stamp handed out
     int64_t head = 0, tail = 0, resident = 0;
+    int64_t sum_ext = 0, sum_int = 0, sum_wr = 0;
 
     // What a trace reads before it touches any state (its extent, kind and the ids of its first 32
     // keys) is fetched one trace ahead, its extent two traces ahead, so that the only load a trace
@@ -256,14 +258,24 @@ __global__ void __launch_bounds__(32) LruSweepKernel(const LruSweep p) {
                 __syncwarp();
             }
         }
-        if (lane == 0) {
+        if (lane == 0 && p.ext_hit != nullptr) {
             p.ext_hit[out0 + t] = ext;
             p.int_hit[out0 + t] = inte;
             p.written[out0 + t] = wr;
             p.cache_blocks[out0 + t] = resident;
         }
+        sum_ext += ext;
+        sum_int += inte;
+        sum_wr += wr;
         beg = beg1, n = n1, ty = ty1, skip = skip1, first_id = next_first_id;
         beg1 = beg2, n1 = n2, ty1 = ty2, skip1 = skip2;
+    }
+    if (lane == 0 && p.totals != nullptr) {
+        int64_t *tot = p.totals + static_cast<int64_t>(cfg) * 4;
+        tot[0] = sum_ext;
+        tot[1] = sum_int;
+        tot[2] = sum_wr;
+        tot[3] = resident;
     }
 }
 
@@ -303,15 +315,18 @@ int32_t kvcm_b200_replay_lru(const int64_t *d_keys, const int64_t *d_key_off, co
                              const int64_t *d_mask_off, int32_t n_traces, int64_t n_keys_total,
                              const int64_t *d_quota_blocks, int32_t n_configs, int32_t evict_batch, int32_t precise,
                              void *d_workspace, int64_t workspace_bytes, int32_t *d_ext_hit, int32_t *d_int_hit,
-                             int32_t *d_written, int64_t *d_cache_blocks, uint32_t *d_status, kvcm_stream_t stream) {
+                             int32_t *d_written, int64_t *d_cache_blocks, int64_t *d_totals, uint32_t *d_status,
+                             kvcm_stream_t stream) {
     if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
     if (n_traces < 0 || n_keys_total < 0 || n_configs <= 0 || evict_batch <= 0) return KVCM_EC_BADARGS;
     const int64_t need = kvcm_b200_replay_lru_workspace_bytes(n_keys_total, n_configs);
     if (need < 0) return KVCM_EC_OUT_OF_LIMIT;
     if (n_traces == 0) return KVCM_OK;
-    if (d_key_off == nullptr || d_trace_type == nullptr || d_quota_blocks == nullptr || d_ext_hit == nullptr ||
-        d_int_hit == nullptr || d_written == nullptr || d_cache_blocks == nullptr || d_workspace == nullptr ||
-        (d_keys == nullptr && n_keys_total > 0)) {
+    const int per_trace = (d_ext_hit != nullptr) + (d_int_hit != nullptr) + (d_written != nullptr) +
+                          (d_cache_blocks != nullptr);
+    if (d_key_off == nullptr || d_trace_type == nullptr || d_quota_blocks == nullptr || d_workspace == nullptr ||
+        (d_keys == nullptr && n_keys_total > 0) || (per_trace != 0 && per_trace != 4) ||
+        (per_trace == 0 && d_totals == nullptr)) {
         return KVCM_ER_INVALID_ADDRESS;
     }
     if (reinterpret_cast<uintptr_t>(d_workspace) & 255u) return KVCM_ER_INVALID_ADDRESS;
@@ -344,6 +359,7 @@ int32_t kvcm_b200_replay_lru(const int64_t *d_keys, const int64_t *d_key_off, co
     p.int_hit = d_int_hit;
     p.written = d_written;
     p.cache_blocks = d_cache_blocks;
+    p.totals = d_totals;
     p.n_keys = n_keys_total > 0 ? n_keys_total : 1;
     p.n_traces = n_traces;
     p.n_configs = n_configs;

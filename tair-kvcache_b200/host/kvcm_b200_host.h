@@ -415,7 +415,8 @@ public:
         rc = kvcm_b200_replay_lru(keys_.dev<int64_t>(), off_.dev<int64_t>(), kind_.dev<uint8_t>(),
                                   mask_.dev<int64_t>(), n, n_keys, quota_.dev<int64_t>(), n_cfg, evict_batch,
                                   precise ? 1 : 0, workspace_.dev<void>(), ws_bytes, ext_.dev<int32_t>(),
-                                  int_.dev<int32_t>(), wr_.dev<int32_t>(), size_.dev<int64_t>(), nullptr, stream_);
+                                  int_.dev<int32_t>(), wr_.dev<int32_t>(), size_.dev<int64_t>(), nullptr, nullptr,
+                                  stream_);
         if (rc != KVCM_OK) return rc;
         rc = Fetch(static_cast<size_t>(n) * n_cfg);
         if (rc != KVCM_OK) return rc;

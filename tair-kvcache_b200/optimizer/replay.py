@@ -58,10 +58,11 @@ def RunTraces(keys: torch.Tensor, key_off: torch.Tensor, trace_type: torch.Tenso
 
 
 class LruSweepResult(NamedTuple):
-    external_hit_blocks: torch.Tensor   # int32 [n_configs, n_traces]
-    internal_hit_blocks: torch.Tensor   # int32 [n_configs, n_traces]
-    write_blocks: torch.Tensor          # int32 [n_configs, n_traces]
-    current_cache_blocks: torch.Tensor  # int64 [n_configs, n_traces], after the trace (and its eviction)
+    external_hit_blocks: Optional[torch.Tensor]   # int32 [n_configs, n_traces]; None with per_trace=False
+    internal_hit_blocks: Optional[torch.Tensor]   # int32 [n_configs, n_traces]
+    write_blocks: Optional[torch.Tensor]          # int32 [n_configs, n_traces]
+    current_cache_blocks: Optional[torch.Tensor]  # int64 [n_configs, n_traces], after the trace (and its eviction)
+    totals: torch.Tensor  # int64 [n_configs, 4]: external hits, internal hits, written blocks, cached blocks at the end
 
 
 def replay_lru_workspace_bytes(n_keys_total: int, n_configs: int) -> int:
@@ -73,11 +74,13 @@ def replay_lru_workspace_bytes(n_keys_total: int, n_configs: int) -> int:
 
 def RunTracesLru(keys: torch.Tensor, key_off: torch.Tensor, trace_type: torch.Tensor, quota_blocks,
                  mask_off: Optional[torch.Tensor] = None, evict_batch: int = 100, precise: bool = False,
-                 workspace: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> LruSweepResult:
+                 workspace: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
+                 per_trace: bool = True) -> LruSweepResult:
     """The replay of RunTraces with the reference's "lru" eviction policy, once per entry of quota_blocks (the
     points of a tradeoff curve: quota_capacity * used_percentage in blocks), all configurations in one launch.
     evict_batch / precise: eviction_batch_size_per_instance and the eviction mode (False = the rough modes, which
-    evict whole batches; True = INSTANCE_PRECISE)."""
+    evict whole batches; True = INSTANCE_PRECISE).  per_trace=False skips the [n_configs, n_traces] records and
+    returns only the totals per configuration (what a tradeoff curve reads)."""
     if not keys.is_cuda:
         raise ValueError("keys must be a CUDA tensor: this path has no CPU implementation")
     dev = keys.device
@@ -91,17 +94,20 @@ def RunTracesLru(keys: torch.Tensor, key_off: torch.Tensor, trace_type: torch.Te
         workspace = torch.empty(need, dtype=torch.uint8, device=dev)
     elif workspace.numel() < need or workspace.device != dev:
         raise ValueError("workspace too small: %d < %d bytes" % (workspace.numel(), need))
-    shape = (n_cfg, max(n_traces, 1))
-    ext = torch.empty(shape, dtype=torch.int32, device=dev)
-    inte, wr = torch.empty_like(ext), torch.empty_like(ext)
-    size = torch.empty(shape, dtype=torch.int64, device=dev)
-    if n_traces > 0:
+    totals = torch.zeros((n_cfg, 4), dtype=torch.int64, device=dev)
+    ext = inte = wr = size = None
+    if per_trace:
         # the C entry point lays its outputs out as [n_configs][n_traces]
-        ext, inte, wr, size = (x[:, :n_traces].contiguous() for x in (ext, inte, wr, size))
+        ext = torch.empty((n_cfg, n_traces), dtype=torch.int32, device=dev)
+        inte, wr = torch.empty_like(ext), torch.empty_like(ext)
+        size = torch.empty((n_cfg, n_traces), dtype=torch.int64, device=dev)
+    ptr = (lambda t: t.data_ptr() if t is not None and t.numel() > 0 else None)
+    if per_trace and n_traces == 0:
+        return LruSweepResult(ext, inte, wr, size, totals)
     _cabi.bind_device(dev.index)
     _cabi.call("kvcm_b200_replay_lru", keys.data_ptr(), key_off.data_ptr(), trace_type.data_ptr(),
                mask_off.contiguous().data_ptr() if mask_off is not None else None, n_traces, keys.numel(),
                quota.data_ptr(), n_cfg, int(evict_batch), 1 if precise else 0, workspace.data_ptr(),
-               workspace.numel(), ext.data_ptr(), inte.data_ptr(), wr.data_ptr(), size.data_ptr(),
+               workspace.numel(), ptr(ext), ptr(inte), ptr(wr), ptr(size), totals.data_ptr(),
                status.data_ptr() if status is not None else None, torch.cuda.current_stream(dev).cuda_stream)
-    return LruSweepResult(ext[:, :n_traces], inte[:, :n_traces], wr[:, :n_traces], size[:, :n_traces])
+    return LruSweepResult(ext, inte, wr, size, totals)

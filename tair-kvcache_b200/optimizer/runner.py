@@ -33,13 +33,7 @@ def replay_instance(traces: List[tr.Trace], device, rw_separation: bool = False,
     quota_blocks = None: nothing is ever evicted; an int: "lru" eviction at that quota (quota_capacity *
     used_percentage, in blocks); a sequence: one record per quota, all replayed in one launch.  evict_batch and
     precise are eviction_batch_size_per_instance and the eviction mode (False = the rough modes)."""
-    keep = []
-    for t in traces:
-        if t.kind != tr.WRITE_CACHE and t.query_type != "prefix_match":
-            continue
-        if (t.kind == tr.DIALOG_TURN) == rw_separation:
-            continue
-        keep.append(t)
+    keep = _kept(traces, rw_separation)
     keys, off, kind, mask, read = tr.to_csr(keep)
     d_keys, d_off = torch.from_numpy(keys).to(device), torch.from_numpy(off).to(device)
     if any(t.needs_prefix_hash for t in keep):  # Qwen-Bailian ids: chain them first
@@ -58,9 +52,42 @@ def replay_instance(traces: List[tr.Trace], device, rw_separation: bool = False,
     if quota_blocks is None:
         return record(*(x.cpu().numpy() for x in RunTraces(d_keys, d_off, d_kind, d_mask)))
     quotas = [int(quota_blocks)] if np.isscalar(quota_blocks) else [int(q) for q in quota_blocks]
-    res = [x.cpu().numpy() for x in RunTracesLru(d_keys, d_off, d_kind, quotas, d_mask, evict_batch, precise)]
+    res = [x.cpu().numpy() for x in RunTracesLru(d_keys, d_off, d_kind, quotas, d_mask, evict_batch, precise)[:4]]
     recs = [record(*(x[c] for x in res)) for c in range(len(quotas))]
     return recs[0] if np.isscalar(quota_blocks) else recs
+
+
+def _kept(traces: List[tr.Trace], rw_separation: bool) -> List[tr.Trace]:
+    """The traces OptimizerRunner::RunTrace replays in the given mode (optimizer_runner.cc:34-68)."""
+    keep = []
+    for t in traces:
+        if t.kind != tr.WRITE_CACHE and t.query_type != "prefix_match":
+            continue
+        if (t.kind == tr.DIALOG_TURN) == rw_separation:
+            continue
+        keep.append(t)
+    return keep
+
+
+def sweep_hit_rates(traces: List[tr.Trace], device, quota_blocks: Sequence[int], rw_separation: bool = False,
+                    evict_batch: int = 100, precise: bool = False) -> np.ndarray:
+    """The points of a tradeoff curve without the per-trace records: rows of accumulated (internal, external, total)
+    hit rates, one per quota, the same numbers tradeoff_curve() computes from full records."""
+    keep = _kept(traces, rw_separation)
+    keys, off, kind, mask, read = tr.to_csr(keep)
+    d_keys, d_off = torch.from_numpy(keys).to(device), torch.from_numpy(off).to(device)
+    if any(t.needs_prefix_hash for t in keep):
+        d_keys = ApplyPrefixHashBatch(d_keys, d_off)
+    res = RunTracesLru(d_keys, d_off, torch.from_numpy(kind).to(device), [int(q) for q in quota_blocks],
+                       torch.from_numpy(mask).to(device), evict_batch, precise, per_trace=False)
+    totals = res.totals.cpu().numpy()
+    total_read = int(read[kind != tr.WRITE_CACHE].sum())
+    out = np.zeros((totals.shape[0], 3))
+    if total_read:
+        out[:, 0] = totals[:, 1] / total_read
+        out[:, 1] = totals[:, 0] / total_read
+    out[:, 2] = out[:, 0] + out[:, 1]
+    return out
 
 
 def tradeoff_curve(recs: Sequence[Dict[str, np.ndarray]]) -> np.ndarray:

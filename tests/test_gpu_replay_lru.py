@@ -20,7 +20,11 @@ def _gpu(keys, off, types, quotas, mask=None, **kw):
                      torch.tensor(types, dtype=torch.uint8, device=DEV), quotas,
                      torch.tensor(mask, dtype=torch.int64, device=DEV) if mask is not None else None, **kw)
     torch.cuda.synchronize()
-    return [t.cpu().numpy() for t in r]
+    ext, inte, wr, size, totals = [t.cpu().numpy() for t in r]
+    # the totals per configuration are the sums of the per-trace records and the last cache size
+    if ext.shape[1] > 0:
+        assert np.array_equal(totals, np.stack([ext.sum(1), inte.sum(1), wr.sum(1), size[:, -1]], axis=1))
+    return [ext, inte, wr, size]
 
 
 def test_reference_policy_known_answers():
@@ -115,3 +119,15 @@ def test_empty_and_rejected_inputs():
         _gpu([1], [0, 1], [W], [5], evict_batch=0)
     with pytest.raises(ValueError):
         _gpu([1], [0, 1], [W], [])
+
+
+def test_totals_only_sweep():
+    rng = np.random.default_rng(91)
+    keys, off, types, mask = _workload(rng, 800, True)
+    quotas = [5, 80, 700, 1 << 40]
+    full = _gpu(keys, off, types, quotas, mask, evict_batch=7)
+    r = RunTracesLru(torch.from_numpy(keys).to(DEV), torch.from_numpy(off).to(DEV), torch.from_numpy(types).to(DEV),
+                     quotas, torch.from_numpy(mask).to(DEV), evict_batch=7, per_trace=False)
+    assert r.external_hit_blocks is None and r.current_cache_blocks is None
+    want = np.stack([full[0].sum(1), full[1].sum(1), full[2].sum(1), full[3][:, -1]], axis=1)
+    assert np.array_equal(r.totals.cpu().numpy(), want)

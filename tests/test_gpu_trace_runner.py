@@ -100,6 +100,10 @@ def test_qwen_bailian_file_with_lru_quota_sweep(tmp_path):
         lines = (tmp_path / "out" / ("instance_quota%d_hit_rates.csv" % q)).read_text().splitlines()
         assert len(lines) == 601 and lines[-1].split(", ")[-1] == "%g" % rates[c, 2]
     assert rates[0, 2] < rates[2, 2] <= rates[4, 2]  # a larger cache never hurts this trace
+    # the same curve from the totals-only sweep
+    from tair_kvcache_b200.optimizer import sweep_hit_rates
+    light = sweep_hit_rates(tr.load_traces(str(path), "qwen_bailian"), "cuda:0", quotas, evict_batch=5)
+    assert np.array_equal(light, rates)
     # a single quota gives one record and the plain file name
     rec = run_trace_file(str(path), "qwen_bailian", str(tmp_path / "one"), device="cuda:0", quota_blocks=50,
                          evict_batch=5)["instance"]
