@@ -1406,17 +1406,121 @@ def main_iov_reference(args):
                       "gpu_launches": 0}))
 
 
+def main_hash(args, rank, world):
+    """Chained block hash alone on a batch with many more requests than schedulers (the regime where the integer pipe,
+    not one request's dependent chain, sets the pace): n requests of the same length, uint32 tokens, block 16.
+    Ranks hash different requests (no exchange)."""
+    import torch
+    import torch.distributed as dist
+
+    import tair_kvcache_b200  # noqa: F401
+    from tair_kvcache_b200.manager import GenKeyVectorBatch, key_offsets
+
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    n_req, length, bs = args.n_requests or 65536, args.request_tokens or 20970, 16
+    off = np.arange(n_req + 1, dtype=np.int64) * length
+    gen = torch.Generator(device=device).manual_seed(0xB2000006 + rank)
+    toks = torch.randint(0, 151936, (n_req * length,), dtype=torch.int32, device=device, generator=gen)
+    ko = key_offsets(off, bs)
+    n_keys = int(ko[-1])
+    d_off, d_ko = torch.from_numpy(off).to(device), torch.from_numpy(ko).to(device)
+    d_keys = torch.empty(n_keys, dtype=torch.int64, device=device)
+
+    def step():
+        GenKeyVectorBatch(toks, d_off, bs, d_ko, n_keys, out=d_keys)
+
+    sampler = ClockSampler(str(torch.cuda.get_device_properties(device).uuid)) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    for _ in range(args.warmup):
+        step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    if sampler:
+        sampler.mark_begin()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize(device)
+    if sampler:
+        sampler.mark_end()
+    clocks = sampler.stop() if sampler else None
+    ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    parity = None
+    if rank == 0 and not args.no_cpu:
+        from oracle import kvcm_oracle as oracle
+        m = min(n_req, 64)
+        want, _ = oracle.hash_blocks(toks[:m * length].cpu().numpy().view(np.uint32), off[:m + 1], bs, threads=4)
+        parity = bool(np.array_equal(want, d_keys[:int(ko[m])].cpu().numpy()))
+    if rank == 0:
+        peak, peak_kind = peaks()
+        achieved = (n_req * length * 4 + n_keys * 8) / (ms * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "chained_block_hash_tokens_per_s", "value": world * n_req * length / (ms * 1e-3),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
+            "config": {"workload": "%d requests x %d uint32 tokens per GPU, block %d, %d keys; hash only, tokens "
+                                   "(%.1f GB) far larger than L2" % (n_req, length, bs, n_keys,
+                                                                      n_req * length * 4 / 1e9),
+                       "parity_sample_ok": parity},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_kind": peak_kind,
+                         "note": "the binding resource is the integer pipe (~14 instructions per token)"},
+            "clocks": clocks, "gpu_launches": args.steps}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main_hash_reference(args):
+    """CPU arm of --workload hash: the same chain on a bounded sample of the requests, all host threads."""
+    from oracle import kvcm_oracle as oracle
+    threads = os.cpu_count() or 1
+    n_req_full, length, bs = args.n_requests or 65536, args.request_tokens or 20970, 16
+    n_req = min(n_req_full, 2048)
+    off = np.arange(n_req + 1, dtype=np.int64) * length
+    toks = np.random.default_rng(0xB2000006).integers(0, 151936, size=n_req * length, dtype=np.int64).astype(np.uint32)
+    oracle.hash_blocks(toks, off, bs, threads=threads)
+    t_total, n = 0.0, 0
+    while t_total < 10.0 and n < 200:
+        t0 = time.perf_counter()
+        oracle.hash_blocks(toks, off, bs, threads=threads)
+        t_total += time.perf_counter() - t0
+        n += 1
+    value = n_req * length * n / t_total
+    print(json.dumps({"impl": "reference", "metric": "chained_block_hash_tokens_per_s", "value": value,
+                      "unit": "tokens/s", "n_gpus": args.gpus, "steps": n, "warmup": 1, "higher_is_better": True,
+                      "dtype": "int64", "data": "synthetic",
+                      "config": {"workload": "CPU restatement of GenKeyVector, one request per task"},
+                      "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
+                                       "sample": "%d of %d requests x %d tokens, %d repetitions" % (
+                                           n_req, n_req_full, length, n)},
+                      "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                      "gpu_launches": 0}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c1", "c4", "c5", "lru", "iov"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c1", "c4", "c5", "lru", "iov", "hash"])
     ap.add_argument("--n-requests", type=int, default=0, help="c4: override the number of requests")
     ap.add_argument("--index-keys", type=int, default=0, help="c4: override the number of indexed keys")
     ap.add_argument("--shard-mode", default="peer", choices=["peer", "exchange"],
                     help="c4 on several GPUs: probe remote shards over NVLink, or exchange keys and reduce results")
+    ap.add_argument("--request-tokens", type=int, default=0, help="hash: tokens per request (default 20970)")
     ap.add_argument("--n-configs", type=int, default=0, help="lru: quota points per GPU (default 148)")
     ap.add_argument("--no-prefix", action="store_true", help="skip the prefix-match side measurement")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-staging leg (profiling runs)")
@@ -1436,6 +1540,13 @@ def main():
                 main_replay_reference(args)
             return
         main_replay(args, rank, world)
+        return
+    if args.workload == "hash":
+        if args.impl == "reference":
+            if rank == 0:
+                main_hash_reference(args)
+            return
+        main_hash(args, rank, world)
         return
     if args.workload == "iov":
         if args.impl == "reference":
