@@ -675,7 +675,7 @@ def main_window(args, rank, world):
     order_np, residency = length_order(w["off"], with_residency=True)  # ragged lengths: longest chains first
     d_order = torch.from_numpy(order_np).to(device)
 
-    def step():
+    def step_serial():
         keys = GenKeyVectorBatch(w["toks"], d_off, bs, d_ko, n_keys, out=d_keys, order=d_order, warps_per_sm=residency)
         if world > 1 and args.shard_mode == "peer":  # every key is probed at its owner over NVLink: no collective
             return searcher.PrefixMatch(keys, d_ko), searcher.ReverseRollSlideWindowMatch(keys, d_ko, sw)
@@ -683,6 +683,49 @@ def main_window(args, rank, world):
             g = searcher.Gather(keys, d_ko)  # one exchange of the keys serves both queries
             return searcher.PrefixMatch(g), searcher.ReverseRollSlideWindowMatch(g, sw_size=sw)
         return local_index.PrefixMatch(keys, d_ko), local_index.ReverseRollSlideWindowMatch(keys, d_ko, sw)
+
+    # The step is ruled by the dependent chains of the few longest requests (131k tokens = 2.6 ms), during which
+    # most SMs idle.  So the batch is laid out longest first (a batcher is free to order its requests) and cut in two:
+    # the long head is hashed and matched on one stream while the rest is hashed and matched on another.  Same
+    # kernels, same results per request.
+    overlap = not args.no_overlap and (world == 1 or args.shard_mode == "peer")
+    if overlap:
+        my_len = w["off"][1:] - w["off"][:-1]
+        perm = np.argsort(-my_len, kind="stable")  # sorted position -> request
+        off_s = np.zeros(len(perm) + 1, dtype=np.int64)
+        np.cumsum(my_len[perm], out=off_s[1:])
+        toks_s = torch.empty_like(w["toks"])
+        for pos, j in enumerate(perm):
+            toks_s[int(off_s[pos]):int(off_s[pos + 1])] = w["toks"][int(w["off"][j]):int(w["off"][j + 1])]
+        ko_s = key_offsets(off_s, bs)
+        d_off_s, d_ko_s = torch.from_numpy(off_s).to(device), torch.from_numpy(ko_s).to(device)
+        n_long = int(np.count_nonzero(my_len >= args.long_fraction * my_len.max()))
+        prefix_s = torch.empty(len(perm), dtype=torch.int32, device=device)
+        window_s = torch.empty(len(perm), dtype=torch.int32, device=device)
+        inv = torch.from_numpy(np.argsort(perm)).to(device)  # request -> sorted position
+        streams = [torch.cuda.Stream(device), torch.cuda.Stream(device)]
+        # (first request, end, hashing warps per SM): 4 for the head, so that its chains sit alone on their
+        # schedulers, and 3 for the rest, which then shares an SM with a head warp without crowding its scheduler
+        # (measured: rest at 2 / 3 / 4 / unlimited warps per SM -> 4.12 / 3.98 / 4.29 / 4.25 ms per step)
+        parts = [(0, n_long, 4), (n_long, len(perm), 3)]
+        match = searcher if world > 1 else local_index
+
+    def step_overlapped():
+        main = torch.cuda.current_stream(device)
+        start = torch.cuda.Event()
+        start.record(main)
+        for st, (a, b, cap) in zip(streams, parts):
+            if b <= a:
+                continue
+            st.wait_event(start)
+            with torch.cuda.stream(st):
+                GenKeyVectorBatch(toks_s, d_off_s[a:b + 1], bs, d_ko_s[a:b + 1], n_keys, out=d_keys, warps_per_sm=cap)
+                prefix_s[a:b] = match.PrefixMatch(d_keys, d_ko_s[a:b + 1])
+                window_s[a:b] = match.ReverseRollSlideWindowMatch(d_keys, d_ko_s[a:b + 1], sw)
+            main.wait_stream(st)
+        return prefix_s[inv], window_s[inv]  # back in request order
+
+    step = step_overlapped if overlap else step_serial
 
     for _ in range(args.warmup):
         prefix, window = step()
@@ -781,8 +824,11 @@ def main_window(args, rank, world):
                                                                  ", all-gather of keys + min/max all-reduce")),
                            "token_blocks": int(total_keys), "longest_request_tokens": longest,
                            "requests_with_prefix_hit": int(n_prefix_hits), "requests_with_window": int(n_windows),
-                           "parity_sample_ok": parity, "phase_ms_rank0": phase_ms},
-                "gpu_launches": (3 if world == 1 else 4) * args.steps * world}
+                           "parity_sample_ok": parity, "phase_ms_rank0": phase_ms,
+                           "schedule": ("two streams: the %d longest requests of rank 0 (>= %.2f of the longest) hashed "
+                                        "and matched beside the rest; phase_ms are the kernels run alone on the "
+                                        "whole batch" % (n_long, args.long_fraction)) if overlap else "one stream"},
+                "gpu_launches": (6 if overlap else (3 if world == 1 else 4)) * args.steps * world}
         print(json.dumps(line))
     if world > 1:
         if args.shard_mode == "peer":
@@ -1520,6 +1566,10 @@ def main():
     ap.add_argument("--index-keys", type=int, default=0, help="c4: override the number of indexed keys")
     ap.add_argument("--shard-mode", default="peer", choices=["peer", "exchange"],
                     help="c4 on several GPUs: probe remote shards over NVLink, or exchange keys and reduce results")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="c4: one stream, requests in arrival order (the earlier form of the step)")
+    ap.add_argument("--long-fraction", type=float, default=0.5,
+                    help="c4: requests at least this fraction of the longest form the head that gets its own stream")
     ap.add_argument("--request-tokens", type=int, default=0, help="hash: tokens per request (default 20970)")
     ap.add_argument("--n-configs", type=int, default=0, help="lru: quota points per GPU (default 148)")
     ap.add_argument("--no-prefix", action="store_true", help="skip the prefix-match side measurement")
