@@ -403,7 +403,8 @@ KVCM_API int32_t kvcm_b200_index_detach_peers(kvcm_b200_index_t *index);
  * PrefixQuery / InsertOnly (kv_cache_manager/optimizer/index/radix_tree_index.cc:198-282, 129-196, 19-87)
  * for one instance.  Traces are given in replay order (sorted by timestamp) in CSR form; the order
  * is the trace number.  d_trace_type[t]: 0 DialogTurn (query + insert of total_keys), 1 GetLocation
- * (query; the first d_mask_off[t] keys are masked, d_mask_off may be NULL), 2 WriteCache (insert).
+ * (query; the first d_mask_off[t] keys are masked, d_mask_off may be NULL; d_mask_bits, optional, one byte per
+ * key of the batch, masks single keys on top of that - a BlockMaskVector with holes), 2 WriteCache (insert).
  * Outputs per trace, as the ReadRecord / WriteRecord of the reference hold them: external hit
  * blocks, internal (masked) hit blocks, blocks newly written, and - if d_cache_blocks is not NULL -
  * the number of cached blocks after the trace.  Exact for prefix-unique chained keys (the output of
@@ -414,10 +415,10 @@ KVCM_API int32_t kvcm_b200_index_detach_peers(kvcm_b200_index_t *index);
  * ---------------------------------------------------------------------------------------- */
 KVCM_API int64_t kvcm_b200_replay_workspace_bytes(int64_t n_keys_total);
 KVCM_API int32_t kvcm_b200_replay(const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type,
-                                  const int64_t *d_mask_off, int32_t n_traces, int64_t n_keys_total,
-                                  void *d_workspace, int64_t workspace_bytes, int32_t *d_ext_hit,
-                                  int32_t *d_int_hit, int32_t *d_written, int64_t *d_cache_blocks,
-                                  uint32_t *d_status, kvcm_stream_t stream);
+                                  const int64_t *d_mask_off, const uint8_t *d_mask_bits, int32_t n_traces,
+                                  int64_t n_keys_total, void *d_workspace, int64_t workspace_bytes,
+                                  int32_t *d_ext_hit, int32_t *d_int_hit, int32_t *d_written,
+                                  int64_t *d_cache_blocks, uint32_t *d_status, kvcm_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
  * (2c') Optimizer trace replay with LRU eviction, for a sweep of quotas in one call.
@@ -446,7 +447,8 @@ KVCM_API int32_t kvcm_b200_replay(const int64_t *d_keys, const int64_t *d_key_of
  * ---------------------------------------------------------------------------------------- */
 KVCM_API int64_t kvcm_b200_replay_lru_workspace_bytes(int64_t n_keys_total, int32_t n_configs);
 KVCM_API int32_t kvcm_b200_replay_lru(const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type,
-                                      const int64_t *d_mask_off, int32_t n_traces, int64_t n_keys_total,
+                                      const int64_t *d_mask_off, const uint8_t *d_mask_bits, int32_t n_traces,
+                                      int64_t n_keys_total,
                                       const int64_t *d_quota_blocks, int32_t n_configs, int32_t evict_batch,
                                       int32_t precise, void *d_workspace, int64_t workspace_bytes,
                                       int32_t *d_ext_hit, int32_t *d_int_hit, int32_t *d_written,
@@ -462,7 +464,8 @@ KVCM_API int32_t kvcm_b200_replay_lru(const int64_t *d_keys, const int64_t *d_ke
  * plugin hosts whose rules simply forbid allocator calls on the serving path.  Such a caller owns its
  * inputs and outputs but has nowhere to get the replay's scratch table from.
  *
- * Same arguments, results and kernels as kvcm_b200_replay minus the workspace pair: the scratch table
+ * Same arguments, results and kernels as kvcm_b200_replay minus the workspace pair and the per-key mask
+ * bytes (offset masks only): the scratch table
  * is a fixed array inside the library's device image, KVCM_B200_REPLAY_NOALLOC_SCRATCH_BYTES (8 MiB +
  * 256 B) held by every GPU that loads the library until the process exits.  Limits and rules:
  *   - at most KVCM_B200_REPLAY_NOALLOC_MAX_KEYS keys per call; more returns KVCM_EC_OUT_OF_LIMIT

@@ -505,8 +505,8 @@ void kvcm_oracle_replay_destroy(void *h) { delete static_cast<OracleReplay *>(h)
 // (kv_cache_manager/optimizer/manager/optimizer_runner.cc:70-215): external hit blocks,
 // internal (masked) hit blocks, newly written blocks, and the cache size after the trace.
 void kvcm_oracle_replay_run(void *h, const int64_t *keys, const int64_t *key_off, const uint8_t *type,
-                            const int64_t *mask_off, int64_t n_traces, int32_t *ext_hit, int32_t *int_hit,
-                            int32_t *written, int64_t *cache_blocks) {
+                            const int64_t *mask_off, const uint8_t *mask_bits, int64_t n_traces, int32_t *ext_hit,
+                            int32_t *int_hit, int32_t *written, int64_t *cache_blocks) {
     auto *st = static_cast<OracleReplay *>(h);
     for (int64_t t = 0; t < n_traces; ++t) {
         const int64_t *k = keys + key_off[t];
@@ -518,8 +518,9 @@ void kvcm_oracle_replay_run(void *h, const int64_t *keys, const int64_t *key_off
             // at some unmasked position, else internal when it occurs at a masked one (:137-146,:165-173).
             const int64_t mo = mask_off ? mask_off[t] : 0;
             std::unordered_map<int64_t, int> cls;  // 1 = query key, 2 = mask key only
+            const uint8_t *bits = mask_bits ? mask_bits + key_off[t] : nullptr;  // a BlockMaskVector, one byte per key
             for (int64_t i = 0; i < n; ++i) {
-                if (i < mo) {
+                if (i < mo || (bits && bits[i])) {
                     cls.emplace(k[i], 2);
                 } else {
                     cls[k[i]] = 1;
@@ -687,10 +688,11 @@ struct OracleLruReplay {
         split(child, m, k + m, n - m);
         return wrote + (n - static_cast<int64_t>(m));
     }
-    void prefix_query(const int64_t *k, int64_t n, int64_t mask_off, int32_t *ext, int32_t *inte) {  // :129-196
+    void prefix_query(const int64_t *k, int64_t n, int64_t mask_off, const uint8_t *bits, int32_t *ext,
+                      int32_t *inte) {  // :129-196
         std::unordered_map<int64_t, int> cls;  // 1 = occurs unmasked, 2 = occurs masked only
         for (int64_t i = 0; i < n; ++i) {
-            if (i < mask_off) {
+            if (i < mask_off || (bits && bits[i])) {
                 cls.emplace(k[i], 2);
             } else {
                 cls[k[i]] = 1;
@@ -784,8 +786,8 @@ void kvcm_oracle_lru_replay_destroy(void *h) { delete static_cast<OracleLruRepla
 // Same trace encoding and outputs as kvcm_oracle_replay_run; cache_blocks[t] is the number of cached
 // blocks after trace t (EvictionPolicy::size(), after CheckAndEvict for the writing kinds).
 void kvcm_oracle_lru_replay_run(void *h, const int64_t *keys, const int64_t *key_off, const uint8_t *type,
-                                const int64_t *mask_off, int64_t n_traces, int32_t *ext_hit, int32_t *int_hit,
-                                int32_t *written, int64_t *cache_blocks) {
+                                const int64_t *mask_off, const uint8_t *mask_bits, int64_t n_traces, int32_t *ext_hit,
+                                int32_t *int_hit, int32_t *written, int64_t *cache_blocks) {
     auto *st = static_cast<OracleLruReplay *>(h);
     for (int64_t t = 0; t < n_traces; ++t) {
         const int64_t *k = keys + key_off[t];
@@ -793,7 +795,10 @@ void kvcm_oracle_lru_replay_run(void *h, const int64_t *keys, const int64_t *key
         int32_t ext = 0, inte = 0;
         int64_t wr = 0, hits = 0;
         if (type[t] == 1) {
-            if (n > 0) st->prefix_query(k, n, mask_off ? mask_off[t] : 0, &ext, &inte);
+            if (n > 0) {
+                st->prefix_query(k, n, mask_off ? mask_off[t] : 0, mask_bits ? mask_bits + key_off[t] : nullptr, &ext,
+                                 &inte);
+            }
         } else {
             wr = st->insert(st->root.get(), k, n, type[t] == 0, true, &hits);
             ext = static_cast<int32_t>(hits);

@@ -381,8 +381,9 @@ class Replay:
             lib().kvcm_oracle_replay_destroy(self._h)
             self._h = None
 
-    def run(self, keys, key_off, trace_type, mask_off=None):
-        """Returns (external hits, internal hits, written blocks, cached blocks after) per trace."""
+    def run(self, keys, key_off, trace_type, mask_off=None, mask_bits=None):
+        """Returns (external hits, internal hits, written blocks, cached blocks after) per trace.  mask_off: leading
+        masked keys per GetLocation trace; mask_bits: optional uint8 per key (a BlockMaskVector, holes allowed)."""
         keys, key_off = _i64(keys), _i64(key_off)
         n = len(key_off) - 1
         trace_type = np.ascontiguousarray(trace_type, dtype=np.uint8)
@@ -394,8 +395,12 @@ class Replay:
         inte = np.zeros(n, dtype=np.int32)
         wr = np.zeros(n, dtype=np.int32)
         cached = np.zeros(n, dtype=np.int64)
+        bp = None
+        if mask_bits is not None:
+            mask_bits = np.ascontiguousarray(mask_bits, dtype=np.uint8)
+            bp = _ptr(mask_bits, ctypes.c_uint8)
         lib().kvcm_oracle_replay_run(self._h, _ptr(keys, ctypes.c_int64), _ptr(key_off, ctypes.c_int64),
-                                     _ptr(trace_type, ctypes.c_uint8), mp, ctypes.c_int64(n),
+                                     _ptr(trace_type, ctypes.c_uint8), mp, bp, ctypes.c_int64(n),
                                      _ptr(ext, ctypes.c_int32), _ptr(inte, ctypes.c_int32), _ptr(wr, ctypes.c_int32),
                                      _ptr(cached, ctypes.c_int64))
         return ext, inte, wr, cached
@@ -419,7 +424,7 @@ class LruReplay(Replay):
             lib().kvcm_oracle_lru_replay_destroy(self._h)
             self._h = None
 
-    def run(self, keys, key_off, trace_type, mask_off=None):
+    def run(self, keys, key_off, trace_type, mask_off=None, mask_bits=None):
         keys, key_off = _i64(keys), _i64(key_off)
         n = len(key_off) - 1
         trace_type = np.ascontiguousarray(trace_type, dtype=np.uint8)
@@ -431,8 +436,12 @@ class LruReplay(Replay):
         inte = np.zeros(n, dtype=np.int32)
         wr = np.zeros(n, dtype=np.int32)
         cached = np.zeros(n, dtype=np.int64)
+        bp = None
+        if mask_bits is not None:
+            mask_bits = np.ascontiguousarray(mask_bits, dtype=np.uint8)
+            bp = _ptr(mask_bits, ctypes.c_uint8)
         lib().kvcm_oracle_lru_replay_run(self._h, _ptr(keys, ctypes.c_int64), _ptr(key_off, ctypes.c_int64),
-                                         _ptr(trace_type, ctypes.c_uint8), mp, ctypes.c_int64(n),
+                                         _ptr(trace_type, ctypes.c_uint8), mp, bp, ctypes.c_int64(n),
                                          _ptr(ext, ctypes.c_int32), _ptr(inte, ctypes.c_int32),
                                          _ptr(wr, ctypes.c_int32), _ptr(cached, ctypes.c_int64))
         return ext, inte, wr, cached

@@ -100,10 +100,10 @@ SIGNATURES = {
     "kvcm_b200_index_attach_local_peers": [_vp, _i32, _i32, _vp],
     "kvcm_b200_index_detach_peers": [_vp],
     "kvcm_b200_replay_workspace_bytes": [_i64],
-    "kvcm_b200_replay": [_vp, _vp, _vp, _vp, _i32, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp],
+    "kvcm_b200_replay": [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp],
     "kvcm_b200_replay_lru_workspace_bytes": [_i64, _i32],
-    "kvcm_b200_replay_lru": [_vp, _vp, _vp, _vp, _i32, _i64, _vp, _i32, _i32, _i32, _vp, _i64, _vp, _vp, _vp, _vp, _vp,
-                             _vp, _vp],
+    "kvcm_b200_replay_lru": [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _vp, _i32, _i32, _i32, _vp, _i64, _vp, _vp, _vp, _vp,
+                             _vp, _vp, _vp],
     "kvcm_b200_replay_noalloc": [_vp, _vp, _vp, _vp, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _vp],
 }
 

@@ -87,7 +87,8 @@ __global__ void __launch_bounds__(kWarps * 32)
 
 __global__ void __launch_bounds__(kWarps * 32)
     ReplayCountKernel(ReplayTable t, const int64_t *__restrict__ keys, const int64_t *__restrict__ key_off,
-                      const uint8_t *__restrict__ type, const int64_t *__restrict__ mask_off, int32_t n_traces,
+                      const uint8_t *__restrict__ type, const int64_t *__restrict__ mask_off,
+                      const uint8_t *__restrict__ mask_bits, int32_t n_traces,
                       int32_t *__restrict__ ext_hit, int32_t *__restrict__ int_hit, int32_t *__restrict__ written) {
     const int32_t trace = blockIdx.x * kWarps + (threadIdx.x >> 5);
     if (trace >= n_traces) return;
@@ -109,7 +110,8 @@ __global__ void __launch_bounds__(kWarps * 32)
         const uint32_t in_range = __ballot_sync(0xffffffffu, i < n);
         const uint32_t before = __ballot_sync(0xffffffffu, i < n && first < me);
         const uint32_t mine = __ballot_sync(0xffffffffu, i < n && first == me);
-        const uint32_t masked = __ballot_sync(0xffffffffu, i < skip);
+        const uint32_t masked =
+            __ballot_sync(0xffffffffu, i < skip || (ty == 1 && mask_bits != nullptr && i < n && mask_bits[beg + i] != 0));
         if (ty != 1) wr += __popc(mine);
         if (prefix_alive) {
             const uint32_t miss = in_range & ~before;
@@ -168,7 +170,8 @@ int64_t kvcm_b200_replay_workspace_bytes(int64_t n_keys_total) {
 }
 
 int32_t kvcm_b200_replay(const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type,
-                         const int64_t *d_mask_off, int32_t n_traces, int64_t n_keys_total, void *d_workspace,
+                         const int64_t *d_mask_off, const uint8_t *d_mask_bits, int32_t n_traces,
+                         int64_t n_keys_total, void *d_workspace,
                          int64_t workspace_bytes, int32_t *d_ext_hit, int32_t *d_int_hit, int32_t *d_written,
                          int64_t *d_cache_blocks, uint32_t *d_status, kvcm_stream_t stream) {
     if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
@@ -191,7 +194,7 @@ int32_t kvcm_b200_replay(const int64_t *d_keys, const int64_t *d_key_off, const 
     kvcm::ReplayFirstWriterKernel<<<grid, kvcm::kWarps * 32, 0, s>>>(t, d_keys, d_key_off, d_trace_type, n_traces,
                                                                      d_status);
     kvcm::ReplayCountKernel<<<grid, kvcm::kWarps * 32, 0, s>>>(t, d_keys, d_key_off, d_trace_type, d_mask_off,
-                                                               n_traces, d_ext_hit, d_int_hit, d_written);
+                                                               d_mask_bits, n_traces, d_ext_hit, d_int_hit, d_written);
     if (d_cache_blocks != nullptr) {
         kvcm::ReplayRunningSizeKernel<<<1, 1024, 0, s>>>(d_written, n_traces, 0, d_cache_blocks);
     }
@@ -235,7 +238,7 @@ int32_t kvcm_b200_replay_noalloc(const int64_t *d_keys, const int64_t *d_key_off
     }
     // The table is rebuilt from its first slot by every call (the init kernel covers every slot
     // the call uses), so what an earlier call left behind is never read.
-    return kvcm_b200_replay(d_keys, d_key_off, d_trace_type, d_mask_off, n_traces, n_keys_total, scratch,
+    return kvcm_b200_replay(d_keys, d_key_off, d_trace_type, d_mask_off, nullptr, n_traces, n_keys_total, scratch,
                             KVCM_B200_REPLAY_NOALLOC_SCRATCH_BYTES, d_ext_hit, d_int_hit, d_written, d_cache_blocks,
                             d_status, stream);
 }

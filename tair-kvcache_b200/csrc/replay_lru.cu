@@ -123,6 +123,7 @@ struct LruSweep {
     const int64_t *key_off;
     const uint8_t *type;
     const int64_t *mask_off;
+    const uint8_t *mask_bits;  // optional, per key: 1 = masked (a BlockMaskVector), on top of mask_off
     const int64_t *quota;
     uint32_t *stamps;  // [n_configs][n_keys]
     uint2 *queue;      // [n_configs][n_keys]
@@ -186,7 +187,8 @@ __global__ void __launch_bounds__(32) LruSweepKernel(const LruSweep p) {
             uint32_t touch = 0;  // leading cached blocks: hits, moved to the front in order
             if (alive) {
                 touch = miss != 0 ? cached & ((1u << (__ffs(miss) - 1)) - 1u) : cached;
-                const uint32_t masked = __ballot_sync(0xffffffffu, i < skip);
+                const uint32_t masked = __ballot_sync(
+                    0xffffffffu, i < skip || (ty == 1 && p.mask_bits != nullptr && have && p.mask_bits[beg + i] != 0));
                 ext += __popc(touch & ~masked);
                 inte += __popc(touch & masked);
                 if (miss != 0) alive = false;
@@ -312,9 +314,9 @@ int64_t kvcm_b200_replay_lru_workspace_bytes(int64_t n_keys_total, int32_t n_con
 }
 
 int32_t kvcm_b200_replay_lru(const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type,
-                             const int64_t *d_mask_off, int32_t n_traces, int64_t n_keys_total,
-                             const int64_t *d_quota_blocks, int32_t n_configs, int32_t evict_batch, int32_t precise,
-                             void *d_workspace, int64_t workspace_bytes, int32_t *d_ext_hit, int32_t *d_int_hit,
+                             const int64_t *d_mask_off, const uint8_t *d_mask_bits, int32_t n_traces,
+                             int64_t n_keys_total, const int64_t *d_quota_blocks, int32_t n_configs, int32_t evict_batch,
+                             int32_t precise, void *d_workspace, int64_t workspace_bytes, int32_t *d_ext_hit, int32_t *d_int_hit,
                              int32_t *d_written, int64_t *d_cache_blocks, int64_t *d_totals, uint32_t *d_status,
                              kvcm_stream_t stream) {
     if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
@@ -352,6 +354,7 @@ int32_t kvcm_b200_replay_lru(const int64_t *d_keys, const int64_t *d_key_off, co
     p.key_off = d_key_off;
     p.type = d_trace_type;
     p.mask_off = d_mask_off;
+    p.mask_bits = d_mask_bits;
     p.quota = d_quota_blocks;
     p.stamps = stamps;
     p.queue = reinterpret_cast<uint2 *>(ws + l.queue_off);

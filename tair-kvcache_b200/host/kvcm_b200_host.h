@@ -380,8 +380,8 @@ public:
         const int64_t ws_bytes = kvcm_b200_replay_workspace_bytes(n_keys);
         if (ws_bytes < 0) return KVCM_EC_BADARGS;
         if (!Outputs(n, 1) || !workspace_.Reserve(static_cast<size_t>(ws_bytes), true)) return KVCM_EC_NOSPC;
-        rc = kvcm_b200_replay(keys_.dev<int64_t>(), off_.dev<int64_t>(), kind_.dev<uint8_t>(), mask_.dev<int64_t>(), n,
-                              n_keys, workspace_.dev<void>(), ws_bytes, ext_.dev<int32_t>(), int_.dev<int32_t>(),
+        rc = kvcm_b200_replay(keys_.dev<int64_t>(), off_.dev<int64_t>(), kind_.dev<uint8_t>(), mask_.dev<int64_t>(),
+                              nullptr, n, n_keys, workspace_.dev<void>(), ws_bytes, ext_.dev<int32_t>(), int_.dev<int32_t>(),
                               wr_.dev<int32_t>(), size_.dev<int64_t>(), nullptr, stream_);
         if (rc != KVCM_OK) return rc;
         rc = Fetch(static_cast<size_t>(n));
@@ -413,7 +413,7 @@ public:
         std::memcpy(quota_.host<int64_t>(), quota_blocks.data(), sizeof(int64_t) * n_cfg);
         if (!quota_.ToDevice(sizeof(int64_t) * n_cfg, stream_)) return KVCM_ER_CUDAMEMCPY_ERROR;
         rc = kvcm_b200_replay_lru(keys_.dev<int64_t>(), off_.dev<int64_t>(), kind_.dev<uint8_t>(),
-                                  mask_.dev<int64_t>(), n, n_keys, quota_.dev<int64_t>(), n_cfg, evict_batch,
+                                  mask_.dev<int64_t>(), nullptr, n, n_keys, quota_.dev<int64_t>(), n_cfg, evict_batch,
                                   precise ? 1 : 0, workspace_.dev<void>(), ws_bytes, ext_.dev<int32_t>(),
                                   int_.dev<int32_t>(), wr_.dev<int32_t>(), size_.dev<int64_t>(), nullptr, nullptr,
                                   stream_);

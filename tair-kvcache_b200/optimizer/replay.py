@@ -28,11 +28,20 @@ def replay_workspace_bytes(n_keys_total: int) -> int:
     return n
 
 
+def _mask_bits_ptr(mask_bits: Optional[torch.Tensor], keys: torch.Tensor):
+    if mask_bits is None:
+        return None
+    if mask_bits.dtype != torch.uint8 or mask_bits.numel() != keys.numel() or mask_bits.device != keys.device:
+        raise ValueError("mask_bits must be a uint8 tensor with one entry per key, on the keys' device")
+    return mask_bits.contiguous().data_ptr()
+
+
 def RunTraces(keys: torch.Tensor, key_off: torch.Tensor, trace_type: torch.Tensor,
               mask_off: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None,
-              status: Optional[torch.Tensor] = None) -> ReplayResult:
+              status: Optional[torch.Tensor] = None, mask_bits: Optional[torch.Tensor] = None) -> ReplayResult:
     """keys: int64 CUDA tensor of chained block keys, CSR by key_off (int64, n_traces + 1), traces in replay
-    (timestamp) order; trace_type: uint8 per trace (TRACE_*); mask_off: int64 per trace for GetLocation traces.
+    (timestamp) order; trace_type: uint8 per trace (TRACE_*); mask_off: int64 per trace for GetLocation traces
+    (BlockMaskOffset); mask_bits: optional uint8 per key, 1 = masked (a BlockMaskVector, holes allowed).
     workspace: optional uint8 CUDA tensor of replay_workspace_bytes(keys.numel()) bytes to reuse across calls."""
     if not keys.is_cuda:
         raise ValueError("keys must be a CUDA tensor: this path has no CPU implementation")
@@ -50,8 +59,9 @@ def RunTraces(keys: torch.Tensor, key_off: torch.Tensor, trace_type: torch.Tenso
     size = torch.empty(max(n_traces, 1), dtype=torch.int64, device=dev)
     _cabi.bind_device(dev.index)
     _cabi.call("kvcm_b200_replay", keys.data_ptr(), key_off.data_ptr(), trace_type.data_ptr(),
-               mask_off.contiguous().data_ptr() if mask_off is not None else None, n_traces, keys.numel(),
-               workspace.data_ptr(), workspace.numel(), ext.data_ptr(), inte.data_ptr(), wr.data_ptr(),
+               mask_off.contiguous().data_ptr() if mask_off is not None else None, _mask_bits_ptr(mask_bits, keys),
+               n_traces, keys.numel(), workspace.data_ptr(), workspace.numel(), ext.data_ptr(), inte.data_ptr(),
+               wr.data_ptr(),
                size.data_ptr(), status.data_ptr() if status is not None else None,
                torch.cuda.current_stream(dev).cuda_stream)
     return ReplayResult(ext[:n_traces], inte[:n_traces], wr[:n_traces], size[:n_traces])
@@ -75,7 +85,7 @@ def replay_lru_workspace_bytes(n_keys_total: int, n_configs: int) -> int:
 def RunTracesLru(keys: torch.Tensor, key_off: torch.Tensor, trace_type: torch.Tensor, quota_blocks,
                  mask_off: Optional[torch.Tensor] = None, evict_batch: int = 100, precise: bool = False,
                  workspace: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
-                 per_trace: bool = True) -> LruSweepResult:
+                 per_trace: bool = True, mask_bits: Optional[torch.Tensor] = None) -> LruSweepResult:
     """The replay of RunTraces with the reference's "lru" eviction policy, once per entry of quota_blocks (the
     points of a tradeoff curve: quota_capacity * used_percentage in blocks), all configurations in one launch.
     evict_batch / precise: eviction_batch_size_per_instance and the eviction mode (False = the rough modes, which
@@ -106,8 +116,8 @@ def RunTracesLru(keys: torch.Tensor, key_off: torch.Tensor, trace_type: torch.Te
         return LruSweepResult(ext, inte, wr, size, totals)
     _cabi.bind_device(dev.index)
     _cabi.call("kvcm_b200_replay_lru", keys.data_ptr(), key_off.data_ptr(), trace_type.data_ptr(),
-               mask_off.contiguous().data_ptr() if mask_off is not None else None, n_traces, keys.numel(),
-               quota.data_ptr(), n_cfg, int(evict_batch), 1 if precise else 0, workspace.data_ptr(),
+               mask_off.contiguous().data_ptr() if mask_off is not None else None, _mask_bits_ptr(mask_bits, keys),
+               n_traces, keys.numel(), quota.data_ptr(), n_cfg, int(evict_batch), 1 if precise else 0, workspace.data_ptr(),
                workspace.numel(), ptr(ext), ptr(inte), ptr(wr), ptr(size), totals.data_ptr(),
                status.data_ptr() if status is not None else None, torch.cuda.current_stream(dev).cuda_stream)
     return LruSweepResult(ext, inte, wr, size, totals)

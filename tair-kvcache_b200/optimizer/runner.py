@@ -39,8 +39,11 @@ def replay_instance(traces: List[tr.Trace], device, rw_separation: bool = False,
     if any(t.needs_prefix_hash for t in keep):  # Qwen-Bailian ids: chain them first
         d_keys = ApplyPrefixHashBatch(d_keys, d_off)
     ts = np.array([t.timestamp_us for t in keep], dtype=np.int64)
+    bits = tr.mask_bits(keep, off)
+    d_bits = torch.from_numpy(bits).to(device) if bits is not None else None
     # GetLocation: masked keys are internal reads; a dialog turn reads its query keys externally and replays total_keys
-    internal_read = np.where(kind == tr.GET_LOCATION, mask, 0)
+    internal_read = np.array([tr.masked_count(t.block_mask, len(t.keys)) if t.kind == tr.GET_LOCATION else 0
+                              for t in keep], dtype=np.int64)
     external_read = np.where(kind == tr.WRITE_CACHE, 0, read - internal_read)
 
     def record(ext, inte, wr, size):
@@ -50,9 +53,10 @@ def replay_instance(traces: List[tr.Trace], device, rw_separation: bool = False,
 
     d_kind, d_mask = torch.from_numpy(kind).to(device), torch.from_numpy(mask).to(device)
     if quota_blocks is None:
-        return record(*(x.cpu().numpy() for x in RunTraces(d_keys, d_off, d_kind, d_mask)))
+        return record(*(x.cpu().numpy() for x in RunTraces(d_keys, d_off, d_kind, d_mask, mask_bits=d_bits)))
     quotas = [int(quota_blocks)] if np.isscalar(quota_blocks) else [int(q) for q in quota_blocks]
-    res = [x.cpu().numpy() for x in RunTracesLru(d_keys, d_off, d_kind, quotas, d_mask, evict_batch, precise)[:4]]
+    res = [x.cpu().numpy() for x in RunTracesLru(d_keys, d_off, d_kind, quotas, d_mask, evict_batch, precise,
+                                                 mask_bits=d_bits)[:4]]
     recs = [record(*(x[c] for x in res)) for c in range(len(quotas))]
     return recs[0] if np.isscalar(quota_blocks) else recs
 
@@ -78,8 +82,10 @@ def sweep_hit_rates(traces: List[tr.Trace], device, quota_blocks: Sequence[int],
     d_keys, d_off = torch.from_numpy(keys).to(device), torch.from_numpy(off).to(device)
     if any(t.needs_prefix_hash for t in keep):
         d_keys = ApplyPrefixHashBatch(d_keys, d_off)
+    bits = tr.mask_bits(keep, off)
     res = RunTracesLru(d_keys, d_off, torch.from_numpy(kind).to(device), [int(q) for q in quota_blocks],
-                       torch.from_numpy(mask).to(device), evict_batch, precise, per_trace=False)
+                       torch.from_numpy(mask).to(device), evict_batch, precise, per_trace=False,
+                       mask_bits=torch.from_numpy(bits).to(device) if bits is not None else None)
     totals = res.totals.cpu().numpy()
     total_read = int(read[kind != tr.WRITE_CACHE].sum())
     out = np.zeros((totals.shape[0], 3))

@@ -172,8 +172,8 @@ def load_traces(path: str, trace_type: str, block_sizes: Optional[Dict[str, int]
 
 
 def mask_offset(mask: BlockMask, n_keys: int) -> int:
-    """A block mask as the number of leading masked keys.  Vector masks that are not a run of leading `true`s
-    cannot be expressed that way and are refused (the replay entry point takes offsets)."""
+    """The leading masked keys of a block mask: the offset itself, or the run of leading `true`s of a vector
+    (kv_cache_manager/manager/cache_location.cc:9-21).  What a vector masks beyond that run is in mask_bits()."""
     if mask is None:
         return 0
     if isinstance(mask, int):
@@ -182,9 +182,33 @@ def mask_offset(mask: BlockMask, n_keys: int) -> int:
     lead = 0
     while lead < len(m) and m[lead]:
         lead += 1
-    if any(m[lead:]):
-        raise ValueError("block mask vector with holes: only leading masks can be replayed on the GPU")
     return lead
+
+
+def mask_bits(traces: Sequence[Trace], key_off: np.ndarray) -> Optional[np.ndarray]:
+    """uint8 per key of the CSR batch, 1 where a GetLocation trace's vector mask masks a key behind its leading
+    run (a mask with holes); None when no trace has such a mask, which is the usual case."""
+    bits = None
+    for i, t in enumerate(traces):
+        if t.kind != GET_LOCATION or t.block_mask is None or isinstance(t.block_mask, int):
+            continue
+        m = [bool(x) for x in list(t.block_mask)[:len(t.keys)]]
+        lead = mask_offset(t.block_mask, len(t.keys))
+        if any(m[lead:]):
+            if bits is None:
+                bits = np.zeros(int(key_off[-1]), dtype=np.uint8)
+            bits[int(key_off[i]):int(key_off[i]) + len(m)] = m
+    return bits
+
+
+def masked_count(mask: BlockMask, n_keys: int) -> int:
+    """Keys a mask covers: what HandleGetLocation records as internal_read_blocks
+    (kv_cache_manager/optimizer/manager/optimizer_runner.cc:97-103)."""
+    if mask is None:
+        return 0
+    if isinstance(mask, int):
+        return min(mask, n_keys)
+    return int(sum(1 for x in list(mask)[:n_keys] if x))
 
 
 def to_csr(traces: Sequence[Trace]):

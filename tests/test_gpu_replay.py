@@ -82,3 +82,22 @@ def test_workspace_reuse_and_size_check():
 def test_empty_traces():
     ext, inte, wr, size = _gpu([], [0, 0, 0], [TRACE_DIALOG_TURN, TRACE_GET_LOCATION])
     assert ext.tolist() == [0, 0] and wr.tolist() == [0, 0] and size.tolist() == [0, 0]
+
+
+def test_vector_masks_with_holes():
+    """A BlockMaskVector may mask any keys, not only a leading run (kv_cache_manager/manager/cache_location.cc:9-21):
+    hits are still the leading cached keys, each counted as internal when its own bit is set."""
+    rng = np.random.default_rng(31)
+    keys, off, types, mask = _workload(rng, 1500, True)
+    bits = (rng.random(len(keys)) < 0.3).astype(np.uint8)
+    got = RunTraces(torch.from_numpy(keys).to(DEV), torch.from_numpy(off).to(DEV), torch.from_numpy(types).to(DEV),
+                    torch.from_numpy(mask).to(DEV), mask_bits=torch.from_numpy(bits).to(DEV))
+    want = oracle.Replay().run(keys, off, types, mask, mask_bits=bits)
+    for a, b in zip(want, got):
+        assert np.array_equal(a, b.cpu().numpy())
+    plain = oracle.Replay().run(keys, off, types, mask)
+    assert not np.array_equal(plain[1], want[1]) and np.array_equal(plain[0] + plain[1], want[0] + want[1])
+    # hand-made: write 1..4, then a query of 1..4 with keys 2 and 4 masked
+    ext, inte, wr, size = _gpu([1, 2, 3, 4, 1, 2, 3, 4], [0, 4, 8], [TRACE_WRITE_CACHE, TRACE_GET_LOCATION], [0, 0],
+                               mask_bits=torch.tensor([0, 0, 0, 0, 0, 1, 0, 1], dtype=torch.uint8, device=DEV))
+    assert ext.tolist() == [0, 2] and inte.tolist() == [0, 2]

@@ -131,3 +131,15 @@ def test_totals_only_sweep():
     assert r.external_hit_blocks is None and r.current_cache_blocks is None
     want = np.stack([full[0].sum(1), full[1].sum(1), full[2].sum(1), full[3][:, -1]], axis=1)
     assert np.array_equal(r.totals.cpu().numpy(), want)
+
+
+def test_vector_masks_with_holes_under_eviction():
+    rng = np.random.default_rng(92)
+    keys, off, types, mask = _workload(rng, 1200, True)
+    bits = (rng.random(len(keys)) < 0.25).astype(np.uint8)
+    quotas = [20, 300, 1 << 40]
+    got = _gpu(keys, off, types, quotas, mask, evict_batch=9, mask_bits=torch.from_numpy(bits).to(DEV))
+    for c, q in enumerate(quotas):
+        want = oracle.LruReplay(q, evict_batch=9).run(keys, off, types, mask, mask_bits=bits)
+        for a, b in zip(want, got):
+            assert np.array_equal(a, b[c]), q

@@ -146,3 +146,18 @@ def test_startup_config_drives_a_publisher_log_replay_with_eviction(tmp_path):
     want = oracle.LruReplay(4, evict_batch=2).run(keys, off, rec["kind"], [0, 0, 0, 0, 1])
     assert np.array_equal(want[0], rec["external_hit_blocks"]) and np.array_equal(want[3], rec["current_cache_blocks"])
     assert len((tmp_path / "out" / "i1_hit_rates.csv").read_text().splitlines()) == 4
+
+
+def test_optimizer_schema_query_with_a_holey_vector_mask(tmp_path):
+    """GetLocation traces of the optimizer schema carry block_mask as an offset or as a bool vector; a vector with
+    holes reaches the GPU as one byte per key."""
+    path = tmp_path / "schema.jsonl"
+    path.write_text("\n".join([
+        json.dumps({"instance_id": "i", "trace_id": "w", "timestamp_us": 1, "tokens": [], "keys": [1, 2, 3, 4]}),
+        json.dumps({"instance_id": "i", "trace_id": "g", "timestamp_us": 2, "tokens": [], "keys": [1, 2, 3, 4, 5],
+                    "query_type": "prefix_match", "block_mask": [False, True, False, True, True], "sw_size": 0,
+                    "location_spec_names": []})]))
+    rec = run_trace_file(str(path), "optimizer_schema", str(tmp_path / "out"), device="cuda:0", rw_separation=True)["i"]
+    assert rec["kind"].tolist() == [tr.WRITE_CACHE, tr.GET_LOCATION]
+    assert rec["external_hit_blocks"].tolist() == [0, 2] and rec["internal_hit_blocks"].tolist() == [0, 2]
+    assert rec["internal_read_blocks"].tolist() == [0, 3] and rec["external_read_blocks"].tolist() == [0, 2]

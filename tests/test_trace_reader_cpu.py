@@ -75,8 +75,15 @@ def test_load_traces_sorts_by_timestamp_and_csr_layout(tmp_path):
 def test_mask_offset_rules():
     assert tr.mask_offset(None, 5) == 0 and tr.mask_offset(3, 5) == 3 and tr.mask_offset(9, 5) == 5
     assert tr.mask_offset([True, True, False], 3) == 2 and tr.mask_offset([], 3) == 0
-    with pytest.raises(ValueError):
-        tr.mask_offset([True, False, True], 3)
+    # a vector with holes: the leading run is the offset, the rest travels as one byte per key
+    assert tr.mask_offset([True, False, True], 3) == 1 and tr.masked_count([True, False, True], 3) == 2
+    traces = [tr.Trace(kind=tr.GET_LOCATION, keys=[1, 2, 3], block_mask=[True, False, True]),
+              tr.Trace(kind=tr.WRITE_CACHE, keys=[4, 5]),
+              tr.Trace(kind=tr.GET_LOCATION, keys=[6, 7], block_mask=[True, True])]
+    keys, off, kind, mask, read = tr.to_csr(traces)
+    assert mask.tolist() == [1, 0, 2]
+    assert tr.mask_bits(traces, off).tolist() == [1, 0, 1, 0, 0, 0, 0]
+    assert tr.mask_bits(traces[1:], tr.to_csr(traces[1:])[1]) is None  # no holes: nothing to pass
 
 
 def test_startup_config_of_the_reference_is_understood():

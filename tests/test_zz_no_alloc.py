@@ -50,7 +50,7 @@ def _run_both(seed, n_traces):
     # existing entry point, scratch owned by the caller
     ws = torch.empty(_cabi.lib().kvcm_b200_replay_workspace_bytes(len(keys)), dtype=torch.uint8, device=DEV)
     want = _outputs(n_traces)
-    _cabi.call("kvcm_b200_replay", d[0].data_ptr(), d[1].data_ptr(), d[2].data_ptr(), d[3].data_ptr(), n_traces,
+    _cabi.call("kvcm_b200_replay", d[0].data_ptr(), d[1].data_ptr(), d[2].data_ptr(), d[3].data_ptr(), None, n_traces,
                len(keys), ws.data_ptr(), ws.numel(), want[0].data_ptr(), want[1].data_ptr(), want[2].data_ptr(),
                want[3].data_ptr(), None, stream)
     # new entry point, nothing allocated by the library
