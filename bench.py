@@ -37,6 +37,8 @@ UNIT = "GB/s"
 # profiles/move_rows_bulk_llama8b_reduced_ncu_full.md (4.2505 GB per 4.2950 GB launch); traffic grows in
 # proportion to the blocks moved, so the full-size figure is this ratio times the launch's algorithmic bytes.
 DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = (2.147519 + 2.102969) / 4.294967296
+# the same ratio for the bulk segment copy (profiles/copy_segments_bulk_256_blocks_ncu_full.md)
+IOV_DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = (2.148165 + 2.106079) / 4.294967296
 
 WORKLOADS = {
     # name: layers, kv pools per layer, page tokens, bytes per token per pool, pages per pool, blocks, pages per block
@@ -1406,8 +1408,10 @@ def main_iov(args, rank, world):
                        "put_ms": put_ms, "get_ms": get_ms, "parity_sample_ok": ok,
                        "memcpy_async_per_iov_GBps": loop_gbs, "memcpy_async_calls": loop_calls,
                        "memcpy_async_us_per_call": loop_us},
-            "roofline": {"bound": "hbm", "achieved": kern, "peak": peak, "unit": UNIT, "frac": kern / peak,
-                         "traffic": None, "peak_kind": peak_kind},
+            "roofline": {"bound": "hbm", "kernel": "CopySegmentsBulkKernel", "achieved": kern, "peak": peak, "unit": UNIT,
+                         "frac": kern / peak, "traffic": int(2 * payload * IOV_DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE),
+                         "traffic_source": "ncu capture on 256 blocks scaled by blocks moved",
+                         "algorithmic_bytes_per_launch": 2 * payload, "peak_kind": peak_kind},
             "clocks": clocks, "gpu_launches": 2 * args.steps}
     if e2e:
         line["e2e"] = e2e
