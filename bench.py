@@ -681,6 +681,9 @@ def main_window(args, rank, world):
         keys = GenKeyVectorBatch(w["toks"], d_off, bs, d_ko, n_keys, out=d_keys, order=d_order, warps_per_sm=residency)
         if world > 1 and args.shard_mode == "peer":  # every key is probed at its owner over NVLink: no collective
             return searcher.PrefixMatch(keys, d_ko), searcher.ReverseRollSlideWindowMatch(keys, d_ko, sw)
+        if world > 1 and args.shard_mode == "route":  # keys to their owners, one flag byte back, both queries local
+            r = searcher.Route(keys, d_ko)
+            return searcher.PrefixMatch(r), searcher.ReverseRollSlideWindowMatch(r, sw_size=sw)
         if world > 1:
             g = searcher.Gather(keys, d_ko)  # one exchange of the keys serves both queries
             return searcher.PrefixMatch(g), searcher.ReverseRollSlideWindowMatch(g, sw_size=sw)
@@ -690,7 +693,7 @@ def main_window(args, rank, world):
     # most SMs idle.  So the batch is laid out longest first (a batcher is free to order its requests) and cut in two:
     # the long head is hashed and matched on one stream while the rest is hashed and matched on another.  Same
     # kernels, same results per request.
-    overlap = not args.no_overlap and (world == 1 or args.shard_mode == "peer")
+    overlap = not args.no_overlap and (world == 1 or args.shard_mode in ("peer", "route"))
     if overlap:
         my_len = w["off"][1:] - w["off"][:-1]
         perm = np.argsort(-my_len, kind="stable")  # sorted position -> request
@@ -711,6 +714,39 @@ def main_window(args, rank, world):
         # (measured: rest at 2 / 3 / 4 / unlimited warps per SM -> 4.12 / 3.98 / 4.29 / 4.25 ms per step)
         parts = [(0, n_long, 4), (n_long, len(perm), 3)]
         match = searcher if world > 1 else local_index
+        # the keys of a part as a batch of its own (routing sends whole batches)
+        rel_ko = [(d_ko_s[a:b + 1] - int(ko_s[a])).contiguous() for a, b, _ in parts]
+
+    def step_overlapped_routed(marks=None):
+        """Both parts are hashed at once; the short requests are routed and matched while the long chains still
+        run, then the long ones.  Every rank issues the collectives in the same order (rest, then head), parts
+        without requests included."""
+        def mark(label, stream):
+            if marks is not None:
+                marks.append((label, torch.cuda.Event(enable_timing=True)))
+                marks[-1][1].record(stream)
+
+        main = torch.cuda.current_stream(device)
+        start = torch.cuda.Event()
+        start.record(main)
+        mark("start", main)
+        for name, st, (a, b, cap) in zip(("head", "rest"), streams, parts):
+            st.wait_event(start)
+            if b > a:
+                with torch.cuda.stream(st):
+                    GenKeyVectorBatch(toks_s, d_off_s[a:b + 1], bs, d_ko_s[a:b + 1], n_keys, out=d_keys,
+                                      warps_per_sm=cap)
+            mark(name + "_hashed", st)
+        for which in (1, 0):
+            a, b, _ = parts[which]
+            with torch.cuda.stream(streams[which]):
+                r = searcher.Route(d_keys[int(ko_s[a]):int(ko_s[b])], rel_ko[which])
+                mark(("head", "rest")[which] + "_routed", streams[which])
+                prefix_s[a:b] = searcher.PrefixMatch(r)
+                window_s[a:b] = searcher.ReverseRollSlideWindowMatch(r, sw_size=sw)
+                mark(("head", "rest")[which] + "_matched", streams[which])
+            main.wait_stream(streams[which])
+        return prefix_s[inv], window_s[inv]
 
     def step_overlapped():
         main = torch.cuda.current_stream(device)
@@ -727,7 +763,9 @@ def main_window(args, rank, world):
             main.wait_stream(st)
         return prefix_s[inv], window_s[inv]  # back in request order
 
-    step = step_overlapped if overlap else step_serial
+    step = step_serial
+    if overlap:
+        step = step_overlapped_routed if world > 1 and args.shard_mode == "route" else step_overlapped
 
     for _ in range(args.warmup):
         prefix, window = step()
@@ -748,7 +786,12 @@ def main_window(args, rank, world):
     ev[0].record()
     keys = GenKeyVectorBatch(w["toks"], d_off, bs, d_ko, n_keys, out=d_keys, order=d_order, warps_per_sm=residency)
     ev[1].record()
-    if world > 1:
+    if world > 1 and args.shard_mode == "route":
+        routed = searcher.Route(keys, d_ko)
+        ev[2].record()
+        searcher.PrefixMatch(routed)
+        searcher.ReverseRollSlideWindowMatch(routed, sw_size=sw)
+    elif world > 1:
         searcher.PrefixMatch(keys, d_ko)
         ev[2].record()
         searcher.ReverseRollSlideWindowMatch(keys, d_ko, sw)
@@ -760,6 +803,15 @@ def main_window(args, rank, world):
     torch.cuda.synchronize(device)
     phase_ms = {"hash": ev[0].elapsed_time(ev[1]), "prefix_match": ev[1].elapsed_time(ev[2]),
                 "window_match": ev[2].elapsed_time(ev[3])}
+    if step is step_overlapped_routed:  # when each part of the two-stream step finished, from the step's start
+        marks = []
+        step(marks)
+        torch.cuda.synchronize(device)
+        phase_ms["two_stream_timeline"] = {k: round(marks[0][1].elapsed_time(e), 3) for k, e in marks[1:]}
+    if world > 1 and args.shard_mode == "route":
+        phase_ms = {"hash": phase_ms["hash"], "dispatch_lookup_combine": phase_ms["prefix_match"],
+                    "prefix_and_window_from_flags": phase_ms["window_match"],
+                    **{k: v for k, v in phase_ms.items() if k == "two_stream_timeline"}}
     if world == 1:
         # the other index operators on the same keys, outside the timed step: BatchGet (one flag byte per key),
         # FilterWriteCache (what StartWriteCache asks before a write) and the write side (upsert of fresh keys into
@@ -821,16 +873,21 @@ def main_window(args, rank, world):
                                        "sharing over 1000 roots, window 256 blocks, index of %d keys split by hash "
                                        "range over %d GPU(s)%s; hash + prefix match + sliding-window match per step"
                                        % (n_req_total, int(total_stored), world,
-                                          "" if world == 1 else (", shards probed over NVLink peer loads"
-                                                                 if args.shard_mode == "peer" else
-                                                                 ", all-gather of keys + min/max all-reduce")),
+                                          "" if world == 1 else {
+                                              "peer": ", shards probed over NVLink peer loads",
+                                              "route": ", keys sent to their owners and one flag byte back "
+                                                       "(two all-to-alls per step)",
+                                              "exchange": ", all-gather of keys + min/max all-reduce",
+                                          }[args.shard_mode]),
                            "token_blocks": int(total_keys), "longest_request_tokens": longest,
                            "requests_with_prefix_hit": int(n_prefix_hits), "requests_with_window": int(n_windows),
                            "parity_sample_ok": parity, "phase_ms_rank0": phase_ms,
                            "schedule": ("two streams: the %d longest requests of rank 0 (>= %.2f of the longest) hashed "
                                         "and matched beside the rest; phase_ms are the kernels run alone on the "
                                         "whole batch" % (n_long, args.long_fraction)) if overlap else "one stream"},
-                "gpu_launches": (6 if overlap else (3 if world == 1 else 4)) * args.steps * world}
+                "gpu_launches": ({"peer": 6, "route": 14}[args.shard_mode] if overlap and world > 1 else
+                                 6 if overlap else 3 if world == 1 else 7 if args.shard_mode == "route" else 4)
+                * args.steps * world}
         print(json.dumps(line))
     if world > 1:
         if args.shard_mode == "peer":
@@ -1568,7 +1625,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c1", "c4", "c5", "lru", "iov", "hash"])
     ap.add_argument("--n-requests", type=int, default=0, help="c4: override the number of requests")
     ap.add_argument("--index-keys", type=int, default=0, help="c4: override the number of indexed keys")
-    ap.add_argument("--shard-mode", default="peer", choices=["peer", "exchange"],
+    ap.add_argument("--shard-mode", default="peer", choices=["peer", "exchange", "route"],
                     help="c4 on several GPUs: probe remote shards over NVLink, or exchange keys and reduce results")
     ap.add_argument("--no-overlap", action="store_true",
                     help="c4: one stream, requests in arrival order (the earlier form of the step)")

@@ -372,6 +372,28 @@ KVCM_API int32_t kvcm_b200_batch_get_sharded(kvcm_b200_index_t *index, const int
 KVCM_API int32_t kvcm_b200_match_sw_from_flags(const uint8_t *d_flags, const int64_t *d_key_off, int32_t n_req,
                                                int32_t sw_blocks, int32_t *d_base_out, kvcm_stream_t stream);
 
+/* Routed exchange: the device-side halves of an all-to-all that sends every key to the shard that owns it and
+ * brings one answer byte back (the transport in between is the caller's: NCCL all-to-all, or its own).  A key
+ * crosses the link once as 8 bytes instead of being probed remotely with 32-byte loads.
+ *   route_count    d_counts[s] = keys of the batch owned by shard s (the array is cleared first);
+ *   route_scatter  d_cursor[s] = where shard s's bucket starts in d_keys_out (the exclusive prefix sums of the
+ *                  counts; advanced by the call); keys land in their owner's bucket in no particular order and
+ *                  d_pos_out[i] says where key i went;
+ *   gather_bytes   d_dst[i] = d_src[d_pos[i]]: the answers, which arrive in bucket order, back in key order;
+ *   match_prefix_from_flags  match_prefix over per-key flag bytes (KVCM_FLAG_SERVABLE) instead of index probes,
+ *                  as match_sw_from_flags is to match_sw.
+ * The owner of a key is the shard of kvcm_b200_index_upsert_sharded.  n < 2^31, shard_count <= 64.  (No
+ * counterpart in the reference, whose index is not sharded.) */
+KVCM_API int32_t kvcm_b200_route_count(const int64_t *d_keys, int64_t n, int32_t shard_count, uint32_t *d_counts,
+                                       kvcm_stream_t stream);
+KVCM_API int32_t kvcm_b200_route_scatter(const int64_t *d_keys, int64_t n, int32_t shard_count, uint32_t *d_cursor,
+                                         int64_t *d_keys_out, int32_t *d_pos_out, kvcm_stream_t stream);
+KVCM_API int32_t kvcm_b200_gather_bytes(const uint8_t *d_src, const int32_t *d_pos, int64_t n, uint8_t *d_dst,
+                                        kvcm_stream_t stream);
+KVCM_API int32_t kvcm_b200_match_prefix_from_flags(const uint8_t *d_flags, const int64_t *d_key_off, int32_t n_req,
+                                                   const int64_t *d_mask_off, const uint8_t *d_mask_bits,
+                                                   int32_t *d_len_out, kvcm_stream_t stream);
+
 /* Peer-attached shards: the collective-free way to query a sharded index on one NVLink / NVSwitch
  * box.  Every GPU exports its shard once; each GPU maps the others' shards (CUDA IPC, peer access)
  * and attaches them to its own handle.  From then on match_prefix, match_sw, batch_get and

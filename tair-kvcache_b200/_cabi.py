@@ -95,6 +95,10 @@ SIGNATURES = {
     "kvcm_b200_match_prefix_sharded": [_vp, _vp, _vp, _i32, _vp, _vp, _u32, _i32, _i32, _vp, _vp],
     "kvcm_b200_batch_get_sharded": [_vp, _vp, _i64, _u32, _i32, _i32, _vp, _vp],
     "kvcm_b200_match_sw_from_flags": [_vp, _vp, _i32, _i32, _vp, _vp],
+    "kvcm_b200_route_count": [_vp, _i64, _i32, _vp, _vp],
+    "kvcm_b200_route_scatter": [_vp, _i64, _i32, _vp, _vp, _vp, _vp],
+    "kvcm_b200_gather_bytes": [_vp, _vp, _i64, _vp, _vp],
+    "kvcm_b200_match_prefix_from_flags": [_vp, _vp, _i32, _vp, _vp, _vp, _vp],
     "kvcm_b200_index_export": [_vp, _vp],
     "kvcm_b200_index_attach_peers": [_vp, _i32, _i32, _vp],
     "kvcm_b200_index_attach_local_peers": [_vp, _i32, _i32, _vp],

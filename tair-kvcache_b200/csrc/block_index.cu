@@ -377,6 +377,107 @@ __global__ void __launch_bounds__(kMatchWarps * 32)
     if (lane == 0) base_out[req] = static_cast<int32_t>(found);
 }
 
+// ------------------------------------------------------------------------------------------
+// Routing a batch of keys to the shards that own them: the two device-side halves of an
+// all-to-all exchange (dispatch: bucket the keys by owner; combine: bring the answers back into
+// the order of the keys).  A key then crosses NVLink once as 8 bytes and its answer comes back as
+// one byte, instead of one or two 32-byte peer loads per probe.
+// ------------------------------------------------------------------------------------------
+constexpr int kRouteThreads = 256;
+constexpr int kRouteKeysPerCta = kRouteThreads * 8;
+constexpr int kMaxShards = 64;
+
+// counts[s] += keys of this batch owned by shard s.
+__global__ void __launch_bounds__(kRouteThreads)
+    RouteCountKernel(const int64_t *__restrict__ keys, int64_t n, uint32_t shards, uint32_t *__restrict__ counts) {
+    __shared__ uint32_t local[kMaxShards];
+    if (threadIdx.x < kMaxShards) local[threadIdx.x] = 0;
+    __syncthreads();
+    const int64_t base = static_cast<int64_t>(blockIdx.x) * kRouteKeysPerCta;
+    for (int64_t i = base + threadIdx.x; i < base + kRouteKeysPerCta && i < n; i += kRouteThreads) {
+        const uint32_t owner = OwnerOf(static_cast<uint64_t>(keys[i]), shards);
+        const uint32_t same = __match_any_sync(__activemask(), owner);  // one atomic per owner and warp
+        if (LaneId() == static_cast<uint32_t>(__ffs(same)) - 1u) atomicAdd(&local[owner], __popc(same));
+    }
+    __syncthreads();
+    if (threadIdx.x < shards && local[threadIdx.x] != 0) atomicAdd(&counts[threadIdx.x], local[threadIdx.x]);
+}
+
+// cursor[s] holds where shard s's bucket continues in keys_out; every CTA reserves room for its keys of each
+// owner with one atomic per owner, then places them.  pos_out[i] = where key i went.
+__global__ void __launch_bounds__(kRouteThreads)
+    RouteScatterKernel(const int64_t *__restrict__ keys, int64_t n, uint32_t shards, uint32_t *__restrict__ cursor,
+                       int64_t *__restrict__ keys_out, int32_t *__restrict__ pos_out) {
+    __shared__ uint32_t local[kMaxShards];
+    __shared__ uint32_t start[kMaxShards];
+    if (threadIdx.x < kMaxShards) local[threadIdx.x] = 0;
+    __syncthreads();
+    const int64_t base = static_cast<int64_t>(blockIdx.x) * kRouteKeysPerCta;
+    uint32_t rank_in_cta[kRouteKeysPerCta / kRouteThreads];
+    uint32_t owner[kRouteKeysPerCta / kRouteThreads];
+#pragma unroll
+    for (int j = 0; j < kRouteKeysPerCta / kRouteThreads; ++j) {
+        const int64_t i = base + j * kRouteThreads + threadIdx.x;
+        if (i < n) {
+            owner[j] = OwnerOf(static_cast<uint64_t>(keys[i]), shards);
+            const uint32_t same = __match_any_sync(__activemask(), owner[j]);
+            const int leader = __ffs(same) - 1;
+            uint32_t first = 0;
+            if (static_cast<int>(LaneId()) == leader) first = atomicAdd(&local[owner[j]], __popc(same));
+            rank_in_cta[j] = __shfl_sync(same, first, leader) + __popc(same & ((1u << LaneId()) - 1u));
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < shards) start[threadIdx.x] = local[threadIdx.x] ? atomicAdd(&cursor[threadIdx.x], local[threadIdx.x]) : 0;
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < kRouteKeysPerCta / kRouteThreads; ++j) {
+        const int64_t i = base + j * kRouteThreads + threadIdx.x;
+        if (i < n) {
+            const uint32_t at = start[owner[j]] + rank_in_cta[j];
+            keys_out[at] = keys[i];
+            pos_out[i] = static_cast<int32_t>(at);
+        }
+    }
+}
+
+__global__ void GatherBytesKernel(const uint8_t *__restrict__ src, const int32_t *__restrict__ pos, int64_t n,
+                                  uint8_t *__restrict__ dst) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = src[pos[i]];
+}
+
+// PrefixMatchKernel over per-key flag bytes (bit0 = servable) instead of index probes: the second half of a
+// routed prefix match.
+__global__ void __launch_bounds__(kMatchWarps * 32)
+    PrefixFromFlagsKernel(const uint8_t *__restrict__ flags, const int64_t *__restrict__ key_off, int32_t n_req,
+                          const int64_t *__restrict__ mask_off, const uint8_t *__restrict__ mask_bits,
+                          int32_t *__restrict__ len_out) {
+    const int32_t req = blockIdx.x * kMatchWarps + (threadIdx.x >> 5);
+    if (req >= n_req) return;
+    const uint32_t lane = LaneId();
+    const int64_t beg = key_off[req];
+    const int64_t n = key_off[req + 1] - beg;
+    const int64_t skip = mask_off != nullptr ? mask_off[req] : 0;
+    int32_t matched = 0;
+    for (int64_t base = 0; base < n; base += 32) {
+        const int64_t i = base + lane;
+        bool counted = false, stop = false;
+        if (i < n && !(i < skip || (mask_bits != nullptr && mask_bits[beg + i] != 0))) {
+            counted = (flags[beg + i] & KVCM_FLAG_SERVABLE) != 0;
+            stop = !counted;
+        }
+        const uint32_t stops = __ballot_sync(0xffffffffu, stop);
+        const uint32_t hits = __ballot_sync(0xffffffffu, counted);
+        if (stops != 0) {
+            matched += __popc(hits & ((1u << (__ffs(stops) - 1)) - 1u));
+            break;
+        }
+        matched += __popc(hits);
+    }
+    if (lane == 0) len_out[req] = matched;
+}
+
 // CacheManager::FilterWriteCache (kv_cache_manager/manager/cache_manager.cc:589-635) for a batch of
 // requests, one warp each.  exists(key) = ExistsForWrite: some location with status != NOT_FOUND and
 // weight > 0.  If the keys that exist form a prefix of the request, the answer is the offset of the
@@ -681,6 +782,58 @@ int32_t kvcm_b200_match_sw_from_flags(const uint8_t *d_flags, const int64_t *d_k
     if (d_key_off == nullptr || d_base_out == nullptr) return KVCM_ER_INVALID_ADDRESS;
     kvcm::SwFromFlagsKernel<<<kvcm::GridFor(n_req, kvcm::kMatchWarps), kvcm::kMatchWarps * 32, 0,
                               kvcm::AsStream(stream)>>>(d_flags, d_key_off, n_req, sw_blocks, d_base_out);
+    return kvcm::LaunchStatus();
+}
+
+int32_t kvcm_b200_route_count(const int64_t *d_keys, int64_t n, int32_t shard_count, uint32_t *d_counts,
+                              kvcm_stream_t stream) {
+    if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
+    if (n < 0 || n > 0x7fffffffll || shard_count < 1 || shard_count > kvcm::kMaxShards) return KVCM_EC_BADARGS;
+    if (d_counts == nullptr || (d_keys == nullptr && n > 0)) return KVCM_ER_INVALID_ADDRESS;
+    if (cudaMemsetAsync(d_counts, 0, sizeof(uint32_t) * shard_count, kvcm::AsStream(stream)) != cudaSuccess) {
+        cudaGetLastError();
+        return KVCM_ER_CUDAMEMCPY_ERROR;
+    }
+    if (n == 0) return KVCM_OK;
+    kvcm::RouteCountKernel<<<kvcm::GridFor(n, kvcm::kRouteKeysPerCta), kvcm::kRouteThreads, 0, kvcm::AsStream(stream)>>>(
+        d_keys, n, static_cast<uint32_t>(shard_count), d_counts);
+    return kvcm::LaunchStatus();
+}
+
+int32_t kvcm_b200_route_scatter(const int64_t *d_keys, int64_t n, int32_t shard_count, uint32_t *d_cursor,
+                                int64_t *d_keys_out, int32_t *d_pos_out, kvcm_stream_t stream) {
+    if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
+    if (n < 0 || n > 0x7fffffffll || shard_count < 1 || shard_count > kvcm::kMaxShards) return KVCM_EC_BADARGS;
+    if (n == 0) return KVCM_OK;
+    if (d_keys == nullptr || d_cursor == nullptr || d_keys_out == nullptr || d_pos_out == nullptr) {
+        return KVCM_ER_INVALID_ADDRESS;
+    }
+    kvcm::RouteScatterKernel<<<kvcm::GridFor(n, kvcm::kRouteKeysPerCta), kvcm::kRouteThreads, 0,
+                               kvcm::AsStream(stream)>>>(d_keys, n, static_cast<uint32_t>(shard_count), d_cursor,
+                                                         d_keys_out, d_pos_out);
+    return kvcm::LaunchStatus();
+}
+
+int32_t kvcm_b200_gather_bytes(const uint8_t *d_src, const int32_t *d_pos, int64_t n, uint8_t *d_dst,
+                               kvcm_stream_t stream) {
+    if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
+    if (n < 0) return KVCM_EC_BADARGS;
+    if (n == 0) return KVCM_OK;
+    if (d_src == nullptr || d_pos == nullptr || d_dst == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    kvcm::GatherBytesKernel<<<kvcm::GridFor(n, 256), 256, 0, kvcm::AsStream(stream)>>>(d_src, d_pos, n, d_dst);
+    return kvcm::LaunchStatus();
+}
+
+int32_t kvcm_b200_match_prefix_from_flags(const uint8_t *d_flags, const int64_t *d_key_off, int32_t n_req,
+                                          const int64_t *d_mask_off, const uint8_t *d_mask_bits, int32_t *d_len_out,
+                                          kvcm_stream_t stream) {
+    if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
+    if (n_req < 0) return KVCM_EC_BADARGS;
+    if (n_req == 0) return KVCM_OK;
+    if (d_key_off == nullptr || d_len_out == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    kvcm::PrefixFromFlagsKernel<<<kvcm::GridFor(n_req, kvcm::kMatchWarps), kvcm::kMatchWarps * 32, 0,
+                                  kvcm::AsStream(stream)>>>(d_flags, d_key_off, n_req, d_mask_off, d_mask_bits,
+                                                            d_len_out);
     return kvcm::LaunchStatus();
 }
 

@@ -12,6 +12,10 @@ Both equal MetaSearcher::PrefixMatch / ReverseRollSlideWindowMatch
 (kv_cache_manager/manager/meta_searcher.cc:120-145, 196-265) on the unsharded index because every key has
 exactly one owner.  The collectives run over the group's backend (NCCL on GPUs); data lands in local
 buffers before any kernel reads it.
+
+A third way, "route", sends every key only to the shard that owns it (an all-to-all of 8-byte keys bucketed on
+the device) and gets one flag byte per key back (a second all-to-all), after which both matchers run locally
+over the flag bytes: the traffic per key is 9 bytes whatever the number of shards.
 """
 from typing import Optional, Tuple
 
@@ -72,6 +76,32 @@ class CudaShardBackend:
                    self.index._s())
         return out
 
+    def prefix_from_flags(self, flags, key_off, mask_off):
+        n_req = key_off.numel() - 1
+        out = torch.empty(n_req, dtype=torch.int32, device=self.device)
+        _cabi.call("kvcm_b200_match_prefix_from_flags", flags.data_ptr(), key_off.data_ptr(), n_req,
+                   mask_off.data_ptr() if mask_off is not None else None, None, out.data_ptr(), self.index._s())
+        return out
+
+    def route_count(self, keys, shard_count):
+        counts = torch.empty(shard_count, dtype=torch.int32, device=self.device)
+        _cabi.call("kvcm_b200_route_count", keys.data_ptr(), keys.numel(), shard_count, counts.data_ptr(),
+                   self.index._s())
+        return counts
+
+    def route_scatter(self, keys, shard_count, cursor):
+        bucketed = torch.empty_like(keys)
+        pos = torch.empty(keys.numel(), dtype=torch.int32, device=self.device)
+        _cabi.call("kvcm_b200_route_scatter", keys.data_ptr(), keys.numel(), shard_count, cursor.data_ptr(),
+                   bucketed.data_ptr(), pos.data_ptr(), self.index._s())
+        return bucketed, pos
+
+    def gather_bytes(self, src, pos):
+        out = torch.empty(pos.numel(), dtype=torch.uint8, device=self.device)
+        _cabi.call("kvcm_b200_gather_bytes", src.data_ptr(), pos.data_ptr(), pos.numel(), out.data_ptr(),
+                   self.index._s())
+        return out
+
     def sw_direct(self, keys, key_off, sw):
         n_req = key_off.numel() - 1
         out = torch.empty(n_req, dtype=torch.int32, device=self.device)
@@ -87,12 +117,22 @@ class GatheredRequests:
         self.keys, self.csr, self.per_req, self.first, self.n_req = keys, csr, per_req, first, n_req
 
 
+class RoutedFlags:
+    """The servable flag of each of this rank's keys, fetched from the owning shards; reusable for several
+    queries on the same keys."""
+
+    def __init__(self, flags, key_off, mask_off):
+        self.flags, self.key_off, self.mask_off = flags, key_off, mask_off
+
+
 class ShardedMetaSearcher:
     """Collective front end: every rank of `group` calls each method with its own requests.
 
     mode "exchange": one all-gather of keys and one min / max all-reduce per query (works on any backend).
     mode "peer":     after `attach_peers()` every rank probes the owner shard of each key directly over NVLink
-                     (CUDA IPC mappings, plain peer loads): queries need no collective at all; only writes do."""
+                     (CUDA IPC mappings, plain peer loads): queries need no collective at all; only writes do.
+    mode "route":    every key goes to its owner and one flag byte comes back (two all-to-alls per batch of
+                     requests, shared by the prefix and the window query when `Route()` is called once)."""
 
     def __init__(self, backend, group: Optional[dist.ProcessGroup] = None, mode: str = "exchange"):
         self.backend = backend
@@ -175,6 +215,26 @@ class ShardedMetaSearcher:
         dist.all_gather_into_tensor(out, seg, group=self.group)
         return torch.cat([out[r * seg.numel(): r * seg.numel() + c] for r, c in enumerate(counts)])
 
+    # ---- route --------------------------------------------------------------------------------
+    def Route(self, keys: torch.Tensor, key_off: torch.Tensor, mask_off: Optional[torch.Tensor] = None
+              ) -> RoutedFlags:
+        """Dispatch this rank's keys to their owners, look them up there, combine the answers back in key order."""
+        keys, key_off = keys.contiguous(), key_off.contiguous()
+        counts = self.backend.route_count(keys, self.world)
+        matrix = torch.empty(self.world * self.world, dtype=torch.int32, device=self.device)
+        dist.all_gather_into_tensor(matrix, counts, group=self.group)
+        matrix = matrix.view(self.world, self.world).cpu()
+        send = matrix[self.rank].tolist()      # my keys per owner
+        recv = matrix[:, self.rank].tolist()   # keys I own, per asking rank
+        cursor = (torch.cumsum(counts, 0, dtype=torch.int32) - counts).contiguous()
+        bucketed, pos = self.backend.route_scatter(keys, self.world, cursor)
+        asked = torch.empty(sum(recv), dtype=torch.int64, device=self.device)
+        dist.all_to_all_single(asked, bucketed, recv, send, group=self.group)
+        answers = self.backend.servable_flags(asked, 1, 0)
+        back = torch.empty(keys.numel(), dtype=torch.uint8, device=self.device)
+        dist.all_to_all_single(back, answers, send, recv, group=self.group)
+        return RoutedFlags(self.backend.gather_bytes(back, pos), key_off, mask_off)
+
     # ---- operators ----------------------------------------------------------------------------
     def upsert(self, keys: torch.Tensor, value_word: int) -> None:
         """Every rank contributes keys; each key is stored on the shard that owns it."""
@@ -192,6 +252,9 @@ class ShardedMetaSearcher:
                     ) -> torch.Tensor:
         if self.mode == "peer":  # the attached handle resolves every key at its owner: a purely local call
             return self.backend.prefix_owned(keys.contiguous(), key_off.contiguous(), mask_off, 1, 0)
+        if self.mode == "route" or isinstance(keys, RoutedFlags):
+            r = keys if isinstance(keys, RoutedFlags) else self.Route(keys, key_off, mask_off)
+            return self.backend.prefix_from_flags(r.flags, r.key_off, r.mask_off)
         g = keys if isinstance(keys, GatheredRequests) else self.Gather(keys, key_off, mask_off)
         lens = self.backend.prefix_owned(g.keys, g.csr, g.per_req, self.world, self.rank)
         dist.all_reduce(lens, op=dist.ReduceOp.MIN, group=self.group)
@@ -203,6 +266,9 @@ class ShardedMetaSearcher:
             raise _cabi.KvcmError(_cabi.KVCM_EC_BADARGS, "ReverseRollSlideWindowMatch")
         if self.mode == "peer":
             return self.backend.sw_direct(keys.contiguous(), key_off.contiguous(), sw_size)
+        if self.mode == "route" or isinstance(keys, RoutedFlags):
+            r = keys if isinstance(keys, RoutedFlags) else self.Route(keys, key_off, None)
+            return self.backend.sw_from_flags(r.flags, r.key_off, sw_size)
         g = keys if isinstance(keys, GatheredRequests) else self.Gather(keys, key_off, None)
         flags = self.backend.servable_flags(g.keys, self.world, self.rank)
         dist.all_reduce(flags, op=dist.ReduceOp.MAX, group=self.group)

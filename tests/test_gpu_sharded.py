@@ -112,6 +112,44 @@ def test_sw_from_flags_equals_match_sw_on_the_same_index():
         assert torch.equal(a, b)
 
 
+def test_routing_kernels_dispatch_to_owners_and_combine_in_key_order():
+    """Dispatch / look-up / combine with the three shards of a split held on one GPU (the transport between ranks
+    is then a slice of the bucketed array)."""
+    present, reqs = _world(27)
+    full = oracle.Index()
+    full.put_uniform(present)
+    count = 3
+    shards = [CudaShardBackend(len(present), torch.device(DEV)) for _ in range(count)]
+    for r, sh in enumerate(shards):
+        sh.upsert_owned(torch.from_numpy(present).to(DEV), encode_locations([(3, 4)]), count, r)
+    for keys, off, mask in reqs:
+        dk, doff, dmask = (torch.from_numpy(a).to(DEV) for a in (keys, off, mask))
+        owner = shard_of_keys(keys, count)
+        counts = shards[0].route_count(dk, count)
+        assert counts.cpu().tolist() == np.bincount(owner, minlength=count).tolist()
+        start = torch.cumsum(counts, 0, dtype=torch.int32) - counts
+        cursor = start.clone()
+        bucketed, pos = shards[0].route_scatter(dk, count, cursor)
+        assert torch.equal(cursor, start + counts)
+        p, b = pos.cpu().numpy(), bucketed.cpu().numpy()
+        assert np.array_equal(np.sort(p), np.arange(len(keys)))          # a permutation
+        assert np.array_equal(b[p], keys)                                 # key i sits at pos[i]
+        edges = np.concatenate([start.cpu().numpy(), [len(keys)]])
+        assert all(((p >= edges[s]) & (p < edges[s + 1]))[owner == s].all() for s in range(count))
+        answers = torch.cat([shards[s].servable_flags(bucketed[edges[s]:edges[s + 1]].contiguous())
+                             for s in range(count)])
+        flags = shards[0].gather_bytes(answers, pos)
+        assert np.array_equal(flags.cpu().numpy(), full.batch_get(keys))
+        assert np.array_equal(shards[0].prefix_from_flags(flags, doff, None).cpu().numpy(),
+                              full.prefix_match_batch(keys, off))
+        assert np.array_equal(shards[0].prefix_from_flags(flags, doff, dmask).cpu().numpy(),
+                              full.prefix_match_batch(keys, off, mask))
+    # an empty batch is a no-op with zero counts
+    none = torch.zeros(0, dtype=torch.int64, device=DEV)
+    assert shards[0].route_count(none, count).cpu().tolist() == [0] * count
+    assert shards[0].route_scatter(none, count, torch.zeros(count, dtype=torch.int32, device=DEV))[1].numel() == 0
+
+
 def _rank_main(rank, port, results, mode):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -129,6 +167,10 @@ def _rank_main(rank, port, results, mode):
             "prefix_masked": searcher.PrefixMatch(keys, off, mask).cpu().numpy(),
             "sw4": searcher.ReverseRollSlideWindowMatch(keys, off, sw_size=4).cpu().numpy(),
         }
+        if mode == "route":  # one dispatch / combine serves both queries
+            routed = searcher.Route(keys, off, mask)
+            assert np.array_equal(searcher.PrefixMatch(routed).cpu().numpy(), out["prefix_masked"])
+            assert np.array_equal(searcher.ReverseRollSlideWindowMatch(routed, sw_size=4).cpu().numpy(), out["sw4"])
         torch.cuda.synchronize()
         results[rank] = out
         if mode == "peer":
@@ -138,7 +180,7 @@ def _rank_main(rank, port, results, mode):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("mode", ["exchange", "peer"])
+@pytest.mark.parametrize("mode", ["exchange", "peer", "route"])
 def test_two_nccl_ranks_match_the_unsharded_oracle(mode):
     import torch.multiprocessing as mp
     with socket.socket() as s:

@@ -45,6 +45,29 @@ class OracleShardBackend:
     def servable_flags(self, keys, shard_count=1, shard_rank=0):
         return torch.from_numpy(self.index.batch_get(keys.numpy()))
 
+    def prefix_from_flags(self, flags, key_off, mask_off):
+        f, off = flags.numpy() & 1, key_off.numpy()
+        out = np.zeros(len(off) - 1, dtype=np.int32)
+        for r in range(len(off) - 1):
+            skip = int(mask_off[r]) if mask_off is not None else 0
+            seg = f[off[r] + skip:off[r + 1]]
+            out[r] = len(seg) if seg.all() else int(np.argmin(seg))
+        return torch.from_numpy(out)
+
+    def route_count(self, keys, shard_count):
+        return torch.from_numpy(np.bincount(shard_of_keys(keys.numpy(), shard_count),
+                                            minlength=shard_count).astype(np.int32))
+
+    def route_scatter(self, keys, shard_count, cursor):
+        k = keys.numpy()
+        order = np.argsort(shard_of_keys(k, shard_count), kind="stable")
+        pos = np.empty(len(k), dtype=np.int32)
+        pos[order] = np.arange(len(k), dtype=np.int32)
+        return torch.from_numpy(k[order].copy()), torch.from_numpy(pos)
+
+    def gather_bytes(self, src, pos):
+        return torch.from_numpy(src.numpy()[pos.numpy()].copy())
+
     def sw_from_flags(self, flags, key_off, sw):
         f, off = flags.numpy() & 1, key_off.numpy()
         out = np.full(len(off) - 1, -1, dtype=np.int32)
@@ -98,6 +121,13 @@ def _rank_main(rank, port, results):
         g = searcher.Gather(tk, to, tm)  # one exchange, two queries
         assert np.array_equal(searcher.PrefixMatch(g).numpy(), out["prefix_masked"])
         assert np.array_equal(searcher.ReverseRollSlideWindowMatch(g, sw_size=5).numpy(), out["sw5"])
+        routed = ShardedMetaSearcher(searcher.backend, mode="route")
+        assert np.array_equal(routed.PrefixMatch(tk, to).numpy(), out["prefix"])
+        assert np.array_equal(routed.PrefixMatch(tk, to, tm).numpy(), out["prefix_masked"])
+        assert np.array_equal(routed.ReverseRollSlideWindowMatch(tk, to, 2).numpy(), out["sw2"])
+        r = routed.Route(tk, to, tm)  # one dispatch / combine, two queries
+        assert np.array_equal(routed.PrefixMatch(r).numpy(), out["prefix_masked"])
+        assert np.array_equal(routed.ReverseRollSlideWindowMatch(r, sw_size=5).numpy(), out["sw5"])
         results[rank] = out
     finally:
         dist.destroy_process_group()
