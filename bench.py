@@ -643,7 +643,10 @@ def main_window(args, rank, world):
 
     # ---- index content: root blocks (this rank hashes a slice of the roots), then request blocks up to the quota
     backend = CudaShardBackend(2 * index_keys // world + 1024, device)
-    searcher = ShardedMetaSearcher(backend, mode=args.shard_mode) if world > 1 else None
+    searcher = None
+    if world > 1:  # exchange areas of the peer-memory route: one per stream, room for a rank's whole batch + 25 %
+        searcher = ShardedMetaSearcher(backend, mode=args.shard_mode, route_areas=2,
+                                       route_capacity=int(key_offsets(w["off"], bs)[-1] * 1.25) + 65536)
     local_index = BatchMetaSearcher(backend.index)
 
     def insert(keys):
@@ -681,7 +684,7 @@ def main_window(args, rank, world):
         keys = GenKeyVectorBatch(w["toks"], d_off, bs, d_ko, n_keys, out=d_keys, order=d_order, warps_per_sm=residency)
         if world > 1 and args.shard_mode == "peer":  # every key is probed at its owner over NVLink: no collective
             return searcher.PrefixMatch(keys, d_ko), searcher.ReverseRollSlideWindowMatch(keys, d_ko, sw)
-        if world > 1 and args.shard_mode == "route":  # keys to their owners, one flag byte back, both queries local
+        if world > 1 and args.shard_mode in ("route", "route_peer"):  # keys to their owners, one flag byte back, both queries local
             r = searcher.Route(keys, d_ko)
             return searcher.PrefixMatch(r), searcher.ReverseRollSlideWindowMatch(r, sw_size=sw)
         if world > 1:
@@ -693,7 +696,8 @@ def main_window(args, rank, world):
     # most SMs idle.  So the batch is laid out longest first (a batcher is free to order its requests) and cut in two:
     # the long head is hashed and matched on one stream while the rest is hashed and matched on another.  Same
     # kernels, same results per request.
-    overlap = not args.no_overlap and (world == 1 or args.shard_mode in ("peer", "route"))
+    routed = args.shard_mode in ("route", "route_peer")
+    overlap = not args.no_overlap and (world == 1 or args.shard_mode == "peer" or routed)
     if overlap:
         my_len = w["off"][1:] - w["off"][:-1]
         perm = np.argsort(-my_len, kind="stable")  # sorted position -> request
@@ -704,6 +708,8 @@ def main_window(args, rank, world):
             toks_s[int(off_s[pos]):int(off_s[pos + 1])] = w["toks"][int(w["off"][j]):int(w["off"][j + 1])]
         ko_s = key_offsets(off_s, bs)
         d_off_s, d_ko_s = torch.from_numpy(off_s).to(device), torch.from_numpy(ko_s).to(device)
+        if args.long_fraction is None:  # measured on 2 GPUs, routed: 0.5 / 0.7 / 0.85 / 0.95 -> 3.80 / 3.44 / 3.51 / 3.77 ms
+            args.long_fraction = 0.7 if world > 1 and routed else 0.5
         n_long = int(np.count_nonzero(my_len >= args.long_fraction * my_len.max()))
         prefix_s = torch.empty(len(perm), dtype=torch.int32, device=device)
         window_s = torch.empty(len(perm), dtype=torch.int32, device=device)
@@ -740,7 +746,7 @@ def main_window(args, rank, world):
         for which in (1, 0):
             a, b, _ = parts[which]
             with torch.cuda.stream(streams[which]):
-                r = searcher.Route(d_keys[int(ko_s[a]):int(ko_s[b])], rel_ko[which])
+                r = searcher.Route(d_keys[int(ko_s[a]):int(ko_s[b])], rel_ko[which], area=which)
                 mark(("head", "rest")[which] + "_routed", streams[which])
                 prefix_s[a:b] = searcher.PrefixMatch(r)
                 window_s[a:b] = searcher.ReverseRollSlideWindowMatch(r, sw_size=sw)
@@ -765,7 +771,7 @@ def main_window(args, rank, world):
 
     step = step_serial
     if overlap:
-        step = step_overlapped_routed if world > 1 and args.shard_mode == "route" else step_overlapped
+        step = step_overlapped_routed if world > 1 and routed else step_overlapped
 
     for _ in range(args.warmup):
         prefix, window = step()
@@ -786,11 +792,11 @@ def main_window(args, rank, world):
     ev[0].record()
     keys = GenKeyVectorBatch(w["toks"], d_off, bs, d_ko, n_keys, out=d_keys, order=d_order, warps_per_sm=residency)
     ev[1].record()
-    if world > 1 and args.shard_mode == "route":
-        routed = searcher.Route(keys, d_ko)
+    if world > 1 and routed:
+        flags = searcher.Route(keys, d_ko)
         ev[2].record()
-        searcher.PrefixMatch(routed)
-        searcher.ReverseRollSlideWindowMatch(routed, sw_size=sw)
+        searcher.PrefixMatch(flags)
+        searcher.ReverseRollSlideWindowMatch(flags, sw_size=sw)
     elif world > 1:
         searcher.PrefixMatch(keys, d_ko)
         ev[2].record()
@@ -808,7 +814,7 @@ def main_window(args, rank, world):
         step(marks)
         torch.cuda.synchronize(device)
         phase_ms["two_stream_timeline"] = {k: round(marks[0][1].elapsed_time(e), 3) for k, e in marks[1:]}
-    if world > 1 and args.shard_mode == "route":
+    if world > 1 and routed:
         phase_ms = {"hash": phase_ms["hash"], "dispatch_lookup_combine": phase_ms["prefix_match"],
                     "prefix_and_window_from_flags": phase_ms["window_match"],
                     **{k: v for k, v in phase_ms.items() if k == "two_stream_timeline"}}
@@ -877,6 +883,8 @@ def main_window(args, rank, world):
                                               "peer": ", shards probed over NVLink peer loads",
                                               "route": ", keys sent to their owners and one flag byte back "
                                                        "(two all-to-alls per step)",
+                                              "route_peer": ", keys stored into their owners' inboxes and one flag "
+                                                            "byte stored back over NVLink peer memory",
                                               "exchange": ", all-gather of keys + min/max all-reduce",
                                           }[args.shard_mode]),
                            "token_blocks": int(total_keys), "longest_request_tokens": longest,
@@ -885,13 +893,15 @@ def main_window(args, rank, world):
                            "schedule": ("two streams: the %d longest requests of rank 0 (>= %.2f of the longest) hashed "
                                         "and matched beside the rest; phase_ms are the kernels run alone on the "
                                         "whole batch" % (n_long, args.long_fraction)) if overlap else "one stream"},
-                "gpu_launches": ({"peer": 6, "route": 14}[args.shard_mode] if overlap and world > 1 else
-                                 6 if overlap else 3 if world == 1 else 7 if args.shard_mode == "route" else 4)
+                "gpu_launches": ({"peer": 6, "route": 14, "route_peer": 14}[args.shard_mode] if overlap and world > 1
+                                 else 6 if overlap else 3 if world == 1 else 7 if routed else 4)
                 * args.steps * world}
         print(json.dumps(line))
     if world > 1:
         if args.shard_mode == "peer":
             searcher.detach_peers()
+        if args.shard_mode == "route_peer":
+            searcher.detach_route_areas()
         dist.destroy_process_group()
 
 
@@ -1625,12 +1635,13 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c1", "c4", "c5", "lru", "iov", "hash"])
     ap.add_argument("--n-requests", type=int, default=0, help="c4: override the number of requests")
     ap.add_argument("--index-keys", type=int, default=0, help="c4: override the number of indexed keys")
-    ap.add_argument("--shard-mode", default="peer", choices=["peer", "exchange", "route"],
+    ap.add_argument("--shard-mode", default="route_peer", choices=["peer", "exchange", "route", "route_peer"],
                     help="c4 on several GPUs: probe remote shards over NVLink, or exchange keys and reduce results")
     ap.add_argument("--no-overlap", action="store_true",
                     help="c4: one stream, requests in arrival order (the earlier form of the step)")
-    ap.add_argument("--long-fraction", type=float, default=0.5,
-                    help="c4: requests at least this fraction of the longest form the head that gets its own stream")
+    ap.add_argument("--long-fraction", type=float, default=None,
+                    help="c4: requests at least this fraction of the longest form the head that gets its own stream "
+                         "(default 0.5; 0.7 for the routed shard modes, whose head is routed after the rest)")
     ap.add_argument("--request-tokens", type=int, default=0, help="hash: tokens per request (default 20970)")
     ap.add_argument("--n-configs", type=int, default=0, help="lru: quota points per GPU (default 148)")
     ap.add_argument("--no-prefix", action="store_true", help="skip the prefix-match side measurement")

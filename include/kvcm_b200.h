@@ -394,6 +394,47 @@ KVCM_API int32_t kvcm_b200_match_prefix_from_flags(const uint8_t *d_flags, const
                                                    const int64_t *d_mask_off, const uint8_t *d_mask_bits,
                                                    int32_t *d_len_out, kvcm_stream_t stream);
 
+/* The routed exchange over peer memory (one NVLink / NVSwitch box), with no transport between the two halves:
+ * every rank owns an exchange area (an inbox of capacity_keys keys and as many answer bytes), exports it once and
+ * maps the others' (CUDA IPC, as for the shards above).  Per batch, with h_counts the shard_count x shard_count
+ * matrix of route_count results of all ranks (h_counts[r * shard_count + s] = keys rank r sends to shard s, host
+ * memory, the same on every rank):
+ *   route_dispatch  stores each of this rank's keys into its owner's inbox (peer stores, staged per CTA so that
+ *                   warps write consecutive addresses) and records in d_pos_out[i] where key i's answer will land;
+ *                   d_cursor is scratch of shard_count words;
+ *   -- all ranks meet (their dispatch kernels have completed) --
+ *   route_answer    looks up the keys that arrived in this rank's inbox and stores each flag byte (batch_get's)
+ *                   into the asking rank's answer buffer;
+ *   -- all ranks meet --
+ *   route_collect   d_flags_out[i] = the answer for key i, in key order.
+ * No kernel waits on another rank; the meeting points are the caller's (a barrier collective enqueued on the
+ * same stream, or stream synchronisation plus a host barrier).  The next batch may be dispatched once every
+ * rank has enqueued its collect behind the second meeting point.  EC_NOSPC when some inbox or answer buffer
+ * would overflow (nothing is launched; the same verdict on every rank, since all hold the same matrix and
+ * capacity).  attach_local is for areas that live in one process.  (No counterpart in the reference.) */
+typedef struct kvcm_b200_route_area kvcm_b200_route_area_t;
+typedef struct kvcm_b200_route_export {
+    uint8_t ipc_handle[64];
+    uint64_t capacity_keys;
+    int32_t device;
+    int32_t reserved_;
+} kvcm_b200_route_export_t;
+KVCM_API int32_t kvcm_b200_route_area_create(int64_t capacity_keys, kvcm_b200_route_area_t **out);
+KVCM_API int32_t kvcm_b200_route_area_destroy(kvcm_b200_route_area_t *area);
+KVCM_API int32_t kvcm_b200_route_area_export(kvcm_b200_route_area_t *area, kvcm_b200_route_export_t *out);
+KVCM_API int32_t kvcm_b200_route_area_attach(kvcm_b200_route_area_t *area, int32_t shard_count, int32_t shard_rank,
+                                             const kvcm_b200_route_export_t *exports);
+KVCM_API int32_t kvcm_b200_route_area_attach_local(kvcm_b200_route_area_t *area, int32_t shard_count,
+                                                   int32_t shard_rank, kvcm_b200_route_area_t *const *areas);
+KVCM_API int32_t kvcm_b200_route_area_detach(kvcm_b200_route_area_t *area);
+KVCM_API int32_t kvcm_b200_route_dispatch(kvcm_b200_route_area_t *area, const int64_t *d_keys, int64_t n,
+                                          const uint32_t *h_counts, uint32_t *d_cursor, int32_t *d_pos_out,
+                                          kvcm_stream_t stream);
+KVCM_API int32_t kvcm_b200_route_answer(kvcm_b200_index_t *index, kvcm_b200_route_area_t *area,
+                                        const uint32_t *h_counts, uint32_t avail_mask, kvcm_stream_t stream);
+KVCM_API int32_t kvcm_b200_route_collect(kvcm_b200_route_area_t *area, const int32_t *d_pos, int64_t n,
+                                         uint8_t *d_flags_out, kvcm_stream_t stream);
+
 /* Peer-attached shards: the collective-free way to query a sharded index on one NVLink / NVSwitch
  * box.  Every GPU exports its shard once; each GPU maps the others' shards (CUDA IPC, peer access)
  * and attaches them to its own handle.  From then on match_prefix, match_sw, batch_get and

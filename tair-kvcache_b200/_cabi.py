@@ -45,6 +45,10 @@ class IndexExport(ctypes.Structure):
     _fields_ = [("ipc_handle", ctypes.c_uint8 * 64), ("n_slots", _u64), ("device", _i32), ("reserved_", _i32)]
 
 
+class RouteExport(ctypes.Structure):
+    _fields_ = [("ipc_handle", ctypes.c_uint8 * 64), ("capacity_keys", _u64), ("device", _i32), ("reserved_", _i32)]
+
+
 class Iov(ctypes.Structure):
     _fields_ = [("type", ctypes.c_uint8), ("ignore", ctypes.c_uint8), ("pad_", ctypes.c_uint8 * 6), ("base", _vp),
                 ("size", _u64)]
@@ -99,6 +103,15 @@ SIGNATURES = {
     "kvcm_b200_route_scatter": [_vp, _i64, _i32, _vp, _vp, _vp, _vp],
     "kvcm_b200_gather_bytes": [_vp, _vp, _i64, _vp, _vp],
     "kvcm_b200_match_prefix_from_flags": [_vp, _vp, _i32, _vp, _vp, _vp, _vp],
+    "kvcm_b200_route_area_create": [_i64, _vp],
+    "kvcm_b200_route_area_destroy": [_vp],
+    "kvcm_b200_route_area_export": [_vp, _vp],
+    "kvcm_b200_route_area_attach": [_vp, _i32, _i32, _vp],
+    "kvcm_b200_route_area_attach_local": [_vp, _i32, _i32, _vp],
+    "kvcm_b200_route_area_detach": [_vp],
+    "kvcm_b200_route_dispatch": [_vp, _vp, _i64, _vp, _vp, _vp, _vp],
+    "kvcm_b200_route_answer": [_vp, _vp, _vp, _u32, _vp],
+    "kvcm_b200_route_collect": [_vp, _vp, _i64, _vp, _vp],
     "kvcm_b200_index_export": [_vp, _vp],
     "kvcm_b200_index_attach_peers": [_vp, _i32, _i32, _vp],
     "kvcm_b200_index_attach_local_peers": [_vp, _i32, _i32, _vp],

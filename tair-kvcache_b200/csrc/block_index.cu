@@ -38,6 +38,21 @@ struct kvcm_b200_index {
     int n_opened;
 };
 
+// Exchange area of one rank of a routed query: the inbox the other ranks store the keys this rank owns into,
+// and the answer bytes the owners store back.  One allocation, exported to the peers like a shard.
+struct kvcm_b200_route_area {
+    void *base;
+    int64_t *inbox;
+    uint8_t *answers;
+    uint64_t capacity;
+    int device;
+    void *d_peer_table;  // device copy of kvcm::RoutePeers, set by attach
+    uint32_t peer_count;
+    uint32_t self;
+    void *opened[64];
+    int n_opened;
+};
+
 namespace kvcm {
 namespace {
 
@@ -227,13 +242,8 @@ __global__ void LookupKernel(IndexView ix, const int64_t *__restrict__ keys, int
     if (i < n) out[i] = Lookup(ix, static_cast<uint64_t>(keys[i]));
 }
 
-__global__ void BatchGetKernel(IndexView ix, const int64_t *__restrict__ keys, int64_t n, uint32_t avail_mask,
-                               Shard shard, uint8_t *__restrict__ flags) {
-    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const uint64_t key = static_cast<uint64_t>(keys[i]);
-    // A key of another shard is reported absent without touching the table.
-    const uint64_t v = Owns(shard, key) ? Lookup(ix, key) : 0;
+// The flag byte of batch_get for a value word (0 = absent).
+__device__ __forceinline__ uint8_t FlagsOf(uint64_t v, uint32_t avail_mask) {
     uint32_t f = 0;
     if (v != 0) {
         f |= KVCM_FLAG_EXISTS;
@@ -241,7 +251,16 @@ __global__ void BatchGetKernel(IndexView ix, const int64_t *__restrict__ keys, i
         if (Servable(v, avail_mask)) f |= KVCM_FLAG_SERVABLE;
         if ((static_cast<uint32_t>(v >> 16) & avail_mask & 0xFFFFu) != 0) f |= KVCM_FLAG_WRITABLE;
     }
-    flags[i] = static_cast<uint8_t>(f);
+    return static_cast<uint8_t>(f);
+}
+
+__global__ void BatchGetKernel(IndexView ix, const int64_t *__restrict__ keys, int64_t n, uint32_t avail_mask,
+                               Shard shard, uint8_t *__restrict__ flags) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint64_t key = static_cast<uint64_t>(keys[i]);
+    // A key of another shard is reported absent without touching the table.
+    flags[i] = FlagsOf(Owns(shard, key) ? Lookup(ix, key) : 0, avail_mask);
 }
 
 // One warp per request; each pass probes 32 consecutive keys, one per lane, and a ballot finds
@@ -476,6 +495,96 @@ __global__ void __launch_bounds__(kMatchWarps * 32)
         matched += __popc(hits);
     }
     if (lane == 0) len_out[req] = matched;
+}
+
+// ------------------------------------------------------------------------------------------
+// The same exchange over peer memory, without a transport in between: the dispatch kernel stores each
+// key straight into its owner's inbox (NVLink peer stores, staged per CTA so that a warp writes
+// consecutive addresses), and the owner's answer kernel stores the flag bytes straight into the asking
+// rank's answer buffer.  No kernel waits for another rank: the ranks meet at a barrier of the caller's
+// between dispatch, answer and collect.
+// ------------------------------------------------------------------------------------------
+struct RoutePeers {
+    int64_t *inbox[kMaxShards];
+    uint8_t *answers[kMaxShards];
+};
+// Per call and per peer s.  Dispatch: a = where this rank's region starts in s's inbox, b = where the bucket
+// of s starts in this rank's answer buffer.  Answer: a = where asker s's region starts in this rank's inbox
+// (a[shards] = keys in the inbox), b = where this rank's bucket starts in asker s's answer buffer.
+struct RouteStarts {
+    uint32_t a[kMaxShards + 1];
+    uint32_t b[kMaxShards];
+};
+
+__global__ void __launch_bounds__(kRouteThreads)
+    RouteDispatchKernel(const int64_t *__restrict__ keys, int64_t n, uint32_t shards, const RoutePeers *__restrict__ peers,
+                        const RouteStarts starts, uint32_t *__restrict__ cursor, int32_t *__restrict__ pos_out) {
+    __shared__ int64_t staged[kRouteKeysPerCta];
+    __shared__ uint32_t local[kMaxShards];        // keys of this CTA per owner
+    __shared__ uint32_t local_start[kMaxShards + 1];
+    __shared__ uint32_t reserved[kMaxShards];     // first index this CTA got in its rank's bucket of the owner
+    constexpr int kPerThread = kRouteKeysPerCta / kRouteThreads;
+    if (threadIdx.x < kMaxShards) local[threadIdx.x] = 0;
+    __syncthreads();
+    const int64_t base = static_cast<int64_t>(blockIdx.x) * kRouteKeysPerCta;
+    int64_t key[kPerThread];
+    uint32_t rank_in_cta[kPerThread];
+    uint32_t owner[kPerThread];
+#pragma unroll
+    for (int j = 0; j < kPerThread; ++j) {
+        const int64_t i = base + j * kRouteThreads + threadIdx.x;
+        if (i < n) {
+            key[j] = keys[i];
+            owner[j] = OwnerOf(static_cast<uint64_t>(key[j]), shards);
+            const uint32_t same = __match_any_sync(__activemask(), owner[j]);
+            const int leader = __ffs(same) - 1;
+            uint32_t first = 0;
+            if (static_cast<int>(LaneId()) == leader) first = atomicAdd(&local[owner[j]], __popc(same));
+            rank_in_cta[j] = __shfl_sync(same, first, leader) + __popc(same & ((1u << LaneId()) - 1u));
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < shards) reserved[threadIdx.x] = local[threadIdx.x] ? atomicAdd(&cursor[threadIdx.x], local[threadIdx.x]) : 0;
+    if (threadIdx.x == 0) {
+        uint32_t sum = 0;
+        for (uint32_t s = 0; s < shards; ++s) {
+            local_start[s] = sum;
+            sum += local[s];
+        }
+        local_start[shards] = sum;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < kPerThread; ++j) {
+        const int64_t i = base + j * kRouteThreads + threadIdx.x;
+        if (i < n) {
+            staged[local_start[owner[j]] + rank_in_cta[j]] = key[j];
+            pos_out[i] = static_cast<int32_t>(starts.b[owner[j]] + reserved[owner[j]] + rank_in_cta[j]);
+        }
+    }
+    __syncthreads();
+    const uint32_t total = local_start[shards];
+    for (uint32_t e = threadIdx.x; e < total; e += kRouteThreads) {
+        uint32_t lo = 0, hi = shards;  // the owner whose run of the staged keys holds e
+        while (hi - lo > 1) {
+            const uint32_t mid = (lo + hi) >> 1;
+            if (local_start[mid] <= e) lo = mid; else hi = mid;
+        }
+        peers->inbox[lo][starts.a[lo] + reserved[lo] + (e - local_start[lo])] = staged[e];
+    }
+}
+
+__global__ void RouteAnswerKernel(IndexView ix, const int64_t *__restrict__ inbox, uint32_t n_inbox, uint32_t shards,
+                                  const RoutePeers *__restrict__ peers, const RouteStarts starts, uint32_t avail_mask) {
+    const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n_inbox) return;
+    uint32_t lo = 0, hi = shards;  // the asker whose region holds j
+    while (hi - lo > 1) {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (starts.a[mid] <= j) lo = mid; else hi = mid;
+    }
+    const uint8_t f = FlagsOf(LookupIn<false>(ix, static_cast<uint64_t>(inbox[j])), avail_mask);
+    peers->answers[lo][starts.b[lo] + (j - starts.a[lo])] = f;
 }
 
 // CacheManager::FilterWriteCache (kv_cache_manager/manager/cache_manager.cc:589-635) for a batch of
@@ -835,6 +944,200 @@ int32_t kvcm_b200_match_prefix_from_flags(const uint8_t *d_flags, const int64_t 
                                   kvcm::AsStream(stream)>>>(d_flags, d_key_off, n_req, d_mask_off, d_mask_bits,
                                                             d_len_out);
     return kvcm::LaunchStatus();
+}
+
+int32_t kvcm_b200_route_area_detach(kvcm_b200_route_area_t *area) {
+    if (area == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (area->d_peer_table != nullptr) cudaFree(area->d_peer_table);
+    area->d_peer_table = nullptr;
+    area->peer_count = 0;
+    for (int i = 0; i < area->n_opened; ++i) cudaIpcCloseMemHandle(area->opened[i]);
+    area->n_opened = 0;
+    cudaGetLastError();
+    return KVCM_OK;
+}
+
+int32_t kvcm_b200_route_area_destroy(kvcm_b200_route_area_t *area) {
+    if (area == nullptr) return KVCM_OK;
+    kvcm_b200_route_area_detach(area);
+    cudaFree(area->base);
+    delete area;
+    return KVCM_OK;
+}
+
+int32_t kvcm_b200_route_area_create(int64_t capacity_keys, kvcm_b200_route_area_t **out) {
+    if (out == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    *out = nullptr;
+    if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
+    if (capacity_keys < 1 || capacity_keys > 0x7fffffffll) return KVCM_EC_BADARGS;
+    auto *area = new kvcm_b200_route_area();
+    area->capacity = (static_cast<uint64_t>(capacity_keys) + 255u) & ~uint64_t{255};
+    if (cudaGetDevice(&area->device) != cudaSuccess || cudaMalloc(&area->base, area->capacity * 9) != cudaSuccess) {
+        cudaGetLastError();
+        delete area;
+        return KVCM_EC_NOSPC;
+    }
+    area->inbox = static_cast<int64_t *>(area->base);
+    area->answers = reinterpret_cast<uint8_t *>(area->inbox + area->capacity);
+    *out = area;
+    return KVCM_OK;
+}
+
+int32_t kvcm_b200_route_area_export(kvcm_b200_route_area_t *area, kvcm_b200_route_export_t *out) {
+    if (area == nullptr || out == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    cudaIpcMemHandle_t h;
+    static_assert(sizeof(h) <= sizeof(out->ipc_handle), "IPC handle does not fit");
+    if (cudaIpcGetMemHandle(&h, area->base) != cudaSuccess) {
+        cudaGetLastError();
+        return KVCM_EC_ERROR;
+    }
+    memset(out, 0, sizeof(*out));
+    memcpy(out->ipc_handle, &h, sizeof(h));
+    out->capacity_keys = area->capacity;
+    out->device = area->device;
+    return KVCM_OK;
+}
+
+static int32_t InstallRoutePeers(kvcm_b200_route_area_t *area, int32_t shard_count, int32_t shard_rank,
+                                 const kvcm::RoutePeers &table) {
+    void *d = nullptr;
+    if (cudaMalloc(&d, sizeof(table)) != cudaSuccess ||
+        cudaMemcpy(d, &table, sizeof(table), cudaMemcpyHostToDevice) != cudaSuccess) {
+        cudaGetLastError();
+        if (d != nullptr) cudaFree(d);
+        return KVCM_EC_NOSPC;
+    }
+    area->d_peer_table = d;
+    area->peer_count = static_cast<uint32_t>(shard_count);
+    area->self = static_cast<uint32_t>(shard_rank);
+    return KVCM_OK;
+}
+
+int32_t kvcm_b200_route_area_attach(kvcm_b200_route_area_t *area, int32_t shard_count, int32_t shard_rank,
+                                    const kvcm_b200_route_export_t *exports) {
+    if (area == nullptr || exports == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (shard_count < 1 || shard_count > kvcm::kMaxShards || shard_rank < 0 || shard_rank >= shard_count) {
+        return KVCM_EC_BADARGS;
+    }
+    kvcm_b200_route_area_detach(area);
+    kvcm::RoutePeers table{};
+    for (int32_t r = 0; r < shard_count; ++r) {
+        if (r == shard_rank) {
+            table.inbox[r] = area->inbox;
+            table.answers[r] = area->answers;
+            continue;
+        }
+        if (exports[r].capacity_keys != area->capacity) {  // one capacity for all ranks: the checks are local then
+            kvcm_b200_route_area_detach(area);
+            return KVCM_EC_BADARGS;
+        }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, exports[r].ipc_handle, sizeof(h));
+        void *base = nullptr;
+        if (cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            cudaGetLastError();
+            kvcm_b200_route_area_detach(area);
+            return KVCM_EC_ERROR;
+        }
+        area->opened[area->n_opened++] = base;
+        table.inbox[r] = static_cast<int64_t *>(base);
+        table.answers[r] = reinterpret_cast<uint8_t *>(table.inbox[r] + exports[r].capacity_keys);
+    }
+    return InstallRoutePeers(area, shard_count, shard_rank, table);
+}
+
+int32_t kvcm_b200_route_area_attach_local(kvcm_b200_route_area_t *area, int32_t shard_count, int32_t shard_rank,
+                                          kvcm_b200_route_area_t *const *areas) {
+    if (area == nullptr || areas == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (shard_count < 1 || shard_count > kvcm::kMaxShards || shard_rank < 0 || shard_rank >= shard_count) {
+        return KVCM_EC_BADARGS;
+    }
+    kvcm_b200_route_area_detach(area);
+    kvcm::RoutePeers table{};
+    for (int32_t r = 0; r < shard_count; ++r) {
+        if (areas[r] == nullptr) return KVCM_ER_INVALID_ADDRESS;
+        if (areas[r]->capacity != area->capacity) return KVCM_EC_BADARGS;
+        table.inbox[r] = areas[r]->inbox;
+        table.answers[r] = areas[r]->answers;
+    }
+    return InstallRoutePeers(area, shard_count, shard_rank, table);
+}
+
+// h_counts[r * shards + s] = keys rank r sends to shard s (the same matrix on every rank).
+static bool RouteFits(const kvcm_b200_route_area_t *area, const uint32_t *h_counts, uint32_t shards) {
+    for (uint32_t owner = 0; owner < shards; ++owner) {  // every inbox holds what all ranks send it
+        uint64_t sum = 0;
+        for (uint32_t r = 0; r < shards; ++r) sum += h_counts[r * shards + owner];
+        if (sum > area->capacity) return false;
+    }
+    for (uint32_t r = 0; r < shards; ++r) {  // every answer buffer holds one byte per key of its rank
+        uint64_t sum = 0;
+        for (uint32_t owner = 0; owner < shards; ++owner) sum += h_counts[r * shards + owner];
+        if (sum > area->capacity) return false;
+    }
+    return true;
+}
+
+int32_t kvcm_b200_route_dispatch(kvcm_b200_route_area_t *area, const int64_t *d_keys, int64_t n,
+                                 const uint32_t *h_counts, uint32_t *d_cursor, int32_t *d_pos_out,
+                                 kvcm_stream_t stream) {
+    if (area == nullptr || h_counts == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (area->d_peer_table == nullptr || n < 0 || n > 0x7fffffffll) return KVCM_EC_BADARGS;
+    const uint32_t shards = area->peer_count, self = area->self;
+    if (!RouteFits(area, h_counts, shards)) return KVCM_EC_NOSPC;
+    uint64_t mine = 0;
+    for (uint32_t owner = 0; owner < shards; ++owner) mine += h_counts[self * shards + owner];
+    if (mine != static_cast<uint64_t>(n)) return KVCM_EC_BADARGS;
+    if (n == 0) return KVCM_OK;
+    if (d_keys == nullptr || d_cursor == nullptr || d_pos_out == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    kvcm::RouteStarts starts{};
+    uint32_t bucket = 0;
+    for (uint32_t owner = 0; owner < shards; ++owner) {
+        uint32_t before = 0;  // what the ranks below this one send to the same owner
+        for (uint32_t r = 0; r < self; ++r) before += h_counts[r * shards + owner];
+        starts.a[owner] = before;
+        starts.b[owner] = bucket;
+        bucket += h_counts[self * shards + owner];
+    }
+    if (cudaMemsetAsync(d_cursor, 0, sizeof(uint32_t) * shards, kvcm::AsStream(stream)) != cudaSuccess) {
+        cudaGetLastError();
+        return KVCM_ER_CUDAMEMCPY_ERROR;
+    }
+    kvcm::RouteDispatchKernel<<<kvcm::GridFor(n, kvcm::kRouteKeysPerCta), kvcm::kRouteThreads, 0,
+                                kvcm::AsStream(stream)>>>(d_keys, n, shards,
+                                                          static_cast<const kvcm::RoutePeers *>(area->d_peer_table),
+                                                          starts, d_cursor, d_pos_out);
+    return kvcm::LaunchStatus();
+}
+
+int32_t kvcm_b200_route_answer(kvcm_b200_index_t *ix, kvcm_b200_route_area_t *area, const uint32_t *h_counts,
+                               uint32_t avail_mask, kvcm_stream_t stream) {
+    if (ix == nullptr || area == nullptr || h_counts == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (area->d_peer_table == nullptr) return KVCM_EC_BADARGS;
+    const uint32_t shards = area->peer_count, self = area->self;
+    if (!RouteFits(area, h_counts, shards)) return KVCM_EC_NOSPC;
+    kvcm::RouteStarts starts{};
+    uint32_t arrived = 0;
+    for (uint32_t asker = 0; asker < shards; ++asker) {
+        starts.a[asker] = arrived;
+        arrived += h_counts[asker * shards + self];
+        uint32_t bucket = 0;  // where this rank's bucket starts among the asker's keys
+        for (uint32_t owner = 0; owner < self; ++owner) bucket += h_counts[asker * shards + owner];
+        starts.b[asker] = bucket;
+    }
+    starts.a[shards] = arrived;
+    if (arrived == 0) return KVCM_OK;
+    kvcm::RouteAnswerKernel<<<kvcm::GridFor(arrived, 256), 256, 0, kvcm::AsStream(stream)>>>(
+        kvcm::LocalView(ix), area->inbox, arrived, shards, static_cast<const kvcm::RoutePeers *>(area->d_peer_table),
+        starts, avail_mask);
+    return kvcm::LaunchStatus();
+}
+
+int32_t kvcm_b200_route_collect(kvcm_b200_route_area_t *area, const int32_t *d_pos, int64_t n, uint8_t *d_flags_out,
+                                kvcm_stream_t stream) {
+    if (area == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (n < 0 || static_cast<uint64_t>(n) > area->capacity) return KVCM_EC_BADARGS;
+    return kvcm_b200_gather_bytes(area->answers, d_pos, n, d_flags_out, stream);
 }
 
 int32_t kvcm_b200_match_sw(kvcm_b200_index_t *ix, const int64_t *d_keys, const int64_t *d_key_off, int32_t n_req,

@@ -102,6 +102,33 @@ class CudaShardBackend:
                    self.index._s())
         return out
 
+    # ---- routed exchange over peer memory ----
+    def route_area_create(self, capacity_keys):
+        import ctypes
+        area = ctypes.c_void_p()
+        _cabi.bind_device(self.device.index)
+        _cabi.call("kvcm_b200_route_area_create", int(capacity_keys), ctypes.byref(area))
+        return area
+
+    def route_area_destroy(self, area):
+        _cabi.call("kvcm_b200_route_area_destroy", area)
+
+    def route_dispatch(self, area, keys, matrix):
+        cursor = torch.empty(matrix.shape[0], dtype=torch.int32, device=self.device)
+        pos = torch.empty(keys.numel(), dtype=torch.int32, device=self.device)
+        _cabi.call("kvcm_b200_route_dispatch", area, keys.data_ptr(), keys.numel(), matrix.ctypes.data,
+                   cursor.data_ptr(), pos.data_ptr(), self.index._s())
+        return pos
+
+    def route_answer(self, area, matrix):
+        _cabi.call("kvcm_b200_route_answer", self.index.handle, area, matrix.ctypes.data, self.avail_mask,
+                   self.index._s())
+
+    def route_collect(self, area, pos):
+        out = torch.empty(pos.numel(), dtype=torch.uint8, device=self.device)
+        _cabi.call("kvcm_b200_route_collect", area, pos.data_ptr(), pos.numel(), out.data_ptr(), self.index._s())
+        return out
+
     def sw_direct(self, keys, key_off, sw):
         n_req = key_off.numel() - 1
         out = torch.empty(n_req, dtype=torch.int32, device=self.device)
@@ -132,17 +159,62 @@ class ShardedMetaSearcher:
     mode "peer":     after `attach_peers()` every rank probes the owner shard of each key directly over NVLink
                      (CUDA IPC mappings, plain peer loads): queries need no collective at all; only writes do.
     mode "route":    every key goes to its owner and one flag byte comes back (two all-to-alls per batch of
-                     requests, shared by the prefix and the window query when `Route()` is called once)."""
+                     requests, shared by the prefix and the window query when `Route()` is called once).
+    mode "route_peer": the same exchange without a transport: after `attach_route_areas()` the dispatch kernel
+                     stores the keys into the owners' inboxes and the owners store the flag bytes back, both
+                     over NVLink peer memory; the ranks meet at two one-word all-reduces per batch.
+                     `route_capacity` = keys one inbox / answer buffer holds (at least the largest batch of a
+                     rank, plus the imbalance of the split); `route_areas` = batches that may be in flight at
+                     once (one per stream the caller routes on)."""
 
-    def __init__(self, backend, group: Optional[dist.ProcessGroup] = None, mode: str = "exchange"):
+    def __init__(self, backend, group: Optional[dist.ProcessGroup] = None, mode: str = "exchange",
+                 route_capacity: int = 0, route_areas: int = 1):
         self.backend = backend
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         self.device = backend.device
         self.mode = mode
+        self.areas = []
         if mode == "peer":
             self.attach_peers()
+        if mode == "route_peer":
+            self.attach_route_areas(route_capacity, route_areas)
+
+    def attach_route_areas(self, capacity_keys: int, count: int = 1) -> None:
+        """Allocate `count` exchange areas, exchange their IPC handles and map the peers' (one-time set-up)."""
+        import ctypes
+        if capacity_keys <= 0:
+            raise _cabi.KvcmError(_cabi.KVCM_EC_BADARGS, "attach_route_areas: route_capacity")
+        asked = [None] * self.world  # one capacity for all ranks: the largest any of them asks for
+        dist.all_gather_object(asked, int(capacity_keys), group=self.group)
+        capacity_keys = max(asked)
+        self._tick = torch.zeros(1, dtype=torch.int32, device=self.device)
+        for _ in range(count):
+            area = self.backend.route_area_create(capacity_keys)
+            exp = _cabi.RouteExport()
+            _cabi.call("kvcm_b200_route_area_export", area, ctypes.byref(exp))
+            blobs = [None] * self.world
+            dist.all_gather_object(blobs, bytes(exp), group=self.group)
+            arr = (_cabi.RouteExport * self.world)()
+            for r, blob in enumerate(blobs):
+                ctypes.memmove(ctypes.addressof(arr[r]), blob, ctypes.sizeof(_cabi.RouteExport))
+            _cabi.bind_device(self.device.index)
+            _cabi.call("kvcm_b200_route_area_attach", area, self.world, self.rank, arr)
+            self.areas.append(area)
+        self.mode = "route_peer"
+
+    def detach_route_areas(self) -> None:
+        """Unmap the peers' areas and free this rank's; every rank calls it, with no batch in flight."""
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        for area in self.areas:
+            _cabi.call("kvcm_b200_route_area_detach", area)
+        dist.barrier(group=self.group)
+        for area in self.areas:
+            self.backend.route_area_destroy(area)
+        self.areas = []
+        self.mode = "exchange"
 
     def attach_peers(self) -> None:
         """Exchange the shards' IPC handles and map every shard into this process (one-time set-up)."""
@@ -216,14 +288,23 @@ class ShardedMetaSearcher:
         return torch.cat([out[r * seg.numel(): r * seg.numel() + c] for r, c in enumerate(counts)])
 
     # ---- route --------------------------------------------------------------------------------
-    def Route(self, keys: torch.Tensor, key_off: torch.Tensor, mask_off: Optional[torch.Tensor] = None
-              ) -> RoutedFlags:
-        """Dispatch this rank's keys to their owners, look them up there, combine the answers back in key order."""
+    def Route(self, keys: torch.Tensor, key_off: torch.Tensor, mask_off: Optional[torch.Tensor] = None,
+              area: int = 0) -> RoutedFlags:
+        """Dispatch this rank's keys to their owners, look them up there, combine the answers back in key order.
+        `area` (mode "route_peer") picks the exchange area: batches in flight at once use different ones, and
+        every rank routes its batches in the same order."""
         keys, key_off = keys.contiguous(), key_off.contiguous()
         counts = self.backend.route_count(keys, self.world)
         matrix = torch.empty(self.world * self.world, dtype=torch.int32, device=self.device)
         dist.all_gather_into_tensor(matrix, counts, group=self.group)
         matrix = matrix.view(self.world, self.world).cpu()
+        if self.mode == "route_peer":
+            h_counts = np.ascontiguousarray(matrix.numpy().astype(np.uint32))
+            pos = self.backend.route_dispatch(self.areas[area], keys, h_counts)
+            dist.all_reduce(self._tick, group=self.group)  # every rank's keys have landed
+            self.backend.route_answer(self.areas[area], h_counts)
+            dist.all_reduce(self._tick, group=self.group)  # every owner's answers have landed
+            return RoutedFlags(self.backend.route_collect(self.areas[area], pos), key_off, mask_off)
         send = matrix[self.rank].tolist()      # my keys per owner
         recv = matrix[:, self.rank].tolist()   # keys I own, per asking rank
         cursor = (torch.cumsum(counts, 0, dtype=torch.int32) - counts).contiguous()
@@ -252,7 +333,7 @@ class ShardedMetaSearcher:
                     ) -> torch.Tensor:
         if self.mode == "peer":  # the attached handle resolves every key at its owner: a purely local call
             return self.backend.prefix_owned(keys.contiguous(), key_off.contiguous(), mask_off, 1, 0)
-        if self.mode == "route" or isinstance(keys, RoutedFlags):
+        if self.mode in ("route", "route_peer") or isinstance(keys, RoutedFlags):
             r = keys if isinstance(keys, RoutedFlags) else self.Route(keys, key_off, mask_off)
             return self.backend.prefix_from_flags(r.flags, r.key_off, r.mask_off)
         g = keys if isinstance(keys, GatheredRequests) else self.Gather(keys, key_off, mask_off)
@@ -266,7 +347,7 @@ class ShardedMetaSearcher:
             raise _cabi.KvcmError(_cabi.KVCM_EC_BADARGS, "ReverseRollSlideWindowMatch")
         if self.mode == "peer":
             return self.backend.sw_direct(keys.contiguous(), key_off.contiguous(), sw_size)
-        if self.mode == "route" or isinstance(keys, RoutedFlags):
+        if self.mode in ("route", "route_peer") or isinstance(keys, RoutedFlags):
             r = keys if isinstance(keys, RoutedFlags) else self.Route(keys, key_off, None)
             return self.backend.sw_from_flags(r.flags, r.key_off, sw_size)
         g = keys if isinstance(keys, GatheredRequests) else self.Gather(keys, key_off, None)

@@ -150,6 +150,50 @@ def test_routing_kernels_dispatch_to_owners_and_combine_in_key_order():
     assert shards[0].route_scatter(none, count, torch.zeros(count, dtype=torch.int32, device=DEV))[1].numel() == 0
 
 
+def test_peer_memory_exchange_between_areas_of_one_process():
+    """Three ranks' exchange areas on one GPU, attached to each other: dispatch of every rank, then answer of every
+    rank, then collect, as the ranks of a box do between their meeting points."""
+    import ctypes
+    present, _ = _world(37)
+    rng = np.random.default_rng(5)
+    full = oracle.Index()
+    full.put_uniform(present)
+    count = 3
+    shards = [CudaShardBackend(len(present), torch.device(DEV)) for _ in range(count)]
+    for r, sh in enumerate(shards):
+        sh.upsert_owned(torch.from_numpy(present).to(DEV), encode_locations([(3, 4)]), count, r)
+    areas = [sh.route_area_create(9000) for sh in shards]
+    handles = (ctypes.c_void_p * count)(*[a.value for a in areas])
+    for r, a in enumerate(areas):
+        _cabi.call("kvcm_b200_route_area_attach_local", a, count, r, handles)
+    for sizes in ((5000, 0, 7777), (1, 2, 3), (9000, 9000, 4096), (9216, 9216, 9216), (9216, 9216, 9100)):
+        batches = []
+        for n in sizes:  # ragged batches: hits, misses and repeated keys
+            k = rng.choice(present, size=n)
+            miss = rng.random(n) < 0.3
+            k[miss] = rng.integers(-(1 << 62), 1 << 62, size=int(miss.sum()), dtype=np.int64)
+            batches.append(k)
+        dks = [torch.from_numpy(k).to(DEV) for k in batches]
+        matrix = np.stack([sh.route_count(dk, count).cpu().numpy() for sh, dk in zip(shards, dks)]).astype(np.uint32)
+        if matrix.sum(0).max() > 9216:  # an inbox would overflow: refused on every rank, nothing launched
+            with pytest.raises(_cabi.KvcmError):
+                shards[0].route_dispatch(areas[0], dks[0], matrix)
+            continue
+        pos = [sh.route_dispatch(a, dk, matrix) for sh, a, dk in zip(shards, areas, dks)]
+        for sh, a in zip(shards, areas):
+            sh.route_answer(a, matrix)
+        for r, (sh, a) in enumerate(zip(shards, areas)):
+            flags = sh.route_collect(a, pos[r])
+            assert np.array_equal(flags.cpu().numpy(), full.batch_get(batches[r]))
+            p = pos[r].cpu().numpy()
+            assert np.array_equal(np.sort(p), np.arange(len(p)))
+    torch.cuda.synchronize()
+    for a in areas:
+        _cabi.call("kvcm_b200_route_area_detach", a)
+    for sh, a in zip(shards, areas):
+        sh.route_area_destroy(a)
+
+
 def _rank_main(rank, port, results, mode):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -158,7 +202,7 @@ def _rank_main(rank, port, results, mode):
     dist.init_process_group("nccl", rank=rank, world_size=2, device_id=dev)
     try:
         present, reqs = _world(9)
-        searcher = ShardedMetaSearcher(CudaShardBackend(len(present), dev), mode=mode)
+        searcher = ShardedMetaSearcher(CudaShardBackend(len(present), dev), mode=mode, route_capacity=1 << 16)
         searcher.upsert(torch.from_numpy(present[rank::2].copy()).to(dev), encode_locations([(3, 4)]))
         keys, off, mask = (torch.from_numpy(a).to(dev) for a in reqs[rank])
         out = {
@@ -167,7 +211,7 @@ def _rank_main(rank, port, results, mode):
             "prefix_masked": searcher.PrefixMatch(keys, off, mask).cpu().numpy(),
             "sw4": searcher.ReverseRollSlideWindowMatch(keys, off, sw_size=4).cpu().numpy(),
         }
-        if mode == "route":  # one dispatch / combine serves both queries
+        if mode in ("route", "route_peer"):  # one dispatch / combine serves both queries
             routed = searcher.Route(keys, off, mask)
             assert np.array_equal(searcher.PrefixMatch(routed).cpu().numpy(), out["prefix_masked"])
             assert np.array_equal(searcher.ReverseRollSlideWindowMatch(routed, sw_size=4).cpu().numpy(), out["sw4"])
@@ -175,12 +219,14 @@ def _rank_main(rank, port, results, mode):
         results[rank] = out
         if mode == "peer":
             searcher.detach_peers()  # nobody frees a shard while a peer still maps it
+        if mode == "route_peer":
+            searcher.detach_route_areas()
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("mode", ["exchange", "peer", "route"])
+@pytest.mark.parametrize("mode", ["exchange", "peer", "route", "route_peer"])
 def test_two_nccl_ranks_match_the_unsharded_oracle(mode):
     import torch.multiprocessing as mp
     with socket.socket() as s:
