@@ -413,10 +413,20 @@ __global__ void __launch_bounds__(kRouteThreads)
     if (threadIdx.x < kMaxShards) local[threadIdx.x] = 0;
     __syncthreads();
     const int64_t base = static_cast<int64_t>(blockIdx.x) * kRouteKeysPerCta;
-    for (int64_t i = base + threadIdx.x; i < base + kRouteKeysPerCta && i < n; i += kRouteThreads) {
-        const uint32_t owner = OwnerOf(static_cast<uint64_t>(keys[i]), shards);
-        const uint32_t same = __match_any_sync(__activemask(), owner);  // one atomic per owner and warp
-        if (LaneId() == static_cast<uint32_t>(__ffs(same)) - 1u) atomicAdd(&local[owner], __popc(same));
+    constexpr int kPerThread = kRouteKeysPerCta / kRouteThreads;
+    int64_t key[kPerThread];
+#pragma unroll
+    for (int j = 0; j < kPerThread; ++j) {  // all loads of the thread in flight before the first vote
+        const int64_t i = base + j * kRouteThreads + threadIdx.x;
+        key[j] = i < n ? keys[i] : 0;
+    }
+#pragma unroll
+    for (int j = 0; j < kPerThread; ++j) {
+        if (base + j * kRouteThreads + threadIdx.x < n) {
+            const uint32_t owner = OwnerOf(static_cast<uint64_t>(key[j]), shards);
+            const uint32_t same = __match_any_sync(__activemask(), owner);  // one atomic per owner and warp
+            if (LaneId() == static_cast<uint32_t>(__ffs(same)) - 1u) atomicAdd(&local[owner], __popc(same));
+        }
     }
     __syncthreads();
     if (threadIdx.x < shards && local[threadIdx.x] != 0) atomicAdd(&counts[threadIdx.x], local[threadIdx.x]);
@@ -531,10 +541,14 @@ __global__ void __launch_bounds__(kRouteThreads)
     uint32_t rank_in_cta[kPerThread];
     uint32_t owner[kPerThread];
 #pragma unroll
+    for (int j = 0; j < kPerThread; ++j) {  // all loads of the thread in flight before the first vote
+        const int64_t i = base + j * kRouteThreads + threadIdx.x;
+        key[j] = i < n ? keys[i] : 0;
+    }
+#pragma unroll
     for (int j = 0; j < kPerThread; ++j) {
         const int64_t i = base + j * kRouteThreads + threadIdx.x;
         if (i < n) {
-            key[j] = keys[i];
             owner[j] = OwnerOf(static_cast<uint64_t>(key[j]), shards);
             const uint32_t same = __match_any_sync(__activemask(), owner[j]);
             const int leader = __ffs(same) - 1;

@@ -62,7 +62,11 @@ class BlockIndex:
             _cabi.lib().kvcm_b200_index_destroy(self._h)
             self._h = None
 
-    __del__ = close
+    def __del__(self):
+        try:
+            self.close()
+        except TypeError:  # interpreter shutdown: the module globals are gone, and so is the CUDA context
+            pass
 
     @property
     def handle(self):
