@@ -1626,14 +1626,216 @@ def main_hash_reference(args):
                       "gpu_launches": 0}))
 
 
+def _route_workload(n_ranks, keys_per_rank, seed=0xB2000007):
+    """Per emulated rank: requests of 64-512 keys whose keys are stored with probability 0.8 in runs (so that
+    prefixes and windows exist), as int64 arrays.  Returns (stored keys, [(keys, key_off)] per rank)."""
+    rng = np.random.default_rng(seed)
+    stored, batches = [], []
+    for _ in range(n_ranks):
+        lens = rng.integers(64, 513, size=keys_per_rank // 288 + 1)
+        off = np.zeros(len(lens) + 1, dtype=np.int64)
+        np.cumsum(lens, out=off[1:])
+        keys = rng.integers(-(1 << 62), 1 << 62, size=int(off[-1]), dtype=np.int64)
+        run = np.repeat(rng.random(len(keys) // 16 + 1) < 0.8, 16)[:len(keys)]  # hits and misses in runs of 16
+        stored.append(keys[run])
+        batches.append((keys, off))
+    return np.concatenate(stored), batches
+
+
+def main_route(args, rank):
+    """The routed exchange's kernels on ONE GPU: R ranks' shards and exchange areas live in one process, attached
+    to each other, and a step runs what the R ranks of a box run between their meeting points - count and dispatch
+    of every rank, answer of every rank, collect and both matchers of every rank.  Peer stores land in this GPU's
+    own memory, so the figures are the kernels' HBM-side cost; the NVLink share is measured by --workload c4."""
+    import ctypes
+
+    import torch
+
+    import tair_kvcache_b200  # noqa: F401
+    from tair_kvcache_b200 import _cabi
+    from tair_kvcache_b200.manager import CudaShardBackend, encode_locations
+
+    if rank != 0:
+        return
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+    torch.cuda.set_device(device)
+    R, per_rank, sw = 8, args.n_requests or 8_000_000, 16
+    stored, batches = _route_workload(R, per_rank)
+    word = encode_locations([(3, 4)])
+    shards = [CudaShardBackend(len(stored) // R * 2 + 1024, device) for _ in range(R)]
+    d_stored = torch.from_numpy(stored).to(device)
+    for r, sh in enumerate(shards):
+        sh.upsert_owned(d_stored, word, R, r)
+    del d_stored
+    d_keys = [torch.from_numpy(k).to(device) for k, _ in batches]
+    d_off = [torch.from_numpy(o).to(device) for _, o in batches]
+    n_keys = sum(len(k) for k, _ in batches)
+    cap = int(max(len(k) for k, _ in batches) * 1.25) + 65536
+    areas = [sh.route_area_create(cap) for sh in shards]
+    handles = (ctypes.c_void_p * R)(*[a.value for a in areas])
+    for r, a in enumerate(areas):
+        _cabi.call("kvcm_b200_route_area_attach_local", a, R, r, handles)
+    matrix = np.stack([sh.route_count(k, R).cpu().numpy() for sh, k in zip(shards, d_keys)]).astype(np.uint32)
+    phase = {"count": 0.0, "dispatch": 0.0, "answer": 0.0, "collect": 0.0, "match_from_flags": 0.0}
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+    out = {}
+
+    def step(timed=False):
+        ev[0].record()
+        for sh, k in zip(shards, d_keys):
+            sh.route_count(k, R)
+        ev[1].record()
+        pos = [sh.route_dispatch(a, k, matrix) for sh, a, k in zip(shards, areas, d_keys)]
+        ev[2].record()
+        for sh, a in zip(shards, areas):
+            sh.route_answer(a, matrix)
+        ev[3].record()
+        flags = [sh.route_collect(a, p) for sh, a, p in zip(shards, areas, pos)]
+        ev[4].record()
+        out["prefix"] = [sh.prefix_from_flags(f, o, None) for sh, f, o in zip(shards, flags, d_off)]
+        out["window"] = [sh.sw_from_flags(f, o, sw) for sh, f, o in zip(shards, flags, d_off)]
+        out["flags"] = flags
+        ev[5].record()
+        if timed:
+            torch.cuda.synchronize(device)
+            for i, k in enumerate(phase):
+                phase[k] += ev[i].elapsed_time(ev[i + 1])
+
+    sampler = ClockSampler(str(torch.cuda.get_device_properties(device).uuid))
+    sampler.start()
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize(device)
+    sampler.mark_begin()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize(device)
+    sampler.mark_end()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+    for _ in range(3):
+        step(timed=True)
+    phase = {k: v / 3 for k, v in phase.items()}
+    prefix0, window0, flags0 = (out["prefix"][0].cpu().numpy(), out["window"][0].cpu().numpy(),
+                                out["flags"][0].cpu().numpy())
+
+    # ---- end to end: every rank's keys start in pinned host memory, its match results end there
+    e2e = None
+    if not args.no_e2e:
+        h_keys = [torch.from_numpy(k).pin_memory() for k, _ in batches]
+        h_out = [torch.empty(2 * (len(o) - 1), dtype=torch.int32).pin_memory() for _, o in batches]
+
+        def e2e_step():
+            for d, h in zip(d_keys, h_keys):
+                d.copy_(h, non_blocking=True)
+            step()
+            for r, h in enumerate(h_out):
+                n_req = h.numel() // 2
+                h[:n_req].copy_(out["prefix"][r], non_blocking=True)
+                h[n_req:].copy_(out["window"][r], non_blocking=True)
+
+        for _ in range(2):
+            e2e_step()
+        torch.cuda.synchronize(device)
+        e0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        e1.record()
+        torch.cuda.synchronize(device)
+        e2e_ms = e0.elapsed_time(e1) / args.steps
+        e2e = {"value": n_keys / (e2e_ms * 1e-3), "unit": "token-blocks/s", "h2d_bytes_per_step": n_keys * 8,
+               "d2h_bytes_per_step": int(sum(h.numel() for h in h_out)) * 4,
+               "parity_ok": bool(np.array_equal(h_out[0][:len(prefix0)].numpy(), prefix0))}
+
+    # ---- parity and CPU side on a sample: the first requests of rank 0 against the unsharded oracle index
+    parity, cpu = None, None
+    if not args.no_cpu:
+        from oracle import kvcm_oracle as oracle
+        threads = os.cpu_count() or 1
+        keys0, off0 = batches[0]
+        m = min(len(off0) - 1, 4096)
+        sk, so = keys0[:int(off0[m])], off0[:m + 1]
+        ox = oracle.Index()
+        ox.put_uniform(sk[np.isin(sk, stored)])  # random 62-bit keys: the sample's keys decide its answers
+        parity = bool(np.array_equal(ox.batch_get(sk), flags0[:len(sk)]) and
+                      np.array_equal(ox.prefix_match_batch(sk, so), prefix0[:m]) and
+                      np.array_equal(ox.sw_match_batch(sk, so, sw), window0[:m]))
+        t_total, n = 0.0, 0
+        while t_total < 5.0 and n < 2000:
+            t0 = time.perf_counter()
+            ox.prefix_match_batch(sk, so, threads=threads)
+            ox.sw_match_batch(sk, so, sw, threads=threads)
+            t_total += time.perf_counter() - t0
+            n += 1
+        cpu = {"value": len(sk) * n / t_total, "unit": "token-blocks/s", "cores": threads, "kind": "port",
+               "sample": "prefix + window match of %d requests (%d keys) of rank 0 on an index holding their stored "
+                         "keys (much smaller than the sharded one, so this over-states the CPU), %d repetitions"
+                         % (m, len(sk), n)}
+    peak, peak_kind = peaks()
+    achieved = n_keys * 20 / (phase["dispatch"] * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "routed_prefix_and_window_match_token_blocks_per_s", "value": n_keys / (ms * 1e-3),
+        "unit": "token-blocks/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
+        "config": {"workload": "%d ranks' shards and exchange areas on one GPU; per rank %d requests of 64-512 keys "
+                               "(%d keys in all, 80 %% stored, %d keys per shard); count + dispatch + answer + collect "
+                               "+ prefix and window (%d) match over the flag bytes; keys (%.2f GB) and shards larger "
+                               "than L2" % (R, len(batches[0][1]) - 1, n_keys, len(stored) // R, sw, n_keys * 8 / 1e9),
+                   "phase_ms": phase, "parity_sample_ok": parity},
+        "roofline": {"bound": "hbm", "kernel": "RouteDispatchKernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                     "algorithmic_bytes_per_launch": n_keys // R * 20, "launch_ms": phase["dispatch"] / R,
+                     "note": "20 B per key: key read, key stored into the owner's inbox, answer position written; the "
+                             "step's longest phase is the answer kernel, bound by random probes"},
+        "e2e": e2e, "cpu_baseline": cpu, "clocks": clocks, "gpu_launches": 6 * R * args.steps}))
+    torch.cuda.synchronize(device)
+    for a in areas:
+        _cabi.call("kvcm_b200_route_area_detach", a)
+    for sh, a in zip(shards, areas):
+        sh.route_area_destroy(a)
+
+
+def main_route_reference(args):
+    """CPU arm of --workload route: the unsharded matchers of the oracle on a bounded sample of one rank's requests
+    (the reference's index is not sharded, so there is nothing to route), all host threads."""
+    from oracle import kvcm_oracle as oracle
+    threads = os.cpu_count() or 1
+    per_rank, sw = min(args.n_requests or 8_000_000, 2_000_000), 16
+    stored, batches = _route_workload(1, per_rank)
+    keys, off = batches[0]
+    ox = oracle.Index()
+    ox.put_uniform(stored)
+    t_total, n = 0.0, 0
+    while t_total < 10.0 and n < 500:
+        t0 = time.perf_counter()
+        ox.prefix_match_batch(keys, off, threads=threads)
+        ox.sw_match_batch(keys, off, sw, threads=threads)
+        t_total += time.perf_counter() - t0
+        n += 1
+    value = len(keys) * n / t_total
+    print(json.dumps({"impl": "reference", "metric": "routed_prefix_and_window_match_token_blocks_per_s",
+                      "value": value, "unit": "token-blocks/s", "n_gpus": args.gpus, "steps": n, "warmup": 0,
+                      "higher_is_better": True, "dtype": "int64", "data": "synthetic",
+                      "config": {"workload": "CPU restatement of prefix + sliding-window match on one unsharded index"},
+                      "cpu_baseline": {"value": value, "unit": "token-blocks/s", "cores": threads, "kind": "port",
+                                       "sample": "%d requests (%d keys) against an index of %d keys, %d repetitions"
+                                                 % (len(off) - 1, len(keys), len(ox), n)},
+                      "e2e": {"value": value, "unit": "token-blocks/s", "h2d_bytes_per_step": 0,
+                              "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c1", "c4", "c5", "lru", "iov", "hash"])
-    ap.add_argument("--n-requests", type=int, default=0, help="c4: override the number of requests")
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c1", "c4", "c5", "lru", "iov", "hash", "route"])
+    ap.add_argument("--n-requests", type=int, default=0,
+                    help="c4: override the number of requests; route: keys per emulated rank (default 8,000,000)")
     ap.add_argument("--index-keys", type=int, default=0, help="c4: override the number of indexed keys")
     ap.add_argument("--shard-mode", default="route_peer", choices=["peer", "exchange", "route", "route_peer"],
                     help="c4 on several GPUs: probe remote shards over NVLink, or exchange keys and reduce results")
@@ -1669,6 +1871,10 @@ def main():
                 main_hash_reference(args)
             return
         main_hash(args, rank, world)
+        return
+    if args.workload == "route":
+        if rank == 0:
+            (main_route_reference(args) if args.impl == "reference" else main_route(args, rank))
         return
     if args.workload == "iov":
         if args.impl == "reference":
