@@ -24,6 +24,7 @@
 #include <functional>
 #include <list>
 #include <memory>
+#include <set>
 #include <thread>
 #include <unordered_map>
 #include <unordered_set>
@@ -564,10 +565,14 @@ void kvcm_oracle_replay_run(void *h, const int64_t *keys, const int64_t *key_off
 // ---------------------------------------------------------------------------------
 // (2c') Optimizer trace replay with LRU eviction
 // ---------------------------------------------------------------------------------
-// Restates, for one instance in a group of its own and the "lru" policy on the shared tier:
+// Restates, for one instance in a group of its own and the "lru" or the "leaf_aware_lru" policy on the
+// shared tier:
 //   RadixTreeIndex InsertNode / SplitNode / PrefixQuery / InsertQuery / CleanEmptyBlocks / WriteToTier
 //     (kv_cache_manager/optimizer/index/radix_tree_index.cc:19-127,129-196,198-282,284-325,327-392),
 //   LruEvictionPolicy (kv_cache_manager/optimizer/eviction_policy/lru.cc:6-49),
+//   LeafAwareLruEvictionPolicy (kv_cache_manager/optimizer/eviction_policy/leaf_aware_lru.cc:20-160) with the
+//     sorted insertions of LinkedList (eviction_policy/common_structure.h:62-89) and RadixTreeNode::isLeaf /
+//     isDataLeaf (kv_cache_manager/optimizer/config/types.h:65-78),
 //   OptEvictionManager::EvictByInstanceRough / EvictByInstancePrecise / GetExcessUsageForInstanceInGroup
 //     (kv_cache_manager/optimizer/manager/eviction_manager.cc:148-239,249-266; with one instance per
 //     group EvictByGroupRough (:86-146) does the same as EvictByInstanceRough),
@@ -578,6 +583,8 @@ void kvcm_oracle_replay_run(void *h, const int64_t *keys, const int64_t *key_off
 // Pins: the recency-order cases of kv_cache_manager/optimizer/test/lru_eviction_policy_test.cc:44-146
 // restated as traces, and the eviction-free replay above when the quota is never reached.  The
 // reference records no end-to-end numbers for tree clean-up under eviction: parity unpinned there.
+// The reference has no test of leaf_aware_lru at all: parity unpinned for that policy; the cases in
+// tests/test_oracle.py were worked out by hand from the cited source lines.
 
 namespace {
 
@@ -585,30 +592,49 @@ struct LruNode;
 struct LruBlock {
     int64_t key = 0;
     bool cached = false;  // location_map non-empty
+    bool listed = false;  // has a position in the recency list (always while cached under "lru")
+    int64_t time = -1;    // last_access_time
     LruNode *owner = nullptr;
-    std::list<LruBlock *>::iterator where;  // position in the recency list while cached
+    std::list<LruBlock *>::iterator where;  // position in the recency list while listed
 };
 struct LruNode {
     LruNode *parent = nullptr;
     std::vector<std::unique_ptr<LruBlock>> blocks;
     std::unordered_map<int64_t, std::unique_ptr<LruNode>> children;
     bool leaf() const { return children.empty(); }
+    bool data_leaf() const {  // types.h:68-78: no immediate child holds a cached block
+        for (const auto &c : children) {
+            for (const auto &b : c.second->blocks) {
+                if (b->cached) return false;
+            }
+        }
+        return true;
+    }
 };
 
 struct OracleLruReplay {
     std::unique_ptr<LruNode> root{new LruNode()};
     std::list<LruBlock *> recency;  // front = most recently written or accessed
+    int64_t n_cached = 0;           // EvictionPolicy::size(): blocks the policy knows (node_map_)
     int64_t quota = 0;
     int32_t batch = 1;
     bool precise = false;
+    bool leaf_aware = false;
+    int64_t now = 0;  // timestamp of the trace being replayed
 
-    void on_written(LruBlock *b) {  // lru.cc:6-11
+    void on_written(LruBlock *b) {  // lru.cc:6-11; leaf_aware_lru.cc:20-31; times: radix_tree_index.cc:335-336,366-367
         b->cached = true;
+        b->time = now;
+        ++n_cached;
+        if (leaf_aware && !(b->owner != nullptr && b->owner->leaf())) return;  // only blocks of leaves queue up
         recency.push_front(b);
         b->where = recency.begin();
+        b->listed = true;
     }
-    void on_accessed(LruBlock *b) {  // lru.cc:18-26
+    void on_accessed(LruBlock *b) {  // lru.cc:18-26; leaf_aware_lru.cc:39-51
         if (!b->cached) return;
+        b->time = now;
+        if (!b->listed) return;
         recency.splice(recency.begin(), recency, b->where);
         b->where = recency.begin();
     }
@@ -722,12 +748,76 @@ struct OracleLruReplay {
         }
     }
     std::vector<LruBlock *> evict_blocks(int64_t count) {  // lru.cc:28-49
+        if (leaf_aware) return evict_leaf_blocks(count);
         std::vector<LruBlock *> out;
         for (int64_t i = 0; i < count && !recency.empty(); ++i) {
             LruBlock *b = recency.back();
             recency.pop_back();
             b->cached = false;
+            b->listed = false;
+            --n_cached;
             out.push_back(b);
+        }
+        return out;
+    }
+    // LinkedList::insert_sorted / insert_sorted_reverse with LeafLRUListNode::compare (a before b while
+    // a's time is smaller), chosen as insert_sorted_by_priority does (leaf_aware_lru.cc:53-83).
+    void insert_by_time(LruBlock *b) {
+        std::list<LruBlock *>::iterator at;
+        if (recency.empty()) {
+            at = recency.end();
+        } else {
+            const int64_t head = recency.front()->time, tail = recency.back()->time, t = b->time;
+            bool from_head;
+            if (t >= head) {
+                from_head = true;
+            } else if (t <= tail) {
+                from_head = false;
+            } else {
+                from_head = (head - t) < (t - tail);
+            }
+            if (from_head) {
+                at = recency.begin();
+                while (at != recency.end() && t < (*at)->time) ++at;
+            } else {
+                auto r = recency.rbegin();
+                while (r != recency.rend() && (*r)->time < t) ++r;
+                at = r.base();  // the position right after *r
+            }
+        }
+        b->where = recency.insert(at, b);
+        b->listed = true;
+    }
+    bool update_node_state(LruNode *node) {  // leaf_aware_lru.cc:135-160
+        if (node == nullptr || !node->data_leaf()) return false;
+        bool any = false;
+        for (const auto &b : node->blocks) {
+            if (b->cached && !b->listed) {
+                insert_by_time(b.get());
+                any = true;
+            }
+        }
+        return any;
+    }
+    std::vector<LruBlock *> evict_leaf_blocks(int64_t count) {  // leaf_aware_lru.cc:85-133
+        std::vector<LruBlock *> out;
+        std::set<LruNode *> done;
+        while (static_cast<int64_t>(out.size()) < count && !recency.empty()) {
+            LruBlock *b = recency.back();
+            LruNode *owner = b->owner;
+            if (owner != nullptr && !owner->data_leaf()) {  // its node got cached children since: leave the queue
+                recency.pop_back();
+                b->listed = false;
+                continue;
+            }
+            recency.pop_back();
+            b->listed = false;
+            b->cached = false;
+            --n_cached;
+            out.push_back(b);
+            if (owner != nullptr && owner->parent != nullptr && done.count(owner->parent) == 0) {
+                if (update_node_state(owner->parent)) done.insert(owner->parent);
+            }
         }
         return out;
     }
@@ -754,7 +844,7 @@ struct OracleLruReplay {
         }
     }
     void check_and_evict() {  // indexer_manager.cc:55-90, eviction_manager.cc:148-266
-        const int64_t used = static_cast<int64_t>(recency.size());
+        const int64_t used = n_cached;
         const int64_t excess = used > quota ? used - quota : 0;
         if (excess == 0) return;
         std::vector<LruBlock *> all;
@@ -781,15 +871,26 @@ void *kvcm_oracle_lru_replay_create(int64_t quota_blocks, int32_t evict_batch, i
     st->precise = precise != 0;
     return st;
 }
+// policy: 0 = "lru", 1 = "leaf_aware_lru"
+void *kvcm_oracle_lru_replay_create_policy(int64_t quota_blocks, int32_t evict_batch, int32_t precise,
+                                           int32_t policy) {
+    auto *st = static_cast<OracleLruReplay *>(kvcm_oracle_lru_replay_create(quota_blocks, evict_batch, precise));
+    st->leaf_aware = policy == 1;
+    return st;
+}
 void kvcm_oracle_lru_replay_destroy(void *h) { delete static_cast<OracleLruReplay *>(h); }
 
 // Same trace encoding and outputs as kvcm_oracle_replay_run; cache_blocks[t] is the number of cached
 // blocks after trace t (EvictionPolicy::size(), after CheckAndEvict for the writing kinds).
-void kvcm_oracle_lru_replay_run(void *h, const int64_t *keys, const int64_t *key_off, const uint8_t *type,
-                                const int64_t *mask_off, const uint8_t *mask_bits, int64_t n_traces, int32_t *ext_hit,
-                                int32_t *int_hit, int32_t *written, int64_t *cache_blocks) {
+// timestamps (optional): the traces' timestamp_us, which "leaf_aware_lru" orders re-queued blocks by; the
+// trace number stands in when it is null.
+void kvcm_oracle_lru_replay_run_ts(void *h, const int64_t *keys, const int64_t *key_off, const uint8_t *type,
+                                   const int64_t *mask_off, const uint8_t *mask_bits, const int64_t *timestamps,
+                                   int64_t n_traces, int32_t *ext_hit, int32_t *int_hit, int32_t *written,
+                                   int64_t *cache_blocks) {
     auto *st = static_cast<OracleLruReplay *>(h);
     for (int64_t t = 0; t < n_traces; ++t) {
+        st->now = timestamps ? timestamps[t] : t;
         const int64_t *k = keys + key_off[t];
         const int64_t n = key_off[t + 1] - key_off[t];
         int32_t ext = 0, inte = 0;
@@ -807,8 +908,14 @@ void kvcm_oracle_lru_replay_run(void *h, const int64_t *keys, const int64_t *key
         ext_hit[t] = ext;
         int_hit[t] = inte;
         written[t] = static_cast<int32_t>(wr);
-        cache_blocks[t] = static_cast<int64_t>(st->recency.size());
+        cache_blocks[t] = st->n_cached;
     }
+}
+void kvcm_oracle_lru_replay_run(void *h, const int64_t *keys, const int64_t *key_off, const uint8_t *type,
+                                const int64_t *mask_off, const uint8_t *mask_bits, int64_t n_traces, int32_t *ext_hit,
+                                int32_t *int_hit, int32_t *written, int64_t *cache_blocks) {
+    kvcm_oracle_lru_replay_run_ts(h, keys, key_off, type, mask_off, mask_bits, nullptr, n_traces, ext_hit, int_hit,
+                                  written, cache_blocks);
 }
 
 }  // extern "C"

@@ -407,24 +407,28 @@ class Replay:
 
 
 class LruReplay(Replay):
-    """Sequential replay over the compressed prefix tree with the "lru" eviction policy and a block quota
-    (kv_cache_manager/optimizer/index/radix_tree_index.cc, eviction_policy/lru.cc,
+    """Sequential replay over the compressed prefix tree with the "lru" or "leaf_aware_lru" eviction policy and a
+    block quota (kv_cache_manager/optimizer/index/radix_tree_index.cc, eviction_policy/lru.cc, leaf_aware_lru.cc,
     manager/eviction_manager.cc:148-266).  precise=False evicts whole batches of evict_batch blocks until the
     excess is covered (EVICTION_MODE_GROUP_ROUGH / INSTANCE_ROUGH with one instance per group), precise=True
     evicts exactly the excess (INSTANCE_PRECISE)."""
 
-    def __init__(self, quota_blocks, evict_batch=100, precise=False):
-        lib().kvcm_oracle_lru_replay_create.restype = ctypes.c_void_p
-        self._h = ctypes.c_void_p(lib().kvcm_oracle_lru_replay_create(ctypes.c_int64(int(quota_blocks)),
-                                                                      ctypes.c_int32(int(evict_batch)),
-                                                                      ctypes.c_int32(1 if precise else 0)))
+    POLICIES = {"lru": 0, "leaf_aware_lru": 1}
+
+    def __init__(self, quota_blocks, evict_batch=100, precise=False, policy="lru"):
+        lib().kvcm_oracle_lru_replay_create_policy.restype = ctypes.c_void_p
+        self._h = ctypes.c_void_p(lib().kvcm_oracle_lru_replay_create_policy(
+            ctypes.c_int64(int(quota_blocks)), ctypes.c_int32(int(evict_batch)), ctypes.c_int32(1 if precise else 0),
+            ctypes.c_int32(self.POLICIES[policy])))
 
     def __del__(self):
         if getattr(self, "_h", None):
             lib().kvcm_oracle_lru_replay_destroy(self._h)
             self._h = None
 
-    def run(self, keys, key_off, trace_type, mask_off=None, mask_bits=None):
+    def run(self, keys, key_off, trace_type, mask_off=None, mask_bits=None, timestamps=None):
+        """timestamps: the traces' timestamp_us (int64 per trace; the trace number when None).  Only the
+        "leaf_aware_lru" policy reads them."""
         keys, key_off = _i64(keys), _i64(key_off)
         n = len(key_off) - 1
         trace_type = np.ascontiguousarray(trace_type, dtype=np.uint8)
@@ -440,8 +444,12 @@ class LruReplay(Replay):
         if mask_bits is not None:
             mask_bits = np.ascontiguousarray(mask_bits, dtype=np.uint8)
             bp = _ptr(mask_bits, ctypes.c_uint8)
-        lib().kvcm_oracle_lru_replay_run(self._h, _ptr(keys, ctypes.c_int64), _ptr(key_off, ctypes.c_int64),
-                                         _ptr(trace_type, ctypes.c_uint8), mp, bp, ctypes.c_int64(n),
-                                         _ptr(ext, ctypes.c_int32), _ptr(inte, ctypes.c_int32),
-                                         _ptr(wr, ctypes.c_int32), _ptr(cached, ctypes.c_int64))
+        tp = None
+        if timestamps is not None:
+            timestamps = _i64(timestamps)
+            tp = _ptr(timestamps, ctypes.c_int64)
+        lib().kvcm_oracle_lru_replay_run_ts(self._h, _ptr(keys, ctypes.c_int64), _ptr(key_off, ctypes.c_int64),
+                                            _ptr(trace_type, ctypes.c_uint8), mp, bp, tp, ctypes.c_int64(n),
+                                            _ptr(ext, ctypes.c_int32), _ptr(inte, ctypes.c_int32),
+                                            _ptr(wr, ctypes.c_int32), _ptr(cached, ctypes.c_int64))
         return ext, inte, wr, cached

@@ -274,3 +274,68 @@ def test_lru_replay_revives_evicted_blocks_inside_a_node():
     ext, inte, wr, size = oracle.LruReplay(2, evict_batch=1, precise=True).run(
         [1, 2, 3, 4, 1, 2, 3, 4, 1, 2, 3, 4], [0, 4, 8, 12], [W, D, G])
     assert wr.tolist() == [4, 2, 0] and ext.tolist() == [0, 0, 2] and size.tolist() == [2, 2, 2]
+
+
+def _leaf(quota, keys, off, types, ts, batch=1, precise=True):
+    return oracle.LruReplay(quota, evict_batch=batch, precise=precise, policy="leaf_aware_lru").run(
+        keys, off, types, timestamps=ts)
+
+
+def _flat(traces):
+    keys, off = [], [0]
+    for k in traces:
+        keys += k
+        off.append(len(keys))
+    return keys, off
+
+
+def test_leaf_aware_lru_keeps_shared_prefixes():
+    # Worked by hand from kv_cache_manager/optimizer/eviction_policy/leaf_aware_lru.cc:85-133 (no test of this
+    # policy exists in the reference).  [1,2,3] then [1,2,9] splits the node into [1,2] -> {[3], [9]}.  Quota 3:
+    # the queue's cold end holds 1 and 2, whose node now has cached children, so they leave the queue (:101-105)
+    # and 3 goes.  Its emptied leaf is removed (radix_tree_index.cc:284-325).  Plain LRU would have taken 1.
+    keys, off = _flat([[1, 2, 3], [1, 2, 9], [1, 2, 3], [1, 2, 9, 10], [1, 2, 9, 10]])
+    ext, inte, wr, size = _leaf(3, keys, off, [W, W, G, W, G], [0, 1, 2, 3, 4])
+    assert wr.tolist() == [3, 1, 0, 1, 0]
+    assert size.tolist() == [3, 3, 3, 3, 3]
+    # trace 3 appends 10 to the leaf [9]; the queue is then 10, 9 and 9 goes although 10 hangs below it
+    assert ext.tolist() == [0, 0, 2, 0, 2]
+    lru = oracle.LruReplay(3, evict_batch=1, precise=True).run(keys, off, [W, W, G, W, G])
+    assert lru[0].tolist()[2] == 0  # plain LRU drops block 1 first, so the same query finds nothing
+
+
+def test_leaf_aware_lru_requeues_a_parent_by_access_time():
+    # Worked by hand: after [1,2,3] (t=10) and [1,2,9] (t=20) the writes of 5, 6 and 8 overflow a quota of 4 one
+    # block at a time.  t=30: 1 and 2 leave the queue, 3 goes.  t=40: 9 goes, which makes [1,2] a data leaf: its
+    # blocks are put back by last access time (:135-160): 1 lands behind 5, and 2, whose time ties with 1's,
+    # behind 1 (insert_sorted_reverse stops at the first entry that is not younger, common_structure.h:77-89),
+    # so at t=50 it is 2 that goes, not 1.
+    keys, off = _flat([[1, 2, 3], [1, 2, 9], [5], [6], [8], [1, 2], [1, 2, 3], [5], [8], [1, 2, 3]])
+    types = [W, W, W, W, W, G, D, G, G, G]
+    ts = [10, 20, 30, 40, 50, 60, 70, 80, 90, 100]
+    ext, inte, wr, size = _leaf(4, keys, off, types, ts)
+    assert wr.tolist() == [3, 1, 1, 1, 1, 0, 2, 0, 0, 0]
+    assert size.tolist() == [3, 4, 4, 4, 4, 4, 4, 4, 4, 4]
+    # trace 6 (a dialog turn) hits 1, rewrites 2 inside the node and appends 3 to it (a leaf again); 5 and 6 go
+    assert ext.tolist() == [0, 0, 0, 0, 0, 1, 1, 0, 1, 3]
+
+
+def test_leaf_aware_lru_with_room_for_everything_is_the_plain_replay():
+    rng = np.random.default_rng(5)
+    prompts = [rng.integers(1, 1 << 60, size=int(rng.integers(1, 30))) for _ in range(8)]
+    keys, off, types, mo = [], [0], [], []
+    for t in range(400):
+        p = prompts[int(rng.integers(0, len(prompts)))]
+        k = list(p[:int(rng.integers(0, len(p) + 1))]) + [int(x) for x in rng.integers(1 << 61, 1 << 62, size=3)]
+        ty = int(rng.integers(0, 3))
+        keys += k
+        off.append(len(keys))
+        types.append(ty)
+        mo.append(int(rng.integers(0, len(k))) if ty == G else 0)
+    want = oracle.Replay().run(keys, off, types, mo)
+    got = oracle.LruReplay(1 << 40, policy="leaf_aware_lru").run(keys, off, types, mo)
+    for a, b in zip(want, got):
+        assert np.array_equal(a, b)
+    tight = oracle.LruReplay(20, evict_batch=4, policy="leaf_aware_lru").run(keys, off, types, mo)
+    lru = oracle.LruReplay(20, evict_batch=4).run(keys, off, types, mo)
+    assert not np.array_equal(tight[0], want[0]) and not np.array_equal(tight[0], lru[0])
