@@ -1191,13 +1191,15 @@ def main_lru(args, rank, world):
     d_type = torch.full((n_req,), TRACE_DIALOG_TURN, dtype=torch.uint8, device=device)
     all_quotas = _lru_quotas(n_keys, n_cfg * world)
     quotas = all_quotas[rank::world]  # every rank gets points from the whole range
-    workspace = torch.empty(replay_lru_workspace_bytes(n_keys, n_cfg), dtype=torch.uint8, device=device)
+    policy = args.policy
+    workspace = torch.empty(replay_lru_workspace_bytes(n_keys, n_cfg, policy, n_req), dtype=torch.uint8,
+                            device=device)
     status = torch.zeros(4, dtype=torch.int32, device=device)
 
     def step():
         keys = GenKeyVectorBatch(toks, d_off, bs, d_ko, n_keys, out=d_keys, order=d_order, warps_per_sm=residency)
         return RunTracesLru(keys, d_ko, d_type, quotas, evict_batch=100, precise=False, workspace=workspace,
-                            status=status)
+                            status=status, policy=policy)
 
     sampler = ClockSampler(str(torch.cuda.get_device_properties(device).uuid)) if rank == 0 else None
     if sampler:
@@ -1225,7 +1227,8 @@ def main_lru(args, rank, world):
     # the sweep kernel alone
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e2.record()
-    RunTracesLru(d_keys, d_ko, d_type, quotas, evict_batch=100, precise=False, workspace=workspace, status=status)
+    RunTracesLru(d_keys, d_ko, d_type, quotas, evict_batch=100, precise=False, workspace=workspace, status=status,
+                 policy=policy)
     e3.record()
     torch.cuda.synchronize(device)
     sweep_ms = e2.elapsed_time(e3)
@@ -1241,19 +1244,20 @@ def main_lru(args, rank, world):
         m = min(n_req, 20000)  # the sequential CPU replay of the first requests sees the same history
         k = d_keys[:int(ko[m])].cpu().numpy()
         c = len(quotas) // 3
-        want = oracle.LruReplay(quotas[c], evict_batch=100, precise=False).run(k, ko[:m + 1], np.zeros(m, np.uint8))
+        want = oracle.LruReplay(quotas[c], evict_batch=100, precise=False, policy=policy).run(
+            k, ko[:m + 1], np.zeros(m, np.uint8))
         parity = bool(np.array_equal(want[0], res.external_hit_blocks[c, :m].cpu().numpy()) and
                       np.array_equal(want[2], res.write_blocks[c, :m].cpu().numpy()) and
                       np.array_equal(want[3], res.current_cache_blocks[c, :m].cpu().numpy()))
     if rank == 0:
         replays = n_req * n_cfg * world
         print(json.dumps({
-            "metric": "lru_tradeoff_sweep_request_replays_per_s", "value": replays / (ms / 1e3),
+            "metric": "%s_tradeoff_sweep_request_replays_per_s" % policy, "value": replays / (ms / 1e3),
             "unit": "request-replays/s", "n_gpus": world, "steps": steps, "warmup": max(1, min(args.warmup, 3)),
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "int64", "data": "synthetic",
             "config": {"workload": "%d requests (dialog turns, 256-2048 uint32 tokens, block 64, Zipf(0.9) prefix "
-                                   "reuse over 10000 prompts = %d token blocks) replayed with LRU eviction at %d quota "
+                                   "reuse over 10000 prompts = %d token blocks) replayed with " + policy + " eviction at %d quota "
                                    "points per GPU (%d..%d blocks, rough mode, batches of 100); hash + sweep per step"
                                    % (n_req, n_keys, n_cfg, min(all_quotas), max(all_quotas)),
                        "sweep_kernel_ms_rank0": sweep_ms, "hit_rate_lowest_quota": float(hit_rate[0]),
@@ -1288,7 +1292,7 @@ def main_lru_reference(args):
     quotas = _lru_quotas(int(ko[-1]), n_cfg)
 
     def one(q):
-        return int(oracle.LruReplay(q, evict_batch=100, precise=False).run(keys, ko, types)[0].sum())
+        return int(oracle.LruReplay(q, evict_batch=100, precise=False, policy=args.policy).run(keys, ko, types)[0].sum())
 
     with ThreadPoolExecutor(max_workers=threads) as pool:
         hits = list(pool.map(one, quotas))
@@ -1296,11 +1300,12 @@ def main_lru_reference(args):
     value = n_req * n_cfg / dt
     sample = "first %d of %d requests (%d token blocks), %d quota points, hit blocks %d..%d" % (
         n_req, n_req_full, int(ko[-1]), n_cfg, min(hits), max(hits))
-    print(json.dumps({"impl": "reference", "metric": "lru_tradeoff_sweep_request_replays_per_s", "value": value,
+    print(json.dumps({"impl": "reference", "metric": "%s_tradeoff_sweep_request_replays_per_s" % args.policy,
+                      "value": value,
                       "unit": "request-replays/s", "n_gpus": args.gpus, "steps": 1, "warmup": 0,
                       "higher_is_better": True, "dtype": "int64", "data": "synthetic",
-                      "config": {"workload": "CPU restatement (hash + radix tree with LRU eviction, one quota point "
-                                             "per thread) on a bounded sample"},
+                      "config": {"workload": "CPU restatement (hash + radix tree with %s eviction, one quota point "
+                                             "per thread) on a bounded sample" % args.policy},
                       "cpu_baseline": {"value": value, "unit": "request-replays/s", "cores": threads, "kind": "port",
                                        "sample": sample},
                       "e2e": {"value": value, "unit": "request-replays/s", "h2d_bytes_per_step": 0,
@@ -1846,6 +1851,8 @@ def main():
                          "(default 0.5; 0.7 for the routed shard modes, whose head is routed after the rest)")
     ap.add_argument("--request-tokens", type=int, default=0, help="hash: tokens per request (default 20970)")
     ap.add_argument("--n-configs", type=int, default=0, help="lru: quota points per GPU (default 148)")
+    ap.add_argument("--policy", default="lru", choices=["lru", "leaf_aware_lru"],
+                    help="lru: the eviction policy of the sweep (eviction_policy_type)")
     ap.add_argument("--no-prefix", action="store_true", help="skip the prefix-match side measurement")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-staging leg (profiling runs)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")

@@ -505,7 +505,7 @@ KVCM_API int32_t kvcm_b200_replay(const int64_t *d_keys, const int64_t *d_key_of
  * independent and run in parallel (one warp each); one configuration is replayed in trace order.
  * d_workspace: kvcm_b200_replay_lru_workspace_bytes(n_keys_total, n_configs) bytes (-1: too large:
  * n_keys_total < 2^32 - 1, n_configs <= 65535), 256-byte aligned, contents irrelevant before and after.
- * Not covered: leaf_aware_lru and random_lru (they depend on the tree shape / a random stream),
+ * Not covered here: leaf_aware_lru (kvcm_b200_replay_leaf_lru below), random_lru (a random stream),
  * several instances sharing one group quota, hierarchical tiers.
  * ---------------------------------------------------------------------------------------- */
 KVCM_API int64_t kvcm_b200_replay_lru_workspace_bytes(int64_t n_keys_total, int32_t n_configs);
@@ -517,6 +517,35 @@ KVCM_API int32_t kvcm_b200_replay_lru(const int64_t *d_keys, const int64_t *d_ke
                                       int32_t *d_ext_hit, int32_t *d_int_hit, int32_t *d_written,
                                       int64_t *d_cache_blocks, int64_t *d_totals, uint32_t *d_status,
                                       kvcm_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * (2c'') The same sweep under the "leaf_aware_lru" eviction policy
+ * (kv_cache_manager/optimizer/eviction_policy/leaf_aware_lru.cc:20-160; chosen by eviction_policy_type in
+ * the optimizer's startup configuration, kv_cache_manager/optimizer/eviction_policy/policy_factory.cc:8-47).
+ * Only blocks of childless tree nodes queue up for eviction; a block whose node has cached children leaves
+ * the queue when it reaches the cold end; a node whose children hold no cached block any more gets its
+ * blocks queued again, placed by last access time.  The tree of RadixTreeIndex
+ * (kv_cache_manager/optimizer/index/radix_tree_index.cc:19-392) is therefore kept per configuration, with
+ * the reference's node splits and its removal of emptied leaves.
+ * Arguments as kvcm_b200_replay_lru, plus d_timestamps (optional, int64 per trace: the traces' timestamp_us,
+ * which order re-queued blocks; the trace number when NULL) and n_traces in the workspace size.
+ * d_status[0] (optional) counts keys the id table refused and walks that hit their iteration limit; non-zero
+ * means the input broke the premise below and the results are void.
+ * Exact for prefix-unique chained keys without repeats inside one trace.  One warp per configuration; list
+ * surgery and eviction run in one lane, so a configuration costs more than under plain LRU.
+ * d_workspace: kvcm_b200_replay_leaf_lru_workspace_bytes(n_keys_total, n_traces, n_configs) bytes
+ * (about 29 bytes per key occurrence and 56 per trace for each configuration; -1: too large), 256-byte aligned.
+ * ---------------------------------------------------------------------------------------- */
+KVCM_API int64_t kvcm_b200_replay_leaf_lru_workspace_bytes(int64_t n_keys_total, int32_t n_traces,
+                                                           int32_t n_configs);
+KVCM_API int32_t kvcm_b200_replay_leaf_lru(const int64_t *d_keys, const int64_t *d_key_off,
+                                           const uint8_t *d_trace_type, const int64_t *d_mask_off,
+                                           const uint8_t *d_mask_bits, const int64_t *d_timestamps, int32_t n_traces,
+                                           int64_t n_keys_total, const int64_t *d_quota_blocks, int32_t n_configs,
+                                           int32_t evict_batch, int32_t precise, void *d_workspace,
+                                           int64_t workspace_bytes, int32_t *d_ext_hit, int32_t *d_int_hit,
+                                           int32_t *d_written, int64_t *d_cache_blocks, int64_t *d_totals,
+                                           uint32_t *d_status, kvcm_stream_t stream);
 
 /* Trace replay for callers that cannot allocate device memory.  (No counterpart in the reference: it
  * exists for how this library gets embedded, not for a reference interface.)

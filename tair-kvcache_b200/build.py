@@ -9,7 +9,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libkvcm_b200.so")
 
 SOURCES = ["runtime.cu", "move_rows.cu", "copy_segments.cu", "hash_blocks.cu", "block_index.cu", "replay.cu",
-           "replay_lru.cu"]
+           "replay_lru.cu", "replay_leaf_lru.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -32,7 +32,7 @@ def is_stale():
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    deps = sources() + [os.path.join(CSRC, "kvcm_common.cuh"), os.path.join(ROOT, "include", "kvcm_b200.h")]
+    deps = sources() + [os.path.join(CSRC, "kvcm_common.cuh"), os.path.join(CSRC, "replay_ids.cuh"), os.path.join(ROOT, "include", "kvcm_b200.h")]
     return any(os.path.getmtime(d) > t for d in deps)
 
 

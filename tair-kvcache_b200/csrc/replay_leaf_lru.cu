@@ -1,0 +1,573 @@
+// Optimizer trace replay with the "leaf_aware_lru" eviction policy, for a sweep of cache quotas at once (sm_100a).
+//
+// Stands in for OptimizerRunner::RunTraces (kv_cache_manager/optimizer/manager/optimizer_runner.cc:29-215) over
+// RadixTreeIndex (kv_cache_manager/optimizer/index/radix_tree_index.cc:19-392) with LeafAwareLruEvictionPolicy
+// (kv_cache_manager/optimizer/eviction_policy/leaf_aware_lru.cc:20-160) and the quota check after every write
+// (OptIndexerManager::CheckAndEvict, kv_cache_manager/optimizer/manager/indexer_manager.cc:55-90;
+// OptEvictionManager, kv_cache_manager/optimizer/manager/eviction_manager.cc:148-266), one instance per group.
+//
+// Unlike plain LRU this policy reads the shape of the tree: only blocks of childless nodes queue up for
+// eviction, a block whose node has cached children is dropped from the queue when it reaches the cold end, and a
+// node whose children have all been emptied gets its blocks queued again, sorted by last access time.  So the
+// tree is kept, per configuration, in a form a warp can walk without pointers.  Keys are prefix-unique chained
+// hashes: a key fixes the key before it.  Hence
+//   pred[id]      the key before id in its chain - the same for every configuration, built once;
+//   node_of[id]   the tree node that holds the block of key id (kNone: not in the tree).  If a key is in the
+//                 tree, so is its whole chain, and a trace's walk down the tree is the run of its leading keys
+//                 with node_of != kNone;
+//   per node      parent, number of children, number of blocks, last key, cached blocks, cached blocks of the
+//                 immediate children (zero = RadixTreeNode::isDataLeaf), cached blocks outside the queue.
+// A node's blocks are pred-steps back from its last key.  Splitting a node (radix_tree_index.cc:89-127) gives
+// the new number to the UPPER part, whose keys are the ones the splitting trace has just walked.
+// The queue is the reference's doubly linked list over key ids (two sentinels), because the sorted re-insertions
+// (kv_cache_manager/optimizer/eviction_policy/common_structure.h:62-89) depend on list order, ties included.
+//
+// One warp per configuration.  Lanes share the scan of a trace's keys, the relabelling at a split and the
+// writes of new blocks; list surgery and eviction are serial in lane 0 (latency-bound on L2).
+// Every walk carries an iteration limit so that keys that break the prefix-unique premise end in a status
+// count, not in an endless loop.
+#include "kvcm_common.cuh"
+#include "replay_ids.cuh"
+
+namespace kvcm {
+namespace {
+
+constexpr uint32_t kNone = 0xFFFFFFFFu;
+constexpr uint8_t kCached = 1, kListed = 2;
+constexpr int kNodeFields = 7;
+
+struct LeafSweep {
+    const uint32_t *ids;
+    const uint32_t *pred;
+    const int64_t *key_off;
+    const uint8_t *type;
+    const int64_t *mask_off;
+    const uint8_t *mask_bits;
+    const int64_t *timestamps;  // optional, per trace; the trace number when null
+    const int64_t *quota;
+    uint32_t *node_of;  // [n_configs][n_keys]
+    uint8_t *flags;     // [n_configs][n_keys]
+    int64_t *time;      // [n_configs][n_keys]  last_access_time
+    uint32_t *lprev;    // [n_configs][n_keys + 2]
+    uint32_t *lnext;    // [n_configs][n_keys + 2]
+    uint32_t *tmp;      // [n_configs][n_keys]  a node's blocks in order, while they are re-queued
+    uint32_t *evicted;  // [n_configs][n_keys]  the blocks evicted after one trace
+    uint32_t *nodes;    // [n_configs][kNodeFields][max_nodes]
+    int32_t *ext_hit, *int_hit, *written;
+    int64_t *cache_blocks;
+    int64_t *totals;
+    uint32_t *status;
+    int64_t n_keys;
+    int64_t max_nodes;
+    int32_t n_traces;
+    int32_t n_configs;
+    int32_t evict_batch;
+    int32_t precise;
+};
+
+__global__ void LeafInitKernel(IdTable t, uint32_t *node_of, uint8_t *flags, uint64_t n_state, uint32_t *pred,
+                               uint64_t n_keys) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    const uint64_t first = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (uint64_t i = first; i <= t.mask; i += stride) t.slots[i] = make_ulonglong2(kEmptyKey, ~0ull);
+    for (uint64_t i = first; i < n_state; i += stride) {
+        node_of[i] = kNone;
+        flags[i] = 0;
+    }
+    for (uint64_t i = first; i < n_keys; i += stride) pred[i] = kNone;
+    if (first == 0) {
+        t.cells[0] = 0ull;
+        t.cells[1] = ~0ull;
+    }
+}
+
+// pred[id of key i] = id of key i - 1 of the same trace.  Every occurrence of a key writes the same value.
+__global__ void __launch_bounds__(256)
+    LeafPredKernel(const uint32_t *__restrict__ ids, const int64_t *__restrict__ key_off, int32_t n_traces,
+                   uint32_t *pred) {
+    const int32_t warps = static_cast<int32_t>(gridDim.x * (blockDim.x >> 5));
+    const uint32_t lane = LaneId();
+    for (int32_t t = static_cast<int32_t>(blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)); t < n_traces;
+         t += warps) {
+        const int64_t beg = key_off[t], end = key_off[t + 1];
+        for (int64_t i = beg + 1 + lane; i < end; i += 32) pred[ids[i]] = ids[i - 1];
+    }
+}
+
+// type: 0 DialogTurn (InsertWithQuery), 1 GetLocation (PrefixQuery), 2 WriteCache (InsertOnly).
+__global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
+    const int64_t cfg = blockIdx.x;
+    const uint32_t lane = LaneId();
+    const uint32_t full = 0xffffffffu;
+    const int64_t nk = p.n_keys;
+    uint32_t *node_of = p.node_of + cfg * nk;
+    uint8_t *flags = p.flags + cfg * nk;
+    int64_t *time = p.time + cfg * nk;
+    uint32_t *lprev = p.lprev + cfg * (nk + 2);
+    uint32_t *lnext = p.lnext + cfg * (nk + 2);
+    uint32_t *tmp = p.tmp + cfg * nk;
+    uint32_t *evicted = p.evicted + cfg * nk;
+    uint32_t *node = p.nodes + cfg * kNodeFields * p.max_nodes;
+    uint32_t *n_parent = node, *n_children = node + p.max_nodes, *n_blocks = node + 2 * p.max_nodes;
+    uint32_t *n_last = node + 3 * p.max_nodes, *n_cached = node + 4 * p.max_nodes;
+    uint32_t *n_childc = node + 5 * p.max_nodes;  // cached blocks of the immediate children
+    uint32_t *n_unlisted = node + 6 * p.max_nodes;  // cached blocks of the node that are not in the queue
+    const uint32_t kHead = static_cast<uint32_t>(nk), kTail = static_cast<uint32_t>(nk + 1);
+    const int64_t quota = p.quota[cfg];
+    const int64_t out0 = cfg * p.n_traces;
+    const uint64_t walk_cap = static_cast<uint64_t>(nk) + 2;
+
+    // owned by lane 0
+    uint32_t n_nodes = 1, faults = 0;
+    int64_t resident = 0, sum_ext = 0, sum_int = 0, sum_wr = 0;
+
+    auto push_front = [&](uint32_t id) {
+        const uint32_t f = lnext[kHead];
+        lnext[id] = f;
+        lprev[id] = kHead;
+        lprev[f] = id;
+        lnext[kHead] = id;
+    };
+    auto new_node = [&](uint32_t parent) -> uint32_t {
+        uint32_t x = n_nodes;
+        if (static_cast<int64_t>(x) >= p.max_nodes) {  // cannot happen: a trace makes at most two nodes
+            ++faults;
+            x = static_cast<uint32_t>(p.max_nodes - 1);
+        } else {
+            ++n_nodes;
+        }
+        n_parent[x] = parent;
+        n_children[x] = 0;
+        n_blocks[x] = 0;
+        n_last[x] = kNone;
+        n_cached[x] = 0;
+        n_childc[x] = 0;
+        n_unlisted[x] = 0;
+        return x;
+    };
+    // LinkedList::insert_sorted / insert_sorted_reverse under LeafLRUListNode::compare, picked as
+    // insert_sorted_by_priority picks (leaf_aware_lru.cc:53-83).
+    auto insert_by_time = [&](uint32_t b) {
+        const uint32_t h = lnext[kHead];
+        uint32_t before;  // b goes in front of this entry
+        if (h == kTail) {
+            before = kTail;
+        } else {
+            const uint32_t tl = lprev[kTail];
+            const int64_t ht = time[h], tt = time[tl], bt = time[b];
+            const bool from_head = bt >= ht ? true : (bt <= tt ? false : (ht - bt) < (bt - tt));
+            uint64_t steps = 0;
+            if (from_head) {
+                uint32_t cur = h;
+                while (cur != kTail && bt < time[cur] && ++steps < walk_cap) cur = lnext[cur];
+                before = cur;
+            } else {
+                uint32_t cur = tl;
+                while (cur != kHead && time[cur] < bt && ++steps < walk_cap) cur = lprev[cur];
+                before = lnext[cur];
+            }
+            if (steps >= walk_cap) ++faults;
+        }
+        const uint32_t a = lprev[before];
+        lnext[a] = b;
+        lprev[b] = a;
+        lnext[b] = before;
+        lprev[before] = b;
+    };
+
+    if (lane == 0) {
+        n_parent[0] = kNone;
+        n_children[0] = 0;
+        n_blocks[0] = 0;
+        n_last[0] = kNone;
+        n_cached[0] = 0;
+        n_childc[0] = 0;
+        n_unlisted[0] = 0;
+        lnext[kHead] = kTail;
+        lprev[kTail] = kHead;
+    }
+    __syncwarp();
+
+    for (int32_t t = 0; t < p.n_traces; ++t) {
+        const int64_t beg = p.key_off[t];
+        const int64_t n = p.key_off[t + 1] - beg;
+        const uint8_t ty = p.type[t];
+        const int64_t skip = (ty == 1 && p.mask_off != nullptr) ? p.mask_off[t] : 0;
+        const int64_t now = p.timestamps != nullptr ? p.timestamps[t] : static_cast<int64_t>(t);
+        int32_t ext = 0, inte = 0, wr = 0;
+
+        // ---- scan: where the trace leaves the tree (div) and its first block that is not cached (first_gone)
+        int64_t div = n, first_gone = -1;
+        for (int64_t base = 0; base < n; base += 32) {
+            const int64_t i = base + lane;
+            const bool have = i < n;
+            const uint32_t id = have ? p.ids[beg + i] : 0u;
+            const uint32_t nd = have ? node_of[id] : kNone;
+            const uint8_t fl = have ? flags[id] : 0;
+            const uint32_t in_range = __ballot_sync(full, have);
+            const uint32_t in_tree = __ballot_sync(full, have && nd != kNone);
+            const uint32_t cached = __ballot_sync(full, have && nd != kNone && (fl & kCached) != 0);
+            const uint32_t out = in_range & ~in_tree;
+            const uint32_t valid = out != 0 ? ((1u << (__ffs(out) - 1)) - 1u) : in_range;
+            const uint32_t gone = valid & ~cached;
+            if (first_gone < 0) {
+                if (ty != 2) {
+                    const uint32_t lead = gone != 0 ? (valid & ((1u << (__ffs(gone) - 1)) - 1u)) : valid;
+                    const uint32_t masked = __ballot_sync(
+                        full, i < skip || (ty == 1 && p.mask_bits != nullptr && have && p.mask_bits[beg + i] != 0));
+                    ext += __popc(lead & ~masked);
+                    inte += __popc(lead & masked);
+                }
+                if (gone != 0) first_gone = base + __ffs(gone) - 1;
+            }
+            if (out != 0) {
+                div = base + __ffs(out) - 1;
+                break;
+            }
+            if (ty == 1 && first_gone >= 0) break;
+        }
+        const int64_t hit_len = ty == 2 ? 0 : (first_gone >= 0 ? first_gone : div);
+
+        // ---- the leading cached blocks are accessed, in order (radix_tree_index.cc:166-172,246-249)
+        if (lane == 0 && ty != 2) {
+            for (int64_t i = 0; i < hit_len; ++i) {
+                const uint32_t id = p.ids[beg + i];
+                time[id] = now;
+                if ((flags[id] & kListed) != 0) {
+                    const uint32_t a = lprev[id];
+                    if (a != kHead) {
+                        const uint32_t b = lnext[id];
+                        lnext[a] = b;
+                        lprev[b] = a;
+                        push_front(id);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+
+        if (ty != 1) {
+            // ---- evicted blocks on the walked path get their location back (:60-63,250-252,355-375)
+            if (lane == 0) {
+                for (int64_t i = hit_len; i < div; ++i) {
+                    const uint32_t id = p.ids[beg + i];
+                    if ((flags[id] & kCached) != 0) continue;
+                    const uint32_t nd = node_of[id];
+                    time[id] = now;
+                    n_cached[nd] += 1;
+                    n_childc[n_parent[nd]] += 1;
+                    ++resident;
+                    ++wr;
+                    if (n_children[nd] == 0) {
+                        flags[id] = kCached | kListed;
+                        push_front(id);
+                    } else {
+                        flags[id] = kCached;
+                        n_unlisted[nd] += 1;
+                    }
+                }
+            }
+            __syncwarp();
+            if (div < n) {
+                // ---- where the rest goes: the end of a childless node, a new child, or a split (:30-87,89-127)
+                uint32_t target = 0, child = 0, mid = 0, do_split = 0, old_front = 0;
+                if (lane == 0) {
+                    const uint32_t last_id = div > 0 ? p.ids[beg + div - 1] : kNone;
+                    const uint32_t at = div > 0 ? node_of[last_id] : 0u;
+                    if (div == 0 || n_last[at] == last_id) {
+                        if (at != 0 && n_children[at] == 0) {
+                            target = at;
+                        } else {
+                            target = new_node(at);
+                            n_children[at] += 1;
+                        }
+                    } else {
+                        do_split = 1;
+                        child = at;
+                        mid = new_node(n_parent[at]);
+                        target = new_node(mid);
+                    }
+                    old_front = lnext[kHead];
+                }
+                target = __shfl_sync(full, target, 0);
+                child = __shfl_sync(full, child, 0);
+                mid = __shfl_sync(full, mid, 0);
+                do_split = __shfl_sync(full, do_split, 0);
+                old_front = __shfl_sync(full, old_front, 0);
+                if (do_split != 0) {
+                    // the upper part takes the new number: its keys are the walked keys that sit in `child`
+                    uint32_t pos = 0, unl = 0;
+                    for (int64_t j0 = div - 1; j0 >= 0; j0 -= 32) {
+                        const int64_t j = j0 - lane;
+                        const bool have = j >= 0;
+                        const uint32_t id = have ? p.ids[beg + j] : 0u;
+                        const uint32_t nd = have ? node_of[id] : kNone;
+                        const uint32_t member = __ballot_sync(full, have && nd == child);
+                        const uint32_t run = member == full ? 32u : static_cast<uint32_t>(__ffs(~member) - 1);
+                        const bool mine = lane < run;
+                        const uint8_t fl = mine ? flags[id] : 0;
+                        if (mine) node_of[id] = mid;
+                        unl += __popc(__ballot_sync(full, mine && (fl & (kCached | kListed)) == kCached));
+                        pos += run;
+                        if (run < 32u) break;
+                    }
+                    if (lane == 0) {
+                        // every walked block is cached by now (hit, or just given its location back)
+                        const uint32_t up = n_parent[child];
+                        n_children[mid] = 2;
+                        n_blocks[mid] = pos;
+                        n_last[mid] = p.ids[beg + div - 1];
+                        n_cached[mid] = pos;
+                        n_unlisted[mid] = unl;
+                        n_blocks[child] -= pos;
+                        n_cached[child] -= pos;
+                        n_unlisted[child] -= unl;
+                        n_parent[child] = mid;
+                        n_childc[mid] = n_cached[child];
+                        n_childc[up] -= n_cached[child];
+                    }
+                }
+                __syncwarp();
+                // ---- the new blocks, pushed to the front one after the other (:327-343, leaf_aware_lru.cc:20-31)
+                for (int64_t base = div; base < n; base += 32) {
+                    const int64_t i = base + lane;
+                    if (i < n) {
+                        const uint32_t id = p.ids[beg + i];
+                        node_of[id] = target;
+                        flags[id] = kCached | kListed;
+                        time[id] = now;
+                        lnext[id] = i == div ? old_front : p.ids[beg + i - 1];
+                        lprev[id] = i == n - 1 ? kHead : p.ids[beg + i + 1];
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) {
+                    const uint32_t cnt = static_cast<uint32_t>(n - div);
+                    lprev[old_front] = p.ids[beg + div];
+                    lnext[kHead] = p.ids[beg + n - 1];
+                    n_blocks[target] += cnt;
+                    n_cached[target] += cnt;
+                    n_last[target] = p.ids[beg + n - 1];
+                    n_childc[n_parent[target]] += cnt;
+                    resident += cnt;
+                    wr += static_cast<int32_t>(cnt);
+                }
+                __syncwarp();
+            }
+
+            // ---- CheckAndEvict: whole batches until the excess is covered, or exactly the excess
+            if (lane == 0 && resident > quota) {
+                const int64_t excess = resident - quota;
+                int64_t total = 0;
+                uint32_t n_ev = 0;
+                uint64_t spins = 0;
+                while (total < excess) {
+                    const int64_t rest = excess - total;
+                    const int64_t count = p.precise != 0 ? (rest < p.evict_batch ? rest : p.evict_batch) : p.evict_batch;
+                    int64_t got = 0;
+                    // LeafAwareLruEvictionPolicy::EvictBlocks (leaf_aware_lru.cc:85-133).  Its set of parents
+                    // already handled only saves work: a handled parent has nothing left outside the queue.
+                    while (got < count) {
+                        const uint32_t b = lprev[kTail];
+                        if (b == kHead) break;
+                        if (++spins > 2 * walk_cap || static_cast<int64_t>(n_ev) >= nk) {
+                            ++faults;  // a block leaves the queue at most twice per check, and is evicted once
+                            break;
+                        }
+                        const uint32_t a = lprev[b];
+                        lnext[a] = kTail;
+                        lprev[kTail] = a;
+                        const uint32_t nd = node_of[b];
+                        if (n_childc[nd] != 0) {  // its node has cached children by now: out of the queue, stays cached
+                            flags[b] = kCached;
+                            n_unlisted[nd] += 1;
+                            continue;
+                        }
+                        flags[b] = 0;
+                        n_cached[nd] -= 1;
+                        const uint32_t up = n_parent[nd];
+                        n_childc[up] -= 1;
+                        --resident;
+                        evicted[n_ev++] = b;
+                        ++got;
+                        // UpdateNodeState(parent): a parent that became a data leaf queues its blocks, in block order
+                        if (up != 0 && n_childc[up] == 0 && n_unlisted[up] != 0) {
+                            const uint32_t c = n_blocks[up];
+                            uint32_t id = n_last[up];
+                            uint32_t k = c;
+                            while (k > 0 && id != kNone) {
+                                tmp[--k] = id;
+                                id = p.pred[id];
+                            }
+                            if (k != 0) ++faults;
+                            for (; k < c; ++k) {
+                                const uint32_t x = tmp[k];
+                                if ((flags[x] & (kCached | kListed)) == kCached) {
+                                    insert_by_time(x);
+                                    flags[x] = kCached | kListed;
+                                }
+                            }
+                            n_unlisted[up] = 0;
+                        }
+                    }
+                    if (got == 0) break;
+                    total += got;
+                }
+                // CleanEmptyBlocks (radix_tree_index.cc:284-325): childless nodes without a cached block go,
+                // among the nodes that own an evicted block, until nothing more goes
+                bool removed = n_ev != 0;
+                while (removed) {
+                    removed = false;
+                    for (uint32_t e = 0; e < n_ev; ++e) {
+                        const uint32_t nd = node_of[evicted[e]];
+                        if (nd == kNone || nd == 0 || n_cached[nd] != 0 || n_children[nd] != 0) continue;
+                        n_children[n_parent[nd]] -= 1;
+                        uint32_t id = n_last[nd];
+                        for (uint32_t k = n_blocks[nd]; k > 0 && id != kNone; --k) {
+                            node_of[id] = kNone;
+                            id = p.pred[id];
+                        }
+                        node_of[evicted[e]] = kNone;  // so that every pass that removes something ends an entry
+                        n_blocks[nd] = 0;
+                        removed = true;
+                    }
+                }
+            }
+            __syncwarp();
+        }
+        if (lane == 0) {
+            if (p.ext_hit != nullptr) {
+                p.ext_hit[out0 + t] = ext;
+                p.int_hit[out0 + t] = inte;
+                p.written[out0 + t] = wr;
+                p.cache_blocks[out0 + t] = resident;
+            }
+            sum_ext += ext;
+            sum_int += inte;
+            sum_wr += wr;
+        }
+    }
+    if (lane == 0) {
+        if (p.totals != nullptr) {
+            int64_t *tot = p.totals + cfg * 4;
+            tot[0] = sum_ext;
+            tot[1] = sum_int;
+            tot[2] = sum_wr;
+            tot[3] = resident;
+        }
+        if (faults != 0 && p.status != nullptr) atomicAdd(&p.status[0], faults);
+    }
+}
+
+struct LeafLayout {
+    uint64_t table_off, ids_off, pred_off, node_of_off, flags_off, time_off, lprev_off, lnext_off, tmp_off, evicted_off,
+        nodes_off, total;
+    int64_t max_nodes;
+};
+
+LeafLayout LayoutFor(int64_t n_keys, int32_t n_traces, int32_t n_configs) {
+    auto up = [](uint64_t v) { return (v + 255u) & ~static_cast<uint64_t>(255u); };
+    LeafLayout l;
+    const uint64_t nk = static_cast<uint64_t>(n_keys > 0 ? n_keys : 1);
+    const uint64_t nc = static_cast<uint64_t>(n_configs);
+    l.max_nodes = 2 * static_cast<int64_t>(n_traces) + 2;  // the root, and at most two new nodes per trace
+    l.table_off = 256;
+    l.ids_off = up(l.table_off + SlotsFor(n_keys) * sizeof(ulonglong2));
+    l.pred_off = up(l.ids_off + nk * 4);
+    l.node_of_off = up(l.pred_off + nk * 4);
+    l.flags_off = up(l.node_of_off + nk * 4 * nc);
+    l.time_off = up(l.flags_off + nk * nc);
+    l.lprev_off = up(l.time_off + nk * 8 * nc);
+    l.lnext_off = up(l.lprev_off + (nk + 2) * 4 * nc);
+    l.tmp_off = up(l.lnext_off + (nk + 2) * 4 * nc);
+    l.evicted_off = up(l.tmp_off + nk * 4 * nc);
+    l.nodes_off = up(l.evicted_off + nk * 4 * nc);
+    l.total = up(l.nodes_off + static_cast<uint64_t>(l.max_nodes) * 4 * kNodeFields * nc);
+    return l;
+}
+
+}  // namespace
+}  // namespace kvcm
+
+extern "C" {
+
+int64_t kvcm_b200_replay_leaf_lru_workspace_bytes(int64_t n_keys_total, int32_t n_traces, int32_t n_configs) {
+    if (n_keys_total < 0 || n_keys_total >= (1ll << 32) - 3 || n_traces < 0 || n_traces >= (1 << 30) ||
+        n_configs <= 0 || n_configs > 65535) {
+        return -1;
+    }
+    return static_cast<int64_t>(kvcm::LayoutFor(n_keys_total, n_traces, n_configs).total);
+}
+
+int32_t kvcm_b200_replay_leaf_lru(const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type,
+                                  const int64_t *d_mask_off, const uint8_t *d_mask_bits, const int64_t *d_timestamps,
+                                  int32_t n_traces, int64_t n_keys_total, const int64_t *d_quota_blocks,
+                                  int32_t n_configs, int32_t evict_batch, int32_t precise, void *d_workspace,
+                                  int64_t workspace_bytes, int32_t *d_ext_hit, int32_t *d_int_hit, int32_t *d_written,
+                                  int64_t *d_cache_blocks, int64_t *d_totals, uint32_t *d_status,
+                                  kvcm_stream_t stream) {
+    if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
+    if (n_traces < 0 || n_keys_total < 0 || n_configs <= 0 || evict_batch <= 0) return KVCM_EC_BADARGS;
+    const int64_t need = kvcm_b200_replay_leaf_lru_workspace_bytes(n_keys_total, n_traces, n_configs);
+    if (need < 0) return KVCM_EC_OUT_OF_LIMIT;
+    if (n_traces == 0) return KVCM_OK;
+    const int per_trace = (d_ext_hit != nullptr) + (d_int_hit != nullptr) + (d_written != nullptr) +
+                          (d_cache_blocks != nullptr);
+    if (d_key_off == nullptr || d_trace_type == nullptr || d_quota_blocks == nullptr || d_workspace == nullptr ||
+        (d_keys == nullptr && n_keys_total > 0) || (per_trace != 0 && per_trace != 4) ||
+        (per_trace == 0 && d_totals == nullptr)) {
+        return KVCM_ER_INVALID_ADDRESS;
+    }
+    if (reinterpret_cast<uintptr_t>(d_workspace) & 255u) return KVCM_ER_INVALID_ADDRESS;
+    if (workspace_bytes < need) return KVCM_EC_NOSPC;
+    const kvcm::LeafLayout l = kvcm::LayoutFor(n_keys_total, n_traces, n_configs);
+    uint8_t *ws = static_cast<uint8_t *>(d_workspace);
+    kvcm::IdTable t;
+    t.cells = reinterpret_cast<unsigned long long *>(ws);
+    t.slots = reinterpret_cast<ulonglong2 *>(ws + l.table_off);
+    t.mask = kvcm::SlotsFor(n_keys_total) - 1;
+    uint32_t *ids = reinterpret_cast<uint32_t *>(ws + l.ids_off);
+    uint32_t *pred = reinterpret_cast<uint32_t *>(ws + l.pred_off);
+    const uint64_t nk = static_cast<uint64_t>(n_keys_total > 0 ? n_keys_total : 1);
+    cudaStream_t s = kvcm::AsStream(stream);
+    const int sms = kvcm::GetDeviceInfo().sm_count;
+    kvcm::LeafSweep p;
+    p.ids = ids;
+    p.pred = pred;
+    p.key_off = d_key_off;
+    p.type = d_trace_type;
+    p.mask_off = d_mask_off;
+    p.mask_bits = d_mask_bits;
+    p.timestamps = d_timestamps;
+    p.quota = d_quota_blocks;
+    p.node_of = reinterpret_cast<uint32_t *>(ws + l.node_of_off);
+    p.flags = ws + l.flags_off;
+    p.time = reinterpret_cast<int64_t *>(ws + l.time_off);
+    p.lprev = reinterpret_cast<uint32_t *>(ws + l.lprev_off);
+    p.lnext = reinterpret_cast<uint32_t *>(ws + l.lnext_off);
+    p.tmp = reinterpret_cast<uint32_t *>(ws + l.tmp_off);
+    p.evicted = reinterpret_cast<uint32_t *>(ws + l.evicted_off);
+    p.nodes = reinterpret_cast<uint32_t *>(ws + l.nodes_off);
+    p.ext_hit = d_ext_hit;
+    p.int_hit = d_int_hit;
+    p.written = d_written;
+    p.cache_blocks = d_cache_blocks;
+    p.totals = d_totals;
+    p.status = d_status;
+    p.n_keys = static_cast<int64_t>(nk);
+    p.max_nodes = l.max_nodes;
+    p.n_traces = n_traces;
+    p.n_configs = n_configs;
+    p.evict_batch = evict_batch;
+    p.precise = precise;
+    kvcm::LeafInitKernel<<<sms * 8, 256, 0, s>>>(t, p.node_of, p.flags, nk * static_cast<uint64_t>(n_configs), pred, nk);
+    if (n_keys_total > 0) {
+        kvcm::LruClaimIdsKernel<<<sms * 8, 256, 0, s>>>(t, d_keys, n_keys_total, d_status);
+        kvcm::LruLookupIdsKernel<<<sms * 8, 256, 0, s>>>(t, d_keys, n_keys_total, ids);
+        kvcm::LeafPredKernel<<<sms * 4, 256, 0, s>>>(ids, d_key_off, n_traces, pred);
+    }
+    kvcm::LeafSweepKernel<<<static_cast<unsigned>(n_configs), 32, 0, s>>>(p);
+    return kvcm::LaunchStatus();
+}
+
+}  // extern "C"

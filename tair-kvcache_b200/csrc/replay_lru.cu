@@ -27,27 +27,12 @@
 // Keys are renamed to dense ids 0..D-1 once, for all configurations, so that per-configuration
 // state is two flat arrays (4 + 8 bytes per key occurrence of the trace).
 #include "kvcm_common.cuh"
+#include "replay_ids.cuh"
 
 namespace kvcm {
 namespace {
 
-constexpr uint64_t kEmptyKey = 0x8000000000000000ull;
 constexpr int kEvictWindows = 4;
-
-struct IdTable {
-    ulonglong2 *slots;         // {key, id}
-    unsigned long long *cells;  // [0] = number of ids handed out, [1] = id of the key equal to kEmptyKey (or ~0)
-    uint64_t mask;
-};
-
-__host__ __device__ __forceinline__ uint64_t Mix(uint64_t k) {
-    k ^= k >> 33;
-    k *= 0xff51afd7ed558ccdull;
-    k ^= k >> 33;
-    k *= 0xc4ceb9fe1a85ec53ull;
-    k ^= k >> 33;
-    return k;
-}
 
 __global__ void LruInitKernel(IdTable t, uint32_t *stamps, uint64_t n_stamps) {
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
@@ -57,64 +42,6 @@ __global__ void LruInitKernel(IdTable t, uint32_t *stamps, uint64_t n_stamps) {
     if (first == 0) {
         t.cells[0] = 0ull;
         t.cells[1] = ~0ull;
-    }
-}
-
-// Pass 1: every key gets a slot; the thread that claims the slot takes the next id.
-__global__ void __launch_bounds__(256)
-    LruClaimIdsKernel(IdTable t, const int64_t *__restrict__ keys, int64_t n_keys, uint32_t *status) {
-    unsigned long long *words = reinterpret_cast<unsigned long long *>(t.slots);
-    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_keys; i += stride) {
-        const uint64_t key = static_cast<uint64_t>(keys[i]);
-        if (key == kEmptyKey) {
-            if (atomicCAS(&t.cells[1], ~0ull, ~0ull - 1) == ~0ull) t.cells[1] = atomicAdd(&t.cells[0], 1ull);
-            continue;
-        }
-        uint64_t slot = Mix(key) & t.mask;
-        bool placed = false;
-        for (uint64_t probe = 0; probe <= t.mask; ++probe) {
-            unsigned long long seen = *reinterpret_cast<volatile unsigned long long *>(&words[2 * slot]);
-            if (seen == kEmptyKey) {
-                seen = atomicCAS(&words[2 * slot], kEmptyKey, key);
-                if (seen == kEmptyKey) {
-                    words[2 * slot + 1] = atomicAdd(&t.cells[0], 1ull);
-                    placed = true;
-                    break;
-                }
-            }
-            if (seen == key) {
-                placed = true;
-                break;
-            }
-            slot = (slot + 1) & t.mask;
-        }
-        if (!placed && status != nullptr) atomicAdd(&status[0], 1u);
-    }
-}
-
-// Pass 2 (a launch of its own, so every id of pass 1 is visible): key occurrence -> id.
-__global__ void __launch_bounds__(256)
-    LruLookupIdsKernel(IdTable t, const int64_t *__restrict__ keys, int64_t n_keys, uint32_t *__restrict__ ids) {
-    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_keys; i += stride) {
-        const uint64_t key = static_cast<uint64_t>(keys[i]);
-        uint32_t id = 0;
-        if (key == kEmptyKey) {
-            id = static_cast<uint32_t>(t.cells[1]);
-        } else {
-            uint64_t slot = Mix(key) & t.mask;
-            for (uint64_t probe = 0; probe <= t.mask; ++probe) {
-                const ulonglong2 s = t.slots[slot];
-                if (s.x == key) {
-                    id = static_cast<uint32_t>(s.y);
-                    break;
-                }
-                if (s.x == kEmptyKey) break;  // not reached for a key that pass 1 placed
-                slot = (slot + 1) & t.mask;
-            }
-        }
-        ids[i] = id;
     }
 }
 
@@ -279,12 +206,6 @@ __global__ void __launch_bounds__(32) LruSweepKernel(const LruSweep p) {
         tot[2] = sum_wr;
         tot[3] = resident;
     }
-}
-
-uint64_t SlotsFor(int64_t n_keys) {
-    uint64_t n = 1024;
-    while (n < 2ull * static_cast<uint64_t>(n_keys)) n <<= 1;
-    return n;
 }
 
 struct LruLayout {

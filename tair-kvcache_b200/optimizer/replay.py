@@ -75,8 +75,16 @@ class LruSweepResult(NamedTuple):
     totals: torch.Tensor  # int64 [n_configs, 4]: external hits, internal hits, written blocks, cached blocks at the end
 
 
-def replay_lru_workspace_bytes(n_keys_total: int, n_configs: int) -> int:
-    n = _cabi.lib().kvcm_b200_replay_lru_workspace_bytes(n_keys_total, n_configs)
+POLICIES = ("lru", "leaf_aware_lru")  # EvictionPolicyType names (kv_cache_manager/optimizer/config/types.cc)
+
+
+def replay_lru_workspace_bytes(n_keys_total: int, n_configs: int, policy: str = "lru", n_traces: int = 0) -> int:
+    if policy == "leaf_aware_lru":
+        n = _cabi.lib().kvcm_b200_replay_leaf_lru_workspace_bytes(n_keys_total, n_traces, n_configs)
+    elif policy == "lru":
+        n = _cabi.lib().kvcm_b200_replay_lru_workspace_bytes(n_keys_total, n_configs)
+    else:
+        raise ValueError("eviction policy %r is not built (have: %s)" % (policy, ", ".join(POLICIES)))
     if n < 0:
         raise ValueError("too many keys or configurations for one LRU replay call")
     return n
@@ -85,8 +93,11 @@ def replay_lru_workspace_bytes(n_keys_total: int, n_configs: int) -> int:
 def RunTracesLru(keys: torch.Tensor, key_off: torch.Tensor, trace_type: torch.Tensor, quota_blocks,
                  mask_off: Optional[torch.Tensor] = None, evict_batch: int = 100, precise: bool = False,
                  workspace: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
-                 per_trace: bool = True, mask_bits: Optional[torch.Tensor] = None) -> LruSweepResult:
-    """The replay of RunTraces with the reference's "lru" eviction policy, once per entry of quota_blocks (the
+                 per_trace: bool = True, mask_bits: Optional[torch.Tensor] = None, policy: str = "lru",
+                 timestamps: Optional[torch.Tensor] = None) -> LruSweepResult:
+    """The replay of RunTraces with the reference's "lru" (default) or "leaf_aware_lru" eviction policy
+    (policy; timestamps = the traces' timestamp_us as an int64 CUDA tensor, read by "leaf_aware_lru" only, the
+    trace number when None), once per entry of quota_blocks (the
     points of a tradeoff curve: quota_capacity * used_percentage in blocks), all configurations in one launch.
     evict_batch / precise: eviction_batch_size_per_instance and the eviction mode (False = the rough modes, which
     evict whole batches; True = INSTANCE_PRECISE).  per_trace=False skips the [n_configs, n_traces] records and
@@ -99,7 +110,7 @@ def RunTracesLru(keys: torch.Tensor, key_off: torch.Tensor, trace_type: torch.Te
     n_cfg, n_traces = quota.numel(), key_off.numel() - 1
     if n_cfg == 0:
         raise ValueError("quota_blocks is empty")
-    need = replay_lru_workspace_bytes(keys.numel(), n_cfg)
+    need = replay_lru_workspace_bytes(keys.numel(), n_cfg, policy, n_traces)
     if workspace is None:
         workspace = torch.empty(need, dtype=torch.uint8, device=dev)
     elif workspace.numel() < need or workspace.device != dev:
@@ -115,6 +126,19 @@ def RunTracesLru(keys: torch.Tensor, key_off: torch.Tensor, trace_type: torch.Te
     if per_trace and n_traces == 0:
         return LruSweepResult(ext, inte, wr, size, totals)
     _cabi.bind_device(dev.index)
+    if policy == "leaf_aware_lru":
+        if timestamps is not None:
+            if timestamps.dtype != torch.int64 or timestamps.numel() != n_traces or timestamps.device != dev:
+                raise ValueError("timestamps must be an int64 tensor with one entry per trace, on the keys' device")
+            timestamps = timestamps.contiguous()
+        _cabi.call("kvcm_b200_replay_leaf_lru", keys.data_ptr(), key_off.data_ptr(), trace_type.data_ptr(),
+                   mask_off.contiguous().data_ptr() if mask_off is not None else None,
+                   _mask_bits_ptr(mask_bits, keys), timestamps.data_ptr() if timestamps is not None else None,
+                   n_traces, keys.numel(), quota.data_ptr(), n_cfg, int(evict_batch), 1 if precise else 0,
+                   workspace.data_ptr(), workspace.numel(), ptr(ext), ptr(inte), ptr(wr), ptr(size),
+                   totals.data_ptr(), status.data_ptr() if status is not None else None,
+                   torch.cuda.current_stream(dev).cuda_stream)
+        return LruSweepResult(ext, inte, wr, size, totals)
     _cabi.call("kvcm_b200_replay_lru", keys.data_ptr(), key_off.data_ptr(), trace_type.data_ptr(),
                mask_off.contiguous().data_ptr() if mask_off is not None else None, _mask_bits_ptr(mask_bits, keys),
                n_traces, keys.numel(), quota.data_ptr(), n_cfg, int(evict_batch), 1 if precise else 0, workspace.data_ptr(),

@@ -1,6 +1,6 @@
 """Trace file -> per-instance replay on the GPU -> hit-rate table, the shape of OptimizerRunner::Run followed by
 HitAnalysis::Analyze (kv_cache_manager/optimizer/manager/optimizer_runner.cc:13-68,
-kv_cache_manager/optimizer/analysis/result_analysis.cc:10-113): without eviction, or with the "lru" policy at
+kv_cache_manager/optimizer/analysis/result_analysis.cc:10-113): without eviction, or with the "lru" or "leaf_aware_lru" policy at
 one or many quota points (the tradeoff curves of kv_cache_manager/optimizer/analysis/script/
 tradeoff_curve_by_instances.py)."""
 import json
@@ -27,10 +27,11 @@ def _g(x: float) -> str:
 
 def replay_instance(traces: List[tr.Trace], device, rw_separation: bool = False,
                     quota_blocks: Union[None, int, Sequence[int]] = None, evict_batch: int = 100,
-                    precise: bool = False):
+                    precise: bool = False, policy: str = "lru"):
     """Replays the traces of one instance.  As OptimizerRunner::RunTrace does, only prefix_match queries are
     replayed, dialog turns are skipped in read/write-separation mode and Get/Write traces are skipped otherwise.
-    quota_blocks = None: nothing is ever evicted; an int: "lru" eviction at that quota (quota_capacity *
+    quota_blocks = None: nothing is ever evicted; an int: eviction under `policy` ("lru" or "leaf_aware_lru",
+    the instance's eviction_policy_type) at that quota (quota_capacity *
     used_percentage, in blocks); a sequence: one record per quota, all replayed in one launch.  evict_batch and
     precise are eviction_batch_size_per_instance and the eviction mode (False = the rough modes)."""
     keep = _kept(traces, rw_separation)
@@ -56,7 +57,8 @@ def replay_instance(traces: List[tr.Trace], device, rw_separation: bool = False,
         return record(*(x.cpu().numpy() for x in RunTraces(d_keys, d_off, d_kind, d_mask, mask_bits=d_bits)))
     quotas = [int(quota_blocks)] if np.isscalar(quota_blocks) else [int(q) for q in quota_blocks]
     res = [x.cpu().numpy() for x in RunTracesLru(d_keys, d_off, d_kind, quotas, d_mask, evict_batch, precise,
-                                                 mask_bits=d_bits)[:4]]
+                                                 mask_bits=d_bits, policy=policy,
+                                                 timestamps=torch.from_numpy(ts).to(device))[:4]]
     recs = [record(*(x[c] for x in res)) for c in range(len(quotas))]
     return recs[0] if np.isscalar(quota_blocks) else recs
 
@@ -74,7 +76,7 @@ def _kept(traces: List[tr.Trace], rw_separation: bool) -> List[tr.Trace]:
 
 
 def sweep_hit_rates(traces: List[tr.Trace], device, quota_blocks: Sequence[int], rw_separation: bool = False,
-                    evict_batch: int = 100, precise: bool = False) -> np.ndarray:
+                    evict_batch: int = 100, precise: bool = False, policy: str = "lru") -> np.ndarray:
     """The points of a tradeoff curve without the per-trace records: rows of accumulated (internal, external, total)
     hit rates, one per quota, the same numbers tradeoff_curve() computes from full records."""
     keep = _kept(traces, rw_separation)
@@ -85,7 +87,8 @@ def sweep_hit_rates(traces: List[tr.Trace], device, quota_blocks: Sequence[int],
     bits = tr.mask_bits(keep, off)
     res = RunTracesLru(d_keys, d_off, torch.from_numpy(kind).to(device), [int(q) for q in quota_blocks],
                        torch.from_numpy(mask).to(device), evict_batch, precise, per_trace=False,
-                       mask_bits=torch.from_numpy(bits).to(device) if bits is not None else None)
+                       mask_bits=torch.from_numpy(bits).to(device) if bits is not None else None, policy=policy,
+                       timestamps=torch.from_numpy(np.array([t.timestamp_us for t in keep], dtype=np.int64)).to(device))
     totals = res.totals.cpu().numpy()
     total_read = int(read[kind != tr.WRITE_CACHE].sum())
     out = np.zeros((totals.shape[0], 3))
@@ -137,7 +140,8 @@ def export_hit_rates(path: str, rec: Dict[str, np.ndarray]) -> None:
 def run_trace_file(trace_path: str, trace_type: str, output_dir: str, device=None,
                    block_sizes: Optional[Dict[str, int]] = None, rw_separation: bool = False,
                    quota_blocks: Union[None, int, Sequence[int], Dict[str, Union[int, Sequence[int]]]] = None,
-                   evict_batch: int = 100, precise: bool = False):
+                   evict_batch: int = 100, precise: bool = False,
+                   policy: Union[str, Dict[str, str]] = "lru"):
     """Loads a trace file, replays every instance on the GPU and writes `<instance>_hit_rates.csv` per instance
     (`<instance>_quota<q>_hit_rates.csv` per instance and quota when quota_blocks is a sequence).  Every instance is
     replayed on its own: instances that share one group quota in the reference's configuration are not modelled."""
@@ -152,7 +156,9 @@ def run_trace_file(trace_path: str, trace_type: str, output_dir: str, device=Non
         # a dict gives every instance its own quota (or quotas); instances it does not name are never evicted
         quota = quota_blocks.get(instance_id) if isinstance(quota_blocks, dict) else quota_blocks
         sweep = quota is not None and not np.isscalar(quota)
-        rec = replay_instance(ts, device, rw_separation, quota, evict_batch, precise)
+        # policy: one name for all instances, or a dict by instance ("lru" for instances it does not name)
+        pol = policy.get(instance_id, "lru") if isinstance(policy, dict) else policy
+        rec = replay_instance(ts, device, rw_separation, quota, evict_batch, precise, pol)
         for c, r in enumerate(rec if sweep else [rec]):
             if (r["kind"] != tr.WRITE_CACHE).any():
                 name = "%s_quota%d_hit_rates.csv" % (instance_id, int(quota[c])) if sweep else \
@@ -170,7 +176,7 @@ def parse_startup_config(config: Union[str, dict]) -> dict:
     """The Optimizer's startup configuration (kv_cache_manager/optimizer/optimizer_startup_config_load.json, read
     by kv_cache_manager/optimizer/config/optimizer_config.cc:4-12, instance_group_config.cc:5-12,
     instance_config.cc:6-22, eviction_config.cc:5-8) reduced to what the GPU replay needs.  Raises
-    NotImplementedError for what it cannot replay exactly: policies other than "lru", hierarchical eviction, and
+    NotImplementedError for what it cannot replay exactly: the "random_lru" policy, hierarchical eviction, and
     groups whose quota is shared by several instances."""
     if isinstance(config, str):
         with open(config) as f:
@@ -180,7 +186,7 @@ def parse_startup_config(config: Union[str, dict]) -> dict:
     if mode not in (EVICTION_MODE_UNSPECIFIED, EVICTION_MODE_GROUP_ROUGH, EVICTION_MODE_INSTANCE_ROUGH,
                     EVICTION_MODE_INSTANCE_PRECISE):
         raise ValueError("unknown eviction_mode %r" % mode)
-    quotas, block_sizes = {}, {}
+    quotas, block_sizes, policies = {}, {}, {}
     for group in config.get("instance_groups", []):
         instances = group.get("instances", [])
         if group.get("hierarchical_eviction_enabled", False):
@@ -190,10 +196,11 @@ def parse_startup_config(config: Union[str, dict]) -> dict:
                                                                                    len(instances)))
         for inst in instances:
             policy = inst.get("eviction_policy_type", "lru")
-            if policy != "lru" and mode != EVICTION_MODE_UNSPECIFIED:
-                raise NotImplementedError("instance %r: eviction policy %r is not replayed (only \"lru\")"
-                                          % (inst.get("instance_id"), policy))
+            if policy not in ("lru", "leaf_aware_lru") and mode != EVICTION_MODE_UNSPECIFIED:
+                raise NotImplementedError("instance %r: eviction policy %r is not replayed (\"lru\" and "
+                                          "\"leaf_aware_lru\" are)" % (inst.get("instance_id"), policy))
             iid = str(inst["instance_id"])
+            policies[iid] = policy
             block_sizes[iid] = int(inst.get("block_size", 16))
             # eviction_manager.cc:249-266: quota = size_t(quota_capacity * used_percentage); an unspecified mode
             # never evicts (:60-63)
@@ -202,7 +209,7 @@ def parse_startup_config(config: Union[str, dict]) -> dict:
     return dict(trace_file_path=config.get("trace_file_path"), trace_type=config.get("trace_type"),
                 output_result_path=config.get("output_result_path"), quota_blocks=quotas, block_sizes=block_sizes,
                 evict_batch=int(ev.get("eviction_batch_size_per_instance", 100)),
-                precise=mode == EVICTION_MODE_INSTANCE_PRECISE)
+                precise=mode == EVICTION_MODE_INSTANCE_PRECISE, policies=policies)
 
 
 def run_startup_config(config: Union[str, dict], device=None, rw_separation: Optional[bool] = None):
@@ -215,4 +222,4 @@ def run_startup_config(config: Union[str, dict], device=None, rw_separation: Opt
     if rw_separation is None:
         rw_separation = c["trace_type"] == "publisher_log"
     return run_trace_file(c["trace_file_path"], c["trace_type"], c["output_result_path"], device, c["block_sizes"],
-                          rw_separation, c["quota_blocks"] or None, c["evict_batch"], c["precise"])
+                          rw_separation, c["quota_blocks"] or None, c["evict_batch"], c["precise"], c["policies"])

@@ -146,6 +146,13 @@ def test_startup_config_drives_a_publisher_log_replay_with_eviction(tmp_path):
     want = oracle.LruReplay(4, evict_batch=2).run(keys, off, rec["kind"], [0, 0, 0, 0, 1])
     assert np.array_equal(want[0], rec["external_hit_blocks"]) and np.array_equal(want[3], rec["current_cache_blocks"])
     assert len((tmp_path / "out" / "i1_hit_rates.csv").read_text().splitlines()) == 4
+    # the same file under the instance's other policy: the configuration picks the kernel, the event times reach it
+    cfg["instance_groups"][0]["instances"][0]["eviction_policy_type"] = "leaf_aware_lru"
+    rec = run_startup_config(cfg, device="cuda:0")["i1"]
+    want = oracle.LruReplay(4, evict_batch=2, policy="leaf_aware_lru").run(keys, off, rec["kind"], [0, 0, 0, 0, 1],
+                                                                           timestamps=rec["timestamp_us"])
+    for name, w in zip(("external_hit_blocks", "internal_hit_blocks", "write_blocks", "current_cache_blocks"), want):
+        assert np.array_equal(w, rec[name]), name
 
 
 def test_optimizer_schema_query_with_a_holey_vector_mask(tmp_path):

@@ -109,6 +109,8 @@ def test_startup_config_of_the_reference_is_understood():
     assert c["quota_blocks"]["3780643326877293460"] == 9000 and c["precise"] is True
     # what the GPU replay does not reproduce is refused, not approximated
     cfg["instance_groups"][0]["instances"][0]["eviction_policy_type"] = "leaf_aware_lru"
+    assert parse_startup_config(cfg)["policies"] == {"3780643326877293460": "leaf_aware_lru"}
+    cfg["instance_groups"][0]["instances"][0]["eviction_policy_type"] = "random_lru"
     with pytest.raises(NotImplementedError):
         parse_startup_config(cfg)
     cfg["instance_groups"][0]["instances"][0]["eviction_policy_type"] = "lru"
