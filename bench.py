@@ -1257,9 +1257,9 @@ def main_lru(args, rank, world):
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "int64", "data": "synthetic",
             "config": {"workload": "%d requests (dialog turns, 256-2048 uint32 tokens, block 64, Zipf(0.9) prefix "
-                                   "reuse over 10000 prompts = %d token blocks) replayed with " + policy + " eviction at %d quota "
+                                   "reuse over 10000 prompts = %d token blocks) replayed with %s eviction at %d quota "
                                    "points per GPU (%d..%d blocks, rough mode, batches of 100); hash + sweep per step"
-                                   % (n_req, n_keys, n_cfg, min(all_quotas), max(all_quotas)),
+                                   % (n_req, n_keys, policy, n_cfg, min(all_quotas), max(all_quotas)),
                        "sweep_kernel_ms_rank0": sweep_ms, "hit_rate_lowest_quota": float(hit_rate[0]),
                        "hit_rate_highest_quota": float(hit_rate[-1]), "table_overflows": int(status[0].item()),
                        "parity_sample_ok": parity},

@@ -228,23 +228,50 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
         }
         const int64_t hit_len = ty == 2 ? 0 : (first_gone >= 0 ? first_gone : div);
 
-        // ---- the leading cached blocks are accessed, in order (radix_tree_index.cc:166-172,246-249)
-        if (lane == 0 && ty != 2) {
-            for (int64_t i = 0; i < hit_len; ++i) {
-                const uint32_t id = p.ids[beg + i];
-                time[id] = now;
-                if ((flags[id] & kListed) != 0) {
-                    const uint32_t a = lprev[id];
-                    if (a != kHead) {
-                        const uint32_t b = lnext[id];
-                        lnext[a] = b;
-                        lprev[b] = a;
-                        push_front(id);
+        // ---- the leading cached blocks are accessed, in order (radix_tree_index.cc:166-172,246-249): each one
+        // moves to the front of the queue.  Blocks that already follow each other in the queue the way the moves
+        // would leave them (the later one in front of the earlier one) move as one piece; a piece of one block is
+        // the plain move.  The links inside a piece are read by all lanes at once, the splice is lane 0's.
+        if (ty != 2) {
+            for (int64_t base = 0; base < hit_len; base += 32) {
+                const int64_t i = base + lane;
+                const bool have = i < hit_len;
+                const uint32_t id = have ? p.ids[beg + i] : 0u;
+                bool listed = false;
+                uint32_t towards_tail = kNone;
+                if (have) {
+                    time[id] = now;
+                    listed = (flags[id] & kListed) != 0;
+                    if (listed) towards_tail = lnext[id];
+                }
+                const uint32_t id_before = __shfl_up_sync(full, id, 1);
+                const uint32_t listed_m = __ballot_sync(full, listed);
+                const bool joins = listed && lane > 0 && ((listed_m >> (lane - 1)) & 1u) != 0 && towards_tail == id_before;
+                const uint32_t joins_m = __ballot_sync(full, joins);
+                uint32_t starts = listed_m & ~joins_m;
+                while (starts != 0) {
+                    const int first = __ffs(starts) - 1;
+                    starts &= starts - 1;
+                    const int len = first == 31 ? 0 : __ffs(~(joins_m >> (first + 1))) - 1;
+                    const uint32_t piece_tail = __shfl_sync(full, id, first);        // accessed first: ends up deepest
+                    const uint32_t piece_head = __shfl_sync(full, id, first + len);  // accessed last: ends up in front
+                    if (lane == 0) {
+                        const uint32_t a = lprev[piece_head];
+                        if (a != kHead) {
+                            const uint32_t b = lnext[piece_tail];
+                            const uint32_t f = lnext[kHead];
+                            lnext[a] = b;
+                            lprev[b] = a;
+                            lnext[piece_tail] = f;
+                            lprev[f] = piece_tail;
+                            lnext[kHead] = piece_head;
+                            lprev[piece_head] = kHead;
+                        }
                     }
                 }
+                __syncwarp();
             }
         }
-        __syncwarp();
 
         if (ty != 1) {
             // ---- evicted blocks on the walked path get their location back (:60-63,250-252,355-375)
@@ -356,81 +383,159 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
             }
 
             // ---- CheckAndEvict: whole batches until the excess is covered, or exactly the excess
-            if (lane == 0 && resident > quota) {
-                const int64_t excess = resident - quota;
-                int64_t total = 0;
+            const int64_t resident_now = __shfl_sync(full, resident, 0);
+            if (resident_now > quota) {
+                const int64_t excess = resident_now - quota;
+                int64_t total = 0;   // these three are kept equal in all lanes
                 uint32_t n_ev = 0;
-                uint64_t spins = 0;
-                while (total < excess) {
+                bool dry = false;    // the queue ran out
+                uint64_t spins = 0;  // lane 0
+                while (total < excess && !dry) {
                     const int64_t rest = excess - total;
                     const int64_t count = p.precise != 0 ? (rest < p.evict_batch ? rest : p.evict_batch) : p.evict_batch;
                     int64_t got = 0;
-                    // LeafAwareLruEvictionPolicy::EvictBlocks (leaf_aware_lru.cc:85-133).  Its set of parents
-                    // already handled only saves work: a handled parent has nothing left outside the queue.
+                    // LeafAwareLruEvictionPolicy::EvictBlocks (leaf_aware_lru.cc:85-133), up to 32 blocks at a time.
+                    // Its set of parents already handled only saves work: a handled parent has nothing left outside
+                    // the queue.
                     while (got < count) {
-                        const uint32_t b = lprev[kTail];
-                        if (b == kHead) break;
-                        if (++spins > 2 * walk_cap || static_cast<int64_t>(n_ev) >= nk) {
-                            ++faults;  // a block leaves the queue at most twice per check, and is evicted once
+                        const uint32_t want = static_cast<uint32_t>(count - got < 32 ? count - got : 32);
+                        // lane 0 follows the queue from its cold end; the others then look at one candidate each
+                        uint32_t m = 0, after = kHead;
+                        if (lane == 0) {
+                            uint32_t b = lprev[kTail];
+                            while (m < want && b != kHead) {
+                                tmp[m++] = b;
+                                b = lprev[b];
+                            }
+                            after = b;
+                        }
+                        m = __shfl_sync(full, m, 0);
+                        after = __shfl_sync(full, after, 0);
+                        if (m == 0) {
+                            dry = true;
                             break;
                         }
-                        const uint32_t a = lprev[b];
-                        lnext[a] = kTail;
-                        lprev[kTail] = a;
-                        const uint32_t nd = node_of[b];
-                        if (n_childc[nd] != 0) {  // its node has cached children by now: out of the queue, stays cached
-                            flags[b] = kCached;
-                            n_unlisted[nd] += 1;
+                        __syncwarp();
+                        const bool mine = lane < m;
+                        const uint32_t cand = mine ? tmp[lane] : 0u;
+                        const uint32_t nd = mine ? node_of[cand] : 0u;
+                        const uint32_t up = mine ? n_parent[nd] : 0u;
+                        // The whole group goes at once when every candidate sits in a data leaf and no parent runs
+                        // out of cached children while it still has blocks outside the queue (nothing is re-queued,
+                        // so the queue stays as it was followed).
+                        const uint32_t same_up = __match_any_sync(full, mine ? up : kNone - lane);
+                        const uint32_t same_nd = __match_any_sync(full, mine ? nd : kNone - lane);
+                        bool plain = true;
+                        if (mine) {
+                            const uint32_t under = static_cast<uint32_t>(__popc(same_up));
+                            plain = n_childc[nd] == 0 && (up == 0 || n_unlisted[up] == 0 || n_childc[up] > under);
+                        }
+                        if (__all_sync(full, plain) && static_cast<int64_t>(n_ev) + m <= nk) {
+                            if (mine) {
+                                flags[cand] = 0;
+                                evicted[n_ev + lane] = cand;
+                                if (static_cast<uint32_t>(__ffs(same_nd) - 1) == lane) n_cached[nd] -= __popc(same_nd);
+                            }
+                            __syncwarp();  // n_childc is read above for nodes that are parents here
+                            if (mine && static_cast<uint32_t>(__ffs(same_up) - 1) == lane) n_childc[up] -= __popc(same_up);
+                            if (lane == 0) {
+                                lnext[after] = kTail;
+                                lprev[kTail] = after;
+                                resident -= m;
+                            }
+                            __syncwarp();
+                            n_ev += m;
+                            got += m;
                             continue;
                         }
-                        flags[b] = 0;
-                        n_cached[nd] -= 1;
-                        const uint32_t up = n_parent[nd];
-                        n_childc[up] -= 1;
-                        --resident;
-                        evicted[n_ev++] = b;
-                        ++got;
-                        // UpdateNodeState(parent): a parent that became a data leaf queues its blocks, in block order
-                        if (up != 0 && n_childc[up] == 0 && n_unlisted[up] != 0) {
-                            const uint32_t c = n_blocks[up];
-                            uint32_t id = n_last[up];
-                            uint32_t k = c;
-                            while (k > 0 && id != kNone) {
-                                tmp[--k] = id;
-                                id = p.pred[id];
-                            }
-                            if (k != 0) ++faults;
-                            for (; k < c; ++k) {
-                                const uint32_t x = tmp[k];
-                                if ((flags[x] & (kCached | kListed)) == kCached) {
-                                    insert_by_time(x);
-                                    flags[x] = kCached | kListed;
+                        // otherwise one block after the other, up to the same number
+                        uint32_t g = 0;
+                        if (lane == 0) {
+                            while (g < want) {
+                                const uint32_t b = lprev[kTail];
+                                if (b == kHead) break;
+                                if (++spins > 2 * walk_cap || static_cast<int64_t>(n_ev) >= nk) {
+                                    ++faults;  // a block leaves the queue at most twice per check, and is evicted once
+                                    break;
+                                }
+                                const uint32_t a = lprev[b];
+                                lnext[a] = kTail;
+                                lprev[kTail] = a;
+                                const uint32_t node_b = node_of[b];
+                                if (n_childc[node_b] != 0) {  // its node has cached children by now: out of the queue
+                                    flags[b] = kCached;
+                                    n_unlisted[node_b] += 1;
+                                    continue;
+                                }
+                                flags[b] = 0;
+                                n_cached[node_b] -= 1;
+                                const uint32_t up_b = n_parent[node_b];
+                                n_childc[up_b] -= 1;
+                                --resident;
+                                evicted[n_ev++] = b;
+                                ++g;
+                                // UpdateNodeState(parent): a parent that became a data leaf queues its blocks, in order
+                                if (up_b != 0 && n_childc[up_b] == 0 && n_unlisted[up_b] != 0) {
+                                    const uint32_t c = n_blocks[up_b];
+                                    uint32_t id = n_last[up_b];
+                                    uint32_t k = c;
+                                    while (k > 0 && id != kNone) {
+                                        tmp[--k] = id;
+                                        id = p.pred[id];
+                                    }
+                                    if (k != 0) ++faults;
+                                    for (; k < c; ++k) {
+                                        const uint32_t x = tmp[k];
+                                        if ((flags[x] & (kCached | kListed)) == kCached) {
+                                            insert_by_time(x);
+                                            flags[x] = kCached | kListed;
+                                        }
+                                    }
+                                    n_unlisted[up_b] = 0;
                                 }
                             }
-                            n_unlisted[up] = 0;
+                        }
+                        g = __shfl_sync(full, g, 0);
+                        n_ev = __shfl_sync(full, n_ev, 0);
+                        __syncwarp();
+                        got += g;
+                        if (g < want) {
+                            dry = true;
+                            break;
                         }
                     }
                     if (got == 0) break;
                     total += got;
                 }
-                // CleanEmptyBlocks (radix_tree_index.cc:284-325): childless nodes without a cached block go,
-                // among the nodes that own an evicted block, until nothing more goes
+                // CleanEmptyBlocks (radix_tree_index.cc:284-325): childless nodes without a cached block go, among
+                // the nodes that own an evicted block, until nothing more goes.  The lanes look at 32 evicted blocks
+                // at a time; lane 0 removes the nodes found.  The order of removals does not change what remains.
                 bool removed = n_ev != 0;
                 while (removed) {
-                    removed = false;
-                    for (uint32_t e = 0; e < n_ev; ++e) {
-                        const uint32_t nd = node_of[evicted[e]];
-                        if (nd == kNone || nd == 0 || n_cached[nd] != 0 || n_children[nd] != 0) continue;
-                        n_children[n_parent[nd]] -= 1;
-                        uint32_t id = n_last[nd];
-                        for (uint32_t k = n_blocks[nd]; k > 0 && id != kNone; --k) {
-                            node_of[id] = kNone;
-                            id = p.pred[id];
+                    uint32_t any = 0;
+                    for (uint32_t e0 = 0; e0 < n_ev; e0 += 32) {
+                        const uint32_t e = e0 + lane;
+                        const uint32_t nd = e < n_ev ? node_of[evicted[e]] : kNone;
+                        const bool empty = nd != kNone && nd != 0 && n_cached[nd] == 0 && n_children[nd] == 0;
+                        uint32_t found = __ballot_sync(full, empty);
+                        while (found != 0) {
+                            const int src = __ffs(found) - 1;
+                            found &= found - 1;
+                            const uint32_t gone = __shfl_sync(full, nd, src);
+                            if (lane == 0 && n_blocks[gone] != 0) {  // not already removed for another of its blocks
+                                n_children[n_parent[gone]] -= 1;
+                                uint32_t id = n_last[gone];
+                                for (uint32_t k = n_blocks[gone]; k > 0 && id != kNone; --k) {
+                                    node_of[id] = kNone;
+                                    id = p.pred[id];
+                                }
+                                n_blocks[gone] = 0;
+                                any = 1;
+                            }
                         }
-                        node_of[evicted[e]] = kNone;  // so that every pass that removes something ends an entry
-                        n_blocks[nd] = 0;
-                        removed = true;
+                        __syncwarp();
                     }
+                    removed = __shfl_sync(full, any, 0) != 0;
                 }
             }
             __syncwarp();
