@@ -12,9 +12,10 @@
 // tree is kept, per configuration, in a form a warp can walk without pointers.  Keys are prefix-unique chained
 // hashes: a key fixes the key before it.  Hence
 //   pred[id]      the key before id in its chain - the same for every configuration, built once;
-//   node_of[id]   the tree node that holds the block of key id (kNone: not in the tree).  If a key is in the
-//                 tree, so is its whole chain, and a trace's walk down the tree is the run of its leading keys
-//                 with node_of != kNone;
+//   node_of[id]   the tree node that holds the block of key id; the key is in the tree while that node has
+//                 blocks (removing a node zeroes its block count, node numbers are never reused).  If a key is
+//                 in the tree, so is its whole chain, and a trace's walk down the tree is the run of its leading
+//                 keys that are in the tree;
 //   per node      parent, number of children, number of blocks, last key, cached blocks, cached blocks of the
 //                 immediate children (zero = RadixTreeNode::isDataLeaf), cached blocks outside the queue.
 // A node's blocks are pred-steps back from its last key.  Splitting a node (radix_tree_index.cc:89-127) gives
@@ -39,6 +40,7 @@ constexpr int kNodeFields = 7;
 struct LeafSweep {
     const uint32_t *ids;
     const uint32_t *pred;
+    const uint32_t *occ;  // one position of each key in ids
     const int64_t *key_off;
     const uint8_t *type;
     const int64_t *mask_off;
@@ -51,13 +53,14 @@ struct LeafSweep {
     uint32_t *lprev;    // [n_configs][n_keys + 2]
     uint32_t *lnext;    // [n_configs][n_keys + 2]
     uint32_t *tmp;      // [n_configs][n_keys]  a node's blocks in order, while they are re-queued
-    uint32_t *evicted;  // [n_configs][n_keys]  the blocks evicted after one trace
+    uint32_t *evicted;  // [n_configs][n_keys]  the nodes of the blocks evicted after one trace
     uint32_t *nodes;    // [n_configs][kNodeFields][max_nodes]
     int32_t *ext_hit, *int_hit, *written;
     int64_t *cache_blocks;
     int64_t *totals;
     uint32_t *status;
     int64_t n_keys;
+    int64_t n_ids;  // key occurrences in ids (n_keys is this, or 1 for an empty input)
     int64_t max_nodes;
     int32_t n_traces;
     int32_t n_configs;
@@ -82,15 +85,21 @@ __global__ void LeafInitKernel(IdTable t, uint32_t *node_of, uint8_t *flags, uin
 }
 
 // pred[id of key i] = id of key i - 1 of the same trace.  Every occurrence of a key writes the same value.
+// occ[id] = a position of the key in ids (whichever occurrence writes last): the keys behind it there are a
+// guess at what follows the key in a queue, checked against the queue's links before it is used.
 __global__ void __launch_bounds__(256)
     LeafPredKernel(const uint32_t *__restrict__ ids, const int64_t *__restrict__ key_off, int32_t n_traces,
-                   uint32_t *pred) {
+                   uint32_t *pred, uint32_t *occ) {
     const int32_t warps = static_cast<int32_t>(gridDim.x * (blockDim.x >> 5));
     const uint32_t lane = LaneId();
     for (int32_t t = static_cast<int32_t>(blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)); t < n_traces;
          t += warps) {
         const int64_t beg = key_off[t], end = key_off[t + 1];
-        for (int64_t i = beg + 1 + lane; i < end; i += 32) pred[ids[i]] = ids[i - 1];
+        for (int64_t i = beg + lane; i < end; i += 32) {
+            const uint32_t id = ids[i];
+            if (i > beg) pred[id] = ids[i - 1];
+            occ[id] = static_cast<uint32_t>(i);
+        }
     }
 }
 
@@ -188,22 +197,44 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
     }
     __syncwarp();
 
+    // What a trace reads before it touches any state (its extent, kind, time and the ids of its first 32 keys) is
+    // fetched one trace ahead, its extent two traces ahead: those loads do not wait for the traces before it.
+    auto extent = [&](int32_t t, int64_t *beg, int64_t *n, uint8_t *ty, int64_t *skip, int64_t *now) {
+        if (t < p.n_traces) {
+            *beg = p.key_off[t];
+            *n = p.key_off[t + 1] - *beg;
+            *ty = p.type[t];
+            *skip = (*ty == 1 && p.mask_off != nullptr) ? p.mask_off[t] : 0;
+            *now = p.timestamps != nullptr ? p.timestamps[t] : static_cast<int64_t>(t);
+        } else {
+            *beg = 0, *n = 0, *ty = 1, *skip = 0, *now = 0;
+        }
+    };
+    int64_t beg, n, skip, now, beg1, n1, skip1, now1;
+    uint8_t ty, ty1;
+    extent(0, &beg, &n, &ty, &skip, &now);
+    extent(1, &beg1, &n1, &ty1, &skip1, &now1);
+    uint32_t first_id = lane < n ? p.ids[beg + lane] : 0u;
+
     for (int32_t t = 0; t < p.n_traces; ++t) {
-        const int64_t beg = p.key_off[t];
-        const int64_t n = p.key_off[t + 1] - beg;
-        const uint8_t ty = p.type[t];
-        const int64_t skip = (ty == 1 && p.mask_off != nullptr) ? p.mask_off[t] : 0;
-        const int64_t now = p.timestamps != nullptr ? p.timestamps[t] : static_cast<int64_t>(t);
+        const uint32_t next_first_id = lane < n1 ? p.ids[beg1 + lane] : 0u;
+        int64_t beg2, n2, skip2, now2;
+        uint8_t ty2;
+        extent(t + 2, &beg2, &n2, &ty2, &skip2, &now2);
         int32_t ext = 0, inte = 0, wr = 0;
 
         // ---- scan: where the trace leaves the tree (div) and its first block that is not cached (first_gone)
+        // A key is in the tree when its node still has blocks: removing a node only zeroes its block count.
         int64_t div = n, first_gone = -1;
+        uint32_t at_id = kNone, at_node = 0;      // the last block inside the tree and its node (the root if none)
+        uint32_t carry_id = kNone, carry_node = 0;  // the same for the previous 32 keys
         for (int64_t base = 0; base < n; base += 32) {
             const int64_t i = base + lane;
             const bool have = i < n;
-            const uint32_t id = have ? p.ids[beg + i] : 0u;
-            const uint32_t nd = have ? node_of[id] : kNone;
+            const uint32_t id = base == 0 ? first_id : (have ? p.ids[beg + i] : 0u);
+            uint32_t nd = have ? node_of[id] : kNone;
             const uint8_t fl = have ? flags[id] : 0;
+            if (nd != kNone && n_blocks[nd] == 0) nd = kNone;
             const uint32_t in_range = __ballot_sync(full, have);
             const uint32_t in_tree = __ballot_sync(full, have && nd != kNone);
             const uint32_t cached = __ballot_sync(full, have && nd != kNone && (fl & kCached) != 0);
@@ -221,10 +252,17 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                 if (gone != 0) first_gone = base + __ffs(gone) - 1;
             }
             if (out != 0) {
-                div = base + __ffs(out) - 1;
+                const int src = __ffs(out) - 1;
+                div = base + src;
+                const uint32_t id_before = __shfl_sync(full, id, src > 0 ? src - 1 : 0);
+                const uint32_t node_before = __shfl_sync(full, nd, src > 0 ? src - 1 : 0);
+                at_id = src > 0 ? id_before : carry_id;
+                at_node = src > 0 ? node_before : carry_node;
                 break;
             }
             if (ty == 1 && first_gone >= 0) break;
+            carry_id = __shfl_sync(full, id, 31);
+            carry_node = __shfl_sync(full, nd, 31);
         }
         const int64_t hit_len = ty == 2 ? 0 : (first_gone >= 0 ? first_gone : div);
 
@@ -298,23 +336,28 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
             if (div < n) {
                 // ---- where the rest goes: the end of a childless node, a new child, or a split (:30-87,89-127)
                 uint32_t target = 0, child = 0, mid = 0, do_split = 0, old_front = 0;
+                uint32_t above_target = 0, above_at = 0;  // lane 0: the parents of the target node and of at_node
                 if (lane == 0) {
-                    const uint32_t last_id = div > 0 ? p.ids[beg + div - 1] : kNone;
-                    const uint32_t at = div > 0 ? node_of[last_id] : 0u;
-                    if (div == 0 || n_last[at] == last_id) {
-                        if (at != 0 && n_children[at] == 0) {
+                    const uint32_t at = at_node;
+                    const uint32_t last_of_at = n_last[at], kids = n_children[at];
+                    above_at = n_parent[at];
+                    old_front = lnext[kHead];
+                    if (div == 0 || last_of_at == at_id) {
+                        if (at != 0 && kids == 0) {
                             target = at;
+                            above_target = above_at;
                         } else {
                             target = new_node(at);
-                            n_children[at] += 1;
+                            n_children[at] = kids + 1;
+                            above_target = at;
                         }
                     } else {
                         do_split = 1;
                         child = at;
-                        mid = new_node(n_parent[at]);
+                        mid = new_node(above_at);
                         target = new_node(mid);
+                        above_target = mid;
                     }
-                    old_front = lnext[kHead];
                 }
                 target = __shfl_sync(full, target, 0);
                 child = __shfl_sync(full, child, 0);
@@ -340,7 +383,7 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                     }
                     if (lane == 0) {
                         // every walked block is cached by now (hit, or just given its location back)
-                        const uint32_t up = n_parent[child];
+                        const uint32_t up = above_at;
                         n_children[mid] = 2;
                         n_blocks[mid] = pos;
                         n_last[mid] = p.ids[beg + div - 1];
@@ -375,7 +418,7 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                     n_blocks[target] += cnt;
                     n_cached[target] += cnt;
                     n_last[target] = p.ids[beg + n - 1];
-                    n_childc[n_parent[target]] += cnt;
+                    n_childc[above_target] += cnt;
                     resident += cnt;
                     wr += static_cast<int32_t>(cnt);
                 }
@@ -399,25 +442,41 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                     // the queue.
                     while (got < count) {
                         const uint32_t want = static_cast<uint32_t>(count - got < 32 ? count - got : 32);
-                        // lane 0 follows the queue from its cold end; the others then look at one candidate each
-                        uint32_t m = 0, after = kHead;
-                        if (lane == 0) {
-                            uint32_t b = lprev[kTail];
-                            while (m < want && b != kHead) {
-                                tmp[m++] = b;
-                                b = lprev[b];
-                            }
-                            after = b;
-                        }
-                        m = __shfl_sync(full, m, 0);
-                        after = __shfl_sync(full, after, 0);
-                        if (m == 0) {
+                        // The candidates, from the cold end of the queue.  Blocks written by one trace sit in the
+                        // queue in the trace's key order, so the keys that follow the coldest block in ids are a
+                        // guess at the blocks that follow it in the queue; each lane checks one link of the guess
+                        // and the group is the part that the queue's own links confirm.  A short group (keys shared
+                        // by many traces) falls back to lane 0 following the links one by one.
+                        const uint32_t coldest = lprev[kTail];
+                        if (coldest == kHead) {
                             dry = true;
                             break;
                         }
-                        __syncwarp();
+                        const int64_t guess_at = static_cast<int64_t>(p.occ[coldest]) + lane;
+                        uint32_t cand = lane == 0 ? coldest : (guess_at < p.n_ids ? p.ids[guess_at] : kNone);
+                        const uint32_t towards_head = cand != kNone ? lprev[cand] : kNone;
+                        const uint32_t cand_after = __shfl_down_sync(full, cand, 1);
+                        const uint32_t linked =
+                            __ballot_sync(full, lane < 31 && cand_after != kNone && towards_head == cand_after);
+                        uint32_t m = static_cast<uint32_t>(__ffs(~linked));  // confirmed links + 1 (bit 31 is never set)
+                        if (m > want) m = want;
+                        uint32_t after = __shfl_sync(full, towards_head, m - 1);
+                        if (m < want && m < 8) {
+                            m = 0;
+                            if (lane == 0) {
+                                uint32_t b = coldest;
+                                while (m < want && b != kHead) {
+                                    tmp[m++] = b;
+                                    b = lprev[b];
+                                }
+                                after = b;
+                            }
+                            m = __shfl_sync(full, m, 0);
+                            after = __shfl_sync(full, after, 0);
+                            __syncwarp();
+                            cand = lane < m ? tmp[lane] : kNone;
+                        }
                         const bool mine = lane < m;
-                        const uint32_t cand = mine ? tmp[lane] : 0u;
                         const uint32_t nd = mine ? node_of[cand] : 0u;
                         const uint32_t up = mine ? n_parent[nd] : 0u;
                         // The whole group goes at once when every candidate sits in a data leaf and no parent runs
@@ -433,7 +492,7 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                         if (__all_sync(full, plain) && static_cast<int64_t>(n_ev) + m <= nk) {
                             if (mine) {
                                 flags[cand] = 0;
-                                evicted[n_ev + lane] = cand;
+                                evicted[n_ev + lane] = nd;
                                 if (static_cast<uint32_t>(__ffs(same_nd) - 1) == lane) n_cached[nd] -= __popc(same_nd);
                             }
                             __syncwarp();  // n_childc is read above for nodes that are parents here
@@ -472,7 +531,7 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                                 const uint32_t up_b = n_parent[node_b];
                                 n_childc[up_b] -= 1;
                                 --resident;
-                                evicted[n_ev++] = b;
+                                evicted[n_ev++] = node_b;
                                 ++g;
                                 // UpdateNodeState(parent): a parent that became a data leaf queues its blocks, in order
                                 if (up_b != 0 && n_childc[up_b] == 0 && n_unlisted[up_b] != 0) {
@@ -508,34 +567,27 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                     total += got;
                 }
                 // CleanEmptyBlocks (radix_tree_index.cc:284-325): childless nodes without a cached block go, among
-                // the nodes that own an evicted block, until nothing more goes.  The lanes look at 32 evicted blocks
-                // at a time; lane 0 removes the nodes found.  The order of removals does not change what remains.
-                bool removed = n_ev != 0;
-                while (removed) {
-                    uint32_t any = 0;
+                // the nodes that own an evicted block, until nothing more goes.  The lanes look at the nodes of 32
+                // evicted blocks at a time and remove what they find; the order of removals does not change what
+                // remains.  Another round is needed only when a removal left a parent childless.
+                bool again = n_ev != 0;
+                while (again) {
+                    again = false;
                     for (uint32_t e0 = 0; e0 < n_ev; e0 += 32) {
                         const uint32_t e = e0 + lane;
-                        const uint32_t nd = e < n_ev ? node_of[evicted[e]] : kNone;
-                        const bool empty = nd != kNone && nd != 0 && n_cached[nd] == 0 && n_children[nd] == 0;
-                        uint32_t found = __ballot_sync(full, empty);
-                        while (found != 0) {
-                            const int src = __ffs(found) - 1;
-                            found &= found - 1;
-                            const uint32_t gone = __shfl_sync(full, nd, src);
-                            if (lane == 0 && n_blocks[gone] != 0) {  // not already removed for another of its blocks
-                                n_children[n_parent[gone]] -= 1;
-                                uint32_t id = n_last[gone];
-                                for (uint32_t k = n_blocks[gone]; k > 0 && id != kNone; --k) {
-                                    node_of[id] = kNone;
-                                    id = p.pred[id];
-                                }
-                                n_blocks[gone] = 0;
-                                any = 1;
-                            }
+                        const uint32_t node_e = e < n_ev ? evicted[e] : 0u;
+                        const bool empty = node_e != 0 && n_cached[node_e] == 0 && n_children[node_e] == 0 &&
+                                           n_blocks[node_e] != 0;
+                        const uint32_t same = __match_any_sync(full, empty ? node_e : kNone - lane);
+                        bool orphaned = false;
+                        if (empty && static_cast<uint32_t>(__ffs(same) - 1) == lane) {  // once per node
+                            n_blocks[node_e] = 0;  // its keys are out of the tree from here on
+                            const uint32_t above = n_parent[node_e];
+                            orphaned = atomicSub(&n_children[above], 1u) == 1u && above != 0;
                         }
+                        again = __any_sync(full, orphaned) || again;
                         __syncwarp();
                     }
-                    removed = __shfl_sync(full, any, 0) != 0;
                 }
             }
             __syncwarp();
@@ -551,6 +603,8 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
             sum_int += inte;
             sum_wr += wr;
         }
+        beg = beg1, n = n1, ty = ty1, skip = skip1, now = now1, first_id = next_first_id;
+        beg1 = beg2, n1 = n2, ty1 = ty2, skip1 = skip2, now1 = now2;
     }
     if (lane == 0) {
         if (p.totals != nullptr) {
@@ -565,7 +619,7 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
 }
 
 struct LeafLayout {
-    uint64_t table_off, ids_off, pred_off, node_of_off, flags_off, time_off, lprev_off, lnext_off, tmp_off, evicted_off,
+    uint64_t table_off, ids_off, pred_off, occ_off, node_of_off, flags_off, time_off, lprev_off, lnext_off, tmp_off, evicted_off,
         nodes_off, total;
     int64_t max_nodes;
 };
@@ -579,7 +633,8 @@ LeafLayout LayoutFor(int64_t n_keys, int32_t n_traces, int32_t n_configs) {
     l.table_off = 256;
     l.ids_off = up(l.table_off + SlotsFor(n_keys) * sizeof(ulonglong2));
     l.pred_off = up(l.ids_off + nk * 4);
-    l.node_of_off = up(l.pred_off + nk * 4);
+    l.occ_off = up(l.pred_off + nk * 4);
+    l.node_of_off = up(l.occ_off + nk * 4);
     l.flags_off = up(l.node_of_off + nk * 4 * nc);
     l.time_off = up(l.flags_off + nk * nc);
     l.lprev_off = up(l.time_off + nk * 8 * nc);
@@ -633,12 +688,14 @@ int32_t kvcm_b200_replay_leaf_lru(const int64_t *d_keys, const int64_t *d_key_of
     t.mask = kvcm::SlotsFor(n_keys_total) - 1;
     uint32_t *ids = reinterpret_cast<uint32_t *>(ws + l.ids_off);
     uint32_t *pred = reinterpret_cast<uint32_t *>(ws + l.pred_off);
+    uint32_t *occ = reinterpret_cast<uint32_t *>(ws + l.occ_off);
     const uint64_t nk = static_cast<uint64_t>(n_keys_total > 0 ? n_keys_total : 1);
     cudaStream_t s = kvcm::AsStream(stream);
     const int sms = kvcm::GetDeviceInfo().sm_count;
     kvcm::LeafSweep p;
     p.ids = ids;
     p.pred = pred;
+    p.occ = occ;
     p.key_off = d_key_off;
     p.type = d_trace_type;
     p.mask_off = d_mask_off;
@@ -660,6 +717,7 @@ int32_t kvcm_b200_replay_leaf_lru(const int64_t *d_keys, const int64_t *d_key_of
     p.totals = d_totals;
     p.status = d_status;
     p.n_keys = static_cast<int64_t>(nk);
+    p.n_ids = n_keys_total;
     p.max_nodes = l.max_nodes;
     p.n_traces = n_traces;
     p.n_configs = n_configs;
@@ -669,7 +727,7 @@ int32_t kvcm_b200_replay_leaf_lru(const int64_t *d_keys, const int64_t *d_key_of
     if (n_keys_total > 0) {
         kvcm::LruClaimIdsKernel<<<sms * 8, 256, 0, s>>>(t, d_keys, n_keys_total, d_status);
         kvcm::LruLookupIdsKernel<<<sms * 8, 256, 0, s>>>(t, d_keys, n_keys_total, ids);
-        kvcm::LeafPredKernel<<<sms * 4, 256, 0, s>>>(ids, d_key_off, n_traces, pred);
+        kvcm::LeafPredKernel<<<sms * 4, 256, 0, s>>>(ids, d_key_off, n_traces, pred, occ);
     }
     kvcm::LeafSweepKernel<<<static_cast<unsigned>(n_configs), 32, 0, s>>>(p);
     return kvcm::LaunchStatus();
