@@ -234,7 +234,8 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
             const uint32_t id = base == 0 ? first_id : (have ? p.ids[beg + i] : 0u);
             uint32_t nd = have ? node_of[id] : kNone;
             const uint8_t fl = have ? flags[id] : 0;
-            if (nd != kNone && n_blocks[nd] == 0) nd = kNone;
+            // (a cached block's node has blocks for sure, so only the others pay for the second load)
+            if (nd != kNone && (fl & kCached) == 0 && n_blocks[nd] == 0) nd = kNone;
             const uint32_t in_range = __ballot_sync(full, have);
             const uint32_t in_tree = __ballot_sync(full, have && nd != kNone);
             const uint32_t cached = __ballot_sync(full, have && nd != kNone && (fl & kCached) != 0);
@@ -279,8 +280,9 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                 uint32_t towards_tail = kNone;
                 if (have) {
                     time[id] = now;
+                    const uint32_t link = lnext[id];  // read beside the flag; it means something only when queued
                     listed = (flags[id] & kListed) != 0;
-                    if (listed) towards_tail = lnext[id];
+                    if (listed) towards_tail = link;
                 }
                 const uint32_t id_before = __shfl_up_sync(full, id, 1);
                 const uint32_t listed_m = __ballot_sync(full, listed);
@@ -319,16 +321,17 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                     if ((flags[id] & kCached) != 0) continue;
                     const uint32_t nd = node_of[id];
                     time[id] = now;
-                    n_cached[nd] += 1;
-                    n_childc[n_parent[nd]] += 1;
+                    const uint32_t above = n_parent[nd], kids = n_children[nd];
+                    atomicAdd(&n_cached[nd], 1u);
+                    atomicAdd(&n_childc[above], 1u);
                     ++resident;
                     ++wr;
-                    if (n_children[nd] == 0) {
+                    if (kids == 0) {
                         flags[id] = kCached | kListed;
                         push_front(id);
                     } else {
                         flags[id] = kCached;
-                        n_unlisted[nd] += 1;
+                        atomicAdd(&n_unlisted[nd], 1u);
                     }
                 }
             }
@@ -415,10 +418,11 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                     const uint32_t cnt = static_cast<uint32_t>(n - div);
                     lprev[old_front] = p.ids[beg + div];
                     lnext[kHead] = p.ids[beg + n - 1];
-                    n_blocks[target] += cnt;
-                    n_cached[target] += cnt;
+                    // additions without a returned value do not wait for memory
+                    atomicAdd(&n_blocks[target], cnt);
+                    atomicAdd(&n_cached[target], cnt);
                     n_last[target] = p.ids[beg + n - 1];
-                    n_childc[above_target] += cnt;
+                    atomicAdd(&n_childc[above_target], cnt);
                     resident += cnt;
                     wr += static_cast<int32_t>(cnt);
                 }
@@ -493,10 +497,14 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                             if (mine) {
                                 flags[cand] = 0;
                                 evicted[n_ev + lane] = nd;
-                                if (static_cast<uint32_t>(__ffs(same_nd) - 1) == lane) n_cached[nd] -= __popc(same_nd);
+                                if (static_cast<uint32_t>(__ffs(same_nd) - 1) == lane) {
+                                    atomicSub(&n_cached[nd], static_cast<uint32_t>(__popc(same_nd)));
+                                }
                             }
                             __syncwarp();  // n_childc is read above for nodes that are parents here
-                            if (mine && static_cast<uint32_t>(__ffs(same_up) - 1) == lane) n_childc[up] -= __popc(same_up);
+                            if (mine && static_cast<uint32_t>(__ffs(same_up) - 1) == lane) {
+                                atomicSub(&n_childc[up], static_cast<uint32_t>(__popc(same_up)));
+                            }
                             if (lane == 0) {
                                 lnext[after] = kTail;
                                 lprev[kTail] = after;

@@ -393,9 +393,12 @@ public:
     // The same traces replayed with the "lru" eviction policy once per entry of quota_blocks (the points of a
     // tradeoff curve; quota_capacity * used_percentage in blocks), all in one launch.  evict_batch and precise are
     // eviction_batch_size_per_instance and the eviction mode (false = the rough modes, which evict whole batches;
-    // true = INSTANCE_PRECISE).  (*records)[c][t] belongs to quota c and trace t.
+    // true = INSTANCE_PRECISE).  (*records)[c][t] belongs to quota c and trace t.  leaf_aware = true replays under
+    // the "leaf_aware_lru" policy instead (kv_cache_manager/optimizer/eviction_policy/leaf_aware_lru.cc:20-160); the
+    // traces' order stands in for their timestamps.
     int32_t RunTracesLru(const std::vector<ReplayTrace> &traces, const std::vector<int64_t> &quota_blocks,
-                         int32_t evict_batch, bool precise, std::vector<std::vector<ReplayRecord>> *records) {
+                         int32_t evict_batch, bool precise, std::vector<std::vector<ReplayRecord>> *records,
+                         bool leaf_aware = false) {
         const int32_t n = static_cast<int32_t>(traces.size());
         const int32_t n_cfg = static_cast<int32_t>(quota_blocks.size());
         records->assign(n_cfg, std::vector<ReplayRecord>(n, ReplayRecord{0, 0, 0, 0}));
@@ -404,7 +407,8 @@ public:
         int64_t n_keys = 0;
         int32_t rc = Pack(traces, &n_keys);
         if (rc != KVCM_OK) return rc;
-        const int64_t ws_bytes = kvcm_b200_replay_lru_workspace_bytes(n_keys, n_cfg);
+        const int64_t ws_bytes = leaf_aware ? kvcm_b200_replay_leaf_lru_workspace_bytes(n_keys, n, n_cfg)
+                                            : kvcm_b200_replay_lru_workspace_bytes(n_keys, n_cfg);
         if (ws_bytes < 0) return KVCM_EC_OUT_OF_LIMIT;
         if (!Outputs(n, n_cfg) || !quota_.Reserve(sizeof(int64_t) * n_cfg) ||
             !workspace_.Reserve(static_cast<size_t>(ws_bytes), true)) {
@@ -412,11 +416,19 @@ public:
         }
         std::memcpy(quota_.host<int64_t>(), quota_blocks.data(), sizeof(int64_t) * n_cfg);
         if (!quota_.ToDevice(sizeof(int64_t) * n_cfg, stream_)) return KVCM_ER_CUDAMEMCPY_ERROR;
-        rc = kvcm_b200_replay_lru(keys_.dev<int64_t>(), off_.dev<int64_t>(), kind_.dev<uint8_t>(),
-                                  mask_.dev<int64_t>(), nullptr, n, n_keys, quota_.dev<int64_t>(), n_cfg, evict_batch,
-                                  precise ? 1 : 0, workspace_.dev<void>(), ws_bytes, ext_.dev<int32_t>(),
-                                  int_.dev<int32_t>(), wr_.dev<int32_t>(), size_.dev<int64_t>(), nullptr, nullptr,
-                                  stream_);
+        if (leaf_aware) {
+            rc = kvcm_b200_replay_leaf_lru(keys_.dev<int64_t>(), off_.dev<int64_t>(), kind_.dev<uint8_t>(),
+                                           mask_.dev<int64_t>(), nullptr, nullptr, n, n_keys, quota_.dev<int64_t>(),
+                                           n_cfg, evict_batch, precise ? 1 : 0, workspace_.dev<void>(), ws_bytes,
+                                           ext_.dev<int32_t>(), int_.dev<int32_t>(), wr_.dev<int32_t>(),
+                                           size_.dev<int64_t>(), nullptr, nullptr, stream_);
+        } else {
+            rc = kvcm_b200_replay_lru(keys_.dev<int64_t>(), off_.dev<int64_t>(), kind_.dev<uint8_t>(),
+                                      mask_.dev<int64_t>(), nullptr, n, n_keys, quota_.dev<int64_t>(), n_cfg,
+                                      evict_batch, precise ? 1 : 0, workspace_.dev<void>(), ws_bytes,
+                                      ext_.dev<int32_t>(), int_.dev<int32_t>(), wr_.dev<int32_t>(),
+                                      size_.dev<int64_t>(), nullptr, nullptr, stream_);
+        }
         if (rc != KVCM_OK) return rc;
         rc = Fetch(static_cast<size_t>(n) * n_cfg);
         if (rc != KVCM_OK) return rc;

@@ -223,6 +223,16 @@ static void TestReplay() {
     EXPECT_EQ(sweep[1][4].external_hit_blocks, 1);
     EXPECT_EQ(sweep[1][5].current_cache_blocks, 3);
     EXPECT_EQ(replayer.RunTracesLru(lru, {}, 1, true, &sweep), KVCM_EC_BADARGS);
+    // "leaf_aware_lru" (no test in the reference; worked from eviction_policy/leaf_aware_lru.cc:85-133): [1,2,3] then
+    // [1,2,9] splits the node; with room for three blocks the shared prefix 1,2 stays and the leaf block 3 goes, where
+    // plain LRU drops block 1.
+    const std::vector<ReplayTrace> shared = {{TraceKind::WriteCache, {1, 2, 3}}, {TraceKind::WriteCache, {1, 2, 9}},
+                                             {TraceKind::GetLocation, {1, 2, 3}}};
+    EXPECT_EQ(replayer.RunTracesLru(shared, {3}, 1, true, &sweep, /*leaf_aware=*/true), KVCM_OK);
+    EXPECT_EQ(sweep[0][2].external_hit_blocks, 2);
+    EXPECT_EQ(sweep[0][2].current_cache_blocks, 3);
+    EXPECT_EQ(replayer.RunTracesLru(shared, {3}, 1, true, &sweep), KVCM_OK);
+    EXPECT_EQ(sweep[0][2].external_hit_blocks, 0);
 }
 
 int main() {
