@@ -505,8 +505,8 @@ KVCM_API int32_t kvcm_b200_replay(const int64_t *d_keys, const int64_t *d_key_of
  * independent and run in parallel (one warp each); one configuration is replayed in trace order.
  * d_workspace: kvcm_b200_replay_lru_workspace_bytes(n_keys_total, n_configs) bytes (-1: too large:
  * n_keys_total < 2^32 - 1, n_configs <= 65535), 256-byte aligned, contents irrelevant before and after.
- * Not covered here: leaf_aware_lru (kvcm_b200_replay_leaf_lru below), random_lru (a random stream),
- * several instances sharing one group quota, hierarchical tiers.
+ * Not covered here: leaf_aware_lru (kvcm_b200_replay_leaf_lru below), several instances sharing one group
+ * quota (kvcm_b200_replay_lru_group below), random_lru, hierarchical tiers.
  * ---------------------------------------------------------------------------------------- */
 KVCM_API int64_t kvcm_b200_replay_lru_workspace_bytes(int64_t n_keys_total, int32_t n_configs);
 KVCM_API int32_t kvcm_b200_replay_lru(const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type,
@@ -517,6 +517,31 @@ KVCM_API int32_t kvcm_b200_replay_lru(const int64_t *d_keys, const int64_t *d_ke
                                       int32_t *d_ext_hit, int32_t *d_int_hit, int32_t *d_written,
                                       int64_t *d_cache_blocks, int64_t *d_totals, uint32_t *d_status,
                                       kvcm_stream_t stream);
+
+/* The LRU sweep for an instance group whose instances share one quota
+ * (OptEvictionManager::EvictByGroupRough / EvictByInstanceRough / EvictByInstancePrecise and
+ * GetExcessUsageForInstanceInGroup, kv_cache_manager/optimizer/manager/eviction_manager.cc:86-266).  Every instance
+ * has a tree and a recency list of its own (kv_cache_manager/optimizer/manager/optimizer_manager.cc:66-99), so the
+ * same key in two instances is two blocks; after a write the usage of all instances is summed against the quota.
+ * d_trace_instance[t] in [0, n_instances) names the instance of trace t; the traces of all instances come in one
+ * replay (timestamp) order.  eviction_mode: 1 = EVICTION_MODE_GROUP_ROUGH (rounds of evict_batch blocks from every
+ * instance of the group), 2 = INSTANCE_ROUGH and 3 = INSTANCE_PRECISE (from the writing instance only).
+ * d_cache_blocks[c][t] is the usage of trace t's own instance after the trace (GetCurrentInstanceUsage,
+ * kv_cache_manager/optimizer/manager/optimizer_runner.cc:116,196), d_totals[c][3] the usage of the group at the end,
+ * d_instance_blocks (optional, [n_configs][n_instances]) that of every instance.  Otherwise as kvcm_b200_replay_lru
+ * ("lru" policy in every instance).  d_status[0] also counts traces with an instance out of range. */
+#define KVCM_B200_REPLAY_GROUP_MAX_INSTANCES 64
+KVCM_API int64_t kvcm_b200_replay_lru_group_workspace_bytes(int64_t n_keys_total, int32_t n_configs,
+                                                            int32_t n_instances);
+KVCM_API int32_t kvcm_b200_replay_lru_group(const int64_t *d_keys, const int64_t *d_key_off,
+                                            const uint8_t *d_trace_type, const int64_t *d_mask_off,
+                                            const uint8_t *d_mask_bits, const int32_t *d_trace_instance,
+                                            int32_t n_instances, int32_t n_traces, int64_t n_keys_total,
+                                            const int64_t *d_quota_blocks, int32_t n_configs, int32_t evict_batch,
+                                            int32_t eviction_mode, void *d_workspace, int64_t workspace_bytes,
+                                            int32_t *d_ext_hit, int32_t *d_int_hit, int32_t *d_written,
+                                            int64_t *d_cache_blocks, int64_t *d_totals, int64_t *d_instance_blocks,
+                                            uint32_t *d_status, kvcm_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
  * (2c'') The same sweep under the "leaf_aware_lru" eviction policy

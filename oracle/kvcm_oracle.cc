@@ -860,9 +860,103 @@ struct OracleLruReplay {
     }
 };
 
+// Several instances that share one group quota (OptEvictionManager::EvictByGroupRough / EvictByInstanceRough /
+// EvictByInstancePrecise over GetExcessUsageForInstanceInGroup, eviction_manager.cc:86-266; every instance has a
+// tree and a policy of its own, optimizer_manager.cc:66-99; the blocks each instance lost go to that instance's
+// CleanEmptyBlocks, indexer_manager.cc:55-90).  mode: 1 group rough, 2 instance rough, 3 instance precise.
+struct OracleLruGroup {
+    std::vector<std::unique_ptr<OracleLruReplay>> inst;
+    int64_t quota = 0;
+    int32_t batch = 1;
+    int32_t mode = 1;
+
+    void check_and_evict(size_t writer) {
+        int64_t used = 0;
+        for (const auto &i : inst) used += i->n_cached;
+        const int64_t excess = used > quota ? used - quota : 0;
+        if (excess == 0) return;
+        std::vector<std::vector<LruBlock *>> gone(inst.size());
+        int64_t total = 0;
+        if (mode == 1) {
+            while (total < excess) {
+                bool any = false;
+                for (size_t j = 0; j < inst.size(); ++j) {  // a whole round even when the excess is covered midway
+                    std::vector<LruBlock *> round = inst[j]->evict_blocks(batch);
+                    if (round.empty()) continue;
+                    any = true;
+                    total += static_cast<int64_t>(round.size());
+                    gone[j].insert(gone[j].end(), round.begin(), round.end());
+                }
+                if (!any) break;
+            }
+        } else {
+            while (total < excess) {
+                const int64_t count = mode == 3 ? std::min<int64_t>(batch, excess - total) : batch;
+                std::vector<LruBlock *> round = inst[writer]->evict_blocks(count);
+                if (round.empty()) break;
+                total += static_cast<int64_t>(round.size());
+                gone[writer].insert(gone[writer].end(), round.begin(), round.end());
+            }
+        }
+        for (size_t j = 0; j < inst.size(); ++j) {
+            if (!gone[j].empty()) inst[j]->clean(gone[j]);
+        }
+    }
+};
+
 }  // namespace
 
 extern "C" {
+
+void *kvcm_oracle_lru_group_create(int64_t quota_blocks, int32_t evict_batch, int32_t mode, int32_t n_instances,
+                                   int32_t policy) {
+    auto *g = new OracleLruGroup();
+    g->quota = quota_blocks;
+    g->batch = evict_batch;
+    g->mode = mode;
+    for (int32_t i = 0; i < n_instances; ++i) {
+        g->inst.emplace_back(new OracleLruReplay());
+        g->inst.back()->leaf_aware = policy == 1;
+    }
+    return g;
+}
+void kvcm_oracle_lru_group_destroy(void *h) { delete static_cast<OracleLruGroup *>(h); }
+
+// trace_inst[t]: the instance (0 .. n_instances-1) trace t belongs to; traces in replay order over all instances.
+// cache_blocks[t] is the usage of the trace's own instance after the trace (GetCurrentInstanceUsage,
+// optimizer_runner.cc:116,196); inst_blocks (optional, [n_instances]) the usage of every instance at the end.
+void kvcm_oracle_lru_group_run(void *h, const int64_t *keys, const int64_t *key_off, const uint8_t *type,
+                               const int64_t *mask_off, const uint8_t *mask_bits, const int64_t *timestamps,
+                               const int32_t *trace_inst, int64_t n_traces, int32_t *ext_hit, int32_t *int_hit,
+                               int32_t *written, int64_t *cache_blocks, int64_t *inst_blocks) {
+    auto *g = static_cast<OracleLruGroup *>(h);
+    for (int64_t t = 0; t < n_traces; ++t) {
+        const size_t i = static_cast<size_t>(trace_inst[t]);
+        OracleLruReplay *st = g->inst[i].get();
+        st->now = timestamps ? timestamps[t] : t;
+        const int64_t *k = keys + key_off[t];
+        const int64_t n = key_off[t + 1] - key_off[t];
+        int32_t ext = 0, inte = 0;
+        int64_t wr = 0, hits = 0;
+        if (type[t] == 1) {
+            if (n > 0) {
+                st->prefix_query(k, n, mask_off ? mask_off[t] : 0, mask_bits ? mask_bits + key_off[t] : nullptr, &ext,
+                                 &inte);
+            }
+        } else {
+            wr = st->insert(st->root.get(), k, n, type[t] == 0, true, &hits);
+            ext = static_cast<int32_t>(hits);
+            g->check_and_evict(i);
+        }
+        ext_hit[t] = ext;
+        int_hit[t] = inte;
+        written[t] = static_cast<int32_t>(wr);
+        cache_blocks[t] = st->n_cached;
+    }
+    if (inst_blocks != nullptr) {
+        for (size_t j = 0; j < g->inst.size(); ++j) inst_blocks[j] = g->inst[j]->n_cached;
+    }
+}
 
 void *kvcm_oracle_lru_replay_create(int64_t quota_blocks, int32_t evict_batch, int32_t precise) {
     auto *st = new OracleLruReplay();

@@ -453,3 +453,51 @@ class LruReplay(Replay):
                                             _ptr(ext, ctypes.c_int32), _ptr(inte, ctypes.c_int32),
                                             _ptr(wr, ctypes.c_int32), _ptr(cached, ctypes.c_int64))
         return ext, inte, wr, cached
+
+
+class LruGroupReplay:
+    """Several instances that share one group quota (kv_cache_manager/optimizer/manager/eviction_manager.cc:86-266):
+    every instance has its own radix tree and eviction policy, the quota is checked against the sum of their usage
+    after every write.  mode: 1 = EVICTION_MODE_GROUP_ROUGH (rounds of evict_batch blocks from every instance),
+    2 = INSTANCE_ROUGH and 3 = INSTANCE_PRECISE (from the writing instance only)."""
+
+    def __init__(self, quota_blocks, n_instances, evict_batch=100, mode=1, policy="lru"):
+        lib().kvcm_oracle_lru_group_create.restype = ctypes.c_void_p
+        self.n_instances = int(n_instances)
+        self._h = ctypes.c_void_p(lib().kvcm_oracle_lru_group_create(
+            ctypes.c_int64(int(quota_blocks)), ctypes.c_int32(int(evict_batch)), ctypes.c_int32(int(mode)),
+            ctypes.c_int32(self.n_instances), ctypes.c_int32(LruReplay.POLICIES[policy])))
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().kvcm_oracle_lru_group_destroy(self._h)
+            self._h = None
+
+    def run(self, keys, key_off, trace_type, trace_instance, mask_off=None, mask_bits=None, timestamps=None):
+        """Returns (external hits, internal hits, written, usage of the trace's instance) per trace and the usage
+        of every instance at the end."""
+        keys, key_off = _i64(keys), _i64(key_off)
+        n = len(key_off) - 1
+        trace_type = np.ascontiguousarray(trace_type, dtype=np.uint8)
+        trace_instance = np.ascontiguousarray(trace_instance, dtype=np.int32)
+        assert len(trace_instance) == n and (n == 0 or 0 <= trace_instance.min() <= trace_instance.max() < self.n_instances)
+        mp = bp = tp = None
+        if mask_off is not None:
+            mask_off = _i64(mask_off)
+            mp = _ptr(mask_off, ctypes.c_int64)
+        if mask_bits is not None:
+            mask_bits = np.ascontiguousarray(mask_bits, dtype=np.uint8)
+            bp = _ptr(mask_bits, ctypes.c_uint8)
+        if timestamps is not None:
+            timestamps = _i64(timestamps)
+            tp = _ptr(timestamps, ctypes.c_int64)
+        ext, inte, wr = (np.zeros(n, dtype=np.int32) for _ in range(3))
+        cached = np.zeros(n, dtype=np.int64)
+        final = np.zeros(self.n_instances, dtype=np.int64)
+        lib().kvcm_oracle_lru_group_run(self._h, _ptr(keys, ctypes.c_int64), _ptr(key_off, ctypes.c_int64),
+                                        _ptr(trace_type, ctypes.c_uint8), mp, bp, tp,
+                                        _ptr(trace_instance, ctypes.c_int32), ctypes.c_int64(n),
+                                        _ptr(ext, ctypes.c_int32), _ptr(inte, ctypes.c_int32),
+                                        _ptr(wr, ctypes.c_int32), _ptr(cached, ctypes.c_int64),
+                                        _ptr(final, ctypes.c_int64))
+        return ext, inte, wr, cached, final

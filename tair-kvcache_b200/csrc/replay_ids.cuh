@@ -25,60 +25,97 @@ __host__ __device__ __forceinline__ uint64_t Mix(uint64_t k) {
 }
 
 // Pass 1: every key gets a slot; the thread that claims the slot takes the next id.
-__global__ void __launch_bounds__(256)
-    LruClaimIdsKernel(IdTable t, const int64_t *__restrict__ keys, int64_t n_keys, uint32_t *status) {
+__device__ __forceinline__ void ClaimId(const IdTable &t, uint64_t key, uint32_t *status) {
     unsigned long long *words = reinterpret_cast<unsigned long long *>(t.slots);
-    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_keys; i += stride) {
-        const uint64_t key = static_cast<uint64_t>(keys[i]);
-        if (key == kEmptyKey) {
-            if (atomicCAS(&t.cells[1], ~0ull, ~0ull - 1) == ~0ull) t.cells[1] = atomicAdd(&t.cells[0], 1ull);
-            continue;
-        }
-        uint64_t slot = Mix(key) & t.mask;
-        bool placed = false;
-        for (uint64_t probe = 0; probe <= t.mask; ++probe) {
-            unsigned long long seen = *reinterpret_cast<volatile unsigned long long *>(&words[2 * slot]);
+    if (key == kEmptyKey) {
+        if (atomicCAS(&t.cells[1], ~0ull, ~0ull - 1) == ~0ull) t.cells[1] = atomicAdd(&t.cells[0], 1ull);
+        return;
+    }
+    uint64_t slot = Mix(key) & t.mask;
+    bool placed = false;
+    for (uint64_t probe = 0; probe <= t.mask; ++probe) {
+        unsigned long long seen = *reinterpret_cast<volatile unsigned long long *>(&words[2 * slot]);
+        if (seen == kEmptyKey) {
+            seen = atomicCAS(&words[2 * slot], kEmptyKey, key);
             if (seen == kEmptyKey) {
-                seen = atomicCAS(&words[2 * slot], kEmptyKey, key);
-                if (seen == kEmptyKey) {
-                    words[2 * slot + 1] = atomicAdd(&t.cells[0], 1ull);
-                    placed = true;
-                    break;
-                }
-            }
-            if (seen == key) {
+                words[2 * slot + 1] = atomicAdd(&t.cells[0], 1ull);
                 placed = true;
                 break;
             }
-            slot = (slot + 1) & t.mask;
         }
-        if (!placed && status != nullptr) atomicAdd(&status[0], 1u);
+        if (seen == key) {
+            placed = true;
+            break;
+        }
+        slot = (slot + 1) & t.mask;
+    }
+    if (!placed && status != nullptr) atomicAdd(&status[0], 1u);
+}
+
+// Pass 2 (a launch of its own, so every id of pass 1 is visible): key -> id.
+__device__ __forceinline__ uint32_t LookupId(const IdTable &t, uint64_t key) {
+    if (key == kEmptyKey) return static_cast<uint32_t>(t.cells[1]);
+    uint64_t slot = Mix(key) & t.mask;
+    for (uint64_t probe = 0; probe <= t.mask; ++probe) {
+        const ulonglong2 s = t.slots[slot];
+        if (s.x == key) return static_cast<uint32_t>(s.y);
+        if (s.x == kEmptyKey) break;  // not reached for a key that pass 1 placed
+        slot = (slot + 1) & t.mask;
+    }
+    return 0u;
+}
+
+__global__ void __launch_bounds__(256)
+    LruClaimIdsKernel(IdTable t, const int64_t *__restrict__ keys, int64_t n_keys, uint32_t *status) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_keys; i += stride) {
+        ClaimId(t, static_cast<uint64_t>(keys[i]), status);
     }
 }
 
-// Pass 2 (a launch of its own, so every id of pass 1 is visible): key occurrence -> id.
 __global__ void __launch_bounds__(256)
     LruLookupIdsKernel(IdTable t, const int64_t *__restrict__ keys, int64_t n_keys, uint32_t *__restrict__ ids) {
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_keys; i += stride) {
-        const uint64_t key = static_cast<uint64_t>(keys[i]);
-        uint32_t id = 0;
-        if (key == kEmptyKey) {
-            id = static_cast<uint32_t>(t.cells[1]);
-        } else {
-            uint64_t slot = Mix(key) & t.mask;
-            for (uint64_t probe = 0; probe <= t.mask; ++probe) {
-                const ulonglong2 s = t.slots[slot];
-                if (s.x == key) {
-                    id = static_cast<uint32_t>(s.y);
-                    break;
-                }
-                if (s.x == kEmptyKey) break;  // not reached for a key that pass 1 placed
-                slot = (slot + 1) & t.mask;
-            }
-        }
-        ids[i] = id;
+        ids[i] = LookupId(t, static_cast<uint64_t>(keys[i]));
+    }
+}
+
+// The same two passes over the traces of ONE instance (a warp per trace).  Instances have separate trees, so the
+// same key in two instances is two blocks: the table is cleared between instances while the id counter runs on,
+// which makes ids unique over (instance, key).
+__global__ void IdTableClearKernel(IdTable t) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    const uint64_t first = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (uint64_t i = first; i <= t.mask; i += stride) t.slots[i] = make_ulonglong2(kEmptyKey, ~0ull);
+    if (first == 0) t.cells[1] = ~0ull;
+}
+
+__global__ void __launch_bounds__(256)
+    LruClaimIdsOfInstanceKernel(IdTable t, const int64_t *__restrict__ keys, const int64_t *__restrict__ key_off,
+                                const int32_t *__restrict__ trace_inst, int32_t n_traces, int32_t which,
+                                uint32_t *status) {
+    const int32_t warps = static_cast<int32_t>(gridDim.x * (blockDim.x >> 5));
+    const uint32_t lane = LaneId();
+    for (int32_t tr = static_cast<int32_t>(blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)); tr < n_traces;
+         tr += warps) {
+        if (trace_inst[tr] != which) continue;
+        const int64_t end = key_off[tr + 1];
+        for (int64_t i = key_off[tr] + lane; i < end; i += 32) ClaimId(t, static_cast<uint64_t>(keys[i]), status);
+    }
+}
+
+__global__ void __launch_bounds__(256)
+    LruLookupIdsOfInstanceKernel(IdTable t, const int64_t *__restrict__ keys, const int64_t *__restrict__ key_off,
+                                 const int32_t *__restrict__ trace_inst, int32_t n_traces, int32_t which,
+                                 uint32_t *__restrict__ ids) {
+    const int32_t warps = static_cast<int32_t>(gridDim.x * (blockDim.x >> 5));
+    const uint32_t lane = LaneId();
+    for (int32_t tr = static_cast<int32_t>(blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)); tr < n_traces;
+         tr += warps) {
+        if (trace_inst[tr] != which) continue;
+        const int64_t end = key_off[tr + 1];
+        for (int64_t i = key_off[tr] + lane; i < end; i += 32) ids[i] = LookupId(t, static_cast<uint64_t>(keys[i]));
     }
 }
 

@@ -208,6 +208,203 @@ __global__ void __launch_bounds__(32) LruSweepKernel(const LruSweep p) {
     }
 }
 
+// ---- several instances that share one group quota -------------------------------------------------------------
+// OptEvictionManager::EvictByGroupRough / EvictByInstanceRough / EvictByInstancePrecise over the summed usage of the
+// group (kv_cache_manager/optimizer/manager/eviction_manager.cc:86-266).  Every instance has a tree and a recency list
+// of its own (kv_cache_manager/optimizer/manager/optimizer_manager.cc:66-99), here a region of the queue per
+// instance; ids are unique over (instance, key), so the per-key stamps need no instance.
+struct LruGroup {
+    const int32_t *trace_inst;  // per trace, 0 .. n_instances-1
+    const int64_t *queue_base;  // [n_instances + 1]: where each instance's region of the queue starts
+    int64_t *inst_blocks;       // optional, [n_configs][n_instances]: usage per instance at the end
+    int32_t n_instances;
+    int32_t mode;               // 1 group rough, 2 instance rough, 3 instance precise
+};
+
+// Key occurrences per instance, then their running sum: an instance appends at most one queue entry per occurrence.
+__global__ void __launch_bounds__(1024)
+    LruGroupExtentKernel(const int64_t *__restrict__ key_off, const int32_t *__restrict__ trace_inst, int32_t n_traces,
+                         int32_t n_instances, int64_t *queue_base, uint32_t *status) {
+    extern __shared__ unsigned long long count[];
+    for (int32_t j = threadIdx.x; j < n_instances; j += blockDim.x) count[j] = 0ull;
+    __syncthreads();
+    for (int32_t t = threadIdx.x; t < n_traces; t += blockDim.x) {
+        const int32_t j = trace_inst[t];
+        if (j < 0 || j >= n_instances) {
+            if (status != nullptr) atomicAdd(&status[0], 1u);
+            continue;
+        }
+        atomicAdd(&count[j], static_cast<unsigned long long>(key_off[t + 1] - key_off[t]));
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int64_t at = 0;
+        for (int32_t j = 0; j < n_instances; ++j) {
+            queue_base[j] = at;
+            at += static_cast<int64_t>(count[j]);
+        }
+        queue_base[n_instances] = at;
+    }
+}
+
+__global__ void __launch_bounds__(32) LruGroupSweepKernel(const LruSweep p, const LruGroup g) {
+    extern __shared__ int64_t per_inst[];
+    const int32_t K = g.n_instances;
+    int64_t *head = per_inst, *tail = per_inst + K, *cached = per_inst + 2 * K, *take = per_inst + 3 * K;
+    const int32_t cfg = blockIdx.x;
+    const uint32_t lane = LaneId();
+    const uint32_t lt = (1u << lane) - 1u;
+    uint32_t *stamp = p.stamps + static_cast<int64_t>(cfg) * p.n_keys;
+    uint2 *queue = p.queue + static_cast<int64_t>(cfg) * p.n_keys;
+    const int64_t quota = p.quota[cfg];
+    const int64_t out0 = static_cast<int64_t>(cfg) * p.n_traces;
+    uint32_t counter = 0;
+    int64_t resident = 0;  // of the whole group
+    int64_t sum_ext = 0, sum_int = 0, sum_wr = 0;
+    for (int32_t j = lane; j < K; j += 32) {
+        head[j] = tail[j] = g.queue_base[j];
+        cached[j] = 0;
+    }
+    __syncwarp();
+
+    for (int32_t t = 0; t < p.n_traces; ++t) {
+        const int64_t beg = p.key_off[t];
+        const int64_t n = p.key_off[t + 1] - beg;
+        const uint8_t ty = p.type[t];
+        const int64_t skip = (ty == 1 && p.mask_off != nullptr) ? p.mask_off[t] : 0;
+        int32_t me = g.trace_inst[t];
+        if (me < 0 || me >= K) me = 0;  // counted by LruGroupExtentKernel
+        int64_t my_tail = tail[me];
+        int32_t ext = 0, inte = 0, wr = 0;
+        bool alive = ty != 2;
+        for (int64_t base = 0; base < n; base += 32) {
+            const int64_t i = base + lane;
+            const bool have = i < n;
+            const uint32_t id = have ? p.ids[beg + i] : 0u;
+            const uint32_t cur = have ? stamp[id] : 0u;
+            const uint32_t in_range = __ballot_sync(0xffffffffu, have);
+            const uint32_t hit = __ballot_sync(0xffffffffu, have && cur != 0u);
+            const uint32_t miss = in_range & ~hit;
+            uint32_t touch = 0;
+            if (alive) {
+                touch = miss != 0 ? hit & ((1u << (__ffs(miss) - 1)) - 1u) : hit;
+                const uint32_t masked = __ballot_sync(
+                    0xffffffffu, i < skip || (ty == 1 && p.mask_bits != nullptr && have && p.mask_bits[beg + i] != 0));
+                ext += __popc(touch & ~masked);
+                inte += __popc(touch & masked);
+                if (miss != 0) alive = false;
+            }
+            const uint32_t write = ty == 1 ? 0u : miss;
+            const uint32_t n_touch = __popc(touch), n_write = __popc(write);
+            if ((touch >> lane) & 1u) {
+                const uint32_t r = __popc(touch & lt);
+                stamp[id] = counter + 1 + r;
+                queue[my_tail + r] = make_uint2(id, counter + 1 + r);
+            } else if ((write >> lane) & 1u) {
+                const uint32_t r = n_touch + __popc(write & lt);
+                stamp[id] = counter + 1 + r;
+                queue[my_tail + r] = make_uint2(id, counter + 1 + r);
+            }
+            counter += n_touch + n_write;
+            my_tail += n_touch + n_write;
+            resident += n_write;
+            wr += static_cast<int32_t>(n_write);
+            __syncwarp();
+            if (ty == 1 && !alive) break;
+        }
+        int64_t my_cached = cached[me] + wr;
+        __syncwarp();
+        if (lane == 0) {
+            tail[me] = my_tail;
+            cached[me] = my_cached;
+        }
+        __syncwarp();
+        if (ty != 1 && resident > quota) {
+            const int64_t excess = resident - quota;
+            // How many blocks every instance loses.  The instances' lists are independent, so only the counts
+            // depend on the order of the reference's rounds, and they follow from the usages alone.
+            if (g.mode == 1) {
+                if (lane == 0) {
+                    for (int32_t j = 0; j < K; ++j) take[j] = 0;
+                    int64_t total = 0;
+                    while (total < excess) {
+                        bool any = false;
+                        for (int32_t j = 0; j < K; ++j) {  // a whole round even when the excess is covered midway
+                            const int64_t left = cached[j] - take[j];
+                            const int64_t got = left < p.evict_batch ? left : p.evict_batch;
+                            if (got > 0) {
+                                take[j] += got;
+                                total += got;
+                                any = true;
+                            }
+                        }
+                        if (!any) break;
+                    }
+                }
+            } else {
+                int64_t need = excess;
+                if (g.mode == 2) need = (excess + p.evict_batch - 1) / p.evict_batch * p.evict_batch;
+                if (need > my_cached) need = my_cached;
+                for (int32_t j = lane; j < K; j += 32) take[j] = j == me ? need : 0;
+            }
+            __syncwarp();
+            const int32_t first = g.mode == 1 ? 0 : me, last = g.mode == 1 ? K : me + 1;
+            for (int32_t j = first; j < last; ++j) {
+                int64_t need = take[j];
+                if (need == 0) continue;
+                int64_t hd = head[j];
+                const int64_t tl = tail[j];
+                int64_t popped = 0;
+                while (need > 0 && hd < tl) {
+                    const int64_t q = hd + lane;
+                    const uint2 e = q < tl ? queue[q] : make_uint2(0u, 0u);
+                    const bool live = q < tl && stamp[e.x] == e.y;
+                    const uint32_t lives = __ballot_sync(0xffffffffu, live);
+                    uint32_t out = lives;
+                    int64_t step = tl - hd < 32 ? tl - hd : 32;
+                    if (static_cast<int64_t>(__popc(lives)) > need) {
+                        const bool mine = live && static_cast<int64_t>(__popc(lives & lt)) < need;
+                        out = __ballot_sync(0xffffffffu, mine);
+                        step = 32 - __clz(out);
+                    }
+                    if ((out >> lane) & 1u) stamp[e.x] = 0u;
+                    const int64_t n_out = __popc(out);
+                    need -= n_out;
+                    popped += n_out;
+                    hd += step;
+                    __syncwarp();
+                }
+                resident -= popped;
+                if (j == me) my_cached -= popped;
+                if (lane == 0) {
+                    head[j] = hd;
+                    cached[j] -= popped;
+                }
+                __syncwarp();
+            }
+        }
+        if (lane == 0 && p.ext_hit != nullptr) {
+            p.ext_hit[out0 + t] = ext;
+            p.int_hit[out0 + t] = inte;
+            p.written[out0 + t] = wr;
+            p.cache_blocks[out0 + t] = my_cached;
+        }
+        sum_ext += ext;
+        sum_int += inte;
+        sum_wr += wr;
+    }
+    if (lane == 0 && p.totals != nullptr) {
+        int64_t *tot = p.totals + static_cast<int64_t>(cfg) * 4;
+        tot[0] = sum_ext;
+        tot[1] = sum_int;
+        tot[2] = sum_wr;
+        tot[3] = resident;
+    }
+    if (g.inst_blocks != nullptr) {
+        for (int32_t j = lane; j < K; j += 32) g.inst_blocks[static_cast<int64_t>(cfg) * K + j] = cached[j];
+    }
+}
+
 struct LruLayout {
     uint64_t table_off, ids_off, stamps_off, queue_off, total;
 };
@@ -290,6 +487,95 @@ int32_t kvcm_b200_replay_lru(const int64_t *d_keys, const int64_t *d_key_off, co
     p.evict_batch = evict_batch;
     p.precise = precise;
     kvcm::LruSweepKernel<<<static_cast<unsigned>(n_configs), 32, 0, s>>>(p);
+    return kvcm::LaunchStatus();
+}
+
+}  // extern "C"
+
+extern "C" {
+
+int64_t kvcm_b200_replay_lru_group_workspace_bytes(int64_t n_keys_total, int32_t n_configs, int32_t n_instances) {
+    const int64_t base = kvcm_b200_replay_lru_workspace_bytes(n_keys_total, n_configs);
+    if (base < 0 || n_instances <= 0 || n_instances > KVCM_B200_REPLAY_GROUP_MAX_INSTANCES) return -1;
+    return base + ((static_cast<int64_t>(n_instances) + 1) * 8 + 255) / 256 * 256;
+}
+
+int32_t kvcm_b200_replay_lru_group(const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type,
+                                   const int64_t *d_mask_off, const uint8_t *d_mask_bits,
+                                   const int32_t *d_trace_instance, int32_t n_instances, int32_t n_traces,
+                                   int64_t n_keys_total, const int64_t *d_quota_blocks, int32_t n_configs,
+                                   int32_t evict_batch, int32_t eviction_mode, void *d_workspace,
+                                   int64_t workspace_bytes, int32_t *d_ext_hit, int32_t *d_int_hit, int32_t *d_written,
+                                   int64_t *d_cache_blocks, int64_t *d_totals, int64_t *d_instance_blocks,
+                                   uint32_t *d_status, kvcm_stream_t stream) {
+    if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
+    if (n_traces < 0 || n_keys_total < 0 || n_configs <= 0 || evict_batch <= 0 || n_instances <= 0 ||
+        eviction_mode < 1 || eviction_mode > 3) {
+        return KVCM_EC_BADARGS;
+    }
+    const int64_t need = kvcm_b200_replay_lru_group_workspace_bytes(n_keys_total, n_configs, n_instances);
+    if (need < 0) return KVCM_EC_OUT_OF_LIMIT;
+    if (n_traces == 0) return KVCM_OK;
+    const int per_trace = (d_ext_hit != nullptr) + (d_int_hit != nullptr) + (d_written != nullptr) +
+                          (d_cache_blocks != nullptr);
+    if (d_key_off == nullptr || d_trace_type == nullptr || d_quota_blocks == nullptr || d_workspace == nullptr ||
+        d_trace_instance == nullptr || (d_keys == nullptr && n_keys_total > 0) || (per_trace != 0 && per_trace != 4) ||
+        (per_trace == 0 && d_totals == nullptr)) {
+        return KVCM_ER_INVALID_ADDRESS;
+    }
+    if (reinterpret_cast<uintptr_t>(d_workspace) & 255u) return KVCM_ER_INVALID_ADDRESS;
+    if (workspace_bytes < need) return KVCM_EC_NOSPC;
+    const kvcm::LruLayout l = kvcm::LayoutFor(n_keys_total, n_configs);
+    uint8_t *ws = static_cast<uint8_t *>(d_workspace);
+    kvcm::IdTable t;
+    t.cells = reinterpret_cast<unsigned long long *>(ws);
+    t.slots = reinterpret_cast<ulonglong2 *>(ws + l.table_off);
+    t.mask = kvcm::SlotsFor(n_keys_total) - 1;
+    uint32_t *ids = reinterpret_cast<uint32_t *>(ws + l.ids_off);
+    uint32_t *stamps = reinterpret_cast<uint32_t *>(ws + l.stamps_off);
+    int64_t *queue_base = reinterpret_cast<int64_t *>(ws + l.total);
+    cudaStream_t s = kvcm::AsStream(stream);
+    const int sms = kvcm::GetDeviceInfo().sm_count;
+    const uint64_t n_stamps = static_cast<uint64_t>(n_keys_total) * static_cast<uint64_t>(n_configs);
+    kvcm::LruInitKernel<<<sms * 8, 256, 0, s>>>(t, stamps, n_stamps);
+    kvcm::LruGroupExtentKernel<<<1, 1024, sizeof(unsigned long long) * n_instances, s>>>(
+        d_key_off, d_trace_instance, n_traces, n_instances, queue_base, d_status);
+    if (n_keys_total > 0) {
+        // one instance after the other: the table starts empty each time, the id counter runs on
+        for (int32_t j = 0; j < n_instances; ++j) {
+            if (j > 0) kvcm::IdTableClearKernel<<<sms * 8, 256, 0, s>>>(t);
+            kvcm::LruClaimIdsOfInstanceKernel<<<sms * 4, 256, 0, s>>>(t, d_keys, d_key_off, d_trace_instance, n_traces, j,
+                                                                     d_status);
+            kvcm::LruLookupIdsOfInstanceKernel<<<sms * 4, 256, 0, s>>>(t, d_keys, d_key_off, d_trace_instance, n_traces,
+                                                                      j, ids);
+        }
+    }
+    kvcm::LruSweep p;
+    p.ids = ids;
+    p.key_off = d_key_off;
+    p.type = d_trace_type;
+    p.mask_off = d_mask_off;
+    p.mask_bits = d_mask_bits;
+    p.quota = d_quota_blocks;
+    p.stamps = stamps;
+    p.queue = reinterpret_cast<uint2 *>(ws + l.queue_off);
+    p.ext_hit = d_ext_hit;
+    p.int_hit = d_int_hit;
+    p.written = d_written;
+    p.cache_blocks = d_cache_blocks;
+    p.totals = d_totals;
+    p.n_keys = n_keys_total > 0 ? n_keys_total : 1;
+    p.n_traces = n_traces;
+    p.n_configs = n_configs;
+    p.evict_batch = evict_batch;
+    p.precise = eviction_mode == 3;
+    kvcm::LruGroup g;
+    g.trace_inst = d_trace_instance;
+    g.queue_base = queue_base;
+    g.inst_blocks = d_instance_blocks;
+    g.n_instances = n_instances;
+    g.mode = eviction_mode;
+    kvcm::LruGroupSweepKernel<<<static_cast<unsigned>(n_configs), 32, sizeof(int64_t) * 4 * n_instances, s>>>(p, g);
     return kvcm::LaunchStatus();
 }
 

@@ -145,3 +145,64 @@ def RunTracesLru(keys: torch.Tensor, key_off: torch.Tensor, trace_type: torch.Te
                workspace.numel(), ptr(ext), ptr(inte), ptr(wr), ptr(size), totals.data_ptr(),
                status.data_ptr() if status is not None else None, torch.cuda.current_stream(dev).cuda_stream)
     return LruSweepResult(ext, inte, wr, size, totals)
+
+
+EVICTION_MODE_GROUP_ROUGH, EVICTION_MODE_INSTANCE_ROUGH, EVICTION_MODE_INSTANCE_PRECISE = 1, 2, 3
+
+
+class LruGroupSweepResult(NamedTuple):
+    external_hit_blocks: Optional[torch.Tensor]   # int32 [n_configs, n_traces]; None with per_trace=False
+    internal_hit_blocks: Optional[torch.Tensor]
+    write_blocks: Optional[torch.Tensor]
+    current_cache_blocks: Optional[torch.Tensor]  # int64 [n_configs, n_traces]: usage of the trace's own instance
+    totals: torch.Tensor           # int64 [n_configs, 4]: hits ext / int, written blocks, usage of the group at the end
+    instance_blocks: torch.Tensor  # int64 [n_configs, n_instances]: usage of every instance at the end
+
+
+def RunTracesLruGroup(keys: torch.Tensor, key_off: torch.Tensor, trace_type: torch.Tensor,
+                      trace_instance: torch.Tensor, n_instances: int, quota_blocks,
+                      mask_off: Optional[torch.Tensor] = None, evict_batch: int = 100,
+                      mode: int = EVICTION_MODE_GROUP_ROUGH, workspace: Optional[torch.Tensor] = None,
+                      status: Optional[torch.Tensor] = None, per_trace: bool = True,
+                      mask_bits: Optional[torch.Tensor] = None) -> LruGroupSweepResult:
+    """The "lru" sweep for an instance group whose instances share one quota
+    (kv_cache_manager/optimizer/manager/eviction_manager.cc:86-266): trace_instance (int32 per trace, values in
+    [0, n_instances)) names each trace's instance, the traces of all instances come in one replay order, and the
+    same key in two instances is two blocks.  mode is the reference's eviction_mode: GROUP_ROUGH takes rounds of
+    evict_batch blocks from every instance, the INSTANCE modes take from the writing instance only."""
+    if not keys.is_cuda:
+        raise ValueError("keys must be a CUDA tensor: this path has no CPU implementation")
+    dev = keys.device
+    keys, key_off, trace_type = keys.contiguous(), key_off.contiguous(), trace_type.contiguous()
+    quota = torch.as_tensor(quota_blocks, dtype=torch.int64).reshape(-1).to(dev).contiguous()
+    n_cfg, n_traces = quota.numel(), key_off.numel() - 1
+    if n_cfg == 0:
+        raise ValueError("quota_blocks is empty")
+    if trace_instance.dtype != torch.int32 or trace_instance.numel() != n_traces or trace_instance.device != dev:
+        raise ValueError("trace_instance must be an int32 tensor with one entry per trace, on the keys' device")
+    trace_instance = trace_instance.contiguous()
+    need = _cabi.lib().kvcm_b200_replay_lru_group_workspace_bytes(keys.numel(), n_cfg, int(n_instances))
+    if need < 0:
+        raise ValueError("too many keys, configurations or instances for one group replay call")
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+    elif workspace.numel() < need or workspace.device != dev:
+        raise ValueError("workspace too small: %d < %d bytes" % (workspace.numel(), need))
+    totals = torch.zeros((n_cfg, 4), dtype=torch.int64, device=dev)
+    inst = torch.zeros((n_cfg, int(n_instances)), dtype=torch.int64, device=dev)
+    ext = inte = wr = size = None
+    if per_trace:
+        ext = torch.empty((n_cfg, n_traces), dtype=torch.int32, device=dev)
+        inte, wr = torch.empty_like(ext), torch.empty_like(ext)
+        size = torch.empty((n_cfg, n_traces), dtype=torch.int64, device=dev)
+    ptr = (lambda t: t.data_ptr() if t is not None and t.numel() > 0 else None)
+    if n_traces == 0:
+        return LruGroupSweepResult(ext, inte, wr, size, totals, inst)
+    _cabi.bind_device(dev.index)
+    _cabi.call("kvcm_b200_replay_lru_group", keys.data_ptr(), key_off.data_ptr(), trace_type.data_ptr(),
+               mask_off.contiguous().data_ptr() if mask_off is not None else None, _mask_bits_ptr(mask_bits, keys),
+               trace_instance.data_ptr(), int(n_instances), n_traces, keys.numel(), quota.data_ptr(), n_cfg,
+               int(evict_batch), int(mode), workspace.data_ptr(), workspace.numel(), ptr(ext), ptr(inte), ptr(wr),
+               ptr(size), totals.data_ptr(), inst.data_ptr(), status.data_ptr() if status is not None else None,
+               torch.cuda.current_stream(dev).cuda_stream)
+    return LruGroupSweepResult(ext, inte, wr, size, totals, inst)

@@ -339,3 +339,26 @@ def test_leaf_aware_lru_with_room_for_everything_is_the_plain_replay():
     tight = oracle.LruReplay(20, evict_batch=4, policy="leaf_aware_lru").run(keys, off, types, mo)
     lru = oracle.LruReplay(20, evict_batch=4).run(keys, off, types, mo)
     assert not np.array_equal(tight[0], want[0]) and not np.array_equal(tight[0], lru[0])
+
+
+def test_lru_group_quota_shared_by_two_instances():
+    # kv_cache_manager/optimizer/manager/eviction_manager.cc:86-146,148-239 by hand (the reference tests groups of one
+    # instance only, eviction_manager_test.cc): instances a and b write the same keys into separate trees, quota 4,
+    # batches of 1.  a: 1 2 3, b: 1 2 -> 5 cached, one over.  GROUP_ROUGH takes a block from a AND from b in its one
+    # round; the instance modes take one block from the writer b only.
+    keys, off, types, inst = [1, 2, 3, 1, 2, 1, 2, 3, 1, 2], [0, 3, 5, 8, 10], [W, W, G, G], [0, 1, 0, 1]
+    ext, inte, wr, size, final = oracle.LruGroupReplay(4, 2, evict_batch=1, mode=1).run(keys, off, types, inst)
+    assert size.tolist() == [3, 1, 2, 1] and final.tolist() == [2, 1] and ext.tolist() == [0, 0, 0, 0]
+    for mode in (2, 3):
+        ext, inte, wr, size, final = oracle.LruGroupReplay(4, 2, evict_batch=1, mode=mode).run(keys, off, types, inst)
+        assert size.tolist() == [3, 1, 3, 1] and final.tolist() == [3, 1] and ext.tolist() == [0, 0, 3, 0]
+    # a group of one instance is the plain replay in every mode
+    rng = np.random.default_rng(9)
+    k = rng.integers(1, 50, size=400).tolist()
+    o = list(range(0, 401, 4))
+    ty = rng.integers(0, 3, size=100).tolist()
+    for mode, precise in ((1, False), (2, False), (3, True)):
+        a = oracle.LruReplay(30, evict_batch=3, precise=precise).run(k, o, ty)
+        b = oracle.LruGroupReplay(30, 1, evict_batch=3, mode=mode).run(k, o, ty, [0] * 100)
+        for x, y in zip(a, b):
+            assert np.array_equal(x, y)
