@@ -4,5 +4,5 @@ from .replay import (EVICTION_MODE_GROUP_ROUGH, EVICTION_MODE_INSTANCE_PRECISE, 
                      LruGroupSweepResult, LruSweepResult, ReplayResult, RunTraces, RunTracesLru, RunTracesLruGroup,
                      replay_lru_workspace_bytes, replay_workspace_bytes)
 from . import trace_reader  # noqa: F401
-from .runner import (export_hit_rates, parse_startup_config, replay_instance, run_startup_config,  # noqa: F401
-                     run_trace_file, sweep_hit_rates, tradeoff_curve)
+from .runner import (export_hit_rates, parse_startup_config, replay_group, replay_instance,  # noqa: F401
+                     run_startup_config, run_trace_file, sweep_hit_rates, tradeoff_curve)

@@ -12,7 +12,7 @@ import torch
 
 from ..manager.hash_util import ApplyPrefixHashBatch
 from . import trace_reader as tr
-from .replay import RunTraces, RunTracesLru
+from .replay import RunTraces, RunTracesLru, RunTracesLruGroup
 
 CSV_HEADER = ("TimestampUs,CachedBlocksCurrentInstance,CachedBlocksPerInstance,CachedBlocksAllInstance,"
               "InternalReadBlocks,ExternalReadBlocks,TotalReadBlocks,InternalHitBlocks,"
@@ -73,6 +73,38 @@ def _kept(traces: List[tr.Trace], rw_separation: bool) -> List[tr.Trace]:
             continue
         keep.append(t)
     return keep
+
+
+def replay_group(traces: List[tr.Trace], instance_ids: Sequence[str], device, quota_blocks: int,
+                 rw_separation: bool = False, evict_batch: int = 100, mode: int = 1) -> Dict[str, Dict[str, np.ndarray]]:
+    """Replays the traces of the instances of ONE group that share a quota ("lru" policy in every instance), in the
+    order given (all instances together, by timestamp), and returns one record per instance as replay_instance
+    does.  mode is the configuration's eviction_mode (1 group rough, 2 instance rough, 3 instance precise;
+    kv_cache_manager/optimizer/manager/eviction_manager.cc:57-239).  current_cache_blocks is the usage of the
+    trace's own instance; the usage of the other instances at that moment is not recorded."""
+    index = {iid: j for j, iid in enumerate(instance_ids)}
+    keep = [t for t in _kept(traces, rw_separation) if t.instance_id in index]
+    keys, off, kind, mask, read = tr.to_csr(keep)
+    d_keys, d_off = torch.from_numpy(keys).to(device), torch.from_numpy(off).to(device)
+    if any(t.needs_prefix_hash for t in keep):
+        d_keys = ApplyPrefixHashBatch(d_keys, d_off)
+    inst = np.array([index[t.instance_id] for t in keep], dtype=np.int32)
+    ts = np.array([t.timestamp_us for t in keep], dtype=np.int64)
+    bits = tr.mask_bits(keep, off)
+    res = RunTracesLruGroup(d_keys, d_off, torch.from_numpy(kind).to(device), torch.from_numpy(inst).to(device),
+                            len(instance_ids), [int(quota_blocks)], torch.from_numpy(mask).to(device), evict_batch,
+                            mode, mask_bits=torch.from_numpy(bits).to(device) if bits is not None else None)
+    ext, inte, wr, size = (x[0].cpu().numpy() for x in res[:4])
+    internal_read = np.array([tr.masked_count(t.block_mask, len(t.keys)) if t.kind == tr.GET_LOCATION else 0
+                              for t in keep], dtype=np.int64)
+    external_read = np.where(kind == tr.WRITE_CACHE, 0, read - internal_read)
+    out = {}
+    for iid, j in index.items():
+        m = inst == j
+        out[iid] = dict(timestamp_us=ts[m], kind=kind[m], external_read_blocks=external_read[m],
+                        internal_read_blocks=internal_read[m], external_hit_blocks=ext[m],
+                        internal_hit_blocks=inte[m], write_blocks=wr[m], current_cache_blocks=size[m])
+    return out
 
 
 def sweep_hit_rates(traces: List[tr.Trace], device, quota_blocks: Sequence[int], rw_separation: bool = False,
@@ -141,10 +173,14 @@ def run_trace_file(trace_path: str, trace_type: str, output_dir: str, device=Non
                    block_sizes: Optional[Dict[str, int]] = None, rw_separation: bool = False,
                    quota_blocks: Union[None, int, Sequence[int], Dict[str, Union[int, Sequence[int]]]] = None,
                    evict_batch: int = 100, precise: bool = False,
-                   policy: Union[str, Dict[str, str]] = "lru"):
+                   policy: Union[str, Dict[str, str]] = "lru",
+                   groups: Optional[Sequence[dict]] = None, mode: int = 1):
     """Loads a trace file, replays every instance on the GPU and writes `<instance>_hit_rates.csv` per instance
     (`<instance>_quota<q>_hit_rates.csv` per instance and quota when quota_blocks is a sequence).  Every instance is
-    replayed on its own: instances that share one group quota in the reference's configuration are not modelled."""
+    replayed on its own, except the instances of a group in `groups` (dicts with "instances" = the ids and "quota" =
+    the shared quota in blocks, as parse_startup_config returns them), which are replayed together against their
+    shared quota under eviction `mode` (replay_group; in their CSV files the three cached-blocks columns hold the
+    file's own instance, the reference lists every instance there in the order of an unordered_map)."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     traces = tr.load_traces(trace_path, trace_type, block_sizes)
     by_instance: Dict[str, List[tr.Trace]] = {}
@@ -152,6 +188,13 @@ def run_trace_file(trace_path: str, trace_type: str, output_dir: str, device=Non
         by_instance.setdefault(t.instance_id, []).append(t)
     os.makedirs(output_dir, exist_ok=True)
     out = {}
+    for group in groups or []:
+        recs = replay_group(traces, group["instances"], device, group["quota"], rw_separation, evict_batch, mode)
+        for instance_id, r in recs.items():
+            by_instance.pop(instance_id, None)
+            if (r["kind"] != tr.WRITE_CACHE).any():
+                export_hit_rates(os.path.join(output_dir, instance_id + "_hit_rates.csv"), r)
+            out[instance_id] = r
     for instance_id, ts in sorted(by_instance.items()):
         # a dict gives every instance its own quota (or quotas); instances it does not name are never evicted
         quota = quota_blocks.get(instance_id) if isinstance(quota_blocks, dict) else quota_blocks
@@ -177,7 +220,7 @@ def parse_startup_config(config: Union[str, dict]) -> dict:
     by kv_cache_manager/optimizer/config/optimizer_config.cc:4-12, instance_group_config.cc:5-12,
     instance_config.cc:6-22, eviction_config.cc:5-8) reduced to what the GPU replay needs.  Raises
     NotImplementedError for what it cannot replay exactly: the "random_lru" policy, hierarchical eviction, and
-    groups whose quota is shared by several instances."""
+    groups of several instances unless all of them use "lru" (those come back under "groups")."""
     if isinstance(config, str):
         with open(config) as f:
             config = json.load(f)
@@ -186,14 +229,18 @@ def parse_startup_config(config: Union[str, dict]) -> dict:
     if mode not in (EVICTION_MODE_UNSPECIFIED, EVICTION_MODE_GROUP_ROUGH, EVICTION_MODE_INSTANCE_ROUGH,
                     EVICTION_MODE_INSTANCE_PRECISE):
         raise ValueError("unknown eviction_mode %r" % mode)
-    quotas, block_sizes, policies = {}, {}, {}
+    quotas, block_sizes, policies, shared = {}, {}, {}, []
     for group in config.get("instance_groups", []):
         instances = group.get("instances", [])
         if group.get("hierarchical_eviction_enabled", False):
             raise NotImplementedError("group %r: hierarchical eviction is not replayed" % group.get("group_name"))
-        if len(instances) > 1 and mode != EVICTION_MODE_UNSPECIFIED:
-            raise NotImplementedError("group %r: %d instances share one quota" % (group.get("group_name"),
-                                                                                   len(instances)))
+        together = len(instances) > 1 and mode != EVICTION_MODE_UNSPECIFIED
+        if together and any(i.get("eviction_policy_type", "lru") != "lru" for i in instances):
+            raise NotImplementedError("group %r: %d instances share one quota and not all of them use \"lru\""
+                                      % (group.get("group_name"), len(instances)))
+        if together:
+            shared.append(dict(group_name=group.get("group_name"), instances=[str(i["instance_id"]) for i in instances],
+                               quota=int(group["quota_capacity"] * float(group.get("used_percentage", 1.0)))))
         for inst in instances:
             policy = inst.get("eviction_policy_type", "lru")
             if policy not in ("lru", "leaf_aware_lru") and mode != EVICTION_MODE_UNSPECIFIED:
@@ -204,12 +251,12 @@ def parse_startup_config(config: Union[str, dict]) -> dict:
             block_sizes[iid] = int(inst.get("block_size", 16))
             # eviction_manager.cc:249-266: quota = size_t(quota_capacity * used_percentage); an unspecified mode
             # never evicts (:60-63)
-            if mode != EVICTION_MODE_UNSPECIFIED:
+            if mode != EVICTION_MODE_UNSPECIFIED and not together:
                 quotas[iid] = int(group["quota_capacity"] * float(group.get("used_percentage", 1.0)))
     return dict(trace_file_path=config.get("trace_file_path"), trace_type=config.get("trace_type"),
                 output_result_path=config.get("output_result_path"), quota_blocks=quotas, block_sizes=block_sizes,
                 evict_batch=int(ev.get("eviction_batch_size_per_instance", 100)),
-                precise=mode == EVICTION_MODE_INSTANCE_PRECISE, policies=policies)
+                precise=mode == EVICTION_MODE_INSTANCE_PRECISE, policies=policies, groups=shared, mode=mode)
 
 
 def run_startup_config(config: Union[str, dict], device=None, rw_separation: Optional[bool] = None):
@@ -222,4 +269,5 @@ def run_startup_config(config: Union[str, dict], device=None, rw_separation: Opt
     if rw_separation is None:
         rw_separation = c["trace_type"] == "publisher_log"
     return run_trace_file(c["trace_file_path"], c["trace_type"], c["output_result_path"], device, c["block_sizes"],
-                          rw_separation, c["quota_blocks"] or None, c["evict_batch"], c["precise"], c["policies"])
+                          rw_separation, c["quota_blocks"] or None, c["evict_batch"], c["precise"], c["policies"],
+                          c["groups"], c["mode"] or 1)

@@ -168,3 +168,31 @@ def test_optimizer_schema_query_with_a_holey_vector_mask(tmp_path):
     assert rec["kind"].tolist() == [tr.WRITE_CACHE, tr.GET_LOCATION]
     assert rec["external_hit_blocks"].tolist() == [0, 2] and rec["internal_hit_blocks"].tolist() == [0, 2]
     assert rec["internal_read_blocks"].tolist() == [0, 3] and rec["external_read_blocks"].tolist() == [0, 2]
+
+
+def test_two_instances_of_one_group_share_the_quota(tmp_path):
+    """The startup configuration names two "lru" instances in one group: they are replayed together against the
+    shared quota (kv_cache_manager/optimizer/manager/eviction_manager.cc:86-146), each gets its own CSV."""
+    path = tmp_path / "schema.jsonl"
+
+    def line(inst, ts, keys, query=False):
+        d = {"instance_id": inst, "trace_id": "t%d" % ts, "timestamp_us": ts, "tokens": [], "keys": keys}
+        if query:
+            d.update(query_type="prefix_match", block_mask=0, sw_size=0, location_spec_names=[])
+        return json.dumps(d)
+    path.write_text("\n".join([line("a", 1, [1, 2, 3]), line("b", 2, [1, 2]), line("a", 3, [1, 2, 3], True),
+                               line("b", 4, [1, 2], True)]))
+    cfg = {"trace_file_path": str(path), "trace_type": "optimizer_schema", "output_result_path": str(tmp_path / "out"),
+           "eviction_params": {"eviction_mode": 1, "eviction_batch_size_per_instance": 1},
+           "instance_groups": [{"group_name": "g", "quota_capacity": 4, "used_percentage": 1.0,
+                                "hierarchical_eviction_enabled": False, "storages": [],
+                                "instances": [{"instance_id": "a", "block_size": 16, "eviction_policy_type": "lru"},
+                                              {"instance_id": "b", "block_size": 16, "eviction_policy_type": "lru"}]}]}
+    recs = run_startup_config(cfg, device="cuda:0", rw_separation=True)
+    # 5 blocks against a quota of 4: one round takes block 1 from a and from b (see tests/test_oracle.py)
+    assert recs["a"]["current_cache_blocks"].tolist() == [3, 2] and recs["a"]["external_hit_blocks"].tolist() == [0, 0]
+    assert recs["b"]["current_cache_blocks"].tolist() == [1, 1] and recs["b"]["write_blocks"].tolist() == [2, 0]
+    assert (tmp_path / "out" / "a_hit_rates.csv").exists() and (tmp_path / "out" / "b_hit_rates.csv").exists()
+    cfg["eviction_params"]["eviction_mode"] = 2  # only the writer b pays
+    recs = run_startup_config(cfg, device="cuda:0", rw_separation=True)
+    assert recs["a"]["current_cache_blocks"].tolist() == [3, 3] and recs["a"]["external_hit_blocks"].tolist() == [0, 3]

@@ -115,6 +115,11 @@ def test_startup_config_of_the_reference_is_understood():
         parse_startup_config(cfg)
     cfg["instance_groups"][0]["instances"][0]["eviction_policy_type"] = "lru"
     cfg["instance_groups"][0]["instances"].append({"instance_id": "b", "block_size": 16, "eviction_policy_type": "lru"})
+    c = parse_startup_config(cfg)  # two "lru" instances share the quota: replayed together
+    assert c["groups"] == [dict(group_name=cfg["instance_groups"][0]["group_name"],
+                                instances=["3780643326877293460", "b"], quota=9000)]
+    assert c["quota_blocks"] == {} and c["mode"] == 3
+    cfg["instance_groups"][0]["instances"][1]["eviction_policy_type"] = "leaf_aware_lru"
     with pytest.raises(NotImplementedError):
         parse_startup_config(cfg)
     cfg["eviction_params"]["eviction_mode"] = 0  # no eviction is ever performed: any grouping replays
