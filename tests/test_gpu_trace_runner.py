@@ -173,6 +173,7 @@ def test_optimizer_schema_query_with_a_holey_vector_mask(tmp_path):
 def test_two_instances_of_one_group_share_the_quota(tmp_path):
     """The startup configuration names two "lru" instances in one group: they are replayed together against the
     shared quota (kv_cache_manager/optimizer/manager/eviction_manager.cc:86-146), each gets its own CSV."""
+    from tair_kvcache_b200.optimizer import run_startup_config
     path = tmp_path / "schema.jsonl"
 
     def line(inst, ts, keys, query=False):
