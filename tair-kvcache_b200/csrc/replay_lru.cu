@@ -5,7 +5,8 @@
 // eviction policy (kv_cache_manager/optimizer/eviction_policy/lru.cc:6-49) and the quota check after
 // every write (OptIndexerManager::CheckAndEvict, kv_cache_manager/optimizer/manager/indexer_manager.cc:55-90;
 // OptEvictionManager::EvictByInstanceRough / EvictByInstancePrecise / GetExcessUsageForInstanceInGroup,
-// kv_cache_manager/optimizer/manager/eviction_manager.cc:148-266), one instance per group.
+// kv_cache_manager/optimizer/manager/eviction_manager.cc:148-266), one instance per group; groups of several
+// instances that share the quota (EvictByGroupRough, :86-146) have a kernel of their own further down.
 //
 // With eviction the replay of ONE configuration is sequential: what trace t hits depends on what
 // the traces before it touched and evicted.  The reference's tradeoff-curve scripts run the same
