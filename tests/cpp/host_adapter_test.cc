@@ -233,6 +233,21 @@ static void TestReplay() {
     EXPECT_EQ(sweep[0][2].current_cache_blocks, 3);
     EXPECT_EQ(replayer.RunTracesLru(shared, {3}, 1, true, &sweep), KVCM_OK);
     EXPECT_EQ(sweep[0][2].external_hit_blocks, 0);
+    // Two instances share a quota of 4 blocks (worked from kv_cache_manager/optimizer/manager/eviction_manager.cc:86-192;
+    // the reference tests groups of one instance only): a writes 1 2 3, b writes 1 2.  GROUP_ROUGH takes one block
+    // from a and one from b; INSTANCE_ROUGH takes one from the writer b only.
+    const std::vector<ReplayTrace> two = {{TraceKind::WriteCache, {1, 2, 3}}, {TraceKind::WriteCache, {1, 2}},
+                                          {TraceKind::GetLocation, {1, 2, 3}}, {TraceKind::GetLocation, {1, 2}}};
+    std::vector<int64_t> usage;
+    EXPECT_EQ(replayer.RunTracesLruGroup(two, {0, 1, 0, 1}, 2, 4, 1, 1, &rec, &usage), KVCM_OK);
+    EXPECT_EQ(rec[1].current_cache_blocks, 1);
+    EXPECT_EQ(rec[2].external_hit_blocks, 0);
+    EXPECT_EQ(usage[0], 2);
+    EXPECT_EQ(usage[1], 1);
+    EXPECT_EQ(replayer.RunTracesLruGroup(two, {0, 1, 0, 1}, 2, 4, 1, 2, &rec, &usage), KVCM_OK);
+    EXPECT_EQ(rec[2].external_hit_blocks, 3);
+    EXPECT_EQ(usage[0], 3);
+    EXPECT_EQ(replayer.RunTracesLruGroup(two, {0, 1}, 2, 4, 1, 2, &rec, &usage), KVCM_EC_BADARGS);
 }
 
 int main() {
