@@ -124,3 +124,45 @@ def test_startup_config_of_the_reference_is_understood():
         parse_startup_config(cfg)
     cfg["eviction_params"]["eviction_mode"] = 0  # no eviction is ever performed: any grouping replays
     assert parse_startup_config(cfg)["quota_blocks"] == {}
+
+
+def test_shared_quota_groups_host_side(tmp_path, monkeypatch):
+    """The runner's handling of a group whose instances share a quota, without a GPU: the device call is replaced by
+    the oracle, so this covers the grouping of traces by instance, the per-instance records and the CSV files."""
+    import json
+
+    import numpy as np
+    import torch
+
+    from oracle import kvcm_oracle as oracle
+    from tair_kvcache_b200.optimizer import runner
+
+    def stand_in(keys, off, kind, inst, n_inst, quotas, mask, evict_batch, mode, mask_bits=None):
+        r = oracle.LruGroupReplay(quotas[0], n_inst, evict_batch=evict_batch, mode=mode).run(
+            keys.numpy(), off.numpy(), kind.numpy(), inst.numpy(), mask.numpy())
+        return [torch.from_numpy(x)[None] for x in r[:4]] + [None, None]
+
+    monkeypatch.setattr(runner, "RunTracesLruGroup", stand_in)
+
+    def line(inst, ts, keys, query=False):
+        d = {"instance_id": inst, "trace_id": "t%d" % ts, "timestamp_us": ts, "tokens": [], "keys": keys}
+        if query:
+            d.update(query_type="prefix_match", block_mask=0, sw_size=0, location_spec_names=[])
+        return json.dumps(d)
+    path = tmp_path / "schema.jsonl"
+    path.write_text("\n".join([line("a", 1, [1, 2, 3]), line("b", 2, [1, 2]), line("a", 3, [1, 2, 3], True),
+                               line("b", 4, [1, 2], True)]))
+    cfg = {"trace_file_path": str(path), "trace_type": "optimizer_schema", "output_result_path": str(tmp_path / "out"),
+           "eviction_params": {"eviction_mode": 1, "eviction_batch_size_per_instance": 1},
+           "instance_groups": [{"group_name": "g", "quota_capacity": 4, "used_percentage": 1.0,
+                                "hierarchical_eviction_enabled": False, "storages": [],
+                                "instances": [{"instance_id": "a", "block_size": 16, "eviction_policy_type": "lru"},
+                                              {"instance_id": "b", "block_size": 16, "eviction_policy_type": "lru"}]}]}
+    recs = runner.run_startup_config(cfg, device="cpu", rw_separation=True)
+    assert recs["a"]["current_cache_blocks"].tolist() == [3, 2] and recs["b"]["current_cache_blocks"].tolist() == [1, 1]
+    assert recs["a"]["timestamp_us"].tolist() == [1, 3] and recs["b"]["write_blocks"].tolist() == [2, 0]
+    rows = (tmp_path / "out" / "a_hit_rates.csv").read_text().splitlines()
+    assert len(rows) == 2 and rows[1].startswith("3, 2, 2, 2, 0, 3, 3, 0, ")
+    cfg["eviction_params"]["eviction_mode"] = 2
+    recs = runner.run_startup_config(cfg, device="cpu", rw_separation=True)
+    assert recs["a"]["external_hit_blocks"].tolist() == [0, 3] and np.array_equal(recs["a"]["kind"], [2, 1])
