@@ -1162,7 +1162,8 @@ def main_lru(args, rank, world):
 
     import tair_kvcache_b200  # noqa: F401
     from tair_kvcache_b200.manager import GenKeyVectorBatch, key_offsets, length_order
-    from tair_kvcache_b200.optimizer import TRACE_DIALOG_TURN, RunTracesLru, replay_lru_workspace_bytes
+    from tair_kvcache_b200.optimizer import (TRACE_DIALOG_TURN, RunTracesLru, RunTracesLruGroup,
+                                             replay_lru_workspace_bytes)
 
     local = int(os.environ.get("LOCAL_RANK", 0))
     device = torch.device("cuda", local)
@@ -1192,14 +1193,24 @@ def main_lru(args, rank, world):
     all_quotas = _lru_quotas(n_keys, n_cfg * world)
     quotas = all_quotas[rank::world]  # every rank gets points from the whole range
     policy = args.policy
-    workspace = torch.empty(replay_lru_workspace_bytes(n_keys, n_cfg, policy, n_req), dtype=torch.uint8,
+    n_inst = max(1, args.instances)  # > 1: the requests go round-robin to instances that share the quota
+    if n_inst > 1 and policy != "lru":
+        raise SystemExit("--instances needs --policy lru")
+    d_inst = (torch.arange(n_req, device=device, dtype=torch.int32) % n_inst).contiguous()
+    workspace = torch.empty(replay_lru_workspace_bytes(n_keys, n_cfg, policy, n_req) + 4096, dtype=torch.uint8,
                             device=device)
     status = torch.zeros(4, dtype=torch.int32, device=device)
 
-    def step():
-        keys = GenKeyVectorBatch(toks, d_off, bs, d_ko, n_keys, out=d_keys, order=d_order, warps_per_sm=residency)
+    def sweep(keys):
+        if n_inst > 1:
+            return RunTracesLruGroup(keys, d_ko, d_type, d_inst, n_inst, quotas, evict_batch=100, mode=1,
+                                     workspace=workspace, status=status)
         return RunTracesLru(keys, d_ko, d_type, quotas, evict_batch=100, precise=False, workspace=workspace,
                             status=status, policy=policy)
+
+    def step():
+        keys = GenKeyVectorBatch(toks, d_off, bs, d_ko, n_keys, out=d_keys, order=d_order, warps_per_sm=residency)
+        return sweep(keys)
 
     sampler = ClockSampler(str(torch.cuda.get_device_properties(device).uuid)) if rank == 0 else None
     if sampler:
@@ -1227,8 +1238,7 @@ def main_lru(args, rank, world):
     # the sweep kernel alone
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e2.record()
-    RunTracesLru(d_keys, d_ko, d_type, quotas, evict_batch=100, precise=False, workspace=workspace, status=status,
-                 policy=policy)
+    sweep(d_keys)
     e3.record()
     torch.cuda.synchronize(device)
     sweep_ms = e2.elapsed_time(e3)
@@ -1244,8 +1254,12 @@ def main_lru(args, rank, world):
         m = min(n_req, 20000)  # the sequential CPU replay of the first requests sees the same history
         k = d_keys[:int(ko[m])].cpu().numpy()
         c = len(quotas) // 3
-        want = oracle.LruReplay(quotas[c], evict_batch=100, precise=False, policy=policy).run(
-            k, ko[:m + 1], np.zeros(m, np.uint8))
+        if n_inst > 1:
+            want = oracle.LruGroupReplay(quotas[c], n_inst, evict_batch=100, mode=1).run(
+                k, ko[:m + 1], np.zeros(m, np.uint8), np.arange(m, dtype=np.int32) % n_inst)
+        else:
+            want = oracle.LruReplay(quotas[c], evict_batch=100, precise=False, policy=policy).run(
+                k, ko[:m + 1], np.zeros(m, np.uint8))
         parity = bool(np.array_equal(want[0], res.external_hit_blocks[c, :m].cpu().numpy()) and
                       np.array_equal(want[2], res.write_blocks[c, :m].cpu().numpy()) and
                       np.array_equal(want[3], res.current_cache_blocks[c, :m].cpu().numpy()))
@@ -1260,10 +1274,14 @@ def main_lru(args, rank, world):
                                    "reuse over 10000 prompts = %d token blocks) replayed with %s eviction at %d quota "
                                    "points per GPU (%d..%d blocks, rough mode, batches of 100); hash + sweep per step"
                                    % (n_req, n_keys, policy, n_cfg, min(all_quotas), max(all_quotas)),
+                       "instances_sharing_the_quota": n_inst,
                        "sweep_kernel_ms_rank0": sweep_ms, "hit_rate_lowest_quota": float(hit_rate[0]),
                        "hit_rate_highest_quota": float(hit_rate[-1]), "table_overflows": int(status[0].item()),
                        "parity_sample_ok": parity},
-            "clocks": clocks, "gpu_launches": 5 * steps}))
+            # per step: the hash, then table init + claim + lookup + sweep ("lru"), one more pass for the key
+            # predecessors ("leaf_aware_lru"), or extents + (clear, claim, lookup) per instance + sweep (groups)
+            "clocks": clocks,
+            "gpu_launches": (3 * n_inst + 3 if n_inst > 1 else 6 if policy == "leaf_aware_lru" else 5) * steps}))
     if world > 1:
         dist.destroy_process_group()
 
@@ -1292,6 +1310,9 @@ def main_lru_reference(args):
     quotas = _lru_quotas(int(ko[-1]), n_cfg)
 
     def one(q):
+        if args.instances > 1:
+            return int(oracle.LruGroupReplay(q, args.instances, evict_batch=100, mode=1).run(
+                keys, ko, types, np.arange(n_req, dtype=np.int32) % args.instances)[0].sum())
         return int(oracle.LruReplay(q, evict_batch=100, precise=False, policy=args.policy).run(keys, ko, types)[0].sum())
 
     with ThreadPoolExecutor(max_workers=threads) as pool:
@@ -1851,6 +1872,8 @@ def main():
                          "(default 0.5; 0.7 for the routed shard modes, whose head is routed after the rest)")
     ap.add_argument("--request-tokens", type=int, default=0, help="hash: tokens per request (default 20970)")
     ap.add_argument("--n-configs", type=int, default=0, help="lru: quota points per GPU (default 148)")
+    ap.add_argument("--instances", type=int, default=1,
+                    help="lru: instances that share each quota (requests go to them round-robin; group-rough eviction)")
     ap.add_argument("--policy", default="lru", choices=["lru", "leaf_aware_lru"],
                     help="lru: the eviction policy of the sweep (eviction_policy_type)")
     ap.add_argument("--no-prefix", action="store_true", help="skip the prefix-match side measurement")
