@@ -268,20 +268,40 @@ __global__ void __launch_bounds__(32) LruGroupSweepKernel(const LruSweep p, cons
     }
     __syncwarp();
 
+    // As in the single-instance kernel: a trace's extent, kind, instance and first 32 ids are fetched one trace
+    // ahead (the extent two ahead), so that the load a trace waits for is stamp[id].
+    auto extent = [&](int32_t t, int64_t *beg, int64_t *n, uint8_t *ty, int64_t *skip, int32_t *who) {
+        if (t < p.n_traces) {
+            *beg = p.key_off[t];
+            *n = p.key_off[t + 1] - *beg;
+            *ty = p.type[t];
+            *skip = (*ty == 1 && p.mask_off != nullptr) ? p.mask_off[t] : 0;
+            *who = g.trace_inst[t];
+            if (*who < 0 || *who >= K) *who = 0;  // counted by LruGroupExtentKernel
+        } else {
+            *beg = 0, *n = 0, *ty = 1, *skip = 0, *who = 0;
+        }
+    };
+    int64_t beg, n, skip, beg1, n1, skip1;
+    uint8_t ty, ty1;
+    int32_t me, me1;
+    extent(0, &beg, &n, &ty, &skip, &me);
+    extent(1, &beg1, &n1, &ty1, &skip1, &me1);
+    uint32_t first_id = lane < n ? p.ids[beg + lane] : 0u;
+
     for (int32_t t = 0; t < p.n_traces; ++t) {
-        const int64_t beg = p.key_off[t];
-        const int64_t n = p.key_off[t + 1] - beg;
-        const uint8_t ty = p.type[t];
-        const int64_t skip = (ty == 1 && p.mask_off != nullptr) ? p.mask_off[t] : 0;
-        int32_t me = g.trace_inst[t];
-        if (me < 0 || me >= K) me = 0;  // counted by LruGroupExtentKernel
+        const uint32_t next_first_id = lane < n1 ? p.ids[beg1 + lane] : 0u;
+        int64_t beg2, n2, skip2;
+        uint8_t ty2;
+        int32_t me2;
+        extent(t + 2, &beg2, &n2, &ty2, &skip2, &me2);
         int64_t my_tail = tail[me];
         int32_t ext = 0, inte = 0, wr = 0;
         bool alive = ty != 2;
         for (int64_t base = 0; base < n; base += 32) {
             const int64_t i = base + lane;
             const bool have = i < n;
-            const uint32_t id = have ? p.ids[beg + i] : 0u;
+            const uint32_t id = base == 0 ? first_id : (have ? p.ids[beg + i] : 0u);
             const uint32_t cur = have ? stamp[id] : 0u;
             const uint32_t in_range = __ballot_sync(0xffffffffu, have);
             const uint32_t hit = __ballot_sync(0xffffffffu, have && cur != 0u);
@@ -393,6 +413,8 @@ __global__ void __launch_bounds__(32) LruGroupSweepKernel(const LruSweep p, cons
         sum_ext += ext;
         sum_int += inte;
         sum_wr += wr;
+        beg = beg1, n = n1, ty = ty1, skip = skip1, me = me1, first_id = next_first_id;
+        beg1 = beg2, n1 = n2, ty1 = ty2, skip1 = skip2, me1 = me2;
     }
     if (lane == 0 && p.totals != nullptr) {
         int64_t *tot = p.totals + static_cast<int64_t>(cfg) * 4;
