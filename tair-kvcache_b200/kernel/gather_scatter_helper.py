@@ -3,9 +3,11 @@
 Same names and arguments as kv_cache_manager/py_connector/kernel/gather_scatter_helper.py:
 scatter_kv_caches (:110-140), gather_kv_caches (:143-172), CopyBufferAllocator (:175-252).
 """
+import collections
 import threading
 from typing import List, Sequence, Union
 
+import numpy as np
 import torch
 
 from .. import _cabi
@@ -14,7 +16,9 @@ from .batch_gather_scatter_helper import _index_tensor, _stream
 
 def _legacy(entry: str, kv_caches_ptrs: torch.Tensor, total_token_in_kvcache: int, tensor: torch.Tensor,
             token_indices: Union[Sequence[int], torch.Tensor]) -> None:
-    assert kv_caches_ptrs.shape[0] == tensor.shape[0], "Number of layers mismatch"
+    if kv_caches_ptrs.shape[0] != tensor.shape[0]:
+        raise ValueError("%d layer pointers but the staging tensor holds %d layers"
+                         % (kv_caches_ptrs.shape[0], tensor.shape[0]))
     if not tensor.is_contiguous():
         raise ValueError("the staging tensor must be contiguous")
     idx = _index_tensor(token_indices, kv_caches_ptrs.device)
@@ -41,49 +45,84 @@ def gather_kv_caches(kv_caches_ptrs: torch.Tensor, total_token_in_kvcache: int, 
 class CopyBufferAllocator:
     """Fixed pool of `max_count` staging blocks carved from one tensor (pinned when on the CPU).
 
-    Indices are handed out under a condition variable; `alloc_buffer_idx_blocking` waits until
-    enough blocks are free.  Staging slots are therefore arbitrary, non-contiguous indices into
-    `_raw_buffer`, which is what the batched operators take as `dst_block_indices`."""
+    Public surface of the reference's allocator (kv_cache_manager/py_connector/kernel/gather_scatter_helper.py:175-252):
+    `alloc_buffer_idx_blocking`, `get_buffer_by_idx`, `free_buffer`, `_raw_buffer`, `shape`, `max_count`.  Slot
+    numbers are arbitrary, non-contiguous indices into `_raw_buffer`, which is what the batched operators take as
+    `dst_block_indices`.
+
+    Bookkeeping: the free slots are a stack in a preallocated int32 array (`_stack[:_n_free]`), and one flag per
+    slot says whether it is out on loan, so that a slot returned twice, or never handed out, is refused instead of
+    ending up in the stack twice.  Requests are served in arrival order: a large request is not starved by a
+    stream of small ones that would each fit."""
 
     def __init__(self, device, dtype, shape: List[int], max_count: int):
-        if max_count <= 0:
-            raise ValueError("max_count must be positive")
-        self.max_count = max_count
+        if int(max_count) < 1:
+            raise ValueError("a staging pool needs at least one block, got max_count=%r" % (max_count,))
+        self.max_count = int(max_count)
         self.device = torch.device(device)
         self.dtype = dtype
-        self._cond = threading.Condition()
-        self._raw_buffer = torch.zeros([max_count] + list(shape), dtype=dtype, device=self.device,
-                                       pin_memory=self.device.type == "cpu")
-        self._free_idx_list = list(range(max_count))
-        self._free_buffer_list = [self._raw_buffer[i] for i in range(max_count)]
-        self.shape = self._free_buffer_list[0].shape
-        self._inuse_count = 0
+        self._raw_buffer = torch.zeros([self.max_count] + list(shape), dtype=dtype, device=self.device,
+                                       pin_memory=self.device.type == "cpu" and torch.cuda.is_available())
+        self._views = tuple(self._raw_buffer.unbind(0))
+        self.shape = self._views[0].shape
+        self._stack = np.arange(self.max_count, dtype=np.int32)
+        self._n_free = self.max_count
+        self._on_loan = np.zeros(self.max_count, dtype=bool)
+        self._lock = threading.Lock()
+        self._waiters = collections.deque()  # one Event per blocked request, oldest first
 
     def alloc_buffer_idx_blocking(self, count: int) -> List[int]:
-        if count <= 0:
-            raise ValueError("count must be positive")
-        if count > self.max_count:
-            raise ValueError(f"count ({count}) exceeds max_count ({self.max_count})")
-        with self._cond:
-            while self._inuse_count + count > self.max_count:
-                self._cond.wait()
-            self._inuse_count += count
-            taken = self._free_idx_list[-count:]
-            del self._free_idx_list[-count:]
-            return taken
+        """Takes `count` slots, waiting until that many are free.  Returns their indices."""
+        count = int(count)
+        if not 1 <= count <= self.max_count:
+            raise ValueError("cannot hand out %d blocks from a pool of %d" % (count, self.max_count))
+        with self._lock:
+            if not self._waiters and self._n_free >= count:
+                return self._pop(count)
+            turn = threading.Event()
+            self._waiters.append((turn, count))
+        while True:
+            # Only the request at the head of the queue is ever signalled, and it stays queued until it has its
+            # slots; later arrivals line up behind it, so between the signal and the wake-up the free count can
+            # only grow.
+            turn.wait()
+            with self._lock:
+                if self._n_free >= count:
+                    self._waiters.popleft()
+                    got = self._pop(count)
+                    self._signal_head()
+                    return got
+                turn.clear()
+
+    def _pop(self, count: int) -> List[int]:
+        top = self._n_free
+        taken = self._stack[top - count:top]
+        self._on_loan[taken] = True
+        self._n_free = top - count
+        return taken.tolist()
+
+    def _signal_head(self) -> None:
+        """With the lock held: wakes the oldest waiting request once it fits."""
+        if self._waiters and self._n_free >= self._waiters[0][1]:
+            self._waiters[0][0].set()
 
     def get_buffer_by_idx(self, indices: List[int]):
-        return [self._free_buffer_list[i] for i in indices]
+        return [self._views[i] for i in indices]
 
     def free_buffer(self, buffers: List[int]):
-        if not buffers:
+        """Returns slots to the pool.  Refuses, without changing anything, a list that names a slot outside the
+        pool, a slot that is not on loan, or the same slot twice."""
+        if len(buffers) == 0:
             return
-        with self._cond:
-            for idx in buffers:
-                if idx >= self.max_count or idx < 0:
-                    raise ValueError(f"Buffer idx {idx} wrong")
-            if self._inuse_count < len(buffers):
-                raise RuntimeError(f"Trying to free {len(buffers)} buffers, but only {self._inuse_count} are in use")
-            self._inuse_count -= len(buffers)
-            self._free_idx_list.extend(buffers)
-            self._cond.notify_all()
+        back = np.asarray(buffers, dtype=np.int64).reshape(-1)
+        with self._lock:
+            bad = back[(back < 0) | (back >= self.max_count)]
+            if bad.size:
+                raise ValueError("staging block %d is outside this pool of %d" % (int(bad[0]), self.max_count))
+            if np.unique(back).size != back.size or not self._on_loan[back].all():
+                raise RuntimeError("free_buffer got %d blocks of which some are not on loan (%d are)"
+                                   % (back.size, self.max_count - self._n_free))
+            self._on_loan[back] = False
+            self._stack[self._n_free:self._n_free + back.size] = back
+            self._n_free += back.size
+            self._signal_head()
