@@ -128,9 +128,14 @@ KVCM_API int32_t kvcm_b200_scatter_pages(const void *const *d_pool_ptrs, int32_t
  * kv_cache_manager/py_connector/vllm/data_transfer.py:119-150, 205-217).  Same layout rule as gather /
  * scatter above (a row is a token or a page), but the PCIe leg is done by the copy engines: blocks are
  * gathered into the caller's device bounce buffer and copied out (save), or copied in and scattered
- * (load), in groups of floor(bounce_bytes / block_bytes) blocks, all ordered on `stream`.  A save on
- * one stream and a load on another then use both PCIe directions at full rate, which kernels writing
- * host memory directly do not.  h_slot_idx is a HOST array of staging slots (NULL = slot b); slots
+ * (load).  The buffer is used as two halves of floor(bounce_bytes / 2 / block_bytes) blocks: the copies
+ * run on a copy stream that the library keeps per device and direction, so that one half crosses PCIe
+ * while the kernel works on the other; events tie that stream to `stream`, on which the whole call is
+ * ordered as seen by the caller (nothing is copied before the work that precedes the call, and what
+ * follows the call on `stream` sees every block in place).  A bounce buffer smaller than two blocks is
+ * used whole, group after group, on `stream` alone.  A save on one stream and a load on another use
+ * both PCIe directions at full rate, which kernels writing host memory directly do not.  Calls of one
+ * direction on one device are enqueued one at a time (a mutex); they may come from any thread.  h_slot_idx is a HOST array of staging slots (NULL = slot b); slots
  * outside [0, n_slots) return KVCM_ER_INVALID_PARAMS before anything is launched or copied.
  * d_bounce: device memory, 16-byte aligned, at least one block (n_pools * rows_per_block * row_bytes). */
 KVCM_API int32_t kvcm_b200_save_rows_to_host(const void *const *d_pool_ptrs, int32_t n_pools, void *h_staging,

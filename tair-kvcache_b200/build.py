@@ -28,27 +28,50 @@ def sources():
     return [os.path.join(CSRC, s) for s in SOURCES]
 
 
+HEADERS = [os.path.join(CSRC, "kvcm_common.cuh"), os.path.join(CSRC, "replay_ids.cuh"),
+           os.path.join(ROOT, "include", "kvcm_b200.h")]
+OBJ_DIR = os.path.join(HERE, "build")
+
+
+def _newer(path, than):
+    return not os.path.exists(than) or os.path.getmtime(path) > os.path.getmtime(than)
+
+
 def is_stale():
-    if not os.path.exists(LIB):
-        return True
-    t = os.path.getmtime(LIB)
-    deps = sources() + [os.path.join(CSRC, "kvcm_common.cuh"), os.path.join(CSRC, "replay_ids.cuh"), os.path.join(ROOT, "include", "kvcm_b200.h")]
-    return any(os.path.getmtime(d) > t for d in deps)
+    return any(_newer(d, LIB) for d in sources() + HEADERS)
 
 
 def build_library(force=False, verbose=False):
-    """Compile every kernel for sm_100a into tair-kvcache_b200/libkvcm_b200.so."""
+    """Compile every kernel for sm_100a into tair-kvcache_b200/libkvcm_b200.so: one object per source file
+    (compiled side by side, only the ones whose source or a shared header changed), then one link."""
+    from concurrent.futures import ThreadPoolExecutor
     if not force and not is_stale():
         return LIB
-    cmd = [nvcc()] + NVCC_FLAGS + ["-I", os.path.join(ROOT, "include"), "-I", CSRC]
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    flags = [f for f in NVCC_FLAGS if f != "-shared"] + ["-I", os.path.join(ROOT, "include"), "-I", CSRC]
     if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", LIB] + sources()
+        flags += ["-Xptxas", "-v"]
+
+    def compile_one(src):
+        obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")
+        if not force and not verbose and not _newer(src, obj) and not any(_newer(h, obj) for h in HEADERS):
+            return obj, 0, ""
+        proc = subprocess.run([nvcc()] + flags + ["-c", "-o", obj, src], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True)
+        return obj, proc.returncode, proc.stdout
+
+    with ThreadPoolExecutor(max_workers=min(len(SOURCES), os.cpu_count() or 1)) as pool:
+        results = list(pool.map(compile_one, sources()))
+    for obj, rc, out in results:
+        if verbose or rc != 0:
+            print(out)
+        if rc != 0:
+            raise RuntimeError("nvcc failed on %s (exit %d)" % (os.path.basename(obj), rc))
+    cmd = [nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB] + [o for o, _, _ in results]
     proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
-    if verbose or proc.returncode != 0:
-        print(proc.stdout)
     if proc.returncode != 0:
-        raise RuntimeError("nvcc failed (exit %d)" % proc.returncode)
+        print(proc.stdout)
+        raise RuntimeError("linking libkvcm_b200.so failed (exit %d)" % proc.returncode)
     return LIB
 
 

@@ -635,7 +635,82 @@ int32_t kvcm_b200_scatter_legacy(const void *const *d_layer_ptrs, int32_t n_laye
 // but a save and a load running at once reach only ~35 GB/s each; the DMA engines sustain ~50 GB/s
 // each way at the same time.  So blocks are gathered into a device bounce buffer at HBM speed and
 // leave through cudaMemcpyAsync (save), or arrive through cudaMemcpyAsync and are scattered (load).
-// Blocks are processed in groups that fit the bounce buffer; everything is ordered on `stream`.
+//
+// The bounce buffer is used as two halves and the copies run on a copy stream of the library's own
+// (one per device and direction), tied to the caller's stream by events: while the copy engine moves
+// the blocks of one half across PCIe, the kernel fills (or empties) the other half, so neither the
+// link nor the caller's stream idles between groups.  To the caller everything is still ordered on
+// `stream`: the first copy waits for the work that precedes the call, and the stream waits for the
+// last copy before the call's successors run.
+namespace {
+
+struct CopyLane {
+    cudaStream_t copy = nullptr;
+    cudaEvent_t entry = nullptr;      // recorded on the caller's stream when a load begins
+    cudaEvent_t filled[2] = {};       // save: half gathered (caller's stream); load: half arrived (copy stream)
+    cudaEvent_t drained[2] = {};      // save: half copied out (copy stream); load: half scattered (caller's stream)
+    std::mutex mu;                    // one call at a time enqueues on a lane: the events are shared
+    bool ok = false;
+};
+
+// Lane of the current device for one direction (0 = save, 1 = load), created at first use.
+CopyLane *GetCopyLane(int direction) {
+    static std::mutex mu;
+    static std::vector<CopyLane *> lanes;  // [device * 2 + direction]; never freed: they live as long as the library
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    const size_t slot = static_cast<size_t>(device) * 2 + direction;
+    if (lanes.size() <= slot) lanes.resize(slot + 1, nullptr);
+    if (lanes[slot] == nullptr) {
+        CopyLane *lane = new CopyLane;
+        bool ok = cudaStreamCreateWithFlags(&lane->copy, cudaStreamNonBlocking) == cudaSuccess;
+        ok = ok && cudaEventCreateWithFlags(&lane->entry, cudaEventDisableTiming) == cudaSuccess;
+        for (int h = 0; h < 2; ++h) {
+            ok = ok && cudaEventCreateWithFlags(&lane->filled[h], cudaEventDisableTiming) == cudaSuccess;
+            ok = ok && cudaEventCreateWithFlags(&lane->drained[h], cudaEventDisableTiming) == cudaSuccess;
+        }
+        if (!ok) cudaGetLastError();
+        lane->ok = ok;
+        lanes[slot] = lane;
+    }
+    return lanes[slot]->ok ? lanes[slot] : nullptr;
+}
+
+// One cudaMemcpyAsync per run of blocks whose host slots are consecutive.
+int32_t CopyGroup(bool save, uint8_t *host, uint8_t *bounce, const int32_t *h_slot_idx, int64_t first, int32_t n,
+                  int64_t n_slots, int64_t block_bytes, cudaStream_t copy) {
+    for (int32_t i = 0; i < n;) {
+        const int64_t slot = h_slot_idx != nullptr ? h_slot_idx[first + i] : first + i;
+        if (slot < 0 || slot >= n_slots) return KVCM_ER_INVALID_PARAMS;
+        int32_t j = i + 1;
+        while (j < n && (h_slot_idx != nullptr ? h_slot_idx[first + j] : first + j) == slot + (j - i)) ++j;
+        if (slot + (j - i) > n_slots) return KVCM_ER_INVALID_PARAMS;
+        const size_t bytes = static_cast<size_t>(j - i) * block_bytes;
+        const cudaError_t e = save ? cudaMemcpyAsync(host + slot * block_bytes, bounce + i * block_bytes, bytes,
+                                                     cudaMemcpyDeviceToHost, copy)
+                                   : cudaMemcpyAsync(bounce + i * block_bytes, host + slot * block_bytes, bytes,
+                                                     cudaMemcpyHostToDevice, copy);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return KVCM_ER_CUDAMEMCPY_ERROR;
+        }
+        i = j;
+    }
+    return KVCM_OK;
+}
+
+inline bool Ok(cudaError_t e) {
+    if (e == cudaSuccess) return true;
+    cudaGetLastError();
+    return false;
+}
+
+}  // namespace
+
 static int32_t MoveRowsThroughBounce(bool save, const void *const *d_pool_ptrs, int32_t n_pools, void *h_staging,
                                      int64_t n_slots, const int32_t *d_row_idx, const int32_t *h_slot_idx,
                                      int32_t n_blocks, int32_t rows_per_block, int64_t row_bytes, int64_t pool_rows,
@@ -647,8 +722,7 @@ static int32_t MoveRowsThroughBounce(bool save, const void *const *d_pool_ptrs, 
     if (n_blocks == 0) return KVCM_OK;
     if (h_staging == nullptr || d_bounce == nullptr || d_row_idx == nullptr) return KVCM_ER_INVALID_ADDRESS;
     const int64_t block_bytes = static_cast<int64_t>(n_pools) * rows_per_block * row_bytes;
-    const int64_t group = bounce_bytes / block_bytes;
-    if (group < 1) return KVCM_ER_INVALID_PARAMS;
+    if (bounce_bytes / block_bytes < 1) return KVCM_ER_INVALID_PARAMS;
     if (h_slot_idx != nullptr) {  // refuse a bad slot before anything is launched or copied
         for (int32_t b = 0; b < n_blocks; ++b) {
             if (h_slot_idx[b] < 0 || h_slot_idx[b] >= n_slots) return KVCM_ER_INVALID_PARAMS;
@@ -659,40 +733,84 @@ static int32_t MoveRowsThroughBounce(bool save, const void *const *d_pool_ptrs, 
     cudaStream_t s = kvcm::AsStream(stream);
     uint8_t *host = static_cast<uint8_t *>(h_staging);
     uint8_t *bounce = static_cast<uint8_t *>(d_bounce);
-    for (int64_t first = 0; first < n_blocks; first += group) {
+
+    // Two halves when each holds at least one block and there is more than one block to move; the second half
+    // starts on a 256-byte boundary.  Otherwise (a bounce buffer of one block) the groups run back to back on
+    // the caller's stream.
+    const int64_t half_bytes = (bounce_bytes / 2) & ~int64_t{255};
+    CopyLane *lane = (n_blocks > 1 && half_bytes >= block_bytes) ? GetCopyLane(save ? 0 : 1) : nullptr;
+    if (lane == nullptr) {
+        const int64_t group = bounce_bytes / block_bytes;
+        for (int64_t first = 0; first < n_blocks; first += group) {
+            const int32_t n = static_cast<int32_t>(first + group <= n_blocks ? group : n_blocks - first);
+            const int32_t *rows = d_row_idx + first * rows_per_block;
+            int32_t rc = KVCM_OK;
+            if (save) {
+                rc = kvcm::LaunchMove(true, d_pool_ptrs, n_pools, 1, 0, bounce, n, rows, nullptr, n, rows_per_block,
+                                      row_bytes, pool_rows, d_status, true, 0, stream);
+            }
+            if (rc == KVCM_OK) rc = CopyGroup(save, host, bounce, h_slot_idx, first, n, n_slots, block_bytes, s);
+            if (rc == KVCM_OK && !save) {
+                rc = kvcm::LaunchMove(false, d_pool_ptrs, n_pools, 1, 0, bounce, n, rows, nullptr, n, rows_per_block,
+                                      row_bytes, pool_rows, d_status, true, 0, stream);
+            }
+            if (rc != KVCM_OK) return rc;
+        }
+        return KVCM_OK;
+    }
+
+    std::lock_guard<std::mutex> lock(lane->mu);
+    // No more blocks per group than needed to cut the transfer in two: a short transfer is pipelined too.
+    int64_t group = half_bytes / block_bytes;
+    if (group > (n_blocks + 1) / 2) group = (n_blocks + 1) / 2;
+    if (!save && !Ok(cudaEventRecord(lane->entry, s))) return KVCM_ER_CUDAMEMCPY_ERROR;
+    int32_t rc = KVCM_OK;
+    bool used[2] = {false, false};
+    int64_t k = 0;
+    for (int64_t first = 0; first < n_blocks && rc == KVCM_OK; first += group, ++k) {
+        const int h = static_cast<int>(k & 1);
         const int32_t n = static_cast<int32_t>(first + group <= n_blocks ? group : n_blocks - first);
         const int32_t *rows = d_row_idx + first * rows_per_block;
+        uint8_t *half = bounce + h * half_bytes;
+        bool ok = true;
         if (save) {
-            const int32_t rc = kvcm::LaunchMove(true, d_pool_ptrs, n_pools, 1, 0, bounce, n, rows, nullptr, n,
-                                                rows_per_block, row_bytes, pool_rows, d_status, true, 0, stream);
-            if (rc != KVCM_OK) return rc;
-        }
-        // One copy per run of blocks whose host slots are consecutive.
-        for (int32_t i = 0; i < n;) {
-            const int64_t slot = h_slot_idx != nullptr ? h_slot_idx[first + i] : first + i;
-            if (slot < 0 || slot >= n_slots) return KVCM_ER_INVALID_PARAMS;
-            int32_t j = i + 1;
-            while (j < n && (h_slot_idx != nullptr ? h_slot_idx[first + j] : first + j) == slot + (j - i)) ++j;
-            if (slot + (j - i) > n_slots) return KVCM_ER_INVALID_PARAMS;
-            const size_t bytes = static_cast<size_t>(j - i) * block_bytes;
-            const cudaError_t e =
-                save ? cudaMemcpyAsync(host + slot * block_bytes, bounce + i * block_bytes, bytes,
-                                       cudaMemcpyDeviceToHost, s)
-                     : cudaMemcpyAsync(bounce + i * block_bytes, host + slot * block_bytes, bytes,
-                                       cudaMemcpyHostToDevice, s);
-            if (e != cudaSuccess) {
-                cudaGetLastError();
-                return KVCM_ER_CUDAMEMCPY_ERROR;
+            // the kernel may refill a half once the copy engine has emptied it (an event that was never
+            // recorded counts as complete)
+            ok = Ok(cudaStreamWaitEvent(s, lane->drained[h], 0));
+            if (ok) {
+                rc = kvcm::LaunchMove(true, d_pool_ptrs, n_pools, 1, 0, half, n, rows, nullptr, n, rows_per_block,
+                                      row_bytes, pool_rows, d_status, true, 0, stream);
+                if (rc != KVCM_OK) break;
             }
-            i = j;
+            ok = ok && Ok(cudaEventRecord(lane->filled[h], s)) && Ok(cudaStreamWaitEvent(lane->copy, lane->filled[h], 0));
+            if (ok) rc = CopyGroup(true, host, half, h_slot_idx, first, n, n_slots, block_bytes, lane->copy);
+            ok = ok && Ok(cudaEventRecord(lane->drained[h], lane->copy));
+        } else {
+            // the copy engine may refill a half once the kernel has scattered it; the first copies wait for
+            // whatever precedes this call on the caller's stream
+            ok = Ok(cudaStreamWaitEvent(lane->copy, k < 2 ? lane->entry : lane->drained[h], 0));
+            if (ok) rc = CopyGroup(false, host, half, h_slot_idx, first, n, n_slots, block_bytes, lane->copy);
+            ok = ok && Ok(cudaEventRecord(lane->filled[h], lane->copy)) && Ok(cudaStreamWaitEvent(s, lane->filled[h], 0));
+            if (ok && rc == KVCM_OK) {
+                rc = kvcm::LaunchMove(false, d_pool_ptrs, n_pools, 1, 0, half, n, rows, nullptr, n, rows_per_block,
+                                      row_bytes, pool_rows, d_status, true, 0, stream);
+            }
+            ok = ok && Ok(cudaEventRecord(lane->drained[h], s));
         }
-        if (!save) {
-            const int32_t rc = kvcm::LaunchMove(false, d_pool_ptrs, n_pools, 1, 0, bounce, n, rows, nullptr, n,
-                                                rows_per_block, row_bytes, pool_rows, d_status, true, 0, stream);
-            if (rc != KVCM_OK) return rc;
+        used[h] = true;
+        if (!ok && rc == KVCM_OK) rc = KVCM_ER_CUDAMEMCPY_ERROR;
+    }
+    // Whatever was enqueued on the copy stream is joined back into the caller's stream, on the error paths too.
+    if (save) {
+        for (int h = 0; h < 2; ++h) {
+            if (used[h] && !Ok(cudaStreamWaitEvent(s, lane->drained[h], 0)) && rc == KVCM_OK) rc = KVCM_ER_CUDAMEMCPY_ERROR;
+        }
+    } else {
+        for (int h = 0; h < 2; ++h) {
+            if (used[h] && !Ok(cudaStreamWaitEvent(s, lane->filled[h], 0)) && rc == KVCM_OK) rc = KVCM_ER_CUDAMEMCPY_ERROR;
         }
     }
-    return KVCM_OK;
+    return rc;
 }
 
 int32_t kvcm_b200_save_rows_to_host(const void *const *d_pool_ptrs, int32_t n_pools, void *h_staging, int64_t n_slots,
