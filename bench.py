@@ -59,6 +59,42 @@ def peaks():
     return 6650.0, "fallback"
 
 
+
+class Ctx:
+    """This process's place in the job: one process per GPU, one process group for the whole run."""
+
+    def __init__(self):
+        import torch
+        self.rank = int(os.environ.get("RANK", 0))
+        self.world = int(os.environ.get("WORLD_SIZE", 1))
+        self.local = int(os.environ.get("LOCAL_RANK", 0))
+        self.device = torch.device("cuda", self.local)
+        torch.cuda.set_device(self.device)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=self.device)
+
+    def barrier(self):
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+
+    def max_over_ranks(self, values):
+        """Element-wise maximum of a list of floats over the ranks (device-timed figures: the slowest rank counts)."""
+        import torch
+        if self.world == 1:
+            return list(values)
+        import torch.distributed as dist
+        t = torch.tensor(list(values), dtype=torch.float64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
+
+    def close(self):
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
 # ----------------------------------------------------------------------------------------------
 # clocks
 # ----------------------------------------------------------------------------------------------
@@ -161,32 +197,76 @@ def build_transfer_workload(cfg, device, seed):
                 page_bytes=page_bytes, payload=payload, n_pools=n_pools, n_blocks=n_blocks, ppb=ppb)
 
 
-def verify_staging(w, n_check=64):
-    """Staged bytes equal a torch gather of the pools on a sample of (block, pool) tiles."""
+def verify_gather(w):
+    """Every staged tile equals a torch gather of the pools (all blocks, all pools): the check shares no code
+    with the kernel under test."""
     import torch
-    rng = np.random.default_rng(1)
     st = w["staging"].view(w["n_blocks"], w["n_pools"], w["ppb"], -1)
     table = w["table"].long().view(w["n_blocks"], w["ppb"])
     slots = w["slots"].long()
-    for _ in range(n_check):
-        b, p = int(rng.integers(0, w["n_blocks"])), int(rng.integers(0, w["n_pools"]))
-        want = w["pools"][p].view(w["pool_pages"], -1)[table[b]]
-        if not torch.equal(st[slots[b], p], want):
+    for p in range(w["n_pools"]):
+        if not torch.equal(st[slots, p], w["pools"][p].view(w["pool_pages"], -1)[table]):
             return False
     return True
 
 
-def run_cpu_transfer(cfg, threads, steps, warmup, budget_s=20.0):
-    """The CPU restatement of one gather + scatter step on a bounded sample (host memory)."""
+def verify_scatter(w, scatter):
+    """The scatter direction at full size, in a form that can fail: every staged word is changed, the blocks are
+    scattered, then every referenced page must equal its staged tile and a sample of unreferenced pages must be
+    untouched.  (Scattering back what was just gathered would rewrite the pools with their own content.)"""
+    import torch
+    rng = np.random.default_rng(3)
+    referenced = np.zeros(w["pool_pages"], dtype=bool)
+    referenced[w["table"].cpu().numpy()] = True
+    others = np.flatnonzero(~referenced)
+    others = torch.from_numpy(rng.choice(others, size=min(256, len(others)), replace=False)).to(w["staging"].device) \
+        if len(others) else None
+    before = [pool.view(w["pool_pages"], -1)[others].clone() for pool in w["pools"]] if others is not None else []
+    w["staging"].bitwise_xor_(0x5A5A5A5A)
+    scatter()
+    torch.cuda.synchronize()
+    ok = verify_gather(w)  # pools[table] == staging[slots] again, now with the new content
+    for pool, b in zip(w["pools"], before):
+        ok = ok and torch.equal(pool.view(w["pool_pages"], -1)[others], b)
+    return bool(ok)
+
+
+def transfer_config(cfg, payload):
+    """The `config` object of the transfer workloads: what is moved, nothing about how a run went, so that the GPU
+    arm and the CPU arm print the same object."""
+    return {"workload": cfg["desc"], "pool_pages": cfg["pool_pages"], "payload_bytes_per_direction": payload,
+            "l2": "inputs (%.1f GiB staged per direction) far exceed the 126 MB L2; no flush needed"
+                  % (payload / 2 ** 30)}
+
+
+def full_payload(cfg):
+    return cfg["n_blocks"] * cfg["n_pools"] * cfg["pages_per_block"] * cfg["page_tokens"] * cfg["token_bytes"]
+
+
+def run_cpu_transfer(cfg, threads, steps, warmup, budget_s=20.0, max_payload=None):
+    """The CPU restatement of one gather + scatter step on a bounded sample (host memory): as many of the
+    workload's blocks as fit a quarter of the free host memory (pools twice the payload, staging once) and
+    `max_payload`, up to the whole workload."""
+    import psutil
+
     from oracle import kvcm_oracle as oracle
     n_pools, page_bytes, ppb = cfg["n_pools"], cfg["page_tokens"] * cfg["token_bytes"], cfg["pages_per_block"]
-    n_blocks = max(1, (1 << 30) // (n_pools * ppb * page_bytes))  # ~1 GiB of payload per step
+    block_bytes = n_pools * ppb * page_bytes
+    room = psutil.virtual_memory().available // 4 // 3
+    if max_payload is not None:
+        room = min(room, max_payload)
+    n_blocks = int(max(1, min(cfg["n_blocks"], room // block_bytes)))
     pool_pages = 2 * n_blocks * ppb
     rng = np.random.default_rng(0xB2000002)
-    pools = [rng.integers(0, 256, size=pool_pages * page_bytes, dtype=np.uint8) for _ in range(n_pools)]
+    # uniform-random bytes: one random 16 MiB piece per pool laid end to end (memcpy speed does not depend on
+    # the values, and drawing tens of GiB from a generator would take longer than the measurement)
+    pools = []
+    for _ in range(n_pools):
+        piece = rng.integers(0, 256, size=min(16 << 20, pool_pages * page_bytes), dtype=np.uint8)
+        pools.append(np.resize(piece, pool_pages * page_bytes))
     table = rng.permutation(pool_pages)[:n_blocks * ppb].astype(np.int32)
     slots = rng.permutation(n_blocks).astype(np.int32)
-    staging = np.zeros(n_blocks * n_pools * ppb * page_bytes, dtype=np.uint8)
+    staging = np.zeros(n_blocks * block_bytes, dtype=np.uint8)
     payload = staging.nbytes
 
     def step():
@@ -337,38 +417,70 @@ def run_prefix_cpu(data, threads, budget_s=12.0):
 # main arms
 # ----------------------------------------------------------------------------------------------
 def main_reference(args, cfg, rank):
+    """CPU arm of the transfer workloads: the same step on the host cores (rank 0 only), `--steps` steps after
+    `--warmup` warm-up steps, on as many of the workload's blocks as the host memory holds."""
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    gbs, ms, sample, n = run_cpu_transfer(cfg, threads, args.steps, min(args.warmup, 1))
+    gbs, ms, sample, n = run_cpu_transfer(cfg, threads, args.steps, args.warmup, budget_s=240.0)
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": n,
-        "warmup": min(args.warmup, 1), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-        "config": {"workload": cfg["desc"], "note": "the reference has no CPU gather/scatter (Triton only, and its "
-                   "sources cannot travel to the GPU box); this arm times the CPU restatement of the same index "
-                   "rule with all host threads on a bounded sample"},
-        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "config": transfer_config(cfg, full_payload(cfg)),
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": sample + "; the reference has no CPU gather/scatter (Triton only), so this arm "
+                                            "times the CPU restatement of the same index rule with all host threads"},
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
 
 
-def main_b200(args, cfg, rank, world):
+def measure_link(ctx, d_buf, h_out, h_in, piece=256 << 20, reps=3):
+    """What the host link gives plain copies, with no kernel and no operator in the way: every rank, after a
+    barrier, copies `d_buf` to the pinned `h_out` and the pinned `h_in` to `d_buf`'s second half with
+    cudaMemcpyAsync in pieces of 256 MiB - each direction alone, then both at once on two streams - and the
+    slowest rank counts.  GB/s of payload per direction and per GPU."""
     import torch
-    import torch.distributed as dist
+    n = min(d_buf.numel() // 2, h_out.numel(), h_in.numel())
+    s_out, s_in = torch.cuda.Stream(ctx.device), torch.cuda.Stream(ctx.device)
+    d_src, d_dst = d_buf[:n], d_buf[n:2 * n]
+
+    def run(out, inn):
+        for a in range(0, n, piece):
+            b = min(n, a + piece)
+            if out:
+                with torch.cuda.stream(s_out):
+                    h_out[a:b].copy_(d_src[a:b], non_blocking=True)
+            if inn:
+                with torch.cuda.stream(s_in):
+                    d_dst[a:b].copy_(h_in[a:b], non_blocking=True)
+
+    res = {}
+    for name, out, inn in (("d2h_alone", True, False), ("h2d_alone", False, True), ("both", True, True)):
+        run(out, inn)
+        torch.cuda.synchronize(ctx.device)
+        ctx.barrier()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            run(out, inn)
+        torch.cuda.synchronize(ctx.device)
+        dt = ctx.max_over_ranks([time.perf_counter() - t0])[0]
+        res[name] = n * h_out.element_size() * reps / dt / 1e9
+    return res
+
+
+def run_transfer(args, cfg, ctx, with_e2e=True, with_cpu=True):
+    """One transfer workload on this rank's GPU (every rank its own tensor-parallel slice); returns the JSON line
+    on every rank (the figures are already reduced over the ranks)."""
+    import torch
 
     import tair_kvcache_b200  # noqa: F401
     from tair_kvcache_b200.kernel import (batch_gather_kv_caches, batch_gather_kv_pages, batch_scatter_kv_caches,
                                           batch_scatter_kv_pages)
 
-    local = int(os.environ.get("LOCAL_RANK", 0))
-    device = torch.device("cuda", local)
-    torch.cuda.set_device(device)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-
+    rank, world, device = ctx.rank, ctx.world, ctx.device
     w = build_transfer_workload(cfg, device, seed=0xB2000002 + rank)
     ptrs, table, slots, staging = w["ptrs"], w["table"], w["slots"], w["staging"]
     ppb, page_bytes, pool_pages, payload = w["ppb"], w["page_bytes"], w["pool_pages"], w["payload"]
@@ -381,7 +493,7 @@ def main_b200(args, cfg, rank, world):
 
     gather()
     torch.cuda.synchronize(device)
-    parity_ok = verify_staging(w)
+    gather_ok = verify_gather(w)
 
     sampler = ClockSampler(str(torch.cuda.get_device_properties(device).uuid)) if rank == 0 else None
     if sampler:
@@ -390,8 +502,7 @@ def main_b200(args, cfg, rank, world):
         gather()
         scatter()
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
-    if world > 1:
-        dist.barrier()
+    ctx.barrier()
     torch.cuda.synchronize(device)
     if sampler:
         sampler.mark_begin()
@@ -407,18 +518,15 @@ def main_b200(args, cfg, rank, world):
     torch.cuda.synchronize(device)
     if sampler:
         sampler.mark_end()
-    if world > 1:
-        dist.barrier()
+    ctx.barrier()
     clocks = sampler.stop() if sampler else None
     elapsed_ms = start.elapsed_time(stop)
     gather_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
     scatter_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
-    if world > 1:
-        t = torch.tensor([elapsed_ms, gather_ms, scatter_ms], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms, gather_ms, scatter_ms = t.tolist()
+    elapsed_ms, gather_ms, scatter_ms = ctx.max_over_ranks([elapsed_ms, gather_ms, scatter_ms])
     alg_bytes_step = 4 * payload  # gather: read + write payload; scatter: the same
     value = world * alg_bytes_step * args.steps / (elapsed_ms * 1e-3) / 1e9
+    scatter_ok = verify_scatter(w, scatter)
 
     # ---- end to end: pinned host staging through the operator API, python index lists included.
     # As in the reference connector (kv_cache_manager/py_connector/vllm/data_transfer.py:77-78,138,203) saves run
@@ -431,8 +539,8 @@ def main_b200(args, cfg, rank, world):
     dim = cfg["token_bytes"] // 2
     task_payload = task_blocks * w["n_pools"] * T * cfg["token_bytes"]
     idx_bytes = n_tasks * 2 * (task_blocks * T + task_blocks) * 4
-    e2e_value, e2e_steps, e2e_parity = None, 0, None
-    if not args.no_e2e:
+    e2e = None
+    if with_e2e:
         save_pool = torch.empty(task_blocks, w["n_pools"], T, dim, dtype=torch.bfloat16, pin_memory=True)
         load_pool = torch.empty(n_tasks, task_blocks, w["n_pools"], T, dim, dtype=torch.bfloat16, pin_memory=True)
         table_np = table.cpu().numpy().reshape(w["n_blocks"], ppb)
@@ -440,8 +548,15 @@ def main_b200(args, cfg, rank, world):
                   np.arange(cfg["page_tokens"])[None, None, :]).reshape(w["n_blocks"], T)
         task_tok = [tok_np[i * task_blocks:(i + 1) * task_blocks].reshape(-1).tolist() for i in range(n_tasks)]
         task_slots = list(range(task_blocks))
-        for i in range(n_tasks):  # what storage would hand back: the blocks as saved
-            batch_gather_kv_caches(ptrs, load_pool[i], task_tok[i], task_slots, T, dim)
+
+        def torch_gather_of_task(i):
+            """What storage hands back for task i: the blocks as a torch gather of the pools lays them out
+            ([block, pool, tokens x dim]); built without the kernels under test."""
+            pages = torch.from_numpy(table_np[i * task_blocks:(i + 1) * task_blocks]).to(device).long()
+            return torch.stack([pool.view(pool_pages, -1)[pages].reshape(task_blocks, -1) for pool in w["pools"]], 1)
+
+        for i in range(n_tasks):
+            load_pool[i].view(torch.int32).view(task_blocks, w["n_pools"], -1).copy_(torch_gather_of_task(i))
         torch.cuda.synchronize(device)
         save_stream, load_stream = torch.cuda.Stream(device), torch.cuda.Stream(device)
 
@@ -455,37 +570,64 @@ def main_b200(args, cfg, rank, world):
         e2e_steps = max(1, min(args.steps, 3))
         e2e_step()
         torch.cuda.synchronize(device)
-        if world > 1:
-            dist.barrier()
+        ctx.barrier()
         t_wall = time.perf_counter()
         for _ in range(e2e_steps):
             e2e_step()
         torch.cuda.synchronize(device)  # both streams drained: every staged byte has crossed PCIe
         e2e_ms = (time.perf_counter() - t_wall) * 1e3  # wall clock around the calls: host list conversion counts
-        if world > 1:
-            t = torch.tensor([e2e_ms], dtype=torch.float64, device=device)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e2e_ms = t.item()
+        e2e_ms = ctx.max_over_ranks([e2e_ms])[0]
         e2e_value = world * 4 * task_payload * n_tasks * e2e_steps / (e2e_ms * 1e-3) / 1e9
-        e2e_parity = bool(torch.equal(save_pool.view(torch.int16), load_pool[n_tasks - 1].view(torch.int16)))
-        del save_pool, load_pool
-
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
+        # parity of both directions, against torch indexing.  Save: the pinned blocks of the last save task.  Load:
+        # one task scattered from pinned host memory into zeroed scratch pools through a page table of its own,
+        # then every scratch page compared with the page of the real pools it stands for.
+        want_last = torch_gather_of_task(n_tasks - 1)
+        save_ok = bool(torch.equal(save_pool.view(torch.int32).view(task_blocks, w["n_pools"], -1).to(device),
+                                   want_last))
+        del want_last
+        n_scr = task_blocks * ppb
+        scratch = [torch.zeros(n_scr * page_bytes // 4, dtype=torch.int32, device=device) for _ in range(w["n_pools"])]
+        scr_ptrs = torch.tensor([t.data_ptr() for t in scratch], dtype=torch.int64, device=device)
+        scr_table = np.random.default_rng(5).permutation(n_scr).reshape(task_blocks, ppb)
+        scr_tok = (scr_table[:, :, None].astype(np.int64) * cfg["page_tokens"] +
+                   np.arange(cfg["page_tokens"])[None, None, :]).reshape(-1).tolist()
+        batch_scatter_kv_caches(scr_ptrs, load_pool[0], scr_tok, task_slots, T, dim)
+        torch.cuda.synchronize(device)
+        real = torch.from_numpy(table_np[:task_blocks]).to(device).long()
+        scr = torch.from_numpy(scr_table).to(device).long()
+        load_ok = all(bool(torch.equal(sp.view(n_scr, -1)[scr], pool.view(pool_pages, -1)[real]))
+                      for sp, pool in zip(scratch, w["pools"]))
+        # the host link's own ceiling, measured beside it with plain copies of the same pinned pools
+        del scratch
+        d_buf = torch.empty(2 * save_pool.numel(), dtype=torch.int16, device=device)
+        link = measure_link(ctx, d_buf, save_pool.view(torch.int16).view(-1),
+                            load_pool[0].view(torch.int16).view(-1))
+        per_dir = e2e_value / 4 / world  # payload GB/s per direction and GPU through the operators
+        e2e = {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": task_payload * n_tasks + idx_bytes,
+               "d2h_bytes_per_step": task_payload * n_tasks, "parity_ok": save_ok and load_ok,
+               "parity": {"saved_blocks_equal_torch_gather": save_ok, "load_into_zeroed_scratch_pools": load_ok},
+               "payload_GBps_per_direction_per_gpu": per_dir,
+               "link_peak": {"unit": "GB/s of payload per direction per GPU, plain cudaMemcpyAsync of the same pinned "
+                                     "pools in 256 MiB pieces, max over ranks",
+                             "both_directions_at_once": link["both"], "d2h_alone": link["d2h_alone"],
+                             "h2d_alone": link["h2d_alone"], "aggregate_both": link["both"] * world},
+               "frac_of_link": per_dir / link["both"],
+               "note": "%d save tasks and %d load tasks of %d blocks per step on two streams, staging in pinned "
+                       "host memory, token-index lists converted per call" % (n_tasks, n_tasks, task_blocks)}
+        del save_pool, load_pool, d_buf
 
     peak, peak_kind = peaks()
     gather_gbs = 2 * payload / (gather_ms * 1e-3) / 1e9
     scatter_gbs = 2 * payload / (scatter_ms * 1e-3) / 1e9
+    config = transfer_config(cfg, payload)
+    config["pool_pages"] = pool_pages
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "u8", "data": "synthetic",
-        "config": {"workload": cfg["desc"], "pool_pages": pool_pages, "payload_bytes_per_direction": payload,
-                   "l2": "inputs (%.1f GiB staged per direction) far exceed the 126 MB L2; no flush needed"
-                         % (payload / 2 ** 30),
-                   "parity_sample_ok": parity_ok},
+        "dtype": "u8", "data": "synthetic", "config": config,
+        "parity_sample_ok": gather_ok and scatter_ok,
+        "parity": {"gather_all_tiles_equal_torch_gather": gather_ok,
+                   "scatter_of_changed_staging_all_pages_and_untouched_sample": scatter_ok},
         "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "MoveRowsBulkKernel<gather>", "achieved": gather_gbs, "peak": peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": gather_gbs / peak,
@@ -494,34 +636,28 @@ def main_b200(args, cfg, rank, world):
                      "algorithmic_bytes_per_launch": 2 * payload, "launch_ms": gather_ms,
                      "scatter": {"kernel": "MoveRowsBulkKernel<scatter>", "achieved": scatter_gbs,
                                  "frac": scatter_gbs / peak, "launch_ms": scatter_ms}},
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": task_payload * n_tasks + idx_bytes,
-                "d2h_bytes_per_step": task_payload * n_tasks, "parity_ok": e2e_parity,
-                "note": "%d save tasks and %d load tasks of %d blocks per step on two streams, staging in pinned "
-                        "host memory, token-index lists converted per call" % (n_tasks, n_tasks, task_blocks)},
         "gpu_launches": 2 * args.steps * world,
     }
-    if world == 1 and not args.no_cpu:
+    if e2e is not None:
+        line["e2e"] = e2e
+    if world == 1 and with_cpu and not args.no_cpu:
         threads = os.cpu_count() or 1
-        cpu_gbs, _, sample, _ = run_cpu_transfer(cfg, threads, 40, 1, budget_s=8.0)
+        cpu_gbs, _, sample, _ = run_cpu_transfer(cfg, threads, 40, 1, budget_s=8.0, max_payload=2 << 30)
         line["cpu_baseline"] = {"value": cpu_gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
-        if not args.no_prefix:
-            del w, staging
-            torch.cuda.empty_cache()
-            pm, data = run_prefix_gpu(device, 20, 3)
-            cpu_pm, n_rep = run_prefix_cpu(data, threads)
-            pm["cpu_baseline"] = {"value": cpu_pm, "unit": "token-blocks/s", "cores": threads, "kind": "port",
-                                  "sample": "the whole workload, %d repetitions; omits the reference's per-key JSON "
-                                            "parse and string copies, so it over-states the reference" % n_rep}
-            line["prefix_match"] = pm
-    print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+    return line
 
 
-def main_prefix(args, rank, world):
+def extra_of(line, keep=("metric", "value", "unit", "ms_per_step", "steps", "warmup", "scaling", "config",
+                         "parity_sample_ok", "parity", "roofline", "clocks", "gpu_launches", "e2e", "cpu_baseline")):
+    """A workload's line cut down to what an extra key of the default line carries."""
+    return {k: line[k] for k in keep if k in line}
+
+
+def main_prefix(args, ctx):
     """--workload c1: the CPU-runnable prefix-match configuration on its own (hash + prefix match of 4,096
-    requests against an index of 200k prior blocks).  Replicas only: every rank runs the same batch."""
-    if rank != 0:
+    requests against an index of 200k prior blocks).  Replicas only: every rank would run the same batch, so
+    rank 0 alone runs it.  `ctx` is None for the CPU arm."""
+    if ctx is not None and ctx.rank != 0:
         return
     threads = os.cpu_count() or 1
     if args.impl == "reference":
@@ -539,11 +675,8 @@ def main_prefix(args, rank, world):
                           "e2e": {"value": cpu, "unit": "token-blocks/s", "h2d_bytes_per_step": 0,
                                   "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
         return
-    import torch
-
     import tair_kvcache_b200  # noqa: F401
-    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
-    torch.cuda.set_device(device)
+    device = ctx.device
     pm, data = run_prefix_gpu(device, args.steps, args.warmup)
     line = {"metric": "prefix_match_token_blocks_per_s", "value": pm["token_blocks_per_s"], "unit": "token-blocks/s",
             "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
@@ -614,7 +747,10 @@ def build_window_workload(device, rank, world, n_req_total, n_roots, index_keys_
                 mine=mine, bs=bs, index_keys_total=index_keys_total, req_len=req_len)
 
 
-def main_window(args, rank, world):
+def run_window(args, ctx):
+    """--workload c4 (and the `window_match` key of the default line): hash + prefix match + sliding-window match
+    of this rank's share of the requests against the index split by hash range over the ranks.  Returns the JSON
+    line on rank 0, None elsewhere."""
     import torch
     import torch.distributed as dist
 
@@ -622,11 +758,7 @@ def main_window(args, rank, world):
     from tair_kvcache_b200.manager import (BatchMetaSearcher, CudaShardBackend, GenKeyVectorBatch,
                                            ShardedMetaSearcher, encode_locations, key_offsets, length_order)
 
-    local = int(os.environ.get("LOCAL_RANK", 0))
-    device = torch.device("cuda", local)
-    torch.cuda.set_device(device)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+    rank, world, device = ctx.rank, ctx.world, ctx.device
     n_req_total = args.n_requests or 65536
     index_keys = args.index_keys or 10_000_000
     sw = 4096 // 16
@@ -773,19 +905,27 @@ def main_window(args, rank, world):
     if overlap:
         step = step_overlapped_routed if world > 1 and routed else step_overlapped
 
+    sampler = ClockSampler(str(torch.cuda.get_device_properties(device).uuid)) if rank == 0 else None
+    if sampler:
+        sampler.start()
     for _ in range(args.warmup):
         prefix, window = step()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize(device)
+    if sampler:
+        sampler.mark_begin()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
         prefix, window = step()
     e1.record()
     torch.cuda.synchronize(device)
+    if sampler:
+        sampler.mark_end()
     if world > 1:
         dist.barrier()
+    clocks = sampler.stop() if sampler else None
     ms = e0.elapsed_time(e1)
     # where a step goes (one extra untimed step, phases bracketed by events)
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
@@ -852,22 +992,40 @@ def main_window(args, rank, world):
         stats[0] = mx[0]
     ms, total_keys, total_stored, n_prefix_hits, n_windows = stats.tolist()
 
-    # ---- parity on a sample of this rank's requests against the CPU oracle (rank 0, unsharded index rebuilt on the CPU)
+    # ---- parity on a sample of rank 0's requests against the CPU oracle's UNSHARDED index, rebuilt on the CPU from
+    # the keys every rank inserted (the root blocks are known to every rank; the request blocks are collected)
     parity = None
-    if rank == 0 and not args.no_cpu and world == 1:
-        from oracle import kvcm_oracle as oracle
-        ox = oracle.Index()
-        ox.put_uniform(root_keys[keep].cpu().numpy())
-        ox.put_uniform(req_keys[:int(req_ko[n_from_reqs])].cpu().numpy())
-        sample = np.random.default_rng(0).choice(len(w["mine"]), size=min(1024, len(w["mine"])), replace=False)
-        toks_h = w["toks"].cpu().numpy().view(np.uint32)
-        parity = True
-        for j in sample:
-            k = oracle.gen_key_vector(toks_h[w["off"][j]:w["off"][j + 1]], bs)
-            ok_keys = np.array_equal(k, req_keys[int(req_ko[j]):int(req_ko[j + 1])].cpu().numpy())
-            ec, base = ox.sw_match(k, sw)
-            want_w = base if ec == 0 else -2
-            parity = parity and ok_keys and ox.prefix_match(k) == int(prefix[j]) and want_w == int(window[j])
+    if not args.no_cpu:
+        n_ins = int(req_ko[n_from_reqs])
+        inserted = [req_keys[:n_ins]]
+        if world > 1:
+            sizes = torch.zeros(world, dtype=torch.int64, device=device)
+            sizes[rank] = n_ins
+            dist.all_reduce(sizes)
+            width = int(sizes.max().item())
+            mine_padded = torch.zeros(max(width, 1), dtype=torch.int64, device=device)
+            mine_padded[:n_ins] = req_keys[:n_ins]
+            parts_all = [torch.empty_like(mine_padded) for _ in range(world)]
+            dist.all_gather(parts_all, mine_padded)
+            inserted = [t[:int(n)] for t, n in zip(parts_all, sizes.tolist())]
+        if rank == 0:
+            from oracle import kvcm_oracle as oracle
+            ox = oracle.Index()
+            ox.put_uniform(root_keys[keep].cpu().numpy())
+            for t in inserted:
+                ox.put_uniform(t.cpu().numpy())
+            sample = np.random.default_rng(0).choice(len(w["mine"]), size=min(1024, len(w["mine"])), replace=False)
+            toks_h = w["toks"].cpu().numpy().view(np.uint32)
+            prefix_h, window_h = prefix.cpu().numpy(), window.cpu().numpy()
+            parity = True
+            for j in sample:
+                k = oracle.gen_key_vector(toks_h[w["off"][j]:w["off"][j + 1]], bs)
+                ok_keys = np.array_equal(k, req_keys[int(req_ko[j]):int(req_ko[j + 1])].cpu().numpy())
+                ec, base = ox.sw_match(k, sw)
+                want_w = base if ec == 0 else -2
+                parity = bool(parity and ok_keys and ox.prefix_match(k) == int(prefix_h[j]) and
+                              want_w == int(window_h[j]))
+        del inserted
 
     if rank == 0:
         longest = int(w["req_len"].max())
@@ -889,6 +1047,8 @@ def main_window(args, rank, world):
                                           }[args.shard_mode]),
                            "token_blocks": int(total_keys), "longest_request_tokens": longest,
                            "requests_with_prefix_hit": int(n_prefix_hits), "requests_with_window": int(n_windows),
+                           "shard_mode": args.shard_mode if world > 1 else "one unsharded index",
+                           "lookups_per_s": 2 * total_keys * args.steps / (ms * 1e-3),
                            "parity_sample_ok": parity, "phase_ms_rank0": phase_ms,
                            "schedule": ("two streams: the %d longest requests of rank 0 (>= %.2f of the longest) hashed "
                                         "and matched beside the rest; phase_ms are the kernels run alone on the "
@@ -896,19 +1056,36 @@ def main_window(args, rank, world):
                 "gpu_launches": ({"peer": 6, "route": 14, "route_peer": 14}[args.shard_mode] if overlap and world > 1
                                  else 6 if overlap else 3 if world == 1 else 7 if routed else 4)
                 * args.steps * world}
-        print(json.dumps(line))
+        # Roofline of the step.  Algorithmic bytes per token block: its 16 tokens (64 B), the key written (8 B), and
+        # per matcher the key read (8 B) and one index slot (16 B) = 120 B.  The binding limit is not HBM but the
+        # dependent chain of the longest request, one hash step per token: its floor is stated beside the fraction.
+        peak, peak_kind = peaks()
+        per_gpu = total_keys * 120 / world / (ms / args.steps * 1e-3) / 1e9
+        mhz = (clocks or {}).get("sm_mhz") or 1965.0
+        line["parity_sample_ok"] = parity
+        line["clocks"] = clocks
+        line["roofline"] = {
+            "bound": "hbm", "kernel": "HashBlocksKernel + matchers (whole step)", "achieved": per_gpu, "peak": peak,
+            "peak_kind": peak_kind, "unit": "GB/s", "frac": per_gpu / peak, "traffic": None,
+            "algorithmic_bytes_per_token_block": 120,
+            "hash_launch_ms_whole_batch": phase_ms["hash"],
+            "hash_cycles_per_token_on_longest_chain": phase_ms["hash"] * 1e-3 * mhz * 1e6 / longest,
+            "chain_latency_floor_ms": phase_ms["hash"],
+            "note": "latency-bound: the hash of the longest request (%d tokens, one dependent step per token) takes "
+                    "%.2f ms whatever the number of GPUs; the HBM fraction is reported for completeness" % (
+                        longest, phase_ms["hash"])}
     if world > 1:
         if args.shard_mode == "peer":
             searcher.detach_peers()
         if args.shard_mode == "route_peer":
             searcher.detach_route_areas()
-        dist.destroy_process_group()
+    return line if rank == 0 else None
 
 
 # ----------------------------------------------------------------------------------------------
 # mixed trace replay (--workload c5): hash -> replay against all earlier requests -> gather the misses (MLA layout)
 # ----------------------------------------------------------------------------------------------
-def main_replay(args, rank, world):
+def run_replay(args, ctx):
     """Per rank (one instance each, no exchange between instances): n requests with Poisson arrivals whose prompts
     reuse a prefix of one of 10,000 pool prompts chosen by Zipf(0.9), uint32 tokens, block 64.  One step = hash every
     request, replay the whole trace in arrival order (each request hits the blocks written by earlier ones and
@@ -923,11 +1100,7 @@ def main_replay(args, rank, world):
     from tair_kvcache_b200.manager import GenKeyVectorBatch, key_offsets, length_order
     from tair_kvcache_b200.optimizer import TRACE_DIALOG_TURN, RunTraces, replay_workspace_bytes
 
-    local = int(os.environ.get("LOCAL_RANK", 0))
-    device = torch.device("cuda", local)
-    torch.cuda.set_device(device)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+    rank, world, device = ctx.rank, ctx.world, ctx.device
     n_req = args.n_requests or 125000
     bs, n_prompts, n_layers, page_bytes = 64, 10000, 61, 64 * 1152
     pool_pages = args.pool_pages or 8192
@@ -1016,9 +1189,12 @@ def main_replay(args, rank, world):
         want = oracle.Replay().run(k, ko[:m + 1], np.zeros(m, dtype=np.uint8))
         parity = bool(np.array_equal(want[0], res.external_hit_blocks[:m].cpu().numpy()) and
                       np.array_equal(want[2], res.write_blocks[:m].cpu().numpy()))
+    line = None
     if rank == 0:
         gather_bytes = 2 * tot_miss * n_layers * page_bytes
-        print(json.dumps({
+        peak, peak_kind = peaks()
+        per_gpu = gather_bytes / world / (ms * 1e-3) / 1e9
+        line = ({
             "metric": "mixed_replay_requests_per_s", "value": tot_req / (ms * 1e-3), "unit": "requests/s",
             "n_gpus": world, "steps": steps, "warmup": 1, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "int64+u8", "data": "synthetic",
@@ -1027,10 +1203,15 @@ def main_replay(args, rank, world):
                                    "cache (61 layers x 73,728 B per block)" % n_req,
                        "token_blocks": int(tot_keys), "hit_blocks": int(tot_hits), "missed_blocks": int(tot_miss),
                        "token_blocks_per_s": tot_keys / (ms * 1e-3),
+                       "instances": "%d independent instances, one per GPU, no exchange between them" % world,
                        "gather_algorithmic_GBps": gather_bytes / (ms * 1e-3) / 1e9, "parity_sample_ok": parity},
-            "gpu_launches": int(world * (5 + (tot_miss / world + round_blocks - 1) // round_blocks))}))
-    if world > 1:
-        dist.destroy_process_group()
+            "parity_sample_ok": parity,
+            "roofline": {"bound": "hbm", "kernel": "MoveRowsBulkKernel<gather> (the step's dominant kernel: the gather "
+                                                   "of the missed MLA blocks)", "achieved": per_gpu, "peak": peak,
+                         "peak_kind": peak_kind, "unit": "GB/s", "frac": per_gpu / peak, "traffic": None,
+                         "note": "whole step time (hash + replay + gathers) against the gathers' algorithmic bytes"},
+            "gpu_launches": int(world * (5 + (tot_miss / world + round_blocks - 1) // round_blocks))})
+    return line
 
 
 def main_window_reference(args):
@@ -1153,7 +1334,7 @@ def _lru_quotas(n_keys, n_configs):
     return [max(100, int(n_keys * (c + 1) / (2 * n_configs))) for c in range(n_configs)]
 
 
-def main_lru(args, rank, world):
+def main_lru(args, ctx):
     """Tradeoff-curve sweep of the Optimizer: the mixed-replay trace (dialog turns, block 64) replayed with the "lru"
     policy once per quota point, all points of this rank in one launch (one warp each).  Ranks take different
     quota points of the same curve (no exchange).  One step = hash the trace + the whole sweep."""
@@ -1165,11 +1346,7 @@ def main_lru(args, rank, world):
     from tair_kvcache_b200.optimizer import (TRACE_DIALOG_TURN, RunTracesLru, RunTracesLruGroup,
                                              replay_lru_workspace_bytes)
 
-    local = int(os.environ.get("LOCAL_RANK", 0))
-    device = torch.device("cuda", local)
-    torch.cuda.set_device(device)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+    rank, world, device, local = ctx.rank, ctx.world, ctx.device, ctx.local
     n_req = args.n_requests or 125000
     n_cfg = args.n_configs or 148
     bs = 64
@@ -1282,8 +1459,6 @@ def main_lru(args, rank, world):
             # predecessors ("leaf_aware_lru"), or extents + (clear, claim, lookup) per instance + sweep (groups)
             "clocks": clocks,
             "gpu_launches": (3 * n_inst + 3 if n_inst > 1 else 6 if policy == "leaf_aware_lru" else 5) * steps}))
-    if world > 1:
-        dist.destroy_process_group()
 
 
 def main_lru_reference(args):
@@ -1333,7 +1508,7 @@ def main_lru_reference(args):
                               "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
 
 
-def main_iov(args, rank, world):
+def main_iov(args, ctx):
     """TransferClient side (the per-iov copy loops of LocalFileSdk::DoGet / DoPut and Hf3fsUsrbioClient::CopyIovs):
     blocks of layer_num x (K, V) iovs <-> contiguous block strings, at the Llama-3-8B shape (64 iovs of 128 KiB per
     block, 2,048 blocks = 131,072 iovs, 16 GiB).  One step = Put (iovs -> strings) + Get (strings -> iovs), each one
@@ -1347,11 +1522,7 @@ def main_iov(args, rank, world):
     import tair_kvcache_b200  # noqa: F401
     from tair_kvcache_b200 import _cabi
 
-    local = int(os.environ.get("LOCAL_RANK", 0))
-    device = torch.device("cuda", local)
-    torch.cuda.set_device(device)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+    rank, world, device, local = ctx.rank, ctx.world, ctx.device, ctx.local
     _cabi.bind_device(local)
     n_blocks = args.n_blocks or 2048
     n_iovs, iov_bytes = 64, 64 * 2048  # 32 layers x (K, V); 64 tokens x 2 KiB
@@ -1480,11 +1651,12 @@ def main_iov(args, rank, world):
         e2e_step()
         torch.cuda.synchronize(device)
         reps = max(1, min(args.steps, 3))
+        ctx.barrier()  # every rank crosses the host link during the same interval; the slowest one counts
         t0 = time.perf_counter()
         for _ in range(reps):
             e2e_step()
         torch.cuda.synchronize(device)
-        dt = time.perf_counter() - t0
+        dt = ctx.max_over_ranks([time.perf_counter() - t0])[0]
         e2e = {"value": world * 4 * m * block_bytes * reps / dt / 1e9, "unit": UNIT,
                "h2d_bytes_per_step": m * block_bytes + 2 * m * n_iovs * 24, "d2h_bytes_per_step": m * block_bytes,
                "parity_ok": bool(torch.equal(h_str, h_back))}
@@ -1509,8 +1681,6 @@ def main_iov(args, rank, world):
     if e2e:
         line["e2e"] = e2e
     print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
 
 
 def main_iov_reference(args):
@@ -1549,7 +1719,7 @@ def main_iov_reference(args):
                       "gpu_launches": 0}))
 
 
-def main_hash(args, rank, world):
+def main_hash(args, ctx):
     """Chained block hash alone on a batch with many more requests than schedulers (the regime where the integer pipe,
     not one request's dependent chain, sets the pace): n requests of the same length, uint32 tokens, block 16.
     Ranks hash different requests (no exchange)."""
@@ -1559,11 +1729,7 @@ def main_hash(args, rank, world):
     import tair_kvcache_b200  # noqa: F401
     from tair_kvcache_b200.manager import GenKeyVectorBatch, key_offsets
 
-    local = int(os.environ.get("LOCAL_RANK", 0))
-    device = torch.device("cuda", local)
-    torch.cuda.set_device(device)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+    rank, world, device, local = ctx.rank, ctx.world, ctx.device, ctx.local
     n_req, length, bs = args.n_requests or 65536, args.request_tokens or 20970, 16
     off = np.arange(n_req + 1, dtype=np.int64) * length
     gen = torch.Generator(device=device).manual_seed(0xB2000006 + rank)
@@ -1621,8 +1787,6 @@ def main_hash(args, rank, world):
                          "traffic": None, "peak_kind": peak_kind,
                          "note": "the binding resource is the integer pipe (~14 instructions per token)"},
             "clocks": clocks, "gpu_launches": args.steps}))
-    if world > 1:
-        dist.destroy_process_group()
 
 
 def main_hash_reference(args):
@@ -1879,54 +2043,50 @@ def main():
     ap.add_argument("--no-prefix", action="store_true", help="skip the prefix-match side measurement")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-staging leg (profiling runs)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    ap.add_argument("--extras", default="auto", choices=["auto", "none", "all"],
+                    help="default workload only: the other configurations measured after the headline and printed "
+                         "as keys of the same line.  auto = the Llama-70B/TP8 slice (c3) and the sharded window "
+                         "match (window_match) at every GPU count, the mixed replay (mixed_replay) at 8 GPUs; "
+                         "all = the three of them at any GPU count; none = the headline alone (profiling runs)")
     ap.add_argument("--n-blocks", type=int, default=0, help="override the number of transfer blocks (small cases)")
     ap.add_argument("--pool-pages", type=int, default=0, help="override the pages per pool (small cases)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
-    if args.workload == "c1":
-        main_prefix(args, rank, world)
-        return
-    if args.workload == "c5":
-        if args.impl == "reference":
-            if rank == 0:
-                main_replay_reference(args)
+    if args.impl == "reference":  # CPU arms: rank 0 alone works, the other ranks leave at once
+        if rank != 0:
             return
-        main_replay(args, rank, world)
+        arms = {"c1": lambda: main_prefix(args, None), "c4": lambda: main_window_reference(args),
+                "c5": lambda: main_replay_reference(args), "lru": lambda: main_lru_reference(args),
+                "iov": lambda: main_iov_reference(args), "hash": lambda: main_hash_reference(args),
+                "route": lambda: main_route_reference(args)}
+        if args.workload in arms:
+            arms[args.workload]()
+        else:
+            main_reference(args, transfer_cfg(args), rank)
         return
-    if args.workload == "hash":
-        if args.impl == "reference":
+
+    ctx = Ctx()
+    try:
+        if args.workload == "c1":
+            main_prefix(args, ctx)
+        elif args.workload == "route":
             if rank == 0:
-                main_hash_reference(args)
-            return
-        main_hash(args, rank, world)
-        return
-    if args.workload == "route":
-        if rank == 0:
-            (main_route_reference(args) if args.impl == "reference" else main_route(args, rank))
-        return
-    if args.workload == "iov":
-        if args.impl == "reference":
+                main_route(args, rank)
+        elif args.workload in ("lru", "iov", "hash"):
+            {"lru": main_lru, "iov": main_iov, "hash": main_hash}[args.workload](args, ctx)
+        elif args.workload in ("c4", "c5"):
+            line = (run_window if args.workload == "c4" else run_replay)(args, ctx)
             if rank == 0:
-                main_iov_reference(args)
-            return
-        main_iov(args, rank, world)
-        return
-    if args.workload == "lru":
-        if args.impl == "reference":
-            if rank == 0:
-                main_lru_reference(args)
-            return
-        main_lru(args, rank, world)
-        return
-    if args.workload == "c4":
-        if args.impl == "reference":
-            if rank == 0:
-                main_window_reference(args)
-            return
-        main_window(args, rank, world)
-        return
+                print(json.dumps(line))
+        else:
+            main_b200(args, transfer_cfg(args), ctx)
+    finally:
+        ctx.close()
+
+
+def transfer_cfg(args):
     cfg = dict(WORKLOADS[args.workload])
     cfg["full_size"] = not (args.n_blocks or args.pool_pages)
     if args.n_blocks:
@@ -1935,10 +2095,61 @@ def main():
         cfg["pool_pages"] = args.pool_pages
     if not cfg["full_size"]:
         cfg["desc"] += " [REDUCED for profiling: %d blocks, %d pages per pool]" % (cfg["n_blocks"], cfg["pool_pages"])
-    if args.impl == "reference":
-        main_reference(args, cfg, rank)
-    else:
-        main_b200(args, cfg, rank, world)
+    return cfg
+
+
+def main_b200(args, cfg, ctx):
+    """The default line: the headline transfer workload, then - with inputs of the earlier parts freed - the other
+    configurations as extra keys of the same line (every rank takes part in each; rank 0 prints)."""
+    import gc
+
+    import torch
+    t_start = time.perf_counter()
+    line = run_transfer(args, cfg, ctx, with_e2e=not args.no_e2e)
+    seconds = {"headline": round(time.perf_counter() - t_start, 1)}
+
+    def freed():
+        gc.collect()
+        torch.cuda.empty_cache()
+
+    freed()
+    if ctx.world == 1 and not args.no_cpu and not args.no_prefix:
+        t0 = time.perf_counter()
+        threads = os.cpu_count() or 1
+        pm, data = run_prefix_gpu(ctx.device, 20, 3)
+        cpu_pm, n_rep = run_prefix_cpu(data, threads)
+        pm["cpu_baseline"] = {"value": cpu_pm, "unit": "token-blocks/s", "cores": threads, "kind": "port",
+                              "sample": "the whole workload, %d repetitions; omits the reference's per-key JSON "
+                                        "parse and string copies, so it over-states the reference" % n_rep}
+        line["prefix_match"] = pm
+        seconds["prefix_match"] = round(time.perf_counter() - t0, 1)
+        freed()
+    extras = args.extras if args.workload == "c2" and cfg["full_size"] else "none"
+    if extras != "none":
+        t0 = time.perf_counter()
+        c3 = run_transfer(args, dict(WORKLOADS["c3"], full_size=True), ctx, with_e2e=not args.no_e2e, with_cpu=False)
+        line["c3"] = extra_of(c3)
+        seconds["c3"] = round(time.perf_counter() - t0, 1)
+        del c3
+        freed()
+        t0 = time.perf_counter()
+        wm = run_window(args, ctx)
+        if wm is not None:
+            line["window_match"] = extra_of(wm)
+        seconds["window_match"] = round(time.perf_counter() - t0, 1)
+        del wm
+        freed()
+        if extras == "all" or ctx.world == 8:
+            t0 = time.perf_counter()
+            mr = run_replay(args, ctx)
+            if mr is not None:
+                line["mixed_replay"] = extra_of(mr)
+            seconds["mixed_replay"] = round(time.perf_counter() - t0, 1)
+            del mr
+            freed()
+    line["wall_seconds_by_part"] = seconds
+    if ctx.rank == 0:
+        print(json.dumps(line))
 
 
 if __name__ == "__main__":

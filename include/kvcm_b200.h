@@ -54,15 +54,26 @@ extern "C" {
 #define KVCM_EC_BADARGS (KVCM_EC_BASE + 6)          /* EC_BADARGS */
 #define KVCM_EC_NOSPC (KVCM_EC_BASE + 9)            /* EC_NOSPC: index full */
 #define KVCM_EC_OUT_OF_LIMIT (KVCM_EC_BASE + 14)    /* EC_OUT_OF_LIMIT: size beyond a fixed limit */
+#define KVCM_EC_MISMATCH (KVCM_EC_BASE + 16)        /* EC_MISMATCH: a compare-and-set found another status */
 
 typedef void *kvcm_stream_t; /* cudaStream_t */
 
 KVCM_API int32_t kvcm_b200_abi_version(void);
 /* Binds the calling thread to CUDA device `device` for the calls that follow (one process drives
  * one GPU; a host that already selected its device through the CUDA runtime it shares with this
- * library need not call it).  Grid sizing uses the properties of the device current at first use. */
+ * library need not call it).  Grid sizes come from the properties of the calling thread's current device,
+ * which the library keeps per device. */
 KVCM_API int32_t kvcm_b200_set_device(int32_t device);
 KVCM_API const char *kvcm_b200_error_string(int32_t code);
+/* Self test of the give-up path of the kernels' bounded waits.  Every kernel here that waits on an mbarrier
+ * (the bulk-copy rings of gather / scatter, of the segment copy and of the hash) polls through one shared helper
+ * and, when the poll limit runs out, raises an error word (status[2] of gather / scatter,
+ * kvcm_b200_copy_wait_timeouts, kvcm_b200_hash_wait_timeouts), waits - bounded again - for the copies it still
+ * has in flight and returns.  This entry point runs that helper once, in one warp, on a barrier armed for bytes
+ * that are never sent (no copy is issued), with `poll_limit` polls (1..65536): the wait runs out by
+ * construction, d_status[0] = 1 (gave up) and d_status[1] = poll_limit are written, and the kernel returns;
+ * nothing faults, traps or hangs, and the context stays usable.  No counterpart in the reference. */
+KVCM_API int32_t kvcm_b200_selftest_bounded_wait(uint32_t poll_limit, uint32_t *d_status, kvcm_stream_t stream);
 /* Number of SMs and L2 bytes of the current device (synchronous, cached). */
 KVCM_API int32_t kvcm_b200_device_info(int32_t *sm_count, int64_t *l2_bytes, int64_t *free_bytes,
                                        int64_t *total_bytes);
@@ -274,6 +285,10 @@ KVCM_API int32_t kvcm_b200_key_offsets(const int64_t *h_tok_off, int32_t n_req, 
  *   bit c        (0..15)  some location of class c is CLS_SERVING
  *   bit 16 + c   (16..31) some location of class c has status != CLS_NOT_FOUND
  *   bit 32                the location map is non-empty
+ *   bits 33 + 3c .. 35 + 3c, c in [0,8)   status of the key's location in class c: 0 = the map has no
+ *                         location of that class, else CacheLocationStatus + 1.  Read and written only by
+ *                         kvcm_b200_index_update_status; the matchers read the summary bits above, which
+ *                         that entry point keeps in step.  KVCM_VAL_LOCATION(c, status) builds all three.
  *   bit 63                always set in a stored value (lookups return 0 for an absent key)
  * `avail_mask` arguments carry bit c set when the active SelectLocationPolicy gives class c a
  * weight > 0 (all classes with the default static weights).
@@ -282,6 +297,11 @@ KVCM_API int32_t kvcm_b200_key_offsets(const int64_t *h_tok_off, int32_t n_req, 
 #define KVCM_VAL_WRITABLE(c) (1ull << (16 + (c)))
 #define KVCM_VAL_NONEMPTY (1ull << 32)
 #define KVCM_VAL_PRESENT (1ull << 63)
+#define KVCM_VAL_STATUS_SHIFT 33u
+/* The bits one location of class c in [0,8) with CacheLocationStatus `status` contributes to a value word. */
+#define KVCM_VAL_LOCATION(c, status)                                                                  \
+    (KVCM_VAL_NONEMPTY | ((uint64_t)((status) + 1) << (KVCM_VAL_STATUS_SHIFT + 3u * (c))) |            \
+     ((status) == 3 ? KVCM_VAL_SERVING(c) : 0ull) | ((status) != 0 ? KVCM_VAL_WRITABLE(c) : 0ull))
 #define KVCM_AVAIL_ALL 0xFFFFu
 
 typedef struct kvcm_b200_index kvcm_b200_index_t;
@@ -301,6 +321,60 @@ KVCM_API int32_t kvcm_b200_index_upsert(kvcm_b200_index_t *index, const int64_t 
                                         uint64_t uniform_value, int64_t n, uint32_t *d_status, kvcm_stream_t stream);
 KVCM_API int32_t kvcm_b200_index_erase(kvcm_b200_index_t *index, const int64_t *d_keys, int64_t n,
                                        kvcm_stream_t stream);
+/* Number of slots and, synchronous on `stream`, the live keys and the slots in use (live keys + the
+ * tombstones erased keys leave behind).  An insert reuses the first tombstone on its key's probe chain, so
+ * under steady insert / erase churn `used_slots` levels off; it only claims a never-used slot while
+ * used_slots < 7/8 of the slots, and is refused (d_status[0] of upsert) beyond that even though
+ * live_keys may be far below the capacity: time for kvcm_b200_index_rehash. */
+KVCM_API int32_t kvcm_b200_index_usage(kvcm_b200_index_t *index, int64_t *slots, int64_t *live_keys,
+                                       int64_t *used_slots, kvcm_stream_t stream);
+/* Rebuilds the table in place without its tombstones: the live {key, value} pairs are copied to the
+ * caller's device workspace (16-byte aligned, at least kvcm_b200_index_rehash_workspace_bytes), the slots
+ * are reset and the pairs inserted again.  Three launches on `stream`; no other call may use the index
+ * while they run.  d_status[0] (may be NULL) counts pairs that could not be put back (never, unless the
+ * index is written concurrently).  Counterpart of nothing in the reference, whose std::unordered_map
+ * (kv_cache_manager/meta/meta_local_backend.h:60) frees a node when a key is deleted. */
+KVCM_API int64_t kvcm_b200_index_rehash_workspace_bytes(kvcm_b200_index_t *index);
+/* By default the library rebuilds the table by itself: it adds up, on the host, the keys passed to erase and
+ * to the status transitions since the last rebuild, and once that sum reaches slots / 8 the next upsert runs
+ * the rebuild first, on the upsert's stream, with a workspace taken from and returned to the stream-ordered
+ * allocator (cudaMallocAsync; when that fails the rebuild is put off to the next upsert).  So tombstones
+ * never take more than an eighth of the slots and probe chains stay short under any amount of insert /
+ * erase churn.  erased_keys = 0 turns this off for callers that call kvcm_b200_index_rehash themselves. */
+KVCM_API int32_t kvcm_b200_index_set_auto_rehash(kvcm_b200_index_t *index, int64_t erased_keys);
+KVCM_API int32_t kvcm_b200_index_rehash(kvcm_b200_index_t *index, void *d_workspace, int64_t workspace_bytes,
+                                        uint32_t *d_status, kvcm_stream_t stream);
+
+/* Location-status transitions, one task per key, applied with a compare-and-swap on the key's value word:
+ * the device-side counterpart of MetaSearcher::BatchUpdateLocationStatus, BatchCASLocationStatus,
+ * BatchCADLocationStatus and BatchDeleteLocation (kv_cache_manager/manager/meta_searcher.cc:410-487,
+ * 489-580, 582-717, 719-820).  A task names the storage class of the location (the stand-in for the
+ * reference's location id: the word keeps one status per class, classes 0..7), the status it must have
+ * (KVCM_STATUS_ANY = unconditional update / delete) and the status it gets (KVCM_STATUS_DELETE removes the
+ * location and, with the key's last location, the key, as BatchCADLocationStatus does;
+ * KVCM_STATUS_DELETE_KEEP_KEY removes the location the way BatchDeleteLocation does: an absent key is
+ * KVCM_OK, and a key that loses its last location stays in the index with an empty location map).  d_tasks[i] = KVCM_STATUS_TASK(class, expected, new), or NULL and every key gets `uniform_task`.
+ * d_results[i]: KVCM_OK; KVCM_EC_NOENT when the key is absent or has no location of that class
+ * (BlockCacheLocationsMeta::UpdateLocationStatus / GetLocationStatus, kv_cache_manager/manager/cache_location.cc:60-82);
+ * KVCM_EC_MISMATCH when the status differs from the expected one; KVCM_EC_BADARGS for a malformed task.
+ * A key whose last location is deleted leaves the index, as MetaIndexer::MA_DELETE does.  Several tasks of
+ * one call may name the same key; they are applied one after the other in an unspecified order.  A key
+ * with more than one location in one class cannot be represented: keep such a key's map on the host and
+ * write its word with kvcm_b200_index_upsert.  The _sharded form touches only the keys this shard owns
+ * and leaves the d_results entries of the other keys as they were. */
+#define KVCM_STATUS_ANY 0xFFu
+#define KVCM_STATUS_DELETE 0xFFu
+#define KVCM_STATUS_DELETE_KEEP_KEY 0xFEu
+#define KVCM_STATUS_TASK(cls, expected, next) \
+    ((uint32_t)(cls) | ((uint32_t)(expected) << 8) | ((uint32_t)(next) << 16))
+KVCM_API int32_t kvcm_b200_index_update_status(kvcm_b200_index_t *index, const int64_t *d_keys,
+                                               const uint32_t *d_tasks, uint32_t uniform_task, int64_t n,
+                                               int32_t *d_results, kvcm_stream_t stream);
+KVCM_API int32_t kvcm_b200_index_update_status_sharded(kvcm_b200_index_t *index, const int64_t *d_keys,
+                                                       const uint32_t *d_tasks, uint32_t uniform_task, int64_t n,
+                                                       int32_t shard_count, int32_t shard_rank,
+                                                       int32_t *d_results, kvcm_stream_t stream);
+
 /* d_values_out[i] = stored value of key i, 0 when absent (MetaIndexer::Get -> EC_NOENT). */
 KVCM_API int32_t kvcm_b200_index_lookup(kvcm_b200_index_t *index, const int64_t *d_keys, int64_t n,
                                         uint64_t *d_values_out, kvcm_stream_t stream);

@@ -283,6 +283,60 @@ int32_t kvcm_oracle_sw_match(void *h, const int64_t *keys, int64_t n, int64_t sw
     return 0;
 }
 
+// Location-status transitions, one task per key.  Restates the modifiers of
+//   MetaSearcher::BatchUpdateLocationStatus  kv_cache_manager/manager/meta_searcher.cc:410-487
+//   MetaSearcher::BatchCASLocationStatus     kv_cache_manager/manager/meta_searcher.cc:489-580
+//   MetaSearcher::BatchCADLocationStatus     kv_cache_manager/manager/meta_searcher.cc:582-717
+//   MetaSearcher::BatchDeleteLocation        kv_cache_manager/manager/meta_searcher.cc:719-820
+// over BlockCacheLocationsMeta::UpdateLocationStatus / GetLocationStatus / DeleteLocation
+// (kv_cache_manager/manager/cache_location.cc:60-82).  The reference names a location by its id string; here
+// the location of key i is named by its storage type types[i] (the first location of that type in the key's
+// list).  expected[i] < 0: no comparison (update / delete).  new_status[i] == -1: the location is deleted the
+// way BatchCADLocationStatus does it - a key whose location map becomes empty is removed (MA_DELETE, :689-691);
+// new_status[i] == -2: the way BatchDeleteLocation does it - a missing key is skipped with EC_OK (:741-744) and
+// a key whose last location goes stays, with an empty map (MA_OK, :783-786).  results[i]: 0 EC_OK, 2 EC_NOENT
+// (no such key - the modifier's get_ec - or no such location), 16 EC_MISMATCH.
+void kvcm_oracle_index_update_status(void *h, const int64_t *keys, int64_t n, const int32_t *types,
+                                     const int32_t *expected, const int32_t *new_status, int32_t *results) {
+    auto *ix = static_cast<OracleIndex *>(h);
+    for (int64_t i = 0; i < n; ++i) {
+        auto it = ix->table.find(keys[i]);
+        if (it == ix->table.end()) {
+            results[i] = new_status[i] == -2 ? 0 : 2;
+            continue;
+        }
+        std::vector<Loc> &locs = it->second;
+        size_t at = 0;
+        while (at < locs.size() && locs[at].type != types[i]) ++at;
+        if (at == locs.size()) {
+            results[i] = 2;
+            continue;
+        }
+        if (expected[i] >= 0 && locs[at].status != expected[i]) {
+            results[i] = 16;
+            continue;
+        }
+        results[i] = 0;
+        if (new_status[i] < 0) {
+            locs.erase(locs.begin() + static_cast<std::ptrdiff_t>(at));
+            if (locs.empty() && new_status[i] == -1) ix->table.erase(it);
+        } else {
+            locs[at].status = new_status[i];
+        }
+    }
+}
+
+// The location list of one key: returns its length (at most `room` entries are written), -1 for a missing key.
+int64_t kvcm_oracle_index_get(void *h, int64_t key, int32_t *statuses, int32_t *types, int64_t room) {
+    const std::vector<Loc> *locs = Get(static_cast<OracleIndex *>(h), key);
+    if (locs == nullptr) return -1;
+    for (size_t j = 0; j < locs->size() && static_cast<int64_t>(j) < room; ++j) {
+        statuses[j] = (*locs)[j].status;
+        types[j] = (*locs)[j].type;
+    }
+    return static_cast<int64_t>(locs->size());
+}
+
 // kv_cache_manager/manager/meta_searcher.cc:147-194 (BatchGetBestLocation) and
 // kv_cache_manager/manager/cache_manager.cc:589-635 (what FilterWriteCache reads from
 // BatchGetLocation).  flags[i]: bit0 servable (a location would be returned), bit1 key

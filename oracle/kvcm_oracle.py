@@ -53,6 +53,7 @@ def lib():
             getattr(L, name).restype = ctypes.c_int64
         L.kvcm_oracle_index_create.restype = ctypes.c_void_p
         L.kvcm_oracle_index_size.restype = ctypes.c_int64
+        L.kvcm_oracle_index_get.restype = ctypes.c_int64
         L.kvcm_oracle_prefix_match.restype = ctypes.c_int64
         L.kvcm_oracle_sw_match.restype = ctypes.c_int32
         L.kvcm_oracle_filter_write.restype = ctypes.c_int32
@@ -198,6 +199,30 @@ class Index:
     def erase(self, keys):
         keys = _i64(keys)
         lib().kvcm_oracle_index_erase(self._h, _ptr(keys, ctypes.c_int64), ctypes.c_int64(len(keys)))
+
+    def update_status(self, keys, types, expected, new_status):
+        """One task per key on the location of storage type types[i]: expected[i] < 0 = no comparison;
+        new_status[i] = -1 deletes the location as BatchCADLocationStatus does (an emptied key goes), -2 as
+        BatchDeleteLocation does (an emptied key stays, a missing key is EC_OK).  Returns the reference's
+        ErrorCode per key (0, 2 EC_NOENT, 16 EC_MISMATCH).  kv_cache_manager/manager/meta_searcher.cc:410-820."""
+        keys = _i64(keys)
+        n = len(keys)
+        ty = np.ascontiguousarray(np.broadcast_to(np.asarray(types, dtype=np.int32), (n,)))
+        ex = np.ascontiguousarray(np.broadcast_to(np.asarray(expected, dtype=np.int32), (n,)))
+        nw = np.ascontiguousarray(np.broadcast_to(np.asarray(new_status, dtype=np.int32), (n,)))
+        res = np.zeros(n, dtype=np.int32)
+        lib().kvcm_oracle_index_update_status(self._h, _ptr(keys, ctypes.c_int64), ctypes.c_int64(n),
+                                              _ptr(ty, ctypes.c_int32), _ptr(ex, ctypes.c_int32),
+                                              _ptr(nw, ctypes.c_int32), _ptr(res, ctypes.c_int32))
+        return res
+
+    def get(self, key):
+        """The (status, storage type) list of one key, or None when the key is absent."""
+        st = np.zeros(64, dtype=np.int32)
+        ty = np.zeros(64, dtype=np.int32)
+        n = int(lib().kvcm_oracle_index_get(self._h, ctypes.c_int64(int(key)), _ptr(st, ctypes.c_int32),
+                                            _ptr(ty, ctypes.c_int32), ctypes.c_int64(64)))
+        return None if n < 0 else [(int(st[j]), int(ty[j])) for j in range(min(n, 64))]
 
     def prefix_match(self, keys, mask=None, weights=DEFAULT_WEIGHTS):
         """mask: None, an int offset, or a sequence of bools (kv_cache_manager/manager/cache_location.h:52-57)."""

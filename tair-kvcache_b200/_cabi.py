@@ -23,6 +23,10 @@ KVCM_EC_NOENT = KVCM_EC_BASE + 2
 KVCM_EC_BADARGS = KVCM_EC_BASE + 6
 KVCM_EC_NOSPC = KVCM_EC_BASE + 9
 KVCM_EC_OUT_OF_LIMIT = KVCM_EC_BASE + 14
+KVCM_EC_MISMATCH = KVCM_EC_BASE + 16
+STATUS_ANY = STATUS_DELETE = 0xFF
+STATUS_DELETE_KEEP_KEY = 0xFE
+VAL_STATUS_SHIFT = 33
 REPLAY_NOALLOC_MAX_KEYS = 262144
 
 VAL_NONEMPTY = 1 << 32
@@ -63,6 +67,7 @@ SIGNATURES = {
     "kvcm_b200_set_device": [_i32],
     "kvcm_b200_error_string": [_i32],
     "kvcm_b200_device_info": [_vp, _vp, _vp, _vp],
+    "kvcm_b200_selftest_bounded_wait": [_u32, _vp, _vp],
     "kvcm_b200_gather_tokens": _MOVE,
     "kvcm_b200_scatter_tokens": _MOVE,
     "kvcm_b200_gather_pages": _MOVE,
@@ -88,6 +93,12 @@ SIGNATURES = {
     "kvcm_b200_index_destroy": [_vp],
     "kvcm_b200_index_clear": [_vp, _vp],
     "kvcm_b200_index_stats": [_vp, _vp, _vp, _vp],
+    "kvcm_b200_index_usage": [_vp, _vp, _vp, _vp, _vp],
+    "kvcm_b200_index_rehash_workspace_bytes": [_vp],
+    "kvcm_b200_index_rehash": [_vp, _vp, _i64, _vp, _vp],
+    "kvcm_b200_index_set_auto_rehash": [_vp, _i64],
+    "kvcm_b200_index_update_status": [_vp, _vp, _vp, _u32, _i64, _vp, _vp],
+    "kvcm_b200_index_update_status_sharded": [_vp, _vp, _vp, _u32, _i64, _i32, _i32, _vp, _vp],
     "kvcm_b200_index_upsert": [_vp, _vp, _vp, _u64, _i64, _vp, _vp],
     "kvcm_b200_index_erase": [_vp, _vp, _i64, _vp],
     "kvcm_b200_index_lookup": [_vp, _vp, _i64, _vp, _vp],

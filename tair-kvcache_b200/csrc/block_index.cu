@@ -26,7 +26,7 @@ struct kvcm_b200_index {
     void *base;         // one allocation: 256-byte header (the cells), the slots, then one tag byte per slot
     ulonglong2 *slots;
     uint8_t *tags;
-    uint64_t *cells;    // [0],[1]: values of the two reserved keys; [2]: live key count
+    uint64_t *cells;    // [0],[1]: values of the two reserved keys; [2]: live keys; [3]: slots that are not EMPTY
     uint64_t n_slots;
     uint64_t max_live;
     int device;
@@ -36,6 +36,10 @@ struct kvcm_b200_index {
     uint32_t peer_count;
     void *opened[64];
     int n_opened;
+    // Host-side upper bound of the tombstones made since the table was last rebuilt (keys passed to erase and to
+    // the status transitions), and the bound at which the next upsert rebuilds the table first (0 = never).
+    uint64_t tomb_debt;
+    uint64_t auto_rehash_at;
 };
 
 // Exchange area of one rank of a routed query: the inbox the other ranks store the keys this rank owns into,
@@ -160,7 +164,76 @@ __global__ void ClearKernel(IndexView ix) {
         ix.slots[i] = make_ulonglong2(kEmptyKey, 0);
         ix.tags[i] = kTagEmpty;
     }
-    if (blockIdx.x == 0 && threadIdx.x < 3) ix.cells[threadIdx.x] = 0;
+    if (blockIdx.x == 0 && threadIdx.x < 4) ix.cells[threadIdx.x] = 0;
+}
+
+__device__ __forceinline__ void AddCell(uint64_t *cell, int64_t delta) {
+    atomicAdd(reinterpret_cast<unsigned long long *>(cell), static_cast<unsigned long long>(delta));
+}
+
+// Inserts or overwrites one key.  The probe runs to the end of the key's chain (the first EMPTY slot) and
+// remembers the first tombstone it passes; a key that is not there goes into that tombstone, and only when
+// the chain holds none into the EMPTY slot.  So a table under steady insert / erase churn reuses the slots
+// of erased keys instead of lengthening its chains.  cells[3] counts the slots that are not EMPTY (live +
+// tombstones) and an EMPTY slot is claimed only while that count is below `max_live`, which keeps EMPTY
+// slots in the table (every miss ends at one) whatever the history.
+// Several threads of one launch may insert the same new key: all of them walk the same chain, free slots
+// only get fewer while the launch runs, and a thread whose claim fails looks at what took the slot - the
+// key itself (then it only stores the value) or another key (then it walks the chain again).
+__device__ __forceinline__ bool UpsertOne(const IndexView &ix, uint64_t key, uint64_t value) {
+    unsigned long long *words = reinterpret_cast<unsigned long long *>(ix.slots);
+    const uint64_t mixed = Mix(key);
+    const uint64_t home = mixed & ix.mask;
+    for (int attempt = 0; attempt < 64; ++attempt) {
+        uint64_t slot = home, tomb = ~0ull, empty = ~0ull;
+        for (uint64_t probe = 0; probe <= ix.mask; ++probe) {
+            const uint64_t seen = LoadSlot(ix.slots + slot).x;
+            if (seen == key) {  // present already (or inserted by a duplicate of this key in the same batch)
+                atomicExch(&words[2 * slot + 1], value);
+                return true;
+            }
+            if (seen == kEmptyKey) {
+                empty = slot;
+                break;
+            }
+            if (seen == kTombKey && tomb == ~0ull) tomb = slot;
+            slot = (slot + 1) & ix.mask;
+        }
+        if (tomb != ~0ull) {
+            const uint64_t was = atomicCAS(&words[2 * tomb], kTombKey, key);
+            if (was == kTombKey) {
+                atomicExch(&words[2 * tomb + 1], value);
+                ix.tags[tomb] = TagOf(mixed);  // readers of later launches find the slot through its tag
+                AddCell(&ix.cells[2], 1);
+                return true;
+            }
+            if (was == key) {
+                atomicExch(&words[2 * tomb + 1], value);
+                return true;
+            }
+            continue;  // another key took the tombstone: walk again
+        }
+        if (empty == ~0ull) return false;  // no EMPTY slot on the whole table: cannot happen below the limit
+        // Take a seat before claiming an EMPTY slot so that the table can never run out of them.
+        const uint64_t used = atomicAdd(reinterpret_cast<unsigned long long *>(&ix.cells[3]), 1ull);
+        if (used >= ix.max_live) {
+            AddCell(&ix.cells[3], -1);
+            return false;
+        }
+        const uint64_t was = atomicCAS(&words[2 * empty], kEmptyKey, key);
+        if (was == kEmptyKey) {
+            atomicExch(&words[2 * empty + 1], value);
+            ix.tags[empty] = TagOf(mixed);
+            AddCell(&ix.cells[2], 1);
+            return true;
+        }
+        AddCell(&ix.cells[3], -1);
+        if (was == key) {
+            atomicExch(&words[2 * empty + 1], value);
+            return true;
+        }
+    }
+    return false;
 }
 
 __global__ void UpsertKernel(IndexView ix, const int64_t *__restrict__ keys, const uint64_t *__restrict__ values,
@@ -172,42 +245,37 @@ __global__ void UpsertKernel(IndexView ix, const int64_t *__restrict__ keys, con
     const uint64_t value = (values != nullptr ? values[i] : uniform_value) | KVCM_VAL_PRESENT;
     if (key == kEmptyKey || key == kTombKey) {
         const uint64_t old = atomicExch(reinterpret_cast<unsigned long long *>(&ix.cells[key - kEmptyKey]), value);
-        if (old == 0) atomicAdd(reinterpret_cast<unsigned long long *>(&ix.cells[2]), 1ull);
+        if (old == 0) AddCell(&ix.cells[2], 1);
         return;
     }
+    if (!UpsertOne(ix, key, value) && status != nullptr) atomicAdd(&status[0], 1u);
+}
+
+__device__ __forceinline__ uint64_t LoadKeyCoherent(const ulonglong2 *slot) {
+    uint64_t k;
+    asm volatile("ld.global.cg.u64 %0, [%1];\n" : "=l"(k) : "l"(slot));  // from L2: sees this launch's atomics
+    return k;
+}
+
+// The slot of an erased key becomes a tombstone so that the probe chains through it stay whole.  A tombstone
+// directly before an EMPTY slot holds no chain together (no key can lie beyond an EMPTY slot), so it is turned
+// into an EMPTY slot at once, and so are the tombstones before it: the tail of a cluster is given back.  During
+// an erase launch slots only move key -> tombstone -> EMPTY, so "the next slot is EMPTY" stays true once seen.
+// The tag of a slot may be written by the thread that made it a tombstone and by the thread that freed it;
+// whoever writes a tombstone tag looks at the slot again afterwards, so the tag ends up EMPTY when the slot did.
+__device__ __forceinline__ void ReleaseSlot(const IndexView &ix, uint64_t slot) {
     unsigned long long *words = reinterpret_cast<unsigned long long *>(ix.slots);
-    uint64_t slot = Mix(key) & ix.mask;
-    bool reserved = false;
-    for (uint64_t probe = 0; probe <= ix.mask; ++probe) {
-        uint64_t seen = LoadSlot(ix.slots + slot).x;
-        if (seen == kEmptyKey) {
-            if (!reserved) {
-                // Take a seat before claiming a slot so the table can never fill up completely.
-                const uint64_t live = atomicAdd(reinterpret_cast<unsigned long long *>(&ix.cells[2]), 1ull);
-                if (live >= ix.max_live) {
-                    atomicAdd(reinterpret_cast<unsigned long long *>(&ix.cells[2]), ~0ull);  // -1
-                    if (status != nullptr) atomicAdd(&status[0], 1u);
-                    return;
-                }
-                reserved = true;
-            }
-            seen = atomicCAS(&words[2 * slot], kEmptyKey, key);
-            if (seen == kEmptyKey) {
-                atomicExch(&words[2 * slot + 1], value);
-                ix.tags[slot] = TagOf(Mix(key));  // readers of later launches find the slot through its tag
-                return;
-            }
-        }
-        if (seen == key) {
-            // Present already (or inserted by a duplicate of this key in the same batch).
-            if (reserved) atomicAdd(reinterpret_cast<unsigned long long *>(&ix.cells[2]), ~0ull);
-            atomicExch(&words[2 * slot + 1], value);
-            return;
-        }
-        slot = (slot + 1) & ix.mask;
+    atomicExch(&words[2 * slot + 1], 0ull);
+    ix.tags[slot] = kTagTomb;
+    if (LoadKeyCoherent(ix.slots + slot) == kEmptyKey) ix.tags[slot] = kTagEmpty;
+    if (LoadKeyCoherent(ix.slots + ((slot + 1) & ix.mask)) != kEmptyKey) return;
+    uint64_t p = slot;
+    for (uint64_t n = 0; n <= ix.mask; ++n) {
+        if (atomicCAS(&words[2 * p], kTombKey, kEmptyKey) != kTombKey) break;
+        ix.tags[p] = kTagEmpty;
+        AddCell(&ix.cells[3], -1);
+        p = (p - 1) & ix.mask;
     }
-    if (reserved) atomicAdd(reinterpret_cast<unsigned long long *>(&ix.cells[2]), ~0ull);
-    if (status != nullptr) atomicAdd(&status[0], 1u);
 }
 
 __global__ void EraseKernel(IndexView ix, const int64_t *__restrict__ keys, int64_t n) {
@@ -216,7 +284,7 @@ __global__ void EraseKernel(IndexView ix, const int64_t *__restrict__ keys, int6
     const uint64_t key = static_cast<uint64_t>(keys[i]);
     if (key == kEmptyKey || key == kTombKey) {
         const uint64_t old = atomicExch(reinterpret_cast<unsigned long long *>(&ix.cells[key - kEmptyKey]), 0ull);
-        if (old != 0) atomicAdd(reinterpret_cast<unsigned long long *>(&ix.cells[2]), ~0ull);
+        if (old != 0) AddCell(&ix.cells[2], -1);
         return;
     }
     unsigned long long *words = reinterpret_cast<unsigned long long *>(ix.slots);
@@ -225,15 +293,154 @@ __global__ void EraseKernel(IndexView ix, const int64_t *__restrict__ keys, int6
         const uint64_t seen = LoadSlot(ix.slots + slot).x;
         if (seen == kEmptyKey) return;
         if (seen == key) {
-            // The slot stays occupied (tombstone) so that probe chains through it stay intact.
             if (atomicCAS(&words[2 * slot], key, kTombKey) == key) {
-                atomicExch(&words[2 * slot + 1], 0ull);
-                ix.tags[slot] = kTagTomb;
-                atomicAdd(reinterpret_cast<unsigned long long *>(&ix.cells[2]), ~0ull);
+                AddCell(&ix.cells[2], -1);
+                ReleaseSlot(ix, slot);
             }
             return;
         }
         slot = (slot + 1) & ix.mask;
+    }
+}
+
+// ---- location-status transitions on the value word (MetaSearcher::BatchUpdateLocationStatus,
+// BatchCASLocationStatus, BatchCADLocationStatus, BatchDeleteLocation:
+// kv_cache_manager/manager/meta_searcher.cc:410-820 over BlockCacheLocationsMeta::UpdateLocationStatus /
+// GetLocationStatus / DeleteLocation, kv_cache_manager/manager/cache_location.cc:60-82).
+// The word keeps, for storage classes 0..7, the status of the key's location in that class as a 3-bit field
+// (0 = no location of the class, else status + 1); a task names the class, so it plays the part of the
+// reference's location id.  The summary bits the matchers read are recomputed from the field.
+__device__ __forceinline__ uint32_t StatusField(uint64_t word, uint32_t cls) {
+    return static_cast<uint32_t>(word >> (KVCM_VAL_STATUS_SHIFT + 3u * cls)) & 7u;
+}
+
+constexpr uint64_t kAllStatusFields = ((1ull << 24) - 1) << KVCM_VAL_STATUS_SHIFT;
+constexpr uint64_t kLocationBits = 0xFFFFFFFFull | kAllStatusFields;  // anything that says "a location is here"
+
+// The word after the task, or `word` unchanged with *code != KVCM_OK.  A returned 0 means that the last
+// location went away: the key leaves the index (MetaIndexer::MA_DELETE, meta_searcher.cc:689-691,790-792).
+__device__ __forceinline__ uint64_t ApplyStatusTask(uint64_t word, uint32_t task, int32_t *code) {
+    const uint32_t cls = task & 0xFFu, expected = (task >> 8) & 0xFFu, next = (task >> 16) & 0xFFu;
+    if (cls > 7 || (expected > 4 && expected != KVCM_STATUS_ANY) ||
+        (next > 4 && next != KVCM_STATUS_DELETE && next != KVCM_STATUS_DELETE_KEEP_KEY)) {
+        *code = KVCM_EC_BADARGS;
+        return word;
+    }
+    if (word == 0 && next == KVCM_STATUS_DELETE_KEEP_KEY) {
+        *code = KVCM_OK;  // BatchDeleteLocation skips a key that is not there (meta_searcher.cc:741-744)
+        return 0;
+    }
+    const uint32_t field = word != 0 ? StatusField(word, cls) : 0;
+    if (field == 0) {
+        *code = KVCM_EC_NOENT;  // no such key, or no location of this class in its map
+        return word;
+    }
+    if (expected != KVCM_STATUS_ANY && field - 1 != expected) {
+        *code = KVCM_EC_MISMATCH;
+        return word;
+    }
+    *code = KVCM_OK;
+    uint64_t w = word & ~(7ull << (KVCM_VAL_STATUS_SHIFT + 3u * cls)) & ~KVCM_VAL_SERVING(cls) & ~KVCM_VAL_WRITABLE(cls);
+    if (next == KVCM_STATUS_DELETE || next == KVCM_STATUS_DELETE_KEEP_KEY) {
+        if ((w & kLocationBits) == 0) return next == KVCM_STATUS_DELETE ? 0 : KVCM_VAL_PRESENT;  // empty map
+        return w;
+    }
+    w |= static_cast<uint64_t>(next + 1) << (KVCM_VAL_STATUS_SHIFT + 3u * cls);
+    if (next == 3) w |= KVCM_VAL_SERVING(cls);   // CLS_SERVING
+    if (next != 0) w |= KVCM_VAL_WRITABLE(cls);  // anything but CLS_NOT_FOUND
+    return w | KVCM_VAL_NONEMPTY | KVCM_VAL_PRESENT;
+}
+
+__global__ void UpdateStatusKernel(IndexView ix, const int64_t *__restrict__ keys, const uint32_t *__restrict__ tasks,
+                                   uint32_t uniform_task, int64_t n, Shard shard, int32_t *__restrict__ results) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint64_t key = static_cast<uint64_t>(keys[i]);
+    if (!Owns(shard, key)) return;  // the owner shard answers for this key
+    const uint32_t task = tasks != nullptr ? tasks[i] : uniform_task;
+    unsigned long long *word_at = nullptr;
+    uint64_t slot = 0;
+    const bool in_cell = key == kEmptyKey || key == kTombKey;
+    if (in_cell) {
+        word_at = reinterpret_cast<unsigned long long *>(&ix.cells[key - kEmptyKey]);
+    } else {
+        slot = Mix(key) & ix.mask;
+        for (uint64_t probe = 0; probe <= ix.mask; ++probe) {
+            const uint64_t seen = LoadSlot(ix.slots + slot).x;
+            if (seen == key) {
+                word_at = reinterpret_cast<unsigned long long *>(ix.slots) + 2 * slot + 1;
+                break;
+            }
+            if (seen == kEmptyKey) break;
+            slot = (slot + 1) & ix.mask;
+        }
+    }
+    int32_t code = KVCM_EC_NOENT;
+    if (word_at == nullptr) {
+        ApplyStatusTask(0, task, &code);  // the answer for a key that is not there
+    } else {
+        // Tasks of one launch that name the same key take turns through the compare-and-swap.
+        unsigned long long seen = *reinterpret_cast<volatile unsigned long long *>(word_at);
+        for (int turn = 0; turn < 1024; ++turn) {
+            const uint64_t next = ApplyStatusTask(seen, task, &code);
+            if (code != KVCM_OK || (next == 0 && seen == 0)) break;
+            const unsigned long long was = atomicCAS(word_at, seen, next);
+            if (was == seen) {
+                if (next == 0) {  // the key's last location is gone: the key goes too
+                    AddCell(&ix.cells[2], -1);
+                    if (!in_cell) {
+                        unsigned long long *words = reinterpret_cast<unsigned long long *>(ix.slots);
+                        if (atomicCAS(&words[2 * slot], key, kTombKey) == key) ReleaseSlot(ix, slot);
+                    }
+                }
+                break;
+            }
+            seen = was;
+            code = KVCM_EC_ERROR;  // stays only if the turns run out
+        }
+    }
+    results[i] = code;
+}
+
+// ---- rebuilding the table in place: live pairs out to a workspace, table reset, pairs back in.  Drops every
+// tombstone, so probe chains are as short again as in a freshly filled table.
+__global__ void CollectLiveKernel(IndexView ix, ulonglong2 *__restrict__ pairs, unsigned long long *counter) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    const uint64_t first = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const uint64_t rounds = (ix.mask + stride) / stride;  // the same for every thread: the ballots stay converged
+    for (uint64_t r = 0; r < rounds; ++r) {
+        const uint64_t i = first + r * stride;
+        ulonglong2 s = make_ulonglong2(kEmptyKey, 0);
+        if (i <= ix.mask) s = LoadSlot(ix.slots + i);
+        const bool live = s.x != kEmptyKey && s.x != kTombKey && s.y != 0;
+        const uint32_t votes = __ballot_sync(0xffffffffu, live);
+        if (votes == 0) continue;
+        const uint32_t lane = LaneId();
+        unsigned long long base = 0;
+        if (lane == static_cast<uint32_t>(__ffs(votes) - 1)) base = atomicAdd(counter, static_cast<unsigned long long>(__popc(votes)));
+        base = __shfl_sync(0xffffffffu, base, __ffs(votes) - 1);
+        if (live) pairs[base + __popc(votes & ((1u << lane) - 1u))] = s;
+    }
+}
+
+__global__ void ResetSlotsKernel(IndexView ix) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i <= ix.mask; i += stride) {
+        ix.slots[i] = make_ulonglong2(kEmptyKey, 0);
+        ix.tags[i] = kTagEmpty;
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) {  // the two reserved keys live in their cells and stay
+        ix.cells[2] = (ix.cells[0] != 0 ? 1 : 0) + (ix.cells[1] != 0 ? 1 : 0);
+        ix.cells[3] = 0;
+    }
+}
+
+__global__ void ReinsertKernel(IndexView ix, const ulonglong2 *__restrict__ pairs, const unsigned long long *counter,
+                               uint32_t *status) {
+    const uint64_t n = *counter;
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        if (!UpsertOne(ix, pairs[i].x, pairs[i].y) && status != nullptr) atomicAdd(&status[0], 1u);
     }
 }
 
@@ -691,6 +898,8 @@ int32_t kvcm_b200_index_create(int64_t max_keys, kvcm_b200_index_t **out) {
     auto *ix = new kvcm_b200_index();
     ix->n_slots = n_slots;
     ix->max_live = n_slots - n_slots / 8;  // the matchers rely on at least one EMPTY slot per chain
+    ix->tomb_debt = 0;
+    ix->auto_rehash_at = n_slots / 8;
     cudaGetDevice(&ix->device);
     if (cudaMalloc(&ix->base, kvcm::kIndexHeaderBytes + n_slots * (sizeof(ulonglong2) + 1)) != cudaSuccess) {
         cudaGetLastError();
@@ -806,6 +1015,7 @@ int32_t kvcm_b200_index_attach_local_peers(kvcm_b200_index_t *ix, int32_t shard_
 int32_t kvcm_b200_index_clear(kvcm_b200_index_t *ix, kvcm_stream_t stream) {
     if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
     const unsigned grid = static_cast<unsigned>(kvcm::GetDeviceInfo().sm_count * 8);
+    ix->tomb_debt = 0;
     kvcm::ClearKernel<<<grid, 256, 0, kvcm::AsStream(stream)>>>(kvcm::LocalView(ix));
     return kvcm::LaunchStatus();
 }
@@ -825,12 +1035,107 @@ int32_t kvcm_b200_index_stats(kvcm_b200_index_t *ix, int64_t *slots, int64_t *li
     return KVCM_OK;
 }
 
+int32_t kvcm_b200_index_usage(kvcm_b200_index_t *ix, int64_t *slots, int64_t *live_keys, int64_t *used_slots,
+                              kvcm_stream_t stream) {
+    if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    uint64_t cells[2] = {0, 0};
+    if (cudaMemcpyAsync(cells, ix->cells + 2, sizeof(cells), cudaMemcpyDeviceToHost, kvcm::AsStream(stream)) !=
+            cudaSuccess ||
+        cudaStreamSynchronize(kvcm::AsStream(stream)) != cudaSuccess) {
+        return KVCM_ER_CUDA_STREAM_SYNCHRONIZE_ERROR;
+    }
+    if (slots != nullptr) *slots = static_cast<int64_t>(ix->n_slots);
+    if (live_keys != nullptr) *live_keys = static_cast<int64_t>(cells[0]);
+    if (used_slots != nullptr) *used_slots = static_cast<int64_t>(cells[1]);
+    return KVCM_OK;
+}
+
+int64_t kvcm_b200_index_rehash_workspace_bytes(kvcm_b200_index_t *ix) {
+    if (ix == nullptr) return 0;
+    return 256 + static_cast<int64_t>(ix->n_slots) * static_cast<int64_t>(sizeof(ulonglong2));
+}
+
+int32_t kvcm_b200_index_set_auto_rehash(kvcm_b200_index_t *ix, int64_t erased_keys) {
+    if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (erased_keys < 0) return KVCM_EC_BADARGS;
+    ix->auto_rehash_at = static_cast<uint64_t>(erased_keys);
+    return KVCM_OK;
+}
+
+// Before an insert: once enough keys have been erased since the last rebuild, rebuild first.  The workspace comes
+// from and goes back to the stream-ordered allocator, so nothing waits on the host; when it cannot be had the
+// rebuild is skipped and tried again at the next insert.
+static void MaybeRehash(kvcm_b200_index_t *ix, kvcm_stream_t stream) {
+    if (ix->auto_rehash_at == 0 || ix->tomb_debt < ix->auto_rehash_at) return;
+    const int64_t bytes = kvcm_b200_index_rehash_workspace_bytes(ix);
+    void *ws = nullptr;
+    if (cudaMallocAsync(&ws, static_cast<size_t>(bytes), kvcm::AsStream(stream)) != cudaSuccess) {
+        cudaGetLastError();
+        return;
+    }
+    kvcm_b200_index_rehash(ix, ws, bytes, nullptr, stream);
+    cudaFreeAsync(ws, kvcm::AsStream(stream));
+}
+
+int32_t kvcm_b200_index_rehash(kvcm_b200_index_t *ix, void *d_workspace, int64_t workspace_bytes, uint32_t *d_status,
+                               kvcm_stream_t stream) {
+    if (ix == nullptr || d_workspace == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if ((reinterpret_cast<uintptr_t>(d_workspace) & 15u) != 0) return KVCM_ER_INVALID_ADDRESS;
+    if (workspace_bytes < kvcm_b200_index_rehash_workspace_bytes(ix)) return KVCM_EC_NOSPC;
+    cudaStream_t s = kvcm::AsStream(stream);
+    auto *counter = static_cast<unsigned long long *>(d_workspace);
+    auto *pairs = reinterpret_cast<ulonglong2 *>(static_cast<uint8_t *>(d_workspace) + 256);
+    if (cudaMemsetAsync(counter, 0, 256, s) != cudaSuccess) return KVCM_ER_CUDAMEMCPY_ERROR;
+    const kvcm::IndexView view = kvcm::LocalView(ix);
+    const unsigned grid = static_cast<unsigned>(kvcm::GetDeviceInfo().sm_count * 8);
+    kvcm::CollectLiveKernel<<<grid, 256, 0, s>>>(view, pairs, counter);
+    kvcm::ResetSlotsKernel<<<grid, 256, 0, s>>>(view);
+    kvcm::ReinsertKernel<<<grid, 256, 0, s>>>(view, pairs, counter, d_status);
+    ix->tomb_debt = 0;
+    return kvcm::LaunchStatus();
+}
+
+static int32_t UpdateStatus(kvcm_b200_index_t *ix, const int64_t *d_keys, const uint32_t *d_tasks, uint32_t uniform_task,
+                            int64_t n, kvcm::Shard shard, int32_t *d_results, kvcm_stream_t stream) {
+    if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (n < 0) return KVCM_EC_BADARGS;
+    if (d_tasks == nullptr) {
+        const uint32_t cls = uniform_task & 0xFFu, expected = (uniform_task >> 8) & 0xFFu,
+                       next = (uniform_task >> 16) & 0xFFu;
+        if (cls > 7 || (expected > 4 && expected != KVCM_STATUS_ANY) ||
+            (next > 4 && next != KVCM_STATUS_DELETE && next != KVCM_STATUS_DELETE_KEEP_KEY)) {
+            return KVCM_EC_BADARGS;
+        }
+    }
+    if (n == 0) return KVCM_OK;
+    if (d_keys == nullptr || d_results == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    ix->tomb_debt += static_cast<uint64_t>(n);  // any of the tasks may remove its key's last location
+    kvcm::UpdateStatusKernel<<<kvcm::GridFor(n, 256), 256, 0, kvcm::AsStream(stream)>>>(
+        kvcm::LocalView(ix), d_keys, d_tasks, uniform_task, n, shard, d_results);
+    return kvcm::LaunchStatus();
+}
+
+int32_t kvcm_b200_index_update_status(kvcm_b200_index_t *ix, const int64_t *d_keys, const uint32_t *d_tasks,
+                                      uint32_t uniform_task, int64_t n, int32_t *d_results, kvcm_stream_t stream) {
+    return UpdateStatus(ix, d_keys, d_tasks, uniform_task, n, kvcm::Shard{1, 0}, d_results, stream);
+}
+
+int32_t kvcm_b200_index_update_status_sharded(kvcm_b200_index_t *ix, const int64_t *d_keys, const uint32_t *d_tasks,
+                                              uint32_t uniform_task, int64_t n, int32_t shard_count, int32_t shard_rank,
+                                              int32_t *d_results, kvcm_stream_t stream) {
+    if (shard_count < 1 || shard_rank < 0 || shard_rank >= shard_count) return KVCM_EC_BADARGS;
+    return UpdateStatus(ix, d_keys, d_tasks, uniform_task, n,
+                        kvcm::Shard{static_cast<uint32_t>(shard_count), static_cast<uint32_t>(shard_rank)}, d_results,
+                        stream);
+}
+
 int32_t kvcm_b200_index_upsert(kvcm_b200_index_t *ix, const int64_t *d_keys, const uint64_t *d_values,
                                uint64_t uniform_value, int64_t n, uint32_t *d_status, kvcm_stream_t stream) {
     if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
     if (n < 0) return KVCM_EC_BADARGS;
     if (n == 0) return KVCM_OK;
     if (d_keys == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    MaybeRehash(ix, stream);
     kvcm::UpsertKernel<<<kvcm::GridFor(n, 256), 256, 0, kvcm::AsStream(stream)>>>(
         kvcm::LocalView(ix), d_keys, d_values, uniform_value, n, kvcm::Shard{1, 0}, d_status);
     return kvcm::LaunchStatus();
@@ -843,6 +1148,7 @@ int32_t kvcm_b200_index_upsert_sharded(kvcm_b200_index_t *ix, const int64_t *d_k
     if (n < 0 || shard_count < 1 || shard_rank < 0 || shard_rank >= shard_count) return KVCM_EC_BADARGS;
     if (n == 0) return KVCM_OK;
     if (d_keys == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    MaybeRehash(ix, stream);
     kvcm::UpsertKernel<<<kvcm::GridFor(n, 256), 256, 0, kvcm::AsStream(stream)>>>(
         kvcm::LocalView(ix), d_keys, d_values, uniform_value, n,
         kvcm::Shard{static_cast<uint32_t>(shard_count), static_cast<uint32_t>(shard_rank)}, d_status);
@@ -854,6 +1160,7 @@ int32_t kvcm_b200_index_erase(kvcm_b200_index_t *ix, const int64_t *d_keys, int6
     if (n < 0) return KVCM_EC_BADARGS;
     if (n == 0) return KVCM_OK;
     if (d_keys == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    ix->tomb_debt += static_cast<uint64_t>(n);
     kvcm::EraseKernel<<<kvcm::GridFor(n, 256), 256, 0, kvcm::AsStream(stream)>>>(kvcm::LocalView(ix), d_keys, n);
     return kvcm::LaunchStatus();
 }

@@ -98,16 +98,9 @@ __global__ void __launch_bounds__(32)
     while (true) {
         const int s = k % kBulkStages;
         if (!live[s]) break;
-        if (lane == 0) {
-            uint32_t spins = 0;
-            while (!MbarTryWait(SmemAddr(&bars[s]), (k / kBulkStages) & 1u)) {
-                if (++spins >= kSpinLimit) {
-                    failed = true;
-                    break;
-                }
-            }
-        }
+        if (lane == 0) failed = !BoundedWait(SmemAddr(&bars[s]), (k / kBulkStages) & 1u);
         failed = __shfl_sync(0xffffffffu, failed ? 1 : 0, 0) != 0;
+        __syncwarp();
         if (failed) break;
         if (lane == 0 && items[s].bulk_len > 0) BulkStore(items[s].dst, ring_base + s * chunk_bytes, items[s].bulk_len);
         BulkCommit();
@@ -117,6 +110,13 @@ __global__ void __launch_bounds__(32)
         __syncwarp();
         load((k + kBulkStages - 1) % kBulkStages);
         ++k;
+    }
+    if (failed && lane == 0) {
+        // Leave no copy in flight behind: the loads of the chunk that was waited for and of the chunks fetched
+        // ahead may still be writing this CTA's shared memory; one more bounded wait for each of them.
+        for (uint32_t j = k; j < k + kBulkStages - 1; ++j) {
+            if (live[j % kBulkStages]) BoundedWait(SmemAddr(&bars[j % kBulkStages]), (j / kBulkStages) & 1u);
+        }
     }
     BulkWaitAll();
     if (failed && lane == 0) atomicAdd(&g_copy_wait_timeouts, 1u);

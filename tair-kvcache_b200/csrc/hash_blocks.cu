@@ -171,18 +171,6 @@ __device__ __forceinline__ LaneSpan<T> DescribeLane(const T *tokens, int64_t n_t
     return s;
 }
 
-// kRelaxed: the waiter is far ahead of what it waits for (the producer), so it sleeps between polls
-// instead of taking issue slots from the chains.
-template <bool kRelaxed = false>
-__device__ __forceinline__ bool BoundedWait(uint32_t bar, uint32_t parity) {
-    uint32_t spins = 0;
-    while (!MbarTryWait(bar, parity)) {
-        if (++spins >= kSpinLimit) return false;
-        if (kRelaxed) __nanosleep(256);
-    }
-    return true;
-}
-
 template <typename T, bool kAligned>
 __global__ void __launch_bounds__(2 * kMaxWarpsPerCta * 32)
     HashBlocksKernel(const T *__restrict__ tokens, int64_t n_tokens_total, const int64_t *__restrict__ tok_off,

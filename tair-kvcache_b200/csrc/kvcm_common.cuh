@@ -20,6 +20,7 @@ struct DeviceInfo {
     bool ok = false;
 };
 
+// Properties of the device that is current for the calling thread (kept per device after the first query).
 const DeviceInfo &GetDeviceInfo();
 
 inline cudaStream_t AsStream(kvcm_stream_t s) { return static_cast<cudaStream_t>(s); }
@@ -92,6 +93,22 @@ __device__ __forceinline__ bool MbarTryWait(uint32_t bar, uint32_t parity) {
         : "r"(bar), "r"(parity)
         : "memory");
     return ok != 0;
+}
+// The one wait loop of every kernel that waits on an mbarrier: polls until the phase with `parity` completes,
+// at most `limit` times.  false = gave up; the caller then raises its error word, waits (again bounded) for the
+// copies it may still have in flight, and returns.  kRelaxed: the waiter is far ahead of what it waits for, so
+// it sleeps between polls instead of taking issue slots from the warps that do the work.
+template <bool kRelaxed = false>
+__device__ __forceinline__ bool BoundedWait(uint32_t bar, uint32_t parity, uint32_t limit = kSpinLimit) {
+    uint32_t polls = 0;
+    while (!MbarTryWait(bar, parity)) {
+        if (++polls >= limit) return false;
+        if (kRelaxed) __nanosleep(256);
+    }
+    return true;
+}
+__device__ __forceinline__ void MbarInval(uint32_t bar) {
+    asm volatile("mbarrier.inval.shared::cta.b64 [%0];\n" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void BulkLoad(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(

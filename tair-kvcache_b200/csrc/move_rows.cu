@@ -346,20 +346,16 @@ __global__ void __launch_bounds__(32) MoveRowsBulkKernel(const MoveParams p) {
     const uint32_t ahead = n_stages - 1;
     for (uint32_t k = 0; k < ahead && k < n_my; ++k) load(k);
     bool failed = false;
+    uint32_t fail_k = 0;
     for (uint32_t k = 0; k < n_my; ++k) {
         const uint32_t s = k % n_stages;
-        if (lane == 0) {
-            const uint32_t parity = (k / n_stages) & 1u;
-            uint32_t spins = 0;
-            while (!MbarTryWait(SmemAddr(&bars[s]), parity)) {
-                if (++spins >= kSpinLimit) {
-                    failed = true;
-                    break;
-                }
-            }
-        }
+        if (lane == 0) failed = !BoundedWait(SmemAddr(&bars[s]), (k / n_stages) & 1u);
         failed = __shfl_sync(0xffffffffu, failed ? 1 : 0, 0) != 0;
-        if (failed) break;
+        __syncwarp();  // the lanes that store out of the stage are ordered after the poll that saw it filled
+        if (failed) {
+            fail_k = k;
+            break;
+        }
         store(k);
         if (k + ahead < n_my) {
             // The stage about to be refilled was drained by the stores of chunk k-1: every lane
@@ -367,6 +363,13 @@ __global__ void __launch_bounds__(32) MoveRowsBulkKernel(const MoveParams p) {
             BulkWaitRead<1>();
             __syncwarp();
             load(k + ahead);
+        }
+    }
+    if (failed && lane == 0) {
+        // Leave no copy in flight behind: the loads of the chunk that was waited for and of the chunks fetched
+        // ahead may still be writing this CTA's shared memory; one more bounded wait for each of them.
+        for (uint32_t k = fail_k; k < n_my && k < fail_k + n_stages - 1; ++k) {
+            BoundedWait(SmemAddr(&bars[k % n_stages]), (k / n_stages) & 1u);
         }
     }
     BulkWaitAll();

@@ -16,7 +16,10 @@ def encode_locations(locations: Iterable[Tuple[int, int]]) -> int:
 
     Bit c: a CLS_SERVING location of class c; bit 16+c: a location of class c whose status is not
     CLS_NOT_FOUND; bit 32: the map is non-empty.  These are exactly the facts SelectForMatch and
-    ExistsForWrite (kv_cache_manager/manager/select_location_policy.cc:8-38) read."""
+    ExistsForWrite (kv_cache_manager/manager/select_location_policy.cc:8-38) read.  For classes 0..7 the
+    word also carries the status itself (three bits per class, status + 1), which is what
+    BlockIndex.update_status compares and rewrites; when a map holds several locations of one class the
+    field keeps the first one's status and the key should be maintained with upsert only."""
     word = 0
     for status, cls in locations:
         c = min(max(int(cls), 0), 15)
@@ -25,7 +28,20 @@ def encode_locations(locations: Iterable[Tuple[int, int]]) -> int:
             word |= 1 << c
         if status != CLS_NOT_FOUND:
             word |= 1 << (16 + c)
+        shift = _cabi.VAL_STATUS_SHIFT + 3 * c
+        if c < 8 and not (word >> shift) & 7:
+            word |= (int(status) + 1) << shift
     return word
+
+
+def status_task(storage_class: int, expected: Optional[int], new_status: Optional[int], keep_key: bool = False) -> int:
+    """One task of BlockIndex.update_status: the location of `storage_class` goes from `expected` (None = whatever
+    it is) to `new_status` (None = the location is deleted; with `keep_key` the way BatchDeleteLocation deletes,
+    which leaves an emptied key in the index and takes an absent key for done)."""
+    e = _cabi.STATUS_ANY if expected is None else int(expected)
+    n = int(new_status) if new_status is not None else (
+        _cabi.STATUS_DELETE_KEEP_KEY if keep_key else _cabi.STATUS_DELETE)
+    return int(storage_class) | (e << 8) | (n << 16)
 
 
 def avail_mask_from_weights(weights: Sequence[int], default_weight: int = 1) -> int:
@@ -83,6 +99,48 @@ class BlockIndex:
         slots, live = ctypes.c_int64(), ctypes.c_int64()
         _cabi.call("kvcm_b200_index_stats", self._h, ctypes.byref(slots), ctypes.byref(live), self._s())
         return slots.value, live.value
+
+    def usage(self):
+        """(slots, live keys, slots in use = live keys + tombstones of erased keys)."""
+        slots, live, used = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64()
+        _cabi.call("kvcm_b200_index_usage", self._h, ctypes.byref(slots), ctypes.byref(live), ctypes.byref(used),
+                   self._s())
+        return slots.value, live.value, used.value
+
+    def rehash(self, status: Optional[torch.Tensor] = None):
+        """Rebuilds the table in place without the tombstones erased keys left behind."""
+        need = int(_cabi.lib().kvcm_b200_index_rehash_workspace_bytes(self._h))
+        workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
+        _cabi.call("kvcm_b200_index_rehash", self._h, workspace.data_ptr(), need,
+                   status.data_ptr() if status is not None else None, self._s())
+        workspace.record_stream(torch.cuda.current_stream(self.device))
+
+    def update_status(self, keys: torch.Tensor, tasks, shard: Optional[Tuple[int, int]] = None,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Location-status transitions on the device (MetaSearcher::BatchUpdateLocationStatus / BatchCASLocationStatus /
+        BatchCADLocationStatus / BatchDeleteLocation, kv_cache_manager/manager/meta_searcher.cc:410-820).  `tasks`: one
+        status_task() word for all keys, or an int32 CUDA tensor with one word per key.  Returns the int32 result
+        code per key (0, KVCM_EC_NOENT, KVCM_EC_MISMATCH, KVCM_EC_BADARGS).  shard=(count, rank) limits the call to
+        the keys this shard owns."""
+        keys = _keys(keys, self.device)
+        if out is None:
+            out = torch.zeros(keys.numel(), dtype=torch.int32, device=self.device)
+        d_tasks, uniform = None, 0
+        if isinstance(tasks, torch.Tensor):
+            d_tasks = tasks.to(torch.int32).contiguous()
+            if d_tasks.numel() != keys.numel() or d_tasks.device != self.device:
+                raise ValueError("one task word per key, on the index's device")
+        else:
+            uniform = int(tasks)
+        if shard is None:
+            _cabi.call("kvcm_b200_index_update_status", self._h, keys.data_ptr(),
+                       d_tasks.data_ptr() if d_tasks is not None else None, uniform, keys.numel(), out.data_ptr(),
+                       self._s())
+        else:
+            _cabi.call("kvcm_b200_index_update_status_sharded", self._h, keys.data_ptr(),
+                       d_tasks.data_ptr() if d_tasks is not None else None, uniform, keys.numel(), shard[0], shard[1],
+                       out.data_ptr(), self._s())
+        return out
 
     def upsert(self, keys: torch.Tensor, values: Optional[torch.Tensor] = None, uniform_value: int = 0,
                status: Optional[torch.Tensor] = None):

@@ -398,3 +398,30 @@ def test_token_lists_made_of_page_runs_take_the_page_path():
             oracle.move_rows(wantp, want, idx.astype(np.int32), slots, T, tok_bytes, 1, threads=4)
             for z, w in zip(zero, wantp):
                 assert np.array_equal(z.cpu().numpy(), w), (name, staging_on)
+
+
+def test_bounded_wait_gives_up_reports_and_leaves_the_context_usable():
+    """The give-up path of the kernels' mbarrier waits, run once in a form with nothing in flight: a barrier armed
+    for bytes that are never sent, polled through the shared helper with a limit of a few polls.  The call comes
+    back at once with the status words set, and the next gather is bit-exact."""
+    import time
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    _cabi.bind_device(0)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    _cabi.call("kvcm_b200_selftest_bounded_wait", 64, status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 1.0
+    assert status.cpu().tolist()[:2] == [1, 64]          # gave up after exactly the polls it was allowed
+    for bad in (0, 1 << 20):
+        assert _cabi.lib().kvcm_b200_selftest_bounded_wait(bad, status.data_ptr(), None) == _cabi.KVCM_ER_INVALID_PARAMS
+    # the context is intact: a gather on the bulk-copy ring right after it, against the oracle
+    host, dev, ptrs = _make(4, 4, 64, 16 * 2048)
+    table = np.random.default_rng(0).permutation(64)[:32].astype(np.int32)
+    staging = torch.zeros(8 * 4 * 4 * 16 * 2048, dtype=torch.uint8, device=DEV)
+    st = torch.zeros(4, dtype=torch.int32, device=DEV)
+    batch_gather_kv_pages(ptrs, staging, torch.from_numpy(table), None, 4, 16 * 2048, 64, status=st)
+    torch.cuda.synchronize()
+    want = np.zeros(staging.numel(), dtype=np.uint8)
+    oracle.move_rows(_np(host), want, table, None, 4, 16 * 2048, 0)
+    assert np.array_equal(staging.cpu().numpy(), want) and st.cpu().tolist()[2] == 0

@@ -362,3 +362,21 @@ def test_lru_group_quota_shared_by_two_instances():
         b = oracle.LruGroupReplay(30, 1, evict_batch=3, mode=mode).run(k, o, ty, [0] * 100)
         for x, y in zip(a, b):
             assert np.array_equal(x, y)
+
+
+def test_location_status_cases_of_the_reference_tests():
+    """Update / compare-and-set / compare-and-delete / delete of location statuses, replayed from the tables of
+    kv_cache_manager/manager/test/meta_searcher_test.cc (tests/golden/status_kat.json)."""
+    from conftest import load_golden
+    for case in load_golden("status_kat.json")["cases"]:
+        ix = oracle.Index()
+        keys0 = [int(k) for k in case["initial"]]
+        ix.put(keys0, [[tuple(l) for l in case["initial"][str(k)]] for k in keys0])
+        for step in case["steps"]:
+            got = ix.update_status(step["keys"], step["types"], step["expected"], step["new"])
+            assert got.tolist() == step["results"], case["name"]
+            for k, want in step["after"].items():
+                have = ix.get(int(k))
+                assert (have is None) == (want is None), case["name"]
+                if want is not None:
+                    assert sorted(have) == sorted(tuple(l) for l in want), case["name"]

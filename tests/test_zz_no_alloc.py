@@ -4,11 +4,17 @@ An engine plugin that runs after the engine has taken almost all of HBM cannot c
 succeeding (and a successful one stalls the engine's streams), so this entry point keeps its scratch table
 in a fixed array inside the library.  The test drives it through the C ABI only and checks, twice in a row
 with different traces, that it returns exactly what kvcm_b200_replay returns with caller-provided scratch -
-the second call runs over whatever the first one left in the shared array.
+the second call runs over whatever the first one left in the shared array - and what the CPU oracle's
+sequential prefix-tree replay returns for the same traces.  It also reads the device's free memory before and
+after the second call: the entry point exists for callers that must not allocate, so the figure may not move.
 """
+import ctypes
+
 import numpy as np
 import pytest
 import torch
+
+from oracle import kvcm_oracle as oracle
 
 import tair_kvcache_b200  # noqa: F401
 from tair_kvcache_b200 import _cabi
@@ -42,7 +48,13 @@ def _outputs(n):
            [torch.full((max(n, 1),), -7, dtype=torch.int64, device=DEV)]
 
 
-def _run_both(seed, n_traces):
+def _free_bytes():
+    free = ctypes.c_int64()
+    _cabi.call("kvcm_b200_device_info", None, None, ctypes.byref(free), None)
+    return free.value
+
+
+def _run_both(seed, n_traces, check_free=False):
     keys, off, types, mask = _traces(seed, n_traces)
     d = [torch.from_numpy(a).to(DEV) for a in (keys, off, types, mask)]
     stream = torch.cuda.current_stream().cuda_stream
@@ -56,12 +68,20 @@ def _run_both(seed, n_traces):
     # new entry point, nothing allocated by the library
     got = _outputs(n_traces)
     status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    torch.cuda.synchronize()
+    free_before = _free_bytes()
     _cabi.call("kvcm_b200_replay_noalloc", d[0].data_ptr(), d[1].data_ptr(), d[2].data_ptr(), d[3].data_ptr(),
                n_traces, len(keys), got[0].data_ptr(), got[1].data_ptr(), got[2].data_ptr(), got[3].data_ptr(),
                status.data_ptr(), stream)
     torch.cuda.synchronize()
-    for g, w, name in zip(got, want, ["external hits", "internal hits", "written blocks", "cache size"]):
+    if check_free:  # the device's set-up happened in an earlier call: this one may not take a byte
+        assert _free_bytes() == free_before
+    names = ["external hits", "internal hits", "written blocks", "cache size"]
+    for g, w, name in zip(got, want, names):
         assert torch.equal(g[:n_traces], w[:n_traces]), name  # integer results: exact equality
+    cpu = oracle.Replay().run(keys, off, types, mask_off=mask)
+    for g, c, name in zip(got, cpu, names):
+        assert np.array_equal(g[:n_traces].cpu().numpy(), c), name + " (oracle)"
     assert status[0].item() == 0
     assert int(want[0].sum()) > 0 and int(want[2].sum()) > 0
     return len(keys)
@@ -69,7 +89,7 @@ def _run_both(seed, n_traces):
 
 def test_noalloc_replay_equals_replay_on_two_calls_in_a_row():
     n1 = _run_both(seed=1, n_traces=4000)   # ~118k keys: most of the fixed table
-    n2 = _run_both(seed=2, n_traces=700)    # smaller table laid over the first call's leftovers
+    n2 = _run_both(seed=2, n_traces=700, check_free=True)  # smaller table laid over the first call's leftovers
     assert n2 < n1 <= _cabi.REPLAY_NOALLOC_MAX_KEYS
 
 
