@@ -219,7 +219,12 @@ KVCM_API int32_t kvcm_b200_copy_segments_sized(const kvcm_b200_seg_t *d_segs, in
 KVCM_API int32_t kvcm_b200_copy_wait_timeouts(uint32_t *h_count_out);
 /* Host-only: direction 0 = iovs -> block string (Put), 1 = block string -> iovs (Get).  Writes at
  * most n_iovs segments to h_segs_out, returns their number in *n_segs_out and the bytes the iov
- * list spans in *span_bytes_out. */
+ * list spans in *span_bytes_out.  Every address it emits is one a kernel may touch: an iov of type CPU
+ * is accepted only when the driver knows its base as pinned, registered, managed or device memory;
+ * ordinary pageable memory - which the reference copies with std::memcpy
+ * (kv_cache_manager/client/src/internal/sdk/local_file_sdk.cc:231-233, 339-341) - returns
+ * KVCM_ER_UNSUPPORTED_MEMORY_TYPE before anything is launched.  A caller with such iovs copies them on
+ * the host and passes them with `ignore` set, as the IovCopier adapter does. */
 KVCM_API int32_t kvcm_b200_iovs_to_segments(const kvcm_b200_iov_t *h_iovs, int32_t n_iovs, void *block_string,
                                             int32_t direction, kvcm_b200_seg_t *h_segs_out, int32_t *n_segs_out,
                                             uint64_t *span_bytes_out);

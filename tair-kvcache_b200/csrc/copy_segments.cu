@@ -239,6 +239,18 @@ int32_t kvcm_b200_iovs_to_segments(const kvcm_b200_iov_t *h_iovs, int32_t n_iovs
         if (iov.type > 1) return KVCM_ER_UNSUPPORTED_MEMORY_TYPE;
         if (!iov.ignore && iov.base != nullptr && iov.size > 0) {
             if (str == nullptr) return KVCM_ER_INVALID_ADDRESS;
+            if (iov.type == 0) {
+                // A CPU iov goes into the table only if a kernel can address it: pinned or registered host
+                // memory (or memory the driver knows as device / managed).  Ordinary pageable memory - what the
+                // reference copies with std::memcpy - is refused here, before any launch; the caller moves such
+                // iovs on the host (IovCopier does) and marks them `ignore`.
+                cudaPointerAttributes attr;
+                if (cudaPointerGetAttributes(&attr, iov.base) != cudaSuccess) {
+                    cudaGetLastError();
+                    return KVCM_ER_UNSUPPORTED_MEMORY_TYPE;
+                }
+                if (attr.type == cudaMemoryTypeUnregistered) return KVCM_ER_UNSUPPORTED_MEMORY_TYPE;
+            }
             kvcm_b200_seg_t &seg = h_segs_out[n++];
             seg.bytes = iov.size;
             if (direction == 0) {

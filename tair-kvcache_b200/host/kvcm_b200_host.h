@@ -563,20 +563,36 @@ public:
     // host memory that is pinned or registered with cudaHostRegister (as the reference's LocalFileSdk does for its
     // mmap); pageable host memory is refused.  Asynchronous on the adapter's stream; the caller keeps the
     // reference's single cudaStreamSynchronize.  *span_bytes = bytes the iov list covers.  Bytes of block_string
-    // under ignored, null or empty iovs are never written.
+    // under ignored, null or empty iovs are never written.  An iov of MemoryType::CPU in ordinary (pageable)
+    // memory is moved on the host as the reference moves it and never reaches a kernel; a CPU iov in pinned or
+    // registered memory is copied by the kernel like a GPU iov.
     int32_t CopyIovs(const BlockBuffer &buffer, void *block_string, int direction, uint64_t *span_bytes) {
         const int32_t n = static_cast<int32_t>(buffer.iovs.size());
         if (span_bytes) *span_bytes = 0;
         if (n == 0) return KVCM_OK;
         if (direction != 0 && direction != 1) return KVCM_ER_INVALID_PARAMS;
         std::vector<kvcm_b200_iov_t> iovs(n);
+        std::vector<uint8_t> on_host(n, 0);  // CPU iovs in pageable memory: moved here, never shown to a kernel
         uint64_t span = 0;
+        bool any_on_host = false;
         for (int32_t i = 0; i < n; ++i) {
             iovs[i].type = static_cast<uint8_t>(buffer.iovs[i].type);
             iovs[i].ignore = buffer.iovs[i].ignore ? 1 : 0;
             iovs[i].base = buffer.iovs[i].base;
             iovs[i].size = buffer.iovs[i].size;
             span += buffer.iovs[i].size;
+            if (buffer.iovs[i].type == MemoryType::CPU && !buffer.iovs[i].ignore && buffer.iovs[i].base != nullptr &&
+                buffer.iovs[i].size > 0) {
+                cudaPointerAttributes a{};
+                if (cudaPointerGetAttributes(&a, buffer.iovs[i].base) != cudaSuccess) {
+                    cudaGetLastError();
+                    a.type = cudaMemoryTypeUnregistered;
+                }
+                if (a.type == cudaMemoryTypeUnregistered) {
+                    on_host[i] = 1;
+                    any_on_host = true;
+                }
+            }
         }
         bool host_string = false;
         if (block_string != nullptr) {
@@ -587,6 +603,34 @@ public:
             }
             if (attr.type == cudaMemoryTypeUnregistered) return KVCM_ER_UNSUPPORTED_MEMORY_TYPE;
             host_string = attr.type == cudaMemoryTypeHost;
+        }
+        if (any_on_host) {
+            // What the reference does for MemoryType::CPU (kv_cache_manager/client/src/internal/sdk/
+            // local_file_sdk.cc:231-233,339-341): std::memcpy when the block string is host memory too; with a
+            // device string the bytes cross with cudaMemcpyAsync on the adapter's stream (the driver stages
+            // pageable memory itself).  These iovs are then hidden from the kernel's table.
+            if (block_string == nullptr) return KVCM_ER_INVALID_ADDRESS;
+            uint64_t at = 0;
+            for (int32_t i = 0; i < n; ++i) {
+                if (on_host[i]) {
+                    uint8_t *in_string = static_cast<uint8_t *>(block_string) + at;
+                    if (host_string) {
+                        if (direction == 0) {
+                            std::memcpy(in_string, iovs[i].base, iovs[i].size);
+                        } else {
+                            std::memcpy(iovs[i].base, in_string, iovs[i].size);
+                        }
+                    } else if ((direction == 0 ? cudaMemcpyAsync(in_string, iovs[i].base, iovs[i].size,
+                                                                 cudaMemcpyHostToDevice, stream_)
+                                               : cudaMemcpyAsync(iovs[i].base, in_string, iovs[i].size,
+                                                                 cudaMemcpyDeviceToHost, stream_)) != cudaSuccess) {
+                        cudaGetLastError();
+                        return KVCM_ER_CUDAMEMCPY_ERROR;
+                    }
+                    iovs[i].ignore = 1;
+                }
+                at += iovs[i].size;
+            }
         }
         // The pinned segment table and the bounce buffer are reused: wait until the previous call is through.
         if (cudaEventSynchronize(staged_) != cudaSuccess) return KVCM_ER_CUDA_STREAM_SYNCHRONIZE_ERROR;

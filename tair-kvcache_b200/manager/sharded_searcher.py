@@ -292,7 +292,15 @@ class ShardedMetaSearcher:
               area: int = 0) -> RoutedFlags:
         """Dispatch this rank's keys to their owners, look them up there, combine the answers back in key order.
         `area` (mode "route_peer") picks the exchange area: batches in flight at once use different ones, and
-        every rank routes its batches in the same order."""
+        every rank routes its batches in the same order.
+
+        Stream rule: the whole call runs on torch's CURRENT stream.  The kernels are launched on it, and the
+        collectives between them are enqueued by torch.distributed, which orders NCCL's work after and before the
+        current stream only; that ordering is all that keeps "dispatch | answer | collect" apart (a peer's keys
+        have landed before this rank answers, its answers have landed before this rank collects).  A caller that
+        wants two batches in flight wraps each call in `with torch.cuda.stream(s):` and gives each its own area;
+        launching the kernels on any other stream than the current one would let an answer run ahead of the
+        keys it answers."""
         keys, key_off = keys.contiguous(), key_off.contiguous()
         counts = self.backend.route_count(keys, self.world)
         matrix = torch.empty(self.world * self.world, dtype=torch.int32, device=self.device)

@@ -56,6 +56,7 @@ def replay_instance(traces: List[tr.Trace], device, rw_separation: bool = False,
     if quota_blocks is None:
         return record(*(x.cpu().numpy() for x in RunTraces(d_keys, d_off, d_kind, d_mask, mask_bits=d_bits)))
     quotas = [int(quota_blocks)] if np.isscalar(quota_blocks) else [int(q) for q in quota_blocks]
+    tr.require_no_repeats(keep, keys, off)
     res = [x.cpu().numpy() for x in RunTracesLru(d_keys, d_off, d_kind, quotas, d_mask, evict_batch, precise,
                                                  mask_bits=d_bits, policy=policy,
                                                  timestamps=torch.from_numpy(ts).to(device))[:4]]
@@ -91,6 +92,7 @@ def replay_group(traces: List[tr.Trace], instance_ids: Sequence[str], device, qu
     inst = np.array([index[t.instance_id] for t in keep], dtype=np.int32)
     ts = np.array([t.timestamp_us for t in keep], dtype=np.int64)
     bits = tr.mask_bits(keep, off)
+    tr.require_no_repeats(keep, keys, off)
     res = RunTracesLruGroup(d_keys, d_off, torch.from_numpy(kind).to(device), torch.from_numpy(inst).to(device),
                             len(instance_ids), [int(quota_blocks)], torch.from_numpy(mask).to(device), evict_batch,
                             mode, mask_bits=torch.from_numpy(bits).to(device) if bits is not None else None)
@@ -117,6 +119,7 @@ def sweep_hit_rates(traces: List[tr.Trace], device, quota_blocks: Sequence[int],
     if any(t.needs_prefix_hash for t in keep):
         d_keys = ApplyPrefixHashBatch(d_keys, d_off)
     bits = tr.mask_bits(keep, off)
+    tr.require_no_repeats(keep, keys, off)
     res = RunTracesLru(d_keys, d_off, torch.from_numpy(kind).to(device), [int(q) for q in quota_blocks],
                        torch.from_numpy(mask).to(device), evict_batch, precise, per_trace=False,
                        mask_bits=torch.from_numpy(bits).to(device) if bits is not None else None, policy=policy,

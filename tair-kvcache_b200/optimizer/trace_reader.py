@@ -222,3 +222,29 @@ def to_csr(traces: Sequence[Trace]):
     read = np.array([len(t.keys) if t.kind != WRITE_CACHE else 0 for t in traces], dtype=np.int64)
     flat = np.concatenate(keys) if keys else np.zeros(0, dtype=np.int64)
     return flat, off, kind, mask, read
+
+
+def first_repeat_within_a_trace(keys: np.ndarray, key_off: np.ndarray) -> Optional[int]:
+    """Index of a trace in which some key occurs twice, or None.  The eviction-aware replays keep one state per key
+    and configuration and walk a trace 32 keys at a time, which is only the reference's tree
+    (kv_cache_manager/optimizer/index/radix_tree_index.cc:19-60) when no key repeats inside a trace.  Chained
+    hashes never do; keys taken verbatim from a trace file can."""
+    n = len(keys)
+    if n < 2:
+        return None
+    trace_of = np.repeat(np.arange(len(key_off) - 1, dtype=np.int64), np.diff(key_off))
+    order = np.lexsort((trace_of, keys))  # by key, ties by trace: two occurrences in one trace end up adjacent
+    k, t = keys[order], trace_of[order]
+    hit = np.flatnonzero((k[1:] == k[:-1]) & (t[1:] == t[:-1]))
+    return int(t[hit[0]]) if hit.size else None
+
+
+def require_no_repeats(traces: Sequence[Trace], keys: np.ndarray, key_off: np.ndarray) -> None:
+    """Refuses, before anything is launched, verbatim keys that repeat inside one trace: the eviction-aware sweeps
+    would count such a block twice and return wrong curves without noticing."""
+    if all(t.needs_prefix_hash for t in traces):
+        return  # the chained hash makes every key of a trace distinct
+    bad = first_repeat_within_a_trace(np.asarray(keys, dtype=np.int64), np.asarray(key_off, dtype=np.int64))
+    if bad is not None:
+        raise NotImplementedError("trace %d names the same block key twice; the eviction-aware replay needs keys "
+                                  "that do not repeat inside a trace (chained block hashes never do)" % bad)

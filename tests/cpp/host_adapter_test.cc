@@ -181,6 +181,63 @@ static void TestIovCopier() {
     // pageable host memory is refused, not dereferenced
     std::vector<uint8_t> pageable(host.size());
     EXPECT_EQ(copier.CopyIovs(put, pageable.data(), 0, &span), KVCM_ER_UNSUPPORTED_MEMORY_TYPE);
+    // Iovs of MemoryType::CPU in ordinary malloc'ed memory (the reference copies those with std::memcpy,
+    // local_file_sdk.cc:231-233,339-341) mixed with GPU iovs: iovs 1 and 4 live on the host.  With a device
+    // string, with a pinned host string through the bounce buffer, and with the kernel on the host string itself.
+    std::vector<uint8_t> cpu_src(2 * sz), cpu_back(2 * sz);
+    std::memcpy(cpu_src.data(), host.data() + 1 * sz, sz);
+    std::memcpy(cpu_src.data() + sz, host.data() + 4 * sz, sz);
+    BlockBuffer mput = put, mget = get;
+    mput.iovs[1] = {MemoryType::CPU, cpu_src.data(), sz, false};
+    mput.iovs[4] = {MemoryType::CPU, cpu_src.data() + sz, sz, false};
+    mget.iovs[1] = {MemoryType::CPU, cpu_back.data(), sz, false};
+    mget.iovs[4] = {MemoryType::CPU, cpu_back.data() + sz, sz, false};
+    for (int mode = 0; mode < 3; ++mode) {
+        IovCopier mixed(nullptr, mode != 2);
+        uint8_t *string = mode == 0 ? d_string : h_string;
+        if (mode == 0) {
+            cudaMemset(d_string, 0xEE, host.size());
+        } else {
+            std::memset(h_string, 0xEE, host.size());
+        }
+        cudaMemset(d_back, 0, host.size());
+        std::fill(cpu_back.begin(), cpu_back.end(), 0);
+        EXPECT_EQ(mixed.CopyIovs(mput, string, 0, &span), KVCM_OK);
+        EXPECT_EQ(span, uint64_t(6 * sz));
+        cudaDeviceSynchronize();
+        std::vector<uint8_t> str(host.size());
+        cudaMemcpy(str.data(), string, str.size(), cudaMemcpyDefault);
+        for (int i = 0; i < 6; ++i) {
+            bool same = std::memcmp(str.data() + i * sz, host.data() + i * sz, sz) == 0;
+            bool kept = true;
+            for (size_t j = 0; j < sz; ++j) kept = kept && str[i * sz + j] == 0xEE;
+            EXPECT_EQ(i == 2 ? kept : same, true);
+        }
+        EXPECT_EQ(mixed.CopyIovs(mget, string, 1, &span), KVCM_OK);
+        cudaDeviceSynchronize();
+        cudaMemcpy(back.data(), d_back, back.size(), cudaMemcpyDeviceToHost);
+        for (int i = 0; i < 6; ++i) {
+            if (i == 1 || i == 4) {
+                EXPECT_EQ(std::memcmp(cpu_back.data() + (i == 1 ? 0 : sz), host.data() + i * sz, sz), 0);
+            } else if (i != 2) {
+                EXPECT_EQ(std::memcmp(back.data() + i * sz, host.data() + i * sz, sz), 0);
+            }
+        }
+    }
+    // the C entry point by itself never puts a pageable CPU base into a table a kernel would read
+    {
+        kvcm_b200_iov_t one{};
+        one.type = 0;
+        one.base = cpu_src.data();
+        one.size = sz;
+        kvcm_b200_seg_t seg{};
+        int32_t n_segs = -1;
+        EXPECT_EQ(kvcm_b200_iovs_to_segments(&one, 1, d_string, 0, &seg, &n_segs, nullptr),
+                  KVCM_ER_UNSUPPORTED_MEMORY_TYPE);
+        one.base = h_string;  // pinned: a kernel can address it
+        EXPECT_EQ(kvcm_b200_iovs_to_segments(&one, 1, d_string, 0, &seg, &n_segs, nullptr), KVCM_OK);
+        EXPECT_EQ(n_segs, 1);
+    }
     cudaFreeHost(h_string);
     cudaFree(d_src);
     cudaFree(d_string);

@@ -67,6 +67,25 @@ def test_iovs_to_segments_honours_ignore():
     assert segs[1].src == string.ctypes.data + 12 and segs[1].dst == bufs[2].ctypes.data
 
 
+def test_iovs_to_segments_refuses_pageable_cpu_iovs():
+    """An iov of MemoryType CPU in ordinary memory (which the reference copies with std::memcpy,
+    kv_cache_manager/client/src/internal/sdk/local_file_sdk.cc:231-233) never lands in a table a kernel reads."""
+    iovs = (_cabi.Iov * 2)()
+    gpu_like, cpu_buf = np.zeros(8, np.uint8), np.zeros(8, np.uint8)
+    for i, (b, ty, ign) in enumerate([(gpu_like, 1, 0), (cpu_buf, 0, 0)]):
+        iovs[i].type, iovs[i].ignore, iovs[i].base, iovs[i].size = ty, ign, b.ctypes.data, 8
+    segs = (_cabi.Seg * 2)()
+    n, span = ctypes.c_int32(), ctypes.c_uint64()
+    string = np.zeros(16, np.uint8)
+    rc = _cabi.lib().kvcm_b200_iovs_to_segments(ctypes.addressof(iovs), 2, string.ctypes.data, 0,
+                                                ctypes.addressof(segs), ctypes.addressof(n), ctypes.addressof(span))
+    assert rc == _cabi.KVCM_ER_UNSUPPORTED_MEMORY_TYPE
+    iovs[1].ignore = 1  # moved by the caller on the host: skipped, its bytes still counted in the span
+    _cabi.call("kvcm_b200_iovs_to_segments", ctypes.addressof(iovs), 2, string.ctypes.data, 0,
+               ctypes.addressof(segs), ctypes.addressof(n), ctypes.addressof(span))
+    assert (n.value, span.value) == (1, 16)
+
+
 def test_compute_entry_points_refuse_without_a_device():
     import torch
     if torch.cuda.is_available():

@@ -166,3 +166,19 @@ def test_shared_quota_groups_host_side(tmp_path, monkeypatch):
     cfg["eviction_params"]["eviction_mode"] = 2
     recs = runner.run_startup_config(cfg, device="cpu", rw_separation=True)
     assert recs["a"]["external_hit_blocks"].tolist() == [0, 3] and np.array_equal(recs["a"]["kind"], [2, 1])
+
+
+def test_a_key_repeated_inside_a_trace_is_found_before_any_launch():
+    import pytest
+    from tair_kvcache_b200.optimizer import trace_reader as tr
+    keys = np.array([5, 6, 7, 5, 8, 9, 8, 10, 6], dtype=np.int64)
+    assert tr.first_repeat_within_a_trace(keys, np.array([0, 3, 6, 9])) is None      # repeats only across traces
+    assert tr.first_repeat_within_a_trace(keys, np.array([0, 3, 7, 9])) == 1         # 8 twice in the second trace
+    assert tr.first_repeat_within_a_trace(keys[:1], np.array([0, 1])) is None
+    verbatim = [tr.Trace(kind=tr.GET_LOCATION, keys=[1, 2, 3]), tr.Trace(kind=tr.GET_LOCATION, keys=[4, 5, 4])]
+    k, off = tr.to_csr(verbatim)[:2]
+    with pytest.raises(NotImplementedError):
+        tr.require_no_repeats(verbatim, k, off)
+    hashed = [tr.Trace(kind=tr.DIALOG_TURN, keys=[4, 5, 4], needs_prefix_hash=True)]
+    k, off = tr.to_csr(hashed)[:2]
+    tr.require_no_repeats(hashed, k, off)  # ids that repeat are chained into distinct keys before the replay
