@@ -27,6 +27,11 @@ import time
 
 import numpy as np
 
+# The default of 8 hardware work queues per process lets two of this program's many CUDA streams (two per
+# end-to-end leg, two copy streams of the library, two of the two-stream match step) land on one queue, where their
+# kernels then run one after the other.  32 is the driver's maximum; it must be set before CUDA is initialised.
+os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)

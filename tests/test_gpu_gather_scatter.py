@@ -425,3 +425,43 @@ def test_bounded_wait_gives_up_reports_and_leaves_the_context_usable():
     want = np.zeros(staging.numel(), dtype=np.uint8)
     oracle.move_rows(_np(host), want, table, None, 4, 16 * 2048, 0)
     assert np.array_equal(staging.cpu().numpy(), want) and st.cpu().tolist()[2] == 0
+
+
+@pytest.mark.parametrize("use_mla", [False, True])
+def test_trtllm_block_major_layout(use_mla):
+    """The TensorRT-LLM connector's pool is ONE tensor [num_blocks, num_layers, kv_factor, block_size] with
+    block_size = kv heads x head size x tokens per block and kv_factor 1 under MLA
+    (kv_cache_manager/py_connector/trtllm/connector.py:173-179): a block is one contiguous row.  The reference saves
+    a block as `kv_cache_tensor[block_id].cpu()` handed over as one iov and loads it with
+    `kv_cache_tensor[block_id].copy_(cpu_tensor)` (:209-216, :261-279).  Here that is the page form with one pool,
+    one row per block and the block ids as the page table; the staged bytes must be those very tensors."""
+    num_blocks, num_layers, kv_factor = 96, 6, 1 if use_mla else 2
+    block_size = (1 * 576 if use_mla else 8 * 128) * 32          # elements: heads x head size x 32 tokens per block
+    gen = torch.Generator(device=DEV).manual_seed(17)
+    kv_cache_tensor = torch.randint(-(1 << 15), 1 << 15, (num_blocks, num_layers, kv_factor, block_size),
+                                    dtype=torch.int16, device=DEV, generator=gen).view(torch.bfloat16)
+    row_bytes = num_layers * kv_factor * block_size * 2          # the connector's location_spec_size
+    ptrs = torch.tensor([kv_cache_tensor.data_ptr()], dtype=torch.int64, device=DEV)
+    block_ids = [77, 3, 41, 42, 0, 95, 18]
+    # save: one staging slot per block, in pinned host memory
+    staged = torch.zeros(len(block_ids), num_layers, kv_factor, block_size, dtype=torch.bfloat16, pin_memory=True)
+    batch_gather_kv_pages(ptrs, staged, block_ids, None, 1, row_bytes, num_blocks)
+    torch.cuda.synchronize()
+    for slot, block_id in enumerate(block_ids):
+        cpu_tensor = kv_cache_tensor[block_id].cpu()             # what the reference hands to SaveKvCaches
+        assert torch.equal(staged[slot].view(torch.int16), cpu_tensor.view(torch.int16))
+    # load: into an engine pool that holds other bytes, through other block ids
+    target = torch.zeros_like(kv_cache_tensor)
+    tptrs = torch.tensor([target.data_ptr()], dtype=torch.int64, device=DEV)
+    new_ids = [5, 6, 90, 1, 50, 51, 52]
+    batch_scatter_kv_pages(tptrs, staged, new_ids, None, 1, row_bytes, num_blocks)
+    torch.cuda.synchronize()
+    want = torch.zeros_like(kv_cache_tensor)
+    for slot, block_id in enumerate(new_ids):
+        want[block_id].copy_(staged[slot])                       # the reference's load
+    assert torch.equal(target.view(torch.int16), want.view(torch.int16))
+    # the same bytes through the oracle's index rule
+    pool = kv_cache_tensor.view(torch.uint8).reshape(-1).cpu().numpy()
+    ref = np.zeros(len(block_ids) * row_bytes, dtype=np.uint8)
+    oracle.move_rows([pool], ref, np.array(block_ids, dtype=np.int32), None, 1, row_bytes, 0)
+    assert np.array_equal(staged.view(torch.uint8).reshape(-1).numpy(), ref)
