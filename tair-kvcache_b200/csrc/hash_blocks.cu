@@ -24,14 +24,26 @@ namespace {
 
 constexpr int kStageBytes = 64;            // bytes of one lane unpacked into registers at a time
 constexpr int kPieces = kStageBytes / 16;  // 128-bit shared loads per stage
-constexpr int kMinis = 4;                  // 64-byte stages per ring fill: one bulk copy brings 256 bytes of a request
 constexpr int kSlots = 3;                  // ring fills per warp: two in flight ahead of the one being hashed
-constexpr int kLaneStride = kMinis * kStageBytes + 16;  // an odd number of 16-byte words
-constexpr int kWarpRingBytes = kSlots * 32 * kLaneStride;  // 25.5 KiB
 constexpr int kMaxWarpsPerCta = 4;         // consumer warps; a CTA has as many producer warps again
 constexpr int kMaxHashSmemPerSm = 224 * 1024;
-// Consumer warps that fit on an SM (1 KiB of shared memory per CTA goes to the system).
-constexpr int kResidentWarpsPerSm = kMaxHashSmemPerSm / (kWarpRingBytes + 1024);
+// Ring geometry for fills of kMinis 64-byte stages per lane: one bulk copy brings kMinis x 64 bytes of a request.
+// A bulk copy costs its issuing lane the same ~54 cycles whatever its size (measured, 256 B to 2 KiB), so a warp
+// fills a slot in ~1,700 cycles.  A chain that runs at ~21 cycles per token eats 64 tokens in ~1,350 cycles: with
+// 256-byte fills the producer would hold it back, with 512-byte fills (kMinis = 8) it does not.  Launches ruled by
+// their longest chains take kMinis = 8; launches with many warps per SM, ruled by the integer pipe, keep
+// kMinis = 4, whose smaller ring lets twice as many warps stay resident.
+template <int kMinis>
+struct RingGeo {
+    static constexpr int kLaneStride = kMinis * kStageBytes + 16;  // an odd number of 16-byte words
+    static constexpr int kFillBytes = kMinis * kStageBytes;        // bytes of one lane in one ring slot
+    static constexpr int kSlotBytes = 32 * kLaneStride;            // one ring slot of a warp
+    static constexpr int kWarpRingBytes = kSlots * kSlotBytes;     // 25.5 KiB (kMinis 4), 49.5 KiB (kMinis 8)
+    // Consumer warps that fit on an SM (1 KiB of shared memory per CTA goes to the system).
+    static constexpr int kResidentWarpsPerSm = kMaxHashSmemPerSm / (kWarpRingBytes + 1024);
+    static_assert(kMinis % 2 == 0 && (kLaneStride / 16) % 2 == 1, "ring geometry");
+};
+constexpr int kShallowMinis = 4, kDeepMinis = 8;
 // Batches of up to 16 x SMs x this many requests run with half-filled warps.
 constexpr int kHalfWarpSmMultiple = 2;
 
@@ -106,6 +118,64 @@ __device__ __forceinline__ void RunFullStage(uint64_t &h, const uint64_t (&vc)[k
     left -= kPerStage;
 }
 
+// A whole ring fill (kMinis full stages of one lane) straight out of shared memory, for block sizes that are a
+// multiple of the tokens per stage.  The loop body is nothing but plain 128-bit shared loads and chain steps: the
+// compiler schedules the loads ahead of the chain by itself, and nothing that depends on run-time counters sits
+// between two steps (a counter-driven store after every token costs a lone warp 43 cycles per token against 20 for
+// the bare chain, measured).  A block can only end after the last token of a stage or after one of its first
+// tokens-per-16-bytes - 1 (the request's misalignment against the 16-byte copy grid is a per-lane constant), so
+// the hash after those few positions is kept, and once per stage the lane picks the one its block ends on.
+template <typename T, int kMinis, bool kPlainStep>
+__device__ __forceinline__ void RunFullFill(uint64_t &h, const uint4 *fill, int32_t &left, int64_t *&out,
+                                            int32_t block_size) {
+    constexpr int kPerPiece = 16 / sizeof(T);
+    constexpr int kPerStage = kStageBytes / sizeof(T);
+    uint64_t hx = h;
+    uint32_t hl = static_cast<uint32_t>(h), hh = static_cast<uint32_t>(h >> 32);
+#pragma unroll
+    for (int s = 0; s < kMinis; ++s) {
+        uint64_t at_end = 0, early[kPerPiece];  // hash after the stage's last token / after token e of the stage
+#pragma unroll
+        for (int c = 0; c < kPieces; ++c) {
+            const uint4 q = fill[s * kPieces + c];
+            if constexpr (sizeof(T) == 4) {
+                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if constexpr (kPlainStep) {
+                        hx = HashStep(hx, w[j]);
+                    } else {
+                        HashStepTok(hl, hh, w[j]);
+                        hx = static_cast<uint64_t>(hl) | (static_cast<uint64_t>(hh) << 32);
+                    }
+                    if (c == 0 && j < kPerPiece - 1) early[j] = hx;
+                    if (c == kPieces - 1 && j == 3) at_end = hx;
+                }
+            } else {
+                const uint64_t w[2] = {static_cast<uint64_t>(q.x) | (static_cast<uint64_t>(q.y) << 32),
+                                       static_cast<uint64_t>(q.z) | (static_cast<uint64_t>(q.w) << 32)};
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    hx = HashStep(hx, w[j]);
+                    if (c == 0 && j < kPerPiece - 1) early[j] = hx;
+                    if (c == kPieces - 1 && j == 1) at_end = hx;
+                }
+            }
+        }
+        if (left <= kPerStage) {  // the block ends in this stage, after token left - 1
+            uint64_t key = at_end;
+#pragma unroll
+            for (int e = 0; e < kPerPiece - 1; ++e) {
+                if (left == e + 1) key = early[e];
+            }
+            *out++ = static_cast<int64_t>(key);
+            left += block_size;
+        }
+        left -= kPerStage;
+    }
+    h = hx;
+}
+
 // ---------------------------------------------------------------------------------------------
 // The staging ring.  One lane = one request, so the 32 lanes of a warp read 32 unrelated places of
 // the token array.  Fetched with per-lane 16-byte copies that is 32 cache lines per warp instruction,
@@ -139,7 +209,7 @@ struct LaneSpan {
     int64_t key_base;
 };
 
-template <typename T>
+template <typename T, int kMinis>
 __device__ __forceinline__ LaneSpan<T> DescribeLane(const T *tokens, int64_t n_tokens_total, const int64_t *tok_off,
                                                     const int64_t *key_off, const int32_t *order, int64_t pos,
                                                     bool active, int32_t block_size) {
@@ -171,21 +241,23 @@ __device__ __forceinline__ LaneSpan<T> DescribeLane(const T *tokens, int64_t n_t
     return s;
 }
 
-template <typename T, bool kAligned>
+template <typename T, bool kAligned, int kMinis>
 __global__ void __launch_bounds__(2 * kMaxWarpsPerCta * 32)
     HashBlocksKernel(const T *__restrict__ tokens, int64_t n_tokens_total, const int64_t *__restrict__ tok_off,
                          int32_t n_req, int32_t block_size, int64_t *__restrict__ keys,
                          const int64_t *__restrict__ key_off, const int32_t *__restrict__ order,
                          uint32_t lanes_per_warp, uint32_t warp_smem_bytes) {
-    static_assert(kMinis % 2 == 0 && kSlots >= 2 && (kLaneStride / 16) % 2 == 1, "ring geometry");
+    using Geo = RingGeo<kMinis>;
+    static_assert(kSlots >= 2, "ring geometry");
+    constexpr int kLaneStride = Geo::kLaneStride;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t full_bars[kMaxWarpsPerCta][kSlots];
     __shared__ __align__(8) uint64_t empty_bars[kMaxWarpsPerCta][kSlots];
     constexpr int kPerPiece = 16 / sizeof(T);
     constexpr int kPerStage = kStageBytes / sizeof(T);
     constexpr uint64_t kGolden = 0x9e3779b97f4a7c15ull;
-    constexpr uint32_t kFull = kMinis * kStageBytes;   // bytes of one lane in one ring slot
-    constexpr uint32_t kSlotBytes = 32 * kLaneStride;  // one ring slot of a warp
+    constexpr uint32_t kFull = Geo::kFillBytes;   // bytes of one lane in one ring slot
+    constexpr uint32_t kSlotBytes = Geo::kSlotBytes;  // one ring slot of a warp
     const uint32_t lane = LaneId();
     const uint32_t n_consumers = blockDim.x >> 6;
     const uint32_t warp_in_cta = threadIdx.x >> 5;
@@ -217,7 +289,7 @@ __global__ void __launch_bounds__(2 * kMaxWarpsPerCta * 32)
     const bool active = lane < lanes_per_warp && pos < n_req;
 
     const LaneSpan<T> sp =
-        DescribeLane<T>(tokens, n_tokens_total, tok_off, key_off, order, pos, active, block_size);
+        DescribeLane<T, kMinis>(tokens, n_tokens_total, tok_off, key_off, order, pos, active, block_size);
     int64_t max_ring = sp.n_ring;
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) {
@@ -319,6 +391,50 @@ __global__ void __launch_bounds__(2 * kMaxWarpsPerCta * 32)
         }
     };
 
+    if constexpr (kAligned) {
+        // Block sizes that are a multiple of a stage (16, 32, 64 ... tokens): a fill that lies wholly inside the
+        // lane's request runs as one straight piece of code out of shared memory (RunFullFill); the first and the
+        // last fill of a request, which hold tokens that are not the request's, go stage by stage through the
+        // checked path.  The wait for a fill sits right before its first use: the producer runs two fills ahead,
+        // so it returns at once, and the slot is handed back when the fill has been hashed.
+        const uint8_t *lane_ring = smem + warp * warp_smem_bytes + lane * kLaneStride;
+        bool ok = true;
+        uint32_t slot = 0, round = 0;  // fill r = round * kSlots + slot
+        int64_t waited = 0;            // fills whose `full` wait has returned
+        uint64_t stage[kPerStage];
+        for (int64_t r = 0; r < max_ring; ++r) {
+            ok = BoundedWait(full0 + slot * 8, round & 1u);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            ++waited;
+            const int64_t k0 = r * kMinis;
+            const bool whole = k0 + kMinis <= n_stages && (k0 > 0 || sp.head_skip == 0) &&
+                               (k0 + kMinis < n_stages || sp.tail_count == kPerStage);
+            if (whole) {
+                RunFullFill<T, kMinis, kMinis == kDeepMinis>(
+                    h, reinterpret_cast<const uint4 *>(lane_ring + slot * kSlotBytes), left, out, block_size);
+            } else if (k0 < n_stages) {
+#pragma unroll 1
+                for (int m = 0; m < kMinis; ++m) {
+                    unpack(ring + slot * kSlotBytes, m, stage);
+                    consume(k0 + m, stage);
+                }
+            }
+            MbarArrive(empty0 + slot * 8);  // hashed: the slot may be refilled
+            if (++slot == kSlots) {
+                slot = 0;
+                ++round;
+            }
+        }
+        if (!ok) {
+            // Leave no copy in flight behind: one more bounded wait for each fill the producer may have started.
+            for (int64_t r = waited; r < max_ring && r < waited + kSlots; ++r) {
+                BoundedWait(full0 + static_cast<uint32_t>(r % kSlots) * 8, static_cast<uint32_t>(r / kSlots) & 1u);
+            }
+            if (lane == 0) atomicAdd(&g_hash_wait_timeouts, 1u);
+        }
+        return;
+    }
     bool ok = max_ring == 0 || BoundedWait(full0, 0);
     ok = __all_sync(0xffffffffu, ok);
     uint64_t even[kPerStage], odd[kPerStage];
@@ -391,12 +507,17 @@ int32_t LaunchHash(const T *d_tokens, int64_t n_tokens_total, const int64_t *d_t
     // for fewer resident warps per SM: shared memory per CTA is then padded so that only that many
     // one-warp CTAs fit, the longest chains - launched first - run alone on their scheduler, and the
     // shorter ones take over the slots as they free up.
-    int warps_per_cta = n_warps <= static_cast<int64_t>(kResidentWarpsPerSm) * sms ? 1 : kMaxWarpsPerCta;
-    size_t smem_per_warp = kWarpRingBytes;
-    if (warps_per_sm > 0 && warps_per_sm < kResidentWarpsPerSm) {
+    // Ruled by the longest chains (the caller says so, or there are no more warps than schedulers): deep fills.
+    const bool deep = (warps_per_sm > 0 && warps_per_sm <= RingGeo<kDeepMinis>::kResidentWarpsPerSm) ||
+                      n_warps <= static_cast<int64_t>(RingGeo<kDeepMinis>::kResidentWarpsPerSm) * sms;
+    const int ring_bytes = deep ? RingGeo<kDeepMinis>::kWarpRingBytes : RingGeo<kShallowMinis>::kWarpRingBytes;
+    const int resident = deep ? RingGeo<kDeepMinis>::kResidentWarpsPerSm : RingGeo<kShallowMinis>::kResidentWarpsPerSm;
+    int warps_per_cta = n_warps <= static_cast<int64_t>(resident) * sms ? 1 : kMaxWarpsPerCta;
+    size_t smem_per_warp = static_cast<size_t>(ring_bytes);
+    if (warps_per_sm > 0 && warps_per_sm < resident) {
         warps_per_cta = 1;
-        smem_per_warp = std::max<size_t>(kWarpRingBytes, (static_cast<size_t>(kMaxHashSmemPerSm) / warps_per_sm - 1024) &
-                                                             ~static_cast<size_t>(1023));
+        smem_per_warp = std::max<size_t>(smem_per_warp, (static_cast<size_t>(kMaxHashSmemPerSm) / warps_per_sm - 1024) &
+                                                            ~static_cast<size_t>(1023));
     }
     const size_t smem = static_cast<size_t>(warps_per_cta) * smem_per_warp;
     const unsigned grid = static_cast<unsigned>((n_warps + warps_per_cta - 1) / warps_per_cta);
@@ -409,9 +530,9 @@ int32_t LaunchHash(const T *d_tokens, int64_t n_tokens_total, const int64_t *d_t
                                                           static_cast<uint32_t>(smem_per_warp));
     };
     if (block_size % kPerStage == 0) {
-        launch(HashBlocksKernel<T, true>);
+        deep ? launch(HashBlocksKernel<T, true, kDeepMinis>) : launch(HashBlocksKernel<T, true, kShallowMinis>);
     } else {
-        launch(HashBlocksKernel<T, false>);
+        deep ? launch(HashBlocksKernel<T, false, kDeepMinis>) : launch(HashBlocksKernel<T, false, kShallowMinis>);
     }
     return LaunchStatus();
 }
