@@ -845,17 +845,32 @@ def run_window(args, ctx):
             toks_s[int(off_s[pos]):int(off_s[pos + 1])] = w["toks"][int(w["off"][j]):int(w["off"][j + 1])]
         ko_s = key_offsets(off_s, bs)
         d_off_s, d_ko_s = torch.from_numpy(off_s).to(device), torch.from_numpy(ko_s).to(device)
-        if args.long_fraction is None:  # measured on 2 GPUs, routed: 0.5 / 0.7 / 0.85 / 0.95 -> 3.80 / 3.44 / 3.51 / 3.77 ms
-            args.long_fraction = 0.7 if world > 1 and routed else 0.5
+        if args.long_fraction is None:
+            # measured: one GPU, head at 2 warps per SM: 0.3 / 0.5 / 0.7 -> 3.17 / 3.68 / 3.73 ms per step;
+            # 2 GPUs routed, head at 4: 0.5 / 0.7 -> 2.80 / 2.84 ms
+            args.long_fraction = 0.7 if world > 1 and routed else 0.3
+        if args.head_cap is None:  # one GPU: head 4 / 2 warps per SM -> 3.27 / 3.17 ms; 2 GPUs routed: 2.84 / 2.99 ms
+            args.head_cap = 4 if world > 1 and routed else 2
         n_long = int(np.count_nonzero(my_len >= args.long_fraction * my_len.max()))
         prefix_s = torch.empty(len(perm), dtype=torch.int32, device=device)
         window_s = torch.empty(len(perm), dtype=torch.int32, device=device)
         inv = torch.from_numpy(np.argsort(perm)).to(device)  # request -> sorted position
-        streams = [torch.cuda.Stream(device), torch.cuda.Stream(device)]
         # (first request, end, hashing warps per SM): 4 for the head, so that its chains sit alone on their
         # schedulers, and 3 for the rest, which then shares an SM with a head warp without crowding its scheduler
         # (measured: rest at 2 / 3 / 4 / unlimited warps per SM -> 4.12 / 3.98 / 4.29 / 4.25 ms per step)
-        parts = [(0, n_long, 4), (n_long, len(perm), 3)]
+        parts = [(0, n_long, args.head_cap), (n_long, len(perm), args.rest_cap)]
+        if not (world > 1 and routed) and args.rest_chunks > 1 and len(perm) - n_long > args.rest_chunks:
+            # The rest is bound by throughput, and its two halves use different resources: hashing the integer
+            # pipe, matching the random-sector rate of the memory system.  Cut into chunks of equal token count on
+            # streams of their own, the match of one chunk runs under the hash of the next.
+            cuts = np.searchsorted(off_s, off_s[n_long] + (off_s[-1] - off_s[n_long]) *
+                                   np.arange(1, args.rest_chunks) // args.rest_chunks)
+            edges = sorted(set([n_long] + [int(c) for c in cuts if n_long < c < len(perm)] + [len(perm)]))
+            parts = [(0, n_long, args.head_cap)] + [(a, b, args.rest_cap) for a, b in zip(edges[:-1], edges[1:])]
+        # the head's stream comes first in the queues of the SMs: once its long chains are through, its matchers
+        # are not left waiting behind the kernels of the rest
+        streams = [torch.cuda.Stream(device, priority=-1 if i == 0 and args.head_priority else 0)
+                   for i in range(len(parts))]
         match = searcher if world > 1 else local_index
         # the keys of a part as a batch of its own (routing sends whole batches)
         rel_ko = [(d_ko_s[a:b + 1] - int(ko_s[a])).contiguous() for a, b, _ in parts]
@@ -891,18 +906,26 @@ def run_window(args, ctx):
             main.wait_stream(streams[which])
         return prefix_s[inv], window_s[inv]
 
-    def step_overlapped():
+    def step_overlapped(marks=None):
         main = torch.cuda.current_stream(device)
-        start = torch.cuda.Event()
+        start = torch.cuda.Event(enable_timing=marks is not None)
         start.record(main)
-        for st, (a, b, cap) in zip(streams, parts):
+        if marks is not None:
+            marks.append(("start", start))
+        for i, (st, (a, b, cap)) in enumerate(zip(streams, parts)):
             if b <= a:
                 continue
             st.wait_event(start)
             with torch.cuda.stream(st):
                 GenKeyVectorBatch(toks_s, d_off_s[a:b + 1], bs, d_ko_s[a:b + 1], n_keys, out=d_keys, warps_per_sm=cap)
+                if marks is not None:
+                    marks.append(("part%d_hashed" % i, torch.cuda.Event(enable_timing=True)))
+                    marks[-1][1].record(st)
                 prefix_s[a:b] = match.PrefixMatch(d_keys, d_ko_s[a:b + 1])
                 window_s[a:b] = match.ReverseRollSlideWindowMatch(d_keys, d_ko_s[a:b + 1], sw)
+                if marks is not None:
+                    marks.append(("part%d_matched" % i, torch.cuda.Event(enable_timing=True)))
+                    marks[-1][1].record(st)
             main.wait_stream(st)
         return prefix_s[inv], window_s[inv]  # back in request order
 
@@ -954,7 +977,7 @@ def run_window(args, ctx):
     torch.cuda.synchronize(device)
     phase_ms = {"hash": ev[0].elapsed_time(ev[1]), "prefix_match": ev[1].elapsed_time(ev[2]),
                 "window_match": ev[2].elapsed_time(ev[3])}
-    if step is step_overlapped_routed:  # when each part of the two-stream step finished, from the step's start
+    if step is step_overlapped_routed or step is step_overlapped:  # when each part finished, from the step's start
         marks = []
         step(marks)
         torch.cuda.synchronize(device)
@@ -1055,11 +1078,13 @@ def run_window(args, ctx):
                            "shard_mode": args.shard_mode if world > 1 else "one unsharded index",
                            "lookups_per_s": 2 * total_keys * args.steps / (ms * 1e-3),
                            "parity_sample_ok": parity, "phase_ms_rank0": phase_ms,
-                           "schedule": ("two streams: the %d longest requests of rank 0 (>= %.2f of the longest) hashed "
-                                        "and matched beside the rest; phase_ms are the kernels run alone on the "
-                                        "whole batch" % (n_long, args.long_fraction)) if overlap else "one stream"},
+                           "schedule": ("%d streams: the %d longest requests of rank 0 (>= %.2f of the longest) hashed "
+                                        "and matched beside the rest%s; phase_ms are the kernels run alone on the "
+                                        "whole batch" % (len(parts), n_long, args.long_fraction,
+                                                         " (in %d chunks of equal token count)" % (len(parts) - 1)
+                                                         if len(parts) > 2 else "")) if overlap else "one stream"},
                 "gpu_launches": ({"peer": 6, "route": 14, "route_peer": 14}[args.shard_mode] if overlap and world > 1
-                                 else 6 if overlap else 3 if world == 1 else 7 if routed else 4)
+                                 else 3 * len(parts) if overlap else 3 if world == 1 else 7 if routed else 4)
                 * args.steps * world}
         # Roofline of the step.  Algorithmic bytes per token block: its 16 tokens (64 B), the key written (8 B), and
         # per matcher the key read (8 B) and one index slot (16 B) = 120 B.  The binding limit is not HBM but the
@@ -2038,7 +2063,13 @@ def main():
                     help="c4: one stream, requests in arrival order (the earlier form of the step)")
     ap.add_argument("--long-fraction", type=float, default=None,
                     help="c4: requests at least this fraction of the longest form the head that gets its own stream "
-                         "(default 0.5; 0.7 for the routed shard modes, whose head is routed after the rest)")
+                         "(default 0.3; 0.7 for the routed shard modes, whose head is routed after the rest)")
+    ap.add_argument("--head-priority", type=int, default=1, help="c4: 1 = the head's stream has high priority")
+    ap.add_argument("--head-cap", type=int, default=None,
+                    help="c4: hashing warps per SM of the long head (default 2 on one GPU, 4 in the routed modes)")
+    ap.add_argument("--rest-cap", type=int, default=3, help="c4: hashing warps per SM of the rest")
+    ap.add_argument("--rest-chunks", type=int, default=1,
+                    help="c4 on one GPU or with peer loads: streams the requests behind the long head are spread over")
     ap.add_argument("--request-tokens", type=int, default=0, help="hash: tokens per request (default 20970)")
     ap.add_argument("--n-configs", type=int, default=0, help="lru: quota points per GPU (default 148)")
     ap.add_argument("--instances", type=int, default=1,

@@ -248,9 +248,12 @@ KVCM_API int32_t kvcm_b200_iov_crc(const kvcm_b200_seg_t *d_segs, int32_t n_segs
  * d_req_order (optional, NULL = request order) is a permutation of [0, n_req) saying which request
  * each lane takes; listing requests longest first (kvcm_b200_length_order) groups chains of similar
  * length into one warp and starts the longest chains first, which matters for ragged batches.
- * warps_per_sm (0 = fill the SMs) caps the hashing warps resident per SM; 4 gives every such warp a
- * scheduler of its own, which is what a batch ruled by a few very long requests wants
- * (kvcm_b200_length_order suggests the value).  The keys written depend on neither.
+ * warps_per_sm (0 = fill the SMs) caps the hashing warps resident per SM.  A chain advances one token per
+ * ~25 cycles alone on its SM, ~29 / ~32 / ~35 with 2 / 3 / 4 hashing warps there and ~55 on a full SM, so a
+ * batch ruled by a few very long requests wants a small cap and a batch of many requests none
+ * (kvcm_b200_length_order suggests the value).  A cap of 1..4 also selects 512-byte fills of the staging
+ * ring (one bulk copy per lane and fill), without which the copies could not keep up with a lone chain.
+ * The keys written depend on neither.
  * Tokens reach shared memory by bulk copies that complete on mbarriers; every wait on one is bounded,
  * and a warp whose wait ran out stops writing keys and counts itself in a per-device counter that
  * kvcm_b200_hash_wait_timeouts reads (0 in any healthy run).

@@ -184,13 +184,21 @@ __device__ __forceinline__ bool UpsertOne(const IndexView &ix, uint64_t key, uin
     unsigned long long *words = reinterpret_cast<unsigned long long *>(ix.slots);
     const uint64_t mixed = Mix(key);
     const uint64_t home = mixed & ix.mask;
-    for (int attempt = 0; attempt < 64; ++attempt) {
+    // A seat (one count of cells[3]) is taken before an EMPTY slot is claimed, so that the table can never run
+    // out of EMPTY slots, and it is kept while the claim is retried: a thread that lost a slot to another key
+    // does not hand its seat back in between, or threads arriving at that moment would be refused although
+    // there is room for them.
+    bool seated = false;
+    bool done = false, stored = false;
+    for (int attempt = 0; attempt < 64 && !done; ++attempt) {
         uint64_t slot = home, tomb = ~0ull, empty = ~0ull;
+        bool found = false;
         for (uint64_t probe = 0; probe <= ix.mask; ++probe) {
             const uint64_t seen = LoadSlot(ix.slots + slot).x;
             if (seen == key) {  // present already (or inserted by a duplicate of this key in the same batch)
                 atomicExch(&words[2 * slot + 1], value);
-                return true;
+                found = true;
+                break;
             }
             if (seen == kEmptyKey) {
                 empty = slot;
@@ -199,41 +207,44 @@ __device__ __forceinline__ bool UpsertOne(const IndexView &ix, uint64_t key, uin
             if (seen == kTombKey && tomb == ~0ull) tomb = slot;
             slot = (slot + 1) & ix.mask;
         }
-        if (tomb != ~0ull) {
+        if (found) {
+            done = stored = true;
+        } else if (tomb != ~0ull) {
             const uint64_t was = atomicCAS(&words[2 * tomb], kTombKey, key);
-            if (was == kTombKey) {
+            if (was == kTombKey || was == key) {
                 atomicExch(&words[2 * tomb + 1], value);
-                ix.tags[tomb] = TagOf(mixed);  // readers of later launches find the slot through its tag
+                if (was == kTombKey) {
+                    ix.tags[tomb] = TagOf(mixed);  // readers of later launches find the slot through its tag
+                    AddCell(&ix.cells[2], 1);
+                }
+                done = stored = true;
+            }  // else another key took the tombstone: walk again
+        } else if (empty == ~0ull) {
+            done = true;  // no EMPTY slot on the whole table: cannot happen below the limit
+        } else {
+            if (!seated) {
+                const uint64_t used = atomicAdd(reinterpret_cast<unsigned long long *>(&ix.cells[3]), 1ull);
+                if (used >= ix.max_live) {
+                    AddCell(&ix.cells[3], -1);
+                    return false;
+                }
+                seated = true;
+            }
+            const uint64_t was = atomicCAS(&words[2 * empty], kEmptyKey, key);
+            if (was == kEmptyKey) {
+                atomicExch(&words[2 * empty + 1], value);
+                ix.tags[empty] = TagOf(mixed);
                 AddCell(&ix.cells[2], 1);
-                return true;
+                return true;  // the seat is now this slot's
             }
             if (was == key) {
-                atomicExch(&words[2 * tomb + 1], value);
-                return true;
-            }
-            continue;  // another key took the tombstone: walk again
-        }
-        if (empty == ~0ull) return false;  // no EMPTY slot on the whole table: cannot happen below the limit
-        // Take a seat before claiming an EMPTY slot so that the table can never run out of them.
-        const uint64_t used = atomicAdd(reinterpret_cast<unsigned long long *>(&ix.cells[3]), 1ull);
-        if (used >= ix.max_live) {
-            AddCell(&ix.cells[3], -1);
-            return false;
-        }
-        const uint64_t was = atomicCAS(&words[2 * empty], kEmptyKey, key);
-        if (was == kEmptyKey) {
-            atomicExch(&words[2 * empty + 1], value);
-            ix.tags[empty] = TagOf(mixed);
-            AddCell(&ix.cells[2], 1);
-            return true;
-        }
-        AddCell(&ix.cells[3], -1);
-        if (was == key) {
-            atomicExch(&words[2 * empty + 1], value);
-            return true;
+                atomicExch(&words[2 * empty + 1], value);
+                done = stored = true;
+            }  // else another key took the slot: walk again, seat kept
         }
     }
-    return false;
+    if (seated) AddCell(&ix.cells[3], -1);  // ended without claiming an EMPTY slot
+    return stored;
 }
 
 __global__ void UpsertKernel(IndexView ix, const int64_t *__restrict__ keys, const uint64_t *__restrict__ values,

@@ -187,8 +187,8 @@ __device__ __forceinline__ void RunFullFill(uint64_t &h, const uint4 *fill, int3
 // CTA = consumer warps [0, n) that run the chains + producer warps [n, 2n), producer lane j
 // fetching for consumer lane j (a one-consumer CTA may swap the two roles, see the kernel).  Per
 // consumer warp and ring slot
-// there is a `full` barrier (32 producer arrivals + the bytes in flight) and an `empty` barrier
-// (32 consumer arrivals once the slot has been read into registers).  A lane's bytes of a slot are
+// there is a `full` barrier (one arrival by the producer's lane 0 + the bytes in flight) and an `empty` barrier
+// (one arrival by the consumer's lane 0 once every lane is through with the slot).  A lane's bytes of a slot are
 // contiguous; lanes are kMinis*64+16 bytes apart, an odd number of 16-byte words, so the 128-bit
 // reads of a warp stay conflict-free.  Every wait is bounded: after kSpinLimit polls the warp
 // raises g_hash_wait_timeouts, waits once more (bounded) for the copies in flight, and returns.
@@ -275,8 +275,8 @@ __global__ void __launch_bounds__(2 * kMaxWarpsPerCta * 32)
         for (uint32_t w = 0; w < n_consumers; ++w) {
 #pragma unroll
             for (int s = 0; s < kSlots; ++s) {
-                MbarInit(SmemAddr(&full_bars[w][s]), 32);
-                MbarInit(SmemAddr(&empty_bars[w][s]), 32);
+                MbarInit(SmemAddr(&full_bars[w][s]), 1);   // one arrival per fill: the producer's lane 0
+                MbarInit(SmemAddr(&empty_bars[w][s]), 1);  // one arrival per fill: the consumer's lane 0
             }
         }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -302,7 +302,7 @@ __global__ void __launch_bounds__(2 * kMaxWarpsPerCta * 32)
 
     if (producer) {
         // Fill r carries this lane's bytes [r*kFull, (r+1)*kFull) of its request into slot r % kSlots.
-        // Every lane arrives for every fill, with or without bytes: a phase of `full` is one fill of the warp.
+        // A phase of `full` is one fill of the warp, whether or not every lane still has bytes to fetch.
         bool ok = true;
         uint32_t slot = 0, round = 0;  // r = round * kSlots + slot
         for (int64_t r = 0; r < max_ring && ok; ++r) {
@@ -326,14 +326,19 @@ __global__ void __launch_bounds__(2 * kMaxWarpsPerCta * 32)
                     }
                 }
             }
+            // One arrival per fill, by lane 0, announcing the bytes of all 32 lanes (a barrier operation is a
+            // shared-memory atomic on the pipe the consumers' shared loads use: 32 per fill and warp were felt by
+            // the chains of every warp on the SM).  It follows the warp's tail words (__syncwarp orders them before
+            // it, its release publishes them) and precedes the copies.
+            uint32_t bytes = 0;
             if (r < sp.n_ring && at < sp.bulk_total) {
-                const uint32_t bytes =
-                    sp.bulk_total - at >= kFull ? kFull : static_cast<uint32_t>(sp.bulk_total - at);
-                MbarArriveExpectTx(bar, bytes);
-                BulkLoad(ring + slot * kSlotBytes, reinterpret_cast<const void *>(sp.a0 + at), bytes, bar);
-            } else {
-                MbarArrive(bar);  // releases the tail words stored above to the consumer, too
+                bytes = sp.bulk_total - at >= kFull ? kFull : static_cast<uint32_t>(sp.bulk_total - at);
             }
+            const uint32_t warp_bytes = __reduce_add_sync(0xffffffffu, bytes);
+            __syncwarp();
+            if (lane == 0) MbarArriveExpectTx(bar, warp_bytes);
+            __syncwarp();
+            if (bytes > 0) BulkLoad(ring + slot * kSlotBytes, reinterpret_cast<const void *>(sp.a0 + at), bytes, bar);
             if (++slot == kSlots) {
                 slot = 0;
                 ++round;
@@ -420,7 +425,8 @@ __global__ void __launch_bounds__(2 * kMaxWarpsPerCta * 32)
                     consume(k0 + m, stage);
                 }
             }
-            MbarArrive(empty0 + slot * 8);  // hashed: the slot may be refilled
+            __syncwarp();
+            if (lane == 0) MbarArrive(empty0 + slot * 8);  // every lane has hashed its part: the slot may be refilled
             if (++slot == kSlots) {
                 slot = 0;
                 ++round;
@@ -457,7 +463,8 @@ __global__ void __launch_bounds__(2 * kMaxWarpsPerCta * 32)
                 if (m + 2 < kMinis) {
                     unpack(cur, m + 2, even);
                 } else {
-                    MbarArrive(empty0 + slot * 8);  // this fill now lives in registers: the slot may be refilled
+                    __syncwarp();
+                    if (lane == 0) MbarArrive(empty0 + slot * 8);  // this fill now lives in registers: the slot may be refilled
                     if (r + 1 < max_ring) {
                         ok = BoundedWait(full0 + next_slot * 8, next_round & 1u);
                         ok = __all_sync(0xffffffffu, ok);
@@ -575,15 +582,28 @@ int32_t kvcm_b200_length_order(const int64_t *h_tok_off, int32_t n_req, int32_t 
     });
     for (int32_t r = 0; r < n_req; ++r) h_order_out[r] = idx[r];
     if (warps_per_sm_out != nullptr && n_req > 0) {
-        // A warp alone on its scheduler advances one token per ~40 cycles (the dependent chain); two warps
-        // sharing a scheduler advance one token each per ~78 cycles.  If the longest chain alone outlasts
-        // the whole batch spread over all schedulers, keep one hashing warp per scheduler (4 per SM) so that
-        // chain is never slowed down; otherwise fill the SMs.
+        // How many hashing warps per SM finish the batch first.  Measured cycles per token of a chain with c
+        // hashing warps (and their producers) on its SM: 25 alone, ~29 with 2, ~32 with 3, ~35 with 4; with the
+        // SM filled (8 warps, small fills) a chain crawls at ~55 but the SM as a whole does about as many steps
+        // per cycle as with 4.  A batch takes the longer of its longest chain at that pace and of all its warp
+        // steps spread over the resident warps; pick the c that makes that shortest (0 = fill the SMs).
         const int sms = kvcm::HaveDevice() ? kvcm::GetDeviceInfo().sm_count : 148;
         const double longest = static_cast<double>(h_tok_off[idx[0] + 1] - h_tok_off[idx[0]]);
         double warp_steps = 0;
         for (int32_t r = 0; r < n_req; r += 32) warp_steps += static_cast<double>(h_tok_off[idx[r] + 1] - h_tok_off[idx[r]]);
-        *warps_per_sm_out = longest * 40.0 >= warp_steps * 39.0 / (4.0 * sms) ? 4 : 0;
+        const int caps[4] = {2, 3, 4, 0};
+        const double pace[4] = {29.0, 32.0, 35.0, 55.0};
+        const double steps_per_cycle_per_sm[4] = {2 / 29.0, 3 / 32.0, 4 / 35.0, 4 / 34.0};
+        double best = 0;
+        for (int i = 0; i < 4; ++i) {
+            const double chain = longest * pace[i];
+            const double volume = warp_steps / (steps_per_cycle_per_sm[i] * sms);
+            const double t = chain > volume ? chain : volume;
+            if (i == 0 || t < best) {
+                best = t;
+                *warps_per_sm_out = caps[i];
+            }
+        }
     }
     return KVCM_OK;
 }

@@ -24,7 +24,7 @@ def key_offsets(tok_off, block_size: int) -> np.ndarray:
 def length_order(tok_off, with_residency: bool = False):
     """Requests sorted by token count, longest first (int32 permutation, host side).  Passing it to
     GenKeyVectorBatch speeds up ragged batches; the keys are the same.  with_residency=True also returns the
-    `warps_per_sm` value to pass along (4 when a few very long requests rule the batch, else 0)."""
+    `warps_per_sm` value to pass along (2, 3 or 4 hashing warps per SM when long requests rule the batch, else 0)."""
     tok_off = np.ascontiguousarray(tok_off, dtype=np.int64)
     out = np.empty(len(tok_off) - 1, dtype=np.int32)
     residency = ctypes.c_int32(0)
