@@ -631,6 +631,42 @@ KVCM_API int32_t kvcm_b200_replay_lru_group(const int64_t *d_keys, const int64_t
                                             uint32_t *d_status, kvcm_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
+ * (2d) The same sweep under the "random_lru" eviction policy
+ * (kv_cache_manager/optimizer/eviction_policy/random_lru.cc:5-131, random_lru.h:13-47): the cached blocks sit in a
+ * dense vector beside their last access times; a round of evictions draws sampling_size = evict_batch /
+ * sample_rate indices with the policy's xorshift generator (sample_rate <= 0 means 0.1, as in the reference's
+ * constructor), orders the first k of them by access time with std::partial_sort and removes those blocks by
+ * swap-and-pop.  Equal access times are common (the blocks of one trace share one), and which of several
+ * equally old samples go is decided by the order partial_sort leaves equal elements in: the kernel restates
+ * that algorithm (heap-select + sort-heap) step for step, and every configuration starts from the reference's
+ * generator seed, so the victims are the reference's.
+ * Arguments as kvcm_b200_replay_lru, plus d_timestamps (optional, int64 per trace: the traces' timestamp_us;
+ * the trace number when NULL) and sample_rate.  evict_batch <= KVCM_B200_RANDOM_LRU_MAX_BATCH and
+ * sampling_size <= KVCM_B200_RANDOM_LRU_MAX_SAMPLE (the sample lives in shared memory), else
+ * KVCM_EC_OUT_OF_LIMIT.  Exact for prefix-unique chained keys without repeats inside one trace.  One warp per
+ * configuration; the generator, the heap and the removals are sequential, so a round of evictions costs tens of
+ * microseconds.  d_workspace: kvcm_b200_replay_random_lru_workspace_bytes(n_keys_total, n_configs) bytes
+ * (16 bytes per key occurrence for each configuration; -1: too large), 256-byte aligned.
+ * ---------------------------------------------------------------------------------------- */
+#define KVCM_B200_RANDOM_LRU_MAX_SAMPLE 2048
+#define KVCM_B200_RANDOM_LRU_MAX_BATCH 512
+KVCM_API int64_t kvcm_b200_replay_random_lru_workspace_bytes(int64_t n_keys_total, int32_t n_configs);
+/* Host-only self test: runs, on host arrays, the very routine the sweep kernel orders its samples with
+ * (h_idx[i] travels with h_times[i]; afterwards the first k entries are the k smallest times in ascending
+ * order, equal times in the order std::partial_sort leaves them).  Lets a box without a GPU check the
+ * restatement against the standard library.  No counterpart in the reference. */
+KVCM_API int32_t kvcm_b200_selftest_partial_sort(uint32_t *h_idx, int64_t *h_times, uint32_t k, uint32_t n);
+KVCM_API int32_t kvcm_b200_replay_random_lru(const int64_t *d_keys, const int64_t *d_key_off,
+                                             const uint8_t *d_trace_type, const int64_t *d_mask_off,
+                                             const uint8_t *d_mask_bits, const int64_t *d_timestamps,
+                                             int32_t n_traces, int64_t n_keys_total, const int64_t *d_quota_blocks,
+                                             int32_t n_configs, int32_t evict_batch, int32_t precise,
+                                             double sample_rate, void *d_workspace, int64_t workspace_bytes,
+                                             int32_t *d_ext_hit, int32_t *d_int_hit, int32_t *d_written,
+                                             int64_t *d_cache_blocks, int64_t *d_totals, uint32_t *d_status,
+                                             kvcm_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
  * (2c'') The same sweep under the "leaf_aware_lru" eviction policy
  * (kv_cache_manager/optimizer/eviction_policy/leaf_aware_lru.cc:20-160; chosen by eviction_policy_type in
  * the optimizer's startup configuration, kv_cache_manager/optimizer/eviction_policy/policy_factory.cc:8-47).

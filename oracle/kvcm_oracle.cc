@@ -650,6 +650,7 @@ struct LruBlock {
     int64_t time = -1;    // last_access_time
     LruNode *owner = nullptr;
     std::list<LruBlock *>::iterator where;  // position in the recency list while listed
+    size_t sampled_at = 0;                  // index in the random policy's block vector while cached
 };
 struct LruNode {
     LruNode *parent = nullptr;
@@ -675,11 +676,69 @@ struct OracleLruReplay {
     bool precise = false;
     bool leaf_aware = false;
     int64_t now = 0;  // timestamp of the trace being replayed
+    // "random_lru" (kv_cache_manager/optimizer/eviction_policy/random_lru.cc:5-131, random_lru.h:17-22): every cached
+    // block sits in a dense vector beside its last access time; a round of evictions samples `sampling_size`
+    // indices with a xorshift generator, orders the first k of them by time with std::partial_sort - called here as
+    // the reference calls it, so that equal times come out in the standard library's order - and evicts those.
+    bool random = false;
+    std::vector<LruBlock *> sampled_blocks;
+    std::vector<int64_t> sampled_times;
+    uint64_t xor_state = 0x12345678ABCDEF01ULL;
+    size_t sampling_size = 0;
+
+    size_t fast_rand(size_t mod) {  // random_lru.cc:121-131
+        if (mod == 0) return 0;
+        uint64_t x = xor_state;
+        x ^= x << 13;
+        x ^= x >> 7;
+        x ^= x << 17;
+        xor_state = x;
+        return x % mod;
+    }
+    void random_remove(LruBlock *b) {  // RemoveBlock, random_lru.cc:84-103: swap with the last entry, pop
+        const size_t at = b->sampled_at;
+        LruBlock *last = sampled_blocks.back();
+        sampled_blocks[at] = last;
+        sampled_times[at] = sampled_times.back();
+        last->sampled_at = at;
+        sampled_blocks.pop_back();
+        sampled_times.pop_back();
+        b->cached = false;
+        --n_cached;
+    }
+    std::vector<LruBlock *> evict_random_blocks(int64_t count) {  // EvictBlocks + SampleAndPickLru, :38-82
+        std::vector<LruBlock *> out;
+        if (sampled_blocks.empty()) return out;
+        const size_t total = std::min<size_t>(static_cast<size_t>(count), sampled_blocks.size());
+        const size_t n = sampled_blocks.size();
+        const size_t sample = std::min(sampling_size, n);
+        const size_t k = std::min(total, sample);
+        std::vector<size_t> indices;
+        indices.reserve(sample);
+        for (size_t i = 0; i < sample; ++i) indices.push_back(fast_rand(n));
+        std::partial_sort(indices.begin(), indices.begin() + static_cast<std::ptrdiff_t>(k), indices.end(),
+                          [this](size_t a, size_t b) { return sampled_times[a] < sampled_times[b]; });
+        std::vector<LruBlock *> victims;
+        for (size_t i = 0; i < k; ++i) victims.push_back(sampled_blocks[indices[i]]);
+        for (LruBlock *v : victims) {
+            if (!v->cached) continue;  // sampled twice: gone already
+            random_remove(v);
+            out.push_back(v);
+            if (out.size() == total) break;
+        }
+        return out;
+    }
 
     void on_written(LruBlock *b) {  // lru.cc:6-11; leaf_aware_lru.cc:20-31; times: radix_tree_index.cc:335-336,366-367
         b->cached = true;
         b->time = now;
         ++n_cached;
+        if (random) {  // OnBlockWritten, random_lru.cc:17-21
+            b->sampled_at = sampled_blocks.size();
+            sampled_blocks.push_back(b);
+            sampled_times.push_back(b->time);
+            return;
+        }
         if (leaf_aware && !(b->owner != nullptr && b->owner->leaf())) return;  // only blocks of leaves queue up
         recency.push_front(b);
         b->where = recency.begin();
@@ -688,6 +747,10 @@ struct OracleLruReplay {
     void on_accessed(LruBlock *b) {  // lru.cc:18-26; leaf_aware_lru.cc:39-51
         if (!b->cached) return;
         b->time = now;
+        if (random) {  // OnBlockAccessed, random_lru.cc:27-35
+            sampled_times[b->sampled_at] = now;
+            return;
+        }
         if (!b->listed) return;
         recency.splice(recency.begin(), recency, b->where);
         b->where = recency.begin();
@@ -803,6 +866,7 @@ struct OracleLruReplay {
     }
     std::vector<LruBlock *> evict_blocks(int64_t count) {  // lru.cc:28-49
         if (leaf_aware) return evict_leaf_blocks(count);
+        if (random) return evict_random_blocks(count);
         std::vector<LruBlock *> out;
         for (int64_t i = 0; i < count && !recency.empty(); ++i) {
             LruBlock *b = recency.back();
@@ -1024,6 +1088,25 @@ void *kvcm_oracle_lru_replay_create_policy(int64_t quota_blocks, int32_t evict_b
                                            int32_t policy) {
     auto *st = static_cast<OracleLruReplay *>(kvcm_oracle_lru_replay_create(quota_blocks, evict_batch, precise));
     st->leaf_aware = policy == 1;
+    return st;
+}
+// std::partial_sort exactly as RandomLruEvictionPolicy::SampleAndPickLru calls it (random_lru.cc:72-74): indices
+// ordered by the time they point at.  Test infrastructure for the restatement of that algorithm in the sweep kernel.
+void kvcm_oracle_partial_sort_by_time(uint64_t *indices, int64_t n, int64_t k, const int64_t *times) {
+    std::vector<size_t> idx(indices, indices + n);
+    std::partial_sort(idx.begin(), idx.begin() + static_cast<std::ptrdiff_t>(k), idx.end(),
+                      [times](size_t a, size_t b) { return times[a] < times[b]; });
+    for (int64_t i = 0; i < n; ++i) indices[i] = idx[static_cast<size_t>(i)];
+}
+
+// "random_lru": sampling_size = batch / sample_rate as a double division cut to an integer, 0.1 for a rate <= 0
+// (RandomLruEvictionPolicy's constructor, random_lru.cc:5-14).
+void *kvcm_oracle_random_lru_replay_create(int64_t quota_blocks, int32_t evict_batch, int32_t precise,
+                                           double sample_rate) {
+    auto *st = static_cast<OracleLruReplay *>(kvcm_oracle_lru_replay_create(quota_blocks, evict_batch, precise));
+    st->random = true;
+    if (sample_rate <= 0.0) sample_rate = 0.1;
+    st->sampling_size = static_cast<size_t>(evict_batch / sample_rate);
     return st;
 }
 void kvcm_oracle_lru_replay_destroy(void *h) { delete static_cast<OracleLruReplay *>(h); }

@@ -393,6 +393,16 @@ def iov_crc(buf, cal_bytes):
 TRACE_DIALOG_TURN, TRACE_GET_LOCATION, TRACE_WRITE_CACHE = 0, 1, 2
 
 
+def partial_sort_by_time(indices, k, times):
+    """std::partial_sort(indices, indices + k, end) with the comparator times[a] < times[b], as the reference's
+    random_lru policy calls it (eviction_policy/random_lru.cc:72-74).  Returns the reordered index array."""
+    idx = np.ascontiguousarray(indices, dtype=np.uint64).copy()
+    times = _i64(times)
+    lib().kvcm_oracle_partial_sort_by_time(_ptr(idx, ctypes.c_uint64), ctypes.c_int64(len(idx)), ctypes.c_int64(int(k)),
+                                           _ptr(times, ctypes.c_int64))
+    return idx
+
+
 class Replay:
     """Sequential replay over the prefix tree, no eviction
     (kv_cache_manager/optimizer/manager/optimizer_runner.cc:29-215)."""
@@ -440,7 +450,14 @@ class LruReplay(Replay):
 
     POLICIES = {"lru": 0, "leaf_aware_lru": 1}
 
-    def __init__(self, quota_blocks, evict_batch=100, precise=False, policy="lru"):
+    def __init__(self, quota_blocks, evict_batch=100, precise=False, policy="lru", sample_rate=0.0):
+        """policy "random_lru" (eviction_policy/random_lru.cc) takes `sample_rate` (RandomLruParams; <= 0 means 0.1)."""
+        if policy == "random_lru":
+            lib().kvcm_oracle_random_lru_replay_create.restype = ctypes.c_void_p
+            self._h = ctypes.c_void_p(lib().kvcm_oracle_random_lru_replay_create(
+                ctypes.c_int64(int(quota_blocks)), ctypes.c_int32(int(evict_batch)),
+                ctypes.c_int32(1 if precise else 0), ctypes.c_double(float(sample_rate))))
+            return
         lib().kvcm_oracle_lru_replay_create_policy.restype = ctypes.c_void_p
         self._h = ctypes.c_void_p(lib().kvcm_oracle_lru_replay_create_policy(
             ctypes.c_int64(int(quota_blocks)), ctypes.c_int32(int(evict_batch)), ctypes.c_int32(1 if precise else 0),

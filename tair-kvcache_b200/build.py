@@ -9,7 +9,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libkvcm_b200.so")
 
 SOURCES = ["runtime.cu", "move_rows.cu", "copy_segments.cu", "hash_blocks.cu", "block_index.cu", "replay.cu",
-           "replay_lru.cu", "replay_leaf_lru.cu"]
+           "replay_lru.cu", "replay_leaf_lru.cu", "replay_random_lru.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

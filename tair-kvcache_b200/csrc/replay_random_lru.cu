@@ -1,0 +1,415 @@
+// Optimizer trace replay with the "random_lru" eviction policy, for a sweep of cache quotas at once (sm_100a).
+//
+// Stands in for OptimizerRunner::RunTraces (kv_cache_manager/optimizer/manager/optimizer_runner.cc:29-215) over
+// RadixTreeIndex (kv_cache_manager/optimizer/index/radix_tree_index.cc:19-392) with RandomLruEvictionPolicy
+// (kv_cache_manager/optimizer/eviction_policy/random_lru.cc:5-131, random_lru.h:13-47) and the quota check after
+// every write (OptIndexerManager::CheckAndEvict, kv_cache_manager/optimizer/manager/indexer_manager.cc:55-90;
+// OptEvictionManager::EvictByInstanceRough / EvictByInstancePrecise, manager/eviction_manager.cc:148-239), one
+// instance per group.
+//
+// One warp replays one quota point, as in the "lru" sweep, and the tree collapses to per-key state for the same
+// reasons (keys are prefix-unique; a trace touches its leading cached blocks, then writes its missing ones).  The
+// policy's own state is what the reference keeps: a dense vector of the cached blocks beside their last access
+// times, a key's index in it, and the state of its xorshift generator.
+//   pos[id]   0 = not cached, else index + 1 in blk / ts
+//   blk[i]    id of the block at index i; ts[i] its last access time; i < resident
+// A round of evictions (EvictBlocks, random_lru.cc:38-57) draws `sampling_size` indices with replacement
+// (FastRand, :121-131), orders the first k of them by access time with std::partial_sort (:59-82) and removes those
+// blocks by swap-and-pop (:84-103).  Blocks written or read by one trace share a timestamp, so WHICH of several
+// equally old samples go depends on the order std::partial_sort leaves equal elements in.  That order is a
+// property of the algorithm the C++ standard library documents for it - heap-select followed by sort-heap on a
+// binary max-heap with hole-based sift-down and sift-up - which is restated below, step for step, on the sample
+// held in shared memory; the CPU oracle calls std::partial_sort itself, and the parity tests compare the two on
+// traces full of tied timestamps.
+// The generator is sequential, the heap is sequential: both run in lane 0 (the raw draws first, the modulo of all
+// draws then in parallel; the times of the sampled indices are gathered by all lanes).  The removals are
+// sequential too - every one changes the index of the block that was last - but run out of shared memory: the
+// tail of the block vector is staged there, and the victims' indices are kept current by a warp-wide scan.
+#include "kvcm_common.cuh"
+#include "replay_ids.cuh"
+
+namespace kvcm {
+namespace {
+
+constexpr uint32_t kMaxSample = KVCM_B200_RANDOM_LRU_MAX_SAMPLE;  // sampled indices per round held in shared memory
+constexpr uint32_t kMaxBatch = KVCM_B200_RANDOM_LRU_MAX_BATCH;    // blocks evicted per round
+constexpr uint32_t kGone = 0xFFFFFFFFu;
+
+__global__ void RandomInitKernel(IdTable t, uint32_t *pos, uint64_t n_pos) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    const uint64_t first = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (uint64_t i = first; i <= t.mask; i += stride) t.slots[i] = make_ulonglong2(kEmptyKey, ~0ull);
+    for (uint64_t i = first; i < n_pos; i += stride) pos[i] = 0u;
+    if (first == 0) {
+        t.cells[0] = 0ull;
+        t.cells[1] = ~0ull;
+    }
+}
+
+struct RandomSweep {
+    const uint32_t *ids;
+    const int64_t *key_off;
+    const uint8_t *type;
+    const int64_t *mask_off;
+    const uint8_t *mask_bits;
+    const int64_t *timestamps;  // per trace; null = the trace number
+    const int64_t *quota;
+    uint32_t *pos;  // [n_configs][n_keys]
+    uint32_t *blk;  // [n_configs][n_keys]
+    int64_t *ts;    // [n_configs][n_keys]
+    int32_t *ext_hit, *int_hit, *written;  // per trace; all four may be null when only totals are wanted
+    int64_t *cache_blocks;
+    int64_t *totals;  // [n_configs][4]
+    int64_t n_keys;
+    int32_t n_traces;
+    int32_t n_configs;
+    int32_t evict_batch;
+    int32_t precise;
+    uint32_t sampling_size;
+};
+
+// The sample: index into the block vector and that block's time, moved together.
+struct Sample {
+    uint32_t *idx;
+    int64_t *t;
+    __host__ __device__ __forceinline__ void Move(uint32_t to, uint32_t from) {
+        idx[to] = idx[from];
+        t[to] = t[from];
+    }
+    __host__ __device__ __forceinline__ void Put(uint32_t to, uint32_t i, int64_t time) {
+        idx[to] = i;
+        t[to] = time;
+    }
+};
+
+// Sift-up of `value` from `hole` towards `top` in a max-heap ordered by time (the standard library's push-heap step).
+__host__ __device__ __forceinline__ void PushHeap(Sample &s, uint32_t hole, uint32_t top, uint32_t v_idx, int64_t v_t) {
+    while (hole > top) {
+        const uint32_t parent = (hole - 1) / 2;
+        if (!(s.t[parent] < v_t)) break;
+        s.Move(hole, parent);
+        hole = parent;
+    }
+    s.Put(hole, v_idx, v_t);
+}
+
+// The hole at `hole` sinks to a leaf along the larger children (the right child unless it is smaller than the
+// left), then `value` is sifted up from there: the standard library's adjust-heap step.
+__host__ __device__ __forceinline__ void AdjustHeap(Sample &s, uint32_t hole, uint32_t len, uint32_t v_idx, int64_t v_t) {
+    const uint32_t top = hole;
+    uint32_t child = hole;
+    while (child < (len - 1) / 2) {
+        child = 2 * (child + 1);
+        if (s.t[child] < s.t[child - 1]) --child;
+        s.Move(hole, child);
+        hole = child;
+    }
+    if ((len & 1u) == 0 && child == (len - 2) / 2) {
+        child = 2 * (child + 1);
+        s.Move(hole, child - 1);
+        hole = child - 1;
+    }
+    PushHeap(s, hole, top, v_idx, v_t);
+}
+
+// std::partial_sort(first, first + k, first + n) by time: heap-select, then sort-heap.
+__host__ __device__ void PartialSortByTime(Sample &s, uint32_t k, uint32_t n) {
+    if (k == 0) return;
+    if (k >= 2) {  // make-heap over the first k
+        uint32_t parent = (k - 2) / 2;
+        while (true) {
+            const uint32_t vi = s.idx[parent];
+            const int64_t vt = s.t[parent];
+            AdjustHeap(s, parent, k, vi, vt);
+            if (parent == 0) break;
+            --parent;
+        }
+    }
+    for (uint32_t i = k; i < n; ++i) {  // an element older than the heap's top takes its place
+        if (s.t[i] < s.t[0]) {
+            const uint32_t vi = s.idx[i];
+            const int64_t vt = s.t[i];
+            s.Move(i, 0);
+            AdjustHeap(s, 0, k, vi, vt);
+        }
+    }
+    for (uint32_t last = k; last > 1;) {  // sort-heap
+        --last;
+        const uint32_t vi = s.idx[last];
+        const int64_t vt = s.t[last];
+        s.Move(last, 0);
+        AdjustHeap(s, 0, last, vi, vt);
+    }
+}
+
+// type: 0 DialogTurn (InsertWithQuery), 1 GetLocation (PrefixQuery), 2 WriteCache (InsertOnly).
+__global__ void __launch_bounds__(32) RandomLruSweepKernel(const RandomSweep p) {
+    __shared__ uint32_t s_idx[kMaxSample];
+    __shared__ int64_t s_t[kMaxSample];
+    __shared__ uint32_t v_id[kMaxBatch], v_at[kMaxBatch];      // the round's victims: block id, current index
+    __shared__ uint32_t tail_blk[kMaxBatch];                   // blk / ts of the last entries, [j] = index r0 - 1 - j
+    __shared__ int64_t tail_ts[kMaxBatch];
+    const int32_t cfg = blockIdx.x;
+    const uint32_t lane = LaneId();
+    const uint32_t lt = (1u << lane) - 1u;
+    uint32_t *pos = p.pos + static_cast<int64_t>(cfg) * p.n_keys;
+    uint32_t *blk = p.blk + static_cast<int64_t>(cfg) * p.n_keys;
+    int64_t *ts = p.ts + static_cast<int64_t>(cfg) * p.n_keys;
+    const int64_t quota = p.quota[cfg];
+    const int64_t out0 = static_cast<int64_t>(cfg) * p.n_traces;
+    Sample sample{s_idx, s_t};
+    uint64_t rng = 0x12345678ABCDEF01ull;  // random_lru.h:20; every configuration is a run of its own
+    int64_t resident = 0;
+    int64_t sum_ext = 0, sum_int = 0, sum_wr = 0;
+
+    for (int32_t t = 0; t < p.n_traces; ++t) {
+        const int64_t beg = p.key_off[t];
+        const int64_t n = p.key_off[t + 1] - beg;
+        const uint8_t ty = p.type[t];
+        const int64_t skip = (ty == 1 && p.mask_off != nullptr) ? p.mask_off[t] : 0;
+        const int64_t now = p.timestamps != nullptr ? p.timestamps[t] : static_cast<int64_t>(t);
+        int32_t ext = 0, inte = 0, wr = 0;
+        bool alive = ty != 2;  // still inside the leading run of cached blocks
+        for (int64_t base = 0; base < n; base += 32) {
+            const int64_t i = base + lane;
+            const bool have = i < n;
+            const uint32_t id = have ? p.ids[beg + i] : 0u;
+            const uint32_t cur = have ? pos[id] : 0u;
+            const uint32_t in_range = __ballot_sync(0xffffffffu, have);
+            const uint32_t cached = __ballot_sync(0xffffffffu, have && cur != 0u);
+            const uint32_t miss = in_range & ~cached;
+            uint32_t touch = 0;  // leading cached blocks: hits, their access time becomes the trace's
+            if (alive) {
+                touch = miss != 0 ? cached & ((1u << (__ffs(miss) - 1)) - 1u) : cached;
+                const uint32_t masked = __ballot_sync(
+                    0xffffffffu, i < skip || (ty == 1 && p.mask_bits != nullptr && have && p.mask_bits[beg + i] != 0));
+                ext += __popc(touch & ~masked);
+                inte += __popc(touch & masked);
+                if (miss != 0) alive = false;
+            }
+            const uint32_t write = ty == 1 ? 0u : miss;  // then the missing blocks are written, in order
+            if ((touch >> lane) & 1u) {
+                ts[cur - 1] = now;  // OnBlockAccessed
+            } else if ((write >> lane) & 1u) {
+                const int64_t at = resident + __popc(write & lt);  // OnBlockWritten: appended in key order
+                blk[at] = id;
+                ts[at] = now;
+                pos[id] = static_cast<uint32_t>(at) + 1u;
+            }
+            const uint32_t n_write = __popc(write);
+            resident += n_write;
+            wr += static_cast<int32_t>(n_write);
+            __syncwarp();
+            if (ty == 1 && !alive) break;
+        }
+        if (ty != 1 && resident > quota) {
+            // CheckAndEvict: rounds of EvictBlocks until the excess is covered or a round evicts nothing.
+            const int64_t excess = resident - quota;
+            int64_t total = 0;
+            while (total < excess) {
+                int64_t count = p.evict_batch;
+                if (p.precise != 0 && excess - total < count) count = excess - total;
+                if (resident == 0) break;
+                const uint32_t n_blocks = static_cast<uint32_t>(resident);
+                const uint32_t want = count < resident ? static_cast<uint32_t>(count) : n_blocks;  // total_to_evict
+                const uint32_t n_sample = p.sampling_size < n_blocks ? p.sampling_size : n_blocks;
+                const uint32_t k = want < n_sample ? want : n_sample;
+                // the draws, in sequence (lane 0), then their modulo and the sampled blocks' times (all lanes)
+                if (lane == 0) {
+                    uint64_t x = rng;
+                    uint64_t *raw = reinterpret_cast<uint64_t *>(s_t);
+                    for (uint32_t j = 0; j < n_sample; ++j) {
+                        x ^= x << 13;
+                        x ^= x >> 7;
+                        x ^= x << 17;
+                        raw[j] = x;
+                    }
+                    rng = x;
+                }
+                __syncwarp();
+                for (uint32_t j = lane; j < n_sample; j += 32) {
+                    const uint32_t at = static_cast<uint32_t>(reinterpret_cast<uint64_t *>(s_t)[j] % n_blocks);
+                    s_idx[j] = at;
+                    s_t[j] = ts[at];
+                }
+                __syncwarp();
+                if (lane == 0) PartialSortByTime(sample, k, n_sample);
+                __syncwarp();
+                // the victims as blocks (resolved before the first removal, as the reference resolves them),
+                // and the tail of the vector, which the removals read
+                const uint32_t n_tail = k < n_blocks ? k : n_blocks;
+                for (uint32_t j = lane; j < k; j += 32) {
+                    v_at[j] = s_idx[j];
+                    v_id[j] = blk[s_idx[j]];
+                }
+                for (uint32_t j = lane; j < n_tail; j += 32) {
+                    tail_blk[j] = blk[n_blocks - 1 - j];
+                    tail_ts[j] = ts[n_blocks - 1 - j];
+                }
+                __syncwarp();
+                uint32_t evicted = 0;
+                uint32_t size = n_blocks;
+                for (uint32_t i = 0; i < k && evicted < want; ++i) {
+                    const uint32_t at = v_at[i];
+                    if (at == kGone) continue;  // sampled twice: removed already
+                    const uint32_t id = v_id[i];
+                    const uint32_t last = size - 1;
+                    const uint32_t moved = tail_blk[n_blocks - 1 - last];  // the block that sits last now
+                    const int64_t moved_t = tail_ts[n_blocks - 1 - last];
+                    if (lane == 0) {
+                        if (at != last) {
+                            blk[at] = moved;
+                            ts[at] = moved_t;
+                            pos[moved] = at + 1u;
+                            if (n_blocks - 1 - at < n_tail) {  // the staged tail follows
+                                tail_blk[n_blocks - 1 - at] = moved;
+                                tail_ts[n_blocks - 1 - at] = moved_t;
+                            }
+                        }
+                        pos[id] = 0u;
+                    }
+                    __syncwarp();
+                    // later victims: further samples of this block are gone; the moved block has a new index
+                    for (uint32_t j = i + 1 + lane; j < k; j += 32) {
+                        if (v_at[j] == kGone) continue;
+                        if (v_id[j] == id) {
+                            v_at[j] = kGone;
+                        } else if (at != last && v_id[j] == moved) {
+                            v_at[j] = at;
+                        }
+                    }
+                    __syncwarp();
+                    --size;
+                    ++evicted;
+                }
+                resident = size;
+                if (evicted == 0) break;
+                total += evicted;
+            }
+        }
+        if (lane == 0 && p.ext_hit != nullptr) {
+            p.ext_hit[out0 + t] = ext;
+            p.int_hit[out0 + t] = inte;
+            p.written[out0 + t] = wr;
+            p.cache_blocks[out0 + t] = resident;
+        }
+        sum_ext += ext;
+        sum_int += inte;
+        sum_wr += wr;
+    }
+    if (lane == 0 && p.totals != nullptr) {
+        int64_t *tot = p.totals + static_cast<int64_t>(cfg) * 4;
+        tot[0] = sum_ext;
+        tot[1] = sum_int;
+        tot[2] = sum_wr;
+        tot[3] = resident;
+    }
+}
+
+struct RandomLayout {
+    size_t table_off, ids_off, pos_off, blk_off, ts_off, total;
+};
+
+RandomLayout RandomLayoutFor(int64_t n_keys, int32_t n_configs) {
+    auto up = [](size_t x) { return (x + 255) / 256 * 256; };
+    const size_t keys = static_cast<size_t>(n_keys > 0 ? n_keys : 1);
+    RandomLayout l;
+    l.table_off = 256;
+    l.ids_off = l.table_off + up(SlotsFor(n_keys) * sizeof(ulonglong2));
+    l.pos_off = l.ids_off + up(keys * sizeof(uint32_t));
+    l.blk_off = l.pos_off + up(keys * n_configs * sizeof(uint32_t));
+    l.ts_off = l.blk_off + up(keys * n_configs * sizeof(uint32_t));
+    l.total = l.ts_off + up(keys * n_configs * sizeof(int64_t));
+    return l;
+}
+
+}  // namespace
+}  // namespace kvcm
+
+extern "C" {
+
+int32_t kvcm_b200_selftest_partial_sort(uint32_t *h_idx, int64_t *h_times, uint32_t k, uint32_t n) {
+    if (h_idx == nullptr || h_times == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (k > n) return KVCM_EC_BADARGS;
+    kvcm::Sample s{h_idx, h_times};
+    kvcm::PartialSortByTime(s, k, n);
+    return KVCM_OK;
+}
+
+int64_t kvcm_b200_replay_random_lru_workspace_bytes(int64_t n_keys_total, int32_t n_configs) {
+    if (n_keys_total < 0 || n_keys_total >= (1ll << 32) - 1 || n_configs <= 0 || n_configs > 65535) return -1;
+    return static_cast<int64_t>(kvcm::RandomLayoutFor(n_keys_total, n_configs).total);
+}
+
+int32_t kvcm_b200_replay_random_lru(const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type,
+                                    const int64_t *d_mask_off, const uint8_t *d_mask_bits, const int64_t *d_timestamps,
+                                    int32_t n_traces, int64_t n_keys_total, const int64_t *d_quota_blocks,
+                                    int32_t n_configs, int32_t evict_batch, int32_t precise, double sample_rate,
+                                    void *d_workspace, int64_t workspace_bytes, int32_t *d_ext_hit, int32_t *d_int_hit,
+                                    int32_t *d_written, int64_t *d_cache_blocks, int64_t *d_totals, uint32_t *d_status,
+                                    kvcm_stream_t stream) {
+    if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
+    if (n_traces < 0 || n_keys_total < 0 || n_configs <= 0 || evict_batch <= 0) return KVCM_EC_BADARGS;
+    // RandomLruEvictionPolicy's constructor (random_lru.cc:5-14): a rate <= 0 means 0.1; the size is a double
+    // division cut to an integer
+    if (sample_rate <= 0.0) sample_rate = 0.1;
+    const double sampling = static_cast<double>(evict_batch) / sample_rate;
+    if (static_cast<uint32_t>(evict_batch) > kvcm::kMaxBatch || sampling > static_cast<double>(kvcm::kMaxSample) ||
+        sampling < 1.0) {
+        return KVCM_EC_OUT_OF_LIMIT;
+    }
+    const int64_t need = kvcm_b200_replay_random_lru_workspace_bytes(n_keys_total, n_configs);
+    if (need < 0) return KVCM_EC_OUT_OF_LIMIT;
+    if (n_traces == 0) return KVCM_OK;
+    const int per_trace = (d_ext_hit != nullptr) + (d_int_hit != nullptr) + (d_written != nullptr) +
+                          (d_cache_blocks != nullptr);
+    if (d_key_off == nullptr || d_trace_type == nullptr || d_quota_blocks == nullptr || d_workspace == nullptr ||
+        (d_keys == nullptr && n_keys_total > 0) || (per_trace != 0 && per_trace != 4) ||
+        (per_trace == 0 && d_totals == nullptr)) {
+        return KVCM_ER_INVALID_ADDRESS;
+    }
+    if (reinterpret_cast<uintptr_t>(d_workspace) & 255u) return KVCM_ER_INVALID_ADDRESS;
+    if (workspace_bytes < need) return KVCM_EC_NOSPC;
+    const kvcm::RandomLayout l = kvcm::RandomLayoutFor(n_keys_total, n_configs);
+    uint8_t *ws = static_cast<uint8_t *>(d_workspace);
+    kvcm::IdTable t;
+    t.cells = reinterpret_cast<unsigned long long *>(ws);
+    t.slots = reinterpret_cast<ulonglong2 *>(ws + l.table_off);
+    t.mask = kvcm::SlotsFor(n_keys_total) - 1;
+    uint32_t *ids = reinterpret_cast<uint32_t *>(ws + l.ids_off);
+    uint32_t *pos = reinterpret_cast<uint32_t *>(ws + l.pos_off);
+    cudaStream_t s = kvcm::AsStream(stream);
+    const int sms = kvcm::GetDeviceInfo().sm_count;
+    const uint64_t n_pos = static_cast<uint64_t>(n_keys_total > 0 ? n_keys_total : 1) * static_cast<uint64_t>(n_configs);
+    kvcm::RandomInitKernel<<<sms * 8, 256, 0, s>>>(t, pos, n_pos);
+    if (n_keys_total > 0) {
+        kvcm::LruClaimIdsKernel<<<sms * 8, 256, 0, s>>>(t, d_keys, n_keys_total, d_status);
+        kvcm::LruLookupIdsKernel<<<sms * 8, 256, 0, s>>>(t, d_keys, n_keys_total, ids);
+    }
+    kvcm::RandomSweep p;
+    p.ids = ids;
+    p.key_off = d_key_off;
+    p.type = d_trace_type;
+    p.mask_off = d_mask_off;
+    p.mask_bits = d_mask_bits;
+    p.timestamps = d_timestamps;
+    p.quota = d_quota_blocks;
+    p.pos = pos;
+    p.blk = reinterpret_cast<uint32_t *>(ws + l.blk_off);
+    p.ts = reinterpret_cast<int64_t *>(ws + l.ts_off);
+    p.ext_hit = d_ext_hit;
+    p.int_hit = d_int_hit;
+    p.written = d_written;
+    p.cache_blocks = d_cache_blocks;
+    p.totals = d_totals;
+    p.n_keys = n_keys_total > 0 ? n_keys_total : 1;
+    p.n_traces = n_traces;
+    p.n_configs = n_configs;
+    p.evict_batch = evict_batch;
+    p.precise = precise;
+    p.sampling_size = static_cast<uint32_t>(sampling);
+    kvcm::RandomLruSweepKernel<<<static_cast<unsigned>(n_configs), 32, 0, s>>>(p);
+    return kvcm::LaunchStatus();
+}
+
+}  // extern "C"

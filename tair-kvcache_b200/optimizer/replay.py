@@ -75,7 +75,7 @@ class LruSweepResult(NamedTuple):
     totals: torch.Tensor  # int64 [n_configs, 4]: external hits, internal hits, written blocks, cached blocks at the end
 
 
-POLICIES = ("lru", "leaf_aware_lru")  # EvictionPolicyType names (kv_cache_manager/optimizer/config/types.cc)
+POLICIES = ("lru", "leaf_aware_lru", "random_lru")  # EvictionPolicyType names (kv_cache_manager/optimizer/config/types.cc)
 
 
 def replay_lru_workspace_bytes(n_keys_total: int, n_configs: int, policy: str = "lru", n_traces: int = 0) -> int:
@@ -83,6 +83,8 @@ def replay_lru_workspace_bytes(n_keys_total: int, n_configs: int, policy: str = 
         n = _cabi.lib().kvcm_b200_replay_leaf_lru_workspace_bytes(n_keys_total, n_traces, n_configs)
     elif policy == "lru":
         n = _cabi.lib().kvcm_b200_replay_lru_workspace_bytes(n_keys_total, n_configs)
+    elif policy == "random_lru":
+        n = _cabi.lib().kvcm_b200_replay_random_lru_workspace_bytes(n_keys_total, n_configs)
     else:
         raise ValueError("eviction policy %r is not built (have: %s)" % (policy, ", ".join(POLICIES)))
     if n < 0:
@@ -94,10 +96,11 @@ def RunTracesLru(keys: torch.Tensor, key_off: torch.Tensor, trace_type: torch.Te
                  mask_off: Optional[torch.Tensor] = None, evict_batch: int = 100, precise: bool = False,
                  workspace: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
                  per_trace: bool = True, mask_bits: Optional[torch.Tensor] = None, policy: str = "lru",
-                 timestamps: Optional[torch.Tensor] = None) -> LruSweepResult:
-    """The replay of RunTraces with the reference's "lru" (default) or "leaf_aware_lru" eviction policy
-    (policy; timestamps = the traces' timestamp_us as an int64 CUDA tensor, read by "leaf_aware_lru" only, the
-    trace number when None), once per entry of quota_blocks (the
+                 timestamps: Optional[torch.Tensor] = None, sample_rate: float = 0.0) -> LruSweepResult:
+    """The replay of RunTraces with the reference's "lru" (default), "leaf_aware_lru" or "random_lru" eviction
+    policy (policy; timestamps = the traces' timestamp_us as an int64 CUDA tensor, read by "leaf_aware_lru" and
+    "random_lru", the trace number when None; sample_rate = RandomLruParams.sample_rate of "random_lru", 0.1 when
+    <= 0 as in the reference), once per entry of quota_blocks (the
     points of a tradeoff curve: quota_capacity * used_percentage in blocks), all configurations in one launch.
     evict_batch / precise: eviction_batch_size_per_instance and the eviction mode (False = the rough modes, which
     evict whole batches; True = INSTANCE_PRECISE).  per_trace=False skips the [n_configs, n_traces] records and
@@ -126,11 +129,20 @@ def RunTracesLru(keys: torch.Tensor, key_off: torch.Tensor, trace_type: torch.Te
     if per_trace and n_traces == 0:
         return LruSweepResult(ext, inte, wr, size, totals)
     _cabi.bind_device(dev.index)
+    if policy in ("leaf_aware_lru", "random_lru") and timestamps is not None:
+        if timestamps.dtype != torch.int64 or timestamps.numel() != n_traces or timestamps.device != dev:
+            raise ValueError("timestamps must be an int64 tensor with one entry per trace, on the keys' device")
+        timestamps = timestamps.contiguous()
+    if policy == "random_lru":
+        _cabi.call("kvcm_b200_replay_random_lru", keys.data_ptr(), key_off.data_ptr(), trace_type.data_ptr(),
+                   mask_off.contiguous().data_ptr() if mask_off is not None else None,
+                   _mask_bits_ptr(mask_bits, keys), timestamps.data_ptr() if timestamps is not None else None,
+                   n_traces, keys.numel(), quota.data_ptr(), n_cfg, int(evict_batch), 1 if precise else 0,
+                   float(sample_rate), workspace.data_ptr(), workspace.numel(), ptr(ext), ptr(inte), ptr(wr),
+                   ptr(size), totals.data_ptr(), status.data_ptr() if status is not None else None,
+                   torch.cuda.current_stream(dev).cuda_stream)
+        return LruSweepResult(ext, inte, wr, size, totals)
     if policy == "leaf_aware_lru":
-        if timestamps is not None:
-            if timestamps.dtype != torch.int64 or timestamps.numel() != n_traces or timestamps.device != dev:
-                raise ValueError("timestamps must be an int64 tensor with one entry per trace, on the keys' device")
-            timestamps = timestamps.contiguous()
         _cabi.call("kvcm_b200_replay_leaf_lru", keys.data_ptr(), key_off.data_ptr(), trace_type.data_ptr(),
                    mask_off.contiguous().data_ptr() if mask_off is not None else None,
                    _mask_bits_ptr(mask_bits, keys), timestamps.data_ptr() if timestamps is not None else None,

@@ -27,11 +27,11 @@ def _g(x: float) -> str:
 
 def replay_instance(traces: List[tr.Trace], device, rw_separation: bool = False,
                     quota_blocks: Union[None, int, Sequence[int]] = None, evict_batch: int = 100,
-                    precise: bool = False, policy: str = "lru"):
+                    precise: bool = False, policy: str = "lru", sample_rate: float = 0.0):
     """Replays the traces of one instance.  As OptimizerRunner::RunTrace does, only prefix_match queries are
     replayed, dialog turns are skipped in read/write-separation mode and Get/Write traces are skipped otherwise.
-    quota_blocks = None: nothing is ever evicted; an int: eviction under `policy` ("lru" or "leaf_aware_lru",
-    the instance's eviction_policy_type) at that quota (quota_capacity *
+    quota_blocks = None: nothing is ever evicted; an int: eviction under `policy` ("lru", "leaf_aware_lru" or
+    "random_lru" with its `sample_rate`: the instance's eviction_policy_type and eviction_policy_params) at that quota (quota_capacity *
     used_percentage, in blocks); a sequence: one record per quota, all replayed in one launch.  evict_batch and
     precise are eviction_batch_size_per_instance and the eviction mode (False = the rough modes)."""
     keep = _kept(traces, rw_separation)
@@ -58,7 +58,7 @@ def replay_instance(traces: List[tr.Trace], device, rw_separation: bool = False,
     quotas = [int(quota_blocks)] if np.isscalar(quota_blocks) else [int(q) for q in quota_blocks]
     tr.require_no_repeats(keep, keys, off)
     res = [x.cpu().numpy() for x in RunTracesLru(d_keys, d_off, d_kind, quotas, d_mask, evict_batch, precise,
-                                                 mask_bits=d_bits, policy=policy,
+                                                 mask_bits=d_bits, policy=policy, sample_rate=sample_rate,
                                                  timestamps=torch.from_numpy(ts).to(device))[:4]]
     recs = [record(*(x[c] for x in res)) for c in range(len(quotas))]
     return recs[0] if np.isscalar(quota_blocks) else recs
@@ -177,7 +177,8 @@ def run_trace_file(trace_path: str, trace_type: str, output_dir: str, device=Non
                    quota_blocks: Union[None, int, Sequence[int], Dict[str, Union[int, Sequence[int]]]] = None,
                    evict_batch: int = 100, precise: bool = False,
                    policy: Union[str, Dict[str, str]] = "lru",
-                   groups: Optional[Sequence[dict]] = None, mode: int = 1):
+                   groups: Optional[Sequence[dict]] = None, mode: int = 1,
+                   sample_rate: Union[float, Dict[str, float]] = 0.0):
     """Loads a trace file, replays every instance on the GPU and writes `<instance>_hit_rates.csv` per instance
     (`<instance>_quota<q>_hit_rates.csv` per instance and quota when quota_blocks is a sequence).  Every instance is
     replayed on its own, except the instances of a group in `groups` (dicts with "instances" = the ids and "quota" =
@@ -204,7 +205,8 @@ def run_trace_file(trace_path: str, trace_type: str, output_dir: str, device=Non
         sweep = quota is not None and not np.isscalar(quota)
         # policy: one name for all instances, or a dict by instance ("lru" for instances it does not name)
         pol = policy.get(instance_id, "lru") if isinstance(policy, dict) else policy
-        rec = replay_instance(ts, device, rw_separation, quota, evict_batch, precise, pol)
+        rate = sample_rate.get(instance_id, 0.0) if isinstance(sample_rate, dict) else sample_rate
+        rec = replay_instance(ts, device, rw_separation, quota, evict_batch, precise, pol, rate)
         for c, r in enumerate(rec if sweep else [rec]):
             if (r["kind"] != tr.WRITE_CACHE).any():
                 name = "%s_quota%d_hit_rates.csv" % (instance_id, int(quota[c])) if sweep else \
@@ -222,8 +224,8 @@ def parse_startup_config(config: Union[str, dict]) -> dict:
     """The Optimizer's startup configuration (kv_cache_manager/optimizer/optimizer_startup_config_load.json, read
     by kv_cache_manager/optimizer/config/optimizer_config.cc:4-12, instance_group_config.cc:5-12,
     instance_config.cc:6-22, eviction_config.cc:5-8) reduced to what the GPU replay needs.  Raises
-    NotImplementedError for what it cannot replay exactly: the "random_lru" policy, hierarchical eviction, and
-    groups of several instances unless all of them use "lru" (those come back under "groups")."""
+    NotImplementedError for what it cannot replay exactly: hierarchical eviction, and groups of several instances
+    unless all of them use "lru" (those come back under "groups")."""
     if isinstance(config, str):
         with open(config) as f:
             config = json.load(f)
@@ -232,7 +234,7 @@ def parse_startup_config(config: Union[str, dict]) -> dict:
     if mode not in (EVICTION_MODE_UNSPECIFIED, EVICTION_MODE_GROUP_ROUGH, EVICTION_MODE_INSTANCE_ROUGH,
                     EVICTION_MODE_INSTANCE_PRECISE):
         raise ValueError("unknown eviction_mode %r" % mode)
-    quotas, block_sizes, policies, shared = {}, {}, {}, []
+    quotas, block_sizes, policies, sample_rates, shared = {}, {}, {}, {}, []
     for group in config.get("instance_groups", []):
         instances = group.get("instances", [])
         if group.get("hierarchical_eviction_enabled", False):
@@ -246,11 +248,14 @@ def parse_startup_config(config: Union[str, dict]) -> dict:
                                quota=int(group["quota_capacity"] * float(group.get("used_percentage", 1.0)))))
         for inst in instances:
             policy = inst.get("eviction_policy_type", "lru")
-            if policy not in ("lru", "leaf_aware_lru") and mode != EVICTION_MODE_UNSPECIFIED:
-                raise NotImplementedError("instance %r: eviction policy %r is not replayed (\"lru\" and "
-                                          "\"leaf_aware_lru\" are)" % (inst.get("instance_id"), policy))
+            if policy not in ("lru", "leaf_aware_lru", "random_lru") and mode != EVICTION_MODE_UNSPECIFIED:
+                raise NotImplementedError("instance %r: eviction policy %r is not replayed (\"lru\", "
+                                          "\"leaf_aware_lru\" and \"random_lru\" are)"
+                                          % (inst.get("instance_id"), policy))
             iid = str(inst["instance_id"])
             policies[iid] = policy
+            # RandomLruParams (kv_cache_manager/optimizer/config/instance_config.cc:18-22, eviction_config.h:20-29)
+            sample_rates[iid] = float((inst.get("eviction_policy_params") or {}).get("sample_rate", 0.0))
             block_sizes[iid] = int(inst.get("block_size", 16))
             # eviction_manager.cc:249-266: quota = size_t(quota_capacity * used_percentage); an unspecified mode
             # never evicts (:60-63)
@@ -259,7 +264,8 @@ def parse_startup_config(config: Union[str, dict]) -> dict:
     return dict(trace_file_path=config.get("trace_file_path"), trace_type=config.get("trace_type"),
                 output_result_path=config.get("output_result_path"), quota_blocks=quotas, block_sizes=block_sizes,
                 evict_batch=int(ev.get("eviction_batch_size_per_instance", 100)),
-                precise=mode == EVICTION_MODE_INSTANCE_PRECISE, policies=policies, groups=shared, mode=mode)
+                precise=mode == EVICTION_MODE_INSTANCE_PRECISE, policies=policies, sample_rates=sample_rates,
+                groups=shared, mode=mode)
 
 
 def run_startup_config(config: Union[str, dict], device=None, rw_separation: Optional[bool] = None):
@@ -273,4 +279,4 @@ def run_startup_config(config: Union[str, dict], device=None, rw_separation: Opt
         rw_separation = c["trace_type"] == "publisher_log"
     return run_trace_file(c["trace_file_path"], c["trace_type"], c["output_result_path"], device, c["block_sizes"],
                           rw_separation, c["quota_blocks"] or None, c["evict_batch"], c["precise"], c["policies"],
-                          c["groups"], c["mode"] or 1)
+                          c["groups"], c["mode"] or 1, c["sample_rates"])

@@ -143,3 +143,25 @@ def test_block_table_helpers_match_the_connector_loop():
             assert tok.tolist() == reference_loop(mbs, ids, M, L)
     with pytest.raises(ValueError):
         generate_block_page_table([0], [1, 2], 32, 64)
+
+
+def test_partial_sort_restatement_matches_the_standard_library():
+    """The heap-select + sort-heap routine the random_lru sweep orders its samples with, run on the host through
+    the C ABI, against std::partial_sort called the way the reference calls it
+    (kv_cache_manager/optimizer/eviction_policy/random_lru.cc:59-82): same order of the first k, ties included."""
+    from oracle import kvcm_oracle as oracle
+    rng = np.random.default_rng(21)
+    for trial in range(300):
+        n_blocks = int(rng.integers(1, 400))
+        times = rng.integers(0, int(rng.integers(1, 12)), size=n_blocks).astype(np.int64)  # few distinct times: ties
+        n = int(rng.integers(1, 300))
+        k = int(rng.integers(0, n + 1))
+        sample = rng.integers(0, n_blocks, size=n).astype(np.uint64)                        # with repeats
+        want = oracle.partial_sort_by_time(sample, k, times)
+        idx = sample.astype(np.uint32)
+        t = times[sample.astype(np.int64)].copy()
+        rc = _cabi.lib().kvcm_b200_selftest_partial_sort(idx.ctypes.data, t.ctypes.data, k, n)
+        assert rc == _cabi.KVCM_OK
+        assert np.array_equal(idx[:k].astype(np.uint64), want[:k]), (trial, n, k)
+        assert np.array_equal(t[:k], times[want[:k].astype(np.int64)])
+    assert _cabi.lib().kvcm_b200_selftest_partial_sort(None, None, 0, 0) == _cabi.KVCM_ER_INVALID_ADDRESS

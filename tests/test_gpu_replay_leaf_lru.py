@@ -119,4 +119,4 @@ def test_vector_masks_totals_only_and_empty_inputs():
     assert ext.shape == (1, 2) and size[0].tolist() == [0, 0]
     with pytest.raises(ValueError):
         RunTracesLru(torch.zeros(1, dtype=torch.int64, device=DEV), torch.tensor([0, 1], device=DEV),
-                     torch.zeros(1, dtype=torch.uint8, device=DEV), [5], policy="random_lru")
+                     torch.zeros(1, dtype=torch.uint8, device=DEV), [5], policy="fifo")

@@ -111,6 +111,9 @@ def test_startup_config_of_the_reference_is_understood():
     cfg["instance_groups"][0]["instances"][0]["eviction_policy_type"] = "leaf_aware_lru"
     assert parse_startup_config(cfg)["policies"] == {"3780643326877293460": "leaf_aware_lru"}
     cfg["instance_groups"][0]["instances"][0]["eviction_policy_type"] = "random_lru"
+    c = parse_startup_config(cfg)
+    assert c["policies"] == {"3780643326877293460": "random_lru"} and c["sample_rates"] == {"3780643326877293460": 0.1}
+    cfg["instance_groups"][0]["instances"][0]["eviction_policy_type"] = "fifo"
     with pytest.raises(NotImplementedError):
         parse_startup_config(cfg)
     cfg["instance_groups"][0]["instances"][0]["eviction_policy_type"] = "lru"
