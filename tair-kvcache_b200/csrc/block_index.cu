@@ -40,6 +40,10 @@ struct kvcm_b200_index {
     // the status transitions), and the bound at which the next upsert rebuilds the table first (0 = never).
     uint64_t tomb_debt;
     uint64_t auto_rehash_at;
+    // Host-side upper bound of the slots in use (every key ever passed to upsert since the last clear; refreshed
+    // to the true figure by kvcm_b200_index_usage).  While bound + batch stays under the limit an upsert launch
+    // cannot overfill the table and runs without per-key seat atomics.
+    uint64_t used_upper;
 };
 
 // Exchange area of one rank of a routed query: the inbox the other ranks store the keys this rank owns into,
@@ -180,7 +184,12 @@ __device__ __forceinline__ void AddCell(uint64_t *cell, int64_t delta) {
 // Several threads of one launch may insert the same new key: all of them walk the same chain, free slots
 // only get fewer while the launch runs, and a thread whose claim fails looks at what took the slot - the
 // key itself (then it only stores the value) or another key (then it walks the chain again).
-__device__ __forceinline__ bool UpsertOne(const IndexView &ix, uint64_t key, uint64_t value) {
+// kCareful: the launch could push the slots in use past the bound, so every claim of an EMPTY slot takes a seat
+// on the shared counter first.  Otherwise (the host knows that even if every key of the launch claimed one the bound
+// holds) nothing is counted on the way: the caller sums `d_live` and `d_used` per warp and adds them once.
+template <bool kCareful>
+__device__ __forceinline__ bool UpsertOne(const IndexView &ix, uint64_t key, uint64_t value, int32_t *d_live,
+                                          int32_t *d_used) {
     unsigned long long *words = reinterpret_cast<unsigned long long *>(ix.slots);
     const uint64_t mixed = Mix(key);
     const uint64_t home = mixed & ix.mask;
@@ -215,14 +224,14 @@ __device__ __forceinline__ bool UpsertOne(const IndexView &ix, uint64_t key, uin
                 atomicExch(&words[2 * tomb + 1], value);
                 if (was == kTombKey) {
                     ix.tags[tomb] = TagOf(mixed);  // readers of later launches find the slot through its tag
-                    AddCell(&ix.cells[2], 1);
+                    *d_live += 1;
                 }
                 done = stored = true;
             }  // else another key took the tombstone: walk again
         } else if (empty == ~0ull) {
             done = true;  // no EMPTY slot on the whole table: cannot happen below the limit
         } else {
-            if (!seated) {
+            if (kCareful && !seated) {
                 const uint64_t used = atomicAdd(reinterpret_cast<unsigned long long *>(&ix.cells[3]), 1ull);
                 if (used >= ix.max_live) {
                     AddCell(&ix.cells[3], -1);
@@ -234,8 +243,9 @@ __device__ __forceinline__ bool UpsertOne(const IndexView &ix, uint64_t key, uin
             if (was == kEmptyKey) {
                 atomicExch(&words[2 * empty + 1], value);
                 ix.tags[empty] = TagOf(mixed);
-                AddCell(&ix.cells[2], 1);
-                return true;  // the seat is now this slot's
+                *d_live += 1;
+                if (!kCareful) *d_used += 1;  // in careful mode the seat is this slot's count already
+                return true;
             }
             if (was == key) {
                 atomicExch(&words[2 * empty + 1], value);
@@ -247,19 +257,36 @@ __device__ __forceinline__ bool UpsertOne(const IndexView &ix, uint64_t key, uin
     return stored;
 }
 
-__global__ void UpsertKernel(IndexView ix, const int64_t *__restrict__ keys, const uint64_t *__restrict__ values,
-                             uint64_t uniform_value, int64_t n, Shard shard, uint32_t *status) {
-    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const uint64_t key = static_cast<uint64_t>(keys[i]);
-    if (!Owns(shard, key)) return;
-    const uint64_t value = (values != nullptr ? values[i] : uniform_value) | KVCM_VAL_PRESENT;
-    if (key == kEmptyKey || key == kTombKey) {
-        const uint64_t old = atomicExch(reinterpret_cast<unsigned long long *>(&ix.cells[key - kEmptyKey]), value);
-        if (old == 0) AddCell(&ix.cells[2], 1);
-        return;
+// One atomic per warp and counter instead of one per key: every lane of the warp gets here.
+__device__ __forceinline__ void AddCellsPerWarp(const IndexView &ix, int32_t d_live, int32_t d_used) {
+    const int32_t live = __reduce_add_sync(0xffffffffu, d_live);
+    const int32_t used = __reduce_add_sync(0xffffffffu, d_used);
+    if (LaneId() == 0) {
+        if (live != 0) AddCell(&ix.cells[2], live);
+        if (used != 0) AddCell(&ix.cells[3], used);
     }
-    if (!UpsertOne(ix, key, value) && status != nullptr) atomicAdd(&status[0], 1u);
+}
+
+template <bool kCareful>
+__global__ void __launch_bounds__(256)
+    UpsertKernel(IndexView ix, const int64_t *__restrict__ keys, const uint64_t *__restrict__ values,
+                 uint64_t uniform_value, int64_t n, Shard shard, uint32_t *status) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    int32_t d_live = 0, d_used = 0;
+    if (i < n) {
+        const uint64_t key = static_cast<uint64_t>(keys[i]);
+        if (Owns(shard, key)) {
+            const uint64_t value = (values != nullptr ? values[i] : uniform_value) | KVCM_VAL_PRESENT;
+            if (key == kEmptyKey || key == kTombKey) {
+                const uint64_t old =
+                    atomicExch(reinterpret_cast<unsigned long long *>(&ix.cells[key - kEmptyKey]), value);
+                if (old == 0) d_live = 1;
+            } else if (!UpsertOne<kCareful>(ix, key, value, &d_live, &d_used) && status != nullptr) {
+                atomicAdd(&status[0], 1u);
+            }
+        }
+    }
+    AddCellsPerWarp(ix, d_live, d_used);
 }
 
 __device__ __forceinline__ uint64_t LoadKeyCoherent(const ulonglong2 *slot) {
@@ -274,44 +301,50 @@ __device__ __forceinline__ uint64_t LoadKeyCoherent(const ulonglong2 *slot) {
 // an erase launch slots only move key -> tombstone -> EMPTY, so "the next slot is EMPTY" stays true once seen.
 // The tag of a slot may be written by the thread that made it a tombstone and by the thread that freed it;
 // whoever writes a tombstone tag looks at the slot again afterwards, so the tag ends up EMPTY when the slot did.
-__device__ __forceinline__ void ReleaseSlot(const IndexView &ix, uint64_t slot) {
+// Returns the number of slots it turned EMPTY (the caller takes them off the count of slots in use).
+__device__ __forceinline__ int32_t ReleaseSlot(const IndexView &ix, uint64_t slot) {
     unsigned long long *words = reinterpret_cast<unsigned long long *>(ix.slots);
     atomicExch(&words[2 * slot + 1], 0ull);
     ix.tags[slot] = kTagTomb;
     if (LoadKeyCoherent(ix.slots + slot) == kEmptyKey) ix.tags[slot] = kTagEmpty;
-    if (LoadKeyCoherent(ix.slots + ((slot + 1) & ix.mask)) != kEmptyKey) return;
+    if (LoadKeyCoherent(ix.slots + ((slot + 1) & ix.mask)) != kEmptyKey) return 0;
     uint64_t p = slot;
+    int32_t freed = 0;
     for (uint64_t n = 0; n <= ix.mask; ++n) {
         if (atomicCAS(&words[2 * p], kTombKey, kEmptyKey) != kTombKey) break;
         ix.tags[p] = kTagEmpty;
-        AddCell(&ix.cells[3], -1);
+        ++freed;
         p = (p - 1) & ix.mask;
     }
+    return freed;
 }
 
-__global__ void EraseKernel(IndexView ix, const int64_t *__restrict__ keys, int64_t n) {
+__global__ void __launch_bounds__(256) EraseKernel(IndexView ix, const int64_t *__restrict__ keys, int64_t n) {
     const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const uint64_t key = static_cast<uint64_t>(keys[i]);
-    if (key == kEmptyKey || key == kTombKey) {
-        const uint64_t old = atomicExch(reinterpret_cast<unsigned long long *>(&ix.cells[key - kEmptyKey]), 0ull);
-        if (old != 0) AddCell(&ix.cells[2], -1);
-        return;
-    }
-    unsigned long long *words = reinterpret_cast<unsigned long long *>(ix.slots);
-    uint64_t slot = Mix(key) & ix.mask;
-    for (uint64_t probe = 0; probe <= ix.mask; ++probe) {
-        const uint64_t seen = LoadSlot(ix.slots + slot).x;
-        if (seen == kEmptyKey) return;
-        if (seen == key) {
-            if (atomicCAS(&words[2 * slot], key, kTombKey) == key) {
-                AddCell(&ix.cells[2], -1);
-                ReleaseSlot(ix, slot);
+    int32_t d_live = 0, d_used = 0;
+    if (i < n) {
+        const uint64_t key = static_cast<uint64_t>(keys[i]);
+        if (key == kEmptyKey || key == kTombKey) {
+            const uint64_t old = atomicExch(reinterpret_cast<unsigned long long *>(&ix.cells[key - kEmptyKey]), 0ull);
+            if (old != 0) d_live = -1;
+        } else {
+            unsigned long long *words = reinterpret_cast<unsigned long long *>(ix.slots);
+            uint64_t slot = Mix(key) & ix.mask;
+            for (uint64_t probe = 0; probe <= ix.mask; ++probe) {
+                const uint64_t seen = LoadSlot(ix.slots + slot).x;
+                if (seen == kEmptyKey) break;
+                if (seen == key) {
+                    if (atomicCAS(&words[2 * slot], key, kTombKey) == key) {
+                        d_live = -1;
+                        d_used = -ReleaseSlot(ix, slot);
+                    }
+                    break;
+                }
+                slot = (slot + 1) & ix.mask;
             }
-            return;
         }
-        slot = (slot + 1) & ix.mask;
     }
+    AddCellsPerWarp(ix, d_live, d_used);
 }
 
 // ---- location-status transitions on the value word (MetaSearcher::BatchUpdateLocationStatus,
@@ -401,7 +434,10 @@ __global__ void UpdateStatusKernel(IndexView ix, const int64_t *__restrict__ key
                     AddCell(&ix.cells[2], -1);
                     if (!in_cell) {
                         unsigned long long *words = reinterpret_cast<unsigned long long *>(ix.slots);
-                        if (atomicCAS(&words[2 * slot], key, kTombKey) == key) ReleaseSlot(ix, slot);
+                        if (atomicCAS(&words[2 * slot], key, kTombKey) == key) {
+                            const int32_t freed = ReleaseSlot(ix, slot);
+                            if (freed != 0) AddCell(&ix.cells[3], -freed);
+                        }
                     }
                 }
                 break;
@@ -451,7 +487,12 @@ __global__ void ReinsertKernel(IndexView ix, const ulonglong2 *__restrict__ pair
     const uint64_t n = *counter;
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
-        if (!UpsertOne(ix, pairs[i].x, pairs[i].y) && status != nullptr) atomicAdd(&status[0], 1u);
+        int32_t d_live = 0, d_used = 0;
+        if (!UpsertOne<false>(ix, pairs[i].x, pairs[i].y, &d_live, &d_used) && status != nullptr) {
+            atomicAdd(&status[0], 1u);
+        }
+        if (d_live != 0) AddCell(&ix.cells[2], d_live);  // the pairs fitted before: no bound to watch
+        if (d_used != 0) AddCell(&ix.cells[3], d_used);
     }
 }
 
@@ -911,6 +952,7 @@ int32_t kvcm_b200_index_create(int64_t max_keys, kvcm_b200_index_t **out) {
     ix->max_live = n_slots - n_slots / 8;  // the matchers rely on at least one EMPTY slot per chain
     ix->tomb_debt = 0;
     ix->auto_rehash_at = n_slots / 8;
+    ix->used_upper = 0;
     cudaGetDevice(&ix->device);
     if (cudaMalloc(&ix->base, kvcm::kIndexHeaderBytes + n_slots * (sizeof(ulonglong2) + 1)) != cudaSuccess) {
         cudaGetLastError();
@@ -1027,6 +1069,7 @@ int32_t kvcm_b200_index_clear(kvcm_b200_index_t *ix, kvcm_stream_t stream) {
     if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
     const unsigned grid = static_cast<unsigned>(kvcm::GetDeviceInfo().sm_count * 8);
     ix->tomb_debt = 0;
+    ix->used_upper = 0;
     kvcm::ClearKernel<<<grid, 256, 0, kvcm::AsStream(stream)>>>(kvcm::LocalView(ix));
     return kvcm::LaunchStatus();
 }
@@ -1058,6 +1101,7 @@ int32_t kvcm_b200_index_usage(kvcm_b200_index_t *ix, int64_t *slots, int64_t *li
     if (slots != nullptr) *slots = static_cast<int64_t>(ix->n_slots);
     if (live_keys != nullptr) *live_keys = static_cast<int64_t>(cells[0]);
     if (used_slots != nullptr) *used_slots = static_cast<int64_t>(cells[1]);
+    ix->used_upper = cells[1];  // everything enqueued before the read has run: this is the true figure
     return KVCM_OK;
 }
 
@@ -1140,6 +1184,21 @@ int32_t kvcm_b200_index_update_status_sharded(kvcm_b200_index_t *ix, const int64
                         stream);
 }
 
+static void LaunchUpsert(kvcm_b200_index_t *ix, const int64_t *d_keys, const uint64_t *d_values, uint64_t uniform_value,
+                         int64_t n, kvcm::Shard shard, uint32_t *d_status, kvcm_stream_t stream) {
+    const bool careful = ix->used_upper + static_cast<uint64_t>(n) > ix->max_live;
+    ix->used_upper += static_cast<uint64_t>(n);
+    if (ix->used_upper > ix->n_slots) ix->used_upper = ix->n_slots;
+    const unsigned grid = kvcm::GridFor(n, 256);
+    if (careful) {
+        kvcm::UpsertKernel<true><<<grid, 256, 0, kvcm::AsStream(stream)>>>(kvcm::LocalView(ix), d_keys, d_values,
+                                                                            uniform_value, n, shard, d_status);
+    } else {
+        kvcm::UpsertKernel<false><<<grid, 256, 0, kvcm::AsStream(stream)>>>(kvcm::LocalView(ix), d_keys, d_values,
+                                                                             uniform_value, n, shard, d_status);
+    }
+}
+
 int32_t kvcm_b200_index_upsert(kvcm_b200_index_t *ix, const int64_t *d_keys, const uint64_t *d_values,
                                uint64_t uniform_value, int64_t n, uint32_t *d_status, kvcm_stream_t stream) {
     if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
@@ -1147,8 +1206,7 @@ int32_t kvcm_b200_index_upsert(kvcm_b200_index_t *ix, const int64_t *d_keys, con
     if (n == 0) return KVCM_OK;
     if (d_keys == nullptr) return KVCM_ER_INVALID_ADDRESS;
     MaybeRehash(ix, stream);
-    kvcm::UpsertKernel<<<kvcm::GridFor(n, 256), 256, 0, kvcm::AsStream(stream)>>>(
-        kvcm::LocalView(ix), d_keys, d_values, uniform_value, n, kvcm::Shard{1, 0}, d_status);
+    LaunchUpsert(ix, d_keys, d_values, uniform_value, n, kvcm::Shard{1, 0}, d_status, stream);
     return kvcm::LaunchStatus();
 }
 
@@ -1160,9 +1218,8 @@ int32_t kvcm_b200_index_upsert_sharded(kvcm_b200_index_t *ix, const int64_t *d_k
     if (n == 0) return KVCM_OK;
     if (d_keys == nullptr) return KVCM_ER_INVALID_ADDRESS;
     MaybeRehash(ix, stream);
-    kvcm::UpsertKernel<<<kvcm::GridFor(n, 256), 256, 0, kvcm::AsStream(stream)>>>(
-        kvcm::LocalView(ix), d_keys, d_values, uniform_value, n,
-        kvcm::Shard{static_cast<uint32_t>(shard_count), static_cast<uint32_t>(shard_rank)}, d_status);
+    LaunchUpsert(ix, d_keys, d_values, uniform_value, n,
+                 kvcm::Shard{static_cast<uint32_t>(shard_count), static_cast<uint32_t>(shard_rank)}, d_status, stream);
     return kvcm::LaunchStatus();
 }
 
