@@ -629,6 +629,18 @@ KVCM_API int32_t kvcm_b200_replay_lru_group(const int64_t *d_keys, const int64_t
                                             int32_t *d_ext_hit, int32_t *d_int_hit, int32_t *d_written,
                                             int64_t *d_cache_blocks, int64_t *d_totals, int64_t *d_instance_blocks,
                                             uint32_t *d_status, kvcm_stream_t stream);
+/* The same call with one more output: d_instance_blocks_per_trace (optional, int64 [n_configs][n_traces][n_instances])
+ * = the usage of EVERY instance of the group after each trace, i.e. ReadRecord::blocks_per_instance, which the
+ * reference writes into the CachedBlocksPerInstance / CachedBlocksAllInstance columns of its hit-rate CSV
+ * (kv_cache_manager/optimizer/analysis/result_analysis.cc:96-113).  Instances are numbered as d_trace_instance
+ * numbers them (the reference lists them in the order of an unordered_map). */
+KVCM_API int32_t kvcm_b200_replay_lru_group_records(
+    const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type, const int64_t *d_mask_off,
+    const uint8_t *d_mask_bits, const int32_t *d_trace_instance, int32_t n_instances, int32_t n_traces,
+    int64_t n_keys_total, const int64_t *d_quota_blocks, int32_t n_configs, int32_t evict_batch, int32_t eviction_mode,
+    void *d_workspace, int64_t workspace_bytes, int32_t *d_ext_hit, int32_t *d_int_hit, int32_t *d_written,
+    int64_t *d_cache_blocks, int64_t *d_totals, int64_t *d_instance_blocks, int64_t *d_instance_blocks_per_trace,
+    uint32_t *d_status, kvcm_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
  * (2d) The same sweep under the "random_lru" eviction policy

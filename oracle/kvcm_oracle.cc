@@ -1046,7 +1046,10 @@ void kvcm_oracle_lru_group_destroy(void *h) { delete static_cast<OracleLruGroup 
 void kvcm_oracle_lru_group_run(void *h, const int64_t *keys, const int64_t *key_off, const uint8_t *type,
                                const int64_t *mask_off, const uint8_t *mask_bits, const int64_t *timestamps,
                                const int32_t *trace_inst, int64_t n_traces, int32_t *ext_hit, int32_t *int_hit,
-                               int32_t *written, int64_t *cache_blocks, int64_t *inst_blocks) {
+                               int32_t *written, int64_t *cache_blocks, int64_t *inst_blocks,
+                               int64_t *inst_blocks_trace) {
+    // inst_blocks_trace (optional, [n_traces][instances]): GetCurrentInstanceUsage of every instance when the
+    // trace's record is made (ReadRecord::blocks_per_instance, optimizer_runner.cc:116-124,196-203)
     auto *g = static_cast<OracleLruGroup *>(h);
     for (int64_t t = 0; t < n_traces; ++t) {
         const size_t i = static_cast<size_t>(trace_inst[t]);
@@ -1070,6 +1073,11 @@ void kvcm_oracle_lru_group_run(void *h, const int64_t *keys, const int64_t *key_
         int_hit[t] = inte;
         written[t] = static_cast<int32_t>(wr);
         cache_blocks[t] = st->n_cached;
+        if (inst_blocks_trace != nullptr) {
+            for (size_t j = 0; j < g->inst.size(); ++j) {
+                inst_blocks_trace[static_cast<size_t>(t) * g->inst.size() + j] = g->inst[j]->n_cached;
+            }
+        }
     }
     if (inst_blocks != nullptr) {
         for (size_t j = 0; j < g->inst.size(); ++j) inst_blocks[j] = g->inst[j]->n_cached;

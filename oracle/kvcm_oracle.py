@@ -515,9 +515,11 @@ class LruGroupReplay:
             lib().kvcm_oracle_lru_group_destroy(self._h)
             self._h = None
 
-    def run(self, keys, key_off, trace_type, trace_instance, mask_off=None, mask_bits=None, timestamps=None):
+    def run(self, keys, key_off, trace_type, trace_instance, mask_off=None, mask_bits=None, timestamps=None,
+            instance_records=False):
         """Returns (external hits, internal hits, written, usage of the trace's instance) per trace and the usage
-        of every instance at the end."""
+        of every instance at the end; with instance_records=True also the usage of every instance after each trace
+        ([n_traces, n_instances]; ReadRecord::blocks_per_instance, optimizer_runner.cc:116-124)."""
         keys, key_off = _i64(keys), _i64(key_off)
         n = len(key_off) - 1
         trace_type = np.ascontiguousarray(trace_type, dtype=np.uint8)
@@ -536,10 +538,12 @@ class LruGroupReplay:
         ext, inte, wr = (np.zeros(n, dtype=np.int32) for _ in range(3))
         cached = np.zeros(n, dtype=np.int64)
         final = np.zeros(self.n_instances, dtype=np.int64)
+        every = np.zeros((max(n, 1), self.n_instances), dtype=np.int64)[:n]
         lib().kvcm_oracle_lru_group_run(self._h, _ptr(keys, ctypes.c_int64), _ptr(key_off, ctypes.c_int64),
                                         _ptr(trace_type, ctypes.c_uint8), mp, bp, tp,
                                         _ptr(trace_instance, ctypes.c_int32), ctypes.c_int64(n),
                                         _ptr(ext, ctypes.c_int32), _ptr(inte, ctypes.c_int32),
                                         _ptr(wr, ctypes.c_int32), _ptr(cached, ctypes.c_int64),
-                                        _ptr(final, ctypes.c_int64))
-        return ext, inte, wr, cached, final
+                                        _ptr(final, ctypes.c_int64),
+                                        _ptr(every, ctypes.c_int64) if instance_records else None)
+        return (ext, inte, wr, cached, final, every) if instance_records else (ext, inte, wr, cached, final)

@@ -133,6 +133,8 @@ SIGNATURES = {
     "kvcm_b200_replay_lru": [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _vp, _i32, _i32, _i32, _vp, _i64, _vp, _vp, _vp, _vp,
                              _vp, _vp, _vp],
     "kvcm_b200_replay_lru_group_workspace_bytes": [_i64, _i32, _i32],
+    "kvcm_b200_replay_lru_group_records": [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i64, _vp, _i32, _i32, _i32, _vp,
+                                           _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "kvcm_b200_replay_lru_group": [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i64, _vp, _i32, _i32, _i32, _vp, _i64,
                                    _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "kvcm_b200_replay_leaf_lru_workspace_bytes": [_i64, _i32, _i32],

@@ -218,6 +218,7 @@ struct LruGroup {
     const int32_t *trace_inst;  // per trace, 0 .. n_instances-1
     const int64_t *queue_base;  // [n_instances + 1]: where each instance's region of the queue starts
     int64_t *inst_blocks;       // optional, [n_configs][n_instances]: usage per instance at the end
+    int64_t *inst_blocks_trace;  // optional, [n_configs][n_traces][n_instances]: usage of every instance after each trace
     int32_t n_instances;
     int32_t mode;               // 1 group rough, 2 instance rough, 3 instance precise
 };
@@ -410,6 +411,11 @@ __global__ void __launch_bounds__(32) LruGroupSweepKernel(const LruSweep p, cons
             p.written[out0 + t] = wr;
             p.cache_blocks[out0 + t] = my_cached;
         }
+        if (g.inst_blocks_trace != nullptr) {  // ReadRecord::blocks_per_instance of the reference's result records
+            __syncwarp();
+            int64_t *row = g.inst_blocks_trace + (out0 + t) * K;
+            for (int32_t j = lane; j < K; j += 32) row[j] = cached[j];
+        }
         sum_ext += ext;
         sum_int += inte;
         sum_wr += wr;
@@ -531,6 +537,22 @@ int32_t kvcm_b200_replay_lru_group(const int64_t *d_keys, const int64_t *d_key_o
                                    int64_t workspace_bytes, int32_t *d_ext_hit, int32_t *d_int_hit, int32_t *d_written,
                                    int64_t *d_cache_blocks, int64_t *d_totals, int64_t *d_instance_blocks,
                                    uint32_t *d_status, kvcm_stream_t stream) {
+    return kvcm_b200_replay_lru_group_records(d_keys, d_key_off, d_trace_type, d_mask_off, d_mask_bits, d_trace_instance,
+                                              n_instances, n_traces, n_keys_total, d_quota_blocks, n_configs,
+                                              evict_batch, eviction_mode, d_workspace, workspace_bytes, d_ext_hit,
+                                              d_int_hit, d_written, d_cache_blocks, d_totals, d_instance_blocks, nullptr,
+                                              d_status, stream);
+}
+
+int32_t kvcm_b200_replay_lru_group_records(const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type,
+                                           const int64_t *d_mask_off, const uint8_t *d_mask_bits,
+                                           const int32_t *d_trace_instance, int32_t n_instances, int32_t n_traces,
+                                           int64_t n_keys_total, const int64_t *d_quota_blocks, int32_t n_configs,
+                                           int32_t evict_batch, int32_t eviction_mode, void *d_workspace,
+                                           int64_t workspace_bytes, int32_t *d_ext_hit, int32_t *d_int_hit,
+                                           int32_t *d_written, int64_t *d_cache_blocks, int64_t *d_totals,
+                                           int64_t *d_instance_blocks, int64_t *d_instance_blocks_per_trace,
+                                           uint32_t *d_status, kvcm_stream_t stream) {
     if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
     if (n_traces < 0 || n_keys_total < 0 || n_configs <= 0 || evict_batch <= 0 || n_instances <= 0 ||
         eviction_mode < 1 || eviction_mode > 3) {
@@ -596,6 +618,7 @@ int32_t kvcm_b200_replay_lru_group(const int64_t *d_keys, const int64_t *d_key_o
     g.trace_inst = d_trace_instance;
     g.queue_base = queue_base;
     g.inst_blocks = d_instance_blocks;
+    g.inst_blocks_trace = d_instance_blocks_per_trace;
     g.n_instances = n_instances;
     g.mode = eviction_mode;
     kvcm::LruGroupSweepKernel<<<static_cast<unsigned>(n_configs), 32, sizeof(int64_t) * 4 * n_instances, s>>>(p, g);

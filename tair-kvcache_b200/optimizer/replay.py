@@ -169,6 +169,8 @@ class LruGroupSweepResult(NamedTuple):
     current_cache_blocks: Optional[torch.Tensor]  # int64 [n_configs, n_traces]: usage of the trace's own instance
     totals: torch.Tensor           # int64 [n_configs, 4]: hits ext / int, written blocks, usage of the group at the end
     instance_blocks: torch.Tensor  # int64 [n_configs, n_instances]: usage of every instance at the end
+    # int64 [n_configs, n_traces, n_instances]: usage of every instance after each trace (with instance_records=True)
+    instance_blocks_per_trace: Optional[torch.Tensor] = None
 
 
 def RunTracesLruGroup(keys: torch.Tensor, key_off: torch.Tensor, trace_type: torch.Tensor,
@@ -176,12 +178,14 @@ def RunTracesLruGroup(keys: torch.Tensor, key_off: torch.Tensor, trace_type: tor
                       mask_off: Optional[torch.Tensor] = None, evict_batch: int = 100,
                       mode: int = EVICTION_MODE_GROUP_ROUGH, workspace: Optional[torch.Tensor] = None,
                       status: Optional[torch.Tensor] = None, per_trace: bool = True,
-                      mask_bits: Optional[torch.Tensor] = None) -> LruGroupSweepResult:
+                      mask_bits: Optional[torch.Tensor] = None, instance_records: bool = False) -> LruGroupSweepResult:
     """The "lru" sweep for an instance group whose instances share one quota
     (kv_cache_manager/optimizer/manager/eviction_manager.cc:86-266): trace_instance (int32 per trace, values in
     [0, n_instances)) names each trace's instance, the traces of all instances come in one replay order, and the
     same key in two instances is two blocks.  mode is the reference's eviction_mode: GROUP_ROUGH takes rounds of
-    evict_batch blocks from every instance, the INSTANCE modes take from the writing instance only."""
+    evict_batch blocks from every instance, the INSTANCE modes take from the writing instance only.
+    instance_records=True also returns the usage of every instance after each trace (the reference's
+    ReadRecord::blocks_per_instance, which fills two columns of its hit-rate CSV)."""
     if not keys.is_cuda:
         raise ValueError("keys must be a CUDA tensor: this path has no CPU implementation")
     dev = keys.device
@@ -208,13 +212,16 @@ def RunTracesLruGroup(keys: torch.Tensor, key_off: torch.Tensor, trace_type: tor
         inte, wr = torch.empty_like(ext), torch.empty_like(ext)
         size = torch.empty((n_cfg, n_traces), dtype=torch.int64, device=dev)
     ptr = (lambda t: t.data_ptr() if t is not None and t.numel() > 0 else None)
+    per_inst = None
+    if instance_records:
+        per_inst = torch.zeros((n_cfg, n_traces, int(n_instances)), dtype=torch.int64, device=dev)
     if n_traces == 0:
-        return LruGroupSweepResult(ext, inte, wr, size, totals, inst)
+        return LruGroupSweepResult(ext, inte, wr, size, totals, inst, per_inst)
     _cabi.bind_device(dev.index)
-    _cabi.call("kvcm_b200_replay_lru_group", keys.data_ptr(), key_off.data_ptr(), trace_type.data_ptr(),
+    _cabi.call("kvcm_b200_replay_lru_group_records", keys.data_ptr(), key_off.data_ptr(), trace_type.data_ptr(),
                mask_off.contiguous().data_ptr() if mask_off is not None else None, _mask_bits_ptr(mask_bits, keys),
                trace_instance.data_ptr(), int(n_instances), n_traces, keys.numel(), quota.data_ptr(), n_cfg,
                int(evict_batch), int(mode), workspace.data_ptr(), workspace.numel(), ptr(ext), ptr(inte), ptr(wr),
-               ptr(size), totals.data_ptr(), inst.data_ptr(), status.data_ptr() if status is not None else None,
-               torch.cuda.current_stream(dev).cuda_stream)
-    return LruGroupSweepResult(ext, inte, wr, size, totals, inst)
+               ptr(size), totals.data_ptr(), inst.data_ptr(), ptr(per_inst),
+               status.data_ptr() if status is not None else None, torch.cuda.current_stream(dev).cuda_stream)
+    return LruGroupSweepResult(ext, inte, wr, size, totals, inst, per_inst)

@@ -82,7 +82,8 @@ def replay_group(traces: List[tr.Trace], instance_ids: Sequence[str], device, qu
     order given (all instances together, by timestamp), and returns one record per instance as replay_instance
     does.  mode is the configuration's eviction_mode (1 group rough, 2 instance rough, 3 instance precise;
     kv_cache_manager/optimizer/manager/eviction_manager.cc:57-239).  current_cache_blocks is the usage of the
-    trace's own instance; the usage of the other instances at that moment is not recorded."""
+    trace's own instance; blocks_per_instance [record, instance] is the usage of every instance of the group at
+    that moment, in the order of `instance_ids` (ReadRecord::blocks_per_instance)."""
     index = {iid: j for j, iid in enumerate(instance_ids)}
     keep = [t for t in _kept(traces, rw_separation) if t.instance_id in index]
     keys, off, kind, mask, read = tr.to_csr(keep)
@@ -95,8 +96,10 @@ def replay_group(traces: List[tr.Trace], instance_ids: Sequence[str], device, qu
     tr.require_no_repeats(keep, keys, off)
     res = RunTracesLruGroup(d_keys, d_off, torch.from_numpy(kind).to(device), torch.from_numpy(inst).to(device),
                             len(instance_ids), [int(quota_blocks)], torch.from_numpy(mask).to(device), evict_batch,
-                            mode, mask_bits=torch.from_numpy(bits).to(device) if bits is not None else None)
+                            mode, mask_bits=torch.from_numpy(bits).to(device) if bits is not None else None,
+                            instance_records=True)
     ext, inte, wr, size = (x[0].cpu().numpy() for x in res[:4])
+    every = res.instance_blocks_per_trace[0].cpu().numpy()  # [trace, instance], instances in the order of instance_ids
     internal_read = np.array([tr.masked_count(t.block_mask, len(t.keys)) if t.kind == tr.GET_LOCATION else 0
                               for t in keep], dtype=np.int64)
     external_read = np.where(kind == tr.WRITE_CACHE, 0, read - internal_read)
@@ -105,7 +108,8 @@ def replay_group(traces: List[tr.Trace], instance_ids: Sequence[str], device, qu
         m = inst == j
         out[iid] = dict(timestamp_us=ts[m], kind=kind[m], external_read_blocks=external_read[m],
                         internal_read_blocks=internal_read[m], external_hit_blocks=ext[m],
-                        internal_hit_blocks=inte[m], write_blocks=wr[m], current_cache_blocks=size[m])
+                        internal_hit_blocks=inte[m], write_blocks=wr[m], current_cache_blocks=size[m],
+                        blocks_per_instance=every[m])
     return out
 
 
@@ -151,8 +155,10 @@ def tradeoff_curve(recs: Sequence[Dict[str, np.ndarray]]) -> np.ndarray:
 
 def export_hit_rates(path: str, rec: Dict[str, np.ndarray]) -> None:
     """`<instance>_hit_rates.csv` of HitAnalysis::ExportHitRates (result_analysis.cc:64-113): one line per read
-    record, same columns, separators and number formatting; one instance per file, so the per-instance column holds
-    this instance's cached blocks."""
+    record, same columns, separators and number formatting.  A record of an instance replayed alone holds that
+    instance's cached blocks in all three cached-blocks columns; a record of replay_group lists every instance of
+    the group in CachedBlocksPerInstance (in the order the group was given - the reference's order is that of an
+    unordered_map) and their sum in CachedBlocksAllInstance."""
     reads = rec["kind"] != tr.WRITE_CACHE
     acc_total = acc_ext = acc_int = 0
     with open(path, "w") as f:
@@ -167,7 +173,11 @@ def export_hit_rates(path: str, rec: Dict[str, np.ndarray]) -> None:
             acc_e = acc_ext / acc_total if acc_total else 0.0
             acc_i = acc_int / acc_total if acc_total else 0.0
             cached = int(rec["current_cache_blocks"][i])
-            f.write(", ".join([str(int(rec["timestamp_us"][i])), str(cached), str(cached), str(cached), str(ir),
+            per, total_cached = str(cached), str(cached)
+            if "blocks_per_instance" in rec:  # a group of several instances: every instance's usage, ';'-separated
+                row = [int(x) for x in rec["blocks_per_instance"][i]]
+                per, total_cached = ";".join(str(x) for x in row), str(sum(row))
+            f.write(", ".join([str(int(rec["timestamp_us"][i])), str(cached), per, total_cached, str(ir),
                                str(er), str(total), str(ih), _g(int_rate), str(eh), _g(ext_rate),
                                _g(int_rate + ext_rate), _g(acc_i), _g(acc_e), _g(acc_i + acc_e)]) + "\n")
 
@@ -183,8 +193,9 @@ def run_trace_file(trace_path: str, trace_type: str, output_dir: str, device=Non
     (`<instance>_quota<q>_hit_rates.csv` per instance and quota when quota_blocks is a sequence).  Every instance is
     replayed on its own, except the instances of a group in `groups` (dicts with "instances" = the ids and "quota" =
     the shared quota in blocks, as parse_startup_config returns them), which are replayed together against their
-    shared quota under eviction `mode` (replay_group; in their CSV files the three cached-blocks columns hold the
-    file's own instance, the reference lists every instance there in the order of an unordered_map)."""
+    shared quota under eviction `mode` (replay_group; in their CSV files CachedBlocksPerInstance lists the instances
+    of the group in the group's order - the reference lists every instance of the whole configuration there, in
+    the order of an unordered_map)."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     traces = tr.load_traces(trace_path, trace_type, block_sizes)
     by_instance: Dict[str, List[tr.Trace]] = {}

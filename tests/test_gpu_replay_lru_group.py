@@ -22,7 +22,13 @@ def _gpu(keys, off, types, inst, n_inst, quotas, mask=None, **kw):
                           torch.as_tensor(np.asarray(mask, dtype=np.int64), device=DEV) if mask is not None else None,
                           **kw)
     torch.cuda.synchronize()
-    ext, inte, wr, size, totals, final = [t.cpu().numpy() for t in r]
+    ext, inte, wr, size, totals, final = [t.cpu().numpy() for t in r[:6]]
+    if r.instance_blocks_per_trace is not None:
+        every = r.instance_blocks_per_trace.cpu().numpy()
+        assert every.shape == (len(quotas), ext.shape[1], n_inst)
+        if ext.shape[1] > 0:  # the trace's own instance is one of them, and the last record is the final usage
+            own = np.take_along_axis(every, np.asarray(inst, dtype=np.int64)[None, :, None].repeat(len(quotas), 0), 2)
+            assert np.array_equal(own[:, :, 0], size) and np.array_equal(every[:, -1, :], final)
     if ext.shape[1] > 0:
         assert np.array_equal(totals[:, :3], np.stack([ext.sum(1), inte.sum(1), wr.sum(1)], axis=1))
         assert np.array_equal(totals[:, 3], final.sum(1))
@@ -84,3 +90,30 @@ def test_one_instance_group_is_the_plain_sweep_and_bad_instances_are_counted():
     assert status[0].item() == 1
     with pytest.raises(ValueError):
         _gpu(keys, off, types, zeros, 65, quotas, mask)
+
+
+@pytest.mark.parametrize("mode", [1, 3])
+def test_usage_of_every_instance_after_each_trace(mode):
+    """ReadRecord::blocks_per_instance (kv_cache_manager/optimizer/manager/optimizer_runner.cc:116-124): under
+    group-rough eviction a write of one instance shrinks the others too, so the column cannot be derived from the
+    per-trace usage of the trace's own instance."""
+    rng = np.random.default_rng(330 + mode)
+    keys, off, types, mask = _workload(rng, 900, True)
+    n_inst = 4
+    inst = rng.integers(0, n_inst, size=len(types)).astype(np.int32)
+    quotas = [40, 300, 1 << 40]
+    r = RunTracesLruGroup(torch.from_numpy(keys).to(DEV), torch.from_numpy(off).to(DEV), torch.from_numpy(types).to(DEV),
+                          torch.from_numpy(inst).to(DEV), n_inst, quotas, torch.from_numpy(mask).to(DEV), evict_batch=5,
+                          mode=mode, instance_records=True)
+    got = r.instance_blocks_per_trace.cpu().numpy()
+    changed_others = 0
+    for c, q in enumerate(quotas):
+        want = oracle.LruGroupReplay(q, n_inst, evict_batch=5, mode=mode).run(keys, off, types, inst, mask,
+                                                                              instance_records=True)
+        assert np.array_equal(want[5], got[c]), q
+        d = np.diff(want[5], axis=0)
+        others = d.copy()
+        others[np.arange(len(d)), inst[1:]] = 0
+        changed_others += int((others != 0).sum())
+    assert (changed_others > 0) == (mode == 1)
+    _gpu(keys, off, types, inst, n_inst, quotas, mask, evict_batch=5, mode=mode, instance_records=True)

@@ -140,10 +140,14 @@ def test_shared_quota_groups_host_side(tmp_path, monkeypatch):
     from oracle import kvcm_oracle as oracle
     from tair_kvcache_b200.optimizer import runner
 
-    def stand_in(keys, off, kind, inst, n_inst, quotas, mask, evict_batch, mode, mask_bits=None):
+    from tair_kvcache_b200.optimizer.replay import LruGroupSweepResult
+
+    def stand_in(keys, off, kind, inst, n_inst, quotas, mask, evict_batch, mode, mask_bits=None,
+                 instance_records=False):
         r = oracle.LruGroupReplay(quotas[0], n_inst, evict_batch=evict_batch, mode=mode).run(
-            keys.numpy(), off.numpy(), kind.numpy(), inst.numpy(), mask.numpy())
-        return [torch.from_numpy(x)[None] for x in r[:4]] + [None, None]
+            keys.numpy(), off.numpy(), kind.numpy(), inst.numpy(), mask.numpy(), instance_records=True)
+        ext, inte, wr, size = [torch.from_numpy(x)[None] for x in r[:4]]
+        return LruGroupSweepResult(ext, inte, wr, size, None, None, torch.from_numpy(r[5])[None])
 
     monkeypatch.setattr(runner, "RunTracesLruGroup", stand_in)
 
@@ -165,7 +169,10 @@ def test_shared_quota_groups_host_side(tmp_path, monkeypatch):
     assert recs["a"]["current_cache_blocks"].tolist() == [3, 2] and recs["b"]["current_cache_blocks"].tolist() == [1, 1]
     assert recs["a"]["timestamp_us"].tolist() == [1, 3] and recs["b"]["write_blocks"].tolist() == [2, 0]
     rows = (tmp_path / "out" / "a_hit_rates.csv").read_text().splitlines()
-    assert len(rows) == 2 and rows[1].startswith("3, 2, 2, 2, 0, 3, 3, 0, ")
+    # CachedBlocksCurrentInstance, CachedBlocksPerInstance (a;b), CachedBlocksAllInstance: after b's write the group
+    # held 5 blocks, one round of group-rough eviction took one from each
+    assert len(rows) == 2 and rows[1].startswith("3, 2, 2;1, 3, 0, 3, 3, 0, ")
+    assert recs["b"]["blocks_per_instance"].tolist() == [[2, 1], [2, 1]]
     cfg["eviction_params"]["eviction_mode"] = 2
     recs = runner.run_startup_config(cfg, device="cpu", rw_separation=True)
     assert recs["a"]["external_hit_blocks"].tolist() == [0, 3] and np.array_equal(recs["a"]["kind"], [2, 1])
