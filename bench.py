@@ -1401,17 +1401,18 @@ def main_lru(args, ctx):
     quotas = all_quotas[rank::world]  # every rank gets points from the whole range
     policy = args.policy
     n_inst = max(1, args.instances)  # > 1: the requests go round-robin to instances that share the quota
-    if n_inst > 1 and policy != "lru":
-        raise SystemExit("--instances needs --policy lru")
     d_inst = (torch.arange(n_req, device=device, dtype=torch.int32) % n_inst).contiguous()
-    workspace = torch.empty(replay_lru_workspace_bytes(n_keys, n_cfg, policy, n_req) + 4096, dtype=torch.uint8,
-                            device=device)
+    ws_bytes = replay_lru_workspace_bytes(n_keys, n_cfg, policy, n_req)
+    if n_inst > 1 and policy == "leaf_aware_lru":
+        from tair_kvcache_b200 import _cabi
+        ws_bytes = _cabi.lib().kvcm_b200_replay_leaf_lru_group_workspace_bytes(n_keys, n_req, n_cfg, n_inst)
+    workspace = torch.empty(ws_bytes + 4096, dtype=torch.uint8, device=device)
     status = torch.zeros(4, dtype=torch.int32, device=device)
 
     def sweep(keys):
         if n_inst > 1:
             return RunTracesLruGroup(keys, d_ko, d_type, d_inst, n_inst, quotas, evict_batch=100, mode=1,
-                                     workspace=workspace, status=status)
+                                     workspace=workspace, status=status, policy=policy)
         return RunTracesLru(keys, d_ko, d_type, quotas, evict_batch=100, precise=False, workspace=workspace,
                             status=status, policy=policy)
 
@@ -1462,7 +1463,7 @@ def main_lru(args, ctx):
         k = d_keys[:int(ko[m])].cpu().numpy()
         c = len(quotas) // 3
         if n_inst > 1:
-            want = oracle.LruGroupReplay(quotas[c], n_inst, evict_batch=100, mode=1).run(
+            want = oracle.LruGroupReplay(quotas[c], n_inst, evict_batch=100, mode=1, policy=policy).run(
                 k, ko[:m + 1], np.zeros(m, np.uint8), np.arange(m, dtype=np.int32) % n_inst)
         else:
             want = oracle.LruReplay(quotas[c], evict_batch=100, precise=False, policy=policy).run(
@@ -1486,9 +1487,11 @@ def main_lru(args, ctx):
                        "hit_rate_highest_quota": float(hit_rate[-1]), "table_overflows": int(status[0].item()),
                        "parity_sample_ok": parity},
             # per step: the hash, then table init + claim + lookup + sweep ("lru"), one more pass for the key
-            # predecessors ("leaf_aware_lru"), or extents + (clear, claim, lookup) per instance + sweep (groups)
+            # positions ("leaf_aware_lru"), or extents / instance check + (clear, claim, lookup) per instance + sweep
+            # (groups; one more pass for the key positions under "leaf_aware_lru")
             "clocks": clocks,
-            "gpu_launches": (3 * n_inst + 3 if n_inst > 1 else 6 if policy == "leaf_aware_lru" else 5) * steps}))
+            "gpu_launches": ((3 * n_inst + (4 if policy == "leaf_aware_lru" else 3)) if n_inst > 1
+                             else 6 if policy == "leaf_aware_lru" else 5) * steps}))
 
 
 def main_lru_reference(args):

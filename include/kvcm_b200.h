@@ -616,7 +616,8 @@ KVCM_API int32_t kvcm_b200_replay_lru(const int64_t *d_keys, const int64_t *d_ke
  * d_cache_blocks[c][t] is the usage of trace t's own instance after the trace (GetCurrentInstanceUsage,
  * kv_cache_manager/optimizer/manager/optimizer_runner.cc:116,196), d_totals[c][3] the usage of the group at the end,
  * d_instance_blocks (optional, [n_configs][n_instances]) that of every instance.  Otherwise as kvcm_b200_replay_lru
- * ("lru" policy in every instance).  d_status[0] also counts traces with an instance out of range. */
+ * ("lru" policy in every instance; kvcm_b200_replay_leaf_lru_group is the "leaf_aware_lru" twin).  A trace whose
+ * instance is out of range is replayed as an empty trace and counted in d_status[0]. */
 #define KVCM_B200_REPLAY_GROUP_MAX_INSTANCES 64
 KVCM_API int64_t kvcm_b200_replay_lru_group_workspace_bytes(int64_t n_keys_total, int32_t n_configs,
                                                             int32_t n_instances);
@@ -691,10 +692,11 @@ KVCM_API int32_t kvcm_b200_replay_random_lru(const int64_t *d_keys, const int64_
  * which order re-queued blocks; the trace number when NULL) and n_traces in the workspace size.
  * d_status[0] (optional) counts keys the id table refused and walks that hit their iteration limit; non-zero
  * means the input broke the premise below and the results are void.
- * Exact for prefix-unique chained keys without repeats inside one trace.  One warp per configuration; list
- * surgery and eviction run in one lane, so a configuration costs more than under plain LRU.
+ * Exact for prefix-unique chained keys without repeats inside one trace.  One warp per configuration; the
+ * walk to a sorted insertion point and the list surgery around a group of blocks run in one lane, so a
+ * configuration costs more than under plain LRU.
  * d_workspace: kvcm_b200_replay_leaf_lru_workspace_bytes(n_keys_total, n_traces, n_configs) bytes
- * (about 29 bytes per key occurrence and 56 per trace for each configuration; -1: too large), 256-byte aligned.
+ * (about 25 bytes per key occurrence and 56 per trace for each configuration; -1: too large), 256-byte aligned.
  * ---------------------------------------------------------------------------------------- */
 KVCM_API int64_t kvcm_b200_replay_leaf_lru_workspace_bytes(int64_t n_keys_total, int32_t n_traces,
                                                            int32_t n_configs);
@@ -706,6 +708,27 @@ KVCM_API int32_t kvcm_b200_replay_leaf_lru(const int64_t *d_keys, const int64_t 
                                            int64_t workspace_bytes, int32_t *d_ext_hit, int32_t *d_int_hit,
                                            int32_t *d_written, int64_t *d_cache_blocks, int64_t *d_totals,
                                            uint32_t *d_status, kvcm_stream_t stream);
+/* The leaf_aware_lru sweep for an instance group whose instances share one quota: every instance has its own tree
+ * and its own leaf-aware queue, the usage of all of them is summed against the quota after a write, and blocks
+ * go in rounds over the instances or from the writing instance only - d_trace_instance, n_instances (up to
+ * KVCM_B200_REPLAY_GROUP_MAX_INSTANCES), eviction_mode, d_cache_blocks, d_totals, d_instance_blocks and
+ * d_instance_blocks_per_trace exactly as in kvcm_b200_replay_lru_group_records, everything else as in
+ * kvcm_b200_replay_leaf_lru.  A round asks every instance for evict_batch blocks in the configuration's order
+ * (LeafAwareLruEvictionPolicy::EvictBlocks per instance, kv_cache_manager/optimizer/manager/
+ * eviction_manager.cc:86-146), and the emptied leaves of every instance are removed afterwards
+ * (OptIndexerManager::CheckAndEvict, kv_cache_manager/optimizer/manager/indexer_manager.cc:55-90).
+ * A trace whose instance is out of range is replayed as an empty trace and counted in d_status[0].
+ * d_trace_instance may be NULL when n_instances is 1.  kvcm_b200_replay_leaf_lru is this call with one instance
+ * and eviction_mode 3 (precise) or 2. */
+KVCM_API int64_t kvcm_b200_replay_leaf_lru_group_workspace_bytes(int64_t n_keys_total, int32_t n_traces,
+                                                                 int32_t n_configs, int32_t n_instances);
+KVCM_API int32_t kvcm_b200_replay_leaf_lru_group(
+    const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type, const int64_t *d_mask_off,
+    const uint8_t *d_mask_bits, const int64_t *d_timestamps, const int32_t *d_trace_instance, int32_t n_instances,
+    int32_t n_traces, int64_t n_keys_total, const int64_t *d_quota_blocks, int32_t n_configs, int32_t evict_batch,
+    int32_t eviction_mode, void *d_workspace, int64_t workspace_bytes, int32_t *d_ext_hit, int32_t *d_int_hit,
+    int32_t *d_written, int64_t *d_cache_blocks, int64_t *d_totals, int64_t *d_instance_blocks,
+    int64_t *d_instance_blocks_per_trace, uint32_t *d_status, kvcm_stream_t stream);
 
 /* Trace replay for callers that cannot allocate device memory.  (No counterpart in the reference: it
  * exists for how this library gets embedded, not for a reference interface.)

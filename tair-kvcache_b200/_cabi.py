@@ -140,6 +140,9 @@ SIGNATURES = {
     "kvcm_b200_replay_leaf_lru_workspace_bytes": [_i64, _i32, _i32],
     "kvcm_b200_replay_leaf_lru": [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _vp, _i32, _i32, _i32, _vp, _i64, _vp, _vp,
                                   _vp, _vp, _vp, _vp, _vp],
+    "kvcm_b200_replay_leaf_lru_group_workspace_bytes": [_i64, _i32, _i32, _i32],
+    "kvcm_b200_replay_leaf_lru_group": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i64, _vp, _i32, _i32, _i32, _vp,
+                                        _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "kvcm_b200_replay_random_lru_workspace_bytes": [_i64, _i32],
     "kvcm_b200_selftest_partial_sort": [_vp, _vp, _u32, _u32],
     "kvcm_b200_replay_random_lru": [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _vp, _i32, _i32, _i32, ctypes.c_double,

@@ -4,27 +4,33 @@
 // RadixTreeIndex (kv_cache_manager/optimizer/index/radix_tree_index.cc:19-392) with LeafAwareLruEvictionPolicy
 // (kv_cache_manager/optimizer/eviction_policy/leaf_aware_lru.cc:20-160) and the quota check after every write
 // (OptIndexerManager::CheckAndEvict, kv_cache_manager/optimizer/manager/indexer_manager.cc:55-90;
-// OptEvictionManager, kv_cache_manager/optimizer/manager/eviction_manager.cc:148-266), one instance per group.
+// OptEvictionManager, kv_cache_manager/optimizer/manager/eviction_manager.cc:86-266), for one instance or for a
+// group of instances that share the quota: every instance has a tree and a queue of its own
+// (kv_cache_manager/optimizer/manager/optimizer_manager.cc:66-99), here one pool of node numbers whose first
+// n_instances entries are the roots, and one pair of queue sentinels per instance; ids are unique over
+// (instance, key), so everything that is kept per key needs no instance.
 //
 // Unlike plain LRU this policy reads the shape of the tree: only blocks of childless nodes queue up for
 // eviction, a block whose node has cached children is dropped from the queue when it reaches the cold end, and a
 // node whose children have all been emptied gets its blocks queued again, sorted by last access time.  So the
 // tree is kept, per configuration, in a form a warp can walk without pointers.  Keys are prefix-unique chained
 // hashes: a key fixes the key before it.  Hence
-//   pred[id]      the key before id in its chain - the same for every configuration, built once;
+//   occ[id]       a position of key id in the id array - the same for every configuration, built once.  The
+//                 ids in front of it there, back to the start of that trace, are the key's chain;
 //   node_of[id]   the tree node that holds the block of key id; the key is in the tree while that node has
 //                 blocks (removing a node zeroes its block count, node numbers are never reused).  If a key is
 //                 in the tree, so is its whole chain, and a trace's walk down the tree is the run of its leading
 //                 keys that are in the tree;
 //   per node      parent, number of children, number of blocks, last key, cached blocks, cached blocks of the
 //                 immediate children (zero = RadixTreeNode::isDataLeaf), cached blocks outside the queue.
-// A node's blocks are pred-steps back from its last key.  Splitting a node (radix_tree_index.cc:89-127) gives
+// A node's blocks are the end of the chain of its last key.  Splitting a node (radix_tree_index.cc:89-127) gives
 // the new number to the UPPER part, whose keys are the ones the splitting trace has just walked.
 // The queue is the reference's doubly linked list over key ids (two sentinels), because the sorted re-insertions
 // (kv_cache_manager/optimizer/eviction_policy/common_structure.h:62-89) depend on list order, ties included.
 //
-// One warp per configuration.  Lanes share the scan of a trace's keys, the relabelling at a split and the
-// writes of new blocks; list surgery and eviction are serial in lane 0 (latency-bound on L2).
+// One warp per configuration.  Lanes share the scan of a trace's keys, the relabelling at a split, the writes of
+// new blocks, the eviction of a group of cold blocks and the re-queueing of a node's blocks; what is left to lane 0
+// is the list surgery around them and the walk to a sorted insertion point (latency-bound on L2).
 // Every walk carries an iteration limit so that keys that break the prefix-unique premise end in a status
 // count, not in an endless loop.
 #include "kvcm_common.cuh"
@@ -39,25 +45,26 @@ constexpr int kNodeFields = 7;
 
 struct LeafSweep {
     const uint32_t *ids;
-    const uint32_t *pred;
     const uint32_t *occ;  // one position of each key in ids
     const int64_t *key_off;
     const uint8_t *type;
     const int64_t *mask_off;
     const uint8_t *mask_bits;
     const int64_t *timestamps;  // optional, per trace; the trace number when null
+    const int32_t *trace_inst;  // optional, per trace, 0 .. n_instances-1; instance 0 when null
     const int64_t *quota;
     uint32_t *node_of;  // [n_configs][n_keys]
     uint8_t *flags;     // [n_configs][n_keys]
     int64_t *time;      // [n_configs][n_keys]  last_access_time
-    uint32_t *lprev;    // [n_configs][n_keys + 2]
-    uint32_t *lnext;    // [n_configs][n_keys + 2]
-    uint32_t *tmp;      // [n_configs][n_keys]  a node's blocks in order, while they are re-queued
+    uint32_t *lprev;    // [n_configs][n_keys + 2 * n_instances]
+    uint32_t *lnext;    // [n_configs][n_keys + 2 * n_instances]
     uint32_t *evicted;  // [n_configs][n_keys]  the nodes of the blocks evicted after one trace
     uint32_t *nodes;    // [n_configs][kNodeFields][max_nodes]
     int32_t *ext_hit, *int_hit, *written;
     int64_t *cache_blocks;
     int64_t *totals;
+    int64_t *inst_blocks;        // optional, [n_configs][n_instances]: usage per instance at the end
+    int64_t *inst_blocks_trace;  // optional, [n_configs][n_traces][n_instances]: usage of every instance after each trace
     uint32_t *status;
     int64_t n_keys;
     int64_t n_ids;  // key occurrences in ids (n_keys is this, or 1 for an empty input)
@@ -65,11 +72,11 @@ struct LeafSweep {
     int32_t n_traces;
     int32_t n_configs;
     int32_t evict_batch;
-    int32_t precise;
+    int32_t n_instances;
+    int32_t mode;  // 1 group rough, 2 instance rough, 3 instance precise
 };
 
-__global__ void LeafInitKernel(IdTable t, uint32_t *node_of, uint8_t *flags, uint64_t n_state, uint32_t *pred,
-                               uint64_t n_keys) {
+__global__ void LeafInitKernel(IdTable t, uint32_t *node_of, uint8_t *flags, uint64_t n_state) {
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
     const uint64_t first = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     for (uint64_t i = first; i <= t.mask; i += stride) t.slots[i] = make_ulonglong2(kEmptyKey, ~0ull);
@@ -77,66 +84,72 @@ __global__ void LeafInitKernel(IdTable t, uint32_t *node_of, uint8_t *flags, uin
         node_of[i] = kNone;
         flags[i] = 0;
     }
-    for (uint64_t i = first; i < n_keys; i += stride) pred[i] = kNone;
     if (first == 0) {
         t.cells[0] = 0ull;
         t.cells[1] = ~0ull;
     }
 }
 
-// pred[id of key i] = id of key i - 1 of the same trace.  Every occurrence of a key writes the same value.
-// occ[id] = a position of the key in ids (whichever occurrence writes last): the keys behind it there are a
-// guess at what follows the key in a queue, checked against the queue's links before it is used.
+// occ[id] = a position of the key in ids (whichever occurrence writes last).  Keys are prefix-unique, so the ids
+// in front of that position, back to the start of its trace, are the key's chain whichever occurrence it is; and
+// the ids behind it are a guess at what follows the key in a queue, checked against the queue's links before use.
+// Traces that name no instance of the group have no ids and are left out.
 __global__ void __launch_bounds__(256)
-    LeafPredKernel(const uint32_t *__restrict__ ids, const int64_t *__restrict__ key_off, int32_t n_traces,
-                   uint32_t *pred, uint32_t *occ) {
+    LeafOccKernel(const uint32_t *__restrict__ ids, const int64_t *__restrict__ key_off,
+                  const int32_t *__restrict__ trace_inst, int32_t n_instances, int32_t n_traces, uint32_t *occ) {
     const int32_t warps = static_cast<int32_t>(gridDim.x * (blockDim.x >> 5));
     const uint32_t lane = LaneId();
     for (int32_t t = static_cast<int32_t>(blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)); t < n_traces;
          t += warps) {
-        const int64_t beg = key_off[t], end = key_off[t + 1];
-        for (int64_t i = beg + lane; i < end; i += 32) {
-            const uint32_t id = ids[i];
-            if (i > beg) pred[id] = ids[i - 1];
-            occ[id] = static_cast<uint32_t>(i);
-        }
+        if (trace_inst != nullptr && (trace_inst[t] < 0 || trace_inst[t] >= n_instances)) continue;
+        const int64_t end = key_off[t + 1];
+        for (int64_t i = key_off[t] + lane; i < end; i += 32) occ[ids[i]] = static_cast<uint32_t>(i);
+    }
+}
+
+// Traces of an instance number outside the group are replayed as empty traces (the sweep does the same) and counted.
+__global__ void __launch_bounds__(256)
+    LeafCheckInstancesKernel(const int32_t *__restrict__ trace_inst, int32_t n_traces, int32_t n_instances,
+                             uint32_t *status) {
+    const int32_t stride = static_cast<int32_t>(gridDim.x * blockDim.x);
+    for (int32_t t = static_cast<int32_t>(blockIdx.x * blockDim.x + threadIdx.x); t < n_traces; t += stride) {
+        const int32_t j = trace_inst[t];
+        if ((j < 0 || j >= n_instances) && status != nullptr) atomicAdd(&status[0], 1u);
     }
 }
 
 // type: 0 DialogTurn (InsertWithQuery), 1 GetLocation (PrefixQuery), 2 WriteCache (InsertOnly).
 __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
+    extern __shared__ int64_t cached_of[];  // [n_instances]: cached blocks per instance (EvictionPolicy::size())
+    __shared__ uint32_t short_group[32];
     const int64_t cfg = blockIdx.x;
     const uint32_t lane = LaneId();
     const uint32_t full = 0xffffffffu;
+    const uint32_t below = (1u << lane) - 1u;
     const int64_t nk = p.n_keys;
+    const int32_t K = p.n_instances;
+    const uint32_t n_roots = static_cast<uint32_t>(K);  // node j is the root of instance j
     uint32_t *node_of = p.node_of + cfg * nk;
     uint8_t *flags = p.flags + cfg * nk;
     int64_t *time = p.time + cfg * nk;
-    uint32_t *lprev = p.lprev + cfg * (nk + 2);
-    uint32_t *lnext = p.lnext + cfg * (nk + 2);
-    uint32_t *tmp = p.tmp + cfg * nk;
+    uint32_t *lprev = p.lprev + cfg * (nk + 2 * K);
+    uint32_t *lnext = p.lnext + cfg * (nk + 2 * K);
     uint32_t *evicted = p.evicted + cfg * nk;
     uint32_t *node = p.nodes + cfg * kNodeFields * p.max_nodes;
     uint32_t *n_parent = node, *n_children = node + p.max_nodes, *n_blocks = node + 2 * p.max_nodes;
     uint32_t *n_last = node + 3 * p.max_nodes, *n_cached = node + 4 * p.max_nodes;
     uint32_t *n_childc = node + 5 * p.max_nodes;  // cached blocks of the immediate children
     uint32_t *n_unlisted = node + 6 * p.max_nodes;  // cached blocks of the node that are not in the queue
-    const uint32_t kHead = static_cast<uint32_t>(nk), kTail = static_cast<uint32_t>(nk + 1);
     const int64_t quota = p.quota[cfg];
     const int64_t out0 = cfg * p.n_traces;
     const uint64_t walk_cap = static_cast<uint64_t>(nk) + 2;
+    // the queue of instance j lies between the sentinels head_of(j) (hot end) and head_of(j) + 1 (cold end)
+    auto head_of = [&](int32_t j) { return static_cast<uint32_t>(nk) + 2u * static_cast<uint32_t>(j); };
 
     // owned by lane 0
-    uint32_t n_nodes = 1, faults = 0;
-    int64_t resident = 0, sum_ext = 0, sum_int = 0, sum_wr = 0;
+    uint32_t n_nodes = n_roots, faults = 0;
+    int64_t resident = 0, sum_ext = 0, sum_int = 0, sum_wr = 0;  // resident: of the whole group
 
-    auto push_front = [&](uint32_t id) {
-        const uint32_t f = lnext[kHead];
-        lnext[id] = f;
-        lprev[id] = kHead;
-        lprev[f] = id;
-        lnext[kHead] = id;
-    };
     auto new_node = [&](uint32_t parent) -> uint32_t {
         uint32_t x = n_nodes;
         if (static_cast<int64_t>(x) >= p.max_nodes) {  // cannot happen: a trace makes at most two nodes
@@ -154,80 +167,286 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
         n_unlisted[x] = 0;
         return x;
     };
-    // LinkedList::insert_sorted / insert_sorted_reverse under LeafLRUListNode::compare, picked as
-    // insert_sorted_by_priority picks (leaf_aware_lru.cc:53-83).
-    auto insert_by_time = [&](uint32_t b) {
-        const uint32_t h = lnext[kHead];
-        uint32_t before;  // b goes in front of this entry
-        if (h == kTail) {
-            before = kTail;
+    // Where LinkedList::insert_sorted / insert_sorted_reverse under LeafLRUListNode::compare, picked as
+    // insert_sorted_by_priority picks them (leaf_aware_lru.cc:53-83), put a block of time bt into the queue between
+    // hd and hd + 1: the entry it goes in front of, and whether the walk came from the hot end.  An insertion from the
+    // hot end lands in front of the entries of equal time, one from the cold end behind them.  Lane 0.
+    auto insertion_point = [&](int64_t bt, uint32_t hd, bool *from_hot) -> uint32_t {
+        const uint32_t tl = hd + 1;
+        const uint32_t h = lnext[hd];
+        *from_hot = true;
+        if (h == tl) return tl;
+        const uint32_t c = lprev[tl];
+        const int64_t ht = time[h], ct = time[c];
+        *from_hot = bt >= ht ? true : (bt <= ct ? false : (ht - bt) < (bt - ct));
+        uint64_t steps = 0;
+        uint32_t before;
+        if (*from_hot) {
+            uint32_t cur = h;
+            while (cur != tl && bt < time[cur] && ++steps < walk_cap) cur = lnext[cur];
+            before = cur;
         } else {
-            const uint32_t tl = lprev[kTail];
-            const int64_t ht = time[h], tt = time[tl], bt = time[b];
-            const bool from_head = bt >= ht ? true : (bt <= tt ? false : (ht - bt) < (bt - tt));
-            uint64_t steps = 0;
-            if (from_head) {
-                uint32_t cur = h;
-                while (cur != kTail && bt < time[cur] && ++steps < walk_cap) cur = lnext[cur];
-                before = cur;
-            } else {
-                uint32_t cur = tl;
-                while (cur != kHead && time[cur] < bt && ++steps < walk_cap) cur = lprev[cur];
-                before = lnext[cur];
-            }
-            if (steps >= walk_cap) ++faults;
+            uint32_t cur = c;
+            while (cur != hd && time[cur] < bt && ++steps < walk_cap) cur = lprev[cur];
+            before = lnext[cur];
         }
-        const uint32_t a = lprev[before];
-        lnext[a] = b;
-        lprev[b] = a;
-        lnext[b] = before;
-        lprev[before] = b;
+        if (steps >= walk_cap) ++faults;
+        return before;
+    };
+    // UpdateNodeState (leaf_aware_lru.cc:135-160) for a node that has just become a data leaf: its cached blocks
+    // that are outside the queue go back in, in key order, each by sorted insertion.  All lanes.  The node's
+    // blocks are the last n_blocks ids of the chain that ends at its last key, read straight out of the id array.
+    // Consecutive insertions of one time end up side by side - the second one walks from the same end, stops at
+    // the first one and lands in front of it (from the hot end) or behind it (from the cold end), and so on - so a
+    // run of blocks that share a time costs one walk for its first block and one splice: lanes write the links
+    // inside the run, lane 0 the two links around it.  Blocks written or touched by one trace share a time.
+    auto requeue_node = [&](uint32_t u, uint32_t hd) {
+        const uint32_t c = n_blocks[u];
+        const uint32_t last = n_last[u];
+        const int64_t first_pos = last != kNone ? static_cast<int64_t>(p.occ[last]) - static_cast<int64_t>(c) + 1 : -1;
+        bool broken = last == kNone || first_pos < 0;
+        for (uint32_t base = 0; base < c && !broken; base += 32) {
+            const uint32_t k = base + lane;
+            const bool have = k < c;
+            const uint32_t x = have ? p.ids[first_pos + k] : kNone;
+            const bool member = have && node_of[x] == u;
+            broken = __any_sync(full, have && !member);
+            const bool need = member && (flags[x] & (kCached | kListed)) == kCached;
+            const int64_t tm = need ? time[x] : 0;
+            const uint32_t need_m = __ballot_sync(full, need);
+            const int lower_need = 31 - __clz(need_m & below);  // the needing lane before this one, -1 if none
+            const int64_t tm_lower = __shfl_sync(full, tm, lower_need < 0 ? 0 : lower_need);
+            uint32_t starts = __ballot_sync(full, need && (lower_need < 0 || tm_lower != tm));
+            while (starts != 0) {
+                const int first = __ffs(starts) - 1;
+                starts &= starts - 1;
+                const uint32_t upto = starts != 0 ? ((1u << (__ffs(starts) - 1)) - 1u) : full;
+                const uint32_t run = need_m & upto & ~((1u << first) - 1u);
+                const int top = 31 - __clz(run);
+                const uint32_t x_first = __shfl_sync(full, x, first), x_top = __shfl_sync(full, x, top);
+                const int64_t bt = __shfl_sync(full, tm, first);
+                uint32_t before = 0, after = 0, hot = 0;  // the run goes between `after` (hotter) and `before`
+                if (lane == 0) {
+                    bool from_hot;
+                    before = insertion_point(bt, hd, &from_hot);
+                    after = lprev[before];
+                    hot = from_hot ? 1u : 0u;
+                }
+                before = __shfl_sync(full, before, 0);
+                after = __shfl_sync(full, after, 0);
+                hot = __shfl_sync(full, hot, 0);
+                const bool mine = ((run >> lane) & 1u) != 0;
+                const int lower = 31 - __clz(run & below);
+                const uint32_t above_m = run & ~below & ~(1u << lane);
+                const int higher = above_m != 0 ? __ffs(above_m) - 1 : -1;
+                const uint32_t x_lower = __shfl_sync(full, x, lower < 0 ? 0 : lower);
+                const uint32_t x_higher = __shfl_sync(full, x, higher < 0 ? 0 : higher);
+                if (mine) {
+                    // from the hot end the later block lies in front of the earlier one; from the cold end behind it
+                    const uint32_t colder = hot != 0 ? (lower < 0 ? before : x_lower) : (higher < 0 ? before : x_higher);
+                    const uint32_t hotter = hot != 0 ? (higher < 0 ? after : x_higher) : (lower < 0 ? after : x_lower);
+                    lnext[x] = colder;
+                    lprev[x] = hotter;
+                    flags[x] = kCached | kListed;
+                }
+                if (lane == 0) {
+                    lnext[after] = hot != 0 ? x_top : x_first;
+                    lprev[before] = hot != 0 ? x_first : x_top;
+                }
+                __syncwarp();
+            }
+        }
+        if (lane == 0) {
+            if (broken) ++faults;
+            n_unlisted[u] = 0;
+        }
+        __syncwarp();
+    };
+
+    uint32_t n_ev = 0;   // kept equal in all lanes: entries of `evicted` since the last check began
+    uint64_t spins = 0;  // lane 0: steps of the one-by-one path since the last check began
+    // LeafAwareLruEvictionPolicy::EvictBlocks(count) of instance j (leaf_aware_lru.cc:85-133), up to 32 blocks at
+    // a time; all lanes, returns how many blocks went.  Its set of parents already handled only saves work: a
+    // handled parent has nothing left outside the queue.
+    auto evict_from = [&](int32_t j, int64_t count) -> int64_t {
+        const uint32_t hd = head_of(j), tl = hd + 1;
+        int64_t got = 0;
+        while (got < count) {
+            const uint32_t want = static_cast<uint32_t>(count - got < 32 ? count - got : 32);
+            // The candidates, from the cold end of the queue.  Blocks written by one trace sit in the queue in the
+            // trace's key order, so the keys that follow the coldest block in ids are a guess at the blocks that
+            // follow it in the queue; each lane checks one link of the guess and the group is the part that the
+            // queue's own links confirm.  A short group (keys shared by many traces) falls back to lane 0
+            // following the links one by one.
+            const uint32_t coldest = lprev[tl];
+            if (coldest == hd) break;  // the queue ran out
+            const int64_t guess_at = static_cast<int64_t>(p.occ[coldest]) + lane;
+            uint32_t cand = lane == 0 ? coldest : (guess_at < p.n_ids ? p.ids[guess_at] : kNone);
+            const uint32_t towards_head = cand != kNone ? lprev[cand] : kNone;
+            const uint32_t cand_after = __shfl_down_sync(full, cand, 1);
+            const uint32_t linked = __ballot_sync(full, lane < 31 && cand_after != kNone && towards_head == cand_after);
+            uint32_t m = static_cast<uint32_t>(__ffs(~linked));  // confirmed links + 1 (bit 31 is never set)
+            if (m > want) m = want;
+            uint32_t after = __shfl_sync(full, towards_head, m - 1);
+            if (m < want && m < 8) {
+                m = 0;
+                if (lane == 0) {
+                    uint32_t b = coldest;
+                    while (m < want && b != hd) {
+                        short_group[m++] = b;
+                        b = lprev[b];
+                    }
+                    after = b;
+                }
+                m = __shfl_sync(full, m, 0);
+                after = __shfl_sync(full, after, 0);
+                __syncwarp();
+                cand = lane < m ? short_group[lane] : kNone;
+                __syncwarp();
+            }
+            const bool mine = lane < m;
+            const uint32_t nd = mine ? node_of[cand] : 0u;
+            const uint32_t up = mine ? n_parent[nd] : 0u;
+            // The whole group goes at once when every candidate sits in a data leaf and no parent runs out of
+            // cached children while it still has blocks outside the queue (nothing is re-queued, so the queue
+            // stays as it was followed).
+            const uint32_t same_up = __match_any_sync(full, mine ? up : kNone - lane);
+            const uint32_t same_nd = __match_any_sync(full, mine ? nd : kNone - lane);
+            bool plain = true;
+            if (mine) {
+                const uint32_t under = static_cast<uint32_t>(__popc(same_up));
+                plain = n_childc[nd] == 0 && (up < n_roots || n_unlisted[up] == 0 || n_childc[up] > under);
+            }
+            if (__all_sync(full, plain) && static_cast<int64_t>(n_ev) + m <= nk) {
+                if (mine) {
+                    flags[cand] = 0;
+                    evicted[n_ev + lane] = nd;
+                    if (static_cast<uint32_t>(__ffs(same_nd) - 1) == lane) {
+                        atomicSub(&n_cached[nd], static_cast<uint32_t>(__popc(same_nd)));
+                    }
+                }
+                __syncwarp();  // n_childc is read above for nodes that are parents here
+                if (mine && static_cast<uint32_t>(__ffs(same_up) - 1) == lane) {
+                    atomicSub(&n_childc[up], static_cast<uint32_t>(__popc(same_up)));
+                }
+                if (lane == 0) {
+                    lnext[after] = tl;
+                    lprev[tl] = after;
+                    resident -= m;
+                    cached_of[j] -= m;
+                }
+                __syncwarp();
+                n_ev += m;
+                got += m;
+                continue;
+            }
+            // otherwise one block after the other, up to the same number; lane 0 stops where a parent has become
+            // a data leaf with blocks outside the queue, the warp queues them, lane 0 goes on
+            uint32_t g = 0;
+            for (;;) {
+                uint32_t turned = kNone;
+                if (lane == 0) {
+                    while (g < want) {
+                        const uint32_t b = lprev[tl];
+                        if (b == hd) break;
+                        if (++spins > 2 * walk_cap || static_cast<int64_t>(n_ev) >= nk) {
+                            ++faults;  // a block leaves the queue at most twice per check, and is evicted once
+                            break;
+                        }
+                        const uint32_t a = lprev[b];
+                        lnext[a] = tl;
+                        lprev[tl] = a;
+                        const uint32_t node_b = node_of[b];
+                        if (n_childc[node_b] != 0) {  // its node has cached children by now: out of the queue
+                            flags[b] = kCached;
+                            n_unlisted[node_b] += 1;
+                            continue;
+                        }
+                        flags[b] = 0;
+                        n_cached[node_b] -= 1;
+                        const uint32_t up_b = n_parent[node_b];
+                        n_childc[up_b] -= 1;
+                        evicted[n_ev++] = node_b;
+                        ++g;
+                        if (up_b >= n_roots && n_childc[up_b] == 0 && n_unlisted[up_b] != 0) {
+                            turned = up_b;
+                            break;
+                        }
+                    }
+                }
+                turned = __shfl_sync(full, turned, 0);
+                if (turned == kNone) break;
+                requeue_node(turned, hd);
+            }
+            g = __shfl_sync(full, g, 0);
+            n_ev = __shfl_sync(full, n_ev, 0);
+            if (lane == 0) {
+                resident -= g;
+                cached_of[j] -= g;
+            }
+            __syncwarp();
+            got += g;
+            if (g < want) break;  // the queue ran out (or a walk limit did)
+        }
+        return got;
     };
 
     if (lane == 0) {
-        n_parent[0] = kNone;
-        n_children[0] = 0;
-        n_blocks[0] = 0;
-        n_last[0] = kNone;
-        n_cached[0] = 0;
-        n_childc[0] = 0;
-        n_unlisted[0] = 0;
-        lnext[kHead] = kTail;
-        lprev[kTail] = kHead;
+        for (int32_t j = 0; j < K; ++j) {
+            n_parent[j] = kNone;
+            n_children[j] = 0;
+            n_blocks[j] = 0;
+            n_last[j] = kNone;
+            n_cached[j] = 0;
+            n_childc[j] = 0;
+            n_unlisted[j] = 0;
+            lnext[head_of(j)] = head_of(j) + 1;
+            lprev[head_of(j) + 1] = head_of(j);
+            cached_of[j] = 0;
+        }
     }
     __syncwarp();
 
-    // What a trace reads before it touches any state (its extent, kind, time and the ids of its first 32 keys) is
-    // fetched one trace ahead, its extent two traces ahead: those loads do not wait for the traces before it.
-    auto extent = [&](int32_t t, int64_t *beg, int64_t *n, uint8_t *ty, int64_t *skip, int64_t *now) {
+    // What a trace reads before it touches any state (its extent, kind, time, instance and the ids of its first 32
+    // keys) is fetched one trace ahead, its extent two traces ahead: those loads do not wait for the traces before it.
+    auto extent = [&](int32_t t, int64_t *beg, int64_t *n, uint8_t *ty, int64_t *skip, int64_t *now, int32_t *who) {
         if (t < p.n_traces) {
             *beg = p.key_off[t];
             *n = p.key_off[t + 1] - *beg;
             *ty = p.type[t];
             *skip = (*ty == 1 && p.mask_off != nullptr) ? p.mask_off[t] : 0;
             *now = p.timestamps != nullptr ? p.timestamps[t] : static_cast<int64_t>(t);
+            *who = p.trace_inst != nullptr ? p.trace_inst[t] : 0;
+            if (*who < 0 || *who >= K) {  // counted by LeafCheckInstancesKernel; its keys have no ids
+                *who = 0;
+                *n = 0;
+            }
         } else {
-            *beg = 0, *n = 0, *ty = 1, *skip = 0, *now = 0;
+            *beg = 0, *n = 0, *ty = 1, *skip = 0, *now = 0, *who = 0;
         }
     };
     int64_t beg, n, skip, now, beg1, n1, skip1, now1;
     uint8_t ty, ty1;
-    extent(0, &beg, &n, &ty, &skip, &now);
-    extent(1, &beg1, &n1, &ty1, &skip1, &now1);
+    int32_t me, me1;
+    extent(0, &beg, &n, &ty, &skip, &now, &me);
+    extent(1, &beg1, &n1, &ty1, &skip1, &now1, &me1);
     uint32_t first_id = lane < n ? p.ids[beg + lane] : 0u;
 
     for (int32_t t = 0; t < p.n_traces; ++t) {
         const uint32_t next_first_id = lane < n1 ? p.ids[beg1 + lane] : 0u;
         int64_t beg2, n2, skip2, now2;
         uint8_t ty2;
-        extent(t + 2, &beg2, &n2, &ty2, &skip2, &now2);
+        int32_t me2;
+        extent(t + 2, &beg2, &n2, &ty2, &skip2, &now2, &me2);
         int32_t ext = 0, inte = 0, wr = 0;
+        const uint32_t my_root = static_cast<uint32_t>(me);
+        const uint32_t kHead = head_of(me);
 
         // ---- scan: where the trace leaves the tree (div) and its first block that is not cached (first_gone)
         // A key is in the tree when its node still has blocks: removing a node only zeroes its block count.
         int64_t div = n, first_gone = -1;
-        uint32_t at_id = kNone, at_node = 0;      // the last block inside the tree and its node (the root if none)
-        uint32_t carry_id = kNone, carry_node = 0;  // the same for the previous 32 keys
+        uint32_t at_id = kNone, at_node = my_root;      // the last block inside the tree and its node (the root if none)
+        uint32_t carry_id = kNone, carry_node = my_root;  // the same for the previous 32 keys
         for (int64_t base = 0; base < n; base += 32) {
             const int64_t i = base + lane;
             const bool have = i < n;
@@ -324,11 +543,14 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                     const uint32_t above = n_parent[nd], kids = n_children[nd];
                     atomicAdd(&n_cached[nd], 1u);
                     atomicAdd(&n_childc[above], 1u);
-                    ++resident;
                     ++wr;
                     if (kids == 0) {
                         flags[id] = kCached | kListed;
-                        push_front(id);
+                        const uint32_t f = lnext[kHead];
+                        lnext[id] = f;
+                        lprev[id] = kHead;
+                        lprev[f] = id;
+                        lnext[kHead] = id;
                     } else {
                         flags[id] = kCached;
                         atomicAdd(&n_unlisted[nd], 1u);
@@ -346,7 +568,7 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                     above_at = n_parent[at];
                     old_front = lnext[kHead];
                     if (div == 0 || last_of_at == at_id) {
-                        if (at != 0 && kids == 0) {
+                        if (at >= n_roots && kids == 0) {
                             target = at;
                             above_target = above_at;
                         } else {
@@ -423,175 +645,63 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                     atomicAdd(&n_cached[target], cnt);
                     n_last[target] = p.ids[beg + n - 1];
                     atomicAdd(&n_childc[above_target], cnt);
-                    resident += cnt;
                     wr += static_cast<int32_t>(cnt);
                 }
                 __syncwarp();
             }
+            if (lane == 0) {
+                resident += wr;
+                cached_of[me] += wr;
+            }
+            __syncwarp();
 
-            // ---- CheckAndEvict: whole batches until the excess is covered, or exactly the excess
+            // ---- CheckAndEvict over the usage of the whole group (eviction_manager.cc:86-266): in turns over the
+            // instances, a batch each, until a round covers the excess or takes nothing (group rough); or from the
+            // writing instance only, whole batches (instance rough) or exactly the excess (instance precise).
             const int64_t resident_now = __shfl_sync(full, resident, 0);
             if (resident_now > quota) {
                 const int64_t excess = resident_now - quota;
-                int64_t total = 0;   // these three are kept equal in all lanes
-                uint32_t n_ev = 0;
-                bool dry = false;    // the queue ran out
-                uint64_t spins = 0;  // lane 0
-                while (total < excess && !dry) {
-                    const int64_t rest = excess - total;
-                    const int64_t count = p.precise != 0 ? (rest < p.evict_batch ? rest : p.evict_batch) : p.evict_batch;
-                    int64_t got = 0;
-                    // LeafAwareLruEvictionPolicy::EvictBlocks (leaf_aware_lru.cc:85-133), up to 32 blocks at a time.
-                    // Its set of parents already handled only saves work: a handled parent has nothing left outside
-                    // the queue.
-                    while (got < count) {
-                        const uint32_t want = static_cast<uint32_t>(count - got < 32 ? count - got : 32);
-                        // The candidates, from the cold end of the queue.  Blocks written by one trace sit in the
-                        // queue in the trace's key order, so the keys that follow the coldest block in ids are a
-                        // guess at the blocks that follow it in the queue; each lane checks one link of the guess
-                        // and the group is the part that the queue's own links confirm.  A short group (keys shared
-                        // by many traces) falls back to lane 0 following the links one by one.
-                        const uint32_t coldest = lprev[kTail];
-                        if (coldest == kHead) {
-                            dry = true;
-                            break;
+                int64_t total = 0;  // kept equal in all lanes
+                n_ev = 0;
+                spins = 0;
+                if (p.mode == 1) {
+                    while (total < excess) {
+                        bool any = false;
+                        for (int32_t j = 0; j < K; ++j) {  // a whole round even when the excess is covered midway
+                            const int64_t got = evict_from(j, p.evict_batch);
+                            any = any || got > 0;
+                            total += got;
                         }
-                        const int64_t guess_at = static_cast<int64_t>(p.occ[coldest]) + lane;
-                        uint32_t cand = lane == 0 ? coldest : (guess_at < p.n_ids ? p.ids[guess_at] : kNone);
-                        const uint32_t towards_head = cand != kNone ? lprev[cand] : kNone;
-                        const uint32_t cand_after = __shfl_down_sync(full, cand, 1);
-                        const uint32_t linked =
-                            __ballot_sync(full, lane < 31 && cand_after != kNone && towards_head == cand_after);
-                        uint32_t m = static_cast<uint32_t>(__ffs(~linked));  // confirmed links + 1 (bit 31 is never set)
-                        if (m > want) m = want;
-                        uint32_t after = __shfl_sync(full, towards_head, m - 1);
-                        if (m < want && m < 8) {
-                            m = 0;
-                            if (lane == 0) {
-                                uint32_t b = coldest;
-                                while (m < want && b != kHead) {
-                                    tmp[m++] = b;
-                                    b = lprev[b];
-                                }
-                                after = b;
-                            }
-                            m = __shfl_sync(full, m, 0);
-                            after = __shfl_sync(full, after, 0);
-                            __syncwarp();
-                            cand = lane < m ? tmp[lane] : kNone;
-                        }
-                        const bool mine = lane < m;
-                        const uint32_t nd = mine ? node_of[cand] : 0u;
-                        const uint32_t up = mine ? n_parent[nd] : 0u;
-                        // The whole group goes at once when every candidate sits in a data leaf and no parent runs
-                        // out of cached children while it still has blocks outside the queue (nothing is re-queued,
-                        // so the queue stays as it was followed).
-                        const uint32_t same_up = __match_any_sync(full, mine ? up : kNone - lane);
-                        const uint32_t same_nd = __match_any_sync(full, mine ? nd : kNone - lane);
-                        bool plain = true;
-                        if (mine) {
-                            const uint32_t under = static_cast<uint32_t>(__popc(same_up));
-                            plain = n_childc[nd] == 0 && (up == 0 || n_unlisted[up] == 0 || n_childc[up] > under);
-                        }
-                        if (__all_sync(full, plain) && static_cast<int64_t>(n_ev) + m <= nk) {
-                            if (mine) {
-                                flags[cand] = 0;
-                                evicted[n_ev + lane] = nd;
-                                if (static_cast<uint32_t>(__ffs(same_nd) - 1) == lane) {
-                                    atomicSub(&n_cached[nd], static_cast<uint32_t>(__popc(same_nd)));
-                                }
-                            }
-                            __syncwarp();  // n_childc is read above for nodes that are parents here
-                            if (mine && static_cast<uint32_t>(__ffs(same_up) - 1) == lane) {
-                                atomicSub(&n_childc[up], static_cast<uint32_t>(__popc(same_up)));
-                            }
-                            if (lane == 0) {
-                                lnext[after] = kTail;
-                                lprev[kTail] = after;
-                                resident -= m;
-                            }
-                            __syncwarp();
-                            n_ev += m;
-                            got += m;
-                            continue;
-                        }
-                        // otherwise one block after the other, up to the same number
-                        uint32_t g = 0;
-                        if (lane == 0) {
-                            while (g < want) {
-                                const uint32_t b = lprev[kTail];
-                                if (b == kHead) break;
-                                if (++spins > 2 * walk_cap || static_cast<int64_t>(n_ev) >= nk) {
-                                    ++faults;  // a block leaves the queue at most twice per check, and is evicted once
-                                    break;
-                                }
-                                const uint32_t a = lprev[b];
-                                lnext[a] = kTail;
-                                lprev[kTail] = a;
-                                const uint32_t node_b = node_of[b];
-                                if (n_childc[node_b] != 0) {  // its node has cached children by now: out of the queue
-                                    flags[b] = kCached;
-                                    n_unlisted[node_b] += 1;
-                                    continue;
-                                }
-                                flags[b] = 0;
-                                n_cached[node_b] -= 1;
-                                const uint32_t up_b = n_parent[node_b];
-                                n_childc[up_b] -= 1;
-                                --resident;
-                                evicted[n_ev++] = node_b;
-                                ++g;
-                                // UpdateNodeState(parent): a parent that became a data leaf queues its blocks, in order
-                                if (up_b != 0 && n_childc[up_b] == 0 && n_unlisted[up_b] != 0) {
-                                    const uint32_t c = n_blocks[up_b];
-                                    uint32_t id = n_last[up_b];
-                                    uint32_t k = c;
-                                    while (k > 0 && id != kNone) {
-                                        tmp[--k] = id;
-                                        id = p.pred[id];
-                                    }
-                                    if (k != 0) ++faults;
-                                    for (; k < c; ++k) {
-                                        const uint32_t x = tmp[k];
-                                        if ((flags[x] & (kCached | kListed)) == kCached) {
-                                            insert_by_time(x);
-                                            flags[x] = kCached | kListed;
-                                        }
-                                    }
-                                    n_unlisted[up_b] = 0;
-                                }
-                            }
-                        }
-                        g = __shfl_sync(full, g, 0);
-                        n_ev = __shfl_sync(full, n_ev, 0);
-                        __syncwarp();
-                        got += g;
-                        if (g < want) {
-                            dry = true;
-                            break;
-                        }
+                        if (!any) break;
                     }
-                    if (got == 0) break;
-                    total += got;
+                } else {
+                    while (total < excess) {
+                        const int64_t rest = excess - total;
+                        const int64_t count = p.mode == 3 && rest < p.evict_batch ? rest : p.evict_batch;
+                        const int64_t got = evict_from(me, count);
+                        if (got == 0) break;
+                        total += got;
+                    }
                 }
-                // CleanEmptyBlocks (radix_tree_index.cc:284-325): childless nodes without a cached block go, among
-                // the nodes that own an evicted block, until nothing more goes.  The lanes look at the nodes of 32
-                // evicted blocks at a time and remove what they find; the order of removals does not change what
-                // remains.  Another round is needed only when a removal left a parent childless.
+                // CleanEmptyBlocks (radix_tree_index.cc:284-325), per instance in the reference; the trees do not
+                // touch, so one pass over everything evicted does the same: childless nodes without a cached block
+                // go, among the nodes that own an evicted block, until nothing more goes.  The lanes look at the
+                // nodes of 32 evicted blocks at a time and remove what they find; the order of removals does not
+                // change what remains.  Another round is needed only when a removal left a parent childless.
                 bool again = n_ev != 0;
                 while (again) {
                     again = false;
                     for (uint32_t e0 = 0; e0 < n_ev; e0 += 32) {
                         const uint32_t e = e0 + lane;
                         const uint32_t node_e = e < n_ev ? evicted[e] : 0u;
-                        const bool empty = node_e != 0 && n_cached[node_e] == 0 && n_children[node_e] == 0 &&
+                        const bool empty = node_e >= n_roots && n_cached[node_e] == 0 && n_children[node_e] == 0 &&
                                            n_blocks[node_e] != 0;
                         const uint32_t same = __match_any_sync(full, empty ? node_e : kNone - lane);
                         bool orphaned = false;
                         if (empty && static_cast<uint32_t>(__ffs(same) - 1) == lane) {  // once per node
                             n_blocks[node_e] = 0;  // its keys are out of the tree from here on
                             const uint32_t above = n_parent[node_e];
-                            orphaned = atomicSub(&n_children[above], 1u) == 1u && above != 0;
+                            orphaned = atomicSub(&n_children[above], 1u) == 1u && above >= n_roots;
                         }
                         again = __any_sync(full, orphaned) || again;
                         __syncwarp();
@@ -605,14 +715,18 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                 p.ext_hit[out0 + t] = ext;
                 p.int_hit[out0 + t] = inte;
                 p.written[out0 + t] = wr;
-                p.cache_blocks[out0 + t] = resident;
+                p.cache_blocks[out0 + t] = cached_of[me];
             }
             sum_ext += ext;
             sum_int += inte;
             sum_wr += wr;
         }
-        beg = beg1, n = n1, ty = ty1, skip = skip1, now = now1, first_id = next_first_id;
-        beg1 = beg2, n1 = n2, ty1 = ty2, skip1 = skip2, now1 = now2;
+        if (p.inst_blocks_trace != nullptr) {  // ReadRecord::blocks_per_instance of the reference's result records
+            int64_t *row = p.inst_blocks_trace + (out0 + t) * K;
+            for (int32_t j = lane; j < K; j += 32) row[j] = cached_of[j];
+        }
+        beg = beg1, n = n1, ty = ty1, skip = skip1, now = now1, me = me1, first_id = next_first_id;
+        beg1 = beg2, n1 = n2, ty1 = ty2, skip1 = skip2, now1 = now2, me1 = me2;
     }
     if (lane == 0) {
         if (p.totals != nullptr) {
@@ -624,31 +738,33 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
         }
         if (faults != 0 && p.status != nullptr) atomicAdd(&p.status[0], faults);
     }
+    if (p.inst_blocks != nullptr) {
+        for (int32_t j = lane; j < K; j += 32) p.inst_blocks[cfg * K + j] = cached_of[j];
+    }
 }
 
 struct LeafLayout {
-    uint64_t table_off, ids_off, pred_off, occ_off, node_of_off, flags_off, time_off, lprev_off, lnext_off, tmp_off, evicted_off,
-        nodes_off, total;
+    uint64_t table_off, ids_off, occ_off, node_of_off, flags_off, time_off, lprev_off, lnext_off, evicted_off, nodes_off,
+        total;
     int64_t max_nodes;
 };
 
-LeafLayout LayoutFor(int64_t n_keys, int32_t n_traces, int32_t n_configs) {
+LeafLayout LayoutFor(int64_t n_keys, int32_t n_traces, int32_t n_configs, int32_t n_instances) {
     auto up = [](uint64_t v) { return (v + 255u) & ~static_cast<uint64_t>(255u); };
     LeafLayout l;
     const uint64_t nk = static_cast<uint64_t>(n_keys > 0 ? n_keys : 1);
     const uint64_t nc = static_cast<uint64_t>(n_configs);
-    l.max_nodes = 2 * static_cast<int64_t>(n_traces) + 2;  // the root, and at most two new nodes per trace
+    const uint64_t links = nk + 2ull * static_cast<uint64_t>(n_instances);
+    l.max_nodes = 2 * static_cast<int64_t>(n_traces) + n_instances + 1;  // the roots, and at most two new nodes per trace
     l.table_off = 256;
     l.ids_off = up(l.table_off + SlotsFor(n_keys) * sizeof(ulonglong2));
-    l.pred_off = up(l.ids_off + nk * 4);
-    l.occ_off = up(l.pred_off + nk * 4);
+    l.occ_off = up(l.ids_off + nk * 4);
     l.node_of_off = up(l.occ_off + nk * 4);
     l.flags_off = up(l.node_of_off + nk * 4 * nc);
     l.time_off = up(l.flags_off + nk * nc);
     l.lprev_off = up(l.time_off + nk * 8 * nc);
-    l.lnext_off = up(l.lprev_off + (nk + 2) * 4 * nc);
-    l.tmp_off = up(l.lnext_off + (nk + 2) * 4 * nc);
-    l.evicted_off = up(l.tmp_off + nk * 4 * nc);
+    l.lnext_off = up(l.lprev_off + links * 4 * nc);
+    l.evicted_off = up(l.lnext_off + links * 4 * nc);
     l.nodes_off = up(l.evicted_off + nk * 4 * nc);
     l.total = up(l.nodes_off + static_cast<uint64_t>(l.max_nodes) * 4 * kNodeFields * nc);
     return l;
@@ -659,12 +775,115 @@ LeafLayout LayoutFor(int64_t n_keys, int32_t n_traces, int32_t n_configs) {
 
 extern "C" {
 
-int64_t kvcm_b200_replay_leaf_lru_workspace_bytes(int64_t n_keys_total, int32_t n_traces, int32_t n_configs) {
-    if (n_keys_total < 0 || n_keys_total >= (1ll << 32) - 3 || n_traces < 0 || n_traces >= (1 << 30) ||
-        n_configs <= 0 || n_configs > 65535) {
+int64_t kvcm_b200_replay_leaf_lru_group_workspace_bytes(int64_t n_keys_total, int32_t n_traces, int32_t n_configs,
+                                                        int32_t n_instances) {
+    if (n_keys_total < 0 || n_keys_total >= (1ll << 32) - 3 - 2 * KVCM_B200_REPLAY_GROUP_MAX_INSTANCES || n_traces < 0 ||
+        n_traces >= (1 << 30) || n_configs <= 0 || n_configs > 65535 || n_instances <= 0 ||
+        n_instances > KVCM_B200_REPLAY_GROUP_MAX_INSTANCES) {
         return -1;
     }
-    return static_cast<int64_t>(kvcm::LayoutFor(n_keys_total, n_traces, n_configs).total);
+    return static_cast<int64_t>(kvcm::LayoutFor(n_keys_total, n_traces, n_configs, n_instances).total);
+}
+
+int64_t kvcm_b200_replay_leaf_lru_workspace_bytes(int64_t n_keys_total, int32_t n_traces, int32_t n_configs) {
+    return kvcm_b200_replay_leaf_lru_group_workspace_bytes(n_keys_total, n_traces, n_configs, 1);
+}
+
+int32_t kvcm_b200_replay_leaf_lru_group(const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type,
+                                        const int64_t *d_mask_off, const uint8_t *d_mask_bits,
+                                        const int64_t *d_timestamps, const int32_t *d_trace_instance,
+                                        int32_t n_instances, int32_t n_traces, int64_t n_keys_total,
+                                        const int64_t *d_quota_blocks, int32_t n_configs, int32_t evict_batch,
+                                        int32_t eviction_mode, void *d_workspace, int64_t workspace_bytes,
+                                        int32_t *d_ext_hit, int32_t *d_int_hit, int32_t *d_written,
+                                        int64_t *d_cache_blocks, int64_t *d_totals, int64_t *d_instance_blocks,
+                                        int64_t *d_instance_blocks_per_trace, uint32_t *d_status,
+                                        kvcm_stream_t stream) {
+    if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
+    if (n_traces < 0 || n_keys_total < 0 || n_configs <= 0 || evict_batch <= 0 || n_instances <= 0 ||
+        eviction_mode < 1 || eviction_mode > 3) {
+        return KVCM_EC_BADARGS;
+    }
+    const int64_t need = kvcm_b200_replay_leaf_lru_group_workspace_bytes(n_keys_total, n_traces, n_configs, n_instances);
+    if (need < 0) return KVCM_EC_OUT_OF_LIMIT;
+    if (n_traces == 0) return KVCM_OK;
+    const int per_trace = (d_ext_hit != nullptr) + (d_int_hit != nullptr) + (d_written != nullptr) +
+                          (d_cache_blocks != nullptr);
+    if (d_key_off == nullptr || d_trace_type == nullptr || d_quota_blocks == nullptr || d_workspace == nullptr ||
+        (d_trace_instance == nullptr && n_instances > 1) || (d_keys == nullptr && n_keys_total > 0) ||
+        (per_trace != 0 && per_trace != 4) || (per_trace == 0 && d_totals == nullptr)) {
+        return KVCM_ER_INVALID_ADDRESS;
+    }
+    if (reinterpret_cast<uintptr_t>(d_workspace) & 255u) return KVCM_ER_INVALID_ADDRESS;
+    if (workspace_bytes < need) return KVCM_EC_NOSPC;
+    const kvcm::LeafLayout l = kvcm::LayoutFor(n_keys_total, n_traces, n_configs, n_instances);
+    uint8_t *ws = static_cast<uint8_t *>(d_workspace);
+    kvcm::IdTable t;
+    t.cells = reinterpret_cast<unsigned long long *>(ws);
+    t.slots = reinterpret_cast<ulonglong2 *>(ws + l.table_off);
+    t.mask = kvcm::SlotsFor(n_keys_total) - 1;
+    uint32_t *ids = reinterpret_cast<uint32_t *>(ws + l.ids_off);
+    uint32_t *occ = reinterpret_cast<uint32_t *>(ws + l.occ_off);
+    const uint64_t nk = static_cast<uint64_t>(n_keys_total > 0 ? n_keys_total : 1);
+    cudaStream_t s = kvcm::AsStream(stream);
+    const int sms = kvcm::GetDeviceInfo().sm_count;
+    kvcm::LeafSweep p;
+    p.ids = ids;
+    p.occ = occ;
+    p.key_off = d_key_off;
+    p.type = d_trace_type;
+    p.mask_off = d_mask_off;
+    p.mask_bits = d_mask_bits;
+    p.timestamps = d_timestamps;
+    p.trace_inst = d_trace_instance;
+    p.quota = d_quota_blocks;
+    p.node_of = reinterpret_cast<uint32_t *>(ws + l.node_of_off);
+    p.flags = ws + l.flags_off;
+    p.time = reinterpret_cast<int64_t *>(ws + l.time_off);
+    p.lprev = reinterpret_cast<uint32_t *>(ws + l.lprev_off);
+    p.lnext = reinterpret_cast<uint32_t *>(ws + l.lnext_off);
+    p.evicted = reinterpret_cast<uint32_t *>(ws + l.evicted_off);
+    p.nodes = reinterpret_cast<uint32_t *>(ws + l.nodes_off);
+    p.ext_hit = d_ext_hit;
+    p.int_hit = d_int_hit;
+    p.written = d_written;
+    p.cache_blocks = d_cache_blocks;
+    p.totals = d_totals;
+    p.inst_blocks = d_instance_blocks;
+    p.inst_blocks_trace = d_instance_blocks_per_trace;
+    p.status = d_status;
+    p.n_keys = static_cast<int64_t>(nk);
+    p.n_ids = n_keys_total;
+    p.max_nodes = l.max_nodes;
+    p.n_traces = n_traces;
+    p.n_configs = n_configs;
+    p.evict_batch = evict_batch;
+    p.n_instances = n_instances;
+    p.mode = eviction_mode;
+    kvcm::LeafInitKernel<<<sms * 8, 256, 0, s>>>(t, p.node_of, p.flags, nk * static_cast<uint64_t>(n_configs));
+    if (d_trace_instance != nullptr) {
+        kvcm::LeafCheckInstancesKernel<<<sms, 256, 0, s>>>(d_trace_instance, n_traces, n_instances, d_status);
+    }
+    if (n_keys_total > 0) {
+        if (d_trace_instance == nullptr) {
+            kvcm::LruClaimIdsKernel<<<sms * 8, 256, 0, s>>>(t, d_keys, n_keys_total, d_status);
+            kvcm::LruLookupIdsKernel<<<sms * 8, 256, 0, s>>>(t, d_keys, n_keys_total, ids);
+        } else {
+            // keys of traces that name no instance of the group keep id 0: the sweep replays those traces as empty
+            cudaMemsetAsync(ids, 0, static_cast<size_t>(n_keys_total) * sizeof(uint32_t), s);
+            // one instance after the other: the table starts empty each time, the id counter runs on
+            for (int32_t j = 0; j < n_instances; ++j) {
+                if (j > 0) kvcm::IdTableClearKernel<<<sms * 8, 256, 0, s>>>(t);
+                kvcm::LruClaimIdsOfInstanceKernel<<<sms * 4, 256, 0, s>>>(t, d_keys, d_key_off, d_trace_instance,
+                                                                         n_traces, j, d_status);
+                kvcm::LruLookupIdsOfInstanceKernel<<<sms * 4, 256, 0, s>>>(t, d_keys, d_key_off, d_trace_instance,
+                                                                          n_traces, j, ids);
+            }
+        }
+        kvcm::LeafOccKernel<<<sms * 4, 256, 0, s>>>(ids, d_key_off, d_trace_instance, n_instances, n_traces, occ);
+    }
+    kvcm::LeafSweepKernel<<<static_cast<unsigned>(n_configs), 32, sizeof(int64_t) * n_instances, s>>>(p);
+    return kvcm::LaunchStatus();
 }
 
 int32_t kvcm_b200_replay_leaf_lru(const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type,
@@ -674,71 +893,10 @@ int32_t kvcm_b200_replay_leaf_lru(const int64_t *d_keys, const int64_t *d_key_of
                                   int64_t workspace_bytes, int32_t *d_ext_hit, int32_t *d_int_hit, int32_t *d_written,
                                   int64_t *d_cache_blocks, int64_t *d_totals, uint32_t *d_status,
                                   kvcm_stream_t stream) {
-    if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
-    if (n_traces < 0 || n_keys_total < 0 || n_configs <= 0 || evict_batch <= 0) return KVCM_EC_BADARGS;
-    const int64_t need = kvcm_b200_replay_leaf_lru_workspace_bytes(n_keys_total, n_traces, n_configs);
-    if (need < 0) return KVCM_EC_OUT_OF_LIMIT;
-    if (n_traces == 0) return KVCM_OK;
-    const int per_trace = (d_ext_hit != nullptr) + (d_int_hit != nullptr) + (d_written != nullptr) +
-                          (d_cache_blocks != nullptr);
-    if (d_key_off == nullptr || d_trace_type == nullptr || d_quota_blocks == nullptr || d_workspace == nullptr ||
-        (d_keys == nullptr && n_keys_total > 0) || (per_trace != 0 && per_trace != 4) ||
-        (per_trace == 0 && d_totals == nullptr)) {
-        return KVCM_ER_INVALID_ADDRESS;
-    }
-    if (reinterpret_cast<uintptr_t>(d_workspace) & 255u) return KVCM_ER_INVALID_ADDRESS;
-    if (workspace_bytes < need) return KVCM_EC_NOSPC;
-    const kvcm::LeafLayout l = kvcm::LayoutFor(n_keys_total, n_traces, n_configs);
-    uint8_t *ws = static_cast<uint8_t *>(d_workspace);
-    kvcm::IdTable t;
-    t.cells = reinterpret_cast<unsigned long long *>(ws);
-    t.slots = reinterpret_cast<ulonglong2 *>(ws + l.table_off);
-    t.mask = kvcm::SlotsFor(n_keys_total) - 1;
-    uint32_t *ids = reinterpret_cast<uint32_t *>(ws + l.ids_off);
-    uint32_t *pred = reinterpret_cast<uint32_t *>(ws + l.pred_off);
-    uint32_t *occ = reinterpret_cast<uint32_t *>(ws + l.occ_off);
-    const uint64_t nk = static_cast<uint64_t>(n_keys_total > 0 ? n_keys_total : 1);
-    cudaStream_t s = kvcm::AsStream(stream);
-    const int sms = kvcm::GetDeviceInfo().sm_count;
-    kvcm::LeafSweep p;
-    p.ids = ids;
-    p.pred = pred;
-    p.occ = occ;
-    p.key_off = d_key_off;
-    p.type = d_trace_type;
-    p.mask_off = d_mask_off;
-    p.mask_bits = d_mask_bits;
-    p.timestamps = d_timestamps;
-    p.quota = d_quota_blocks;
-    p.node_of = reinterpret_cast<uint32_t *>(ws + l.node_of_off);
-    p.flags = ws + l.flags_off;
-    p.time = reinterpret_cast<int64_t *>(ws + l.time_off);
-    p.lprev = reinterpret_cast<uint32_t *>(ws + l.lprev_off);
-    p.lnext = reinterpret_cast<uint32_t *>(ws + l.lnext_off);
-    p.tmp = reinterpret_cast<uint32_t *>(ws + l.tmp_off);
-    p.evicted = reinterpret_cast<uint32_t *>(ws + l.evicted_off);
-    p.nodes = reinterpret_cast<uint32_t *>(ws + l.nodes_off);
-    p.ext_hit = d_ext_hit;
-    p.int_hit = d_int_hit;
-    p.written = d_written;
-    p.cache_blocks = d_cache_blocks;
-    p.totals = d_totals;
-    p.status = d_status;
-    p.n_keys = static_cast<int64_t>(nk);
-    p.n_ids = n_keys_total;
-    p.max_nodes = l.max_nodes;
-    p.n_traces = n_traces;
-    p.n_configs = n_configs;
-    p.evict_batch = evict_batch;
-    p.precise = precise;
-    kvcm::LeafInitKernel<<<sms * 8, 256, 0, s>>>(t, p.node_of, p.flags, nk * static_cast<uint64_t>(n_configs), pred, nk);
-    if (n_keys_total > 0) {
-        kvcm::LruClaimIdsKernel<<<sms * 8, 256, 0, s>>>(t, d_keys, n_keys_total, d_status);
-        kvcm::LruLookupIdsKernel<<<sms * 8, 256, 0, s>>>(t, d_keys, n_keys_total, ids);
-        kvcm::LeafPredKernel<<<sms * 4, 256, 0, s>>>(ids, d_key_off, n_traces, pred, occ);
-    }
-    kvcm::LeafSweepKernel<<<static_cast<unsigned>(n_configs), 32, 0, s>>>(p);
-    return kvcm::LaunchStatus();
+    return kvcm_b200_replay_leaf_lru_group(d_keys, d_key_off, d_trace_type, d_mask_off, d_mask_bits, d_timestamps,
+                                           nullptr, 1, n_traces, n_keys_total, d_quota_blocks, n_configs, evict_batch,
+                                           precise != 0 ? 3 : 2, d_workspace, workspace_bytes, d_ext_hit, d_int_hit,
+                                           d_written, d_cache_blocks, d_totals, nullptr, nullptr, d_status, stream);
 }
 
 }  // extern "C"

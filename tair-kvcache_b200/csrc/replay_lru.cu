@@ -278,7 +278,10 @@ __global__ void __launch_bounds__(32) LruGroupSweepKernel(const LruSweep p, cons
             *ty = p.type[t];
             *skip = (*ty == 1 && p.mask_off != nullptr) ? p.mask_off[t] : 0;
             *who = g.trace_inst[t];
-            if (*who < 0 || *who >= K) *who = 0;  // counted by LruGroupExtentKernel
+            if (*who < 0 || *who >= K) {  // counted by LruGroupExtentKernel; its keys have no ids: an empty trace
+                *who = 0;
+                *n = 0;
+            }
         } else {
             *beg = 0, *n = 0, *ty = 1, *skip = 0, *who = 0;
         }

@@ -178,14 +178,19 @@ def RunTracesLruGroup(keys: torch.Tensor, key_off: torch.Tensor, trace_type: tor
                       mask_off: Optional[torch.Tensor] = None, evict_batch: int = 100,
                       mode: int = EVICTION_MODE_GROUP_ROUGH, workspace: Optional[torch.Tensor] = None,
                       status: Optional[torch.Tensor] = None, per_trace: bool = True,
-                      mask_bits: Optional[torch.Tensor] = None, instance_records: bool = False) -> LruGroupSweepResult:
-    """The "lru" sweep for an instance group whose instances share one quota
+                      mask_bits: Optional[torch.Tensor] = None, instance_records: bool = False,
+                      policy: str = "lru", timestamps: Optional[torch.Tensor] = None) -> LruGroupSweepResult:
+    """The "lru" (default) or "leaf_aware_lru" sweep for an instance group whose instances share one quota
     (kv_cache_manager/optimizer/manager/eviction_manager.cc:86-266): trace_instance (int32 per trace, values in
     [0, n_instances)) names each trace's instance, the traces of all instances come in one replay order, and the
     same key in two instances is two blocks.  mode is the reference's eviction_mode: GROUP_ROUGH takes rounds of
     evict_batch blocks from every instance, the INSTANCE modes take from the writing instance only.
     instance_records=True also returns the usage of every instance after each trace (the reference's
-    ReadRecord::blocks_per_instance, which fills two columns of its hit-rate CSV)."""
+    ReadRecord::blocks_per_instance, which fills two columns of its hit-rate CSV).  policy is the
+    eviction_policy_type of every instance of the group; timestamps (int64 per trace, the traces' timestamp_us)
+    is read by "leaf_aware_lru" only, which orders re-queued blocks by it (the trace number when None)."""
+    if policy not in ("lru", "leaf_aware_lru"):
+        raise ValueError("eviction policy %r is not built for groups of instances (have: lru, leaf_aware_lru)" % (policy,))
     if not keys.is_cuda:
         raise ValueError("keys must be a CUDA tensor: this path has no CPU implementation")
     dev = keys.device
@@ -197,7 +202,12 @@ def RunTracesLruGroup(keys: torch.Tensor, key_off: torch.Tensor, trace_type: tor
     if trace_instance.dtype != torch.int32 or trace_instance.numel() != n_traces or trace_instance.device != dev:
         raise ValueError("trace_instance must be an int32 tensor with one entry per trace, on the keys' device")
     trace_instance = trace_instance.contiguous()
-    need = _cabi.lib().kvcm_b200_replay_lru_group_workspace_bytes(keys.numel(), n_cfg, int(n_instances))
+    leaf = policy == "leaf_aware_lru"
+    if leaf:
+        need = _cabi.lib().kvcm_b200_replay_leaf_lru_group_workspace_bytes(keys.numel(), n_traces, n_cfg,
+                                                                          int(n_instances))
+    else:
+        need = _cabi.lib().kvcm_b200_replay_lru_group_workspace_bytes(keys.numel(), n_cfg, int(n_instances))
     if need < 0:
         raise ValueError("too many keys, configurations or instances for one group replay call")
     if workspace is None:
@@ -218,6 +228,19 @@ def RunTracesLruGroup(keys: torch.Tensor, key_off: torch.Tensor, trace_type: tor
     if n_traces == 0:
         return LruGroupSweepResult(ext, inte, wr, size, totals, inst, per_inst)
     _cabi.bind_device(dev.index)
+    if leaf:
+        if timestamps is not None:
+            if timestamps.dtype != torch.int64 or timestamps.numel() != n_traces or timestamps.device != dev:
+                raise ValueError("timestamps must be an int64 tensor with one entry per trace, on the keys' device")
+            timestamps = timestamps.contiguous()
+        _cabi.call("kvcm_b200_replay_leaf_lru_group", keys.data_ptr(), key_off.data_ptr(), trace_type.data_ptr(),
+                   mask_off.contiguous().data_ptr() if mask_off is not None else None, _mask_bits_ptr(mask_bits, keys),
+                   timestamps.data_ptr() if timestamps is not None else None, trace_instance.data_ptr(),
+                   int(n_instances), n_traces, keys.numel(), quota.data_ptr(), n_cfg, int(evict_batch), int(mode),
+                   workspace.data_ptr(), workspace.numel(), ptr(ext), ptr(inte), ptr(wr), ptr(size), totals.data_ptr(),
+                   inst.data_ptr(), ptr(per_inst), status.data_ptr() if status is not None else None,
+                   torch.cuda.current_stream(dev).cuda_stream)
+        return LruGroupSweepResult(ext, inte, wr, size, totals, inst, per_inst)
     _cabi.call("kvcm_b200_replay_lru_group_records", keys.data_ptr(), key_off.data_ptr(), trace_type.data_ptr(),
                mask_off.contiguous().data_ptr() if mask_off is not None else None, _mask_bits_ptr(mask_bits, keys),
                trace_instance.data_ptr(), int(n_instances), n_traces, keys.numel(), quota.data_ptr(), n_cfg,

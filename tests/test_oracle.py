@@ -364,6 +364,31 @@ def test_lru_group_quota_shared_by_two_instances():
             assert np.array_equal(x, y)
 
 
+def test_leaf_aware_group_of_two_instances_by_hand():
+    # kv_cache_manager/optimizer/manager/eviction_manager.cc:86-146 over LeafAwareLruEvictionPolicy::EvictBlocks
+    # (kv_cache_manager/optimizer/eviction_policy/leaf_aware_lru.cc:85-160), quota 5, batches of 1, group rough; no
+    # test of the reference covers this.
+    #   a writes 1 2 3, then 1 2 9 (a split: {1 2} over {3} and {9}); b writes 1 2: the group holds 6.
+    #   The round asks a first: 1 and 2 sit in a node with cached children and only leave the queue, 3 goes;
+    #   then b, whose {1 2} is a leaf: 1 goes.  a reads 1 2 3 -> 2 hits; b reads 1 2 -> none.
+    #   a writes 5, b writes 7 8 (7 held).  a loses 9, which turns {1 2} into a data leaf: both are queued again,
+    #   at the cold end behind 5 (their time, 3, is the oldest), 1 before 2; b loses 2.
+    #   a reads 1 2 9 -> 2 hits and both move to the front, so a's next victim is 5; b's is 7.
+    traces = [[1, 2, 3], [1, 2, 9], [1, 2], [1, 2, 3], [1, 2], [5], [7, 8], [1, 2, 9], [6]]
+    inst = [0, 0, 1, 0, 1, 0, 1, 0, 0]
+    types = [W, W, W, G, G, W, W, G, W]
+    keys = [k for t in traces for k in t]
+    off = np.cumsum([0] + [len(t) for t in traces])
+    run = lambda mode: oracle.LruGroupReplay(5, 2, evict_batch=1, mode=mode, policy="leaf_aware_lru").run(
+        keys, off, types, inst, timestamps=list(range(9)))
+    ext, inte, wr, size, final = run(1)
+    assert ext.tolist() == [0, 0, 0, 2, 0, 0, 0, 2, 0] and wr.tolist() == [3, 1, 2, 0, 0, 1, 2, 0, 1]
+    assert size.tolist() == [3, 4, 1, 3, 1, 4, 2, 3, 3] and final.tolist() == [3, 1]
+    for mode in (2, 3):  # from the writing instance only: b pays for its own writes, a keeps 3
+        ext, inte, wr, size, final = run(mode)
+        assert ext.tolist() == [0, 0, 0, 3, 0, 0, 0, 2, 0] and final.tolist() == [4, 1]
+
+
 def test_location_status_cases_of_the_reference_tests():
     """Update / compare-and-set / compare-and-delete / delete of location statuses, replayed from the tables of
     kv_cache_manager/manager/test/meta_searcher_test.cc (tests/golden/status_kat.json)."""
