@@ -56,8 +56,8 @@ struct LeafSweep {
     uint32_t *node_of;  // [n_configs][n_keys]
     uint8_t *flags;     // [n_configs][n_keys]
     int64_t *time;      // [n_configs][n_keys]  last_access_time
-    uint32_t *lprev;    // [n_configs][n_keys + 2 * n_instances]
-    uint32_t *lnext;    // [n_configs][n_keys + 2 * n_instances]
+    uint32_t *lprev;    // [n_configs][n_keys]  towards the hot end; the sentinels' links are in shared memory
+    uint32_t *lnext;    // [n_configs][n_keys]  towards the cold end
     uint32_t *evicted;  // [n_configs][n_keys]  the nodes of the blocks evicted after one trace
     uint32_t *nodes;    // [n_configs][kNodeFields][max_nodes]
     int32_t *ext_hit, *int_hit, *written;
@@ -122,6 +122,10 @@ __global__ void __launch_bounds__(256)
 __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
     extern __shared__ int64_t cached_of[];  // [n_instances]: cached blocks per instance (EvictionPolicy::size())
     __shared__ uint32_t short_group[32];
+    // The sentinels' own links live in shared memory only (the hot and the cold end of every instance's queue are
+    // read for every trace and every eviction): the links of keys are in global memory.
+    uint32_t *front_of = reinterpret_cast<uint32_t *>(cached_of + p.n_instances);  // [n_instances]: hottest entry
+    uint32_t *cold_of = front_of + p.n_instances;                                  // [n_instances]: coldest entry
     const int64_t cfg = blockIdx.x;
     const uint32_t lane = LaneId();
     const uint32_t full = 0xffffffffu;
@@ -132,8 +136,8 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
     uint32_t *node_of = p.node_of + cfg * nk;
     uint8_t *flags = p.flags + cfg * nk;
     int64_t *time = p.time + cfg * nk;
-    uint32_t *lprev = p.lprev + cfg * (nk + 2 * K);
-    uint32_t *lnext = p.lnext + cfg * (nk + 2 * K);
+    uint32_t *lprev = p.lprev + cfg * nk;
+    uint32_t *lnext = p.lnext + cfg * nk;
     uint32_t *evicted = p.evicted + cfg * nk;
     uint32_t *node = p.nodes + cfg * kNodeFields * p.max_nodes;
     uint32_t *n_parent = node, *n_children = node + p.max_nodes, *n_blocks = node + 2 * p.max_nodes;
@@ -145,6 +149,23 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
     const uint64_t walk_cap = static_cast<uint64_t>(nk) + 2;
     // the queue of instance j lies between the sentinels head_of(j) (hot end) and head_of(j) + 1 (cold end)
     auto head_of = [&](int32_t j) { return static_cast<uint32_t>(nk) + 2u * static_cast<uint32_t>(j); };
+    // x is a key or a sentinel of instance j's queue (hd = its hot-end sentinel)
+    auto get_next = [&](uint32_t x, uint32_t hd, int32_t j) { return x == hd ? front_of[j] : lnext[x]; };
+    auto get_prev = [&](uint32_t x, uint32_t hd, int32_t j) { return x == hd + 1 ? cold_of[j] : lprev[x]; };
+    auto set_next = [&](uint32_t x, uint32_t v, uint32_t hd, int32_t j) {
+        if (x == hd) {
+            front_of[j] = v;
+        } else {
+            lnext[x] = v;
+        }
+    };
+    auto set_prev = [&](uint32_t x, uint32_t v, uint32_t hd, int32_t j) {
+        if (x == hd + 1) {
+            cold_of[j] = v;
+        } else {
+            lprev[x] = v;
+        }
+    };
 
     // owned by lane 0
     uint32_t n_nodes = n_roots, faults = 0;
@@ -171,12 +192,12 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
     // insert_sorted_by_priority picks them (leaf_aware_lru.cc:53-83), put a block of time bt into the queue between
     // hd and hd + 1: the entry it goes in front of, and whether the walk came from the hot end.  An insertion from the
     // hot end lands in front of the entries of equal time, one from the cold end behind them.  Lane 0.
-    auto insertion_point = [&](int64_t bt, uint32_t hd, bool *from_hot) -> uint32_t {
+    auto insertion_point = [&](int64_t bt, uint32_t hd, int32_t j, bool *from_hot) -> uint32_t {
         const uint32_t tl = hd + 1;
-        const uint32_t h = lnext[hd];
+        const uint32_t h = front_of[j];
         *from_hot = true;
         if (h == tl) return tl;
-        const uint32_t c = lprev[tl];
+        const uint32_t c = cold_of[j];
         const int64_t ht = time[h], ct = time[c];
         *from_hot = bt >= ht ? true : (bt <= ct ? false : (ht - bt) < (bt - ct));
         uint64_t steps = 0;
@@ -188,7 +209,7 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
         } else {
             uint32_t cur = c;
             while (cur != hd && time[cur] < bt && ++steps < walk_cap) cur = lprev[cur];
-            before = lnext[cur];
+            before = get_next(cur, hd, j);
         }
         if (steps >= walk_cap) ++faults;
         return before;
@@ -200,7 +221,7 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
     // the first one and lands in front of it (from the hot end) or behind it (from the cold end), and so on - so a
     // run of blocks that share a time costs one walk for its first block and one splice: lanes write the links
     // inside the run, lane 0 the two links around it.  Blocks written or touched by one trace share a time.
-    auto requeue_node = [&](uint32_t u, uint32_t hd) {
+    auto requeue_node = [&](uint32_t u, uint32_t hd, int32_t j) {
         const uint32_t c = n_blocks[u];
         const uint32_t last = n_last[u];
         const int64_t first_pos = last != kNone ? static_cast<int64_t>(p.occ[last]) - static_cast<int64_t>(c) + 1 : -1;
@@ -228,8 +249,8 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                 uint32_t before = 0, after = 0, hot = 0;  // the run goes between `after` (hotter) and `before`
                 if (lane == 0) {
                     bool from_hot;
-                    before = insertion_point(bt, hd, &from_hot);
-                    after = lprev[before];
+                    before = insertion_point(bt, hd, j, &from_hot);
+                    after = get_prev(before, hd, j);
                     hot = from_hot ? 1u : 0u;
                 }
                 before = __shfl_sync(full, before, 0);
@@ -250,8 +271,8 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                     flags[x] = kCached | kListed;
                 }
                 if (lane == 0) {
-                    lnext[after] = hot != 0 ? x_top : x_first;
-                    lprev[before] = hot != 0 ? x_first : x_top;
+                    set_next(after, hot != 0 ? x_top : x_first, hd, j);
+                    set_prev(before, hot != 0 ? x_first : x_top, hd, j);
                 }
                 __syncwarp();
             }
@@ -278,7 +299,7 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
             // follow it in the queue; each lane checks one link of the guess and the group is the part that the
             // queue's own links confirm.  A short group (keys shared by many traces) falls back to lane 0
             // following the links one by one.
-            const uint32_t coldest = lprev[tl];
+            const uint32_t coldest = cold_of[j];
             if (coldest == hd) break;  // the queue ran out
             const int64_t guess_at = static_cast<int64_t>(p.occ[coldest]) + lane;
             uint32_t cand = lane == 0 ? coldest : (guess_at < p.n_ids ? p.ids[guess_at] : kNone);
@@ -330,8 +351,8 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                     atomicSub(&n_childc[up], static_cast<uint32_t>(__popc(same_up)));
                 }
                 if (lane == 0) {
-                    lnext[after] = tl;
-                    lprev[tl] = after;
+                    set_next(after, tl, hd, j);
+                    cold_of[j] = after;
                     resident -= m;
                     cached_of[j] -= m;
                 }
@@ -347,16 +368,16 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                 uint32_t turned = kNone;
                 if (lane == 0) {
                     while (g < want) {
-                        const uint32_t b = lprev[tl];
+                        const uint32_t b = cold_of[j];
                         if (b == hd) break;
                         if (++spins > 2 * walk_cap || static_cast<int64_t>(n_ev) >= nk) {
                             ++faults;  // a block leaves the queue at most twice per check, and is evicted once
                             break;
                         }
                         const uint32_t a = lprev[b];
-                        lnext[a] = tl;
-                        lprev[tl] = a;
                         const uint32_t node_b = node_of[b];
+                        set_next(a, tl, hd, j);
+                        cold_of[j] = a;
                         if (n_childc[node_b] != 0) {  // its node has cached children by now: out of the queue
                             flags[b] = kCached;
                             n_unlisted[node_b] += 1;
@@ -376,7 +397,7 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                 }
                 turned = __shfl_sync(full, turned, 0);
                 if (turned == kNone) break;
-                requeue_node(turned, hd);
+                requeue_node(turned, hd, j);
             }
             g = __shfl_sync(full, g, 0);
             n_ev = __shfl_sync(full, n_ev, 0);
@@ -400,8 +421,8 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
             n_cached[j] = 0;
             n_childc[j] = 0;
             n_unlisted[j] = 0;
-            lnext[head_of(j)] = head_of(j) + 1;
-            lprev[head_of(j) + 1] = head_of(j);
+            front_of[j] = head_of(j) + 1;
+            cold_of[j] = head_of(j);
             cached_of[j] = 0;
         }
     }
@@ -494,18 +515,19 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
             for (int64_t base = 0; base < hit_len; base += 32) {
                 const int64_t i = base + lane;
                 const bool have = i < hit_len;
-                const uint32_t id = have ? p.ids[beg + i] : 0u;
+                const uint32_t id = have ? p.ids[beg + i] : kNone;
                 bool listed = false;
-                uint32_t towards_tail = kNone;
+                uint32_t ln = kNone, lp = kNone;  // this key's links, kept up to date below; they mean something only when queued
                 if (have) {
                     time[id] = now;
-                    const uint32_t link = lnext[id];  // read beside the flag; it means something only when queued
+                    ln = lnext[id];
+                    lp = lprev[id];
                     listed = (flags[id] & kListed) != 0;
-                    if (listed) towards_tail = link;
                 }
+                uint32_t front = front_of[me];  // kept equal in all lanes
                 const uint32_t id_before = __shfl_up_sync(full, id, 1);
                 const uint32_t listed_m = __ballot_sync(full, listed);
-                const bool joins = listed && lane > 0 && ((listed_m >> (lane - 1)) & 1u) != 0 && towards_tail == id_before;
+                const bool joins = listed && lane > 0 && ((listed_m >> (lane - 1)) & 1u) != 0 && ln == id_before;
                 const uint32_t joins_m = __ballot_sync(full, joins);
                 uint32_t starts = listed_m & ~joins_m;
                 while (starts != 0) {
@@ -514,20 +536,27 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                     const int len = first == 31 ? 0 : __ffs(~(joins_m >> (first + 1))) - 1;
                     const uint32_t piece_tail = __shfl_sync(full, id, first);        // accessed first: ends up deepest
                     const uint32_t piece_head = __shfl_sync(full, id, first + len);  // accessed last: ends up in front
+                    const uint32_t b = __shfl_sync(full, ln, first);        // what follows the piece, towards the cold end
+                    const uint32_t a = __shfl_sync(full, lp, first + len);  // what precedes it
+                    if (a == kHead) continue;  // in front already
                     if (lane == 0) {
-                        const uint32_t a = lprev[piece_head];
-                        if (a != kHead) {
-                            const uint32_t b = lnext[piece_tail];
-                            const uint32_t f = lnext[kHead];
-                            lnext[a] = b;
-                            lprev[b] = a;
-                            lnext[piece_tail] = f;
-                            lprev[f] = piece_tail;
-                            lnext[kHead] = piece_head;
-                            lprev[piece_head] = kHead;
-                        }
+                        lnext[a] = b;  // a is a key: the piece is not in front
+                        set_prev(b, a, kHead, me);
+                        lnext[piece_tail] = front;
+                        lprev[front] = piece_tail;  // a key: the queue holds the piece and more
+                        lprev[piece_head] = kHead;
                     }
+                    // the same five links in the lanes' copies, so that a later piece needs no load
+                    if (listed) {
+                        if (id == a) ln = b;
+                        if (id == b) lp = a;
+                        if (id == piece_tail) ln = front;
+                        if (id == front) lp = piece_tail;
+                        if (id == piece_head) lp = kHead;
+                    }
+                    front = piece_head;
                 }
+                if (lane == 0) front_of[me] = front;
                 __syncwarp();
             }
         }
@@ -546,11 +575,11 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                     ++wr;
                     if (kids == 0) {
                         flags[id] = kCached | kListed;
-                        const uint32_t f = lnext[kHead];
+                        const uint32_t f = front_of[me];
                         lnext[id] = f;
                         lprev[id] = kHead;
-                        lprev[f] = id;
-                        lnext[kHead] = id;
+                        set_prev(f, id, kHead, me);
+                        front_of[me] = id;
                     } else {
                         flags[id] = kCached;
                         atomicAdd(&n_unlisted[nd], 1u);
@@ -566,7 +595,7 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                     const uint32_t at = at_node;
                     const uint32_t last_of_at = n_last[at], kids = n_children[at];
                     above_at = n_parent[at];
-                    old_front = lnext[kHead];
+                    old_front = front_of[me];
                     if (div == 0 || last_of_at == at_id) {
                         if (at >= n_roots && kids == 0) {
                             target = at;
@@ -638,8 +667,8 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                 __syncwarp();
                 if (lane == 0) {
                     const uint32_t cnt = static_cast<uint32_t>(n - div);
-                    lprev[old_front] = p.ids[beg + div];
-                    lnext[kHead] = p.ids[beg + n - 1];
+                    set_prev(old_front, p.ids[beg + div], kHead, me);
+                    front_of[me] = p.ids[beg + n - 1];
                     // additions without a returned value do not wait for memory
                     atomicAdd(&n_blocks[target], cnt);
                     atomicAdd(&n_cached[target], cnt);
@@ -754,7 +783,6 @@ LeafLayout LayoutFor(int64_t n_keys, int32_t n_traces, int32_t n_configs, int32_
     LeafLayout l;
     const uint64_t nk = static_cast<uint64_t>(n_keys > 0 ? n_keys : 1);
     const uint64_t nc = static_cast<uint64_t>(n_configs);
-    const uint64_t links = nk + 2ull * static_cast<uint64_t>(n_instances);
     l.max_nodes = 2 * static_cast<int64_t>(n_traces) + n_instances + 1;  // the roots, and at most two new nodes per trace
     l.table_off = 256;
     l.ids_off = up(l.table_off + SlotsFor(n_keys) * sizeof(ulonglong2));
@@ -763,8 +791,8 @@ LeafLayout LayoutFor(int64_t n_keys, int32_t n_traces, int32_t n_configs, int32_
     l.flags_off = up(l.node_of_off + nk * 4 * nc);
     l.time_off = up(l.flags_off + nk * nc);
     l.lprev_off = up(l.time_off + nk * 8 * nc);
-    l.lnext_off = up(l.lprev_off + links * 4 * nc);
-    l.evicted_off = up(l.lnext_off + links * 4 * nc);
+    l.lnext_off = up(l.lprev_off + nk * 4 * nc);
+    l.evicted_off = up(l.lnext_off + nk * 4 * nc);
     l.nodes_off = up(l.evicted_off + nk * 4 * nc);
     l.total = up(l.nodes_off + static_cast<uint64_t>(l.max_nodes) * 4 * kNodeFields * nc);
     return l;
@@ -882,7 +910,7 @@ int32_t kvcm_b200_replay_leaf_lru_group(const int64_t *d_keys, const int64_t *d_
         }
         kvcm::LeafOccKernel<<<sms * 4, 256, 0, s>>>(ids, d_key_off, d_trace_instance, n_instances, n_traces, occ);
     }
-    kvcm::LeafSweepKernel<<<static_cast<unsigned>(n_configs), 32, sizeof(int64_t) * n_instances, s>>>(p);
+    kvcm::LeafSweepKernel<<<static_cast<unsigned>(n_configs), 32, sizeof(int64_t) * 2 * n_instances, s>>>(p);
     return kvcm::LaunchStatus();
 }
 

@@ -77,10 +77,11 @@ def _kept(traces: List[tr.Trace], rw_separation: bool) -> List[tr.Trace]:
 
 
 def replay_group(traces: List[tr.Trace], instance_ids: Sequence[str], device, quota_blocks: int,
-                 rw_separation: bool = False, evict_batch: int = 100, mode: int = 1) -> Dict[str, Dict[str, np.ndarray]]:
-    """Replays the traces of the instances of ONE group that share a quota ("lru" policy in every instance), in the
-    order given (all instances together, by timestamp), and returns one record per instance as replay_instance
-    does.  mode is the configuration's eviction_mode (1 group rough, 2 instance rough, 3 instance precise;
+                 rw_separation: bool = False, evict_batch: int = 100, mode: int = 1,
+                 policy: str = "lru") -> Dict[str, Dict[str, np.ndarray]]:
+    """Replays the traces of the instances of ONE group that share a quota (every instance under `policy`: "lru" or
+    "leaf_aware_lru"), in the order given (all instances together, by timestamp), and returns one record per
+    instance as replay_instance does.  mode is the configuration's eviction_mode (1 group rough, 2 instance rough, 3 instance precise;
     kv_cache_manager/optimizer/manager/eviction_manager.cc:57-239).  current_cache_blocks is the usage of the
     trace's own instance; blocks_per_instance [record, instance] is the usage of every instance of the group at
     that moment, in the order of `instance_ids` (ReadRecord::blocks_per_instance)."""
@@ -97,7 +98,8 @@ def replay_group(traces: List[tr.Trace], instance_ids: Sequence[str], device, qu
     res = RunTracesLruGroup(d_keys, d_off, torch.from_numpy(kind).to(device), torch.from_numpy(inst).to(device),
                             len(instance_ids), [int(quota_blocks)], torch.from_numpy(mask).to(device), evict_batch,
                             mode, mask_bits=torch.from_numpy(bits).to(device) if bits is not None else None,
-                            instance_records=True)
+                            instance_records=True, policy=policy,
+                            timestamps=torch.from_numpy(ts).to(device) if policy == "leaf_aware_lru" else None)
     ext, inte, wr, size = (x[0].cpu().numpy() for x in res[:4])
     every = res.instance_blocks_per_trace[0].cpu().numpy()  # [trace, instance], instances in the order of instance_ids
     internal_read = np.array([tr.masked_count(t.block_mask, len(t.keys)) if t.kind == tr.GET_LOCATION else 0
@@ -192,7 +194,8 @@ def run_trace_file(trace_path: str, trace_type: str, output_dir: str, device=Non
     """Loads a trace file, replays every instance on the GPU and writes `<instance>_hit_rates.csv` per instance
     (`<instance>_quota<q>_hit_rates.csv` per instance and quota when quota_blocks is a sequence).  Every instance is
     replayed on its own, except the instances of a group in `groups` (dicts with "instances" = the ids and "quota" =
-    the shared quota in blocks, as parse_startup_config returns them), which are replayed together against their
+    the shared quota in blocks, "policy" = the eviction policy of all of them, "lru" when absent, as
+    parse_startup_config returns them), which are replayed together against their
     shared quota under eviction `mode` (replay_group; in their CSV files CachedBlocksPerInstance lists the instances
     of the group in the group's order - the reference lists every instance of the whole configuration there, in
     the order of an unordered_map)."""
@@ -204,7 +207,8 @@ def run_trace_file(trace_path: str, trace_type: str, output_dir: str, device=Non
     os.makedirs(output_dir, exist_ok=True)
     out = {}
     for group in groups or []:
-        recs = replay_group(traces, group["instances"], device, group["quota"], rw_separation, evict_batch, mode)
+        recs = replay_group(traces, group["instances"], device, group["quota"], rw_separation, evict_batch, mode,
+                            group.get("policy", "lru"))
         for instance_id, r in recs.items():
             by_instance.pop(instance_id, None)
             if (r["kind"] != tr.WRITE_CACHE).any():
@@ -236,7 +240,7 @@ def parse_startup_config(config: Union[str, dict]) -> dict:
     by kv_cache_manager/optimizer/config/optimizer_config.cc:4-12, instance_group_config.cc:5-12,
     instance_config.cc:6-22, eviction_config.cc:5-8) reduced to what the GPU replay needs.  Raises
     NotImplementedError for what it cannot replay exactly: hierarchical eviction, and groups of several instances
-    unless all of them use "lru" (those come back under "groups")."""
+    unless all of them use "lru" or all of them use "leaf_aware_lru" (those come back under "groups")."""
     if isinstance(config, str):
         with open(config) as f:
             config = json.load(f)
@@ -251,12 +255,15 @@ def parse_startup_config(config: Union[str, dict]) -> dict:
         if group.get("hierarchical_eviction_enabled", False):
             raise NotImplementedError("group %r: hierarchical eviction is not replayed" % group.get("group_name"))
         together = len(instances) > 1 and mode != EVICTION_MODE_UNSPECIFIED
-        if together and any(i.get("eviction_policy_type", "lru") != "lru" for i in instances):
-            raise NotImplementedError("group %r: %d instances share one quota and not all of them use \"lru\""
-                                      % (group.get("group_name"), len(instances)))
+        used = sorted({i.get("eviction_policy_type", "lru") for i in instances})
+        if together and used not in (["lru"], ["leaf_aware_lru"]):
+            raise NotImplementedError("group %r: %d instances share one quota under %s; replayed are groups that use "
+                                      "\"lru\" or \"leaf_aware_lru\" throughout"
+                                      % (group.get("group_name"), len(instances), ", ".join(map(repr, used))))
         if together:
             shared.append(dict(group_name=group.get("group_name"), instances=[str(i["instance_id"]) for i in instances],
-                               quota=int(group["quota_capacity"] * float(group.get("used_percentage", 1.0)))))
+                               quota=int(group["quota_capacity"] * float(group.get("used_percentage", 1.0))),
+                               policy=used[0]))
         for inst in instances:
             policy = inst.get("eviction_policy_type", "lru")
             if policy not in ("lru", "leaf_aware_lru", "random_lru") and mode != EVICTION_MODE_UNSPECIFIED:

@@ -120,9 +120,15 @@ def test_startup_config_of_the_reference_is_understood():
     cfg["instance_groups"][0]["instances"].append({"instance_id": "b", "block_size": 16, "eviction_policy_type": "lru"})
     c = parse_startup_config(cfg)  # two "lru" instances share the quota: replayed together
     assert c["groups"] == [dict(group_name=cfg["instance_groups"][0]["group_name"],
-                                instances=["3780643326877293460", "b"], quota=9000)]
+                                instances=["3780643326877293460", "b"], quota=9000, policy="lru")]
     assert c["quota_blocks"] == {} and c["mode"] == 3
     cfg["instance_groups"][0]["instances"][1]["eviction_policy_type"] = "leaf_aware_lru"
+    with pytest.raises(NotImplementedError):  # mixed policies in one group
+        parse_startup_config(cfg)
+    cfg["instance_groups"][0]["instances"][0]["eviction_policy_type"] = "leaf_aware_lru"
+    assert parse_startup_config(cfg)["groups"][0]["policy"] == "leaf_aware_lru"  # the same policy throughout
+    cfg["instance_groups"][0]["instances"][0]["eviction_policy_type"] = "random_lru"
+    cfg["instance_groups"][0]["instances"][1]["eviction_policy_type"] = "random_lru"
     with pytest.raises(NotImplementedError):
         parse_startup_config(cfg)
     cfg["eviction_params"]["eviction_mode"] = 0  # no eviction is ever performed: any grouping replays
@@ -143,9 +149,11 @@ def test_shared_quota_groups_host_side(tmp_path, monkeypatch):
     from tair_kvcache_b200.optimizer.replay import LruGroupSweepResult
 
     def stand_in(keys, off, kind, inst, n_inst, quotas, mask, evict_batch, mode, mask_bits=None,
-                 instance_records=False):
-        r = oracle.LruGroupReplay(quotas[0], n_inst, evict_batch=evict_batch, mode=mode).run(
-            keys.numpy(), off.numpy(), kind.numpy(), inst.numpy(), mask.numpy(), instance_records=True)
+                 instance_records=False, policy="lru", timestamps=None):
+        assert (timestamps is not None) == (policy == "leaf_aware_lru")
+        r = oracle.LruGroupReplay(quotas[0], n_inst, evict_batch=evict_batch, mode=mode, policy=policy).run(
+            keys.numpy(), off.numpy(), kind.numpy(), inst.numpy(), mask.numpy(), instance_records=True,
+            timestamps=None if timestamps is None else timestamps.numpy())
         ext, inte, wr, size = [torch.from_numpy(x)[None] for x in r[:4]]
         return LruGroupSweepResult(ext, inte, wr, size, None, None, torch.from_numpy(r[5])[None])
 
@@ -176,6 +184,12 @@ def test_shared_quota_groups_host_side(tmp_path, monkeypatch):
     cfg["eviction_params"]["eviction_mode"] = 2
     recs = runner.run_startup_config(cfg, device="cpu", rw_separation=True)
     assert recs["a"]["external_hit_blocks"].tolist() == [0, 3] and np.array_equal(recs["a"]["kind"], [2, 1])
+    # the same group under "leaf_aware_lru": the policy and the traces' timestamps reach the group replay
+    for i in cfg["instance_groups"][0]["instances"]:
+        i["eviction_policy_type"] = "leaf_aware_lru"
+    cfg["eviction_params"]["eviction_mode"] = 1
+    recs = runner.run_startup_config(cfg, device="cpu", rw_separation=True)
+    assert recs["a"]["current_cache_blocks"].tolist() == [3, 2] and recs["b"]["blocks_per_instance"].tolist() == [[2, 1]] * 2
 
 
 def test_a_key_repeated_inside_a_trace_is_found_before_any_launch():
