@@ -5,7 +5,9 @@ The CUDA kernel (tair-kvcache_b200/csrc/replay_leaf_lru.cu) does not keep the re
 node, the queue as a linked list over key ids.  That this representation replays a trace exactly as the tree does
 rests on a few claims - a key is in the tree exactly when its node still has blocks; a split can hand the new
 node number to the upper part; removing an emptied leaf is zeroing its block count; accessed blocks may move to the
-front in pieces; evictions may go in groups when nothing gets re-queued.  This file restates those steps in plain
+front in pieces; evictions may go in groups when nothing gets re-queued; a node's blocks are the ids in front of
+one occurrence of its last key; blocks of one access time that are re-queued one after the other end up side by
+side, so a run of them is one search and one splice.  This file restates those steps in plain
 Python, one key at a time, and compares them with the oracle (which keeps real nodes and lists) on random traces
 with shared prefixes and tied timestamps, so the claims are checked on a box without a GPU.  The GPU tests compare
 the kernel itself with the same oracle.
@@ -23,10 +25,9 @@ def flat_replay(keys, off, types, mask_off, stamps, quota, batch, precise):
     ids_of = {}
     ids = [ids_of.setdefault(k, len(ids_of)) for k in keys]
     nk = len(ids) + 1
-    pred = [NONE] * nk  # the key before a key in its chain
-    for t in range(len(off) - 1):
-        for i in range(off[t] + 1, off[t + 1]):
-            pred[ids[i]] = ids[i - 1]
+    occ = [NONE] * nk  # a position of every key in ids (the last one, as it happens; any would do)
+    for i, k in enumerate(ids):
+        occ[k] = i
     node_of, flags, time = [NONE] * nk, [0] * nk, [0] * nk  # flags: 1 cached, 2 in the queue
     head, tail = nk, nk + 1
     before, after = [0] * (nk + 2), [0] * (nk + 2)  # towards the head / towards the tail
@@ -43,13 +44,14 @@ def flat_replay(keys, off, types, mask_off, stamps, quota, batch, precise):
         f = after[head]
         after[i], before[i], before[f], after[head] = f, head, i, i
 
-    def insert_by_time(b):  # leaf_aware_lru.cc:53-83 over common_structure.h:62-89
+    def insertion_point(bt):  # leaf_aware_lru.cc:53-83 over common_structure.h:62-89: (goes in front of, from the head?)
         h = after[head]
+        from_head = True
         if h == tail:
             spot = tail
         else:
             tl = before[tail]
-            ht, tt, bt = time[h], time[tl], time[b]
+            ht, tt = time[h], time[tl]
             from_head = True if bt >= ht else (False if bt <= tt else (ht - bt) < (bt - tt))
             if from_head:
                 cur = h
@@ -61,8 +63,17 @@ def flat_replay(keys, off, types, mask_off, stamps, quota, batch, precise):
                 while cur != head and time[cur] < bt:
                     cur = before[cur]
                 spot = after[cur]
+        return spot, from_head
+
+    def splice_run(run):  # blocks of one access time, in key order
+        spot, from_head = insertion_point(time[run[0]])
+        # searched from the head each one lands in front of the one before it, from the tail behind it
+        seq = list(reversed(run)) if from_head else list(run)
         a = before[spot]
-        after[a], before[b], after[b], before[spot] = b, a, spot, b
+        for x in seq:
+            after[a], before[x] = x, a
+            a = x
+        after[a], before[spot] = spot, a
 
     resident, out = 0, []
     for t in range(len(off) - 1):
@@ -208,14 +219,21 @@ def flat_replay(keys, off, types, mask_off, stamps, quota, batch, precise):
                             gone.append(x)
                             g += 1
                             if u != 0 and child_cached[u] == 0 and unlisted[u] != 0:
-                                chain, k = [], last[u]
-                                for _ in range(blocks[u]):
-                                    chain.append(k)
-                                    k = pred[k]
-                                for k in reversed(chain):
-                                    if flags[k] & 3 == 1:
-                                        insert_by_time(k)
+                                first = occ[last[u]] - blocks[u] + 1
+                                chain = ids[first:first + blocks[u]]
+                                assert first >= 0 and all(node_of[k] == u for k in chain)
+                                for g0 in range(0, len(chain), GROUP):  # a run ends with the keys handled together
+                                    run = []
+                                    for k in chain[g0:g0 + GROUP]:
+                                        if flags[k] & 3 != 1:
+                                            continue
+                                        if run and time[run[0]] != time[k]:
+                                            splice_run(run)
+                                            run = []
+                                        run.append(k)
                                         flags[k] = 3
+                                    if run:
+                                        splice_run(run)
                                 unlisted[u] = 0
                         got += g
                         if g < want:
