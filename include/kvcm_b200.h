@@ -593,7 +593,9 @@ KVCM_API int32_t kvcm_b200_replay(const int64_t *d_keys, const int64_t *d_key_of
  * d_workspace: kvcm_b200_replay_lru_workspace_bytes(n_keys_total, n_configs) bytes (-1: too large:
  * n_keys_total < 2^32 - 1, n_configs <= 65535), 256-byte aligned, contents irrelevant before and after.
  * Not covered here: leaf_aware_lru (kvcm_b200_replay_leaf_lru below), several instances sharing one group
- * quota (kvcm_b200_replay_lru_group below), random_lru, hierarchical tiers.
+ * quota (kvcm_b200_replay_lru_group below), random_lru (kvcm_b200_replay_random_lru below).  A group with
+ * hierarchical_eviction_enabled differs for a replay only in the capacity its quota derives from (the first
+ * storage tier's, eviction_manager.cc:247-258): the caller passes that quota.
  * ---------------------------------------------------------------------------------------- */
 KVCM_API int64_t kvcm_b200_replay_lru_workspace_bytes(int64_t n_keys_total, int32_t n_configs);
 KVCM_API int32_t kvcm_b200_replay_lru(const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type,

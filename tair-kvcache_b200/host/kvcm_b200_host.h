@@ -441,12 +441,14 @@ public:
     // Several instances that share one group quota (OptEvictionManager::EvictByGroupRough / EvictByInstanceRough /
     // EvictByInstancePrecise, kv_cache_manager/optimizer/manager/eviction_manager.cc:86-239): the traces of all
     // instances of the group in replay order, instance_of[t] in [0, n_instances) for each, eviction_mode as in the
-    // configuration (1 group rough, 2 instance rough, 3 instance precise), the "lru" policy in every instance.
+    // configuration (1 group rough, 2 instance rough, 3 instance precise), the "lru" policy in every instance, or
+    // "leaf_aware_lru" in every instance with leaf_aware = true (the traces' order stands in for their timestamps).
     // (*records)[t].current_cache_blocks is the usage of trace t's own instance; *instance_blocks (optional) receives
     // the usage of every instance at the end.
     int32_t RunTracesLruGroup(const std::vector<ReplayTrace> &traces, const std::vector<int32_t> &instance_of,
                               int32_t n_instances, int64_t quota_blocks, int32_t evict_batch, int32_t eviction_mode,
-                              std::vector<ReplayRecord> *records, std::vector<int64_t> *instance_blocks = nullptr) {
+                              std::vector<ReplayRecord> *records, std::vector<int64_t> *instance_blocks = nullptr,
+                              bool leaf_aware = false) {
         const int32_t n = static_cast<int32_t>(traces.size());
         records->assign(n, ReplayRecord{0, 0, 0, 0});
         if (instance_blocks != nullptr) instance_blocks->assign(n_instances > 0 ? n_instances : 0, 0);
@@ -455,7 +457,9 @@ public:
         int64_t n_keys = 0;
         int32_t rc = Pack(traces, &n_keys);
         if (rc != KVCM_OK) return rc;
-        const int64_t ws_bytes = kvcm_b200_replay_lru_group_workspace_bytes(n_keys, 1, n_instances);
+        const int64_t ws_bytes = leaf_aware
+                                     ? kvcm_b200_replay_leaf_lru_group_workspace_bytes(n_keys, n, 1, n_instances)
+                                     : kvcm_b200_replay_lru_group_workspace_bytes(n_keys, 1, n_instances);
         if (ws_bytes < 0) return KVCM_EC_OUT_OF_LIMIT;
         if (!Outputs(n, 1) || !quota_.Reserve(sizeof(int64_t)) || !inst_.Reserve(sizeof(int32_t) * n) ||
             !inst_blocks_.Reserve(sizeof(int64_t) * n_instances) ||
@@ -467,11 +471,20 @@ public:
         if (!quota_.ToDevice(sizeof(int64_t), stream_) || !inst_.ToDevice(sizeof(int32_t) * n, stream_)) {
             return KVCM_ER_CUDAMEMCPY_ERROR;
         }
-        rc = kvcm_b200_replay_lru_group(keys_.dev<int64_t>(), off_.dev<int64_t>(), kind_.dev<uint8_t>(),
-                                        mask_.dev<int64_t>(), nullptr, inst_.dev<int32_t>(), n_instances, n, n_keys,
-                                        quota_.dev<int64_t>(), 1, evict_batch, eviction_mode, workspace_.dev<void>(),
-                                        ws_bytes, ext_.dev<int32_t>(), int_.dev<int32_t>(), wr_.dev<int32_t>(),
-                                        size_.dev<int64_t>(), nullptr, inst_blocks_.dev<int64_t>(), nullptr, stream_);
+        if (leaf_aware) {
+            rc = kvcm_b200_replay_leaf_lru_group(
+                keys_.dev<int64_t>(), off_.dev<int64_t>(), kind_.dev<uint8_t>(), mask_.dev<int64_t>(), nullptr, nullptr,
+                inst_.dev<int32_t>(), n_instances, n, n_keys, quota_.dev<int64_t>(), 1, evict_batch, eviction_mode,
+                workspace_.dev<void>(), ws_bytes, ext_.dev<int32_t>(), int_.dev<int32_t>(), wr_.dev<int32_t>(),
+                size_.dev<int64_t>(), nullptr, inst_blocks_.dev<int64_t>(), nullptr, nullptr, stream_);
+        } else {
+            rc = kvcm_b200_replay_lru_group(keys_.dev<int64_t>(), off_.dev<int64_t>(), kind_.dev<uint8_t>(),
+                                            mask_.dev<int64_t>(), nullptr, inst_.dev<int32_t>(), n_instances, n,
+                                            n_keys, quota_.dev<int64_t>(), 1, evict_batch, eviction_mode,
+                                            workspace_.dev<void>(), ws_bytes, ext_.dev<int32_t>(), int_.dev<int32_t>(),
+                                            wr_.dev<int32_t>(), size_.dev<int64_t>(), nullptr,
+                                            inst_blocks_.dev<int64_t>(), nullptr, stream_);
+        }
         if (rc != KVCM_OK) return rc;
         if (!inst_blocks_.ToHost(sizeof(int64_t) * n_instances, stream_)) return KVCM_ER_CUDAMEMCPY_ERROR;
         rc = Fetch(static_cast<size_t>(n));

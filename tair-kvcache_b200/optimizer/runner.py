@@ -239,8 +239,13 @@ def parse_startup_config(config: Union[str, dict]) -> dict:
     """The Optimizer's startup configuration (kv_cache_manager/optimizer/optimizer_startup_config_load.json, read
     by kv_cache_manager/optimizer/config/optimizer_config.cc:4-12, instance_group_config.cc:5-12,
     instance_config.cc:6-22, eviction_config.cc:5-8) reduced to what the GPU replay needs.  Raises
-    NotImplementedError for what it cannot replay exactly: hierarchical eviction, and groups of several instances
-    unless all of them use "lru" or all of them use "leaf_aware_lru" (those come back under "groups")."""
+    NotImplementedError for what it cannot replay exactly: groups of several instances unless all of them use "lru"
+    or all of them use "leaf_aware_lru" (those come back under "groups").
+    hierarchical_eviction_enabled: the reference creates an eviction policy for the FIRST storage tier only (later
+    tiers never evict, kv_cache_manager/optimizer/manager/eviction_manager.cc:26-39), every block gets its location
+    on that tier alone (kv_cache_manager/optimizer/index/radix_tree_index.cc:327-353), so erasing that location on
+    eviction empties the block as in the shared case; what changes is the capacity the usage is held against:
+    storages[0].capacity instead of quota_capacity (eviction_manager.cc:247-258).  That is what is replayed."""
     if isinstance(config, str):
         with open(config) as f:
             config = json.load(f)
@@ -252,8 +257,12 @@ def parse_startup_config(config: Union[str, dict]) -> dict:
     quotas, block_sizes, policies, sample_rates, shared = {}, {}, {}, {}, []
     for group in config.get("instance_groups", []):
         instances = group.get("instances", [])
+        capacity = group.get("quota_capacity", 0)
         if group.get("hierarchical_eviction_enabled", False):
-            raise NotImplementedError("group %r: hierarchical eviction is not replayed" % group.get("group_name"))
+            if not group.get("storages"):
+                raise ValueError("group %r: hierarchical eviction without a storage tier" % group.get("group_name"))
+            capacity = group["storages"][0].get("capacity", 0)
+        group_quota = int(capacity * float(group.get("used_percentage", 1.0)))
         together = len(instances) > 1 and mode != EVICTION_MODE_UNSPECIFIED
         used = sorted({i.get("eviction_policy_type", "lru") for i in instances})
         if together and used not in (["lru"], ["leaf_aware_lru"]):
@@ -262,8 +271,7 @@ def parse_startup_config(config: Union[str, dict]) -> dict:
                                       % (group.get("group_name"), len(instances), ", ".join(map(repr, used))))
         if together:
             shared.append(dict(group_name=group.get("group_name"), instances=[str(i["instance_id"]) for i in instances],
-                               quota=int(group["quota_capacity"] * float(group.get("used_percentage", 1.0))),
-                               policy=used[0]))
+                               quota=group_quota, policy=used[0]))
         for inst in instances:
             policy = inst.get("eviction_policy_type", "lru")
             if policy not in ("lru", "leaf_aware_lru", "random_lru") and mode != EVICTION_MODE_UNSPECIFIED:
@@ -278,7 +286,7 @@ def parse_startup_config(config: Union[str, dict]) -> dict:
             # eviction_manager.cc:249-266: quota = size_t(quota_capacity * used_percentage); an unspecified mode
             # never evicts (:60-63)
             if mode != EVICTION_MODE_UNSPECIFIED and not together:
-                quotas[iid] = int(group["quota_capacity"] * float(group.get("used_percentage", 1.0)))
+                quotas[iid] = group_quota
     return dict(trace_file_path=config.get("trace_file_path"), trace_type=config.get("trace_type"),
                 output_result_path=config.get("output_result_path"), quota_blocks=quotas, block_sizes=block_sizes,
                 evict_batch=int(ev.get("eviction_batch_size_per_instance", 100)),

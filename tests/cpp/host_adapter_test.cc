@@ -305,6 +305,22 @@ static void TestReplay() {
     EXPECT_EQ(rec[2].external_hit_blocks, 3);
     EXPECT_EQ(usage[0], 3);
     EXPECT_EQ(replayer.RunTracesLruGroup(two, {0, 1}, 2, 4, 1, 2, &rec, &usage), KVCM_EC_BADARGS);
+    // The same two instances under "leaf_aware_lru", quota 5, batches of 1, group rough (worked by hand from
+    // kv_cache_manager/optimizer/eviction_policy/leaf_aware_lru.cc:85-160 over eviction_manager.cc:86-146): a's split
+    // node {1 2} stays while its children {3} and {9} go, is queued again when the last of them has gone, and so
+    // a still hits 1 2 at the end; b loses the head of its only chain at once.
+    const std::vector<ReplayTrace> leafy = {
+        {TraceKind::WriteCache, {1, 2, 3}}, {TraceKind::WriteCache, {1, 2, 9}}, {TraceKind::WriteCache, {1, 2}},
+        {TraceKind::GetLocation, {1, 2, 3}}, {TraceKind::GetLocation, {1, 2}}, {TraceKind::WriteCache, {5}},
+        {TraceKind::WriteCache, {7, 8}}, {TraceKind::GetLocation, {1, 2, 9}}, {TraceKind::WriteCache, {6}}};
+    EXPECT_EQ(replayer.RunTracesLruGroup(leafy, {0, 0, 1, 0, 1, 0, 1, 0, 0}, 2, 5, 1, 1, &rec, &usage, /*leaf_aware=*/true),
+              KVCM_OK);
+    EXPECT_EQ(rec[3].external_hit_blocks, 2);
+    EXPECT_EQ(rec[4].external_hit_blocks, 0);
+    EXPECT_EQ(rec[7].external_hit_blocks, 2);
+    EXPECT_EQ(rec[6].current_cache_blocks, 2);
+    EXPECT_EQ(usage[0], 3);
+    EXPECT_EQ(usage[1], 1);
 }
 
 int main() {

@@ -107,6 +107,11 @@ def test_startup_config_of_the_reference_is_understood():
     cfg["eviction_params"]["eviction_mode"] = 3
     c = parse_startup_config(cfg)
     assert c["quota_blocks"]["3780643326877293460"] == 9000 and c["precise"] is True
+    # hierarchical eviction: the first tier's capacity takes the place of quota_capacity
+    # (kv_cache_manager/optimizer/manager/eviction_manager.cc:247-258); nothing else changes for a replay
+    cfg["instance_groups"][0]["hierarchical_eviction_enabled"] = True
+    assert parse_startup_config(cfg)["quota_blocks"]["3780643326877293460"] == 75000
+    cfg["instance_groups"][0]["hierarchical_eviction_enabled"] = False
     # what the GPU replay does not reproduce is refused, not approximated
     cfg["instance_groups"][0]["instances"][0]["eviction_policy_type"] = "leaf_aware_lru"
     assert parse_startup_config(cfg)["policies"] == {"3780643326877293460": "leaf_aware_lru"}
