@@ -680,6 +680,25 @@ KVCM_API int32_t kvcm_b200_replay_random_lru(const int64_t *d_keys, const int64_
                                              int32_t *d_ext_hit, int32_t *d_int_hit, int32_t *d_written,
                                              int64_t *d_cache_blocks, int64_t *d_totals, uint32_t *d_status,
                                              kvcm_stream_t stream);
+/* The random_lru sweep for an instance group whose instances share one quota: every instance has its own block
+ * vector, its own generator (each policy object starts from the reference's seed) and its own sampling size;
+ * h_sample_rate (HOST memory, n_instances doubles, NULL = the default rate everywhere) is each instance's
+ * eviction_policy_params.sample_rate.  d_trace_instance, n_instances, eviction_mode, d_cache_blocks, d_totals,
+ * d_instance_blocks and d_instance_blocks_per_trace exactly as in kvcm_b200_replay_lru_group_records, everything else
+ * as in kvcm_b200_replay_random_lru, which is this call with one instance and eviction_mode 3 (precise) or 2.  A
+ * group-rough round draws a fresh sample in every instance in the configuration's order
+ * (kv_cache_manager/optimizer/manager/eviction_manager.cc:86-146), so the generators advance as the reference's do.
+ * A trace whose instance is out of range is replayed as an empty trace and counted in d_status[0]. */
+KVCM_API int64_t kvcm_b200_replay_random_lru_group_workspace_bytes(int64_t n_keys_total, int32_t n_configs,
+                                                                   int32_t n_instances);
+KVCM_API int32_t kvcm_b200_replay_random_lru_group(
+    const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type, const int64_t *d_mask_off,
+    const uint8_t *d_mask_bits, const int64_t *d_timestamps, const int32_t *d_trace_instance,
+    const double *h_sample_rate, int32_t n_instances, int32_t n_traces, int64_t n_keys_total,
+    const int64_t *d_quota_blocks, int32_t n_configs, int32_t evict_batch, int32_t eviction_mode, void *d_workspace,
+    int64_t workspace_bytes, int32_t *d_ext_hit, int32_t *d_int_hit, int32_t *d_written, int64_t *d_cache_blocks,
+    int64_t *d_totals, int64_t *d_instance_blocks, int64_t *d_instance_blocks_per_trace, uint32_t *d_status,
+    kvcm_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
  * (2c'') The same sweep under the "leaf_aware_lru" eviction policy
@@ -724,6 +743,23 @@ KVCM_API int32_t kvcm_b200_replay_leaf_lru(const int64_t *d_keys, const int64_t 
  * and eviction_mode 3 (precise) or 2. */
 KVCM_API int64_t kvcm_b200_replay_leaf_lru_group_workspace_bytes(int64_t n_keys_total, int32_t n_traces,
                                                                  int32_t n_configs, int32_t n_instances);
+/* The same replay for a group whose instances do not all use one policy: h_instance_policy (HOST memory,
+ * n_instances bytes, NULL = all leaf-aware) names every instance's eviction_policy_type, KVCM_POLICY_LEAF_AWARE_LRU or
+ * KVCM_POLICY_LRU (EvictionPolicyFactory::CreatePolicy per instance, kv_cache_manager/optimizer/eviction_policy/
+ * policy_factory.cc:8-47).  An "lru" instance keeps its tree and its queue in the same form; all its cached blocks
+ * stay queued whatever their node's children, and a round takes its coldest blocks (lru.cc:28-49).  Workspace as for
+ * kvcm_b200_replay_leaf_lru_group, whose arguments the others are.  A group of "lru" instances only is cheaper
+ * through kvcm_b200_replay_lru_group, which needs no tree. */
+#define KVCM_POLICY_LEAF_AWARE_LRU 0
+#define KVCM_POLICY_LRU 1
+KVCM_API int32_t kvcm_b200_replay_tree_group(
+    const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type, const int64_t *d_mask_off,
+    const uint8_t *d_mask_bits, const int64_t *d_timestamps, const int32_t *d_trace_instance,
+    const uint8_t *h_instance_policy, int32_t n_instances, int32_t n_traces, int64_t n_keys_total,
+    const int64_t *d_quota_blocks, int32_t n_configs, int32_t evict_batch, int32_t eviction_mode, void *d_workspace,
+    int64_t workspace_bytes, int32_t *d_ext_hit, int32_t *d_int_hit, int32_t *d_written, int64_t *d_cache_blocks,
+    int64_t *d_totals, int64_t *d_instance_blocks, int64_t *d_instance_blocks_per_trace, uint32_t *d_status,
+    kvcm_stream_t stream);
 KVCM_API int32_t kvcm_b200_replay_leaf_lru_group(
     const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type, const int64_t *d_mask_off,
     const uint8_t *d_mask_bits, const int64_t *d_timestamps, const int32_t *d_trace_instance, int32_t n_instances,

@@ -1039,6 +1039,21 @@ void *kvcm_oracle_lru_group_create(int64_t quota_blocks, int32_t evict_batch, in
     return g;
 }
 void kvcm_oracle_lru_group_destroy(void *h) { delete static_cast<OracleLruGroup *>(h); }
+// The eviction_policy_type of one instance of the group (EvictionPolicyFactory::CreatePolicy is called per instance,
+// kv_cache_manager/optimizer/manager/eviction_manager.cc:22-55): 0 = "lru", 1 = "leaf_aware_lru".  Before any trace.
+void kvcm_oracle_lru_group_set_policy(void *h, int32_t instance, int32_t policy) {
+    static_cast<OracleLruGroup *>(h)->inst[static_cast<size_t>(instance)]->leaf_aware = policy == 1;
+}
+// "random_lru" for one instance of the group, with that instance's sample_rate (RandomLruEvictionPolicy's
+// constructor, random_lru.cc:5-14: a rate <= 0 means 0.1, sampling_size = size_t(batch / rate)).  Before any trace.
+void kvcm_oracle_lru_group_set_random(void *h, int32_t instance, double sample_rate) {
+    auto *g = static_cast<OracleLruGroup *>(h);
+    OracleLruReplay *st = g->inst[static_cast<size_t>(instance)].get();
+    st->leaf_aware = false;
+    st->random = true;
+    if (sample_rate <= 0.0) sample_rate = 0.1;
+    st->sampling_size = static_cast<size_t>(g->batch / sample_rate);
+}
 
 // trace_inst[t]: the instance (0 .. n_instances-1) trace t belongs to; traces in replay order over all instances.
 // cache_blocks[t] is the usage of the trace's own instance after the trace (GetCurrentInstanceUsage,

@@ -503,12 +503,24 @@ class LruGroupReplay:
     after every write.  mode: 1 = EVICTION_MODE_GROUP_ROUGH (rounds of evict_batch blocks from every instance),
     2 = INSTANCE_ROUGH and 3 = INSTANCE_PRECISE (from the writing instance only)."""
 
-    def __init__(self, quota_blocks, n_instances, evict_batch=100, mode=1, policy="lru"):
+    def __init__(self, quota_blocks, n_instances, evict_batch=100, mode=1, policy="lru", sample_rate=0.0):
+        """policy: one name for every instance, or a sequence with one name per instance ("lru", "leaf_aware_lru",
+        "random_lru"); sample_rate: that of the "random_lru" instances, one number or one per instance."""
         lib().kvcm_oracle_lru_group_create.restype = ctypes.c_void_p
         self.n_instances = int(n_instances)
+        each = [policy] * self.n_instances if isinstance(policy, str) else list(policy)
+        rates = [sample_rate] * self.n_instances if np.isscalar(sample_rate) else list(sample_rate)
+        assert len(each) == self.n_instances == len(rates)
+        assert all(e in ("lru", "leaf_aware_lru", "random_lru") for e in each)
         self._h = ctypes.c_void_p(lib().kvcm_oracle_lru_group_create(
             ctypes.c_int64(int(quota_blocks)), ctypes.c_int32(int(evict_batch)), ctypes.c_int32(int(mode)),
-            ctypes.c_int32(self.n_instances), ctypes.c_int32(LruReplay.POLICIES[policy])))
+            ctypes.c_int32(self.n_instances), ctypes.c_int32(0)))
+        for j, e in enumerate(each):
+            if e == "random_lru":
+                lib().kvcm_oracle_lru_group_set_random(self._h, ctypes.c_int32(j), ctypes.c_double(float(rates[j])))
+            else:
+                lib().kvcm_oracle_lru_group_set_policy(self._h, ctypes.c_int32(j),
+                                                       ctypes.c_int32(LruReplay.POLICIES[e]))
 
     def __del__(self):
         if getattr(self, "_h", None):

@@ -74,6 +74,9 @@ struct LeafSweep {
     int32_t evict_batch;
     int32_t n_instances;
     int32_t mode;  // 1 group rough, 2 instance rough, 3 instance precise
+    // bit j set: instance j runs the plain "lru" policy (kv_cache_manager/optimizer/eviction_policy/lru.cc:6-49) over
+    // the same tree and queue: every cached block is queued whatever its node's children, the cold end goes first
+    uint64_t lru_instances;
 };
 
 __global__ void LeafInitKernel(IdTable t, uint32_t *node_of, uint8_t *flags, uint64_t n_state) {
@@ -149,6 +152,7 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
     const uint64_t walk_cap = static_cast<uint64_t>(nk) + 2;
     // the queue of instance j lies between the sentinels head_of(j) (hot end) and head_of(j) + 1 (cold end)
     auto head_of = [&](int32_t j) { return static_cast<uint32_t>(nk) + 2u * static_cast<uint32_t>(j); };
+    auto plain_lru = [&](int32_t j) { return ((p.lru_instances >> j) & 1ull) != 0; };
     // x is a key or a sentinel of instance j's queue (hd = its hot-end sentinel)
     auto get_next = [&](uint32_t x, uint32_t hd, int32_t j) { return x == hd ? front_of[j] : lnext[x]; };
     auto get_prev = [&](uint32_t x, uint32_t hd, int32_t j) { return x == hd + 1 ? cold_of[j] : lprev[x]; };
@@ -291,6 +295,7 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
     // handled parent has nothing left outside the queue.
     auto evict_from = [&](int32_t j, int64_t count) -> int64_t {
         const uint32_t hd = head_of(j), tl = hd + 1;
+        const bool lru = plain_lru(j);  // nothing ever leaves this queue but by eviction, nothing is re-queued
         int64_t got = 0;
         while (got < count) {
             const uint32_t want = static_cast<uint32_t>(count - got < 32 ? count - got : 32);
@@ -334,7 +339,7 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
             const uint32_t same_up = __match_any_sync(full, mine ? up : kNone - lane);
             const uint32_t same_nd = __match_any_sync(full, mine ? nd : kNone - lane);
             bool plain = true;
-            if (mine) {
+            if (mine && !lru) {
                 const uint32_t under = static_cast<uint32_t>(__popc(same_up));
                 plain = n_childc[nd] == 0 && (up < n_roots || n_unlisted[up] == 0 || n_childc[up] > under);
             }
@@ -378,7 +383,7 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                         const uint32_t node_b = node_of[b];
                         set_next(a, tl, hd, j);
                         cold_of[j] = a;
-                        if (n_childc[node_b] != 0) {  // its node has cached children by now: out of the queue
+                        if (!lru && n_childc[node_b] != 0) {  // its node has cached children by now: out of the queue
                             flags[b] = kCached;
                             n_unlisted[node_b] += 1;
                             continue;
@@ -389,7 +394,7 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                         n_childc[up_b] -= 1;
                         evicted[n_ev++] = node_b;
                         ++g;
-                        if (up_b >= n_roots && n_childc[up_b] == 0 && n_unlisted[up_b] != 0) {
+                        if (!lru && up_b >= n_roots && n_childc[up_b] == 0 && n_unlisted[up_b] != 0) {
                             turned = up_b;
                             break;
                         }
@@ -573,7 +578,7 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                     atomicAdd(&n_cached[nd], 1u);
                     atomicAdd(&n_childc[above], 1u);
                     ++wr;
-                    if (kids == 0) {
+                    if (kids == 0 || plain_lru(me)) {
                         flags[id] = kCached | kListed;
                         const uint32_t f = front_of[me];
                         lnext[id] = f;
@@ -827,6 +832,22 @@ int32_t kvcm_b200_replay_leaf_lru_group(const int64_t *d_keys, const int64_t *d_
                                         int64_t *d_cache_blocks, int64_t *d_totals, int64_t *d_instance_blocks,
                                         int64_t *d_instance_blocks_per_trace, uint32_t *d_status,
                                         kvcm_stream_t stream) {
+    return kvcm_b200_replay_tree_group(d_keys, d_key_off, d_trace_type, d_mask_off, d_mask_bits, d_timestamps,
+                                       d_trace_instance, nullptr, n_instances, n_traces, n_keys_total, d_quota_blocks,
+                                       n_configs, evict_batch, eviction_mode, d_workspace, workspace_bytes, d_ext_hit,
+                                       d_int_hit, d_written, d_cache_blocks, d_totals, d_instance_blocks,
+                                       d_instance_blocks_per_trace, d_status, stream);
+}
+
+int32_t kvcm_b200_replay_tree_group(const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type,
+                                    const int64_t *d_mask_off, const uint8_t *d_mask_bits, const int64_t *d_timestamps,
+                                    const int32_t *d_trace_instance, const uint8_t *h_instance_policy,
+                                    int32_t n_instances, int32_t n_traces, int64_t n_keys_total,
+                                    const int64_t *d_quota_blocks, int32_t n_configs, int32_t evict_batch,
+                                    int32_t eviction_mode, void *d_workspace, int64_t workspace_bytes,
+                                    int32_t *d_ext_hit, int32_t *d_int_hit, int32_t *d_written, int64_t *d_cache_blocks,
+                                    int64_t *d_totals, int64_t *d_instance_blocks,
+                                    int64_t *d_instance_blocks_per_trace, uint32_t *d_status, kvcm_stream_t stream) {
     if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
     if (n_traces < 0 || n_keys_total < 0 || n_configs <= 0 || evict_batch <= 0 || n_instances <= 0 ||
         eviction_mode < 1 || eviction_mode > 3) {
@@ -834,6 +855,11 @@ int32_t kvcm_b200_replay_leaf_lru_group(const int64_t *d_keys, const int64_t *d_
     }
     const int64_t need = kvcm_b200_replay_leaf_lru_group_workspace_bytes(n_keys_total, n_traces, n_configs, n_instances);
     if (need < 0) return KVCM_EC_OUT_OF_LIMIT;
+    uint64_t lru_instances = 0;
+    for (int32_t j = 0; h_instance_policy != nullptr && j < n_instances; ++j) {
+        if (h_instance_policy[j] > KVCM_POLICY_LRU) return KVCM_EC_BADARGS;
+        if (h_instance_policy[j] == KVCM_POLICY_LRU) lru_instances |= 1ull << j;
+    }
     if (n_traces == 0) return KVCM_OK;
     const int per_trace = (d_ext_hit != nullptr) + (d_int_hit != nullptr) + (d_written != nullptr) +
                           (d_cache_blocks != nullptr);
@@ -888,6 +914,7 @@ int32_t kvcm_b200_replay_leaf_lru_group(const int64_t *d_keys, const int64_t *d_
     p.evict_batch = evict_batch;
     p.n_instances = n_instances;
     p.mode = eviction_mode;
+    p.lru_instances = lru_instances;
     kvcm::LeafInitKernel<<<sms * 8, 256, 0, s>>>(t, p.node_of, p.flags, nk * static_cast<uint64_t>(n_configs));
     if (d_trace_instance != nullptr) {
         kvcm::LeafCheckInstancesKernel<<<sms, 256, 0, s>>>(d_trace_instance, n_traces, n_instances, d_status);

@@ -223,32 +223,6 @@ struct LruGroup {
     int32_t mode;               // 1 group rough, 2 instance rough, 3 instance precise
 };
 
-// Key occurrences per instance, then their running sum: an instance appends at most one queue entry per occurrence.
-__global__ void __launch_bounds__(1024)
-    LruGroupExtentKernel(const int64_t *__restrict__ key_off, const int32_t *__restrict__ trace_inst, int32_t n_traces,
-                         int32_t n_instances, int64_t *queue_base, uint32_t *status) {
-    extern __shared__ unsigned long long count[];
-    for (int32_t j = threadIdx.x; j < n_instances; j += blockDim.x) count[j] = 0ull;
-    __syncthreads();
-    for (int32_t t = threadIdx.x; t < n_traces; t += blockDim.x) {
-        const int32_t j = trace_inst[t];
-        if (j < 0 || j >= n_instances) {
-            if (status != nullptr) atomicAdd(&status[0], 1u);
-            continue;
-        }
-        atomicAdd(&count[j], static_cast<unsigned long long>(key_off[t + 1] - key_off[t]));
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int64_t at = 0;
-        for (int32_t j = 0; j < n_instances; ++j) {
-            queue_base[j] = at;
-            at += static_cast<int64_t>(count[j]);
-        }
-        queue_base[n_instances] = at;
-    }
-}
-
 __global__ void __launch_bounds__(32) LruGroupSweepKernel(const LruSweep p, const LruGroup g) {
     extern __shared__ int64_t per_inst[];
     const int32_t K = g.n_instances;

@@ -4,8 +4,10 @@
 // RadixTreeIndex (kv_cache_manager/optimizer/index/radix_tree_index.cc:19-392) with RandomLruEvictionPolicy
 // (kv_cache_manager/optimizer/eviction_policy/random_lru.cc:5-131, random_lru.h:13-47) and the quota check after
 // every write (OptIndexerManager::CheckAndEvict, kv_cache_manager/optimizer/manager/indexer_manager.cc:55-90;
-// OptEvictionManager::EvictByInstanceRough / EvictByInstancePrecise, manager/eviction_manager.cc:148-239), one
-// instance per group.
+// OptEvictionManager::EvictByGroupRough / EvictByInstanceRough / EvictByInstancePrecise,
+// manager/eviction_manager.cc:86-239), for one instance or for a group of instances that share the quota: every
+// instance has its own block vector (a region of blk / ts), its own generator and its own sampling size; ids are
+// unique over (instance, key).
 //
 // One warp replays one quota point, as in the "lru" sweep, and the tree collapses to per-key state for the same
 // reasons (keys are prefix-unique; a trace touches its leading cached blocks, then writes its missing ones).  The
@@ -64,8 +66,13 @@ struct RandomSweep {
     int32_t n_traces;
     int32_t n_configs;
     int32_t evict_batch;
-    int32_t precise;
-    uint32_t sampling_size;
+    const int32_t *trace_inst;   // optional, per trace, 0 .. n_instances-1; instance 0 when null
+    const int64_t *region_base;  // [n_instances + 1]: where each instance's block vector starts; null = one instance at 0
+    int64_t *inst_blocks;        // optional, [n_configs][n_instances]: usage per instance at the end
+    int64_t *inst_blocks_trace;  // optional, [n_configs][n_traces][n_instances]: usage of every instance after each trace
+    int32_t n_instances;
+    int32_t mode;  // 1 group rough, 2 instance rough, 3 instance precise
+    uint32_t sampling_size[KVCM_B200_REPLAY_GROUP_MAX_INSTANCES];  // per instance
 };
 
 // The sample: index into the block vector and that block's time, moved together.
@@ -149,25 +156,127 @@ __global__ void __launch_bounds__(32) RandomLruSweepKernel(const RandomSweep p) 
     __shared__ uint32_t v_id[kMaxBatch], v_at[kMaxBatch];      // the round's victims: block id, current index
     __shared__ uint32_t tail_blk[kMaxBatch];                   // blk / ts of the last entries, [j] = index r0 - 1 - j
     __shared__ int64_t tail_ts[kMaxBatch];
+    extern __shared__ int64_t per_inst[];
+    const int32_t K = p.n_instances;
+    int64_t *size_of = per_inst;      // [K] cached blocks of the instance = the length of its block vector
+    int64_t *base_of = per_inst + K;  // [K] where its block vector starts in blk / ts
+    uint64_t *rng_of = reinterpret_cast<uint64_t *>(per_inst + 2 * K);  // [K] the state of its generator
     const int32_t cfg = blockIdx.x;
     const uint32_t lane = LaneId();
     const uint32_t lt = (1u << lane) - 1u;
     uint32_t *pos = p.pos + static_cast<int64_t>(cfg) * p.n_keys;
-    uint32_t *blk = p.blk + static_cast<int64_t>(cfg) * p.n_keys;
-    int64_t *ts = p.ts + static_cast<int64_t>(cfg) * p.n_keys;
+    uint32_t *blk_all = p.blk + static_cast<int64_t>(cfg) * p.n_keys;
+    int64_t *ts_all = p.ts + static_cast<int64_t>(cfg) * p.n_keys;
     const int64_t quota = p.quota[cfg];
     const int64_t out0 = static_cast<int64_t>(cfg) * p.n_traces;
     Sample sample{s_idx, s_t};
-    uint64_t rng = 0x12345678ABCDEF01ull;  // random_lru.h:20; every configuration is a run of its own
-    int64_t resident = 0;
+    int64_t resident = 0;  // of the whole group
     int64_t sum_ext = 0, sum_int = 0, sum_wr = 0;
+    for (int32_t j = lane; j < K; j += 32) {
+        size_of[j] = 0;
+        base_of[j] = p.region_base != nullptr ? p.region_base[j] : 0;
+        rng_of[j] = 0x12345678ABCDEF01ull;  // random_lru.h:20; every policy object starts from the same seed
+    }
+    __syncwarp();
+
+    // RandomLruEvictionPolicy::EvictBlocks(count) of instance j (random_lru.cc:38-103); all lanes, returns how many
+    // blocks went.
+    auto evict_round = [&](int32_t j, int64_t count) -> uint32_t {
+        const int64_t held = size_of[j];
+        if (held == 0) return 0u;
+        uint32_t *blk = blk_all + base_of[j];
+        int64_t *ts = ts_all + base_of[j];
+        const uint32_t n_blocks = static_cast<uint32_t>(held);
+        const uint32_t want = count < held ? static_cast<uint32_t>(count) : n_blocks;  // total_to_evict
+        const uint32_t n_sample = p.sampling_size[j] < n_blocks ? p.sampling_size[j] : n_blocks;
+        const uint32_t k = want < n_sample ? want : n_sample;
+        // the draws, in sequence (lane 0), then their modulo and the sampled blocks' times (all lanes)
+        if (lane == 0) {
+            uint64_t x = rng_of[j];
+            uint64_t *raw = reinterpret_cast<uint64_t *>(s_t);
+            for (uint32_t i = 0; i < n_sample; ++i) {
+                x ^= x << 13;
+                x ^= x >> 7;
+                x ^= x << 17;
+                raw[i] = x;
+            }
+            rng_of[j] = x;
+        }
+        __syncwarp();
+        for (uint32_t i = lane; i < n_sample; i += 32) {
+            const uint32_t at = static_cast<uint32_t>(reinterpret_cast<uint64_t *>(s_t)[i] % n_blocks);
+            s_idx[i] = at;
+            s_t[i] = ts[at];
+        }
+        __syncwarp();
+        if (lane == 0) PartialSortByTime(sample, k, n_sample);
+        __syncwarp();
+        // the victims as blocks (resolved before the first removal, as the reference resolves them), and the tail
+        // of the vector, which the removals read
+        const uint32_t n_tail = k < n_blocks ? k : n_blocks;
+        for (uint32_t i = lane; i < k; i += 32) {
+            v_at[i] = s_idx[i];
+            v_id[i] = blk[s_idx[i]];
+        }
+        for (uint32_t i = lane; i < n_tail; i += 32) {
+            tail_blk[i] = blk[n_blocks - 1 - i];
+            tail_ts[i] = ts[n_blocks - 1 - i];
+        }
+        __syncwarp();
+        uint32_t evicted = 0;
+        uint32_t size = n_blocks;
+        for (uint32_t i = 0; i < k && evicted < want; ++i) {
+            const uint32_t at = v_at[i];
+            if (at == kGone) continue;  // sampled twice: removed already
+            const uint32_t id = v_id[i];
+            const uint32_t last = size - 1;
+            const uint32_t moved = tail_blk[n_blocks - 1 - last];  // the block that sits last now
+            const int64_t moved_t = tail_ts[n_blocks - 1 - last];
+            if (lane == 0) {
+                if (at != last) {
+                    blk[at] = moved;
+                    ts[at] = moved_t;
+                    pos[moved] = at + 1u;
+                    if (n_blocks - 1 - at < n_tail) {  // the staged tail follows
+                        tail_blk[n_blocks - 1 - at] = moved;
+                        tail_ts[n_blocks - 1 - at] = moved_t;
+                    }
+                }
+                pos[id] = 0u;
+            }
+            __syncwarp();
+            // later victims: further samples of this block are gone; the moved block has a new index
+            for (uint32_t v = i + 1 + lane; v < k; v += 32) {
+                if (v_at[v] == kGone) continue;
+                if (v_id[v] == id) {
+                    v_at[v] = kGone;
+                } else if (at != last && v_id[v] == moved) {
+                    v_at[v] = at;
+                }
+            }
+            __syncwarp();
+            --size;
+            ++evicted;
+        }
+        if (lane == 0) size_of[j] = size;
+        __syncwarp();
+        return evicted;
+    };
 
     for (int32_t t = 0; t < p.n_traces; ++t) {
         const int64_t beg = p.key_off[t];
-        const int64_t n = p.key_off[t + 1] - beg;
+        int64_t n = p.key_off[t + 1] - beg;
         const uint8_t ty = p.type[t];
         const int64_t skip = (ty == 1 && p.mask_off != nullptr) ? p.mask_off[t] : 0;
         const int64_t now = p.timestamps != nullptr ? p.timestamps[t] : static_cast<int64_t>(t);
+        int32_t me = p.trace_inst != nullptr ? p.trace_inst[t] : 0;
+        if (me < 0 || me >= K) {  // counted by the extent kernel; its keys have no ids: an empty trace
+            me = 0;
+            n = 0;
+        }
+        uint32_t *blk = blk_all + base_of[me];
+        int64_t *ts = ts_all + base_of[me];
+        int64_t my_size = size_of[me];
         int32_t ext = 0, inte = 0, wr = 0;
         bool alive = ty != 2;  // still inside the leading run of cached blocks
         for (int64_t base = 0; base < n; base += 32) {
@@ -191,107 +300,57 @@ __global__ void __launch_bounds__(32) RandomLruSweepKernel(const RandomSweep p) 
             if ((touch >> lane) & 1u) {
                 ts[cur - 1] = now;  // OnBlockAccessed
             } else if ((write >> lane) & 1u) {
-                const int64_t at = resident + __popc(write & lt);  // OnBlockWritten: appended in key order
+                const int64_t at = my_size + __popc(write & lt);  // OnBlockWritten: appended in key order
                 blk[at] = id;
                 ts[at] = now;
                 pos[id] = static_cast<uint32_t>(at) + 1u;
             }
             const uint32_t n_write = __popc(write);
+            my_size += n_write;
             resident += n_write;
             wr += static_cast<int32_t>(n_write);
             __syncwarp();
             if (ty == 1 && !alive) break;
         }
+        __syncwarp();
+        if (lane == 0) size_of[me] = my_size;
+        __syncwarp();
         if (ty != 1 && resident > quota) {
-            // CheckAndEvict: rounds of EvictBlocks until the excess is covered or a round evicts nothing.
+            // CheckAndEvict over the usage of the whole group: in turns over the instances, a batch each, until a
+            // round covers the excess or takes nothing (group rough); or from the writing instance only, whole
+            // batches (instance rough) or exactly the excess (instance precise).
             const int64_t excess = resident - quota;
             int64_t total = 0;
-            while (total < excess) {
-                int64_t count = p.evict_batch;
-                if (p.precise != 0 && excess - total < count) count = excess - total;
-                if (resident == 0) break;
-                const uint32_t n_blocks = static_cast<uint32_t>(resident);
-                const uint32_t want = count < resident ? static_cast<uint32_t>(count) : n_blocks;  // total_to_evict
-                const uint32_t n_sample = p.sampling_size < n_blocks ? p.sampling_size : n_blocks;
-                const uint32_t k = want < n_sample ? want : n_sample;
-                // the draws, in sequence (lane 0), then their modulo and the sampled blocks' times (all lanes)
-                if (lane == 0) {
-                    uint64_t x = rng;
-                    uint64_t *raw = reinterpret_cast<uint64_t *>(s_t);
-                    for (uint32_t j = 0; j < n_sample; ++j) {
-                        x ^= x << 13;
-                        x ^= x >> 7;
-                        x ^= x << 17;
-                        raw[j] = x;
+            if (p.mode == 1) {
+                while (total < excess) {
+                    bool any = false;
+                    for (int32_t j = 0; j < K; ++j) {  // a whole round even when the excess is covered midway
+                        const uint32_t got = evict_round(j, p.evict_batch);
+                        any = any || got != 0;
+                        total += got;
                     }
-                    rng = x;
+                    if (!any) break;
                 }
-                __syncwarp();
-                for (uint32_t j = lane; j < n_sample; j += 32) {
-                    const uint32_t at = static_cast<uint32_t>(reinterpret_cast<uint64_t *>(s_t)[j] % n_blocks);
-                    s_idx[j] = at;
-                    s_t[j] = ts[at];
+            } else {
+                while (total < excess) {
+                    int64_t count = p.evict_batch;
+                    if (p.mode == 3 && excess - total < count) count = excess - total;
+                    const uint32_t got = evict_round(me, count);
+                    if (got == 0) break;
+                    total += got;
                 }
-                __syncwarp();
-                if (lane == 0) PartialSortByTime(sample, k, n_sample);
-                __syncwarp();
-                // the victims as blocks (resolved before the first removal, as the reference resolves them),
-                // and the tail of the vector, which the removals read
-                const uint32_t n_tail = k < n_blocks ? k : n_blocks;
-                for (uint32_t j = lane; j < k; j += 32) {
-                    v_at[j] = s_idx[j];
-                    v_id[j] = blk[s_idx[j]];
-                }
-                for (uint32_t j = lane; j < n_tail; j += 32) {
-                    tail_blk[j] = blk[n_blocks - 1 - j];
-                    tail_ts[j] = ts[n_blocks - 1 - j];
-                }
-                __syncwarp();
-                uint32_t evicted = 0;
-                uint32_t size = n_blocks;
-                for (uint32_t i = 0; i < k && evicted < want; ++i) {
-                    const uint32_t at = v_at[i];
-                    if (at == kGone) continue;  // sampled twice: removed already
-                    const uint32_t id = v_id[i];
-                    const uint32_t last = size - 1;
-                    const uint32_t moved = tail_blk[n_blocks - 1 - last];  // the block that sits last now
-                    const int64_t moved_t = tail_ts[n_blocks - 1 - last];
-                    if (lane == 0) {
-                        if (at != last) {
-                            blk[at] = moved;
-                            ts[at] = moved_t;
-                            pos[moved] = at + 1u;
-                            if (n_blocks - 1 - at < n_tail) {  // the staged tail follows
-                                tail_blk[n_blocks - 1 - at] = moved;
-                                tail_ts[n_blocks - 1 - at] = moved_t;
-                            }
-                        }
-                        pos[id] = 0u;
-                    }
-                    __syncwarp();
-                    // later victims: further samples of this block are gone; the moved block has a new index
-                    for (uint32_t j = i + 1 + lane; j < k; j += 32) {
-                        if (v_at[j] == kGone) continue;
-                        if (v_id[j] == id) {
-                            v_at[j] = kGone;
-                        } else if (at != last && v_id[j] == moved) {
-                            v_at[j] = at;
-                        }
-                    }
-                    __syncwarp();
-                    --size;
-                    ++evicted;
-                }
-                resident = size;
-                if (evicted == 0) break;
-                total += evicted;
             }
+            resident -= total;
         }
         if (lane == 0 && p.ext_hit != nullptr) {
             p.ext_hit[out0 + t] = ext;
             p.int_hit[out0 + t] = inte;
             p.written[out0 + t] = wr;
-            p.cache_blocks[out0 + t] = resident;
+            p.cache_blocks[out0 + t] = size_of[me];
+        }
+        if (p.inst_blocks_trace != nullptr) {  // ReadRecord::blocks_per_instance of the reference's result records
+            int64_t *row = p.inst_blocks_trace + (out0 + t) * K;
+            for (int32_t j = lane; j < K; j += 32) row[j] = size_of[j];
         }
         sum_ext += ext;
         sum_int += inte;
@@ -303,6 +362,9 @@ __global__ void __launch_bounds__(32) RandomLruSweepKernel(const RandomSweep p) 
         tot[1] = sum_int;
         tot[2] = sum_wr;
         tot[3] = resident;
+    }
+    if (p.inst_blocks != nullptr) {
+        for (int32_t j = lane; j < K; j += 32) p.inst_blocks[static_cast<int64_t>(cfg) * K + j] = size_of[j];
     }
 }
 
@@ -336,36 +398,56 @@ int32_t kvcm_b200_selftest_partial_sort(uint32_t *h_idx, int64_t *h_times, uint3
     return KVCM_OK;
 }
 
-int64_t kvcm_b200_replay_random_lru_workspace_bytes(int64_t n_keys_total, int32_t n_configs) {
-    if (n_keys_total < 0 || n_keys_total >= (1ll << 32) - 1 || n_configs <= 0 || n_configs > 65535) return -1;
-    return static_cast<int64_t>(kvcm::RandomLayoutFor(n_keys_total, n_configs).total);
+int64_t kvcm_b200_replay_random_lru_group_workspace_bytes(int64_t n_keys_total, int32_t n_configs,
+                                                          int32_t n_instances) {
+    if (n_keys_total < 0 || n_keys_total >= (1ll << 32) - 1 || n_configs <= 0 || n_configs > 65535 || n_instances <= 0 ||
+        n_instances > KVCM_B200_REPLAY_GROUP_MAX_INSTANCES) {
+        return -1;
+    }
+    return static_cast<int64_t>(kvcm::RandomLayoutFor(n_keys_total, n_configs).total) +
+           ((static_cast<int64_t>(n_instances) + 1) * 8 + 255) / 256 * 256;
 }
 
-int32_t kvcm_b200_replay_random_lru(const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type,
-                                    const int64_t *d_mask_off, const uint8_t *d_mask_bits, const int64_t *d_timestamps,
-                                    int32_t n_traces, int64_t n_keys_total, const int64_t *d_quota_blocks,
-                                    int32_t n_configs, int32_t evict_batch, int32_t precise, double sample_rate,
-                                    void *d_workspace, int64_t workspace_bytes, int32_t *d_ext_hit, int32_t *d_int_hit,
-                                    int32_t *d_written, int64_t *d_cache_blocks, int64_t *d_totals, uint32_t *d_status,
-                                    kvcm_stream_t stream) {
+int64_t kvcm_b200_replay_random_lru_workspace_bytes(int64_t n_keys_total, int32_t n_configs) {
+    return kvcm_b200_replay_random_lru_group_workspace_bytes(n_keys_total, n_configs, 1);
+}
+
+int32_t kvcm_b200_replay_random_lru_group(const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type,
+                                          const int64_t *d_mask_off, const uint8_t *d_mask_bits,
+                                          const int64_t *d_timestamps, const int32_t *d_trace_instance,
+                                          const double *h_sample_rate, int32_t n_instances, int32_t n_traces,
+                                          int64_t n_keys_total, const int64_t *d_quota_blocks, int32_t n_configs,
+                                          int32_t evict_batch, int32_t eviction_mode, void *d_workspace,
+                                          int64_t workspace_bytes, int32_t *d_ext_hit, int32_t *d_int_hit,
+                                          int32_t *d_written, int64_t *d_cache_blocks, int64_t *d_totals,
+                                          int64_t *d_instance_blocks, int64_t *d_instance_blocks_per_trace,
+                                          uint32_t *d_status, kvcm_stream_t stream) {
     if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
-    if (n_traces < 0 || n_keys_total < 0 || n_configs <= 0 || evict_batch <= 0) return KVCM_EC_BADARGS;
-    // RandomLruEvictionPolicy's constructor (random_lru.cc:5-14): a rate <= 0 means 0.1; the size is a double
-    // division cut to an integer
-    if (sample_rate <= 0.0) sample_rate = 0.1;
-    const double sampling = static_cast<double>(evict_batch) / sample_rate;
-    if (static_cast<uint32_t>(evict_batch) > kvcm::kMaxBatch || sampling > static_cast<double>(kvcm::kMaxSample) ||
-        sampling < 1.0) {
-        return KVCM_EC_OUT_OF_LIMIT;
+    if (n_traces < 0 || n_keys_total < 0 || n_configs <= 0 || evict_batch <= 0 || n_instances <= 0 ||
+        eviction_mode < 1 || eviction_mode > 3) {
+        return KVCM_EC_BADARGS;
     }
-    const int64_t need = kvcm_b200_replay_random_lru_workspace_bytes(n_keys_total, n_configs);
+    const int64_t need = kvcm_b200_replay_random_lru_group_workspace_bytes(n_keys_total, n_configs, n_instances);
     if (need < 0) return KVCM_EC_OUT_OF_LIMIT;
+    kvcm::RandomSweep p;
+    for (int32_t j = 0; j < n_instances; ++j) {
+        // RandomLruEvictionPolicy's constructor (random_lru.cc:5-14): a rate <= 0 means 0.1; the size is a double
+        // division cut to an integer
+        double rate = h_sample_rate != nullptr ? h_sample_rate[j] : 0.0;
+        if (rate <= 0.0) rate = 0.1;
+        const double sampling = static_cast<double>(evict_batch) / rate;
+        if (static_cast<uint32_t>(evict_batch) > kvcm::kMaxBatch || sampling > static_cast<double>(kvcm::kMaxSample) ||
+            sampling < 1.0) {
+            return KVCM_EC_OUT_OF_LIMIT;
+        }
+        p.sampling_size[j] = static_cast<uint32_t>(sampling);
+    }
     if (n_traces == 0) return KVCM_OK;
     const int per_trace = (d_ext_hit != nullptr) + (d_int_hit != nullptr) + (d_written != nullptr) +
                           (d_cache_blocks != nullptr);
     if (d_key_off == nullptr || d_trace_type == nullptr || d_quota_blocks == nullptr || d_workspace == nullptr ||
-        (d_keys == nullptr && n_keys_total > 0) || (per_trace != 0 && per_trace != 4) ||
-        (per_trace == 0 && d_totals == nullptr)) {
+        (d_trace_instance == nullptr && n_instances > 1) || (d_keys == nullptr && n_keys_total > 0) ||
+        (per_trace != 0 && per_trace != 4) || (per_trace == 0 && d_totals == nullptr)) {
         return KVCM_ER_INVALID_ADDRESS;
     }
     if (reinterpret_cast<uintptr_t>(d_workspace) & 255u) return KVCM_ER_INVALID_ADDRESS;
@@ -378,15 +460,28 @@ int32_t kvcm_b200_replay_random_lru(const int64_t *d_keys, const int64_t *d_key_
     t.mask = kvcm::SlotsFor(n_keys_total) - 1;
     uint32_t *ids = reinterpret_cast<uint32_t *>(ws + l.ids_off);
     uint32_t *pos = reinterpret_cast<uint32_t *>(ws + l.pos_off);
+    int64_t *region_base = reinterpret_cast<int64_t *>(ws + l.total);
     cudaStream_t s = kvcm::AsStream(stream);
     const int sms = kvcm::GetDeviceInfo().sm_count;
     const uint64_t n_pos = static_cast<uint64_t>(n_keys_total > 0 ? n_keys_total : 1) * static_cast<uint64_t>(n_configs);
     kvcm::RandomInitKernel<<<sms * 8, 256, 0, s>>>(t, pos, n_pos);
-    if (n_keys_total > 0) {
-        kvcm::LruClaimIdsKernel<<<sms * 8, 256, 0, s>>>(t, d_keys, n_keys_total, d_status);
-        kvcm::LruLookupIdsKernel<<<sms * 8, 256, 0, s>>>(t, d_keys, n_keys_total, ids);
+    if (d_trace_instance == nullptr) {
+        if (n_keys_total > 0) {
+            kvcm::LruClaimIdsKernel<<<sms * 8, 256, 0, s>>>(t, d_keys, n_keys_total, d_status);
+            kvcm::LruLookupIdsKernel<<<sms * 8, 256, 0, s>>>(t, d_keys, n_keys_total, ids);
+        }
+    } else {
+        kvcm::LruGroupExtentKernel<<<1, 1024, sizeof(unsigned long long) * n_instances, s>>>(
+            d_key_off, d_trace_instance, n_traces, n_instances, region_base, d_status);
+        // one instance after the other: the table starts empty each time, the id counter runs on
+        for (int32_t j = 0; n_keys_total > 0 && j < n_instances; ++j) {
+            if (j > 0) kvcm::IdTableClearKernel<<<sms * 8, 256, 0, s>>>(t);
+            kvcm::LruClaimIdsOfInstanceKernel<<<sms * 4, 256, 0, s>>>(t, d_keys, d_key_off, d_trace_instance, n_traces, j,
+                                                                     d_status);
+            kvcm::LruLookupIdsOfInstanceKernel<<<sms * 4, 256, 0, s>>>(t, d_keys, d_key_off, d_trace_instance, n_traces,
+                                                                      j, ids);
+        }
     }
-    kvcm::RandomSweep p;
     p.ids = ids;
     p.key_off = d_key_off;
     p.type = d_trace_type;
@@ -406,10 +501,28 @@ int32_t kvcm_b200_replay_random_lru(const int64_t *d_keys, const int64_t *d_key_
     p.n_traces = n_traces;
     p.n_configs = n_configs;
     p.evict_batch = evict_batch;
-    p.precise = precise;
-    p.sampling_size = static_cast<uint32_t>(sampling);
-    kvcm::RandomLruSweepKernel<<<static_cast<unsigned>(n_configs), 32, 0, s>>>(p);
+    p.trace_inst = d_trace_instance;
+    p.region_base = d_trace_instance != nullptr ? region_base : nullptr;
+    p.inst_blocks = d_instance_blocks;
+    p.inst_blocks_trace = d_instance_blocks_per_trace;
+    p.n_instances = n_instances;
+    p.mode = eviction_mode;
+    kvcm::RandomLruSweepKernel<<<static_cast<unsigned>(n_configs), 32, sizeof(int64_t) * 3 * n_instances, s>>>(p);
     return kvcm::LaunchStatus();
+}
+
+int32_t kvcm_b200_replay_random_lru(const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type,
+                                    const int64_t *d_mask_off, const uint8_t *d_mask_bits, const int64_t *d_timestamps,
+                                    int32_t n_traces, int64_t n_keys_total, const int64_t *d_quota_blocks,
+                                    int32_t n_configs, int32_t evict_batch, int32_t precise, double sample_rate,
+                                    void *d_workspace, int64_t workspace_bytes, int32_t *d_ext_hit, int32_t *d_int_hit,
+                                    int32_t *d_written, int64_t *d_cache_blocks, int64_t *d_totals, uint32_t *d_status,
+                                    kvcm_stream_t stream) {
+    return kvcm_b200_replay_random_lru_group(d_keys, d_key_off, d_trace_type, d_mask_off, d_mask_bits, d_timestamps,
+                                             nullptr, &sample_rate, 1, n_traces, n_keys_total, d_quota_blocks,
+                                             n_configs, evict_batch, precise != 0 ? 3 : 2, d_workspace, workspace_bytes,
+                                             d_ext_hit, d_int_hit, d_written, d_cache_blocks, d_totals, nullptr, nullptr,
+                                             d_status, stream);
 }
 
 }  // extern "C"

@@ -78,9 +78,10 @@ def _kept(traces: List[tr.Trace], rw_separation: bool) -> List[tr.Trace]:
 
 def replay_group(traces: List[tr.Trace], instance_ids: Sequence[str], device, quota_blocks: int,
                  rw_separation: bool = False, evict_batch: int = 100, mode: int = 1,
-                 policy: str = "lru") -> Dict[str, Dict[str, np.ndarray]]:
-    """Replays the traces of the instances of ONE group that share a quota (every instance under `policy`: "lru" or
-    "leaf_aware_lru"), in the order given (all instances together, by timestamp), and returns one record per
+                 policy="lru", sample_rate=0.0) -> Dict[str, Dict[str, np.ndarray]]:
+    """Replays the traces of the instances of ONE group that share a quota (every instance under `policy`, or one
+    name per instance in the order of `instance_ids`: "lru" and "leaf_aware_lru" in any mix, or "random_lru"
+    throughout with `sample_rate` one number or one per instance), in the order given (all instances together, by timestamp), and returns one record per
     instance as replay_instance does.  mode is the configuration's eviction_mode (1 group rough, 2 instance rough, 3 instance precise;
     kv_cache_manager/optimizer/manager/eviction_manager.cc:57-239).  current_cache_blocks is the usage of the
     trace's own instance; blocks_per_instance [record, instance] is the usage of every instance of the group at
@@ -99,7 +100,8 @@ def replay_group(traces: List[tr.Trace], instance_ids: Sequence[str], device, qu
                             len(instance_ids), [int(quota_blocks)], torch.from_numpy(mask).to(device), evict_batch,
                             mode, mask_bits=torch.from_numpy(bits).to(device) if bits is not None else None,
                             instance_records=True, policy=policy,
-                            timestamps=torch.from_numpy(ts).to(device) if policy == "leaf_aware_lru" else None)
+                            timestamps=torch.from_numpy(ts).to(device) if policy != "lru" else None,
+                            sample_rate=sample_rate)
     ext, inte, wr, size = (x[0].cpu().numpy() for x in res[:4])
     every = res.instance_blocks_per_trace[0].cpu().numpy()  # [trace, instance], instances in the order of instance_ids
     internal_read = np.array([tr.masked_count(t.block_mask, len(t.keys)) if t.kind == tr.GET_LOCATION else 0
@@ -194,8 +196,8 @@ def run_trace_file(trace_path: str, trace_type: str, output_dir: str, device=Non
     """Loads a trace file, replays every instance on the GPU and writes `<instance>_hit_rates.csv` per instance
     (`<instance>_quota<q>_hit_rates.csv` per instance and quota when quota_blocks is a sequence).  Every instance is
     replayed on its own, except the instances of a group in `groups` (dicts with "instances" = the ids and "quota" =
-    the shared quota in blocks, "policy" = the eviction policy of all of them, "lru" when absent, as
-    parse_startup_config returns them), which are replayed together against their
+    the shared quota in blocks, "policy" = the eviction policy of all of them or one per instance, "lru" when
+    absent, "sample_rate" = the rates of "random_lru" instances, as parse_startup_config returns them), which are replayed together against their
     shared quota under eviction `mode` (replay_group; in their CSV files CachedBlocksPerInstance lists the instances
     of the group in the group's order - the reference lists every instance of the whole configuration there, in
     the order of an unordered_map)."""
@@ -208,7 +210,7 @@ def run_trace_file(trace_path: str, trace_type: str, output_dir: str, device=Non
     out = {}
     for group in groups or []:
         recs = replay_group(traces, group["instances"], device, group["quota"], rw_separation, evict_batch, mode,
-                            group.get("policy", "lru"))
+                            group.get("policy", "lru"), group.get("sample_rate", 0.0))
         for instance_id, r in recs.items():
             by_instance.pop(instance_id, None)
             if (r["kind"] != tr.WRITE_CACHE).any():
@@ -239,8 +241,9 @@ def parse_startup_config(config: Union[str, dict]) -> dict:
     """The Optimizer's startup configuration (kv_cache_manager/optimizer/optimizer_startup_config_load.json, read
     by kv_cache_manager/optimizer/config/optimizer_config.cc:4-12, instance_group_config.cc:5-12,
     instance_config.cc:6-22, eviction_config.cc:5-8) reduced to what the GPU replay needs.  Raises
-    NotImplementedError for what it cannot replay exactly: groups of several instances unless all of them use "lru"
-    or all of them use "leaf_aware_lru" (those come back under "groups").
+    NotImplementedError for what it cannot replay exactly: groups of several instances that mix "random_lru" with
+    another policy (groups of "lru" and "leaf_aware_lru" instances, mixed or not, and groups of "random_lru"
+    instances come back under "groups").
     hierarchical_eviction_enabled: the reference creates an eviction policy for the FIRST storage tier only (later
     tiers never evict, kv_cache_manager/optimizer/manager/eviction_manager.cc:26-39), every block gets its location
     on that tier alone (kv_cache_manager/optimizer/index/radix_tree_index.cc:327-353), so erasing that location on
@@ -264,14 +267,17 @@ def parse_startup_config(config: Union[str, dict]) -> dict:
             capacity = group["storages"][0].get("capacity", 0)
         group_quota = int(capacity * float(group.get("used_percentage", 1.0)))
         together = len(instances) > 1 and mode != EVICTION_MODE_UNSPECIFIED
-        used = sorted({i.get("eviction_policy_type", "lru") for i in instances})
-        if together and used not in (["lru"], ["leaf_aware_lru"]):
-            raise NotImplementedError("group %r: %d instances share one quota under %s; replayed are groups that use "
-                                      "\"lru\" or \"leaf_aware_lru\" throughout"
-                                      % (group.get("group_name"), len(instances), ", ".join(map(repr, used))))
+        used = [i.get("eviction_policy_type", "lru") for i in instances]
+        if together and set(used) != {"random_lru"} and any(u not in ("lru", "leaf_aware_lru") for u in used):
+            raise NotImplementedError("group %r: %d instances share one quota under %s; replayed are groups of "
+                                      "\"lru\" and \"leaf_aware_lru\" instances and groups of \"random_lru\" instances"
+                                      % (group.get("group_name"), len(instances), ", ".join(map(repr, sorted(set(used))))))
         if together:
             shared.append(dict(group_name=group.get("group_name"), instances=[str(i["instance_id"]) for i in instances],
-                               quota=group_quota, policy=used[0]))
+                               quota=group_quota, policy=used[0] if len(set(used)) == 1 else used))
+            if used[0] == "random_lru":
+                shared[-1]["sample_rate"] = [float((i.get("eviction_policy_params") or {}).get("sample_rate", 0.0))
+                                             for i in instances]
         for inst in instances:
             policy = inst.get("eviction_policy_type", "lru")
             if policy not in ("lru", "leaf_aware_lru", "random_lru") and mode != EVICTION_MODE_UNSPECIFIED:

@@ -121,7 +121,7 @@ def test_one_instance_group_is_the_single_instance_sweep_and_bad_instances_are_c
         _gpu(keys, off, types, zeros, 65, quotas, mask)
     with pytest.raises(ValueError):
         RunTracesLruGroup(torch.from_numpy(keys).to(DEV), torch.from_numpy(off).to(DEV), torch.from_numpy(types).to(DEV),
-                          torch.from_numpy(zeros).to(DEV), 1, quotas, policy="random_lru")
+                          torch.from_numpy(zeros).to(DEV), 1, quotas, policy="fifo")
 
 
 def test_deep_shared_prefixes_requeue_whole_nodes():
@@ -160,3 +160,53 @@ def test_deep_shared_prefixes_requeue_whole_nodes():
         for a, b in zip(want, r[:4]):
             assert np.array_equal(a, b.cpu().numpy()[0]), q
     assert status[0].item() == 0
+
+
+@pytest.mark.parametrize("mode", [1, 2, 3])
+def test_a_group_that_mixes_lru_and_leaf_aware_instances(mode):
+    """EvictionPolicyFactory::CreatePolicy runs per instance (kv_cache_manager/optimizer/manager/
+    eviction_manager.cc:22-55), so one group may hold instances of different policies; the reference tests none."""
+    rng = np.random.default_rng(430 + mode)
+    keys, off, types, mask = _workload(rng, 1800, True)
+    ts = np.cumsum(rng.integers(0, 3, size=len(types)))
+    each = ["lru", POLICY, "lru", POLICY, POLICY]
+    inst = rng.integers(0, len(each), size=len(types)).astype(np.int32)
+    quotas = [5, 40, 300, 1500, 1 << 40]
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    r = RunTracesLruGroup(torch.from_numpy(keys).to(DEV), torch.from_numpy(off).to(DEV), torch.from_numpy(types).to(DEV),
+                          torch.from_numpy(inst).to(DEV), len(each), quotas, torch.from_numpy(mask).to(DEV), evict_batch=6,
+                          mode=mode, policy=each, timestamps=torch.from_numpy(ts).to(DEV), status=status,
+                          instance_records=True)
+    torch.cuda.synchronize()
+    assert status[0].item() == 0
+    got = [t.cpu().numpy() for t in (r[0], r[1], r[2], r[3], r[5], r[6])]
+    same_as_all_leaf = 0
+    for c, q in enumerate(quotas):
+        want = oracle.LruGroupReplay(q, len(each), evict_batch=6, mode=mode, policy=each).run(
+            keys, off, types, inst, mask, timestamps=ts, instance_records=True)
+        for name, a, b in zip(("ext", "int", "written", "cached", "final", "every"), want, got):
+            assert np.array_equal(a, b[c]), (name, q)
+        leaf = oracle.LruGroupReplay(q, len(each), evict_batch=6, mode=mode, policy=POLICY).run(
+            keys, off, types, inst, mask, timestamps=ts)
+        same_as_all_leaf += int(np.array_equal(leaf[0], want[0]))
+    assert same_as_all_leaf < len(quotas)  # the "lru" instances do behave differently
+
+
+def test_lru_instances_in_the_tree_kernel_equal_the_lru_group_sweep():
+    rng = np.random.default_rng(440)
+    keys, off, types, mask = _workload(rng, 1200, True)
+    n_inst = 3
+    inst = rng.integers(0, n_inst, size=len(types)).astype(np.int32)
+    quotas = [12, 150, 900]
+    args = [torch.from_numpy(keys).to(DEV), torch.from_numpy(off).to(DEV), torch.from_numpy(types).to(DEV),
+            torch.from_numpy(inst).to(DEV)]
+    for mode in (1, 3):
+        plain = RunTracesLruGroup(*args, n_inst, quotas, torch.from_numpy(mask).to(DEV), evict_batch=5, mode=mode)
+        # one more instance, leaf-aware and without a trace, sends the same group through the kernel that keeps trees
+        tree = RunTracesLruGroup(*args, n_inst + 1, quotas, torch.from_numpy(mask).to(DEV), evict_batch=5, mode=mode,
+                                 policy=["lru"] * n_inst + [POLICY])
+        for a, b in zip(plain[:5], tree[:5]):
+            assert np.array_equal(a.cpu().numpy(), b.cpu().numpy())
+        assert np.array_equal(plain.instance_blocks.cpu().numpy(), tree.instance_blocks.cpu().numpy()[:, :n_inst])
+    with pytest.raises(ValueError):
+        RunTracesLruGroup(*args, n_inst, quotas, policy=["lru", "lru"])

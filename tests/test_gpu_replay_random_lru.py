@@ -107,3 +107,52 @@ def test_limits_and_empty_input():
     r = RunTracesLru(torch.zeros(0, dtype=torch.int64, device=DEV), torch.zeros(3, dtype=torch.int64, device=DEV),
                      torch.tensor([W, G], dtype=torch.uint8, device=DEV), [5], policy=POLICY)
     assert r.current_cache_blocks.cpu().tolist() == [[0, 0]]
+
+
+@pytest.mark.parametrize("mode", [1, 2, 3])
+def test_group_of_sampling_instances_against_the_oracle(mode):
+    """Several "random_lru" instances share a quota (OptEvictionManager::EvictByGroupRough / EvictByInstanceRough /
+    EvictByInstancePrecise, kv_cache_manager/optimizer/manager/eviction_manager.cc:86-239): every instance keeps its
+    own generator and sampling size, and a group-rough round draws in each of them in turn."""
+    from tair_kvcache_b200.optimizer import RunTracesLruGroup
+    rng = np.random.default_rng(700 + mode)
+    keys, off, types, mask, ts = _workload(rng, 1500, True)
+    rates = [0.1, 0.5, 0.0, 1.0]
+    n_inst = len(rates)
+    inst = rng.integers(0, n_inst, size=len(types)).astype(np.int32)
+    quotas = [3, 40, 300, 2000, 1 << 40]
+    batch = 9
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    r = RunTracesLruGroup(torch.from_numpy(keys).to(DEV), torch.from_numpy(off).to(DEV), torch.from_numpy(types).to(DEV),
+                          torch.from_numpy(inst).to(DEV), n_inst, quotas, torch.from_numpy(mask).to(DEV),
+                          evict_batch=batch, mode=mode, policy=POLICY, sample_rate=rates,
+                          timestamps=torch.from_numpy(ts).to(DEV), status=status, instance_records=True)
+    torch.cuda.synchronize()
+    assert status[0].item() == 0
+    got = [t.cpu().numpy() for t in (r[0], r[1], r[2], r[3], r[5], r[6])]
+    assert np.array_equal(r.totals.cpu().numpy()[:, 3], got[4].sum(1))
+    for c, q in enumerate(quotas):
+        want = oracle.LruGroupReplay(q, n_inst, evict_batch=batch, mode=mode, policy=POLICY, sample_rate=rates).run(
+            keys, off, types, inst, mask, timestamps=ts, instance_records=True)
+        for name, a, b in zip(("ext", "int", "written", "cached", "final", "every"), want, got):
+            assert np.array_equal(a, b[c]), (name, q)
+
+
+def test_one_sampling_instance_as_a_group_and_refused_mixtures():
+    from tair_kvcache_b200.optimizer import RunTracesLruGroup
+    rng = np.random.default_rng(710)
+    keys, off, types, mask, ts = _workload(rng, 600, True)
+    quotas = [10, 200]
+    zeros = torch.zeros(len(types), dtype=torch.int32, device=DEV)
+    args = [torch.from_numpy(keys).to(DEV), torch.from_numpy(off).to(DEV), torch.from_numpy(types).to(DEV)]
+    for mode, precise in ((1, False), (2, False), (3, True)):
+        one = _gpu(keys, off, types, quotas, mask, ts, evict_batch=7, precise=precise, sample_rate=0.2)
+        grp = RunTracesLruGroup(*args, zeros, 1, quotas, torch.from_numpy(mask).to(DEV), evict_batch=7, mode=mode,
+                                policy=POLICY, sample_rate=0.2, timestamps=torch.from_numpy(ts).to(DEV))
+        for a, b in zip(one, grp[:4]):
+            assert np.array_equal(a, b.cpu().numpy())
+    with pytest.raises(ValueError):  # a sampling instance beside a queueing one is not replayed
+        RunTracesLruGroup(*args, zeros, 2, quotas, policy=["lru", POLICY])
+    with pytest.raises(_cabi.KvcmError) as e:  # the sample of one of the instances would not fit shared memory
+        RunTracesLruGroup(*args, zeros, 2, quotas, evict_batch=300, policy=POLICY, sample_rate=[0.5, 0.1])
+    assert e.value.code == _cabi.KVCM_EC_OUT_OF_LIMIT

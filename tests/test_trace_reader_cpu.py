@@ -128,14 +128,15 @@ def test_startup_config_of_the_reference_is_understood():
                                 instances=["3780643326877293460", "b"], quota=9000, policy="lru")]
     assert c["quota_blocks"] == {} and c["mode"] == 3
     cfg["instance_groups"][0]["instances"][1]["eviction_policy_type"] = "leaf_aware_lru"
-    with pytest.raises(NotImplementedError):  # mixed policies in one group
-        parse_startup_config(cfg)
+    assert parse_startup_config(cfg)["groups"][0]["policy"] == ["lru", "leaf_aware_lru"]  # one name per instance
     cfg["instance_groups"][0]["instances"][0]["eviction_policy_type"] = "leaf_aware_lru"
     assert parse_startup_config(cfg)["groups"][0]["policy"] == "leaf_aware_lru"  # the same policy throughout
-    cfg["instance_groups"][0]["instances"][0]["eviction_policy_type"] = "random_lru"
     cfg["instance_groups"][0]["instances"][1]["eviction_policy_type"] = "random_lru"
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(NotImplementedError):  # a sampling instance beside a queueing one in a shared quota
         parse_startup_config(cfg)
+    cfg["instance_groups"][0]["instances"][0]["eviction_policy_type"] = "random_lru"
+    g = parse_startup_config(cfg)["groups"][0]  # sampling instances only: replayed, each with its own rate
+    assert g["policy"] == "random_lru" and g["sample_rate"] == [0.1, 0.0]
     cfg["eviction_params"]["eviction_mode"] = 0  # no eviction is ever performed: any grouping replays
     assert parse_startup_config(cfg)["quota_blocks"] == {}
 
@@ -154,8 +155,8 @@ def test_shared_quota_groups_host_side(tmp_path, monkeypatch):
     from tair_kvcache_b200.optimizer.replay import LruGroupSweepResult
 
     def stand_in(keys, off, kind, inst, n_inst, quotas, mask, evict_batch, mode, mask_bits=None,
-                 instance_records=False, policy="lru", timestamps=None):
-        assert (timestamps is not None) == (policy == "leaf_aware_lru")
+                 instance_records=False, policy="lru", timestamps=None, sample_rate=0.0):
+        assert (timestamps is not None) == (policy != "lru")
         r = oracle.LruGroupReplay(quotas[0], n_inst, evict_batch=evict_batch, mode=mode, policy=policy).run(
             keys.numpy(), off.numpy(), kind.numpy(), inst.numpy(), mask.numpy(), instance_records=True,
             timestamps=None if timestamps is None else timestamps.numpy())
@@ -195,6 +196,9 @@ def test_shared_quota_groups_host_side(tmp_path, monkeypatch):
     cfg["eviction_params"]["eviction_mode"] = 1
     recs = runner.run_startup_config(cfg, device="cpu", rw_separation=True)
     assert recs["a"]["current_cache_blocks"].tolist() == [3, 2] and recs["b"]["blocks_per_instance"].tolist() == [[2, 1]] * 2
+    cfg["instance_groups"][0]["instances"][0]["eviction_policy_type"] = "lru"  # a mixed group: one name per instance
+    recs = runner.run_startup_config(cfg, device="cpu", rw_separation=True)
+    assert recs["a"]["current_cache_blocks"].tolist() == [3, 2] and recs["b"]["write_blocks"].tolist() == [2, 0]
 
 
 def test_a_key_repeated_inside_a_trace_is_found_before_any_launch():
