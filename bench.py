@@ -848,17 +848,28 @@ def run_window(args, ctx):
         if args.long_fraction is None:
             # measured: one GPU, head at 2 warps per SM: 0.3 / 0.5 / 0.7 -> 3.17 / 3.68 / 3.73 ms per step;
             # 2 GPUs routed, head at 4: 0.5 / 0.7 -> 2.80 / 2.84 ms
-            args.long_fraction = 0.7 if world > 1 and routed else 0.3
+            args.long_fraction = "0.7" if world > 1 and routed else "0.3"
         if args.head_cap is None:  # one GPU: head 4 / 2 warps per SM -> 3.27 / 3.17 ms; 2 GPUs routed: 2.84 / 2.99 ms
-            args.head_cap = 4 if world > 1 and routed else 2
-        n_long = int(np.count_nonzero(my_len >= args.long_fraction * my_len.max()))
+            args.head_cap = "4" if world > 1 and routed else "2"
+        # several thresholds (comma-separated) cut the head into length classes, longest first, each with its own
+        # stream and cap, so that the keys of a class are matched while the longer chains before it still run;
+        # measured on one GPU: 0.85,0.3 / 0.7,0.3 / 0.6,0.3 -> 4.34 / 3.72 / 3.43 ms per step against 3.21 for 0.3
+        # alone - the step is close to the sum of the kernels' throughput-bound times, more launches only crowd it
+        fractions = sorted((float(f) for f in str(args.long_fraction).split(",")), reverse=True)
+        caps = [int(c) for c in str(args.head_cap).split(",")]
+        caps += [caps[-1]] * (len(fractions) - len(caps))
+        if world > 1 and routed and len(fractions) > 1:
+            raise SystemExit("the routed shard modes take one --long-fraction")
+        edges_long = [int(np.count_nonzero(my_len >= f * my_len.max())) for f in fractions]
+        n_long = edges_long[-1]
         prefix_s = torch.empty(len(perm), dtype=torch.int32, device=device)
         window_s = torch.empty(len(perm), dtype=torch.int32, device=device)
         inv = torch.from_numpy(np.argsort(perm)).to(device)  # request -> sorted position
         # (first request, end, hashing warps per SM): 4 for the head, so that its chains sit alone on their
         # schedulers, and 3 for the rest, which then shares an SM with a head warp without crowding its scheduler
         # (measured: rest at 2 / 3 / 4 / unlimited warps per SM -> 4.12 / 3.98 / 4.29 / 4.25 ms per step)
-        parts = [(0, n_long, args.head_cap), (n_long, len(perm), args.rest_cap)]
+        parts = [(a, b, c) for a, b, c in zip([0] + edges_long[:-1], edges_long, caps)] + \
+                [(n_long, len(perm), args.rest_cap)]
         if not (world > 1 and routed) and args.rest_chunks > 1 and len(perm) - n_long > args.rest_chunks:
             # The rest is bound by throughput, and its two halves use different resources: hashing the integer
             # pipe, matching the random-sector rate of the memory system.  Cut into chunks of equal token count on
@@ -866,11 +877,12 @@ def run_window(args, ctx):
             cuts = np.searchsorted(off_s, off_s[n_long] + (off_s[-1] - off_s[n_long]) *
                                    np.arange(1, args.rest_chunks) // args.rest_chunks)
             edges = sorted(set([n_long] + [int(c) for c in cuts if n_long < c < len(perm)] + [len(perm)]))
-            parts = [(0, n_long, args.head_cap)] + [(a, b, args.rest_cap) for a, b in zip(edges[:-1], edges[1:])]
+            parts = parts[:-1] + [(a, b, args.rest_cap) for a, b in zip(edges[:-1], edges[1:])]
         # the head's stream comes first in the queues of the SMs: once its long chains are through, its matchers
         # are not left waiting behind the kernels of the rest
-        streams = [torch.cuda.Stream(device, priority=-1 if i == 0 and args.head_priority else 0)
+        streams = [torch.cuda.Stream(device, priority=-1 if i < len(fractions) and args.head_priority else 0)
                    for i in range(len(parts))]
+        flag_bytes = torch.empty(max(n_keys, 1), dtype=torch.uint8, device=device)
         match = searcher if world > 1 else local_index
         # the keys of a part as a batch of its own (routing sends whole batches)
         rel_ko = [(d_ko_s[a:b + 1] - int(ko_s[a])).contiguous() for a, b, _ in parts]
@@ -921,8 +933,15 @@ def run_window(args, ctx):
                 if marks is not None:
                     marks.append(("part%d_hashed" % i, torch.cuda.Event(enable_timing=True)))
                     marks[-1][1].record(st)
-                prefix_s[a:b] = match.PrefixMatch(d_keys, d_ko_s[a:b + 1])
-                window_s[a:b] = match.ReverseRollSlideWindowMatch(d_keys, d_ko_s[a:b + 1], sw)
+                if world == 1 and args.match_via == "flags":
+                    # one look-up per key serves both questions
+                    ka, kb = int(ko_s[a]), int(ko_s[b])
+                    fl = local_index.BatchGet(d_keys[ka:kb], out=flag_bytes[ka:kb])
+                    local_index.PrefixMatchFromFlags(fl, rel_ko[i], out=prefix_s[a:b])
+                    local_index.ReverseRollSlideWindowMatchFromFlags(fl, rel_ko[i], sw, out=window_s[a:b])
+                else:
+                    prefix_s[a:b] = match.PrefixMatch(d_keys, d_ko_s[a:b + 1])
+                    window_s[a:b] = match.ReverseRollSlideWindowMatch(d_keys, d_ko_s[a:b + 1], sw)
                 if marks is not None:
                     marks.append(("part%d_matched" % i, torch.cuda.Event(enable_timing=True)))
                     marks[-1][1].record(st)
@@ -1078,11 +1097,16 @@ def run_window(args, ctx):
                            "shard_mode": args.shard_mode if world > 1 else "one unsharded index",
                            "lookups_per_s": 2 * total_keys * args.steps / (ms * 1e-3),
                            "parity_sample_ok": parity, "phase_ms_rank0": phase_ms,
-                           "schedule": ("%d streams: the %d longest requests of rank 0 (>= %.2f of the longest) hashed "
-                                        "and matched beside the rest%s; phase_ms are the kernels run alone on the "
-                                        "whole batch" % (len(parts), n_long, args.long_fraction,
-                                                         " (in %d chunks of equal token count)" % (len(parts) - 1)
-                                                         if len(parts) > 2 else "")) if overlap else "one stream"},
+                           "schedule": ("%d streams: the %d longest requests of rank 0 (length classes >= %s of the "
+                                        "longest, %s hashing warps per SM) hashed and matched beside the rest%s%s; "
+                                        "phase_ms are the kernels run alone on the whole batch"
+                                        % (len(parts), n_long, "/".join("%.2f" % f for f in fractions),
+                                           "/".join(str(c) for c in caps[:len(fractions)]),
+                                           " (in %d chunks of equal token count)" % (len(parts) - len(fractions))
+                                           if len(parts) > len(fractions) + 1 else "",
+                                           "; one BatchGet per key feeds both matchers"
+                                           if world == 1 and args.match_via == "flags" else ""))
+                           if overlap else "one stream"},
                 "gpu_launches": ({"peer": 6, "route": 14, "route_peer": 14}[args.shard_mode] if overlap and world > 1
                                  else 3 * len(parts) if overlap else 3 if world == 1 else 7 if routed else 4)
                 * args.steps * world}
@@ -2064,11 +2088,16 @@ def main():
                     help="c4 on several GPUs: probe remote shards over NVLink, or exchange keys and reduce results")
     ap.add_argument("--no-overlap", action="store_true",
                     help="c4: one stream, requests in arrival order (the earlier form of the step)")
-    ap.add_argument("--long-fraction", type=float, default=None,
+    ap.add_argument("--match-via", default="direct", choices=["flags", "direct"],
+                    help="c4 on one GPU: direct = PrefixMatch and ReverseRollSlideWindowMatch probe the index "
+                         "themselves (they stop at a request's first miss and look at window ends only); flags = one "
+                         "BatchGet per key, then both matchers over the flag bytes (measured: 4.42 ms per step "
+                         "against 3.21: beside the hash kernels the look-up of every key costs more than it saves)")
+    ap.add_argument("--long-fraction", type=str, default=None,
                     help="c4: requests at least this fraction of the longest form the head that gets its own stream "
                          "(default 0.3; 0.7 for the routed shard modes, whose head is routed after the rest)")
     ap.add_argument("--head-priority", type=int, default=1, help="c4: 1 = the head's stream has high priority")
-    ap.add_argument("--head-cap", type=int, default=None,
+    ap.add_argument("--head-cap", type=str, default=None,
                     help="c4: hashing warps per SM of the long head (default 2 on one GPU, 4 in the routed modes)")
     ap.add_argument("--rest-cap", type=int, default=3, help="c4: hashing warps per SM of the rest")
     ap.add_argument("--rest-chunks", type=int, default=1,

@@ -52,13 +52,38 @@ class BatchMetaSearcher:
                    self.avail_mask, out.data_ptr(), self.index._s())
         return out[:n_req]
 
-    def BatchGet(self, keys: torch.Tensor) -> torch.Tensor:
+    def BatchGet(self, keys: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """uint8 flags per key (FLAG_SERVABLE | FLAG_EXISTS | FLAG_NONEMPTY | FLAG_WRITABLE)."""
         keys = _keys(keys, self.index.device)
-        out = torch.empty(max(keys.numel(), 1), dtype=torch.uint8, device=self.index.device)
+        if out is None:
+            out = torch.empty(max(keys.numel(), 1), dtype=torch.uint8, device=self.index.device)
         _cabi.call("kvcm_b200_batch_get", self.index.handle, keys.data_ptr(), keys.numel(), self.avail_mask,
                    out.data_ptr(), self.index._s())
         return out[:keys.numel()]
+
+    # When one batch asks both questions - how long is the cached prefix, where is the last cached window - one
+    # look-up per key (BatchGet) can serve both: the two matchers below read the flag bytes instead of probing the
+    # index again.  Same results as PrefixMatch / ReverseRollSlideWindowMatch on the keys.
+    def PrefixMatchFromFlags(self, flags: torch.Tensor, key_off: torch.Tensor, mask_off: Optional[torch.Tensor] = None,
+                             mask_bits: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        n_req = key_off.numel() - 1
+        key_off = _keys(key_off, self.index.device)
+        if out is None:
+            out = torch.empty(max(n_req, 1), dtype=torch.int32, device=self.index.device)
+        _cabi.call("kvcm_b200_match_prefix_from_flags", flags.data_ptr(), key_off.data_ptr(), n_req,
+                   mask_off.data_ptr() if mask_off is not None else None,
+                   mask_bits.data_ptr() if mask_bits is not None else None, out.data_ptr(), self.index._s())
+        return out[:n_req]
+
+    def ReverseRollSlideWindowMatchFromFlags(self, flags: torch.Tensor, key_off: torch.Tensor, sw_size: int,
+                                             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        n_req = key_off.numel() - 1
+        key_off = _keys(key_off, self.index.device)
+        if out is None:
+            out = torch.empty(max(n_req, 1), dtype=torch.int32, device=self.index.device)
+        _cabi.call("kvcm_b200_match_sw_from_flags", flags.data_ptr(), key_off.data_ptr(), n_req, sw_size,
+                   out.data_ptr(), self.index._s())
+        return out[:n_req]
 
     def FilterWriteCache(self, keys: torch.Tensor, key_off: torch.Tensor):
         """Batched CacheManager::FilterWriteCache.  Returns (offset, mask, n_new): int32 offset per request (index
