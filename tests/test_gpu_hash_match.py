@@ -295,6 +295,22 @@ def test_batch_get_random_against_oracle():
         assert np.array_equal(got.cpu().numpy(), ox.batch_get(keys, weights=weights))
 
 
+def test_both_matchers_from_one_look_up_per_key():
+    """BatchGet once, then prefix and window match over the flag bytes: the plan for batches that ask both questions."""
+    rng = np.random.default_rng(78)
+    ox, ix, keys, off = _random_world(rng, 3000, 400, 300, 0.95)
+    dk, doff = torch.from_numpy(keys).to(DEV), torch.from_numpy(off).to(DEV)
+    for weights in [(1, 3, 3, 3, 5), (1, 3, 0, 3, 5)]:
+        ms = BatchMetaSearcher(ix, avail_mask_from_weights(weights))
+        flags = ms.BatchGet(dk, out=torch.empty(len(keys), dtype=torch.uint8, device=DEV))
+        mask_off = rng.integers(0, 20, size=len(off) - 1).astype(np.int64)
+        got = ms.PrefixMatchFromFlags(flags, doff, torch.from_numpy(mask_off).to(DEV)).cpu().numpy()
+        assert np.array_equal(got, ox.prefix_match_batch(keys, off, mask_off, weights=weights))
+        for sw in (1, 7, 40):
+            got = ms.ReverseRollSlideWindowMatchFromFlags(flags, doff, sw).cpu().numpy()
+            assert np.array_equal(got, ox.sw_match_batch(keys, off, sw, weights=weights, threads=4))
+
+
 def test_filter_write_cache_against_oracle():
     rng = np.random.default_rng(31)
     for hit_bias in (0.3, 0.9):
