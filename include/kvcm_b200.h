@@ -768,6 +768,13 @@ KVCM_API int32_t kvcm_b200_replay_leaf_lru_group(
     int32_t *d_written, int64_t *d_cache_blocks, int64_t *d_totals, int64_t *d_instance_blocks,
     int64_t *d_instance_blocks_per_trace, uint32_t *d_status, kvcm_stream_t stream);
 
+/* Host-only helper: h_order_out[i] = the number of the trace replayed i-th when a trace file's traces are put in
+ * timestamp order the way OptimizerLoader::LoadTrace does it - std::sort by timestamp
+ * (kv_cache_manager/optimizer/trace_converter/trace_util.cc:6-8,42-45), which is not stable, so traces of equal
+ * timestamps come out in the standard library's order.  The same routine runs here, so a replay of a file with
+ * repeated timestamps visits the traces in the reference's order. */
+KVCM_API int32_t kvcm_b200_trace_replay_order(const int64_t *h_timestamps, int64_t n_traces, int64_t *h_order_out);
+
 /* Trace replay for callers that cannot allocate device memory.  (No counterpart in the reference: it
  * exists for how this library gets embedded, not for a reference interface.)
  *

@@ -153,6 +153,7 @@ SIGNATURES = {
     "kvcm_b200_selftest_partial_sort": [_vp, _vp, _u32, _u32],
     "kvcm_b200_replay_random_lru": [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _vp, _i32, _i32, _i32, ctypes.c_double,
                                     _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+    "kvcm_b200_trace_replay_order": [_vp, _i64, _vp],
     "kvcm_b200_replay_noalloc": [_vp, _vp, _vp, _vp, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _vp],
 }
 

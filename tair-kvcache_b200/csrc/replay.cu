@@ -16,6 +16,9 @@
 // workspace, 16-byte slots, at least twice as many slots as keys.
 #include <mutex>
 
+#include <algorithm>
+#include <vector>
+
 #include "kvcm_common.cuh"
 
 // Scratch of kvcm_b200_replay_noalloc: a fixed table that lives in the library's device image.
@@ -241,6 +244,24 @@ int32_t kvcm_b200_replay_noalloc(const int64_t *d_keys, const int64_t *d_key_off
     return kvcm_b200_replay(d_keys, d_key_off, d_trace_type, d_mask_off, nullptr, n_traces, n_keys_total, scratch,
                             KVCM_B200_REPLAY_NOALLOC_SCRATCH_BYTES, d_ext_hit, d_int_hit, d_written, d_cache_blocks,
                             d_status, stream);
+}
+
+// Host-only: the order in which OptimizerLoader::LoadTrace replays the traces of a file.  It sorts them by timestamp
+// with std::sort (TraceTimeSorter::SortTracesByTimestamp, kv_cache_manager/optimizer/trace_converter/
+// trace_util.cc:6-8,42-45), which is not stable: traces of one timestamp come out in whatever order the standard
+// library's introsort leaves them, and since replay order decides hits and evictions that order is part of the
+// result.  So the same routine is called here, on trace numbers compared by their timestamps - the sequence of
+// comparisons and moves does not depend on what the elements are.
+int32_t kvcm_b200_trace_replay_order(const int64_t *h_timestamps, int64_t n_traces, int64_t *h_order_out) {
+    if (n_traces < 0) return KVCM_EC_BADARGS;
+    if (n_traces == 0) return KVCM_OK;
+    if (h_timestamps == nullptr || h_order_out == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    std::vector<int64_t> order(static_cast<size_t>(n_traces));
+    for (int64_t i = 0; i < n_traces; ++i) order[static_cast<size_t>(i)] = i;
+    std::sort(order.begin(), order.end(),
+              [h_timestamps](int64_t a, int64_t b) { return h_timestamps[a] < h_timestamps[b]; });
+    for (int64_t i = 0; i < n_traces; ++i) h_order_out[i] = order[static_cast<size_t>(i)];
+    return KVCM_OK;
 }
 
 }  // extern "C"

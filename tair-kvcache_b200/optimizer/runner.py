@@ -47,8 +47,10 @@ def replay_instance(traces: List[tr.Trace], device, rw_separation: bool = False,
                               for t in keep], dtype=np.int64)
     external_read = np.where(kind == tr.WRITE_CACHE, 0, read - internal_read)
 
+    order = np.array([t.order for t in keep], dtype=np.int64)
+
     def record(ext, inte, wr, size):
-        return dict(timestamp_us=ts, kind=kind, external_read_blocks=external_read,
+        return dict(timestamp_us=ts, kind=kind, order=order, external_read_blocks=external_read,
                     internal_read_blocks=internal_read, external_hit_blocks=ext, internal_hit_blocks=inte,
                     write_blocks=wr, current_cache_blocks=size)
 
@@ -78,14 +80,15 @@ def _kept(traces: List[tr.Trace], rw_separation: bool) -> List[tr.Trace]:
 
 def replay_group(traces: List[tr.Trace], instance_ids: Sequence[str], device, quota_blocks: int,
                  rw_separation: bool = False, evict_batch: int = 100, mode: int = 1,
-                 policy="lru", sample_rate=0.0) -> Dict[str, Dict[str, np.ndarray]]:
+                 policy="lru", sample_rate=0.0, timeline: Optional[list] = None) -> Dict[str, Dict[str, np.ndarray]]:
     """Replays the traces of the instances of ONE group that share a quota (every instance under `policy`, or one
     name per instance in the order of `instance_ids`: "lru" and "leaf_aware_lru" in any mix, or "random_lru"
     throughout with `sample_rate` one number or one per instance), in the order given (all instances together, by timestamp), and returns one record per
     instance as replay_instance does.  mode is the configuration's eviction_mode (1 group rough, 2 instance rough, 3 instance precise;
     kv_cache_manager/optimizer/manager/eviction_manager.cc:57-239).  current_cache_blocks is the usage of the
     trace's own instance; blocks_per_instance [record, instance] is the usage of every instance of the group at
-    that moment, in the order of `instance_ids` (ReadRecord::blocks_per_instance)."""
+    that moment, in the order of `instance_ids` (ReadRecord::blocks_per_instance).  timeline (optional list)
+    receives (instance_ids, replay position of every trace of the group, usage of every instance after it)."""
     index = {iid: j for j, iid in enumerate(instance_ids)}
     keep = [t for t in _kept(traces, rw_separation) if t.instance_id in index]
     keys, off, kind, mask, read = tr.to_csr(keep)
@@ -94,6 +97,7 @@ def replay_group(traces: List[tr.Trace], instance_ids: Sequence[str], device, qu
         d_keys = ApplyPrefixHashBatch(d_keys, d_off)
     inst = np.array([index[t.instance_id] for t in keep], dtype=np.int32)
     ts = np.array([t.timestamp_us for t in keep], dtype=np.int64)
+    order = np.array([t.order for t in keep], dtype=np.int64)
     bits = tr.mask_bits(keep, off)
     tr.require_no_repeats(keep, keys, off)
     res = RunTracesLruGroup(d_keys, d_off, torch.from_numpy(kind).to(device), torch.from_numpy(inst).to(device),
@@ -104,13 +108,15 @@ def replay_group(traces: List[tr.Trace], instance_ids: Sequence[str], device, qu
                             sample_rate=sample_rate)
     ext, inte, wr, size = (x[0].cpu().numpy() for x in res[:4])
     every = res.instance_blocks_per_trace[0].cpu().numpy()  # [trace, instance], instances in the order of instance_ids
+    if timeline is not None:
+        timeline.append((list(instance_ids), order, every))
     internal_read = np.array([tr.masked_count(t.block_mask, len(t.keys)) if t.kind == tr.GET_LOCATION else 0
                               for t in keep], dtype=np.int64)
     external_read = np.where(kind == tr.WRITE_CACHE, 0, read - internal_read)
     out = {}
     for iid, j in index.items():
         m = inst == j
-        out[iid] = dict(timestamp_us=ts[m], kind=kind[m], external_read_blocks=external_read[m],
+        out[iid] = dict(timestamp_us=ts[m], kind=kind[m], order=order[m], external_read_blocks=external_read[m],
                         internal_read_blocks=internal_read[m], external_hit_blocks=ext[m],
                         internal_hit_blocks=inte[m], write_blocks=wr[m], current_cache_blocks=size[m],
                         blocks_per_instance=every[m])
@@ -159,10 +165,10 @@ def tradeoff_curve(recs: Sequence[Dict[str, np.ndarray]]) -> np.ndarray:
 
 def export_hit_rates(path: str, rec: Dict[str, np.ndarray]) -> None:
     """`<instance>_hit_rates.csv` of HitAnalysis::ExportHitRates (result_analysis.cc:64-113): one line per read
-    record, same columns, separators and number formatting.  A record of an instance replayed alone holds that
-    instance's cached blocks in all three cached-blocks columns; a record of replay_group lists every instance of
-    the group in CachedBlocksPerInstance (in the order the group was given - the reference's order is that of an
-    unordered_map) and their sum in CachedBlocksAllInstance."""
+    record, same columns, separators and number formatting.  A record without blocks_per_instance (an instance
+    replayed alone through replay_instance) holds that instance's cached blocks in all three cached-blocks columns;
+    with it (run_trace_file, replay_group) CachedBlocksPerInstance lists every instance's usage, ';'-separated, and
+    CachedBlocksAllInstance their sum."""
     reads = rec["kind"] != tr.WRITE_CACHE
     acc_total = acc_ext = acc_int = 0
     with open(path, "w") as f:
@@ -198,39 +204,65 @@ def run_trace_file(trace_path: str, trace_type: str, output_dir: str, device=Non
     replayed on its own, except the instances of a group in `groups` (dicts with "instances" = the ids and "quota" =
     the shared quota in blocks, "policy" = the eviction policy of all of them or one per instance, "lru" when
     absent, "sample_rate" = the rates of "random_lru" instances, as parse_startup_config returns them), which are replayed together against their
-    shared quota under eviction `mode` (replay_group; in their CSV files CachedBlocksPerInstance lists the instances
-    of the group in the group's order - the reference lists every instance of the whole configuration there, in
-    the order of an unordered_map)."""
+    shared quota under eviction `mode` (replay_group).  As in the reference, the CachedBlocksPerInstance column of
+    every CSV lists the usage of EVERY instance of the configuration at the moment of the record, whichever group it
+    belongs to (ReadRecord::blocks_per_instance, kv_cache_manager/optimizer/manager/optimizer_runner.cc:116-124) -
+    here in the order of block_sizes (the configuration's order; instance ids sorted when block_sizes is not given),
+    in the reference in the order of an unordered_map.  Quota sweeps (a sequence of quotas per instance), which the
+    reference does not have, keep the instance's own usage in that column."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     traces = tr.load_traces(trace_path, trace_type, block_sizes)
     by_instance: Dict[str, List[tr.Trace]] = {}
     for t in traces:
         by_instance.setdefault(t.instance_id, []).append(t)
     os.makedirs(output_dir, exist_ok=True)
-    out = {}
+    out, names, timeline, swept = {}, {}, [], False
     for group in groups or []:
         recs = replay_group(traces, group["instances"], device, group["quota"], rw_separation, evict_batch, mode,
-                            group.get("policy", "lru"), group.get("sample_rate", 0.0))
+                            group.get("policy", "lru"), group.get("sample_rate", 0.0), timeline)
         for instance_id, r in recs.items():
             by_instance.pop(instance_id, None)
-            if (r["kind"] != tr.WRITE_CACHE).any():
-                export_hit_rates(os.path.join(output_dir, instance_id + "_hit_rates.csv"), r)
             out[instance_id] = r
+            names[instance_id] = [instance_id + "_hit_rates.csv"]
     for instance_id, ts in sorted(by_instance.items()):
         # a dict gives every instance its own quota (or quotas); instances it does not name are never evicted
         quota = quota_blocks.get(instance_id) if isinstance(quota_blocks, dict) else quota_blocks
         sweep = quota is not None and not np.isscalar(quota)
+        swept = swept or sweep
         # policy: one name for all instances, or a dict by instance ("lru" for instances it does not name)
         pol = policy.get(instance_id, "lru") if isinstance(policy, dict) else policy
         rate = sample_rate.get(instance_id, 0.0) if isinstance(sample_rate, dict) else sample_rate
         rec = replay_instance(ts, device, rw_separation, quota, evict_batch, precise, pol, rate)
-        for c, r in enumerate(rec if sweep else [rec]):
-            if (r["kind"] != tr.WRITE_CACHE).any():
-                name = "%s_quota%d_hit_rates.csv" % (instance_id, int(quota[c])) if sweep else \
-                    instance_id + "_hit_rates.csv"
-                export_hit_rates(os.path.join(output_dir, name), r)
         out[instance_id] = rec
+        names[instance_id] = ["%s_quota%d_hit_rates.csv" % (instance_id, int(q)) for q in quota] if sweep else \
+            [instance_id + "_hit_rates.csv"]
+        if not sweep:
+            timeline.append(([instance_id], rec["order"], np.asarray(rec["current_cache_blocks"])[:, None]))
+    every = list(block_sizes) if block_sizes else []
+    every += [i for i in sorted(out) if i not in every]
+    if len(every) > 1 and not swept:
+        _usage_of_every_instance(out, timeline, every)
+    for instance_id, rec in out.items():
+        for name, r in zip(names[instance_id], rec if isinstance(rec, list) else [rec]):
+            if (r["kind"] != tr.WRITE_CACHE).any():
+                export_hit_rates(os.path.join(output_dir, name), r)
     return out
+
+
+def _usage_of_every_instance(records: Dict[str, Dict[str, np.ndarray]], timeline, every: List[str]) -> None:
+    """Fills blocks_per_instance of every record with the usage of every instance of the configuration at that
+    moment: its own replay unit's row, and for the other units (instances replayed alone, groups replayed together)
+    the row of their latest trace that was replayed before it.  timeline: (instance ids of a unit, replay positions
+    of its traces, usage of its instances after each of them)."""
+    column = {iid: k for k, iid in enumerate(every)}
+    for rec in records.values():
+        rows = np.zeros((len(rec["order"]), len(every)), dtype=np.int64)
+        for members, order, usage in timeline:
+            at = np.searchsorted(order, rec["order"], side="right") - 1
+            seen = np.where(at[:, None] >= 0, np.asarray(usage)[np.maximum(at, 0)], 0)
+            for m, iid in enumerate(members):
+                rows[:, column[iid]] = seen[:, m]
+        rec["blocks_per_instance"] = rows
 
 
 EVICTION_MODE_UNSPECIFIED, EVICTION_MODE_GROUP_ROUGH, EVICTION_MODE_INSTANCE_ROUGH, EVICTION_MODE_INSTANCE_PRECISE = \

@@ -2,8 +2,8 @@
 
 Each reader follows one converter of the reference and yields `Trace` records; `load_traces` then sorts them by
 timestamp as OptimizerLoader::LoadTrace does (kv_cache_manager/optimizer/manager/optimizer_loader.cc:14-20).
-The reference sorts with std::sort, which is not stable; this reader's sort is stable, so the two agree whenever
-timestamps are distinct.
+The reference sorts with std::sort, which is not stable: the library's host helper runs the same routine, so traces
+of equal timestamps are replayed in the reference's order too (replay_order below).
 
   read_qwen_bailian      kv_cache_manager/optimizer/trace_converter/qwen_bailian_converter.cc:10-146
                          (every line is a dialog turn; hash_ids are per-block ids that still need ApplyPrefixHash)
@@ -17,6 +17,8 @@ from dataclasses import dataclass, field
 from typing import Dict, Iterable, List, Optional, Sequence, Union
 
 import numpy as np
+
+from .. import _cabi
 
 DIALOG_TURN, GET_LOCATION, WRITE_CACHE = 0, 1, 2  # = TRACE_* of the replay entry point
 
@@ -35,6 +37,7 @@ class Trace:
     needs_prefix_hash: bool = False                        # keys are raw per-block ids (Qwen-Bailian)
     input_len: int = 0
     output_len: int = 0
+    order: int = 0                                         # position in the file's replay order (load_traces)
 
     def replay_keys(self) -> List[int]:
         return self.total_keys if (self.kind == DIALOG_TURN and self.total_keys is not None) else self.keys
@@ -167,8 +170,22 @@ def load_traces(path: str, trace_type: str, block_sizes: Optional[Dict[str, int]
             traces = read_publisher_log(f, block_sizes or {})
         else:
             raise ValueError("unknown trace type %r" % trace_type)
-    traces.sort(key=lambda t: t.timestamp_us)
+    traces = [traces[i] for i in replay_order([t.timestamp_us for t in traces])]
+    for position, t in enumerate(traces):
+        t.order = position
     return traces
+
+
+def replay_order(timestamps) -> List[int]:
+    """The order OptimizerLoader::LoadTrace puts traces in: std::sort by timestamp
+    (kv_cache_manager/optimizer/trace_converter/trace_util.cc:6-8,42-45).  That sort is not stable, and which of
+    two traces of one timestamp is replayed first changes hits and evictions, so the library's host helper runs the
+    same standard-library routine instead of a stable sort."""
+    ts = np.ascontiguousarray(timestamps, dtype=np.int64)
+    order = np.empty(len(ts), dtype=np.int64)
+    if len(ts):
+        _cabi.call("kvcm_b200_trace_replay_order", ts.ctypes.data, len(ts), order.ctypes.data)
+    return order.tolist()
 
 
 def mask_offset(mask: BlockMask, n_keys: int) -> int:

@@ -61,38 +61,39 @@ def replay_cases():
     for policies, what in layouts:
         for mode in (1, 2, 3):
             for rw in (True, False):
-                keys, off, types, mask, ts = workload(rng, 90, rw)
+                keys, off, types, mask, ts = workload(rng, 70, rw)
                 k = len(policies)
                 inst = rng.integers(0, k, size=len(types)).astype(np.int32)
                 rates = [float(r) for r in rng.choice([0.1, 0.25, 0.5, 1.0], size=k)]
                 use_bits = bool(rng.random() < 0.3) and rw
                 bits = (rng.random(len(keys)) < 0.25).astype(np.uint8) if use_bits else None
                 batch = int(rng.integers(1, 9))
+                runs = []
                 for quota in (int(rng.integers(3, 25)), int(rng.integers(40, 200))):
                     r = ref.RefOptimizer([dict(quota_capacity=quota,
                                                instances=[(str(j), p, rates[j]) for j, p in enumerate(policies)])],
                                          evict_batch=batch, mode=mode)
                     ext, inte, wr, cached, every = r.run(keys, off, types, inst, None if use_bits else mask, bits, ts)
-                    cases.append(dict(name="%s, mode %d, %s, quota %d" % (what, mode, "read/write" if rw else "turns",
-                                                                        quota),
-                                      policies=policies, sample_rates=rates, mode=mode, evict_batch=batch, quota=quota,
-                                      keys=keys.tolist(), key_off=off.tolist(), types=types.tolist(),
-                                      instance=inst.tolist(), mask_off=None if use_bits else mask.tolist(),
-                                      mask_bits=bits.tolist() if use_bits else None, timestamps=ts.tolist(),
-                                      external_hit_blocks=ext.tolist(), internal_hit_blocks=inte.tolist(),
-                                      write_blocks=wr.tolist(), instance_blocks=cached.tolist(),
-                                      blocks_of_every_instance=every.tolist()))
+                    runs.append(dict(quota=quota, external_hit_blocks=ext.tolist(), internal_hit_blocks=inte.tolist(),
+                                     write_blocks=wr.tolist(), instance_blocks=cached.tolist(),
+                                     blocks_of_every_instance=every.tolist()))
+                cases.append(dict(name="%s, mode %d, %s" % (what, mode, "read/write" if rw else "turns"),
+                                  policies=policies, sample_rates=rates, mode=mode, evict_batch=batch,
+                                  keys=keys.tolist(), key_off=off.tolist(), types=types.tolist(),
+                                  instance=inst.tolist(), mask_off=None if use_bits else mask.tolist(),
+                                  mask_bits=bits.tolist() if use_bits else None, timestamps=ts.tolist(), runs=runs))
     # hierarchical eviction: the first tier's capacity x used_percentage is the quota
     keys, off, types, mask, ts = workload(rng, 120, False)
     r = ref.RefOptimizer([dict(quota_capacity=10 ** 9, hierarchical=True, tier_capacity=120, used_percentage=0.5,
                                instances=[("0", "leaf_aware_lru")])], evict_batch=4, mode=2)
     ext, inte, wr, cached, every = r.run(keys, off, types, None, mask, None, ts)
     cases.append(dict(name="hierarchical group: 0.5 of a first tier of 120 blocks", policies=["leaf_aware_lru"],
-                      sample_rates=[0.1], mode=2, evict_batch=4, quota=60, keys=keys.tolist(), key_off=off.tolist(),
+                      sample_rates=[0.1], mode=2, evict_batch=4, keys=keys.tolist(), key_off=off.tolist(),
                       types=types.tolist(), instance=[0] * len(types), mask_off=mask.tolist(), mask_bits=None,
-                      timestamps=ts.tolist(), external_hit_blocks=ext.tolist(), internal_hit_blocks=inte.tolist(),
-                      write_blocks=wr.tolist(), instance_blocks=cached.tolist(),
-                      blocks_of_every_instance=every.tolist(),
+                      timestamps=ts.tolist(),
+                      runs=[dict(quota=60, external_hit_blocks=ext.tolist(), internal_hit_blocks=inte.tolist(),
+                                 write_blocks=wr.tolist(), instance_blocks=cached.tolist(),
+                                 blocks_of_every_instance=every.tolist())],
                       startup_group=dict(quota_capacity=10 ** 9, used_percentage=0.5,
                                          hierarchical_eviction_enabled=True, storages=[dict(capacity=120)])))
     return cases
@@ -188,12 +189,18 @@ def csv_cases():
              ("qwen_bailian", [("instance", "random_lru")], 3, 10),
              ("publisher_log", [("inst_a", "lru"), ("inst_b", "lru")], 1, 40),
              ("publisher_log", [("inst_a", "leaf_aware_lru"), ("inst_b", "lru")], 2, 15)]
+    # the last two plans put the instances into groups of their own (usage of the other group's instance still
+    # shows in every record), one of them with an instance that no trace names
+    plans += [("publisher_log", [[("inst_a", "lru")], [("inst_b", "leaf_aware_lru")]], 3, 20),
+              ("optimizer_schema", [[("inst_a", "leaf_aware_lru"), ("idle", "lru")], [("inst_b", "random_lru")]], 1, 18)]
     for trace_type, instances, mode, quota in plans:
         with tempfile.TemporaryDirectory() as tmp:
             path = os.path.join(tmp, "trace.jsonl")
             with open(path, "w") as f:
                 f.write(files[trace_type])
-            config = ref.startup_config([dict(quota_capacity=quota, instances=[(i, p, 0.1) for i, p in instances])],
+            grouped = instances if isinstance(instances[0], list) else [instances]
+            config = ref.startup_config([dict(quota_capacity=quota, instances=[(i, p, 0.1) for i, p in members])
+                                         for members in grouped],
                                         evict_batch=3, mode=mode, trace_file_path=path, trace_type=trace_type,
                                         output_result_path=os.path.join(tmp, "out"))
             os.makedirs(os.path.join(tmp, "out"), exist_ok=True)
@@ -215,13 +222,15 @@ def main():
     with open(os.path.join(HERE, "optimizer_ref_kat.json"), "w") as f:
         json.dump({"generator": "tests/golden/make_optimizer_golden.py",
                    "source": "the reference's Optimizer compiled from its own sources (oracle/_ref)",
-                   "trace_types": {"dialog_turn": D, "get_location": G, "write_cache": W}, "cases": cases}, f)
+                   "trace_types": {"dialog_turn": D, "get_location": G, "write_cache": W}, "cases": cases}, f,
+                  separators=(",", ":"))
     csvs = csv_cases()
     with open(os.path.join(HERE, "optimizer_ref_csv.json"), "w") as f:
         json.dump({"generator": "tests/golden/make_optimizer_golden.py",
                    "source": "the reference's optimizer_main path compiled from its own sources (oracle/_ref)",
-                   "cases": csvs}, f)
-    print("%d replay cases, %d trace-file cases" % (len(cases), len(csvs)))
+                   "cases": csvs}, f, separators=(",", ":"))
+    print("%d replay workloads (%d runs), %d trace-file cases" % (len(cases), sum(len(c["runs"]) for c in cases),
+                                                                 len(csvs)))
 
 
 if __name__ == "__main__":
