@@ -1541,10 +1541,20 @@ def main_lru_reference(args):
     keys, ko = oracle.hash_blocks(toks, off, bs, threads=threads)
     quotas = _lru_quotas(int(ko[-1]), n_cfg)
 
+    from oracle import ref_optimizer
+    compiled = ref_optimizer.available()  # the reference's own Optimizer, compiled from its sources (oracle/_ref)
+    n_inst = max(1, args.instances)
+    inst = np.arange(n_req, dtype=np.int32) % n_inst
+
     def one(q):
-        if args.instances > 1:
-            return int(oracle.LruGroupReplay(q, args.instances, evict_batch=100, mode=1).run(
-                keys, ko, types, np.arange(n_req, dtype=np.int32) % args.instances)[0].sum())
+        if compiled:
+            r = ref_optimizer.RefOptimizer([dict(quota_capacity=q, instances=[(str(j), args.policy)
+                                                                              for j in range(n_inst)])],
+                                           evict_batch=100, mode=1 if n_inst > 1 else 2)
+            return int(r.run(keys, ko, types, inst)[0].sum())
+        if n_inst > 1:
+            return int(oracle.LruGroupReplay(q, n_inst, evict_batch=100, mode=1, policy=args.policy).run(
+                keys, ko, types, inst)[0].sum())
         return int(oracle.LruReplay(q, evict_batch=100, precise=False, policy=args.policy).run(keys, ko, types)[0].sum())
 
     with ThreadPoolExecutor(max_workers=threads) as pool:
@@ -1557,10 +1567,12 @@ def main_lru_reference(args):
                       "value": value,
                       "unit": "request-replays/s", "n_gpus": args.gpus, "steps": 1, "warmup": 0,
                       "higher_is_better": True, "dtype": "int64", "data": "synthetic",
-                      "config": {"workload": "CPU restatement (hash + radix tree with %s eviction, one quota point "
-                                             "per thread) on a bounded sample" % args.policy},
-                      "cpu_baseline": {"value": value, "unit": "request-replays/s", "cores": threads, "kind": "port",
-                                       "sample": sample},
+                      "config": {"workload": "%s (hash + radix tree with %s eviction, one quota point per thread) on "
+                                             "a bounded sample" % ("the reference's Optimizer compiled from its own "
+                                                                   "sources" if compiled else "CPU restatement",
+                                                                   args.policy)},
+                      "cpu_baseline": {"value": value, "unit": "request-replays/s", "cores": threads,
+                                       "kind": "reference" if compiled else "port", "sample": sample},
                       "e2e": {"value": value, "unit": "request-replays/s", "h2d_bytes_per_step": 0,
                               "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
 

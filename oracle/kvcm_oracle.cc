@@ -635,10 +635,12 @@ void kvcm_oracle_replay_run(void *h, const int64_t *keys, const int64_t *key_off
 // The tree is kept compressed and split exactly as the reference does, so that this oracle does not
 // assume what the GPU replay assumes (that only per-key residency matters).
 // Pins: the recency-order cases of kv_cache_manager/optimizer/test/lru_eviction_policy_test.cc:44-146
-// restated as traces, and the eviction-free replay above when the quota is never reached.  The
-// reference records no end-to-end numbers for tree clean-up under eviction: parity unpinned there.
-// The reference has no test of leaf_aware_lru at all: parity unpinned for that policy; the cases in
-// tests/test_oracle.py were worked out by hand from the cited source lines.
+// restated as traces, the eviction-free replay above when the quota is never reached, and - for everything the
+// reference's tests leave out (tree clean-up under eviction, leaf_aware_lru, random_lru, groups of instances) -
+// the per-trace records of the reference's own Optimizer, compiled from its sources (ref_optimizer_driver.cc) and
+// recorded in tests/golden/optimizer_ref_kat.json; where that library is present the two are also compared live
+// (tests/test_optimizer_reference_pins.py).  The cases in tests/test_oracle.py were worked out by hand from the
+// cited source lines.
 
 namespace {
 

@@ -1,8 +1,8 @@
 """Parity of the GPU quota sweep under the "random_lru" eviction policy with the oracle's sequential radix-tree
 replay, whose evictions call std::partial_sort the way the reference does
-(kv_cache_manager/optimizer/eviction_policy/random_lru.cc:38-82).  The reference has no test of this policy:
-beyond the standard library's own sort and the generator's seed, parity rests on reading the source ("parity
-unpinned")."""
+(kv_cache_manager/optimizer/eviction_policy/random_lru.cc:38-82).  The reference has no test of this policy; the
+oracle is pinned to records of the reference's own Optimizer (tests/test_optimizer_reference_pins.py), and
+tests/test_gpu_optimizer_pins.py replays those records on the GPU."""
 import numpy as np
 import pytest
 import torch
