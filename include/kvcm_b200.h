@@ -365,7 +365,10 @@ KVCM_API int32_t kvcm_b200_index_rehash(kvcm_b200_index_t *index, void *d_worksp
  * d_results[i]: KVCM_OK; KVCM_EC_NOENT when the key is absent or has no location of that class
  * (BlockCacheLocationsMeta::UpdateLocationStatus / GetLocationStatus, kv_cache_manager/manager/cache_location.cc:60-82);
  * KVCM_EC_MISMATCH when the status differs from the expected one; KVCM_EC_BADARGS for a malformed task.
- * A key whose last location is deleted leaves the index, as MetaIndexer::MA_DELETE does.  Several tasks of
+ * A key whose last location is deleted by KVCM_STATUS_DELETE leaves the index, as MetaIndexer::MA_DELETE does; so does
+ * a key whose map is ALREADY empty (left behind by KVCM_STATUS_DELETE_KEEP_KEY) when a KVCM_STATUS_DELETE task names
+ * it, while the task itself answers KVCM_EC_NOENT: the reference's compare-and-delete drops a key with an empty map
+ * whatever its tasks did (meta_searcher.cc:689-692).  Several tasks of
  * one call may name the same key; they are applied one after the other in an unspecified order.  A key
  * with more than one location in one class cannot be represented: keep such a key's map on the host and
  * write its word with kvcm_b200_index_upsert.  The _sharded form touches only the keys this shard owns

@@ -310,6 +310,9 @@ void kvcm_oracle_index_update_status(void *h, const int64_t *keys, int64_t n, co
         while (at < locs.size() && locs[at].type != types[i]) ++at;
         if (at == locs.size()) {
             results[i] = 2;
+            // compare-and-delete drops a key whose map is empty whatever its tasks did (:689-692): a key that an
+            // earlier BatchDeleteLocation left behind empty goes here, with the task answering EC_NOENT
+            if (new_status[i] == -1 && locs.empty()) ix->table.erase(it);
             continue;
         }
         if (expected[i] >= 0 && locs[at].status != expected[i]) {

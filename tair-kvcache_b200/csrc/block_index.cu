@@ -377,6 +377,9 @@ __device__ __forceinline__ uint64_t ApplyStatusTask(uint64_t word, uint32_t task
     const uint32_t field = word != 0 ? StatusField(word, cls) : 0;
     if (field == 0) {
         *code = KVCM_EC_NOENT;  // no such key, or no location of this class in its map
+        // compare-and-delete drops a key whose map is empty whatever its tasks did (meta_searcher.cc:689-692): a key
+        // that BatchDeleteLocation left behind empty goes here, and the task still answers EC_NOENT
+        if (word != 0 && next == KVCM_STATUS_DELETE && (word & kLocationBits) == 0) return 0;
         return word;
     }
     if (expected != KVCM_STATUS_ANY && field - 1 != expected) {
@@ -427,7 +430,7 @@ __global__ void UpdateStatusKernel(IndexView ix, const int64_t *__restrict__ key
         unsigned long long seen = *reinterpret_cast<volatile unsigned long long *>(word_at);
         for (int turn = 0; turn < 1024; ++turn) {
             const uint64_t next = ApplyStatusTask(seen, task, &code);
-            if (code != KVCM_OK || (next == 0 && seen == 0)) break;
+            if (next == seen) break;  // nothing to write: a refusal, or a task that leaves the word as it is
             const unsigned long long was = atomicCAS(word_at, seen, next);
             if (was == seen) {
                 if (next == 0) {  // the key's last location is gone: the key goes too
@@ -443,7 +446,7 @@ __global__ void UpdateStatusKernel(IndexView ix, const int64_t *__restrict__ key
                 break;
             }
             seen = was;
-            code = KVCM_EC_ERROR;  // stays only if the turns run out
+            if (turn == 1023) code = KVCM_EC_ERROR;  // the turns ran out
         }
     }
     results[i] = code;

@@ -76,6 +76,22 @@ def test_location_status_cases_of_the_reference_tests():
         assert ix.stats()[1] == len(live), case["name"]
 
 
+def test_compare_and_delete_drops_a_key_left_behind_empty():
+    """kv_cache_manager/manager/meta_searcher.cc:689-692: compare-and-delete removes a key whose location map is
+    empty whatever its tasks did; BatchDeleteLocation leaves such keys behind (:783-786)."""
+    ix = BlockIndex(64)
+    keys = torch.tensor([7, 8], dtype=torch.int64, device=DEV)
+    ix.upsert(keys, torch.tensor([encode_locations([(3, 4)]), encode_locations([(3, 4), (2, 1)])], dtype=torch.int64,
+                                 device=DEV))
+    keep = _tasks([4, 4], [-1, -1], [-2, -2])
+    assert ix.update_status(keys, keep).cpu().tolist() == [_cabi.KVCM_OK, _cabi.KVCM_OK]
+    assert [_decode(w) for w in ix.lookup(keys).cpu().numpy()] == [[], [(2, 1)]] and ix.stats()[1] == 2
+    cad = _tasks([4, 4], [3, 3], [-1, -1])
+    assert ix.update_status(keys, cad).cpu().tolist() == [_cabi.KVCM_EC_NOENT, _cabi.KVCM_EC_NOENT]
+    assert [_decode(w) for w in ix.lookup(keys).cpu().numpy()] == [None, [(2, 1)]] and ix.stats()[1] == 1
+    assert ix.update_status(keys[:1], keep[:1]).cpu().tolist() == [_cabi.KVCM_OK]
+
+
 def test_uniform_task_and_bad_tasks():
     ix = BlockIndex(64)
     keys = torch.arange(10, 20, dtype=torch.int64, device=DEV)

@@ -1,0 +1,104 @@
+"""The oracle's block index, matchers and location-status transitions against the REFERENCE's own MetaSearcher.
+
+oracle/_ref/libkvcm_ref_searcher.so is the reference's MetaSearcher over its MetaIndexer and local meta backend,
+compiled from the reference's source files in place (oracle/Makefile, target ref_searcher; oracle/
+ref_searcher_driver.cc wraps it).  The known-answer tables of the reference's own tests pin the oracle everywhere
+(tests/golden/match_kat.json, status_kat.json); here, where that library is present (a container that holds the
+reference tree), the two are also compared live on random location maps, masks, weights and task batches.  No GPU:
+the GPU kernels are compared with the same oracle in tests/test_gpu_hash_match.py and tests/test_gpu_index_write.py.
+"""
+import numpy as np
+import pytest
+
+from oracle import kvcm_oracle as oracle
+from oracle import ref_searcher as ref
+
+pytestmark = pytest.mark.skipif(not ref.available(),
+                                reason="oracle/_ref/libkvcm_ref_searcher.so not built (reference tree absent)")
+
+STATUSES = (oracle.CLS_NEW, oracle.CLS_WRITING, oracle.CLS_SERVING, oracle.CLS_DELETING)
+
+
+def _random_world(rng, n_keys, fill=0.12):
+    """The same random location maps in the reference's index and in the oracle's: per key, each storage type at
+    most once, in a random status."""
+    universe = rng.integers(-(1 << 62), 1 << 62, size=n_keys + n_keys // 4, dtype=np.int64)
+    locs = {int(k): [] for k in universe[:n_keys]}
+    r, ox = ref.RefSearcher(), oracle.Index()
+    for ty in range(5):
+        for st in STATUSES:
+            ks = [k for k in locs if rng.random() < fill and all(t != ty for _, t in locs[k])]
+            if ks:
+                r.add(ks, ty, st)
+                for k in ks:
+                    locs[k].append((st, ty))
+    held = [k for k in locs if locs[k]]  # the reference only knows keys that got a location
+    ox.put(held, [locs[k] for k in held])
+    return universe, {k: locs[k] for k in held}, r, ox
+
+
+def test_matchers_on_random_location_maps():
+    rng = np.random.default_rng(2024)
+    universe, locs, r, ox = _random_world(rng, 1200)
+    serving = [k for k in locs if any(s == oracle.CLS_SERVING for s, _ in locs[k])]
+    hits = windows = 0
+    for weights in (None, (1, 3, 0, 3, 5), (0, 0, 0, 0, 7)):
+        ow = oracle.DEFAULT_WEIGHTS if weights is None else weights
+        for _ in range(150):
+            n = int(rng.integers(0, 40))
+            q = rng.choice(universe, size=n)
+            likely = rng.random(n) < 0.85
+            q[likely] = rng.choice(serving, size=int(likely.sum()))
+            for mask in (None, int(rng.integers(0, n + 2)), rng.random(n) < 0.3):
+                want = r.prefix_match(q, mask, weights)
+                got = ox.prefix_match(q, mask.tolist() if isinstance(mask, np.ndarray) else mask, ow)
+                assert got == want, (mask, weights)
+                hits += want > 0
+            for sw in (1, 3, 8):
+                if n < sw:
+                    continue  # the reference asserts here; the oracle and the kernels answer -2
+                base, count = r.sw_match(q, sw, weights)
+                ec, got = ox.sw_match(q, sw, ow)
+                assert ec == 0 and got == base and count == (sw if base >= 0 else 0), (sw, weights)
+                windows += base >= 0
+            servable, nonempty = r.batch_get(q, weights)
+            flags = ox.batch_get(q, ow)
+            assert np.array_equal(servable, flags & 1) and np.array_equal(nonempty, (flags >> 2) & 1)
+    assert hits > 300 and windows > 100
+
+
+def test_status_transitions_on_random_task_batches():
+    """BatchUpdateLocationStatus / BatchCASLocationStatus / BatchCADLocationStatus / BatchDeleteLocation
+    (kv_cache_manager/manager/meta_searcher.cc:410-820): the per-task error codes, and what the matchers see after."""
+    rng = np.random.default_rng(2025)
+    universe, locs, r, ox = _random_world(rng, 600, fill=0.2)
+    known = np.array(sorted(locs), dtype=np.int64)
+    seen = set()
+    for round_ in range(60):
+        op = int(rng.integers(0, 4))
+        n = int(rng.integers(1, 40))
+        keys = rng.choice(known, size=n, replace=False)  # one task per key and call
+        if rng.random() < 0.3:  # some keys the index has never held
+            keys[: n // 4] = rng.integers(1 << 62, (1 << 62) + 1000, size=n // 4)
+        types = rng.integers(0, 5, size=n).astype(np.int32)
+        expected = rng.choice(STATUSES, size=n).astype(np.int32)
+        new = rng.choice(STATUSES, size=n).astype(np.int32)
+        rc, want = r.status(op, keys, types, expected, new)
+        if op == ref.OP_UPDATE:
+            got = ox.update_status(keys, types, -1, new)
+        elif op == ref.OP_CAS:
+            got = ox.update_status(keys, types, expected, new)
+        elif op == ref.OP_CAD:
+            got = ox.update_status(keys, types, expected, -1)
+        else:
+            got = ox.update_status(keys, types, -1, -2)
+        assert np.array_equal(want, got), (round_, op, want.tolist(), got.tolist())
+        seen.update((op, int(c)) for c in want)
+        probe = rng.choice(known, size=64)
+        servable, nonempty = r.batch_get(probe)
+        flags = ox.batch_get(probe)
+        assert np.array_equal(servable, flags & 1) and np.array_equal(nonempty, (flags >> 2) & 1), (round_, op)
+    # every operation both succeeded and failed somewhere; compare-and-set / -delete also met a wrong status
+    for op in range(4):
+        assert (op, 0) in seen
+    assert (ref.OP_CAS, 16) in seen and (ref.OP_CAD, 16) in seen and (ref.OP_UPDATE, 2) in seen

@@ -389,6 +389,19 @@ def test_leaf_aware_group_of_two_instances_by_hand():
         assert ext.tolist() == [0, 0, 0, 3, 0, 0, 0, 2, 0] and final.tolist() == [4, 1]
 
 
+def test_compare_and_delete_drops_a_key_left_behind_empty():
+    # kv_cache_manager/manager/meta_searcher.cc:689-692: compare-and-delete removes a key whose location map is empty
+    # whatever its tasks did.  BatchDeleteLocation leaves such keys behind (:783-786).  Found by comparing with the
+    # reference's own MetaSearcher compiled in place (tests/test_matchers_reference_pins.py).
+    ix = oracle.Index()
+    ix.put([7, 8], [[(oracle.CLS_SERVING, 4)], [(oracle.CLS_SERVING, 4), (oracle.CLS_WRITING, 1)]])
+    assert ix.update_status([7, 8], 4, -1, -2).tolist() == [0, 0]      # BatchDeleteLocation: 7 stays, empty
+    assert ix.get(7) == [] and ix.get(8) == [(oracle.CLS_WRITING, 1)]
+    assert ix.update_status([7, 8], 4, oracle.CLS_SERVING, -1).tolist() == [2, 2]  # no such location in either
+    assert ix.get(7) is None and ix.get(8) == [(oracle.CLS_WRITING, 1)]  # the empty key is gone, the other is not
+    assert ix.update_status([7], 4, -1, -2).tolist() == [0]            # and a delete of an absent key is EC_OK
+
+
 def test_location_status_cases_of_the_reference_tests():
     """Update / compare-and-set / compare-and-delete / delete of location statuses, replayed from the tables of
     kv_cache_manager/manager/test/meta_searcher_test.cc (tests/golden/status_kat.json)."""
