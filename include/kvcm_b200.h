@@ -777,6 +777,14 @@ KVCM_API int32_t kvcm_b200_replay_leaf_lru_group(
  * timestamps come out in the standard library's order.  The same routine runs here, so a replay of a file with
  * repeated timestamps visits the traces in the reference's order. */
 KVCM_API int32_t kvcm_b200_trace_replay_order(const int64_t *h_timestamps, int64_t n_traces, int64_t *h_order_out);
+/* Host-only helper: the order in which a std::unordered_map<std::string, ...> iterates after n_ops operations -
+ * operation i names key h_keys[h_key_off[i] .. h_key_off[i+1]) and either erases it (h_erase[i] != 0) or assigns it
+ * the value i.  h_order_out receives the values left in iteration order, *h_n_out their number.  The reference's
+ * publisher-log reader appends its unfinished writes in that order
+ * (kv_cache_manager/optimizer/trace_converter/publisher_log_converter.cc:207-219); the same container runs here. */
+KVCM_API int32_t kvcm_b200_string_map_iteration_order(const char *h_keys, const int64_t *h_key_off,
+                                                      const uint8_t *h_erase, int64_t n_ops, int64_t *h_order_out,
+                                                      int64_t *h_n_out);
 
 /* Trace replay for callers that cannot allocate device memory.  (No counterpart in the reference: it
  * exists for how this library gets embedded, not for a reference interface.)

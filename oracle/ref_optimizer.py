@@ -116,6 +116,26 @@ class RefOptimizer:
         return ext, inte, wr, cached, every
 
 
+def load_traces(config):
+    """The traces the reference's loader makes of the configuration's trace file, in its replay order: a list of
+    (kind, dict) with kind 0 dialog turn, 1 GetLocation, 2 WriteCache and the trace's own JSON as a dict."""
+    path = config if isinstance(config, str) else _write_config(config)
+    out = tempfile.NamedTemporaryFile("w", suffix=".traces", delete=False)
+    out.close()
+    try:
+        lib().kvcm_ref_optimizer_dump_traces.restype = ctypes.c_int64
+        n = lib().kvcm_ref_optimizer_dump_traces(path.encode(), out.name.encode())
+        if n < 0:
+            raise RuntimeError("the reference's loader failed")
+        with open(out.name) as f:
+            rows = [line.split(" ", 1) for line in f.read().splitlines()]
+    finally:
+        os.unlink(out.name)
+        if not isinstance(config, str):
+            os.unlink(path)
+    return [(int(kind), json.loads(doc)) for kind, doc in rows]
+
+
 def optimizer_main(config):
     """What the reference's `optimizer_main <config>` does: load the trace file the configuration names, replay it,
     write `<instance>_hit_rates.csv` per instance under output_result_path.  config: a dict or a path."""

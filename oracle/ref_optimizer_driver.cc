@@ -18,12 +18,14 @@
 #include <cstdint>
 #include <cstdlib>
 #include <cstring>
+#include <fstream>
 #include <memory>
 #include <string>
 #include <vector>
 
 #include "kv_cache_manager/common/logger.h"
 #include "kv_cache_manager/optimizer/config/optimizer_config_loader.h"
+#include "kv_cache_manager/optimizer/manager/optimizer_loader.h"
 #include "kv_cache_manager/optimizer/manager/optimizer_manager.h"
 
 namespace kv_cache_manager {
@@ -131,6 +133,29 @@ int32_t kvcm_ref_optimizer_run(void *handle, const char *const *instance_ids, in
         }
     }
     return 0;
+}
+
+// The traces OptimizerLoader::LoadTrace makes of the trace file the configuration names, in replay order, one line
+// per trace into out_path: the kind (0 dialog turn, 1 GetLocation, 2 WriteCache), a space, the trace's own JSON.
+// Returns the number of traces, -1 on failure.
+int64_t kvcm_ref_optimizer_dump_traces(const char *config_path, const char *out_path) {
+    using namespace kv_cache_manager;
+    OptimizerConfigLoader loader;
+    if (config_path == nullptr || out_path == nullptr || !loader.Load(config_path)) return -1;
+    OptimizerConfig config = loader.get_config();
+    auto traces = OptimizerLoader::LoadTrace(config);
+    std::ofstream out(out_path);
+    if (!out.is_open()) return -1;
+    for (const auto &trace : traces) {
+        int kind = 2;
+        if (std::dynamic_pointer_cast<DialogTurnSchemaTrace>(trace)) {
+            kind = 0;
+        } else if (std::dynamic_pointer_cast<GetLocationSchemaTrace>(trace)) {
+            kind = 1;
+        }
+        out << kind << ' ' << trace->ToJsonString() << '\n';
+    }
+    return static_cast<int64_t>(traces.size());
 }
 
 // What `optimizer_main <config>` does after loading its configuration (kv_cache_manager/optimizer/main.cc): load

@@ -154,6 +154,7 @@ SIGNATURES = {
     "kvcm_b200_replay_random_lru": [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _vp, _i32, _i32, _i32, ctypes.c_double,
                                     _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "kvcm_b200_trace_replay_order": [_vp, _i64, _vp],
+    "kvcm_b200_string_map_iteration_order": [_vp, _vp, _vp, _i64, _vp, _vp],
     "kvcm_b200_replay_noalloc": [_vp, _vp, _vp, _vp, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _vp],
 }
 

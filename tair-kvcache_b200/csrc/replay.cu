@@ -17,6 +17,8 @@
 #include <mutex>
 
 #include <algorithm>
+#include <string>
+#include <unordered_map>
 #include <vector>
 
 #include "kvcm_common.cuh"
@@ -261,6 +263,37 @@ int32_t kvcm_b200_trace_replay_order(const int64_t *h_timestamps, int64_t n_trac
     std::sort(order.begin(), order.end(),
               [h_timestamps](int64_t a, int64_t b) { return h_timestamps[a] < h_timestamps[b]; });
     for (int64_t i = 0; i < n_traces; ++i) h_order_out[i] = order[static_cast<size_t>(i)];
+    return KVCM_OK;
+}
+
+// Host-only: the order in which a std::unordered_map<std::string, ...> hands back its entries after a sequence of
+// assignments (map[key] = ...) and erasures.  The reference's publisher-log reader keeps the writes that were
+// started but not finished in such a map and appends what is left in ITERATION order
+// (kv_cache_manager/optimizer/trace_converter/publisher_log_converter.cc:207-219, publisher_log_converter.h:50);
+// that order is the standard library's (hash function, bucket growth, node list), and - through the unstable sort
+// that follows - it decides the replay order of traces with equal timestamps.  So the same container runs here on
+// the same operations.  Operation i names key h_keys[h_key_off[i] .. h_key_off[i+1]); h_erase[i] != 0 erases it,
+// else it is assigned the value i.  h_order_out receives the values left, in iteration order; *h_n_out how many.
+int32_t kvcm_b200_string_map_iteration_order(const char *h_keys, const int64_t *h_key_off, const uint8_t *h_erase,
+                                             int64_t n_ops, int64_t *h_order_out, int64_t *h_n_out) {
+    if (n_ops < 0) return KVCM_EC_BADARGS;
+    if (h_n_out == nullptr || (n_ops > 0 && (h_key_off == nullptr || h_erase == nullptr || h_order_out == nullptr))) {
+        return KVCM_ER_INVALID_ADDRESS;
+    }
+    std::unordered_map<std::string, int64_t> map;
+    for (int64_t i = 0; i < n_ops; ++i) {
+        const int64_t len = h_key_off[i + 1] - h_key_off[i];
+        if (len < 0 || (len > 0 && h_keys == nullptr)) return KVCM_EC_BADARGS;
+        const std::string key(len > 0 ? h_keys + h_key_off[i] : "", static_cast<size_t>(len));
+        if (h_erase[i] != 0) {
+            map.erase(key);
+        } else {
+            map[key] = i;
+        }
+    }
+    int64_t n = 0;
+    for (const auto &entry : map) h_order_out[n++] = entry.second;
+    *h_n_out = n;
     return KVCM_OK;
 }
 

@@ -102,6 +102,7 @@ def read_publisher_log(lines: Iterable[str], block_sizes: Dict[str, int]) -> Lis
     traces: List[Trace] = []
     pending_gets: List[Trace] = []
     pending_writes: Dict[str, Trace] = {}  # write_session_id -> write trace waiting for its FinishWriteCache
+    session_ops: List[tuple] = []          # what happened to that map, in order: (session id, erased?, trace)
     for doc in _json_lines(lines):
         kind = doc.get("type")
         if not isinstance(kind, str):
@@ -123,6 +124,7 @@ def read_publisher_log(lines: Iterable[str], block_sizes: Dict[str, int]) -> Lis
             session = doc.get("write_session_id")
             if isinstance(session, str) and session:
                 pending_writes[session] = w
+                session_ops.append((session, False, w))
             # the latest earlier GetCacheLocation of the same instance whose keys but the last open the write's keys
             # becomes a dialog turn over the written keys (publisher_log_converter.cc:226-256)
             for i in range(len(pending_gets) - 1, -1, -1):
@@ -146,10 +148,13 @@ def read_publisher_log(lines: Iterable[str], block_sizes: Dict[str, int]) -> Lis
             if "source" in doc and (source != w.instance_id or source not in block_sizes):
                 continue
             del pending_writes[session]
+            session_ops.append((session, True, None))
             if isinstance(doc.get("trigger_time_us"), int):
                 w.timestamp_us = doc["trigger_time_us"]
             traces.append(w)
-    for w in pending_writes.values():  # never finished: assumed to end 100 ms after it started (:207-219)
+    # never finished: assumed to end 100 ms after it started, appended in the iteration order of the reference's
+    # std::unordered_map of sessions (:207-219) - which matters because the sort that follows is not stable
+    for w in _in_map_order(session_ops):
         w.timestamp_us += 100000
         traces.append(w)
     for g in pending_gets:  # never followed by a write: replayed as a dialog turn over its own keys (:258-267)
@@ -226,6 +231,23 @@ def masked_count(mask: BlockMask, n_keys: int) -> int:
     if isinstance(mask, int):
         return min(mask, n_keys)
     return int(sum(1 for x in list(mask)[:n_keys] if x))
+
+
+def _in_map_order(session_ops) -> List[Trace]:
+    """The traces still in the reference's session map after session_ops, in that map's iteration order."""
+    if not session_ops:
+        return []
+    names = [name.encode() for name, _, _ in session_ops]
+    off = np.zeros(len(names) + 1, dtype=np.int64)
+    np.cumsum([len(b) for b in names], out=off[1:])
+    blob = b"".join(names) + b"\0"
+    erase = np.array([1 if erased else 0 for _, erased, _ in session_ops], dtype=np.uint8)
+    order = np.empty(len(names), dtype=np.int64)
+    left = np.zeros(1, dtype=np.int64)
+    import ctypes
+    _cabi.call("kvcm_b200_string_map_iteration_order", ctypes.c_char_p(blob), off.ctypes.data, erase.ctypes.data,
+               len(names), order.ctypes.data, left.ctypes.data)
+    return [session_ops[int(i)][2] for i in order[:int(left[0])]]
 
 
 def to_csr(traces: Sequence[Trace]):

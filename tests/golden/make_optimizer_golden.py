@@ -99,8 +99,8 @@ def replay_cases():
     return cases
 
 
-def trace_files(rng):
-    """One small trace file per input format the reference reads, as text."""
+def trace_files(rng, scale=1):
+    """One small trace file per input format the reference reads, as text (scale: times as many traces)."""
     files = {}
     bs = 16
 
@@ -121,7 +121,7 @@ def trace_files(rng):
     # dialog turns are replayed, the read and the write line in between are not (this format runs without read/write
     # separation, kv_cache_manager/optimizer/trace_converter/converter_factory.cc:17-29)
     lines, now = [], 1_700_000_000_000_000
-    for t, total in enumerate(chained(70)):
+    for t, total in enumerate(chained(70 * scale)):
         now += int(rng.integers(0, 3))
         n_in = int(rng.integers(0, len(total) + 1))
         inst = "inst_a" if t % 3 else "inst_b"
@@ -140,8 +140,8 @@ def trace_files(rng):
 
     # qwen_bailian: chat turns with hash_ids per block (trace_converter/qwen_bailian_converter.cc)
     lines, chats = [], {}
-    for t in range(60):
-        chat = int(rng.integers(0, 8))
+    for t in range(60 * scale):
+        chat = int(rng.integers(0, 8 * scale))
         ids = chats.get(chat, []) + rng.integers(1, 1 << 30, size=int(rng.integers(1, 6))).tolist()
         chats[chat] = ids
         lines.append(json.dumps({"chat_id": chat, "parent_chat_id": -1, "timestamp": 1000.0 + 0.5 * (t // 2),
@@ -152,7 +152,7 @@ def trace_files(rng):
     # publisher_log: the events the manager publishes (trace_converter/publisher_log_converter.cc:34-267): reads,
     # writes opened and finished (or never finished), an event of an instance the configuration does not know
     lines, now, session = [], 1_700_000_000_000_000, 0
-    for t, total in enumerate(chained(60)):
+    for t, total in enumerate(chained(60 * scale)):
         inst = "inst_a" if t % 2 else "inst_b"
         now += int(rng.integers(1, 50))
         n_in = int(rng.integers(1, len(total) + 1))

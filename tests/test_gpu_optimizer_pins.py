@@ -78,3 +78,35 @@ def test_trace_files_give_the_reference_csv_files(tmp_path):
         config["output_result_path"] = str(work / "out")
         runner.run_startup_config(config, device=DEV)
         compare_with_reference_files(case, str(work / "out"))
+
+
+@pytest.mark.parametrize("trace_type", ["optimizer_schema", "qwen_bailian", "publisher_log"])
+def test_larger_trace_files_against_the_compiled_reference(tmp_path, trace_type):
+    """Where the reference's Optimizer is present as a built library (it travels with the other built files), a
+    few thousand traces per format go through its optimizer_main path and through the GPU runner: same CSV files."""
+    from oracle import ref_optimizer as ref
+    if not ref.available():
+        pytest.skip("oracle/_ref/libkvcm_ref_optimizer.so not built")
+    from golden.make_optimizer_golden import trace_files
+    rng = np.random.default_rng(0xB2000009)
+    text = trace_files(rng, scale=40)[trace_type]
+    (tmp_path / "trace.jsonl").write_text(text)
+    plans = {"optimizer_schema": ([[("inst_a", "leaf_aware_lru"), ("idle", "lru")], [("inst_b", "random_lru")]], 1, 300),
+             "qwen_bailian": ([[("instance", "leaf_aware_lru")]], 2, 400),
+             "publisher_log": ([[("inst_a", "lru"), ("inst_b", "leaf_aware_lru")]], 1, 500)}
+    groups, mode, quota = plans[trace_type]
+    files = {}
+    for who in ("reference", "gpu"):
+        out = tmp_path / who
+        out.mkdir()
+        config = ref.startup_config([dict(quota_capacity=quota, instances=[(i, p, 0.1) for i, p in members])
+                                     for members in groups], evict_batch=16, mode=mode,
+                                    trace_file_path=str(tmp_path / "trace.jsonl"), trace_type=trace_type,
+                                    output_result_path=str(out))
+        if who == "reference":
+            ref.optimizer_main(config)
+        else:
+            runner.run_startup_config(config, device=DEV)
+        files[who] = {p.name: p.read_text() for p in sorted(out.iterdir())}
+    assert sum(len(t.splitlines()) for t in files["reference"].values()) > 1500
+    compare_with_reference_files(dict(trace_type=trace_type, files=files["reference"]), str(tmp_path / "gpu"))

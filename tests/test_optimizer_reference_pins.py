@@ -167,3 +167,33 @@ def test_trace_files_give_the_reference_csv_files(tmp_path, monkeypatch):
         config["output_result_path"] = str(work / "out")
         runner.run_startup_config(config, device="cpu")
         compare_with_reference_files(case, str(work / "out"))
+
+
+@pytest.mark.skipif(not ref.available(), reason="oracle/_ref/libkvcm_ref_optimizer.so not built (reference tree absent)")
+@pytest.mark.parametrize("trace_type", ["optimizer_schema", "qwen_bailian", "publisher_log"])
+def test_readers_give_the_reference_loader_s_traces_in_its_order(tmp_path, trace_type):
+    """Trace by trace against OptimizerLoader::LoadTrace on a few thousand lines per format: kinds, instances,
+    timestamps, keys, the keys a dialog turn replays, masks - and the ORDER, which for equal timestamps is that of
+    the reference's std::sort over a list whose tail comes out of a std::unordered_map."""
+    from golden.make_optimizer_golden import trace_files
+    from tair_kvcache_b200.optimizer import trace_reader as tr
+    (tmp_path / "trace.jsonl").write_text(trace_files(np.random.default_rng(0xB200000A), scale=40)[trace_type])
+    instances = [("instance", "lru")] if trace_type == "qwen_bailian" else [("inst_a", "lru"), ("inst_b", "lru")]
+    config = ref.startup_config([dict(quota_capacity=100, instances=instances)],
+                                trace_file_path=str(tmp_path / "trace.jsonl"), trace_type=trace_type)
+    want = ref.load_traces(config)
+    got = tr.load_traces(str(tmp_path / "trace.jsonl"), trace_type, {i: 16 for i, _ in instances})
+    assert len(got) == len(want) > 2000
+    ties = 0
+    for n, ((kind, doc), t) in enumerate(zip(want, got)):
+        assert (kind, doc["instance_id"], doc["timestamp_us"]) == (t.kind, t.instance_id, t.timestamp_us), n
+        keys = t.keys if not t.needs_prefix_hash else oracle.apply_prefix_hash(t.keys).tolist()
+        assert doc["keys"] == keys, n
+        if kind == tr.DIALOG_TURN:
+            total = t.replay_keys() if not t.needs_prefix_hash else keys
+            assert doc["total_keys"] == total and (doc["input_len"], doc["output_len"]) == (t.input_len, t.output_len), n
+        if kind != tr.WRITE_CACHE and trace_type != "qwen_bailian":
+            mask = doc["block_mask"]
+            assert (mask == t.block_mask) or (mask == [] and t.block_mask in ([], None)), n
+        ties += n > 0 and want[n - 1][1]["timestamp_us"] == doc["timestamp_us"]
+    assert ties > 50  # equal timestamps are there to be ordered
