@@ -84,6 +84,20 @@ class RefSearcher:
                                                   ctypes.c_int32(kind), ctypes.c_int64(off), _p(vec, ctypes.c_uint8),
                                                   _p(w, ctypes.c_uint32)))
 
+    def prefix_match_batch(self, tokens, tok_off, block_size, threads=1, weights=None):
+        """GenKeyVector + PrefixMatch per request on `threads` host threads: matched blocks per request."""
+        t = np.ascontiguousarray(tokens, dtype=np.int64)
+        off = np.ascontiguousarray(tok_off, dtype=np.int64)
+        out = np.zeros(len(off) - 1, dtype=np.int32)
+        w = _w(weights)
+        rc = lib().kvcm_ref_searcher_prefix_batch(self._h, _p(t, ctypes.c_int64), _p(off, ctypes.c_int64),
+                                                  ctypes.c_int64(len(off) - 1), ctypes.c_int32(block_size),
+                                                  _p(w, ctypes.c_uint32), ctypes.c_int32(threads),
+                                                  _p(out, ctypes.c_int32))
+        if rc != 0:
+            raise RuntimeError("kvcm_ref_searcher_prefix_batch returned %d" % rc)
+        return out
+
     def sw_match(self, keys, sw, weights=None):
         """(start of the matched window or -1, number of locations returned); needs len(keys) >= sw > 0, which the
         reference asserts."""

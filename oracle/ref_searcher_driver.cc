@@ -15,6 +15,7 @@
 #include <map>
 #include <memory>
 #include <string>
+#include <thread>
 #include <utility>
 #include <vector>
 
@@ -22,6 +23,7 @@
 #include "kv_cache_manager/common/request_context.h"
 #include "kv_cache_manager/config/meta_indexer_config.h"
 #include "kv_cache_manager/config/meta_storage_backend_config.h"
+#include "kv_cache_manager/manager/hash_util.h"
 #include "kv_cache_manager/manager/meta_searcher.h"
 #include "kv_cache_manager/meta/meta_indexer.h"
 #include "kv_cache_manager/meta/meta_local_backend.h"
@@ -126,6 +128,40 @@ int64_t kvcm_ref_searcher_prefix(void *handle, const int64_t *keys, int64_t n, i
     ErrorCode ec = h->searcher->PrefixMatch(h->context.get(), MetaSearcher::KeyVector(keys, keys + n),
                                             MaskFor(mask_kind, mask_off, mask_vec, n), out, policy.get());
     return ec == EC_OK ? static_cast<int64_t>(out.size()) : -static_cast<int64_t>(ec);
+}
+
+// The reference's CPU path for a batch of requests: per request the loop of GenKeyVector
+// (kv_cache_manager/manager/cache_manager.cc:76-87) around the reference's hashInt64Array, then
+// MetaSearcher::PrefixMatch without a mask; matched_out[r] = how many locations it returned.  Requests are dealt to
+// `threads` host threads (the index takes concurrent readers: its entries sit behind sharded mutexes); every call
+// of PrefixMatch gets a request context of its own.
+int32_t kvcm_ref_searcher_prefix_batch(void *handle, const int64_t *tokens, const int64_t *tok_off, int64_t n_req,
+                                       int32_t block_size, const uint32_t *weights, int32_t threads,
+                                       int32_t *matched_out) {
+    auto *h = static_cast<RefSearcher *>(handle);
+    if (block_size <= 0 || threads <= 0) return static_cast<int32_t>(EC_BADARGS);
+    auto work = [&](int32_t tid) {
+        auto policy = PolicyFor(weights);
+        for (int64_t r = tid; r < n_req; r += threads) {
+            const int64_t *tok = tokens + tok_off[r];
+            const int64_t blocks = (tok_off[r + 1] - tok_off[r]) / block_size;
+            MetaSearcher::KeyVector keys(static_cast<size_t>(blocks));
+            int64_t hash = 0;
+            for (int64_t b = 0; b < blocks; ++b) {
+                hash = hashInt64Array(hash, tok + b * block_size, tok + (b + 1) * block_size);
+                keys[static_cast<size_t>(b)] = hash;
+            }
+            RequestContext context("oracle");
+            CacheLocationVector out;
+            h->searcher->PrefixMatch(&context, keys, BlockMask(BlockMaskVector{}), out, policy.get());
+            matched_out[r] = static_cast<int32_t>(out.size());
+        }
+    };
+    std::vector<std::thread> pool;
+    for (int32_t t = 1; t < threads; ++t) pool.emplace_back(work, t);
+    work(0);
+    for (auto &t : pool) t.join();
+    return 0;
 }
 
 // MetaSearcher::ReverseRollSlideWindowMatch.  The reference returns one entry per key, empty but for the matched

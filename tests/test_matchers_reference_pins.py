@@ -102,3 +102,36 @@ def test_status_transitions_on_random_task_batches():
     for op in range(4):
         assert (op, 0) in seen
     assert (ref.OP_CAS, 16) in seen and (ref.OP_CAD, 16) in seen and (ref.OP_UPDATE, 2) in seen
+
+
+def test_hash_and_prefix_match_of_a_batch_of_requests():
+    """The reference's CPU path for the prefix-match configuration end to end - the loop of GenKeyVector around its
+    hashInt64Array, then PrefixMatch, on several host threads - against the oracle's hash + batched prefix match.
+    (Small on purpose: the reference's local meta backend rewrites its file on every mutation, so building its index
+    costs time quadratic in the number of keys - 13 s for 2,000 keys here, which is also why bench.py cannot time
+    this path at the configuration's 200,000 keys.)"""
+    rng = np.random.default_rng(2026)
+    bs = 16
+    prior = [rng.integers(0, 50000, size=int(rng.integers(64, 300))).astype(np.int64) for _ in range(60)]
+    reqs = []
+    for _ in range(200):
+        t = rng.integers(0, 50000, size=int(rng.integers(0, 300))).astype(np.int64)
+        if rng.random() < 0.6:
+            src = prior[int(rng.integers(len(prior)))]
+            m = int(rng.integers(0, min(len(t), len(src)) + 1))
+            t[:m] = src[:m]
+        reqs.append(t)
+
+    def csr(seqs):
+        off = np.zeros(len(seqs) + 1, dtype=np.int64)
+        np.cumsum([len(x) for x in seqs], out=off[1:])
+        return np.concatenate(seqs), off
+
+    (ptoks, poff), (toks, off) = csr(prior), csr(reqs)
+    pkeys = np.unique(oracle.hash_blocks(ptoks, poff, bs, threads=2)[0])
+    r, ox = ref.RefSearcher(), oracle.Index()
+    r.add(pkeys, 4, oracle.CLS_SERVING)
+    ox.put_uniform(pkeys)
+    keys, ko = oracle.hash_blocks(toks, off, bs, threads=2)
+    want = r.prefix_match_batch(toks, off, bs, threads=4)
+    assert np.array_equal(want, ox.prefix_match_batch(keys, ko, threads=2)) and want.sum() > 100
