@@ -2200,7 +2200,10 @@ def main_b200(args, cfg, ctx):
         cpu_pm, n_rep = run_prefix_cpu(data, threads)
         pm["cpu_baseline"] = {"value": cpu_pm, "unit": "token-blocks/s", "cores": threads, "kind": "port",
                               "sample": "the whole workload, %d repetitions; omits the reference's per-key JSON "
-                                        "parse and string copies, so it over-states the reference" % n_rep}
+                                        "parse and string copies, so it over-states the reference (whose own "
+                                        "MetaSearcher cannot be timed at this size: its local meta backend rewrites "
+                                        "its file on every mutation, so building the 200k-key index takes time "
+                                        "quadratic in the keys - 13 s for 2,000 of them)" % n_rep}
         line["prefix_match"] = pm
         seconds["prefix_match"] = round(time.perf_counter() - t0, 1)
         freed()
