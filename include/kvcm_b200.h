@@ -770,6 +770,29 @@ KVCM_API int32_t kvcm_b200_replay_leaf_lru_group(
     int32_t eviction_mode, void *d_workspace, int64_t workspace_bytes, int32_t *d_ext_hit, int32_t *d_int_hit,
     int32_t *d_written, int64_t *d_cache_blocks, int64_t *d_totals, int64_t *d_instance_blocks,
     int64_t *d_instance_blocks_per_trace, uint32_t *d_status, kvcm_stream_t stream);
+/* Any mix of the three policies in one group, as the reference's configuration allows it (every instance of a group
+ * names its own eviction_policy_type; kv_cache_manager/optimizer/manager/eviction_manager.cc:21-60 makes one policy
+ * object per instance): h_instance_policy may also hold KVCM_POLICY_RANDOM_LRU, and h_sample_rate (HOST memory,
+ * n_instances doubles, read for the random_lru instances only; NULL or <= 0 = the policy's default 0.1) gives those
+ * instances' eviction_policy_params.sample_rate.  A random_lru instance keeps the policy's block vector, access times
+ * and generator instead of a tree and a queue, exactly as in kvcm_b200_replay_random_lru_group, whose limits on
+ * evict_batch and evict_batch / sample_rate apply when such an instance is present; a round of the quota check asks
+ * every instance in the configuration's order, each through its own EvictBlocks.  The workspace grows by the block
+ * vectors when a random_lru instance is present: kvcm_b200_replay_policy_group_workspace_bytes takes the policy bytes.
+ * Everything else as in kvcm_b200_replay_tree_group, which is this call without sample rates and refuses
+ * KVCM_POLICY_RANDOM_LRU. */
+#define KVCM_POLICY_RANDOM_LRU 2
+KVCM_API int64_t kvcm_b200_replay_policy_group_workspace_bytes(int64_t n_keys_total, int32_t n_traces,
+                                                               int32_t n_configs, const uint8_t *h_instance_policy,
+                                                               int32_t n_instances);
+KVCM_API int32_t kvcm_b200_replay_policy_group(
+    const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type, const int64_t *d_mask_off,
+    const uint8_t *d_mask_bits, const int64_t *d_timestamps, const int32_t *d_trace_instance,
+    const uint8_t *h_instance_policy, const double *h_sample_rate, int32_t n_instances, int32_t n_traces,
+    int64_t n_keys_total, const int64_t *d_quota_blocks, int32_t n_configs, int32_t evict_batch,
+    int32_t eviction_mode, void *d_workspace, int64_t workspace_bytes, int32_t *d_ext_hit, int32_t *d_int_hit,
+    int32_t *d_written, int64_t *d_cache_blocks, int64_t *d_totals, int64_t *d_instance_blocks,
+    int64_t *d_instance_blocks_per_trace, uint32_t *d_status, kvcm_stream_t stream);
 
 /* Host-only helper: h_order_out[i] = the number of the trace replayed i-th when a trace file's traces are put in
  * timestamp order the way OptimizerLoader::LoadTrace does it - std::sort by timestamp

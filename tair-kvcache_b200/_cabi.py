@@ -28,7 +28,7 @@ STATUS_ANY = STATUS_DELETE = 0xFF
 STATUS_DELETE_KEEP_KEY = 0xFE
 VAL_STATUS_SHIFT = 33
 REPLAY_NOALLOC_MAX_KEYS = 262144
-POLICY_LEAF_AWARE_LRU, POLICY_LRU = 0, 1  # kvcm_b200_replay_tree_group's per-instance policy bytes
+POLICY_LEAF_AWARE_LRU, POLICY_LRU, POLICY_RANDOM_LRU = 0, 1, 2  # kvcm_b200_replay_policy_group's per-instance policy bytes
 
 VAL_NONEMPTY = 1 << 32
 VAL_PRESENT = 1 << 63
@@ -146,6 +146,9 @@ SIGNATURES = {
                                         _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "kvcm_b200_replay_tree_group": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i64, _vp, _i32, _i32, _i32, _vp,
                                     _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+    "kvcm_b200_replay_policy_group_workspace_bytes": [_i64, _i32, _i32, _vp, _i32],
+    "kvcm_b200_replay_policy_group": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i64, _vp, _i32, _i32,
+                                      _i32, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "kvcm_b200_replay_random_lru_workspace_bytes": [_i64, _i32],
     "kvcm_b200_replay_random_lru_group_workspace_bytes": [_i64, _i32, _i32],
     "kvcm_b200_replay_random_lru_group": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i64, _vp, _i32, _i32, _i32,

@@ -29,6 +29,7 @@ def sources():
 
 
 HEADERS = [os.path.join(CSRC, "kvcm_common.cuh"), os.path.join(CSRC, "replay_ids.cuh"),
+           os.path.join(CSRC, "replay_sampling.cuh"),
            os.path.join(ROOT, "include", "kvcm_b200.h")]
 OBJ_DIR = os.path.join(HERE, "build")
 

@@ -33,8 +33,15 @@
 // is the list surgery around them and the walk to a sorted insertion point (latency-bound on L2).
 // Every walk carries an iteration limit so that keys that break the prefix-unique premise end in a status
 // count, not in an endless loop.
+//
+// A group may also hold instances of the "random_lru" policy (EvictionPolicyFactory::CreatePolicy makes a policy per
+// instance, whatever the others are).  Such an instance needs no tree here - which blocks a trace hits and writes
+// depends on per-key state alone - so the second form of the kernel keeps, for those instances, the sampling
+// policy's block vector (replay_sampling.cuh) beside the trees and queues of the others, and the quota check calls
+// whichever EvictBlocks the instance's policy has.
 #include "kvcm_common.cuh"
 #include "replay_ids.cuh"
+#include "replay_sampling.cuh"
 
 namespace kvcm {
 namespace {
@@ -77,7 +84,15 @@ struct LeafSweep {
     // bit j set: instance j runs the plain "lru" policy (kv_cache_manager/optimizer/eviction_policy/lru.cc:6-49) over
     // the same tree and queue: every cached block is queued whatever its node's children, the cold end goes first
     uint64_t lru_instances;
+    // bit j set: instance j runs "random_lru".  The node_of entry of one of its keys is the block's index in the
+    // instance's block vector (kNone = not cached); the vector is the instance's region of blk / ts.
+    uint64_t sampling_instances;
+    uint32_t *blk;               // [n_configs][n_keys]; null without a sampling instance
+    int64_t *ts;                 // [n_configs][n_keys]
+    const int64_t *region_base;  // [n_instances + 1]: key occurrences of the instances before (LruGroupExtentKernel)
+    uint32_t sampling_size[KVCM_B200_REPLAY_GROUP_MAX_INSTANCES];
 };
+static_assert(kNone == kNotCached, "a sampling instance's index shares node_of with the tree instances' node numbers");
 
 __global__ void LeafInitKernel(IdTable t, uint32_t *node_of, uint8_t *flags, uint64_t n_state) {
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
@@ -122,6 +137,9 @@ __global__ void __launch_bounds__(256)
 }
 
 // type: 0 DialogTurn (InsertWithQuery), 1 GetLocation (PrefixQuery), 2 WriteCache (InsertOnly).
+// kSampling: the group holds "random_lru" instances too (more shared memory, one more branch per trace and per
+// round of evictions).
+template <bool kSampling>
 __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
     extern __shared__ int64_t cached_of[];  // [n_instances]: cached blocks per instance (EvictionPolicy::size())
     __shared__ uint32_t short_group[32];
@@ -129,6 +147,10 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
     // read for every trace and every eviction): the links of keys are in global memory.
     uint32_t *front_of = reinterpret_cast<uint32_t *>(cached_of + p.n_instances);  // [n_instances]: hottest entry
     uint32_t *cold_of = front_of + p.n_instances;                                  // [n_instances]: coldest entry
+    // sampling instances: the generator's state, where the block vector starts, the warp's scratch for a round
+    uint64_t *rng_of = reinterpret_cast<uint64_t *>(cached_of + 2 * p.n_instances);  // [n_instances]
+    int64_t *base_of = cached_of + 3 * p.n_instances;                                // [n_instances]
+    SamplingScratch *scratch = reinterpret_cast<SamplingScratch *>(cached_of + 4 * p.n_instances);
     const int64_t cfg = blockIdx.x;
     const uint32_t lane = LaneId();
     const uint32_t full = 0xffffffffu;
@@ -153,6 +175,7 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
     // the queue of instance j lies between the sentinels head_of(j) (hot end) and head_of(j) + 1 (cold end)
     auto head_of = [&](int32_t j) { return static_cast<uint32_t>(nk) + 2u * static_cast<uint32_t>(j); };
     auto plain_lru = [&](int32_t j) { return ((p.lru_instances >> j) & 1ull) != 0; };
+    auto sampling = [&](int32_t j) { return kSampling && ((p.sampling_instances >> j) & 1ull) != 0; };
     // x is a key or a sentinel of instance j's queue (hd = its hot-end sentinel)
     auto get_next = [&](uint32_t x, uint32_t hd, int32_t j) { return x == hd ? front_of[j] : lnext[x]; };
     auto get_prev = [&](uint32_t x, uint32_t hd, int32_t j) { return x == hd + 1 ? cold_of[j] : lprev[x]; };
@@ -416,6 +439,20 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
         }
         return got;
     };
+    // EvictBlocks(count) of instance j, whatever its policy; all lanes, returns how many blocks went
+    auto evict_blocks = [&](int32_t j, int64_t count) -> int64_t {
+        if (!sampling(j)) return evict_from(j, count);
+        const int64_t held = cached_of[j];
+        const int64_t got = SamplingEvictRound(*scratch, node_of, p.blk + cfg * nk + base_of[j],
+                                               p.ts + cfg * nk + base_of[j], held, &rng_of[j], p.sampling_size[j],
+                                               count, lane);
+        if (lane == 0) {
+            cached_of[j] = held - got;
+            resident -= got;
+        }
+        __syncwarp();
+        return got;
+    };
 
     if (lane == 0) {
         for (int32_t j = 0; j < K; ++j) {
@@ -429,6 +466,10 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
             front_of[j] = head_of(j) + 1;
             cold_of[j] = head_of(j);
             cached_of[j] = 0;
+            if (kSampling) {
+                rng_of[j] = kSamplingSeed;
+                base_of[j] = p.region_base[j];
+            }
         }
     }
     __syncwarp();
@@ -467,6 +508,14 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
         int32_t ext = 0, inte = 0, wr = 0;
         const uint32_t my_root = static_cast<uint32_t>(me);
         const uint32_t kHead = head_of(me);
+        const bool sampled = sampling(me);  // a trace of a "random_lru" instance: no tree, its block vector only
+        if (sampled) {
+            const SamplingTraceCounts c = SamplingReplayTrace(
+                p.ids + beg, p.mask_bits != nullptr ? p.mask_bits + beg : nullptr, n, ty, skip, now, node_of,
+                p.blk + cfg * nk + base_of[me], p.ts + cfg * nk + base_of[me], cached_of[me], lane);
+            ext = c.ext, inte = c.inte, wr = c.wr;
+            n = 0;  // nothing is left for the tree
+        }
 
         // ---- scan: where the trace leaves the tree (div) and its first block that is not cached (first_gone)
         // A key is in the tree when its node still has blocks: removing a node only zeroes its block count.
@@ -702,7 +751,7 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                     while (total < excess) {
                         bool any = false;
                         for (int32_t j = 0; j < K; ++j) {  // a whole round even when the excess is covered midway
-                            const int64_t got = evict_from(j, p.evict_batch);
+                            const int64_t got = evict_blocks(j, p.evict_batch);
                             any = any || got > 0;
                             total += got;
                         }
@@ -712,7 +761,7 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
                     while (total < excess) {
                         const int64_t rest = excess - total;
                         const int64_t count = p.mode == 3 && rest < p.evict_batch ? rest : p.evict_batch;
-                        const int64_t got = evict_from(me, count);
+                        const int64_t got = evict_blocks(me, count);
                         if (got == 0) break;
                         total += got;
                     }
@@ -779,11 +828,12 @@ __global__ void __launch_bounds__(32) LeafSweepKernel(const LeafSweep p) {
 
 struct LeafLayout {
     uint64_t table_off, ids_off, occ_off, node_of_off, flags_off, time_off, lprev_off, lnext_off, evicted_off, nodes_off,
-        total;
+        blk_off, ts_off, region_off, total;
     int64_t max_nodes;
 };
 
-LeafLayout LayoutFor(int64_t n_keys, int32_t n_traces, int32_t n_configs, int32_t n_instances) {
+// with_sampling: the group holds a "random_lru" instance (block vectors and the instances' regions are added)
+LeafLayout LayoutFor(int64_t n_keys, int32_t n_traces, int32_t n_configs, int32_t n_instances, bool with_sampling) {
     auto up = [](uint64_t v) { return (v + 255u) & ~static_cast<uint64_t>(255u); };
     LeafLayout l;
     const uint64_t nk = static_cast<uint64_t>(n_keys > 0 ? n_keys : 1);
@@ -800,7 +850,35 @@ LeafLayout LayoutFor(int64_t n_keys, int32_t n_traces, int32_t n_configs, int32_
     l.evicted_off = up(l.lnext_off + nk * 4 * nc);
     l.nodes_off = up(l.evicted_off + nk * 4 * nc);
     l.total = up(l.nodes_off + static_cast<uint64_t>(l.max_nodes) * 4 * kNodeFields * nc);
+    l.blk_off = l.ts_off = l.region_off = l.total;
+    if (with_sampling) {
+        l.ts_off = up(l.blk_off + nk * 4 * nc);
+        l.region_off = up(l.ts_off + nk * 8 * nc);
+        l.total = up(l.region_off + (static_cast<uint64_t>(n_instances) + 1) * 8);
+    }
     return l;
+}
+
+}  // namespace
+}  // namespace kvcm
+
+namespace kvcm {
+namespace {
+
+// 1 when some instance runs random_lru, 0 when none does, -1 for a policy byte that names nothing
+int SamplingInstances(const uint8_t *h_instance_policy, int32_t n_instances) {
+    int found = 0;
+    for (int32_t j = 0; h_instance_policy != nullptr && j < n_instances; ++j) {
+        if (h_instance_policy[j] > KVCM_POLICY_RANDOM_LRU) return -1;
+        if (h_instance_policy[j] == KVCM_POLICY_RANDOM_LRU) found = 1;
+    }
+    return found;
+}
+
+bool GroupShapeOk(int64_t n_keys_total, int32_t n_traces, int32_t n_configs, int32_t n_instances) {
+    return n_keys_total >= 0 && n_keys_total < (1ll << 32) - 3 - 2 * KVCM_B200_REPLAY_GROUP_MAX_INSTANCES &&
+           n_traces >= 0 && n_traces < (1 << 30) && n_configs > 0 && n_configs <= 65535 && n_instances > 0 &&
+           n_instances <= KVCM_B200_REPLAY_GROUP_MAX_INSTANCES;
 }
 
 }  // namespace
@@ -808,14 +886,17 @@ LeafLayout LayoutFor(int64_t n_keys, int32_t n_traces, int32_t n_configs, int32_
 
 extern "C" {
 
+int64_t kvcm_b200_replay_policy_group_workspace_bytes(int64_t n_keys_total, int32_t n_traces, int32_t n_configs,
+                                                      const uint8_t *h_instance_policy, int32_t n_instances) {
+    if (!kvcm::GroupShapeOk(n_keys_total, n_traces, n_configs, n_instances)) return -1;
+    const int with_sampling = kvcm::SamplingInstances(h_instance_policy, n_instances);
+    if (with_sampling < 0) return -1;
+    return static_cast<int64_t>(kvcm::LayoutFor(n_keys_total, n_traces, n_configs, n_instances, with_sampling != 0).total);
+}
+
 int64_t kvcm_b200_replay_leaf_lru_group_workspace_bytes(int64_t n_keys_total, int32_t n_traces, int32_t n_configs,
                                                         int32_t n_instances) {
-    if (n_keys_total < 0 || n_keys_total >= (1ll << 32) - 3 - 2 * KVCM_B200_REPLAY_GROUP_MAX_INSTANCES || n_traces < 0 ||
-        n_traces >= (1 << 30) || n_configs <= 0 || n_configs > 65535 || n_instances <= 0 ||
-        n_instances > KVCM_B200_REPLAY_GROUP_MAX_INSTANCES) {
-        return -1;
-    }
-    return static_cast<int64_t>(kvcm::LayoutFor(n_keys_total, n_traces, n_configs, n_instances).total);
+    return kvcm_b200_replay_policy_group_workspace_bytes(n_keys_total, n_traces, n_configs, nullptr, n_instances);
 }
 
 int64_t kvcm_b200_replay_leaf_lru_workspace_bytes(int64_t n_keys_total, int32_t n_traces, int32_t n_configs) {
@@ -832,11 +913,11 @@ int32_t kvcm_b200_replay_leaf_lru_group(const int64_t *d_keys, const int64_t *d_
                                         int64_t *d_cache_blocks, int64_t *d_totals, int64_t *d_instance_blocks,
                                         int64_t *d_instance_blocks_per_trace, uint32_t *d_status,
                                         kvcm_stream_t stream) {
-    return kvcm_b200_replay_tree_group(d_keys, d_key_off, d_trace_type, d_mask_off, d_mask_bits, d_timestamps,
-                                       d_trace_instance, nullptr, n_instances, n_traces, n_keys_total, d_quota_blocks,
-                                       n_configs, evict_batch, eviction_mode, d_workspace, workspace_bytes, d_ext_hit,
-                                       d_int_hit, d_written, d_cache_blocks, d_totals, d_instance_blocks,
-                                       d_instance_blocks_per_trace, d_status, stream);
+    return kvcm_b200_replay_policy_group(d_keys, d_key_off, d_trace_type, d_mask_off, d_mask_bits, d_timestamps,
+                                         d_trace_instance, nullptr, nullptr, n_instances, n_traces, n_keys_total,
+                                         d_quota_blocks, n_configs, evict_batch, eviction_mode, d_workspace,
+                                         workspace_bytes, d_ext_hit, d_int_hit, d_written, d_cache_blocks, d_totals,
+                                         d_instance_blocks, d_instance_blocks_per_trace, d_status, stream);
 }
 
 int32_t kvcm_b200_replay_tree_group(const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type,
@@ -848,17 +929,52 @@ int32_t kvcm_b200_replay_tree_group(const int64_t *d_keys, const int64_t *d_key_
                                     int32_t *d_ext_hit, int32_t *d_int_hit, int32_t *d_written, int64_t *d_cache_blocks,
                                     int64_t *d_totals, int64_t *d_instance_blocks,
                                     int64_t *d_instance_blocks_per_trace, uint32_t *d_status, kvcm_stream_t stream) {
+    if (n_instances > 0 && n_instances <= KVCM_B200_REPLAY_GROUP_MAX_INSTANCES &&
+        kvcm::SamplingInstances(h_instance_policy, n_instances) != 0) {
+        return KVCM_EC_BADARGS;  // the two queue policies only
+    }
+    return kvcm_b200_replay_policy_group(d_keys, d_key_off, d_trace_type, d_mask_off, d_mask_bits, d_timestamps,
+                                         d_trace_instance, h_instance_policy, nullptr, n_instances, n_traces,
+                                         n_keys_total, d_quota_blocks, n_configs, evict_batch, eviction_mode,
+                                         d_workspace, workspace_bytes, d_ext_hit, d_int_hit, d_written, d_cache_blocks,
+                                         d_totals, d_instance_blocks, d_instance_blocks_per_trace, d_status, stream);
+}
+
+int32_t kvcm_b200_replay_policy_group(const int64_t *d_keys, const int64_t *d_key_off, const uint8_t *d_trace_type,
+                                      const int64_t *d_mask_off, const uint8_t *d_mask_bits, const int64_t *d_timestamps,
+                                      const int32_t *d_trace_instance, const uint8_t *h_instance_policy,
+                                      const double *h_sample_rate, int32_t n_instances, int32_t n_traces,
+                                      int64_t n_keys_total, const int64_t *d_quota_blocks, int32_t n_configs,
+                                      int32_t evict_batch, int32_t eviction_mode, void *d_workspace,
+                                      int64_t workspace_bytes, int32_t *d_ext_hit, int32_t *d_int_hit,
+                                      int32_t *d_written, int64_t *d_cache_blocks, int64_t *d_totals,
+                                      int64_t *d_instance_blocks, int64_t *d_instance_blocks_per_trace,
+                                      uint32_t *d_status, kvcm_stream_t stream) {
     if (!kvcm::HaveDevice()) return KVCM_ER_NO_DEVICE;
     if (n_traces < 0 || n_keys_total < 0 || n_configs <= 0 || evict_batch <= 0 || n_instances <= 0 ||
         eviction_mode < 1 || eviction_mode > 3) {
         return KVCM_EC_BADARGS;
     }
-    const int64_t need = kvcm_b200_replay_leaf_lru_group_workspace_bytes(n_keys_total, n_traces, n_configs, n_instances);
-    if (need < 0) return KVCM_EC_OUT_OF_LIMIT;
-    uint64_t lru_instances = 0;
+    if (!kvcm::GroupShapeOk(n_keys_total, n_traces, n_configs, n_instances)) return KVCM_EC_OUT_OF_LIMIT;
+    const int with_sampling = kvcm::SamplingInstances(h_instance_policy, n_instances);
+    if (with_sampling < 0) return KVCM_EC_BADARGS;
+    kvcm::LeafSweep p;
+    uint64_t lru_instances = 0, sampling_instances = 0;
+    for (int32_t j = 0; j < KVCM_B200_REPLAY_GROUP_MAX_INSTANCES; ++j) p.sampling_size[j] = 0;
     for (int32_t j = 0; h_instance_policy != nullptr && j < n_instances; ++j) {
-        if (h_instance_policy[j] > KVCM_POLICY_LRU) return KVCM_EC_BADARGS;
         if (h_instance_policy[j] == KVCM_POLICY_LRU) lru_instances |= 1ull << j;
+        if (h_instance_policy[j] != KVCM_POLICY_RANDOM_LRU) continue;
+        sampling_instances |= 1ull << j;
+        // RandomLruEvictionPolicy's constructor (random_lru.cc:5-14): a rate <= 0 means 0.1; the size is a double
+        // division cut to an integer
+        double rate = h_sample_rate != nullptr ? h_sample_rate[j] : 0.0;
+        if (rate <= 0.0) rate = 0.1;
+        const double size = static_cast<double>(evict_batch) / rate;
+        if (static_cast<uint32_t>(evict_batch) > kvcm::kMaxBatch || size > static_cast<double>(kvcm::kMaxSample) ||
+            size < 1.0) {
+            return KVCM_EC_OUT_OF_LIMIT;
+        }
+        p.sampling_size[j] = static_cast<uint32_t>(size);
     }
     if (n_traces == 0) return KVCM_OK;
     const int per_trace = (d_ext_hit != nullptr) + (d_int_hit != nullptr) + (d_written != nullptr) +
@@ -869,8 +985,8 @@ int32_t kvcm_b200_replay_tree_group(const int64_t *d_keys, const int64_t *d_key_
         return KVCM_ER_INVALID_ADDRESS;
     }
     if (reinterpret_cast<uintptr_t>(d_workspace) & 255u) return KVCM_ER_INVALID_ADDRESS;
-    if (workspace_bytes < need) return KVCM_EC_NOSPC;
-    const kvcm::LeafLayout l = kvcm::LayoutFor(n_keys_total, n_traces, n_configs, n_instances);
+    const kvcm::LeafLayout l = kvcm::LayoutFor(n_keys_total, n_traces, n_configs, n_instances, with_sampling != 0);
+    if (workspace_bytes < static_cast<int64_t>(l.total)) return KVCM_EC_NOSPC;
     uint8_t *ws = static_cast<uint8_t *>(d_workspace);
     kvcm::IdTable t;
     t.cells = reinterpret_cast<unsigned long long *>(ws);
@@ -878,10 +994,10 @@ int32_t kvcm_b200_replay_tree_group(const int64_t *d_keys, const int64_t *d_key_
     t.mask = kvcm::SlotsFor(n_keys_total) - 1;
     uint32_t *ids = reinterpret_cast<uint32_t *>(ws + l.ids_off);
     uint32_t *occ = reinterpret_cast<uint32_t *>(ws + l.occ_off);
+    int64_t *region_base = reinterpret_cast<int64_t *>(ws + l.region_off);
     const uint64_t nk = static_cast<uint64_t>(n_keys_total > 0 ? n_keys_total : 1);
     cudaStream_t s = kvcm::AsStream(stream);
     const int sms = kvcm::GetDeviceInfo().sm_count;
-    kvcm::LeafSweep p;
     p.ids = ids;
     p.occ = occ;
     p.key_off = d_key_off;
@@ -898,6 +1014,9 @@ int32_t kvcm_b200_replay_tree_group(const int64_t *d_keys, const int64_t *d_key_
     p.lnext = reinterpret_cast<uint32_t *>(ws + l.lnext_off);
     p.evicted = reinterpret_cast<uint32_t *>(ws + l.evicted_off);
     p.nodes = reinterpret_cast<uint32_t *>(ws + l.nodes_off);
+    p.blk = with_sampling != 0 ? reinterpret_cast<uint32_t *>(ws + l.blk_off) : nullptr;
+    p.ts = with_sampling != 0 ? reinterpret_cast<int64_t *>(ws + l.ts_off) : nullptr;
+    p.region_base = with_sampling != 0 ? region_base : nullptr;
     p.ext_hit = d_ext_hit;
     p.int_hit = d_int_hit;
     p.written = d_written;
@@ -915,9 +1034,18 @@ int32_t kvcm_b200_replay_tree_group(const int64_t *d_keys, const int64_t *d_key_
     p.n_instances = n_instances;
     p.mode = eviction_mode;
     p.lru_instances = lru_instances;
+    p.sampling_instances = sampling_instances;
     kvcm::LeafInitKernel<<<sms * 8, 256, 0, s>>>(t, p.node_of, p.flags, nk * static_cast<uint64_t>(n_configs));
     if (d_trace_instance != nullptr) {
         kvcm::LeafCheckInstancesKernel<<<sms, 256, 0, s>>>(d_trace_instance, n_traces, n_instances, d_status);
+    }
+    if (with_sampling != 0) {
+        if (d_trace_instance != nullptr) {
+            kvcm::LruGroupExtentKernel<<<1, 1024, sizeof(unsigned long long) * n_instances, s>>>(
+                d_key_off, d_trace_instance, n_traces, n_instances, region_base, nullptr);
+        } else {
+            cudaMemsetAsync(region_base, 0, 2 * sizeof(int64_t), s);  // one instance: its vector starts at 0
+        }
     }
     if (n_keys_total > 0) {
         if (d_trace_instance == nullptr) {
@@ -937,7 +1065,13 @@ int32_t kvcm_b200_replay_tree_group(const int64_t *d_keys, const int64_t *d_key_
         }
         kvcm::LeafOccKernel<<<sms * 4, 256, 0, s>>>(ids, d_key_off, d_trace_instance, n_instances, n_traces, occ);
     }
-    kvcm::LeafSweepKernel<<<static_cast<unsigned>(n_configs), 32, sizeof(int64_t) * 2 * n_instances, s>>>(p);
+    const size_t per_instance = sizeof(int64_t) * static_cast<size_t>(n_instances);
+    if (with_sampling != 0) {
+        kvcm::LeafSweepKernel<true><<<static_cast<unsigned>(n_configs), 32,
+                                      4 * per_instance + sizeof(kvcm::SamplingScratch), s>>>(p);
+    } else {
+        kvcm::LeafSweepKernel<false><<<static_cast<unsigned>(n_configs), 32, 2 * per_instance, s>>>(p);
+    }
     return kvcm::LaunchStatus();
 }
 

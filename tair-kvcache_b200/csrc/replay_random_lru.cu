@@ -11,37 +11,19 @@
 //
 // One warp replays one quota point, as in the "lru" sweep, and the tree collapses to per-key state for the same
 // reasons (keys are prefix-unique; a trace touches its leading cached blocks, then writes its missing ones).  The
-// policy's own state is what the reference keeps: a dense vector of the cached blocks beside their last access
-// times, a key's index in it, and the state of its xorshift generator.
-//   pos[id]   0 = not cached, else index + 1 in blk / ts
-//   blk[i]    id of the block at index i; ts[i] its last access time; i < resident
-// A round of evictions (EvictBlocks, random_lru.cc:38-57) draws `sampling_size` indices with replacement
-// (FastRand, :121-131), orders the first k of them by access time with std::partial_sort (:59-82) and removes those
-// blocks by swap-and-pop (:84-103).  Blocks written or read by one trace share a timestamp, so WHICH of several
-// equally old samples go depends on the order std::partial_sort leaves equal elements in.  That order is a
-// property of the algorithm the C++ standard library documents for it - heap-select followed by sort-heap on a
-// binary max-heap with hole-based sift-down and sift-up - which is restated below, step for step, on the sample
-// held in shared memory; the CPU oracle calls std::partial_sort itself, and the parity tests compare the two on
-// traces full of tied timestamps.
-// The generator is sequential, the heap is sequential: both run in lane 0 (the raw draws first, the modulo of all
-// draws then in parallel; the times of the sampled indices are gathered by all lanes).  The removals are
-// sequential too - every one changes the index of the block that was last - but run out of shared memory: the
-// tail of the block vector is staged there, and the victims' indices are kept current by a warp-wide scan.
+// policy itself - block vector, sampling, partial sort, swap-and-pop - is in replay_sampling.cuh.
 #include "kvcm_common.cuh"
 #include "replay_ids.cuh"
+#include "replay_sampling.cuh"
 
 namespace kvcm {
 namespace {
-
-constexpr uint32_t kMaxSample = KVCM_B200_RANDOM_LRU_MAX_SAMPLE;  // sampled indices per round held in shared memory
-constexpr uint32_t kMaxBatch = KVCM_B200_RANDOM_LRU_MAX_BATCH;    // blocks evicted per round
-constexpr uint32_t kGone = 0xFFFFFFFFu;
 
 __global__ void RandomInitKernel(IdTable t, uint32_t *pos, uint64_t n_pos) {
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
     const uint64_t first = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     for (uint64_t i = first; i <= t.mask; i += stride) t.slots[i] = make_ulonglong2(kEmptyKey, ~0ull);
-    for (uint64_t i = first; i < n_pos; i += stride) pos[i] = 0u;
+    for (uint64_t i = first; i < n_pos; i += stride) pos[i] = kNotCached;
     if (first == 0) {
         t.cells[0] = 0ull;
         t.cells[1] = ~0ull;
@@ -75,87 +57,9 @@ struct RandomSweep {
     uint32_t sampling_size[KVCM_B200_REPLAY_GROUP_MAX_INSTANCES];  // per instance
 };
 
-// The sample: index into the block vector and that block's time, moved together.
-struct Sample {
-    uint32_t *idx;
-    int64_t *t;
-    __host__ __device__ __forceinline__ void Move(uint32_t to, uint32_t from) {
-        idx[to] = idx[from];
-        t[to] = t[from];
-    }
-    __host__ __device__ __forceinline__ void Put(uint32_t to, uint32_t i, int64_t time) {
-        idx[to] = i;
-        t[to] = time;
-    }
-};
-
-// Sift-up of `value` from `hole` towards `top` in a max-heap ordered by time (the standard library's push-heap step).
-__host__ __device__ __forceinline__ void PushHeap(Sample &s, uint32_t hole, uint32_t top, uint32_t v_idx, int64_t v_t) {
-    while (hole > top) {
-        const uint32_t parent = (hole - 1) / 2;
-        if (!(s.t[parent] < v_t)) break;
-        s.Move(hole, parent);
-        hole = parent;
-    }
-    s.Put(hole, v_idx, v_t);
-}
-
-// The hole at `hole` sinks to a leaf along the larger children (the right child unless it is smaller than the
-// left), then `value` is sifted up from there: the standard library's adjust-heap step.
-__host__ __device__ __forceinline__ void AdjustHeap(Sample &s, uint32_t hole, uint32_t len, uint32_t v_idx, int64_t v_t) {
-    const uint32_t top = hole;
-    uint32_t child = hole;
-    while (child < (len - 1) / 2) {
-        child = 2 * (child + 1);
-        if (s.t[child] < s.t[child - 1]) --child;
-        s.Move(hole, child);
-        hole = child;
-    }
-    if ((len & 1u) == 0 && child == (len - 2) / 2) {
-        child = 2 * (child + 1);
-        s.Move(hole, child - 1);
-        hole = child - 1;
-    }
-    PushHeap(s, hole, top, v_idx, v_t);
-}
-
-// std::partial_sort(first, first + k, first + n) by time: heap-select, then sort-heap.
-__host__ __device__ void PartialSortByTime(Sample &s, uint32_t k, uint32_t n) {
-    if (k == 0) return;
-    if (k >= 2) {  // make-heap over the first k
-        uint32_t parent = (k - 2) / 2;
-        while (true) {
-            const uint32_t vi = s.idx[parent];
-            const int64_t vt = s.t[parent];
-            AdjustHeap(s, parent, k, vi, vt);
-            if (parent == 0) break;
-            --parent;
-        }
-    }
-    for (uint32_t i = k; i < n; ++i) {  // an element older than the heap's top takes its place
-        if (s.t[i] < s.t[0]) {
-            const uint32_t vi = s.idx[i];
-            const int64_t vt = s.t[i];
-            s.Move(i, 0);
-            AdjustHeap(s, 0, k, vi, vt);
-        }
-    }
-    for (uint32_t last = k; last > 1;) {  // sort-heap
-        --last;
-        const uint32_t vi = s.idx[last];
-        const int64_t vt = s.t[last];
-        s.Move(last, 0);
-        AdjustHeap(s, 0, last, vi, vt);
-    }
-}
-
 // type: 0 DialogTurn (InsertWithQuery), 1 GetLocation (PrefixQuery), 2 WriteCache (InsertOnly).
 __global__ void __launch_bounds__(32) RandomLruSweepKernel(const RandomSweep p) {
-    __shared__ uint32_t s_idx[kMaxSample];
-    __shared__ int64_t s_t[kMaxSample];
-    __shared__ uint32_t v_id[kMaxBatch], v_at[kMaxBatch];      // the round's victims: block id, current index
-    __shared__ uint32_t tail_blk[kMaxBatch];                   // blk / ts of the last entries, [j] = index r0 - 1 - j
-    __shared__ int64_t tail_ts[kMaxBatch];
+    __shared__ SamplingScratch scratch;
     extern __shared__ int64_t per_inst[];
     const int32_t K = p.n_instances;
     int64_t *size_of = per_inst;      // [K] cached blocks of the instance = the length of its block vector
@@ -163,104 +67,27 @@ __global__ void __launch_bounds__(32) RandomLruSweepKernel(const RandomSweep p) 
     uint64_t *rng_of = reinterpret_cast<uint64_t *>(per_inst + 2 * K);  // [K] the state of its generator
     const int32_t cfg = blockIdx.x;
     const uint32_t lane = LaneId();
-    const uint32_t lt = (1u << lane) - 1u;
     uint32_t *pos = p.pos + static_cast<int64_t>(cfg) * p.n_keys;
     uint32_t *blk_all = p.blk + static_cast<int64_t>(cfg) * p.n_keys;
     int64_t *ts_all = p.ts + static_cast<int64_t>(cfg) * p.n_keys;
     const int64_t quota = p.quota[cfg];
     const int64_t out0 = static_cast<int64_t>(cfg) * p.n_traces;
-    Sample sample{s_idx, s_t};
     int64_t resident = 0;  // of the whole group
     int64_t sum_ext = 0, sum_int = 0, sum_wr = 0;
     for (int32_t j = lane; j < K; j += 32) {
         size_of[j] = 0;
         base_of[j] = p.region_base != nullptr ? p.region_base[j] : 0;
-        rng_of[j] = 0x12345678ABCDEF01ull;  // random_lru.h:20; every policy object starts from the same seed
+        rng_of[j] = kSamplingSeed;
     }
     __syncwarp();
 
-    // RandomLruEvictionPolicy::EvictBlocks(count) of instance j (random_lru.cc:38-103); all lanes, returns how many
-    // blocks went.
     auto evict_round = [&](int32_t j, int64_t count) -> uint32_t {
         const int64_t held = size_of[j];
-        if (held == 0) return 0u;
-        uint32_t *blk = blk_all + base_of[j];
-        int64_t *ts = ts_all + base_of[j];
-        const uint32_t n_blocks = static_cast<uint32_t>(held);
-        const uint32_t want = count < held ? static_cast<uint32_t>(count) : n_blocks;  // total_to_evict
-        const uint32_t n_sample = p.sampling_size[j] < n_blocks ? p.sampling_size[j] : n_blocks;
-        const uint32_t k = want < n_sample ? want : n_sample;
-        // the draws, in sequence (lane 0), then their modulo and the sampled blocks' times (all lanes)
-        if (lane == 0) {
-            uint64_t x = rng_of[j];
-            uint64_t *raw = reinterpret_cast<uint64_t *>(s_t);
-            for (uint32_t i = 0; i < n_sample; ++i) {
-                x ^= x << 13;
-                x ^= x >> 7;
-                x ^= x << 17;
-                raw[i] = x;
-            }
-            rng_of[j] = x;
-        }
+        const uint32_t got = SamplingEvictRound(scratch, pos, blk_all + base_of[j], ts_all + base_of[j], held,
+                                                &rng_of[j], p.sampling_size[j], count, lane);
+        if (lane == 0) size_of[j] = held - got;
         __syncwarp();
-        for (uint32_t i = lane; i < n_sample; i += 32) {
-            const uint32_t at = static_cast<uint32_t>(reinterpret_cast<uint64_t *>(s_t)[i] % n_blocks);
-            s_idx[i] = at;
-            s_t[i] = ts[at];
-        }
-        __syncwarp();
-        if (lane == 0) PartialSortByTime(sample, k, n_sample);
-        __syncwarp();
-        // the victims as blocks (resolved before the first removal, as the reference resolves them), and the tail
-        // of the vector, which the removals read
-        const uint32_t n_tail = k < n_blocks ? k : n_blocks;
-        for (uint32_t i = lane; i < k; i += 32) {
-            v_at[i] = s_idx[i];
-            v_id[i] = blk[s_idx[i]];
-        }
-        for (uint32_t i = lane; i < n_tail; i += 32) {
-            tail_blk[i] = blk[n_blocks - 1 - i];
-            tail_ts[i] = ts[n_blocks - 1 - i];
-        }
-        __syncwarp();
-        uint32_t evicted = 0;
-        uint32_t size = n_blocks;
-        for (uint32_t i = 0; i < k && evicted < want; ++i) {
-            const uint32_t at = v_at[i];
-            if (at == kGone) continue;  // sampled twice: removed already
-            const uint32_t id = v_id[i];
-            const uint32_t last = size - 1;
-            const uint32_t moved = tail_blk[n_blocks - 1 - last];  // the block that sits last now
-            const int64_t moved_t = tail_ts[n_blocks - 1 - last];
-            if (lane == 0) {
-                if (at != last) {
-                    blk[at] = moved;
-                    ts[at] = moved_t;
-                    pos[moved] = at + 1u;
-                    if (n_blocks - 1 - at < n_tail) {  // the staged tail follows
-                        tail_blk[n_blocks - 1 - at] = moved;
-                        tail_ts[n_blocks - 1 - at] = moved_t;
-                    }
-                }
-                pos[id] = 0u;
-            }
-            __syncwarp();
-            // later victims: further samples of this block are gone; the moved block has a new index
-            for (uint32_t v = i + 1 + lane; v < k; v += 32) {
-                if (v_at[v] == kGone) continue;
-                if (v_id[v] == id) {
-                    v_at[v] = kGone;
-                } else if (at != last && v_id[v] == moved) {
-                    v_at[v] = at;
-                }
-            }
-            __syncwarp();
-            --size;
-            ++evicted;
-        }
-        if (lane == 0) size_of[j] = size;
-        __syncwarp();
-        return evicted;
+        return got;
     };
 
     for (int32_t t = 0; t < p.n_traces; ++t) {
@@ -274,46 +101,12 @@ __global__ void __launch_bounds__(32) RandomLruSweepKernel(const RandomSweep p) 
             me = 0;
             n = 0;
         }
-        uint32_t *blk = blk_all + base_of[me];
-        int64_t *ts = ts_all + base_of[me];
-        int64_t my_size = size_of[me];
-        int32_t ext = 0, inte = 0, wr = 0;
-        bool alive = ty != 2;  // still inside the leading run of cached blocks
-        for (int64_t base = 0; base < n; base += 32) {
-            const int64_t i = base + lane;
-            const bool have = i < n;
-            const uint32_t id = have ? p.ids[beg + i] : 0u;
-            const uint32_t cur = have ? pos[id] : 0u;
-            const uint32_t in_range = __ballot_sync(0xffffffffu, have);
-            const uint32_t cached = __ballot_sync(0xffffffffu, have && cur != 0u);
-            const uint32_t miss = in_range & ~cached;
-            uint32_t touch = 0;  // leading cached blocks: hits, their access time becomes the trace's
-            if (alive) {
-                touch = miss != 0 ? cached & ((1u << (__ffs(miss) - 1)) - 1u) : cached;
-                const uint32_t masked = __ballot_sync(
-                    0xffffffffu, i < skip || (ty == 1 && p.mask_bits != nullptr && have && p.mask_bits[beg + i] != 0));
-                ext += __popc(touch & ~masked);
-                inte += __popc(touch & masked);
-                if (miss != 0) alive = false;
-            }
-            const uint32_t write = ty == 1 ? 0u : miss;  // then the missing blocks are written, in order
-            if ((touch >> lane) & 1u) {
-                ts[cur - 1] = now;  // OnBlockAccessed
-            } else if ((write >> lane) & 1u) {
-                const int64_t at = my_size + __popc(write & lt);  // OnBlockWritten: appended in key order
-                blk[at] = id;
-                ts[at] = now;
-                pos[id] = static_cast<uint32_t>(at) + 1u;
-            }
-            const uint32_t n_write = __popc(write);
-            my_size += n_write;
-            resident += n_write;
-            wr += static_cast<int32_t>(n_write);
-            __syncwarp();
-            if (ty == 1 && !alive) break;
-        }
-        __syncwarp();
-        if (lane == 0) size_of[me] = my_size;
+        const int64_t my_size = size_of[me];
+        const SamplingTraceCounts c = SamplingReplayTrace(
+            p.ids + beg, p.mask_bits != nullptr ? p.mask_bits + beg : nullptr, n, ty, skip, now, pos,
+            blk_all + base_of[me], ts_all + base_of[me], my_size, lane);
+        resident += c.wr;
+        if (lane == 0) size_of[me] = my_size + c.wr;
         __syncwarp();
         if (ty != 1 && resident > quota) {
             // CheckAndEvict over the usage of the whole group: in turns over the instances, a batch each, until a
@@ -343,18 +136,18 @@ __global__ void __launch_bounds__(32) RandomLruSweepKernel(const RandomSweep p) 
             resident -= total;
         }
         if (lane == 0 && p.ext_hit != nullptr) {
-            p.ext_hit[out0 + t] = ext;
-            p.int_hit[out0 + t] = inte;
-            p.written[out0 + t] = wr;
+            p.ext_hit[out0 + t] = c.ext;
+            p.int_hit[out0 + t] = c.inte;
+            p.written[out0 + t] = c.wr;
             p.cache_blocks[out0 + t] = size_of[me];
         }
         if (p.inst_blocks_trace != nullptr) {  // ReadRecord::blocks_per_instance of the reference's result records
             int64_t *row = p.inst_blocks_trace + (out0 + t) * K;
             for (int32_t j = lane; j < K; j += 32) row[j] = size_of[j];
         }
-        sum_ext += ext;
-        sum_int += inte;
-        sum_wr += wr;
+        sum_ext += c.ext;
+        sum_int += c.inte;
+        sum_wr += c.wr;
     }
     if (lane == 0 && p.totals != nullptr) {
         int64_t *tot = p.totals + static_cast<int64_t>(cfg) * 4;

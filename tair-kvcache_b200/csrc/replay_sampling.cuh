@@ -1,0 +1,252 @@
+// The "random_lru" eviction policy as a warp runs it: RandomLruEvictionPolicy
+// (kv_cache_manager/optimizer/eviction_policy/random_lru.cc:5-131, random_lru.h:13-47) over per-key state.
+// Shared by the sweep of sampling instances alone (replay_random_lru.cu) and the sweep of groups that mix the
+// policies (replay_leaf_lru.cu).
+//
+// The policy's own state is what the reference keeps: a dense vector of the cached blocks beside their last access
+// times, a key's index in it, and the state of its xorshift generator.
+//   pos[id]   kNotCached, else the block's index in blk / ts
+//   blk[i]    id of the block at index i; ts[i] its last access time; i < size
+// A round of evictions (EvictBlocks, random_lru.cc:38-57) draws `sampling_size` indices with replacement
+// (FastRand, :121-131), orders the first k of them by access time with std::partial_sort (:59-82) and removes those
+// blocks by swap-and-pop (:84-103).  Blocks written or read by one trace share a timestamp, so WHICH of several
+// equally old samples go depends on the order std::partial_sort leaves equal elements in.  That order is a
+// property of the algorithm the C++ standard library documents for it - heap-select followed by sort-heap on a
+// binary max-heap with hole-based sift-down and sift-up - which is restated below, step for step, on the sample
+// held in shared memory; the CPU oracle calls std::partial_sort itself, and the parity tests compare the two on
+// traces full of tied timestamps.
+// The generator is sequential, the heap is sequential: both run in lane 0 (the raw draws first, the modulo of all
+// draws then in parallel; the times of the sampled indices are gathered by all lanes).  The removals are
+// sequential too - every one changes the index of the block that was last - but run out of shared memory: the
+// tail of the block vector is staged there, and the victims' indices are kept current by a warp-wide scan.
+#pragma once
+#include "kvcm_common.cuh"
+
+namespace kvcm {
+namespace {
+
+constexpr uint32_t kMaxSample = KVCM_B200_RANDOM_LRU_MAX_SAMPLE;  // sampled indices per round held in shared memory
+constexpr uint32_t kMaxBatch = KVCM_B200_RANDOM_LRU_MAX_BATCH;    // blocks evicted per round
+constexpr uint32_t kNotCached = 0xFFFFFFFFu;
+constexpr uint64_t kSamplingSeed = 0x12345678ABCDEF01ull;  // random_lru.h:20; every policy object starts from it
+
+// The sample: index into the block vector and that block's time, moved together.
+struct Sample {
+    uint32_t *idx;
+    int64_t *t;
+    __host__ __device__ __forceinline__ void Move(uint32_t to, uint32_t from) {
+        idx[to] = idx[from];
+        t[to] = t[from];
+    }
+    __host__ __device__ __forceinline__ void Put(uint32_t to, uint32_t i, int64_t time) {
+        idx[to] = i;
+        t[to] = time;
+    }
+};
+
+// Sift-up of `value` from `hole` towards `top` in a max-heap ordered by time (the standard library's push-heap step).
+__host__ __device__ __forceinline__ void PushHeap(Sample &s, uint32_t hole, uint32_t top, uint32_t v_idx, int64_t v_t) {
+    while (hole > top) {
+        const uint32_t parent = (hole - 1) / 2;
+        if (!(s.t[parent] < v_t)) break;
+        s.Move(hole, parent);
+        hole = parent;
+    }
+    s.Put(hole, v_idx, v_t);
+}
+
+// The hole at `hole` sinks to a leaf along the larger children (the right child unless it is smaller than the
+// left), then `value` is sifted up from there: the standard library's adjust-heap step.
+__host__ __device__ __forceinline__ void AdjustHeap(Sample &s, uint32_t hole, uint32_t len, uint32_t v_idx, int64_t v_t) {
+    const uint32_t top = hole;
+    uint32_t child = hole;
+    while (child < (len - 1) / 2) {
+        child = 2 * (child + 1);
+        if (s.t[child] < s.t[child - 1]) --child;
+        s.Move(hole, child);
+        hole = child;
+    }
+    if ((len & 1u) == 0 && child == (len - 2) / 2) {
+        child = 2 * (child + 1);
+        s.Move(hole, child - 1);
+        hole = child - 1;
+    }
+    PushHeap(s, hole, top, v_idx, v_t);
+}
+
+// std::partial_sort(first, first + k, first + n) by time: heap-select, then sort-heap.
+__host__ __device__ void PartialSortByTime(Sample &s, uint32_t k, uint32_t n) {
+    if (k == 0) return;
+    if (k >= 2) {  // make-heap over the first k
+        uint32_t parent = (k - 2) / 2;
+        while (true) {
+            const uint32_t vi = s.idx[parent];
+            const int64_t vt = s.t[parent];
+            AdjustHeap(s, parent, k, vi, vt);
+            if (parent == 0) break;
+            --parent;
+        }
+    }
+    for (uint32_t i = k; i < n; ++i) {  // an element older than the heap's top takes its place
+        if (s.t[i] < s.t[0]) {
+            const uint32_t vi = s.idx[i];
+            const int64_t vt = s.t[i];
+            s.Move(i, 0);
+            AdjustHeap(s, 0, k, vi, vt);
+        }
+    }
+    for (uint32_t last = k; last > 1;) {  // sort-heap
+        --last;
+        const uint32_t vi = s.idx[last];
+        const int64_t vt = s.t[last];
+        s.Move(last, 0);
+        AdjustHeap(s, 0, last, vi, vt);
+    }
+}
+
+// One warp's shared memory for a round of evictions.
+struct SamplingScratch {
+    int64_t s_t[kMaxSample];  // the sampled blocks' times (the raw draws before that)
+    int64_t tail_ts[kMaxBatch];  // ts / blk of the last entries of the vector, [j] = index size - 1 - j
+    uint32_t s_idx[kMaxSample];  // the sampled indices
+    uint32_t v_id[kMaxBatch], v_at[kMaxBatch];  // the round's victims: block id, current index
+    uint32_t tail_blk[kMaxBatch];
+};
+
+// RandomLruEvictionPolicy::EvictBlocks(count) (random_lru.cc:38-103) on a block vector of `held` entries; all lanes,
+// returns how many blocks went (the caller keeps the vector's length).  *rng is the generator's state, in shared
+// memory.
+__device__ __forceinline__ uint32_t SamplingEvictRound(SamplingScratch &sc, uint32_t *pos, uint32_t *blk, int64_t *ts,
+                                                       int64_t held, uint64_t *rng, uint32_t sampling_size,
+                                                       int64_t count, uint32_t lane) {
+    if (held == 0) return 0u;
+    const uint32_t n_blocks = static_cast<uint32_t>(held);
+    const uint32_t want = count < held ? static_cast<uint32_t>(count) : n_blocks;  // total_to_evict
+    const uint32_t n_sample = sampling_size < n_blocks ? sampling_size : n_blocks;
+    const uint32_t k = want < n_sample ? want : n_sample;
+    Sample sample{sc.s_idx, sc.s_t};
+    // the draws, in sequence (lane 0), then their modulo and the sampled blocks' times (all lanes)
+    if (lane == 0) {
+        uint64_t x = *rng;
+        uint64_t *raw = reinterpret_cast<uint64_t *>(sc.s_t);
+        for (uint32_t i = 0; i < n_sample; ++i) {
+            x ^= x << 13;
+            x ^= x >> 7;
+            x ^= x << 17;
+            raw[i] = x;
+        }
+        *rng = x;
+    }
+    __syncwarp();
+    for (uint32_t i = lane; i < n_sample; i += 32) {
+        const uint32_t at = static_cast<uint32_t>(reinterpret_cast<uint64_t *>(sc.s_t)[i] % n_blocks);
+        sc.s_idx[i] = at;
+        sc.s_t[i] = ts[at];
+    }
+    __syncwarp();
+    if (lane == 0) PartialSortByTime(sample, k, n_sample);
+    __syncwarp();
+    // the victims as blocks (resolved before the first removal, as the reference resolves them), and the tail
+    // of the vector, which the removals read
+    const uint32_t n_tail = k < n_blocks ? k : n_blocks;
+    for (uint32_t i = lane; i < k; i += 32) {
+        sc.v_at[i] = sc.s_idx[i];
+        sc.v_id[i] = blk[sc.s_idx[i]];
+    }
+    for (uint32_t i = lane; i < n_tail; i += 32) {
+        sc.tail_blk[i] = blk[n_blocks - 1 - i];
+        sc.tail_ts[i] = ts[n_blocks - 1 - i];
+    }
+    __syncwarp();
+    uint32_t evicted = 0;
+    uint32_t size = n_blocks;
+    for (uint32_t i = 0; i < k && evicted < want; ++i) {
+        const uint32_t at = sc.v_at[i];
+        if (at == kNotCached) continue;  // sampled twice: removed already
+        const uint32_t id = sc.v_id[i];
+        const uint32_t last = size - 1;
+        const uint32_t moved = sc.tail_blk[n_blocks - 1 - last];  // the block that sits last now
+        const int64_t moved_t = sc.tail_ts[n_blocks - 1 - last];
+        if (lane == 0) {
+            if (at != last) {
+                blk[at] = moved;
+                ts[at] = moved_t;
+                pos[moved] = at;
+                if (n_blocks - 1 - at < n_tail) {  // the staged tail follows
+                    sc.tail_blk[n_blocks - 1 - at] = moved;
+                    sc.tail_ts[n_blocks - 1 - at] = moved_t;
+                }
+            }
+            pos[id] = kNotCached;
+        }
+        __syncwarp();
+        // later victims: further samples of this block are gone; the moved block has a new index
+        for (uint32_t v = i + 1 + lane; v < k; v += 32) {
+            if (sc.v_at[v] == kNotCached) continue;
+            if (sc.v_id[v] == id) {
+                sc.v_at[v] = kNotCached;
+            } else if (at != last && sc.v_id[v] == moved) {
+                sc.v_at[v] = at;
+            }
+        }
+        __syncwarp();
+        --size;
+        ++evicted;
+    }
+    return evicted;
+}
+
+// One trace of a sampling instance: its leading cached blocks are hits and take the trace's time
+// (OnBlockAccessed), then - unless the trace only reads - its missing blocks are appended in key order
+// (OnBlockWritten).  ids / mask_bits point at the trace's first key (mask_bits may be null); size is the length of the
+// block vector before the trace.  All lanes; the counts come back equal in all lanes.
+// type: 0 DialogTurn (InsertWithQuery), 1 GetLocation (PrefixQuery), 2 WriteCache (InsertOnly).
+struct SamplingTraceCounts {
+    int32_t ext, inte, wr;
+};
+
+__device__ __forceinline__ SamplingTraceCounts SamplingReplayTrace(const uint32_t *ids, const uint8_t *mask_bits,
+                                                                   int64_t n, uint8_t ty, int64_t skip, int64_t now,
+                                                                   uint32_t *pos, uint32_t *blk, int64_t *ts,
+                                                                   int64_t size, uint32_t lane) {
+    const uint32_t lt = (1u << lane) - 1u;
+    SamplingTraceCounts c{0, 0, 0};
+    bool alive = ty != 2;  // still inside the leading run of cached blocks
+    for (int64_t base = 0; base < n; base += 32) {
+        const int64_t i = base + lane;
+        const bool have = i < n;
+        const uint32_t id = have ? ids[i] : 0u;
+        const uint32_t cur = have ? pos[id] : kNotCached;
+        const uint32_t in_range = __ballot_sync(0xffffffffu, have);
+        const uint32_t cached = __ballot_sync(0xffffffffu, have && cur != kNotCached);
+        const uint32_t miss = in_range & ~cached;
+        uint32_t touch = 0;  // leading cached blocks: hits, their access time becomes the trace's
+        if (alive) {
+            touch = miss != 0 ? cached & ((1u << (__ffs(miss) - 1)) - 1u) : cached;
+            const uint32_t masked = __ballot_sync(
+                0xffffffffu, i < skip || (ty == 1 && mask_bits != nullptr && have && mask_bits[i] != 0));
+            c.ext += __popc(touch & ~masked);
+            c.inte += __popc(touch & masked);
+            if (miss != 0) alive = false;
+        }
+        const uint32_t write = ty == 1 ? 0u : miss;  // then the missing blocks are written, in order
+        if ((touch >> lane) & 1u) {
+            ts[cur] = now;
+        } else if ((write >> lane) & 1u) {
+            const int64_t at = size + __popc(write & lt);
+            blk[at] = id;
+            ts[at] = now;
+            pos[id] = static_cast<uint32_t>(at);
+        }
+        const uint32_t n_write = __popc(write);
+        size += n_write;
+        c.wr += static_cast<int32_t>(n_write);
+        __syncwarp();
+        if (ty == 1 && !alive) break;
+    }
+    __syncwarp();
+    return c;
+}
+
+}  // namespace
+}  // namespace kvcm

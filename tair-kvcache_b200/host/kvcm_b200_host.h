@@ -449,17 +449,42 @@ public:
                               int32_t n_instances, int64_t quota_blocks, int32_t evict_batch, int32_t eviction_mode,
                               std::vector<ReplayRecord> *records, std::vector<int64_t> *instance_blocks = nullptr,
                               bool leaf_aware = false) {
+        if (n_instances <= 0) {
+            records->assign(traces.size(), ReplayRecord{0, 0, 0, 0});
+            return KVCM_EC_BADARGS;
+        }
+        const std::vector<uint8_t> policy_of(static_cast<size_t>(n_instances),
+                                             leaf_aware ? KVCM_POLICY_LEAF_AWARE_LRU : KVCM_POLICY_LRU);
+        return RunTracesPolicyGroup(traces, instance_of, policy_of, {}, quota_blocks, evict_batch, eviction_mode, records,
+                                    instance_blocks);
+    }
+
+    // The same for a group whose instances name their eviction_policy_type one by one, as the reference's
+    // configuration lets them (EvictionPolicyFactory::CreatePolicy per instance,
+    // kv_cache_manager/optimizer/eviction_policy/policy_factory.cc:8-47): policy_of[j] is KVCM_POLICY_LRU,
+    // KVCM_POLICY_LEAF_AWARE_LRU or KVCM_POLICY_RANDOM_LRU, sample_rate_of[j] the eviction_policy_params.sample_rate
+    // of a random_lru instance (empty = the policy's default for all).
+    int32_t RunTracesPolicyGroup(const std::vector<ReplayTrace> &traces, const std::vector<int32_t> &instance_of,
+                                 const std::vector<uint8_t> &policy_of, const std::vector<double> &sample_rate_of,
+                                 int64_t quota_blocks, int32_t evict_batch, int32_t eviction_mode,
+                                 std::vector<ReplayRecord> *records, std::vector<int64_t> *instance_blocks = nullptr) {
         const int32_t n = static_cast<int32_t>(traces.size());
+        const int32_t n_instances = static_cast<int32_t>(policy_of.size());
         records->assign(n, ReplayRecord{0, 0, 0, 0});
-        if (instance_blocks != nullptr) instance_blocks->assign(n_instances > 0 ? n_instances : 0, 0);
-        if (instance_of.size() != traces.size() || n_instances <= 0) return KVCM_EC_BADARGS;
+        if (instance_blocks != nullptr) instance_blocks->assign(n_instances, 0);
+        if (instance_of.size() != traces.size() || n_instances <= 0 ||
+            (!sample_rate_of.empty() && sample_rate_of.size() != policy_of.size())) {
+            return KVCM_EC_BADARGS;
+        }
         if (n == 0) return KVCM_OK;
+        bool queues_only = true;  // every instance "lru": the sweep that keeps no tree
+        for (uint8_t policy : policy_of) queues_only = queues_only && policy == KVCM_POLICY_LRU;
         int64_t n_keys = 0;
         int32_t rc = Pack(traces, &n_keys);
         if (rc != KVCM_OK) return rc;
-        const int64_t ws_bytes = leaf_aware
-                                     ? kvcm_b200_replay_leaf_lru_group_workspace_bytes(n_keys, n, 1, n_instances)
-                                     : kvcm_b200_replay_lru_group_workspace_bytes(n_keys, 1, n_instances);
+        const int64_t ws_bytes =
+            queues_only ? kvcm_b200_replay_lru_group_workspace_bytes(n_keys, 1, n_instances)
+                        : kvcm_b200_replay_policy_group_workspace_bytes(n_keys, n, 1, policy_of.data(), n_instances);
         if (ws_bytes < 0) return KVCM_EC_OUT_OF_LIMIT;
         if (!Outputs(n, 1) || !quota_.Reserve(sizeof(int64_t)) || !inst_.Reserve(sizeof(int32_t) * n) ||
             !inst_blocks_.Reserve(sizeof(int64_t) * n_instances) ||
@@ -471,12 +496,13 @@ public:
         if (!quota_.ToDevice(sizeof(int64_t), stream_) || !inst_.ToDevice(sizeof(int32_t) * n, stream_)) {
             return KVCM_ER_CUDAMEMCPY_ERROR;
         }
-        if (leaf_aware) {
-            rc = kvcm_b200_replay_leaf_lru_group(
+        if (!queues_only) {
+            rc = kvcm_b200_replay_policy_group(
                 keys_.dev<int64_t>(), off_.dev<int64_t>(), kind_.dev<uint8_t>(), mask_.dev<int64_t>(), nullptr, nullptr,
-                inst_.dev<int32_t>(), n_instances, n, n_keys, quota_.dev<int64_t>(), 1, evict_batch, eviction_mode,
-                workspace_.dev<void>(), ws_bytes, ext_.dev<int32_t>(), int_.dev<int32_t>(), wr_.dev<int32_t>(),
-                size_.dev<int64_t>(), nullptr, inst_blocks_.dev<int64_t>(), nullptr, nullptr, stream_);
+                inst_.dev<int32_t>(), policy_of.data(), sample_rate_of.empty() ? nullptr : sample_rate_of.data(),
+                n_instances, n, n_keys, quota_.dev<int64_t>(), 1, evict_batch, eviction_mode, workspace_.dev<void>(),
+                ws_bytes, ext_.dev<int32_t>(), int_.dev<int32_t>(), wr_.dev<int32_t>(), size_.dev<int64_t>(), nullptr,
+                inst_blocks_.dev<int64_t>(), nullptr, nullptr, stream_);
         } else {
             rc = kvcm_b200_replay_lru_group(keys_.dev<int64_t>(), off_.dev<int64_t>(), kind_.dev<uint8_t>(),
                                             mask_.dev<int64_t>(), nullptr, inst_.dev<int32_t>(), n_instances, n,

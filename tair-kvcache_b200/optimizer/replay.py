@@ -189,15 +189,18 @@ def RunTracesLruGroup(keys: torch.Tensor, key_off: torch.Tensor, trace_type: tor
     instance_records=True also returns the usage of every instance after each trace (the reference's
     ReadRecord::blocks_per_instance, which fills two columns of its hit-rate CSV).  policy is the
     eviction_policy_type of every instance of the group, or a sequence with one name per instance (a group may mix
-    "lru" and "leaf_aware_lru"; "random_lru" only when every instance uses it, with sample_rate one number or one per
-    instance); timestamps (int64 per trace, the traces' timestamp_us) is read by "leaf_aware_lru" instances, which
-    order re-queued blocks by it, and by "random_lru" ones, which pick the oldest of their samples (the trace number
-    when None)."""
+    "lru", "leaf_aware_lru" and "random_lru" as the reference's configuration may; sample_rate is one number or one
+    per instance and is read for the "random_lru" instances); timestamps (int64 per trace, the traces'
+    timestamp_us) is read by "leaf_aware_lru" instances, which order re-queued blocks by it, and by "random_lru"
+    ones, which pick the oldest of their samples (the trace number when None)."""
     each = [policy] * int(n_instances) if isinstance(policy, str) else list(policy)
-    sampling = set(each) == {"random_lru"}
-    if len(each) != int(n_instances) or (not sampling and any(e not in ("lru", "leaf_aware_lru") for e in each)):
-        raise ValueError("eviction policies %r: groups of instances replay \"lru\" and \"leaf_aware_lru\" (one name "
-                         "per instance, mixed or not) or \"random_lru\" in every instance" % (policy,))
+    sampling = set(each) == {"random_lru"}  # nothing but sampling instances: no tree is kept
+    if len(each) != int(n_instances) or any(e not in ("lru", "leaf_aware_lru", "random_lru") for e in each):
+        raise ValueError("eviction policies %r: one of \"lru\", \"leaf_aware_lru\", \"random_lru\" for the group or "
+                         "one per instance" % (policy,))
+    rates = [sample_rate] * len(each) if isinstance(sample_rate, (int, float)) else list(sample_rate)
+    if len(rates) != len(each):
+        raise ValueError("sample_rate: one number, or one per instance")
     if not keys.is_cuda:
         raise ValueError("keys must be a CUDA tensor: this path has no CPU implementation")
     dev = keys.device
@@ -209,10 +212,15 @@ def RunTracesLruGroup(keys: torch.Tensor, key_off: torch.Tensor, trace_type: tor
     if trace_instance.dtype != torch.int32 or trace_instance.numel() != n_traces or trace_instance.device != dev:
         raise ValueError("trace_instance must be an int32 tensor with one entry per trace, on the keys' device")
     trace_instance = trace_instance.contiguous()
-    leaf = any(e == "leaf_aware_lru" for e in each)  # one such instance and the group needs the trees
+    # one leaf-aware instance, or a sampling instance beside others, and the group needs the kernel that keeps trees
+    leaf = not sampling and any(e != "lru" for e in each)
+    import ctypes
+    codes = {"lru": _cabi.POLICY_LRU, "leaf_aware_lru": _cabi.POLICY_LEAF_AWARE_LRU, "random_lru": _cabi.POLICY_RANDOM_LRU}
+    policy_bytes = (ctypes.c_uint8 * len(each))(*[codes[e] for e in each])
+    rate_doubles = (ctypes.c_double * len(each))(*[float(r) for r in rates])
     if leaf:
-        need = _cabi.lib().kvcm_b200_replay_leaf_lru_group_workspace_bytes(keys.numel(), n_traces, n_cfg,
-                                                                          int(n_instances))
+        need = _cabi.lib().kvcm_b200_replay_policy_group_workspace_bytes(
+            keys.numel(), n_traces, n_cfg, ctypes.cast(policy_bytes, ctypes.c_void_p), int(n_instances))
     elif sampling:
         need = _cabi.lib().kvcm_b200_replay_random_lru_group_workspace_bytes(keys.numel(), n_cfg, int(n_instances))
     else:
@@ -242,27 +250,20 @@ def RunTracesLruGroup(keys: torch.Tensor, key_off: torch.Tensor, trace_type: tor
             raise ValueError("timestamps must be an int64 tensor with one entry per trace, on the keys' device")
         timestamps = timestamps.contiguous()
     if sampling:
-        import ctypes
-        rates = [sample_rate] * len(each) if isinstance(sample_rate, (int, float)) else list(sample_rate)
-        if len(rates) != len(each):
-            raise ValueError("sample_rate: one number, or one per instance")
-        per_instance = (ctypes.c_double * len(each))(*[float(r) for r in rates])
         _cabi.call("kvcm_b200_replay_random_lru_group", keys.data_ptr(), key_off.data_ptr(), trace_type.data_ptr(),
                    mask_off.contiguous().data_ptr() if mask_off is not None else None, _mask_bits_ptr(mask_bits, keys),
                    timestamps.data_ptr() if timestamps is not None else None, trace_instance.data_ptr(),
-                   ctypes.cast(per_instance, ctypes.c_void_p), int(n_instances), n_traces, keys.numel(),
+                   ctypes.cast(rate_doubles, ctypes.c_void_p), int(n_instances), n_traces, keys.numel(),
                    quota.data_ptr(), n_cfg, int(evict_batch), int(mode), workspace.data_ptr(), workspace.numel(),
                    ptr(ext), ptr(inte), ptr(wr), ptr(size), totals.data_ptr(), inst.data_ptr(), ptr(per_inst),
                    status.data_ptr() if status is not None else None, torch.cuda.current_stream(dev).cuda_stream)
         return LruGroupSweepResult(ext, inte, wr, size, totals, inst, per_inst)
     if leaf:
-        import ctypes
-        per_instance = (ctypes.c_uint8 * len(each))(*[_cabi.POLICY_LRU if e == "lru" else _cabi.POLICY_LEAF_AWARE_LRU
-                                                      for e in each])
-        _cabi.call("kvcm_b200_replay_tree_group", keys.data_ptr(), key_off.data_ptr(), trace_type.data_ptr(),
+        _cabi.call("kvcm_b200_replay_policy_group", keys.data_ptr(), key_off.data_ptr(), trace_type.data_ptr(),
                    mask_off.contiguous().data_ptr() if mask_off is not None else None, _mask_bits_ptr(mask_bits, keys),
                    timestamps.data_ptr() if timestamps is not None else None, trace_instance.data_ptr(),
-                   ctypes.cast(per_instance, ctypes.c_void_p), int(n_instances), n_traces, keys.numel(), quota.data_ptr(), n_cfg, int(evict_batch), int(mode),
+                   ctypes.cast(policy_bytes, ctypes.c_void_p), ctypes.cast(rate_doubles, ctypes.c_void_p),
+                   int(n_instances), n_traces, keys.numel(), quota.data_ptr(), n_cfg, int(evict_batch), int(mode),
                    workspace.data_ptr(), workspace.numel(), ptr(ext), ptr(inte), ptr(wr), ptr(size), totals.data_ptr(),
                    inst.data_ptr(), ptr(per_inst), status.data_ptr() if status is not None else None,
                    torch.cuda.current_stream(dev).cuda_stream)

@@ -82,8 +82,8 @@ def replay_group(traces: List[tr.Trace], instance_ids: Sequence[str], device, qu
                  rw_separation: bool = False, evict_batch: int = 100, mode: int = 1,
                  policy="lru", sample_rate=0.0, timeline: Optional[list] = None) -> Dict[str, Dict[str, np.ndarray]]:
     """Replays the traces of the instances of ONE group that share a quota (every instance under `policy`, or one
-    name per instance in the order of `instance_ids`: "lru" and "leaf_aware_lru" in any mix, or "random_lru"
-    throughout with `sample_rate` one number or one per instance), in the order given (all instances together, by timestamp), and returns one record per
+    name per instance in the order of `instance_ids`, in any mix; `sample_rate` is one number or one per instance,
+    read for "random_lru" instances), in the order given (all instances together, by timestamp), and returns one record per
     instance as replay_instance does.  mode is the configuration's eviction_mode (1 group rough, 2 instance rough, 3 instance precise;
     kv_cache_manager/optimizer/manager/eviction_manager.cc:57-239).  current_cache_blocks is the usage of the
     trace's own instance; blocks_per_instance [record, instance] is the usage of every instance of the group at
@@ -272,10 +272,10 @@ EVICTION_MODE_UNSPECIFIED, EVICTION_MODE_GROUP_ROUGH, EVICTION_MODE_INSTANCE_ROU
 def parse_startup_config(config: Union[str, dict]) -> dict:
     """The Optimizer's startup configuration (kv_cache_manager/optimizer/optimizer_startup_config_load.json, read
     by kv_cache_manager/optimizer/config/optimizer_config.cc:4-12, instance_group_config.cc:5-12,
-    instance_config.cc:6-22, eviction_config.cc:5-8) reduced to what the GPU replay needs.  Raises
-    NotImplementedError for what it cannot replay exactly: groups of several instances that mix "random_lru" with
-    another policy (groups of "lru" and "leaf_aware_lru" instances, mixed or not, and groups of "random_lru"
-    instances come back under "groups").
+    instance_config.cc:6-22, eviction_config.cc:5-8) reduced to what the GPU replay needs.  Groups of several
+    instances that share a quota come back under "groups", with one policy name for all or one per instance (any
+    mix of the three policies).  Raises NotImplementedError for an eviction policy the reference's factory does not
+    know either.
     hierarchical_eviction_enabled: the reference creates an eviction policy for the FIRST storage tier only (later
     tiers never evict, kv_cache_manager/optimizer/manager/eviction_manager.cc:26-39), every block gets its location
     on that tier alone (kv_cache_manager/optimizer/index/radix_tree_index.cc:327-353), so erasing that location on
@@ -300,14 +300,10 @@ def parse_startup_config(config: Union[str, dict]) -> dict:
         group_quota = int(capacity * float(group.get("used_percentage", 1.0)))
         together = len(instances) > 1 and mode != EVICTION_MODE_UNSPECIFIED
         used = [i.get("eviction_policy_type", "lru") for i in instances]
-        if together and set(used) != {"random_lru"} and any(u not in ("lru", "leaf_aware_lru") for u in used):
-            raise NotImplementedError("group %r: %d instances share one quota under %s; replayed are groups of "
-                                      "\"lru\" and \"leaf_aware_lru\" instances and groups of \"random_lru\" instances"
-                                      % (group.get("group_name"), len(instances), ", ".join(map(repr, sorted(set(used))))))
         if together:
             shared.append(dict(group_name=group.get("group_name"), instances=[str(i["instance_id"]) for i in instances],
                                quota=group_quota, policy=used[0] if len(set(used)) == 1 else used))
-            if used[0] == "random_lru":
+            if "random_lru" in used:
                 shared[-1]["sample_rate"] = [float((i.get("eviction_policy_params") or {}).get("sample_rate", 0.0))
                                              for i in instances]
         for inst in instances:

@@ -321,6 +321,29 @@ static void TestReplay() {
     EXPECT_EQ(rec[6].current_cache_blocks, 2);
     EXPECT_EQ(usage[0], 3);
     EXPECT_EQ(usage[1], 1);
+    // An "lru" instance a and a "random_lru" instance b (sample_rate 1, batches of 1: one index is drawn per round)
+    // share a quota of 4, group rough.  RandomLruEvictionPolicy's generator (random_lru.h:20, random_lru.cc:121-131)
+    // starts at 0x12345678ABCDEF01; its first draw is odd, its second a multiple of 3.  a writes 1 2 3, b writes 4 5:
+    // a loses 1 and b - draw mod 2 = 1 - loses 5, where a queue would have taken 4; so b's read of 4 5 hits once.
+    // b writes 4 5 7 (two new blocks): a loses 2 and b - draw mod 3 = 0 - loses 4, 7 takes its place.
+    const std::vector<ReplayTrace> sampled = {
+        {TraceKind::WriteCache, {1, 2, 3}}, {TraceKind::WriteCache, {4, 5}}, {TraceKind::GetLocation, {4, 5}},
+        {TraceKind::GetLocation, {1, 2, 3}}, {TraceKind::WriteCache, {4, 5, 7}}, {TraceKind::GetLocation, {4, 5, 7}}};
+    EXPECT_EQ(replayer.RunTracesPolicyGroup(sampled, {0, 1, 1, 0, 1, 1}, {KVCM_POLICY_LRU, KVCM_POLICY_RANDOM_LRU},
+                                            {0.0, 1.0}, 4, 1, 1, &rec, &usage),
+              KVCM_OK);
+    EXPECT_EQ(rec[2].external_hit_blocks, 1);
+    EXPECT_EQ(rec[3].external_hit_blocks, 0);
+    EXPECT_EQ(rec[4].write_blocks, 2);
+    EXPECT_EQ(rec[5].external_hit_blocks, 0);
+    EXPECT_EQ(usage[0], 1);
+    EXPECT_EQ(usage[1], 2);
+    EXPECT_EQ(replayer.RunTracesPolicyGroup(sampled, {0, 1, 1, 0, 1, 1}, {KVCM_POLICY_LRU, KVCM_POLICY_LRU}, {}, 4, 1, 1,
+                                            &rec, &usage),
+              KVCM_OK);
+    EXPECT_EQ(rec[2].external_hit_blocks, 0);  // the queue takes 4, and 4 5 is no hit without its first block
+    EXPECT_EQ(replayer.RunTracesPolicyGroup(sampled, {0, 1, 1, 0, 1, 1}, {KVCM_POLICY_LRU, 7}, {}, 4, 1, 1, &rec, &usage),
+              KVCM_EC_OUT_OF_LIMIT);
 }
 
 int main() {

@@ -58,30 +58,34 @@ def replay_cases():
                (["leaf_aware_lru"] * 3, "three leaf_aware_lru instances"),
                (["lru", "leaf_aware_lru", "lru"], "lru and leaf_aware_lru instances mixed"),
                (["random_lru"] * 2, "two random_lru instances")]
-    for policies, what in layouts:
-        for mode in (1, 2, 3):
-            for rw in (True, False):
-                keys, off, types, mask, ts = workload(rng, 70, rw)
-                k = len(policies)
-                inst = rng.integers(0, k, size=len(types)).astype(np.int32)
-                rates = [float(r) for r in rng.choice([0.1, 0.25, 0.5, 1.0], size=k)]
-                use_bits = bool(rng.random() < 0.3) and rw
-                bits = (rng.random(len(keys)) < 0.25).astype(np.uint8) if use_bits else None
-                batch = int(rng.integers(1, 9))
-                runs = []
-                for quota in (int(rng.integers(3, 25)), int(rng.integers(40, 200))):
-                    r = ref.RefOptimizer([dict(quota_capacity=quota,
-                                               instances=[(str(j), p, rates[j]) for j, p in enumerate(policies)])],
-                                         evict_batch=batch, mode=mode)
-                    ext, inte, wr, cached, every = r.run(keys, off, types, inst, None if use_bits else mask, bits, ts)
-                    runs.append(dict(quota=quota, external_hit_blocks=ext.tolist(), internal_hit_blocks=inte.tolist(),
-                                     write_blocks=wr.tolist(), instance_blocks=cached.tolist(),
-                                     blocks_of_every_instance=every.tolist()))
-                cases.append(dict(name="%s, mode %d, %s" % (what, mode, "read/write" if rw else "turns"),
-                                  policies=policies, sample_rates=rates, mode=mode, evict_batch=batch,
-                                  keys=keys.tolist(), key_off=off.tolist(), types=types.tolist(),
-                                  instance=inst.tolist(), mask_off=None if use_bits else mask.tolist(),
-                                  mask_bits=bits.tolist() if use_bits else None, timestamps=ts.tolist(), runs=runs))
+
+    def record(layouts):
+        for policies, what in layouts:
+            for mode in (1, 2, 3):
+                for rw in (True, False):
+                    keys, off, types, mask, ts = workload(rng, 70, rw)
+                    k = len(policies)
+                    inst = rng.integers(0, k, size=len(types)).astype(np.int32)
+                    rates = [float(r) for r in rng.choice([0.1, 0.25, 0.5, 1.0], size=k)]
+                    use_bits = bool(rng.random() < 0.3) and rw
+                    bits = (rng.random(len(keys)) < 0.25).astype(np.uint8) if use_bits else None
+                    batch = int(rng.integers(1, 9))
+                    runs = []
+                    for quota in (int(rng.integers(3, 25)), int(rng.integers(40, 200))):
+                        r = ref.RefOptimizer([dict(quota_capacity=quota,
+                                                   instances=[(str(j), p, rates[j]) for j, p in enumerate(policies)])],
+                                             evict_batch=batch, mode=mode)
+                        ext, inte, wr, cached, every = r.run(keys, off, types, inst, None if use_bits else mask, bits, ts)
+                        runs.append(dict(quota=quota, external_hit_blocks=ext.tolist(), internal_hit_blocks=inte.tolist(),
+                                         write_blocks=wr.tolist(), instance_blocks=cached.tolist(),
+                                         blocks_of_every_instance=every.tolist()))
+                    cases.append(dict(name="%s, mode %d, %s" % (what, mode, "read/write" if rw else "turns"),
+                                      policies=policies, sample_rates=rates, mode=mode, evict_batch=batch,
+                                      keys=keys.tolist(), key_off=off.tolist(), types=types.tolist(),
+                                      instance=inst.tolist(), mask_off=None if use_bits else mask.tolist(),
+                                      mask_bits=bits.tolist() if use_bits else None, timestamps=ts.tolist(), runs=runs))
+
+    record(layouts)
     # hierarchical eviction: the first tier's capacity x used_percentage is the quota
     keys, off, types, mask, ts = workload(rng, 120, False)
     r = ref.RefOptimizer([dict(quota_capacity=10 ** 9, hierarchical=True, tier_capacity=120, used_percentage=0.5,
@@ -96,6 +100,11 @@ def replay_cases():
                                  blocks_of_every_instance=every.tolist())],
                       startup_group=dict(quota_capacity=10 ** 9, used_percentage=0.5,
                                          hierarchical_eviction_enabled=True, storages=[dict(capacity=120)])))
+    # sampling instances beside queueing ones in one group (recorded after the cases above so that those keep their
+    # workloads)
+    record([(["random_lru", "lru", "leaf_aware_lru"], "all three policies mixed"),
+            (["leaf_aware_lru", "random_lru"], "leaf_aware_lru and random_lru instances"),
+            (["random_lru", "lru", "random_lru", "leaf_aware_lru"], "two random_lru instances among four")])
     return cases
 
 
@@ -193,6 +202,9 @@ def csv_cases():
     # shows in every record), one of them with an instance that no trace names
     plans += [("publisher_log", [[("inst_a", "lru")], [("inst_b", "leaf_aware_lru")]], 3, 20),
               ("optimizer_schema", [[("inst_a", "leaf_aware_lru"), ("idle", "lru")], [("inst_b", "random_lru")]], 1, 18)]
+    # a sampling instance and a queueing one share a quota
+    plans += [("optimizer_schema", [("inst_a", "random_lru"), ("inst_b", "leaf_aware_lru")], 1, 20),
+              ("publisher_log", [("inst_a", "lru"), ("inst_b", "random_lru")], 2, 15)]
     for trace_type, instances, mode, quota in plans:
         with tempfile.TemporaryDirectory() as tmp:
             path = os.path.join(tmp, "trace.jsonl")

@@ -138,7 +138,7 @@ def test_group_of_sampling_instances_against_the_oracle(mode):
             assert np.array_equal(a, b[c]), (name, q)
 
 
-def test_one_sampling_instance_as_a_group_and_refused_mixtures():
+def test_one_sampling_instance_as_a_group_and_refused_arguments():
     from tair_kvcache_b200.optimizer import RunTracesLruGroup
     rng = np.random.default_rng(710)
     keys, off, types, mask, ts = _workload(rng, 600, True)
@@ -151,8 +151,8 @@ def test_one_sampling_instance_as_a_group_and_refused_mixtures():
                                 policy=POLICY, sample_rate=0.2, timestamps=torch.from_numpy(ts).to(DEV))
         for a, b in zip(one, grp[:4]):
             assert np.array_equal(a, b.cpu().numpy())
-    with pytest.raises(ValueError):  # a sampling instance beside a queueing one is not replayed
-        RunTracesLruGroup(*args, zeros, 2, quotas, policy=["lru", POLICY])
+    with pytest.raises(ValueError):  # a policy the reference's factory does not know
+        RunTracesLruGroup(*args, zeros, 2, quotas, policy=["fifo", POLICY])
     with pytest.raises(_cabi.KvcmError) as e:  # the sample of one of the instances would not fit shared memory
         RunTracesLruGroup(*args, zeros, 2, quotas, evict_batch=300, policy=POLICY, sample_rate=[0.5, 0.1])
     assert e.value.code == _cabi.KVCM_EC_OUT_OF_LIMIT

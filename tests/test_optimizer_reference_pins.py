@@ -2,8 +2,8 @@
 
 tests/golden/optimizer_ref_kat.json and optimizer_ref_csv.json were written by tests/golden/make_optimizer_golden.py
 from the reference's optimizer sources compiled in place (oracle/_ref/libkvcm_ref_optimizer.so): per-trace records of
-its runner for the three eviction policies, instance groups in the three eviction modes, mixed groups, offset and
-vector masks, a hierarchical group; and the CSV files its optimizer_main path writes for small trace files in the
+its runner for the three eviction policies, instance groups in the three eviction modes, groups that mix two or all
+three policies, offset and vector masks, a hierarchical group; and the CSV files its optimizer_main path writes for small trace files in the
 three input formats.  The reference's own tests cover none of this beyond plain LRU with one instance, so these
 fixtures are what pins the oracle (and, through it and directly, the GPU kernels: tests/test_gpu_optimizer_pins.py).
 Where the compiled reference is present (a container that holds the reference tree), the oracle is also compared
@@ -37,7 +37,7 @@ def oracle_group(case, quota):
 
 def test_oracle_replays_what_the_reference_recorded():
     kat = load_golden("optimizer_ref_kat.json")
-    assert len(kat["cases"]) >= 40
+    assert len(kat["cases"]) >= 60
     seen = set()
     for case in kat["cases"]:
         for run in case["runs"]:
@@ -46,9 +46,10 @@ def test_oracle_replays_what_the_reference_recorded():
                 assert np.array_equal(np.asarray(run[name]), got), (case["name"], run["quota"], name)
             seen.add((tuple(case["policies"]), case["mode"]))
             assert max(run["instance_blocks"]) > 0
-    # every policy alone and in groups, lru and leaf-aware mixed, all three eviction modes
+    # every policy alone and in groups, the policies mixed in one group, all three eviction modes
     for policies in (("lru",), ("leaf_aware_lru",), ("random_lru",), ("lru",) * 3, ("leaf_aware_lru",) * 3,
-                     ("lru", "leaf_aware_lru", "lru"), ("random_lru",) * 2):
+                     ("lru", "leaf_aware_lru", "lru"), ("random_lru",) * 2, ("random_lru", "lru", "leaf_aware_lru"),
+                     ("leaf_aware_lru", "random_lru"), ("random_lru", "lru", "random_lru", "leaf_aware_lru")):
         for mode in (1, 2, 3):
             assert (policies, mode) in seen
 

@@ -132,8 +132,8 @@ def test_startup_config_of_the_reference_is_understood():
     cfg["instance_groups"][0]["instances"][0]["eviction_policy_type"] = "leaf_aware_lru"
     assert parse_startup_config(cfg)["groups"][0]["policy"] == "leaf_aware_lru"  # the same policy throughout
     cfg["instance_groups"][0]["instances"][1]["eviction_policy_type"] = "random_lru"
-    with pytest.raises(NotImplementedError):  # a sampling instance beside a queueing one in a shared quota
-        parse_startup_config(cfg)
+    g = parse_startup_config(cfg)["groups"][0]  # a sampling instance beside a queueing one in a shared quota
+    assert g["policy"] == ["leaf_aware_lru", "random_lru"] and g["sample_rate"] == [0.1, 0.0]
     cfg["instance_groups"][0]["instances"][0]["eviction_policy_type"] = "random_lru"
     g = parse_startup_config(cfg)["groups"][0]  # sampling instances only: replayed, each with its own rate
     assert g["policy"] == "random_lru" and g["sample_rate"] == [0.1, 0.0]
