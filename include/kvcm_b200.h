@@ -51,6 +51,7 @@ extern "C" {
 #define KVCM_EC_BASE 1000
 #define KVCM_EC_ERROR (KVCM_EC_BASE + 1)            /* EC_ERROR */
 #define KVCM_EC_NOENT (KVCM_EC_BASE + 2)            /* EC_NOENT */
+#define KVCM_EC_EXIST (KVCM_EC_BASE + 4)            /* EC_EXIST: the key has a location of that class already */
 #define KVCM_EC_BADARGS (KVCM_EC_BASE + 6)          /* EC_BADARGS */
 #define KVCM_EC_NOSPC (KVCM_EC_BASE + 9)            /* EC_NOSPC: index full */
 #define KVCM_EC_OUT_OF_LIMIT (KVCM_EC_BASE + 14)    /* EC_OUT_OF_LIMIT: size beyond a fixed limit */
@@ -385,6 +386,26 @@ KVCM_API int32_t kvcm_b200_index_update_status_sharded(kvcm_b200_index_t *index,
                                                        const uint32_t *d_tasks, uint32_t uniform_task, int64_t n,
                                                        int32_t shard_count, int32_t shard_rank,
                                                        int32_t *d_results, kvcm_stream_t stream);
+
+/* One new location per key, merged into the key's location map on the device: the counterpart of
+ * MetaSearcher::BatchAddLocation (kv_cache_manager/manager/meta_searcher.cc:312-408), which reads the key's map or
+ * starts an empty one, adds the location and writes the map back.  Key i gets a location of storage class
+ * d_classes[i] (or `uniform_class` when d_classes is NULL; classes 0..7) in status `status_of_new` -
+ * BatchAddLocation always adds in CLS_WRITING (2); a key that is absent is inserted, a key that is present keeps its
+ * other locations (the merge is a compare-and-swap on the value word, so several tasks of one launch on the same key
+ * take turns).  d_results[i]: KVCM_OK; KVCM_EC_EXIST when the key already holds a location of that class - the
+ * word keeps one status per class, where the reference would add a second location under a fresh id;
+ * KVCM_EC_NOSPC when the table is full (also counted in d_status[0], as kvcm_b200_index_upsert counts it);
+ * KVCM_EC_BADARGS for a class above 7.  The sharded form touches only the keys the shard owns and leaves the other
+ * results as they are. */
+KVCM_API int32_t kvcm_b200_index_add_location(kvcm_b200_index_t *index, const int64_t *d_keys,
+                                              const uint8_t *d_classes, int32_t uniform_class, int32_t status_of_new,
+                                              int64_t n, int32_t *d_results, uint32_t *d_status, kvcm_stream_t stream);
+KVCM_API int32_t kvcm_b200_index_add_location_sharded(kvcm_b200_index_t *index, const int64_t *d_keys,
+                                                      const uint8_t *d_classes, int32_t uniform_class,
+                                                      int32_t status_of_new, int64_t n, int32_t shard_count,
+                                                      int32_t shard_rank, int32_t *d_results, uint32_t *d_status,
+                                                      kvcm_stream_t stream);
 
 /* d_values_out[i] = stored value of key i, 0 when absent (MetaIndexer::Get -> EC_NOENT). */
 KVCM_API int32_t kvcm_b200_index_lookup(kvcm_b200_index_t *index, const int64_t *d_keys, int64_t n,

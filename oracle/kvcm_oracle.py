@@ -216,6 +216,15 @@ class Index:
                                               _ptr(nw, ctypes.c_int32), _ptr(res, ctypes.c_int32))
         return res
 
+    def add_location(self, keys, types, status=CLS_WRITING):
+        """MetaSearcher::BatchAddLocation (kv_cache_manager/manager/meta_searcher.cc:312-408): key i gets one more
+        location of storage type types[i] (the reference adds it in CLS_WRITING); an absent key is created, a present
+        one keeps its other locations.  A plain loop over get / put: small cases only."""
+        keys = _i64(keys)
+        types = np.broadcast_to(np.asarray(types, dtype=np.int32), (len(keys),))
+        for k, t in zip(keys.tolist(), types.tolist()):
+            self.put([k], [(self.get(k) or []) + [(int(status), int(t))]])
+
     def get(self, key):
         """The (status, storage type) list of one key, or None when the key is absent."""
         st = np.zeros(64, dtype=np.int32)

@@ -21,6 +21,7 @@ KVCM_EC_BASE = 1000
 KVCM_EC_ERROR = KVCM_EC_BASE + 1
 KVCM_EC_NOENT = KVCM_EC_BASE + 2
 KVCM_EC_BADARGS = KVCM_EC_BASE + 6
+KVCM_EC_EXIST = KVCM_EC_BASE + 4
 KVCM_EC_NOSPC = KVCM_EC_BASE + 9
 KVCM_EC_OUT_OF_LIMIT = KVCM_EC_BASE + 14
 KVCM_EC_MISMATCH = KVCM_EC_BASE + 16
@@ -100,6 +101,8 @@ SIGNATURES = {
     "kvcm_b200_index_set_auto_rehash": [_vp, _i64],
     "kvcm_b200_index_update_status": [_vp, _vp, _vp, _u32, _i64, _vp, _vp],
     "kvcm_b200_index_update_status_sharded": [_vp, _vp, _vp, _u32, _i64, _i32, _i32, _vp, _vp],
+    "kvcm_b200_index_add_location": [_vp, _vp, _vp, _i32, _i32, _i64, _vp, _vp, _vp],
+    "kvcm_b200_index_add_location_sharded": [_vp, _vp, _vp, _i32, _i32, _i64, _i32, _i32, _vp, _vp, _vp],
     "kvcm_b200_index_upsert": [_vp, _vp, _vp, _u64, _i64, _vp, _vp],
     "kvcm_b200_index_erase": [_vp, _vp, _i64, _vp],
     "kvcm_b200_index_lookup": [_vp, _vp, _i64, _vp, _vp],

@@ -187,8 +187,15 @@ __device__ __forceinline__ void AddCell(uint64_t *cell, int64_t delta) {
 // kCareful: the launch could push the slots in use past the bound, so every claim of an EMPTY slot takes a seat
 // on the shared counter first.  Otherwise (the host knows that even if every key of the launch claimed one the bound
 // holds) nothing is counted on the way: the caller sums `d_live` and `d_used` per warp and adds them once.
-template <bool kCareful>
-__device__ __forceinline__ bool UpsertOne(const IndexView &ix, uint64_t key, uint64_t value, int32_t *d_live,
+// What is done to the value word once the key's slot is known: `put(word)`.  Overwrite stores a whole word;
+// MergeLocation (further down) adds one location to the word that is there.
+struct Overwrite {
+    uint64_t value;
+    __device__ __forceinline__ void operator()(unsigned long long *word) const { atomicExch(word, value); }
+};
+
+template <bool kCareful, typename Put>
+__device__ __forceinline__ bool UpsertOne(const IndexView &ix, uint64_t key, Put &put, int32_t *d_live,
                                           int32_t *d_used) {
     unsigned long long *words = reinterpret_cast<unsigned long long *>(ix.slots);
     const uint64_t mixed = Mix(key);
@@ -205,7 +212,7 @@ __device__ __forceinline__ bool UpsertOne(const IndexView &ix, uint64_t key, uin
         for (uint64_t probe = 0; probe <= ix.mask; ++probe) {
             const uint64_t seen = LoadSlot(ix.slots + slot).x;
             if (seen == key) {  // present already (or inserted by a duplicate of this key in the same batch)
-                atomicExch(&words[2 * slot + 1], value);
+                put(&words[2 * slot + 1]);
                 found = true;
                 break;
             }
@@ -221,7 +228,7 @@ __device__ __forceinline__ bool UpsertOne(const IndexView &ix, uint64_t key, uin
         } else if (tomb != ~0ull) {
             const uint64_t was = atomicCAS(&words[2 * tomb], kTombKey, key);
             if (was == kTombKey || was == key) {
-                atomicExch(&words[2 * tomb + 1], value);
+                put(&words[2 * tomb + 1]);
                 if (was == kTombKey) {
                     ix.tags[tomb] = TagOf(mixed);  // readers of later launches find the slot through its tag
                     *d_live += 1;
@@ -241,14 +248,14 @@ __device__ __forceinline__ bool UpsertOne(const IndexView &ix, uint64_t key, uin
             }
             const uint64_t was = atomicCAS(&words[2 * empty], kEmptyKey, key);
             if (was == kEmptyKey) {
-                atomicExch(&words[2 * empty + 1], value);
+                put(&words[2 * empty + 1]);
                 ix.tags[empty] = TagOf(mixed);
                 *d_live += 1;
                 if (!kCareful) *d_used += 1;  // in careful mode the seat is this slot's count already
                 return true;
             }
             if (was == key) {
-                atomicExch(&words[2 * empty + 1], value);
+                put(&words[2 * empty + 1]);
                 done = stored = true;
             }  // else another key took the slot: walk again, seat kept
         }
@@ -281,8 +288,11 @@ __global__ void __launch_bounds__(256)
                 const uint64_t old =
                     atomicExch(reinterpret_cast<unsigned long long *>(&ix.cells[key - kEmptyKey]), value);
                 if (old == 0) d_live = 1;
-            } else if (!UpsertOne<kCareful>(ix, key, value, &d_live, &d_used) && status != nullptr) {
-                atomicAdd(&status[0], 1u);
+            } else {
+                Overwrite put{value};
+                if (!UpsertOne<kCareful>(ix, key, put, &d_live, &d_used) && status != nullptr) {
+                    atomicAdd(&status[0], 1u);
+                }
             }
         }
     }
@@ -452,6 +462,64 @@ __global__ void UpdateStatusKernel(IndexView ix, const int64_t *__restrict__ key
     results[i] = code;
 }
 
+// ---- a new location for a key (MetaSearcher::BatchAddLocation, kv_cache_manager/manager/meta_searcher.cc:312-408:
+// read the key's location map or start an empty one, add the location in status CLS_WRITING, write the map back).
+// Here: find the key's slot or claim one as an insert does, then merge the location of the task's class into the
+// word that is there with a compare-and-swap, so that tasks of one launch on the same key take turns and the key's
+// other locations stay.  The word keeps one status per class, so a class that holds a location already is refused
+// with KVCM_EC_EXIST where the reference would add a second location under a fresh id.
+struct MergeLocation {
+    uint32_t cls, status;
+    int32_t code;
+    bool into_empty_word;  // the word was 0 when this location went in
+    __device__ __forceinline__ void operator()(unsigned long long *word) {
+        unsigned long long seen = *reinterpret_cast<volatile unsigned long long *>(word);
+        code = KVCM_EC_ERROR;
+        into_empty_word = false;
+        for (int turn = 0; turn < 1024; ++turn) {
+            if (seen != 0 && StatusField(seen, cls) != 0) {
+                code = KVCM_EC_EXIST;
+                return;
+            }
+            const unsigned long long next = seen | KVCM_VAL_PRESENT | KVCM_VAL_LOCATION(cls, status);
+            const unsigned long long was = atomicCAS(word, seen, next);
+            if (was == seen) {
+                code = KVCM_OK;
+                into_empty_word = seen == 0;
+                return;
+            }
+            seen = was;
+        }
+    }
+};
+
+template <bool kCareful>
+__global__ void __launch_bounds__(256)
+    AddLocationKernel(IndexView ix, const int64_t *__restrict__ keys, const uint8_t *__restrict__ classes,
+                      uint32_t uniform_class, uint32_t status_of_new, int64_t n, Shard shard,
+                      int32_t *__restrict__ results, uint32_t *status) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    int32_t d_live = 0, d_used = 0;
+    if (i < n) {
+        const uint64_t key = static_cast<uint64_t>(keys[i]);
+        if (Owns(shard, key)) {
+            MergeLocation put{classes != nullptr ? classes[i] : uniform_class, status_of_new, KVCM_EC_ERROR, false};
+            if (put.cls > 7) {
+                put.code = KVCM_EC_BADARGS;
+            } else if (key == kEmptyKey || key == kTombKey) {
+                // the two reserved key values live in cells of the header; an empty cell is an absent key
+                put(reinterpret_cast<unsigned long long *>(&ix.cells[key - kEmptyKey]));
+                if (put.into_empty_word) d_live = 1;
+            } else if (!UpsertOne<kCareful>(ix, key, put, &d_live, &d_used)) {
+                put.code = KVCM_EC_NOSPC;  // the table is full
+                if (status != nullptr) atomicAdd(&status[0], 1u);
+            }
+            results[i] = put.code;
+        }
+    }
+    AddCellsPerWarp(ix, d_live, d_used);
+}
+
 // ---- rebuilding the table in place: live pairs out to a workspace, table reset, pairs back in.  Drops every
 // tombstone, so probe chains are as short again as in a freshly filled table.
 __global__ void CollectLiveKernel(IndexView ix, ulonglong2 *__restrict__ pairs, unsigned long long *counter) {
@@ -491,7 +559,8 @@ __global__ void ReinsertKernel(IndexView ix, const ulonglong2 *__restrict__ pair
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
         int32_t d_live = 0, d_used = 0;
-        if (!UpsertOne<false>(ix, pairs[i].x, pairs[i].y, &d_live, &d_used) && status != nullptr) {
+        Overwrite put{pairs[i].y};
+        if (!UpsertOne<false>(ix, pairs[i].x, put, &d_live, &d_used) && status != nullptr) {
             atomicAdd(&status[0], 1u);
         }
         if (d_live != 0) AddCell(&ix.cells[2], d_live);  // the pairs fitted before: no bound to watch
@@ -1185,6 +1254,50 @@ int32_t kvcm_b200_index_update_status_sharded(kvcm_b200_index_t *ix, const int64
     return UpdateStatus(ix, d_keys, d_tasks, uniform_task, n,
                         kvcm::Shard{static_cast<uint32_t>(shard_count), static_cast<uint32_t>(shard_rank)}, d_results,
                         stream);
+}
+
+static int32_t AddLocation(kvcm_b200_index_t *ix, const int64_t *d_keys, const uint8_t *d_classes,
+                           int32_t uniform_class, int32_t status_of_new, int64_t n, kvcm::Shard shard,
+                           int32_t *d_results, uint32_t *d_status, kvcm_stream_t stream) {
+    if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (n < 0 || status_of_new < 0 || status_of_new > 4 || (d_classes == nullptr && (uniform_class < 0 || uniform_class > 7))) {
+        return KVCM_EC_BADARGS;
+    }
+    if (n == 0) return KVCM_OK;
+    if (d_keys == nullptr || d_results == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    MaybeRehash(ix, stream);
+    const bool careful = ix->used_upper + static_cast<uint64_t>(n) > ix->max_live;
+    ix->used_upper += static_cast<uint64_t>(n);
+    if (ix->used_upper > ix->n_slots) ix->used_upper = ix->n_slots;
+    const unsigned grid = kvcm::GridFor(n, 256);
+    const uint32_t cls = static_cast<uint32_t>(d_classes == nullptr ? uniform_class : 0);
+    if (careful) {
+        kvcm::AddLocationKernel<true><<<grid, 256, 0, kvcm::AsStream(stream)>>>(
+            kvcm::LocalView(ix), d_keys, d_classes, cls, static_cast<uint32_t>(status_of_new), n, shard, d_results,
+            d_status);
+    } else {
+        kvcm::AddLocationKernel<false><<<grid, 256, 0, kvcm::AsStream(stream)>>>(
+            kvcm::LocalView(ix), d_keys, d_classes, cls, static_cast<uint32_t>(status_of_new), n, shard, d_results,
+            d_status);
+    }
+    return kvcm::LaunchStatus();
+}
+
+int32_t kvcm_b200_index_add_location(kvcm_b200_index_t *ix, const int64_t *d_keys, const uint8_t *d_classes,
+                                     int32_t uniform_class, int32_t status_of_new, int64_t n, int32_t *d_results,
+                                     uint32_t *d_status, kvcm_stream_t stream) {
+    return AddLocation(ix, d_keys, d_classes, uniform_class, status_of_new, n, kvcm::Shard{1, 0}, d_results, d_status,
+                       stream);
+}
+
+int32_t kvcm_b200_index_add_location_sharded(kvcm_b200_index_t *ix, const int64_t *d_keys, const uint8_t *d_classes,
+                                             int32_t uniform_class, int32_t status_of_new, int64_t n,
+                                             int32_t shard_count, int32_t shard_rank, int32_t *d_results,
+                                             uint32_t *d_status, kvcm_stream_t stream) {
+    if (shard_count < 1 || shard_rank < 0 || shard_rank >= shard_count) return KVCM_EC_BADARGS;
+    return AddLocation(ix, d_keys, d_classes, uniform_class, status_of_new, n,
+                       kvcm::Shard{static_cast<uint32_t>(shard_count), static_cast<uint32_t>(shard_rank)}, d_results,
+                       d_status, stream);
 }
 
 static void LaunchUpsert(kvcm_b200_index_t *ix, const int64_t *d_keys, const uint64_t *d_values, uint64_t uniform_value,

@@ -142,6 +142,35 @@ class BlockIndex:
                        out.data_ptr(), self._s())
         return out
 
+    def add_location(self, keys: torch.Tensor, classes, status: int = CLS_WRITING, shard: Optional[Tuple[int, int]] = None,
+                     out: Optional[torch.Tensor] = None, table_full: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One new location per key, merged into the key's location map on the device
+        (MetaSearcher::BatchAddLocation, kv_cache_manager/manager/meta_searcher.cc:312-408): `classes` is one storage
+        class for all keys or a uint8 CUDA tensor with one per key, `status` the CacheLocationStatus the location
+        starts in (CLS_WRITING = 2, as the reference adds it).  An absent key is inserted, a present key keeps its
+        other locations.  Returns the int32 result code per key (0, KVCM_EC_EXIST when the key already holds a
+        location of that class, KVCM_EC_NOSPC when the table is full, KVCM_EC_BADARGS for a class above 7);
+        table_full (uint32 CUDA tensor) counts the refused keys in its first word.  shard=(count, rank) limits the
+        call to the keys this shard owns."""
+        keys = _keys(keys, self.device)
+        if out is None:
+            out = torch.zeros(keys.numel(), dtype=torch.int32, device=self.device)
+        d_classes, uniform = None, 0
+        if isinstance(classes, torch.Tensor):
+            d_classes = classes.to(torch.uint8).contiguous()
+            if d_classes.numel() != keys.numel() or d_classes.device != self.device:
+                raise ValueError("one storage class per key, on the index's device")
+        else:
+            uniform = int(classes)
+        args = [self._h, keys.data_ptr(), d_classes.data_ptr() if d_classes is not None else None, uniform, int(status),
+                keys.numel()]
+        tail = [out.data_ptr(), table_full.data_ptr() if table_full is not None else None, self._s()]
+        if shard is None:
+            _cabi.call("kvcm_b200_index_add_location", *args, *tail)
+        else:
+            _cabi.call("kvcm_b200_index_add_location_sharded", *args, shard[0], shard[1], *tail)
+        return out
+
     def upsert(self, keys: torch.Tensor, values: Optional[torch.Tensor] = None, uniform_value: int = 0,
                status: Optional[torch.Tensor] = None):
         """keys int64 CUDA; values uint64-as-int64 CUDA tensor of value words, or one word for all."""

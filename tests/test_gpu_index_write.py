@@ -212,3 +212,99 @@ def test_explicit_rehash_drops_tombstones_and_keeps_values():
     with pytest.raises(_cabi.KvcmError):                   # a workspace that is too small is refused, nothing runs
         small = torch.empty(1024, dtype=torch.uint8, device=DEV)
         _cabi.call("kvcm_b200_index_rehash", ix.handle, small.data_ptr(), small.numel(), None, ix._s())
+
+
+def test_add_location_write_cycle_of_the_reference():
+    """StartWriteCache adds a location in CLS_WRITING, FinishWriteCache turns it to CLS_SERVING
+    (MetaSearcher::BatchAddLocation + BatchUpdateLocationStatus, kv_cache_manager/manager/meta_searcher.cc:312-487):
+    the matchers see the keys only after the second step, and a second tier's location leaves the first alone."""
+    ix, ox = BlockIndex(64), oracle.Index()
+    keys = np.array([11, 12, 13, -(1 << 63), -(1 << 63) + 1], dtype=np.int64)  # with the two reserved values
+    dk = torch.from_numpy(keys).to(DEV)
+    assert not ix.add_location(dk, 4).cpu().numpy().any()
+    ox.add_location(keys, 4)
+    _check_against_oracle(ix, ox, keys)
+    assert ix.stats()[1] == 5
+    ko = torch.tensor([0, 5], dtype=torch.int64, device=DEV)
+    assert int(BatchMetaSearcher(ix).PrefixMatch(dk, ko).cpu()[0]) == 0       # written, not served yet
+    assert not ix.update_status(dk, status_task(4, oracle.CLS_WRITING, oracle.CLS_SERVING)).cpu().numpy().any()
+    ox.update_status(keys, 4, oracle.CLS_WRITING, oracle.CLS_SERVING)
+    assert int(BatchMetaSearcher(ix).PrefixMatch(dk, ko).cpu()[0]) == 5
+    # a location on another tier for three of them: the served one stays
+    classes = torch.tensor([2, 2, 0], dtype=torch.uint8, device=DEV)
+    assert not ix.add_location(dk[1:4], classes).cpu().numpy().any()
+    ox.add_location(keys[1:4], [2, 2, 0])
+    _check_against_oracle(ix, ox, keys)
+    assert int(BatchMetaSearcher(ix).PrefixMatch(dk, ko).cpu()[0]) == 5 and ix.stats()[1] == 5
+    # the word keeps one status per class: a second location of a class is refused, nothing changes
+    again = ix.add_location(dk, 4).cpu().numpy()
+    assert (again == _cabi.KVCM_EC_EXIST).all()
+    _check_against_oracle(ix, ox, keys)
+    assert (ix.add_location(dk, torch.full((5,), 9, dtype=torch.uint8, device=DEV)).cpu().numpy()
+            == _cabi.KVCM_EC_BADARGS).all()
+    with pytest.raises(_cabi.KvcmError):
+        ix.add_location(dk, 8)
+    with pytest.raises(_cabi.KvcmError):
+        ix.add_location(dk, 4, status=5)
+
+
+def test_add_location_random_rounds_against_the_oracle():
+    """Adds, transitions and deletions interleaved; several tasks of one launch may name the same key with different
+    classes (they take turns on the word), and a key whose last location went away comes back through an add."""
+    rng = np.random.default_rng(21)
+    universe = np.unique(rng.integers(-(1 << 63), (1 << 63) - 1, size=600, dtype=np.int64))
+    universe = np.concatenate([universe, np.array([-(1 << 63), -(1 << 63) + 1], dtype=np.int64)])
+    ix, ox = BlockIndex(len(universe)), oracle.Index()
+    full = torch.zeros(4, dtype=torch.int32, device=DEV)
+    exist = 0
+    for round_no in range(40):
+        if round_no % 3 != 2:
+            # up to three tasks per key in one launch, each on a class of its own
+            pick = universe[rng.permutation(len(universe))[:150]]
+            reps = rng.integers(1, 4, size=len(pick))
+            batch = np.repeat(pick, reps)
+            classes = np.concatenate([rng.permutation(6)[:r] for r in reps]).astype(np.uint8)
+            status = int(rng.integers(0, 5))
+            order = rng.permutation(len(batch))
+            batch, classes = batch[order], classes[order]
+            free = np.array([all(t != c for _, t in (ox.get(int(k)) or [])) for k, c in zip(batch, classes)])
+            got = ix.add_location(torch.from_numpy(batch).to(DEV), torch.from_numpy(classes).to(DEV), status,
+                                  table_full=full).cpu().numpy()
+            assert np.array_equal(got, np.where(free, 0, _cabi.KVCM_EC_EXIST)), round_no
+            exist += int((~free).sum())
+            ox.add_location(batch[free], classes[free], status)
+        else:
+            batch = universe[rng.permutation(len(universe))[:300]]   # no key twice: the order would matter
+            types = rng.integers(0, 6, size=len(batch))
+            expected = rng.choice([-1, 0, 1, 2, 3, 4], size=len(batch))
+            new = rng.choice([-2, -1, -1, 3], size=len(batch))
+            want = ox.update_status(batch, types, expected, new)
+            got = ix.update_status(torch.from_numpy(batch).to(DEV), _tasks(types, expected, new)).cpu().numpy()
+            assert np.array_equal(got, np.array([EC[int(r)] for r in want], dtype=np.int32)), round_no
+        _check_against_oracle(ix, ox, universe)
+        assert ix.stats()[1] == len(ox), round_no
+    assert full[0].item() == 0 and exist > 50
+
+
+def test_add_location_full_table_and_shards():
+    ix = BlockIndex(8)
+    slots = ix.stats()[0]
+    keys = torch.arange(1, 4 * slots + 1, dtype=torch.int64, device=DEV)
+    full = torch.zeros(4, dtype=torch.int32, device=DEV)
+    got = ix.add_location(keys, 3, table_full=full).cpu().numpy()
+    refused = int((got == _cabi.KVCM_EC_NOSPC).sum())
+    assert refused > 0 and refused == full[0].item() and set(got.tolist()) <= {0, _cabi.KVCM_EC_NOSPC}
+    assert ix.stats()[1] == len(keys) - refused
+    held = ix.lookup(keys).cpu().numpy() != 0
+    assert np.array_equal(held, got == 0)
+    # three shards: every key is added by exactly its owner
+    rng = np.random.default_rng(6)
+    k = np.unique(rng.integers(-(1 << 62), 1 << 62, size=1500, dtype=np.int64))
+    dk = torch.from_numpy(k).to(DEV)
+    shards = [BlockIndex(len(k)) for _ in range(3)]
+    out = torch.full((len(k),), -1, dtype=torch.int32, device=DEV)
+    for r, sh in enumerate(shards):
+        sh.add_location(dk, 1, shard=(3, r), out=out)
+    assert not out.cpu().numpy().any() and sum(sh.stats()[1] for sh in shards) == len(k)
+    for sh in shards:
+        assert all(_decode(x) in (None, [(oracle.CLS_WRITING, 1)]) for x in sh.lookup(dk).cpu().numpy())

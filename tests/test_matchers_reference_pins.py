@@ -135,3 +135,41 @@ def test_hash_and_prefix_match_of_a_batch_of_requests():
     keys, ko = oracle.hash_blocks(toks, off, bs, threads=2)
     want = r.prefix_match_batch(toks, off, bs, threads=4)
     assert np.array_equal(want, ox.prefix_match_batch(keys, ko, threads=2)) and want.sum() > 100
+
+
+def test_locations_added_between_transitions():
+    """BatchAddLocation on keys that hold other locations already, that lost their last location to a compare-and-
+    delete, or that BatchDeleteLocation left behind with an empty map (kv_cache_manager/manager/
+    meta_searcher.cc:312-408 between the transitions of :410-820): the oracle's add_location against the reference's,
+    seen through what the matchers answer afterwards and through the codes of the transitions that follow."""
+    rng = np.random.default_rng(2027)
+    universe, locs, r, ox = _random_world(rng, 200, fill=0.15)
+    known = np.array(sorted(locs), dtype=np.int64)
+    fresh = universe[~np.isin(universe, known)][:30]
+    pool = np.concatenate([known, fresh])
+    added = 0
+    for round_ in range(50):
+        if round_ % 2 == 0:
+            ty, st = int(rng.integers(0, 5)), int(rng.choice(STATUSES))
+            # one location per storage type and key, as the device's value word holds them
+            cand = pool[rng.permutation(len(pool))[:25]]
+            keys = np.array([k for k in cand if all(t != ty for _, t in (ox.get(int(k)) or []))], dtype=np.int64)
+            if len(keys) == 0:
+                continue
+            r.add(keys, ty, st)
+            ox.add_location(keys, ty, st)
+            added += len(keys)
+        else:
+            op = int(rng.integers(1, 4))
+            keys = pool[rng.permutation(len(pool))[:40]]
+            types = rng.integers(0, 5, size=len(keys)).astype(np.int32)
+            expected = rng.choice(STATUSES, size=len(keys)).astype(np.int32)
+            new = rng.choice(STATUSES, size=len(keys)).astype(np.int32)
+            rc, want = r.status(op, keys, types, expected, new)
+            got = ox.update_status(keys, types, expected if op != ref.OP_DELETE else -1,
+                                   new if op == ref.OP_CAS else (-1 if op == ref.OP_CAD else -2))
+            assert np.array_equal(want, got), (round_, op)
+        servable, nonempty = r.batch_get(pool)
+        flags = ox.batch_get(pool)
+        assert np.array_equal(servable, flags & 1) and np.array_equal(nonempty, (flags >> 2) & 1), round_
+    assert added > 200
