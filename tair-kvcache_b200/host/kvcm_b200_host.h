@@ -209,10 +209,70 @@ public:
         return rc != KVCM_OK ? rc : detail::Sync(stream_);
     }
 
+    // MetaSearcher::BatchAddLocation (kv_cache_manager/manager/meta_searcher.cc:312-408) on the replica: key i gets a
+    // location of storage class `classes[i]` (DataStorageType's number; one entry = the same class for all) in
+    // CLS_WRITING, merged into the key's map on the device.  (*results)[i]: KVCM_OK, KVCM_EC_EXIST, KVCM_EC_NOSPC.
+    int32_t AddLocation(const KeyVector &keys, const std::vector<uint8_t> &classes, std::vector<int32_t> *results,
+                        int32_t status = 2 /* CLS_WRITING */) {
+        const size_t n = keys.size();
+        results->assign(n, KVCM_OK);
+        if (classes.size() != n && classes.size() != 1) return KVCM_EC_BADARGS;
+        if (n == 0) return KVCM_OK;
+        const bool uniform = classes.size() == 1 && n != 1;
+        if (!keys_.Reserve(sizeof(int64_t) * n) || !vals_.Reserve(sizeof(uint64_t) * n) ||
+            !codes_.Reserve(sizeof(int32_t) * n)) {
+            return KVCM_EC_NOSPC;
+        }
+        std::memcpy(keys_.host<int64_t>(), keys.data(), sizeof(int64_t) * n);
+        if (!uniform) std::memcpy(vals_.host<uint8_t>(), classes.data(), n);
+        if (!keys_.ToDevice(sizeof(int64_t) * n, stream_) || (!uniform && !vals_.ToDevice(n, stream_))) {
+            return KVCM_ER_CUDAMEMCPY_ERROR;
+        }
+        const int32_t rc = kvcm_b200_index_add_location(index_, keys_.dev<int64_t>(),
+                                                        uniform ? nullptr : vals_.dev<uint8_t>(),
+                                                        uniform ? classes[0] : 0, status, static_cast<int64_t>(n),
+                                                        codes_.dev<int32_t>(), nullptr, stream_);
+        return rc != KVCM_OK ? rc : FetchCodes(n, results);
+    }
+
+    // MetaSearcher::BatchUpdateLocationStatus / BatchCASLocationStatus / BatchCADLocationStatus / BatchDeleteLocation
+    // (meta_searcher.cc:410-820) on the replica: tasks[i] = KVCM_STATUS_TASK(class, expected, new); one entry = the
+    // same task for all keys (FinishWriteCache of a batch).  (*results)[i]: KVCM_OK, KVCM_EC_NOENT, KVCM_EC_MISMATCH.
+    int32_t UpdateLocationStatus(const KeyVector &keys, const std::vector<uint32_t> &tasks,
+                                 std::vector<int32_t> *results) {
+        const size_t n = keys.size();
+        results->assign(n, KVCM_OK);
+        if (tasks.size() != n && tasks.size() != 1) return KVCM_EC_BADARGS;
+        if (n == 0) return KVCM_OK;
+        const bool uniform = tasks.size() == 1 && n != 1;
+        if (!keys_.Reserve(sizeof(int64_t) * n) || !vals_.Reserve(sizeof(uint64_t) * n) ||
+            !codes_.Reserve(sizeof(int32_t) * n)) {
+            return KVCM_EC_NOSPC;
+        }
+        std::memcpy(keys_.host<int64_t>(), keys.data(), sizeof(int64_t) * n);
+        if (!uniform) std::memcpy(vals_.host<uint32_t>(), tasks.data(), sizeof(uint32_t) * n);
+        if (!keys_.ToDevice(sizeof(int64_t) * n, stream_) || (!uniform && !vals_.ToDevice(sizeof(uint32_t) * n, stream_))) {
+            return KVCM_ER_CUDAMEMCPY_ERROR;
+        }
+        const int32_t rc = kvcm_b200_index_update_status(index_, keys_.dev<int64_t>(),
+                                                         uniform ? nullptr : vals_.dev<uint32_t>(),
+                                                         uniform ? tasks[0] : 0, static_cast<int64_t>(n),
+                                                         codes_.dev<int32_t>(), stream_);
+        return rc != KVCM_OK ? rc : FetchCodes(n, results);
+    }
+
 private:
+    int32_t FetchCodes(size_t n, std::vector<int32_t> *results) {
+        if (!codes_.ToHost(sizeof(int32_t) * n, stream_)) return KVCM_ER_CUDAMEMCPY_ERROR;
+        const int32_t rc = detail::Sync(stream_);
+        if (rc != KVCM_OK) return rc;
+        std::memcpy(results->data(), codes_.host<int32_t>(), sizeof(int32_t) * n);
+        return KVCM_OK;
+    }
+
     cudaStream_t stream_;
     kvcm_b200_index_t *index_ = nullptr;
-    detail::Mirror keys_, vals_;
+    detail::Mirror keys_, vals_, codes_;
 };
 
 // The matchers of MetaSearcher over a GpuBlockIndex.  Results are lengths / window starts / flags;

@@ -121,6 +121,42 @@ static void TestSlidingWindowAndBatchGet() {
     EXPECT_EQ(flags[3] & KVCM_FLAG_WRITABLE, int(KVCM_FLAG_WRITABLE));
 }
 
+static void TestWriteCycle() {
+    // StartWriteCache -> FinishWriteCache -> reclaim on the replica, without reading a key's map back
+    // (MetaSearcher::BatchAddLocation, BatchUpdateLocationStatus, BatchCADLocationStatus:
+    // kv_cache_manager/manager/meta_searcher.cc:312-487,582-717; the match table of meta_searcher_test.cc:196-252).
+    GpuBlockIndex index(64);
+    GpuMetaSearcher searcher(&index);
+    std::vector<int32_t> codes;
+    size_t len = 99;
+    EXPECT_EQ(index.AddLocation({10, 20, 30}, {4}, &codes), KVCM_OK);
+    EXPECT_EQ(codes[0] | codes[1] | codes[2], KVCM_OK);
+    EXPECT_EQ(searcher.PrefixMatch({10, 20, 30}, BlockMask{}, &len), KVCM_OK);
+    EXPECT_EQ(len, size_t(0));  // written, not served yet
+    EXPECT_EQ(index.UpdateLocationStatus({10, 20}, {KVCM_STATUS_TASK(4, 2, 3)}, &codes), KVCM_OK);  // WRITING -> SERVING
+    EXPECT_EQ(codes[0] | codes[1], KVCM_OK);
+    EXPECT_EQ(searcher.PrefixMatch({10, 20, 30}, BlockMask{}, &len), KVCM_OK);
+    EXPECT_EQ(len, size_t(2));
+    // a second tier for key 20 leaves its served location alone; a second location of one class is refused
+    EXPECT_EQ(index.AddLocation({20, 30}, {1, 4}, &codes), KVCM_OK);
+    EXPECT_EQ(codes[0], KVCM_OK);
+    EXPECT_EQ(codes[1], KVCM_EC_EXIST);
+    EXPECT_EQ(searcher.PrefixMatch({10, 20, 30}, BlockMask{}, &len), KVCM_OK);
+    EXPECT_EQ(len, size_t(2));
+    // compare-and-set on the wrong status, on a missing key; compare-and-delete of the last location drops the key
+    EXPECT_EQ(index.UpdateLocationStatus({30, 40, 10}, {KVCM_STATUS_TASK(4, 3, 4), KVCM_STATUS_TASK(4, 2, 3),
+                                                        KVCM_STATUS_TASK(4, 3, KVCM_STATUS_DELETE)}, &codes), KVCM_OK);
+    EXPECT_EQ(codes[0], KVCM_EC_MISMATCH);
+    EXPECT_EQ(codes[1], KVCM_EC_NOENT);
+    EXPECT_EQ(codes[2], KVCM_OK);
+    std::vector<uint8_t> flags;
+    EXPECT_EQ(searcher.BatchGet({10, 20, 30}, &flags), KVCM_OK);
+    EXPECT_EQ(int(flags[0]), 0);
+    EXPECT_EQ(flags[1] & KVCM_FLAG_SERVABLE, 1);
+    EXPECT_EQ(flags[2] & KVCM_FLAG_SERVABLE, 0);
+    EXPECT_EQ(index.AddLocation({1, 2}, {1, 2, 3}, &codes), KVCM_EC_BADARGS);
+}
+
 static void TestIovCopier() {
     // a block of 3 layers x (K,V) iovs with one ignored iov in the middle
     const size_t sz = 4096;
@@ -355,6 +391,7 @@ int main() {
     TestHash();
     TestPrefixMatch();
     TestSlidingWindowAndBatchGet();
+    TestWriteCycle();
     TestIovCopier();
     TestReplay();
     std::printf(g_failed == 0 ? "host adapter test: all checks passed\n" : "host adapter test: %d checks FAILED\n", g_failed);
