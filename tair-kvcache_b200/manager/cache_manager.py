@@ -177,3 +177,25 @@ class GpuCacheManager:
         codes = inst.index.update_status(new_keys, torch.from_numpy(tasks).to(self.device)).cpu().numpy()
         failed = codes[ok] != EC_OK
         return int(codes[ok][failed][0]) if failed.any() else EC_OK
+
+    def RemoveCache(self, instance_id: str, keys=None, tokens=None) -> int:
+        """The keys (or the keys of the tokens) leave the index with all their locations (cache_manager.cc:503-526;
+        the reference hands the request to its reclaimer, which deletes in the background - here it is done when the
+        call returns).  Its block_mask argument is not read by the reference either."""
+        if (keys is None or len(keys) == 0) and (tokens is None or len(tokens) == 0):
+            return EC_BADARGS
+        inst = self._instances.get(instance_id)
+        if inst is None:
+            return EC_INSTANCE_NOT_EXIST
+        inst.index.erase(self._request_keys(inst, keys, tokens))
+        return EC_OK
+
+    def TrimCache(self, instance_id: str, remove_all: bool = True) -> int:
+        """TS_REMOVE_ALL_CACHE, the one trim strategy the reference implements (cache_manager.cc:528-565)."""
+        if not remove_all:
+            return _cabi.KVCM_EC_BASE + 7  # EC_UNIMPLEMENTED
+        inst = self._instances.get(instance_id)
+        if inst is None:
+            return EC_INSTANCE_NOT_EXIST
+        inst.index.clear()
+        return EC_OK

@@ -121,3 +121,16 @@ def test_tokens_instead_of_keys():
     other[64 * 3 + 1] += 1
     assert len(m.GetCacheLocation("test_instance", PREFIX, tokens=other)[1]) == 3
     assert len(m.GetCacheLocation("test_instance", PREFIX, tokens=toks, block_mask=2)[1]) == 3   # two skipped, three found
+
+
+def test_remove_and_trim():
+    m = _manager()
+    ec, session, _, _ = m.StartWriteCache("test_instance", [1, 2, 3, 4])
+    assert m.FinishWriteCache("test_instance", session, 4) == cm.EC_OK
+    assert m.RemoveCache("test_instance", [3]) == cm.EC_OK
+    assert m.GetCacheLocation("test_instance", BATCH_GET, [1, 2, 3, 4])[1].tolist() == [True, True, False, True]
+    assert len(m.GetCacheLocation("test_instance", PREFIX, [1, 2, 3, 4])[1]) == 2
+    assert m.RemoveCache("test_instance", [], []) == cm.EC_BADARGS and m.RemoveCache("nobody", [1]) == cm.EC_INSTANCE_NOT_EXIST
+    assert m.TrimCache("test_instance") == cm.EC_OK and m.index_of("test_instance").stats()[1] == 0
+    assert len(m.GetCacheLocation("test_instance", PREFIX, [1, 2])[1]) == 0
+    assert m.TrimCache("test_instance", remove_all=False) == cm.EC_OK + 1007

@@ -111,3 +111,45 @@ def test_sampling_instances_alone_take_either_kernel_and_limits_hold():
     # the same batch size is fine for the queue policies alone
     RunTracesLruGroup(*args, 2, quotas, evict_batch=300, policy=["lru", "leaf_aware_lru"])
     torch.cuda.synchronize()
+
+
+def test_sixty_four_instances_and_the_call_without_an_instance_array():
+    rng = np.random.default_rng(960)
+    keys, off, types, mask, ts = _workload(rng, 1500, True)
+    each = [("random_lru", "lru", "leaf_aware_lru")[j % 3] for j in range(64)]   # the most one group may hold
+    rates = [0.5] * 64
+    inst = rng.integers(0, 64, size=len(types)).astype(np.int32)
+    quotas = [50, 900]
+    got = _gpu(keys, off, types, inst, each, quotas, mask, ts, rates, evict_batch=4, mode=1)
+    for c, q in enumerate(quotas):
+        want = oracle.LruGroupReplay(q, 64, evict_batch=4, mode=1, policy=each, sample_rate=rates).run(
+            keys, off, types, inst, mask, timestamps=ts, instance_records=True)
+        for name, a, b in zip(NAMES, want, got):
+            assert np.array_equal(a, b[c]), (name, q)
+    with pytest.raises(ValueError):
+        RunTracesLruGroup(torch.from_numpy(keys).to(DEV), torch.from_numpy(off).to(DEV), torch.from_numpy(types).to(DEV),
+                          torch.from_numpy(inst).to(DEV), 65, quotas, policy=["lru"] * 64 + ["random_lru"])
+    # one sampling instance through the group entry, no instance array: the single-instance sweep
+    from tair_kvcache_b200.optimizer import RunTracesLru
+    one = RunTracesLru(torch.from_numpy(keys).to(DEV), torch.from_numpy(off).to(DEV), torch.from_numpy(types).to(DEV),
+                       quotas, torch.from_numpy(mask).to(DEV), evict_batch=5, precise=True, policy="random_lru",
+                       sample_rate=0.25, timestamps=torch.from_numpy(ts).to(DEV))
+    lib = _cabi.lib()
+    policy = (ctypes.c_uint8 * 1)(_cabi.POLICY_RANDOM_LRU)
+    rate = (ctypes.c_double * 1)(0.25)
+    cast = lambda a: ctypes.cast(a, ctypes.c_void_p)
+    n_tr = len(types)
+    need = lib.kvcm_b200_replay_policy_group_workspace_bytes(len(keys), n_tr, 2, cast(policy), 1)
+    ws = torch.empty(need, dtype=torch.uint8, device=DEV)
+    dq = torch.tensor(quotas, dtype=torch.int64, device=DEV)
+    outs = [torch.empty((2, n_tr), dtype=torch.int32, device=DEV) for _ in range(3)]
+    size = torch.empty((2, n_tr), dtype=torch.int64, device=DEV)
+    totals = torch.zeros((2, 4), dtype=torch.int64, device=DEV)
+    dk, do, dt, dm, dts = (torch.from_numpy(a).to(DEV) for a in (keys, off, types, mask, ts))
+    _cabi.call("kvcm_b200_replay_policy_group", dk.data_ptr(), do.data_ptr(), dt.data_ptr(), dm.data_ptr(), None,
+               dts.data_ptr(), None, cast(policy), cast(rate), 1, n_tr, len(keys), dq.data_ptr(), 2, 5, 3,
+               ws.data_ptr(), need, outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), size.data_ptr(),
+               totals.data_ptr(), None, None, None, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    for a, b in zip(one[:4], outs + [size]):
+        assert np.array_equal(a.cpu().numpy(), b.cpu().numpy())
