@@ -434,6 +434,37 @@ KVCM_API int32_t kvcm_b200_match_sw(kvcm_b200_index_t *index, const int64_t *d_k
                                     int32_t n_req, int32_t sw_blocks, uint32_t avail_mask, int32_t *d_base_out,
                                     kvcm_stream_t stream);
 
+/* CacheManager::StartWriteCache for a batch of requests (kv_cache_manager/manager/cache_manager.cc:334-430):
+ * FilterWriteCache, then MetaSearcher::BatchAddLocation of the keys still to be written, with the answers the
+ * reference gives when it serves the requests one after the other in batch order - what request r sees is the
+ * index before the call plus what requests 0..r-1 of the batch added.  Per request: d_offset_out / d_mask_out /
+ * d_n_new_out exactly as kvcm_b200_filter_write returns them (under that view); per key, d_added_out[i] = 1 when
+ * this request gave key i its new location (storage_class, CLS_WRITING) - those keys, in request order, are the
+ * request's write session; d_new_off_out[r] (n_req + 1 entries) = session keys of the requests before r.  (A new
+ * key that cannot take the location - its map holds one of that class already, in whatever status, or the table is
+ * full - counts in d_n_new_out as in the reference's answer but is not part of the session.)
+ * A key that several requests of the batch name is written by the first of them; the later ones see it as being
+ * written, as they would in the reference.  storage_class (0..7) must be a class avail_mask counts.  The keys of one
+ * request are taken to be distinct (chained hashes are).  d_status[0] counts keys refused because the table is full
+ * (their d_added_out stays 0).  The workspace (kvcm_b200_start_write_workspace_bytes, 256-byte aligned) is scratch.
+ *
+ * kvcm_b200_finish_write is CacheManager::FinishWriteCache (:432-501) for the sessions of such a batch - the same
+ * d_keys / d_key_off / d_added / d_new_off: the j-th session key of request r turns CLS_SERVING when the success mask
+ * holds it (j < d_success_off[r], or d_success_bits[d_new_off[r] + j] != 0 when d_success_bits is given: one byte per
+ * session key of the batch) and loses its location otherwise (what the reference leaves to its reclaimer).
+ * d_results[r]: KVCM_OK; KVCM_EC_BADARGS for an offset beyond the session's keys (nothing is touched); else the code
+ * of a transition that failed. */
+KVCM_API int64_t kvcm_b200_start_write_workspace_bytes(int64_t n_keys_total, int32_t n_req);
+KVCM_API int32_t kvcm_b200_start_write(kvcm_b200_index_t *index, const int64_t *d_keys, const int64_t *d_key_off,
+                                       int32_t n_req, int64_t n_keys_total, uint32_t avail_mask, int32_t storage_class,
+                                       void *d_workspace, int64_t workspace_bytes, int32_t *d_offset_out,
+                                       uint8_t *d_mask_out, int32_t *d_n_new_out, uint8_t *d_added_out,
+                                       int64_t *d_new_off_out, uint32_t *d_status, kvcm_stream_t stream);
+KVCM_API int32_t kvcm_b200_finish_write(kvcm_b200_index_t *index, const int64_t *d_keys, const int64_t *d_key_off,
+                                        int32_t n_req, const uint8_t *d_added, const int64_t *d_new_off,
+                                        const int64_t *d_success_off, const uint8_t *d_success_bits,
+                                        int32_t storage_class, int32_t *d_results, kvcm_stream_t stream);
+
 /* MetaSearcher::BatchGetBestLocation / BatchGetLocation (kv_cache_manager/manager/meta_searcher.cc:147-194,
  * 267-310): per key, no early stop.  d_flags_out[i]: bit0 a location would be returned (servable),
  * bit1 key exists, bit2 location map non-empty, bit3 ExistsForWrite (select_location_policy.cc:29-38). */

@@ -101,6 +101,9 @@ SIGNATURES = {
     "kvcm_b200_index_set_auto_rehash": [_vp, _i64],
     "kvcm_b200_index_update_status": [_vp, _vp, _vp, _u32, _i64, _vp, _vp],
     "kvcm_b200_index_update_status_sharded": [_vp, _vp, _vp, _u32, _i64, _i32, _i32, _vp, _vp],
+    "kvcm_b200_start_write_workspace_bytes": [_i64, _i32],
+    "kvcm_b200_start_write": [_vp, _vp, _vp, _i32, _i64, _u32, _i32, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+    "kvcm_b200_finish_write": [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp],
     "kvcm_b200_index_add_location": [_vp, _vp, _vp, _i32, _i32, _i64, _vp, _vp, _vp],
     "kvcm_b200_index_add_location_sharded": [_vp, _vp, _vp, _i32, _i32, _i64, _i32, _i32, _vp, _vp, _vp],
     "kvcm_b200_index_upsert": [_vp, _vp, _vp, _u64, _i64, _vp, _vp],

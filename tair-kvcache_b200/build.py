@@ -29,7 +29,7 @@ def sources():
 
 
 HEADERS = [os.path.join(CSRC, "kvcm_common.cuh"), os.path.join(CSRC, "replay_ids.cuh"),
-           os.path.join(CSRC, "replay_sampling.cuh"),
+           os.path.join(CSRC, "replay_sampling.cuh"), os.path.join(CSRC, "id_table.cuh"),
            os.path.join(ROOT, "include", "kvcm_b200.h")]
 OBJ_DIR = os.path.join(HERE, "build")
 

@@ -20,6 +20,7 @@
 // keys), which stays in the 126 MB L2, instead of a random 32-byte sector of HBM per probe.
 #include <cstring>
 
+#include "id_table.cuh"
 #include "kvcm_common.cuh"
 
 struct kvcm_b200_index {
@@ -64,7 +65,6 @@ struct kvcm_b200_route_area {
 namespace kvcm {
 namespace {
 
-constexpr uint64_t kEmptyKey = 0x8000000000000000ull;
 constexpr uint64_t kTombKey = 0x8000000000000001ull;
 constexpr int kMatchWarps = 8;
 constexpr size_t kIndexHeaderBytes = 256;
@@ -80,15 +80,6 @@ struct IndexView {
     const IndexView *peers;
     uint32_t peer_count;
 };
-
-__host__ __device__ __forceinline__ uint64_t Mix(uint64_t k) {
-    k ^= k >> 33;
-    k *= 0xff51afd7ed558ccdull;
-    k ^= k >> 33;
-    k *= 0xc4ceb9fe1a85ec53ull;
-    k ^= k >> 33;
-    return k;
-}
 
 constexpr uint8_t kTagEmpty = 0, kTagTomb = 1;
 // Fingerprint 2..255 from the top byte of the mixed hash (the slot comes from its low bits).
@@ -408,13 +399,8 @@ __device__ __forceinline__ uint64_t ApplyStatusTask(uint64_t word, uint32_t task
     return w | KVCM_VAL_NONEMPTY | KVCM_VAL_PRESENT;
 }
 
-__global__ void UpdateStatusKernel(IndexView ix, const int64_t *__restrict__ keys, const uint32_t *__restrict__ tasks,
-                                   uint32_t uniform_task, int64_t n, Shard shard, int32_t *__restrict__ results) {
-    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const uint64_t key = static_cast<uint64_t>(keys[i]);
-    if (!Owns(shard, key)) return;  // the owner shard answers for this key
-    const uint32_t task = tasks != nullptr ? tasks[i] : uniform_task;
+// One task on one key: finds the key's word and runs the compare-and-swap loop; the result code of the task.
+__device__ __forceinline__ int32_t RunStatusTask(const IndexView &ix, uint64_t key, uint32_t task) {
     unsigned long long *word_at = nullptr;
     uint64_t slot = 0;
     const bool in_cell = key == kEmptyKey || key == kTombKey;
@@ -435,31 +421,40 @@ __global__ void UpdateStatusKernel(IndexView ix, const int64_t *__restrict__ key
     int32_t code = KVCM_EC_NOENT;
     if (word_at == nullptr) {
         ApplyStatusTask(0, task, &code);  // the answer for a key that is not there
-    } else {
-        // Tasks of one launch that name the same key take turns through the compare-and-swap.
-        unsigned long long seen = *reinterpret_cast<volatile unsigned long long *>(word_at);
-        for (int turn = 0; turn < 1024; ++turn) {
-            const uint64_t next = ApplyStatusTask(seen, task, &code);
-            if (next == seen) break;  // nothing to write: a refusal, or a task that leaves the word as it is
-            const unsigned long long was = atomicCAS(word_at, seen, next);
-            if (was == seen) {
-                if (next == 0) {  // the key's last location is gone: the key goes too
-                    AddCell(&ix.cells[2], -1);
-                    if (!in_cell) {
-                        unsigned long long *words = reinterpret_cast<unsigned long long *>(ix.slots);
-                        if (atomicCAS(&words[2 * slot], key, kTombKey) == key) {
-                            const int32_t freed = ReleaseSlot(ix, slot);
-                            if (freed != 0) AddCell(&ix.cells[3], -freed);
-                        }
+        return code;
+    }
+    // Tasks of one launch that name the same key take turns through the compare-and-swap.
+    unsigned long long seen = *reinterpret_cast<volatile unsigned long long *>(word_at);
+    for (int turn = 0; turn < 1024; ++turn) {
+        const uint64_t next = ApplyStatusTask(seen, task, &code);
+        if (next == seen) break;  // nothing to write: a refusal, or a task that leaves the word as it is
+        const unsigned long long was = atomicCAS(word_at, seen, next);
+        if (was == seen) {
+            if (next == 0) {  // the key's last location is gone: the key goes too
+                AddCell(&ix.cells[2], -1);
+                if (!in_cell) {
+                    unsigned long long *words = reinterpret_cast<unsigned long long *>(ix.slots);
+                    if (atomicCAS(&words[2 * slot], key, kTombKey) == key) {
+                        const int32_t freed = ReleaseSlot(ix, slot);
+                        if (freed != 0) AddCell(&ix.cells[3], -freed);
                     }
                 }
-                break;
             }
-            seen = was;
-            if (turn == 1023) code = KVCM_EC_ERROR;  // the turns ran out
+            break;
         }
+        seen = was;
+        if (turn == 1023) code = KVCM_EC_ERROR;  // the turns ran out
     }
-    results[i] = code;
+    return code;
+}
+
+__global__ void UpdateStatusKernel(IndexView ix, const int64_t *__restrict__ keys, const uint32_t *__restrict__ tasks,
+                                   uint32_t uniform_task, int64_t n, Shard shard, int32_t *__restrict__ results) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint64_t key = static_cast<uint64_t>(keys[i]);
+    if (!Owns(shard, key)) return;  // the owner shard answers for this key
+    results[i] = RunStatusTask(ix, key, tasks != nullptr ? tasks[i] : uniform_task);
 }
 
 // ---- a new location for a key (MetaSearcher::BatchAddLocation, kv_cache_manager/manager/meta_searcher.cc:312-408:
@@ -982,6 +977,264 @@ __global__ void __launch_bounds__(kMatchWarps * 32)
             n_new_out[req] = n_empty;
         }
     }
+}
+
+// ---- StartWriteCache / FinishWriteCache for a batch of requests (CacheManager::StartWriteCache = FilterWriteCache +
+// MetaSearcher::BatchAddLocation, kv_cache_manager/manager/cache_manager.cc:334-430,589-635; FinishWriteCache,
+// :432-501), with the answers the reference gives when it serves the requests one after the other in batch order.
+// What request r sees of a key is what the index held before the batch plus what the requests before r added.  A
+// key with an empty (or no) location map is added by the FIRST request that names it, whatever that request's
+// block mask looks like - so "the first request that names the key" (an atomic minimum per key, over dense ids
+// of the batch's keys) settles, for all requests at once, both who writes a key and what the later ones see.
+// The one thing that stays sequential is a key whose map is not empty but holds nothing writable (only locations
+// the policy gives no weight, or locations whose status is CLS_NOT_FOUND): a request whose existing keys form a
+// prefix adds a location to it, a request with holes does not, and which of the two a request is may depend on
+// such a key.  Requests that name one are rare; they are marked, left out of the parallel pass, and served
+// afterwards by one warp in batch order.
+struct StartWrite {
+    IndexView ix;
+    const int64_t *keys;
+    const int64_t *key_off;
+    int32_t n_req;
+    uint32_t avail_mask;
+    uint32_t cls;
+    IdTable table;
+    uint32_t *ids;         // per key occurrence: dense id of the key (keys that are writable already have none)
+    uint32_t *first;       // per id: the first request that names the key
+    uint8_t *snap;         // per key occurrence: the flags of the key before the batch
+    uint8_t *ordered;      // per request: 1 = names a key with a map but nothing writable: served in order
+    uint8_t *late_added;   // per id: such a key got its location from an earlier request of the batch
+    int32_t *offset_out;
+    uint8_t *mask_out;
+    int32_t *n_new_out;
+    uint8_t *added_out;    // per key occurrence: 1 = this request gave the key its new location
+    int32_t *n_added;      // per request: how many keys that is (the length of its write session)
+    uint32_t *status;      // [0] keys refused because the table is full
+};
+
+__global__ void StartWriteInitKernel(IdTable t, uint32_t *first, uint8_t *late_added, uint8_t *ordered, int64_t n_keys,
+                                     int32_t n_req) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    const uint64_t at = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (uint64_t i = at; i <= t.mask; i += stride) t.slots[i] = make_ulonglong2(kEmptyKey, ~0ull);
+    for (uint64_t i = at; i < static_cast<uint64_t>(n_keys); i += stride) {
+        first[i] = 0xFFFFFFFFu;
+        late_added[i] = 0;
+    }
+    for (uint64_t i = at; i < static_cast<uint64_t>(n_req); i += stride) ordered[i] = 0;
+    if (at == 0) {
+        t.cells[0] = 0ull;
+        t.cells[1] = ~0ull;
+    }
+}
+
+// Pass 1 (a warp per request): the flags of every key before the batch; keys that are not writable claim an id.
+__global__ void __launch_bounds__(kMatchWarps * 32) StartWriteSnapshotKernel(StartWrite p) {
+    const int32_t req = blockIdx.x * kMatchWarps + (threadIdx.x >> 5);
+    if (req >= p.n_req) return;
+    const int64_t beg = p.key_off[req], end = p.key_off[req + 1];
+    bool late = false;
+    for (int64_t i = beg + LaneId(); i < end; i += 32) {
+        const uint64_t key = static_cast<uint64_t>(p.keys[i]);
+        const uint8_t f = FlagsOf(Lookup(p.ix, key), p.avail_mask);
+        p.snap[i] = f;
+        if ((f & KVCM_FLAG_WRITABLE) == 0) {
+            ClaimId(p.table, key, nullptr);
+            late = late || (f & KVCM_FLAG_NONEMPTY) != 0;
+        }
+    }
+    if (__any_sync(0xffffffffu, late) && LaneId() == 0) p.ordered[req] = 1;
+}
+
+// Pass 2 (a warp per request): ids, and per key the first request that names it.
+__global__ void __launch_bounds__(kMatchWarps * 32) StartWriteOwnersKernel(StartWrite p) {
+    const int32_t req = blockIdx.x * kMatchWarps + (threadIdx.x >> 5);
+    if (req >= p.n_req) return;
+    const int64_t beg = p.key_off[req], end = p.key_off[req + 1];
+    for (int64_t i = beg + LaneId(); i < end; i += 32) {
+        if ((p.snap[i] & KVCM_FLAG_WRITABLE) != 0) continue;
+        const uint32_t id = LookupId(p.table, static_cast<uint64_t>(p.keys[i]));
+        p.ids[i] = id;
+        if ((p.snap[i] & KVCM_FLAG_NONEMPTY) == 0) atomicMin(&p.first[id], static_cast<uint32_t>(req));
+    }
+}
+
+// One request, all lanes of a warp: its block mask, and the locations it adds.
+__device__ __forceinline__ void StartWriteOne(const StartWrite &p, int32_t req, int32_t *d_live, int32_t *d_used) {
+    const uint32_t lane = LaneId();
+    const uint32_t full = 0xffffffffu;
+    const int64_t beg = p.key_off[req];
+    const int64_t n = p.key_off[req + 1] - beg;
+    const uint32_t r = static_cast<uint32_t>(req);
+    // what this request sees of key i: (exists for write, location map non-empty, id)
+    auto view = [&](int64_t i, bool *exists, bool *nonempty, uint32_t *id) {
+        const uint8_t f = p.snap[beg + i];
+        *exists = (f & KVCM_FLAG_WRITABLE) != 0;
+        *nonempty = (f & KVCM_FLAG_NONEMPTY) != 0;
+        *id = 0xFFFFFFFFu;
+        if (*exists) return;
+        *id = p.ids[beg + i];
+        if (*nonempty) {  // a map with nothing writable: writable once an earlier request has added to it
+            *exists = *reinterpret_cast<volatile uint8_t *>(&p.late_added[*id]) != 0;
+        } else if (p.first[*id] < r) {  // added by an earlier request of the batch (in CLS_WRITING)
+            *exists = *nonempty = true;
+        }
+    };
+    int64_t first_missing = n;
+    bool exists_after = false;
+    int32_t n_empty = 0;
+    for (int64_t base = 0; base < n; base += 32) {
+        const int64_t i = base + lane;
+        bool exists = false, nonempty = false;
+        uint32_t id;
+        if (i < n) {
+            view(i, &exists, &nonempty, &id);
+            if (p.mask_out != nullptr) p.mask_out[beg + i] = nonempty ? 1 : 0;
+        }
+        const uint32_t in_range = __ballot_sync(full, i < n);
+        const uint32_t ex = __ballot_sync(full, exists);
+        const uint32_t ne = __ballot_sync(full, nonempty);
+        n_empty += __popc(in_range & ~ne);
+        if (first_missing == n) {
+            const uint32_t missing = in_range & ~ex;
+            if (missing != 0) {
+                const int pos = __ffs(missing) - 1;
+                first_missing = base + pos;
+                if ((ex >> pos) != 0) exists_after = true;
+            }
+        } else if (ex != 0) {
+            exists_after = true;
+        }
+    }
+    const bool prefix_form = !exists_after;
+    if (lane == 0) {
+        p.offset_out[req] = prefix_form ? static_cast<int32_t>(first_missing) : -1;
+        p.n_new_out[req] = prefix_form ? static_cast<int32_t>(n - first_missing) : n_empty;
+    }
+    // the new keys: everything from the first missing key on, or the keys whose map is empty
+    int32_t session = 0;
+    for (int64_t base = 0; base < n; base += 32) {
+        const int64_t i = base + lane;
+        bool exists = false, nonempty = false;
+        uint32_t id = 0xFFFFFFFFu;
+        if (i < n) view(i, &exists, &nonempty, &id);
+        const bool is_new = i < n && (prefix_form ? i >= first_missing : !nonempty);
+        uint8_t added = 0;
+        if (is_new) {
+            const uint64_t key = static_cast<uint64_t>(p.keys[beg + i]);
+            MergeLocation put{p.cls, 2u /* CLS_WRITING */, KVCM_EC_ERROR, false};
+            if (key == kEmptyKey || key == kTombKey) {
+                put(reinterpret_cast<unsigned long long *>(&p.ix.cells[key - kEmptyKey]));
+                if (put.into_empty_word) *d_live += 1;
+            } else if (!UpsertOne<true>(p.ix, key, put, d_live, d_used)) {
+                put.code = KVCM_EC_NOSPC;
+                if (p.status != nullptr) atomicAdd(&p.status[0], 1u);
+            }
+            added = put.code == KVCM_OK ? 1 : 0;
+            if (added != 0 && nonempty) p.late_added[id] = 1;
+        }
+        if (i < n) p.added_out[beg + i] = added;
+        session += __popc(__ballot_sync(full, added != 0));
+    }
+    if (lane == 0) p.n_added[req] = session;
+}
+
+// Pass 3: every request that can be served by itself, a warp each.
+__global__ void __launch_bounds__(kMatchWarps * 32) StartWriteParallelKernel(StartWrite p) {
+    const int32_t req = blockIdx.x * kMatchWarps + (threadIdx.x >> 5);
+    int32_t d_live = 0, d_used = 0;
+    if (req < p.n_req && p.ordered[req] == 0) StartWriteOne(p, req, &d_live, &d_used);
+    AddCellsPerWarp(p.ix, d_live, d_used);
+}
+
+// Pass 4: the others, one warp, in batch order.
+__global__ void __launch_bounds__(32) StartWriteOrderedKernel(StartWrite p) {
+    int32_t d_live = 0, d_used = 0;
+    for (int32_t base = 0; base < p.n_req; base += 32) {
+        const int32_t mine = base + static_cast<int32_t>(LaneId());
+        uint32_t todo = __ballot_sync(0xffffffffu, mine < p.n_req && p.ordered[mine] != 0);
+        while (todo != 0) {
+            const int32_t req = base + __ffs(todo) - 1;
+            todo &= todo - 1;
+            StartWriteOne(p, req, &d_live, &d_used);
+            __threadfence();  // what this request added is what the next one sees
+            __syncwarp();
+        }
+    }
+    AddCellsPerWarp(p.ix, d_live, d_used);
+}
+
+// new_off[r] = session keys of the requests before r (one CTA; a running sum over chunks of 1,024 requests).
+__global__ void __launch_bounds__(1024) StartWriteOffsetsKernel(const int32_t *__restrict__ n_new, int32_t n_req,
+                                                                 int64_t *__restrict__ new_off) {
+    __shared__ int64_t warp_sum[32];
+    __shared__ int64_t carry;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    for (int32_t base = 0; base < n_req; base += 1024) {
+        const int32_t r = base + static_cast<int32_t>(threadIdx.x);
+        const int64_t mine = r < n_req ? n_new[r] : 0;
+        int64_t scan = mine;
+        for (int d = 1; d < 32; d <<= 1) {
+            const int64_t up = __shfl_up_sync(0xffffffffu, scan, d);
+            if (static_cast<int>(LaneId()) >= d) scan += up;
+        }
+        if (LaneId() == 31) warp_sum[threadIdx.x >> 5] = scan;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            int64_t w = warp_sum[threadIdx.x];
+            for (int d = 1; d < 32; d <<= 1) {
+                const int64_t up = __shfl_up_sync(0xffffffffu, w, d);
+                if (static_cast<int>(threadIdx.x) >= d) w += up;
+            }
+            warp_sum[threadIdx.x] = w;
+        }
+        __syncthreads();
+        const int64_t before = carry + ((threadIdx.x >> 5) > 0 ? warp_sum[(threadIdx.x >> 5) - 1] : 0) + scan - mine;
+        if (r < n_req) new_off[r] = before;
+        __syncthreads();
+        if (threadIdx.x == 1023) carry = before + mine;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) new_off[n_req] = carry;
+}
+
+// FinishWriteCache of a batch of sessions (a warp per request): the j-th key a request added (its session's keys,
+// in request order) turns CLS_SERVING when the success mask holds it - an offset (j < offset) or one byte per
+// session key - and loses its location otherwise.  An invalid mask (an offset beyond the session's keys) leaves the
+// session untouched and answers KVCM_EC_BADARGS for the request.
+__global__ void __launch_bounds__(kMatchWarps * 32)
+    FinishWriteKernel(IndexView ix, const int64_t *__restrict__ keys, const int64_t *__restrict__ key_off, int32_t n_req,
+                      const uint8_t *__restrict__ added, const int64_t *__restrict__ new_off,
+                      const int64_t *__restrict__ success_off, const uint8_t *__restrict__ success_bits, uint32_t cls,
+                      int32_t *__restrict__ results) {
+    const int32_t req = blockIdx.x * kMatchWarps + (threadIdx.x >> 5);
+    if (req >= n_req) return;
+    const uint32_t lane = LaneId();
+    const int64_t beg = key_off[req], n = key_off[req + 1] - beg;
+    const int64_t mine = new_off[req + 1] - new_off[req];
+    if (success_bits == nullptr && (success_off[req] < 0 || success_off[req] > mine)) {
+        if (lane == 0) results[req] = KVCM_EC_BADARGS;
+        return;
+    }
+    const uint32_t serve = KVCM_STATUS_TASK(cls, KVCM_STATUS_ANY, 3u);
+    const uint32_t drop = KVCM_STATUS_TASK(cls, KVCM_STATUS_ANY, KVCM_STATUS_DELETE);
+    int64_t rank = 0;  // session keys in front of this pass
+    int32_t worst = KVCM_OK;
+    for (int64_t base = 0; base < n; base += 32) {
+        const int64_t i = base + lane;
+        const bool is_mine = i < n && added[beg + i] != 0;
+        const uint32_t m = __ballot_sync(0xffffffffu, is_mine);
+        if (is_mine) {
+            const int64_t j = rank + __popc(m & ((1u << lane) - 1u));
+            const bool ok = success_bits != nullptr ? success_bits[new_off[req] + j] != 0 : j < success_off[req];
+            const int32_t code = RunStatusTask(ix, static_cast<uint64_t>(keys[beg + i]), ok ? serve : drop);
+            if (ok && code != KVCM_OK) worst = code;
+        }
+        rank += __popc(m);
+    }
+    worst = __reduce_max_sync(0xffffffffu, worst);
+    if (lane == 0) results[req] = worst;
 }
 
 // View for the matchers: probes follow the attached peers.
@@ -1667,6 +1920,112 @@ int32_t kvcm_b200_filter_write(kvcm_b200_index_t *ix, const int64_t *d_keys, con
     kvcm::FilterWriteKernel<<<kvcm::GridFor(n_req, kvcm::kMatchWarps), kvcm::kMatchWarps * 32, 0,
                               kvcm::AsStream(stream)>>>(kvcm::View(ix), d_keys, d_key_off, n_req, avail_mask,
                                                         d_offset_out, d_mask_out, d_n_new_out);
+    return kvcm::LaunchStatus();
+}
+
+namespace {
+
+struct StartWriteLayout {
+    size_t table_off, ids_off, first_off, snap_off, late_off, ordered_off, n_added_off, total;
+};
+
+StartWriteLayout StartWriteLayoutFor(int64_t n_keys, int32_t n_req) {
+    auto up = [](size_t v) { return (v + 255) & ~static_cast<size_t>(255); };
+    const size_t nk = static_cast<size_t>(n_keys > 0 ? n_keys : 1);
+    StartWriteLayout l;
+    l.table_off = 256;
+    l.ids_off = up(l.table_off + kvcm::SlotsFor(n_keys) * sizeof(ulonglong2));
+    l.first_off = up(l.ids_off + nk * 4);
+    l.snap_off = up(l.first_off + nk * 4);
+    l.late_off = up(l.snap_off + nk);
+    l.ordered_off = up(l.late_off + nk);
+    l.n_added_off = up(l.ordered_off + static_cast<size_t>(n_req > 0 ? n_req : 1));
+    l.total = up(l.n_added_off + static_cast<size_t>(n_req > 0 ? n_req : 1) * 4);
+    return l;
+}
+
+}  // namespace
+
+int64_t kvcm_b200_start_write_workspace_bytes(int64_t n_keys_total, int32_t n_req) {
+    if (n_keys_total < 0 || n_keys_total >= (1ll << 31) || n_req < 0) return -1;
+    return static_cast<int64_t>(StartWriteLayoutFor(n_keys_total, n_req).total);
+}
+
+int32_t kvcm_b200_start_write(kvcm_b200_index_t *ix, const int64_t *d_keys, const int64_t *d_key_off, int32_t n_req,
+                              int64_t n_keys_total, uint32_t avail_mask, int32_t storage_class, void *d_workspace,
+                              int64_t workspace_bytes, int32_t *d_offset_out, uint8_t *d_mask_out,
+                              int32_t *d_n_new_out, uint8_t *d_added_out, int64_t *d_new_off_out, uint32_t *d_status,
+                              kvcm_stream_t stream) {
+    if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    // the class new locations go to has to count for the policy, or what a request adds would not be there for the next
+    if (n_req < 0 || n_keys_total < 0 || storage_class < 0 || storage_class > 7 ||
+        ((avail_mask >> storage_class) & 1u) == 0) {
+        return KVCM_EC_BADARGS;
+    }
+    const int64_t need = kvcm_b200_start_write_workspace_bytes(n_keys_total, n_req);
+    if (need < 0) return KVCM_EC_OUT_OF_LIMIT;
+    if (n_req == 0) return KVCM_OK;
+    if (d_key_off == nullptr || d_offset_out == nullptr || d_n_new_out == nullptr || d_added_out == nullptr ||
+        d_new_off_out == nullptr || d_workspace == nullptr || (d_keys == nullptr && n_keys_total > 0)) {
+        return KVCM_ER_INVALID_ADDRESS;
+    }
+    if (reinterpret_cast<uintptr_t>(d_workspace) & 255u) return KVCM_ER_INVALID_ADDRESS;
+    if (workspace_bytes < need) return KVCM_EC_NOSPC;
+    MaybeRehash(ix, stream);
+    ix->used_upper += static_cast<uint64_t>(n_keys_total);
+    if (ix->used_upper > ix->n_slots) ix->used_upper = ix->n_slots;
+    const StartWriteLayout l = StartWriteLayoutFor(n_keys_total, n_req);
+    uint8_t *ws = static_cast<uint8_t *>(d_workspace);
+    kvcm::StartWrite p;
+    p.ix = kvcm::LocalView(ix);
+    p.keys = d_keys;
+    p.key_off = d_key_off;
+    p.n_req = n_req;
+    p.avail_mask = avail_mask;
+    p.cls = static_cast<uint32_t>(storage_class);
+    p.table.cells = reinterpret_cast<unsigned long long *>(ws);
+    p.table.slots = reinterpret_cast<ulonglong2 *>(ws + l.table_off);
+    p.table.mask = kvcm::SlotsFor(n_keys_total) - 1;
+    p.ids = reinterpret_cast<uint32_t *>(ws + l.ids_off);
+    p.first = reinterpret_cast<uint32_t *>(ws + l.first_off);
+    p.snap = ws + l.snap_off;
+    p.late_added = ws + l.late_off;
+    p.ordered = ws + l.ordered_off;
+    p.n_added = reinterpret_cast<int32_t *>(ws + l.n_added_off);
+    p.offset_out = d_offset_out;
+    p.mask_out = d_mask_out;
+    p.n_new_out = d_n_new_out;
+    p.added_out = d_added_out;
+    p.status = d_status;
+    cudaStream_t s = kvcm::AsStream(stream);
+    const int sms = kvcm::GetDeviceInfo().sm_count;
+    const unsigned grid = kvcm::GridFor(n_req, kvcm::kMatchWarps);
+    const unsigned threads = kvcm::kMatchWarps * 32;
+    kvcm::StartWriteInitKernel<<<sms * 4, 256, 0, s>>>(p.table, p.first, p.late_added, p.ordered, n_keys_total, n_req);
+    kvcm::StartWriteSnapshotKernel<<<grid, threads, 0, s>>>(p);
+    kvcm::StartWriteOwnersKernel<<<grid, threads, 0, s>>>(p);
+    kvcm::StartWriteParallelKernel<<<grid, threads, 0, s>>>(p);
+    kvcm::StartWriteOrderedKernel<<<1, 32, 0, s>>>(p);
+    kvcm::StartWriteOffsetsKernel<<<1, 1024, 0, s>>>(p.n_added, n_req, d_new_off_out);
+    return kvcm::LaunchStatus();
+}
+
+int32_t kvcm_b200_finish_write(kvcm_b200_index_t *ix, const int64_t *d_keys, const int64_t *d_key_off, int32_t n_req,
+                               const uint8_t *d_added, const int64_t *d_new_off, const int64_t *d_success_off,
+                               const uint8_t *d_success_bits, int32_t storage_class, int32_t *d_results,
+                               kvcm_stream_t stream) {
+    if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (n_req < 0 || storage_class < 0 || storage_class > 7) return KVCM_EC_BADARGS;
+    if (n_req == 0) return KVCM_OK;
+    if (d_key_off == nullptr || d_added == nullptr || d_new_off == nullptr || d_results == nullptr ||
+        (d_success_off == nullptr && d_success_bits == nullptr)) {
+        return KVCM_ER_INVALID_ADDRESS;
+    }
+    ix->tomb_debt += static_cast<uint64_t>(n_req);  // failed blocks may take their keys with them
+    kvcm::FinishWriteKernel<<<kvcm::GridFor(n_req, kvcm::kMatchWarps), kvcm::kMatchWarps * 32, 0,
+                              kvcm::AsStream(stream)>>>(kvcm::LocalView(ix), d_keys, d_key_off, n_req, d_added,
+                                                        d_new_off, d_success_off, d_success_bits,
+                                                        static_cast<uint32_t>(storage_class), d_results);
     return kvcm::LaunchStatus();
 }
 

@@ -53,6 +53,19 @@ inline void EnsureDynamicSmem(Kernel kernel, int bytes) {
 
 __device__ __forceinline__ uint32_t LaneId() { return threadIdx.x & 31u; }
 
+// The key value an empty slot of the library's open-addressing tables holds (INT64_MIN; a real key of that value is
+// kept beside the table), and the 64-bit finaliser that spreads keys over their slots and over hash-range shards.
+constexpr uint64_t kEmptyKey = 0x8000000000000000ull;
+
+__host__ __device__ __forceinline__ uint64_t Mix(uint64_t k) {
+    k ^= k >> 33;
+    k *= 0xff51afd7ed558ccdull;
+    k ^= k >> 33;
+    k *= 0xc4ceb9fe1a85ec53ull;
+    k ^= k >> 33;
+    return k;
+}
+
 // One step of the reference's chained block hash (kv_cache_manager/manager/hash_util.h:8-12):
 //   hash ^= value + 0x9e3779b97f4a7c15 + (hash << 12) + (hash >> 32)
 // on int64 with wrap-around; `>>` is the arithmetic shift of a signed value.  Written on

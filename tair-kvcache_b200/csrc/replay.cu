@@ -30,7 +30,6 @@ static __device__ __align__(256) unsigned char g_replay_noalloc_scratch[KVCM_B20
 namespace kvcm {
 namespace {
 
-constexpr uint64_t kEmptyKey = 0x8000000000000000ull;
 constexpr uint64_t kNoWriter = ~0ull;
 constexpr int kWarps = 8;
 
@@ -39,15 +38,6 @@ struct ReplayTable {
     unsigned long long *cells;  // first_writer of the key equal to kEmptyKey
     uint64_t mask;
 };
-
-__host__ __device__ __forceinline__ uint64_t Mix(uint64_t k) {
-    k ^= k >> 33;
-    k *= 0xff51afd7ed558ccdull;
-    k ^= k >> 33;
-    k *= 0xc4ceb9fe1a85ec53ull;
-    k ^= k >> 33;
-    return k;
-}
 
 __global__ void ReplayInitKernel(ReplayTable t) {
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;

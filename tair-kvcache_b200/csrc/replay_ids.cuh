@@ -2,68 +2,11 @@
 // configurations of a sweep, so that per-configuration replay state is flat arrays indexed by id.
 // Shared by the eviction-aware replays (replay_lru.cu, replay_leaf_lru.cu).
 #pragma once
+#include "id_table.cuh"
 #include "kvcm_common.cuh"
 
 namespace kvcm {
 namespace {
-
-constexpr uint64_t kEmptyKey = 0x8000000000000000ull;
-
-struct IdTable {
-    ulonglong2 *slots;         // {key, id}
-    unsigned long long *cells;  // [0] = number of ids handed out, [1] = id of the key equal to kEmptyKey (or ~0)
-    uint64_t mask;
-};
-
-__host__ __device__ __forceinline__ uint64_t Mix(uint64_t k) {
-    k ^= k >> 33;
-    k *= 0xff51afd7ed558ccdull;
-    k ^= k >> 33;
-    k *= 0xc4ceb9fe1a85ec53ull;
-    k ^= k >> 33;
-    return k;
-}
-
-// Pass 1: every key gets a slot; the thread that claims the slot takes the next id.
-__device__ __forceinline__ void ClaimId(const IdTable &t, uint64_t key, uint32_t *status) {
-    unsigned long long *words = reinterpret_cast<unsigned long long *>(t.slots);
-    if (key == kEmptyKey) {
-        if (atomicCAS(&t.cells[1], ~0ull, ~0ull - 1) == ~0ull) t.cells[1] = atomicAdd(&t.cells[0], 1ull);
-        return;
-    }
-    uint64_t slot = Mix(key) & t.mask;
-    bool placed = false;
-    for (uint64_t probe = 0; probe <= t.mask; ++probe) {
-        unsigned long long seen = *reinterpret_cast<volatile unsigned long long *>(&words[2 * slot]);
-        if (seen == kEmptyKey) {
-            seen = atomicCAS(&words[2 * slot], kEmptyKey, key);
-            if (seen == kEmptyKey) {
-                words[2 * slot + 1] = atomicAdd(&t.cells[0], 1ull);
-                placed = true;
-                break;
-            }
-        }
-        if (seen == key) {
-            placed = true;
-            break;
-        }
-        slot = (slot + 1) & t.mask;
-    }
-    if (!placed && status != nullptr) atomicAdd(&status[0], 1u);
-}
-
-// Pass 2 (a launch of its own, so every id of pass 1 is visible): key -> id.
-__device__ __forceinline__ uint32_t LookupId(const IdTable &t, uint64_t key) {
-    if (key == kEmptyKey) return static_cast<uint32_t>(t.cells[1]);
-    uint64_t slot = Mix(key) & t.mask;
-    for (uint64_t probe = 0; probe <= t.mask; ++probe) {
-        const ulonglong2 s = t.slots[slot];
-        if (s.x == key) return static_cast<uint32_t>(s.y);
-        if (s.x == kEmptyKey) break;  // not reached for a key that pass 1 placed
-        slot = (slot + 1) & t.mask;
-    }
-    return 0u;
-}
 
 __global__ void __launch_bounds__(256)
     LruClaimIdsKernel(IdTable t, const int64_t *__restrict__ keys, int64_t n_keys, uint32_t *status) {
@@ -145,12 +88,6 @@ __global__ void __launch_bounds__(1024)
         }
         queue_base[n_instances] = at;
     }
-}
-
-uint64_t SlotsFor(int64_t n_keys) {
-    uint64_t n = 1024;
-    while (n < 2ull * static_cast<uint64_t>(n_keys)) n <<= 1;
-    return n;
 }
 
 }  // namespace
