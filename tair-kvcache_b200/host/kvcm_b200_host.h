@@ -377,6 +377,98 @@ public:
         return rc;
     }
 
+    // CacheManager::StartWriteCache for a batch of requests, answered as if they were served in batch order
+    // (kv_cache_manager/manager/cache_manager.cc:334-430): (*masks)[r] is the block mask FilterWriteCache gives
+    // request r, (*new_keys)[r] the keys that got a location of `storage_class` in CLS_WRITING - the request's write
+    // session.  The batch stays staged on the device for FinishWriteCacheBatch.
+    int32_t StartWriteCacheBatch(const std::vector<KeyVector> &keys, int32_t storage_class,
+                                 std::vector<BlockMask> *masks, std::vector<KeyVector> *new_keys) {
+        const int32_t n_req = static_cast<int32_t>(keys.size());
+        masks->assign(n_req, BlockMask{BlockMaskOffset{0}});
+        new_keys->assign(n_req, KeyVector{});
+        session_requests_ = 0;
+        if (n_req == 0) return KVCM_OK;
+        int32_t rc = Stage(keys);
+        if (rc != KVCM_OK) return rc;
+        const int64_t *off = key_off_.host<int64_t>();
+        const int64_t n_keys = off[n_req];
+        const int64_t ws_bytes = kvcm_b200_start_write_workspace_bytes(n_keys, n_req);
+        if (ws_bytes < 0) return KVCM_EC_OUT_OF_LIMIT;
+        const size_t per_req = sizeof(int32_t) * n_req, per_key = static_cast<size_t>(n_keys) + 1;
+        if (!ws_.Reserve(static_cast<size_t>(ws_bytes), true) || !out_.Reserve(per_req) || !n_new_.Reserve(per_req) ||
+            !bits_.Reserve(per_key) || !added_.Reserve(per_key) || !new_off_.Reserve(sizeof(int64_t) * (n_req + 1))) {
+            return KVCM_EC_NOSPC;
+        }
+        rc = kvcm_b200_start_write(index_->handle(), keys_.dev<int64_t>(), key_off_.dev<int64_t>(), n_req, n_keys,
+                                   avail_mask_, storage_class, ws_.dev<void>(), ws_bytes, out_.dev<int32_t>(),
+                                   bits_.dev<uint8_t>(), n_new_.dev<int32_t>(), added_.dev<uint8_t>(),
+                                   new_off_.dev<int64_t>(), nullptr, stream_);
+        if (rc != KVCM_OK) return rc;
+        if (!out_.ToHost(per_req, stream_) || !bits_.ToHost(per_key - 1, stream_) ||
+            !added_.ToHost(per_key - 1, stream_) || !new_off_.ToHost(sizeof(int64_t) * (n_req + 1), stream_)) {
+            return KVCM_ER_CUDAMEMCPY_ERROR;
+        }
+        rc = detail::Sync(stream_);
+        if (rc != KVCM_OK) return rc;
+        for (int32_t r = 0; r < n_req; ++r) {
+            const int32_t first = out_.host<int32_t>()[r];
+            if (first >= 0) {
+                (*masks)[r] = BlockMask{BlockMaskOffset{static_cast<size_t>(first)}};
+            } else {
+                BlockMaskVector held(keys[r].size());
+                for (size_t i = 0; i < keys[r].size(); ++i) held[i] = bits_.host<uint8_t>()[off[r] + i] != 0;
+                (*masks)[r] = BlockMask{std::move(held)};
+            }
+            for (size_t i = 0; i < keys[r].size(); ++i) {
+                if (added_.host<uint8_t>()[off[r] + i] != 0) (*new_keys)[r].push_back(keys[r][i]);
+            }
+        }
+        session_requests_ = n_req;
+        session_class_ = storage_class;
+        return KVCM_OK;
+    }
+
+    // CacheManager::FinishWriteCache (:432-501) for the sessions of the last StartWriteCacheBatch: success_masks[r]
+    // is over request r's session keys (an offset, or a vector of exactly that many entries); the keys inside it turn
+    // CLS_SERVING, the others lose their location.  (*codes)[r]: KVCM_OK, KVCM_EC_BADARGS for an invalid mask.
+    int32_t FinishWriteCacheBatch(const std::vector<BlockMask> &success_masks, std::vector<int32_t> *codes) {
+        const int32_t n_req = session_requests_;
+        codes->assign(n_req, KVCM_OK);
+        if (static_cast<int32_t>(success_masks.size()) != n_req) return KVCM_EC_BADARGS;
+        if (n_req == 0) return KVCM_OK;
+        const int64_t *new_off = new_off_.host<int64_t>();
+        const size_t n_session = static_cast<size_t>(new_off[n_req]);
+        if (!bits_.Reserve(n_session + 1) || !out_.Reserve(sizeof(int32_t) * n_req)) return KVCM_EC_NOSPC;
+        uint8_t *bits = bits_.host<uint8_t>();
+        std::vector<bool> invalid(n_req, false);
+        for (int32_t r = 0; r < n_req; ++r) {  // IsBlockMaskValid / IsIndexInMaskRange (cache_location.cc:9-31)
+            const size_t mine = static_cast<size_t>(new_off[r + 1] - new_off[r]);
+            uint8_t *b = bits + new_off[r];
+            if (std::holds_alternative<BlockMaskVector>(success_masks[r])) {
+                const auto &v = std::get<BlockMaskVector>(success_masks[r]);
+                invalid[r] = v.size() != mine;
+                for (size_t j = 0; j < mine; ++j) b[j] = (!invalid[r] && v[j]) ? 1 : 0;
+            } else {
+                const size_t upto = std::get<BlockMaskOffset>(success_masks[r]);
+                invalid[r] = upto > mine;
+                for (size_t j = 0; j < mine; ++j) b[j] = (!invalid[r] && j < upto) ? 1 : 0;
+            }
+        }
+        for (int32_t r = 0; r < n_req; ++r) {
+            if (invalid[r]) return KVCM_EC_BADARGS;  // as the reference: nothing of an invalid call is applied
+        }
+        if (!bits_.ToDevice(n_session, stream_)) return KVCM_ER_CUDAMEMCPY_ERROR;
+        int32_t rc = kvcm_b200_finish_write(index_->handle(), keys_.dev<int64_t>(), key_off_.dev<int64_t>(), n_req,
+                                            added_.dev<uint8_t>(), new_off_.dev<int64_t>(), nullptr,
+                                            bits_.dev<uint8_t>(), session_class_, out_.dev<int32_t>(), stream_);
+        if (rc != KVCM_OK) return rc;
+        if (!out_.ToHost(sizeof(int32_t) * n_req, stream_)) return KVCM_ER_CUDAMEMCPY_ERROR;
+        rc = detail::Sync(stream_);
+        if (rc == KVCM_OK) std::memcpy(codes->data(), out_.host<int32_t>(), sizeof(int32_t) * n_req);
+        session_requests_ = 0;
+        return rc;
+    }
+
 private:
     // Copies the requests to the device in CSR form.
     int32_t Stage(const std::vector<KeyVector> &keys) {
@@ -403,7 +495,8 @@ private:
     GpuBlockIndex *index_;
     uint32_t avail_mask_;
     cudaStream_t stream_;
-    detail::Mirror keys_, key_off_, bits_, out_;
+    detail::Mirror keys_, key_off_, bits_, out_, n_new_, added_, new_off_, ws_;
+    int32_t session_requests_ = 0, session_class_ = 0;
 };
 
 // Trace replay without eviction, the loop of OptimizerRunner::RunTraces

@@ -157,6 +157,42 @@ static void TestWriteCycle() {
     EXPECT_EQ(index.AddLocation({1, 2}, {1, 2, 3}, &codes), KVCM_EC_BADARGS);
 }
 
+static void TestWriteBatch() {
+    // Three StartWriteCache requests in one call, answered as if served in order (cache_manager.cc:334-430,589-635):
+    // a b c writes all three; a b d e sees a b being written and writes d e; x b sees b and writes x (vector form).
+    GpuBlockIndex index(64);
+    GpuMetaSearcher searcher(&index);
+    std::vector<BlockMask> masks;
+    std::vector<KeyVector> fresh;
+    EXPECT_EQ(searcher.StartWriteCacheBatch({{11, 12, 13}, {11, 12, 14, 15}, {99, 12}}, 4, &masks, &fresh), KVCM_OK);
+    EXPECT_EQ(std::get<BlockMaskOffset>(masks[0]), size_t(0));
+    EXPECT_EQ(std::get<BlockMaskOffset>(masks[1]), size_t(2));
+    EXPECT_EQ(std::holds_alternative<BlockMaskVector>(masks[2]), true);
+    EXPECT_EQ(std::get<BlockMaskVector>(masks[2])[0], false);
+    EXPECT_EQ(std::get<BlockMaskVector>(masks[2])[1], true);
+    EXPECT_EQ(fresh[0].size(), size_t(3));
+    EXPECT_EQ(fresh[1].size(), size_t(2));
+    EXPECT_EQ(fresh[1][0], 14);
+    EXPECT_EQ(fresh[2].size(), size_t(1));
+    EXPECT_EQ(fresh[2][0], 99);
+    size_t len = 99;
+    EXPECT_EQ(searcher.PrefixMatch({11, 12, 13}, BlockMask{}, &len), KVCM_OK);
+    EXPECT_EQ(len, size_t(0));
+    std::vector<int32_t> codes;
+    // an invalid mask (a vector of the wrong length) refuses the call
+    EXPECT_EQ(searcher.FinishWriteCacheBatch({BlockMask{BlockMaskOffset{3}}, BlockMask{BlockMaskVector{true}},
+                                              BlockMask{BlockMaskOffset{0}}}, &codes), KVCM_EC_BADARGS);
+    EXPECT_EQ(searcher.FinishWriteCacheBatch({BlockMask{BlockMaskOffset{3}}, BlockMask{BlockMaskVector{true, false}},
+                                              BlockMask{BlockMaskOffset{0}}}, &codes), KVCM_OK);
+    EXPECT_EQ(codes[0] | codes[1] | codes[2], KVCM_OK);
+    EXPECT_EQ(searcher.PrefixMatch({11, 12, 14, 15}, BlockMask{}, &len), KVCM_OK);
+    EXPECT_EQ(len, size_t(3));  // 15 failed and is gone
+    std::vector<uint8_t> flags;
+    EXPECT_EQ(searcher.BatchGet({15, 99}, &flags), KVCM_OK);
+    EXPECT_EQ(int(flags[0]), 0);
+    EXPECT_EQ(int(flags[1]), 0);
+}
+
 static void TestIovCopier() {
     // a block of 3 layers x (K,V) iovs with one ignored iov in the middle
     const size_t sz = 4096;
@@ -392,6 +428,7 @@ int main() {
     TestPrefixMatch();
     TestSlidingWindowAndBatchGet();
     TestWriteCycle();
+    TestWriteBatch();
     TestIovCopier();
     TestReplay();
     std::printf(g_failed == 0 ? "host adapter test: all checks passed\n" : "host adapter test: %d checks FAILED\n", g_failed);
