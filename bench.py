@@ -394,12 +394,50 @@ def run_prefix_gpu(device, steps, warmup):
         torch.cuda.synchronize(device)
         out[name] = n_keys * steps / (e0.elapsed_time(e1) * 1e-3)
     matched = int(h_len.sum().item())
-    return dict(workload="4096 requests x 512-8192 uint32 tokens, block 64, 50% prefix reuse, index of 200k prior "
+    write_cycle = run_write_cycle(device, pkeys, d_keys, d_ko, max(3, steps // 4))
+    return dict(write_cycle=write_cycle,
+                workload="4096 requests x 512-8192 uint32 tokens, block 64, 50% prefix reuse, index of 200k prior "
                          "blocks; hash + prefix match",
                 token_blocks=n_keys, matched_blocks=matched, token_blocks_per_s=out["resident"],
                 block_size=bs, longest_request_tokens=int(np.max(off[1:] - off[:-1])),
                 e2e_token_blocks_per_s=out["e2e"], h2d_bytes_per_step=int(h_toks.numel() * 4 + h_off.numel() * 16),
                 d2h_bytes_per_step=int(h_len.numel() * 4), gpu_launches_per_step=2), (toks, off, ko, bs, ptoks, poff)
+
+
+def run_write_cycle(device, prior_keys, d_keys, d_ko, reps):
+    """The write side of the same batch: StartWriteCache of all requests in one call (filter + new locations in
+    CLS_WRITING, answered as if the requests were served in order), then FinishWriteCache of all sessions.  Every
+    repetition starts from an index that holds the prior blocks only.  Checked by what must hold afterwards: every
+    request's keys are served in full, every key is in the index once, and no request was left a key to write twice."""
+    import torch
+    from tair_kvcache_b200.manager import BatchMetaSearcher, BlockIndex, encode_locations
+    n_req = d_ko.numel() - 1
+    start_ms, finish_ms = [], []
+    for _ in range(reps):
+        index = BlockIndex(prior_keys.numel() + d_keys.numel(), device)
+        index.upsert(prior_keys, None, encode_locations([(3, 4)]))
+        searcher = BatchMetaSearcher(index)
+        torch.cuda.synchronize(device)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        ev[0].record()
+        sessions = searcher.StartWriteCache(d_keys, d_ko, 4)
+        ev[1].record()
+        codes = searcher.FinishWriteCache(sessions, success_off=sessions.new_off[1:] - sessions.new_off[:-1])
+        ev[2].record()
+        torch.cuda.synchronize(device)
+        start_ms.append(ev[0].elapsed_time(ev[1]))
+        finish_ms.append(ev[1].elapsed_time(ev[2]))
+    new_locations = int(sessions.new_off[-1].item())
+    served = searcher.PrefixMatch(d_keys, d_ko)
+    distinct = int(torch.unique(torch.cat([prior_keys, d_keys])).numel())
+    ok = (bool(torch.equal(served.long(), d_ko[1:] - d_ko[:-1])) and int(codes.abs().sum().item()) == 0 and
+          index.stats()[1] == distinct and new_locations == distinct - int(torch.unique(prior_keys).numel()))
+    start, finish = float(np.median(start_ms)), float(np.median(finish_ms))
+    return {"requests": n_req, "keys": int(d_keys.numel()), "new_locations": new_locations,
+            "start_write_ms": start, "finish_write_ms": finish,
+            "keys_per_s": d_keys.numel() / ((start + finish) * 1e-3), "gpu_launches": 7, "parity_ok": ok,
+            "parity": "after the cycle every request is served in full, the index holds every distinct key once, "
+                      "and the sessions hold every new key exactly once"}
 
 
 def run_prefix_cpu(data, threads, budget_s=12.0):
@@ -700,6 +738,7 @@ def main_prefix(args, ctx):
     line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                         "traffic": None, "peak_kind": peak_kind,
                         "chain_latency_floor_ms": pm["longest_request_tokens"] * 40 / 1.965e6}
+    line["write_cycle"] = pm["write_cycle"]
     if not args.no_cpu:
         cpu, n_rep = run_prefix_cpu(data, threads)
         line["cpu_baseline"] = {"value": cpu, "unit": "token-blocks/s", "cores": threads, "kind": "port",
