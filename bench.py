@@ -1469,6 +1469,9 @@ def main_lru(args, ctx):
     if n_inst > 1 and policy == "leaf_aware_lru":
         from tair_kvcache_b200 import _cabi
         ws_bytes = _cabi.lib().kvcm_b200_replay_leaf_lru_group_workspace_bytes(n_keys, n_req, n_cfg, n_inst)
+    if n_inst > 1 and policy == "random_lru":
+        from tair_kvcache_b200 import _cabi
+        ws_bytes = _cabi.lib().kvcm_b200_replay_random_lru_group_workspace_bytes(n_keys, n_cfg, n_inst)
     workspace = torch.empty(ws_bytes + 4096, dtype=torch.uint8, device=device)
     status = torch.zeros(4, dtype=torch.int32, device=device)
 
@@ -2157,7 +2160,7 @@ def main():
     ap.add_argument("--n-configs", type=int, default=0, help="lru: quota points per GPU (default 148)")
     ap.add_argument("--instances", type=int, default=1,
                     help="lru: instances that share each quota (requests go to them round-robin; group-rough eviction)")
-    ap.add_argument("--policy", default="lru", choices=["lru", "leaf_aware_lru"],
+    ap.add_argument("--policy", default="lru", choices=["lru", "leaf_aware_lru", "random_lru"],
                     help="lru: the eviction policy of the sweep (eviction_policy_type)")
     ap.add_argument("--no-prefix", action="store_true", help="skip the prefix-match side measurement")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-staging leg (profiling runs)")
