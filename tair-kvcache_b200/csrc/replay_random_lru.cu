@@ -186,8 +186,13 @@ extern "C" {
 int32_t kvcm_b200_selftest_partial_sort(uint32_t *h_idx, int64_t *h_times, uint32_t k, uint32_t n) {
     if (h_idx == nullptr || h_times == nullptr) return KVCM_ER_INVALID_ADDRESS;
     if (k > n) return KVCM_EC_BADARGS;
-    kvcm::Sample s{h_idx, h_times};
-    kvcm::PartialSortByTime(s, k, n);
+    std::vector<kvcm::SampleEntry> s(n);
+    for (uint32_t i = 0; i < n; ++i) s[i] = kvcm::SampleEntry{h_times[i], h_idx[i], 0};
+    kvcm::PartialSortByTime(s.data(), k, n);
+    for (uint32_t i = 0; i < n; ++i) {
+        h_times[i] = s[i].t;
+        h_idx[i] = s[i].idx;
+    }
     return KVCM_OK;
 }
 

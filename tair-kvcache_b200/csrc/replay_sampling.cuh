@@ -30,85 +30,136 @@ constexpr uint32_t kMaxBatch = KVCM_B200_RANDOM_LRU_MAX_BATCH;    // blocks evic
 constexpr uint32_t kNotCached = 0xFFFFFFFFu;
 constexpr uint64_t kSamplingSeed = 0x12345678ABCDEF01ull;  // random_lru.h:20; every policy object starts from it
 
-// The sample: index into the block vector and that block's time, moved together.
-struct Sample {
-    uint32_t *idx;
-    int64_t *t;
-    __host__ __device__ __forceinline__ void Move(uint32_t to, uint32_t from) {
-        idx[to] = idx[from];
-        t[to] = t[from];
-    }
-    __host__ __device__ __forceinline__ void Put(uint32_t to, uint32_t i, int64_t time) {
-        idx[to] = i;
-        t[to] = time;
-    }
+// One sampled block: its last access time and its index in the block vector, moved together - one 16-byte shared
+// memory access each way.
+struct __align__(16) SampleEntry {
+    int64_t t;
+    uint32_t idx;
+    uint32_t pad;
 };
 
+__host__ __device__ __forceinline__ SampleEntry LoadEntry(const SampleEntry *s, uint32_t i) {
+#ifdef __CUDA_ARCH__
+    const int4 v = *reinterpret_cast<const int4 *>(s + i);
+    SampleEntry e;
+    e.t = static_cast<int64_t>(static_cast<uint32_t>(v.x)) | (static_cast<int64_t>(v.y) << 32);
+    e.idx = static_cast<uint32_t>(v.z);
+    e.pad = 0;
+    return e;
+#else
+    return s[i];
+#endif
+}
+
+__host__ __device__ __forceinline__ void StoreEntry(SampleEntry *s, uint32_t i, const SampleEntry &e) {
+#ifdef __CUDA_ARCH__
+    *reinterpret_cast<int4 *>(s + i) = make_int4(static_cast<int>(static_cast<uint32_t>(e.t)),
+                                                 static_cast<int>(e.t >> 32), static_cast<int>(e.idx), 0);
+#else
+    s[i] = e;
+#endif
+}
+
 // Sift-up of `value` from `hole` towards `top` in a max-heap ordered by time (the standard library's push-heap step).
-__host__ __device__ __forceinline__ void PushHeap(Sample &s, uint32_t hole, uint32_t top, uint32_t v_idx, int64_t v_t) {
+__host__ __device__ __forceinline__ void PushHeap(SampleEntry *s, uint32_t hole, uint32_t top, const SampleEntry &value) {
     while (hole > top) {
         const uint32_t parent = (hole - 1) / 2;
-        if (!(s.t[parent] < v_t)) break;
-        s.Move(hole, parent);
+        const SampleEntry above = LoadEntry(s, parent);
+        if (!(above.t < value.t)) break;
+        StoreEntry(s, hole, above);
         hole = parent;
     }
-    s.Put(hole, v_idx, v_t);
+    StoreEntry(s, hole, value);
 }
 
 // The hole at `hole` sinks to a leaf along the larger children (the right child unless it is smaller than the
 // left), then `value` is sifted up from there: the standard library's adjust-heap step.
-__host__ __device__ __forceinline__ void AdjustHeap(Sample &s, uint32_t hole, uint32_t len, uint32_t v_idx, int64_t v_t) {
+__host__ __device__ __forceinline__ void AdjustHeap(SampleEntry *s, uint32_t hole, uint32_t len, const SampleEntry &value) {
     const uint32_t top = hole;
     uint32_t child = hole;
     while (child < (len - 1) / 2) {
         child = 2 * (child + 1);
-        if (s.t[child] < s.t[child - 1]) --child;
-        s.Move(hole, child);
+        const SampleEntry right = LoadEntry(s, child), left = LoadEntry(s, child - 1);
+        const bool take_left = right.t < left.t;
+        if (take_left) --child;
+        StoreEntry(s, hole, take_left ? left : right);
         hole = child;
     }
     if ((len & 1u) == 0 && child == (len - 2) / 2) {
         child = 2 * (child + 1);
-        s.Move(hole, child - 1);
+        StoreEntry(s, hole, LoadEntry(s, child - 1));
         hole = child - 1;
     }
-    PushHeap(s, hole, top, v_idx, v_t);
+    PushHeap(s, hole, top, value);
 }
 
-// std::partial_sort(first, first + k, first + n) by time: heap-select, then sort-heap.
-__host__ __device__ void PartialSortByTime(Sample &s, uint32_t k, uint32_t n) {
-    if (k == 0) return;
-    if (k >= 2) {  // make-heap over the first k
-        uint32_t parent = (k - 2) / 2;
-        while (true) {
-            const uint32_t vi = s.idx[parent];
-            const int64_t vt = s.t[parent];
-            AdjustHeap(s, parent, k, vi, vt);
-            if (parent == 0) break;
-            --parent;
-        }
-    }
-    for (uint32_t i = k; i < n; ++i) {  // an element older than the heap's top takes its place
-        if (s.t[i] < s.t[0]) {
-            const uint32_t vi = s.idx[i];
-            const int64_t vt = s.t[i];
-            s.Move(i, 0);
-            AdjustHeap(s, 0, k, vi, vt);
-        }
-    }
-    for (uint32_t last = k; last > 1;) {  // sort-heap
-        --last;
-        const uint32_t vi = s.idx[last];
-        const int64_t vt = s.t[last];
-        s.Move(last, 0);
-        AdjustHeap(s, 0, last, vi, vt);
+__host__ __device__ __forceinline__ void MakeHeap(SampleEntry *s, uint32_t k) {
+    if (k < 2) return;
+    uint32_t parent = (k - 2) / 2;
+    while (true) {
+        AdjustHeap(s, parent, k, LoadEntry(s, parent));
+        if (parent == 0) break;
+        --parent;
     }
 }
+
+__host__ __device__ __forceinline__ void SortHeap(SampleEntry *s, uint32_t k) {
+    for (uint32_t last = k; last > 1;) {
+        --last;
+        const SampleEntry value = LoadEntry(s, last);
+        StoreEntry(s, last, LoadEntry(s, 0));
+        AdjustHeap(s, 0, last, value);
+    }
+}
+
+// std::partial_sort(first, first + k, first + n) by time: make-heap over the first k, heap-select (an element older
+// than the heap's top takes its place), sort-heap.  One thread, as the algorithm is written.
+__host__ __device__ __forceinline__ void PartialSortByTime(SampleEntry *s, uint32_t k, uint32_t n) {
+    if (k == 0) return;
+    MakeHeap(s, k);
+    for (uint32_t i = k; i < n; ++i) {
+        const SampleEntry value = LoadEntry(s, i);
+        if (value.t < s[0].t) {
+            StoreEntry(s, i, LoadEntry(s, 0));
+            AdjustHeap(s, 0, k, value);
+        }
+    }
+    SortHeap(s, k);
+}
+
+#ifdef __CUDACC__
+// The same for a warp: the heap steps stay lane 0's, in the algorithm's order, but the search for the next sample
+// that is older than the heap's top - most samples are not - is a ballot over 32 samples at a time.  The top only
+// gets older, so a sample that fails the test once is out for good, and the samples of a chunk that still pass
+// after a replacement are visited in their order, exactly as the loop above visits them.
+__device__ __forceinline__ void PartialSortByTimeWarp(SampleEntry *s, uint32_t k, uint32_t n, uint32_t lane) {
+    if (k == 0) return;
+    if (lane == 0) MakeHeap(s, k);
+    __syncwarp();
+    for (uint32_t base = k; base < n; base += 32) {
+        const uint32_t i = base + lane;
+        const int64_t mine = i < n ? s[i].t : 0;
+        uint32_t below = __ballot_sync(0xffffffffu, i < n && mine < s[0].t);
+        while (below != 0) {
+            const uint32_t j = static_cast<uint32_t>(__ffs(below)) - 1u;
+            if (lane == 0) {
+                const SampleEntry value = LoadEntry(s, base + j);
+                StoreEntry(s, base + j, LoadEntry(s, 0));
+                AdjustHeap(s, 0, k, value);
+            }
+            __syncwarp();
+            below = __ballot_sync(0xffffffffu, lane > j && i < n && mine < s[0].t);
+        }
+    }
+    if (lane == 0) SortHeap(s, k);
+    __syncwarp();
+}
+#endif
 
 // One warp's shared memory for a round of evictions.
 struct SamplingScratch {
-    int64_t s_t[kMaxSample];  // the sampled blocks' times (the raw draws before that)
-    int64_t tail_ts[kMaxBatch];  // ts / blk of the last entries of the vector, [j] = index size - 1 - j
-    uint32_t s_idx[kMaxSample];  // the sampled indices
+    SampleEntry sample[kMaxSample];  // the sampled blocks (the raw draws in .t before that)
+    int64_t tail_ts[kMaxBatch];      // ts / blk of the last entries of the vector, [j] = index size - 1 - j
     uint32_t v_id[kMaxBatch], v_at[kMaxBatch];  // the round's victims: block id, current index
     uint32_t tail_blk[kMaxBatch];
 };
@@ -124,34 +175,41 @@ __device__ __forceinline__ uint32_t SamplingEvictRound(SamplingScratch &sc, uint
     const uint32_t want = count < held ? static_cast<uint32_t>(count) : n_blocks;  // total_to_evict
     const uint32_t n_sample = sampling_size < n_blocks ? sampling_size : n_blocks;
     const uint32_t k = want < n_sample ? want : n_sample;
-    Sample sample{sc.s_idx, sc.s_t};
     // the draws, in sequence (lane 0), then their modulo and the sampled blocks' times (all lanes)
     if (lane == 0) {
         uint64_t x = *rng;
-        uint64_t *raw = reinterpret_cast<uint64_t *>(sc.s_t);
         for (uint32_t i = 0; i < n_sample; ++i) {
             x ^= x << 13;
             x ^= x >> 7;
             x ^= x << 17;
-            raw[i] = x;
+            sc.sample[i].t = static_cast<int64_t>(x);
         }
         *rng = x;
     }
     __syncwarp();
-    for (uint32_t i = lane; i < n_sample; i += 32) {
-        const uint32_t at = static_cast<uint32_t>(reinterpret_cast<uint64_t *>(sc.s_t)[i] % n_blocks);
-        sc.s_idx[i] = at;
-        sc.s_t[i] = ts[at];
+    for (uint32_t i0 = lane; i0 < n_sample; i0 += 128) {  // four sampled times in flight per lane
+        uint32_t at[4];
+        int64_t seen[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const uint32_t i = i0 + 32u * u;
+            at[u] = i < n_sample ? static_cast<uint32_t>(static_cast<uint64_t>(sc.sample[i].t) % n_blocks) : 0u;
+            seen[u] = i < n_sample ? ts[at[u]] : 0;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const uint32_t i = i0 + 32u * u;
+            if (i < n_sample) StoreEntry(sc.sample, i, SampleEntry{seen[u], at[u], 0u});
+        }
     }
     __syncwarp();
-    if (lane == 0) PartialSortByTime(sample, k, n_sample);
-    __syncwarp();
+    PartialSortByTimeWarp(sc.sample, k, n_sample, lane);
     // the victims as blocks (resolved before the first removal, as the reference resolves them), and the tail
     // of the vector, which the removals read
     const uint32_t n_tail = k < n_blocks ? k : n_blocks;
     for (uint32_t i = lane; i < k; i += 32) {
-        sc.v_at[i] = sc.s_idx[i];
-        sc.v_id[i] = blk[sc.s_idx[i]];
+        sc.v_at[i] = sc.sample[i].idx;
+        sc.v_id[i] = blk[sc.sample[i].idx];
     }
     for (uint32_t i = lane; i < n_tail; i += 32) {
         sc.tail_blk[i] = blk[n_blocks - 1 - i];
