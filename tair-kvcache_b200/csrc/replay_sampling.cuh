@@ -128,10 +128,10 @@ __host__ __device__ __forceinline__ void PartialSortByTime(SampleEntry *s, uint3
 }
 
 #ifdef __CUDACC__
-// The same for a warp: the heap steps stay lane 0's, in the algorithm's order, but the search for the next sample
-// that is older than the heap's top - most samples are not - is a ballot over 32 samples at a time.  The top only
-// gets older, so a sample that fails the test once is out for good, and the samples of a chunk that still pass
-// after a replacement are visited in their order, exactly as the loop above visits them.
+// The same for a warp: the heap steps stay lane 0's, in the algorithm's order, but the search for the samples
+// that are older than the heap's top - most are not - is a ballot over 32 samples at a time.  The top only gets
+// older, so a sample that fails the test once is out for good; lane 0 visits the ones that passed in their order
+// and tests each again against the top of that moment, exactly as the loop above does.
 __device__ __forceinline__ void PartialSortByTimeWarp(SampleEntry *s, uint32_t k, uint32_t n, uint32_t lane) {
     if (k == 0) return;
     if (lane == 0) MakeHeap(s, k);
@@ -140,16 +140,19 @@ __device__ __forceinline__ void PartialSortByTimeWarp(SampleEntry *s, uint32_t k
         const uint32_t i = base + lane;
         const int64_t mine = i < n ? s[i].t : 0;
         uint32_t below = __ballot_sync(0xffffffffu, i < n && mine < s[0].t);
-        while (below != 0) {
-            const uint32_t j = static_cast<uint32_t>(__ffs(below)) - 1u;
-            if (lane == 0) {
-                const SampleEntry value = LoadEntry(s, base + j);
-                StoreEntry(s, base + j, LoadEntry(s, 0));
-                AdjustHeap(s, 0, k, value);
+        if (below == 0) continue;
+        if (lane == 0) {
+            while (below != 0) {
+                const uint32_t j = base + static_cast<uint32_t>(__ffs(below)) - 1u;
+                below &= below - 1u;
+                const SampleEntry value = LoadEntry(s, j);
+                if (value.t < s[0].t) {
+                    StoreEntry(s, j, LoadEntry(s, 0));
+                    AdjustHeap(s, 0, k, value);
+                }
             }
-            __syncwarp();
-            below = __ballot_sync(0xffffffffu, lane > j && i < n && mine < s[0].t);
         }
+        __syncwarp();
     }
     if (lane == 0) SortHeap(s, k);
     __syncwarp();
