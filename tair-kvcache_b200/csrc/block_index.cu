@@ -1003,6 +1003,7 @@ struct StartWrite {
     uint32_t *first;       // per id: the first request that names the key
     uint8_t *snap;         // per key occurrence: the flags of the key before the batch
     uint8_t *ordered;      // per request: 1 = names a key with a map but nothing writable: served in order
+    uint32_t *n_ordered;   // how many requests that is
     uint8_t *late_added;   // per id: such a key got its location from an earlier request of the batch
     int32_t *offset_out;
     uint8_t *mask_out;
@@ -1012,8 +1013,8 @@ struct StartWrite {
     uint32_t *status;      // [0] keys refused because the table is full
 };
 
-__global__ void StartWriteInitKernel(IdTable t, uint32_t *first, uint8_t *late_added, uint8_t *ordered, int64_t n_keys,
-                                     int32_t n_req) {
+__global__ void StartWriteInitKernel(IdTable t, uint32_t *first, uint8_t *late_added, uint8_t *ordered,
+                                     uint32_t *n_ordered, int64_t n_keys, int32_t n_req) {
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
     const uint64_t at = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     for (uint64_t i = at; i <= t.mask; i += stride) t.slots[i] = make_ulonglong2(kEmptyKey, ~0ull);
@@ -1025,6 +1026,7 @@ __global__ void StartWriteInitKernel(IdTable t, uint32_t *first, uint8_t *late_a
     if (at == 0) {
         t.cells[0] = 0ull;
         t.cells[1] = ~0ull;
+        *n_ordered = 0u;
     }
 }
 
@@ -1043,7 +1045,10 @@ __global__ void __launch_bounds__(kMatchWarps * 32) StartWriteSnapshotKernel(Sta
             late = late || (f & KVCM_FLAG_NONEMPTY) != 0;
         }
     }
-    if (__any_sync(0xffffffffu, late) && LaneId() == 0) p.ordered[req] = 1;
+    if (__any_sync(0xffffffffu, late) && LaneId() == 0) {
+        p.ordered[req] = 1;
+        atomicAdd(p.n_ordered, 1u);
+    }
 }
 
 // Pass 2 (a warp per request): ids, and per key the first request that names it.
@@ -1059,7 +1064,9 @@ __global__ void __launch_bounds__(kMatchWarps * 32) StartWriteOwnersKernel(Start
     }
 }
 
-// One request, all lanes of a warp: its block mask, and the locations it adds.
+// One request, all lanes of a warp: its block mask, and the locations it adds.  kCareful as in UpsertOne: the batch
+// could push the slots in use past the table's bound, so every claim of an empty slot takes a seat first.
+template <bool kCareful>
 __device__ __forceinline__ void StartWriteOne(const StartWrite &p, int32_t req, int32_t *d_live, int32_t *d_used) {
     const uint32_t lane = LaneId();
     const uint32_t full = 0xffffffffu;
@@ -1126,7 +1133,7 @@ __device__ __forceinline__ void StartWriteOne(const StartWrite &p, int32_t req, 
             if (key == kEmptyKey || key == kTombKey) {
                 put(reinterpret_cast<unsigned long long *>(&p.ix.cells[key - kEmptyKey]));
                 if (put.into_empty_word) *d_live += 1;
-            } else if (!UpsertOne<true>(p.ix, key, put, d_live, d_used)) {
+            } else if (!UpsertOne<kCareful>(p.ix, key, put, d_live, d_used)) {
                 put.code = KVCM_EC_NOSPC;
                 if (p.status != nullptr) atomicAdd(&p.status[0], 1u);
             }
@@ -1140,15 +1147,18 @@ __device__ __forceinline__ void StartWriteOne(const StartWrite &p, int32_t req, 
 }
 
 // Pass 3: every request that can be served by itself, a warp each.
+template <bool kCareful>
 __global__ void __launch_bounds__(kMatchWarps * 32) StartWriteParallelKernel(StartWrite p) {
     const int32_t req = blockIdx.x * kMatchWarps + (threadIdx.x >> 5);
     int32_t d_live = 0, d_used = 0;
-    if (req < p.n_req && p.ordered[req] == 0) StartWriteOne(p, req, &d_live, &d_used);
+    if (req < p.n_req && p.ordered[req] == 0) StartWriteOne<kCareful>(p, req, &d_live, &d_used);
     AddCellsPerWarp(p.ix, d_live, d_used);
 }
 
-// Pass 4: the others, one warp, in batch order.
+// Pass 4: the others, one warp, in batch order (nothing to do for most batches).
+template <bool kCareful>
 __global__ void __launch_bounds__(32) StartWriteOrderedKernel(StartWrite p) {
+    if (*p.n_ordered == 0u) return;
     int32_t d_live = 0, d_used = 0;
     for (int32_t base = 0; base < p.n_req; base += 32) {
         const int32_t mine = base + static_cast<int32_t>(LaneId());
@@ -1156,7 +1166,7 @@ __global__ void __launch_bounds__(32) StartWriteOrderedKernel(StartWrite p) {
         while (todo != 0) {
             const int32_t req = base + __ffs(todo) - 1;
             todo &= todo - 1;
-            StartWriteOne(p, req, &d_live, &d_used);
+            StartWriteOne<kCareful>(p, req, &d_live, &d_used);
             __threadfence();  // what this request added is what the next one sees
             __syncwarp();
         }
@@ -1926,6 +1936,7 @@ int32_t kvcm_b200_filter_write(kvcm_b200_index_t *ix, const int64_t *d_keys, con
 namespace {
 
 struct StartWriteLayout {
+    // (the first 256 bytes hold the id table's two cells and the count of requests served in order)
     size_t table_off, ids_off, first_off, snap_off, late_off, ordered_off, n_added_off, total;
 };
 
@@ -1972,6 +1983,7 @@ int32_t kvcm_b200_start_write(kvcm_b200_index_t *ix, const int64_t *d_keys, cons
     if (reinterpret_cast<uintptr_t>(d_workspace) & 255u) return KVCM_ER_INVALID_ADDRESS;
     if (workspace_bytes < need) return KVCM_EC_NOSPC;
     MaybeRehash(ix, stream);
+    const bool careful = ix->used_upper + static_cast<uint64_t>(n_keys_total) > ix->max_live;
     ix->used_upper += static_cast<uint64_t>(n_keys_total);
     if (ix->used_upper > ix->n_slots) ix->used_upper = ix->n_slots;
     const StartWriteLayout l = StartWriteLayoutFor(n_keys_total, n_req);
@@ -1991,6 +2003,7 @@ int32_t kvcm_b200_start_write(kvcm_b200_index_t *ix, const int64_t *d_keys, cons
     p.snap = ws + l.snap_off;
     p.late_added = ws + l.late_off;
     p.ordered = ws + l.ordered_off;
+    p.n_ordered = reinterpret_cast<uint32_t *>(ws + 16);  // beside the id table's two cells in the first 256 bytes
     p.n_added = reinterpret_cast<int32_t *>(ws + l.n_added_off);
     p.offset_out = d_offset_out;
     p.mask_out = d_mask_out;
@@ -2001,11 +2014,17 @@ int32_t kvcm_b200_start_write(kvcm_b200_index_t *ix, const int64_t *d_keys, cons
     const int sms = kvcm::GetDeviceInfo().sm_count;
     const unsigned grid = kvcm::GridFor(n_req, kvcm::kMatchWarps);
     const unsigned threads = kvcm::kMatchWarps * 32;
-    kvcm::StartWriteInitKernel<<<sms * 4, 256, 0, s>>>(p.table, p.first, p.late_added, p.ordered, n_keys_total, n_req);
+    kvcm::StartWriteInitKernel<<<sms * 4, 256, 0, s>>>(p.table, p.first, p.late_added, p.ordered, p.n_ordered,
+                                                       n_keys_total, n_req);
     kvcm::StartWriteSnapshotKernel<<<grid, threads, 0, s>>>(p);
     kvcm::StartWriteOwnersKernel<<<grid, threads, 0, s>>>(p);
-    kvcm::StartWriteParallelKernel<<<grid, threads, 0, s>>>(p);
-    kvcm::StartWriteOrderedKernel<<<1, 32, 0, s>>>(p);
+    if (careful) {
+        kvcm::StartWriteParallelKernel<true><<<grid, threads, 0, s>>>(p);
+        kvcm::StartWriteOrderedKernel<true><<<1, 32, 0, s>>>(p);
+    } else {
+        kvcm::StartWriteParallelKernel<false><<<grid, threads, 0, s>>>(p);
+        kvcm::StartWriteOrderedKernel<false><<<1, 32, 0, s>>>(p);
+    }
     kvcm::StartWriteOffsetsKernel<<<1, 1024, 0, s>>>(p.n_added, n_req, d_new_off_out);
     return kvcm::LaunchStatus();
 }
