@@ -10,7 +10,7 @@ Like the reference, the calls return as soon as the kernel is enqueued on the cu
 callers record an event and synchronise (kv_cache_manager/py_connector/vllm/data_transfer.py:138-150).
 """
 import os
-from typing import List, Optional, Sequence, Union
+from typing import Optional, Sequence, Union
 
 import numpy as np
 import torch

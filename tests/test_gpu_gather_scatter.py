@@ -328,7 +328,6 @@ def test_large_roundtrip_property():
 
 
 def test_pageable_host_staging_is_refused_not_dereferenced():
-    import ctypes
     host, dev, ptrs = _make(31, 1, 16, 64)
     pageable = np.zeros(4096, dtype=np.uint8)
     rows = torch.arange(4, dtype=torch.int32, device=DEV)

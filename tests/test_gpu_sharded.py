@@ -14,7 +14,7 @@ from oracle import kvcm_oracle as oracle
 
 import tair_kvcache_b200  # noqa: F401
 from tair_kvcache_b200 import _cabi
-from tair_kvcache_b200.manager import BlockIndex, CudaShardBackend, ShardedMetaSearcher, encode_locations, shard_of_keys
+from tair_kvcache_b200.manager import CudaShardBackend, ShardedMetaSearcher, encode_locations, shard_of_keys
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"

@@ -3,7 +3,6 @@ import json
 
 import numpy as np
 import pytest
-import torch
 
 from oracle import kvcm_oracle as oracle
 
