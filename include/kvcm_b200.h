@@ -464,6 +464,36 @@ KVCM_API int32_t kvcm_b200_finish_write(kvcm_b200_index_t *index, const int64_t 
                                         int32_t n_req, const uint8_t *d_added, const int64_t *d_new_off,
                                         const int64_t *d_success_off, const uint8_t *d_success_bits,
                                         int32_t storage_class, int32_t *d_results, kvcm_stream_t stream);
+/* The same two calls for ONE table of a hash-range-sharded index .  Every shard runs them on
+ * the same batch - all shards' requests in one order, e.g. gathered rank after rank - and gets the same answers:
+ *   1. kvcm_b200_write_snapshot_sharded: d_flags_out[i] = the flags of key i (KVCM_FLAG_*, with KVCM_FLAG_HAS_CLASS)
+ *      where this shard owns it, 0 elsewhere; a bytewise maximum over the shards (an all-reduce) gives every shard
+ *      every key's flags as its owner sees them before the batch.
+ *   2. kvcm_b200_start_write_sharded with those flags: block masks and write sessions for all requests, computed
+ *      alike on every shard; each shard merges the new locations of the keys it owns.  Whether a key takes its
+ *      location is read off its flags (the class is free or not), so the sessions agree everywhere; a full table
+ *      shows in the owner's d_status[0] only.  d_request_skip (optional, one byte per request) marks entries of
+ *      the batch that are no requests (padding of a gathered batch): they get empty answers.
+ *   3. kvcm_b200_finish_write_sharded: every shard makes the transitions of the session keys it owns; d_results[r]
+ *      holds this shard's part (a maximum over the shards gives the request's code).
+ * No kernel of these reads another shard's table. */
+KVCM_API int32_t kvcm_b200_write_snapshot_sharded(kvcm_b200_index_t *index, const int64_t *d_keys, int64_t n,
+                                                  uint32_t avail_mask, int32_t storage_class, int32_t shard_count,
+                                                  int32_t shard_rank, uint8_t *d_flags_out, kvcm_stream_t stream);
+KVCM_API int32_t kvcm_b200_start_write_sharded(kvcm_b200_index_t *index, const int64_t *d_keys,
+                                               const int64_t *d_key_off, int32_t n_req, int64_t n_keys_total,
+                                               uint32_t avail_mask, int32_t storage_class,
+                                               const uint8_t *d_snapshot_flags, const uint8_t *d_request_skip,
+                                               int32_t shard_count, int32_t shard_rank, void *d_workspace,
+                                               int64_t workspace_bytes, int32_t *d_offset_out, uint8_t *d_mask_out,
+                                               int32_t *d_n_new_out, uint8_t *d_added_out, int64_t *d_new_off_out,
+                                               uint32_t *d_status, kvcm_stream_t stream);
+KVCM_API int32_t kvcm_b200_finish_write_sharded(kvcm_b200_index_t *index, const int64_t *d_keys,
+                                                const int64_t *d_key_off, int32_t n_req, const uint8_t *d_added,
+                                                const int64_t *d_new_off, const int64_t *d_success_off,
+                                                const uint8_t *d_success_bits, int32_t storage_class,
+                                                int32_t shard_count, int32_t shard_rank, int32_t *d_results,
+                                                kvcm_stream_t stream);
 
 /* MetaSearcher::BatchGetBestLocation / BatchGetLocation (kv_cache_manager/manager/meta_searcher.cc:147-194,
  * 267-310): per key, no early stop.  d_flags_out[i]: bit0 a location would be returned (servable),
@@ -472,6 +502,7 @@ KVCM_API int32_t kvcm_b200_finish_write(kvcm_b200_index_t *index, const int64_t 
 #define KVCM_FLAG_EXISTS 2u
 #define KVCM_FLAG_NONEMPTY 4u
 #define KVCM_FLAG_WRITABLE 8u
+#define KVCM_FLAG_HAS_CLASS 16u /* only in the flags of kvcm_b200_write_snapshot_sharded: the key holds a location of the write's class */
 KVCM_API int32_t kvcm_b200_batch_get(kvcm_b200_index_t *index, const int64_t *d_keys, int64_t n, uint32_t avail_mask,
                                      uint8_t *d_flags_out, kvcm_stream_t stream);
 

@@ -34,7 +34,7 @@ POLICY_LEAF_AWARE_LRU, POLICY_LRU, POLICY_RANDOM_LRU = 0, 1, 2  # kvcm_b200_repl
 VAL_NONEMPTY = 1 << 32
 VAL_PRESENT = 1 << 63
 AVAIL_ALL = 0xFFFF
-FLAG_SERVABLE, FLAG_EXISTS, FLAG_NONEMPTY, FLAG_WRITABLE = 1, 2, 4, 8
+FLAG_SERVABLE, FLAG_EXISTS, FLAG_NONEMPTY, FLAG_WRITABLE, FLAG_HAS_CLASS = 1, 2, 4, 8, 16
 
 _vp = ctypes.c_void_p
 _i32 = ctypes.c_int32
@@ -103,6 +103,10 @@ SIGNATURES = {
     "kvcm_b200_index_update_status_sharded": [_vp, _vp, _vp, _u32, _i64, _i32, _i32, _vp, _vp],
     "kvcm_b200_start_write_workspace_bytes": [_i64, _i32],
     "kvcm_b200_start_write": [_vp, _vp, _vp, _i32, _i64, _u32, _i32, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+    "kvcm_b200_write_snapshot_sharded": [_vp, _vp, _i64, _u32, _i32, _i32, _i32, _vp, _vp],
+    "kvcm_b200_start_write_sharded": [_vp, _vp, _vp, _i32, _i64, _u32, _i32, _vp, _vp, _i32, _i32, _vp, _i64, _vp, _vp,
+                                      _vp, _vp, _vp, _vp, _vp],
+    "kvcm_b200_finish_write_sharded": [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp],
     "kvcm_b200_finish_write": [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp],
     "kvcm_b200_index_add_location": [_vp, _vp, _vp, _i32, _i32, _i64, _vp, _vp, _vp],
     "kvcm_b200_index_add_location_sharded": [_vp, _vp, _vp, _i32, _i32, _i64, _i32, _i32, _vp, _vp, _vp],

@@ -580,6 +580,22 @@ __device__ __forceinline__ uint8_t FlagsOf(uint64_t v, uint32_t avail_mask) {
     return static_cast<uint8_t>(f);
 }
 
+// The flags a write looks at: the ones above, and whether the key already holds a location of the class the write
+// goes to (whatever its status).
+__device__ __forceinline__ uint8_t WriteFlagsOf(uint64_t v, uint32_t avail_mask, uint32_t cls) {
+    uint8_t f = FlagsOf(v, avail_mask);
+    if (v != 0 && ((v >> (KVCM_VAL_STATUS_SHIFT + 3u * cls)) & 7u) != 0) f |= KVCM_FLAG_HAS_CLASS;
+    return f;
+}
+
+__global__ void WriteSnapshotKernel(IndexView ix, const int64_t *__restrict__ keys, int64_t n, uint32_t avail_mask,
+                                    uint32_t cls, Shard shard, uint8_t *__restrict__ flags) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint64_t key = static_cast<uint64_t>(keys[i]);
+    flags[i] = Owns(shard, key) ? WriteFlagsOf(Lookup(ix, key), avail_mask, cls) : 0;
+}
+
 __global__ void BatchGetKernel(IndexView ix, const int64_t *__restrict__ keys, int64_t n, uint32_t avail_mask,
                                Shard shard, uint8_t *__restrict__ flags) {
     const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -1010,6 +1026,12 @@ struct StartWrite {
     int32_t *n_new_out;
     uint8_t *added_out;    // per key occurrence: 1 = this request gave the key its new location
     int32_t *n_added;      // per request: how many keys that is (the length of its write session)
+    // One table of a hash-range-sharded index: every shard runs the call on the same batch (all shards' requests in
+    // one order) with the same flags per key - each key's flags come from its owner, snap_in - and merges the
+    // locations of the keys it owns; whether a key of another shard takes its location is read off its flags.
+    const uint8_t *snap_in;
+    const uint8_t *skip;   // optional, per request: 1 = not a request (padding of the gathered batch)
+    Shard shard;
     uint32_t *status;      // [0] keys refused because the table is full
 };
 
@@ -1033,12 +1055,12 @@ __global__ void StartWriteInitKernel(IdTable t, uint32_t *first, uint8_t *late_a
 // Pass 1 (a warp per request): the flags of every key before the batch; keys that are not writable claim an id.
 __global__ void __launch_bounds__(kMatchWarps * 32) StartWriteSnapshotKernel(StartWrite p) {
     const int32_t req = blockIdx.x * kMatchWarps + (threadIdx.x >> 5);
-    if (req >= p.n_req) return;
+    if (req >= p.n_req || (p.skip != nullptr && p.skip[req] != 0)) return;
     const int64_t beg = p.key_off[req], end = p.key_off[req + 1];
     bool late = false;
     for (int64_t i = beg + LaneId(); i < end; i += 32) {
         const uint64_t key = static_cast<uint64_t>(p.keys[i]);
-        const uint8_t f = FlagsOf(Lookup(p.ix, key), p.avail_mask);
+        const uint8_t f = p.snap_in != nullptr ? p.snap_in[i] : WriteFlagsOf(Lookup(p.ix, key), p.avail_mask, p.cls);
         p.snap[i] = f;
         if ((f & KVCM_FLAG_WRITABLE) == 0) {
             ClaimId(p.table, key, nullptr);
@@ -1054,7 +1076,7 @@ __global__ void __launch_bounds__(kMatchWarps * 32) StartWriteSnapshotKernel(Sta
 // Pass 2 (a warp per request): ids, and per key the first request that names it.
 __global__ void __launch_bounds__(kMatchWarps * 32) StartWriteOwnersKernel(StartWrite p) {
     const int32_t req = blockIdx.x * kMatchWarps + (threadIdx.x >> 5);
-    if (req >= p.n_req) return;
+    if (req >= p.n_req || (p.skip != nullptr && p.skip[req] != 0)) return;
     const int64_t beg = p.key_off[req], end = p.key_off[req + 1];
     for (int64_t i = beg + LaneId(); i < end; i += 32) {
         if ((p.snap[i] & KVCM_FLAG_WRITABLE) != 0) continue;
@@ -1073,6 +1095,15 @@ __device__ __forceinline__ void StartWriteOne(const StartWrite &p, int32_t req, 
     const int64_t beg = p.key_off[req];
     const int64_t n = p.key_off[req + 1] - beg;
     const uint32_t r = static_cast<uint32_t>(req);
+    if (p.skip != nullptr && p.skip[req] != 0) {  // padding: no keys of its own, nothing to answer
+        for (int64_t i = lane; i < n; i += 32) {
+            p.added_out[beg + i] = 0;
+            if (p.mask_out != nullptr) p.mask_out[beg + i] = 0;
+        }
+        if (lane == 0) p.offset_out[req] = p.n_new_out[req] = p.n_added[req] = 0;
+        return;
+    }
+    const bool sharded = p.snap_in != nullptr;
     // what this request sees of key i: (exists for write, location map non-empty, id)
     auto view = [&](int64_t i, bool *exists, bool *nonempty, uint32_t *id) {
         const uint8_t f = p.snap[beg + i];
@@ -1129,15 +1160,20 @@ __device__ __forceinline__ void StartWriteOne(const StartWrite &p, int32_t req, 
         uint8_t added = 0;
         if (is_new) {
             const uint64_t key = static_cast<uint64_t>(p.keys[beg + i]);
+            // in a sharded call every shard has to give the same answer: the class is free or it is not, which the
+            // key's flags say (a full table shows in the owner's status count only)
+            const bool takes_it = (p.snap[beg + i] & KVCM_FLAG_HAS_CLASS) == 0;
             MergeLocation put{p.cls, 2u /* CLS_WRITING */, KVCM_EC_ERROR, false};
-            if (key == kEmptyKey || key == kTombKey) {
+            if (!Owns(p.shard, key)) {
+                put.code = takes_it ? KVCM_OK : KVCM_EC_EXIST;
+            } else if (key == kEmptyKey || key == kTombKey) {
                 put(reinterpret_cast<unsigned long long *>(&p.ix.cells[key - kEmptyKey]));
                 if (put.into_empty_word) *d_live += 1;
             } else if (!UpsertOne<kCareful>(p.ix, key, put, d_live, d_used)) {
                 put.code = KVCM_EC_NOSPC;
                 if (p.status != nullptr) atomicAdd(&p.status[0], 1u);
             }
-            added = put.code == KVCM_OK ? 1 : 0;
+            added = (sharded ? takes_it : put.code == KVCM_OK) ? 1 : 0;
             if (added != 0 && nonempty) p.late_added[id] = 1;
         }
         if (i < n) p.added_out[beg + i] = added;
@@ -1217,7 +1253,7 @@ __global__ void __launch_bounds__(kMatchWarps * 32)
     FinishWriteKernel(IndexView ix, const int64_t *__restrict__ keys, const int64_t *__restrict__ key_off, int32_t n_req,
                       const uint8_t *__restrict__ added, const int64_t *__restrict__ new_off,
                       const int64_t *__restrict__ success_off, const uint8_t *__restrict__ success_bits, uint32_t cls,
-                      int32_t *__restrict__ results) {
+                      Shard shard, int32_t *__restrict__ results) {
     const int32_t req = blockIdx.x * kMatchWarps + (threadIdx.x >> 5);
     if (req >= n_req) return;
     const uint32_t lane = LaneId();
@@ -1238,8 +1274,11 @@ __global__ void __launch_bounds__(kMatchWarps * 32)
         if (is_mine) {
             const int64_t j = rank + __popc(m & ((1u << lane) - 1u));
             const bool ok = success_bits != nullptr ? success_bits[new_off[req] + j] != 0 : j < success_off[req];
-            const int32_t code = RunStatusTask(ix, static_cast<uint64_t>(keys[beg + i]), ok ? serve : drop);
-            if (ok && code != KVCM_OK) worst = code;
+            const uint64_t key = static_cast<uint64_t>(keys[beg + i]);
+            if (Owns(shard, key)) {  // the owner shard makes the transition
+                const int32_t code = RunStatusTask(ix, key, ok ? serve : drop);
+                if (ok && code != KVCM_OK) worst = code;
+            }
         }
         rank += __popc(m);
     }
@@ -1962,9 +2001,10 @@ int64_t kvcm_b200_start_write_workspace_bytes(int64_t n_keys_total, int32_t n_re
     return static_cast<int64_t>(StartWriteLayoutFor(n_keys_total, n_req).total);
 }
 
-int32_t kvcm_b200_start_write(kvcm_b200_index_t *ix, const int64_t *d_keys, const int64_t *d_key_off, int32_t n_req,
-                              int64_t n_keys_total, uint32_t avail_mask, int32_t storage_class, void *d_workspace,
-                              int64_t workspace_bytes, int32_t *d_offset_out, uint8_t *d_mask_out,
+static int32_t StartWriteImpl(kvcm_b200_index_t *ix, const int64_t *d_keys, const int64_t *d_key_off, int32_t n_req,
+                              int64_t n_keys_total, uint32_t avail_mask, int32_t storage_class,
+                              const uint8_t *d_snapshot_flags, const uint8_t *d_request_skip, kvcm::Shard shard,
+                              void *d_workspace, int64_t workspace_bytes, int32_t *d_offset_out, uint8_t *d_mask_out,
                               int32_t *d_n_new_out, uint8_t *d_added_out, int64_t *d_new_off_out, uint32_t *d_status,
                               kvcm_stream_t stream) {
     if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
@@ -2010,6 +2050,9 @@ int32_t kvcm_b200_start_write(kvcm_b200_index_t *ix, const int64_t *d_keys, cons
     p.n_new_out = d_n_new_out;
     p.added_out = d_added_out;
     p.status = d_status;
+    p.snap_in = d_snapshot_flags;
+    p.skip = d_request_skip;
+    p.shard = shard;
     cudaStream_t s = kvcm::AsStream(stream);
     const int sms = kvcm::GetDeviceInfo().sm_count;
     const unsigned grid = kvcm::GridFor(n_req, kvcm::kMatchWarps);
@@ -2029,10 +2072,51 @@ int32_t kvcm_b200_start_write(kvcm_b200_index_t *ix, const int64_t *d_keys, cons
     return kvcm::LaunchStatus();
 }
 
-int32_t kvcm_b200_finish_write(kvcm_b200_index_t *ix, const int64_t *d_keys, const int64_t *d_key_off, int32_t n_req,
+int32_t kvcm_b200_start_write(kvcm_b200_index_t *ix, const int64_t *d_keys, const int64_t *d_key_off, int32_t n_req,
+                              int64_t n_keys_total, uint32_t avail_mask, int32_t storage_class, void *d_workspace,
+                              int64_t workspace_bytes, int32_t *d_offset_out, uint8_t *d_mask_out,
+                              int32_t *d_n_new_out, uint8_t *d_added_out, int64_t *d_new_off_out, uint32_t *d_status,
+                              kvcm_stream_t stream) {
+    return StartWriteImpl(ix, d_keys, d_key_off, n_req, n_keys_total, avail_mask, storage_class, nullptr, nullptr,
+                          kvcm::Shard{1, 0}, d_workspace, workspace_bytes, d_offset_out, d_mask_out, d_n_new_out,
+                          d_added_out, d_new_off_out, d_status, stream);
+}
+
+int32_t kvcm_b200_start_write_sharded(kvcm_b200_index_t *ix, const int64_t *d_keys, const int64_t *d_key_off,
+                                      int32_t n_req, int64_t n_keys_total, uint32_t avail_mask, int32_t storage_class,
+                                      const uint8_t *d_snapshot_flags, const uint8_t *d_request_skip,
+                                      int32_t shard_count, int32_t shard_rank, void *d_workspace,
+                                      int64_t workspace_bytes, int32_t *d_offset_out, uint8_t *d_mask_out,
+                                      int32_t *d_n_new_out, uint8_t *d_added_out, int64_t *d_new_off_out,
+                                      uint32_t *d_status, kvcm_stream_t stream) {
+    if (shard_count < 1 || shard_rank < 0 || shard_rank >= shard_count) return KVCM_EC_BADARGS;
+    if (d_snapshot_flags == nullptr && n_keys_total > 0) return KVCM_ER_INVALID_ADDRESS;
+    return StartWriteImpl(ix, d_keys, d_key_off, n_req, n_keys_total, avail_mask, storage_class, d_snapshot_flags,
+                          d_request_skip, kvcm::Shard{static_cast<uint32_t>(shard_count), static_cast<uint32_t>(shard_rank)},
+                          d_workspace, workspace_bytes, d_offset_out, d_mask_out, d_n_new_out, d_added_out,
+                          d_new_off_out, d_status, stream);
+}
+
+int32_t kvcm_b200_write_snapshot_sharded(kvcm_b200_index_t *ix, const int64_t *d_keys, int64_t n, uint32_t avail_mask,
+                                         int32_t storage_class, int32_t shard_count, int32_t shard_rank,
+                                         uint8_t *d_flags_out, kvcm_stream_t stream) {
+    if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    if (n < 0 || storage_class < 0 || storage_class > 7 || shard_count < 1 || shard_rank < 0 ||
+        shard_rank >= shard_count) {
+        return KVCM_EC_BADARGS;
+    }
+    if (n == 0) return KVCM_OK;
+    if (d_keys == nullptr || d_flags_out == nullptr) return KVCM_ER_INVALID_ADDRESS;
+    kvcm::WriteSnapshotKernel<<<kvcm::GridFor(n, 256), 256, 0, kvcm::AsStream(stream)>>>(
+        kvcm::LocalView(ix), d_keys, n, avail_mask, static_cast<uint32_t>(storage_class),
+        kvcm::Shard{static_cast<uint32_t>(shard_count), static_cast<uint32_t>(shard_rank)}, d_flags_out);
+    return kvcm::LaunchStatus();
+}
+
+static int32_t FinishWriteImpl(kvcm_b200_index_t *ix, const int64_t *d_keys, const int64_t *d_key_off, int32_t n_req,
                                const uint8_t *d_added, const int64_t *d_new_off, const int64_t *d_success_off,
-                               const uint8_t *d_success_bits, int32_t storage_class, int32_t *d_results,
-                               kvcm_stream_t stream) {
+                               const uint8_t *d_success_bits, int32_t storage_class, kvcm::Shard shard,
+                               int32_t *d_results, kvcm_stream_t stream) {
     if (ix == nullptr) return KVCM_ER_INVALID_ADDRESS;
     if (n_req < 0 || storage_class < 0 || storage_class > 7) return KVCM_EC_BADARGS;
     if (n_req == 0) return KVCM_OK;
@@ -2044,8 +2128,27 @@ int32_t kvcm_b200_finish_write(kvcm_b200_index_t *ix, const int64_t *d_keys, con
     kvcm::FinishWriteKernel<<<kvcm::GridFor(n_req, kvcm::kMatchWarps), kvcm::kMatchWarps * 32, 0,
                               kvcm::AsStream(stream)>>>(kvcm::LocalView(ix), d_keys, d_key_off, n_req, d_added,
                                                         d_new_off, d_success_off, d_success_bits,
-                                                        static_cast<uint32_t>(storage_class), d_results);
+                                                        static_cast<uint32_t>(storage_class), shard, d_results);
     return kvcm::LaunchStatus();
+}
+
+int32_t kvcm_b200_finish_write(kvcm_b200_index_t *ix, const int64_t *d_keys, const int64_t *d_key_off, int32_t n_req,
+                               const uint8_t *d_added, const int64_t *d_new_off, const int64_t *d_success_off,
+                               const uint8_t *d_success_bits, int32_t storage_class, int32_t *d_results,
+                               kvcm_stream_t stream) {
+    return FinishWriteImpl(ix, d_keys, d_key_off, n_req, d_added, d_new_off, d_success_off, d_success_bits,
+                           storage_class, kvcm::Shard{1, 0}, d_results, stream);
+}
+
+int32_t kvcm_b200_finish_write_sharded(kvcm_b200_index_t *ix, const int64_t *d_keys, const int64_t *d_key_off,
+                                       int32_t n_req, const uint8_t *d_added, const int64_t *d_new_off,
+                                       const int64_t *d_success_off, const uint8_t *d_success_bits,
+                                       int32_t storage_class, int32_t shard_count, int32_t shard_rank,
+                                       int32_t *d_results, kvcm_stream_t stream) {
+    if (shard_count < 1 || shard_rank < 0 || shard_rank >= shard_count) return KVCM_EC_BADARGS;
+    return FinishWriteImpl(ix, d_keys, d_key_off, n_req, d_added, d_new_off, d_success_off, d_success_bits,
+                           storage_class, kvcm::Shard{static_cast<uint32_t>(shard_count), static_cast<uint32_t>(shard_rank)},
+                           d_results, stream);
 }
 
 int32_t kvcm_b200_batch_get(kvcm_b200_index_t *ix, const int64_t *d_keys, int64_t n, uint32_t avail_mask,

@@ -63,6 +63,44 @@ class CudaShardBackend:
                    shard_rank, out.data_ptr(), self.index._s())
         return out
 
+    def write_snapshot(self, keys, storage_class, shard_count, shard_rank):
+        """The flags a write looks at for the keys this shard owns, 0 for the others."""
+        out = torch.zeros(max(keys.numel(), 1), dtype=torch.uint8, device=self.device)
+        _cabi.call("kvcm_b200_write_snapshot_sharded", self.index.handle, keys.data_ptr(), keys.numel(), self.avail_mask,
+                   int(storage_class), shard_count, shard_rank, out.data_ptr(), self.index._s())
+        return out[:keys.numel()]
+
+    def start_write_owned(self, keys, key_off, flags, skip, storage_class, shard_count, shard_rank, table_full=None):
+        """StartWriteCache of the whole (gathered) batch on this shard: the answers for every request, the new
+        locations of the keys this shard owns.  Returns (offset, mask, n_new, added, new_off)."""
+        n_req = key_off.numel() - 1
+        dev = self.device
+        need = int(_cabi.lib().kvcm_b200_start_write_workspace_bytes(keys.numel(), n_req))
+        if need < 0:
+            raise ValueError("too many keys for one StartWriteCache batch")
+        ws = torch.empty(need, dtype=torch.uint8, device=dev)
+        offset = torch.empty(max(n_req, 1), dtype=torch.int32, device=dev)
+        n_new = torch.empty(max(n_req, 1), dtype=torch.int32, device=dev)
+        mask = torch.empty(max(keys.numel(), 1), dtype=torch.uint8, device=dev)
+        added = torch.zeros(max(keys.numel(), 1), dtype=torch.uint8, device=dev)
+        new_off = torch.zeros(n_req + 1, dtype=torch.int64, device=dev)
+        flags = flags if flags.numel() > 0 else torch.zeros(1, dtype=torch.uint8, device=dev)
+        _cabi.call("kvcm_b200_start_write_sharded", self.index.handle, keys.data_ptr(), key_off.data_ptr(), n_req,
+                   keys.numel(), self.avail_mask, int(storage_class), flags.data_ptr(),
+                   skip.data_ptr() if skip is not None else None, shard_count, shard_rank, ws.data_ptr(), need,
+                   offset.data_ptr(), mask.data_ptr(), n_new.data_ptr(), added.data_ptr(), new_off.data_ptr(),
+                   table_full.data_ptr() if table_full is not None else None, self.index._s())
+        ws.record_stream(torch.cuda.current_stream(dev))
+        return offset[:n_req], mask, n_new[:n_req], added, new_off
+
+    def finish_write_owned(self, keys, key_off, added, new_off, success_off, storage_class, shard_count, shard_rank):
+        n_req = key_off.numel() - 1
+        out = torch.zeros(max(n_req, 1), dtype=torch.int32, device=self.device)
+        _cabi.call("kvcm_b200_finish_write_sharded", self.index.handle, keys.data_ptr(), key_off.data_ptr(), n_req,
+                   added.data_ptr(), new_off.data_ptr(), success_off.data_ptr(), None, int(storage_class), shard_count,
+                   shard_rank, out.data_ptr(), self.index._s())
+        return out[:n_req]
+
     def servable_flags(self, keys, shard_count=1, shard_rank=0):
         out = torch.empty(keys.numel(), dtype=torch.uint8, device=self.device)
         _cabi.call("kvcm_b200_batch_get_sharded", self.index.handle, keys.data_ptr(), keys.numel(), self.avail_mask,
@@ -142,6 +180,23 @@ class GatheredRequests:
 
     def __init__(self, keys, csr, per_req, first, n_req):
         self.keys, self.csr, self.per_req, self.first, self.n_req = keys, csr, per_req, first, n_req
+
+
+class ShardedWriteSessions:
+    """This rank's answers of a sharded StartWriteCache (offset / mask / n_new / added as in WriteSessions) and the
+    gathered batch its FinishWriteCache works on."""
+
+    def __init__(self, offset, mask, n_new, added, all_keys, csr, all_added, new_off, first, n_req, max_req,
+                 storage_class):
+        self.offset, self.mask, self.n_new, self.added = offset, mask, n_new, added
+        self.all_keys, self.csr, self.all_added, self.new_off = all_keys, csr, all_added, new_off
+        self.first, self.n_req, self.max_req, self.storage_class = first, n_req, max_req, storage_class
+
+    @property
+    def session_lengths(self) -> torch.Tensor:
+        """Session keys per request of this rank."""
+        lens = self.new_off[1:] - self.new_off[:-1]
+        return lens[self.first:self.first + self.n_req]
 
 
 class RoutedFlags:
@@ -329,6 +384,42 @@ class ShardedMetaSearcher:
         """Every rank contributes keys; each key is stored on the shard that owns it."""
         self.backend.upsert_owned(self._gather_keys(keys.contiguous()), value_word, self.world, self.rank)
         self._publish_writes()
+
+    # ---- write side ---------------------------------------------------------------------------
+    def StartWriteCache(self, keys: torch.Tensor, key_off: torch.Tensor, storage_class: int,
+                        table_full: Optional[torch.Tensor] = None) -> "ShardedWriteSessions":
+        """CacheManager::StartWriteCache (kv_cache_manager/manager/cache_manager.cc:334-430) for every rank's
+        requests at once, answered as if the reference had served them one after the other in the order (rank,
+        request): one all-gather of the requests, one all-reduce (bytewise maximum) of the flags each key's owner
+        sees, then every rank computes the same block masks and write sessions and merges the new locations of the
+        keys it owns.  Returns this rank's answers and what FinishWriteCache of the batch needs."""
+        n_req = key_off.numel() - 1
+        all_keys, csr, _, max_req, first = self._gather_requests(keys.contiguous(), key_off.contiguous(), None)
+        skip = torch.zeros(self.world * (max_req + 1), dtype=torch.uint8, device=self.device)
+        skip[max_req::max_req + 1] = 1  # every rank's last entry covers the padding of its segment
+        flags = self.backend.write_snapshot(all_keys, storage_class, self.world, self.rank)
+        dist.all_reduce(flags, op=dist.ReduceOp.MAX, group=self.group)
+        offset, mask, n_new, added, new_off = self.backend.start_write_owned(
+            all_keys, csr, flags, skip, storage_class, self.world, self.rank, table_full)
+        self._publish_writes()
+        k0 = int(csr[first].item())
+        return ShardedWriteSessions(offset[first:first + n_req], mask[k0:k0 + keys.numel()], n_new[first:first + n_req],
+                                    added[k0:k0 + keys.numel()], all_keys, csr, added, new_off, first, n_req, max_req,
+                                    int(storage_class))
+
+    def FinishWriteCache(self, sessions: "ShardedWriteSessions", success_off: torch.Tensor) -> torch.Tensor:
+        """CacheManager::FinishWriteCache (:432-501) for the sessions of one StartWriteCache batch: success_off is
+        this rank's BlockMaskOffset per request over its session keys.  Every rank makes the transitions of the
+        session keys it owns; returns this rank's result code per request."""
+        seg = torch.zeros(sessions.max_req + 1, dtype=torch.int64, device=self.device)
+        seg[:sessions.n_req] = success_off
+        all_success = torch.empty(self.world * (sessions.max_req + 1), dtype=torch.int64, device=self.device)
+        dist.all_gather_into_tensor(all_success, seg, group=self.group)
+        codes = self.backend.finish_write_owned(sessions.all_keys, sessions.csr, sessions.all_added, sessions.new_off,
+                                                all_success, sessions.storage_class, self.world, self.rank)
+        dist.all_reduce(codes, op=dist.ReduceOp.MAX, group=self.group)
+        self._publish_writes()
+        return codes[sessions.first:sessions.first + sessions.n_req]
 
     def Gather(self, keys: torch.Tensor, key_off: torch.Tensor, mask_off: Optional[torch.Tensor] = None
                ) -> GatheredRequests:

@@ -245,3 +245,169 @@ def test_two_nccl_ranks_match_the_unsharded_oracle(mode):
         assert np.array_equal(results[rank]["prefix"], full.prefix_match_batch(keys, off))
         assert np.array_equal(results[rank]["prefix_masked"], full.prefix_match_batch(keys, off, mask))
         assert np.array_equal(results[rank]["sw4"], full.sw_match_batch(keys, off, 4))
+
+
+def _write_world(seed, n_ranks):
+    """Per rank a few requests that share keys within and across ranks, over an index that already holds served,
+    half-written and nothing-writable keys."""
+    rng = np.random.default_rng(seed)
+    universe = np.unique(rng.integers(-(1 << 62), 1 << 62, size=2500, dtype=np.int64))
+    held = universe[rng.permutation(len(universe))[:700]]
+    maps = [[(oracle.CLS_SERVING, 4)] if j % 3 else ([(oracle.CLS_WRITING, 2)] if j % 2 else
+                                                      [(oracle.CLS_NOT_FOUND, 1)]) for j in range(len(held))]
+    reqs = []
+    for rank in range(n_ranks):
+        mine = []
+        for _ in range(60 + 10 * rank):
+            n = int(rng.integers(0, 30))
+            r = rng.choice(universe, size=n, replace=False)
+            everyone = [q for per_rank in reqs for q in per_rank] + mine
+            if everyone and rng.random() < 0.7:
+                src = everyone[int(rng.integers(len(everyone)))]
+                m = int(rng.integers(0, min(len(src), n) + 1))
+                r = np.concatenate([src[:m], r[~np.isin(r, src[:m])]])[:max(n, m)]
+            mine.append(r.astype(np.int64))
+        reqs.append(mine)
+    return universe, held, maps, reqs
+
+
+def _serve_in_order(ox, reqs, cls, success):
+    """The reference's order of events over all ranks' requests: (rank, request), filter then add; then every session
+    finishes with its success offset."""
+    want = []
+    for per_rank in reqs:
+        for r in per_rank:
+            kind, what, n_new = ox.filter_write(r)
+            new = r[what:] if kind == "offset" else r[~what]
+            free = np.array([all(t != cls for _, t in (ox.get(int(k)) or [])) for k in new], dtype=bool)
+            ox.add_location(new[free], cls, oracle.CLS_WRITING)
+            want.append((kind, what, n_new, new[free]))
+    for (kind, what, n_new, new), s in zip(want, success):
+        good = np.arange(len(new)) < s
+        ox.update_status(new[good], cls, -1, oracle.CLS_SERVING)
+        ox.update_status(new[~good], cls, -1, -1)
+    return want
+
+
+def test_sharded_write_batch_on_one_gpu():
+    """Three shards in one process, the collectives replaced by what they compute (concatenation, bytewise maximum):
+    every shard answers alike, and together the shards hold what the unsharded oracle holds after serving the same
+    requests in order."""
+    from test_gpu_index_write import _decode
+    count = 3
+    universe, held, maps, reqs = _write_world(31, count)
+    ox = oracle.Index()
+    ox.put(held, maps)
+    shards = [CudaShardBackend(len(universe), torch.device(DEV)) for _ in range(count)]
+    words = torch.tensor([encode_locations(m) for m in maps], dtype=torch.int64, device=DEV)
+    for r, sh in enumerate(shards):
+        _cabi.call("kvcm_b200_index_upsert_sharded", sh.index.handle, torch.from_numpy(held).to(DEV).data_ptr(),
+                   words.data_ptr(), 0, len(held), count, r, None, sh.index._s())
+    flat = [q for per_rank in reqs for q in per_rank]
+    off = np.zeros(len(flat) + 1, dtype=np.int64)
+    np.cumsum([len(q) for q in flat], out=off[1:])
+    keys = np.concatenate(flat + [np.zeros(0, np.int64)])
+    dk, doff = torch.from_numpy(keys).to(DEV), torch.from_numpy(off).to(DEV)
+    flags = torch.stack([sh.write_snapshot(dk, 4, count, r) for r, sh in enumerate(shards)]).max(0).values
+    outs = [sh.start_write_owned(dk, doff, flags, None, 4, count, r) for r, sh in enumerate(shards)]
+    for o in outs[1:]:  # every shard gives the same answers
+        for a, b in zip(outs[0], o):
+            assert torch.equal(a, b)
+    offset, mask, n_new, added, new_off = (t.cpu().numpy() for t in outs[0])
+    rng = np.random.default_rng(5)
+    lens = new_off[1:] - new_off[:-1]
+    success = np.array([int(rng.integers(0, n + 1)) for n in lens], dtype=np.int64)
+    want = _serve_in_order(ox, reqs, 4, success)
+    kinds = set()
+    for r, (kind, what, n, new) in enumerate(want):
+        a, b = off[r], off[r + 1]
+        kinds.add(kind)
+        assert n_new[r] == n
+        if kind == "offset":
+            assert offset[r] == what
+        else:
+            assert offset[r] == -1 and np.array_equal(mask[a:b].astype(bool), what)
+        assert np.array_equal(flat[r][added[a:b].astype(bool)], new), r
+    assert kinds == {"offset", "vector"}
+    codes = torch.stack([sh.finish_write_owned(dk, doff, outs[0][3], outs[0][4], torch.from_numpy(success).to(DEV), 4,
+                                               count, r) for r, sh in enumerate(shards)]).max(0).values
+    assert not codes.cpu().numpy().any()
+    # together the shards hold the oracle's maps, each key on its owner only
+    du = torch.from_numpy(universe).to(DEV)
+    words = torch.stack([sh.index.lookup(du) for sh in shards]).cpu().numpy()
+    owner = shard_of_keys(universe, count)
+    for j, k in enumerate(universe):
+        want_map = ox.get(int(k))
+        for r in range(count):
+            have = _decode(words[r][j])
+            if r != owner[j]:
+                assert have is None
+            else:
+                assert (have is None) == (want_map is None) and (want_map is None or sorted(have) == sorted(want_map)), k
+    assert sum(sh.index.stats()[1] for sh in shards) == len(ox)
+
+
+def _write_rank_main(rank, port, results):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=2, device_id=dev)
+    try:
+        universe, held, maps, reqs = _write_world(33, 2)
+        searcher = ShardedMetaSearcher(CudaShardBackend(len(universe), dev), mode="exchange")
+        words = torch.tensor([encode_locations(m) for m in maps], dtype=torch.int64, device=dev)
+        _cabi.call("kvcm_b200_index_upsert_sharded", searcher.backend.index.handle,
+                   torch.from_numpy(held).to(dev).data_ptr(), words.data_ptr(), 0, len(held), 2, rank, None,
+                   searcher.backend.index._s())
+        mine = reqs[rank]
+        off = np.zeros(len(mine) + 1, dtype=np.int64)
+        np.cumsum([len(q) for q in mine], out=off[1:])
+        keys = np.concatenate(mine + [np.zeros(0, np.int64)])
+        s = searcher.StartWriteCache(torch.from_numpy(keys).to(dev), torch.from_numpy(off).to(dev), 4)
+        lens = s.session_lengths.cpu().numpy()
+        success = (lens + 1) // 2
+        codes = searcher.FinishWriteCache(s, torch.from_numpy(success.astype(np.int64)).to(dev))
+        prefix = searcher.PrefixMatch(torch.from_numpy(keys).to(dev), torch.from_numpy(off).to(dev))
+        torch.cuda.synchronize()
+        results[rank] = dict(offset=s.offset.cpu().numpy(), mask=s.mask.cpu().numpy(), n_new=s.n_new.cpu().numpy(),
+                             added=s.added.cpu().numpy(), lens=lens, codes=codes.cpu().numpy(),
+                             prefix=prefix.cpu().numpy(), stored=searcher.backend.index.stats()[1])
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_nccl_ranks_write_batch():
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    with mp.Manager() as m:
+        results = m.dict()
+        mp.spawn(_write_rank_main, args=(port, results), nprocs=2, join=True)
+        results = dict(results)
+    universe, held, maps, reqs = _write_world(33, 2)
+    ox = oracle.Index()
+    ox.put(held, maps)
+    success = np.concatenate([(results[r]["lens"] + 1) // 2 for r in range(2)])
+    want = _serve_in_order(ox, reqs, 4, success)
+    at = 0
+    for rank in range(2):
+        res, k0 = results[rank], 0
+        assert not res["codes"].any()
+        for j, r in enumerate(reqs[rank]):
+            kind, what, n, new = want[at]
+            assert res["n_new"][j] == n and res["lens"][j] == len(new)
+            if kind == "offset":
+                assert res["offset"][j] == what
+            else:
+                assert res["offset"][j] == -1 and np.array_equal(res["mask"][k0:k0 + len(r)].astype(bool), what)
+            assert np.array_equal(r[res["added"][k0:k0 + len(r)].astype(bool)], new)
+            k0 += len(r)
+            at += 1
+        flat = np.concatenate(reqs[rank] + [np.zeros(0, np.int64)])
+        off = np.zeros(len(reqs[rank]) + 1, dtype=np.int64)
+        np.cumsum([len(q) for q in reqs[rank]], out=off[1:])
+        assert np.array_equal(res["prefix"], ox.prefix_match_batch(flat, off))
+    assert results[0]["stored"] + results[1]["stored"] == len(ox)
