@@ -44,6 +44,58 @@ class OracleShardBackend:
     def servable_flags(self, keys, shard_count=1, shard_rank=0):
         return torch.from_numpy(self.index.batch_get(keys.numpy()))
 
+    # ---- the write side: the same contract as CudaShardBackend, served request after request ----
+    def write_snapshot(self, keys, storage_class, shard_count, shard_rank):
+        k = keys.numpy()
+        flags = self.index.batch_get(k).astype(np.uint8)
+        for i, key in enumerate(k):
+            if any(t == storage_class for _, t in (self.index.get(int(key)) or [])):
+                flags[i] |= 16
+        flags[shard_of_keys(k, shard_count) != shard_rank] = 0
+        return torch.from_numpy(flags)
+
+    def start_write_owned(self, keys, key_off, flags, skip, storage_class, shard_count, shard_rank, table_full=None):
+        k, off, f = keys.numpy(), key_off.numpy(), flags.numpy()
+        n_req = len(off) - 1
+        owner = shard_of_keys(k, shard_count)
+        offset, n_new = np.zeros(n_req, np.int32), np.zeros(n_req, np.int32)
+        mask, added = np.zeros(len(k), np.uint8), np.zeros(len(k), np.uint8)
+        written = set()  # keys that got their location from a request served before
+        for r in range(n_req):
+            if skip is not None and skip[r]:
+                continue
+            a, b = off[r], off[r + 1]
+            exists = np.array([bool(f[i] & 8) or int(k[i]) in written for i in range(a, b)], dtype=bool)
+            nonempty = np.array([bool(f[i] & 4) or int(k[i]) in written for i in range(a, b)], dtype=bool)
+            mask[a:b] = nonempty
+            first = int(np.argmin(exists)) if not exists.all() else b - a
+            if not exists[first:].any():
+                offset[r], new = first, np.arange(first, b - a)
+            else:
+                offset[r], new = -1, np.flatnonzero(~nonempty)
+            n_new[r] = len(new)
+            for i in new + a:
+                if f[i] & 16:
+                    continue
+                added[i] = 1
+                written.add(int(k[i]))
+                if owner[i] == shard_rank:
+                    self.index.add_location([k[i]], storage_class, oracle.CLS_WRITING)
+        new_off = np.zeros(n_req + 1, np.int64)
+        np.cumsum([added[off[r]:off[r + 1]].sum() for r in range(n_req)], out=new_off[1:])
+        return tuple(torch.from_numpy(x) for x in (offset, mask, n_new, added, new_off))
+
+    def finish_write_owned(self, keys, key_off, added, new_off, success_off, storage_class, shard_count, shard_rank):
+        k, off, ad = keys.numpy(), key_off.numpy(), added.numpy().astype(bool)
+        owner = shard_of_keys(k, shard_count)
+        for r in range(len(off) - 1):
+            session = np.flatnonzero(ad[off[r]:off[r + 1]]) + off[r]
+            for j, i in enumerate(session):
+                if owner[i] == shard_rank:
+                    self.index.update_status([k[i]], storage_class, -1,
+                                             oracle.CLS_SERVING if j < int(success_off[r]) else -1)
+        return torch.zeros(len(off) - 1, dtype=torch.int32)
+
     def prefix_from_flags(self, flags, key_off, mask_off):
         f, off = flags.numpy() & 1, key_off.numpy()
         out = np.zeros(len(off) - 1, dtype=np.int32)
@@ -164,3 +216,91 @@ def test_shard_of_keys_is_a_balanced_partition():
     # chained block hashes of consecutive blocks spread too
     chain = oracle.gen_key_vector(np.arange(64 * 800, dtype=np.int64), 64)
     assert np.bincount(shard_of_keys(chain, 8), minlength=8).min() > 60
+
+
+def _write_rank_main(rank, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=2)
+    try:
+        universe, held, reqs = _write_world()
+        searcher = ShardedMetaSearcher(OracleShardBackend())
+        searcher.upsert(torch.from_numpy(held[rank::2].copy()), 0)
+        mine = reqs[rank]
+        off = np.zeros(len(mine) + 1, dtype=np.int64)
+        np.cumsum([len(q) for q in mine], out=off[1:])
+        keys = np.concatenate(mine + [np.zeros(0, np.int64)])
+        s = searcher.StartWriteCache(torch.from_numpy(keys), torch.from_numpy(off), 4)
+        lens = s.session_lengths.numpy().copy()
+        codes = searcher.FinishWriteCache(s, torch.from_numpy((lens + 1) // 2))
+        prefix = searcher.PrefixMatch(torch.from_numpy(keys), torch.from_numpy(off))
+        results[rank] = dict(offset=s.offset.numpy().copy(), mask=s.mask.numpy().copy(), n_new=s.n_new.numpy().copy(),
+                             added=s.added.numpy().copy(), lens=lens, codes=codes.numpy().copy(),
+                             prefix=prefix.numpy().copy(), stored=len(searcher.backend.index))
+    finally:
+        dist.destroy_process_group()
+
+
+def _write_world():
+    rng = np.random.default_rng(321)
+    universe = np.unique(rng.integers(-(1 << 62), 1 << 62, size=300, dtype=np.int64))
+    held = universe[rng.permutation(len(universe))[:80]]
+    reqs = {0: [], 1: []}
+    for rank in range(2):
+        for _ in range(6 + 3 * rank):
+            n = int(rng.integers(0, 12))
+            r = rng.choice(universe, size=n, replace=False)
+            everyone = reqs[0] + reqs[1]
+            if everyone and rng.random() < 0.7:
+                src = everyone[int(rng.integers(len(everyone)))]
+                m = int(rng.integers(0, min(len(src), n) + 1))
+                r = np.concatenate([src[:m], r[~np.isin(r, src[:m])]])[:max(n, m)]
+            reqs[rank].append(r.astype(np.int64))
+    return universe, held, reqs
+
+
+def test_two_gloo_ranks_write_batch():
+    """StartWriteCache / FinishWriteCache over two ranks: the gathering, the padding entries, the all-reduce of the
+    owners' flags and the slicing of each rank's answers, against the unsharded oracle serving all requests in the
+    order (rank, request)."""
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    with mp.Manager() as m:
+        results = m.dict()
+        mp.spawn(_write_rank_main, args=(port, results), nprocs=2, join=True)
+        results = dict(results)
+    universe, held, reqs = _write_world()
+    ox = oracle.Index()
+    ox.put_uniform(held)
+    want = []
+    for rank in range(2):
+        for r in reqs[rank]:
+            kind, what, n_new = ox.filter_write(r)
+            new = r[what:] if kind == "offset" else r[~what]
+            ox.add_location(new, 4, oracle.CLS_WRITING)
+            want.append((kind, what, n_new, new))
+    at, kinds = 0, set()
+    for rank in range(2):
+        res, k0 = results[rank], 0
+        assert not res["codes"].any()
+        for j, r in enumerate(reqs[rank]):
+            kind, what, n, new = want[at]
+            kinds.add(kind)
+            assert res["n_new"][j] == n and res["lens"][j] == len(new)
+            if kind == "offset":
+                assert res["offset"][j] == what
+            else:
+                assert res["offset"][j] == -1 and np.array_equal(res["mask"][k0:k0 + len(r)].astype(bool), what)
+            assert np.array_equal(r[res["added"][k0:k0 + len(r)].astype(bool)], new)
+            k0 += len(r)
+            at += 1
+    for (kind, what, n, new) in want:
+        good = np.arange(len(new)) < (len(new) + 1) // 2
+        ox.update_status(new[good], 4, -1, oracle.CLS_SERVING)
+        ox.update_status(new[~good], 4, -1, -1)
+    for rank in range(2):
+        flat = np.concatenate(reqs[rank] + [np.zeros(0, np.int64)])
+        off = np.zeros(len(reqs[rank]) + 1, dtype=np.int64)
+        np.cumsum([len(q) for q in reqs[rank]], out=off[1:])
+        assert np.array_equal(results[rank]["prefix"], ox.prefix_match_batch(flat, off))
+    assert results[0]["stored"] + results[1]["stored"] == len(ox) and kinds == {"offset", "vector"}
