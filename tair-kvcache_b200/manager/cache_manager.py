@@ -10,6 +10,7 @@ on the instance's index: hash (when tokens are given), match / batch-get, filter
 status transitions.  Batches of requests go through BatchMetaSearcher directly.
 """
 import secrets
+import time
 from typing import Dict, Optional, Sequence, Tuple, Union
 
 import numpy as np
@@ -53,7 +54,7 @@ class GpuCacheManager:
         self._instances: Dict[str, _Instance] = {}
         # WriteLocationManager (kv_cache_manager/manager/write_location_manager.h): write_session_id -> the keys
         # that got a location from StartWriteCache, and the storage class it lies in
-        self._sessions: Dict[str, Tuple[str, torch.Tensor]] = {}
+        self._sessions: Dict[str, Tuple[str, torch.Tensor, float]] = {}
 
     def RegisterInstance(self, instance_id: str, block_size: int, max_keys: int, storage_class: int = 4,
                          weights: Optional[Sequence[int]] = None) -> int:
@@ -128,7 +129,8 @@ class GpuCacheManager:
             return EC_OK, out
         return EC_ERROR, none
 
-    def StartWriteCache(self, instance_id: str, keys=None, tokens=None) -> Tuple[int, Optional[str], BlockMask, int]:
+    def StartWriteCache(self, instance_id: str, keys=None, tokens=None, write_timeout_seconds: float = 1800.0
+                        ) -> Tuple[int, Optional[str], BlockMask, int]:
         """(error code, write_session_id, block_mask, number of new locations).  block_mask is what FilterWriteCache
         decides (cache_manager.cc:589-635): the offset of the first key still to be written when the keys that exist
         form a prefix, else one bool per key (True = the key's location map is not empty); the keys outside it get a
@@ -153,8 +155,21 @@ class GpuCacheManager:
             if (codes != EC_OK).any():  # a full table, as the reference's "indexer reach max key count"
                 return int(codes[codes != EC_OK][0]), None, block_mask, 0
         session = secrets.token_hex(16)
-        self._sessions[session] = (instance_id, new_keys)
+        if new_keys.numel() == 0:
+            write_timeout_seconds = 10.0  # nothing to write: the session is dropped soon (cache_manager.cc:387-390)
+        self._sessions[session] = (instance_id, new_keys, time.monotonic() + float(write_timeout_seconds))
         return EC_OK, session, block_mask, int(new_keys.numel())
+
+    def ExpireWriteSessions(self, now: Optional[float] = None) -> int:
+        """What the reference's WriteLocationManager does when a session's write_timeout_seconds have passed: it
+        finishes the session with nothing written (FinishWriteCache with an offset of 0, cache_manager.cc:400-409),
+        so its locations are removed and a later FinishWriteCache of the session finds nothing.  Returns how many
+        sessions went.  The reference runs this from a timer thread; here the caller decides when."""
+        now = time.monotonic() if now is None else now
+        late = [sid for sid, (_, _, deadline) in self._sessions.items() if deadline <= now]
+        for sid in late:
+            self.FinishWriteCache(self._sessions[sid][0], sid, 0)
+        return len(late)
 
     def FinishWriteCache(self, instance_id: str, write_session_id: str, success_block_mask: BlockMask) -> int:
         """The session's keys inside success_block_mask turn CLS_SERVING (BatchUpdateLocationStatus); the locations
@@ -162,7 +177,7 @@ class GpuCacheManager:
         entry = self._sessions.pop(write_session_id, None)  # GetAndDelete: a session finishes once
         if entry is None:
             return EC_ERROR
-        _, new_keys = entry
+        _, new_keys, _ = entry
         n = int(new_keys.numel())
         if not IsBlockMaskValid(success_block_mask, n):
             return EC_BADARGS

@@ -134,3 +134,16 @@ def test_remove_and_trim():
     assert m.TrimCache("test_instance") == cm.EC_OK and m.index_of("test_instance").stats()[1] == 0
     assert len(m.GetCacheLocation("test_instance", PREFIX, [1, 2])[1]) == 0
     assert m.TrimCache("test_instance", remove_all=False) == cm.EC_OK + 1007
+
+
+def test_write_session_times_out():  # TestWriteCacheTimeout, cache_manager_test.cc:437-461
+    import time
+    m = _manager()
+    keys = [1, 2]
+    ec, session, mask, n_new = m.StartWriteCache("test_instance", keys, write_timeout_seconds=1)
+    assert (ec, mask, n_new) == (cm.EC_OK, 0, 2)
+    assert m.ExpireWriteSessions(now=time.monotonic() + 0.5) == 0        # not yet
+    assert m.ExpireWriteSessions(now=time.monotonic() + 6.0) == 1        # the reference's test sleeps six seconds
+    assert m.FinishWriteCache("test_instance", session, 2) == cm.EC_ERROR
+    assert m.GetCacheLocation("test_instance", BATCH_GET, keys)[1].tolist() == [False, False]
+    assert m.index_of("test_instance").stats()[1] == 0                   # the half-written locations are gone
