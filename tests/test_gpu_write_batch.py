@@ -188,3 +188,36 @@ def test_small_universes_drawn_by_hypothesis():
         _check_against_oracle(ix, ox, universe)
 
     run()
+
+
+def test_batch_of_the_window_match_configuration_by_its_properties():
+    """65,536 requests of 16-8,192 keys that share prefixes of 1,000 root prompts (the shape of the sliding-window
+    configuration, some 86 M keys): too large for the oracle, so checked by what must hold after StartWriteCache and a
+    FinishWriteCache in which every block succeeds - every request is served in full, the index holds every distinct
+    key once, and the sessions hold every new key exactly once."""
+    dev = torch.device(DEV)
+    rng = np.random.default_rng(7)
+    n_req, n_roots = 65536, 1000
+    lens = np.exp(rng.uniform(np.log(16), np.log(8192), size=n_req)).astype(np.int64)
+    root_len = np.exp(rng.uniform(np.log(16), np.log(8192), size=n_roots)).astype(np.int64)
+    root = (rng.zipf(1.1, size=n_req) - 1) % n_roots
+    share = np.minimum((rng.random(n_req) * np.minimum(lens, root_len[root])).astype(np.int64), lens)
+    off = np.zeros(n_req + 1, dtype=np.int64)
+    np.cumsum(lens, out=off[1:])
+    d_off, d_len = torch.from_numpy(off).to(dev), torch.from_numpy(lens).to(dev)
+    req_of = torch.repeat_interleave(torch.arange(n_req, device=dev), d_len)
+    within = torch.arange(int(off[-1]), device=dev) - d_off[:-1][req_of]
+    keys = torch.where(within < torch.from_numpy(share).to(dev)[req_of],
+                       (torch.from_numpy(root).to(dev)[req_of] << 32) | within, ((req_of + n_roots) << 32) | within)
+    del req_of, within
+    distinct = int(torch.unique(keys).numel())
+    index = BlockIndex(distinct + 1000, dev)
+    ms = BatchMetaSearcher(index)
+    full = torch.zeros(4, dtype=torch.int32, device=dev)
+    s = ms.StartWriteCache(keys, d_off, 4, full)
+    assert int(ms.PrefixMatch(keys, d_off).sum()) == 0                     # written, not served yet
+    codes = ms.FinishWriteCache(s, success_off=s.new_off[1:] - s.new_off[:-1])
+    torch.cuda.synchronize()
+    assert torch.equal(ms.PrefixMatch(keys, d_off).long(), d_len)
+    assert index.stats()[1] == distinct == int(s.new_off[-1]) and full[0].item() == 0 and not codes.any()
+    assert int((s.offset < 0).sum()) == 0 and int(s.n_new.sum()) == distinct   # new keys form suffixes here
