@@ -51,9 +51,12 @@ def _w(weights):
 
 
 class RefSearcher:
-    def __init__(self, max_keys=100000):
+    def __init__(self, max_keys=100000, in_memory=False):
+        """in_memory: the local backend without a storage URI - the reference's own switch
+        (meta/meta_local_backend.cc:27-34) - so that it keeps no file; with one it rewrites the file on every
+        mutation and a large index takes time quadratic in its keys to build."""
         self._dir = tempfile.mkdtemp(prefix="kvcm_ref_searcher_")
-        path = os.path.join(self._dir, "meta_local_backend_file")
+        path = "" if in_memory else os.path.join(self._dir, "meta_local_backend_file")
         self._h = ctypes.c_void_p(lib().kvcm_ref_searcher_create(path.encode(), ctypes.c_int64(max_keys)))
         if not self._h:
             raise RuntimeError("the reference's MetaIndexer did not initialise")

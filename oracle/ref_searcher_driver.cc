@@ -74,10 +74,14 @@ BlockMask MaskFor(int32_t mask_kind, int64_t mask_off, const uint8_t *mask_vec, 
 
 extern "C" {
 
-// backend_file: where the local backend keeps its file (a fresh path).
+// backend_file: where the local backend keeps its file (a fresh path); empty or null = no storage URI, which is the
+// reference's own switch for a local backend that lives in memory only (meta_local_backend.cc:27-34) - with a file it
+// rewrites the whole file on every mutation, which makes a large index quadratic to build.
 void *kvcm_ref_searcher_create(const char *backend_file, int64_t max_keys) {
     auto backend_config = std::make_shared<MetaStorageBackendConfig>();
-    backend_config->SetStorageUri(std::string("file://") + backend_file);
+    if (backend_file != nullptr && backend_file[0] != 0) {
+        backend_config->SetStorageUri(std::string("file://") + backend_file);
+    }
     auto config = std::make_shared<MetaIndexerConfig>();
     config->SetMetaStorageBackendConfig(backend_config);
     config->SetMutexShardNum(32);

@@ -107,9 +107,9 @@ def test_status_transitions_on_random_task_batches():
 def test_hash_and_prefix_match_of_a_batch_of_requests():
     """The reference's CPU path for the prefix-match configuration end to end - the loop of GenKeyVector around its
     hashInt64Array, then PrefixMatch, on several host threads - against the oracle's hash + batched prefix match.
-    (Small on purpose: the reference's local meta backend rewrites its file on every mutation, so building its index
-    costs time quadratic in the number of keys - 13 s for 2,000 keys here, which is also why bench.py cannot time
-    this path at the configuration's 200,000 keys.)"""
+    Once with the local meta backend on a file, as the reference's own tests run it (it rewrites the file on every
+    mutation: 13 s for 2,000 keys), once without a storage URI, the reference's switch for a backend that lives in
+    memory - which is how bench.py builds the configuration's 200,000-key index in seconds and times this path."""
     rng = np.random.default_rng(2026)
     bs = 16
     prior = [rng.integers(0, 50000, size=int(rng.integers(64, 300))).astype(np.int64) for _ in range(60)]
@@ -129,12 +129,14 @@ def test_hash_and_prefix_match_of_a_batch_of_requests():
 
     (ptoks, poff), (toks, off) = csr(prior), csr(reqs)
     pkeys = np.unique(oracle.hash_blocks(ptoks, poff, bs, threads=2)[0])
-    r, ox = ref.RefSearcher(), oracle.Index()
-    r.add(pkeys, 4, oracle.CLS_SERVING)
+    ox = oracle.Index()
     ox.put_uniform(pkeys)
     keys, ko = oracle.hash_blocks(toks, off, bs, threads=2)
-    want = r.prefix_match_batch(toks, off, bs, threads=4)
-    assert np.array_equal(want, ox.prefix_match_batch(keys, ko, threads=2)) and want.sum() > 100
+    for in_memory in (False, True):
+        r = ref.RefSearcher(in_memory=in_memory)
+        r.add(pkeys, 4, oracle.CLS_SERVING)
+        want = r.prefix_match_batch(toks, off, bs, threads=4)
+        assert np.array_equal(want, ox.prefix_match_batch(keys, ko, threads=2)) and want.sum() > 100
 
 
 def test_locations_added_between_transitions():
