@@ -24,7 +24,7 @@ def _random_world(rng, n_keys, fill=0.12):
     most once, in a random status."""
     universe = rng.integers(-(1 << 62), 1 << 62, size=n_keys + n_keys // 4, dtype=np.int64)
     locs = {int(k): [] for k in universe[:n_keys]}
-    r, ox = ref.RefSearcher(), oracle.Index()
+    r, ox = ref.RefSearcher(in_memory=n_keys > 1000), oracle.Index()  # small worlds on a file, as the reference's tests
     for ty in range(5):
         for st in STATUSES:
             ks = [k for k in locs if rng.random() < fill and all(t != ty for _, t in locs[k])]
@@ -39,7 +39,7 @@ def _random_world(rng, n_keys, fill=0.12):
 
 def test_matchers_on_random_location_maps():
     rng = np.random.default_rng(2024)
-    universe, locs, r, ox = _random_world(rng, 1200)
+    universe, locs, r, ox = _random_world(rng, 6000)
     serving = [k for k in locs if any(s == oracle.CLS_SERVING for s, _ in locs[k])]
     hits = windows = 0
     for weights in (None, (1, 3, 0, 3, 5), (0, 0, 0, 0, 7)):
