@@ -101,6 +101,22 @@ class RefSearcher:
             raise RuntimeError("kvcm_ref_searcher_prefix_batch returned %d" % rc)
         return out
 
+    def window_match_batch(self, tokens, tok_off, block_size, sw, threads=1, weights=None):
+        """GenKeyVector + PrefixMatch + ReverseRollSlideWindowMatch per request on `threads` host threads:
+        (matched blocks, start of the window or -1 / -2) per request."""
+        t = np.ascontiguousarray(tokens, dtype=np.int64)
+        off = np.ascontiguousarray(tok_off, dtype=np.int64)
+        matched = np.zeros(len(off) - 1, dtype=np.int32)
+        base = np.zeros(len(off) - 1, dtype=np.int32)
+        w = _w(weights)
+        rc = lib().kvcm_ref_searcher_window_batch(self._h, _p(t, ctypes.c_int64), _p(off, ctypes.c_int64),
+                                                  ctypes.c_int64(len(off) - 1), ctypes.c_int32(block_size),
+                                                  ctypes.c_int32(sw), _p(w, ctypes.c_uint32), ctypes.c_int32(threads),
+                                                  _p(matched, ctypes.c_int32), _p(base, ctypes.c_int32))
+        if rc != 0:
+            raise RuntimeError("kvcm_ref_searcher_window_batch failed with %d" % rc)
+        return matched, base
+
     def sw_match(self, keys, sw, weights=None):
         """(start of the matched window or -1, number of locations returned); needs len(keys) >= sw > 0, which the
         reference asserts."""

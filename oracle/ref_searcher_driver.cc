@@ -168,6 +168,50 @@ int32_t kvcm_ref_searcher_prefix_batch(void *handle, const int64_t *tokens, cons
     return 0;
 }
 
+// The sliding-window configuration's CPU path per request: GenKeyVector, PrefixMatch and - where the request has at
+// least sw_size keys, which the reference asserts - ReverseRollSlideWindowMatch, on `threads` host threads.
+// matched_out[r] as above; base_out[r] = where the non-empty entries of the window answer start (-1 none, -2 fewer
+// keys than the window).
+int32_t kvcm_ref_searcher_window_batch(void *handle, const int64_t *tokens, const int64_t *tok_off, int64_t n_req,
+                                       int32_t block_size, int32_t sw, const uint32_t *weights, int32_t threads,
+                                       int32_t *matched_out, int32_t *base_out) {
+    auto *h = static_cast<RefSearcher *>(handle);
+    if (block_size <= 0 || threads <= 0 || sw <= 0) return static_cast<int32_t>(EC_BADARGS);
+    auto work = [&](int32_t tid) {
+        auto policy = PolicyFor(weights);
+        for (int64_t r = tid; r < n_req; r += threads) {
+            const int64_t *tok = tokens + tok_off[r];
+            const int64_t blocks = (tok_off[r + 1] - tok_off[r]) / block_size;
+            MetaSearcher::KeyVector keys(static_cast<size_t>(blocks));
+            int64_t hash = 0;
+            for (int64_t b = 0; b < blocks; ++b) {
+                hash = hashInt64Array(hash, tok + b * block_size, tok + (b + 1) * block_size);
+                keys[static_cast<size_t>(b)] = hash;
+            }
+            RequestContext context("oracle");
+            CacheLocationVector out;
+            h->searcher->PrefixMatch(&context, keys, BlockMask(BlockMaskVector{}), out, policy.get());
+            matched_out[r] = static_cast<int32_t>(out.size());
+            base_out[r] = -2;
+            if (blocks < sw) continue;
+            CacheLocationVector window;
+            h->searcher->ReverseRollSlideWindowMatch(&context, keys, sw, window, policy.get());
+            base_out[r] = -1;
+            for (size_t i = 0; i < window.size(); ++i) {
+                if (!window[i].id().empty()) {
+                    base_out[r] = static_cast<int32_t>(i);
+                    break;
+                }
+            }
+        }
+    };
+    std::vector<std::thread> pool;
+    for (int32_t t = 1; t < threads; ++t) pool.emplace_back(work, t);
+    work(0);
+    for (auto &t : pool) t.join();
+    return 0;
+}
+
 // MetaSearcher::ReverseRollSlideWindowMatch.  The reference returns one entry per key, empty but for the matched
 // window: the result here is where the non-empty entries start (-1: none; the reference's error code negated when
 // it fails), *count_out how many there are.  The reference asserts keys.size() >= sw_size > 0; such calls are not

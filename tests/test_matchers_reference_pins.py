@@ -137,6 +137,11 @@ def test_hash_and_prefix_match_of_a_batch_of_requests():
         r.add(pkeys, 4, oracle.CLS_SERVING)
         want = r.prefix_match_batch(toks, off, bs, threads=4)
         assert np.array_equal(want, ox.prefix_match_batch(keys, ko, threads=2)) and want.sum() > 100
+        # the sliding-window configuration's path: prefix and window match per request
+        for sw in (1, 3):
+            matched, base = r.window_match_batch(toks, off, bs, sw, threads=4)
+            assert np.array_equal(matched, want)
+            assert np.array_equal(base, ox.sw_match_batch(keys, ko, sw, threads=2)) and (base >= 0).any()
 
 
 def test_locations_added_between_transitions():
