@@ -1349,12 +1349,13 @@ def run_replay(args, ctx):
     return line
 
 
-def main_window_reference(args):
-    """CPU arm of --workload c4 on a bounded sample: the same length / sharing distributions at 1/32 of the requests
-    and of the index, hashed and matched by the oracle with all host threads."""
+def window_cpu_baseline(n_requests_total, threads, budget_s=10.0):
+    """The CPU side of the sliding-window configuration on a bounded sample - the same length / sharing
+    distributions at 1/32 of the requests and of the index - through the reference's own searcher compiled from its
+    sources where that library is there (checking its answers against the oracle's on the way), else through the
+    oracle.  Returns (token-blocks/s, repetitions, cpu_baseline dict, description of what ran)."""
     from oracle import kvcm_oracle as oracle
-    threads = os.cpu_count() or 1
-    n_req, n_roots, bs, sw = (args.n_requests or 65536) // 32, 64, 16, 256
+    n_req, n_roots, bs, sw = n_requests_total // 32, 64, 16, 256
     rng = np.random.default_rng(0xB2000004)
 
     def loguniform(n):
@@ -1389,7 +1390,7 @@ def main_window_reference(args):
         for a in range(0, len(index_keys), 20000):
             searcher.add(index_keys[a:a + 20000], 4, oracle.CLS_SERVING)
         t64 = toks.astype(np.int64)
-        while t_total < 10.0 and n < 500:
+        while t_total < budget_s and n < 500:
             t0 = time.perf_counter()
             matched, base = searcher.window_match_batch(t64, off, bs, sw, threads=threads)
             t_total += time.perf_counter() - t0
@@ -1397,7 +1398,7 @@ def main_window_reference(args):
         # the sample's answers are the oracle's
         assert np.array_equal(matched, ox.prefix_match_batch(keys0, ko0, threads=threads))
         assert np.array_equal(base, ox.sw_match_batch(keys0, ko0, sw, threads=threads))
-    while kind == "port" and t_total < 10.0 and n < 500:
+    while kind == "port" and t_total < budget_s and n < 500:
         t0 = time.perf_counter()
         keys, ko = oracle.hash_blocks(toks, off, bs, threads=threads)
         ox.prefix_match_batch(keys, ko, threads=threads)
@@ -1406,16 +1407,23 @@ def main_window_reference(args):
         n += 1
     value = int(ko0[-1]) * n / t_total
     sample = "%d of %d requests (%d token blocks), index of %d keys, %d repetitions" % (
-        n_req, args.n_requests or 65536, int(ko0[-1]), len(ox), n)
+        n_req, n_requests_total, int(ko0[-1]), len(ox), n)
     what = ("the reference's own GenKeyVector + MetaSearcher::PrefixMatch + ReverseRollSlideWindowMatch compiled from "
             "its sources (local meta backend in memory)" if kind == "reference" else
             "CPU restatement (hash + prefix + sliding-window match, without the reference's per-key JSON parse)")
+    base = {"value": value, "unit": "token-blocks/s", "cores": threads, "kind": kind, "sample": sample + "; " + what}
+    return value, n, base, what
+
+
+def main_window_reference(args):
+    """CPU arm of --workload c4."""
+    threads = os.cpu_count() or 1
+    value, n, base, what = window_cpu_baseline(args.n_requests or 65536, threads)
     print(json.dumps({"impl": "reference", "metric": "prefix_and_window_match_token_blocks_per_s", "value": value,
                       "unit": "token-blocks/s", "n_gpus": args.gpus, "steps": n, "warmup": 0, "higher_is_better": True,
                       "dtype": "int64", "data": "synthetic",
                       "config": {"workload": what + " on a bounded sample"},
-                      "cpu_baseline": {"value": value, "unit": "token-blocks/s", "cores": threads, "kind": kind,
-                                       "sample": sample},
+                      "cpu_baseline": base,
                       "e2e": {"value": value, "unit": "token-blocks/s", "h2d_bytes_per_step": 0,
                               "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
 
@@ -2317,6 +2325,8 @@ def main_b200(args, cfg, ctx):
         wm = run_window(args, ctx)
         if wm is not None:
             line["window_match"] = extra_of(wm)
+            if ctx.world == 1 and not args.no_cpu:
+                line["window_match"]["cpu_baseline"] = window_cpu_baseline(65536, os.cpu_count() or 1, budget_s=6.0)[2]
         seconds["window_match"] = round(time.perf_counter() - t0, 1)
         del wm
         freed()
