@@ -141,6 +141,24 @@ class RefSearcher:
             raise RuntimeError("BatchGetBestLocation / BatchGetLocation returned %d" % rc)
         return servable, nonempty
 
+    def filter_write(self, keys, weights=None):
+        """CacheManager::FilterWriteCache (kv_cache_manager/manager/cache_manager.cc:589-635) put together from what
+        the reference's own BatchGetLocation and policy object say per key: ("offset", first missing, new keys) when
+        the keys that exist for a write form a prefix, else ("vector", non-empty flags, keys with an empty map)."""
+        k = np.ascontiguousarray(keys, dtype=np.int64)
+        exists, nonempty = np.zeros(len(k), dtype=np.uint8), np.zeros(len(k), dtype=np.uint8)
+        w = _w(weights)
+        rc = lib().kvcm_ref_searcher_write_view(self._h, _p(k, ctypes.c_int64), ctypes.c_int64(len(k)),
+                                                _p(w, ctypes.c_uint32), _p(exists, ctypes.c_uint8),
+                                                _p(nonempty, ctypes.c_uint8))
+        if rc != 0:
+            raise RuntimeError("BatchGetLocation returned %d" % rc)
+        exists, nonempty = exists.astype(bool), nonempty.astype(bool)
+        first = int(np.argmin(exists)) if not exists.all() else len(k)
+        if not exists[first:].any():
+            return "offset", first, len(k) - first
+        return "vector", nonempty, int((~nonempty).sum())
+
     def status(self, op, keys, types, expected=0, new_status=0):
         """One task per key (OP_UPDATE / OP_CAS / OP_CAD / OP_DELETE) on the key's location of storage type types[i]:
         (the call's ErrorCode, the ErrorCode of every task)."""

@@ -253,6 +253,24 @@ int32_t kvcm_ref_searcher_batch_get(void *handle, const int64_t *keys, int64_t n
     return 0;
 }
 
+// What CacheManager::FilterWriteCache looks at per key (kv_cache_manager/manager/cache_manager.cc:589-635; the
+// CacheManager itself needs the RPC stack and is not compiled here): the location map BatchGetLocation returns, and
+// whether the reference's own policy object says it exists for a write.
+int32_t kvcm_ref_searcher_write_view(void *handle, const int64_t *keys, int64_t n, const uint32_t *weights,
+                                     uint8_t *exists_for_write_out, uint8_t *nonempty_out) {
+    auto *h = static_cast<RefSearcher *>(handle);
+    auto policy = PolicyFor(weights);
+    MetaSearcher::KeyVector k(keys, keys + n);
+    std::vector<CacheLocationMap> maps;
+    ErrorCode ec = h->searcher->BatchGetLocation(h->context.get(), k, BlockMask(static_cast<BlockMaskOffset>(0)), maps);
+    if (ec != EC_OK || static_cast<int64_t>(maps.size()) != n) return ec != EC_OK ? static_cast<int32_t>(ec) : -1;
+    for (int64_t i = 0; i < n; ++i) {
+        exists_for_write_out[i] = policy->ExistsForWrite(maps[static_cast<size_t>(i)]) ? 1 : 0;
+        nonempty_out[i] = maps[static_cast<size_t>(i)].empty() ? 0 : 1;
+    }
+    return 0;
+}
+
 // One task per key on the key's location of storage type types[i]: op 0 BatchUpdateLocationStatus (to
 // new_status[i]), 1 BatchCASLocationStatus (expected[i] -> new_status[i]), 2 BatchCADLocationStatus (delete when
 // expected[i]), 3 BatchDeleteLocation.  results[i] = the ErrorCode of the task.  Returns the call's own ErrorCode.

@@ -42,6 +42,7 @@ def test_matchers_on_random_location_maps():
     universe, locs, r, ox = _random_world(rng, 6000)
     serving = [k for k in locs if any(s == oracle.CLS_SERVING for s, _ in locs[k])]
     hits = windows = 0
+    forms = set()
     for weights in (None, (1, 3, 0, 3, 5), (0, 0, 0, 0, 7)):
         ow = oracle.DEFAULT_WEIGHTS if weights is None else weights
         for _ in range(150):
@@ -64,7 +65,11 @@ def test_matchers_on_random_location_maps():
             servable, nonempty = r.batch_get(q, weights)
             flags = ox.batch_get(q, ow)
             assert np.array_equal(servable, flags & 1) and np.array_equal(nonempty, (flags >> 2) & 1)
-    assert hits > 300 and windows > 100
+            # what StartWriteCache would still have to write (FilterWriteCache over the reference's own policy object)
+            want, got = r.filter_write(q, weights), ox.filter_write(q, weights=ow)
+            forms.add(want[0])
+            assert want[0] == got[0] and np.array_equal(want[1], got[1]) and want[2] == got[2], (weights, want, got)
+    assert hits > 300 and windows > 100 and forms == {"offset", "vector"}
 
 
 def test_status_transitions_on_random_task_batches():
