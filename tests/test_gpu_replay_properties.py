@@ -76,3 +76,27 @@ def test_single_instance_sweeps(case):
             timestamps=case["timestamps"])
         for name, a, b in zip(NAMES, want, r[:4]):
             assert np.array_equal(a, b.cpu().numpy()[c]), (policy, name, q)
+
+
+@settings(max_examples=150, deadline=None, suppress_health_check=list(HealthCheck))
+@given(replay_cases())
+def test_groups_against_the_compiled_reference_itself(case):
+    """The same draws against the reference's own Optimizer (compiled from its sources, where that library has
+    travelled with the build), with no oracle in between."""
+    from oracle import ref_optimizer as ref
+    if not ref.available():
+        pytest.skip("oracle/_ref/libkvcm_ref_optimizer.so not built")
+    k = len(case["policies"])
+    want = ref.RefOptimizer([dict(quota_capacity=case["quota"],
+                                  instances=[(str(j), p, case["sample_rates"][j])
+                                             for j, p in enumerate(case["policies"])])],
+                            evict_batch=case["evict_batch"], mode=case["mode"]).run(
+        case["keys"], case["key_off"], case["types"], case["instance"], case["mask_off"], case["mask_bits"],
+        case["timestamps"])
+    r = RunTracesLruGroup(_dev(case["keys"]), _dev(case["key_off"]), _dev(case["types"]), _dev(case["instance"]), k,
+                          [case["quota"]], _dev(case["mask_off"]), evict_batch=case["evict_batch"], mode=case["mode"],
+                          mask_bits=_dev(case["mask_bits"]), instance_records=True, policy=case["policies"],
+                          timestamps=_dev(case["timestamps"]), sample_rate=case["sample_rates"])
+    torch.cuda.synchronize()
+    for name, a, b in zip(NAMES, want, (r[0], r[1], r[2], r[3], r[6])):
+        assert np.array_equal(a, b.cpu().numpy()[0]), name
