@@ -46,19 +46,19 @@ def _group_parity(case):
         assert np.array_equal(want[4], final[c])
 
 
-@settings(max_examples=250, deadline=None, suppress_health_check=list(HealthCheck))
+@settings(max_examples=250, deadline=None, derandomize=True, suppress_health_check=list(HealthCheck))
 @given(replay_cases())
 def test_groups_of_any_mix_of_policies(case):
     _group_parity(case)
 
 
-@settings(max_examples=120, deadline=None, suppress_health_check=list(HealthCheck))
+@settings(max_examples=120, deadline=None, derandomize=True, suppress_health_check=list(HealthCheck))
 @given(replay_cases(policies=("leaf_aware_lru", "lru"), max_traces=40, max_blocks=9))
 def test_tree_kernel_on_longer_traces(case):
     _group_parity(case)
 
 
-@settings(max_examples=150, deadline=None, suppress_health_check=list(HealthCheck))
+@settings(max_examples=150, deadline=None, derandomize=True, suppress_health_check=list(HealthCheck))
 @given(replay_cases(max_instances=1, max_traces=30))
 def test_single_instance_sweeps(case):
     policy = case["policies"][0]
@@ -78,7 +78,7 @@ def test_single_instance_sweeps(case):
             assert np.array_equal(a, b.cpu().numpy()[c]), (policy, name, q)
 
 
-@settings(max_examples=150, deadline=None, suppress_health_check=list(HealthCheck))
+@settings(max_examples=150, deadline=None, derandomize=True, suppress_health_check=list(HealthCheck))
 @given(replay_cases())
 def test_groups_against_the_compiled_reference_itself(case):
     """The same draws against the reference's own Optimizer (compiled from its sources, where that library has

@@ -152,7 +152,7 @@ def test_small_universes_drawn_by_hypothesis():
     states = [None, [(S, 4)], [(W, 4)], [(oracle.CLS_NOT_FOUND, 1)], [(S, 2)], [(oracle.CLS_NOT_FOUND, 4)], []]
     universe = np.array([5, 6, 7, 8, 9, 10, -(1 << 63), -(1 << 63) + 1], dtype=np.int64)
 
-    @settings(max_examples=200, deadline=None, suppress_health_check=list(HealthCheck))
+    @settings(max_examples=200, deadline=None, derandomize=True, suppress_health_check=list(HealthCheck))
     @given(st.lists(st.integers(0, len(states) - 1), min_size=8, max_size=8),
            st.lists(st.lists(st.integers(0, 7), min_size=0, max_size=6, unique=True), min_size=1, max_size=8),
            st.integers(0, 1 << 30))
