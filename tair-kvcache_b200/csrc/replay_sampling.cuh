@@ -30,6 +30,52 @@ constexpr uint32_t kMaxBatch = KVCM_B200_RANDOM_LRU_MAX_BATCH;    // blocks evic
 constexpr uint32_t kNotCached = 0xFFFFFFFFu;
 constexpr uint64_t kSamplingSeed = 0x12345678ABCDEF01ull;  // random_lru.h:20; every policy object starts from it
 
+// The policy's generator (FastRand, random_lru.cc:121-131) is xorshift64: three shift-and-xor steps, a linear map of
+// the 64 state bits over GF(2).  So is its 32nd power, which lets every lane of a warp produce every 32nd draw by
+// itself: the first 32 draws are made in sequence, then lane l jumps from draw l to draw l + 32, l + 64, ...  The
+// jump is the matrix of that power applied to the state, stored as eight tables of 256 entries (one per state byte:
+// the xor of the columns its set bits select), worked out by the compiler.
+__host__ __device__ constexpr uint64_t XorShiftStep(uint64_t x) {
+    x ^= x << 13;
+    x ^= x >> 7;
+    x ^= x << 17;
+    return x;
+}
+
+struct JumpTables {
+    uint64_t of_byte[8][256];
+};
+
+constexpr JumpTables MakeJump32() {
+    JumpTables t{};
+    uint64_t column[64] = {};
+    for (int bit = 0; bit < 64; ++bit) {
+        uint64_t x = 1ull << bit;
+        for (int step = 0; step < 32; ++step) x = XorShiftStep(x);
+        column[bit] = x;
+    }
+    for (int byte = 0; byte < 8; ++byte) {
+        for (int value = 0; value < 256; ++value) {
+            uint64_t x = 0;
+            for (int bit = 0; bit < 8; ++bit) {
+                if ((value >> bit) & 1) x ^= column[8 * byte + bit];
+            }
+            t.of_byte[byte][value] = x;
+        }
+    }
+    return t;
+}
+
+constexpr JumpTables kHostJump32 = MakeJump32();
+__device__ const JumpTables kJump32 = kHostJump32;
+
+__device__ __forceinline__ uint64_t Jump32(uint64_t x) {
+    uint64_t r = 0;
+#pragma unroll
+    for (int byte = 0; byte < 8; ++byte) r ^= kJump32.of_byte[byte][(x >> (8 * byte)) & 255u];
+    return r;
+}
+
 // One sampled block: its last access time and its index in the block vector, moved together - one 16-byte shared
 // memory access each way.
 struct __align__(16) SampleEntry {
@@ -178,17 +224,26 @@ __device__ __forceinline__ uint32_t SamplingEvictRound(SamplingScratch &sc, uint
     const uint32_t want = count < held ? static_cast<uint32_t>(count) : n_blocks;  // total_to_evict
     const uint32_t n_sample = sampling_size < n_blocks ? sampling_size : n_blocks;
     const uint32_t k = want < n_sample ? want : n_sample;
-    // the draws, in sequence (lane 0), then their modulo and the sampled blocks' times (all lanes)
+    // the draws: the first 32 in sequence (lane 0), the rest by every lane jumping 32 draws at a time; then their
+    // modulo and the sampled blocks' times (all lanes)
     if (lane == 0) {
         uint64_t x = *rng;
-        for (uint32_t i = 0; i < n_sample; ++i) {
-            x ^= x << 13;
-            x ^= x >> 7;
-            x ^= x << 17;
+        const uint32_t head = n_sample < 32u ? n_sample : 32u;
+        for (uint32_t i = 0; i < head; ++i) {
+            x = XorShiftStep(x);
             sc.sample[i].t = static_cast<int64_t>(x);
         }
-        *rng = x;
     }
+    __syncwarp();
+    {
+        uint64_t x = lane < n_sample ? static_cast<uint64_t>(sc.sample[lane].t) : 0ull;
+        for (uint32_t i = lane + 32u; i < n_sample; i += 32u) {
+            x = Jump32(x);
+            sc.sample[i].t = static_cast<int64_t>(x);
+        }
+    }
+    __syncwarp();
+    if (lane == 0) *rng = static_cast<uint64_t>(sc.sample[n_sample - 1].t);  // the state after the last draw
     __syncwarp();
     for (uint32_t i0 = lane; i0 < n_sample; i0 += 128) {  // four sampled times in flight per lane
         uint32_t at[4];
