@@ -211,7 +211,9 @@ struct SamplingScratch {
     int64_t tail_ts[kMaxBatch];      // ts / blk of the last entries of the vector, [j] = index size - 1 - j
     uint32_t v_id[kMaxBatch], v_at[kMaxBatch];  // the round's victims: block id, current index
     uint32_t tail_blk[kMaxBatch];
+    uint16_t tail_victim[kMaxBatch];  // which victim the block at that tail position is (kNoVictim: none)
 };
+constexpr uint16_t kNoVictim = 0xFFFFu;
 
 // RandomLruEvictionPolicy::EvictBlocks(count) (random_lru.cc:38-103) on a block vector of `held` entries; all lanes,
 // returns how many blocks went (the caller keeps the vector's length).  *rng is the generator's state, in shared
@@ -272,43 +274,56 @@ __device__ __forceinline__ uint32_t SamplingEvictRound(SamplingScratch &sc, uint
     for (uint32_t i = lane; i < n_tail; i += 32) {
         sc.tail_blk[i] = blk[n_blocks - 1 - i];
         sc.tail_ts[i] = ts[n_blocks - 1 - i];
+        sc.tail_victim[i] = kNoVictim;
     }
     __syncwarp();
+    // A block sampled twice is removed once: every later sample of an index is struck out before the removals start
+    // (the reference finds it gone when its turn comes).  Then, for the last n_tail positions of the vector - the only
+    // ones a removal ever moves a block away from - which victim sits there.
+    for (uint32_t v = lane; v < k; v += 32) {
+        const uint32_t at = sc.sample[v].idx;
+        bool again = false;
+        for (uint32_t u = 0; u < v && !again; ++u) again = sc.sample[u].idx == at;
+        if (again) sc.v_at[v] = kNotCached;
+    }
+    __syncwarp();
+    for (uint32_t v = lane; v < k; v += 32) {
+        const uint32_t at = sc.v_at[v];
+        if (at != kNotCached && n_blocks - 1 - at < n_tail) sc.tail_victim[n_blocks - 1 - at] = static_cast<uint16_t>(v);
+    }
+    __syncwarp();
+    // The removals, swap-and-pop in the victims' order (random_lru.cc:84-103): one lane, no look at the other
+    // victims - when the block that sits last is itself a later victim, the table above says so and its index follows.
     uint32_t evicted = 0;
-    uint32_t size = n_blocks;
-    for (uint32_t i = 0; i < k && evicted < want; ++i) {
-        const uint32_t at = sc.v_at[i];
-        if (at == kNotCached) continue;  // sampled twice: removed already
-        const uint32_t id = sc.v_id[i];
-        const uint32_t last = size - 1;
-        const uint32_t moved = sc.tail_blk[n_blocks - 1 - last];  // the block that sits last now
-        const int64_t moved_t = sc.tail_ts[n_blocks - 1 - last];
-        if (lane == 0) {
+    if (lane == 0) {
+        uint32_t size = n_blocks;
+        for (uint32_t i = 0; i < k && evicted < want; ++i) {
+            const uint32_t at = sc.v_at[i];
+            if (at == kNotCached) continue;  // sampled twice: removed already
+            const uint32_t id = sc.v_id[i];
+            const uint32_t last = size - 1;
             if (at != last) {
+                const uint32_t from_end = n_blocks - 1 - last;
+                const uint32_t moved = sc.tail_blk[from_end];  // the block that sits last now
+                const int64_t moved_t = sc.tail_ts[from_end];
+                const uint16_t rider = sc.tail_victim[from_end];  // the later victim that block is, if any
                 blk[at] = moved;
                 ts[at] = moved_t;
                 pos[moved] = at;
+                if (rider != kNoVictim) sc.v_at[rider] = at;
                 if (n_blocks - 1 - at < n_tail) {  // the staged tail follows
                     sc.tail_blk[n_blocks - 1 - at] = moved;
                     sc.tail_ts[n_blocks - 1 - at] = moved_t;
+                    sc.tail_victim[n_blocks - 1 - at] = rider;
                 }
             }
             pos[id] = kNotCached;
+            --size;
+            ++evicted;
         }
-        __syncwarp();
-        // later victims: further samples of this block are gone; the moved block has a new index
-        for (uint32_t v = i + 1 + lane; v < k; v += 32) {
-            if (sc.v_at[v] == kNotCached) continue;
-            if (sc.v_id[v] == id) {
-                sc.v_at[v] = kNotCached;
-            } else if (at != last && sc.v_id[v] == moved) {
-                sc.v_at[v] = at;
-            }
-        }
-        __syncwarp();
-        --size;
-        ++evicted;
     }
+    evicted = __shfl_sync(0xffffffffu, evicted, 0);
+    __syncwarp();
     return evicted;
 }
 
