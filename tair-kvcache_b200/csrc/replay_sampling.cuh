@@ -174,6 +174,136 @@ __host__ __device__ __forceinline__ void PartialSortByTime(SampleEntry *s, uint3
 }
 
 #ifdef __CUDACC__
+// ---- the same heap steps, shared by the lanes of a warp (heaps of up to kWarpHeapMax entries).
+// What makes a sift slow in one lane is that every level waits for the level above: load two children, compare,
+// store, next address.  Which child is the larger one does not depend on the value being sifted, so that answer is
+// kept, for every inner node, as one bit of a 64-bit word all lanes hold (`choice`: 1 = the left child, i.e. the
+// right one is smaller).  A sift then is: (1) every lane follows the bits from the hole to a leaf - registers only -
+// and lane l keeps the l-th position of that path; (2) lane l loads the entry one step further down; a ballot finds
+// where the new value stops on its way back up (the standard library's adjust-heap lets the hole sink to a leaf and
+// pushes the value up from there, passing entries that are smaller); (3) the entries above that point move up one
+// position, the value goes in, and the positions below stay as they were; (4) the bits of the nodes whose children
+// changed are put right.  The array ends up exactly as the one-lane routines above leave it.
+constexpr uint32_t kWarpHeapMax = 128;
+
+struct WarpHeap {
+    SampleEntry *s;
+    uint64_t choice;
+    uint32_t lane;
+
+    __device__ __forceinline__ bool LeftIsLarger(uint32_t node) const { return s[2 * node + 2].t < s[2 * node + 1].t; }
+
+    // the bits of all inner nodes of a heap of `len` entries, from the array as it is
+    __device__ __forceinline__ void InitChoice(uint32_t len) {
+        uint32_t lo = 0, hi = 0;
+        for (uint32_t node = lane; 2 * node + 2 < len; node += 32) {
+            if (LeftIsLarger(node)) {
+                if (node < 32) {
+                    lo |= 1u << node;
+                } else {
+                    hi |= 1u << (node - 32);
+                }
+            }
+        }
+        lo = __reduce_or_sync(0xffffffffu, lo);
+        hi = __reduce_or_sync(0xffffffffu, hi);
+        choice = static_cast<uint64_t>(lo) | (static_cast<uint64_t>(hi) << 32);
+    }
+
+    // AdjustHeap(s, hole, len, value) above, all lanes; value is the same in all lanes
+    __device__ __forceinline__ void Adjust(uint32_t hole, uint32_t len, int64_t v_t, uint32_t v_idx) {
+        const uint32_t full = 0xffffffffu;
+        // (1) the path: p_0 = hole, then the larger child each time; lane l keeps p_l, depth = index of the last
+        uint32_t mine = hole, child = hole, depth = 0;
+        while (child < (len - 1) / 2) {
+            child = 2 * child + 2 - static_cast<uint32_t>((choice >> child) & 1ull);
+            ++depth;
+            if (depth == lane) mine = child;
+        }
+        if ((len & 1u) == 0 && child == (len - 2) / 2) {  // a node with a left child only
+            child = 2 * child + 1;
+            ++depth;
+            if (depth == lane) mine = child;
+        }
+        // (2) what sits one step further down, and where the value stops on its way back up
+        const uint32_t below = __shfl_down_sync(full, mine, 1);
+        SampleEntry e;
+        e.t = 0, e.idx = 0, e.pad = 0;
+        if (lane < depth) e = LoadEntry(s, below);
+        const uint32_t stays = __ballot_sync(full, lane < depth && !(e.t < v_t));  // entries the value does not pass
+        const uint32_t stop = stays == 0 ? 0u : 32u - static_cast<uint32_t>(__clz(stays));  // the value ends at p_stop
+        __syncwarp();
+        // (3) entries above the stop move up one position; the value goes in
+        if (lane < stop) {
+            StoreEntry(s, mine, e);
+        } else if (lane == stop) {
+            SampleEntry v;
+            v.t = v_t, v.idx = v_idx, v.pad = 0;
+            StoreEntry(s, mine, v);
+        }
+        __syncwarp();
+        // (4) the bits of the nodes whose children changed: p_0 .. p_{stop-1}, and the parent of p_0
+        uint32_t node = 0xFFFFFFFFu;
+        if (lane < stop) {
+            node = mine;
+        } else if (lane == 31 && hole > 0) {
+            node = (hole - 1) / 2;
+        }
+        uint32_t set_lo = 0, set_hi = 0, clr_lo = 0, clr_hi = 0;
+        if (node != 0xFFFFFFFFu && 2 * node + 2 < len) {
+            const bool left = LeftIsLarger(node);
+            if (node < 32) {
+                clr_lo = 1u << node;
+                set_lo = left ? clr_lo : 0u;
+            } else {
+                clr_hi = 1u << (node - 32);
+                set_hi = left ? clr_hi : 0u;
+            }
+        }
+        set_lo = __reduce_or_sync(full, set_lo);
+        set_hi = __reduce_or_sync(full, set_hi);
+        clr_lo = __reduce_or_sync(full, clr_lo);
+        clr_hi = __reduce_or_sync(full, clr_hi);
+        const uint64_t clr = static_cast<uint64_t>(clr_lo) | (static_cast<uint64_t>(clr_hi) << 32);
+        const uint64_t set = static_cast<uint64_t>(set_lo) | (static_cast<uint64_t>(set_hi) << 32);
+        choice = (choice & ~clr) | set;
+    }
+
+    // the value at position i, read by lane 0 and handed to all lanes
+    __device__ __forceinline__ void Fetch(uint32_t i, int64_t *t, uint32_t *idx) const {
+        const SampleEntry e = LoadEntry(s, i);  // every lane reads the same entry: a broadcast
+        *t = e.t;
+        *idx = e.idx;
+    }
+};
+
+// Heap-select with shared sifts: the heap over s[0, k) is made already; every sample of s[k, n) that is older than
+// the heap's top takes its place, in order.  (Measured: a shared sift costs about as much as a one-lane sift of the
+// sort-heap phase, where the value stays near the bottom, and clearly less than one of this phase, where the value
+// climbs back up several levels - so make-heap and sort-heap keep the one-lane routines.)
+__device__ __forceinline__ void HeapSelectShared(SampleEntry *s, uint32_t k, uint32_t n, uint32_t lane) {
+    WarpHeap heap{s, 0ull, lane};
+    int64_t v_t;
+    uint32_t v_idx;
+    heap.InitChoice(k);
+    for (uint32_t base = k; base < n; base += 32) {
+        const uint32_t i = base + lane;
+        const int64_t mine = i < n ? s[i].t : 0;
+        uint32_t below = __ballot_sync(0xffffffffu, i < n && mine < s[0].t);
+        while (below != 0) {
+            const uint32_t j = base + static_cast<uint32_t>(__ffs(below)) - 1u;
+            below &= below - 1u;
+            heap.Fetch(j, &v_t, &v_idx);
+            if (!(v_t < s[0].t)) continue;  // the top has got older meanwhile
+            __syncwarp();
+            if (lane == 0) StoreEntry(s, j, LoadEntry(s, 0));
+            __syncwarp();
+            heap.Adjust(0, k, v_t, v_idx);
+        }
+    }
+    __syncwarp();
+}
+
 // The same for a warp: the heap steps stay lane 0's, in the algorithm's order, but the search for the samples
 // that are older than the heap's top - most are not - is a ballot over 32 samples at a time.  The top only gets
 // older, so a sample that fails the test once is out for good; lane 0 visits the ones that passed in their order
@@ -182,6 +312,12 @@ __device__ __forceinline__ void PartialSortByTimeWarp(SampleEntry *s, uint32_t k
     if (k == 0) return;
     if (lane == 0) MakeHeap(s, k);
     __syncwarp();
+    if (k >= 32 && k <= kWarpHeapMax) {  // deep enough for the shared sift to pay, small enough for its word of bits
+        HeapSelectShared(s, k, n, lane);
+        if (lane == 0) SortHeap(s, k);
+        __syncwarp();
+        return;
+    }
     for (uint32_t base = k; base < n; base += 32) {
         const uint32_t i = base + lane;
         const int64_t mine = i < n ? s[i].t : 0;
