@@ -76,6 +76,26 @@ def test_quota_sweep_against_sequential_oracle(rw_separation, precise, batch, ra
     assert not np.array_equal(lru[0], got[0][3])
 
 
+@pytest.mark.parametrize("batch,rate", [(32, 0.25), (33, 0.1), (64, 0.5), (100, 0.05), (127, 0.1), (128, 0.25),
+                                        (129, 0.1), (300, 0.2)])
+def test_batches_around_the_shared_sift_s_limits(batch, rate):
+    """Heaps of 32 to 128 samples take the sift that the warp shares (heap-select phase), smaller and larger ones the
+    one-lane routines: the same victims either way, with timestamps that repeat (every block of a trace shares one,
+    and neighbouring traces do too), so that the order std::partial_sort leaves equal times in decides who goes."""
+    rng = np.random.default_rng(900 + batch)
+    keys, off, types, mask, ts = _workload(rng, 1200, False, max_blocks=120)
+    n_keys = len(np.unique(keys))
+    quotas = [batch + 3, n_keys // 20, n_keys // 5, n_keys // 2]
+    for precise in (False, True):
+        got = _gpu(keys, off, types, quotas, mask, ts, evict_batch=batch, precise=precise, sample_rate=rate)
+        for c, q in enumerate(quotas):
+            want = oracle.LruReplay(q, evict_batch=batch, precise=precise, policy=POLICY, sample_rate=rate).run(
+                keys, off, types, mask, timestamps=ts)
+            for name, a, b in zip(("ext", "int", "written", "cached"), want, got):
+                assert np.array_equal(a, b[c]), (name, q, precise)
+        assert got[2][0].sum() > 20 * batch  # many rounds of evictions at the smallest quota
+
+
 def test_trace_number_as_time_many_configurations_and_workspace_reuse():
     rng = np.random.default_rng(177)
     keys, off, types, mask, _ = _workload(rng, 300, True, max_blocks=200)
