@@ -110,3 +110,37 @@ def test_larger_trace_files_against_the_compiled_reference(tmp_path, trace_type)
         files[who] = {p.name: p.read_text() for p in sorted(out.iterdir())}
     assert sum(len(t.splitlines()) for t in files["reference"].values()) > 1500
     compare_with_reference_files(dict(trace_type=trace_type, files=files["reference"]), str(tmp_path / "gpu"))
+
+
+def test_large_eviction_batches_against_the_compiled_reference():
+    """Batches of 32 to 128 blocks per round (the fixtures above use up to 8): the sizes at which the sampling
+    policy's heap-select runs its warp-shared sift, in groups of up to three instances that mix the policies."""
+    from oracle import ref_optimizer as ref
+    if not ref.available():
+        pytest.skip("oracle/_ref/libkvcm_ref_optimizer.so not built")
+    from test_gpu_replay_random_lru import _workload
+    compared = 0
+    for seed in range(8):
+        rng = np.random.default_rng(5000 + seed)
+        keys, off, types, mask, ts = _workload(rng, 700, bool(seed % 2), max_blocks=100)
+        k = int(rng.integers(1, 4))
+        policies = ["random_lru"] + [str(rng.choice(["random_lru", "lru", "leaf_aware_lru"])) for _ in range(k - 1)]
+        inst = rng.integers(0, k, size=len(types)).astype(np.int32)
+        batch = int(rng.choice([32, 48, 64, 100, 128]))
+        rates = [float(x) for x in rng.choice([0.1, 0.25, 0.5], size=k)]
+        mode = int(rng.integers(1, 4))
+        n_keys = len(np.unique(keys))
+        quotas = [batch + 5, n_keys // 10, n_keys // 3]
+        r = RunTracesLruGroup(_dev(keys, np.int64), _dev(off, np.int64), _dev(types, np.uint8), _dev(inst, np.int32), k,
+                              quotas, _dev(mask, np.int64), evict_batch=batch, mode=mode, instance_records=True,
+                              policy=policies, timestamps=_dev(ts, np.int64), sample_rate=rates)
+        torch.cuda.synchronize()
+        got = [t.cpu().numpy() for t in (r[0], r[1], r[2], r[3], r[6])]
+        for c, quota in enumerate(quotas):
+            want = ref.RefOptimizer([dict(quota_capacity=quota,
+                                          instances=[(str(j), p, rates[j]) for j, p in enumerate(policies)])],
+                                    evict_batch=batch, mode=mode).run(keys, off, types, inst, mask, None, ts)
+            for name, a, b in zip(NAMES, want, got):
+                assert np.array_equal(a, b[c]), (seed, policies, batch, mode, quota, name)
+            compared += 1
+    assert compared == 24
