@@ -472,7 +472,11 @@ def run_prefix_cpu_reference(data, threads, budget_s=12.0):
 def prefix_cpu_baseline(data, threads):
     """cpu_baseline of the prefix-match configuration: the reference itself where its compiled searcher travelled
     with the build, else the oracle's restatement (which leaves out the reference's per-key JSON work)."""
-    ref = run_prefix_cpu_reference(data, threads)
+    try:
+        ref = run_prefix_cpu_reference(data, threads)
+    except (OSError, RuntimeError, AttributeError) as err:  # the library is there but does not load or run here
+        print("reference searcher not usable (%s): timing the restatement instead" % err, file=sys.stderr)
+        ref = None
     if ref is not None:
         value, n_rep, built_s = ref
         return {"value": value, "unit": "token-blocks/s", "cores": threads, "kind": "reference",
@@ -1381,23 +1385,29 @@ def window_cpu_baseline(n_requests_total, threads, budget_s=10.0):
     ox.put_uniform(keys0[:int(ko0[n_req // 8])])
     from oracle import ref_searcher
     t_total, n, kind = 0.0, 0, "port"
+    searcher = None
     if ref_searcher.available():
-        # the reference's own searcher compiled from its sources, its local meta backend in memory
+        try:
+            # the reference's own searcher compiled from its sources, its local meta backend in memory
+            index_keys = np.unique(np.concatenate([oracle.gen_key_vector(t, bs) for t in roots] +
+                                                  [keys0[:int(ko0[n_req // 8])]]))
+            searcher = ref_searcher.RefSearcher(max_keys=2 * len(index_keys), in_memory=True)
+            for a in range(0, len(index_keys), 20000):
+                searcher.add(index_keys[a:a + 20000], 4, oracle.CLS_SERVING)
+        except (OSError, RuntimeError, AttributeError) as err:  # there, but it does not load or run here
+            print("reference searcher not usable (%s): timing the restatement instead" % err, file=sys.stderr)
+            searcher = None
+    if searcher is not None:
         kind = "reference"
-        index_keys = np.unique(np.concatenate([oracle.gen_key_vector(t, bs) for t in roots] +
-                                              [keys0[:int(ko0[n_req // 8])]]))
-        searcher = ref_searcher.RefSearcher(max_keys=2 * len(index_keys), in_memory=True)
-        for a in range(0, len(index_keys), 20000):
-            searcher.add(index_keys[a:a + 20000], 4, oracle.CLS_SERVING)
         t64 = toks.astype(np.int64)
         while t_total < budget_s and n < 500:
             t0 = time.perf_counter()
             matched, base = searcher.window_match_batch(t64, off, bs, sw, threads=threads)
             t_total += time.perf_counter() - t0
             n += 1
-        # the sample's answers are the oracle's
-        assert np.array_equal(matched, ox.prefix_match_batch(keys0, ko0, threads=threads))
-        assert np.array_equal(base, ox.sw_match_batch(keys0, ko0, sw, threads=threads))
+        # the sample's answers are the oracle's (reported, not asserted: a timing run should end with its line)
+        agrees = bool(np.array_equal(matched, ox.prefix_match_batch(keys0, ko0, threads=threads)) and
+                      np.array_equal(base, ox.sw_match_batch(keys0, ko0, sw, threads=threads)))
     while kind == "port" and t_total < budget_s and n < 500:
         t0 = time.perf_counter()
         keys, ko = oracle.hash_blocks(toks, off, bs, threads=threads)
@@ -1412,6 +1422,8 @@ def window_cpu_baseline(n_requests_total, threads, budget_s=10.0):
             "its sources (local meta backend in memory)" if kind == "reference" else
             "CPU restatement (hash + prefix + sliding-window match, without the reference's per-key JSON parse)")
     base = {"value": value, "unit": "token-blocks/s", "cores": threads, "kind": kind, "sample": sample + "; " + what}
+    if kind == "reference":
+        base["reference_equals_oracle"] = agrees
     return value, n, base, what
 
 
