@@ -165,3 +165,25 @@ def test_partial_sort_restatement_matches_the_standard_library():
         assert np.array_equal(idx[:k].astype(np.uint64), want[:k]), (trial, n, k)
         assert np.array_equal(t[:k], times[want[:k].astype(np.int64)])
     assert _cabi.lib().kvcm_b200_selftest_partial_sort(None, None, 0, 0) == _cabi.KVCM_ER_INVALID_ADDRESS
+
+
+def test_workspace_sizes_of_the_write_batch_and_the_policy_group_need_no_device():
+    """Host arithmetic only: sizes grow with the batch, are 256-byte multiples, and bad arguments give -1."""
+    L = _cabi.lib()
+    small = L.kvcm_b200_start_write_workspace_bytes(1000, 10)
+    large = L.kvcm_b200_start_write_workspace_bytes(100000, 1000)
+    assert 0 < small < large and small % 256 == 0 and large % 256 == 0
+    assert L.kvcm_b200_start_write_workspace_bytes(0, 0) > 0
+    assert L.kvcm_b200_start_write_workspace_bytes(-1, 10) == -1
+    assert L.kvcm_b200_start_write_workspace_bytes(10, -1) == -1
+
+    size = L.kvcm_b200_replay_policy_group_workspace_bytes
+    plain = np.array([_cabi.POLICY_LRU, _cabi.POLICY_LEAF_AWARE_LRU, _cabi.POLICY_LEAF_AWARE_LRU], np.uint8)
+    mixed = np.array([_cabi.POLICY_LRU, _cabi.POLICY_LEAF_AWARE_LRU, _cabi.POLICY_RANDOM_LRU], np.uint8)
+    a = size(1000, 10, 4, plain.ctypes.data, 3)
+    b = size(1000, 10, 4, mixed.ctypes.data, 3)
+    assert 0 < a < b and a % 256 == 0 and b % 256 == 0  # a sampled instance adds its block and stamp vectors
+    assert size(1000, 10, 4, np.array([0, 9], np.uint8).ctypes.data, 2) == -1  # no such policy
+    assert size(-1, 10, 4, mixed.ctypes.data, 3) == -1
+    assert size(1000, 10, 4, None, 3) == a  # no policy bytes: no sampled instance
+    assert L.kvcm_b200_replay_leaf_lru_group_workspace_bytes(1000, 10, 4, 3) == a
